@@ -1,0 +1,411 @@
+#!/usr/bin/env python
+"""Benchmark of the fused row-reduction hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE.json configs[1]): softmax and LayerNorm (eps 1e-5, gamma 1,
+beta 0) over X of Julia shape 4096 x 65536 (65536 rows of 4096 contiguous
+elements), forward and autodiff backward, Float32 and BFloat16, X and the
+upstream gradient ~ N(0,1), synthetic and seeded.  One step = the eight fused
+kernels (4 operators x 2 element types) over the whole of X.
+
+value  = algorithmic bytes of a step / device time of a step, inputs resident
+         in HBM, summed over ranks (rows shard across GPUs with no exchange:
+         weak scaling, every rank folds its own 65536 rows).
+e2e    = the same through the plugin mirror with HOST buffers: every step
+         copies X and dY from pinned host memory and reads every result back.
+--impl reference times the CPU restatement of the reference's CPU path
+         (oracle/) on the host cores over a bounded sample of the rows.
+
+Prints one JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_REDUCE, ROWS = 4096, 65536
+SEED = 20261125 + 2
+METRIC, UNIT = "fused-kernel HBM GB/s", "GB/s"
+WORKLOAD = "softmax+layernorm fwd+bwd, X 4096x65536, f32 and bf16"
+# row-sized arrays each kernel reads + writes: the algorithmic traffic
+STREAMS = {"softmax_fwd": 2, "softmax_bwd": 3, "layernorm_fwd": 2, "layernorm_bwd": 3}
+CPU_SAMPLE_ROWS = 2048
+
+
+def algorithmic_bytes(op, rows, size):
+    extra = 0
+    if op == "softmax_fwd":
+        extra = rows * 4                      # the log-sum-exp saved for the backward
+    elif op == "layernorm_fwd":
+        extra = 2 * N_REDUCE * size           # gamma, beta
+    elif op == "layernorm_bwd":
+        extra = 3 * N_REDUCE * size           # gamma, dgamma, dbeta
+    return STREAMS[op] * N_REDUCE * rows * size + extra
+
+
+def step_bytes(rows):
+    return sum(algorithmic_bytes(op, rows, size) for op in STREAMS for size in (4, 2))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get("hbm_gbs", 6650.0), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.out = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.flush()
+        self.out.seek(0)
+        clocks, peak, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.out.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                peak = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        self.out.close()
+        os.unlink(self.out.name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": peak,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def physical_gpu_index(local):
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if visible:
+        ids = [v.strip() for v in visible.split(",") if v.strip()]
+        if local < len(ids) and ids[local].isdigit():
+            return int(ids[local])
+    return local
+
+
+# ------------------------------------------------------------------ GPU arm --
+
+class Workload:
+    """The eight launches of a step, built once through the plugin mirror
+    (Binding -> build -> launch), as Tempest builds a plan's kernels once and
+    replays them."""
+
+    def __init__(self, torch, pkg, rows):
+        I = pkg.implement
+        self.torch, self.I, self.rows = torch, I, rows
+        self.lib, self.target = I.B200Kernels(), I.Target()
+        self.resources = self.lib.resources(self.target)
+        gen = torch.Generator(device="cuda").manual_seed(SEED)
+        n = N_REDUCE
+        x32 = torch.randn(rows, n, device="cuda", generator=gen)
+        g32 = torch.randn(rows, n, device="cuda", generator=gen)
+        self.inputs = {"Float32": (x32, g32), "BFloat16": (x32.bfloat16(), g32.bfloat16())}
+        self.launches = []   # (name, eltype, launch, algorithmic bytes)
+        self.outputs = {}
+        for eltype, (x, g) in self.inputs.items():
+            size = x.element_size()
+            w = torch.ones(n, device="cuda", dtype=x.dtype)
+            b = torch.zeros(n, device="cuda", dtype=x.dtype)
+            y, dx, yl, dxl = (torch.empty_like(x) for _ in range(4))
+            lse = torch.empty(rows, device="cuda")
+            dw, db = torch.empty_like(w), torch.empty_like(w)
+            self.outputs[eltype] = (y, dx, yl, dxl, lse, dw, db)
+            col = lambda t, v: I.dense_columns(t, eltype, n, rows, v)  # noqa: E731
+            vec = lambda t, v: I.dense_vector(t, eltype, n, v)         # noqa: E731
+            plans = [
+                ("softmax_fwd", "softmax_columns_lse",
+                 {"x": col(x, 1), "y": col(y, 2), "lse": I.Strided("Float32", 0, (1, rows), (1, 1), lse, 3)}),
+                ("softmax_bwd", "softmax_columns_pullback", {"y": col(y, 2), "g": col(g, 4), "dx": col(dx, 5)}),
+                ("layernorm_fwd", "layernorm_bias", {"x": col(x, 1), "w": vec(w, 6), "b": vec(b, 7), "y": col(yl, 8)}),
+                ("layernorm_bwd", "layernorm_pullback",
+                 {"x": col(x, 1), "w": vec(w, 6), "g": col(g, 4), "dx": col(dxl, 9), "dw": vec(dw, 10),
+                  "db": vec(db, 11)}),
+            ]
+            for name, template, arrays in plans:
+                launch, _ = self.lib.build(self.target, I.Binding(template, {"n": n, "rows": rows}, arrays),
+                                           self.resources)
+                self.launches.append((name, eltype, launch, algorithmic_bytes(name, rows, size)))
+        self.kernels_per_step = len(self.launches) + 2   # + the two dgamma/dbeta merge launches
+
+    def step(self, events=None):
+        for i, (_, _, launch, _) in enumerate(self.launches):
+            if events is not None:
+                events[i][0].record()
+            launch()
+            if events is not None:
+                events[i][1].record()
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the backend has no CPU fallback)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = entry.load_package()
+    pkg.lib.load()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    rows = args.rows
+    wl = Workload(torch, pkg, rows)
+    nk = len(wl.launches)
+    for _ in range(max(args.warmup, 3)):
+        wl.step()
+    barrier()
+
+    sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
+    events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nk)]
+              for _ in range(args.steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for s in range(args.steps):
+        wl.step(events[s])
+    stop.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    total_ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * step_bytes(rows) / (ms_per_step * 1e-3) / 1e9
+
+    # per-kernel device time inside the timed region
+    kernels = {}
+    peak, peak_kind = measured_peaks()
+    for i, (name, eltype, _, nbytes) in enumerate(wl.launches):
+        ms = statistics.mean(events[s][i][0].elapsed_time(events[s][i][1]) for s in range(args.steps))
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        kernels[f"{name}_{'f32' if eltype == 'Float32' else 'bf16'}"] = {
+            "ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 4),
+            "frac_of_8TBps": round(gbs / 8000.0, 4), "algorithmic_bytes": nbytes}
+    dominant = max(kernels, key=lambda k: kernels[k]["ms"])
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": kernels[dominant]["GB/s"], "peak": peak,
+                "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback",
+                "unit": "GB/s", "frac": round(kernels[dominant]["GB/s"] / peak, 4),
+                "traffic": load_traffic(dominant)}
+
+    # end to end: host buffers in, host buffers out, through the same launches
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(torch, dist, wl, world, args)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(sample_rows=CPU_SAMPLE_ROWS, repeats=1)
+
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD if rows == ROWS else f"reduced case: {rows} rows of {N_REDUCE}",
+                   "rows_per_gpu": rows, "row_length": N_REDUCE,
+                   "element_types": ["f32", "bf16"], "sharding": f"rows x{world}, no collective",
+                   "l2": "inputs larger than L2 (each operand 0.5-1 GiB vs 126 MB)"},
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": wl.kernels_per_step * args.steps, "kernels": kernels,
+    }
+    print(json.dumps(line))
+
+
+def load_traffic(kernel):
+    """DRAM bytes per launch of `kernel` from the committed ncu summary, if there is one."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get(kernel)
+    return None
+
+
+def run_e2e(torch, dist, wl, world, args):
+    """Every step: X and dY from pinned host memory to the device, the eight
+    kernels, every result back to pinned host memory."""
+    rows, n = wl.rows, N_REDUCE
+    host_in, dev_in = {}, {}
+    for eltype, (x, g) in wl.inputs.items():
+        host_in[eltype] = (torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x),
+                           torch.empty(g.shape, dtype=g.dtype, pin_memory=True).copy_(g))
+        dev_in[eltype] = (x, g)
+    # results land in one pinned buffer per element type, one after another
+    host_out = {e: torch.empty(wl.inputs[e][0].shape, dtype=wl.inputs[e][0].dtype, pin_memory=True)
+                for e in wl.inputs}
+    host_small = torch.empty(rows, dtype=torch.float32, pin_memory=True)
+    host_vec = {e: torch.empty(n, dtype=wl.inputs[e][0].dtype, pin_memory=True) for e in wl.inputs}
+    h2d = sum(t.numel() * t.element_size() for pair in host_in.values() for t in pair)
+    d2h = 0
+    for eltype, outs in wl.outputs.items():
+        d2h += sum(t.numel() * t.element_size() for t in outs)
+
+    def one_step():
+        for eltype in wl.inputs:
+            dev_in[eltype][0].copy_(host_in[eltype][0], non_blocking=True)
+            dev_in[eltype][1].copy_(host_in[eltype][1], non_blocking=True)
+        wl.step()
+        for eltype, (y, dx, yl, dxl, lse, dw, db) in wl.outputs.items():
+            for t in (y, dx, yl, dxl):
+                host_out[eltype].copy_(t, non_blocking=True)
+            host_small.copy_(lse, non_blocking=True)
+            host_vec[eltype].copy_(dw, non_blocking=True)
+            host_vec[eltype].copy_(db, non_blocking=True)
+
+    steps = max(1, min(args.steps, args.e2e_steps))
+    one_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one_step()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return {"value": round(world * step_bytes(rows) / (ms * 1e-3) / 1e9, 2), "unit": UNIT,
+            "ms_per_step": round(ms, 3), "steps": steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+
+# ------------------------------------------------------------------ CPU arm --
+
+def cpu_step(O, arrays, threads):
+    """The same eight operators on the host, as the reference's CPU path runs
+    them (BFloat16 rounding every operation), over the sampled rows."""
+    for eltype in ("f32", "bf16"):
+        x, g, w, b = arrays[eltype]
+        y, _ = O.softmax_fwd(x, faithful=True, threads=threads)
+        O.softmax_bwd(y, g, faithful=True, threads=threads)
+        O.layernorm_fwd(x, w, b, faithful=True, threads=threads)
+        O.layernorm_bwd(x, w, g, threads=threads)
+
+
+def cpu_arrays(O, rows):
+    import numpy as np
+    x = O.normal((rows, N_REDUCE), SEED)
+    g = O.normal((rows, N_REDUCE), SEED + 1)
+    w, b = np.ones(N_REDUCE, np.float32), np.zeros(N_REDUCE, np.float32)
+    return {"f32": (x, g, w, b), "bf16": tuple(O.to_bf16(a) for a in (x, g, w, b))}
+
+
+def cpu_baseline(sample_rows, repeats):
+    import __graft_entry__ as entry
+    O = entry.load_oracle()
+    O.build()
+    threads = O.threads_available()
+    arrays = cpu_arrays(O, sample_rows)
+    cpu_step(O, cpu_arrays(O, 64), threads)   # touch the code once
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        cpu_step(O, arrays, threads)
+    dt = (time.perf_counter() - t0) / repeats
+    return {"value": round(step_bytes(sample_rows) / dt / 1e9, 4), "unit": UNIT, "cores": threads, "kind": "port",
+            "seconds_per_sample": round(dt, 3),
+            "sample": f"{sample_rows} of {ROWS} rows of the same workload (all 8 operators), rows over "
+                      f"{threads} host threads; the reference's CPU path itself runs on one thread "
+                      "(Julia is not installed on the box: C restatement in oracle/)"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import __graft_entry__ as entry
+    O = entry.load_oracle()
+    O.build()
+    threads = O.threads_available()
+    rows = CPU_SAMPLE_ROWS
+    arrays = cpu_arrays(O, rows)
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu_step(O, arrays, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(O, arrays, threads)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = round(step_bytes(rows) / dt / 1e9, 4)
+    sample = (f"each step = {rows} of {ROWS} rows of the same workload (all 8 operators); rows spread over "
+              f"{threads} host threads; the reference's CPU path itself is single-threaded")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "rows_per_step": rows, "row_length": N_REDUCE,
+                   "element_types": ["f32", "bf16"]},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--rows", type=int, default=ROWS, help="rows per GPU (smaller only for profiling captures)")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,127 @@
+/*
+ * tempest_b200.h -- C ABI of the B200 (sm_100a) kernel backend for Tempest.jl's
+ * fused-kernel hot path.
+ *
+ * Every entry point takes raw device pointers (a CUdeviceptr from Julia's
+ * `pointer(buffer)`), extents and strides in ELEMENTS, a dtype code and the
+ * CUDA stream (a cudaStream_t passed as void*) of the calling task.  Unless
+ * its comment says otherwise an entry point only enqueues work on that
+ * stream: it does not allocate, synchronise or keep state between calls, so a
+ * call can sit inside a stream capture (Tempest records its launches into a
+ * CUDA graph, ext/CUDAExt.jl:515-545).  Every entry point returns TB200_OK or
+ * a negative tb200_status; none of them aborts or traps.  A Tempest
+ * `build_claim`/`build` turns a non-zero status into a throw, which makes the
+ * cover fall to its next option (src/Compiler/cover/choose.jl:1014-1028).
+ *
+ * Layout convention: Julia arrays are dense column-major
+ * (src/Compiler/IR/layout.jl:22-29).  A Julia (n, rows) matrix folded over its
+ * first axis is passed as rows x n with the folded axis innermost; `ld` is the
+ * distance between consecutive rows in elements (ld == n when dense).
+ */
+#ifndef TEMPEST_B200_H
+#define TEMPEST_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum tb200_dtype {
+    TB200_F32 = 0,
+    TB200_BF16 = 1
+} tb200_dtype;
+
+typedef enum tb200_status {
+    TB200_OK = 0,
+    TB200_ERR_NULL = -1,        /* a required pointer is null */
+    TB200_ERR_SHAPE = -2,       /* an extent or stride is out of range */
+    TB200_ERR_DTYPE = -3,       /* unknown or unsupported element type */
+    TB200_ERR_ALIGN = -4,       /* a pointer is not aligned to its element type */
+    TB200_ERR_WORKSPACE = -5,   /* workspace missing or too small */
+    TB200_ERR_CUDA = -6,        /* a CUDA call failed; see tb200_last_cuda_error */
+    TB200_ERR_UNSUPPORTED = -7, /* valid request the library has no kernel for */
+    TB200_ERR_DEVICE = -8       /* the current device is not compute capability 10.x */
+} tb200_status;
+
+/* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
+int tb200_version(void);
+/* Text of a tb200_status. No reference counterpart. */
+const char *tb200_strerror(int status);
+/* Text of the CUDA error behind the calling thread's last TB200_ERR_CUDA. */
+const char *tb200_last_cuda_error(void);
+/* Number of SMs of the current device (the grid-sizing unit). Replaces the
+ * device query of ext/CUDAExt.jl:959 (RESIDENT_LANES per SM). */
+int tb200_sm_count(void);
+
+/* ---- fused row reductions (softmax, LayerNorm, forward and backward) -------
+ * These replace the kernels ext/cuTileExt/build.jl:138-286 (`unsplit_kernel`,
+ * resident and streamed sketches) and :560-705 (split + merge) generate for
+ * the reduction groups of softmax_columns / layernorm and their derivatives
+ * (test/fixtures/programs.jl:8, 13-17), and the floor kernels of
+ * src/Compiler/codegen/scalar.jl:200-256.
+ */
+
+/* Operators of tb200_rowop_workspace_bytes. */
+typedef enum tb200_rowop {
+    TB200_SOFTMAX_FWD = 0,
+    TB200_SOFTMAX_BWD = 1,
+    TB200_LAYERNORM_FWD = 2,
+    TB200_LAYERNORM_BWD = 3
+} tb200_rowop;
+
+/* Bytes of scratch the operator may need for rows x n elements of `dtype` on
+ * the current device; 0 for most shapes (a row of up to 16384 elements is
+ * folded in registers).  Non-zero for rows long enough to take the two-pass
+ * split schedule and for the LayerNorm backward's dgamma/dbeta partial sums.
+ * Replaces the partial-state workspace the reference sizes in
+ * ext/cuTileExt/build.jl:560-609 (`split_kernels`).  A `build_claim` calls it
+ * once and keeps the buffer alive with the launch (build.jl:957-961). */
+size_t tb200_rowop_workspace_bytes(int rowop, int64_t n, int64_t rows, int dtype);
+
+/* y[r, :] = exp(x[r, :] - lse_r), lse_r = logsumexp(x[r, :]).
+ * lse (optional) receives lse_r in Float32 (stat_dtype TB200_F32) or in the
+ * element type (TB200_BF16), the type the fold's value has in a Tempest plan
+ * (src/Compiler/IR/folds.jl:42-55).  y may alias x (the row is read whole
+ * before it is written: `in_place`, src/Compiler/Implement/Implement.jl:195-202)
+ * unless the shape takes the split schedule.  An empty row gives lse = -Inf
+ * (folds.jl:184).  workspace: tb200_rowop_workspace_bytes bytes, 16-byte
+ * aligned, or NULL when that is 0. */
+int tb200_softmax_fwd(const void *x, void *y, void *lse, int64_t n, int64_t rows, int64_t ld,
+                      int dtype, int stat_dtype, void *workspace, size_t workspace_bytes,
+                      void *stream);
+
+/* dx = y * (dy - sum(y * dy)) per row.  With lse == NULL `y_or_x` holds the
+ * forward's output y; otherwise it holds x and y = exp(x - lse) is recomputed
+ * (the planner's save-or-recompute choice, src/Compiler/plan/partition.jl).
+ * dx may alias dy or y_or_x under the resident schedule. */
+int tb200_softmax_bwd(const void *y_or_x, const void *lse, const void *dy, void *dx, int64_t n,
+                      int64_t rows, int64_t ld, int dtype, int stat_dtype, void *workspace,
+                      size_t workspace_bytes, void *stream);
+
+/* y = (x - mean) * rstd * gamma (+ beta); mean and variance of each row from
+ * one read of it (the reference's Relative{Square} fold,
+ * src/Compiler/IR/folds.jl:143, 166-182).  beta, mean, rstd may be NULL; mean
+ * and rstd are Float32 [rows]; gamma and beta have the element type. */
+int tb200_layernorm_fwd(const void *x, const void *gamma, const void *beta, void *y, float *mean,
+                        float *rstd, float eps, int64_t n, int64_t rows, int64_t ld, int dtype,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
+/* dx = rstd * (gh - mean(gh) - xh * mean(gh * xh)), gh = dy * gamma,
+ * xh = (x - mean) * rstd; dgamma[i] = sum over rows of dy * xh and
+ * dbeta[i] = sum over rows of dy, in the element type: per-block partial sums
+ * in the workspace merged by a second launch in a fixed order (the
+ * reference's partial folds and merge kernel, ext/cuTileExt/emit.jl:744-753,
+ * build.jl:654-696), so results repeat bit for bit.
+ * mean/rstd NULL: recomputed from x.  dgamma and dbeta both NULL: no workspace
+ * is needed.  Rows longer than 8192 elements: TB200_ERR_UNSUPPORTED. */
+int tb200_layernorm_bwd(const void *x, const void *gamma, const void *dy, const float *mean,
+                        const float *rstd, void *dx, void *dgamma, void *dbeta, float eps,
+                        int64_t n, int64_t rows, int64_t ld, int dtype, void *workspace,
+                        size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TEMPEST_B200_H */

@@ -1,0 +1,279 @@
+"""Python face of the CPU oracle (test infrastructure only).
+
+Loads oracle/liboracle.so (the C restatement of Tempest.jl's reference CPU
+path, built by `make -C oracle`) and wraps each function over numpy arrays.
+BFloat16 arrays are numpy uint16 holding the bit patterns.  Only the tests,
+the smoke check and the benchmark's CPU-baseline leg may import this module.
+
+Also here: the reference's deterministic test-data generator
+`data(dims...; scale) = 2 sin(scale * (1:n))` (test/setup.jl:33), the seeded
+N(0,1) generator every config's synthetic inputs come from, and Float64
+closed forms used as a second yardstick.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(HERE, "liboracle.so")
+
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+_u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
+_i64, _int, _flt, _void = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+
+def build(force=False):
+    srcs = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith(".c")]
+    if force or not os.path.exists(LIB) or any(os.path.getmtime(s) > os.path.getmtime(LIB) for s in srcs):
+        subprocess.run(["make", "-C", HERE, "-B", "liboracle.so"], check=True, capture_output=True)
+    return LIB
+
+
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(build())
+        _lib.oracle_sum_f32.restype = ctypes.c_float
+        _lib.oracle_sum_abs2_f32.restype = ctypes.c_float
+        _lib.oracle_sum_bf16.restype = ctypes.c_uint16
+        _lib.oracle_logsumexp_f32.restype = ctypes.c_float
+        _lib.oracle_readme_loss_grad.restype = ctypes.c_float
+        _lib.oracle_gelu_tanh.restype = ctypes.c_float
+        _lib.oracle_gelu_tanh.argtypes = [_flt]
+        _lib.oracle_gelu_tanh_grad.restype = ctypes.c_float
+        _lib.oracle_gelu_tanh_grad.argtypes = [_flt]
+    return _lib
+
+
+def threads_available():
+    """Host cores this process may use."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:  # pragma: no cover
+        return os.cpu_count() or 1
+
+
+def _over_rows(call, rows, threads):
+    """Runs call(r0, r1) over [0, rows): on this thread, or on `threads`
+    threads over disjoint row ranges (rows are independent items, and ctypes
+    releases the GIL, so results are the single-thread results)."""
+    if threads <= 1 or rows < 2:
+        call(0, rows)
+        return
+    from concurrent.futures import ThreadPoolExecutor
+    parts = min(threads * 4, rows)
+    edges = [rows * i // parts for i in range(parts + 1)]
+    with ThreadPoolExecutor(threads) as pool:
+        list(pool.map(lambda i: call(edges[i], edges[i + 1]), range(parts)))
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(_void)
+
+
+# ------------------------------------------------------------------ data ----
+
+def data(*dims, scale=1.0):
+    """test/setup.jl:33 -- 2 sin(scale * k), k = 1..prod(dims), as a Julia
+    column-major array of `dims`; returned as the numpy array whose C-order
+    memory is the Julia array's memory (axes reversed)."""
+    n = int(np.prod(dims))
+    flat = 2.0 * np.sin(scale * np.arange(1, n + 1, dtype=np.float64))
+    return flat.reshape(tuple(reversed(dims)))
+
+
+def normal(shape, seed, dtype=np.float32):
+    """Seeded N(0,1) draws (numpy Philox, counter-based): the synthetic inputs."""
+    g = np.random.Generator(np.random.Philox(seed))
+    return g.standard_normal(shape, dtype=np.float32).astype(dtype, copy=False)
+
+
+def to_bf16(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, np.uint16)
+    load().oracle_bf16_from_f32(_ptr(x), _ptr(out), _i64(x.size))
+    return out
+
+
+def from_bf16(h):
+    h = np.ascontiguousarray(h, dtype=np.uint16)
+    out = np.empty(h.shape, np.float32)
+    load().oracle_f32_from_bf16(_ptr(h), _ptr(out), _i64(h.size))
+    return out
+
+
+# ----------------------------------------------------------------- folds ----
+
+def sum_f32(x):
+    x = np.ascontiguousarray(x, np.float32)
+    return float(load().oracle_sum_f32(_ptr(x), _i64(x.size)))
+
+
+def sum_abs2_f32(x):
+    x = np.ascontiguousarray(x, np.float32)
+    return float(load().oracle_sum_abs2_f32(_ptr(x), _i64(x.size)))
+
+
+def sum_bf16(h):
+    h = np.ascontiguousarray(h, np.uint16)
+    return int(load().oracle_sum_bf16(_ptr(h), _i64(h.size)))
+
+
+def logsumexp_f32(x):
+    x = np.ascontiguousarray(x, np.float32)
+    return float(load().oracle_logsumexp_f32(_ptr(x), _i64(x.size)))
+
+
+def mean_var_f32(x):
+    x = np.ascontiguousarray(x, np.float32)
+    m, v = ctypes.c_float(), ctypes.c_float()
+    load().oracle_mean_var_f32(_ptr(x), _i64(x.size), ctypes.byref(m), ctypes.byref(v))
+    return m.value, v.value
+
+
+# ------------------------------------------------------------ row kernels ----
+
+def _rows(x):
+    assert x.ndim == 2 and x.flags.c_contiguous
+    return x.shape[1], x.shape[0]
+
+
+def softmax_fwd(x, faithful=True, threads=1):
+    """x: [rows][n] float32 or uint16 (bf16 bits) -> (y, lse float32)."""
+    n, rows = _rows(x)
+    y = np.empty_like(x)
+    lse = np.empty(rows, np.float32)
+    L = load()
+
+    def call(r0, r1):
+        if x.dtype == np.float32:
+            L.oracle_softmax_fwd_f32(_ptr(x[r0:r1]), _ptr(y[r0:r1]), _ptr(lse[r0:r1]), _i64(n), _i64(r1 - r0), _i64(n))
+        else:
+            L.oracle_softmax_fwd_bf16(_ptr(x[r0:r1]), _ptr(y[r0:r1]), _ptr(lse[r0:r1]), _i64(n), _i64(r1 - r0),
+                                      _i64(n), _int(int(faithful)))
+    _over_rows(call, rows, threads)
+    return y, lse
+
+
+def softmax_bwd(y, g, faithful=True, threads=1):
+    n, rows = _rows(y)
+    dx = np.empty_like(y)
+    L = load()
+
+    def call(r0, r1):
+        if y.dtype == np.float32:
+            L.oracle_softmax_bwd_f32(_ptr(y[r0:r1]), _ptr(g[r0:r1]), _ptr(dx[r0:r1]), _i64(n), _i64(r1 - r0), _i64(n))
+        else:
+            L.oracle_softmax_bwd_bf16(_ptr(y[r0:r1]), _ptr(g[r0:r1]), _ptr(dx[r0:r1]), _i64(n), _i64(r1 - r0),
+                                      _i64(n), _int(int(faithful)))
+    _over_rows(call, rows, threads)
+    return dx
+
+
+def layernorm_fwd(x, gamma, beta=None, eps=1e-5, faithful=True, threads=1):
+    n, rows = _rows(x)
+    y = np.empty_like(x)
+    mean, rstd = np.empty(rows, np.float32), np.empty(rows, np.float32)
+    L = load()
+
+    def call(r0, r1):
+        if x.dtype == np.float32:
+            L.oracle_layernorm_fwd_f32(_ptr(x[r0:r1]), _ptr(gamma), _ptr(beta), _ptr(y[r0:r1]), _ptr(mean[r0:r1]),
+                                       _ptr(rstd[r0:r1]), _flt(eps), _i64(n), _i64(r1 - r0), _i64(n))
+        else:
+            L.oracle_layernorm_fwd_bf16(_ptr(x[r0:r1]), _ptr(gamma), _ptr(beta), _ptr(y[r0:r1]), _ptr(mean[r0:r1]),
+                                        _ptr(rstd[r0:r1]), _flt(eps), _i64(n), _i64(r1 - r0), _i64(n),
+                                        _int(int(faithful)))
+    _over_rows(call, rows, threads)
+    return y, mean, rstd
+
+
+def layernorm_bwd(x, gamma, g, eps=1e-5, wide=False, threads=1):
+    """With threads > 1 only dx is formed (per row range); dgamma and dbeta, sums
+    over all rows in order, need the single thread and come back as None."""
+    n, rows = _rows(x)
+    dx = np.empty_like(x)
+    fn = load().oracle_layernorm_bwd_f32 if x.dtype == np.float32 else load().oracle_layernorm_bwd_bf16
+    if threads <= 1:
+        dgamma, dbeta = np.empty(n, x.dtype), np.empty(n, x.dtype)
+        fn(_ptr(x), _ptr(gamma), _ptr(g), _ptr(dx), _ptr(dgamma), _ptr(dbeta), _flt(eps), _i64(n), _i64(rows),
+           _i64(n), _int(int(wide)))
+        return dx, dgamma, dbeta
+
+    def call(r0, r1):
+        fn(_ptr(x[r0:r1]), _ptr(gamma), _ptr(g[r0:r1]), _ptr(dx[r0:r1]), None, None, _flt(eps), _i64(n),
+           _i64(r1 - r0), _i64(n), _int(0))
+    _over_rows(call, rows, threads)
+    return dx, None, None
+
+
+# ------------------------------------------------------------------ GEMM ----
+
+def gemm(A, B, bias=None, M=None, N=None, K=None, a_km=False, b_kn=True, epilogue=0, threads=1, want_pre=False):
+    """C[M][N] = A * B (+bias, activation); float32 or bf16 bits (uint16)."""
+    C = np.empty((M, N), A.dtype)
+    if A.dtype == np.float32:
+        load().oracle_gemm_f32(_ptr(A), _ptr(B), _ptr(bias), _ptr(C), _i64(M), _i64(N), _i64(K), _int(int(a_km)),
+                               _int(int(b_kn)), _int(epilogue))
+        return C
+    pre = np.empty((M, N), np.float32) if want_pre else None
+    load().oracle_gemm_bf16(_ptr(A), _ptr(B), _ptr(bias), _ptr(C), _ptr(pre), _i64(M), _i64(N), _i64(K),
+                            _int(int(a_km)), _int(int(b_kn)), _int(epilogue))
+    return (C, pre) if want_pre else C
+
+
+def gelu_tanh(x):
+    return load().oracle_gelu_tanh(float(x))
+
+
+def gelu_tanh_grad(x):
+    return load().oracle_gelu_tanh_grad(float(x))
+
+
+def readme_loss_grad(w, b, x):
+    """w: Julia (I,J) as numpy [J][I]; b: [J]; x: Julia (I,N) as numpy [N][I]."""
+    J, I = w.shape
+    N = x.shape[0]
+    dw, db, dx = np.empty_like(w), np.empty_like(b), np.empty_like(x)
+    loss = load().oracle_readme_loss_grad(_ptr(w), _ptr(b), _ptr(x), _ptr(dw), _ptr(db), _ptr(dx), _i64(I), _i64(J),
+                                          _i64(N))
+    return float(loss), dw, db, dx
+
+
+# ------------------------------------------------- Float64 closed forms -----
+
+def softmax_fwd_f64(x):
+    x = x.astype(np.float64)
+    m = x.max(axis=1, keepdims=True)
+    e = np.exp(x - m)
+    s = e.sum(axis=1, keepdims=True)
+    return e / s, (m + np.log(s))[:, 0]
+
+
+def softmax_bwd_f64(y, g):
+    y, g = y.astype(np.float64), g.astype(np.float64)
+    return y * (g - (y * g).sum(axis=1, keepdims=True))
+
+
+def layernorm_fwd_f64(x, gamma, beta=None, eps=1e-5):
+    x = x.astype(np.float64)
+    m = x.mean(axis=1, keepdims=True)
+    v = ((x - m) ** 2).mean(axis=1, keepdims=True)
+    y = (x - m) / np.sqrt(v + eps) * gamma.astype(np.float64)
+    return y if beta is None else y + beta.astype(np.float64)
+
+
+def layernorm_bwd_f64(x, gamma, g, eps=1e-5):
+    x, g, gamma = x.astype(np.float64), g.astype(np.float64), gamma.astype(np.float64)
+    m = x.mean(axis=1, keepdims=True)
+    v = ((x - m) ** 2).mean(axis=1, keepdims=True)
+    rstd = 1.0 / np.sqrt(v + eps)
+    xh = (x - m) * rstd
+    gh = g * gamma
+    dx = rstd * (gh - gh.mean(axis=1, keepdims=True) - xh * (gh * xh).mean(axis=1, keepdims=True))
+    return dx, (g * xh).sum(axis=0), g.sum(axis=0)

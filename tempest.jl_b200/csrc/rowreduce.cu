@@ -1,0 +1,845 @@
+// Fused row reductions for sm_100a: softmax and LayerNorm, forward and the
+// backward the tape's derivative rules produce, over rows whose folded axis is
+// contiguous.
+//
+// Two schedules, chosen from the row length (the counterpart of the
+// reference's resident / split sketches, ext/cuTileExt/cuTileExt.jl:438-455):
+//
+//  * resident: `tpr` threads share a row and hold all of it in registers
+//    (up to 32 elements each, fetched as 128-bit loads), so the row crosses
+//    HBM once in and once out.  Blocks are persistent: a grid of
+//    SMs x resident-blocks walks the row groups, which lets LayerNorm keep
+//    gamma/beta and its dgamma/dbeta partial sums in registers across rows.
+//  * split: a long row is cut into chunks of 256 threads x 32 elements; a first
+//    launch folds every chunk to a partial state in the workspace, a second
+//    merges the row's partial states and writes the outputs ("split-K, two
+//    passes").
+//
+// Numerics: Float32 arithmetic for either element type, sums as fixed-order
+// trees (deterministic), exp as ex2.approx of a scaled argument, outputs
+// rounded once.
+#include <initializer_list>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kResidentMaxThreads = 512;
+constexpr int kSplitThreads = 256;
+
+struct RowArgs {
+    const void *in0;    // x (forward), y or x (softmax backward), x (LayerNorm backward)
+    const void *in1;    // dy
+    const void *gamma;
+    const void *beta;
+    void *out0;         // y (forward) or dx (backward)
+    void *stat0;        // lse | mean
+    void *stat1;        // rstd
+    const void *cstat0; // saved lse | mean
+    const void *cstat1; // saved rstd
+    float *part0;       // dgamma partial sums [parts][n] | split states
+    float *part1;       // dbeta partial sums [parts][n]
+    float eps;
+    int n;              // row length
+    int tpr;            // threads per row (resident)
+    int rpc;            // rows per block (resident)
+    int splits;         // chunks per row (split)
+    int stat_bf16;
+    long long rows, ld;
+};
+
+template <typename T, bool VEC, int VPT>
+struct Row {
+    using A = Access<T, VEC>;
+    static constexpr int EPV = A::EPV;
+    static constexpr int E = VPT * EPV;
+    static __device__ __forceinline__ int at(int k, int t, int tpr) { return (k * tpr + t) * EPV; }
+
+    static __device__ __forceinline__ void load(float (&v)[E], const T *row, int n, int t, int tpr, float fill,
+                                                bool live) {
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            int idx = at(k, t, tpr);
+            if (live && idx < n) A::load(row + idx, &v[k * EPV]);
+            else
+#pragma unroll
+                for (int e = 0; e < EPV; e++) v[k * EPV + e] = fill;
+        }
+    }
+    static __device__ __forceinline__ void load_cached(float (&v)[E], const T *row, int n, int t, int tpr,
+                                                       float fill) {
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            int idx = at(k, t, tpr);
+            if (idx < n) A::load_cached(row + idx, &v[k * EPV]);
+            else
+#pragma unroll
+                for (int e = 0; e < EPV; e++) v[k * EPV + e] = fill;
+        }
+    }
+    static __device__ __forceinline__ void store(const float (&v)[E], T *row, int n, int t, int tpr, bool live) {
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            int idx = at(k, t, tpr);
+            if (live && idx < n) A::store(row + idx, &v[k * EPV]);
+        }
+    }
+    // Float32 partial sums, one row of the workspace
+    static __device__ __forceinline__ void store_f32(const float (&v)[E], float *row, int n, int t, int tpr) {
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            int idx = at(k, t, tpr);
+            if (idx < n) {
+                if constexpr (EPV % 4 == 0) {
+#pragma unroll
+                    for (int e = 0; e < EPV; e += 4)
+                        *reinterpret_cast<float4 *>(row + idx + e) =
+                            make_float4(v[k * EPV + e], v[k * EPV + e + 1], v[k * EPV + e + 2], v[k * EPV + e + 3]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < EPV; e++) row[idx + e] = v[k * EPV + e];
+                }
+            }
+        }
+    }
+    // whether element slot (k, e) of thread t lies inside the row
+    static __device__ __forceinline__ bool inside(int k, int t, int tpr, int n) { return at(k, t, tpr) < n; }
+};
+
+// ------------------------------------------------------------ resident ------
+
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kResidentMaxThreads) softmax_fwd_resident(RowArgs a) {
+    using R = Row<T, VEC, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(a.tpr, red);
+    const T *x = static_cast<const T *>(a.in0);
+    T *y = static_cast<T *>(a.out0);
+    const long long groups = (a.rows + a.rpc - 1) / a.rpc;
+    for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
+        const long long r = g * a.rpc + c.slot;
+        const bool live = r < a.rows;
+        float v[R::E];
+        R::load(v, x + r * a.ld, a.n, c.t, a.tpr, -INFINITY, live);
+        float m = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < R::E; e++) m = fmaxf(m, v[e]);
+        m = row_allreduce1(m, c, MaxOp());
+        // exponentials are taken relative to the maximum, or to zero when it
+        // is infinite (an empty or all -Inf row sums to zero)
+        const float sh = (fabsf(m) <= 3.402823466e38f) ? m : 0.0f;
+        const float off = sh * kLog2e;
+        float s = 0.0f;
+#pragma unroll
+        for (int e = 0; e < R::E; e++) {
+            v[e] = fast_exp2(fmaf(v[e], kLog2e, -off));
+            s += v[e];
+        }
+        s = row_allreduce1(s, c, SumOp());
+        if (live && c.t == 0 && a.stat0) store_stat(a.stat0, r, m + logf(s), a.stat_bf16);
+        const float inv = 1.0f / s;
+#pragma unroll
+        for (int e = 0; e < R::E; e++) v[e] *= inv;
+        R::store(v, y + r * a.ld, a.n, c.t, a.tpr, live);
+    }
+}
+
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kResidentMaxThreads) softmax_bwd_resident(RowArgs a) {
+    using R = Row<T, VEC, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(a.tpr, red);
+    const T *yx = static_cast<const T *>(a.in0);
+    const T *dy = static_cast<const T *>(a.in1);
+    T *dx = static_cast<T *>(a.out0);
+    const long long groups = (a.rows + a.rpc - 1) / a.rpc;
+    for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
+        const long long r = g * a.rpc + c.slot;
+        const bool live = r < a.rows;
+        float y[R::E], d[R::E];
+        R::load(y, yx + r * a.ld, a.n, c.t, a.tpr, a.cstat0 ? -INFINITY : 0.0f, live);
+        R::load(d, dy + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
+        if (a.cstat0) {
+            const float off = (live ? load_stat(a.cstat0, r, a.stat_bf16) : 0.0f) * kLog2e;
+#pragma unroll
+            for (int e = 0; e < R::E; e++) y[e] = fast_exp2(fmaf(y[e], kLog2e, -off));
+        }
+        float s = 0.0f;
+#pragma unroll
+        for (int e = 0; e < R::E; e++) s = fmaf(y[e], d[e], s);
+        s = row_allreduce1(s, c, SumOp());
+#pragma unroll
+        for (int e = 0; e < R::E; e++) d[e] = y[e] * (d[e] - s);
+        R::store(d, dx + r * a.ld, a.n, c.t, a.tpr, live);
+    }
+}
+
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kResidentMaxThreads) layernorm_fwd_resident(RowArgs a) {
+    using R = Row<T, VEC, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(a.tpr, red);
+    const T *x = static_cast<const T *>(a.in0);
+    T *y = static_cast<T *>(a.out0);
+    float gam[R::E], bet[R::E];
+    R::load_cached(gam, static_cast<const T *>(a.gamma), a.n, c.t, a.tpr, 0.0f);
+    if (a.beta) R::load_cached(bet, static_cast<const T *>(a.beta), a.n, c.t, a.tpr, 0.0f);
+    else
+#pragma unroll
+        for (int e = 0; e < R::E; e++) bet[e] = 0.0f;
+    const float fn = static_cast<float>(a.n);
+    const long long groups = (a.rows + a.rpc - 1) / a.rpc;
+    for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
+        const long long r = g * a.rpc + c.slot;
+        const bool live = r < a.rows;
+        float v[R::E];
+        R::load(v, x + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
+        float s = 0.0f;
+#pragma unroll
+        for (int e = 0; e < R::E; e++) s += v[e];
+        const float mean = row_allreduce1(s, c, SumOp()) / fn;
+        float q = 0.0f;
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const bool in = R::inside(k, c.t, a.tpr, a.n);
+#pragma unroll
+            for (int e = 0; e < R::EPV; e++) {
+                const float d = v[k * R::EPV + e] - mean;
+                v[k * R::EPV + e] = d;
+                q = in ? fmaf(d, d, q) : q;
+            }
+        }
+        const float var = row_allreduce1(q, c, SumOp()) / fn;
+        const float rstd = 1.0f / sqrtf(var + a.eps);
+        if (live && c.t == 0) {
+            if (a.stat0) static_cast<float *>(a.stat0)[r] = mean;
+            if (a.stat1) static_cast<float *>(a.stat1)[r] = rstd;
+        }
+#pragma unroll
+        for (int e = 0; e < R::E; e++) v[e] = fmaf(v[e] * rstd, gam[e], bet[e]);
+        R::store(v, y + r * a.ld, a.n, c.t, a.tpr, live);
+    }
+}
+
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kResidentMaxThreads) layernorm_bwd_resident(RowArgs a) {
+    using R = Row<T, VEC, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(a.tpr, red);
+    const T *x = static_cast<const T *>(a.in0);
+    const T *dy = static_cast<const T *>(a.in1);
+    T *dx = static_cast<T *>(a.out0);
+    float gam[R::E], dg[R::E], db[R::E];
+    R::load_cached(gam, static_cast<const T *>(a.gamma), a.n, c.t, a.tpr, 0.0f);
+#pragma unroll
+    for (int e = 0; e < R::E; e++) dg[e] = db[e] = 0.0f;
+    const float fn = static_cast<float>(a.n);
+    const long long groups = (a.rows + a.rpc - 1) / a.rpc;
+    for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
+        const long long r = g * a.rpc + c.slot;
+        const bool live = r < a.rows;
+        float v[R::E], d[R::E];
+        R::load(v, x + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
+        R::load(d, dy + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
+        float mean, rstd;
+        if (a.cstat0 && a.cstat1) {
+            mean = live ? static_cast<const float *>(a.cstat0)[r] : 0.0f;
+            rstd = live ? static_cast<const float *>(a.cstat1)[r] : 0.0f;
+        } else {
+            float s = 0.0f;
+#pragma unroll
+            for (int e = 0; e < R::E; e++) s += v[e];
+            mean = row_allreduce1(s, c, SumOp()) / fn;
+            float q = 0.0f;
+#pragma unroll
+            for (int k = 0; k < VPT; k++) {
+                const bool in = R::inside(k, c.t, a.tpr, a.n);
+#pragma unroll
+                for (int e = 0; e < R::EPV; e++) {
+                    const float t = v[k * R::EPV + e] - mean;
+                    q = in ? fmaf(t, t, q) : q;
+                }
+            }
+            rstd = 1.0f / sqrtf(row_allreduce1(q, c, SumOp()) / fn + a.eps);
+        }
+        // xh in v; padded slots have gamma = 0 and dy = 0, so they add nothing
+        float s2[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int e = 0; e < R::E; e++) {
+            v[e] = (v[e] - mean) * rstd;
+            const float gh = d[e] * gam[e];
+            s2[0] += gh;
+            s2[1] = fmaf(gh, v[e], s2[1]);
+            dg[e] = fmaf(d[e], v[e], dg[e]);
+            db[e] += d[e];
+        }
+        row_allreduce<2>(s2, c, SumOp());
+        const float c1 = s2[0] / fn, c2 = s2[1] / fn;
+#pragma unroll
+        for (int e = 0; e < R::E; e++) d[e] = rstd * (fmaf(d[e], gam[e], -c1) - v[e] * c2);
+        R::store(d, dx + r * a.ld, a.n, c.t, a.tpr, live);
+    }
+    if (a.part0) {
+        const long long p = static_cast<long long>(blockIdx.x) * a.rpc + c.slot;
+        R::store_f32(dg, a.part0 + p * a.n, a.n, c.t, a.tpr);
+        R::store_f32(db, a.part1 + p * a.n, a.n, c.t, a.tpr);
+    }
+}
+
+// Column sums of the partial dgamma / dbeta rows: 32 columns x 8 lanes per
+// block; each lane strides over the parts in order, the 8 lanes merge in a
+// fixed tree.  Output in the element type, rounded once.
+template <typename T>
+__global__ void __launch_bounds__(256) merge_parts(const float *part0, const float *part1, T *out0, T *out1,
+                                                   int n, int parts) {
+    __shared__ float sm[2][8][33];
+    const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int lane = threadIdx.x >> 5;
+    float s0 = 0.0f, s1 = 0.0f;
+    if (col < n)
+        for (int p = lane; p < parts; p += 8) {
+            s0 += part0[static_cast<long long>(p) * n + col];
+            s1 += part1[static_cast<long long>(p) * n + col];
+        }
+    sm[0][lane][threadIdx.x & 31] = s0;
+    sm[1][lane][threadIdx.x & 31] = s1;
+    __syncthreads();
+    if (lane == 0 && col < n) {
+        float t0 = 0.0f, t1 = 0.0f;
+#pragma unroll
+        for (int l = 0; l < 8; l++) {
+            t0 += sm[0][l][threadIdx.x];
+            t1 += sm[1][l][threadIdx.x];
+        }
+        float o0[1] = {t0}, o1[1] = {t1};
+        if (out0) Access<T, false>::store(out0 + col, o0);
+        if (out1) Access<T, false>::store(out1 + col, o1);
+    }
+}
+
+__global__ void fill_stat(void *p, long long count, float value, int as_bf16) {
+    long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i < count) store_stat(p, i, value, as_bf16);
+}
+
+// --------------------------------------------------------------- split ------
+// Block b folds chunk (b % splits) of row (b / splits); a chunk is
+// kSplitThreads x E elements held in registers.  States live in part0 as
+// float4 per (row, chunk).
+
+template <typename T, bool VEC, int VPT>
+struct Chunk {
+    using R = Row<T, VEC, VPT>;
+    static constexpr int LEN = kSplitThreads * R::E;
+    long long r;
+    int c, base, len;
+    __device__ __forceinline__ Chunk(const RowArgs &a) {
+        r = blockIdx.x / a.splits;
+        c = static_cast<int>(blockIdx.x - r * a.splits);
+        base = c * LEN;
+        len = min(LEN, a.n - base);
+    }
+};
+
+// merge of the row's log-sum-exp states (m, s): the maximum first, then each
+// sum moved to it once (the reference's RebasedSums, src/Compiler/IR/folds.jl:240-264)
+__device__ __forceinline__ float merged_lse(const float4 *states, int splits, RowCtx &c) {
+    float m = -INFINITY;
+    for (int i = threadIdx.x; i < splits; i += blockDim.x) m = fmaxf(m, states[i].x);
+    m = row_allreduce1(m, c, MaxOp());
+    const float sh = (fabsf(m) <= 3.402823466e38f) ? m : 0.0f;
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < splits; i += blockDim.x) {
+        const float4 st = states[i];
+        const float shi = (fabsf(st.x) <= 3.402823466e38f) ? st.x : 0.0f;
+        s += st.y * fast_exp2((shi - sh) * kLog2e);
+    }
+    s = row_allreduce1(s, c, SumOp());
+    return m + logf(s);
+}
+
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kSplitThreads) softmax_fwd_split_fold(RowArgs a) {
+    using R = Row<T, VEC, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(kSplitThreads, red);
+    Chunk<T, VEC, VPT> ch(a);
+    float v[R::E];
+    R::load(v, static_cast<const T *>(a.in0) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads, -INFINITY, true);
+    float m = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < R::E; e++) m = fmaxf(m, v[e]);
+    m = row_allreduce1(m, c, MaxOp());
+    const float sh = (fabsf(m) <= 3.402823466e38f) ? m : 0.0f;
+    float s = 0.0f;
+#pragma unroll
+    for (int e = 0; e < R::E; e++) s += fast_exp2((v[e] - sh) * kLog2e);
+    s = row_allreduce1(s, c, SumOp());
+    if (threadIdx.x == 0) reinterpret_cast<float4 *>(a.part0)[blockIdx.x] = make_float4(m, s, 0.0f, 0.0f);
+}
+
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kSplitThreads) softmax_fwd_split_write(RowArgs a) {
+    using R = Row<T, VEC, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(kSplitThreads, red);
+    Chunk<T, VEC, VPT> ch(a);
+    const float lse = merged_lse(reinterpret_cast<const float4 *>(a.part0) + ch.r * a.splits, a.splits, c);
+    if (ch.c == 0 && threadIdx.x == 0 && a.stat0) store_stat(a.stat0, ch.r, lse, a.stat_bf16);
+    float v[R::E];
+    R::load(v, static_cast<const T *>(a.in0) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads, 0.0f, true);
+    const float off = lse * kLog2e;
+#pragma unroll
+    for (int e = 0; e < R::E; e++) v[e] = fast_exp2(fmaf(v[e], kLog2e, -off));
+    R::store(v, static_cast<T *>(a.out0) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads, true);
+}
+
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kSplitThreads) softmax_bwd_split_fold(RowArgs a) {
+    using R = Row<T, VEC, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(kSplitThreads, red);
+    Chunk<T, VEC, VPT> ch(a);
+    float y[R::E], d[R::E];
+    R::load(y, static_cast<const T *>(a.in0) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads,
+            a.cstat0 ? -INFINITY : 0.0f, true);
+    R::load(d, static_cast<const T *>(a.in1) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads, 0.0f, true);
+    if (a.cstat0) {
+        const float off = load_stat(a.cstat0, ch.r, a.stat_bf16) * kLog2e;
+#pragma unroll
+        for (int e = 0; e < R::E; e++) y[e] = fast_exp2(fmaf(y[e], kLog2e, -off));
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int e = 0; e < R::E; e++) s = fmaf(y[e], d[e], s);
+    s = row_allreduce1(s, c, SumOp());
+    if (threadIdx.x == 0) reinterpret_cast<float4 *>(a.part0)[blockIdx.x] = make_float4(s, 0.0f, 0.0f, 0.0f);
+}
+
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kSplitThreads) softmax_bwd_split_write(RowArgs a) {
+    using R = Row<T, VEC, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(kSplitThreads, red);
+    Chunk<T, VEC, VPT> ch(a);
+    const float4 *states = reinterpret_cast<const float4 *>(a.part0) + ch.r * a.splits;
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < a.splits; i += blockDim.x) s += states[i].x;
+    s = row_allreduce1(s, c, SumOp());
+    float y[R::E], d[R::E];
+    R::load(y, static_cast<const T *>(a.in0) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads,
+            a.cstat0 ? -INFINITY : 0.0f, true);
+    R::load(d, static_cast<const T *>(a.in1) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads, 0.0f, true);
+    if (a.cstat0) {
+        const float off = load_stat(a.cstat0, ch.r, a.stat_bf16) * kLog2e;
+#pragma unroll
+        for (int e = 0; e < R::E; e++) y[e] = fast_exp2(fmaf(y[e], kLog2e, -off));
+    }
+#pragma unroll
+    for (int e = 0; e < R::E; e++) d[e] = y[e] * (d[e] - s);
+    R::store(d, static_cast<T *>(a.out0) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads, true);
+}
+
+// LayerNorm: chunk states (count, mean, M2) merged as Chan combines them
+// (src/Compiler/IR/folds.jl:166-182).
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kSplitThreads) layernorm_split_fold(RowArgs a) {
+    using R = Row<T, VEC, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(kSplitThreads, red);
+    Chunk<T, VEC, VPT> ch(a);
+    float v[R::E];
+    R::load(v, static_cast<const T *>(a.in0) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads, 0.0f, true);
+    float s = 0.0f;
+#pragma unroll
+    for (int e = 0; e < R::E; e++) s += v[e];
+    const float cnt = static_cast<float>(ch.len);
+    const float mean = row_allreduce1(s, c, SumOp()) / cnt;
+    float q = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const bool in = R::inside(k, c.t, kSplitThreads, ch.len);
+#pragma unroll
+        for (int e = 0; e < R::EPV; e++) {
+            const float d = v[k * R::EPV + e] - mean;
+            q = in ? fmaf(d, d, q) : q;
+        }
+    }
+    q = row_allreduce1(q, c, SumOp());
+    if (threadIdx.x == 0) reinterpret_cast<float4 *>(a.part0)[blockIdx.x] = make_float4(cnt, mean, q, 0.0f);
+}
+
+__device__ __forceinline__ void merged_moments(const float4 *states, int splits, float fn, float eps, RowCtx &c,
+                                               float &mean, float &rstd) {
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < splits; i += blockDim.x) s = fmaf(states[i].x, states[i].y, s);
+    mean = row_allreduce1(s, c, SumOp()) / fn;
+    float q = 0.0f;
+    for (int i = threadIdx.x; i < splits; i += blockDim.x) {
+        const float4 st = states[i];
+        const float d = st.y - mean;
+        q += st.z + st.x * d * d;
+    }
+    rstd = 1.0f / sqrtf(row_allreduce1(q, c, SumOp()) / fn + eps);
+}
+
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kSplitThreads) layernorm_fwd_split_write(RowArgs a) {
+    using R = Row<T, VEC, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(kSplitThreads, red);
+    Chunk<T, VEC, VPT> ch(a);
+    float mean, rstd;
+    merged_moments(reinterpret_cast<const float4 *>(a.part0) + ch.r * a.splits, a.splits, static_cast<float>(a.n),
+                   a.eps, c, mean, rstd);
+    if (ch.c == 0 && threadIdx.x == 0) {
+        if (a.stat0) static_cast<float *>(a.stat0)[ch.r] = mean;
+        if (a.stat1) static_cast<float *>(a.stat1)[ch.r] = rstd;
+    }
+    float v[R::E], gam[R::E], bet[R::E];
+    R::load(v, static_cast<const T *>(a.in0) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads, 0.0f, true);
+    R::load_cached(gam, static_cast<const T *>(a.gamma) + ch.base, ch.len, c.t, kSplitThreads, 0.0f);
+    if (a.beta) R::load_cached(bet, static_cast<const T *>(a.beta) + ch.base, ch.len, c.t, kSplitThreads, 0.0f);
+    else
+#pragma unroll
+        for (int e = 0; e < R::E; e++) bet[e] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < R::E; e++) v[e] = fmaf((v[e] - mean) * rstd, gam[e], bet[e]);
+    R::store(v, static_cast<T *>(a.out0) + ch.r * a.ld + ch.base, ch.len, c.t, kSplitThreads, true);
+}
+
+// ------------------------------------------------------------- dispatch -----
+
+enum RowOp { OP_SOFTMAX_FWD, OP_SOFTMAX_BWD, OP_LN_FWD, OP_LN_BWD };
+
+// elements a thread holds in the resident schedule, by how many row-sized
+// register arrays the kernel keeps
+inline int resident_elems(RowOp op) { return op == OP_LN_BWD ? 16 : 32; }
+
+struct Schedule {
+    bool vec;     // 128-bit accesses
+    bool split;   // two-pass schedule
+    int vpt;      // vectors per thread
+    int tpr, rpc; // resident geometry
+    int threads;
+    int splits;
+    long long blocks; // grid (resident: an upper bound before occupancy)
+};
+
+inline int round_vpt(int64_t v) { return v <= 1 ? 1 : v <= 2 ? 2 : v <= 4 ? 4 : 8; }
+
+Schedule plan_rows(RowOp op, int64_t n, int64_t rows, int64_t ld, int dtype, bool aligned16) {
+    Schedule s{};
+    const int es = static_cast<int>(dtype_size(dtype));
+    const int epv_vec = 16 / es;
+    s.vec = aligned16 && n % epv_vec == 0 && ld % epv_vec == 0;
+    const int epv = s.vec ? epv_vec : 1;
+    const int max_e = resident_elems(op);
+    const int max_vpt = s.vec ? max_e / epv : 8;
+    const int64_t nvec = n / epv;
+    const int tpr = next_pow2(ceil_div(nvec, max_vpt));
+    if (tpr <= kResidentMaxThreads) {
+        s.split = false;
+        s.tpr = tpr;
+        s.vpt = round_vpt(ceil_div(nvec, tpr));
+        s.threads = tpr >= 128 ? tpr : 128;
+        s.rpc = s.threads / tpr;
+        s.splits = 1;
+        s.blocks = ceil_div(rows, s.rpc);
+    } else {
+        s.split = true;
+        s.vpt = s.vec ? 32 / epv : 8;  // split chunks hold 32 elements per thread (8 when scalar)
+        s.tpr = kSplitThreads;
+        s.rpc = 1;
+        s.threads = kSplitThreads;
+        const int64_t chunk = static_cast<int64_t>(kSplitThreads) * s.vpt * epv;
+        s.splits = static_cast<int>(ceil_div(n, chunk));
+        s.blocks = rows * s.splits;
+    }
+    return s;
+}
+
+using RowKernel = void (*)(RowArgs);
+
+// One struct per kernel family, so a family can be named as a type and
+// instantiated for the schedule's (element type, access width, vectors per thread).
+#define TB200_FAMILY(NAME, KERNEL)                                         \
+    struct NAME {                                                          \
+        template <typename T, bool VEC, int VPT>                           \
+        static RowKernel get() { return KERNEL<T, VEC, VPT>; }             \
+    }
+TB200_FAMILY(SoftmaxFwdResident, softmax_fwd_resident);
+TB200_FAMILY(SoftmaxBwdResident, softmax_bwd_resident);
+TB200_FAMILY(LayernormFwdResident, layernorm_fwd_resident);
+TB200_FAMILY(LayernormBwdResident, layernorm_bwd_resident);
+TB200_FAMILY(SoftmaxFwdSplitFold, softmax_fwd_split_fold);
+TB200_FAMILY(SoftmaxFwdSplitWrite, softmax_fwd_split_write);
+TB200_FAMILY(SoftmaxBwdSplitFold, softmax_bwd_split_fold);
+TB200_FAMILY(SoftmaxBwdSplitWrite, softmax_bwd_split_write);
+TB200_FAMILY(LayernormSplitFold, layernorm_split_fold);
+TB200_FAMILY(LayernormFwdSplitWrite, layernorm_fwd_split_write);
+#undef TB200_FAMILY
+
+template <typename Fam, typename T, bool VEC>
+RowKernel pick_vpt(int vpt) {
+    switch (vpt) {
+        case 1: return Fam::template get<T, VEC, 1>();
+        case 2: return Fam::template get<T, VEC, 2>();
+        case 4: return Fam::template get<T, VEC, 4>();
+        case 8:
+            // 8 vectors of 8 BFloat16 would be 64 elements a thread: never scheduled
+            if constexpr (!VEC || sizeof(T) == 4) return Fam::template get<T, VEC, 8>();
+            else return nullptr;
+        default: return nullptr;
+    }
+}
+
+template <typename Fam>
+RowKernel pick(int dtype, const Schedule &s) {
+    if (dtype == TB200_F32) return s.vec ? pick_vpt<Fam, float, true>(s.vpt) : pick_vpt<Fam, float, false>(s.vpt);
+    return s.vec ? pick_vpt<Fam, __nv_bfloat16, true>(s.vpt) : pick_vpt<Fam, __nv_bfloat16, false>(s.vpt);
+}
+
+// Resident blocks per SM of a kernel at a block size, asked of the runtime once
+// per (kernel, block size, device).
+int blocks_per_sm(RowKernel kernel, int threads, int device, int *out) {
+    static std::mutex lock;
+    static std::map<std::tuple<const void *, int, int>, int> memo;
+    const auto key = std::make_tuple(reinterpret_cast<const void *>(kernel), threads, device);
+    {
+        std::lock_guard<std::mutex> hold(lock);
+        auto it = memo.find(key);
+        if (it != memo.end()) {
+            *out = it->second;
+            return TB200_OK;
+        }
+    }
+    int per_sm = 0;
+    TB200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
+    if (per_sm < 1) per_sm = 1;
+    std::lock_guard<std::mutex> hold(lock);
+    memo[key] = per_sm;
+    *out = per_sm;
+    return TB200_OK;
+}
+
+// Persistent grid of a resident kernel: every SM full, never more blocks than row groups.
+int resident_grid(RowKernel kernel, const Schedule &s, const DeviceInfo &dev, long long *grid) {
+    if (!kernel) return TB200_ERR_UNSUPPORTED;
+    int per_sm = 0;
+    int st = blocks_per_sm(kernel, s.threads, dev.device, &per_sm);
+    if (st) return st;
+    long long g = static_cast<long long>(dev.sms) * per_sm;
+    *grid = g < s.blocks ? g : s.blocks;
+    return TB200_OK;
+}
+
+int launch_resident(RowKernel kernel, const Schedule &s, const DeviceInfo &dev, const RowArgs &a,
+                    cudaStream_t stream) {
+    long long grid = 0;
+    int st = resident_grid(kernel, s, dev, &grid);
+    if (st) return st;
+    kernel<<<static_cast<unsigned>(grid), s.threads, 0, stream>>>(a);
+    TB200_CUDA(cudaGetLastError());
+    return TB200_OK;
+}
+
+int launch_split(RowKernel kernel, const Schedule &s, const RowArgs &a, cudaStream_t stream) {
+    if (!kernel) return TB200_ERR_UNSUPPORTED;
+    kernel<<<static_cast<unsigned>(s.blocks), s.threads, 0, stream>>>(a);
+    TB200_CUDA(cudaGetLastError());
+    return TB200_OK;
+}
+
+int check_rows(int64_t n, int64_t rows, int64_t ld, int dtype) {
+    if (dtype != TB200_F32 && dtype != TB200_BF16) return TB200_ERR_DTYPE;
+    if (n < 0 || rows < 0 || ld < n) return TB200_ERR_SHAPE;
+    if (n > (int64_t(1) << 30) || rows > (int64_t(1) << 40)) return TB200_ERR_SHAPE;
+    return TB200_OK;
+}
+
+bool all_aligned(size_t a, std::initializer_list<const void *> ps) {
+    for (const void *p : ps)
+        if (p && !aligned_to(p, a)) return false;
+    return true;
+}
+
+int fill(void *p, int64_t count, float value, int as_bf16, cudaStream_t stream) {
+    if (!p || count == 0) return TB200_OK;
+    fill_stat<<<static_cast<unsigned>(ceil_div(count, 256)), 256, 0, stream>>>(p, count, value, as_bf16);
+    TB200_CUDA(cudaGetLastError());
+    return TB200_OK;
+}
+
+size_t split_state_bytes(const Schedule &s, int64_t rows) {
+    return static_cast<size_t>(rows) * s.splits * sizeof(float4);
+}
+
+}  // namespace
+}  // namespace tb200
+
+using namespace tb200;
+
+namespace {
+
+// Bytes of scratch one schedule of an operator needs.
+int schedule_workspace(RowOp op, const Schedule &s, const DeviceInfo &dev, int64_t n, int64_t rows, int dtype,
+                       size_t *bytes) {
+    *bytes = 0;
+    if (s.split) {
+        *bytes = split_state_bytes(s, rows);
+        return TB200_OK;
+    }
+    if (op == OP_LN_BWD) {
+        long long grid = 0;
+        int st = resident_grid(pick<LayernormBwdResident>(dtype, s), s, dev, &grid);
+        if (st) return st;
+        *bytes = static_cast<size_t>(grid) * s.rpc * static_cast<size_t>(n) * 2 * sizeof(float);
+    }
+    return TB200_OK;
+}
+
+bool workspace_ok(const void *workspace, size_t have, size_t need) {
+    return need == 0 || (workspace && have >= need && aligned_to(workspace, 16));
+}
+
+}  // namespace
+
+extern "C" size_t tb200_rowop_workspace_bytes(int op, int64_t n, int64_t rows, int dtype) {
+    if (op < OP_SOFTMAX_FWD || op > OP_LN_BWD) return 0;
+    if (check_rows(n, rows, n, dtype) != TB200_OK || n == 0 || rows == 0) return 0;
+    DeviceInfo dev;
+    if (current_device(&dev) != TB200_OK) return 0;
+    // the call picks 128-bit or scalar accesses from its pointers and ld: cover both
+    size_t most = 0;
+    for (int vec = 0; vec < 2; vec++) {
+        const Schedule s = plan_rows(static_cast<RowOp>(op), n, rows, vec ? n : n + 1, dtype, vec != 0);
+        size_t bytes = 0;
+        if (schedule_workspace(static_cast<RowOp>(op), s, dev, n, rows, dtype, &bytes) != TB200_OK) return 0;
+        if (bytes > most) most = bytes;
+    }
+    return most;
+}
+
+extern "C" int tb200_softmax_fwd(const void *x, void *y, void *lse, int64_t n, int64_t rows, int64_t ld, int dtype,
+                                 int stat_dtype, void *workspace, size_t workspace_bytes, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int st = check_rows(n, rows, ld, dtype);
+    if (st) return st;
+    if (stat_dtype != TB200_F32 && stat_dtype != TB200_BF16) return TB200_ERR_DTYPE;
+    if (rows == 0) return TB200_OK;
+    if (n == 0) return fill(lse, rows, -INFINITY, stat_dtype == TB200_BF16, stream);
+    if (!x || !y) return TB200_ERR_NULL;
+    if (!all_aligned(dtype_size(dtype), {x, y}) || !all_aligned(dtype_size(stat_dtype), {lse})) return TB200_ERR_ALIGN;
+    DeviceInfo dev;
+    if ((st = current_device(&dev))) return st;
+    const Schedule s = plan_rows(OP_SOFTMAX_FWD, n, rows, ld, dtype, all_aligned(16, {x, y}));
+    RowArgs a{};
+    a.in0 = x; a.out0 = y; a.stat0 = lse; a.n = static_cast<int>(n); a.rows = rows; a.ld = ld;
+    a.tpr = s.tpr; a.rpc = s.rpc; a.splits = s.splits; a.stat_bf16 = stat_dtype == TB200_BF16;
+    if (!s.split) return launch_resident(pick<SoftmaxFwdResident>(dtype, s), s, dev, a, stream);
+    if (!workspace_ok(workspace, workspace_bytes, split_state_bytes(s, rows))) return TB200_ERR_WORKSPACE;
+    a.part0 = static_cast<float *>(workspace);
+    if ((st = launch_split(pick<SoftmaxFwdSplitFold>(dtype, s), s, a, stream))) return st;
+    return launch_split(pick<SoftmaxFwdSplitWrite>(dtype, s), s, a, stream);
+}
+
+extern "C" int tb200_softmax_bwd(const void *y_or_x, const void *lse, const void *dy, void *dx, int64_t n,
+                                 int64_t rows, int64_t ld, int dtype, int stat_dtype, void *workspace,
+                                 size_t workspace_bytes, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int st = check_rows(n, rows, ld, dtype);
+    if (st) return st;
+    if (stat_dtype != TB200_F32 && stat_dtype != TB200_BF16) return TB200_ERR_DTYPE;
+    if (rows == 0 || n == 0) return TB200_OK;
+    if (!y_or_x || !dy || !dx) return TB200_ERR_NULL;
+    if (!all_aligned(dtype_size(dtype), {y_or_x, dy, dx}) || !all_aligned(dtype_size(stat_dtype), {lse}))
+        return TB200_ERR_ALIGN;
+    DeviceInfo dev;
+    if ((st = current_device(&dev))) return st;
+    const Schedule s = plan_rows(OP_SOFTMAX_BWD, n, rows, ld, dtype, all_aligned(16, {y_or_x, dy, dx}));
+    RowArgs a{};
+    a.in0 = y_or_x; a.in1 = dy; a.out0 = dx; a.cstat0 = lse; a.n = static_cast<int>(n); a.rows = rows; a.ld = ld;
+    a.tpr = s.tpr; a.rpc = s.rpc; a.splits = s.splits; a.stat_bf16 = stat_dtype == TB200_BF16;
+    if (!s.split) return launch_resident(pick<SoftmaxBwdResident>(dtype, s), s, dev, a, stream);
+    if (!workspace_ok(workspace, workspace_bytes, split_state_bytes(s, rows))) return TB200_ERR_WORKSPACE;
+    a.part0 = static_cast<float *>(workspace);
+    if ((st = launch_split(pick<SoftmaxBwdSplitFold>(dtype, s), s, a, stream))) return st;
+    return launch_split(pick<SoftmaxBwdSplitWrite>(dtype, s), s, a, stream);
+}
+
+extern "C" int tb200_layernorm_fwd(const void *x, const void *gamma, const void *beta, void *y, float *mean,
+                                   float *rstd, float eps, int64_t n, int64_t rows, int64_t ld, int dtype,
+                                   void *workspace, size_t workspace_bytes, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int st = check_rows(n, rows, ld, dtype);
+    if (st) return st;
+    if (rows == 0 || n == 0) return TB200_OK;
+    if (!x || !y || !gamma) return TB200_ERR_NULL;
+    if (!all_aligned(dtype_size(dtype), {x, y, gamma, beta}) || !all_aligned(4, {mean, rstd})) return TB200_ERR_ALIGN;
+    DeviceInfo dev;
+    if ((st = current_device(&dev))) return st;
+    const Schedule s = plan_rows(OP_LN_FWD, n, rows, ld, dtype, all_aligned(16, {x, y, gamma, beta}));
+    RowArgs a{};
+    a.in0 = x; a.gamma = gamma; a.beta = beta; a.out0 = y; a.stat0 = mean; a.stat1 = rstd; a.eps = eps;
+    a.n = static_cast<int>(n); a.rows = rows; a.ld = ld; a.tpr = s.tpr; a.rpc = s.rpc; a.splits = s.splits;
+    if (!s.split) return launch_resident(pick<LayernormFwdResident>(dtype, s), s, dev, a, stream);
+    if (!workspace_ok(workspace, workspace_bytes, split_state_bytes(s, rows))) return TB200_ERR_WORKSPACE;
+    a.part0 = static_cast<float *>(workspace);
+    if ((st = launch_split(pick<LayernormSplitFold>(dtype, s), s, a, stream))) return st;
+    return launch_split(pick<LayernormFwdSplitWrite>(dtype, s), s, a, stream);
+}
+
+extern "C" int tb200_layernorm_bwd(const void *x, const void *gamma, const void *dy, const float *mean,
+                                   const float *rstd, void *dx, void *dgamma, void *dbeta, float eps, int64_t n,
+                                   int64_t rows, int64_t ld, int dtype, void *workspace, size_t workspace_bytes,
+                                   void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int st = check_rows(n, rows, ld, dtype);
+    if (st) return st;
+    if (n == 0) return TB200_OK;
+    if (rows == 0) {  // sums over no rows are zero
+        if (dgamma) TB200_CUDA(cudaMemsetAsync(dgamma, 0, n * dtype_size(dtype), stream));
+        if (dbeta) TB200_CUDA(cudaMemsetAsync(dbeta, 0, n * dtype_size(dtype), stream));
+        return TB200_OK;
+    }
+    if (!x || !gamma || !dy || !dx) return TB200_ERR_NULL;
+    if (!all_aligned(dtype_size(dtype), {x, gamma, dy, dx, dgamma, dbeta}) || !all_aligned(4, {mean, rstd}))
+        return TB200_ERR_ALIGN;
+    DeviceInfo dev;
+    if ((st = current_device(&dev))) return st;
+    const Schedule s = plan_rows(OP_LN_BWD, n, rows, ld, dtype, all_aligned(16, {x, gamma, dy, dx}));
+    if (s.split) return TB200_ERR_UNSUPPORTED;
+    RowArgs a{};
+    a.in0 = x; a.in1 = dy; a.gamma = gamma; a.out0 = dx; a.cstat0 = mean; a.cstat1 = rstd; a.eps = eps;
+    a.n = static_cast<int>(n); a.rows = rows; a.ld = ld; a.tpr = s.tpr; a.rpc = s.rpc; a.splits = 1;
+    const RowKernel kernel = pick<LayernormBwdResident>(dtype, s);
+    long long grid = 0;
+    if ((st = resident_grid(kernel, s, dev, &grid))) return st;
+    const bool sums = dgamma || dbeta;
+    const size_t part_len = static_cast<size_t>(grid) * s.rpc * static_cast<size_t>(n);
+    if (sums) {
+        if (!workspace_ok(workspace, workspace_bytes, part_len * 2 * sizeof(float))) return TB200_ERR_WORKSPACE;
+        a.part0 = static_cast<float *>(workspace);
+        a.part1 = a.part0 + part_len;
+    }
+    kernel<<<static_cast<unsigned>(grid), s.threads, 0, stream>>>(a);
+    TB200_CUDA(cudaGetLastError());
+    if (sums) {
+        const int parts = static_cast<int>(grid * s.rpc);
+        const unsigned blocks = static_cast<unsigned>(ceil_div(n, 32));
+        if (dtype == TB200_F32)
+            merge_parts<float><<<blocks, 256, 0, stream>>>(a.part0, a.part1, static_cast<float *>(dgamma),
+                                                           static_cast<float *>(dbeta), a.n, parts);
+        else
+            merge_parts<__nv_bfloat16><<<blocks, 256, 0, stream>>>(a.part0, a.part1,
+                                                                   static_cast<__nv_bfloat16 *>(dgamma),
+                                                                   static_cast<__nv_bfloat16 *>(dbeta), a.n, parts);
+        TB200_CUDA(cudaGetLastError());
+    }
+    return TB200_OK;
+}

@@ -1,0 +1,63 @@
+"""Host logic of the plugin mirror (no GPU): templates, supports, estimate, build errors."""
+import pytest
+
+
+@pytest.fixture()
+def I(pkg):
+    return pkg.implement
+
+
+def binding(I, template="softmax_columns", n=4096, rows=8, eltype="Float32", **over):
+    arrays = {"x": I.dense_columns(None, eltype, n, rows, 1), "y": I.dense_columns(None, eltype, n, rows, 2)}
+    arrays.update(over)
+    return I.Binding(template, {"n": n, "rows": rows}, arrays)
+
+
+def test_templates_follow_the_target(I):
+    lib = I.B200Kernels()
+    names = [t.name for t in lib.templates(I.Target(online=True))]
+    assert "softmax_columns" in names and "layernorm_pullback" in names
+    # a target that keeps the two passes is offered nothing (ext/cuDNNExt.jl:60-62)
+    assert lib.templates(I.Target(online=False)) == ()
+
+
+def test_supports(I):
+    lib, t = I.B200Kernels(), I.Target()
+    assert lib.supports(t, binding(I))
+    assert lib.supports(t, binding(I, eltype="BFloat16"))
+    assert not lib.supports(t, binding(I, template="attention"))
+    assert not lib.supports(t, binding(I, y=I.dense_columns(None, "BFloat16", 4096, 8, 2)))  # mixed types
+    strided = I.Strided("Float32", 0, (4096, 8), (2, 8192), None, 2)
+    assert not lib.supports(t, binding(I, y=strided))  # folded axis not contiguous
+    other_ld = I.dense_columns(None, "Float32", 4096, 8, 2, ld=4100)
+    assert not lib.supports(t, binding(I, y=other_ld))  # two leading dimensions
+    both = binding(I, x=I.dense_columns(None, "Float32", 4096, 8, 1, ld=4100), y=other_ld)
+    assert lib.supports(t, both)
+
+
+def test_estimate_counts_algorithmic_bytes(I):
+    lib, t = I.B200Kernels(), I.Target()
+    (w,) = lib.estimate(t, binding(I, n=4096, rows=65536))
+    assert w.bytes == 2 * 4096 * 65536 * 4 and w.launches == 1
+    (w,) = lib.estimate(t, binding(I, template="softmax_columns_pullback", n=4096, rows=65536, eltype="BFloat16"))
+    assert w.bytes == 3 * 4096 * 65536 * 2
+    (w,) = lib.estimate(t, binding(I, n=40000, rows=4))
+    assert w.launches == 2
+
+
+def test_build_refuses_without_buffers(I):
+    lib, t = I.B200Kernels(), I.Target()
+    with pytest.raises(ValueError):
+        lib.build(t, binding(I))
+    with pytest.raises(ValueError):
+        lib.build(t, binding(I, template="attention"))
+
+
+def test_strided_pointer_and_repoint(I):
+    s = I.Strided("BFloat16", 8, (16, 4), (1, 16), 4096, 3)
+    assert s.pointer() == 4096 + 16
+    b = I.Binding("softmax_columns", {"n": 16, "rows": 4}, {"x": s, "y": I.Strided("BFloat16", 0, (16, 4), (1, 16), 8192, 4)})
+    launch = I.RowLaunch(b, 1e-5, None, 0)
+    assert launch.repoints()
+    launch.repoint(3, 65536)
+    assert b.arrays["x"].pointer() == 65536 + 16 and b.arrays["y"].pointer() == 8192
