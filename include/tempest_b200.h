@@ -121,6 +121,94 @@ int tb200_layernorm_bwd(const void *x, const void *gamma, const void *dy, const 
                         int64_t n, int64_t rows, int64_t ld, int dtype, void *workspace,
                         size_t workspace_bytes, void *stream);
 
+/* ---- products with fused epilogues ----------------------------------------
+ * C = epilogue(alpha * A * B), row-major C[M][N].  Replaces the generated
+ * `:product` kernels of ext/cuTileExt/contract.jl:112-161 with their fused
+ * outputs (ext/cuTileExt/build.jl:243-246) and the library calls of
+ * ext/cuBLASExt.jl:247-259 (`cublasGemmStridedBatchedEx`), including its
+ * `accumulated` template D .+ A*B (cuBLASExt.jl:25-29).
+ *
+ * Operand layouts cover cuBLAS's four transposes (cuBLASExt.jl:70-80): an
+ * operand is K-major when its contracted axis is contiguous (A stored [M][K],
+ * B stored [N][K]) and MN-major otherwise (A stored [K][M], B stored [K][N]).
+ * A Julia `w::(out,in)` is memory [in][out]: for y = w*x it is an MN-major B.
+ */
+typedef enum tb200_layout {
+    TB200_K_MAJOR = 0,
+    TB200_MN_MAJOR = 1
+} tb200_layout;
+
+typedef enum tb200_epilogue {
+    TB200_EPI_NONE = 0,          /* alpha * acc */
+    TB200_EPI_BIAS = 1,          /* alpha * acc + bias[n] */
+    TB200_EPI_BIAS_GELU = 2,     /* gelu_tanh(alpha * acc + bias[n]); aux_out <- the value before gelu */
+    TB200_EPI_BIAS_TANH = 3,     /* tanh(alpha * acc + bias[n]) */
+    TB200_EPI_MUL_GELU_GRAD = 4, /* alpha * acc * gelu_tanh'(aux[m][n]): the pullback through the activation */
+    TB200_EPI_MUL_TANH_GRAD = 5, /* alpha * acc * (1 - aux[m][n]^2), aux = tanh's output */
+    TB200_EPI_AXPY = 6           /* aux[m][n] + alpha * acc (aux in the output type; may alias C) */
+} tb200_epilogue;
+
+typedef struct tb200_gemm_desc {
+    int64_t m, n, k;
+    int64_t lda, ldb, ldc;       /* leading dimensions in elements */
+    int64_t ld_aux, ld_aux_out;
+    int a_layout, b_layout;      /* tb200_layout */
+    int in_dtype, out_dtype;     /* tb200_dtype; bias and aux have in_dtype (aux of AXPY: out_dtype) */
+    int epilogue;                /* tb200_epilogue */
+    float alpha;
+    int tile_n;                  /* 0 = choose; 128 or 256 = the variant the tuner picked
+                                    (the counterpart of TEMPEST_PRODUCT_TILE, ext/cuTileExt/contract.jl:36-49) */
+    int force_simt;              /* 1 = the generic kernel (Float32-exact, any alignment) */
+} tb200_gemm_desc;
+
+/* Enqueues the product.  BFloat16 operands with 16-byte aligned bases and
+ * leading dimensions that are multiples of 8 run on the tensor cores
+ * (tcgen05, Float32 accumulation, one rounding at the store); everything else
+ * runs the generic kernel.  The tensor-core path builds its TMA descriptors
+ * from the raw pointers on every call and passes them as kernel parameters. */
+int tb200_gemm(const tb200_gemm_desc *desc, const void *a, const void *b, void *c, const void *bias,
+               const void *aux, void *aux_out, void *stream);
+
+/* Synchronises the device, then returns and clears the code a tensor-core
+ * kernel recorded if one of its bounded waits gave up (0 = none).  No
+ * reference counterpart: Tempest's kernels have no device-side waits. */
+int tb200_device_error(void);
+
+/* ---- pointwise maps and folds over other axes -------------------------------
+ * These replace the generated `:pointwise` kernels (ext/cuTileExt/build.jl:3-10)
+ * and the full / partial folds with their merge launches
+ * (ext/cuTileExt/build.jl:560-705) for the loss, bias-gradient and update
+ * groups of a training step (examples/mlp.jl:28-35). */
+
+/* Clears a workspace (the squared-error ticket must start at zero; every call
+ * leaves it zero again).  No reference counterpart. */
+int tb200_workspace_clear(void *workspace, size_t workspace_bytes, void *stream);
+
+size_t tb200_squared_error_workspace_bytes(void);
+
+/* loss[0] = scale * sum((a - b)^2) (b NULL: sum(a^2), the README's
+ * sum(abs2, ...)), and, when grad is not NULL, the loss's pullback
+ * grad = grad_scale * 2 (a - b), times (1 - a^2) when through_tanh (a is a
+ * tanh's output: src/Compiler/program/differentiate.jl:127, 134).  The sum is
+ * merged in a fixed order.  workspace: tb200_squared_error_workspace_bytes
+ * bytes, cleared once before its first use. */
+int tb200_squared_error(const void *a, const void *b, void *grad, float *loss, int64_t count,
+                        float scale, float grad_scale, int through_tanh, int dtype, void *workspace,
+                        size_t workspace_bytes, void *stream);
+
+size_t tb200_colsum_workspace_bytes(int64_t rows, int64_t n);
+
+/* out[j] = scale * sum over rows of x[r][j]: the bias gradient, a fold over the
+ * axis that is not contiguous (the reference's partial folds + merge,
+ * ext/cuTileExt/emit.jl:744-753).  Float32 accumulation, fixed order. */
+int tb200_colsum(const void *x, void *out, int64_t rows, int64_t n, int64_t ld, float scale,
+                 int dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/* y[i] += alpha * x[i]: the update w .- rate .* dw (examples/mlp.jl:32-35).
+ * y and x 16-byte aligned. */
+int tb200_axpy(void *y, const void *x, float alpha, int64_t count, int y_dtype, int x_dtype,
+               void *stream);
+
 #ifdef __cplusplus
 }
 #endif

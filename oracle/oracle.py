@@ -277,3 +277,47 @@ def layernorm_bwd_f64(x, gamma, g, eps=1e-5):
     gh = g * gamma
     dx = rstd * (gh - gh.mean(axis=1, keepdims=True) - xh * (gh * xh).mean(axis=1, keepdims=True))
     return dx, (g * xh).sum(axis=0), g.sum(axis=0)
+
+
+# ------------------------------------------------------------ MLP step ----
+
+def _gelu_grad_f32(z):
+    z = z.astype(np.float32)
+    u = np.float32(0.7978846) * (z + np.float32(0.044715) * z * z * z)
+    t = np.tanh(u)
+    du = np.float32(0.7978846) * (np.float32(1.0) + np.float32(3.0 * 0.044715) * z * z)
+    return (np.float32(0.5) * (1 + t) + np.float32(0.5) * z * (1 - t * t) * du).astype(np.float32)
+
+
+def mlp_step(ws, bs, x, y, rate, global_batch=None):
+    """One training step of examples/mlp.jl:13-35 with GELU(tanh) between layers
+    (test/fixtures/programs.jl:19), BFloat16 arrays (uint16 bit patterns), every
+    product accumulated in Float32 and rounded once (program/interpret.jl:59-63),
+    every stored array rounded to BFloat16, everything in between Float32.
+    ws[i] is a Julia (out, in) weight, i.e. numpy [in][out]; x [batch][in]; y [batch][out].
+    Returns loss, [dz], [dw (Float32, before rounding)], [db (Float32)], new ws, new bs."""
+    L = len(ws)
+    batch = x.shape[0]
+    gb = global_batch or batch
+    a, z = [x], []
+    for i in range(L):
+        fin, fout = ws[i].shape
+        out, pre = gemm(a[-1], ws[i], bias=bs[i], M=batch, N=fout, K=fin, a_km=False, b_kn=True,
+                        epilogue=1 if i == L - 1 else 2, want_pre=True)
+        a.append(out)
+        z.append(to_bf16(pre))
+    d = from_bf16(a[-1]) - from_bf16(y)
+    loss = float(np.sum(d.astype(np.float64) ** 2) / gb)
+    dz = [None] * L
+    dz[L - 1] = to_bf16((np.float32(1.0 / gb) * (np.float32(2.0) * d)).astype(np.float32))
+    dws, dbs, new_w, new_b = [None] * L, [None] * L, [None] * L, [None] * L
+    for i in range(L - 1, -1, -1):
+        fin, fout = ws[i].shape
+        if i > 0:
+            _, acc = gemm(dz[i], ws[i], M=batch, N=fin, K=fout, a_km=False, b_kn=False, epilogue=0, want_pre=True)
+            dz[i - 1] = to_bf16(acc * _gelu_grad_f32(from_bf16(z[i - 1])))
+        dbs[i] = from_bf16(dz[i]).astype(np.float64).sum(axis=0).astype(np.float32)
+        _, dws[i] = gemm(a[i], dz[i], M=fin, N=fout, K=batch, a_km=True, b_kn=True, epilogue=0, want_pre=True)
+        new_w[i] = to_bf16(from_bf16(ws[i]) - np.float32(rate) * dws[i])
+        new_b[i] = to_bf16(from_bf16(bs[i]) - np.float32(rate) * from_bf16(to_bf16(dbs[i])))
+    return loss, dz, dws, dbs, new_w, new_b, a, z

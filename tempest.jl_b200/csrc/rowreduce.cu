@@ -179,18 +179,16 @@ __global__ void __launch_bounds__(kResidentMaxThreads) softmax_bwd_resident(RowA
 }
 
 template <typename T, bool VEC, int VPT>
-__global__ void __launch_bounds__(kResidentMaxThreads) layernorm_fwd_resident(RowArgs a) {
+__global__ void __launch_bounds__(kResidentMaxThreads, 2) layernorm_fwd_resident(RowArgs a) {
     using R = Row<T, VEC, VPT>;
     __shared__ float red[2 * 32 * kRedWidth];
     RowCtx c = make_row_ctx(a.tpr, red);
     const T *x = static_cast<const T *>(a.in0);
     T *y = static_cast<T *>(a.out0);
-    float gam[R::E], bet[R::E];
-    R::load_cached(gam, static_cast<const T *>(a.gamma), a.n, c.t, a.tpr, 0.0f);
-    if (a.beta) R::load_cached(bet, static_cast<const T *>(a.beta), a.n, c.t, a.tpr, 0.0f);
-    else
-#pragma unroll
-        for (int e = 0; e < R::E; e++) bet[e] = 0.0f;
+    // gamma and beta (a few KB, shared by every row) are re-read through L1 for
+    // each row rather than pinned in registers: the registers buy occupancy
+    const T *gamma = static_cast<const T *>(a.gamma);
+    const T *beta = static_cast<const T *>(a.beta);
     const float fn = static_cast<float>(a.n);
     const long long groups = (a.rows + a.rpc - 1) / a.rpc;
     for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
@@ -220,7 +218,17 @@ __global__ void __launch_bounds__(kResidentMaxThreads) layernorm_fwd_resident(Ro
             if (a.stat1) static_cast<float *>(a.stat1)[r] = rstd;
         }
 #pragma unroll
-        for (int e = 0; e < R::E; e++) v[e] = fmaf(v[e] * rstd, gam[e], bet[e]);
+        for (int k = 0; k < VPT; k++) {
+            const int idx = R::at(k, c.t, a.tpr);
+            if (idx < a.n) {
+                float gam[R::EPV], bet[R::EPV];
+                R::A::load_cached(gamma + idx, gam);
+                if (beta) R::A::load_cached(beta + idx, bet);
+#pragma unroll
+                for (int e = 0; e < R::EPV; e++)
+                    v[k * R::EPV + e] = fmaf(v[k * R::EPV + e] * rstd, gam[e], beta ? bet[e] : 0.0f);
+            }
+        }
         R::store(v, y + r * a.ld, a.n, c.t, a.tpr, live);
     }
 }
@@ -280,7 +288,7 @@ __global__ void __launch_bounds__(kResidentMaxThreads) layernorm_bwd_resident(Ro
         row_allreduce<2>(s2, c, SumOp());
         const float c1 = s2[0] / fn, c2 = s2[1] / fn;
 #pragma unroll
-        for (int e = 0; e < R::E; e++) d[e] = rstd * (fmaf(d[e], gam[e], -c1) - v[e] * c2);
+        for (int e = 0; e < R::E; e++) d[e] = rstd * ((__fmul_rn(d[e], gam[e]) - c1) - v[e] * c2);
         R::store(d, dx + r * a.ld, a.n, c.t, a.tpr, live);
     }
     if (a.part0) {

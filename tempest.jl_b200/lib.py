@@ -10,11 +10,27 @@ import os
 F32, BF16 = 0, 1
 SOFTMAX_FWD, SOFTMAX_BWD, LAYERNORM_FWD, LAYERNORM_BWD = 0, 1, 2, 3
 
+K_MAJOR, MN_MAJOR = 0, 1
+EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_TANH, EPI_MUL_GELU_GRAD, EPI_MUL_TANH_GRAD, EPI_AXPY = range(7)
+
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtempest_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "tempest_b200.h")
 
 _p, _i, _i64, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
+
+
+
+class GemmDesc(ctypes.Structure):
+    """tb200_gemm_desc of include/tempest_b200.h."""
+    _fields_ = [("m", ctypes.c_int64), ("n", ctypes.c_int64), ("k", ctypes.c_int64),
+                ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64),
+                ("ld_aux", ctypes.c_int64), ("ld_aux_out", ctypes.c_int64),
+                ("a_layout", ctypes.c_int), ("b_layout", ctypes.c_int),
+                ("in_dtype", ctypes.c_int), ("out_dtype", ctypes.c_int),
+                ("epilogue", ctypes.c_int), ("alpha", ctypes.c_float),
+                ("tile_n", ctypes.c_int), ("force_simt", ctypes.c_int)]
+
 
 # name -> (restype, argtypes): the declarations of include/tempest_b200.h
 SIGNATURES = {
@@ -27,6 +43,14 @@ SIGNATURES = {
     "tb200_softmax_bwd": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i, _i, _p, _sz, _p]),
     "tb200_layernorm_fwd": (_i, [_p, _p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i, _p, _sz, _p]),
     "tb200_layernorm_bwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i, _p, _sz, _p]),
+    "tb200_gemm": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
+    "tb200_device_error": (_i, []),
+    "tb200_workspace_clear": (_i, [_p, _sz, _p]),
+    "tb200_squared_error_workspace_bytes": (_sz, []),
+    "tb200_squared_error": (_i, [_p, _p, _p, _p, _i64, _f, _f, _i, _i, _p, _sz, _p]),
+    "tb200_colsum_workspace_bytes": (_sz, [_i64, _i64]),
+    "tb200_colsum": (_i, [_p, _p, _i64, _i64, _i64, _f, _i, _p, _sz, _p]),
+    "tb200_axpy": (_i, [_p, _p, _f, _i64, _i, _i, _p]),
 }
 
 
@@ -105,3 +129,58 @@ def layernorm_bwd(x, gamma, dy, mean, rstd, dx, dgamma, dbeta, eps, n, rows, ld,
     check("tb200_layernorm_bwd", load().tb200_layernorm_bwd(
         x, gamma, dy, mean or None, rstd or None, dx, dgamma or None, dbeta or None, eps, n, rows, ld, dtype,
         workspace or None, workspace_bytes, stream or None))
+
+
+def gemm(a, b, c, m, n, k, *, lda=None, ldb=None, ldc=None, a_layout=K_MAJOR, b_layout=MN_MAJOR, in_dtype=BF16,
+         out_dtype=None, epilogue=EPI_NONE, bias=0, aux=0, ld_aux=None, aux_out=0, ld_aux_out=None, alpha=1.0,
+         tile_n=0, force_simt=False, stream=0):
+    """C[m][n] = epilogue(alpha * A * B).  a_layout K_MAJOR: A is [m][k]; MN_MAJOR: [k][m].
+    b_layout K_MAJOR: B is [n][k]; MN_MAJOR: [k][n] (a Julia (out,in) weight for y = w*x)."""
+    d = GemmDesc()
+    d.m, d.n, d.k = m, n, k
+    d.lda = lda if lda is not None else (m if a_layout == MN_MAJOR else k)
+    d.ldb = ldb if ldb is not None else (n if b_layout == MN_MAJOR else k)
+    d.ldc = ldc if ldc is not None else n
+    d.ld_aux = ld_aux if ld_aux is not None else n
+    d.ld_aux_out = ld_aux_out if ld_aux_out is not None else n
+    d.a_layout, d.b_layout = a_layout, b_layout
+    d.in_dtype = in_dtype
+    d.out_dtype = in_dtype if out_dtype is None else out_dtype
+    d.epilogue, d.alpha, d.tile_n, d.force_simt = epilogue, alpha, tile_n, int(force_simt)
+    check("tb200_gemm", load().tb200_gemm(ctypes.byref(d), a or None, b or None, c or None, bias or None,
+                                          aux or None, aux_out or None, stream or None))
+
+
+def device_error():
+    code = load().tb200_device_error()
+    if code < 0:
+        check("tb200_device_error", code)
+    return code
+
+
+def workspace_clear(workspace, nbytes, stream=0):
+    check("tb200_workspace_clear", load().tb200_workspace_clear(workspace, nbytes, stream or None))
+
+
+def squared_error_workspace_bytes():
+    return load().tb200_squared_error_workspace_bytes()
+
+
+def squared_error(a, b, grad, loss, count, scale, grad_scale, through_tanh, dtype, workspace, workspace_bytes,
+                  stream=0):
+    check("tb200_squared_error", load().tb200_squared_error(
+        a, b or None, grad or None, loss, count, scale, grad_scale, int(through_tanh), dtype, workspace,
+        workspace_bytes, stream or None))
+
+
+def colsum_workspace_bytes(rows, n):
+    return load().tb200_colsum_workspace_bytes(rows, n)
+
+
+def colsum(x, out, rows, n, ld, scale, dtype, workspace, workspace_bytes, stream=0):
+    check("tb200_colsum", load().tb200_colsum(x, out, rows, n, ld, scale, dtype, workspace or None, workspace_bytes,
+                                              stream or None))
+
+
+def axpy(y, x, alpha, count, y_dtype, x_dtype, stream=0):
+    check("tb200_axpy", load().tb200_axpy(y, x, alpha, count, y_dtype, x_dtype, stream or None))

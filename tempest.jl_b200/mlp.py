@@ -1,0 +1,157 @@
+"""The MLP training step of examples/mlp.jl on the B200 kernels.
+
+The reference spells it as plain Julia (examples/mlp.jl:13-35): layers
+`h = act.(w * h .+ b)` with no activation after the last, loss
+`sum(abs2, forward(x) .- y) / size(y, 2)`, `withgradient`, and the update
+`w .- rate .* dw`, `b .- rate .* db`; `Tempest.compile` turns the step into
+kernels.  Here the same step is the kernel list a Tempest plan of it reaches:
+
+  forward   one product per layer with the bias and activation fused in its
+            epilogue (the value before the activation kept for the backward),
+  loss      one squared-error fold that also writes the loss's pullback,
+  backward  per layer, last first: db = column sums of dz; dw = h_in' * dz;
+            dz_below = (dz * w') .* act'(z_below) fused in the product's
+            epilogue; and the update either fused into dw's epilogue
+            (w = w - rate * dw, single GPU) or applied after the gradients of
+            all replicas are summed (data parallel).
+
+Layout: a Julia `w::(out,in)` is memory [in][out]; activations `(features,
+batch)` are memory [batch][features].  All arrays BFloat16, Float32 accumulate.
+
+Data parallel (one process per GPU): each replica runs the step on its batch
+shard; gradients go into one flat BFloat16 bucket per layer, summed across
+replicas by an NCCL all-reduce issued on a side stream as soon as the layer's
+gradients exist (last layer first), overlapping the remaining backward
+products; the update runs when the bucket has landed.  The MSE is a mean over
+the global batch, so each replica scales its pullback by 1 / global batch.
+"""
+from . import lib
+
+ACTIVATIONS = {"gelu_tanh": (lib.EPI_BIAS_GELU, lib.EPI_MUL_GELU_GRAD, "z"),
+               "tanh": (lib.EPI_BIAS_TANH, lib.EPI_MUL_TANH_GRAD, "a")}
+
+
+def glorot_uniform(torch, fan_in, fan_out, generator, device="cuda"):
+    """W (out, in) ~ U(+-sqrt(6 / (in + out))), stored [in][out] BFloat16."""
+    limit = (6.0 / (fan_in + fan_out)) ** 0.5
+    w = (torch.rand(fan_in, fan_out, device=device, generator=generator) * 2.0 - 1.0) * limit
+    return w.to(torch.bfloat16)
+
+
+class MLPStep:
+    """One compiled training step; `step(x, y)` runs it once."""
+
+    def __init__(self, torch, sizes, batch, rate, activation="gelu_tanh", world=1, global_batch=None,
+                 process_group=None, seed=0, weights=None, biases=None, fuse_update=None):
+        self.torch = torch
+        self.sizes, self.batch, self.rate = list(sizes), batch, rate
+        self.world = world
+        self.global_batch = global_batch if global_batch is not None else batch * world
+        self.group = process_group
+        # the update rides in dw's epilogue unless gradients must first be summed across replicas
+        self.fuse_update = (world == 1) if fuse_update is None else (fuse_update and world == 1)
+        self.fwd_epi, self.bwd_epi, self.saved = ACTIVATIONS[activation]
+        bf = torch.bfloat16
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        L = len(sizes) - 1
+        self.L = L
+        self.w = [glorot_uniform(torch, sizes[i], sizes[i + 1], gen) for i in range(L)] if weights is None \
+            else [w.clone() for w in weights]
+        self.b = [torch.zeros(sizes[i + 1], device="cuda", dtype=bf) for i in range(L)] if biases is None \
+            else [b.clone() for b in biases]
+        # activations a[i] (input of layer i), z[i] (what layer i's activation saw)
+        self.a = [None] + [torch.empty(batch, sizes[i + 1], device="cuda", dtype=bf) for i in range(L)]
+        self.z = [torch.empty(batch, sizes[i + 1], device="cuda", dtype=bf) if self.saved == "z" and i < L - 1
+                  else None for i in range(L)]
+        self.dz = [torch.empty(batch, sizes[i + 1], device="cuda", dtype=bf) for i in range(L)]
+        self.loss = torch.zeros(1, device="cuda", dtype=torch.float32)
+        # per-layer gradient buckets: dw then db, contiguous, so one all-reduce moves both
+        self.bucket = [torch.empty(sizes[i] * sizes[i + 1] + sizes[i + 1], device="cuda", dtype=bf) for i in range(L)]
+        self.dw = [self.bucket[i][: sizes[i] * sizes[i + 1]].view(sizes[i], sizes[i + 1]) for i in range(L)]
+        self.db = [self.bucket[i][sizes[i] * sizes[i + 1]:] for i in range(L)]
+        self.sq_ws_bytes = lib.squared_error_workspace_bytes()
+        self.sq_ws = torch.zeros(self.sq_ws_bytes, device="cuda", dtype=torch.uint8)
+        cs = max(lib.colsum_workspace_bytes(batch, sizes[i + 1]) for i in range(L))
+        self.cs_ws_bytes = cs
+        self.cs_ws = torch.empty(max(cs, 16), device="cuda", dtype=torch.uint8)
+        self.comm_stream = torch.cuda.Stream() if world > 1 else None
+        self.launches = 0
+
+    def parameters(self):
+        return self.w, self.b
+
+    # ---- forward + loss -------------------------------------------------
+    def forward(self, x, stream):
+        bf16 = lib.BF16
+        h = x
+        for i in range(self.L):
+            fin, fout = self.sizes[i], self.sizes[i + 1]
+            last = i == self.L - 1
+            lib.gemm(h.data_ptr(), self.w[i].data_ptr(), self.a[i + 1].data_ptr(), self.batch, fout, fin,
+                     a_layout=lib.K_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=bf16,
+                     epilogue=lib.EPI_BIAS if last else self.fwd_epi, bias=self.b[i].data_ptr(),
+                     aux_out=0 if (last or self.z[i] is None) else self.z[i].data_ptr(), stream=stream)
+            h = self.a[i + 1]
+            self.launches += 1
+        return h
+
+    def step(self, x, y):
+        """x [batch][in], y [batch][out] BFloat16 on the device.  Returns the
+        loss tensor (1 Float32 on the device; its value is this replica's share
+        of the global mean when data parallel)."""
+        torch = self.torch
+        cur = torch.cuda.current_stream()
+        stream = cur.cuda_stream
+        bf16 = lib.BF16
+        self.a[0] = x
+        out = self.forward(x, stream)
+        L = self.L
+        # loss = sum(abs2, out - y) / batch ; dz_last = 2 (out - y) / batch
+        inv = 1.0 / self.global_batch
+        lib.squared_error(out.data_ptr(), y.data_ptr(), self.dz[L - 1].data_ptr(), self.loss.data_ptr(),
+                          out.numel(), inv, inv, False, bf16, self.sq_ws.data_ptr(), self.sq_ws_bytes, stream)
+        self.launches += 1
+        events = []
+        for i in range(L - 1, -1, -1):
+            fin, fout = self.sizes[i], self.sizes[i + 1]
+            dz = self.dz[i]
+            if i > 0:
+                # dz_below = (dz * w') .* act'(saved): A = dz [batch][fout], B = w as [n = fin][k = fout]
+                saved = self.z[i - 1] if self.saved == "z" else self.a[i]
+                lib.gemm(dz.data_ptr(), self.w[i].data_ptr(), self.dz[i - 1].data_ptr(), self.batch, fin, fout,
+                         a_layout=lib.K_MAJOR, b_layout=lib.K_MAJOR, in_dtype=bf16, epilogue=self.bwd_epi,
+                         aux=saved.data_ptr(), stream=stream)
+                self.launches += 1
+            lib.colsum(dz.data_ptr(), self.db[i].data_ptr(), self.batch, fout, fout, 1.0, bf16,
+                       self.cs_ws.data_ptr(), self.cs_ws_bytes, stream)
+            self.launches += 2
+            if self.fuse_update:
+                # w = w - rate * (a_in' * dz): the update rides in the product's epilogue
+                lib.gemm(self.a[i].data_ptr(), dz.data_ptr(), self.w[i].data_ptr(), fin, fout, self.batch,
+                         a_layout=lib.MN_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=bf16, epilogue=lib.EPI_AXPY,
+                         aux=self.w[i].data_ptr(), alpha=-self.rate, stream=stream)
+                lib.axpy(self.b[i].data_ptr(), self.db[i].data_ptr(), -self.rate, fout, bf16, bf16, stream)
+                self.launches += 2
+            else:
+                lib.gemm(self.a[i].data_ptr(), dz.data_ptr(), self.dw[i].data_ptr(), fin, fout, self.batch,
+                         a_layout=lib.MN_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=bf16, stream=stream)
+                self.launches += 1
+                done = None
+                if self.world > 1:
+                    ready = torch.cuda.Event()
+                    ready.record(cur)
+                    with torch.cuda.stream(self.comm_stream):
+                        self.comm_stream.wait_event(ready)
+                        torch.distributed.all_reduce(self.bucket[i], group=self.group)
+                        done = torch.cuda.Event()
+                        done.record(self.comm_stream)
+                events.append((i, done))
+        for i, done in events:
+            if done is not None:
+                cur.wait_event(done)
+            n = self.bucket[i].numel()
+            nw = self.sizes[i] * self.sizes[i + 1]
+            lib.axpy(self.w[i].data_ptr(), self.dw[i].data_ptr(), -self.rate, nw, bf16, bf16, stream)
+            lib.axpy(self.b[i].data_ptr(), self.db[i].data_ptr(), -self.rate, n - nw, bf16, bf16, stream)
+            self.launches += 2
+        return self.loss

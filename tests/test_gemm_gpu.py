@@ -1,0 +1,267 @@
+"""Products with fused epilogues through the C ABI against the CPU oracle:
+the reference's product tests' shapes (test/cuda/products.jl:9-64: 96x80 * 80x112
+with a GELU epilogue, split-K 64x3000 * 3000x48, layouts NN/TN/NT/TT, BFloat16
+with a cast in the epilogue), ragged edges, both tile variants, and the
+benchmark's layer shapes against a plain Float32 matmul of the same inputs."""
+import numpy as np
+import pytest
+
+from helpers import ATOL_BF16, RTOL_F32, agree
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(torch, a):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    return (t.view(torch.bfloat16) if a.dtype == np.uint16 else t).cuda()
+
+
+def host(torch, t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.cpu().numpy()
+
+
+def operands(oracle, M, N, K, a_mn, b_mn, seed, bf16):
+    A = oracle.normal((K, M) if a_mn else (M, K), seed)
+    B = oracle.normal((K, N) if b_mn else (N, K), seed + 1)
+    if bf16:
+        A, B = oracle.to_bf16(A), oracle.to_bf16(B)
+    return A, B
+
+
+def close_bf16(oracle, got_bits, want_f32, k):
+    """2e-2 max-abs against the Float32 CPU reference, scaled by the product's
+    magnitude sqrt(K) for N(0,1) factors (the tolerance is stated for O(1) results)."""
+    got = oracle.from_bf16(got_bits).astype(np.float64)
+    want = np.asarray(want_f32, np.float64)
+    scale = max(1.0, np.abs(want).max())
+    worst = np.abs(got - want).max()
+    assert worst <= ATOL_BF16 * scale, f"max-abs {worst:.3e} vs {ATOL_BF16 * scale:.3e}"
+
+
+LAYOUTS = [(False, False), (False, True), (True, False), (True, True)]
+SHAPES = [(96, 112, 80), (128, 256, 64), (200, 136, 200), (64, 48, 3000), (256, 512, 320), (8, 8, 8), (130, 264, 72)]
+
+
+@pytest.mark.parametrize("a_mn,b_mn", LAYOUTS)
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_bf16_tensor_core_product(pkg, cuda, oracle, M, N, K, a_mn, b_mn):
+    L = pkg.lib
+    A, B = operands(oracle, M, N, K, a_mn, b_mn, 1000 + M + K, True)
+    want = oracle.gemm(A, B, M=M, N=N, K=K, a_km=a_mn, b_kn=b_mn, want_pre=True)[1]
+    Ad, Bd = dev(cuda, A), dev(cuda, B)
+    for tile_n in (128, 256):
+        C = cuda.full((M, N), float("nan"), device="cuda", dtype=cuda.bfloat16)
+        L.gemm(Ad.data_ptr(), Bd.data_ptr(), C.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn),
+               tile_n=tile_n, stream=cuda.cuda.current_stream().cuda_stream)
+        assert L.device_error() == 0
+        close_bf16(oracle, host(cuda, C), want, K)
+        # and Float32 output of the same accumulators: tight, the only difference is summation order
+        C32 = cuda.empty((M, N), device="cuda")
+        L.gemm(Ad.data_ptr(), Bd.data_ptr(), C32.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn),
+               out_dtype=L.F32, tile_n=tile_n)
+        assert L.device_error() == 0
+        agree(C32.cpu().numpy(), want, 1e-5)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", LAYOUTS)
+def test_generic_kernel_float32(pkg, cuda, oracle, a_mn, b_mn):
+    L = pkg.lib
+    M, N, K = 96, 112, 80
+    A, B = operands(oracle, M, N, K, a_mn, b_mn, 7, False)
+    Ad, Bd = dev(cuda, A), dev(cuda, B)
+    C = cuda.empty((M, N), device="cuda")
+    L.gemm(Ad.data_ptr(), Bd.data_ptr(), C.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn),
+           in_dtype=L.F32)
+    agree(C.cpu().numpy(), oracle.gemm(A, B, M=M, N=N, K=K, a_km=a_mn, b_kn=b_mn), RTOL_F32)
+    # odd sizes and leading dimensions, BFloat16 through the generic kernel
+    M, N, K = 33, 45, 51
+    A, B = operands(oracle, M, N, K, a_mn, b_mn, 9, True)
+    C = cuda.empty((M, N), device="cuda", dtype=cuda.bfloat16)
+    L.gemm(dev(cuda, A).data_ptr(), dev(cuda, B).data_ptr(), C.data_ptr(), M, N, K, a_layout=int(a_mn),
+           b_layout=int(b_mn))
+    close_bf16(oracle, host(cuda, C), oracle.gemm(A, B, M=M, N=N, K=K, a_km=a_mn, b_kn=b_mn, want_pre=True)[1], K)
+
+
+@pytest.mark.parametrize("force_simt", [False, True])
+def test_epilogues(pkg, cuda, oracle, force_simt):
+    L = pkg.lib
+    M, N, K = 200, 136, 96
+    A, B = operands(oracle, M, N, K, False, True, 21, True)
+    A = oracle.to_bf16(oracle.from_bf16(A) * 0.1)
+    bias = oracle.to_bf16(oracle.normal((N,), 23))
+    Ad, Bd, bd = dev(cuda, A), dev(cuda, B), dev(cuda, bias)
+    acc = oracle.gemm(A, B, M=M, N=N, K=K, want_pre=True)[1]
+    pre = acc + oracle.from_bf16(bias)
+    run = dict(a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR, force_simt=force_simt)
+
+    def call(**kw):
+        C = cuda.empty((M, N), device="cuda", dtype=cuda.bfloat16)
+        L.gemm(Ad.data_ptr(), Bd.data_ptr(), C.data_ptr(), M, N, K, **run, **kw)
+        assert L.device_error() == 0
+        return C
+
+    close_bf16(oracle, host(cuda, call(epilogue=L.EPI_BIAS, bias=bd.data_ptr())), pre, K)
+    Z = cuda.empty((M, N), device="cuda", dtype=cuda.bfloat16)
+    got = call(epilogue=L.EPI_BIAS_GELU, bias=bd.data_ptr(), aux_out=Z.data_ptr())
+    gelu = np.vectorize(oracle.gelu_tanh)(pre)
+    close_bf16(oracle, host(cuda, got), gelu, K)
+    close_bf16(oracle, host(cuda, Z), pre, K)
+    close_bf16(oracle, host(cuda, call(epilogue=L.EPI_BIAS_TANH, bias=bd.data_ptr())), np.tanh(pre), K)
+    aux = oracle.to_bf16(oracle.normal((M, N), 29))
+    auxd = dev(cuda, aux)
+    grad = np.vectorize(oracle.gelu_tanh_grad)(oracle.from_bf16(aux))
+    close_bf16(oracle, host(cuda, call(epilogue=L.EPI_MUL_GELU_GRAD, aux=auxd.data_ptr())), acc * grad, K)
+    t = np.tanh(oracle.from_bf16(aux))
+    tb = oracle.to_bf16(t.astype(np.float32))
+    close_bf16(oracle, host(cuda, call(epilogue=L.EPI_MUL_TANH_GRAD, aux=dev(cuda, tb).data_ptr())),
+               acc * (1 - oracle.from_bf16(tb) ** 2), K)
+    # accumulate into an existing array, scaled: D .+ alpha * A*B (ext/cuBLASExt.jl:25-29), in place
+    D = dev(cuda, aux).clone()
+    L.gemm(Ad.data_ptr(), Bd.data_ptr(), D.data_ptr(), M, N, K, **run, epilogue=L.EPI_AXPY, aux=D.data_ptr(),
+           alpha=-0.5)
+    assert L.device_error() == 0
+    close_bf16(oracle, host(cuda, D), oracle.from_bf16(aux) - 0.5 * acc, K)
+
+
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [
+    (8192, 4096, 1024, False, True),    # layer 1 forward
+    (2048, 4096, 4096, False, False),   # dX
+    (4096, 4096, 2048, True, True),     # dW over a quarter of the batch
+    (1024, 1024, 4096, False, True),    # last layer, narrow tiles
+])
+def test_layer_shapes_against_float32_matmul(pkg, cuda, M, N, K, a_mn, b_mn):
+    """The benchmark's products, too large for the scalar oracle: compared with a plain
+    Float32 matmul of the same BFloat16 inputs (cuBLAS, TF32 off) and by linearity."""
+    torch, L = cuda, pkg.lib
+    torch.backends.cuda.matmul.allow_tf32 = False
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    A = torch.randn((K, M) if a_mn else (M, K), device="cuda", generator=g).bfloat16()
+    B = torch.randn((K, N) if b_mn else (N, K), device="cuda", generator=g).bfloat16()
+    Af = (A.float().t() if a_mn else A.float())
+    Bf = (B.float() if b_mn else B.float().t())
+    want = Af @ Bf
+    C = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
+    L.gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn))
+    assert L.device_error() == 0
+    err = (C.float() - want).abs().max().item()
+    scale = want.abs().max().item()
+    assert err <= 2e-2 * scale, (err, scale)
+    rel = ((C.float() - want).norm() / want.norm()).item()
+    assert rel < 4e-3, rel   # BFloat16 rounding of the result alone is 2^-9 relative
+    C32 = torch.empty((M, N), device="cuda")
+    L.gemm(A.data_ptr(), B.data_ptr(), C32.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn),
+           out_dtype=L.F32)
+    assert L.device_error() == 0
+    assert ((C32 - want).norm() / want.norm()).item() < 2e-5
+
+
+def test_pointwise_and_folds(pkg, cuda, oracle):
+    torch, L = cuda, pkg.lib
+    stream = torch.cuda.current_stream().cuda_stream
+    ws_bytes = L.squared_error_workspace_bytes()
+    ws = torch.zeros(ws_bytes, device="cuda", dtype=torch.uint8)
+    for count, dt in ((64 * 16, torch.float32), (1000003, torch.float32), (8192 * 1024, torch.bfloat16), (77, torch.bfloat16)):
+        g = torch.Generator(device="cuda").manual_seed(count)
+        a = torch.randn(count, device="cuda", generator=g).to(dt)
+        b = torch.randn(count, device="cuda", generator=g).to(dt)
+        grad = torch.empty_like(a)
+        loss = torch.zeros(1, device="cuda")
+        code = L.F32 if dt == torch.float32 else L.BF16
+        for _ in range(2):   # the ticket is left ready for the next call
+            L.squared_error(a.data_ptr(), b.data_ptr(), grad.data_ptr(), loss.data_ptr(), count, 0.25, 0.5, False,
+                            code, ws.data_ptr(), ws_bytes, stream)
+            d = a.double() - b.double()
+            assert abs(loss.item() - 0.25 * (d * d).sum().item()) <= 1e-5 * 0.25 * (d * d).sum().item()
+            tol = 1e-6 if dt == torch.float32 else 2e-2
+            assert (grad.double() - d).abs().max().item() <= tol * max(1.0, d.abs().max().item())
+        # the README's sum(abs2, tanh(z)) and its pullback 2y(1 - y^2)
+        y = torch.tanh(a.float()).to(dt)
+        L.squared_error(y.data_ptr(), 0, grad.data_ptr(), loss.data_ptr(), count, 1.0, 1.0, True, code,
+                        ws.data_ptr(), ws_bytes, stream)
+        yd = y.double()
+        assert abs(loss.item() - (yd * yd).sum().item()) <= 1e-5 * (yd * yd).sum().item()
+        assert (grad.double() - 2 * yd * (1 - yd * yd)).abs().max().item() <= (1e-6 if dt == torch.float32 else 1e-2)
+    # column sums: the bias gradient
+    for rows, n, dt in ((8192, 4096, torch.bfloat16), (100, 33, torch.float32), (1, 8, torch.bfloat16), (5000, 1024, torch.float32)):
+        x = torch.randn(rows, n, device="cuda").to(dt)
+        out = torch.empty(n, device="cuda", dtype=dt)
+        need = L.colsum_workspace_bytes(rows, n)
+        cws = torch.empty(max(need, 16), device="cuda", dtype=torch.uint8)
+        L.colsum(x.data_ptr(), out.data_ptr(), rows, n, n, 1.0, L.F32 if dt == torch.float32 else L.BF16,
+                 cws.data_ptr(), need, stream)
+        want = x.double().sum(dim=0)
+        tol = 1e-5 if dt == torch.float32 else 2 ** -8
+        assert ((out.double() - want).abs() <= tol * want.abs().clamp(min=1.0) * 2).all()
+    # y += alpha x
+    for count in (8, 1003, 4096 * 4096):
+        yv = torch.randn(count, device="cuda").bfloat16()
+        xv = torch.randn(count, device="cuda").bfloat16()
+        want = (yv.float() - 0.125 * xv.float()).bfloat16()
+        L.axpy(yv.data_ptr(), xv.data_ptr(), -0.125, count, L.BF16, L.BF16, stream)
+        assert torch.equal(yv, want)
+
+
+def test_readme_loss_and_gradient(pkg, cuda, oracle):
+    """loss(w,b,x) = sum(abs2, tanh.(w'x .+ b)), w 32x64, b 64, x 32x16, Float32 (README.md:15):
+    the loss and (dw, db, dx) through the C ABI against the oracle's restatement."""
+    torch, L = cuda, pkg.lib
+    stream = torch.cuda.current_stream().cuda_stream
+    I, J, N = 32, 64, 16
+    w, b, x = oracle.normal((J, I), 20261126), oracle.normal((J,), 20261127), oracle.normal((N, I), 20261128)
+    loss_ref, dw_ref, db_ref, dx_ref = oracle.readme_loss_grad(w, b, x)
+    wd, bd, xd = dev(torch, w), dev(torch, b), dev(torch, x)
+    y = torch.empty(N, J, device="cuda")
+    gz = torch.empty(N, J, device="cuda")
+    dw, db, dx = torch.empty(J, I, device="cuda"), torch.empty(J, device="cuda"), torch.empty(N, I, device="cuda")
+    loss = torch.zeros(1, device="cuda")
+    ws_bytes = L.squared_error_workspace_bytes()
+    ws = torch.zeros(ws_bytes, device="cuda", dtype=torch.uint8)
+    f32 = dict(in_dtype=L.F32, stream=stream)
+    # y[n][j] = tanh(sum_i x[n][i] w[j][i] + b[j])
+    L.gemm(xd.data_ptr(), wd.data_ptr(), y.data_ptr(), N, J, I, a_layout=L.K_MAJOR, b_layout=L.K_MAJOR,
+           epilogue=L.EPI_BIAS_TANH, bias=bd.data_ptr(), **f32)
+    L.squared_error(y.data_ptr(), 0, gz.data_ptr(), loss.data_ptr(), N * J, 1.0, 1.0, True, L.F32, ws.data_ptr(),
+                    ws_bytes, stream)
+    # dw[j][i] = sum_n gz[n][j] x[n][i];  dx[n][i] = sum_j gz[n][j] w[j][i];  db[j] = sum_n gz[n][j]
+    L.gemm(gz.data_ptr(), xd.data_ptr(), dw.data_ptr(), J, I, N, a_layout=L.MN_MAJOR, b_layout=L.MN_MAJOR, **f32)
+    L.gemm(gz.data_ptr(), wd.data_ptr(), dx.data_ptr(), N, I, J, a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR, **f32)
+    need = L.colsum_workspace_bytes(N, J)
+    cws = torch.empty(max(need, 16), device="cuda", dtype=torch.uint8)
+    L.colsum(gz.data_ptr(), db.data_ptr(), N, J, J, 1.0, L.F32, cws.data_ptr(), need, stream)
+    torch.cuda.synchronize()
+    assert abs(loss.item() - loss_ref) <= RTOL_F32 * abs(loss_ref)
+    agree(dw.cpu().numpy(), dw_ref, RTOL_F32)
+    agree(db.cpu().numpy(), db_ref, RTOL_F32)
+    agree(dx.cpu().numpy(), dx_ref, RTOL_F32)
+
+
+def test_mlp_step_against_oracle(pkg, cuda, oracle):
+    """A small MLP step (same structure as the benchmark's: GELU(tanh) between layers, bias, MSE,
+    SGD) against the oracle's restatement: loss, every layer's pullback, gradients and the update."""
+    torch = cuda
+    sizes, batch, rate = (64, 128, 96, 32), 48, 1e-3
+    ws = [oracle.to_bf16(0.2 * oracle.normal((sizes[i], sizes[i + 1]), 50 + i)) for i in range(3)]
+    bs = [oracle.to_bf16(0.1 * oracle.normal((sizes[i + 1],), 60 + i)) for i in range(3)]
+    x = oracle.to_bf16(oracle.normal((batch, sizes[0]), 70))
+    y = oracle.to_bf16(oracle.normal((batch, sizes[-1]), 71))
+    loss_ref, dz_ref, dw_ref, db_ref, w_ref, b_ref, a_ref, z_ref = oracle.mlp_step(ws, bs, x, y, rate)
+    for fuse in (False, True):
+        step = pkg.mlp.MLPStep(torch, sizes, batch, rate, weights=[dev(torch, w) for w in ws],
+                               biases=[dev(torch, b) for b in bs], fuse_update=fuse)
+        loss = step.step(dev(torch, x), dev(torch, y))
+        torch.cuda.synchronize()
+        assert pkg.lib.device_error() == 0
+        assert abs(loss.item() - loss_ref) <= 2e-3 * abs(loss_ref)
+        for i in range(3):
+            close_bf16(oracle, host(torch, step.a[i + 1]), oracle.from_bf16(a_ref[i + 1]), sizes[i])
+            close_bf16(oracle, host(torch, step.dz[i]), oracle.from_bf16(dz_ref[i]), 1)
+            ref = oracle.from_bf16(dz_ref[i])
+            assert np.linalg.norm(oracle.from_bf16(host(torch, step.dz[i])) - ref) <= 1e-2 * np.linalg.norm(ref)
+            close_bf16(oracle, host(torch, step.w[i]), oracle.from_bf16(w_ref[i]), 1)
+            close_bf16(oracle, host(torch, step.b[i]), oracle.from_bf16(b_ref[i]), 1)
+            got_db = oracle.from_bf16(host(torch, step.db[i]))
+            assert np.abs(got_db - db_ref[i]).max() <= 2e-2 * max(1.0, np.abs(db_ref[i]).max())
+            if not fuse:
+                got = oracle.from_bf16(host(torch, step.dw[i]))
+                rel = np.linalg.norm(got - dw_ref[i]) / np.linalg.norm(dw_ref[i])
+                assert rel < 5e-3, rel
