@@ -159,6 +159,8 @@ typedef struct tb200_gemm_desc {
     int tile_n;                  /* 0 = choose; 128 or 256 = the variant the tuner picked
                                     (the counterpart of TEMPEST_PRODUCT_TILE, ext/cuTileExt/contract.jl:36-49) */
     int force_simt;              /* 1 = the generic kernel (Float32-exact, any alignment) */
+    int direct_epilogue;         /* 1 = each thread stores its own output row instead of staging
+                                    tiles through shared memory for TMA stores (a tuner variant) */
 } tb200_gemm_desc;
 
 /* Enqueues the product.  BFloat16 operands with 16-byte aligned bases and

@@ -40,6 +40,10 @@ __device__ int g_gemm_error = 0;
 struct GemmArgs {
     CUtensorMap tmap_a;
     CUtensorMap tmap_b;
+    CUtensorMap tmap_c;        // output tiles of 32 rows x 128 bytes (TMA epilogue only)
+    CUtensorMap tmap_aux;
+    CUtensorMap tmap_aux_out;
+    int tma_epilogue;
     void *c;
     const void *bias;
     const void *aux;
@@ -96,10 +100,24 @@ __device__ __forceinline__ float epilogue_value(int kind, float acc, float bias,
     }
 }
 
-__device__ __forceinline__ bool epilogue_reads_bias(int kind) {
+// The same with the kind known at compile time: the tensor-core kernel is instantiated per epilogue,
+// which keeps its drain loop a few hundred instructions (a run-time switch inlined for each of a
+// chunk's 32 values made the loop outgrow the instruction cache and the drain, not the MMAs, set the pace).
+template <int EPI>
+__device__ __forceinline__ float epilogue_fixed(float acc, float bias, float aux, float &pre) {
+    if constexpr (EPI == TB200_EPI_BIAS) return acc + bias;
+    else if constexpr (EPI == TB200_EPI_BIAS_GELU) { pre = acc + bias; return gelu_tanh<false>(pre); }
+    else if constexpr (EPI == TB200_EPI_BIAS_TANH) { pre = acc + bias; return tanh_of<false>(pre); }
+    else if constexpr (EPI == TB200_EPI_MUL_GELU_GRAD) return acc * gelu_tanh_grad<false>(aux);
+    else if constexpr (EPI == TB200_EPI_MUL_TANH_GRAD) return acc * (1.0f - aux * aux);
+    else if constexpr (EPI == TB200_EPI_AXPY) return aux + acc;
+    else return acc;
+}
+
+__host__ __device__ constexpr bool epilogue_reads_bias(int kind) {
     return kind == TB200_EPI_BIAS || kind == TB200_EPI_BIAS_GELU || kind == TB200_EPI_BIAS_TANH;
 }
-__device__ __forceinline__ bool epilogue_reads_aux(int kind) {
+__host__ __device__ constexpr bool epilogue_reads_aux(int kind) {
     return kind == TB200_EPI_MUL_GELU_GRAD || kind == TB200_EPI_MUL_TANH_GRAD || kind == TB200_EPI_AXPY;
 }
 
@@ -164,7 +182,115 @@ __device__ __forceinline__ bool wait_or_fail(uint64_t *bar, uint32_t parity, vol
     }
 }
 
-template <int BN>
+constexpr int kStageLine = 128;                   // bytes per staged row: one 128-byte swizzle line
+constexpr int kEpilogueStage = 32 * kStageLine;   // 32 rows of one warp
+
+// One warp's share of a finished accumulator tile, through shared memory: 32 rows x 128 bytes at a
+// time are written (128-byte swizzled, so a thread writing its own row does not collide with its
+// neighbours) into a staging buffer and handed to a TMA store, which writes whole lines; the operand an
+// epilogue reads (aux) arrives the same way by a TMA load.  Returns false if a bounded wait gave up.
+template <int BN, int EPI, bool OUT_F32>
+__device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tmem_acc, int row0, int n0, int lane,
+                                                  uint8_t *stage_c, uint8_t *stage_x, uint64_t *aux_bar,
+                                                  uint32_t &aux_phase, volatile int *failed) {
+    constexpr int EPL = OUT_F32 ? 32 : 64;   // elements per 128-byte line
+    constexpr bool reads_bias = epilogue_reads_bias(EPI), reads_aux = epilogue_reads_aux(EPI);
+    const bool has_aux_out = EPI == TB200_EPI_BIAS_GELU && p.aux_out != nullptr;
+    const int sw = lane & 7;
+#pragma unroll 1
+    for (int g = 0; g < BN / EPL; g++) {
+        const int col0 = n0 + g * EPL;
+        if (col0 >= p.n) break;
+        // one staging buffer per warp: the previous group's stores must have read it
+        if (lane == 0) bulk_wait_group_read<0>();
+        __syncwarp();
+        if (reads_aux) {
+            if (lane == 0) {
+                mbar_arrive_expect_tx(aux_bar, kEpilogueStage);
+                tma_load_2d(stage_x, &p.tmap_aux, aux_bar, col0, row0);
+            }
+            if (!wait_or_fail(aux_bar, aux_phase, failed, 5)) return false;
+            aux_phase ^= 1;
+        }
+#pragma unroll 1
+        for (int h = 0; h < EPL / 32; h++) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_acc + g * EPL + h * 32, r);
+            tmem_ld_wait();
+            const int c0 = col0 + h * 32;
+            float v[32], auxv[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]) * p.alpha;
+            if (reads_aux) {
+                if constexpr (OUT_F32) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const float4 q = *reinterpret_cast<const float4 *>(stage_x + lane * kStageLine + ((j ^ sw) << 4));
+                        auxv[4 * j] = q.x; auxv[4 * j + 1] = q.y; auxv[4 * j + 2] = q.z; auxv[4 * j + 3] = q.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint4 q =
+                            *reinterpret_cast<const uint4 *>(stage_x + lane * kStageLine + (((4 * h + j) ^ sw) << 4));
+                        Access<__nv_bfloat16, true>::unpack(q, &auxv[8 * j]);
+                    }
+                }
+            }
+            float bv[32];
+            if (reads_bias) {
+                const __nv_bfloat16 *bp = static_cast<const __nv_bfloat16 *>(p.bias) + c0;
+                if (c0 + 32 <= p.n && aligned_dev(bp, 16)) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        Access<__nv_bfloat16, true>::unpack(__ldg(reinterpret_cast<const uint4 *>(bp) + j), &bv[8 * j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) bv[j] = (c0 + j < p.n) ? __bfloat162float(bp[j]) : 0.0f;
+                }
+            }
+            float pre[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                pre[j] = v[j];
+                v[j] = epilogue_fixed<EPI>(v[j], reads_bias ? bv[j] : 0.0f, reads_aux ? auxv[j] : 0.0f, pre[j]);
+            }
+            if constexpr (OUT_F32) {
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    *reinterpret_cast<float4 *>(stage_c + lane * kStageLine + ((j ^ sw) << 4)) =
+                        make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    uint4 q;
+                    q.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
+                    q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+                    q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+                    q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+                    *reinterpret_cast<uint4 *>(stage_c + lane * kStageLine + (((4 * h + j) ^ sw) << 4)) = q;
+                    if (has_aux_out) {
+                        q.x = pack_bf16x2(pre[8 * j], pre[8 * j + 1]);
+                        q.y = pack_bf16x2(pre[8 * j + 2], pre[8 * j + 3]);
+                        q.z = pack_bf16x2(pre[8 * j + 4], pre[8 * j + 5]);
+                        q.w = pack_bf16x2(pre[8 * j + 6], pre[8 * j + 7]);
+                        *reinterpret_cast<uint4 *>(stage_x + lane * kStageLine + (((4 * h + j) ^ sw) << 4)) = q;
+                    }
+                }
+            }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(&p.tmap_c, stage_c, col0, row0);
+            if (has_aux_out) tma_store_2d(&p.tmap_aux_out, stage_x, col0, row0);
+            bulk_commit_group();
+        }
+    }
+    return true;
+}
+
+template <int BN, int EPI, bool OUT_F32>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_constant__ GemmArgs p) {
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzle atoms are 1024 bytes: align the ring
@@ -178,6 +304,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
     __shared__ __align__(8) uint64_t tmem_full_bar[kAccumStages];
     __shared__ __align__(8) uint64_t tmem_empty_bar[kAccumStages];
+    __shared__ __align__(8) uint64_t aux_bar[4];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int failed_smem;
     volatile int *failed = &failed_smem;
@@ -198,9 +325,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             mbar_init(&tmem_full_bar[s], 1);
             mbar_init(&tmem_empty_bar[s], 4);
         }
+        for (int s = 0; s < 4; s++) mbar_init(&aux_bar[s], 1);
         fence_barrier_init();
         prefetch_tensormap(&p.tmap_a);
         prefetch_tensormap(&p.tmap_b);
+        if (p.tma_epilogue) prefetch_tensormap(&p.tmap_c);
     }
     if (warp == 1) {
         tmem_alloc(&tmem_base_smem, kAccumStages * BN);
@@ -277,15 +406,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
         // ---- epilogue: warp q owns tensor-memory lanes [32 q, 32 q + 32)
         const int q = warp & 3;
         int it = 0;
+        // staging for the TMA epilogue sits behind the operand ring: per warp one buffer for the
+        // output and one for the operand the epilogue reads or the second array it writes
+        uint8_t *stage_c = smem + stages * STAGE_BYTES + (warp - 2) * 2 * kEpilogueStage;
+        uint8_t *stage_x = stage_c + kEpilogueStage;
+        uint32_t aux_phase = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, it++) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             if (!wait_or_fail(&tmem_full_bar[acc], acc_phase, failed, 4)) break;
             tcgen05_fence_after();
+            if (p.tma_epilogue) {
+                const int row0 = (tile / p.tiles_n) * BM + q * 32;
+                const uint32_t tmem_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+                bool ok = true;
+                if (row0 < p.m)
+                    ok = epilogue_tile_tma<BN, EPI, OUT_F32>(p, tmem_acc, row0, (tile % p.tiles_n) * BN, lane, stage_c,
+                                                             stage_x, &aux_bar[warp - 2], aux_phase, failed);
+                if (!ok) break;
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+                continue;
+            }
             const int m = (tile / p.tiles_n) * BM + q * 32 + lane;
             const int n0 = (tile % p.tiles_n) * BN;
             const bool row_ok = m < p.m;
-            const bool reads_bias = epilogue_reads_bias(p.epilogue), reads_aux = epilogue_reads_aux(p.epilogue);
+            constexpr bool reads_bias = epilogue_reads_bias(EPI), reads_aux = epilogue_reads_aux(EPI);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c++) {
                 uint32_t r[32];
@@ -300,7 +447,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
                 for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]) * p.alpha;
                 float auxv[32];
                 if (reads_aux) {
-                    if (p.out_f32 && p.epilogue == TB200_EPI_AXPY) {
+                    if (OUT_F32 && EPI == TB200_EPI_AXPY) {
                         const float *ap = static_cast<const float *>(p.aux) + static_cast<long long>(m) * p.ld_aux + col0;
 #pragma unroll
                         for (int j = 0; j < 32; j++) auxv[j] = (whole || col0 + j < p.n) ? ap[j] : 0.0f;
@@ -324,9 +471,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
                     if (reads_bias && (whole || col0 + j < p.n))
                         b = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.bias)[col0 + j]);
                     pre[j] = v[j];
-                    v[j] = epilogue_value<false>(p.epilogue, v[j], b, reads_aux ? auxv[j] : 0.0f, pre[j]);
+                    v[j] = epilogue_fixed<EPI>(v[j], b, reads_aux ? auxv[j] : 0.0f, pre[j]);
                 }
-                store_row32(p.c, p.out_f32, static_cast<long long>(m) * p.ldc + col0, v, whole ? 32 : p.n - col0);
+                store_row32(p.c, OUT_F32, static_cast<long long>(m) * p.ldc + col0, v, whole ? 32 : p.n - col0);
                 if (p.aux_out)
                     store_row32(p.aux_out, 0, static_cast<long long>(m) * p.ld_aux_out + col0, pre,
                                 whole ? 32 : p.n - col0);
@@ -335,6 +482,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
         }
+        // the staging buffers must outlive the stores that read them
+        if (p.tma_epilogue && lane == 0) bulk_wait_group<0>();
     }
 
     tcgen05_fence_before();
@@ -446,46 +595,71 @@ int encode_fn(EncodeTiledFn *out) {
     return TB200_OK;
 }
 
-// A 2-D BFloat16 array `rows` x `cols` (cols contiguous, row pitch ld elements) as boxes of box_rows x 64.
-int make_tmap(CUtensorMap *map, const void *base, int64_t cols, int64_t rows, int64_t ld, int box_rows) {
+// A 2-D array `rows` x `cols` (cols contiguous, row pitch ld elements) as 128-byte-swizzled boxes of
+// box_rows rows x 128 bytes (64 BFloat16 or 32 Float32).
+int make_tmap(CUtensorMap *map, const void *base, int64_t cols, int64_t rows, int64_t ld, int box_rows,
+              bool f32 = false) {
     EncodeTiledFn fn;
     int st = encode_fn(&fn);
     if (st) return st;
+    const cuuint64_t es = f32 ? 4 : 2;
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-    cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * es};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(box_rows)};
     cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? TB200_OK : TB200_ERR_UNSUPPORTED;
 }
 
-template <int BN>
+template <int BN, int EPI, bool OUT_F32>
 int launch_tcgen05(GemmArgs &p, const DeviceInfo &dev, cudaStream_t stream) {
     constexpr size_t stage_bytes = (BM + BN) * BK * 2;
-    int stages = static_cast<int>((dev.smem_optin - 2048) / stage_bytes);
+    constexpr size_t epilogue_bytes = 4 * 2 * kEpilogueStage;
+    int stages = static_cast<int>((dev.smem_optin - 2048 - epilogue_bytes) / stage_bytes);
     if (stages > 8) stages = 8;
     if (stages < 2) return TB200_ERR_UNSUPPORTED;
     p.stages = stages;
     p.tiles_m = static_cast<int>(ceil_div(p.m, BM));
     p.tiles_n = static_cast<int>(ceil_div(p.n, BN));
-    const size_t smem = stages * stage_bytes + 1024;
+    const size_t smem = stages * stage_bytes + epilogue_bytes + 1024;
     static std::mutex lock;
     static bool configured[64] = {};
     {
         std::lock_guard<std::mutex> hold(lock);
         if (!configured[dev.device]) {
-            TB200_CUDA(cudaFuncSetAttribute(gemm_tcgen05<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            TB200_CUDA(cudaFuncSetAttribute(gemm_tcgen05<BN, EPI, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             static_cast<int>(dev.smem_optin - 1024)));
             configured[dev.device] = true;
         }
     }
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     const unsigned grid = static_cast<unsigned>(tiles < dev.sms ? tiles : dev.sms);
-    gemm_tcgen05<BN><<<grid, kGemmThreads, smem, stream>>>(p);
+    gemm_tcgen05<BN, EPI, OUT_F32><<<grid, kGemmThreads, smem, stream>>>(p);
     TB200_CUDA(cudaGetLastError());
     return TB200_OK;
+}
+
+template <int BN, bool OUT_F32>
+int launch_by_epilogue(GemmArgs &p, const DeviceInfo &dev, cudaStream_t stream) {
+    switch (p.epilogue) {
+        case TB200_EPI_NONE: return launch_tcgen05<BN, TB200_EPI_NONE, OUT_F32>(p, dev, stream);
+        case TB200_EPI_BIAS: return launch_tcgen05<BN, TB200_EPI_BIAS, OUT_F32>(p, dev, stream);
+        case TB200_EPI_AXPY: return launch_tcgen05<BN, TB200_EPI_AXPY, OUT_F32>(p, dev, stream);
+        default: break;
+    }
+    // activations and their pullbacks are instantiated for BFloat16 results only
+    if constexpr (!OUT_F32) {
+        switch (p.epilogue) {
+            case TB200_EPI_BIAS_GELU: return launch_tcgen05<BN, TB200_EPI_BIAS_GELU, false>(p, dev, stream);
+            case TB200_EPI_BIAS_TANH: return launch_tcgen05<BN, TB200_EPI_BIAS_TANH, false>(p, dev, stream);
+            case TB200_EPI_MUL_GELU_GRAD: return launch_tcgen05<BN, TB200_EPI_MUL_GELU_GRAD, false>(p, dev, stream);
+            case TB200_EPI_MUL_TANH_GRAD: return launch_tcgen05<BN, TB200_EPI_MUL_TANH_GRAD, false>(p, dev, stream);
+            default: break;
+        }
+    }
+    return TB200_ERR_UNSUPPORTED;
 }
 
 }  // namespace
@@ -523,8 +697,11 @@ extern "C" int tb200_gemm(const tb200_gemm_desc *d, const void *a, const void *b
     int st = current_device(&dev);
     if (st) return st;
 
+    const bool activation = d->epilogue == TB200_EPI_BIAS_GELU || d->epilogue == TB200_EPI_BIAS_TANH ||
+                            d->epilogue == TB200_EPI_MUL_GELU_GRAD || d->epilogue == TB200_EPI_MUL_TANH_GRAD;
     const bool tma_ok = d->in_dtype == TB200_BF16 && d->k > 0 && aligned_to(a, 16) && aligned_to(b, 16) &&
-                        d->lda % 8 == 0 && d->ldb % 8 == 0 && !d->force_simt;
+                        d->lda % 8 == 0 && d->ldb % 8 == 0 && !d->force_simt &&
+                        !(activation && d->out_dtype == TB200_F32);
     if (tma_ok) {
         GemmArgs p{};
         p.c = c; p.bias = bias; p.aux = aux; p.aux_out = aux_out;
@@ -532,8 +709,9 @@ extern "C" int tb200_gemm(const tb200_gemm_desc *d, const void *a, const void *b
         p.alpha = d->alpha; p.m = static_cast<int>(d->m); p.n = static_cast<int>(d->n); p.k = static_cast<int>(d->k);
         p.epilogue = d->epilogue; p.out_f32 = d->out_dtype == TB200_F32;
         p.a_mn = d->a_layout == TB200_MN_MAJOR; p.b_mn = d->b_layout == TB200_MN_MAJOR;
-        // wide tiles when there are enough of them to fill the device
-        const bool wide = d->tile_n == 256 || (d->tile_n == 0 && ceil_div(d->m, BM) * ceil_div(d->n, 256) >= dev.sms);
+        // 128 x 256 tiles halve the operand bytes per flop of 128 x 128 ones and measured faster on every
+        // shape wide enough to hold one, even when they leave a few SMs idle
+        const bool wide = d->tile_n == 256 || (d->tile_n == 0 && d->n > 128);
         const int bn = wide ? 256 : 128;
         if (p.a_mn) st = make_tmap(&p.tmap_a, a, d->m, d->k, d->lda, 64);
         else st = make_tmap(&p.tmap_a, a, d->k, d->m, d->lda, BM);
@@ -541,7 +719,21 @@ extern "C" int tb200_gemm(const tb200_gemm_desc *d, const void *a, const void *b
         if (p.b_mn) st = make_tmap(&p.tmap_b, b, d->n, d->k, d->ldb, 64);
         else st = make_tmap(&p.tmap_b, b, d->k, d->n, d->ldb, bn);
         if (st) return st;
-        return wide ? launch_tcgen05<256>(p, dev, stream) : launch_tcgen05<128>(p, dev, stream);
+        // the epilogue goes through shared memory and TMA when every array it touches can be
+        // described to the TMA unit; otherwise each thread stores its own row
+        const bool out_f32 = d->out_dtype == TB200_F32;
+        const size_t aux_size = (d->epilogue == TB200_EPI_AXPY) ? out_size : 2;
+        bool tma_epi = !d->direct_epilogue && aligned_to(c, 16) && (d->ldc * out_size) % 16 == 0;
+        if (needs_aux) tma_epi = tma_epi && aux_size == out_size && aligned_to(aux, 16) && (d->ld_aux * aux_size) % 16 == 0;
+        if (aux_out) tma_epi = tma_epi && !out_f32 && aligned_to(aux_out, 16) && (d->ld_aux_out * 2) % 16 == 0;
+        if (tma_epi) {
+            if ((st = make_tmap(&p.tmap_c, c, d->n, d->m, d->ldc, 32, out_f32))) return st;
+            if (needs_aux && (st = make_tmap(&p.tmap_aux, aux, d->n, d->m, d->ld_aux, 32, out_f32))) return st;
+            if (aux_out && (st = make_tmap(&p.tmap_aux_out, aux_out, d->n, d->m, d->ld_aux_out, 32, false))) return st;
+        }
+        p.tma_epilogue = tma_epi;
+        if (out_f32) return wide ? launch_by_epilogue<256, true>(p, dev, stream) : launch_by_epilogue<128, true>(p, dev, stream);
+        return wide ? launch_by_epilogue<256, false>(p, dev, stream) : launch_by_epilogue<128, false>(p, dev, stream);
     }
 
     SimtArgs p{};

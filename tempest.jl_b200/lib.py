@@ -29,7 +29,7 @@ class GemmDesc(ctypes.Structure):
                 ("a_layout", ctypes.c_int), ("b_layout", ctypes.c_int),
                 ("in_dtype", ctypes.c_int), ("out_dtype", ctypes.c_int),
                 ("epilogue", ctypes.c_int), ("alpha", ctypes.c_float),
-                ("tile_n", ctypes.c_int), ("force_simt", ctypes.c_int)]
+                ("tile_n", ctypes.c_int), ("force_simt", ctypes.c_int), ("direct_epilogue", ctypes.c_int)]
 
 
 # name -> (restype, argtypes): the declarations of include/tempest_b200.h
@@ -133,7 +133,7 @@ def layernorm_bwd(x, gamma, dy, mean, rstd, dx, dgamma, dbeta, eps, n, rows, ld,
 
 def gemm(a, b, c, m, n, k, *, lda=None, ldb=None, ldc=None, a_layout=K_MAJOR, b_layout=MN_MAJOR, in_dtype=BF16,
          out_dtype=None, epilogue=EPI_NONE, bias=0, aux=0, ld_aux=None, aux_out=0, ld_aux_out=None, alpha=1.0,
-         tile_n=0, force_simt=False, stream=0):
+         tile_n=0, force_simt=False, direct_epilogue=False, stream=0):
     """C[m][n] = epilogue(alpha * A * B).  a_layout K_MAJOR: A is [m][k]; MN_MAJOR: [k][m].
     b_layout K_MAJOR: B is [n][k]; MN_MAJOR: [k][n] (a Julia (out,in) weight for y = w*x)."""
     d = GemmDesc()
@@ -147,6 +147,7 @@ def gemm(a, b, c, m, n, k, *, lda=None, ldb=None, ldc=None, a_layout=K_MAJOR, b_
     d.in_dtype = in_dtype
     d.out_dtype = in_dtype if out_dtype is None else out_dtype
     d.epilogue, d.alpha, d.tile_n, d.force_simt = epilogue, alpha, tile_n, int(force_simt)
+    d.direct_epilogue = int(direct_epilogue)
     check("tb200_gemm", load().tb200_gemm(ctypes.byref(d), a or None, b or None, c or None, bias or None,
                                           aux or None, aux_out or None, stream or None))
 

@@ -49,16 +49,16 @@ def test_bf16_tensor_core_product(pkg, cuda, oracle, M, N, K, a_mn, b_mn):
     A, B = operands(oracle, M, N, K, a_mn, b_mn, 1000 + M + K, True)
     want = oracle.gemm(A, B, M=M, N=N, K=K, a_km=a_mn, b_kn=b_mn, want_pre=True)[1]
     Ad, Bd = dev(cuda, A), dev(cuda, B)
-    for tile_n in (128, 256):
+    for tile_n, direct in ((128, False), (256, False), (256, True)):
         C = cuda.full((M, N), float("nan"), device="cuda", dtype=cuda.bfloat16)
         L.gemm(Ad.data_ptr(), Bd.data_ptr(), C.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn),
-               tile_n=tile_n, stream=cuda.cuda.current_stream().cuda_stream)
+               tile_n=tile_n, direct_epilogue=direct, stream=cuda.cuda.current_stream().cuda_stream)
         assert L.device_error() == 0
         close_bf16(oracle, host(cuda, C), want, K)
         # and Float32 output of the same accumulators: tight, the only difference is summation order
         C32 = cuda.empty((M, N), device="cuda")
         L.gemm(Ad.data_ptr(), Bd.data_ptr(), C32.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn),
-               out_dtype=L.F32, tile_n=tile_n)
+               out_dtype=L.F32, tile_n=tile_n, direct_epilogue=direct)
         assert L.device_error() == 0
         agree(C32.cpu().numpy(), want, 1e-5)
 
@@ -77,13 +77,13 @@ def test_generic_kernel_float32(pkg, cuda, oracle, a_mn, b_mn):
     M, N, K = 33, 45, 51
     A, B = operands(oracle, M, N, K, a_mn, b_mn, 9, True)
     C = cuda.empty((M, N), device="cuda", dtype=cuda.bfloat16)
-    L.gemm(dev(cuda, A).data_ptr(), dev(cuda, B).data_ptr(), C.data_ptr(), M, N, K, a_layout=int(a_mn),
-           b_layout=int(b_mn))
+    Ad, Bd = dev(cuda, A), dev(cuda, B)
+    L.gemm(Ad.data_ptr(), Bd.data_ptr(), C.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn))
     close_bf16(oracle, host(cuda, C), oracle.gemm(A, B, M=M, N=N, K=K, a_km=a_mn, b_kn=b_mn, want_pre=True)[1], K)
 
 
-@pytest.mark.parametrize("force_simt", [False, True])
-def test_epilogues(pkg, cuda, oracle, force_simt):
+@pytest.mark.parametrize("force_simt,direct", [(False, False), (False, True), (True, False)])
+def test_epilogues(pkg, cuda, oracle, force_simt, direct):
     L = pkg.lib
     M, N, K = 200, 136, 96
     A, B = operands(oracle, M, N, K, False, True, 21, True)
@@ -92,7 +92,7 @@ def test_epilogues(pkg, cuda, oracle, force_simt):
     Ad, Bd, bd = dev(cuda, A), dev(cuda, B), dev(cuda, bias)
     acc = oracle.gemm(A, B, M=M, N=N, K=K, want_pre=True)[1]
     pre = acc + oracle.from_bf16(bias)
-    run = dict(a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR, force_simt=force_simt)
+    run = dict(a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR, force_simt=force_simt, direct_epilogue=direct)
 
     def call(**kw):
         C = cuda.empty((M, N), device="cuda", dtype=cuda.bfloat16)
@@ -113,7 +113,8 @@ def test_epilogues(pkg, cuda, oracle, force_simt):
     close_bf16(oracle, host(cuda, call(epilogue=L.EPI_MUL_GELU_GRAD, aux=auxd.data_ptr())), acc * grad, K)
     t = np.tanh(oracle.from_bf16(aux))
     tb = oracle.to_bf16(t.astype(np.float32))
-    close_bf16(oracle, host(cuda, call(epilogue=L.EPI_MUL_TANH_GRAD, aux=dev(cuda, tb).data_ptr())),
+    tbd = dev(cuda, tb)
+    close_bf16(oracle, host(cuda, call(epilogue=L.EPI_MUL_TANH_GRAD, aux=tbd.data_ptr())),
                acc * (1 - oracle.from_bf16(tb) ** 2), K)
     # accumulate into an existing array, scaled: D .+ alpha * A*B (ext/cuBLASExt.jl:25-29), in place
     D = dev(cuda, aux).clone()

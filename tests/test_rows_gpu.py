@@ -55,9 +55,13 @@ def test_layernorm_f32(run, oracle, rows, n):
     y, mean, rstd = run.layernorm(x, w, b, stats=True)
     y_ref, mean_ref, rstd_ref = oracle.layernorm_fwd(x, w, b)
     if n > 1:
-        agree(y, oracle.layernorm_fwd_f64(x, w, b), RTOL_F32)
-        agree(y, y_ref, 2 * RTOL_F32)  # the oracle's own one-pass Float32 fold drifts this far from Float64
-        agree(rstd, rstd_ref, 2 * RTOL_F32)
+        y64 = oracle.layernorm_fwd_f64(x, w, b)
+        agree(y, y64, RTOL_F32)
+        # the oracle folds each row sequentially in Float32 as the reference's CPU path does, which
+        # itself drifts from Float64 as rows grow: allow its own distance on top of the tolerance
+        drift = np.linalg.norm(y_ref - y64) / np.linalg.norm(y64)
+        agree(y, y_ref, RTOL_F32 + drift)
+        agree(rstd, rstd_ref, RTOL_F32 + drift)
     agree(mean, x.astype(np.float64).mean(axis=1), RTOL_F32)
     agree(run.layernorm(x, w), oracle.layernorm_fwd_f64(x, w), RTOL_F32)
     if n > 8192:
@@ -131,7 +135,7 @@ def test_leading_dimension_and_unaligned_views(run, oracle, cuda):
                        "y": I.Strided("Float32", off, (n, rows), (1, ld), out, 2)})
         launch, _ = run.lib.build(run.target, b, run.resources)
         launch()
-        cuda.synchronize()
+        cuda.cuda.synchronize()
         got = out[off:off + rows * ld].view(rows, ld).cpu().numpy()
         agree(got[:, :n], oracle.softmax_fwd(x)[0], RTOL_F32)
         assert (got[:, n:] == -7.0).all(), "wrote outside the rows"
@@ -148,11 +152,11 @@ def test_in_place_and_repoint(run, oracle, cuda):
                      {"x": I.dense_columns(a, "Float32", n, rows, 1), "y": I.dense_columns(a, "Float32", n, rows, 1)})
     launch, _ = run.lib.build(run.target, bind, run.resources)
     launch()
-    cuda.synchronize()
+    cuda.cuda.synchronize()
     agree(a.cpu().numpy(), oracle.softmax_fwd(x)[0], RTOL_F32)
     launch.repoint(1, b2)
     launch()
-    cuda.synchronize()
+    cuda.cuda.synchronize()
     agree(b2.cpu().numpy(), oracle.softmax_fwd(x * 0.5)[0], RTOL_F32)
 
 
@@ -162,7 +166,7 @@ def test_empty_and_infinite_rows(run, oracle, cuda):
     # rows of no elements: the log-sum-exp of nothing is -Inf (src/Compiler/IR/folds.jl:121-127)
     lse = cuda.zeros(5, device="cuda")
     L.softmax_fwd(0, 0, lse.data_ptr(), 0, 5, 0, L.F32, stream=stream)
-    cuda.synchronize()
+    cuda.cuda.synchronize()
     assert (lse.cpu().numpy() == -np.inf).all()
     # no rows: nothing runs, nothing is read
     L.softmax_fwd(0, 0, 0, 128, 0, 128, L.F32, stream=stream)
