@@ -121,6 +121,26 @@ int tb200_layernorm_bwd(const void *x, const void *gamma, const void *dy, const 
                         int64_t n, int64_t rows, int64_t ld, int dtype, void *workspace,
                         size_t workspace_bytes, void *stream);
 
+/* tb200_layernorm_bwd without a workspace argument, for callers that cannot
+ * supply scratch memory: programs whose device buffers were all laid out
+ * before the kernels were chosen and that have no allocator to turn to at call
+ * time, or that must stay clear of the driver's allocator (it takes a
+ * process-wide lock and may wait for the device).  The partial dgamma/dbeta
+ * sums go to an 8 MiB array built into the library, which every GPU that loads
+ * the library keeps resident until the process ends.  Rows longer than
+ * tb200_layernorm_bwd_noalloc_max_row() elements (8192) are refused with
+ * TB200_ERR_WORKSPACE.  The entry point itself allocates nothing.
+ * The first call on each device looks up the array's device address; make that
+ * call outside any stream capture.  Every call on a device uses the same
+ * array: calls whose kernels could overlap on the GPU (two streams) corrupt
+ * each other's sums, so the caller must order them.  Results equal
+ * tb200_layernorm_bwd's dx exactly and its dgamma/dbeta up to the order of
+ * the partial sums.  This entry point has no counterpart in the reference. */
+size_t tb200_layernorm_bwd_noalloc_max_row(void);
+int tb200_layernorm_bwd_noalloc(const void *x, const void *gamma, const void *dy, const float *mean,
+                                const float *rstd, void *dx, void *dgamma, void *dbeta, float eps,
+                                int64_t n, int64_t rows, int64_t ld, int dtype, void *stream);
+
 /* ---- products with fused epilogues ----------------------------------------
  * C = epilogue(alpha * A * B), row-major C[M][N].  Replaces the generated
  * `:product` kernels of ext/cuTileExt/contract.jl:112-161 with their fused

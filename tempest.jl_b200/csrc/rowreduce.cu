@@ -851,3 +851,106 @@ extern "C" int tb200_layernorm_bwd(const void *x, const void *gamma, const void 
     }
     return TB200_OK;
 }
+
+// ------------------------------------------------- LayerNorm backward, no allocation ----
+//
+// tb200_layernorm_bwd_noalloc is tb200_layernorm_bwd for callers that have no way to hand
+// over scratch memory: a host program that fixed all of its device buffers before it knew
+// which kernels it would run and has no allocator to ask afterwards (a plugin called from a
+// runtime that owns every byte of device memory, an embedded or real-time loop that must
+// not reach the driver's allocator, which takes a process-wide lock and may synchronise the
+// device).  The dgamma / dbeta partial sums then live in the fixed array below, which is
+// part of the library's image: every GPU that loads the library holds these 8 MiB until the
+// process exits.
+//
+// The array's name is a host-side handle in host code, not an address a kernel can use; the
+// device address comes from cudaGetSymbolAddress, asked once per device (with that device
+// current) by the first call on it, which is why that first call should be made outside any
+// stream capture.  All calls on a device share the array and nothing is kept between calls:
+// each launch overwrites the partial rows it later merges, so nothing needs clearing, but two
+// calls whose kernels overlap on the GPU (different streams) would overwrite each other's
+// partial sums.  Calls must be ordered by the caller.
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchBytes / sizeof(float)];
+
+// Device address of the scratch on the current device, looked up on first use.
+int noalloc_scratch(const tb200::DeviceInfo &dev, float **out) {
+    static std::mutex lock;
+    static float *known[64] = {};
+    std::lock_guard<std::mutex> hold(lock);
+    if (!known[dev.device]) {
+        float *ptr = nullptr;
+        TB200_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_scratch));
+        if (!ptr) return TB200_ERR_CUDA;
+        known[dev.device] = ptr;
+    }
+    *out = known[dev.device];
+    return TB200_OK;
+}
+
+}  // namespace
+
+extern "C" size_t tb200_layernorm_bwd_noalloc_max_row(void) {
+    // the longest row the resident schedule of the LayerNorm backward takes; one block's
+    // partial sums for it (2 x 8192 Float32) fit the scratch 128 times over
+    return 8192;
+}
+
+extern "C" int tb200_layernorm_bwd_noalloc(const void *x, const void *gamma, const void *dy, const float *mean,
+                                           const float *rstd, void *dx, void *dgamma, void *dbeta, float eps,
+                                           int64_t n, int64_t rows, int64_t ld, int dtype, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int st = check_rows(n, rows, ld, dtype);
+    if (st) return st;
+    if (n == 0) return TB200_OK;
+    // beyond the built-in scratch: say so instead of running with too little
+    if (static_cast<size_t>(n) > tb200_layernorm_bwd_noalloc_max_row()) return TB200_ERR_WORKSPACE;
+    if (rows == 0) {
+        if (dgamma) TB200_CUDA(cudaMemsetAsync(dgamma, 0, n * dtype_size(dtype), stream));
+        if (dbeta) TB200_CUDA(cudaMemsetAsync(dbeta, 0, n * dtype_size(dtype), stream));
+        return TB200_OK;
+    }
+    if (!x || !gamma || !dy || !dx) return TB200_ERR_NULL;
+    if (!all_aligned(dtype_size(dtype), {x, gamma, dy, dx, dgamma, dbeta}) || !all_aligned(4, {mean, rstd}))
+        return TB200_ERR_ALIGN;
+    DeviceInfo dev;
+    if ((st = current_device(&dev))) return st;
+    const Schedule s = plan_rows(OP_LN_BWD, n, rows, ld, dtype, all_aligned(16, {x, gamma, dy, dx}));
+    if (s.split) return TB200_ERR_WORKSPACE;
+    const RowKernel kernel = pick<LayernormBwdResident>(dtype, s);
+    long long grid = 0;
+    if ((st = resident_grid(kernel, s, dev, &grid))) return st;
+    // as many blocks as the scratch has partial rows for
+    const long long room = static_cast<long long>(kNoAllocScratchBytes / (2 * sizeof(float) * static_cast<size_t>(n))) /
+                           s.rpc;
+    if (room < 1) return TB200_ERR_WORKSPACE;
+    if (grid > room) grid = room;
+    float *scratch = nullptr;
+    if ((st = noalloc_scratch(dev, &scratch))) return st;
+    RowArgs a{};
+    a.in0 = x; a.in1 = dy; a.gamma = gamma; a.out0 = dx; a.cstat0 = mean; a.cstat1 = rstd; a.eps = eps;
+    a.n = static_cast<int>(n); a.rows = rows; a.ld = ld; a.tpr = s.tpr; a.rpc = s.rpc; a.splits = 1;
+    const bool sums = dgamma || dbeta;
+    const size_t part_len = static_cast<size_t>(grid) * s.rpc * static_cast<size_t>(n);
+    if (sums) {
+        a.part0 = scratch;
+        a.part1 = scratch + part_len;
+    }
+    kernel<<<static_cast<unsigned>(grid), s.threads, 0, stream>>>(a);
+    TB200_CUDA(cudaGetLastError());
+    if (sums) {
+        const int parts = static_cast<int>(grid * s.rpc);
+        const unsigned blocks = static_cast<unsigned>(ceil_div(n, 32));
+        if (dtype == TB200_F32)
+            merge_parts<float><<<blocks, 256, 0, stream>>>(a.part0, a.part1, static_cast<float *>(dgamma),
+                                                           static_cast<float *>(dbeta), a.n, parts);
+        else
+            merge_parts<__nv_bfloat16><<<blocks, 256, 0, stream>>>(a.part0, a.part1,
+                                                                   static_cast<__nv_bfloat16 *>(dgamma),
+                                                                   static_cast<__nv_bfloat16 *>(dbeta), a.n, parts);
+        TB200_CUDA(cudaGetLastError());
+    }
+    return TB200_OK;
+}

@@ -43,6 +43,8 @@ SIGNATURES = {
     "tb200_softmax_bwd": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i, _i, _p, _sz, _p]),
     "tb200_layernorm_fwd": (_i, [_p, _p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i, _p, _sz, _p]),
     "tb200_layernorm_bwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i, _p, _sz, _p]),
+    "tb200_layernorm_bwd_noalloc_max_row": (_sz, []),
+    "tb200_layernorm_bwd_noalloc": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i, _p]),
     "tb200_gemm": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
     "tb200_device_error": (_i, []),
     "tb200_workspace_clear": (_i, [_p, _sz, _p]),
@@ -185,3 +187,15 @@ def colsum(x, out, rows, n, ld, scale, dtype, workspace, workspace_bytes, stream
 
 def axpy(y, x, alpha, count, y_dtype, x_dtype, stream=0):
     check("tb200_axpy", load().tb200_axpy(y, x, alpha, count, y_dtype, x_dtype, stream or None))
+
+
+def layernorm_bwd_noalloc_max_row():
+    return load().tb200_layernorm_bwd_noalloc_max_row()
+
+
+def layernorm_bwd_noalloc(x, gamma, dy, mean, rstd, dx, dgamma, dbeta, eps, n, rows, ld, dtype, stream=0):
+    """tb200_layernorm_bwd for callers without scratch memory to give: the partial
+    sums use the library's built-in 8 MiB array (see the header for the limits)."""
+    check("tb200_layernorm_bwd_noalloc", load().tb200_layernorm_bwd_noalloc(
+        x, gamma, dy, mean or None, rstd or None, dx, dgamma or None, dbeta or None, eps, n, rows, ld, dtype,
+        stream or None))
