@@ -238,6 +238,13 @@ def run_gpu(args):
     if not args.no_e2e:
         e2e = run_e2e(torch, dist, wl, world, args)
 
+    also = None
+    if not args.no_also:
+        try:
+            also = run_also(torch, dist, pkg, world, rank)
+        except Exception as err:  # the headline line must survive a failure of the side measurements
+            also = {"error": repr(err)[:300]}
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline(sample_rows=CPU_SAMPLE_ROWS, repeats=1)
@@ -256,9 +263,80 @@ def run_gpu(args):
                    "element_types": ["f32", "bf16"], "sharding": f"rows x{world}, no collective",
                    "l2": "inputs larger than L2 (each operand 0.5-1 GiB vs 126 MB)"},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-        "gpu_launches": wl.kernels_per_step * args.steps, "kernels": kernels,
+        "gpu_launches": wl.kernels_per_step * args.steps, "kernels": kernels, "also": also,
     }
     print(json.dumps(line))
+
+
+def run_also(torch, dist, pkg, world, rank):
+    """Side measurements of the other kernel families on the same box (not the headline value):
+    the MLP training step of BASELINE.json configs[2] (1024-4096-4096-4096-1024, GELU(tanh), bias,
+    BFloat16, MSE, SGD 1e-3), global batch 8192 sharded over the ranks with an NCCL all-reduce of the
+    gradients (strong scaling), and its largest product alone."""
+    sizes, gb = (1024, 4096, 4096, 4096, 1024), 8192
+    per = gb // world
+    tensor_peak = 1676.5
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            tensor_peak = json.load(f).get("bf16_tflops", tensor_peak)
+    L = pkg.lib
+
+    def timed(fn, iters, warm):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / iters
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    step = pkg.mlp.MLPStep(torch, sizes, per, 1e-3, world=world, global_batch=gb, seed=1)
+    x = torch.randn(per, sizes[0], device="cuda").bfloat16()
+    y = torch.randn(per, sizes[-1], device="cuda").bfloat16()
+    ms = timed(lambda: step.step(x, y), 20, 5)
+    flops = 2 * gb * (1024 * 4096 + 2 * 4096 * 4096 + 4096 * 1024) * 3 - 2 * gb * 1024 * 4096
+    out = {"mlp_train": {"steps_per_s": round(1000.0 / ms, 1), "ms_per_step": round(ms, 4), "n_gpus": world,
+                         "global_batch": gb, "scaling": "strong", "TFLOP/s": round(flops / ms / 1e9, 1),
+                         "frac_of_measured_bf16_peak_per_gpu": round(flops / ms / 1e9 / world / tensor_peak, 4),
+                         "gradient_allreduce_bytes": sum(b.numel() * 2 for b in step.bucket) if world > 1 else 0,
+                         "device_error": L.device_error()}}
+    if rank == 0 or world == 1:
+        M, N, K = 8192, 4096, 4096
+        A = torch.randn(M, K, device="cuda").bfloat16()
+        B = torch.randn(K, N, device="cuda").bfloat16()
+        C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        bias = torch.zeros(N, device="cuda", dtype=torch.bfloat16)
+        Z = torch.empty_like(C)
+        stream = torch.cuda.current_stream().cuda_stream
+
+        def gemm():
+            L.gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR,
+                   epilogue=L.EPI_BIAS_GELU, bias=bias.data_ptr(), aux_out=Z.data_ptr(), stream=stream)
+        for _ in range(3):
+            gemm()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(20):
+            gemm()
+        b.record()
+        torch.cuda.synchronize()
+        gms = a.elapsed_time(b) / 20
+        tf = 2.0 * M * N * K / gms / 1e9
+        out["gemm_bias_gelu_8192x4096x4096"] = {"TFLOP/s": round(tf, 1), "ms": round(gms, 4),
+                                                "frac_of_measured_bf16_peak": round(tf / tensor_peak, 4)}
+    return out
 
 
 def load_traffic(kernel):
@@ -400,6 +478,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the side measurements (MLP step, GEMM)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

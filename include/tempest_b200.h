@@ -196,6 +196,33 @@ int tb200_gemm(const tb200_gemm_desc *desc, const void *a, const void *b, void *
  * reference counterpart: Tempest's kernels have no device-side waits. */
 int tb200_device_error(void);
 
+/* ---- attention -----------------------------------------------------------------
+ * Arrays are the reference's (features, heads, positions, batch) Julia arrays
+ * (test/fixtures/operations.jl:21-29), i.e. dense memory
+ * [batch][position][head][feature]; the log-sum-exp is (1, heads, queries, batch),
+ * memory [batch][query][head], Float32.  Query head h reads key/value head
+ * h / (heads / kv_heads). */
+typedef struct tb200_attn_desc {
+    int batch, heads, kv_heads;
+    int queries, keys, head_dim;
+    int causal;                  /* keys after a query masked out (key index <= query index kept) */
+    float scale;                 /* scores are scale * q.k ; 1/sqrt(head_dim) in the reference */
+    int dtype;                   /* TB200_BF16 */
+} tb200_attn_desc;
+
+/* o = softmax(scale * k'q + mask) weighted sum of v, lse beside it (NULL: not
+ * stored).  Scores and softmax in Float32 from the BFloat16 queries and keys,
+ * weights rounded to BFloat16 for the second product, output rounded once: what
+ * the reference's generated kernel (ext/cuTileExt/build.jl:419-488,
+ * ext/cuTileExt/emit.jl:1079-1135) and its cuDNN call (ext/cuDNNExt.jl:116-132,
+ * 186-210) compute.  head_dim 128 on the tensor-core path; other sizes:
+ * TB200_ERR_UNSUPPORTED. */
+int tb200_attention_fwd(const tb200_attn_desc *desc, const void *q, const void *k, const void *v,
+                        void *o, float *lse, void *stream);
+
+/* As tb200_device_error, for the attention kernels. */
+int tb200_attention_device_error(void);
+
 /* ---- pointwise maps and folds over other axes -------------------------------
  * These replace the generated `:pointwise` kernels (ext/cuTileExt/build.jl:3-10)
  * and the full / partial folds with their merge launches

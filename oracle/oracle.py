@@ -321,3 +321,83 @@ def mlp_step(ws, bs, x, y, rate, global_batch=None):
         new_w[i] = to_bf16(from_bf16(ws[i]) - np.float32(rate) * dws[i])
         new_b[i] = to_bf16(from_bf16(bs[i]) - np.float32(rate) * from_bf16(to_bf16(dbs[i])))
     return loss, dz, dws, dbs, new_w, new_b, a, z
+
+
+# ------------------------------------------------------------- attention ----
+
+def _pool(jobs, threads):
+    if threads <= 1:
+        for j in jobs:
+            j()
+        return
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(threads) as pool:
+        list(pool.map(lambda j: j(), jobs))
+
+
+def attention_fwd(q, k, v, causal, scale=None, round_p=False, threads=1):
+    """q [B][S][H][D], k/v [B][Skv][Hkv][D] as BFloat16 bits (uint16).  Returns (o bits, lse float32 [B][S][H])."""
+    B, S, H, D = q.shape
+    _, Skv, Hkv, _ = k.shape
+    scale = float(D) ** -0.5 if scale is None else scale
+    o = np.empty_like(q)
+    lse = np.empty((B, S, H), np.float32)
+    fn = load().oracle_attention_fwd_rows
+    step = max(1, S // max(1, threads // max(1, B * H) + 1))
+    jobs = []
+    for b in range(B):
+        for h in range(H):
+            for m0 in range(0, S, step):
+                jobs.append(lambda b=b, h=h, m0=m0: fn(
+                    _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _int(B), _int(H), _int(Hkv), _int(S), _int(Skv),
+                    _int(D), _int(int(causal)), _flt(scale), _int(b), _int(h), _int(m0), _int(min(S, m0 + step)),
+                    _int(int(round_p))))
+    _pool(jobs, threads)
+    return o, lse
+
+
+def attention_bwd(q, k, v, o, lse, dout, causal, scale=None, round_p=False, threads=1):
+    """The pullback of attention_fwd: (dq, dk, dv) as BFloat16 bits."""
+    B, S, H, D = q.shape
+    _, Skv, Hkv, _ = k.shape
+    scale = float(D) ** -0.5 if scale is None else scale
+    dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    fn = load().oracle_attention_bwd_head
+    jobs = [lambda b=b, hk=hk: fn(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(dout), _ptr(dq), _ptr(dk),
+                                  _ptr(dv), _int(B), _int(H), _int(Hkv), _int(S), _int(Skv), _int(D),
+                                  _int(int(causal)), _flt(scale), _int(b), _int(hk), _int(int(round_p)))
+            for b in range(B) for hk in range(Hkv)]
+    _pool(jobs, threads)
+    return dq, dk, dv
+
+
+def attention_f64(q, k, v, causal, scale=None, dout=None):
+    """Float64 closed form on the BFloat16 inputs: (o, lse) and, with dout, (dq, dk, dv)."""
+    qf, kf, vf = (from_bf16(a).astype(np.float64) for a in (q, k, v))
+    B, S, H, D = qf.shape
+    Skv, Hkv = kf.shape[1], kf.shape[2]
+    g = H // Hkv
+    scale = float(D) ** -0.5 if scale is None else scale
+    kx, vx = np.repeat(kf, g, axis=2), np.repeat(vf, g, axis=2)
+    s = np.einsum("bmhd,bnhd->bhmn", qf, kx) * scale
+    if causal:
+        mask = np.arange(Skv)[None, :] > np.arange(S)[:, None]
+        s = np.where(mask[None, None], -np.inf, s)
+    mx = s.max(axis=-1, keepdims=True)
+    e = np.exp(s - mx)
+    l = e.sum(axis=-1, keepdims=True)
+    p = e / l
+    o = np.einsum("bhmn,bnhd->bmhd", p, vx)
+    lse = (mx + np.log(l))[..., 0].transpose(0, 2, 1)
+    if dout is None:
+        return o, lse
+    go = from_bf16(dout).astype(np.float64)
+    dvx = np.einsum("bhmn,bmhd->bnhd", p, go)
+    dp = np.einsum("bmhd,bnhd->bhmn", go, vx)
+    delta = (go * o).sum(axis=-1).transpose(0, 2, 1)[..., None]
+    ds = p * (dp - delta)
+    dq = np.einsum("bhmn,bnhd->bmhd", ds, kx) * scale
+    dkx = np.einsum("bhmn,bmhd->bnhd", ds, qf) * scale
+    dk = dkx.reshape(B, Skv, Hkv, g, D).sum(axis=3)
+    dv = dvx.reshape(B, Skv, Hkv, g, D).sum(axis=3)
+    return o, lse, dq, dk, dv

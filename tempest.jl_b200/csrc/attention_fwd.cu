@@ -1,0 +1,487 @@
+// Flash-attention forward for sm_100a: O = softmax(scale * Q K^T + causal mask) V and the
+// log-sum-exp of each query's scores, BFloat16 in and out, Float32 scores and statistics.
+//
+// Arrays are the reference's (features, heads, positions, batch) Julia arrays, i.e. memory
+// [batch][position][head][feature]; the log-sum-exp is (1, heads, queries, batch) = [batch][query][head].
+// The scores are computed from the BFloat16 queries and keys with Float32 accumulation, the softmax
+// weights are rounded to BFloat16 for the second product, the output is rounded once
+// (test/fixtures/operations.jl:21-76 and docs/src/cuda.md:40-46 of the reference).
+//
+// One persistent CTA per SM works through (batch, head, 128-query tile) items, heaviest (most key
+// tiles under the causal mask) first.  Warp roles:
+//   warp 0      TMA loads: Q once per item, K and V tiles of 128 keys through 2-stage rings
+//   warp 1      tcgen05.mma: S = Q K^T into one of two tensor-memory score buffers, then
+//               O += P V (P from shared memory, V as an MN-major operand straight from its
+//               [key][feature] layout); S of tile j+1 is issued before P V of tile j, so the tensor
+//               core works while the softmax of tile j runs
+//   warps 2-5   softmax: one thread per query row reads its 128 scores from tensor memory, keeps the
+//               running maximum and sum (online softmax, exponentials as ex2 of pre-scaled scores),
+//               writes P as BFloat16 into a 128-byte-swizzled shared tile, rescales the O accumulator
+//               in tensor memory only when a row's maximum grew by more than 2^8 (the sum absorbs
+//               smaller drifts exactly), and at the end normalises O, stages it in shared memory and
+//               stores it by TMA.
+// No load uses cluster multicast.  Every barrier wait is bounded.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace tb200 {
+namespace {
+
+using namespace sm100;
+
+constexpr int kTile = 128;            // queries per item, keys per step
+constexpr int kHeadDim = 128;
+constexpr int kSlab = kTile * 128;    // one 64-feature slab of a 128-row tile: 16 KB
+constexpr int kTileBytes = 2 * kSlab; // 128 x 128 BFloat16
+constexpr int kAttnThreads = 192;
+constexpr float kRescaleThreshold = 8.0f;   // in log2 units
+
+__device__ int g_attn_error = 0;
+
+struct AttnFwdArgs {
+    CUtensorMap q, k, v, o;   // 4-D (feature, head, position, batch), boxes of 64 features x 128 positions
+    float *lse;               // [batch][query][head] or null
+    int batch, heads, kv_heads, queries, keys;
+    int q_tiles, items;
+    int causal;
+    float scale_log2;         // scale * log2(e)
+};
+
+__device__ __forceinline__ uint64_t now_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity, volatile int *failed, int code) {
+    if (mbar_wait(bar, parity, 4096)) return true;
+    const uint64_t t0 = now_ns();
+    while (true) {
+        if (mbar_wait(bar, parity, 1024)) return true;
+        if (*failed) return false;
+        if (now_ns() - t0 > 2000000000ull) {
+            *failed = code;
+            atomicCAS(&g_attn_error, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// item -> (batch*head index, query tile), heaviest query tiles first under the causal mask
+__device__ __forceinline__ void decode_item(const AttnFwdArgs &p, int item, int &bh, int &qt) {
+    const int per = p.batch * p.heads;
+    qt = p.q_tiles - 1 - item / per;
+    bh = item % per;
+}
+
+__device__ __forceinline__ int kv_tiles_of(const AttnFwdArgs &p, int qt) {
+    const int all = (p.keys + kTile - 1) / kTile;
+    if (!p.causal) return all;
+    const int upto = qt + 1;   // keys <= the tile's last query
+    return upto < all ? upto : all;
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __grid_constant__ AttnFwdArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *sq = smem;                       // Q tile
+    uint8_t *sk = sq + kTileBytes;            // K ring, 2 stages
+    uint8_t *sv = sk + 2 * kTileBytes;        // V ring, 2 stages
+    uint8_t *sp = sv + 2 * kTileBytes;        // P, 2 buffers (buffer 0 also stages the O store)
+
+    __shared__ __align__(8) uint64_t q_full, q_empty, o_done, o_free, pv_done;
+    __shared__ __align__(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+    __shared__ __align__(8) uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int failed_smem;
+    volatile int *failed = &failed_smem;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        failed_smem = 0;
+        mbar_init(&q_full, 1); mbar_init(&q_empty, 1); mbar_init(&o_done, 1); mbar_init(&o_free, 4);
+        mbar_init(&pv_done, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+            mbar_init(&p_full[s], 4); mbar_init(&p_empty[s], 1);
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&p.q); prefetch_tensormap(&p.k); prefetch_tensormap(&p.v); prefetch_tensormap(&p.o);
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_smem, 512);   // S0 | S1 | O | (spare)
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+    const uint32_t tmem_o = tmem_base + 2 * kTile;
+    const int group = p.heads / p.kv_heads;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            uint32_t q_phase = 0, kv_count = 0;
+            for (int item = blockIdx.x; item < p.items && !*failed; item += gridDim.x) {
+                int bh, qt;
+                decode_item(p, item, bh, qt);
+                const int b = bh / p.heads, h = bh % p.heads, hk = h / group;
+                if (!wait_bounded(&q_empty, q_phase ^ 1, failed, 1)) break;
+                mbar_arrive_expect_tx(&q_full, kTileBytes);
+                tma_load_4d(sq, &p.q, &q_full, 0, h, qt * kTile, b);
+                tma_load_4d(sq + kSlab, &p.q, &q_full, 64, h, qt * kTile, b);
+                q_phase ^= 1;
+                const int nkv = kv_tiles_of(p, qt);
+                for (int j = 0; j < nkv; j++, kv_count++) {
+                    const int st = kv_count & 1;
+                    const uint32_t ph = (kv_count >> 1) & 1;
+                    if (!wait_bounded(&k_empty[st], ph ^ 1, failed, 2)) break;
+                    mbar_arrive_expect_tx(&k_full[st], kTileBytes);
+                    tma_load_4d(sk + st * kTileBytes, &p.k, &k_full[st], 0, hk, j * kTile, b);
+                    tma_load_4d(sk + st * kTileBytes + kSlab, &p.k, &k_full[st], 64, hk, j * kTile, b);
+                    if (!wait_bounded(&v_empty[st], ph ^ 1, failed, 3)) break;
+                    mbar_arrive_expect_tx(&v_full[st], kTileBytes);
+                    tma_load_4d(sv + st * kTileBytes, &p.v, &v_full[st], 0, hk, j * kTile, b);
+                    tma_load_4d(sv + st * kTileBytes + kSlab, &p.v, &v_full[st], 64, hk, j * kTile, b);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            // S = Q K^T: both operands K-major (feature axis contiguous), two 64-feature slabs
+            const uint32_t idesc_qk = umma_idesc_bf16(kTile, kTile, false, false);
+            // O += P V: P K-major (key axis contiguous), V MN-major (feature axis contiguous)
+            const uint32_t idesc_pv = umma_idesc_bf16(kTile, kHeadDim, false, true);
+            uint32_t q_phase = 0, kv_count = 0, pv_count = 0, item_count = 0;
+            for (int item = blockIdx.x; item < p.items && !*failed; item += gridDim.x, item_count++) {
+                int bh, qt;
+                decode_item(p, item, bh, qt);
+                const int nkv = kv_tiles_of(p, qt);
+                if (!wait_bounded(&q_full, q_phase, failed, 4)) break;
+                q_phase ^= 1;
+                tcgen05_fence_after();
+                bool ok = true;
+                for (int j = 0; j <= nkv && ok; j++) {
+                    if (j < nkv) {
+                        const uint32_t c = kv_count + j;
+                        const int st = c & 1;
+                        const uint32_t ph = (c >> 1) & 1;
+                        if (!wait_bounded(&k_full[st], ph, failed, 6)) { ok = false; break; }
+                        if (!wait_bounded(&s_empty[st], ph ^ 1, failed, 7)) { ok = false; break; }
+                        tcgen05_fence_after();
+                        const uint32_t qa = smem_u32(sq), ka = smem_u32(sk + st * kTileBytes);
+#pragma unroll
+                        for (int k = 0; k < kHeadDim / 16; k++) {
+                            const uint32_t off = (k >> 2) * kSlab + (k & 3) * 32;
+                            tcgen05_mma_f16(tmem_base + st * kTile, umma_smem_desc(qa + off, 16, 1024),
+                                            umma_smem_desc(ka + off, 16, 1024), idesc_qk, k != 0);
+                        }
+                        tcgen05_commit(&k_empty[st]);
+                        tcgen05_commit(&s_full[st]);
+                        if (j == nkv - 1) tcgen05_commit(&q_empty);
+                    }
+                    if (j > 0) {
+                        const uint32_t c = pv_count;
+                        const int st = c & 1;
+                        const uint32_t ph = (c >> 1) & 1;
+                        // the first product of an item overwrites O: the previous item's epilogue must have read it
+                        if (j == 1 && !wait_bounded(&o_free, (item_count & 1) ^ 1, failed, 5)) { ok = false; break; }
+                        if (!wait_bounded(&v_full[st], ph, failed, 8)) { ok = false; break; }
+                        if (!wait_bounded(&p_full[st], ph, failed, 9)) { ok = false; break; }
+                        tcgen05_fence_after();
+                        const uint32_t pa = smem_u32(sp + st * kTileBytes), va = smem_u32(sv + st * kTileBytes);
+#pragma unroll
+                        for (int k = 0; k < kTile / 16; k++) {
+                            const uint32_t poff = (k >> 2) * kSlab + (k & 3) * 32;   // 16 keys = 32 bytes along P's rows
+                            const uint32_t voff = k * 16 * 128;                       // 16 key lines of 128 bytes
+                            tcgen05_mma_f16(tmem_o, umma_smem_desc(pa + poff, 16, 1024),
+                                            umma_smem_desc(va + voff, kSlab, 1024), idesc_pv, (j - 1) | k);
+                        }
+                        tcgen05_commit(&v_empty[st]);
+                        tcgen05_commit(&p_empty[st]);
+                        tcgen05_commit(&pv_done);
+                        if (j == nkv) tcgen05_commit(&o_done);
+                        pv_count++;
+                    }
+                }
+                kv_count += nkv;
+                if (!ok) break;
+            }
+        }
+    } else {
+        // ---- softmax, correction and epilogue: thread = query row
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+        uint32_t kv_count = 0, item_count = 0, pv_seen = 0;
+        for (int item = blockIdx.x; item < p.items; item += gridDim.x, item_count++) {
+            int bh, qt;
+            decode_item(p, item, bh, qt);
+            const int b = bh / p.heads, h = bh % p.heads;
+            const int nkv = kv_tiles_of(p, qt);
+            const int qi = qt * kTile + row;    // this thread's query
+            float m_used = -INFINITY, l = 0.0f;
+            bool ok = true;
+            for (int j = 0; j < nkv; j++, kv_count++) {
+                const int st = kv_count & 1;
+                const uint32_t ph = (kv_count >> 1) & 1;
+                if (!wait_bounded(&s_full[st], ph, failed, 10)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t ts = tmem_base + lane_base + st * kTile;
+                const int key0 = j * kTile;
+                const bool edge = (p.causal && key0 + kTile - 1 > qt * kTile) || key0 + kTile > p.keys;
+                // pass 1: the row's maximum
+                float m_tile = -INFINITY;
+#pragma unroll 1
+                for (int c = 0; c < kTile / 32; c++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(ts + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        float t = __uint_as_float(r[i]);
+                        if (edge) {
+                            const int key = key0 + c * 32 + i;
+                            if ((p.causal && key > qi) || key >= p.keys) t = -INFINITY;
+                        }
+                        m_tile = fmaxf(m_tile, t);
+                    }
+                }
+                m_tile *= p.scale_log2;   // scale > 0: the maximum commutes with the scaling
+                float alpha = 1.0f;
+                bool grew = false;
+                if (m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY)) {
+                    alpha = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_tile);
+                    grew = j > 0 && m_used != -INFINITY;
+                    m_used = m_tile;
+                    l *= alpha;
+                }
+                // the P buffer must have been read by the product that used it two tiles ago
+                if (!wait_bounded(&p_empty[st], ph ^ 1, failed, 11)) { ok = false; break; }
+                // pass 2: weights, their sum, P to shared memory
+                const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
+                uint8_t *prow = sp + st * kTileBytes + row * 128;
+#pragma unroll 1
+                for (int c = 0; c < kTile / 32; c++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(ts + c * 32, r);
+                    tmem_ld_wait();
+                    float w[32];
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        float t = __uint_as_float(r[i]);
+                        if (edge) {
+                            const int key = key0 + c * 32 + i;
+                            if ((p.causal && key > qi) || key >= p.keys) t = -INFINITY;
+                        }
+                        w[i] = fast_exp2(fmaf(t, p.scale_log2, neg_m));
+                        l += w[i];
+                    }
+                    // keys [32c, 32c+32) = slab c/2, 16-byte chunks 4(c%2) .. 4(c%2)+3 of the row
+                    uint8_t *slab = prow + (c >> 1) * kSlab;
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        uint4 v4;
+                        v4.x = pack_bf16x2(w[8 * g], w[8 * g + 1]);
+                        v4.y = pack_bf16x2(w[8 * g + 2], w[8 * g + 3]);
+                        v4.z = pack_bf16x2(w[8 * g + 4], w[8 * g + 5]);
+                        v4.w = pack_bf16x2(w[8 * g + 6], w[8 * g + 7]);
+                        const int chunk = (c & 1) * 4 + g;
+                        *reinterpret_cast<uint4 *>(slab + ((chunk ^ (row & 7)) << 4)) = v4;
+                    }
+                }
+                // the score buffer is free for the tile after next
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_empty[st]);
+                // O holds the products up to tile j-1 once pv_done has completed j times for this item
+                if (j > 0) {
+                    if (!wait_bounded(&pv_done, pv_seen & 1, failed, 12)) { ok = false; break; }
+                    pv_seen++;
+                    tcgen05_fence_after();
+                    if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll 1
+                        for (int c = 0; c < kHeadDim / 32; c++) {
+                            uint32_t r[32];
+                            tmem_ld_32x32(tmem_o + lane_base + c * 32, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                            tmem_st_32x32(tmem_o + lane_base + c * 32, r);
+                        }
+                        tmem_st_wait();
+                    }
+                }
+                tcgen05_fence_before();
+                fence_proxy_async();   // P was written by ordinary stores; the MMA reads it through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[st]);
+            }
+            if (!ok) break;
+            // ---- epilogue: O / l, the log-sum-exp, store
+            if (!wait_bounded(&o_done, item_count & 1, failed, 13)) break;
+            if (!wait_bounded(&pv_done, pv_seen & 1, failed, 14)) break;   // the last product's arrival
+            pv_seen++;
+            tcgen05_fence_after();
+            const float inv = 1.0f / l;
+            // every product of the item is complete, so P buffer 0 is idle: each warp stages its own 32
+            // rows of O there (the rows it alone writes when the buffer next holds P)
+#pragma unroll 1
+            for (int c = 0; c < kHeadDim / 32; c++) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_o + lane_base + c * 32, r);
+                tmem_ld_wait();
+                uint8_t *slab = sp + row * 128 + (c >> 1) * kSlab;   // P buffer 0 is idle: all products are done
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    uint4 v4;
+                    v4.x = pack_bf16x2(__uint_as_float(r[8 * g]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
+                    v4.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
+                    v4.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
+                    v4.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
+                    const int chunk = (c & 1) * 4 + g;
+                    *reinterpret_cast<uint4 *>(slab + ((chunk ^ (row & 7)) << 4)) = v4;
+                }
+            }
+            if (p.lse && qi < p.queries)
+                p.lse[(static_cast<long long>(b) * p.queries + qi) * p.heads + h] =
+                    (m_used == -INFINITY) ? -INFINITY : (m_used + log2f(l)) * 0.6931471805599453f;
+            tcgen05_fence_before();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                // this warp's 32 rows, two 64-feature slabs
+                tma_store_4d(&p.o, sp + q * 32 * 128, 0, h, qt * kTile + q * 32, b);
+                tma_store_4d(&p.o, sp + kSlab + q * 32 * 128, 64, h, qt * kTile + q * 32, b);
+                bulk_commit_group();
+                bulk_wait_group_read<0>();   // P buffer 0 is written again by the next item's first tile
+                mbar_arrive(&o_free);
+            }
+            __syncwarp();
+        }
+        if (lane == 0) bulk_wait_group<0>();
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int attn_encode_fn(EncodeTiledFn *out) {
+    static std::mutex lock;
+    static EncodeTiledFn fn = nullptr;
+    std::lock_guard<std::mutex> hold(lock);
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        TB200_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+        if (!sym || qres != cudaDriverEntryPointSuccess) return TB200_ERR_UNSUPPORTED;
+        fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    *out = fn;
+    return TB200_OK;
+}
+
+// (feature, head, position, batch) BFloat16 array, dense, as boxes of 64 features x `rows` positions.
+int attn_tmap(CUtensorMap *map, const void *base, int d, int heads, int positions, int batch, int rows) {
+    EncodeTiledFn fn;
+    int st = attn_encode_fn(&fn);
+    if (st) return st;
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(heads),
+                          static_cast<cuuint64_t>(positions), static_cast<cuuint64_t>(batch)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(d) * 2, static_cast<cuuint64_t>(d) * heads * 2,
+                             static_cast<cuuint64_t>(d) * heads * positions * 2};
+    cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(rows), 1};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? TB200_OK : TB200_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+}  // namespace tb200
+
+using namespace tb200;
+
+extern "C" int tb200_attention_fwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, void *o,
+                                   float *lse, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!d) return TB200_ERR_NULL;
+    if (d->batch < 0 || d->heads <= 0 || d->kv_heads <= 0 || d->queries < 0 || d->keys < 0 || d->head_dim <= 0)
+        return TB200_ERR_SHAPE;
+    if (d->heads % d->kv_heads != 0 || !(d->scale > 0.0f)) return TB200_ERR_SHAPE;
+    if (d->causal && d->queries != d->keys) return TB200_ERR_SHAPE;
+    if (d->dtype != TB200_BF16) return TB200_ERR_DTYPE;
+    if (d->head_dim != kHeadDim) return TB200_ERR_UNSUPPORTED;
+    if (d->batch == 0 || d->queries == 0) return TB200_OK;
+    if (d->keys == 0) return TB200_ERR_UNSUPPORTED;
+    if (!q || !k || !v || !o) return TB200_ERR_NULL;
+    if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(o, 16) || !aligned_to(lse, 4))
+        return TB200_ERR_ALIGN;
+    if (d->queries > (1 << 24) || d->keys > (1 << 24)) return TB200_ERR_SHAPE;
+    DeviceInfo dev;
+    int st = current_device(&dev);
+    if (st) return st;
+    AttnFwdArgs p{};
+    if ((st = attn_tmap(&p.q, q, d->head_dim, d->heads, d->queries, d->batch, kTile))) return st;
+    if ((st = attn_tmap(&p.k, k, d->head_dim, d->kv_heads, d->keys, d->batch, kTile))) return st;
+    if ((st = attn_tmap(&p.v, v, d->head_dim, d->kv_heads, d->keys, d->batch, kTile))) return st;
+    if ((st = attn_tmap(&p.o, o, d->head_dim, d->heads, d->queries, d->batch, 32))) return st;
+    p.lse = lse;
+    p.batch = d->batch; p.heads = d->heads; p.kv_heads = d->kv_heads; p.queries = d->queries; p.keys = d->keys;
+    p.q_tiles = static_cast<int>(ceil_div(d->queries, kTile));
+    p.items = p.q_tiles * d->batch * d->heads;
+    p.causal = d->causal;
+    p.scale_log2 = d->scale * kLog2e;
+    const size_t smem = 7 * kTileBytes + 1024;
+    static std::mutex lock;
+    static bool configured[64] = {};
+    {
+        std::lock_guard<std::mutex> hold(lock);
+        if (!configured[dev.device]) {
+            TB200_CUDA(cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(smem)));
+            configured[dev.device] = true;
+        }
+    }
+    const unsigned grid = static_cast<unsigned>(p.items < dev.sms ? p.items : dev.sms);
+    attention_fwd_kernel<<<grid, kAttnThreads, smem, stream>>>(p);
+    TB200_CUDA(cudaGetLastError());
+    return TB200_OK;
+}
+
+extern "C" int tb200_attention_device_error(void) {
+    int code = 0, zero = 0;
+    TB200_CUDA(cudaDeviceSynchronize());
+    TB200_CUDA(cudaMemcpyFromSymbol(&code, g_attn_error, sizeof(int)));
+    if (code) TB200_CUDA(cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int)));
+    return code;
+}

@@ -32,6 +32,13 @@ class GemmDesc(ctypes.Structure):
                 ("tile_n", ctypes.c_int), ("force_simt", ctypes.c_int), ("direct_epilogue", ctypes.c_int)]
 
 
+class AttnDesc(ctypes.Structure):
+    """tb200_attn_desc of include/tempest_b200.h."""
+    _fields_ = [("batch", ctypes.c_int), ("heads", ctypes.c_int), ("kv_heads", ctypes.c_int),
+                ("queries", ctypes.c_int), ("keys", ctypes.c_int), ("head_dim", ctypes.c_int),
+                ("causal", ctypes.c_int), ("scale", ctypes.c_float), ("dtype", ctypes.c_int)]
+
+
 # name -> (restype, argtypes): the declarations of include/tempest_b200.h
 SIGNATURES = {
     "tb200_version": (_i, []),
@@ -47,6 +54,8 @@ SIGNATURES = {
     "tb200_layernorm_bwd_noalloc": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i, _p]),
     "tb200_gemm": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
     "tb200_device_error": (_i, []),
+    "tb200_attention_fwd": (_i, [ctypes.POINTER(AttnDesc), _p, _p, _p, _p, _p, _p]),
+    "tb200_attention_device_error": (_i, []),
     "tb200_workspace_clear": (_i, [_p, _sz, _p]),
     "tb200_squared_error_workspace_bytes": (_sz, []),
     "tb200_squared_error": (_i, [_p, _p, _p, _p, _i64, _f, _f, _i, _i, _p, _sz, _p]),
@@ -199,3 +208,26 @@ def layernorm_bwd_noalloc(x, gamma, dy, mean, rstd, dx, dgamma, dbeta, eps, n, r
     check("tb200_layernorm_bwd_noalloc", load().tb200_layernorm_bwd_noalloc(
         x, gamma, dy, mean or None, rstd or None, dx, dgamma or None, dbeta or None, eps, n, rows, ld, dtype,
         stream or None))
+
+
+def attn_desc(batch, heads, queries, keys, head_dim, causal, scale=None, kv_heads=None, dtype=BF16):
+    d = AttnDesc()
+    d.batch, d.heads, d.kv_heads = batch, heads, kv_heads or heads
+    d.queries, d.keys, d.head_dim = queries, keys, head_dim
+    d.causal = int(causal)
+    d.scale = scale if scale is not None else head_dim ** -0.5
+    d.dtype = dtype
+    return d
+
+
+def attention_fwd(desc, q, k, v, o, lse=0, stream=0):
+    """q, o: [batch][queries][heads][head_dim]; k, v: [batch][keys][kv_heads][head_dim]; lse: [batch][queries][heads]."""
+    check("tb200_attention_fwd", load().tb200_attention_fwd(ctypes.byref(desc), q, k, v, o, lse or None,
+                                                            stream or None))
+
+
+def attention_device_error():
+    code = load().tb200_attention_device_error()
+    if code < 0:
+        check("tb200_attention_device_error", code)
+    return code

@@ -1,0 +1,135 @@
+"""Attention through the C ABI against the CPU oracle (the reference's attention program restated,
+test/fixtures/operations.jl:21-76): causal and not, grouped heads, sequence lengths that are not a
+multiple of the tile (the reference's own geometries use 70, 133, 200 positions,
+test/cuda/attention.jl:10-16), and the benchmark geometry on its 1/8 sub-batch against sampled
+oracle rows and a plain Float32 PyTorch restatement."""
+import numpy as np
+import pytest
+
+from helpers import ATOL_BF16, RTOL_F32
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).view(torch.bfloat16).cuda()
+
+
+def host(torch, t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def run_fwd(pkg, torch, q, k, v, causal, want_lse=True):
+    L = pkg.lib
+    B, S, H, D = q.shape
+    Skv, Hkv = k.shape[1], k.shape[2]
+    qd, kd, vd = dev(torch, q), dev(torch, k), dev(torch, v)
+    o = torch.full_like(qd, float("nan"))
+    lse = torch.full((B, S, H), float("nan"), device="cuda") if want_lse else None
+    desc = L.attn_desc(B, H, S, Skv, D, causal, kv_heads=Hkv)
+    L.attention_fwd(desc, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr() if want_lse else 0,
+                    torch.cuda.current_stream().cuda_stream)
+    assert L.attention_device_error() == 0
+    return host(torch, o), (lse.cpu().numpy() if want_lse else None)
+
+
+# (batch, heads, kv_heads, positions)
+GEOMETRIES = [(1, 2, 2, 128), (1, 2, 1, 256), (2, 3, 3, 200), (1, 1, 1, 70), (1, 4, 2, 384), (1, 2, 2, 133), (2, 2, 2, 640)]
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("B,H,Hkv,S", GEOMETRIES)
+def test_forward_against_oracle(pkg, cuda, oracle, B, H, Hkv, S, causal):
+    D = 128
+    q = oracle.to_bf16(oracle.normal((B, S, H, D), 1 + S))
+    k = oracle.to_bf16(oracle.normal((B, S, Hkv, D), 2 + S))
+    v = oracle.to_bf16(oracle.normal((B, S, Hkv, D), 3 + S))
+    o, lse = run_fwd(pkg, cuda, q, k, v, causal)
+    # the Float32 CPU reference (weights kept in Float32) and the variant that rounds the weights as the GPU does
+    o_ref, lse_ref = oracle.attention_fwd(q, k, v, causal, threads=8)
+    err = np.abs(oracle.from_bf16(o) - oracle.from_bf16(o_ref)).max()
+    assert err <= ATOL_BF16, err
+    assert np.abs(lse - lse_ref).max() <= 2e-5 * max(1.0, np.abs(lse_ref).max())
+    o64, lse64 = oracle.attention_f64(q, k, v, causal)
+    assert np.abs(oracle.from_bf16(o) - o64).max() <= ATOL_BF16
+    assert np.abs(lse - lse64).max() <= 2e-5 * max(1.0, np.abs(lse64).max())
+
+
+def test_forward_without_lse_and_peaked_scores(pkg, cuda, oracle):
+    """No log-sum-exp requested; and scores whose maximum keeps growing along the keys, which is what
+    makes the kernel rescale its accumulator."""
+    B, S, H, D = 1, 512, 2, 128
+    q = oracle.normal((B, S, H, D), 11)
+    k = oracle.normal((B, S, H, D), 12)
+    k = k * (1.0 + np.arange(S, dtype=np.float32)[None, :, None, None] / 64.0)   # later keys score higher
+    v = oracle.normal((B, S, H, D), 13)
+    qb, kb, vb = (oracle.to_bf16(a) for a in (q, k, v))
+    o, _ = run_fwd(pkg, cuda, qb, kb, vb, False, want_lse=False)
+    o64, _ = oracle.attention_f64(qb, kb, vb, False)
+    assert np.abs(oracle.from_bf16(o) - o64).max() <= ATOL_BF16
+    o, lse = run_fwd(pkg, cuda, qb, kb, vb, True)
+    o64, lse64 = oracle.attention_f64(qb, kb, vb, True)
+    assert np.abs(oracle.from_bf16(o) - o64).max() <= ATOL_BF16
+    assert np.abs(lse - lse64).max() <= 2e-5 * np.abs(lse64).max()
+
+
+def test_forward_refuses_what_it_does_not_compute(pkg, cuda):
+    L, torch = pkg.lib, cuda
+    x = torch.zeros(1, 128, 2, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(L.TB200Error) as e:
+        L.attention_fwd(L.attn_desc(1, 2, 128, 128, 64, True), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr())
+    assert e.value.status == -7
+    with pytest.raises(L.TB200Error) as e:   # causal needs as many queries as keys (operations.jl:40-41)
+        L.attention_fwd(L.attn_desc(1, 2, 128, 256, 128, True), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr())
+    assert e.value.status == -2
+
+
+def torch_reference(torch, q, k, v, causal, dout=None):
+    """Plain Float32 PyTorch restatement on the device, one head at a time."""
+    B, S, H, D = q.shape
+    qf, kf, vf = q.float().requires_grad_(dout is not None), k.float().requires_grad_(dout is not None), \
+        v.float().requires_grad_(dout is not None)
+    s = torch.einsum("bmhd,bnhd->bhmn", qf, kf) * (D ** -0.5)
+    if causal:
+        mask = torch.ones(S, S, device="cuda", dtype=torch.bool).triu(1)
+        s = s.masked_fill(mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    o = torch.einsum("bhmn,bnhd->bmhd", torch.exp(s - lse[..., None]), vf)
+    if dout is None:
+        return o, lse.permute(0, 2, 1)
+    o.backward(dout.float())
+    return o.detach(), lse.permute(0, 2, 1).detach(), qf.grad, kf.grad, vf.grad
+
+
+def test_forward_benchmark_geometry(pkg, cuda, oracle):
+    """B=8, H=32, S=4096, D=128 causal on its 1/8 sub-batch: sampled query rows against the oracle, and
+    4 heads in full against the Float32 restatement."""
+    torch, L = cuda, pkg.lib
+    torch.backends.cuda.matmul.allow_tf32 = False
+    B, S, H, D = 1, 4096, 32, 128
+    g = torch.Generator(device="cuda").manual_seed(20261125 + 4)
+    q, k, v = (torch.randn(B, S, H, D, device="cuda", generator=g).bfloat16() for _ in range(3))
+    o = torch.empty_like(q)
+    lse = torch.empty(B, S, H, device="cuda")
+    L.attention_fwd(L.attn_desc(B, H, S, S, D, True), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                    lse.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert L.attention_device_error() == 0
+    qh, kh, vh = host(torch, q), host(torch, k), host(torch, v)
+    fn = oracle.load().oracle_attention_fwd_rows
+    o_ref = np.zeros_like(qh)
+    lse_ref = np.zeros((B, S, H), np.float32)
+    import ctypes
+    rows = [(0, 4), (1000, 1003), (2047, 2050), (4092, 4096)]
+    for h in (0, 13, 31):
+        for m0, m1 in rows:
+            fn(oracle._ptr(qh), oracle._ptr(kh), oracle._ptr(vh), oracle._ptr(o_ref), oracle._ptr(lse_ref),
+               ctypes.c_int(B), ctypes.c_int(H), ctypes.c_int(H), ctypes.c_int(S), ctypes.c_int(S), ctypes.c_int(D),
+               ctypes.c_int(1), ctypes.c_float(D ** -0.5), ctypes.c_int(0), ctypes.c_int(h), ctypes.c_int(m0),
+               ctypes.c_int(m1), ctypes.c_int(0))
+            got = oracle.from_bf16(host(torch, o)[0, m0:m1, h])
+            assert np.abs(got - oracle.from_bf16(o_ref[0, m0:m1, h])).max() <= ATOL_BF16
+            assert np.abs(lse.cpu().numpy()[0, m0:m1, h] - lse_ref[0, m0:m1, h]).max() <= 2e-5 * 10
+    hs = slice(8, 12)
+    o32, lse32 = torch_reference(torch, q[:, :, hs], k[:, :, hs], v[:, :, hs], True)
+    assert (o[:, :, hs].float() - o32).abs().max().item() <= ATOL_BF16
+    assert (lse[:, :, hs] - lse32).abs().max().item() <= 1e-4
