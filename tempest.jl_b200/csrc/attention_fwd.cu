@@ -250,23 +250,31 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
                 const uint32_t ts = tmem_base + lane_base + st * kTile;
                 const int key0 = j * kTile;
                 const bool edge = (p.causal && key0 + kTile - 1 > qt * kTile) || key0 + kTile > p.keys;
-                // pass 1: the row's maximum
-                float m_tile = -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < kTile / 32; c++) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(ts + c * 32, r);
-                    tmem_ld_wait();
+                // the whole row of 128 scores into registers: the four loads are in flight together
+                // (one load-then-wait at a time costs about 800 cycles each)
+                uint32_t r[kTile];
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        float t = __uint_as_float(r[i]);
-                        if (edge) {
-                            const int key = key0 + c * 32 + i;
-                            if ((p.causal && key > qi) || key >= p.keys) t = -INFINITY;
-                        }
-                        m_tile = fmaxf(m_tile, t);
+                for (int c = 0; c < kTile / 32; c++)
+                    tmem_ld_32x32(ts + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+                tmem_ld_wait();
+                // the score buffer is free for the tile after next
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_empty[st]);
+                if (edge) {
+#pragma unroll
+                    for (int i = 0; i < kTile; i++) {
+                        const int key = key0 + i;
+                        if ((p.causal && key > qi) || key >= p.keys) r[i] = 0xff800000u;   // -Inf
                     }
                 }
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < kTile; i += 4) {
+#pragma unroll
+                    for (int u = 0; u < 4; u++) mx[u] = fmaxf(mx[u], __uint_as_float(r[i + u]));
+                }
+                float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
                 m_tile *= p.scale_log2;   // scale > 0: the maximum commutes with the scaling
                 float alpha = 1.0f;
                 bool grew = false;
@@ -278,42 +286,27 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
                 }
                 // the P buffer must have been read by the product that used it two tiles ago
                 if (!wait_bounded(&p_empty[st], ph ^ 1, failed, 11)) { ok = false; break; }
-                // pass 2: weights, their sum, P to shared memory
+                // weights, their sum, P to shared memory
                 const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
                 uint8_t *prow = sp + st * kTileBytes + row * 128;
-#pragma unroll 1
-                for (int c = 0; c < kTile / 32; c++) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(ts + c * 32, r);
-                    tmem_ld_wait();
-                    float w[32];
+                float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        float t = __uint_as_float(r[i]);
-                        if (edge) {
-                            const int key = key0 + c * 32 + i;
-                            if ((p.causal && key > qi) || key >= p.keys) t = -INFINITY;
-                        }
-                        w[i] = fast_exp2(fmaf(t, p.scale_log2, neg_m));
-                        l += w[i];
-                    }
-                    // keys [32c, 32c+32) = slab c/2, 16-byte chunks 4(c%2) .. 4(c%2)+3 of the row
-                    uint8_t *slab = prow + (c >> 1) * kSlab;
+                for (int g = 0; g < kTile / 8; g++) {
+                    float w[8];
 #pragma unroll
-                    for (int g = 0; g < 4; g++) {
-                        uint4 v4;
-                        v4.x = pack_bf16x2(w[8 * g], w[8 * g + 1]);
-                        v4.y = pack_bf16x2(w[8 * g + 2], w[8 * g + 3]);
-                        v4.z = pack_bf16x2(w[8 * g + 4], w[8 * g + 5]);
-                        v4.w = pack_bf16x2(w[8 * g + 6], w[8 * g + 7]);
-                        const int chunk = (c & 1) * 4 + g;
-                        *reinterpret_cast<uint4 *>(slab + ((chunk ^ (row & 7)) << 4)) = v4;
+                    for (int u = 0; u < 8; u++) {
+                        w[u] = fast_exp2(fmaf(__uint_as_float(r[8 * g + u]), p.scale_log2, neg_m));
+                        ls[u & 3] += w[u];
                     }
+                    uint4 v4;
+                    v4.x = pack_bf16x2(w[0], w[1]);
+                    v4.y = pack_bf16x2(w[2], w[3]);
+                    v4.z = pack_bf16x2(w[4], w[5]);
+                    v4.w = pack_bf16x2(w[6], w[7]);
+                    // keys [8g, 8g+8) = slab g/8, 16-byte chunk g%8 of the row
+                    *reinterpret_cast<uint4 *>(prow + (g >> 3) * kSlab + (((g & 7) ^ (row & 7)) << 4)) = v4;
                 }
-                // the score buffer is free for the tile after next
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&s_empty[st]);
+                l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
                 // O holds the products up to tile j-1 once pv_done has completed j times for this item
                 if (j > 0) {
                     if (!wait_bounded(&pv_done, pv_seen & 1, failed, 12)) { ok = false; break; }
@@ -346,21 +339,21 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
             const float inv = 1.0f / l;
             // every product of the item is complete, so P buffer 0 is idle: each warp stages its own 32
             // rows of O there (the rows it alone writes when the buffer next holds P)
-#pragma unroll 1
-            for (int c = 0; c < kHeadDim / 32; c++) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_o + lane_base + c * 32, r);
-                tmem_ld_wait();
-                uint8_t *slab = sp + row * 128 + (c >> 1) * kSlab;   // P buffer 0 is idle: all products are done
+            {
+                uint32_t r[kHeadDim];
 #pragma unroll
-                for (int g = 0; g < 4; g++) {
+                for (int c = 0; c < kHeadDim / 32; c++)
+                    tmem_ld_32x32(tmem_o + lane_base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+                tmem_ld_wait();
+#pragma unroll
+                for (int g = 0; g < kHeadDim / 8; g++) {
                     uint4 v4;
                     v4.x = pack_bf16x2(__uint_as_float(r[8 * g]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
                     v4.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
                     v4.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
                     v4.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
-                    const int chunk = (c & 1) * 4 + g;
-                    *reinterpret_cast<uint4 *>(slab + ((chunk ^ (row & 7)) << 4)) = v4;
+                    // P buffer 0 is idle: all products are done
+                    *reinterpret_cast<uint4 *>(sp + row * 128 + (g >> 3) * kSlab + (((g & 7) ^ (row & 7)) << 4)) = v4;
                 }
             }
             if (p.lse && qi < p.queries)
