@@ -223,6 +223,24 @@ int tb200_attention_fwd(const tb200_attn_desc *desc, const void *q, const void *
 /* As tb200_device_error, for the attention kernels. */
 int tb200_attention_device_error(void);
 
+size_t tb200_attention_bwd_workspace_bytes(const tb200_attn_desc *desc);
+
+/* The pullback of tb200_attention_fwd for upstream dout: dq, dk, dv (BFloat16,
+ * laid out as q, k, v).  Recomputes the scores, P = exp(s - lse), with
+ * delta = sum_d dout*o from the output as stored (the reference's
+ * `rounded_backward`, docs/src/cuda.md:54-63); P and dS enter their products
+ * rounded to BFloat16 (docs/src/cuda.md:40-46).  Deterministic: dk and dv are
+ * folded per key tile over the queries, dq by a second kernel per query tile
+ * over the keys, with no atomic adds -- the reference's `deterministic = true`
+ * form (ext/cuTileExt/build.jl:295-318) of its backward kernel
+ * (ext/cuTileExt/transpose.jl:32-48, 165-213).  workspace:
+ * tb200_attention_bwd_workspace_bytes bytes, 16-byte aligned. */
+int tb200_attention_bwd(const tb200_attn_desc *desc, const void *q, const void *k, const void *v,
+                        const void *o, const float *lse, const void *dout, void *dq, void *dk,
+                        void *dv, void *workspace, size_t workspace_bytes, void *stream);
+
+int tb200_attention_bwd_device_error(void);
+
 /* ---- pointwise maps and folds over other axes -------------------------------
  * These replace the generated `:pointwise` kernels (ext/cuTileExt/build.jl:3-10)
  * and the full / partial folds with their merge launches

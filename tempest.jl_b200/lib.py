@@ -56,6 +56,9 @@ SIGNATURES = {
     "tb200_device_error": (_i, []),
     "tb200_attention_fwd": (_i, [ctypes.POINTER(AttnDesc), _p, _p, _p, _p, _p, _p]),
     "tb200_attention_device_error": (_i, []),
+    "tb200_attention_bwd_workspace_bytes": (_sz, [ctypes.POINTER(AttnDesc)]),
+    "tb200_attention_bwd": (_i, [ctypes.POINTER(AttnDesc), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "tb200_attention_bwd_device_error": (_i, []),
     "tb200_workspace_clear": (_i, [_p, _sz, _p]),
     "tb200_squared_error_workspace_bytes": (_sz, []),
     "tb200_squared_error": (_i, [_p, _p, _p, _p, _i64, _f, _f, _i, _i, _p, _sz, _p]),
@@ -230,4 +233,20 @@ def attention_device_error():
     code = load().tb200_attention_device_error()
     if code < 0:
         check("tb200_attention_device_error", code)
+    return code
+
+
+def attention_bwd_workspace_bytes(desc):
+    return load().tb200_attention_bwd_workspace_bytes(ctypes.byref(desc))
+
+
+def attention_bwd(desc, q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream=0):
+    check("tb200_attention_bwd", load().tb200_attention_bwd(
+        ctypes.byref(desc), q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream or None))
+
+
+def attention_bwd_device_error():
+    code = load().tb200_attention_bwd_device_error()
+    if code < 0:
+        check("tb200_attention_bwd_device_error", code)
     return code

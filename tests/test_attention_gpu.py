@@ -133,3 +133,87 @@ def test_forward_benchmark_geometry(pkg, cuda, oracle):
     o32, lse32 = torch_reference(torch, q[:, :, hs], k[:, :, hs], v[:, :, hs], True)
     assert (o[:, :, hs].float() - o32).abs().max().item() <= ATOL_BF16
     assert (lse[:, :, hs] - lse32).abs().max().item() <= 1e-4
+
+
+def run_bwd(pkg, torch, q, k, v, dout, causal):
+    L = pkg.lib
+    B, S, H, D = q.shape
+    Skv, Hkv = k.shape[1], k.shape[2]
+    qd, kd, vd, gd = dev(torch, q), dev(torch, k), dev(torch, v), dev(torch, dout)
+    o = torch.empty_like(qd)
+    lse = torch.empty(B, S, H, device="cuda")
+    desc = L.attn_desc(B, H, S, Skv, D, causal, kv_heads=Hkv)
+    stream = torch.cuda.current_stream().cuda_stream
+    L.attention_fwd(desc, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr(), stream)
+    dq, dk, dv = (torch.full_like(t, float("nan")) for t in (qd, kd, vd))
+    need = L.attention_bwd_workspace_bytes(desc)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    L.attention_bwd(desc, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr(), gd.data_ptr(),
+                    dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), need, stream)
+    assert L.attention_device_error() == 0 and L.attention_bwd_device_error() == 0
+    return host(torch, dq), host(torch, dk), host(torch, dv), host(torch, o), lse.cpu().numpy()
+
+
+def close_grad(oracle, got_bits, want, what):
+    """2e-2 max-abs against the Float32 CPU reference, relative to the gradient's own scale
+    (gradients of N(0,1) data reach tens), and 1e-2 in norm."""
+    got = oracle.from_bf16(got_bits).astype(np.float64)
+    want = np.asarray(want, np.float64)
+    assert np.isfinite(got).all(), what
+    scale = max(1.0, np.abs(want).max())
+    assert np.abs(got - want).max() <= ATOL_BF16 * scale, (what, np.abs(got - want).max(), scale)
+    assert np.linalg.norm(got - want) <= 1e-2 * np.linalg.norm(want), what
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("B,H,Hkv,S", GEOMETRIES)
+def test_backward_against_oracle(pkg, cuda, oracle, B, H, Hkv, S, causal):
+    D = 128
+    q = oracle.to_bf16(oracle.normal((B, S, H, D), 21 + S))
+    k = oracle.to_bf16(oracle.normal((B, S, Hkv, D), 22 + S))
+    v = oracle.to_bf16(oracle.normal((B, S, Hkv, D), 23 + S))
+    g = oracle.to_bf16(oracle.normal((B, S, H, D), 24 + S))
+    dq, dk, dv, o, lse = run_bwd(pkg, cuda, q, k, v, g, causal)
+    # the oracle's pullback from the same saved output and log-sum-exp the kernel read
+    dq_ref, dk_ref, dv_ref = oracle.attention_bwd(q, k, v, o, lse, g, causal, threads=8)
+    close_grad(oracle, dq, oracle.from_bf16(dq_ref), "dq")
+    close_grad(oracle, dk, oracle.from_bf16(dk_ref), "dk")
+    close_grad(oracle, dv, oracle.from_bf16(dv_ref), "dv")
+    _, _, dq64, dk64, dv64 = oracle.attention_f64(q, k, v, causal, dout=g)
+    close_grad(oracle, dq, dq64, "dq vs Float64")
+    close_grad(oracle, dk, dk64, "dk vs Float64")
+    close_grad(oracle, dv, dv64, "dv vs Float64")
+
+
+def test_backward_repeats_bit_for_bit(pkg, cuda, oracle):
+    B, S, H, D = 1, 384, 4, 128
+    q, k, v, g = (oracle.to_bf16(oracle.normal((B, S, H if i != 1 and i != 2 else 2, D), 31 + i)) for i in range(4))
+    first = run_bwd(pkg, cuda, q, k, v, g, True)
+    again = run_bwd(pkg, cuda, q, k, v, g, True)
+    for a, b in zip(first[:3], again[:3]):
+        assert np.array_equal(a, b)
+
+
+def test_backward_benchmark_geometry(pkg, cuda):
+    """S=4096, D=128 causal, 4 heads of the 1/8 sub-batch against the Float32 PyTorch restatement."""
+    torch, L = cuda, pkg.lib
+    torch.backends.cuda.matmul.allow_tf32 = False
+    B, S, H, D = 1, 4096, 4, 128
+    gen = torch.Generator(device="cuda").manual_seed(20261125 + 5)
+    q, k, v, g = (torch.randn(B, S, H, D, device="cuda", generator=gen).bfloat16() for _ in range(4))
+    o, lse = torch.empty_like(q), torch.empty(B, S, H, device="cuda")
+    desc = L.attn_desc(B, H, S, S, D, True)
+    stream = torch.cuda.current_stream().cuda_stream
+    L.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), stream)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    need = L.attention_bwd_workspace_bytes(desc)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    L.attention_bwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), g.data_ptr(),
+                    dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), need, stream)
+    assert L.attention_device_error() == 0 and L.attention_bwd_device_error() == 0
+    _, _, dq32, dk32, dv32 = torch_reference(torch, q, k, v, True, dout=g)
+    for got, want, name in ((dq, dq32, "dq"), (dk, dk32, "dk"), (dv, dv32, "dv")):
+        err = (got.float() - want).abs().max().item()
+        scale = max(1.0, want.abs().max().item())
+        assert err <= ATOL_BF16 * scale, (name, err, scale)
+        assert ((got.float() - want).norm() / want.norm()).item() <= 1e-2, name
