@@ -241,6 +241,27 @@ int tb200_attention_bwd(const tb200_attn_desc *desc, const void *q, const void *
 
 int tb200_attention_bwd_device_error(void);
 
+/* ---- chunked gated DeltaNet ------------------------------------------------------
+ * The program of examples/deltanet.jl:56-85: q, k (dk, T, heads) = memory
+ * [head][t][dk], v (dv, T, heads), a (log decay) and beta (T, heads) in
+ * Float32, result (T, dv, heads) = memory [head][dv][t].  Replaces the batched
+ * products and the `:recurrence` kernel Tempest plans for it
+ * (ext/cuTileExt/build.jl:772-835, ext/cuTileExt/cuTileExt.jl:831-852). */
+typedef struct tb200_deltanet_desc {
+    int heads;        /* batch * heads sequences */
+    int positions;    /* T, a multiple of chunk */
+    int dk, dv;       /* 128, 128 */
+    int chunk;        /* 64 */
+    int dtype;        /* TB200_BF16 for q, k, v and the result */
+} tb200_deltanet_desc;
+
+size_t tb200_deltanet_workspace_bytes(const tb200_deltanet_desc *desc);
+
+/* Forward pass.  Other geometries than dk = dv = 128, chunk = 64: TB200_ERR_UNSUPPORTED. */
+int tb200_deltanet_fwd(const tb200_deltanet_desc *desc, const void *q, const void *k, const void *v,
+                       const float *a, const float *beta, void *o, void *workspace,
+                       size_t workspace_bytes, void *stream);
+
 /* ---- pointwise maps and folds over other axes -------------------------------
  * These replace the generated `:pointwise` kernels (ext/cuTileExt/build.jl:3-10)
  * and the full / partial folds with their merge launches

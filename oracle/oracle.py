@@ -401,3 +401,34 @@ def attention_f64(q, k, v, causal, scale=None, dout=None):
     dk = dkx.reshape(B, Skv, Hkv, g, D).sum(axis=3)
     dv = dvx.reshape(B, Skv, Hkv, g, D).sum(axis=3)
     return o, lse, dq, dk, dv
+
+
+# -------------------------------------------------------------- DeltaNet ----
+
+def deltanet_sequential(q, k, v, a, beta, threads=1):
+    """The gated delta rule token by token in Float64 (examples/deltanet.jl:89-101).
+    q, k [heads][T][dk], v [heads][T][dv] BFloat16 bits; a, beta [heads][T] float32.
+    Returns o [heads][dv][T] float64 (the Julia (T, dv, heads) result's memory)."""
+    Hn, T, dk = q.shape
+    dv = v.shape[2]
+    o = np.zeros((Hn, dv, T), np.float64)
+    a = np.ascontiguousarray(a, np.float32)
+    beta = np.ascontiguousarray(beta, np.float32)
+    fn = load().oracle_deltanet_head
+    jobs = [lambda h=h: fn(_ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(beta), _ptr(o), _int(T), _int(dk), _int(dv), _int(h))
+            for h in range(Hn)]
+    _pool(jobs, threads)
+    return o
+
+
+def deltanet_inputs(heads, T, dk, dv, seed):
+    """The benchmark's distributions: q, k ~ N(0,1) L2-normalised per position, v ~ N(0,1),
+    beta = sigmoid(N(0,1)), a = -softplus(N(0,1))."""
+    q = normal((heads, T, dk), seed)
+    k = normal((heads, T, dk), seed + 1)
+    q /= np.linalg.norm(q, axis=-1, keepdims=True)
+    k /= np.linalg.norm(k, axis=-1, keepdims=True)
+    v = normal((heads, T, dv), seed + 2)
+    beta = (1.0 / (1.0 + np.exp(-normal((heads, T), seed + 3)))).astype(np.float32)
+    a = (-np.log1p(np.exp(normal((heads, T), seed + 4)))).astype(np.float32)
+    return to_bf16(q), to_bf16(k), to_bf16(v), a, beta

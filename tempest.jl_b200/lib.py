@@ -39,6 +39,12 @@ class AttnDesc(ctypes.Structure):
                 ("causal", ctypes.c_int), ("scale", ctypes.c_float), ("dtype", ctypes.c_int)]
 
 
+class DeltanetDesc(ctypes.Structure):
+    """tb200_deltanet_desc of include/tempest_b200.h."""
+    _fields_ = [("heads", ctypes.c_int), ("positions", ctypes.c_int), ("dk", ctypes.c_int), ("dv", ctypes.c_int),
+                ("chunk", ctypes.c_int), ("dtype", ctypes.c_int)]
+
+
 # name -> (restype, argtypes): the declarations of include/tempest_b200.h
 SIGNATURES = {
     "tb200_version": (_i, []),
@@ -59,6 +65,8 @@ SIGNATURES = {
     "tb200_attention_bwd_workspace_bytes": (_sz, [ctypes.POINTER(AttnDesc)]),
     "tb200_attention_bwd": (_i, [ctypes.POINTER(AttnDesc), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "tb200_attention_bwd_device_error": (_i, []),
+    "tb200_deltanet_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
+    "tb200_deltanet_fwd": (_i, [ctypes.POINTER(DeltanetDesc), _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "tb200_workspace_clear": (_i, [_p, _sz, _p]),
     "tb200_squared_error_workspace_bytes": (_sz, []),
     "tb200_squared_error": (_i, [_p, _p, _p, _p, _i64, _f, _f, _i, _i, _p, _sz, _p]),
@@ -250,3 +258,19 @@ def attention_bwd_device_error():
     if code < 0:
         check("tb200_attention_bwd_device_error", code)
     return code
+
+
+def deltanet_desc(heads, positions, dk=128, dv=128, chunk=64, dtype=BF16):
+    d = DeltanetDesc()
+    d.heads, d.positions, d.dk, d.dv, d.chunk, d.dtype = heads, positions, dk, dv, chunk, dtype
+    return d
+
+
+def deltanet_workspace_bytes(desc):
+    return load().tb200_deltanet_workspace_bytes(ctypes.byref(desc))
+
+
+def deltanet_fwd(desc, q, k, v, a, beta, o, workspace, workspace_bytes, stream=0):
+    """q, k [heads][T][dk], v [heads][T][dv] BFloat16; a, beta [heads][T] Float32; o [heads][dv][T] BFloat16."""
+    check("tb200_deltanet_fwd", load().tb200_deltanet_fwd(ctypes.byref(desc), q, k, v, a, beta, o, workspace,
+                                                          workspace_bytes, stream or None))
