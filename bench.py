@@ -45,9 +45,9 @@ def algorithmic_bytes(op, rows, size):
     if op == "softmax_fwd":
         extra = rows * 4                      # the log-sum-exp saved for the backward
     elif op == "layernorm_fwd":
-        extra = 2 * N_REDUCE * size           # gamma, beta
+        extra = 2 * N_REDUCE * size + 2 * rows * 4   # gamma, beta; mean and rstd saved for the backward
     elif op == "layernorm_bwd":
-        extra = 3 * N_REDUCE * size           # gamma, dgamma, dbeta
+        extra = 3 * N_REDUCE * size + 2 * rows * 4   # gamma, dgamma, dbeta; the saved mean and rstd
     return STREAMS[op] * N_REDUCE * rows * size + extra
 
 
@@ -143,7 +143,9 @@ class Workload:
             b = torch.zeros(n, device="cuda", dtype=x.dtype)
             y, dx, yl, dxl = (torch.empty_like(x) for _ in range(4))
             lse = torch.empty(rows, device="cuda")
+            mean, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
             dw, db = torch.empty_like(w), torch.empty_like(w)
+            stat = lambda t, v: I.Strided("Float32", 0, (1, rows), (1, 1), t, v)  # noqa: E731
             self.outputs[eltype] = (y, dx, yl, dxl, lse, dw, db)
             col = lambda t, v: I.dense_columns(t, eltype, n, rows, v)  # noqa: E731
             vec = lambda t, v: I.dense_vector(t, eltype, n, v)         # noqa: E731
@@ -151,10 +153,13 @@ class Workload:
                 ("softmax_fwd", "softmax_columns_lse",
                  {"x": col(x, 1), "y": col(y, 2), "lse": I.Strided("Float32", 0, (1, rows), (1, 1), lse, 3)}),
                 ("softmax_bwd", "softmax_columns_pullback", {"y": col(y, 2), "g": col(g, 4), "dx": col(dx, 5)}),
-                ("layernorm_fwd", "layernorm_bias", {"x": col(x, 1), "w": vec(w, 6), "b": vec(b, 7), "y": col(yl, 8)}),
+                # the forward keeps each row's mean and rstd (8 bytes a row) and the backward reads them
+                # instead of folding the row twice more: the planner's save-over-recompute choice
+                ("layernorm_fwd", "layernorm_bias", {"x": col(x, 1), "w": vec(w, 6), "b": vec(b, 7), "y": col(yl, 8),
+                                                     "mean": stat(mean, 12), "rstd": stat(rstd, 13)}),
                 ("layernorm_bwd", "layernorm_pullback",
                  {"x": col(x, 1), "w": vec(w, 6), "g": col(g, 4), "dx": col(dxl, 9), "dw": vec(dw, 10),
-                  "db": vec(db, 11)}),
+                  "db": vec(db, 11), "mean": stat(mean, 12), "rstd": stat(rstd, 13)}),
             ]
             for name, template, arrays in plans:
                 launch, _ = self.lib.build(self.target, I.Binding(template, {"n": n, "rows": rows}, arrays),
@@ -336,6 +341,58 @@ def run_also(torch, dist, pkg, world, rank):
         tf = 2.0 * M * N * K / gms / 1e9
         out["gemm_bias_gelu_8192x4096x4096"] = {"TFLOP/s": round(tf, 1), "ms": round(gms, 4),
                                                 "frac_of_measured_bf16_peak": round(tf / tensor_peak, 4)}
+
+        def clock(fn, iters):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / iters
+
+        # BASELINE.json configs[3]: causal attention, B=8, H=32, S=4096, D=128, BFloat16, forward + backward
+        Bq, Hq, Sq, Dq = 8, 32, 4096, 128
+        q, k, v, g = (torch.randn(Bq, Sq, Hq, Dq, device="cuda").bfloat16() for _ in range(4))
+        o, lse = torch.empty_like(q), torch.empty(Bq, Sq, Hq, device="cuda")
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        desc = L.attn_desc(Bq, Hq, Sq, Sq, Dq, True)
+        need = L.attention_bwd_workspace_bytes(desc)
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        fwd = clock(lambda: L.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                            lse.data_ptr(), stream), 10)
+        bwd = clock(lambda: L.attention_bwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                            lse.data_ptr(), g.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                            ws.data_ptr(), need, stream), 5)
+        fl = 4.0 * Bq * Hq * Sq * Sq * Dq * 0.5
+        out["attention_causal_B8_H32_S4096_D128"] = {
+            "fwd_ms": round(fwd, 4), "fwd_TFLOP/s": round(fl / fwd / 1e9, 1),
+            "fwd_frac_of_measured_bf16_peak": round(fl / fwd / 1e9 / tensor_peak, 4),
+            "bwd_ms": round(bwd, 4), "bwd_TFLOP/s": round(2.5 * fl / bwd / 1e9, 1),
+            "bwd_frac_of_measured_bf16_peak": round(2.5 * fl / bwd / 1e9 / tensor_peak, 4),
+            "bwd_note": "algorithmic 5 products (2.5 x forward); the deterministic two-kernel form executes 7",
+            "device_error": L.attention_device_error() + L.attention_bwd_device_error()}
+        del q, k, v, g, o, dq, dk, dv, ws
+        # BASELINE.json configs[4]: chunked gated DeltaNet forward, B*H = 64 sequences of 8192, dk = dv = 128
+        Hn, T = 64, 8192
+        qd = torch.nn.functional.normalize(torch.randn(Hn, T, 128, device="cuda"), dim=-1).bfloat16()
+        kd = torch.nn.functional.normalize(torch.randn(Hn, T, 128, device="cuda"), dim=-1).bfloat16()
+        vd = torch.randn(Hn, T, 128, device="cuda").bfloat16()
+        ad = -torch.nn.functional.softplus(torch.randn(Hn, T, device="cuda"))
+        bd = torch.sigmoid(torch.randn(Hn, T, device="cuda"))
+        od = torch.empty(Hn, 128, T, device="cuda", dtype=torch.bfloat16)
+        dd = L.deltanet_desc(Hn, T)
+        dneed = L.deltanet_workspace_bytes(dd)
+        dws = torch.empty(dneed, dtype=torch.uint8, device="cuda")
+        dms = clock(lambda: L.deltanet_fwd(dd, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ad.data_ptr(), bd.data_ptr(),
+                                           od.data_ptr(), dws.data_ptr(), dneed, stream), 5)
+        dbytes = 4 * Hn * T * 128 * 2 + 2 * Hn * T * 4
+        hbm, _ = measured_peaks()
+        out["deltanet_fwd_B4_H16_S8192"] = {"ms": round(dms, 4), "algorithmic_GB/s": round(dbytes / dms / 1e6, 1),
+                                            "frac_of_measured_hbm_peak": round(dbytes / dms / 1e6 / hbm, 4)}
     return out
 
 

@@ -49,6 +49,7 @@ struct RowArgs {
     int rpc;            // rows per block (resident)
     int splits;         // chunks per row (split)
     int stat_bf16;
+    int exact;          // every vector slot of every row slot is inside the data: no bounds checks
     long long rows, ld;
 };
 
@@ -59,12 +60,13 @@ struct Row {
     static constexpr int E = VPT * EPV;
     static __device__ __forceinline__ int at(int k, int t, int tpr) { return (k * tpr + t) * EPV; }
 
+    template <bool EXACT = false>
     static __device__ __forceinline__ void load(float (&v)[E], const T *row, int n, int t, int tpr, float fill,
                                                 bool live) {
 #pragma unroll
         for (int k = 0; k < VPT; k++) {
             int idx = at(k, t, tpr);
-            if (live && idx < n) A::load(row + idx, &v[k * EPV]);
+            if (EXACT || (live && idx < n)) A::load(row + idx, &v[k * EPV]);
             else
 #pragma unroll
                 for (int e = 0; e < EPV; e++) v[k * EPV + e] = fill;
@@ -81,11 +83,12 @@ struct Row {
                 for (int e = 0; e < EPV; e++) v[k * EPV + e] = fill;
         }
     }
+    template <bool EXACT = false>
     static __device__ __forceinline__ void store(const float (&v)[E], T *row, int n, int t, int tpr, bool live) {
 #pragma unroll
         for (int k = 0; k < VPT; k++) {
             int idx = at(k, t, tpr);
-            if (live && idx < n) A::store(row + idx, &v[k * EPV]);
+            if (EXACT || (live && idx < n)) A::store(row + idx, &v[k * EPV]);
         }
     }
     // Float32 partial sums, one row of the workspace
@@ -112,8 +115,8 @@ struct Row {
 
 // ------------------------------------------------------------ resident ------
 
-template <typename T, bool VEC, int VPT>
-__global__ void __launch_bounds__(kResidentMaxThreads) softmax_fwd_resident(RowArgs a) {
+template <typename T, bool VEC, int VPT, bool EXACT>
+__device__ __forceinline__ void softmax_fwd_resident_body(const RowArgs &a) {
     using R = Row<T, VEC, VPT>;
     __shared__ float red[2 * 32 * kRedWidth];
     RowCtx c = make_row_ctx(a.tpr, red);
@@ -122,9 +125,9 @@ __global__ void __launch_bounds__(kResidentMaxThreads) softmax_fwd_resident(RowA
     const long long groups = (a.rows + a.rpc - 1) / a.rpc;
     for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
         const long long r = g * a.rpc + c.slot;
-        const bool live = r < a.rows;
+        const bool live = EXACT || r < a.rows;
         float v[R::E];
-        R::load(v, x + r * a.ld, a.n, c.t, a.tpr, -INFINITY, live);
+        R::template load<EXACT>(v, x + r * a.ld, a.n, c.t, a.tpr, -INFINITY, live);
         float m = -INFINITY;
 #pragma unroll
         for (int e = 0; e < R::E; e++) m = fmaxf(m, v[e]);
@@ -144,12 +147,18 @@ __global__ void __launch_bounds__(kResidentMaxThreads) softmax_fwd_resident(RowA
         const float inv = 1.0f / s;
 #pragma unroll
         for (int e = 0; e < R::E; e++) v[e] *= inv;
-        R::store(v, y + r * a.ld, a.n, c.t, a.tpr, live);
+        R::template store<EXACT>(v, y + r * a.ld, a.n, c.t, a.tpr, live);
     }
 }
 
 template <typename T, bool VEC, int VPT>
-__global__ void __launch_bounds__(kResidentMaxThreads) softmax_bwd_resident(RowArgs a) {
+__global__ void __launch_bounds__(kResidentMaxThreads) softmax_fwd_resident(RowArgs a) {
+    if (a.exact) softmax_fwd_resident_body<T, VEC, VPT, true>(a);
+    else softmax_fwd_resident_body<T, VEC, VPT, false>(a);
+}
+
+template <typename T, bool VEC, int VPT, bool EXACT>
+__device__ __forceinline__ void softmax_bwd_resident_body(const RowArgs &a) {
     using R = Row<T, VEC, VPT>;
     __shared__ float red[2 * 32 * kRedWidth];
     RowCtx c = make_row_ctx(a.tpr, red);
@@ -159,10 +168,10 @@ __global__ void __launch_bounds__(kResidentMaxThreads) softmax_bwd_resident(RowA
     const long long groups = (a.rows + a.rpc - 1) / a.rpc;
     for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
         const long long r = g * a.rpc + c.slot;
-        const bool live = r < a.rows;
+        const bool live = EXACT || r < a.rows;
         float y[R::E], d[R::E];
-        R::load(y, yx + r * a.ld, a.n, c.t, a.tpr, a.cstat0 ? -INFINITY : 0.0f, live);
-        R::load(d, dy + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
+        R::template load<EXACT>(y, yx + r * a.ld, a.n, c.t, a.tpr, a.cstat0 ? -INFINITY : 0.0f, live);
+        R::template load<EXACT>(d, dy + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
         if (a.cstat0) {
             const float off = (live ? load_stat(a.cstat0, r, a.stat_bf16) : 0.0f) * kLog2e;
 #pragma unroll
@@ -174,12 +183,18 @@ __global__ void __launch_bounds__(kResidentMaxThreads) softmax_bwd_resident(RowA
         s = row_allreduce1(s, c, SumOp());
 #pragma unroll
         for (int e = 0; e < R::E; e++) d[e] = y[e] * (d[e] - s);
-        R::store(d, dx + r * a.ld, a.n, c.t, a.tpr, live);
+        R::template store<EXACT>(d, dx + r * a.ld, a.n, c.t, a.tpr, live);
     }
 }
 
 template <typename T, bool VEC, int VPT>
-__global__ void __launch_bounds__(kResidentMaxThreads, 2) layernorm_fwd_resident(RowArgs a) {
+__global__ void __launch_bounds__(kResidentMaxThreads) softmax_bwd_resident(RowArgs a) {
+    if (a.exact) softmax_bwd_resident_body<T, VEC, VPT, true>(a);
+    else softmax_bwd_resident_body<T, VEC, VPT, false>(a);
+}
+
+template <typename T, bool VEC, int VPT, bool EXACT>
+__device__ __forceinline__ void layernorm_fwd_resident_body(const RowArgs &a) {
     using R = Row<T, VEC, VPT>;
     __shared__ float red[2 * 32 * kRedWidth];
     RowCtx c = make_row_ctx(a.tpr, red);
@@ -193,9 +208,9 @@ __global__ void __launch_bounds__(kResidentMaxThreads, 2) layernorm_fwd_resident
     const long long groups = (a.rows + a.rpc - 1) / a.rpc;
     for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
         const long long r = g * a.rpc + c.slot;
-        const bool live = r < a.rows;
+        const bool live = EXACT || r < a.rows;
         float v[R::E];
-        R::load(v, x + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
+        R::template load<EXACT>(v, x + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
         float s = 0.0f;
 #pragma unroll
         for (int e = 0; e < R::E; e++) s += v[e];
@@ -203,7 +218,7 @@ __global__ void __launch_bounds__(kResidentMaxThreads, 2) layernorm_fwd_resident
         float q = 0.0f;
 #pragma unroll
         for (int k = 0; k < VPT; k++) {
-            const bool in = R::inside(k, c.t, a.tpr, a.n);
+            const bool in = EXACT || R::inside(k, c.t, a.tpr, a.n);
 #pragma unroll
             for (int e = 0; e < R::EPV; e++) {
                 const float d = v[k * R::EPV + e] - mean;
@@ -220,7 +235,7 @@ __global__ void __launch_bounds__(kResidentMaxThreads, 2) layernorm_fwd_resident
 #pragma unroll
         for (int k = 0; k < VPT; k++) {
             const int idx = R::at(k, c.t, a.tpr);
-            if (idx < a.n) {
+            if (EXACT || idx < a.n) {
                 float gam[R::EPV], bet[R::EPV];
                 R::A::load_cached(gamma + idx, gam);
                 if (beta) R::A::load_cached(beta + idx, bet);
@@ -229,12 +244,18 @@ __global__ void __launch_bounds__(kResidentMaxThreads, 2) layernorm_fwd_resident
                     v[k * R::EPV + e] = fmaf(v[k * R::EPV + e] * rstd, gam[e], beta ? bet[e] : 0.0f);
             }
         }
-        R::store(v, y + r * a.ld, a.n, c.t, a.tpr, live);
+        R::template store<EXACT>(v, y + r * a.ld, a.n, c.t, a.tpr, live);
     }
 }
 
 template <typename T, bool VEC, int VPT>
-__global__ void __launch_bounds__(kResidentMaxThreads) layernorm_bwd_resident(RowArgs a) {
+__global__ void __launch_bounds__(kResidentMaxThreads, 2) layernorm_fwd_resident(RowArgs a) {
+    if (a.exact) layernorm_fwd_resident_body<T, VEC, VPT, true>(a);
+    else layernorm_fwd_resident_body<T, VEC, VPT, false>(a);
+}
+
+template <typename T, bool VEC, int VPT, bool EXACT>
+__device__ __forceinline__ void layernorm_bwd_resident_body(const RowArgs &a) {
     using R = Row<T, VEC, VPT>;
     __shared__ float red[2 * 32 * kRedWidth];
     RowCtx c = make_row_ctx(a.tpr, red);
@@ -249,10 +270,10 @@ __global__ void __launch_bounds__(kResidentMaxThreads) layernorm_bwd_resident(Ro
     const long long groups = (a.rows + a.rpc - 1) / a.rpc;
     for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
         const long long r = g * a.rpc + c.slot;
-        const bool live = r < a.rows;
+        const bool live = EXACT || r < a.rows;
         float v[R::E], d[R::E];
-        R::load(v, x + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
-        R::load(d, dy + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
+        R::template load<EXACT>(v, x + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
+        R::template load<EXACT>(d, dy + r * a.ld, a.n, c.t, a.tpr, 0.0f, live);
         float mean, rstd;
         if (a.cstat0 && a.cstat1) {
             mean = live ? static_cast<const float *>(a.cstat0)[r] : 0.0f;
@@ -265,7 +286,7 @@ __global__ void __launch_bounds__(kResidentMaxThreads) layernorm_bwd_resident(Ro
             float q = 0.0f;
 #pragma unroll
             for (int k = 0; k < VPT; k++) {
-                const bool in = R::inside(k, c.t, a.tpr, a.n);
+                const bool in = EXACT || R::inside(k, c.t, a.tpr, a.n);
 #pragma unroll
                 for (int e = 0; e < R::EPV; e++) {
                     const float t = v[k * R::EPV + e] - mean;
@@ -289,13 +310,19 @@ __global__ void __launch_bounds__(kResidentMaxThreads) layernorm_bwd_resident(Ro
         const float c1 = s2[0] / fn, c2 = s2[1] / fn;
 #pragma unroll
         for (int e = 0; e < R::E; e++) d[e] = rstd * ((__fmul_rn(d[e], gam[e]) - c1) - v[e] * c2);
-        R::store(d, dx + r * a.ld, a.n, c.t, a.tpr, live);
+        R::template store<EXACT>(d, dx + r * a.ld, a.n, c.t, a.tpr, live);
     }
     if (a.part0) {
         const long long p = static_cast<long long>(blockIdx.x) * a.rpc + c.slot;
         R::store_f32(dg, a.part0 + p * a.n, a.n, c.t, a.tpr);
         R::store_f32(db, a.part1 + p * a.n, a.n, c.t, a.tpr);
     }
+}
+
+template <typename T, bool VEC, int VPT>
+__global__ void __launch_bounds__(kResidentMaxThreads) layernorm_bwd_resident(RowArgs a) {
+    if (a.exact) layernorm_bwd_resident_body<T, VEC, VPT, true>(a);
+    else layernorm_bwd_resident_body<T, VEC, VPT, false>(a);
 }
 
 // Column sums of the partial dgamma / dbeta rows: 32 columns x 8 lanes per
@@ -536,6 +563,7 @@ struct Schedule {
     int threads;
     int splits;
     long long blocks; // grid (resident: an upper bound before occupancy)
+    bool exact;       // the rows fill every vector slot of every row slot of every block
 };
 
 inline int round_vpt(int64_t v) { return v <= 1 ? 1 : v <= 2 ? 2 : v <= 4 ? 4 : 8; }
@@ -558,6 +586,7 @@ Schedule plan_rows(RowOp op, int64_t n, int64_t rows, int64_t ld, int dtype, boo
         s.rpc = s.threads / tpr;
         s.splits = 1;
         s.blocks = ceil_div(rows, s.rpc);
+        s.exact = s.vec && nvec == static_cast<int64_t>(s.tpr) * s.vpt && rows % s.rpc == 0;
     } else {
         s.split = true;
         s.vpt = s.vec ? 32 / epv : 8;  // split chunks hold 32 elements per thread (8 when scalar)
@@ -748,7 +777,7 @@ extern "C" int tb200_softmax_fwd(const void *x, void *y, void *lse, int64_t n, i
     const Schedule s = plan_rows(OP_SOFTMAX_FWD, n, rows, ld, dtype, all_aligned(16, {x, y}));
     RowArgs a{};
     a.in0 = x; a.out0 = y; a.stat0 = lse; a.n = static_cast<int>(n); a.rows = rows; a.ld = ld;
-    a.tpr = s.tpr; a.rpc = s.rpc; a.splits = s.splits; a.stat_bf16 = stat_dtype == TB200_BF16;
+    a.tpr = s.tpr; a.rpc = s.rpc; a.splits = s.splits; a.stat_bf16 = stat_dtype == TB200_BF16; a.exact = s.exact;
     if (!s.split) return launch_resident(pick<SoftmaxFwdResident>(dtype, s), s, dev, a, stream);
     if (!workspace_ok(workspace, workspace_bytes, split_state_bytes(s, rows))) return TB200_ERR_WORKSPACE;
     a.part0 = static_cast<float *>(workspace);
@@ -772,7 +801,7 @@ extern "C" int tb200_softmax_bwd(const void *y_or_x, const void *lse, const void
     const Schedule s = plan_rows(OP_SOFTMAX_BWD, n, rows, ld, dtype, all_aligned(16, {y_or_x, dy, dx}));
     RowArgs a{};
     a.in0 = y_or_x; a.in1 = dy; a.out0 = dx; a.cstat0 = lse; a.n = static_cast<int>(n); a.rows = rows; a.ld = ld;
-    a.tpr = s.tpr; a.rpc = s.rpc; a.splits = s.splits; a.stat_bf16 = stat_dtype == TB200_BF16;
+    a.tpr = s.tpr; a.rpc = s.rpc; a.splits = s.splits; a.stat_bf16 = stat_dtype == TB200_BF16; a.exact = s.exact;
     if (!s.split) return launch_resident(pick<SoftmaxBwdResident>(dtype, s), s, dev, a, stream);
     if (!workspace_ok(workspace, workspace_bytes, split_state_bytes(s, rows))) return TB200_ERR_WORKSPACE;
     a.part0 = static_cast<float *>(workspace);
@@ -795,6 +824,7 @@ extern "C" int tb200_layernorm_fwd(const void *x, const void *gamma, const void 
     RowArgs a{};
     a.in0 = x; a.gamma = gamma; a.beta = beta; a.out0 = y; a.stat0 = mean; a.stat1 = rstd; a.eps = eps;
     a.n = static_cast<int>(n); a.rows = rows; a.ld = ld; a.tpr = s.tpr; a.rpc = s.rpc; a.splits = s.splits;
+    a.exact = s.exact;
     if (!s.split) return launch_resident(pick<LayernormFwdResident>(dtype, s), s, dev, a, stream);
     if (!workspace_ok(workspace, workspace_bytes, split_state_bytes(s, rows))) return TB200_ERR_WORKSPACE;
     a.part0 = static_cast<float *>(workspace);
@@ -825,6 +855,7 @@ extern "C" int tb200_layernorm_bwd(const void *x, const void *gamma, const void 
     RowArgs a{};
     a.in0 = x; a.in1 = dy; a.gamma = gamma; a.out0 = dx; a.cstat0 = mean; a.cstat1 = rstd; a.eps = eps;
     a.n = static_cast<int>(n); a.rows = rows; a.ld = ld; a.tpr = s.tpr; a.rpc = s.rpc; a.splits = 1;
+    a.exact = s.exact;
     const RowKernel kernel = pick<LayernormBwdResident>(dtype, s);
     long long grid = 0;
     if ((st = resident_grid(kernel, s, dev, &grid))) return st;
@@ -932,6 +963,7 @@ extern "C" int tb200_layernorm_bwd_noalloc(const void *x, const void *gamma, con
     RowArgs a{};
     a.in0 = x; a.in1 = dy; a.gamma = gamma; a.out0 = dx; a.cstat0 = mean; a.cstat1 = rstd; a.eps = eps;
     a.n = static_cast<int>(n); a.rows = rows; a.ld = ld; a.tpr = s.tpr; a.rpc = s.rpc; a.splits = 1;
+    a.exact = s.exact;
     const bool sums = dgamma || dbeta;
     const size_t part_len = static_cast<size_t>(grid) * s.rpc * static_cast<size_t>(n);
     if (sums) {

@@ -31,6 +31,35 @@ ACTIVATIONS = {"gelu_tanh": (lib.EPI_BIAS_GELU, lib.EPI_MUL_GELU_GRAD, "z"),
                "tanh": (lib.EPI_BIAS_TANH, lib.EPI_MUL_TANH_GRAD, "a")}
 
 
+def shard_rows(total, rank, world):
+    """[first, last) rows of a batch of `total` that replica `rank` of `world` trains on: equal
+    contiguous shards (the batch must divide evenly, so every replica runs the same kernels)."""
+    if total % world != 0:
+        raise ValueError(f"a batch of {total} does not split over {world} replicas")
+    per = total // world
+    return rank * per, (rank + 1) * per
+
+
+def sum_over_replicas(torch, buckets, group=None, stream=None):
+    """Sums each gradient bucket over the replicas, last layer first (the order the backward produces
+    them), on `stream` when given.  Returns the events that mark each bucket's sum as landed
+    (None without a stream).  The collective is torch.distributed's all-reduce: NCCL over NVLink on
+    GPUs, and any other backend (gloo on CPU) for the host-side tests."""
+    dist = torch.distributed
+    marks = []
+    for b in reversed(buckets):
+        if stream is None:
+            dist.all_reduce(b, group=group)
+            marks.append(None)
+        else:
+            with torch.cuda.stream(stream):
+                dist.all_reduce(b, group=group)
+                done = torch.cuda.Event()
+                done.record(stream)
+            marks.append(done)
+    return list(reversed(marks))
+
+
 def glorot_uniform(torch, fan_in, fan_out, generator, device="cuda"):
     """W (out, in) ~ U(+-sqrt(6 / (in + out))), stored [in][out] BFloat16."""
     limit = (6.0 / (fan_in + fan_out)) ** 0.5
