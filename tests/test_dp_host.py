@@ -34,7 +34,7 @@ WORKER = textwrap.dedent("""
         pass
     dist.barrier()
     dist.destroy_process_group()
-    sys.stdout.write("rank {} ok\n".format(rank))
+    os.write(1, ("rank " + str(rank) + " ok" + chr(10)).encode())
 """)
 
 
