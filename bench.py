@@ -396,6 +396,65 @@ def run_also(torch, dist, pkg, world, rank):
     return out
 
 
+def run_profile_case(args):
+    """One small case of a kernel family and nothing else, for ncu captures (not a benchmark):
+    few launches before the captured ones, a few GB on the device at most."""
+    import torch
+    import __graft_entry__ as entry
+    torch.cuda.set_device(0)
+    pkg = entry.load_package()
+    L = pkg.lib
+    L.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    case = args.profile_case
+    if case == "gemm":
+        M, N, K = 8192, 4096, 4096
+        A = torch.randn(M, K, device="cuda").bfloat16()
+        B = torch.randn(K, N, device="cuda").bfloat16()
+        C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        bias = torch.zeros(N, device="cuda", dtype=torch.bfloat16)
+        Z = torch.empty_like(C)
+        for _ in range(3):
+            L.gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR,
+                   epilogue=L.EPI_BIAS_GELU, bias=bias.data_ptr(), aux_out=Z.data_ptr(), stream=stream)
+        # the backward's shapes: dX (both K-major) and dW (both MN-major)
+        L.gemm(C.data_ptr(), B.data_ptr(), A.data_ptr(), M, K, N, a_layout=L.K_MAJOR, b_layout=L.K_MAJOR,
+               epilogue=L.EPI_MUL_GELU_GRAD, aux=Z.data_ptr(), stream=stream)
+        L.gemm(A.data_ptr(), C.data_ptr(), B.data_ptr(), K, N, M, a_layout=L.MN_MAJOR, b_layout=L.MN_MAJOR,
+               stream=stream)
+    elif case == "attention":
+        Bq, Hq, Sq, Dq = 1, 32, 4096, 128
+        q, k, v, g = (torch.randn(Bq, Sq, Hq, Dq, device="cuda").bfloat16() for _ in range(4))
+        o, lse = torch.empty_like(q), torch.empty(Bq, Sq, Hq, device="cuda")
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        desc = L.attn_desc(Bq, Hq, Sq, Sq, Dq, True)
+        need = L.attention_bwd_workspace_bytes(desc)
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        for _ in range(2):
+            L.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), stream)
+            L.attention_bwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), g.data_ptr(),
+                            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), need, stream)
+    elif case == "deltanet":
+        Hn, T = 16, 8192
+        qd = torch.nn.functional.normalize(torch.randn(Hn, T, 128, device="cuda"), dim=-1).bfloat16()
+        kd = torch.nn.functional.normalize(torch.randn(Hn, T, 128, device="cuda"), dim=-1).bfloat16()
+        vd = torch.randn(Hn, T, 128, device="cuda").bfloat16()
+        ad = -torch.nn.functional.softplus(torch.randn(Hn, T, device="cuda"))
+        bd = torch.sigmoid(torch.randn(Hn, T, device="cuda"))
+        od = torch.empty(Hn, 128, T, device="cuda", dtype=torch.bfloat16)
+        dd = L.deltanet_desc(Hn, T)
+        need = L.deltanet_workspace_bytes(dd)
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        for _ in range(2):
+            L.deltanet_fwd(dd, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ad.data_ptr(), bd.data_ptr(), od.data_ptr(),
+                           ws.data_ptr(), need, stream)
+    else:
+        raise SystemExit(f"unknown profile case {case}")
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": case, "device_error": L.device_error() + L.attention_device_error() +
+                      L.attention_bwd_device_error()}))
+
+
 def load_traffic(kernel):
     """DRAM bytes per launch of `kernel` from the committed ncu summary, if there is one."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
@@ -536,8 +595,12 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the side measurements (MLP step, GEMM)")
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "attention", "deltanet"],
+                    help="run one small case of a kernel family only (for ncu captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

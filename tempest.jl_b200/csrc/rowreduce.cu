@@ -295,21 +295,55 @@ __device__ __forceinline__ void layernorm_bwd_resident_body(const RowArgs &a) {
             }
             rstd = 1.0f / sqrtf(row_allreduce1(q, c, SumOp()) / fn + a.eps);
         }
-        // xh in v; padded slots have gamma = 0 and dy = 0, so they add nothing
+        // xh in v; padded slots have gamma = 0 and dy = 0, so they add nothing.  The arithmetic runs on
+        // pairs of Float32 (fma.rn.f32x2 and friends): the kernel is bound by instruction issue for
+        // BFloat16 rows, and the packed forms halve its floating-point instructions.
+        static_assert(R::E % 2 == 0 || R::E == 1, "pairs");
         float s2[2] = {0.0f, 0.0f};
+        if constexpr (R::E % 2 == 0) {
+            const float2 rs2 = make_float2(rstd, rstd);
+            const float2 off2 = make_float2(-mean * rstd, -mean * rstd);
+            float2 sa = make_float2(0.0f, 0.0f), sb = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int e = 0; e < R::E; e++) {
-            v[e] = (v[e] - mean) * rstd;
-            const float gh = d[e] * gam[e];
-            s2[0] += gh;
-            s2[1] = fmaf(gh, v[e], s2[1]);
-            dg[e] = fmaf(d[e], v[e], dg[e]);
-            db[e] += d[e];
+            for (int e = 0; e < R::E; e += 2) {
+                const float2 xh = __ffma2_rn(make_float2(v[e], v[e + 1]), rs2, off2);
+                const float2 dy2 = make_float2(d[e], d[e + 1]);
+                const float2 gh = __fmul2_rn(dy2, make_float2(gam[e], gam[e + 1]));
+                sa = __fadd2_rn(sa, gh);
+                sb = __ffma2_rn(gh, xh, sb);
+                const float2 g2 = __ffma2_rn(dy2, xh, make_float2(dg[e], dg[e + 1]));
+                const float2 b2 = __fadd2_rn(make_float2(db[e], db[e + 1]), dy2);
+                dg[e] = g2.x; dg[e + 1] = g2.y;
+                db[e] = b2.x; db[e + 1] = b2.y;
+                v[e] = xh.x; v[e + 1] = xh.y;
+                d[e] = gh.x; d[e + 1] = gh.y;      // dy is not needed again: keep gh in its place
+            }
+            s2[0] = sa.x + sa.y;
+            s2[1] = sb.x + sb.y;
+        } else {
+            const float xh = (v[0] - mean) * rstd;
+            const float gh = d[0] * gam[0];
+            s2[0] = gh;
+            s2[1] = gh * xh;
+            dg[0] = fmaf(d[0], xh, dg[0]);
+            db[0] += d[0];
+            v[0] = xh;
+            d[0] = gh;
         }
         row_allreduce<2>(s2, c, SumOp());
         const float c1 = s2[0] / fn, c2 = s2[1] / fn;
+        if constexpr (R::E % 2 == 0) {
+            const float2 nc1 = make_float2(-c1, -c1), nc2 = make_float2(-c2, -c2), rs2 = make_float2(rstd, rstd);
 #pragma unroll
-        for (int e = 0; e < R::E; e++) d[e] = rstd * ((__fmul_rn(d[e], gam[e]) - c1) - v[e] * c2);
+            for (int e = 0; e < R::E; e += 2) {
+                // (gh - c1) first: exact when they are equal (a row of one element), then - xh c2, then * rstd
+                const float2 t = __fadd2_rn(make_float2(d[e], d[e + 1]), nc1);
+                const float2 u = __fmul2_rn(__ffma2_rn(make_float2(v[e], v[e + 1]), nc2, t), rs2);
+                d[e] = u.x; d[e + 1] = u.y;
+            }
+        } else {
+            d[0] = rstd * ((d[0] - c1) - v[0] * c2);
+        }
         R::template store<EXACT>(d, dx + r * a.ld, a.n, c.t, a.tpr, live);
     }
     if (a.part0) {
