@@ -40,7 +40,7 @@ constexpr int kInnerSlab = kInner * 128;    // [64 rows][64 features]: 8 KB
 constexpr int kInnerBytes = 2 * kInnerSlab;
 constexpr int kDsBytes = kOuter * 128;      // [128 rows][64 positions] BFloat16: 16 KB
 constexpr int kStages = 3;
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;   // loader, MMA issuer, two groups of four row warps taking alternate steps
 
 __device__ int g_attn_bwd_error = 0;
 
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
 
     if (threadIdx.x == 0) {
         failed_smem = 0;
-        mbar_init(&outer_full, 1); mbar_init(&outer_empty, 1); mbar_init(&acc_done, 1); mbar_init(&acc_free, 4);
+        mbar_init(&outer_full, 1); mbar_init(&outer_empty, 1); mbar_init(&acc_done, 1); mbar_init(&acc_free, 8);
         for (int s = 0; s < kStages; s++) { mbar_init(&inner_full[s], 1); mbar_init(&inner_empty[s], 1); }
         for (int s = 0; s < 2; s++) {
             mbar_init(&t_full[s], 1); mbar_init(&t_empty[s], 4);
@@ -267,8 +267,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
             }
         }
     } else {
-        // ---- one thread per row of the item
+        // ---- one thread per row of the item; the two groups of four warps take alternate steps (the
+        // score and P / dS buffers of a step are those of its parity), so one group's chain of
+        // tensor-memory load -> exponentials -> shared-memory stores overlaps the other's
         const int q4 = warp & 3;
+        const int group = (warp - 2) >> 2;
         const int row = q4 * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
         uint32_t step_count = 0, item_count = 0;
@@ -282,9 +285,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 row_delta = p.delta[i];
             }
             bool ok = true;
-            for (int t = 0; t < steps.count; t++, step_count++) {
-                const int tb = step_count & 1;
-                const uint32_t tph = (step_count >> 1) & 1;
+            const uint32_t step_base = step_count;
+            step_count += steps.count;
+            for (int t = 0; t < steps.count; t++) {
+                const uint32_t sc = step_base + t;
+                const int tb = sc & 1;
+                if (tb != group) continue;
+                const uint32_t tph = (sc >> 1) & 1;
                 if (!bwd_wait(&t_full[tb], tph, failed, 8)) { ok = false; break; }
                 tcgen05_fence_after();
                 int hi, pos0;
@@ -374,8 +381,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 if (!bwd_wait(&acc_done, item_count & 1, failed, 10)) break;
             }
             tcgen05_fence_after();
+            // group 0 writes the first accumulator (dV), group 1 the second (dK, or dQ)
 #pragma unroll 1
-            for (int which = DKDV ? 0 : 1; which < 2; which++) {
+            for (int which = group; which <= group && (DKDV || which == 1); which++) {
                 const float mul = which == 0 ? 1.0f : p.scale;
                 uint8_t *stage = s_ds + which * 2 * kDsBytes;   // 32 KB: two 64-feature slabs of 128 rows
                 uint32_t r[kD];
@@ -404,12 +412,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
             __syncwarp();
             if (lane == 0) {
                 const int r0 = steps.tile * kOuter + q4 * 32;
-                if (DKDV) {
+                if (DKDV && group == 0) {
                     tma_store_4d(&p.out1, s_ds + q4 * 32 * 128, 0, steps.head_outer, r0, steps.b);
                     tma_store_4d(&p.out1, s_ds + kOuterSlab + q4 * 32 * 128, 64, steps.head_outer, r0, steps.b);
                 }
-                tma_store_4d(&p.out2, s_ds + 2 * kDsBytes + q4 * 32 * 128, 0, steps.head_outer, r0, steps.b);
-                tma_store_4d(&p.out2, s_ds + 2 * kDsBytes + kOuterSlab + q4 * 32 * 128, 64, steps.head_outer, r0, steps.b);
+                if (group == 1) {
+                    tma_store_4d(&p.out2, s_ds + 2 * kDsBytes + q4 * 32 * 128, 0, steps.head_outer, r0, steps.b);
+                    tma_store_4d(&p.out2, s_ds + 2 * kDsBytes + kOuterSlab + q4 * 32 * 128, 64, steps.head_outer, r0, steps.b);
+                }
                 bulk_commit_group();
                 bulk_wait_group_read<0>();
                 if (steps.count > 0) mbar_arrive(&acc_free);
