@@ -135,6 +135,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
     __shared__ __align__(8) uint64_t t_full[2], t_empty[2], ds_full[2], ds_empty[2];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int failed_smem;
+    // dK/dV: the step's 64 queries' lse*log2(e) [0, 64) and delta [64, 128), per group, double-buffered
+    __shared__ __align__(16) float col_stats[2][2][2 * kInner];
     volatile int *failed = &failed_smem;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -292,10 +294,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 const int tb = sc & 1;
                 if (tb != group) continue;
                 const uint32_t tph = (sc >> 1) & 1;
-                if (!bwd_wait(&t_full[tb], tph, failed, 8)) { ok = false; break; }
-                tcgen05_fence_after();
                 int hi, pos0;
                 steps.at(t, hi, pos0);
+                float *stats = col_stats[group][tph];
+                if (DKDV) {
+                    // fetched before the wait below so that the global-memory latency hides behind it
+                    const int i = row & (kInner - 1);
+                    const int qpos = pos0 + i;
+                    const long long base = (static_cast<long long>(steps.b) * p.heads + hi) * p.queries;
+                    const float *src = row < kInner ? p.lse2 : p.delta;
+                    stats[row] = qpos < p.queries ? __ldg(src + base + qpos) : 0.0f;
+                }
+                if (!bwd_wait(&t_full[tb], tph, failed, 8)) { ok = false; break; }
+                tcgen05_fence_after();
+                if (DKDV) asm volatile("bar.sync %0, 128;" ::"r"(2 + group) : "memory");
                 uint32_t s[kInner], dp[kInner];
                 const uint32_t t1 = tmem_base + lane_base + tb * 128;
                 tmem_ld_32x32(t1, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
@@ -310,12 +322,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 if (!bwd_wait(&ds_empty[tb], tph ^ 1, failed, 9)) { ok = false; break; }
                 uint8_t *prow = s_ds + tb * 2 * kDsBytes + row * 128;
                 uint8_t *drow = prow + kDsBytes;
-                const float *lse_col = nullptr, *delta_col = nullptr;
-                if (DKDV) {
-                    const long long base = (static_cast<long long>(steps.b) * p.heads + hi) * p.queries;
-                    lse_col = p.lse2 + base;
-                    delta_col = p.delta + base;
-                }
                 const bool edge = DKDV ? (pos0 + kInner > p.queries || outer_pos >= p.keys ||
                                           (p.causal && pos0 < steps.tile * kOuter + kOuter))
                                        : (pos0 + kInner > p.keys || outer_pos >= p.queries ||
@@ -325,24 +331,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                     float pv[8], dv[8];
                     float l8[8], d8[8];
                     if (DKDV) {
-                        const int q0 = pos0 + 8 * g;
-                        if (q0 + 8 <= p.queries && (p.queries & 3) == 0) {
-                            const float4 a0 = __ldg(reinterpret_cast<const float4 *>(lse_col + q0));
-                            const float4 a1 = __ldg(reinterpret_cast<const float4 *>(lse_col + q0 + 4));
-                            const float4 b0 = __ldg(reinterpret_cast<const float4 *>(delta_col + q0));
-                            const float4 b1 = __ldg(reinterpret_cast<const float4 *>(delta_col + q0 + 4));
-                            l8[0] = a0.x; l8[1] = a0.y; l8[2] = a0.z; l8[3] = a0.w;
-                            l8[4] = a1.x; l8[5] = a1.y; l8[6] = a1.z; l8[7] = a1.w;
-                            d8[0] = b0.x; d8[1] = b0.y; d8[2] = b0.z; d8[3] = b0.w;
-                            d8[4] = b1.x; d8[5] = b1.y; d8[6] = b1.z; d8[7] = b1.w;
-                        } else {
-#pragma unroll
-                            for (int u = 0; u < 8; u++) {
-                                const bool in = q0 + u < p.queries;
-                                l8[u] = in ? lse_col[q0 + u] : 0.0f;
-                                d8[u] = in ? delta_col[q0 + u] : 0.0f;
-                            }
-                        }
+                        const float4 a0 = *reinterpret_cast<const float4 *>(stats + 8 * g);
+                        const float4 a1 = *reinterpret_cast<const float4 *>(stats + 8 * g + 4);
+                        const float4 b0 = *reinterpret_cast<const float4 *>(stats + kInner + 8 * g);
+                        const float4 b1 = *reinterpret_cast<const float4 *>(stats + kInner + 8 * g + 4);
+                        l8[0] = a0.x; l8[1] = a0.y; l8[2] = a0.z; l8[3] = a0.w;
+                        l8[4] = a1.x; l8[5] = a1.y; l8[6] = a1.z; l8[7] = a1.w;
+                        d8[0] = b0.x; d8[1] = b0.y; d8[2] = b0.z; d8[3] = b0.w;
+                        d8[4] = b1.x; d8[5] = b1.y; d8[6] = b1.z; d8[7] = b1.w;
                     }
 #pragma unroll
                     for (int u = 0; u < 8; u++) {
@@ -505,17 +501,25 @@ int bwd_tmap(CUtensorMap *map, const void *base, int d, int heads, int positions
 
 template <bool DKDV>
 int launch_bwd(AttnBwdArgs &p, const DeviceInfo &dev, cudaStream_t stream) {
-    const size_t smem = 2 * kOuterBytes + kStages * 2 * kInnerBytes + 2 * 2 * kDsBytes + 1024;
+    // the tiles (224 KB, 1024-byte aligned) sit behind the kernel's static shared memory: take all the dynamic
+    // shared memory the SM has left
+    const size_t tiles = 2 * kOuterBytes + kStages * 2 * kInnerBytes + 2 * 2 * kDsBytes;
     static std::mutex lock;
-    static bool configured[64] = {};
+    static size_t dynamic_bytes[64] = {};
     {
         std::lock_guard<std::mutex> hold(lock);
-        if (!configured[dev.device]) {
+        if (!dynamic_bytes[dev.device]) {
+            cudaFuncAttributes attr;
+            TB200_CUDA(cudaFuncGetAttributes(&attr, attention_bwd_kernel<DKDV>));
+            const size_t first = (attr.sharedSizeBytes + 1023) / 1024 * 1024;
+            if (first + tiles > dev.smem_optin) return TB200_ERR_UNSUPPORTED;
+            const size_t room = dev.smem_optin - attr.sharedSizeBytes;
             TB200_CUDA(cudaFuncSetAttribute(attention_bwd_kernel<DKDV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(smem)));
-            configured[dev.device] = true;
+                                            static_cast<int>(room)));
+            dynamic_bytes[dev.device] = room;
         }
     }
+    const size_t smem = dynamic_bytes[dev.device];
     const unsigned grid = static_cast<unsigned>(p.items < dev.sms ? p.items : dev.sms);
     attention_bwd_kernel<DKDV><<<grid, kBwdThreads, smem, stream>>>(p);
     TB200_CUDA(cudaGetLastError());
