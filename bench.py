@@ -74,14 +74,14 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+                 "-lms", "20"], stdout=self.out, stderr=subprocess.DEVNULL)
         except OSError:
             pass
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -205,6 +205,10 @@ def run_gpu(args):
     barrier()
 
     sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
+    if sampler:
+        time.sleep(0.3)   # nvidia-smi takes a moment to start sampling
+        for _ in range(3):
+            wl.step()     # keep the clocks up while it does
     events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nk)]
               for _ in range(args.steps)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -309,7 +313,11 @@ def run_also(torch, dist, pkg, world, rank):
     step = pkg.mlp.MLPStep(torch, sizes, per, 1e-3, world=world, global_batch=gb, seed=1)
     x = torch.randn(per, sizes[0], device="cuda").bfloat16()
     y = torch.randn(per, sizes[-1], device="cuda").bfloat16()
-    ms = timed(lambda: step.step(x, y), 20, 5)
+    step.step(x, y)                      # every launch once, outside any capture
+    # one GPU: the whole step replayed as one CUDA graph, as Tempest replays a compiled call; with
+    # replicas the step is launched eagerly (its all-reduces run on a side stream)
+    run = step.capture(x, y) if world == 1 else (lambda: step.step(x, y))
+    ms = timed(run, 20, 5)
     flops = 2 * gb * (1024 * 4096 + 2 * 4096 * 4096 + 4096 * 1024) * 3 - 2 * gb * 1024 * 4096
     out = {"mlp_train": {"steps_per_s": round(1000.0 / ms, 1), "ms_per_step": round(ms, 4), "n_gpus": world,
                          "global_batch": gb, "scaling": "strong", "TFLOP/s": round(flops / ms / 1e9, 1),
@@ -587,7 +595,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS, help="rows per GPU (smaller only for profiling captures)")

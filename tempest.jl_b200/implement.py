@@ -134,6 +134,111 @@ _STREAMS = {  # row-sized arrays read + written: the algorithmic traffic
 }
 
 
+# Products: y = act.(w * x .+ b) with a Julia w::(m, k) (memory [k][m]) and x::(k, n) (memory [n][k]).
+LINEAR_SPELLINGS = {
+    "linear": ("(w, x) -> w * x", lib.EPI_NONE),
+    "linear_bias": ("(w, x, b) -> w * x .+ b", lib.EPI_BIAS),
+    "linear_bias_gelu": ("(w, x, b) -> gelu.(w * x .+ b)", lib.EPI_BIAS_GELU),
+    "linear_bias_tanh": ("(w, x, b) -> tanh.(w * x .+ b)", lib.EPI_BIAS_TANH),
+}
+LINEAR_TEMPLATES = tuple(
+    Template(name, spelling, {"w": ("m", "k"), "x": ("k", "n"), **({"b": ("m",)} if "bias" in name else {})}, ("y",))
+    for name, (spelling, _) in LINEAR_SPELLINGS.items())
+
+# Attention as the reference spells it (test/fixtures/operations.jl:21-76, ext/cuDNNExt.jl:38-57):
+# q (d, h, m, b), k and v (d, hk, n, b); with the log-sum-exp (1, h, m, b) beside the output or not.
+ATTENTION_TEMPLATES = tuple(
+    Template(f"attention{'_causal' if causal else ''}{'_lse' if stats else ''}",
+             f"(q, k, v) -> Ops.attention_forward(q, k, v; causal = {str(causal).lower()}, scale)" +
+             (".o" if not stats else ""),
+             {"q": ("d", "h", "m", "b"), "k": ("d", "hk", "n", "b"), "v": ("d", "hk", "n", "b")},
+             ("o", "lse") if stats else ("o",))
+    for stats in (False, True) for causal in (False, True))
+ATTENTION_PULLBACKS = tuple(
+    Template(f"attention{'_causal' if causal else ''}_pullback",
+             "(q, k, v, o, lse, g) -> the tape's derivative of attention by q, k and v",
+             {"q": ("d", "h", "m", "b"), "k": ("d", "hk", "n", "b"), "v": ("d", "hk", "n", "b"),
+              "o": ("d", "h", "m", "b"), "lse": ("one", "h", "m", "b"), "g": ("d", "h", "m", "b")},
+             ("dq", "dk", "dv"))
+    for causal in (False, True))
+
+
+def dense_matrix(buffer, eltype, rows, cols, value=0, offset=0):
+    """A Julia (rows, cols) matrix, dense column-major."""
+    return Strided(eltype, offset, (rows, cols), (1, rows), buffer, value)
+
+
+def dense_heads(buffer, eltype, d, heads, positions, batch, value=0):
+    """A Julia (d, heads, positions, batch) array, dense."""
+    return Strided(eltype, 0, (d, heads, positions, batch), (1, d, d * heads, d * heads * positions), buffer, value)
+
+
+def _dense(s: "Strided") -> bool:
+    expect = 1
+    for size, stride in zip(s.size, s.strides):
+        if size > 1 and stride != expect:
+            return False
+        expect *= size
+    return True
+
+
+class LinearLaunch:
+    """One product with its fused epilogue on fixed operands (tb200_gemm)."""
+
+    def __init__(self, binding: Binding):
+        self.binding = binding
+        self.epilogue = LINEAR_SPELLINGS[binding.template][1]
+
+    def repoints(self) -> bool:
+        return True
+
+    def repoint(self, value: int, buffer) -> "LinearLaunch":
+        for s in self.binding.arrays.values():
+            if s.value == value:
+                s.buffer = buffer
+        return self
+
+    def __call__(self):
+        a, e = self.binding.arrays, self.binding.extents
+        w, x, y = a["w"], a["x"], a["y"]
+        dtype = ELTYPES[w.eltype][0]
+        # memory: x [n][k] is the K-major A, w [k][m] the MN-major B, y [n][m] the result
+        lib.gemm(x.pointer(), w.pointer(), y.pointer(), e["n"], e["m"], e["k"], lda=x.strides[1], ldb=w.strides[1],
+                 ldc=y.strides[1], a_layout=lib.K_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=dtype,
+                 epilogue=self.epilogue, bias=a["b"].pointer() if "b" in a else 0, stream=current_stream())
+
+
+class AttentionLaunch:
+    """Attention forward or its pullback on fixed operands."""
+
+    def __init__(self, binding: Binding, workspace=None, workspace_bytes=0):
+        self.binding = binding
+        e = binding.extents
+        self.desc = lib.attn_desc(e["b"], e["h"], e["m"], e["n"], e["d"], "causal" in binding.template,
+                                  kv_heads=e["hk"])
+        self.workspace, self.workspace_bytes = workspace, workspace_bytes
+
+    def repoints(self) -> bool:
+        return True
+
+    def repoint(self, value: int, buffer) -> "AttentionLaunch":
+        for s in self.binding.arrays.values():
+            if s.value == value:
+                s.buffer = buffer
+        return self
+
+    def __call__(self):
+        a = self.binding.arrays
+        stream = current_stream()
+        if self.binding.template.endswith("_pullback"):
+            lib.attention_bwd(self.desc, a["q"].pointer(), a["k"].pointer(), a["v"].pointer(), a["o"].pointer(),
+                              a["lse"].pointer(), a["g"].pointer(), a["dq"].pointer(), a["dk"].pointer(),
+                              a["dv"].pointer(), self.workspace.data_ptr(), self.workspace_bytes, stream)
+        else:
+            lib.attention_fwd(self.desc, a["q"].pointer(), a["k"].pointer(), a["v"].pointer(), a["o"].pointer(),
+                              a["lse"].pointer() if "lse" in a else 0, stream)
+
+
 class Resources:
     """Per-executable scratch (Implement.jl:141): one workspace, grown to the
     largest request while building, used by one launch at a time."""
@@ -220,14 +325,32 @@ class B200Kernels:
         self.eps = eps
 
     def templates(self, target: Target):
-        # the row kernels fold each statistic in one pass, which a target that
-        # forbids the online rewrites does not permit (ext/cuDNNExt.jl:60-62)
-        return ROW_TEMPLATES if target.online else ()
+        # the row kernels and attention fold each statistic in one pass, which a target that
+        # forbids the online rewrites does not permit (ext/cuDNNExt.jl:60-62); products always apply
+        online = ROW_TEMPLATES + ATTENTION_TEMPLATES + ATTENTION_PULLBACKS if target.online else ()
+        return LINEAR_TEMPLATES + online
 
     def resources(self, target: Target) -> Resources:
         return Resources()
 
     def supports(self, target: Target, b: Binding) -> bool:
+        if b.template in LINEAR_SPELLINGS:
+            types = {s.eltype for s in b.arrays.values()}
+            if len(types) != 1 or types.pop() not in ELTYPES:
+                return False
+            # the contracted axis of x and the output axis of w and y must be contiguous
+            return all(s.strides[0] == 1 or s.size[0] == 1 for s in b.arrays.values())
+        if b.template.startswith("attention"):
+            e = b.extents
+            if e.get("d") != 128 or e.get("h", 0) % max(e.get("hk", 1), 1) != 0:
+                return False   # as cuDNNAttention declines what its engines do not take (ext/cuDNNExt.jl:90-109)
+            if "causal" in b.template and e.get("m") != e.get("n"):
+                return False
+            for name, s in b.arrays.items():
+                want = "Float32" if name == "lse" else "BFloat16"
+                if s.eltype != want or not _dense(s):
+                    return False
+            return True
         if b.template not in _ROWOP:
             return False
         n, rows = b.extents.get("n", 0), b.extents.get("rows", 0)
@@ -255,6 +378,19 @@ class B200Kernels:
         return True
 
     def estimate(self, target: Target, b: Binding):
+        if b.template in LINEAR_SPELLINGS:
+            e = b.extents
+            size = ELTYPES[b.arrays["w"].eltype][1]
+            moved = size * (e["m"] * e["k"] + e["k"] * e["n"] + e["m"] * e["n"])
+            return [Work(bytes=moved, flops=2.0 * e["m"] * e["n"] * e["k"])]
+        if b.template.startswith("attention"):
+            e = b.extents
+            flops = 4.0 * e["d"] * e["h"] * e["m"] * e["b"] * e["n"]     # both products (ext/cuDNNExt.jl:141-145)
+            flops = flops / 2 if "causal" in b.template else flops
+            moved = 2 * e["d"] * e["b"] * (2 * e["h"] * e["m"] + 2 * e["hk"] * e["n"])
+            if b.template.endswith("_pullback"):
+                return [Work(bytes=2 * moved, flops=2.5 * flops, launches=3)]
+            return [Work(bytes=moved, flops=flops)]
         first = next(iter(b.arrays.values()))
         size = ELTYPES[first.eltype][1]
         n, rows = b.extents["n"], b.extents["rows"]
@@ -268,6 +404,18 @@ class B200Kernels:
         for s in b.arrays.values():
             if s.buffer is None:
                 raise ValueError("build needs every array's buffer")
+        if b.template in LINEAR_SPELLINGS:
+            e = b.extents
+            return LinearLaunch(b), f"B200 {b.template}, {e['m']} x {e['n']} over {e['k']}, {b.arrays['w'].eltype}"
+        if b.template.startswith("attention"):
+            launch = AttentionLaunch(b)
+            if b.template.endswith("_pullback"):
+                need = lib.attention_bwd_workspace_bytes(launch.desc)
+                resources = resources if resources is not None else Resources()
+                launch.workspace, launch.workspace_bytes = resources.workspace(need), need
+            e = b.extents
+            return launch, (f"B200 {b.template}, {e['h']} heads over {e['hk']} of {e['d']} features, "
+                            f"{e['m']} queries by {e['n']} keys, batch {e['b']}")
         first = next(iter(b.arrays.values()))
         dtype = ELTYPES[first.eltype][0]
         n, rows = b.extents["n"], b.extents["rows"]

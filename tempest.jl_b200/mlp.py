@@ -184,3 +184,24 @@ class MLPStep:
             lib.axpy(self.b[i].data_ptr(), self.db[i].data_ptr(), -self.rate, n - nw, bf16, bf16, stream)
             self.launches += 2
         return self.loss
+
+    def capture(self, x, y):
+        """Records one single-GPU step into a CUDA graph, as Tempest captures a compiled call
+        (ext/CUDAExt.jl:565-572), and returns `replay()`: one graph launch per step instead of some
+        thirty kernel launches.  x and y are read in place at every replay; the loss lands in
+        `self.loss`.  Data-parallel steps are not captured: a capture that included the NCCL
+        all-reduces on their side stream did not complete on this pool, so replicas launch eagerly."""
+        if self.world != 1:
+            raise ValueError("capture() records single-GPU steps only")
+        torch = self.torch
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step(x, y)              # warm up on the capturing stream (NCCL connections, caches)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            self.step(x, y)
+        self._graph = graph
+        return graph.replay

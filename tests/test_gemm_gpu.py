@@ -266,3 +266,53 @@ def test_mlp_step_against_oracle(pkg, cuda, oracle):
                 got = oracle.from_bf16(host(torch, step.dw[i]))
                 rel = np.linalg.norm(got - dw_ref[i]) / np.linalg.norm(dw_ref[i])
                 assert rel < 5e-3, rel
+
+
+def test_products_and_attention_through_the_plugin_mirror(pkg, cuda, oracle):
+    """Binding -> supports -> build -> launch for a product template and an attention template, with the
+    arrays described as Tempest describes them (column-major `Strided` views)."""
+    torch, I = cuda, pkg.implement
+    lib, target = I.B200Kernels(), I.Target()
+    m, k, n = 96, 64, 40   # w (m, k), x (k, n): memory w [k][m], x [n][k], y [n][m]
+    w = oracle.to_bf16(0.2 * oracle.normal((k, m), 3))
+    x = oracle.to_bf16(oracle.normal((n, k), 4))
+    b = oracle.to_bf16(oracle.normal((m,), 5))
+    wd, xd, bd = dev(torch, w), dev(torch, x), dev(torch, b)
+    y = torch.empty(n, m, device="cuda", dtype=torch.bfloat16)
+    bind = I.Binding("linear_bias_gelu", {"m": m, "k": k, "n": n},
+                     {"w": I.dense_matrix(wd, "BFloat16", m, k, 1), "x": I.dense_matrix(xd, "BFloat16", k, n, 2),
+                      "b": I.dense_vector(bd, "BFloat16", m, 3), "y": I.dense_matrix(y, "BFloat16", m, n, 4)})
+    assert lib.supports(target, bind)
+    launch, description = lib.build(target, bind)
+    assert "linear_bias_gelu" in description
+    launch()
+    torch.cuda.synchronize()
+    want = oracle.gemm(x, w, bias=b, M=n, N=m, K=k, a_km=False, b_kn=True, epilogue=2, want_pre=True)[1]
+    want = np.vectorize(oracle.gelu_tanh)(want)
+    close_bf16(oracle, host(torch, y), want, k)
+    # attention, causal, with its log-sum-exp, then its pullback through the same mirror
+    B, S, H, D = 1, 200, 2, 128
+    q, kk, v, g = (oracle.to_bf16(oracle.normal((B, S, H, D), 10 + i)) for i in range(4))
+    qd, kd, vd, gd = (dev(torch, a) for a in (q, kk, v, g))
+    o, lse = torch.empty_like(qd), torch.empty(B, S, H, device="cuda")
+    e = {"d": D, "h": H, "hk": H, "m": S, "n": S, "b": B, "one": 1}
+    heads = lambda t, val: I.dense_heads(t, "BFloat16", D, H, S, B, val)  # noqa: E731
+    fwd = I.Binding("attention_causal_lse", e, {"q": heads(qd, 1), "k": heads(kd, 2), "v": heads(vd, 3), "o": heads(o, 4),
+                                                "lse": I.Strided("Float32", 0, (1, H, S, B), (1, 1, H, H * S), lse, 5)})
+    assert lib.supports(target, fwd)
+    launch, _ = lib.build(target, fwd)
+    launch()
+    dq, dk, dv = (torch.empty_like(qd) for _ in range(3))
+    bwd = I.Binding("attention_causal_pullback", e, dict(fwd.arrays, g=heads(gd, 6), dq=heads(dq, 7), dk=heads(dk, 8),
+                                                         dv=heads(dv, 9)))
+    assert lib.supports(target, bwd)
+    launch, _ = lib.build(target, bwd)
+    launch()
+    torch.cuda.synchronize()
+    assert pkg.lib.attention_device_error() == 0 and pkg.lib.attention_bwd_device_error() == 0
+    o64, lse64, dq64, dk64, dv64 = oracle.attention_f64(q, kk, v, True, dout=g)
+    assert np.abs(oracle.from_bf16(host(torch, o)) - o64).max() <= ATOL_BF16
+    assert np.abs(lse.cpu().numpy() - lse64).max() <= 1e-4
+    for got, want in ((dq, dq64), (dk, dk64), (dv, dv64)):
+        gotf = oracle.from_bf16(host(torch, got))
+        assert np.abs(gotf - want).max() <= ATOL_BF16 * max(1.0, np.abs(want).max())

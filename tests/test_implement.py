@@ -17,8 +17,9 @@ def test_templates_follow_the_target(I):
     lib = I.B200Kernels()
     names = [t.name for t in lib.templates(I.Target(online=True))]
     assert "softmax_columns" in names and "layernorm_pullback" in names
-    # a target that keeps the two passes is offered nothing (ext/cuDNNExt.jl:60-62)
-    assert lib.templates(I.Target(online=False)) == ()
+    # a target that keeps the two passes is offered no one-pass fold (ext/cuDNNExt.jl:60-62), only products
+    kept = [t.name for t in lib.templates(I.Target(online=False))]
+    assert kept and all(n.startswith("linear") for n in kept)
 
 
 def test_supports(I):
@@ -61,3 +62,28 @@ def test_strided_pointer_and_repoint(I):
     assert launch.repoints()
     launch.repoint(3, 65536)
     assert b.arrays["x"].pointer() == 65536 + 16 and b.arrays["y"].pointer() == 8192
+
+
+def test_product_and_attention_templates(I):
+    lib, t = I.B200Kernels(), I.Target()
+    names = [x.name for x in lib.templates(t)]
+    assert "linear_bias_gelu" in names and "attention_causal_lse" in names and "attention_causal_pullback" in names
+    # products do not depend on the online rewrites; attention does
+    off = [x.name for x in lib.templates(I.Target(online=False))]
+    assert "linear" in off and not any(n.startswith("attention") for n in off)
+    b = I.Binding("linear_bias_gelu", {"m": 4096, "k": 1024, "n": 8192},
+                  {"w": I.dense_matrix(None, "BFloat16", 4096, 1024, 1), "x": I.dense_matrix(None, "BFloat16", 1024, 8192, 2),
+                   "b": I.dense_vector(None, "BFloat16", 4096, 3), "y": I.dense_matrix(None, "BFloat16", 4096, 8192, 4)})
+    assert lib.supports(t, b)
+    (w,) = lib.estimate(t, b)
+    assert w.flops == 2.0 * 4096 * 8192 * 1024
+    e = {"d": 128, "h": 32, "hk": 32, "m": 4096, "n": 4096, "b": 8}
+    arrays = {n: I.dense_heads(None, "BFloat16", 128, 32, 4096, 8, i) for i, n in enumerate(("q", "k", "v", "o"))}
+    a = I.Binding("attention_causal", e, arrays)
+    assert lib.supports(t, a)
+    (w,) = lib.estimate(t, a)
+    assert abs(w.flops - 1.0995e12) / 1.0995e12 < 1e-3
+    assert not lib.supports(t, I.Binding("attention_causal", dict(e, d=64), arrays))
+    assert not lib.supports(t, I.Binding("attention_causal", dict(e, n=2048), arrays))
+    strided = dict(arrays, q=I.Strided("BFloat16", 0, (128, 32, 4096, 8), (1, 256, 8192, 1 << 25), None, 0))
+    assert not lib.supports(t, I.Binding("attention_causal", e, strided))
