@@ -262,6 +262,19 @@ int tb200_deltanet_fwd(const tb200_deltanet_desc *desc, const void *q, const voi
                        const float *a, const float *beta, void *o, void *workspace,
                        size_t workspace_bytes, void *stream);
 
+size_t tb200_deltanet_bwd_workspace_bytes(const tb200_deltanet_desc *desc);
+
+/* Pullback of the forward pass: given dout (the result's layout, [head][dv][t]
+ * BFloat16) writes dq, dk [head][t][dk] and dv [head][t][dv] in BFloat16 and da,
+ * dbeta [head][t] in Float32.  It runs the forward again inside (keeping the
+ * state at every chunk start), so it needs no saved tensors, and stands for the
+ * gradient program Tempest derives from the same source
+ * (examples/deltanet.jl:96-101, src/Compiler/Differentiate).  Same geometry
+ * limits as the forward. */
+int tb200_deltanet_bwd(const tb200_deltanet_desc *desc, const void *q, const void *k, const void *v,
+                       const float *a, const float *beta, const void *dout, void *dq, void *dk, void *dv,
+                       float *da, float *dbeta, void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- pointwise maps and folds over other axes -------------------------------
  * These replace the generated `:pointwise` kernels (ext/cuTileExt/build.jl:3-10)
  * and the full / partial folds with their merge launches

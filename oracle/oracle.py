@@ -421,6 +421,43 @@ def deltanet_sequential(q, k, v, a, beta, threads=1):
     return o
 
 
+def deltanet_sequential_bwd(q, k, v, a, beta, dout):
+    """Pullback of the token-by-token rule (examples/deltanet.jl:89-101) in Float64, by reverse
+    accumulation over positions: with r = k' S_prev, Y = S_prev - beta k r', S = g Y + beta k v', o = S' q,
+      dS += q do';  dq = S do;  dg = <dS, Y>;  dY = g dS;
+      dbeta = k' dS v - k' dY r;  dv = beta dS' k;  dk = beta dS v - beta (dY r + S_prev dY' k);
+      dS_prev = dY - beta k (k' dY);  da = dg g.
+    q, k, v BFloat16 bits [heads][T][d]; a, beta float32 [heads][T]; dout float64 [heads][dv][T].
+    Returns dq, dk, dv [heads][T][d], da, dbeta [heads][T], all float64.  Keeps every state: small T only."""
+    Q, K, V = (from_bf16(x).astype(np.float64) for x in (q, k, v))
+    A, B = a.astype(np.float64), beta.astype(np.float64)
+    Hn, T, dk = Q.shape
+    dv_ = V.shape[2]
+    dQ, dK, dV = np.zeros_like(Q), np.zeros_like(K), np.zeros_like(V)
+    dA, dB = np.zeros_like(A), np.zeros_like(B)
+    for h in range(Hn):
+        states = np.zeros((T + 1, dk, dv_))
+        for t in range(T):
+            S, kt, g, b = states[t], K[h, t], np.exp(A[h, t]), B[h, t]
+            states[t + 1] = g * (S - b * np.outer(kt, kt @ S)) + b * np.outer(kt, V[h, t])
+        dS = np.zeros((dk, dv_))
+        for t in range(T - 1, -1, -1):
+            Sp, S, kt, vt, g, b = states[t], states[t + 1], K[h, t], V[h, t], np.exp(A[h, t]), B[h, t]
+            do = dout[h, :, t]
+            dS = dS + np.outer(Q[h, t], do)
+            dQ[h, t] = S @ do
+            r = kt @ Sp
+            Y = Sp - b * np.outer(kt, r)
+            dA[h, t] = (dS * Y).sum() * g
+            dY = g * dS
+            dSv, dYr, dYk = dS @ vt, dY @ r, dY.T @ kt
+            dB[h, t] = kt @ dSv - kt @ dYr
+            dV[h, t] = b * (dS.T @ kt)
+            dK[h, t] = b * dSv - b * (dYr + Sp @ dYk)
+            dS = dY - b * np.outer(kt, dYk)
+    return dQ, dK, dV, dA, dB
+
+
 def deltanet_inputs(heads, T, dk, dv, seed):
     """The benchmark's distributions: q, k ~ N(0,1) L2-normalised per position, v ~ N(0,1),
     beta = sigmoid(N(0,1)), a = -softplus(N(0,1))."""

@@ -36,10 +36,13 @@ __device__ __forceinline__ float bf16_bits_to_float(unsigned short h) { return _
 
 // ---------------------------------------------------------------- within a chunk ----
 
-__global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+// With minv_save (the backward's first launch) the block has 320 threads: the extra 64 solve
+// (I + A) X = I, one identity column each, which is (I + A)^-1 for the reverse scan.
+__global__ void __launch_bounds__(320) deltanet_chunk_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
                                                              const __nv_bfloat16 *v, const float *a, const float *beta,
                                                              __nv_bfloat16 *w_out, __nv_bfloat16 *u_out,
-                                                             __nv_bfloat16 *p_out, int T) {
+                                                             __nv_bfloat16 *p_out, float *minv_save,
+                                                             int T) {
     extern __shared__ float sm[];
     float *Kf = sm;                       // [64][132]
     float *Qf = Kf + kC * kPadF;          // [64][132]
@@ -51,7 +54,7 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
     const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
     const int tid = threadIdx.x;
 
-    for (int i = tid; i < kC * kDK / 8; i += 256) {
+    for (int i = tid; i < kC * kDK / 8; i += blockDim.x) {
         const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
         float kv[8], qv[8];
         Access<__nv_bfloat16, true>::load_cached(k + (row0 + r) * kDK + c, kv);
@@ -67,7 +70,7 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
     __syncthreads();
 
     // A = beta .* decay(t > s) .* (K K'), P = decay(t >= s) .* (Q K'): 4 x 4 outputs per thread
-    {
+    if (tid < 256) {
         const int ty = tid >> 4, tx = tid & 15;
         float kk[4][4] = {}, qk[4][4] = {};
         if (tx <= ty) {   // blocks above the diagonal are zero
@@ -109,15 +112,21 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
         for (int t = 0; t < kC; t++) {
             float rhs;
             if (c < kDK) rhs = be[t] * __expf(ca[t]) * Kf[t * kPadF + c];
+            else if (c >= kDK + kDV) rhs = (t == c - kDK - kDV) ? 1.0f : 0.0f;
             else rhs = be[t] * bf16_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(v) + (row0 + t) * kDV + (c - kDK)));
             float acc = rhs;
 #pragma unroll
             for (int s = 0; s < t; s++) acc = fmaf(-A[t * kC + s], x[s], acc);
             x[t] = acc;
         }
-        __nv_bfloat16 *dst = (c < kDK ? w_out : u_out) + row0 * 128 + (c & 127);
+        if (c >= kDK + kDV) {
 #pragma unroll
-        for (int t = 0; t < kC; t++) dst[t * 128] = __float2bfloat16_rn(x[t]);
+            for (int t = 0; t < kC; t++) minv_save[(row0 + t) * kC + (c - kDK - kDV)] = x[t];
+        } else {
+            __nv_bfloat16 *dst = (c < kDK ? w_out : u_out) + row0 * 128 + (c & 127);
+#pragma unroll
+            for (int t = 0; t < kC; t++) dst[t * 128] = __float2bfloat16_rn(x[t]);
+        }
     }
 }
 
@@ -130,7 +139,7 @@ __device__ __forceinline__ void unpack8(const __nv_bfloat16 *p, float *v) {
 __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
                                                             const float *a, const __nv_bfloat16 *w_in,
                                                             const __nv_bfloat16 *u_in, const __nv_bfloat16 *p_in,
-                                                            __nv_bfloat16 *o, int T) {
+                                                            __nv_bfloat16 *o, float *s_save, float *u_save, int T) {
     extern __shared__ float sm[];
     float *S = sm;                                      // [128][32] the state slice
     float *Ut = S + kDK * kDVP;                         // [64][32]
@@ -153,6 +162,10 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
     for (int chunk = 0; chunk < chunks; chunk++) {
         const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
         __syncthreads();   // the previous chunk's readers are done with the tiles
+        if (s_save) {      // the state this chunk starts from, for the backward
+            float *dst = s_save + (static_cast<long long>(head) * chunks + chunk) * kDK * kDV + part * kDVP;
+            for (int i = tid; i < kDK * kDVP; i += 256) dst[(i / kDVP) * kDV + (i % kDVP)] = S[i];
+        }
         for (int i = tid; i < kC * kDK / 8; i += 256) {
             const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
             *reinterpret_cast<uint4 *>(Wh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(w_in + (row0 + r) * kDK + c));
@@ -200,52 +213,57 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
             }
         }
 #pragma unroll
-        for (int r = 0; r < 2; r++)
-            *reinterpret_cast<float4 *>(U + (2 * ty + r) * kDVP + 4 * tx) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+        for (int r = 0; r < 2; r++) {
+            const float4 u4 = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+            *reinterpret_cast<float4 *>(U + (2 * ty + r) * kDVP + 4 * tx) = u4;
+            if (u_save) *reinterpret_cast<float4 *>(u_save + (row0 + 2 * ty + r) * kDV + part * kDVP + 4 * tx) = u4;
+        }
         __syncthreads();
 
-        // o = (e^ca Q) S + P U
-        float oa[2][4] = {};
-        for (int i = 0; i < kDK; i += 8) {
-            float q0[8], q1[8];
-            unpack8(Qh + (2 * ty) * kPadH + i, q0);
-            unpack8(Qh + (2 * ty + 1) * kPadH + i, q1);
-#pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const float4 s4 = *reinterpret_cast<const float4 *>(S + (i + e) * kDVP + 4 * tx);
-                oa[0][0] = fmaf(q0[e], s4.x, oa[0][0]); oa[0][1] = fmaf(q0[e], s4.y, oa[0][1]);
-                oa[0][2] = fmaf(q0[e], s4.z, oa[0][2]); oa[0][3] = fmaf(q0[e], s4.w, oa[0][3]);
-                oa[1][0] = fmaf(q1[e], s4.x, oa[1][0]); oa[1][1] = fmaf(q1[e], s4.y, oa[1][1]);
-                oa[1][2] = fmaf(q1[e], s4.z, oa[1][2]); oa[1][3] = fmaf(q1[e], s4.w, oa[1][3]);
+        if (o) {
+            // o = (e^ca Q) S + P U
+            float oa[2][4] = {};
+            for (int i = 0; i < kDK; i += 8) {
+                float q0[8], q1[8];
+                unpack8(Qh + (2 * ty) * kPadH + i, q0);
+                unpack8(Qh + (2 * ty + 1) * kPadH + i, q1);
+    #pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const float4 s4 = *reinterpret_cast<const float4 *>(S + (i + e) * kDVP + 4 * tx);
+                    oa[0][0] = fmaf(q0[e], s4.x, oa[0][0]); oa[0][1] = fmaf(q0[e], s4.y, oa[0][1]);
+                    oa[0][2] = fmaf(q0[e], s4.z, oa[0][2]); oa[0][3] = fmaf(q0[e], s4.w, oa[0][3]);
+                    oa[1][0] = fmaf(q1[e], s4.x, oa[1][0]); oa[1][1] = fmaf(q1[e], s4.y, oa[1][1]);
+                    oa[1][2] = fmaf(q1[e], s4.z, oa[1][2]); oa[1][3] = fmaf(q1[e], s4.w, oa[1][3]);
+                }
             }
-        }
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-            const float g = eca[2 * ty + r];
-#pragma unroll
-            for (int j = 0; j < 4; j++) oa[r][j] *= g;
-        }
-        for (int s = 0; s < kC; s += 8) {
-            float p0[8], p1[8];
-            unpack8(Ph + (2 * ty) * kPadP + s, p0);
-            unpack8(Ph + (2 * ty + 1) * kPadP + s, p1);
-#pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const float4 u4 = *reinterpret_cast<const float4 *>(U + (s + e) * kDVP + 4 * tx);
-                oa[0][0] = fmaf(p0[e], u4.x, oa[0][0]); oa[0][1] = fmaf(p0[e], u4.y, oa[0][1]);
-                oa[0][2] = fmaf(p0[e], u4.z, oa[0][2]); oa[0][3] = fmaf(p0[e], u4.w, oa[0][3]);
-                oa[1][0] = fmaf(p1[e], u4.x, oa[1][0]); oa[1][1] = fmaf(p1[e], u4.y, oa[1][1]);
-                oa[1][2] = fmaf(p1[e], u4.z, oa[1][2]); oa[1][3] = fmaf(p1[e], u4.w, oa[1][3]);
+    #pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const float g = eca[2 * ty + r];
+    #pragma unroll
+                for (int j = 0; j < 4; j++) oa[r][j] *= g;
             }
+            for (int s = 0; s < kC; s += 8) {
+                float p0[8], p1[8];
+                unpack8(Ph + (2 * ty) * kPadP + s, p0);
+                unpack8(Ph + (2 * ty + 1) * kPadP + s, p1);
+    #pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const float4 u4 = *reinterpret_cast<const float4 *>(U + (s + e) * kDVP + 4 * tx);
+                    oa[0][0] = fmaf(p0[e], u4.x, oa[0][0]); oa[0][1] = fmaf(p0[e], u4.y, oa[0][1]);
+                    oa[0][2] = fmaf(p0[e], u4.z, oa[0][2]); oa[0][3] = fmaf(p0[e], u4.w, oa[0][3]);
+                    oa[1][0] = fmaf(p1[e], u4.x, oa[1][0]); oa[1][1] = fmaf(p1[e], u4.y, oa[1][1]);
+                    oa[1][2] = fmaf(p1[e], u4.z, oa[1][2]); oa[1][3] = fmaf(p1[e], u4.w, oa[1][3]);
+                }
+            }
+    #pragma unroll
+            for (int r = 0; r < 2; r++)
+    #pragma unroll
+                for (int j = 0; j < 4; j++) Oh[(4 * tx + j) * kPadP + 2 * ty + r] = __float2bfloat16_rn(oa[r][j]);
         }
-#pragma unroll
-        for (int r = 0; r < 2; r++)
-#pragma unroll
-            for (int j = 0; j < 4; j++) Oh[(4 * tx + j) * kPadP + 2 * ty + r] = __float2bfloat16_rn(oa[r][j]);
         __syncthreads();   // every reader of S is done; the staged output is complete
 
         // the result is (positions, features): 128 contiguous bytes per feature
-        {
+        if (o) {
             const int f = tid >> 3, c = (tid & 7) * 8;
             *reinterpret_cast<uint4 *>(o + (static_cast<long long>(head) * kDV + part * kDVP + f) * T +
                                        static_cast<long long>(chunk) * kC + c) =
@@ -281,9 +299,549 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
     }
 }
 
+// ------------------------------------------------------------------ the backward ----
+//
+// With e = exp(ca), ed = exp(ca_C - ca), g = exp(ca_C), D[t][s] = exp(ca_t - ca_s) for t >= s, S the state a
+// chunk starts from, dS' the state gradient arriving from the chunks after it, and Minv = (I + A)^-1:
+//   reverse scan   dU = P' dO + (ed K) dS';   dZ = Minv' dU;   dV = beta dZ
+//                  dS = g dS' + (e Q)' dO - (e K)' (beta dZ)
+//   per chunk      X = tril(dO U') .* D;   G = -stril(dZ U') .* D
+//                  dQ = e (dO S') + X K
+//                  dK = -(e beta) (dZ S') + ed (U dS'') + X' Q + beta (G K) + G' (beta K)
+//                  dbeta = rowsum(dZ .* (V - e (K S))) + rowsum(K .* (G K))
+//                  da = reverse cumulative sum within the chunk of the gradient of ca (below)
+// It is the chain rule through examples/deltanet.jl:58-85 taken by hand; Tempest derives the same
+// pullback from the forward program (examples/deltanet.jl:96-101).
+
+// One block per (head, 32 value features), chunks walked last to first.
+__global__ void __launch_bounds__(256) deltanet_bwd_scan_kernel(
+    const __nv_bfloat16 *q, const __nv_bfloat16 *k, const float *a, const float *beta, const __nv_bfloat16 *p_in,
+    const float *minv, const __nv_bfloat16 *dout, float *dsin_save, float *dz_save, __nv_bfloat16 *dv_out, int T) {
+    extern __shared__ float sm[];
+    float *dS = sm;                         // [128][32]
+    float *dOs = dS + kDK * kDVP;           // [64][32]
+    float *dU = dOs + kC * kDVP;            // [64][32]
+    float *dZ = dU + kC * kDVP;             // [64][32]
+    float *Mi = dZ + kC * kDVP;             // [64][65]
+    float *eca = Mi + kC * 65;              // [64]
+    float *ekd = eca + kC;                  // [64]
+    float *be = ekd + kC;                   // [64]
+    __nv_bfloat16 *Qh = reinterpret_cast<__nv_bfloat16 *>(be + kC);   // [64][136]
+    __nv_bfloat16 *Kh = Qh + kC * kPadH;
+    __nv_bfloat16 *Ph = Kh + kC * kPadH;    // [64][72]
+    __shared__ float gamma_sm;
+
+    const int head = blockIdx.x, part = blockIdx.y;
+    const int tid = threadIdx.x;
+    const int chunks = T / kC;
+    for (int i = tid; i < kDK * kDVP; i += 256) dS[i] = 0.0f;
+    const int ty = tid >> 3, tx = tid & 7;   // [64][32] outputs: rows 2ty, 2ty+1; columns 4tx..4tx+3
+
+    for (int chunk = chunks - 1; chunk >= 0; chunk--) {
+        const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
+        const long long cidx = static_cast<long long>(head) * chunks + chunk;
+        __syncthreads();
+        {   // the incoming state gradient, for the per-chunk kernel
+            float *dst = dsin_save + cidx * kDK * kDV + part * kDVP;
+            for (int i = tid; i < kDK * kDVP; i += 256) dst[(i / kDVP) * kDV + (i % kDVP)] = dS[i];
+        }
+        for (int i = tid; i < kC * kDK / 8; i += 256) {
+            const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
+            *reinterpret_cast<uint4 *>(Qh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(q + (row0 + r) * kDK + c));
+            *reinterpret_cast<uint4 *>(Kh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(k + (row0 + r) * kDK + c));
+        }
+        for (int i = tid; i < kC * kC / 8; i += 256) {
+            const int r = i / (kC / 8), c = (i % (kC / 8)) * 8;
+            *reinterpret_cast<uint4 *>(Ph + r * kPadP + c) = __ldg(reinterpret_cast<const uint4 *>(p_in + cidx * kC * kC + r * kC + c));
+        }
+        for (int i = tid; i < kC * kC; i += 256) Mi[(i / kC) * 65 + (i % kC)] = __ldg(minv + row0 * kC + i);
+        {   // dO arrives as (positions, features): 8 positions of one feature per thread
+            const int f = tid >> 3, t8 = (tid & 7) * 8;
+            float dv8[8];
+            Access<__nv_bfloat16, true>::load_cached(
+                dout + (static_cast<long long>(head) * kDV + part * kDVP + f) * T + static_cast<long long>(chunk) * kC + t8, dv8);
+#pragma unroll
+            for (int e = 0; e < 8; e++) dOs[(t8 + e) * kDVP + f] = dv8[e];
+        }
+        if (tid < kC) be[tid] = beta[row0 + tid];
+        if (tid == 0) {
+            float s = 0.0f;
+            for (int t = 0; t < kC; t++) { s += a[row0 + t]; eca[t] = s; }
+            const float last = s;
+            for (int t = 0; t < kC; t++) { const float c = eca[t]; ekd[t] = __expf(last - c); eca[t] = __expf(c); }
+            gamma_sm = __expf(last);
+        }
+        __syncthreads();
+
+        // dU = P' dO + ed (K dS')
+        float acc[2][4] = {};
+        for (int i = 0; i < kDK; i += 8) {
+            float k0[8], k1[8];
+            unpack8(Kh + (2 * ty) * kPadH + i, k0);
+            unpack8(Kh + (2 * ty + 1) * kPadH + i, k1);
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const float4 s4 = *reinterpret_cast<const float4 *>(dS + (i + e) * kDVP + 4 * tx);
+                acc[0][0] = fmaf(k0[e], s4.x, acc[0][0]); acc[0][1] = fmaf(k0[e], s4.y, acc[0][1]);
+                acc[0][2] = fmaf(k0[e], s4.z, acc[0][2]); acc[0][3] = fmaf(k0[e], s4.w, acc[0][3]);
+                acc[1][0] = fmaf(k1[e], s4.x, acc[1][0]); acc[1][1] = fmaf(k1[e], s4.y, acc[1][1]);
+                acc[1][2] = fmaf(k1[e], s4.z, acc[1][2]); acc[1][3] = fmaf(k1[e], s4.w, acc[1][3]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const float sc = ekd[2 * ty + r];
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[r][j] *= sc;
+        }
+        for (int s = 2 * ty; s < kC; s++) {   // P[s][t] is zero for s < t
+            float p0, p1;
+            unpack_bf16x2(*reinterpret_cast<const uint32_t *>(Ph + s * kPadP + 2 * ty), p0, p1);
+            const float4 d4 = *reinterpret_cast<const float4 *>(dOs + s * kDVP + 4 * tx);
+            acc[0][0] = fmaf(p0, d4.x, acc[0][0]); acc[0][1] = fmaf(p0, d4.y, acc[0][1]);
+            acc[0][2] = fmaf(p0, d4.z, acc[0][2]); acc[0][3] = fmaf(p0, d4.w, acc[0][3]);
+            acc[1][0] = fmaf(p1, d4.x, acc[1][0]); acc[1][1] = fmaf(p1, d4.y, acc[1][1]);
+            acc[1][2] = fmaf(p1, d4.z, acc[1][2]); acc[1][3] = fmaf(p1, d4.w, acc[1][3]);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+            *reinterpret_cast<float4 *>(dU + (2 * ty + r) * kDVP + 4 * tx) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+        __syncthreads();
+
+        // dZ = Minv' dU  (Minv is lower triangular: rows s >= t contribute)
+        float z[2][4] = {};
+        for (int s = 2 * ty; s < kC; s++) {
+            const float m0 = Mi[s * 65 + 2 * ty], m1 = Mi[s * 65 + 2 * ty + 1];
+            const float4 u4 = *reinterpret_cast<const float4 *>(dU + s * kDVP + 4 * tx);
+            z[0][0] = fmaf(m0, u4.x, z[0][0]); z[0][1] = fmaf(m0, u4.y, z[0][1]);
+            z[0][2] = fmaf(m0, u4.z, z[0][2]); z[0][3] = fmaf(m0, u4.w, z[0][3]);
+            z[1][0] = fmaf(m1, u4.x, z[1][0]); z[1][1] = fmaf(m1, u4.y, z[1][1]);
+            z[1][2] = fmaf(m1, u4.z, z[1][2]); z[1][3] = fmaf(m1, u4.w, z[1][3]);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int t = 2 * ty + r;
+            const float4 z4 = make_float4(z[r][0], z[r][1], z[r][2], z[r][3]);
+            *reinterpret_cast<float4 *>(dZ + t * kDVP + 4 * tx) = z4;
+            *reinterpret_cast<float4 *>(dz_save + (row0 + t) * kDV + part * kDVP + 4 * tx) = z4;
+            const float b = be[t];
+            uint2 packed;
+            packed.x = pack_bf16x2(b * z4.x, b * z4.y);
+            packed.y = pack_bf16x2(b * z4.z, b * z4.w);
+            *reinterpret_cast<uint2 *>(dv_out + (row0 + t) * kDV + part * kDVP + 4 * tx) = packed;
+        }
+        __syncthreads();
+
+        // dS = g dS' + (e Q)' dO - (e K)' (beta dZ): rows 4ty..4ty+3, columns 4tx..4tx+3
+        {
+            const float gamma = gamma_sm;
+            float sa[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float4 s4 = *reinterpret_cast<const float4 *>(dS + (4 * ty + i) * kDVP + 4 * tx);
+                sa[i][0] = gamma * s4.x; sa[i][1] = gamma * s4.y; sa[i][2] = gamma * s4.z; sa[i][3] = gamma * s4.w;
+            }
+            for (int t = 0; t < kC; t++) {
+                const float e = eca[t], eb = -e * be[t];
+                const uint2 qb = *reinterpret_cast<const uint2 *>(Qh + t * kPadH + 4 * ty);
+                const uint2 kb = *reinterpret_cast<const uint2 *>(Kh + t * kPadH + 4 * ty);
+                float qv[4], kv[4];
+                unpack_bf16x2(qb.x, qv[0], qv[1]); unpack_bf16x2(qb.y, qv[2], qv[3]);
+                unpack_bf16x2(kb.x, kv[0], kv[1]); unpack_bf16x2(kb.y, kv[2], kv[3]);
+                const float4 d4 = *reinterpret_cast<const float4 *>(dOs + t * kDVP + 4 * tx);
+                const float4 z4 = *reinterpret_cast<const float4 *>(dZ + t * kDVP + 4 * tx);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float qe = qv[i] * e, ke = kv[i] * eb;
+                    sa[i][0] = fmaf(qe, d4.x, sa[i][0]); sa[i][1] = fmaf(qe, d4.y, sa[i][1]);
+                    sa[i][2] = fmaf(qe, d4.z, sa[i][2]); sa[i][3] = fmaf(qe, d4.w, sa[i][3]);
+                    sa[i][0] = fmaf(ke, z4.x, sa[i][0]); sa[i][1] = fmaf(ke, z4.y, sa[i][1]);
+                    sa[i][2] = fmaf(ke, z4.z, sa[i][2]); sa[i][3] = fmaf(ke, z4.w, sa[i][3]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                *reinterpret_cast<float4 *>(dS + (4 * ty + i) * kDVP + 4 * tx) = make_float4(sa[i][0], sa[i][1], sa[i][2], sa[i][3]);
+        }
+    }
+}
+
+// X = tril(dO U') .* D and G = -stril(dZ U') .* D, one block per (head, chunk).
+__global__ void __launch_bounds__(256) deltanet_bwd_xg_kernel(const float *a, const __nv_bfloat16 *dout,
+                                                              const float *u_save, const float *dz_save, float *x_out,
+                                                              float *g_out, int T) {
+    extern __shared__ float sm[];
+    float *dOs = sm;                     // [64][132]
+    float *Us = dOs + kC * kPadF;
+    float *dZs = Us + kC * kPadF;
+    float *ca = dZs + kC * kPadF;        // [64]
+    const int chunks = T / kC;
+    const int head = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
+    const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
+    const int tid = threadIdx.x;
+    for (int i = tid; i < kDV * kC / 8; i += 256) {
+        const int f = i >> 3, t8 = (i & 7) * 8;
+        float dv8[8];
+        Access<__nv_bfloat16, true>::load_cached(dout + (static_cast<long long>(head) * kDV + f) * T + static_cast<long long>(chunk) * kC + t8, dv8);
+#pragma unroll
+        for (int e = 0; e < 8; e++) dOs[(t8 + e) * kPadF + f] = dv8[e];
+    }
+    for (int i = tid; i < kC * kDV / 4; i += 256) {
+        const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
+        *reinterpret_cast<float4 *>(Us + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(u_save + (row0 + r) * kDV + c));
+        *reinterpret_cast<float4 *>(dZs + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(dz_save + (row0 + r) * kDV + c));
+    }
+    if (tid == 0) {
+        float s = 0.0f;
+        for (int t = 0; t < kC; t++) { s += a[row0 + t]; ca[t] = s; }
+    }
+    __syncthreads();
+    const int ty = tid >> 4, tx = tid & 15;
+    float xo[4][4] = {}, zo[4][4] = {};
+    if (tx <= ty) {
+        for (int d = 0; d < kDV; d += 4) {
+            float4 dt[4], zt[4], us[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                dt[i] = *reinterpret_cast<const float4 *>(dOs + (ty * 4 + i) * kPadF + d);
+                zt[i] = *reinterpret_cast<const float4 *>(dZs + (ty * 4 + i) * kPadF + d);
+                us[i] = *reinterpret_cast<const float4 *>(Us + (tx * 4 + i) * kPadF + d);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    xo[i][j] += dt[i].x * us[j].x + dt[i].y * us[j].y + dt[i].z * us[j].z + dt[i].w * us[j].w;
+                    zo[i][j] += zt[i].x * us[j].x + zt[i].y * us[j].y + zt[i].z * us[j].z + zt[i].w * us[j].w;
+                }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int t = ty * 4 + i;
+        float4 xv, gv;
+        float *xp = &xv.x, *gp = &gv.x;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int s = tx * 4 + j;
+            const float dec = t >= s ? __expf(ca[t] - ca[s]) : 0.0f;
+            xp[j] = t >= s ? dec * xo[i][j] : 0.0f;
+            gp[j] = t > s ? -dec * zo[i][j] : 0.0f;
+        }
+        *reinterpret_cast<float4 *>(x_out + (row0 + t) * kC + tx * 4) = xv;
+        *reinterpret_cast<float4 *>(g_out + (row0 + t) * kC + tx * 4) = gv;
+    }
+}
+
+__device__ __forceinline__ float sum16(float v) {   // over the 16 lanes that share a row group
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v;
+}
+
+// acc[r][c] += sum_j  L[4ty + r][j] * R[tx + 16c][j]   for two left operands against one right operand
+__device__ __forceinline__ void rows_dot_rows(const float *L0, const float *L1, const float *R, int ty, int tx,
+                                              float (&o0)[4][8], float (&o1)[4][8]) {
+    for (int j = 0; j < 128; j += 4) {
+        float4 l0[4], l1[4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            l0[r] = *reinterpret_cast<const float4 *>(L0 + (4 * ty + r) * kPadF + j);
+            if (L1) l1[r] = *reinterpret_cast<const float4 *>(L1 + (4 * ty + r) * kPadF + j);
+        }
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            const float4 s4 = *reinterpret_cast<const float4 *>(R + (tx + 16 * c) * kPadF + j);
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                o0[r][c] += l0[r].x * s4.x + l0[r].y * s4.y + l0[r].z * s4.z + l0[r].w * s4.w;
+                if (L1) o1[r][c] += l1[r].x * s4.x + l1[r].y * s4.y + l1[r].z * s4.z + l1[r].w * s4.w;
+            }
+        }
+    }
+}
+
+// dQ, dK, da, dbeta of one chunk; one block per (head, chunk).  Thread (ty, tx) owns rows 4ty..4ty+3 and
+// columns tx + 16c (c = 0..7) of every (position, feature) tile, which keeps the 128-bit reads of the state
+// rows free of bank conflicts.
+__global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
+    const __nv_bfloat16 *q, const __nv_bfloat16 *k, const __nv_bfloat16 *v, const float *a, const float *beta,
+    const __nv_bfloat16 *dout, const float *s_save, const float *dsin_save, const float *u_save, const float *dz_save,
+    const float *x_in, const float *g_in, __nv_bfloat16 *dq, __nv_bfloat16 *dk, float *da, float *dbeta, int T) {
+    extern __shared__ float sm[];
+    float *Sb = sm;                        // [128][132]: S, then dS'
+    float *M0 = Sb + kDK * kPadF;          // [64][132]: dO, then U, then the dQ staging
+    float *M1 = M0 + kC * kPadF;           // [64][132]: dZ, then the dK staging
+    float *Xs = M1 + kC * kPadF;           // [64][65]
+    float *Gs = Xs + kC * 65;              // [64][65]
+    float *vec = Gs + kC * 65;             // 10 x [64]
+    float *eca = vec, *ekd = vec + 64, *be = vec + 128, *v_de = vec + 192, *v_ded = vec + 256, *v_rq = vec + 320,
+          *v_rk = vec + 384, *v_cq = vec + 448, *v_ck = vec + 512, *v_rdz = vec + 576;
+    float *red = vec + 640;                // [8]
+    __nv_bfloat16 *Qh = reinterpret_cast<__nv_bfloat16 *>(red + 8);   // [64][136]
+    __nv_bfloat16 *Kh = Qh + kC * kPadH;
+    __shared__ float gamma_sm;
+
+    const int chunks = T / kC;
+    const int head = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
+    const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
+    const long long cidx = static_cast<long long>(head) * chunks + chunk;
+    const int tid = threadIdx.x;
+    const int ty = tid >> 4, tx = tid & 15;
+
+    for (int i = tid; i < kDK * kDV / 4; i += 256) {
+        const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
+        *reinterpret_cast<float4 *>(Sb + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(s_save + cidx * kDK * kDV + r * kDV + c));
+    }
+    for (int i = tid; i < kDV * kC / 8; i += 256) {
+        const int f = i >> 3, t8 = (i & 7) * 8;
+        float dv8[8];
+        Access<__nv_bfloat16, true>::load_cached(dout + (static_cast<long long>(head) * kDV + f) * T + static_cast<long long>(chunk) * kC + t8, dv8);
+#pragma unroll
+        for (int e = 0; e < 8; e++) M0[(t8 + e) * kPadF + f] = dv8[e];
+    }
+    for (int i = tid; i < kC * kDV / 4; i += 256) {
+        const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
+        *reinterpret_cast<float4 *>(M1 + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(dz_save + (row0 + r) * kDV + c));
+    }
+    for (int i = tid; i < kC * kDK / 8; i += 256) {
+        const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
+        *reinterpret_cast<uint4 *>(Qh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(q + (row0 + r) * kDK + c));
+        *reinterpret_cast<uint4 *>(Kh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(k + (row0 + r) * kDK + c));
+    }
+    for (int i = tid; i < kC * kC; i += 256) {
+        Xs[(i / kC) * 65 + (i % kC)] = __ldg(x_in + row0 * kC + i);
+        Gs[(i / kC) * 65 + (i % kC)] = __ldg(g_in + row0 * kC + i);
+    }
+    if (tid < kC) be[tid] = beta[row0 + tid];
+    if (tid == 0) {
+        float s = 0.0f;
+        for (int t = 0; t < kC; t++) { s += a[row0 + t]; eca[t] = s; }
+        const float last = s;
+        for (int t = 0; t < kC; t++) { const float c = eca[t]; ekd[t] = __expf(last - c); eca[t] = __expf(c); }
+        gamma_sm = __expf(last);
+    }
+    __syncthreads();
+
+    float qv[4][8], kv[4][8];   // this thread's Q and K entries
+#pragma unroll
+    for (int r = 0; r < 4; r++)
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            qv[r][c] = __bfloat162float(Qh[(4 * ty + r) * kPadH + tx + 16 * c]);
+            kv[r][c] = __bfloat162float(Kh[(4 * ty + r) * kPadH + tx + 16 * c]);
+        }
+    float dqa[4][8], dka[4][8];
+
+    // phase 1: T1 = dO S', T2 = dZ S';  K S for dbeta
+    {
+        float t1[4][8] = {}, t2[4][8] = {};
+        rows_dot_rows(M0, M1, Sb, ty, tx, t1, t2);
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int t = 4 * ty + r;
+            const float e = eca[t], b = be[t];
+            float de = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                dqa[r][c] = e * t1[r][c];
+                dka[r][c] = -e * b * t2[r][c];
+                de += qv[r][c] * t1[r][c] - b * kv[r][c] * t2[r][c];
+            }
+            de = sum16(de);
+            if (tx == 0) v_de[t] = de;
+        }
+        // (K S)[t][j] for j = tx + 16c, then rowsum(dZ .* (V - e K S))
+        float ks[4][8] = {};
+        for (int i = 0; i < kDK; i += 8) {
+            float kr[4][8];
+#pragma unroll
+            for (int r = 0; r < 4; r++) unpack8(Kh + (4 * ty + r) * kPadH + i, kr[r]);
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                float sv[8];
+#pragma unroll
+                for (int c = 0; c < 8; c++) sv[c] = Sb[(i + e) * kPadF + tx + 16 * c];
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int c = 0; c < 8; c++) ks[r][c] = fmaf(kr[r][e], sv[c], ks[r][c]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int t = 4 * ty + r;
+            const float e = eca[t];
+            float rdz = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const float vv = bf16_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(v) + (row0 + t) * kDV + tx + 16 * c));
+                rdz += M1[t * kPadF + tx + 16 * c] * (vv - e * ks[r][c]);
+            }
+            rdz = sum16(rdz);
+            if (tx == 0) v_rdz[t] = rdz;
+        }
+    }
+    __syncthreads();
+
+    // phase 2: dS' replaces S (their inner product is the gradient of g), U replaces dO; T3 = U dS''
+    {
+        float dgp = 0.0f;
+        for (int i = tid; i < kDK * kDV / 4; i += 256) {
+            const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
+            const float4 nw = __ldg(reinterpret_cast<const float4 *>(dsin_save + cidx * kDK * kDV + r * kDV + c));
+            float4 *slot = reinterpret_cast<float4 *>(Sb + r * kPadF + c);
+            const float4 old = *slot;
+            dgp += old.x * nw.x + old.y * nw.y + old.z * nw.z + old.w * nw.w;
+            *slot = nw;
+        }
+        for (int i = tid; i < kC * kDV / 4; i += 256) {
+            const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
+            *reinterpret_cast<float4 *>(M0 + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(u_save + (row0 + r) * kDV + c));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dgp += __shfl_xor_sync(0xffffffffu, dgp, o);
+        if ((tid & 31) == 0) red[tid >> 5] = dgp;
+    }
+    __syncthreads();
+    {
+        float t3[4][8] = {};
+        float unused[4][8];
+        rows_dot_rows(M0, nullptr, Sb, ty, tx, t3, unused);
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int t = 4 * ty + r;
+            const float ed = ekd[t];
+            float ded = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                dka[r][c] = fmaf(ed, t3[r][c], dka[r][c]);
+                ded += kv[r][c] * t3[r][c];
+            }
+            ded = sum16(ded);
+            if (tx == 0) v_ded[t] = ded;
+        }
+    }
+
+    // phase 3a: X K and X' Q
+    {
+        float xk[4][8] = {}, xq[4][8] = {};
+        for (int s = 0; s < kC; s++) {
+            float ks[8], qs[8], xr[4], xc[4];
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                ks[c] = __bfloat162float(Kh[s * kPadH + tx + 16 * c]);
+                qs[c] = __bfloat162float(Qh[s * kPadH + tx + 16 * c]);
+            }
+#pragma unroll
+            for (int r = 0; r < 4; r++) { xr[r] = Xs[(4 * ty + r) * 65 + s]; xc[r] = Xs[s * 65 + 4 * ty + r]; }
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    xk[r][c] = fmaf(xr[r], ks[c], xk[r][c]);
+                    xq[r][c] = fmaf(xc[r], qs[c], xq[r][c]);
+                }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            float rq = 0.0f, cq = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                dqa[r][c] += xk[r][c];
+                dka[r][c] += xq[r][c];
+                rq += qv[r][c] * xk[r][c];
+                cq += kv[r][c] * xq[r][c];
+            }
+            rq = sum16(rq);
+            cq = sum16(cq);
+            if (tx == 0) { v_rq[4 * ty + r] = rq; v_cq[4 * ty + r] = cq; }
+        }
+    }
+    // phase 3b: G K and G' (beta K)
+    {
+        float gk[4][8] = {}, gb[4][8] = {};
+        for (int s = 0; s < kC; s++) {
+            float ks[8], gr[4], gc[4];
+            const float bs = be[s];
+#pragma unroll
+            for (int c = 0; c < 8; c++) ks[c] = __bfloat162float(Kh[s * kPadH + tx + 16 * c]);
+#pragma unroll
+            for (int r = 0; r < 4; r++) { gr[r] = Gs[(4 * ty + r) * 65 + s]; gc[r] = Gs[s * 65 + 4 * ty + r] * bs; }
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    gk[r][c] = fmaf(gr[r], ks[c], gk[r][c]);
+                    gb[r][c] = fmaf(gc[r], ks[c], gb[r][c]);
+                }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const float b = be[4 * ty + r];
+            float rk = 0.0f, ck = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                dka[r][c] += b * gk[r][c] + gb[r][c];
+                rk += kv[r][c] * gk[r][c];
+                ck += kv[r][c] * gb[r][c];
+            }
+            rk = sum16(rk);
+            ck = sum16(ck);
+            if (tx == 0) { v_rk[4 * ty + r] = rk; v_ck[4 * ty + r] = ck; }
+        }
+    }
+    __syncthreads();   // every reader of U (M0) and dZ (M1) is done; the row sums are visible
+
+#pragma unroll
+    for (int r = 0; r < 4; r++)
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            M0[(4 * ty + r) * kPadF + tx + 16 * c] = dqa[r][c];
+            M1[(4 * ty + r) * kPadF + tx + 16 * c] = dka[r][c];
+        }
+    if (tid == 0) {
+        // the gradient of ca, then da = its reverse cumulative sum inside the chunk
+        float dg = 0.0f;
+        for (int w = 0; w < 8; w++) dg += red[w];
+        float tail = dg * gamma_sm;
+        for (int t = 0; t < kC; t++) tail += v_ded[t] * ekd[t];
+        float run = 0.0f;
+        for (int t = kC - 1; t >= 0; t--) {
+            float dca = v_rq[t] + be[t] * v_rk[t] - v_cq[t] - v_ck[t] + v_de[t] * eca[t] - v_ded[t] * ekd[t];
+            if (t == kC - 1) dca += tail;
+            run += dca;
+            da[row0 + t] = run;
+        }
+    }
+    if (tid >= 32 && tid < 32 + kC) {
+        const int t = tid - 32;
+        dbeta[row0 + t] = v_rdz[t] + v_rk[t];
+    }
+    __syncthreads();
+    for (int i = tid; i < kC * kDK / 8; i += 256) {
+        const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
+        const float *s0 = M0 + r * kPadF + c, *s1 = M1 + r * kPadF + c;
+        uint4 oq, ok;
+        oq.x = pack_bf16x2(s0[0], s0[1]); oq.y = pack_bf16x2(s0[2], s0[3]);
+        oq.z = pack_bf16x2(s0[4], s0[5]); oq.w = pack_bf16x2(s0[6], s0[7]);
+        ok.x = pack_bf16x2(s1[0], s1[1]); ok.y = pack_bf16x2(s1[2], s1[3]);
+        ok.z = pack_bf16x2(s1[4], s1[5]); ok.w = pack_bf16x2(s1[6], s1[7]);
+        *reinterpret_cast<uint4 *>(dq + (row0 + r) * kDK + c) = oq;
+        *reinterpret_cast<uint4 *>(dk + (row0 + r) * kDK + c) = ok;
+    }
+}
+
 constexpr size_t kChunkSmem = (2 * kC * kPadF + kC * kC + 2 * kC) * sizeof(float);
 constexpr size_t kScanSmem = (kDK * kDVP + 2 * kC * kDVP + 2 * kC) * sizeof(float) +
                              (3 * kC * kPadH + kC * kPadP + kDVP * kPadP) * sizeof(__nv_bfloat16);
+constexpr size_t kBwdScanSmem = (kDK * kDVP + 3 * kC * kDVP + kC * 65 + 3 * kC) * sizeof(float) +
+                                (2 * kC * kPadH + kC * kPadP) * sizeof(__nv_bfloat16);
+constexpr size_t kBwdXgSmem = (3 * kC * kPadF + kC) * sizeof(float);
+constexpr size_t kBwdOutSmem = (kDK * kPadF + 2 * kC * kPadF + 2 * kC * 65 + 10 * kC + 8) * sizeof(float) +
+                               2 * kC * kPadH * sizeof(__nv_bfloat16);
 
 }  // namespace
 }  // namespace tb200
@@ -298,6 +856,24 @@ int check_deltanet(const tb200_deltanet_desc *d) {
     if (d->dk != kDK || d->dv != kDV || d->chunk != kC || d->positions % kC != 0) return TB200_ERR_UNSUPPORTED;
     return TB200_OK;
 }
+
+int configure_deltanet(int device) {
+    static std::mutex lock;
+    static bool configured[64] = {};
+    std::lock_guard<std::mutex> hold(lock);
+    if (configured[device]) return TB200_OK;
+    TB200_CUDA(cudaFuncSetAttribute(deltanet_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kChunkSmem)));
+    TB200_CUDA(cudaFuncSetAttribute(deltanet_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kScanSmem)));
+    TB200_CUDA(cudaFuncSetAttribute(deltanet_bwd_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBwdScanSmem)));
+    TB200_CUDA(cudaFuncSetAttribute(deltanet_bwd_xg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBwdXgSmem)));
+    TB200_CUDA(cudaFuncSetAttribute(deltanet_bwd_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBwdOutSmem)));
+    configured[device] = true;
+    return TB200_OK;
+}
+
+// bytes per position of the backward's workspace, after the forward's part
+constexpr size_t kBwdRowBytes = (kC /*Minv*/ + kDK * kDV / kC /*S*/ + kDV /*U*/ + kDK * kDV / kC /*dS'*/ + kDV /*dZ*/ +
+                                 2 * kC /*X, G*/) * sizeof(float);
 }  // namespace
 
 extern "C" size_t tb200_deltanet_workspace_bytes(const tb200_deltanet_desc *d) {
@@ -321,18 +897,7 @@ extern "C" int tb200_deltanet_fwd(const tb200_deltanet_desc *d, const void *q, c
     if (!workspace || workspace_bytes < need || !aligned_to(workspace, 16)) return TB200_ERR_WORKSPACE;
     DeviceInfo dev;
     if ((st = current_device(&dev))) return st;
-    static std::mutex lock;
-    static bool configured[64] = {};
-    {
-        std::lock_guard<std::mutex> hold(lock);
-        if (!configured[dev.device]) {
-            TB200_CUDA(cudaFuncSetAttribute(deltanet_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(kChunkSmem)));
-            TB200_CUDA(cudaFuncSetAttribute(deltanet_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(kScanSmem)));
-            configured[dev.device] = true;
-        }
-    }
+    if ((st = configure_deltanet(dev.device))) return st;
     const size_t rows = static_cast<size_t>(d->heads) * d->positions;
     __nv_bfloat16 *w = static_cast<__nv_bfloat16 *>(workspace);
     __nv_bfloat16 *u = w + rows * kDK;
@@ -341,12 +906,71 @@ extern "C" int tb200_deltanet_fwd(const tb200_deltanet_desc *d, const void *q, c
     const unsigned chunks = static_cast<unsigned>(d->heads) * (T / kC);
     deltanet_chunk_kernel<<<chunks, 256, kChunkSmem, stream>>>(
         static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k),
-        static_cast<const __nv_bfloat16 *>(v), a, beta, w, u, pw, T);
+        static_cast<const __nv_bfloat16 *>(v), a, beta, w, u, pw, nullptr, T);
     TB200_CUDA(cudaGetLastError());
     dim3 grid(static_cast<unsigned>(d->heads), kDV / kDVP);
     deltanet_scan_kernel<<<grid, 256, kScanSmem, stream>>>(static_cast<const __nv_bfloat16 *>(q),
                                                           static_cast<const __nv_bfloat16 *>(k), a, w, u, pw,
-                                                          static_cast<__nv_bfloat16 *>(o), T);
+                                                          static_cast<__nv_bfloat16 *>(o), nullptr, nullptr, T);
+    TB200_CUDA(cudaGetLastError());
+    return TB200_OK;
+}
+
+extern "C" size_t tb200_deltanet_bwd_workspace_bytes(const tb200_deltanet_desc *d) {
+    if (check_deltanet(d) != TB200_OK) return 0;
+    const size_t rows = static_cast<size_t>(d->heads) * d->positions;
+    return tb200_deltanet_workspace_bytes(d) + rows * kBwdRowBytes;
+}
+
+extern "C" int tb200_deltanet_bwd(const tb200_deltanet_desc *d, const void *q, const void *k, const void *v,
+                                  const float *a, const float *beta, const void *dout, void *dq, void *dk, void *dv,
+                                  float *da, float *dbeta, void *workspace, size_t workspace_bytes, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int st = check_deltanet(d);
+    if (st) return st;
+    if (d->heads == 0 || d->positions == 0) return TB200_OK;
+    if (!q || !k || !v || !a || !beta || !dout || !dq || !dk || !dv || !da || !dbeta) return TB200_ERR_NULL;
+    const void *wide[] = {q, k, v, dout, dq, dk, dv};
+    for (const void *p : wide)
+        if (!aligned_to(p, 16)) return TB200_ERR_ALIGN;
+    if (!aligned_to(a, 4) || !aligned_to(beta, 4) || !aligned_to(da, 4) || !aligned_to(dbeta, 4)) return TB200_ERR_ALIGN;
+    const size_t need = tb200_deltanet_bwd_workspace_bytes(d);
+    if (!workspace || workspace_bytes < need || !aligned_to(workspace, 16)) return TB200_ERR_WORKSPACE;
+    DeviceInfo dev;
+    if ((st = current_device(&dev))) return st;
+    if ((st = configure_deltanet(dev.device))) return st;
+
+    const size_t rows = static_cast<size_t>(d->heads) * d->positions;
+    __nv_bfloat16 *w = static_cast<__nv_bfloat16 *>(workspace);
+    __nv_bfloat16 *u = w + rows * kDK;
+    __nv_bfloat16 *pw = u + rows * kDV;
+    float *minv = reinterpret_cast<float *>(pw + rows * kC);
+    float *s_save = minv + rows * kC;
+    float *u_save = s_save + rows * (kDK * kDV / kC);
+    float *dsin = u_save + rows * kDV;
+    float *dz = dsin + rows * (kDK * kDV / kC);
+    float *xw = dz + rows * kDV;
+    float *gw = xw + rows * kC;
+    const int T = d->positions;
+    const unsigned chunks = static_cast<unsigned>(d->heads) * (T / kC);
+    const __nv_bfloat16 *qb = static_cast<const __nv_bfloat16 *>(q), *kb = static_cast<const __nv_bfloat16 *>(k),
+                        *vb = static_cast<const __nv_bfloat16 *>(v), *dob = static_cast<const __nv_bfloat16 *>(dout);
+    dim3 grid(static_cast<unsigned>(d->heads), kDV / kDVP);
+
+    // the forward again, keeping what the pullback needs: (I + A)^-1, the state at every chunk start, U
+    deltanet_chunk_kernel<<<chunks, 320, kChunkSmem, stream>>>(qb, kb, vb, a, beta, w, u, pw, minv, T);
+    TB200_CUDA(cudaGetLastError());
+    // no result pointer: the scan only carries the state
+    deltanet_scan_kernel<<<grid, 256, kScanSmem, stream>>>(qb, kb, a, w, u, pw, nullptr, s_save, u_save, T);
+    TB200_CUDA(cudaGetLastError());
+    deltanet_bwd_scan_kernel<<<grid, 256, kBwdScanSmem, stream>>>(qb, kb, a, beta, pw, minv, dob, dsin, dz,
+                                                                  static_cast<__nv_bfloat16 *>(dv), T);
+    TB200_CUDA(cudaGetLastError());
+    deltanet_bwd_xg_kernel<<<chunks, 256, kBwdXgSmem, stream>>>(a, dob, u_save, dz, xw, gw, T);
+    TB200_CUDA(cudaGetLastError());
+    deltanet_bwd_out_kernel<<<chunks, 256, kBwdOutSmem, stream>>>(qb, kb, vb, a, beta, dob, s_save, dsin, u_save, dz, xw,
+                                                                 gw, static_cast<__nv_bfloat16 *>(dq),
+                                                                 static_cast<__nv_bfloat16 *>(dk), da, dbeta, T);
     TB200_CUDA(cudaGetLastError());
     return TB200_OK;
 }

@@ -67,6 +67,8 @@ SIGNATURES = {
     "tb200_attention_bwd_device_error": (_i, []),
     "tb200_deltanet_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_fwd": (_i, [ctypes.POINTER(DeltanetDesc), _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "tb200_deltanet_bwd_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
+    "tb200_deltanet_bwd": (_i, [ctypes.POINTER(DeltanetDesc)] + [_p] * 12 + [_sz, _p]),
     "tb200_workspace_clear": (_i, [_p, _sz, _p]),
     "tb200_squared_error_workspace_bytes": (_sz, []),
     "tb200_squared_error": (_i, [_p, _p, _p, _p, _i64, _f, _f, _i, _i, _p, _sz, _p]),
@@ -274,3 +276,13 @@ def deltanet_fwd(desc, q, k, v, a, beta, o, workspace, workspace_bytes, stream=0
     """q, k [heads][T][dk], v [heads][T][dv] BFloat16; a, beta [heads][T] Float32; o [heads][dv][T] BFloat16."""
     check("tb200_deltanet_fwd", load().tb200_deltanet_fwd(ctypes.byref(desc), q, k, v, a, beta, o, workspace,
                                                           workspace_bytes, stream or None))
+
+
+def deltanet_bwd_workspace_bytes(desc):
+    return load().tb200_deltanet_bwd_workspace_bytes(ctypes.byref(desc))
+
+
+def deltanet_bwd(desc, q, k, v, a, beta, dout, dq, dk, dv, da, dbeta, workspace, workspace_bytes, stream=0):
+    """Pullback of `deltanet_fwd`: dout [heads][dv][T]; dq, dk, dv in the inputs' layouts (BFloat16); da, dbeta Float32."""
+    check("tb200_deltanet_bwd", load().tb200_deltanet_bwd(ctypes.byref(desc), q, k, v, a, beta, dout, dq, dk, dv, da,
+                                                          dbeta, workspace, workspace_bytes, stream or None))

@@ -52,6 +52,60 @@ def test_example_distribution(pkg, cuda, oracle):
     assert np.abs(got - want).max() / np.abs(want).max() <= 2e-2
 
 
+def run_bwd(pkg, torch, q, k, v, a, beta, dout_bits):
+    L = pkg.lib
+    Hn, T, dk = q.shape
+    dv = v.shape[2]
+    to = lambda x: torch.from_numpy(np.ascontiguousarray(x)).view(torch.bfloat16).cuda()  # noqa: E731
+    qd, kd, vd, dod = to(q), to(k), to(v), to(dout_bits)
+    ad, bd = torch.from_numpy(a).cuda(), torch.from_numpy(beta).cuda()
+    nan = lambda *shape, dtype: torch.full(shape, float("nan"), device="cuda", dtype=dtype)  # noqa: E731
+    dq, dk_, dv_ = (nan(Hn, T, n, dtype=torch.bfloat16) for n in (dk, dk, dv))
+    da, db = nan(Hn, T, dtype=torch.float32), nan(Hn, T, dtype=torch.float32)
+    desc = L.deltanet_desc(Hn, T, dk, dv)
+    need = L.deltanet_bwd_workspace_bytes(desc)
+    assert need > L.deltanet_workspace_bytes(desc)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    L.deltanet_bwd(desc, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ad.data_ptr(), bd.data_ptr(), dod.data_ptr(),
+                   dq.data_ptr(), dk_.data_ptr(), dv_.data_ptr(), da.data_ptr(), db.data_ptr(), ws.data_ptr(), need,
+                   torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    return [x.float().cpu().numpy().astype(np.float64) for x in (dq, dk_, dv_, da, db)]
+
+
+@pytest.mark.parametrize("heads,T", [(1, 64), (2, 192), (1, 512)])
+def test_pullback_against_the_token_rule(pkg, cuda, oracle, heads, T):
+    """BFloat16 gradients against the Float64 pullback of the token rule: largest difference relative
+    to the largest reference value, the example's yardstick (examples/deltanet.jl:112-124)."""
+    q, k, v, a, beta = oracle.deltanet_inputs(heads, T, 128, 128, 300 + T)
+    dout_bits = oracle.to_bf16(oracle.normal((heads, 128, T), 299 + T))
+    dout = oracle.from_bf16(dout_bits).astype(np.float64)
+    got = run_bwd(pkg, cuda, q, k, v, a, beta, dout_bits)
+    want = oracle.deltanet_sequential_bwd(q, k, v, a, beta, dout)
+    for name, g, w in zip(("dq", "dk", "dv", "da", "dbeta"), got, want):
+        assert np.isfinite(g).all(), name
+        rel = np.abs(g - w).max() / np.abs(w).max()
+        assert rel <= 2e-2, (name, rel)
+        assert np.linalg.norm(g - w) <= 1e-2 * np.linalg.norm(w), name
+
+
+def test_pullback_is_linear_in_the_cotangent(pkg, cuda, oracle):
+    """At a size the oracle cannot reach: the pullback of (d1 + d2) equals the sum of the pullbacks, and
+    a zero cotangent gives zero gradients."""
+    heads, T = 2, 2048
+    q, k, v, a, beta = oracle.deltanet_inputs(heads, T, 128, 128, 900)
+    d1 = oracle.from_bf16(oracle.to_bf16(oracle.normal((heads, 128, T), 901)))
+    d2 = oracle.from_bf16(oracle.to_bf16(oracle.normal((heads, 128, T), 902)))
+    both = oracle.to_bf16((d1 + d2).astype(np.float32))
+    ga = run_bwd(pkg, cuda, q, k, v, a, beta, oracle.to_bf16(d1))
+    gb = run_bwd(pkg, cuda, q, k, v, a, beta, oracle.to_bf16(d2))
+    gs = run_bwd(pkg, cuda, q, k, v, a, beta, both)
+    for x, y, z in zip(ga, gb, gs):
+        assert np.abs(x + y - z).max() <= 3e-2 * np.abs(z).max()
+    for g in run_bwd(pkg, cuda, q, k, v, a, beta, np.zeros((heads, 128, T), np.uint16)):
+        assert (g == 0).all()
+
+
 def test_refuses_other_geometries(pkg, cuda):
     L = pkg.lib
     x = cuda.zeros(64, device="cuda")

@@ -126,3 +126,33 @@ def test_readme_loss_gradient(oracle):
     wm[5, 7] -= eps
     fd = (oracle.readme_loss_grad(wp, b, x)[0] - oracle.readme_loss_grad(wm, b, x)[0]) / (2 * eps)
     assert abs(fd - dw[5, 7]) < 5e-2 * max(1.0, abs(dw[5, 7]))
+
+
+def test_deltanet_pullback_against_autograd_and_differences(oracle):
+    """The hand-written reverse accumulation against torch's Float64 autograd of the same rule and
+    against a central difference of the C oracle's forward in one direction."""
+    import torch
+    H, T, d = 2, 48, 16
+    q, k, v, a, beta = oracle.deltanet_inputs(H, T, d, d, 77)
+    dout = oracle.normal((H, d, T), 78).astype(np.float64)
+    got = oracle.deltanet_sequential_bwd(q, k, v, a, beta, dout)
+    leaves = [torch.tensor(oracle.from_bf16(x).astype(np.float64), requires_grad=True) for x in (q, k, v)]
+    leaves += [torch.tensor(x.astype(np.float64), requires_grad=True) for x in (a, beta)]
+    tq, tk, tv, ta, tb = leaves
+    total = 0.0
+    for h in range(H):
+        S = torch.zeros(d, d, dtype=torch.float64)
+        for t in range(T):
+            kt = tk[h, t]
+            S = torch.exp(ta[h, t]) * (S - tb[h, t] * torch.outer(kt, kt @ S)) + tb[h, t] * torch.outer(kt, tv[h, t])
+            total = total + ((S.T @ tq[h, t]) * torch.tensor(dout[h, :, t])).sum()
+    total.backward()
+    for mine, leaf in zip(got, leaves):
+        want = leaf.grad.numpy()
+        assert np.abs(mine - want).max() <= 1e-10 * max(1.0, np.abs(want).max())
+    # central difference along one direction of the gates, through the C forward
+    da = oracle.normal((H, T), 79).astype(np.float32) * np.float32(2.0 ** -10)
+    up = oracle.deltanet_sequential(q, k, v, a + da, beta)
+    dn = oracle.deltanet_sequential(q, k, v, a - da, beta)
+    step = ((a + da).astype(np.float64) - (a - da).astype(np.float64))
+    assert abs(((up - dn) * dout).sum() - (got[3] * step).sum()) <= 1e-4 * abs((got[3] * step).sum()) + 1e-9
