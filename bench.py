@@ -401,6 +401,19 @@ def run_also(torch, dist, pkg, world, rank):
         hbm, _ = measured_peaks()
         out["deltanet_fwd_B4_H16_S8192"] = {"ms": round(dms, 4), "algorithmic_GB/s": round(dbytes / dms / 1e6, 1),
                                             "frac_of_measured_hbm_peak": round(dbytes / dms / 1e6 / hbm, 4)}
+        # its pullback at the same size (forward recomputed inside)
+        gq, gk, gv = (torch.empty(Hn, T, 128, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        ga, gb = torch.empty(Hn, T, device="cuda"), torch.empty(Hn, T, device="cuda")
+        god = torch.randn(Hn, 128, T, device="cuda").bfloat16()
+        bneed = L.deltanet_bwd_workspace_bytes(dd)
+        del dws
+        bws = torch.empty(bneed, dtype=torch.uint8, device="cuda")
+        bms = clock(lambda: L.deltanet_bwd(dd, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ad.data_ptr(), bd.data_ptr(),
+                                           god.data_ptr(), gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), ga.data_ptr(),
+                                           gb.data_ptr(), bws.data_ptr(), bneed, stream), 5)
+        bbytes = 7 * Hn * T * 128 * 2 + 4 * Hn * T * 4
+        out["deltanet_bwd_B4_H16_S8192"] = {"ms": round(bms, 4), "algorithmic_GB/s": round(bbytes / bms / 1e6, 1),
+                                            "workspace_GB": round(bneed / 1e9, 2)}
     return out
 
 
