@@ -23,6 +23,7 @@
 
 #include <mutex>
 
+#include "attention_simt.cuh"
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -546,7 +547,7 @@ extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, cons
     if (d->heads % d->kv_heads != 0 || !(d->scale > 0.0f)) return TB200_ERR_SHAPE;
     if (d->causal && d->queries != d->keys) return TB200_ERR_SHAPE;
     if (d->dtype != TB200_BF16) return TB200_ERR_DTYPE;
-    if (d->head_dim != kD) return TB200_ERR_UNSUPPORTED;
+    if (d->head_dim != kD && !attention_simt_takes(d)) return TB200_ERR_UNSUPPORTED;
     if (d->batch == 0 || (d->queries == 0 && d->keys == 0)) return TB200_OK;
     if (d->queries == 0 || d->keys == 0) return TB200_ERR_UNSUPPORTED;
     if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv) return TB200_ERR_NULL;
@@ -556,6 +557,7 @@ extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, cons
     if (!aligned_to(lse, 4)) return TB200_ERR_ALIGN;
     const size_t need = tb200_attention_bwd_workspace_bytes(d);
     if (!workspace || workspace_bytes < need || !aligned_to(workspace, 16)) return TB200_ERR_WORKSPACE;
+    if (d->head_dim != kD) return attention_simt_bwd(d, q, k, v, o, lse, dout, dq, dk, dv, stream);
     DeviceInfo dev;
     int st = current_device(&dev);
     if (st) return st;

@@ -1,0 +1,237 @@
+// Attention for head dimensions other than 128: Float32 arithmetic on CUDA cores, any head dimension up to
+// 256, any lengths, grouped heads, causal or not.  It exists so that every geometry of the reference's own
+// attention tests (test/cuda/attention.jl:10-16: D = 8, 16, 32 with 70, 133, 200 positions) has a path through
+// this library; it is a fallback in the sense of Tempest's floor (src/Compiler/codegen/scalar.jl:200-256), not
+// a tuned kernel -- the tensor-core kernels take D = 128.
+//
+// The same program as the fast path (test/fixtures/operations.jl:21-76): scores in Float32 from the BFloat16
+// q, k; causal keeps key <= query; lse = logsumexp over keys (natural log); o = sum_n v exp(s - lse) rounded
+// to BFloat16.  Pullback (src/Compiler/program/differentiate.jl:215-218, 461-467): p = exp(s - lse),
+// delta = sum_d dO o, ds = p (dp - delta), dq = scale ds k, dk = scale ds' q, dv = p' dO.
+//
+// One warp per query (forward, dq) or per key (dk, dv): lanes take 32 keys (queries) of a step for the scores,
+// then the head dimension for the accumulation.
+#include "attention_simt.cuh"
+#include "common.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kMaxD = 256;
+constexpr int kWarps = 4;
+
+struct SimtArgs {
+    int batch, heads, kv_heads, queries, keys, d, causal;
+    float scale;
+};
+
+__device__ __forceinline__ float ldbf(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__global__ void __launch_bounds__(kWarps * 32) attention_simt_fwd_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+                                                                        const __nv_bfloat16 *v, __nv_bfloat16 *o,
+                                                                        float *lse, SimtArgs a) {
+    __shared__ float qs[kWarps][kMaxD];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i = blockIdx.x * kWarps + warp, h = blockIdx.y, b = blockIdx.z;
+    if (i >= a.queries) return;
+    const int g = h / (a.heads / a.kv_heads);
+    const long long qrow = ((static_cast<long long>(b) * a.queries + i) * a.heads + h) * a.d;
+    for (int d = lane; d < a.d; d += 32) qs[warp][d] = ldbf(q + qrow + d) * a.scale;
+    __syncwarp();
+    const int last = a.causal ? i : a.keys - 1;
+    float m = -INFINITY, l = 0.0f, acc[kMaxD / 32] = {};
+    for (int key0 = 0; key0 <= last; key0 += 32) {
+        const int j = key0 + lane;
+        const bool valid = j <= last;
+        float s = -INFINITY;
+        if (valid) {
+            const __nv_bfloat16 *kr = k + ((static_cast<long long>(b) * a.keys + j) * a.kv_heads + g) * a.d;
+            s = 0.0f;
+            for (int d = 0; d < a.d; d++) s = fmaf(qs[warp][d], ldbf(kr + d), s);
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float p = valid ? __expf(s - m_new) : 0.0f;
+        const float corr = __expf(m - m_new);
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int c = 0; c < kMaxD / 32; c++) acc[c] *= corr;
+        const int count = min(32, last - key0 + 1);
+        for (int jj = 0; jj < count; jj++) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const __nv_bfloat16 *vr = v + ((static_cast<long long>(b) * a.keys + key0 + jj) * a.kv_heads + g) * a.d;
+#pragma unroll
+            for (int c = 0; c < kMaxD / 32; c++) {
+                const int d = lane + 32 * c;
+                if (d < a.d) acc[c] = fmaf(pj, ldbf(vr + d), acc[c]);
+            }
+        }
+        m = m_new;
+    }
+    const float inv = 1.0f / l;
+#pragma unroll
+    for (int c = 0; c < kMaxD / 32; c++) {
+        const int d = lane + 32 * c;
+        if (d < a.d) o[qrow + d] = __float2bfloat16_rn(acc[c] * inv);
+    }
+    if (lse && lane == 0) lse[(static_cast<long long>(b) * a.queries + i) * a.heads + h] = m + __logf(l);
+}
+
+__global__ void __launch_bounds__(kWarps * 32) attention_simt_dq_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+                                                                       const __nv_bfloat16 *v, const __nv_bfloat16 *o,
+                                                                       const float *lse, const __nv_bfloat16 *dout,
+                                                                       __nv_bfloat16 *dq, SimtArgs a) {
+    __shared__ float qs[kWarps][kMaxD], gs[kWarps][kMaxD];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i = blockIdx.x * kWarps + warp, h = blockIdx.y, b = blockIdx.z;
+    if (i >= a.queries) return;
+    const int g = h / (a.heads / a.kv_heads);
+    const long long qrow = ((static_cast<long long>(b) * a.queries + i) * a.heads + h) * a.d;
+    float delta = 0.0f;
+    for (int d = lane; d < a.d; d += 32) {
+        qs[warp][d] = ldbf(q + qrow + d) * a.scale;
+        const float gd = ldbf(dout + qrow + d);
+        gs[warp][d] = gd;
+        delta = fmaf(gd, ldbf(o + qrow + d), delta);
+    }
+    delta = warp_sum(delta);
+    __syncwarp();
+    const float L = lse[(static_cast<long long>(b) * a.queries + i) * a.heads + h];
+    const int last = a.causal ? i : a.keys - 1;
+    float acc[kMaxD / 32] = {};
+    for (int key0 = 0; key0 <= last; key0 += 32) {
+        const int j = key0 + lane;
+        float ds = 0.0f;
+        if (j <= last) {
+            const long long kv = ((static_cast<long long>(b) * a.keys + j) * a.kv_heads + g) * a.d;
+            float s = 0.0f, dp = 0.0f;
+            for (int d = 0; d < a.d; d++) {
+                s = fmaf(qs[warp][d], ldbf(k + kv + d), s);
+                dp = fmaf(gs[warp][d], ldbf(v + kv + d), dp);
+            }
+            ds = __expf(s - L) * (dp - delta);
+        }
+        const int count = min(32, last - key0 + 1);
+        for (int jj = 0; jj < count; jj++) {
+            const float dsj = __shfl_sync(0xffffffffu, ds, jj);
+            const __nv_bfloat16 *kr = k + ((static_cast<long long>(b) * a.keys + key0 + jj) * a.kv_heads + g) * a.d;
+#pragma unroll
+            for (int c = 0; c < kMaxD / 32; c++) {
+                const int d = lane + 32 * c;
+                if (d < a.d) acc[c] = fmaf(dsj, ldbf(kr + d), acc[c]);
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < kMaxD / 32; c++) {
+        const int d = lane + 32 * c;
+        if (d < a.d) dq[qrow + d] = __float2bfloat16_rn(acc[c] * a.scale);
+    }
+}
+
+__global__ void __launch_bounds__(kWarps * 32) attention_simt_dkdv_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+                                                                         const __nv_bfloat16 *v, const __nv_bfloat16 *o,
+                                                                         const float *lse, const __nv_bfloat16 *dout,
+                                                                         __nv_bfloat16 *dk, __nv_bfloat16 *dv, SimtArgs a) {
+    __shared__ float ks[kWarps][kMaxD], vs[kWarps][kMaxD];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = blockIdx.x * kWarps + warp, g = blockIdx.y, b = blockIdx.z;
+    if (j >= a.keys) return;
+    const long long krow = ((static_cast<long long>(b) * a.keys + j) * a.kv_heads + g) * a.d;
+    for (int d = lane; d < a.d; d += 32) {
+        ks[warp][d] = ldbf(k + krow + d) * a.scale;
+        vs[warp][d] = ldbf(v + krow + d);
+    }
+    __syncwarp();
+    const int rep = a.heads / a.kv_heads;
+    float acck[kMaxD / 32] = {}, accv[kMaxD / 32] = {};
+    for (int r = 0; r < rep; r++) {
+        const int h = g * rep + r;
+        for (int i0 = a.causal ? (j / 32) * 32 : 0; i0 < a.queries; i0 += 32) {
+            const int i = i0 + lane;
+            float p = 0.0f, ds = 0.0f;
+            if (i < a.queries && (!a.causal || i >= j)) {
+                const long long qr = ((static_cast<long long>(b) * a.queries + i) * a.heads + h) * a.d;
+                float s = 0.0f, dp = 0.0f, delta = 0.0f;
+                for (int d = 0; d < a.d; d++) {
+                    const float gd = ldbf(dout + qr + d);
+                    s = fmaf(ks[warp][d], ldbf(q + qr + d), s);
+                    dp = fmaf(gd, vs[warp][d], dp);
+                    delta = fmaf(gd, ldbf(o + qr + d), delta);
+                }
+                p = __expf(s - lse[(static_cast<long long>(b) * a.queries + i) * a.heads + h]);
+                ds = p * (dp - delta);
+            }
+            const int count = min(32, a.queries - i0);
+            for (int ii = 0; ii < count; ii++) {
+                const float pi = __shfl_sync(0xffffffffu, p, ii), dsi = __shfl_sync(0xffffffffu, ds, ii);
+                if (pi == 0.0f && dsi == 0.0f) continue;   // masked (uniform across the warp)
+                const long long qr = ((static_cast<long long>(b) * a.queries + i0 + ii) * a.heads + h) * a.d;
+#pragma unroll
+                for (int c = 0; c < kMaxD / 32; c++) {
+                    const int d = lane + 32 * c;
+                    if (d < a.d) {
+                        accv[c] = fmaf(pi, ldbf(dout + qr + d), accv[c]);
+                        acck[c] = fmaf(dsi, ldbf(q + qr + d), acck[c]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < kMaxD / 32; c++) {
+        const int d = lane + 32 * c;
+        if (d < a.d) {
+            dk[krow + d] = __float2bfloat16_rn(acck[c] * a.scale);
+            dv[krow + d] = __float2bfloat16_rn(accv[c]);
+        }
+    }
+}
+
+SimtArgs simt_args(const tb200_attn_desc *d) {
+    return SimtArgs{d->batch, d->heads, d->kv_heads, d->queries, d->keys, d->head_dim, d->causal, d->scale};
+}
+
+}  // namespace
+
+bool attention_simt_takes(const tb200_attn_desc *d) {
+    return d->head_dim <= kMaxD && d->heads <= 65535 && d->batch <= 65535;
+}
+
+int attention_simt_fwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, void *o, float *lse,
+                       cudaStream_t stream) {
+    dim3 grid(static_cast<unsigned>(ceil_div(d->queries, kWarps)), d->heads, d->batch);
+    attention_simt_fwd_kernel<<<grid, kWarps * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k), static_cast<const __nv_bfloat16 *>(v),
+        static_cast<__nv_bfloat16 *>(o), lse, simt_args(d));
+    TB200_CUDA(cudaGetLastError());
+    return TB200_OK;
+}
+
+int attention_simt_bwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, const void *o,
+                       const float *lse, const void *dout, void *dq, void *dk, void *dv, cudaStream_t stream) {
+    const __nv_bfloat16 *qb = static_cast<const __nv_bfloat16 *>(q), *kb = static_cast<const __nv_bfloat16 *>(k),
+                        *vb = static_cast<const __nv_bfloat16 *>(v), *ob = static_cast<const __nv_bfloat16 *>(o),
+                        *gb = static_cast<const __nv_bfloat16 *>(dout);
+    dim3 gq(static_cast<unsigned>(ceil_div(d->queries, kWarps)), d->heads, d->batch);
+    attention_simt_dq_kernel<<<gq, kWarps * 32, 0, stream>>>(qb, kb, vb, ob, lse, gb, static_cast<__nv_bfloat16 *>(dq),
+                                                            simt_args(d));
+    TB200_CUDA(cudaGetLastError());
+    dim3 gk(static_cast<unsigned>(ceil_div(d->keys, kWarps)), d->kv_heads, d->batch);
+    attention_simt_dkdv_kernel<<<gk, kWarps * 32, 0, stream>>>(qb, kb, vb, ob, lse, gb, static_cast<__nv_bfloat16 *>(dk),
+                                                              static_cast<__nv_bfloat16 *>(dv), simt_args(d));
+    TB200_CUDA(cudaGetLastError());
+    return TB200_OK;
+}
+
+}  // namespace tb200

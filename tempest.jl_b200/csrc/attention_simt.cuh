@@ -1,0 +1,13 @@
+// CUDA-core attention for head dimensions the tensor-core kernels do not take (attention_simt.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#include "../../include/tempest_b200.h"
+
+namespace tb200 {
+bool attention_simt_takes(const tb200_attn_desc *d);
+int attention_simt_fwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, void *o, float *lse,
+                       cudaStream_t stream);
+int attention_simt_bwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, const void *o,
+                       const float *lse, const void *dout, void *dq, void *dk, void *dv, cudaStream_t stream);
+}  // namespace tb200

@@ -342,7 +342,7 @@ class B200Kernels:
             return all(s.strides[0] == 1 or s.size[0] == 1 for s in b.arrays.values())
         if b.template.startswith("attention"):
             e = b.extents
-            if e.get("d") != 128 or e.get("h", 0) % max(e.get("hk", 1), 1) != 0:
+            if not 0 < e.get("d", 0) <= 256 or e.get("h", 0) % max(e.get("hk", 1), 1) != 0:
                 return False   # as cuDNNAttention declines what its engines do not take (ext/cuDNNExt.jl:90-109)
             if "causal" in b.template and e.get("m") != e.get("n"):
                 return False

@@ -75,13 +75,50 @@ def test_forward_without_lse_and_peaked_scores(pkg, cuda, oracle):
 
 def test_forward_refuses_what_it_does_not_compute(pkg, cuda):
     L, torch = pkg.lib, cuda
-    x = torch.zeros(1, 128, 2, 64, device="cuda", dtype=torch.bfloat16)
-    with pytest.raises(L.TB200Error) as e:
-        L.attention_fwd(L.attn_desc(1, 2, 128, 128, 64, True), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr())
+    x = torch.zeros(1, 128, 2, 512, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(L.TB200Error) as e:   # head dimensions over 256
+        L.attention_fwd(L.attn_desc(1, 2, 128, 128, 512, True), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr())
     assert e.value.status == -7
     with pytest.raises(L.TB200Error) as e:   # causal needs as many queries as keys (operations.jl:40-41)
         L.attention_fwd(L.attn_desc(1, 2, 128, 256, 128, True), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr())
     assert e.value.status == -2
+
+
+# (head dimension, heads, kv heads, positions, batch): the reference's own geometries
+# (test/cuda/attention.jl:10-16) and a few more head dimensions, all on the CUDA-core path
+OTHER_DIMS = [(16, 2, 2, 200, 2), (16, 4, 2, 200, 2), (32, 3, 1, 70, 3), (8, 1, 1, 133, 1), (64, 4, 2, 256, 1),
+              (40, 2, 1, 97, 1), (256, 2, 2, 160, 1)]
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("D,H,Hkv,S,B", OTHER_DIMS)
+def test_other_head_dimensions(pkg, cuda, oracle, D, H, Hkv, S, B, causal):
+    q = oracle.to_bf16(oracle.normal((B, S, H, D), 41 + S))
+    k = oracle.to_bf16(oracle.normal((B, S, Hkv, D), 42 + S))
+    v = oracle.to_bf16(oracle.normal((B, S, Hkv, D), 43 + S))
+    g = oracle.to_bf16(oracle.normal((B, S, H, D), 44 + S))
+    dq, dk, dv, o, lse = run_bwd(pkg, cuda, q, k, v, g, causal)
+    o64, lse64, dq64, dk64, dv64 = oracle.attention_f64(q, k, v, causal, dout=g)
+    assert np.abs(oracle.from_bf16(o) - o64).max() <= ATOL_BF16
+    assert np.abs(lse - lse64).max() <= 2e-5 * max(1.0, np.abs(lse64).max())
+    o_ref, lse_ref = oracle.attention_fwd(q, k, v, causal, threads=4)
+    assert np.abs(oracle.from_bf16(o) - oracle.from_bf16(o_ref)).max() <= ATOL_BF16
+    assert np.abs(lse - lse_ref).max() <= 2e-5 * max(1.0, np.abs(lse_ref).max())
+    close_grad(oracle, dq, dq64, "dq")
+    close_grad(oracle, dk, dk64, "dk")
+    close_grad(oracle, dv, dv64, "dv")
+
+
+def test_more_keys_than_queries(pkg, cuda, oracle):
+    """Cross attention (not causal): 70 queries over 333 keys, head dimension 32."""
+    B, Sq, Sk, H, D = 2, 70, 333, 2, 32
+    q = oracle.to_bf16(oracle.normal((B, Sq, H, D), 51))
+    k = oracle.to_bf16(oracle.normal((B, Sk, H, D), 52))
+    v = oracle.to_bf16(oracle.normal((B, Sk, H, D), 53))
+    o, lse = run_fwd(pkg, cuda, q, k, v, False)
+    o64, lse64 = oracle.attention_f64(q, k, v, False)
+    assert np.abs(oracle.from_bf16(o) - o64).max() <= ATOL_BF16
+    assert np.abs(lse - lse64).max() <= 2e-5 * max(1.0, np.abs(lse64).max())
 
 
 def torch_reference(torch, q, k, v, causal, dout=None):

@@ -83,7 +83,8 @@ def test_product_and_attention_templates(I):
     assert lib.supports(t, a)
     (w,) = lib.estimate(t, a)
     assert abs(w.flops - 1.0995e12) / 1.0995e12 < 1e-3
-    assert not lib.supports(t, I.Binding("attention_causal", dict(e, d=64), arrays))
+    assert lib.supports(t, I.Binding("attention_causal", dict(e, d=64), arrays))      # CUDA-core path
+    assert not lib.supports(t, I.Binding("attention_causal", dict(e, d=512), arrays))
     assert not lib.supports(t, I.Binding("attention_causal", dict(e, n=2048), arrays))
     strided = dict(arrays, q=I.Strided("BFloat16", 0, (128, 32, 4096, 8), (1, 256, 8192, 1 << 25), None, 0))
     assert not lib.supports(t, I.Binding("attention_causal", e, strided))
