@@ -275,6 +275,75 @@ int tb200_deltanet_bwd(const tb200_deltanet_desc *desc, const void *q, const voi
                        const float *a, const float *beta, const void *dout, void *dq, void *dk, void *dv,
                        float *da, float *dbeta, void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- generic fused map -> fold groups ---------------------------------------
+ * Any group of the kinds the four named row entries are instances of: a DAG of
+ * scalar terms over a (n, rows) domain whose first, contiguous axis is folded,
+ * with the folds' finished values readable by later terms.  It is the view the
+ * reference hands every backend (`GroupView`, src/Compiler/Implement/groups.jl:
+ * 106-125) cut down to row groups: terms follow src/Compiler/IR/terms.jl:12-87
+ * (Load, Lit, Ix, Apply, Stat, Cast), folds follow src/Compiler/IR/folds.jl:
+ * 66-89 (sum, max, min, prod), :123-198 (`Relative{Exponential}` = log-sum-exp,
+ * `Relative{Square}` = mean and centred sum of squares by Welford/Chan).
+ * Execution follows the reference's floor (src/Compiler/codegen/scalar.jl:
+ * 200-256): per row, phase by phase, every fold of a phase in one sweep, then a
+ * last sweep for the full-shape outputs -- here with the sweeps of one row
+ * spread over a group of threads, re-reading the row from L1/L2, and the term
+ * DAG run by a small interpreter in registers/local memory (Float32). */
+enum { TB200_GROUP_MAX_INPUTS = 8, TB200_GROUP_MAX_TERMS = 48, TB200_GROUP_MAX_FOLDS = 8, TB200_GROUP_MAX_OUTPUTS = 8 };
+
+typedef enum tb200_term_op {
+    TB200_T_LOAD = 0,    /* a = input index */
+    TB200_T_LIT = 1,     /* imm */
+    TB200_T_INDEX = 2,   /* position along the folded axis, 0-based, as Float32 (Ix) */
+    TB200_T_STAT = 3,    /* a = fold index of an earlier phase: its observed value for this row */
+    TB200_T_STAT2 = 4,   /* the second observed value of TB200_FOLD_MEANVAR (the variance) */
+    TB200_T_ADD = 5, TB200_T_SUB = 6, TB200_T_MUL = 7, TB200_T_DIV = 8, TB200_T_MAX = 9, TB200_T_MIN = 10,
+    TB200_T_NEG = 11, TB200_T_EXP = 12, TB200_T_LOG = 13, TB200_T_TANH = 14, TB200_T_SQRT = 15,
+    TB200_T_RSQRT = 16, TB200_T_ABS = 17, TB200_T_ABS2 = 18, TB200_T_RECIP = 19, TB200_T_SIGMOID = 20,
+    TB200_T_FMA = 21,    /* a * b + c, fused */
+    TB200_T_SELECT = 22, /* a > 0 ? b : c */
+    TB200_T_ROUND_BF16 = 23 /* Cast to BFloat16 and back: the rounding an Apply of that eltype makes */
+} tb200_term_op;
+
+typedef struct tb200_term { int op, a, b, c; float imm; } tb200_term;
+
+typedef enum tb200_fold_kind {
+    TB200_FOLD_SUM = 0, TB200_FOLD_MAX = 1, TB200_FOLD_MIN = 2, TB200_FOLD_PROD = 3,
+    TB200_FOLD_LOGSUMEXP = 4, /* observes log(sum(exp(y))) from the online (max, rebased sum) state */
+    TB200_FOLD_MEANVAR = 5    /* observes the mean; TB200_T_STAT2 reads sum((y - mean)^2) / n */
+} tb200_fold_kind;
+
+typedef struct tb200_fold { int kind, term, phase; } tb200_fold;
+
+typedef enum tb200_group_shape {
+    TB200_SHAPE_FULL = 0,    /* (n, rows): element (i, row) at row * ld + i */
+    TB200_SHAPE_ALONG = 1,   /* (n,): one value per position, shared by all rows (a LayerNorm weight) */
+    TB200_SHAPE_PER_ROW = 2, /* (rows,): one value per row (a saved statistic) */
+    TB200_SHAPE_SCALAR = 3
+} tb200_group_shape;
+
+typedef struct tb200_group_input { int shape, dtype; int64_t ld; } tb200_group_input;
+
+/* from = 0: the term `index`, full shape, rounded once to `dtype`; from = 1 / 2: the
+ * first / second observed value of fold `index`, one per row */
+typedef struct tb200_group_output { int from, index, dtype; int64_t ld; } tb200_group_output;
+
+typedef struct tb200_group_desc {
+    int64_t n, rows;
+    int n_inputs, n_terms, n_folds, n_outputs;
+    tb200_group_input inputs[TB200_GROUP_MAX_INPUTS];
+    tb200_term terms[TB200_GROUP_MAX_TERMS];     /* topologically ordered: arguments come before uses */
+    tb200_fold folds[TB200_GROUP_MAX_FOLDS];     /* phase p may read TB200_T_STAT of phases < p */
+    tb200_group_output outputs[TB200_GROUP_MAX_OUTPUTS];
+} tb200_group_desc;
+
+/* Checks a descriptor without running it: TB200_OK or the status the launch would return. */
+int tb200_rowreduce_generic_check(const tb200_group_desc *desc);
+
+/* inputs[i], outputs[j]: device addresses in the descriptor's order.  No workspace. */
+int tb200_rowreduce_generic(const tb200_group_desc *desc, const void *const *inputs, void *const *outputs,
+                            void *stream);
+
 /* ---- pointwise maps and folds over other axes -------------------------------
  * These replace the generated `:pointwise` kernels (ext/cuTileExt/build.jl:3-10)
  * and the full / partial folds with their merge launches

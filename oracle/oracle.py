@@ -25,7 +25,7 @@ _i64, _int, _flt, _void = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c
 
 
 def build(force=False):
-    srcs = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith(".c")]
+    srcs = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith((".c", ".inc"))]
     if force or not os.path.exists(LIB) or any(os.path.getmtime(s) > os.path.getmtime(LIB) for s in srcs):
         subprocess.run(["make", "-C", HERE, "-B", "liboracle.so"], check=True, capture_output=True)
     return LIB
@@ -404,6 +404,23 @@ def attention_f64(q, k, v, causal, scale=None, dout=None):
 
 
 # -------------------------------------------------------------- DeltaNet ----
+
+def group_eval(desc, inputs, outputs, threads=1, wide=False):
+    """Runs a generic map -> fold row group (a `tb200_group_desc` ctypes structure) on the host, rows in
+    order: the floor of src/Compiler/codegen/scalar.jl:200-256 over the descriptor.  `inputs`, `outputs`:
+    numpy arrays (uint16 for BFloat16) in the descriptor's order; outputs are written in place.
+    `wide` evaluates in Float64 instead (same storage types)."""
+    fn = load().oracle_group_rows_f64 if wide else load().oracle_group_rows
+    fn.restype = ctypes.c_int
+    ins = (ctypes.c_void_p * max(len(inputs), 1))(*[a.ctypes.data for a in inputs])
+    outs = (ctypes.c_void_p * max(len(outputs), 1))(*[a.ctypes.data for a in outputs])
+
+    def call(r0, r1):
+        if fn(ctypes.byref(desc), ins, outs, _i64(r0), _i64(r1)) != 0:
+            raise ValueError("oracle cannot run this group")
+    _over_rows(call, int(desc.rows), threads)
+    return outputs
+
 
 def deltanet_sequential(q, k, v, a, beta, threads=1):
     """The gated delta rule token by token in Float64 (examples/deltanet.jl:89-101).

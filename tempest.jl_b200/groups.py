@@ -1,0 +1,182 @@
+"""Row groups as data: the host-side picture of what Tempest hands a backend.
+
+Tempest's planner gives every backend a `GroupView` (src/Compiler/Implement/groups.jl:106-125): the kind of
+the group, its domain, its terms (`IR/terms.jl:12-87`: Load, Lit, Ix, Apply, Stat, Cast) and its folds
+(`IR/folds.jl`).  `Group` builds the cut of that view this library runs -- a (n, rows) domain whose first,
+contiguous axis is folded -- and turns it into the `tb200_group_desc` of include/tempest_b200.h.  The
+spellings at the bottom are the reference's own test programs (test/fixtures/programs.jl:7-19,
+test/cuda/folds.jl:10-14) written as terms; the named kernels compute the first three faster.
+"""
+from . import lib as L
+
+OPS = {"load": 0, "lit": 1, "index": 2, "stat": 3, "stat2": 4, "add": 5, "sub": 6, "mul": 7, "div": 8, "max": 9,
+       "min": 10, "neg": 11, "exp": 12, "log": 13, "tanh": 14, "sqrt": 15, "rsqrt": 16, "abs": 17, "abs2": 18,
+       "recip": 19, "sigmoid": 20, "fma": 21, "select": 22, "round_bf16": 23}
+ARITY = {**{k: 0 for k in ("load", "lit", "index", "stat", "stat2")},
+         **{k: 2 for k in ("add", "sub", "mul", "div", "max", "min")},
+         **{k: 1 for k in ("neg", "exp", "log", "tanh", "sqrt", "rsqrt", "abs", "abs2", "recip", "sigmoid", "round_bf16")},
+         "fma": 3, "select": 3}
+FOLDS = {"sum": 0, "max": 1, "min": 2, "prod": 3, "logsumexp": 4, "meanvar": 5}
+SHAPES = {"full": 0, "along": 1, "per_row": 2, "scalar": 3}
+DTYPES = {"Float32": L.F32, "BFloat16": L.BF16}
+
+
+class Group:
+    """A map -> fold group over (n, rows).  Methods return the index of the term / fold / input they add."""
+
+    def __init__(self, n, rows):
+        self.n, self.rows = int(n), int(rows)
+        self.inputs, self.terms, self.folds, self.outputs = [], [], [], []
+        self._level = []   # first phase in which a term can be evaluated
+
+    # ---- leaves
+    def input(self, shape="full", eltype="Float32", ld=None):
+        self.inputs.append((SHAPES[shape], DTYPES[eltype], int(ld if ld is not None else self.n)))
+        return len(self.inputs) - 1
+
+    def _term(self, op, a=0, b=0, c=0, imm=0.0, level=0):
+        self.terms.append((OPS[op], int(a), int(b), int(c), float(imm)))
+        self._level.append(level)
+        return len(self.terms) - 1
+
+    def load(self, inp):
+        return self._term("load", inp)
+
+    def lit(self, x):
+        return self._term("lit", imm=x)
+
+    def index(self):
+        return self._term("index")
+
+    def stat(self, fold, second=False):
+        return self._term("stat2" if second else "stat", fold, level=self.folds[fold][2] + 1)
+
+    # ---- Apply nodes
+    def apply(self, op, *args):
+        assert len(args) == ARITY[op], (op, args)
+        padded = list(args) + [0] * (3 - len(args))
+        return self._term(op, *padded, level=max(self._level[a] for a in args))
+
+    def __getattr__(self, op):
+        if op in ARITY and ARITY[op] > 0:
+            return lambda *args: self.apply(op, *args)
+        raise AttributeError(op)
+
+    # ---- folds and outputs
+    def fold(self, kind, term):
+        """The fold runs in the first phase in which its term is known (a term that reads a statistic waits
+        for that statistic's phase to finish)."""
+        self.folds.append((FOLDS[kind], int(term), self._level[term]))
+        return len(self.folds) - 1
+
+    def output(self, term, eltype="Float32", ld=None):
+        self.outputs.append((0, int(term), DTYPES[eltype], int(ld if ld is not None else self.n)))
+        return len(self.outputs) - 1
+
+    def output_stat(self, fold, eltype="Float32", second=False):
+        self.outputs.append((2 if second else 1, int(fold), DTYPES[eltype], 0))
+        return len(self.outputs) - 1
+
+    # ---- the C descriptor
+    def desc(self):
+        if (len(self.inputs) > L.GROUP_MAX_INPUTS or len(self.terms) > L.GROUP_MAX_TERMS or
+                len(self.folds) > L.GROUP_MAX_FOLDS or len(self.outputs) > L.GROUP_MAX_OUTPUTS):
+            raise ValueError("group too large for one descriptor")
+        d = L.GroupDesc()
+        d.n, d.rows = self.n, self.rows
+        d.n_inputs, d.n_terms, d.n_folds, d.n_outputs = (len(self.inputs), len(self.terms), len(self.folds),
+                                                         len(self.outputs))
+        for i, (shape, dtype, ld) in enumerate(self.inputs):
+            d.inputs[i].shape, d.inputs[i].dtype, d.inputs[i].ld = shape, dtype, ld
+        for i, (op, a, b, c, imm) in enumerate(self.terms):
+            t = d.terms[i]
+            t.op, t.a, t.b, t.c, t.imm = op, a, b, c, imm
+        for i, (kind, term, phase) in enumerate(self.folds):
+            d.folds[i].kind, d.folds[i].term, d.folds[i].phase = kind, term, phase
+        for i, (source, index, dtype, ld) in enumerate(self.outputs):
+            o = d.outputs[i]
+            o.source, o.index, o.dtype, o.ld = source, index, dtype, ld
+        return d
+
+    def bytes(self):
+        """Algorithmic bytes: every input once, every output once (the `bytes` of a GroupView)."""
+        size = {L.F32: 4, L.BF16: 2}
+        extent = {0: self.n * self.rows, 1: self.n, 2: self.rows, 3: 1}
+        total = sum(extent[shape] * size[dtype] for shape, dtype, _ in self.inputs)
+        total += sum((self.n * self.rows if source == 0 else self.rows) * size[dtype]
+                     for source, _, dtype, _ in self.outputs)
+        return total
+
+
+# ---- the reference's programs as groups -------------------------------------------------------------------
+
+def softmax(n, rows, eltype="Float32"):
+    """exp.(x .- logsumexp(x; dims=1))  (test/fixtures/programs.jl:8)."""
+    g = Group(n, rows)
+    x = g.load(g.input("full", eltype))
+    lse = g.fold("logsumexp", x)
+    g.output(g.exp(g.sub(x, g.stat(lse))), eltype)
+    g.output_stat(lse)
+    return g
+
+
+def log_softmax(n, rows, eltype="Float32"):
+    g = Group(n, rows)
+    x = g.load(g.input("full", eltype))
+    lse = g.fold("logsumexp", x)
+    g.output(g.sub(x, g.stat(lse)), eltype)
+    return g
+
+
+def softmax_pullback(n, rows, eltype="Float32"):
+    """t = g .* y;  t .- y .* sum(t; dims=1)."""
+    g = Group(n, rows)
+    y = g.load(g.input("full", eltype))
+    dy = g.load(g.input("full", eltype))
+    t = g.mul(dy, y)
+    s = g.fold("sum", t)
+    g.output(g.sub(t, g.mul(y, g.stat(s))), eltype)
+    return g
+
+
+def layernorm(n, rows, eltype="Float32", eps=1.0e-5, two_pass=False):
+    """(x .- m) ./ sqrt.(v .+ eps) .* w .+ b  (test/fixtures/programs.jl:13-17).  `two_pass` spells the variance
+    as the reference's source does -- sum(abs2, x .- m) / n, a fold that waits for the mean -- instead of the
+    one-pass Welford state its rewrite produces (src/Compiler/plan/rewrites.jl:29-44)."""
+    g = Group(n, rows)
+    x = g.load(g.input("full", eltype))
+    w = g.load(g.input("along", eltype))
+    b = g.load(g.input("along", eltype))
+    if two_pass:
+        s = g.fold("sum", x)
+        mean = g.mul(g.stat(s), g.lit(1.0 / n))
+        centred = g.sub(x, mean)
+        q = g.fold("sum", g.abs2(centred))
+        var = g.mul(g.stat(q), g.lit(1.0 / n))
+    else:
+        mv = g.fold("meanvar", x)
+        centred = g.sub(x, g.stat(mv))
+        var = g.stat(mv, second=True)
+    rstd = g.rsqrt(g.add(var, g.lit(eps)))
+    g.output(g.fma(g.mul(centred, rstd), w, b), eltype)
+    return g
+
+
+def rmsnorm(n, rows, eltype="Float32", eps=1.0e-6):
+    """x ./ sqrt.(sum(abs2, x; dims=1) ./ n .+ eps) .* w  (test/cuda/folds.jl:10-14)."""
+    g = Group(n, rows)
+    x = g.load(g.input("full", eltype))
+    w = g.load(g.input("along", eltype))
+    q = g.fold("sum", g.abs2(x))
+    scale = g.rsqrt(g.fma(g.stat(q), g.lit(1.0 / n), g.lit(eps)))
+    g.output(g.mul(g.mul(x, scale), w), eltype)
+    return g
+
+
+def row_extrema(n, rows, eltype="Float32"):
+    """maximum, minimum, sum and product along the folded axis: four statistics in one sweep."""
+    g = Group(n, rows)
+    x = g.load(g.input("full", eltype))
+    for kind in ("max", "min", "sum", "prod"):
+        g.output_stat(g.fold(kind, x))
+    return g

@@ -45,6 +45,35 @@ class DeltanetDesc(ctypes.Structure):
                 ("chunk", ctypes.c_int), ("dtype", ctypes.c_int)]
 
 
+GROUP_MAX_INPUTS, GROUP_MAX_TERMS, GROUP_MAX_FOLDS, GROUP_MAX_OUTPUTS = 8, 48, 8, 8
+
+
+class GroupInput(ctypes.Structure):
+    _fields_ = [("shape", ctypes.c_int), ("dtype", ctypes.c_int), ("ld", ctypes.c_int64)]
+
+
+class GroupTerm(ctypes.Structure):
+    _fields_ = [("op", ctypes.c_int), ("a", ctypes.c_int), ("b", ctypes.c_int), ("c", ctypes.c_int),
+                ("imm", ctypes.c_float)]
+
+
+class GroupFold(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_int), ("term", ctypes.c_int), ("phase", ctypes.c_int)]
+
+
+class GroupOutput(ctypes.Structure):
+    _fields_ = [("source", ctypes.c_int), ("index", ctypes.c_int), ("dtype", ctypes.c_int), ("ld", ctypes.c_int64)]
+
+
+class GroupDesc(ctypes.Structure):
+    """tb200_group_desc of include/tempest_b200.h (`source` is the header's `from`)."""
+    _fields_ = [("n", ctypes.c_int64), ("rows", ctypes.c_int64),
+                ("n_inputs", ctypes.c_int), ("n_terms", ctypes.c_int), ("n_folds", ctypes.c_int),
+                ("n_outputs", ctypes.c_int),
+                ("inputs", GroupInput * GROUP_MAX_INPUTS), ("terms", GroupTerm * GROUP_MAX_TERMS),
+                ("folds", GroupFold * GROUP_MAX_FOLDS), ("outputs", GroupOutput * GROUP_MAX_OUTPUTS)]
+
+
 # name -> (restype, argtypes): the declarations of include/tempest_b200.h
 SIGNATURES = {
     "tb200_version": (_i, []),
@@ -67,6 +96,8 @@ SIGNATURES = {
     "tb200_attention_bwd_device_error": (_i, []),
     "tb200_deltanet_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_fwd": (_i, [ctypes.POINTER(DeltanetDesc), _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "tb200_rowreduce_generic_check": (_i, [ctypes.POINTER(GroupDesc)]),
+    "tb200_rowreduce_generic": (_i, [ctypes.POINTER(GroupDesc), ctypes.POINTER(_p), ctypes.POINTER(_p), _p]),
     "tb200_deltanet_bwd_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_bwd": (_i, [ctypes.POINTER(DeltanetDesc)] + [_p] * 12 + [_sz, _p]),
     "tb200_workspace_clear": (_i, [_p, _sz, _p]),
@@ -286,3 +317,14 @@ def deltanet_bwd(desc, q, k, v, a, beta, dout, dq, dk, dv, da, dbeta, workspace,
     """Pullback of `deltanet_fwd`: dout [heads][dv][T]; dq, dk, dv in the inputs' layouts (BFloat16); da, dbeta Float32."""
     check("tb200_deltanet_bwd", load().tb200_deltanet_bwd(ctypes.byref(desc), q, k, v, a, beta, dout, dq, dk, dv, da,
                                                           dbeta, workspace, workspace_bytes, stream or None))
+
+
+def rowreduce_generic_check(desc):
+    return load().tb200_rowreduce_generic_check(ctypes.byref(desc))
+
+
+def rowreduce_generic(desc, inputs, outputs, stream=0):
+    """Runs a generic map -> fold row group: `inputs`, `outputs` are device addresses in the descriptor's order."""
+    ins = (_p * max(len(inputs), 1))(*inputs)
+    outs = (_p * max(len(outputs), 1))(*outputs)
+    check("tb200_rowreduce_generic", load().tb200_rowreduce_generic(ctypes.byref(desc), ins, outs, stream or None))

@@ -1,0 +1,101 @@
+"""Generic map -> fold row groups on the host: the descriptor builder, the checks the C entry makes
+before any launch, and the C oracle for groups pinned on the named operators' oracles (which are pinned on
+the reference's known answers) and on Float64 closed forms."""
+import numpy as np
+import pytest
+
+
+def run_oracle(oracle, group, inputs, threads=2):
+    d = group.desc()
+    outs = []
+    for source, _, dtype, _ in group.outputs:
+        shape = (group.rows, group.n) if source == 0 else (group.rows,)
+        outs.append(np.zeros(shape, np.float32 if dtype == 0 else np.uint16))
+    oracle.group_eval(d, [np.ascontiguousarray(a) for a in inputs], outs, threads=threads)
+    return outs
+
+
+def test_softmax_group_is_the_named_oracle(pkg, oracle):
+    G = pkg.groups
+    n, rows = 300, 37
+    x = oracle.normal((rows, n), 5) * 3
+    y, lse = run_oracle(oracle, G.softmax(n, rows), [x])
+    y_named, lse_named = oracle.softmax_fwd(x)
+    assert np.abs(lse - lse_named).max() <= 1e-6 * np.abs(lse_named).max()
+    assert np.abs(y - y_named).max() <= 1e-6
+    y64, lse64 = oracle.softmax_fwd_f64(x)
+    assert np.abs(y - y64).max() <= 1e-6 and np.abs(lse - lse64).max() <= 1e-5
+
+
+def test_layernorm_group_both_spellings(pkg, oracle):
+    G = pkg.groups
+    n, rows = 700, 19
+    x = (oracle.normal((rows, n), 6) * 2 + 5).astype(np.float32)
+    w, b = oracle.normal((n,), 7), oracle.normal((n,), 8)
+    want = oracle.layernorm_fwd_f64(x, w, b)
+    named = oracle.layernorm_fwd(x, w, b)[0]
+    for two_pass in (False, True):
+        (y,) = run_oracle(oracle, G.layernorm(n, rows, two_pass=two_pass), [x, w, b])
+        assert np.abs(y - want).max() <= 2e-5 * np.abs(want).max()
+        assert np.abs(y - named).max() <= 2e-5 * np.abs(want).max()
+    assert G.layernorm(n, rows, two_pass=True).desc().folds[1].phase == 1
+
+
+def test_rmsnorm_pullback_extrema_and_bf16(pkg, oracle):
+    G = pkg.groups
+    n, rows = 129, 23
+    x = oracle.normal((rows, n), 9)
+    w = oracle.normal((n,), 10)
+    (y,) = run_oracle(oracle, G.rmsnorm(n, rows), [x, w])
+    x64 = x.astype(np.float64)
+    want = x64 / np.sqrt((x64 ** 2).mean(axis=1, keepdims=True) + 1e-6) * w
+    assert np.abs(y - want).max() <= 1e-5 * np.abs(want).max()
+    yb = oracle.to_bf16(oracle.softmax_fwd_f64(x)[0].astype(np.float32))
+    gb = oracle.to_bf16(oracle.normal((rows, n), 11))
+    (dx,) = run_oracle(oracle, G.softmax_pullback(n, rows, "BFloat16"), [yb, gb])
+    want = oracle.softmax_bwd_f64(oracle.from_bf16(yb), oracle.from_bf16(gb))
+    assert np.abs(oracle.from_bf16(dx) - want).max() <= 2.0 ** -8 * np.abs(want).max() + 1e-6
+    small = (1.0 + 0.01 * oracle.normal((rows, n), 12)).astype(np.float32)
+    mx, mn, sm, pr = run_oracle(oracle, G.row_extrema(n, rows), [small])
+    assert np.array_equal(mx, small.max(axis=1)) and np.array_equal(mn, small.min(axis=1))
+    assert np.abs(sm - small.astype(np.float64).sum(axis=1)).max() <= 1e-5 * n
+    assert np.abs(pr / np.prod(small.astype(np.float64), axis=1) - 1).max() <= 1e-5
+
+
+def test_known_answer_sum_abs2(pkg, oracle):
+    """compile(x -> sum(abs2, x))([1, 2, 3, 4]) == 30  (src/Compiler/runtime/compile.jl:36-39)."""
+    g = pkg.groups.Group(4, 1)
+    g.output_stat(g.fold("sum", g.abs2(g.load(g.input()))))
+    (s,) = run_oracle(oracle, g, [np.array([[1, 2, 3, 4]], np.float32)], threads=1)
+    assert s[0] == 30.0
+
+
+def test_descriptor_checks(pkg):
+    """tb200_rowreduce_generic_check runs on the host: what it refuses never reaches a launch."""
+    G, L = pkg.groups, pkg.lib
+    assert L.rowreduce_generic_check(G.softmax(4096, 65536).desc()) == 0
+    assert L.rowreduce_generic_check(G.layernorm(128, 3, "BFloat16", two_pass=True).desc()) == 0
+    d = G.softmax(16, 2).desc()
+    d.terms[2].a = 7                      # an argument that comes after its use
+    assert L.rowreduce_generic_check(d) == -2
+    d = G.softmax(16, 2).desc()
+    d.folds[0].phase = 1                  # the output sweep's statistic is fine, but ...
+    d.terms[1].op, d.terms[1].a = 3, 0    # ... a fold that reads its own statistic is not
+    d.folds[0].term = 1
+    assert L.rowreduce_generic_check(d) == -2
+    d = G.softmax(16, 2).desc()
+    d.terms[0].op = 99
+    assert L.rowreduce_generic_check(d) == -7
+    d = G.softmax(16, 2).desc()
+    d.inputs[0].ld = 8                    # rows overlap
+    assert L.rowreduce_generic_check(d) == -2
+    d = G.softmax(16, 2).desc()
+    d.outputs[0].dtype = 5
+    assert L.rowreduce_generic_check(d) == -3
+    g = G.Group(8, 1)
+    x = g.load(g.input())
+    for _ in range(60):
+        x = g.neg(x)
+    g.output(x)
+    with pytest.raises(ValueError):
+        g.desc()

@@ -1,0 +1,143 @@
+"""Generic map -> fold row groups through the C ABI against the C oracle for groups (the reference's floor
+over the same descriptor): the reference's programs spelled as terms, on the shapes its fold tests use
+(test/cuda/folds.jl:16-25: 256x700, 9000x40, 100x3000, 512x300) and on ragged, tiny and long rows."""
+import numpy as np
+import pytest
+
+from helpers import RTOL_F32
+
+pytestmark = pytest.mark.gpu
+
+
+def run_both(pkg, torch, oracle, group, inputs, wide=False):
+    """Returns (gpu outputs, oracle outputs) as numpy arrays (uint16 for BFloat16)."""
+    L = pkg.lib
+    d = group.desc()
+    assert L.rowreduce_generic_check(d) == 0
+    dev_in = [torch.from_numpy(np.ascontiguousarray(a).view(np.int16) if a.dtype == np.uint16 else np.ascontiguousarray(a)).cuda()
+              for a in inputs]
+    dev_out, ref_out = [], []
+    for source, _, dtype, ld in group.outputs:
+        shape = (group.rows, ld) if source == 0 else (group.rows,)
+        host = np.zeros(shape, np.float32 if dtype == 0 else np.uint16)
+        ref_out.append(host)
+        dev_out.append(torch.zeros(shape, device="cuda", dtype=torch.float32 if dtype == 0 else torch.int16))
+    L.rowreduce_generic(d, [t.data_ptr() for t in dev_in], [t.data_ptr() for t in dev_out],
+                        torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    oracle.group_eval(d, [np.ascontiguousarray(a) for a in inputs], ref_out, threads=8)
+    got = [t.cpu().numpy().view(np.uint16) if t.dtype == torch.int16 else t.cpu().numpy() for t in dev_out]
+    if not wide:
+        return got, ref_out
+    wide_out = [np.zeros_like(a) for a in ref_out]
+    oracle.group_eval(d, [np.ascontiguousarray(a) for a in inputs], wide_out, threads=8, wide=True)
+    return got, ref_out, wide_out
+
+
+def agree(oracle, got, want, n, what="", wide=None):
+    """Float32: within 1e-5 of the floor's result relative to the output's scale -- or, where the floor's own
+    sequential Float32 sums have drifted further than that from the Float64 evaluation (long rows), no
+    further from Float64 than twice the floor's distance."""
+    if got.dtype == np.uint16:
+        g, w = oracle.from_bf16(got).astype(np.float64), oracle.from_bf16(want).astype(np.float64)
+        assert np.isfinite(g).all(), what
+        assert np.abs(g - w).max() <= 2.0 ** -7 * np.abs(w).max() + 1e-30, what   # one BFloat16 step at the largest value
+        assert (got != want).mean() <= 0.02, what                                  # and nearly all bits equal
+    else:
+        g, w = got.astype(np.float64), want.astype(np.float64)
+        assert np.isfinite(g).all(), what
+        scale = max(np.abs(w).max(), 1e-30)
+        if np.abs(g - w).max() <= RTOL_F32 * scale:
+            return
+        assert wide is not None, (what, np.abs(g - w).max() / scale)
+        w64 = wide.astype(np.float64)
+        assert np.abs(g - w64).max() <= max(RTOL_F32 * scale, 2 * np.abs(w - w64).max()), what
+
+
+SHAPES = [(256, 700), (9000, 40), (100, 3000), (512, 300), (1, 5), (3, 7), (4096, 64), (70001, 3), (33, 1000)]
+
+
+@pytest.mark.parametrize("eltype", ["Float32", "BFloat16"])
+@pytest.mark.parametrize("n,rows", SHAPES)
+def test_programs_as_groups(pkg, cuda, oracle, n, rows, eltype):
+    G = pkg.groups
+    cast = (lambda a: a) if eltype == "Float32" else oracle.to_bf16
+    x = cast((oracle.normal((rows, n), n + rows) * 2).astype(np.float32))
+    w = cast(oracle.normal((n,), n + 1))
+    b = cast(oracle.normal((n,), n + 2))
+    g2 = cast(oracle.normal((rows, n), n + 3))
+    for name, group, inputs in (
+        ("softmax", G.softmax(n, rows, eltype), [x]),
+        ("log_softmax", G.log_softmax(n, rows, eltype), [x]),
+        ("layernorm", G.layernorm(n, rows, eltype), [x, w, b]),
+        ("layernorm two-pass", G.layernorm(n, rows, eltype, two_pass=True), [x, w, b]),
+        ("rmsnorm", G.rmsnorm(n, rows, eltype), [x, w]),
+        ("softmax pullback", G.softmax_pullback(n, rows, eltype), [x, g2]),
+    ):
+        got, want, wide = run_both(pkg, cuda, oracle, group, inputs, wide=True)
+        for a, r, w64 in zip(got, want, wide):
+            agree(oracle, a, r, n, f"{name} {n}x{rows} {eltype}", w64)
+
+
+def test_against_the_named_kernels(pkg, cuda, oracle):
+    """The generic softmax and LayerNorm against the library's own named entries on the same data."""
+    torch, L, G = cuda, pkg.lib, pkg.groups
+    n, rows = 4096, 300
+    x = torch.randn(rows, n, device="cuda") * 3
+    w, b = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    y_named, y_gen = torch.empty_like(x), torch.empty_like(x)
+    lse_named, lse_gen = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    need = L.rowop_workspace_bytes(L.SOFTMAX_FWD, n, rows, L.F32)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    L.softmax_fwd(x.data_ptr(), y_named.data_ptr(), lse_named.data_ptr(), n, rows, n, L.F32, L.F32, ws.data_ptr(), need, stream)
+    L.rowreduce_generic(G.softmax(n, rows).desc(), [x.data_ptr()], [y_gen.data_ptr(), lse_gen.data_ptr()], stream)
+    assert (y_named - y_gen).abs().max().item() <= 1e-6
+    assert (lse_named - lse_gen).abs().max().item() <= 1e-5
+    need = L.rowop_workspace_bytes(L.LAYERNORM_FWD, n, rows, L.F32)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    L.layernorm_fwd(x.data_ptr(), w.data_ptr(), b.data_ptr(), y_named.data_ptr(), 0, 0, 1e-5, n, rows, n, L.F32,
+                    ws.data_ptr(), need, stream)
+    L.rowreduce_generic(G.layernorm(n, rows).desc(), [x.data_ptr(), w.data_ptr(), b.data_ptr()], [y_gen.data_ptr()], stream)
+    assert (y_named - y_gen).abs().max().item() <= 2e-5 * y_named.abs().max().item()
+
+
+def test_strided_rows_statistics_and_saved_inputs(pkg, cuda, oracle):
+    """Rows at a pitch that is not a multiple of four (scalar accesses), four statistics in one sweep, and a
+    per-row input: the softmax pullback from x and the saved log-sum-exp, y recomputed as exp(x - lse)."""
+    G = pkg.groups
+    n, rows, ld = 77, 50, 83
+    x = np.zeros((rows, ld), np.float32)
+    x[:, :n] = 1.0 + 0.02 * oracle.normal((rows, n), 61)
+    g = G.Group(n, rows)
+    xi = g.load(g.input("full", "Float32", ld=ld))
+    for kind in ("max", "min", "sum", "prod"):
+        g.output_stat(g.fold(kind, xi))
+    got, want = run_both(pkg, cuda, oracle, g, [x])
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])
+    assert np.abs(got[2] - want[2]).max() <= 1e-5 * n
+    assert np.abs(got[3] / want[3] - 1).max() <= 1e-5
+
+    n, rows = 1000, 41
+    xs = oracle.normal((rows, n), 62) * 2
+    lse = oracle.softmax_fwd_f64(xs)[1].astype(np.float32)
+    dy = oracle.normal((rows, n), 63)
+    g = G.Group(n, rows)
+    xi, li, di = g.load(g.input()), g.load(g.input("per_row")), g.load(g.input())
+    y = g.exp(g.sub(xi, li))
+    t = g.mul(di, y)
+    s = g.fold("sum", t)
+    g.output(g.sub(t, g.mul(y, g.stat(s))))
+    got, want = run_both(pkg, cuda, oracle, g, [xs, lse, dy])
+    agree(oracle, got[0], want[0], n, "pullback from saved lse")
+    want64 = oracle.softmax_bwd_f64(oracle.softmax_fwd_f64(xs)[0], dy)
+    assert np.abs(got[0] - want64).max() <= 2e-5 * np.abs(want64).max()
+
+
+def test_empty_and_refused(pkg, cuda):
+    L, G = pkg.lib, pkg.groups
+    L.rowreduce_generic(G.softmax(0, 5).desc(), [0], [0, 0])       # nothing to do, nothing touched
+    L.rowreduce_generic(G.softmax(5, 0).desc(), [0], [0, 0])
+    with pytest.raises(L.TB200Error) as e:
+        L.rowreduce_generic(G.softmax(8, 2).desc(), [0], [0, 0])
+    assert e.value.status == -1
