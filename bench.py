@@ -401,6 +401,25 @@ def run_also(torch, dist, pkg, world, rank):
         hbm, _ = measured_peaks()
         out["deltanet_fwd_B4_H16_S8192"] = {"ms": round(dms, 4), "algorithmic_GB/s": round(dbytes / dms / 1e6, 1),
                                             "frac_of_measured_hbm_peak": round(dbytes / dms / 1e6 / hbm, 4)}
+        del od
+        # the generic term-interpreter kernel on the headline shape: softmax and RMSNorm spelled as groups
+        G = pkg.groups
+        n, rows = 4096, 65536
+        xg = torch.randn(rows, n, device="cuda")
+        yg, lg = torch.empty_like(xg), torch.empty(rows, device="cuda")
+        sm = G.softmax(n, rows)
+        smd = sm.desc()
+        gms = clock(lambda: L.rowreduce_generic(smd, [xg.data_ptr()], [yg.data_ptr(), lg.data_ptr()], stream), 5)
+        out["generic_softmax_f32_4096x65536"] = {"ms": round(gms, 4), "algorithmic_GB/s": round(sm.bytes() / gms / 1e6, 1),
+                                                 "frac_of_measured_hbm_peak": round(sm.bytes() / gms / 1e6 / hbm, 4)}
+        xb, wb = xg.bfloat16(), torch.randn(n, device="cuda").bfloat16()
+        yb = torch.empty_like(xb)
+        rn = G.rmsnorm(n, rows, "BFloat16")
+        rnd = rn.desc()
+        gms = clock(lambda: L.rowreduce_generic(rnd, [xb.data_ptr(), wb.data_ptr()], [yb.data_ptr()], stream), 5)
+        out["generic_rmsnorm_bf16_4096x65536"] = {"ms": round(gms, 4), "algorithmic_GB/s": round(rn.bytes() / gms / 1e6, 1),
+                                                  "frac_of_measured_hbm_peak": round(rn.bytes() / gms / 1e6 / hbm, 4)}
+        del xg, yg, xb, yb
         # its pullback at the same size (forward recomputed inside)
         gq, gk, gv = (torch.empty(Hn, T, 128, device="cuda", dtype=torch.bfloat16) for _ in range(3))
         ga, gb = torch.empty(Hn, T, device="cuda"), torch.empty(Hn, T, device="cuda")

@@ -425,3 +425,83 @@ class B200Kernels:
         launch = RowLaunch(b, self.eps, ws, need)
         schedule = "split" if n > 16384 else "resident"
         return launch, f"B200 {b.template}, {rows} rows of {n} {first.eltype}, {schedule}"
+
+
+# ---------------------------------------------------------------- generic groups ----
+#
+# The second door of the reference's plugin API (src/Compiler/Implement/Implement.jl:108-175): an
+# `Implementation` is asked for `claims` on a `GroupView`, states each claim's cost with `estimate`, and turns
+# the chosen one into a launch with `build_claim(impl, claim, target, g, buffers, resources)`, where
+# `buffers[v]` is the device vector of value `v`.  `B200Generator` is that protocol over `groups.Group`.
+
+@dataclass(frozen=True)
+class RowClaim:
+    """What the generator offers for a group: one launch, rows spread over groups of `threads` threads."""
+    threads: int
+    phases: int
+
+
+class GroupLaunch:
+    """Callable with no arguments; enqueues on the current stream; `repoint` swaps one buffer."""
+
+    def __init__(self, group, inputs, outputs):
+        self.group, self.desc = group, group.desc()
+        self.inputs, self.outputs = list(inputs), list(outputs)   # (value id, buffer)
+
+    def repoints(self) -> bool:
+        return True
+
+    def repoint(self, value: int, buffer) -> "GroupLaunch":
+        self.inputs = [(v, buffer if v == value else b) for v, b in self.inputs]
+        self.outputs = [(v, buffer if v == value else b) for v, b in self.outputs]
+        return self
+
+    def __call__(self):
+        address = lambda b: b.data_ptr() if hasattr(b, "data_ptr") else int(b)  # noqa: E731
+        lib.rowreduce_generic(self.desc, [address(b) for _, b in self.inputs], [address(b) for _, b in self.outputs],
+                              _torch_stream())
+
+
+class B200Generator:
+    """`<: Implementation` for row groups: claims every group whose descriptor the library accepts."""
+
+    def claims(self, target: Target, group):
+        try:
+            desc = group.desc()
+        except ValueError:
+            return ()                                  # too large for one descriptor: decline
+        if lib.rowreduce_generic_check(desc) != 0:
+            return ()
+        threads = 8
+        while threads < 256 and threads * 4 < group.n:
+            threads *= 2
+        phases = 1 + max((phase for _, _, phase in group.folds), default=-1) + 1
+        return (RowClaim(threads, phases),)
+
+    def variants(self, target: Target, group, claim):
+        return ()                                      # one schedule: nothing to search
+
+    def estimate(self, claim: RowClaim, target: Target, group):
+        return [Work(bytes=group.bytes(), blocks=group.rows, launches=1)]
+
+    def in_place(self, claim: RowClaim) -> bool:
+        """Every element an output needs is read before that output's sweep starts only for folds; the output
+        sweep re-reads its inputs, so an output may alias an input only when nothing else reads that input --
+        the generator does not promise it."""
+        return False
+
+    def build_claim(self, claim: RowClaim, target: Target, group, buffers, resources=None):
+        """`buffers`: {"inputs": [...], "outputs": [...]} device buffers in the group's order, or a flat
+        {value id: buffer} with inputs numbered first."""
+        if not self.claims(target, group):
+            raise ValueError("B200Generator does not compute this group")
+        if "inputs" in buffers:
+            ins, outs = list(enumerate(buffers["inputs"])), list(enumerate(buffers["outputs"], len(buffers["inputs"])))
+        else:
+            k = len(group.inputs)
+            ins = [(v, buffers[v]) for v in range(k)]
+            outs = [(v, buffers[v]) for v in range(k, k + len(group.outputs))]
+        if len(ins) != len(group.inputs) or len(outs) != len(group.outputs):
+            raise ValueError("build_claim needs one buffer per input and per output")
+        return GroupLaunch(group, ins, outs), (f"B200 generic rows, {group.rows} rows of {group.n}, {len(group.terms)} terms, "
+                                                f"{len(group.folds)} folds in {claim.phases} sweeps")

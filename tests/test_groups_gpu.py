@@ -141,3 +141,22 @@ def test_empty_and_refused(pkg, cuda):
     with pytest.raises(L.TB200Error) as e:
         L.rowreduce_generic(G.softmax(8, 2).desc(), [0], [0, 0])
     assert e.value.status == -1
+
+
+def test_through_the_generator(pkg, cuda, oracle):
+    """claims -> build_claim -> launch() -> repoint -> launch(), the way Tempest's cover drives an Implementation."""
+    torch, I, G = cuda, pkg.implement, pkg.groups
+    n, rows = 515, 64
+    g = G.rmsnorm(n, rows)
+    gen, target = I.B200Generator(), I.Target()
+    (claim,) = gen.claims(target, g)
+    x, w = torch.randn(rows, n, device="cuda"), torch.randn(n, device="cuda")
+    y, y2 = torch.zeros_like(x), torch.zeros_like(x)
+    launch, _ = gen.build_claim(claim, target, g, {0: x, 1: w, 2: y})
+    launch()
+    launch.repoint(2, y2)()
+    torch.cuda.synchronize()
+    want = np.zeros((rows, n), np.float32)
+    oracle.group_eval(g.desc(), [x.cpu().numpy(), w.cpu().numpy()], [want])
+    assert np.abs(y.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
+    assert torch.equal(y, y2)

@@ -88,3 +88,28 @@ def test_product_and_attention_templates(I):
     assert not lib.supports(t, I.Binding("attention_causal", dict(e, n=2048), arrays))
     strided = dict(arrays, q=I.Strided("BFloat16", 0, (128, 32, 4096, 8), (1, 256, 8192, 1 << 25), None, 0))
     assert not lib.supports(t, I.Binding("attention_causal", e, strided))
+
+
+def test_generator_claims_groups(pkg):
+    """The `Implementation` door: claims, estimate and the descriptor checks, without a device."""
+    I, G = pkg.implement, pkg.groups
+    gen, t = I.B200Generator(), I.Target()
+    g = G.layernorm(4096, 65536, "BFloat16", two_pass=True)
+    (claim,) = gen.claims(t, g)
+    assert claim.threads == 256 and claim.phases == 3
+    (w,) = gen.estimate(claim, t, g)
+    assert w.bytes == 2 * 4096 * 65536 * 2 + 2 * 4096 * 2 and w.launches == 1
+    assert gen.claims(t, G.softmax(20, 3))[0].threads == 8
+    big = G.Group(8, 1)
+    x = big.load(big.input())
+    for _ in range(60):
+        x = big.neg(x)
+    big.output(x)
+    assert gen.claims(t, big) == ()
+    import pytest
+    with pytest.raises(ValueError):
+        gen.build_claim(None, t, big, {"inputs": [0], "outputs": [0]})
+    launch, text = gen.build_claim(claim, t, g, {0: 16, 1: 32, 2: 48, 3: 64})
+    assert launch.repoints() and "3 sweeps" in text
+    launch.repoint(3, 128)
+    assert launch.outputs == [(3, 128)] and launch.inputs[0] == (0, 16)
