@@ -412,6 +412,13 @@ def run_also(torch, dist, pkg, world, rank):
         gms = clock(lambda: L.rowreduce_generic(smd, [xg.data_ptr()], [yg.data_ptr(), lg.data_ptr()], stream), 5)
         out["generic_softmax_f32_4096x65536"] = {"ms": round(gms, 4), "algorithmic_GB/s": round(sm.bytes() / gms / 1e6, 1),
                                                  "frac_of_measured_hbm_peak": round(sm.bytes() / gms / 1e6 / hbm, 4)}
+        for name, group, ins, outs in (
+                ("compiled_softmax_f32", sm, [xg.data_ptr()], [yg.data_ptr(), lg.data_ptr()]),
+                ("compiled_log_softmax_f32", G.log_softmax(n, rows), [xg.data_ptr()], [yg.data_ptr()])):
+            gd = group.desc()
+            gms = clock(lambda: L.rowreduce_compiled(gd, ins, outs, stream), 10)
+            out[name + "_4096x65536"] = {"ms": round(gms, 4), "algorithmic_GB/s": round(group.bytes() / gms / 1e6, 1),
+                                         "frac_of_measured_hbm_peak": round(group.bytes() / gms / 1e6 / hbm, 4)}
         xb, wb = xg.bfloat16(), torch.randn(n, device="cuda").bfloat16()
         yb = torch.empty_like(xb)
         rn = G.rmsnorm(n, rows, "BFloat16")
@@ -419,6 +426,15 @@ def run_also(torch, dist, pkg, world, rank):
         gms = clock(lambda: L.rowreduce_generic(rnd, [xb.data_ptr(), wb.data_ptr()], [yb.data_ptr()], stream), 5)
         out["generic_rmsnorm_bf16_4096x65536"] = {"ms": round(gms, 4), "algorithmic_GB/s": round(rn.bytes() / gms / 1e6, 1),
                                                   "frac_of_measured_hbm_peak": round(rn.bytes() / gms / 1e6 / hbm, 4)}
+        gms = clock(lambda: L.rowreduce_compiled(rnd, [xb.data_ptr(), wb.data_ptr()], [yb.data_ptr()], stream), 10)
+        out["compiled_rmsnorm_bf16_4096x65536"] = {"ms": round(gms, 4), "algorithmic_GB/s": round(rn.bytes() / gms / 1e6, 1),
+                                                   "frac_of_measured_hbm_peak": round(rn.bytes() / gms / 1e6 / hbm, 4)}
+        bb = torch.randn(n, device="cuda").bfloat16()
+        ln = G.layernorm(n, rows, "BFloat16")
+        lnd = ln.desc()
+        gms = clock(lambda: L.rowreduce_compiled(lnd, [xb.data_ptr(), wb.data_ptr(), bb.data_ptr()], [yb.data_ptr()], stream), 10)
+        out["compiled_layernorm_bf16_4096x65536"] = {"ms": round(gms, 4), "algorithmic_GB/s": round(ln.bytes() / gms / 1e6, 1),
+                                                     "frac_of_measured_hbm_peak": round(ln.bytes() / gms / 1e6 / hbm, 4)}
         del xg, yg, xb, yb
         # its pullback at the same size (forward recomputed inside)
         gq, gk, gv = (torch.empty(Hn, T, 128, device="cuda", dtype=torch.bfloat16) for _ in range(3))

@@ -344,6 +344,30 @@ int tb200_rowreduce_generic_check(const tb200_group_desc *desc);
 int tb200_rowreduce_generic(const tb200_group_desc *desc, const void *const *inputs, void *const *outputs,
                             void *stream);
 
+/* The same groups compiled: the descriptor is turned into CUDA source with its
+ * extents, element types, alignment and schedule as constants, compiled for
+ * sm_100a by NVRTC (loaded with dlopen on first use) and cached by descriptor --
+ * the counterpart of the kernel the reference's generator emits and caches per
+ * group (ext/cuTileExt/build.jl:138-286, ext/cuTileExt/cache.jl:59).  Rows that
+ * fit in registers are read once and stay resident through every phase.
+ * TB200_ERR_UNSUPPORTED when NVRTC cannot be loaded or the source does not
+ * compile (tb200_rowreduce_compile_log holds the compiler's words); the
+ * interpreter above then remains.
+ *
+ * tb200_rowreduce_compile compiles ahead of time and needs no device: bit i of
+ * vector_inputs / vector_outputs promises that input / output i is aligned for
+ * 128-bit accesses (base address and row pitch).  tb200_rowreduce_compiled works
+ * those bits out from the addresses it is given, compiles on first use (so a
+ * first call belongs outside a stream capture) and launches. */
+int tb200_rowreduce_compile(const tb200_group_desc *desc, unsigned vector_inputs, unsigned vector_outputs);
+int tb200_rowreduce_compiled(const tb200_group_desc *desc, const void *const *inputs, void *const *outputs,
+                             void *stream);
+/* The generated source (for inspection): returns the bytes needed including the
+ * terminator, 0 for a descriptor that is refused; fills `buffer` when given. */
+size_t tb200_rowreduce_source(const tb200_group_desc *desc, unsigned vector_inputs, unsigned vector_outputs,
+                              char *buffer, size_t buffer_bytes);
+const char *tb200_rowreduce_compile_log(void);
+
 /* ---- pointwise maps and folds over other axes -------------------------------
  * These replace the generated `:pointwise` kernels (ext/cuTileExt/build.jl:3-10)
  * and the full / partial folds with their merge launches

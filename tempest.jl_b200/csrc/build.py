@@ -13,8 +13,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 PACKAGE = os.path.dirname(HERE)
 LIB = os.path.join(PACKAGE, "libtempest_b200.so")
-SOURCES = ["abi.cu", "rowreduce.cu", "gemm.cu", "pointwise.cu", "attention_fwd.cu", "attention_bwd.cu", "attention_simt.cu", "deltanet.cu", "generic.cu"]
-HEADERS = ["common.cuh", "sm100.cuh", "attention_simt.cuh", os.path.join("..", "..", "include", "tempest_b200.h")]
+SOURCES = ["abi.cu", "rowreduce.cu", "gemm.cu", "pointwise.cu", "attention_fwd.cu", "attention_bwd.cu", "attention_simt.cu", "deltanet.cu", "generic.cu", "rowgen.cu"]
+HEADERS = ["common.cuh", "sm100.cuh", "attention_simt.cuh", "generic.cuh", os.path.join("..", "..", "include", "tempest_b200.h")]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
@@ -59,7 +59,7 @@ def build(force=False, verbose=False):
     if failed:
         raise RuntimeError("build of libtempest_b200.so failed")
     if force or procs or stale(LIB, objects):
-        cmd = [nvcc(), "-shared", "-o", LIB] + objects + ["-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a"]
+        cmd = [nvcc(), "-shared", "-o", LIB] + objects + ["-cudart", "static", "-ldl", "-gencode", "arch=compute_100a,code=sm_100a"]
         subprocess.run(cmd, check=True)
     return LIB
 

@@ -17,6 +17,7 @@
 // working set is a few rows -- so HBM traffic stays one read per input and one write per output.  The
 // interpreter costs instructions, not bytes: expect a fraction of the named kernels' rate.
 #include "common.cuh"
+#include "generic.cuh"
 
 namespace tb200 {
 namespace {
@@ -386,6 +387,16 @@ int plan_generic(const tb200_group_desc *d, GenericArgs *A) {
 }
 
 }  // namespace
+
+int group_phases(const tb200_group_desc *d, unsigned long long *need, int *phases) {
+    GenericArgs A{};
+    const int st = plan_generic(d, &A);
+    if (st) return st;
+    for (int p = 0; p <= A.phases; p++) need[p] = A.need[p];
+    *phases = A.phases;
+    return TB200_OK;
+}
+
 }  // namespace tb200
 
 using namespace tb200;

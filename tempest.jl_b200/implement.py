@@ -76,6 +76,7 @@ class Work:
     flops: float = 0.0
     blocks: int = 0
     launches: int = 1
+    applied: int = 0     # function applications per element the launch pays for beyond its bytes
 
 
 @dataclass
@@ -436,16 +437,18 @@ class B200Kernels:
 
 @dataclass(frozen=True)
 class RowClaim:
-    """What the generator offers for a group: one launch, rows spread over groups of `threads` threads."""
+    """What the generator offers for a group: one launch, rows spread over groups of `threads` threads;
+    `compiled` = the group's own NVRTC-compiled kernel instead of the term interpreter."""
     threads: int
     phases: int
+    compiled: bool = False
 
 
 class GroupLaunch:
     """Callable with no arguments; enqueues on the current stream; `repoint` swaps one buffer."""
 
-    def __init__(self, group, inputs, outputs):
-        self.group, self.desc = group, group.desc()
+    def __init__(self, group, inputs, outputs, compiled=False):
+        self.group, self.desc, self.compiled = group, group.desc(), compiled
         self.inputs, self.outputs = list(inputs), list(outputs)   # (value id, buffer)
 
     def repoints(self) -> bool:
@@ -458,8 +461,8 @@ class GroupLaunch:
 
     def __call__(self):
         address = lambda b: b.data_ptr() if hasattr(b, "data_ptr") else int(b)  # noqa: E731
-        lib.rowreduce_generic(self.desc, [address(b) for _, b in self.inputs], [address(b) for _, b in self.outputs],
-                              _torch_stream())
+        run = lib.rowreduce_compiled if self.compiled else lib.rowreduce_generic
+        run(self.desc, [address(b) for _, b in self.inputs], [address(b) for _, b in self.outputs], _torch_stream())
 
 
 class B200Generator:
@@ -476,13 +479,19 @@ class B200Generator:
         while threads < 256 and threads * 4 < group.n:
             threads *= 2
         phases = 1 + max((phase for _, _, phase in group.folds), default=-1) + 1
-        return (RowClaim(threads, phases),)
+        claims = [RowClaim(threads, phases)]
+        if lib.rowreduce_compile(desc) == 0:           # NVRTC at hand and the generated source compiles
+            claims.insert(0, RowClaim(threads, phases, compiled=True))
+        return tuple(claims)
 
     def variants(self, target: Target, group, claim):
-        return ()                                      # one schedule: nothing to search
+        return ()                                      # one schedule per claim: nothing further to search
 
     def estimate(self, claim: RowClaim, target: Target, group):
-        return [Work(bytes=group.bytes(), blocks=group.rows, launches=1)]
+        """One launch moving the group's bytes once; the interpreter also pays for every term of every element
+        (`applied` in the reference's Work, src/Compiler/Implement/Implement.jl:61-82)."""
+        applied = 0 if claim.compiled else len(group.terms) * claim.phases
+        return [Work(bytes=group.bytes(), blocks=group.rows, launches=1, applied=applied)]
 
     def in_place(self, claim: RowClaim) -> bool:
         """Every element an output needs is read before that output's sweep starts only for folds; the output
@@ -503,5 +512,10 @@ class B200Generator:
             outs = [(v, buffers[v]) for v in range(k, k + len(group.outputs))]
         if len(ins) != len(group.inputs) or len(outs) != len(group.outputs):
             raise ValueError("build_claim needs one buffer per input and per output")
-        return GroupLaunch(group, ins, outs), (f"B200 generic rows, {group.rows} rows of {group.n}, {len(group.terms)} terms, "
+        if claim.compiled:
+            status = lib.rowreduce_compile(group.desc())
+            if status != 0:
+                raise ValueError(f"the group's kernel did not compile: {lib.rowreduce_compile_log()[:400]}")
+        kind = "compiled" if claim.compiled else "interpreted"
+        return GroupLaunch(group, ins, outs, claim.compiled), (f"B200 {kind} rows, {group.rows} rows of {group.n}, {len(group.terms)} terms, "
                                                 f"{len(group.folds)} folds in {claim.phases} sweeps")

@@ -98,6 +98,10 @@ SIGNATURES = {
     "tb200_deltanet_fwd": (_i, [ctypes.POINTER(DeltanetDesc), _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "tb200_rowreduce_generic_check": (_i, [ctypes.POINTER(GroupDesc)]),
     "tb200_rowreduce_generic": (_i, [ctypes.POINTER(GroupDesc), ctypes.POINTER(_p), ctypes.POINTER(_p), _p]),
+    "tb200_rowreduce_compile": (_i, [ctypes.POINTER(GroupDesc), ctypes.c_uint, ctypes.c_uint]),
+    "tb200_rowreduce_compiled": (_i, [ctypes.POINTER(GroupDesc), ctypes.POINTER(_p), ctypes.POINTER(_p), _p]),
+    "tb200_rowreduce_source": (_sz, [ctypes.POINTER(GroupDesc), ctypes.c_uint, ctypes.c_uint, ctypes.c_char_p, _sz]),
+    "tb200_rowreduce_compile_log": (ctypes.c_char_p, []),
     "tb200_deltanet_bwd_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_bwd": (_i, [ctypes.POINTER(DeltanetDesc)] + [_p] * 12 + [_sz, _p]),
     "tb200_workspace_clear": (_i, [_p, _sz, _p]),
@@ -328,3 +332,28 @@ def rowreduce_generic(desc, inputs, outputs, stream=0):
     ins = (_p * max(len(inputs), 1))(*inputs)
     outs = (_p * max(len(outputs), 1))(*outputs)
     check("tb200_rowreduce_generic", load().tb200_rowreduce_generic(ctypes.byref(desc), ins, outs, stream or None))
+
+
+def rowreduce_compile(desc, vector_inputs=0xff, vector_outputs=0xff):
+    """Compiles (and caches) the group's own kernel; needs NVRTC, not a device.  Returns the status."""
+    return load().tb200_rowreduce_compile(ctypes.byref(desc), vector_inputs, vector_outputs)
+
+
+def rowreduce_source(desc, vector_inputs=0xff, vector_outputs=0xff):
+    need = load().tb200_rowreduce_source(ctypes.byref(desc), vector_inputs, vector_outputs, None, 0)
+    if not need:
+        return ""
+    buf = ctypes.create_string_buffer(need)
+    load().tb200_rowreduce_source(ctypes.byref(desc), vector_inputs, vector_outputs, buf, need)
+    return buf.value.decode()
+
+
+def rowreduce_compile_log():
+    return (load().tb200_rowreduce_compile_log() or b"").decode()
+
+
+def rowreduce_compiled(desc, inputs, outputs, stream=0):
+    """The compiled form of `rowreduce_generic`: same arguments, the group's own kernel."""
+    ins = (_p * max(len(inputs), 1))(*inputs)
+    outs = (_p * max(len(outputs), 1))(*outputs)
+    check("tb200_rowreduce_compiled", load().tb200_rowreduce_compiled(ctypes.byref(desc), ins, outs, stream or None))

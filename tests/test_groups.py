@@ -99,3 +99,24 @@ def test_descriptor_checks(pkg):
     g.output(x)
     with pytest.raises(ValueError):
         g.desc()
+
+
+def test_generated_kernels_compile(pkg):
+    """The generator's source for every spelling and schedule compiles for sm_100a (NVRTC needs no device):
+    resident and streamed rows, whole and ragged chunks, vector and scalar accesses, both element types."""
+    G, L = pkg.groups, pkg.lib
+    if L.rowreduce_compile(G.softmax(64, 4).desc()) == -7 and "nvrtc" not in L.rowreduce_compile_log().lower():
+        pytest.skip("NVRTC cannot be loaded here")
+    for n in (5, 300, 4096, 70001):
+        for eltype in ("Float32", "BFloat16"):
+            for group in (G.softmax(n, 7, eltype), G.log_softmax(n, 7, eltype), G.layernorm(n, 7, eltype),
+                          G.layernorm(n, 7, eltype, two_pass=True), G.rmsnorm(n, 7, eltype),
+                          G.softmax_pullback(n, 7, eltype), G.row_extrema(n, 7, eltype)):
+                for vectors in (0xff, 0):
+                    assert L.rowreduce_compile(group.desc(), vectors, vectors) == 0, (n, eltype, L.rowreduce_compile_log())
+    source = L.rowreduce_source(G.layernorm(4096, 65536).desc())
+    assert "constexpr int N = 4096, V = 4, TPR = 256, K = 4" in source and "float c0[K][V];" in source   # resident
+    assert "float c0[V];" in L.rowreduce_source(G.layernorm(70001, 3).desc())                             # streamed
+    bad = G.softmax(16, 2).desc()
+    bad.terms[0].op = 99
+    assert L.rowreduce_compile(bad) == -7 and L.rowreduce_source(bad) == ""

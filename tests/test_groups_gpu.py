@@ -9,7 +9,7 @@ from helpers import RTOL_F32
 pytestmark = pytest.mark.gpu
 
 
-def run_both(pkg, torch, oracle, group, inputs, wide=False):
+def run_both(pkg, torch, oracle, group, inputs, wide=False, entry="generic"):
     """Returns (gpu outputs, oracle outputs) as numpy arrays (uint16 for BFloat16)."""
     L = pkg.lib
     d = group.desc()
@@ -22,8 +22,8 @@ def run_both(pkg, torch, oracle, group, inputs, wide=False):
         host = np.zeros(shape, np.float32 if dtype == 0 else np.uint16)
         ref_out.append(host)
         dev_out.append(torch.zeros(shape, device="cuda", dtype=torch.float32 if dtype == 0 else torch.int16))
-    L.rowreduce_generic(d, [t.data_ptr() for t in dev_in], [t.data_ptr() for t in dev_out],
-                        torch.cuda.current_stream().cuda_stream)
+    run = L.rowreduce_generic if entry == "generic" else L.rowreduce_compiled
+    run(d, [t.data_ptr() for t in dev_in], [t.data_ptr() for t in dev_out], torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     oracle.group_eval(d, [np.ascontiguousarray(a) for a in inputs], ref_out, threads=8)
     got = [t.cpu().numpy().view(np.uint16) if t.dtype == torch.int16 else t.cpu().numpy() for t in dev_out]
@@ -57,9 +57,13 @@ def agree(oracle, got, want, n, what="", wide=None):
 SHAPES = [(256, 700), (9000, 40), (100, 3000), (512, 300), (1, 5), (3, 7), (4096, 64), (70001, 3), (33, 1000)]
 
 
+ENTRIES = ["generic", "compiled"]   # the term interpreter; the group's own NVRTC-compiled kernel
+
+
+@pytest.mark.parametrize("entry", ENTRIES)
 @pytest.mark.parametrize("eltype", ["Float32", "BFloat16"])
 @pytest.mark.parametrize("n,rows", SHAPES)
-def test_programs_as_groups(pkg, cuda, oracle, n, rows, eltype):
+def test_programs_as_groups(pkg, cuda, oracle, n, rows, eltype, entry):
     G = pkg.groups
     cast = (lambda a: a) if eltype == "Float32" else oracle.to_bf16
     x = cast((oracle.normal((rows, n), n + rows) * 2).astype(np.float32))
@@ -74,9 +78,9 @@ def test_programs_as_groups(pkg, cuda, oracle, n, rows, eltype):
         ("rmsnorm", G.rmsnorm(n, rows, eltype), [x, w]),
         ("softmax pullback", G.softmax_pullback(n, rows, eltype), [x, g2]),
     ):
-        got, want, wide = run_both(pkg, cuda, oracle, group, inputs, wide=True)
+        got, want, wide = run_both(pkg, cuda, oracle, group, inputs, wide=True, entry=entry)
         for a, r, w64 in zip(got, want, wide):
-            agree(oracle, a, r, n, f"{name} {n}x{rows} {eltype}", w64)
+            agree(oracle, a, r, n, f"{name} {n}x{rows} {eltype} {entry}", w64)
 
 
 def test_against_the_named_kernels(pkg, cuda, oracle):
@@ -91,18 +95,23 @@ def test_against_the_named_kernels(pkg, cuda, oracle):
     need = L.rowop_workspace_bytes(L.SOFTMAX_FWD, n, rows, L.F32)
     ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
     L.softmax_fwd(x.data_ptr(), y_named.data_ptr(), lse_named.data_ptr(), n, rows, n, L.F32, L.F32, ws.data_ptr(), need, stream)
-    L.rowreduce_generic(G.softmax(n, rows).desc(), [x.data_ptr()], [y_gen.data_ptr(), lse_gen.data_ptr()], stream)
-    assert (y_named - y_gen).abs().max().item() <= 1e-6
-    assert (lse_named - lse_gen).abs().max().item() <= 1e-5
+    for run in (L.rowreduce_generic, L.rowreduce_compiled):
+        y_gen.zero_()
+        run(G.softmax(n, rows).desc(), [x.data_ptr()], [y_gen.data_ptr(), lse_gen.data_ptr()], stream)
+        assert (y_named - y_gen).abs().max().item() <= 1e-6
+        assert (lse_named - lse_gen).abs().max().item() <= 1e-5
     need = L.rowop_workspace_bytes(L.LAYERNORM_FWD, n, rows, L.F32)
     ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
     L.layernorm_fwd(x.data_ptr(), w.data_ptr(), b.data_ptr(), y_named.data_ptr(), 0, 0, 1e-5, n, rows, n, L.F32,
                     ws.data_ptr(), need, stream)
-    L.rowreduce_generic(G.layernorm(n, rows).desc(), [x.data_ptr(), w.data_ptr(), b.data_ptr()], [y_gen.data_ptr()], stream)
-    assert (y_named - y_gen).abs().max().item() <= 2e-5 * y_named.abs().max().item()
+    for run in (L.rowreduce_generic, L.rowreduce_compiled):
+        y_gen.zero_()
+        run(G.layernorm(n, rows).desc(), [x.data_ptr(), w.data_ptr(), b.data_ptr()], [y_gen.data_ptr()], stream)
+        assert (y_named - y_gen).abs().max().item() <= 2e-5 * y_named.abs().max().item()
 
 
-def test_strided_rows_statistics_and_saved_inputs(pkg, cuda, oracle):
+@pytest.mark.parametrize("entry", ENTRIES)
+def test_strided_rows_statistics_and_saved_inputs(pkg, cuda, oracle, entry):
     """Rows at a pitch that is not a multiple of four (scalar accesses), four statistics in one sweep, and a
     per-row input: the softmax pullback from x and the saved log-sum-exp, y recomputed as exp(x - lse)."""
     G = pkg.groups
@@ -113,7 +122,7 @@ def test_strided_rows_statistics_and_saved_inputs(pkg, cuda, oracle):
     xi = g.load(g.input("full", "Float32", ld=ld))
     for kind in ("max", "min", "sum", "prod"):
         g.output_stat(g.fold(kind, xi))
-    got, want = run_both(pkg, cuda, oracle, g, [x])
+    got, want = run_both(pkg, cuda, oracle, g, [x], entry=entry)
     assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])
     assert np.abs(got[2] - want[2]).max() <= 1e-5 * n
     assert np.abs(got[3] / want[3] - 1).max() <= 1e-5
@@ -128,7 +137,7 @@ def test_strided_rows_statistics_and_saved_inputs(pkg, cuda, oracle):
     t = g.mul(di, y)
     s = g.fold("sum", t)
     g.output(g.sub(t, g.mul(y, g.stat(s))))
-    got, want = run_both(pkg, cuda, oracle, g, [xs, lse, dy])
+    got, want = run_both(pkg, cuda, oracle, g, [xs, lse, dy], entry=entry)
     agree(oracle, got[0], want[0], n, "pullback from saved lse")
     want64 = oracle.softmax_bwd_f64(oracle.softmax_fwd_f64(xs)[0], dy)
     assert np.abs(got[0] - want64).max() <= 2e-5 * np.abs(want64).max()
@@ -138,9 +147,11 @@ def test_empty_and_refused(pkg, cuda):
     L, G = pkg.lib, pkg.groups
     L.rowreduce_generic(G.softmax(0, 5).desc(), [0], [0, 0])       # nothing to do, nothing touched
     L.rowreduce_generic(G.softmax(5, 0).desc(), [0], [0, 0])
-    with pytest.raises(L.TB200Error) as e:
-        L.rowreduce_generic(G.softmax(8, 2).desc(), [0], [0, 0])
-    assert e.value.status == -1
+    for run in (L.rowreduce_generic, L.rowreduce_compiled):
+        run(G.softmax(0, 5).desc(), [0], [0, 0])
+        with pytest.raises(L.TB200Error) as e:
+            run(G.softmax(8, 2).desc(), [0], [0, 0])
+        assert e.value.status == -1
 
 
 def test_through_the_generator(pkg, cuda, oracle):
@@ -149,14 +160,17 @@ def test_through_the_generator(pkg, cuda, oracle):
     n, rows = 515, 64
     g = G.rmsnorm(n, rows)
     gen, target = I.B200Generator(), I.Target()
-    (claim,) = gen.claims(target, g)
+    claims = gen.claims(target, g)
+    assert [c.compiled for c in claims] == [True, False]
     x, w = torch.randn(rows, n, device="cuda"), torch.randn(n, device="cuda")
-    y, y2 = torch.zeros_like(x), torch.zeros_like(x)
-    launch, _ = gen.build_claim(claim, target, g, {0: x, 1: w, 2: y})
-    launch()
-    launch.repoint(2, y2)()
-    torch.cuda.synchronize()
     want = np.zeros((rows, n), np.float32)
     oracle.group_eval(g.desc(), [x.cpu().numpy(), w.cpu().numpy()], [want])
-    assert np.abs(y.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
-    assert torch.equal(y, y2)
+    for claim in claims:
+        y, y2 = torch.zeros_like(x), torch.zeros_like(x)
+        launch, text = gen.build_claim(claim, target, g, {0: x, 1: w, 2: y})
+        assert ("compiled" in text) == claim.compiled
+        launch()
+        launch.repoint(2, y2)()
+        torch.cuda.synchronize()
+        assert np.abs(y.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
+        assert torch.equal(y, y2)

@@ -95,11 +95,13 @@ def test_generator_claims_groups(pkg):
     I, G = pkg.implement, pkg.groups
     gen, t = I.B200Generator(), I.Target()
     g = G.layernorm(4096, 65536, "BFloat16", two_pass=True)
-    (claim,) = gen.claims(t, g)
-    assert claim.threads == 256 and claim.phases == 3
+    claims = gen.claims(t, g)
+    claim = claims[-1]                                   # the interpreter is always offered, last
+    assert claim.threads == 256 and claim.phases == 3 and not claim.compiled
+    assert all(c.compiled for c in claims[:-1])         # the compiled kernel first, when NVRTC is at hand
     (w,) = gen.estimate(claim, t, g)
     assert w.bytes == 2 * 4096 * 65536 * 2 + 2 * 4096 * 2 and w.launches == 1
-    assert gen.claims(t, G.softmax(20, 3))[0].threads == 8
+    assert gen.claims(t, G.softmax(20, 3))[-1].threads == 8
     big = G.Group(8, 1)
     x = big.load(big.input())
     for _ in range(60):
