@@ -129,7 +129,9 @@ std::string term_expr(const tb200_group_desc &d, int k, const std::string &chunk
         case TB200_T_MAX: return "fmaxf(" + t(T.a) + ", " + t(T.b) + ")";
         case TB200_T_MIN: return "fminf(" + t(T.a) + ", " + t(T.b) + ")";
         case TB200_T_NEG: return "-" + t(T.a);
-        case TB200_T_EXP: return "__expf(" + t(T.a) + ")";
+        case TB200_T_EXP:
+            if (d.terms[T.a].op == TB200_T_SUB) return "exp_diff(" + t(d.terms[T.a].a) + ", " + t(d.terms[T.a].b) + ")";
+            return "__expf(" + t(T.a) + ")";
         case TB200_T_LOG: return "logf(" + t(T.a) + ")";
         case TB200_T_TANH: return "tanhf(" + t(T.a) + ")";
         case TB200_T_SQRT: return "sqrtf(" + t(T.a) + ")";
@@ -158,14 +160,14 @@ void emit_chunk_load(Emitter &E, int ind, const tb200_group_desc &d, const Sched
         if (bf) {
             if (S.V == 8) {
                 E.line(ind, "{ const uint4 w_ = " + ld + "((const uint4 *)" + base + ");");
-                E.line(ind, "  " + dst + "[0] = bf2f(w_.x & 0xffffu); " + dst + "[1] = bf2f(w_.x >> 16); " + dst +
-                                "[2] = bf2f(w_.y & 0xffffu); " + dst + "[3] = bf2f(w_.y >> 16);");
-                E.line(ind, "  " + dst + "[4] = bf2f(w_.z & 0xffffu); " + dst + "[5] = bf2f(w_.z >> 16); " + dst +
-                                "[6] = bf2f(w_.w & 0xffffu); " + dst + "[7] = bf2f(w_.w >> 16); }");
+                E.line(ind, "  " + dst + "[0] = bf_lo(w_.x); " + dst + "[1] = bf_hi(w_.x); " + dst + "[2] = bf_lo(w_.y); " + dst +
+                                "[3] = bf_hi(w_.y);");
+                E.line(ind, "  " + dst + "[4] = bf_lo(w_.z); " + dst + "[5] = bf_hi(w_.z); " + dst + "[6] = bf_lo(w_.w); " + dst +
+                                "[7] = bf_hi(w_.w); }");
             } else {
                 E.line(ind, "{ const uint2 w_ = " + ld + "((const uint2 *)" + base + ");");
-                E.line(ind, "  " + dst + "[0] = bf2f(w_.x & 0xffffu); " + dst + "[1] = bf2f(w_.x >> 16); " + dst +
-                                "[2] = bf2f(w_.y & 0xffffu); " + dst + "[3] = bf2f(w_.y >> 16); }");
+                E.line(ind, "  " + dst + "[0] = bf_lo(w_.x); " + dst + "[1] = bf_hi(w_.x); " + dst + "[2] = bf_lo(w_.y); " + dst +
+                                "[3] = bf_hi(w_.y); }");
             }
         } else {
             for (int q = 0; q < S.V / 4; q++) {
@@ -190,7 +192,7 @@ void emit_chunk_store(Emitter &E, int ind, const tb200_group_desc &d, const Sche
     const std::string base = std::string("((") + type + " *)p.out[" + num(o) + "] + row * p.ld_out[" + num(o) + "] + i0)";
     if ((S.vec_out >> o) & 1u) {
         if (bf) {
-            auto pack = [&](int a) { return "(f2bf(" + src + "[" + num(a) + "]) | (f2bf(" + src + "[" + num(a + 1) + "]) << 16))"; };
+            auto pack = [&](int a) { return "pack2(" + src + "[" + num(a) + "], " + src + "[" + num(a + 1) + "])"; };
             if (S.V == 8)
                 E.line(ind, "__stcs((uint4 *)" + base + ", make_uint4(" + pack(0) + ", " + pack(2) + ", " + pack(4) + ", " + pack(6) + "));");
             else
@@ -215,13 +217,15 @@ std::string generate(const tb200_group_desc &d, const Schedule &S) {
     E.line(0, "struct Params { const void *in[8]; void *out[8]; i64 rows; i64 ld_in[8]; i64 ld_out[8]; };");
     E.line(0, "#define NEG_INF __uint_as_float(0xff800000u)");
     E.line(0, "#define POS_INF __uint_as_float(0x7f800000u)");
+    E.line(0, "#define LOG2E 1.4426950408889634f");
+    E.line(0, "static __device__ __forceinline__ float ex2(float x) { float y; asm(\"ex2.approx.ftz.f32 %0, %1;\" : \"=f\"(y) : \"f\"(x)); return y; }");
+    E.line(0, "// exp(a - b) as one multiply-add and one ex2: b * LOG2E is hoisted when b is a row statistic");
+    E.line(0, "static __device__ __forceinline__ float exp_diff(float a, float b) { return ex2(fmaf(a, LOG2E, -(b * LOG2E))); }");
     E.line(0, "static __device__ __forceinline__ float bf2f(u32 h) { return __uint_as_float(h << 16); }");
-    E.line(0, "static __device__ __forceinline__ u32 f2bf(float f) {");
-    E.line(1, "u32 u = __float_as_uint(f);");
-    E.line(1, "if ((u & 0x7fffffffu) > 0x7f800000u) return (u >> 16) | 0x40u;");
-    E.line(1, "u += 0x7fffu + ((u >> 16) & 1u);");
-    E.line(1, "return u >> 16;");
-    E.line(0, "}");
+    E.line(0, "static __device__ __forceinline__ float bf_lo(u32 w) { return __uint_as_float(w << 16); }");
+    E.line(0, "static __device__ __forceinline__ float bf_hi(u32 w) { return __uint_as_float(w & 0xffff0000u); }");
+    E.line(0, "static __device__ __forceinline__ u32 f2bf(float f) { u16 r; asm(\"cvt.rn.bf16.f32 %0, %1;\" : \"=h\"(r) : \"f\"(f)); return r; }");
+    E.line(0, "static __device__ __forceinline__ u32 pack2(float lo, float hi) { u32 r; asm(\"cvt.rn.bf16x2.f32 %0, %1, %2;\" : \"=r\"(r) : \"f\"(hi), \"f\"(lo)); return r; }");
     E.line(0, "constexpr int N = " + num(d.n) + ", V = " + num(S.V) + ", TPR = " + num(S.tpr) + ", K = " + num(S.K) +
                   ", RPB = " + num(S.rpb) + ";");
     E.line(0, "extern \"C\" __global__ void __launch_bounds__(" + num(kThreads) + ") tb200_group(const Params p) {");
@@ -346,8 +350,8 @@ std::string generate(const tb200_group_desc &d, const Schedule &S) {
                     E.line(ind, "  const float m_ = fmaxf(" + n + "a, cm_);");
                     E.line(ind, "  if (m_ > NEG_INF) { float cs_ = 0.0f;");
                     E.line(ind, "#pragma unroll");
-                    E.line(ind, "    for (int e = 0; e < V; e++) cs_ += __expf(" + y + "[e] - m_);");
-                    E.line(ind, "    " + n + "b = " + n + "b * __expf(" + n + "a - m_) + cs_; }");
+                    E.line(ind, "    for (int e = 0; e < V; e++) cs_ += exp_diff(" + y + "[e], m_);");
+                    E.line(ind, "    " + n + "b = " + n + "b * exp_diff(" + n + "a, m_) + cs_; }");
                     E.line(ind, "  " + n + "a = m_; }");
                 } else if (kind == TB200_FOLD_MEANVAR) {
                     const std::string valid = S.whole_elems ? "" : "if (i0 + e < N) ";
@@ -466,9 +470,9 @@ int make_schedule(const tb200_group_desc *d, unsigned vec_in, unsigned vec_out, 
     for (int o = 0; o < d->n_outputs; o++)
         if (d->outputs[o].from == 0) any_f32 |= d->outputs[o].dtype == TB200_F32;
     S->V = any_f32 ? 4 : 8;
-    int tpr = next_pow2(ceil_div(d->n, S->V));
-    // long rows: a few chunks per thread keep more loads in flight than one chunk over more threads
-    if (tpr > 64 && ceil_div(d->n, static_cast<int64_t>(tpr) * S->V) < 2 && d->n >= 2048) tpr /= 2;
+    // four chunks per thread where the row allows: four independent 128-bit loads in flight per thread is what
+    // keeps HBM busy at the occupancy these kernels reach (two left BFloat16 rows at half the rate)
+    int tpr = next_pow2(ceil_div(d->n, static_cast<int64_t>(S->V) * 4));
     S->tpr = tpr < 8 ? 8 : tpr > kThreads ? kThreads : tpr;
     S->K = static_cast<int>(ceil_div(d->n, static_cast<int64_t>(S->tpr) * S->V));
     S->rpb = kThreads / S->tpr;
