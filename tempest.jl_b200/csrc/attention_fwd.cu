@@ -23,6 +23,7 @@
 // No load uses cluster multicast.  Every barrier wait is bounded.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "attention_simt.cuh"
@@ -384,6 +385,307 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
     }
 }
 
+// ---------------------------------------------------------------- two query tiles per CTA ----
+//
+// The kernel above leaves its four softmax warps alone on their schedulers: every wait on tensor memory, on
+// the exponential unit or on a barrier is a bubble.  Here a CTA takes 256 queries of one head as two
+// independent 128-query tiles, each with its own four softmax warps, score buffer and accumulator in tensor
+// memory (S_A | S_B | O_A | O_B = 512 columns).  The two tiles have nothing to exchange, so one tile's
+// softmax fills the other's bubbles and the tensor core always has the other tile's product to run.  The
+// weights do not go through shared memory: each softmax thread writes its row of P as packed BFloat16 over
+// the first 64 columns of its own score buffer and the second product reads its A operand from tensor memory.
+// The MMAs of one CTA execute in issue order, so S of the next key tile (issued after P V of this one) cannot
+// overwrite P early.  Shared memory: Q_A, Q_B, two K stages, two V stages; a tile's Q buffer stages its O
+// store once the tile's products are complete.
+constexpr int kPairThreads = 320;
+
+__device__ __forceinline__ int pair_kv_tiles(const AttnFwdArgs &p, int qt) {
+    if (qt >= p.q_tiles) return 0;
+    return kv_tiles_of(p, qt);
+}
+
+__global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(const __grid_constant__ AttnFwdArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *sq = smem;                       // Q_A, Q_B
+    uint8_t *sk = sq + 2 * kTileBytes;        // K ring, 2 stages
+    uint8_t *sv = sk + 2 * kTileBytes;        // V ring, 2 stages
+
+    __shared__ __align__(8) uint64_t q_full[2], q_empty[2], s_full[2], p_full[2], pv_done[2], o_free[2];
+    __shared__ __align__(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int failed_smem;
+    volatile int *failed = &failed_smem;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        failed_smem = 0;
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 4); mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4);
+            mbar_init(&pv_done[s], 1); mbar_init(&o_free[s], 4);
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&p.q); prefetch_tensormap(&p.k); prefetch_tensormap(&p.v); prefetch_tensormap(&p.o);
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_smem, 512);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+    const int group = p.heads / p.kv_heads;
+    const int pair_tiles = (p.q_tiles + 1) / 2;
+    const int per = p.batch * p.heads;
+    const int items = pair_tiles * per;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            uint32_t kv_count = 0, q_loads[2] = {0, 0};
+            for (int item = blockIdx.x; item < items && !*failed; item += gridDim.x) {
+                const int pt = pair_tiles - 1 - item / per, bh = item % per;
+                const int b = bh / p.heads, h = bh % p.heads, hk = h / group;
+                bool ok = true;
+                for (int g = 0; g < 2 && ok; g++) {
+                    const int qt = 2 * pt + g;
+                    if (qt >= p.q_tiles) continue;
+                    // a tile's Q buffer is released by its softmax warps once their O store has read it; the
+                    // second tile is absent from some items, so each tile counts its own loads
+                    if (!wait_bounded(&q_empty[g], (q_loads[g] & 1) ^ 1, failed, 1)) { ok = false; break; }
+                    q_loads[g]++;
+                    mbar_arrive_expect_tx(&q_full[g], kTileBytes);
+                    tma_load_4d(sq + g * kTileBytes, &p.q, &q_full[g], 0, h, qt * kTile, b);
+                    tma_load_4d(sq + g * kTileBytes + kSlab, &p.q, &q_full[g], 64, h, qt * kTile, b);
+                }
+                if (!ok) break;
+                const int n0 = pair_kv_tiles(p, 2 * pt), n1 = pair_kv_tiles(p, 2 * pt + 1);
+                const int nkv = n0 > n1 ? n0 : n1;
+                for (int j = 0; j < nkv; j++, kv_count++) {
+                    const int st = kv_count & 1;
+                    const uint32_t ph = (kv_count >> 1) & 1;
+                    if (!wait_bounded(&k_empty[st], ph ^ 1, failed, 2)) break;
+                    mbar_arrive_expect_tx(&k_full[st], kTileBytes);
+                    tma_load_4d(sk + st * kTileBytes, &p.k, &k_full[st], 0, hk, j * kTile, b);
+                    tma_load_4d(sk + st * kTileBytes + kSlab, &p.k, &k_full[st], 64, hk, j * kTile, b);
+                    if (!wait_bounded(&v_empty[st], ph ^ 1, failed, 3)) break;
+                    mbar_arrive_expect_tx(&v_full[st], kTileBytes);
+                    tma_load_4d(sv + st * kTileBytes, &p.v, &v_full[st], 0, hk, j * kTile, b);
+                    tma_load_4d(sv + st * kTileBytes + kSlab, &p.v, &v_full[st], 64, hk, j * kTile, b);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            const uint32_t idesc_qk = umma_idesc_bf16(kTile, kTile, false, false);
+            const uint32_t idesc_pv = umma_idesc_bf16(kTile, kHeadDim, false, true);
+            uint32_t kv_count = 0;
+            uint32_t items_of[2] = {0, 0}, p_count[2] = {0, 0};
+            auto scores = [&](int g, int st) {   // S_g = Q_g K^T
+                const uint32_t qa = smem_u32(sq + g * kTileBytes), ka = smem_u32(sk + st * kTileBytes);
+#pragma unroll
+                for (int k = 0; k < kHeadDim / 16; k++) {
+                    const uint32_t off = (k >> 2) * kSlab + (k & 3) * 32;
+                    tcgen05_mma_f16(tmem_base + g * kTile, umma_smem_desc(qa + off, 16, 1024), umma_smem_desc(ka + off, 16, 1024),
+                                    idesc_qk, k != 0);
+                }
+                tcgen05_commit(&s_full[g]);
+            };
+            for (int item = blockIdx.x; item < items && !*failed; item += gridDim.x) {
+                const int pt = pair_tiles - 1 - item / per;
+                const int n[2] = {pair_kv_tiles(p, 2 * pt), pair_kv_tiles(p, 2 * pt + 1)};
+                const int nkv = n[0] > n[1] ? n[0] : n[1];
+                bool ok = true;
+                for (int g = 0; g < 2 && ok; g++)
+                    if (n[g] > 0) {
+                        if (!wait_bounded(&q_full[g], items_of[g] & 1, failed, 4)) ok = false;
+                    }
+                if (!ok) break;
+                tcgen05_fence_after();
+                // the first key tile's scores for both query tiles
+                {
+                    const int st = kv_count & 1;
+                    if (!wait_bounded(&k_full[st], (kv_count >> 1) & 1, failed, 6)) break;
+                    tcgen05_fence_after();
+                    for (int g = 0; g < 2; g++)
+                        if (n[g] > 0) scores(g, st);
+                    tcgen05_commit(&k_empty[st]);   // K of tile 0 is free once both score products have run
+                }
+                for (int j = 0; j < nkv && ok; j++) {
+                    const uint32_t c = kv_count + j;
+                    const int st = c & 1;
+                    const uint32_t ph = (c >> 1) & 1;
+                    const int st_next = (c + 1) & 1;
+                    const uint32_t ph_next = ((c + 1) >> 1) & 1;
+                    bool k_next_ready = false;
+                    for (int g = 0; g < 2 && ok; g++) {
+                        if (j >= n[g]) continue;
+                        // O_g += P_g V_j
+                        if (j == 0 && !wait_bounded(&o_free[g], (items_of[g] & 1) ^ 1, failed, 5)) { ok = false; break; }
+                        if (!wait_bounded(&v_full[st], ph, failed, 8)) { ok = false; break; }
+                        if (!wait_bounded(&p_full[g], p_count[g] & 1, failed, 9)) { ok = false; break; }
+                        p_count[g]++;
+                        tcgen05_fence_after();
+                        const uint32_t va = smem_u32(sv + st * kTileBytes);
+#pragma unroll
+                        for (int k = 0; k < kTile / 16; k++)
+                            tcgen05_mma_f16_ts(tmem_base + (2 + g) * kTile, tmem_base + g * kTile + k * 8,
+                                               umma_smem_desc(va + k * 16 * 128, kSlab, 1024), idesc_pv, j | k);
+                        tcgen05_commit(&pv_done[g]);
+                        // scores of the next key tile for this query tile
+                        if (j + 1 < n[g]) {
+                            if (!k_next_ready) {
+                                if (!wait_bounded(&k_full[st_next], ph_next, failed, 6)) { ok = false; break; }
+                                tcgen05_fence_after();
+                                k_next_ready = true;
+                            }
+                            scores(g, st_next);
+                        }
+                    }
+                    if (!ok) break;
+                    tcgen05_commit(&v_empty[st]);                       // V_j: both products issued
+                    if (j + 1 < nkv) tcgen05_commit(&k_empty[st_next]);  // K_{j+1}: both score products issued
+                }
+                kv_count += nkv;
+                for (int g = 0; g < 2; g++)
+                    if (n[g] > 0) items_of[g]++;
+                if (!ok) break;
+            }
+        }
+    } else {
+        // ---- softmax warps: tile g, thread = query row
+        const int g = (warp - 2) >> 2;
+        const int q = warp & 3;   // the warp's quarter of the 128 tensor-memory lanes (warp id mod 4)
+        const int row = q * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+        const uint32_t tmem_s = tmem_base + lane_base + g * kTile;
+        const uint32_t tmem_o = tmem_base + lane_base + (2 + g) * kTile;
+        uint8_t *stage = sq + g * kTileBytes;
+        uint32_t s_count = 0, pv_seen = 0;
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            const int pt = pair_tiles - 1 - item / per, bh = item % per;
+            const int b = bh / p.heads, h = bh % p.heads;
+            const int qt = 2 * pt + g;
+            const int nkv = pair_kv_tiles(p, qt);
+            if (nkv == 0) continue;
+            const int qi = qt * kTile + row;
+            float m_used = -INFINITY, l = 0.0f;
+            bool ok = true;
+            for (int j = 0; j < nkv; j++, s_count++) {
+                if (!wait_bounded(&s_full[g], s_count & 1, failed, 10)) { ok = false; break; }
+                tcgen05_fence_after();
+                const int key0 = j * kTile;
+                const bool edge = (p.causal && key0 + kTile - 1 > qt * kTile) || key0 + kTile > p.keys;
+                uint32_t r[kTile];
+#pragma unroll
+                for (int c = 0; c < kTile / 32; c++) tmem_ld_32x32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+                tmem_ld_wait();
+                if (edge) {
+#pragma unroll
+                    for (int i = 0; i < kTile; i++) {
+                        const int key = key0 + i;
+                        if ((p.causal && key > qi) || key >= p.keys) r[i] = 0xff800000u;
+                    }
+                }
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < kTile; i += 4) {
+#pragma unroll
+                    for (int u = 0; u < 4; u++) mx[u] = fmaxf(mx[u], __uint_as_float(r[i + u]));
+                }
+                float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+                float alpha = 1.0f;
+                bool grew = false;
+                if (m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY)) {
+                    alpha = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_tile);
+                    grew = j > 0 && m_used != -INFINITY;
+                    m_used = m_tile;
+                    l *= alpha;
+                }
+                const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
+                float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                // weights packed two per column over the row's own scores
+#pragma unroll
+                for (int i = 0; i < kTile; i += 2) {
+                    const float w0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+                    const float w1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
+                    ls[(i >> 1) & 3] += w0 + w1;
+                    r[i >> 1] = pack_bf16x2(w0, w1);
+                }
+                l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                tmem_st_32x32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                tmem_st_32x32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+                // O_g holds the products up to tile j-1 once pv_done has completed
+                if (j > 0) {
+                    if (!wait_bounded(&pv_done[g], pv_seen & 1, failed, 12)) { ok = false; break; }
+                    pv_seen++;
+                    tcgen05_fence_after();
+                    if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll 1
+                        for (int c = 0; c < kHeadDim / 32; c++) {
+                            uint32_t o[32];
+                            tmem_ld_32x32(tmem_o + c * 32, o);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st_32x32(tmem_o + c * 32, o);
+                        }
+                    }
+                }
+                tmem_st_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[g]);
+            }
+            if (!ok) break;
+            // ---- epilogue: O / l, the log-sum-exp, store through the tile's own Q buffer
+            if (!wait_bounded(&pv_done[g], pv_seen & 1, failed, 14)) break;
+            pv_seen++;
+            tcgen05_fence_after();
+            const float inv = 1.0f / l;
+            {
+                uint32_t r[kHeadDim];
+#pragma unroll
+                for (int c = 0; c < kHeadDim / 32; c++) tmem_ld_32x32(tmem_o + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+                tmem_ld_wait();
+#pragma unroll
+                for (int gg = 0; gg < kHeadDim / 8; gg++) {
+                    uint4 v4;
+                    v4.x = pack_bf16x2(__uint_as_float(r[8 * gg]) * inv, __uint_as_float(r[8 * gg + 1]) * inv);
+                    v4.y = pack_bf16x2(__uint_as_float(r[8 * gg + 2]) * inv, __uint_as_float(r[8 * gg + 3]) * inv);
+                    v4.z = pack_bf16x2(__uint_as_float(r[8 * gg + 4]) * inv, __uint_as_float(r[8 * gg + 5]) * inv);
+                    v4.w = pack_bf16x2(__uint_as_float(r[8 * gg + 6]) * inv, __uint_as_float(r[8 * gg + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(stage + row * 128 + (gg >> 3) * kSlab + (((gg & 7) ^ (row & 7)) << 4)) = v4;
+                }
+            }
+            if (p.lse && qi < p.queries)
+                p.lse[(static_cast<long long>(b) * p.queries + qi) * p.heads + h] =
+                    (m_used == -INFINITY) ? -INFINITY : (m_used + log2f(l)) * 0.6931471805599453f;
+            tcgen05_fence_before();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_4d(&p.o, stage + q * 32 * 128, 0, h, qt * kTile + q * 32, b);
+                tma_store_4d(&p.o, stage + kSlab + q * 32 * 128, 64, h, qt * kTile + q * 32, b);
+                bulk_commit_group();
+                bulk_wait_group_read<0>();
+                mbar_arrive(&o_free[g]);    // the accumulator has been read
+                mbar_arrive(&q_empty[g]);   // and the Q buffer is free for the next item's load
+            }
+            __syncwarp();
+        }
+        if (lane == 0) bulk_wait_group<0>();
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -466,6 +768,25 @@ extern "C" int tb200_attention_fwd(const tb200_attn_desc *d, const void *q, cons
                                             static_cast<int>(smem)));
             configured[dev.device] = true;
         }
+    }
+    // more than one query tile: two tiles per CTA, each with its own softmax warps
+    static const bool force_single = getenv("TB200_ATTN_SINGLE") != nullptr;
+    if (p.q_tiles > 1 && !force_single) {
+        const size_t pair_smem = 6 * kTileBytes + 1024;
+        {
+            std::lock_guard<std::mutex> hold(lock);
+            static bool pair_configured[64] = {};
+            if (!pair_configured[dev.device]) {
+                TB200_CUDA(cudaFuncSetAttribute(attention_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                static_cast<int>(pair_smem)));
+                pair_configured[dev.device] = true;
+            }
+        }
+        const int pair_items = (p.q_tiles + 1) / 2 * d->batch * d->heads;
+        attention_fwd_pair_kernel<<<static_cast<unsigned>(pair_items < dev.sms ? pair_items : dev.sms), kPairThreads, pair_smem,
+                                    stream>>>(p);
+        TB200_CUDA(cudaGetLastError());
+        return TB200_OK;
     }
     const unsigned grid = static_cast<unsigned>(p.items < dev.sms ? p.items : dev.sms);
     attention_fwd_kernel<<<grid, kAttnThreads, smem, stream>>>(p);

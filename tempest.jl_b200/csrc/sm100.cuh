@@ -145,6 +145,18 @@ __device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t a_desc
         : "memory");
 }
 
+// The same with A read from tensor memory: 128 lanes (rows) by K/2 columns holding two 16-bit values each,
+// the lower K index in the low half.
+__device__ __forceinline__ void tcgen05_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // 32 lanes x 32 columns of 32-bit accumulators: thread i of the warp gets row
 // (lane base + i), columns [col, col + 32).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
