@@ -23,7 +23,6 @@
 // No load uses cluster multicast.  Every barrier wait is bounded.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "attention_simt.cuh"
@@ -509,7 +508,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
                     if (!wait_bounded(&k_full[st], (kv_count >> 1) & 1, failed, 6)) break;
                     tcgen05_fence_after();
                     for (int g = 0; g < 2; g++)
-                        if (n[g] > 0) scores(g, st);
+                        if (n[g] > 0) {
+                            scores(g, st);
+                        }
                     tcgen05_commit(&k_empty[st]);   // K of tile 0 is free once both score products have run
                 }
                 for (int j = 0; j < nkv && ok; j++) {
@@ -770,8 +771,7 @@ extern "C" int tb200_attention_fwd(const tb200_attn_desc *d, const void *q, cons
         }
     }
     // more than one query tile: two tiles per CTA, each with its own softmax warps
-    static const bool force_single = getenv("TB200_ATTN_SINGLE") != nullptr;
-    if (p.q_tiles > 1 && !force_single) {
+    if (p.q_tiles > 1) {
         const size_t pair_smem = 6 * kTileBytes + 1024;
         {
             std::lock_guard<std::mutex> hold(lock);
@@ -783,8 +783,8 @@ extern "C" int tb200_attention_fwd(const tb200_attn_desc *d, const void *q, cons
             }
         }
         const int pair_items = (p.q_tiles + 1) / 2 * d->batch * d->heads;
-        attention_fwd_pair_kernel<<<static_cast<unsigned>(pair_items < dev.sms ? pair_items : dev.sms), kPairThreads, pair_smem,
-                                    stream>>>(p);
+        const unsigned pair_grid = static_cast<unsigned>(pair_items < dev.sms ? pair_items : dev.sms);
+        attention_fwd_pair_kernel<<<pair_grid, kPairThreads, pair_smem, stream>>>(p);
         TB200_CUDA(cudaGetLastError());
         return TB200_OK;
     }
