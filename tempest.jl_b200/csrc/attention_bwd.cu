@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
 
     __shared__ __align__(8) uint64_t outer_full, outer_empty, acc_done, acc_free;
     __shared__ __align__(8) uint64_t inner_full[kStages], inner_empty[kStages];
-    __shared__ __align__(8) uint64_t t_full[2], t_empty[2], ds_full[2], ds_empty[2];
+    __shared__ __align__(8) uint64_t t_full[2], ds_full[2];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int failed_smem;
     // dK/dV: the step's 64 queries' lse*log2(e) [0, 64) and delta [64, 128), per group, double-buffered
@@ -147,8 +147,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
         mbar_init(&outer_full, 1); mbar_init(&outer_empty, 1); mbar_init(&acc_done, 1); mbar_init(&acc_free, 8);
         for (int s = 0; s < kStages; s++) { mbar_init(&inner_full[s], 1); mbar_init(&inner_empty[s], 1); }
         for (int s = 0; s < 2; s++) {
-            mbar_init(&t_full[s], 1); mbar_init(&t_empty[s], 4);
-            mbar_init(&ds_full[s], 4); mbar_init(&ds_empty[s], 1);
+            mbar_init(&t_full[s], 1);
+            mbar_init(&ds_full[s], 4);
         }
         fence_barrier_init();
         prefetch_tensormap(&p.outer_a); prefetch_tensormap(&p.outer_b);
@@ -215,8 +215,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                         const uint32_t ph = (c / kStages) & 1;
                         const int tb = c & 1;
                         const uint32_t tph = (c >> 1) & 1;
+                        // buffer tb was last read by the gradient products of two steps ago, issued before this
+                        // point: MMAs of one CTA run in issue order, so no barrier is needed to reuse it
                         if (!bwd_wait(&inner_full[st], ph, failed, 4)) { ok = false; break; }
-                        if (!bwd_wait(&t_empty[tb], tph ^ 1, failed, 5)) { ok = false; break; }
                         tcgen05_fence_after();
                         const uint32_t oa = smem_u32(s_outer_a), ob = smem_u32(s_outer_b);
                         const uint32_t ia = smem_u32(s_inner + st * 2 * kInnerBytes), ib = ia + kInnerBytes;
@@ -248,18 +249,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                         if (!bwd_wait(&ds_full[db], dph, failed, 7)) { ok = false; break; }
                         tcgen05_fence_after();
                         const uint32_t ia = smem_u32(s_inner + st * 2 * kInnerBytes), ib = ia + kInnerBytes;
-                        const uint32_t pa = smem_u32(s_ds + db * 2 * kDsBytes), da = pa + kDsBytes;
+                        // A: P / dS from tensor memory, 16 positions = 8 packed columns per MMA, written by the row
+                        // threads over the scores / dP they were computed from; B: 16 position lines of 128 bytes
+                        const uint32_t pa = tmem_base + db * 128, da = pa + 64;
 #pragma unroll
                         for (int k = 0; k < kInner / 16; k++) {
-                            // A: 16 positions = 32 bytes along the P / dS rows; B: 16 position lines of 128 bytes
                             if (DKDV)
-                                tcgen05_mma_f16(tmem_acc1, umma_smem_desc(pa + k * 32, 16, 1024),
-                                                umma_smem_desc(ib + k * 2048, kInnerSlab, 1024), idesc_g, (t - 1) | k);
-                            tcgen05_mma_f16(tmem_acc2, umma_smem_desc(da + k * 32, 16, 1024),
-                                            umma_smem_desc(ia + k * 2048, kInnerSlab, 1024), idesc_g, (t - 1) | k);
+                                tcgen05_mma_f16_ts(tmem_acc1, pa + k * 8, umma_smem_desc(ib + k * 2048, kInnerSlab, 1024), idesc_g,
+                                                   (t - 1) | k);
+                            tcgen05_mma_f16_ts(tmem_acc2, da + k * 8, umma_smem_desc(ia + k * 2048, kInnerSlab, 1024), idesc_g,
+                                               (t - 1) | k);
                         }
                         tcgen05_commit(&inner_empty[st]);
-                        tcgen05_commit(&ds_empty[db]);
                         if (t == steps.count) tcgen05_commit(&acc_done);
                         grad_count++;
                     }
@@ -316,13 +317,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 tmem_ld_32x32(t1 + 64, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
                 tmem_ld_32x32(t1 + 96, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
                 tmem_ld_wait();
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&t_empty[tb]);
-                // the P / dS tiles of two steps ago must have been consumed
-                if (!bwd_wait(&ds_empty[tb], tph ^ 1, failed, 9)) { ok = false; break; }
-                uint8_t *prow = s_ds + tb * 2 * kDsBytes + row * 128;
-                uint8_t *drow = prow + kDsBytes;
                 const bool edge = DKDV ? (pos0 + kInner > p.queries || outer_pos >= p.keys ||
                                           (p.causal && pos0 < steps.tile * kOuter + kOuter))
                                        : (pos0 + kInner > p.keys || outer_pos >= p.queries ||
@@ -356,19 +350,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                         pv[u] = pw;
                         dv[u] = pw * (__uint_as_float(dp[i]) - dl);
                     }
-                    const int chunk = (g ^ (row & 7)) << 4;
-                    if (DKDV) {
-                        uint4 v4;
-                        v4.x = pack_bf16x2(pv[0], pv[1]); v4.y = pack_bf16x2(pv[2], pv[3]);
-                        v4.z = pack_bf16x2(pv[4], pv[5]); v4.w = pack_bf16x2(pv[6], pv[7]);
-                        *reinterpret_cast<uint4 *>(prow + chunk) = v4;
+                    // packed two per column over the values they came from: s becomes P, dp becomes dS
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        if (DKDV) s[4 * g + u] = pack_bf16x2(pv[2 * u], pv[2 * u + 1]);
+                        dp[4 * g + u] = pack_bf16x2(dv[2 * u], dv[2 * u + 1]);
                     }
-                    uint4 w4;
-                    w4.x = pack_bf16x2(dv[0], dv[1]); w4.y = pack_bf16x2(dv[2], dv[3]);
-                    w4.z = pack_bf16x2(dv[4], dv[5]); w4.w = pack_bf16x2(dv[6], dv[7]);
-                    *reinterpret_cast<uint4 *>(drow + chunk) = w4;
                 }
-                fence_proxy_async();
+                if (DKDV) tmem_st_32x32(t1, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+                tmem_st_32x32(t1 + 64, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+                tmem_st_wait();
+                tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ds_full[tb]);
             }
