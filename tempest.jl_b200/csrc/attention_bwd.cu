@@ -321,6 +321,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                                           (p.causal && pos0 < steps.tile * kOuter + kOuter))
                                        : (pos0 + kInner > p.keys || outer_pos >= p.queries ||
                                           (p.causal && pos0 + kInner - 1 > steps.tile * kOuter));
+                if (edge) {
+                    // masked positions get a score of -Inf: their weight and their dS are then exactly zero
+#pragma unroll
+                    for (int i = 0; i < kInner; i++) {
+                        const int inner_pos = pos0 + i;
+                        const int key = DKDV ? outer_pos : inner_pos;
+                        const int query = DKDV ? inner_pos : outer_pos;
+                        if (key >= p.keys || query >= p.queries || (p.causal && key > query)) s[i] = 0xff800000u;
+                    }
+                }
 #pragma unroll
                 for (int g = 0; g < kInner / 8; g++) {
                     float pv[8], dv[8];
@@ -340,13 +350,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                         const int i = 8 * g + u;
                         const float lse2 = DKDV ? l8[u] : row_lse2;
                         const float dl = DKDV ? d8[u] : row_delta;
-                        float pw = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
-                        if (edge) {
-                            const int inner_pos = pos0 + i;
-                            const int key = DKDV ? outer_pos : inner_pos;
-                            const int query = DKDV ? inner_pos : outer_pos;
-                            if (key >= p.keys || query >= p.queries || (p.causal && key > query)) pw = 0.0f;
-                        }
+                        const float pw = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
                         pv[u] = pw;
                         dv[u] = pw * (__uint_as_float(dp[i]) - dl);
                     }
