@@ -504,6 +504,34 @@ def run_profile_case(args):
         for _ in range(2):
             L.deltanet_fwd(dd, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ad.data_ptr(), bd.data_ptr(), od.data_ptr(),
                            ws.data_ptr(), need, stream)
+        # the pullback: the forward's two kernels again (keeping states) and three of its own
+        gq, gk, gv = (torch.empty(Hn, T, 128, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        ga, gb = torch.empty(Hn, T, device="cuda"), torch.empty(Hn, T, device="cuda")
+        god = torch.randn(Hn, 128, T, device="cuda").bfloat16()
+        bneed = L.deltanet_bwd_workspace_bytes(dd)
+        bws = torch.empty(bneed, dtype=torch.uint8, device="cuda")
+        L.deltanet_bwd(dd, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ad.data_ptr(), bd.data_ptr(), god.data_ptr(),
+                       gq.data_ptr(), gk.data_ptr(), gv.data_ptr(), ga.data_ptr(), gb.data_ptr(), bws.data_ptr(), bneed, stream)
+    elif case == "groups":
+        # map -> fold row groups, 16384 rows of 4096: the term interpreter and the groups' own compiled kernels
+        G = pkg.groups
+        n, rows = 4096, 16384
+        x = torch.randn(rows, n, device="cuda")
+        y, lse = torch.empty_like(x), torch.empty(rows, device="cuda")
+        xb = x.bfloat16()
+        yb = torch.empty_like(xb)
+        w = torch.randn(n, device="cuda")
+        wb = w.bfloat16()
+        cases = [(G.softmax(n, rows), [x], [y, lse]),
+                 (G.layernorm(n, rows), [x, w, w], [y]),
+                 (G.softmax(n, rows, "BFloat16"), [xb], [yb, lse]),
+                 (G.layernorm(n, rows, "BFloat16"), [xb, wb, wb], [yb]),
+                 (G.rmsnorm(n, rows, "BFloat16"), [xb, wb], [yb])]
+        for _ in range(2):
+            for group, ins, outs in cases:
+                L.rowreduce_compiled(group.desc(), [t.data_ptr() for t in ins], [t.data_ptr() for t in outs], stream)
+        group, ins, outs = cases[0]
+        L.rowreduce_generic(group.desc(), [t.data_ptr() for t in ins], [t.data_ptr() for t in outs], stream)
     else:
         raise SystemExit(f"unknown profile case {case}")
     torch.cuda.synchronize()
@@ -651,7 +679,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the side measurements (MLP step, GEMM)")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "attention", "deltanet"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "attention", "deltanet", "groups"],
                     help="run one small case of a kernel family only (for ncu captures)")
     args = ap.parse_args()
     if args.profile_case:
