@@ -136,15 +136,36 @@ __device__ __forceinline__ void unpack8(const __nv_bfloat16 *p, float *v) {
     Access<__nv_bfloat16, true>::unpack(*reinterpret_cast<const uint4 *>(p), v);
 }
 
+// Warp-level TF32 tensor-core product step: D(16 x 8) += A(16 x 8) B(8 x 8), Float32 accumulate.  With
+// g = lane / 4 and t = lane % 4 a thread holds A[g][t], A[g+8][t], A[g][t+4], A[g+8][t+4]; B[t][g], B[t+4][g];
+// D[g][2t], D[g][2t+1], D[g+8][2t], D[g+8][2t+1].  The products of a chunk are small (64 x 32 x 128) and sit on
+// the chain of chunks: the warp-level form keeps operands in shared memory and results in registers, with no
+// tensor-memory round trip per link of the chain.  TF32 operands: BFloat16 values are exact in TF32; the
+// Float32 state and U are rounded to TF32 (10 mantissa bits) as operands only, never in storage.
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t tf32_of(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ uint32_t tf32_of_bf16(const __nv_bfloat16 *p) {
+    return static_cast<uint32_t>(*reinterpret_cast<const unsigned short *>(p)) << 16;
+}
+
+constexpr int kPadS = 40;   // Float32 row pitch of the 32-wide state and U tiles: B-fragment reads hit 32 banks
+
 __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
                                                             const float *a, const __nv_bfloat16 *w_in,
                                                             const __nv_bfloat16 *u_in, const __nv_bfloat16 *p_in,
                                                             __nv_bfloat16 *o, float *s_save, float *u_save, int T) {
     extern __shared__ float sm[];
-    float *S = sm;                                      // [128][32] the state slice
-    float *Ut = S + kDK * kDVP;                         // [64][32]
-    float *U = Ut + kC * kDVP;                          // [64][32]
-    float *eca = U + kC * kDVP;                         // [64] exp(ca)
+    float *S = sm;                                      // [128][40] the state slice
+    float *U = S + kDK * kPadS;                         // [64][40]
+    float *eca = U + kC * kPadS;                        // [64] exp(ca)
     float *ekd = eca + kC;                              // [64] exp(ca_C - ca)
     __nv_bfloat16 *Wh = reinterpret_cast<__nv_bfloat16 *>(ekd + kC);   // [64][136]
     __nv_bfloat16 *Qh = Wh + kC * kPadH;
@@ -154,17 +175,29 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
     __shared__ float gamma_sm;
 
     const int head = blockIdx.x, part = blockIdx.y;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
     const int chunks = T / kC;
-    for (int i = tid; i < kDK * kDVP; i += 256) S[i] = 0.0f;
+    for (int i = tid; i < kDK * kPadS; i += 256) S[i] = 0.0f;
 
-    const int ty = tid >> 3, tx = tid & 7;   // outputs [64][32]: rows 2ty, 2ty+1; columns 4tx..4tx+3
+    // U and o: warp -> 16 positions (mt) x 16 features (nh), two 8-feature tiles
+    const int mt = warp & 3, nh = warp >> 2;
     for (int chunk = 0; chunk < chunks; chunk++) {
         const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
+        // Ut at this thread's accumulator positions, straight from global memory (latency hides behind the tile loads)
+        float acc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int hr = 0; hr < 2; hr++) {
+                const uint32_t two = __ldg(reinterpret_cast<const uint32_t *>(
+                    u_in + (row0 + 16 * mt + g + 8 * hr) * kDV + part * kDVP + 16 * nh + 8 * nt + 2 * t4));
+                unpack_bf16x2(two, acc[nt][2 * hr], acc[nt][2 * hr + 1]);
+            }
         __syncthreads();   // the previous chunk's readers are done with the tiles
         if (s_save) {      // the state this chunk starts from, for the backward
             float *dst = s_save + (static_cast<long long>(head) * chunks + chunk) * kDK * kDV + part * kDVP;
-            for (int i = tid; i < kDK * kDVP; i += 256) dst[(i / kDVP) * kDV + (i % kDVP)] = S[i];
+            for (int i = tid; i < kDK * kDVP; i += 256) dst[(i / kDVP) * kDV + (i % kDVP)] = S[(i / kDVP) * kPadS + (i % kDVP)];
         }
         for (int i = tid; i < kC * kDK / 8; i += 256) {
             const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
@@ -177,13 +210,6 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
             *reinterpret_cast<uint4 *>(Ph + r * kPadP + c) =
                 __ldg(reinterpret_cast<const uint4 *>(p_in + (static_cast<long long>(head) * chunks + chunk) * kC * kC + r * kC + c));
         }
-        for (int i = tid; i < kC * kDVP / 8; i += 256) {
-            const int r = i / (kDVP / 8), c = (i % (kDVP / 8)) * 8;
-            float uv[8];
-            Access<__nv_bfloat16, true>::load_cached(u_in + (row0 + r) * kDV + part * kDVP + c, uv);
-#pragma unroll
-            for (int e = 0; e < 8; e++) Ut[r * kDVP + c + e] = uv[e];
-        }
         if (tid == 0) {
             float s = 0.0f;
             for (int t = 0; t < kC; t++) { s += a[row0 + t]; eca[t] = s; }
@@ -194,71 +220,58 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
         __syncthreads();
 
         // U = Ut - W S
-        float acc[2][4];
+        {
+            float ws[2][4] = {};
+            const __nv_bfloat16 *w0 = Wh + (16 * mt + g) * kPadH + t4, *w1 = w0 + 8 * kPadH;
+            const float *sb = S + t4 * kPadS + 16 * nh + g;
+#pragma unroll 4
+            for (int k0 = 0; k0 < kDK; k0 += 8) {
+                const uint32_t af[4] = {tf32_of_bf16(w0 + k0), tf32_of_bf16(w1 + k0), tf32_of_bf16(w0 + k0 + 4), tf32_of_bf16(w1 + k0 + 4)};
 #pragma unroll
-        for (int r = 0; r < 2; r++)
-#pragma unroll
-            for (int j = 0; j < 4; j++) acc[r][j] = Ut[(2 * ty + r) * kDVP + 4 * tx + j];
-        for (int i = 0; i < kDK; i += 8) {
-            float w0[8], w1[8];
-            unpack8(Wh + (2 * ty) * kPadH + i, w0);
-            unpack8(Wh + (2 * ty + 1) * kPadH + i, w1);
-#pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const float4 s4 = *reinterpret_cast<const float4 *>(S + (i + e) * kDVP + 4 * tx);
-                acc[0][0] = fmaf(-w0[e], s4.x, acc[0][0]); acc[0][1] = fmaf(-w0[e], s4.y, acc[0][1]);
-                acc[0][2] = fmaf(-w0[e], s4.z, acc[0][2]); acc[0][3] = fmaf(-w0[e], s4.w, acc[0][3]);
-                acc[1][0] = fmaf(-w1[e], s4.x, acc[1][0]); acc[1][1] = fmaf(-w1[e], s4.y, acc[1][1]);
-                acc[1][2] = fmaf(-w1[e], s4.z, acc[1][2]); acc[1][3] = fmaf(-w1[e], s4.w, acc[1][3]);
+                for (int nt = 0; nt < 2; nt++)
+                    mma_tf32(ws[nt], af, tf32_of(sb[k0 * kPadS + 8 * nt]), tf32_of(sb[(k0 + 4) * kPadS + 8 * nt]));
             }
-        }
 #pragma unroll
-        for (int r = 0; r < 2; r++) {
-            const float4 u4 = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
-            *reinterpret_cast<float4 *>(U + (2 * ty + r) * kDVP + 4 * tx) = u4;
-            if (u_save) *reinterpret_cast<float4 *>(u_save + (row0 + 2 * ty + r) * kDV + part * kDVP + 4 * tx) = u4;
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int hr = 0; hr < 2; hr++) {
+                    const float2 u2 = make_float2(acc[nt][2 * hr] - ws[nt][2 * hr], acc[nt][2 * hr + 1] - ws[nt][2 * hr + 1]);
+                    const int row = 16 * mt + g + 8 * hr, col = 16 * nh + 8 * nt + 2 * t4;
+                    *reinterpret_cast<float2 *>(U + row * kPadS + col) = u2;
+                    if (u_save) *reinterpret_cast<float2 *>(u_save + (row0 + row) * kDV + part * kDVP + col) = u2;
+                }
         }
         __syncthreads();
 
+        // o = (e^ca Q) S + P U
         if (o) {
-            // o = (e^ca Q) S + P U
             float oa[2][4] = {};
-            for (int i = 0; i < kDK; i += 8) {
-                float q0[8], q1[8];
-                unpack8(Qh + (2 * ty) * kPadH + i, q0);
-                unpack8(Qh + (2 * ty + 1) * kPadH + i, q1);
-    #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const float4 s4 = *reinterpret_cast<const float4 *>(S + (i + e) * kDVP + 4 * tx);
-                    oa[0][0] = fmaf(q0[e], s4.x, oa[0][0]); oa[0][1] = fmaf(q0[e], s4.y, oa[0][1]);
-                    oa[0][2] = fmaf(q0[e], s4.z, oa[0][2]); oa[0][3] = fmaf(q0[e], s4.w, oa[0][3]);
-                    oa[1][0] = fmaf(q1[e], s4.x, oa[1][0]); oa[1][1] = fmaf(q1[e], s4.y, oa[1][1]);
-                    oa[1][2] = fmaf(q1[e], s4.z, oa[1][2]); oa[1][3] = fmaf(q1[e], s4.w, oa[1][3]);
-                }
+            const __nv_bfloat16 *q0 = Qh + (16 * mt + g) * kPadH + t4, *q1 = q0 + 8 * kPadH;
+            const float *sb = S + t4 * kPadS + 16 * nh + g;
+#pragma unroll 4
+            for (int k0 = 0; k0 < kDK; k0 += 8) {
+                const uint32_t af[4] = {tf32_of_bf16(q0 + k0), tf32_of_bf16(q1 + k0), tf32_of_bf16(q0 + k0 + 4), tf32_of_bf16(q1 + k0 + 4)};
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+                    mma_tf32(oa[nt], af, tf32_of(sb[k0 * kPadS + 8 * nt]), tf32_of(sb[(k0 + 4) * kPadS + 8 * nt]));
             }
-    #pragma unroll
-            for (int r = 0; r < 2; r++) {
-                const float g = eca[2 * ty + r];
-    #pragma unroll
-                for (int j = 0; j < 4; j++) oa[r][j] *= g;
+            const float e0 = eca[16 * mt + g], e1 = eca[16 * mt + g + 8];
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) { oa[nt][0] *= e0; oa[nt][1] *= e0; oa[nt][2] *= e1; oa[nt][3] *= e1; }
+            const __nv_bfloat16 *p0 = Ph + (16 * mt + g) * kPadP + t4, *p1 = p0 + 8 * kPadP;
+            const float *ub = U + t4 * kPadS + 16 * nh + g;
+#pragma unroll 4
+            for (int k0 = 0; k0 < kC; k0 += 8) {
+                const uint32_t af[4] = {tf32_of_bf16(p0 + k0), tf32_of_bf16(p1 + k0), tf32_of_bf16(p0 + k0 + 4), tf32_of_bf16(p1 + k0 + 4)};
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+                    mma_tf32(oa[nt], af, tf32_of(ub[k0 * kPadS + 8 * nt]), tf32_of(ub[(k0 + 4) * kPadS + 8 * nt]));
             }
-            for (int s = 0; s < kC; s += 8) {
-                float p0[8], p1[8];
-                unpack8(Ph + (2 * ty) * kPadP + s, p0);
-                unpack8(Ph + (2 * ty + 1) * kPadP + s, p1);
-    #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const float4 u4 = *reinterpret_cast<const float4 *>(U + (s + e) * kDVP + 4 * tx);
-                    oa[0][0] = fmaf(p0[e], u4.x, oa[0][0]); oa[0][1] = fmaf(p0[e], u4.y, oa[0][1]);
-                    oa[0][2] = fmaf(p0[e], u4.z, oa[0][2]); oa[0][3] = fmaf(p0[e], u4.w, oa[0][3]);
-                    oa[1][0] = fmaf(p1[e], u4.x, oa[1][0]); oa[1][1] = fmaf(p1[e], u4.y, oa[1][1]);
-                    oa[1][2] = fmaf(p1[e], u4.z, oa[1][2]); oa[1][3] = fmaf(p1[e], u4.w, oa[1][3]);
-                }
-            }
-    #pragma unroll
-            for (int r = 0; r < 2; r++)
-    #pragma unroll
-                for (int j = 0; j < 4; j++) Oh[(4 * tx + j) * kPadP + 2 * ty + r] = __float2bfloat16_rn(oa[r][j]);
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    Oh[(16 * nh + 8 * nt + 2 * t4 + (e & 1)) * kPadP + 16 * mt + g + 8 * (e >> 1)] = __float2bfloat16_rn(oa[nt][e]);
         }
         __syncthreads();   // every reader of S is done; the staged output is complete
 
@@ -269,32 +282,34 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
                                        static_cast<long long>(chunk) * kC + c) =
                 *reinterpret_cast<const uint4 *>(Oh + f * kPadP + c);
         }
-        // S <- e^{ca_C} S + (e^{ca_C - ca} K)' U : rows 4 ty2 .. +3 of S, columns 4 tx .. +3
+        // S <- e^{ca_C} S + (e^{ca_C - ca} K)' U : warp -> 16 state rows, all 32 features
         {
             const float gamma = gamma_sm;
             float sa[4][4];
+            float *s0 = S + (16 * warp + g) * kPadS + 2 * t4, *s1 = s0 + 8 * kPadS;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float4 s4 = *reinterpret_cast<const float4 *>(S + (4 * ty + i) * kDVP + 4 * tx);
-                sa[i][0] = gamma * s4.x; sa[i][1] = gamma * s4.y; sa[i][2] = gamma * s4.z; sa[i][3] = gamma * s4.w;
+            for (int nt = 0; nt < 4; nt++) {
+                const float2 lo = *reinterpret_cast<const float2 *>(s0 + 8 * nt), hi = *reinterpret_cast<const float2 *>(s1 + 8 * nt);
+                sa[nt][0] = gamma * lo.x; sa[nt][1] = gamma * lo.y; sa[nt][2] = gamma * hi.x; sa[nt][3] = gamma * hi.y;
             }
-            for (int t = 0; t < kC; t++) {
-                const float e = ekd[t];
-                const uint2 kb = *reinterpret_cast<const uint2 *>(Kh + t * kPadH + 4 * ty);
-                float kv[4];
-                unpack_bf16x2(kb.x, kv[0], kv[1]);
-                unpack_bf16x2(kb.y, kv[2], kv[3]);
-                const float4 u4 = *reinterpret_cast<const float4 *>(U + t * kDVP + 4 * tx);
+            // A[i][t] = ekd[t] K[t][i]: rows i = 16 warp + g (+8), columns t = k0 + t4 (+4)
+            const __nv_bfloat16 *kb = Kh + t4 * kPadH + 16 * warp + g;
+            const float *ub = U + t4 * kPadS + g;
+#pragma unroll 2
+            for (int k0 = 0; k0 < kC; k0 += 8) {
+                const float ea = ekd[k0 + t4], eb = ekd[k0 + t4 + 4];
+                const uint32_t af[4] = {tf32_of(__bfloat162float(kb[k0 * kPadH]) * ea), tf32_of(__bfloat162float(kb[k0 * kPadH + 8]) * ea),
+                                        tf32_of(__bfloat162float(kb[(k0 + 4) * kPadH]) * eb),
+                                        tf32_of(__bfloat162float(kb[(k0 + 4) * kPadH + 8]) * eb)};
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float kd = kv[i] * e;
-                    sa[i][0] = fmaf(kd, u4.x, sa[i][0]); sa[i][1] = fmaf(kd, u4.y, sa[i][1]);
-                    sa[i][2] = fmaf(kd, u4.z, sa[i][2]); sa[i][3] = fmaf(kd, u4.w, sa[i][3]);
-                }
+                for (int nt = 0; nt < 4; nt++)
+                    mma_tf32(sa[nt], af, tf32_of(ub[k0 * kPadS + 8 * nt]), tf32_of(ub[(k0 + 4) * kPadS + 8 * nt]));
             }
 #pragma unroll
-            for (int i = 0; i < 4; i++)
-                *reinterpret_cast<float4 *>(S + (4 * ty + i) * kDVP + 4 * tx) = make_float4(sa[i][0], sa[i][1], sa[i][2], sa[i][3]);
+            for (int nt = 0; nt < 4; nt++) {
+                *reinterpret_cast<float2 *>(s0 + 8 * nt) = make_float2(sa[nt][0], sa[nt][1]);
+                *reinterpret_cast<float2 *>(s1 + 8 * nt) = make_float2(sa[nt][2], sa[nt][3]);
+            }
         }
     }
 }
@@ -835,7 +850,7 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
 }
 
 constexpr size_t kChunkSmem = (2 * kC * kPadF + kC * kC + 2 * kC) * sizeof(float);
-constexpr size_t kScanSmem = (kDK * kDVP + 2 * kC * kDVP + 2 * kC) * sizeof(float) +
+constexpr size_t kScanSmem = (kDK * kPadS + kC * kPadS + 2 * kC) * sizeof(float) +
                              (3 * kC * kPadH + kC * kPadP + kDVP * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdScanSmem = (kDK * kDVP + 3 * kC * kDVP + kC * 65 + 3 * kC) * sizeof(float) +
                                 (2 * kC * kPadH + kC * kPadP) * sizeof(__nv_bfloat16);
