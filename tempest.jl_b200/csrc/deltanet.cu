@@ -34,6 +34,20 @@ constexpr int kPadP = 72;     // BFloat16 row pitch of a 64-wide tile
 
 __device__ __forceinline__ float bf16_bits_to_float(unsigned short h) { return __uint_as_float(static_cast<uint32_t>(h) << 16); }
 
+// Inclusive running sum of a chunk's 64 log-decay gates by one warp: lane l gets ca[l] and ca[l + 32].  (One
+// thread adding them in turn would wait for 64 loads one after another at the head of every link of the
+// chain of chunks.)
+__device__ __forceinline__ void chunk_cumsum(const float *a, int lane, float &lo, float &hi) {
+    lo = __ldg(a + lane);
+    hi = __ldg(a + lane + 32);
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const float l2 = __shfl_up_sync(0xffffffffu, lo, off), h2 = __shfl_up_sync(0xffffffffu, hi, off);
+        if (lane >= off) { lo += l2; hi += h2; }
+    }
+    hi += __shfl_sync(0xffffffffu, lo, 31);
+}
+
 // ---------------------------------------------------------------- within a chunk ----
 
 // With minv_save (the backward's first launch) the block has 320 threads: the extra 64 solve
@@ -63,9 +77,11 @@ __global__ void __launch_bounds__(320) deltanet_chunk_kernel(const __nv_bfloat16
         for (int e = 0; e < 8; e++) { Kf[r * kPadF + c + e] = kv[e]; Qf[r * kPadF + c + e] = qv[e]; }
     }
     if (tid < kC) be[tid] = beta[row0 + tid];
-    if (tid == 0) {
-        float s = 0.0f;
-        for (int t = 0; t < kC; t++) { s += a[row0 + t]; ca[t] = s; }
+    if (tid < 32) {
+        float lo, hi;
+        chunk_cumsum(a + row0, tid, lo, hi);
+        ca[tid] = lo;
+        ca[tid + 32] = hi;
     }
     __syncthreads();
 
@@ -210,12 +226,13 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
             *reinterpret_cast<uint4 *>(Ph + r * kPadP + c) =
                 __ldg(reinterpret_cast<const uint4 *>(p_in + (static_cast<long long>(head) * chunks + chunk) * kC * kC + r * kC + c));
         }
-        if (tid == 0) {
-            float s = 0.0f;
-            for (int t = 0; t < kC; t++) { s += a[row0 + t]; eca[t] = s; }
-            const float last = s;
-            for (int t = 0; t < kC; t++) { const float c = eca[t]; ekd[t] = __expf(last - c); eca[t] = __expf(c); }
-            gamma_sm = __expf(last);
+        if (tid < 32) {
+            float lo, hi;
+            chunk_cumsum(a + row0, tid, lo, hi);
+            const float last = __shfl_sync(0xffffffffu, hi, 31);
+            eca[tid] = __expf(lo); eca[tid + 32] = __expf(hi);
+            ekd[tid] = __expf(last - lo); ekd[tid + 32] = __expf(last - hi);
+            if (tid == 0) gamma_sm = __expf(last);
         }
         __syncthreads();
 
@@ -379,12 +396,13 @@ __global__ void __launch_bounds__(256) deltanet_bwd_scan_kernel(
             for (int e = 0; e < 8; e++) dOs[(t8 + e) * kDVP + f] = dv8[e];
         }
         if (tid < kC) be[tid] = beta[row0 + tid];
-        if (tid == 0) {
-            float s = 0.0f;
-            for (int t = 0; t < kC; t++) { s += a[row0 + t]; eca[t] = s; }
-            const float last = s;
-            for (int t = 0; t < kC; t++) { const float c = eca[t]; ekd[t] = __expf(last - c); eca[t] = __expf(c); }
-            gamma_sm = __expf(last);
+        if (tid < 32) {
+            float lo, hi;
+            chunk_cumsum(a + row0, tid, lo, hi);
+            const float last = __shfl_sync(0xffffffffu, hi, 31);
+            eca[tid] = __expf(lo); eca[tid + 32] = __expf(hi);
+            ekd[tid] = __expf(last - lo); ekd[tid + 32] = __expf(last - hi);
+            if (tid == 0) gamma_sm = __expf(last);
         }
         __syncthreads();
 
@@ -506,9 +524,11 @@ __global__ void __launch_bounds__(256) deltanet_bwd_xg_kernel(const float *a, co
         *reinterpret_cast<float4 *>(Us + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(u_save + (row0 + r) * kDV + c));
         *reinterpret_cast<float4 *>(dZs + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(dz_save + (row0 + r) * kDV + c));
     }
-    if (tid == 0) {
-        float s = 0.0f;
-        for (int t = 0; t < kC; t++) { s += a[row0 + t]; ca[t] = s; }
+    if (tid < 32) {
+        float lo, hi;
+        chunk_cumsum(a + row0, tid, lo, hi);
+        ca[tid] = lo;
+        ca[tid + 32] = hi;
     }
     __syncthreads();
     const int ty = tid >> 4, tx = tid & 15;
@@ -631,12 +651,13 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
         Gs[(i / kC) * 65 + (i % kC)] = __ldg(g_in + row0 * kC + i);
     }
     if (tid < kC) be[tid] = beta[row0 + tid];
-    if (tid == 0) {
-        float s = 0.0f;
-        for (int t = 0; t < kC; t++) { s += a[row0 + t]; eca[t] = s; }
-        const float last = s;
-        for (int t = 0; t < kC; t++) { const float c = eca[t]; ekd[t] = __expf(last - c); eca[t] = __expf(c); }
-        gamma_sm = __expf(last);
+    if (tid < 32) {
+        float lo, hi;
+        chunk_cumsum(a + row0, tid, lo, hi);
+        const float last = __shfl_sync(0xffffffffu, hi, 31);
+        eca[tid] = __expf(lo); eca[tid + 32] = __expf(hi);
+        ekd[tid] = __expf(last - lo); ekd[tid + 32] = __expf(last - hi);
+        if (tid == 0) gamma_sm = __expf(last);
     }
     __syncthreads();
 
