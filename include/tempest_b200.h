@@ -241,6 +241,32 @@ int tb200_attention_bwd(const tb200_attn_desc *desc, const void *q, const void *
 
 int tb200_attention_bwd_device_error(void);
 
+/* Masks the device holds, and operands at other strides.  Two of the reference's
+ * mask programs (test/cuda/attention.jl:217-246, 248-275; the scheduling side is
+ * ext/cuTileExt/mask.jl:299-353):
+ *   packed documents -- with `causal`, query j sees keys doc_start[b][j] <= i <= j
+ *     (0-based here; FlashAttention's variable-length batches);
+ *   lengths -- keys at and beyond kv_len[b] are masked (decode over a cache).
+ * A query that sees no key gets a zero output and a log-sum-exp of -Inf.
+ * Strides are in elements over (batch, position, head) with the features
+ * contiguous; all zero = the dense [batch][position][head][feature] default.  A
+ * key cache laid out (features, positions, key heads, sequences) is
+ * kv_stride = {kv_heads * keys * d, d, keys * d}.  These entries run the
+ * CUDA-core kernels for every head dimension up to 256 (the tensor-core kernels
+ * take the unmasked and the plain causal programs). */
+typedef struct tb200_attn_mask {
+    const int32_t *doc_start;   /* [batch][queries] or NULL */
+    const int32_t *kv_len;      /* [batch] or NULL */
+    int64_t q_stride[3];        /* q, o, dq, dout */
+    int64_t kv_stride[3];       /* k, v, dk, dv */
+} tb200_attn_mask;
+
+int tb200_attention_fwd_masked(const tb200_attn_desc *desc, const tb200_attn_mask *mask, const void *q,
+                               const void *k, const void *v, void *o, float *lse, void *stream);
+int tb200_attention_bwd_masked(const tb200_attn_desc *desc, const tb200_attn_mask *mask, const void *q,
+                               const void *k, const void *v, const void *o, const float *lse, const void *dout,
+                               void *dq, void *dk, void *dv, void *stream);
+
 /* ---- chunked gated DeltaNet ------------------------------------------------------
  * The program of examples/deltanet.jl:56-85: q, k (dk, T, heads) = memory
  * [head][t][dk], v (dv, T, heads), a (log decay) and beta (T, heads) in

@@ -371,8 +371,11 @@ def attention_bwd(q, k, v, o, lse, dout, causal, scale=None, round_p=False, thre
     return dq, dk, dv
 
 
-def attention_f64(q, k, v, causal, scale=None, dout=None):
-    """Float64 closed form on the BFloat16 inputs: (o, lse) and, with dout, (dq, dk, dv)."""
+def attention_f64(q, k, v, causal, scale=None, dout=None, doc_start=None, kv_len=None):
+    """Float64 closed form on the BFloat16 inputs: (o, lse) and, with dout, (dq, dk, dv).
+    doc_start [B][S] (0-based first key each query sees) and kv_len [B] are the masks of the reference's
+    packed-documents and decode programs (test/cuda/attention.jl:223-228, 256-260); a query that sees no key
+    gets a zero output, a log-sum-exp of -Inf and no gradient."""
     qf, kf, vf = (from_bf16(a).astype(np.float64) for a in (q, k, v))
     B, S, H, D = qf.shape
     Skv, Hkv = kf.shape[1], kf.shape[2]
@@ -383,12 +386,20 @@ def attention_f64(q, k, v, causal, scale=None, dout=None):
     if causal:
         mask = np.arange(Skv)[None, :] > np.arange(S)[:, None]
         s = np.where(mask[None, None], -np.inf, s)
+    if doc_start is not None:
+        before = np.arange(Skv)[None, None, :] < np.asarray(doc_start)[:, :, None]      # [B][S][Skv]
+        s = np.where(before[:, None], -np.inf, s)
+    if kv_len is not None:
+        beyond = np.arange(Skv)[None, :] >= np.asarray(kv_len)[:, None]                  # [B][Skv]
+        s = np.where(beyond[:, None, None, :], -np.inf, s)
     mx = s.max(axis=-1, keepdims=True)
+    mx = np.where(np.isfinite(mx), mx, 0.0)
     e = np.exp(s - mx)
     l = e.sum(axis=-1, keepdims=True)
-    p = e / l
+    with np.errstate(divide="ignore", invalid="ignore"):
+        p = np.where(l > 0, e / l, 0.0)
+        lse = np.where(l > 0, mx + np.log(l), -np.inf)[..., 0].transpose(0, 2, 1)
     o = np.einsum("bhmn,bnhd->bmhd", p, vx)
-    lse = (mx + np.log(l))[..., 0].transpose(0, 2, 1)
     if dout is None:
         return o, lse
     go = from_bf16(dout).astype(np.float64)

@@ -23,7 +23,20 @@ constexpr int kWarps = 4;
 struct SimtArgs {
     int batch, heads, kv_heads, queries, keys, d, causal;
     float scale;
+    long long qb, qs, qh;          // element strides of q, o, dq, dout over (batch, position, head)
+    long long kb, ks, kh;          // and of k, v, dk, dv
+    const int *doc_start;          // [batch][queries]: first key a query sees, or null
+    const int *kv_len;             // [batch]: keys from this index on are masked, or null
 };
+
+// the keys query i of batch b sees: [first, last]
+__device__ __forceinline__ void key_range(const SimtArgs &a, int b, int i, int &first, int &last) {
+    first = a.doc_start ? a.doc_start[static_cast<long long>(b) * a.queries + i] : 0;
+    last = a.causal ? i : a.keys - 1;
+    if (a.kv_len) last = min(last, a.kv_len[b] - 1);
+    if (last > a.keys - 1) last = a.keys - 1;
+    if (first < 0) first = 0;
+}
 
 __device__ __forceinline__ float ldbf(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
 
@@ -46,17 +59,18 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_fwd_kernel(const _
     const int i = blockIdx.x * kWarps + warp, h = blockIdx.y, b = blockIdx.z;
     if (i >= a.queries) return;
     const int g = h / (a.heads / a.kv_heads);
-    const long long qrow = ((static_cast<long long>(b) * a.queries + i) * a.heads + h) * a.d;
+    const long long qrow = b * a.qb + i * a.qs + h * a.qh;
     for (int d = lane; d < a.d; d += 32) qs[warp][d] = ldbf(q + qrow + d) * a.scale;
     __syncwarp();
-    const int last = a.causal ? i : a.keys - 1;
+    int first, last;
+    key_range(a, b, i, first, last);
     float m = -INFINITY, l = 0.0f, acc[kMaxD / 32] = {};
-    for (int key0 = 0; key0 <= last; key0 += 32) {
+    for (int key0 = first; key0 <= last; key0 += 32) {
         const int j = key0 + lane;
         const bool valid = j <= last;
         float s = -INFINITY;
         if (valid) {
-            const __nv_bfloat16 *kr = k + ((static_cast<long long>(b) * a.keys + j) * a.kv_heads + g) * a.d;
+            const __nv_bfloat16 *kr = k + b * a.kb + j * a.ks + g * a.kh;
             s = 0.0f;
             for (int d = 0; d < a.d; d++) s = fmaf(qs[warp][d], ldbf(kr + d), s);
         }
@@ -69,7 +83,7 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_fwd_kernel(const _
         const int count = min(32, last - key0 + 1);
         for (int jj = 0; jj < count; jj++) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const __nv_bfloat16 *vr = v + ((static_cast<long long>(b) * a.keys + key0 + jj) * a.kv_heads + g) * a.d;
+            const __nv_bfloat16 *vr = v + b * a.kb + (key0 + jj) * a.ks + g * a.kh;
 #pragma unroll
             for (int c = 0; c < kMaxD / 32; c++) {
                 const int d = lane + 32 * c;
@@ -78,13 +92,13 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_fwd_kernel(const _
         }
         m = m_new;
     }
-    const float inv = 1.0f / l;
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;   // a query that sees no key: zero output, log-sum-exp -Inf
 #pragma unroll
     for (int c = 0; c < kMaxD / 32; c++) {
         const int d = lane + 32 * c;
         if (d < a.d) o[qrow + d] = __float2bfloat16_rn(acc[c] * inv);
     }
-    if (lse && lane == 0) lse[(static_cast<long long>(b) * a.queries + i) * a.heads + h] = m + __logf(l);
+    if (lse && lane == 0) lse[(static_cast<long long>(b) * a.queries + i) * a.heads + h] = l > 0.0f ? m + __logf(l) : -INFINITY;
 }
 
 __global__ void __launch_bounds__(kWarps * 32) attention_simt_dq_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
@@ -96,7 +110,7 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dq_kernel(const __
     const int i = blockIdx.x * kWarps + warp, h = blockIdx.y, b = blockIdx.z;
     if (i >= a.queries) return;
     const int g = h / (a.heads / a.kv_heads);
-    const long long qrow = ((static_cast<long long>(b) * a.queries + i) * a.heads + h) * a.d;
+    const long long qrow = b * a.qb + i * a.qs + h * a.qh;
     float delta = 0.0f;
     for (int d = lane; d < a.d; d += 32) {
         qs[warp][d] = ldbf(q + qrow + d) * a.scale;
@@ -107,13 +121,14 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dq_kernel(const __
     delta = warp_sum(delta);
     __syncwarp();
     const float L = lse[(static_cast<long long>(b) * a.queries + i) * a.heads + h];
-    const int last = a.causal ? i : a.keys - 1;
+    int first, last;
+    key_range(a, b, i, first, last);
     float acc[kMaxD / 32] = {};
-    for (int key0 = 0; key0 <= last; key0 += 32) {
+    for (int key0 = first; key0 <= last; key0 += 32) {
         const int j = key0 + lane;
         float ds = 0.0f;
         if (j <= last) {
-            const long long kv = ((static_cast<long long>(b) * a.keys + j) * a.kv_heads + g) * a.d;
+            const long long kv = b * a.kb + j * a.ks + g * a.kh;
             float s = 0.0f, dp = 0.0f;
             for (int d = 0; d < a.d; d++) {
                 s = fmaf(qs[warp][d], ldbf(k + kv + d), s);
@@ -124,7 +139,7 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dq_kernel(const __
         const int count = min(32, last - key0 + 1);
         for (int jj = 0; jj < count; jj++) {
             const float dsj = __shfl_sync(0xffffffffu, ds, jj);
-            const __nv_bfloat16 *kr = k + ((static_cast<long long>(b) * a.keys + key0 + jj) * a.kv_heads + g) * a.d;
+            const __nv_bfloat16 *kr = k + b * a.kb + (key0 + jj) * a.ks + g * a.kh;
 #pragma unroll
             for (int c = 0; c < kMaxD / 32; c++) {
                 const int d = lane + 32 * c;
@@ -147,7 +162,8 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dkdv_kernel(const 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int j = blockIdx.x * kWarps + warp, g = blockIdx.y, b = blockIdx.z;
     if (j >= a.keys) return;
-    const long long krow = ((static_cast<long long>(b) * a.keys + j) * a.kv_heads + g) * a.d;
+    const long long krow = b * a.kb + j * a.ks + g * a.kh;
+    const bool key_live = !a.kv_len || j < a.kv_len[b];
     for (int d = lane; d < a.d; d += 32) {
         ks[warp][d] = ldbf(k + krow + d) * a.scale;
         vs[warp][d] = ldbf(v + krow + d);
@@ -160,8 +176,9 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dkdv_kernel(const 
         for (int i0 = a.causal ? (j / 32) * 32 : 0; i0 < a.queries; i0 += 32) {
             const int i = i0 + lane;
             float p = 0.0f, ds = 0.0f;
-            if (i < a.queries && (!a.causal || i >= j)) {
-                const long long qr = ((static_cast<long long>(b) * a.queries + i) * a.heads + h) * a.d;
+            if (key_live && i < a.queries && (!a.causal || i >= j) &&
+                (!a.doc_start || a.doc_start[static_cast<long long>(b) * a.queries + i] <= j)) {
+                const long long qr = b * a.qb + i * a.qs + h * a.qh;
                 float s = 0.0f, dp = 0.0f, delta = 0.0f;
                 for (int d = 0; d < a.d; d++) {
                     const float gd = ldbf(dout + qr + d);
@@ -176,7 +193,7 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dkdv_kernel(const 
             for (int ii = 0; ii < count; ii++) {
                 const float pi = __shfl_sync(0xffffffffu, p, ii), dsi = __shfl_sync(0xffffffffu, ds, ii);
                 if (pi == 0.0f && dsi == 0.0f) continue;   // masked (uniform across the warp)
-                const long long qr = ((static_cast<long long>(b) * a.queries + i0 + ii) * a.heads + h) * a.d;
+                const long long qr = b * a.qb + (i0 + ii) * a.qs + h * a.qh;
 #pragma unroll
                 for (int c = 0; c < kMaxD / 32; c++) {
                     const int d = lane + 32 * c;
@@ -198,8 +215,20 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dkdv_kernel(const 
     }
 }
 
-SimtArgs simt_args(const tb200_attn_desc *d) {
-    return SimtArgs{d->batch, d->heads, d->kv_heads, d->queries, d->keys, d->head_dim, d->causal, d->scale};
+SimtArgs simt_args(const tb200_attn_desc *d, const tb200_attn_mask *m) {
+    SimtArgs a{};
+    a.batch = d->batch; a.heads = d->heads; a.kv_heads = d->kv_heads; a.queries = d->queries; a.keys = d->keys;
+    a.d = d->head_dim; a.causal = d->causal; a.scale = d->scale;
+    // the dense default: [batch][position][head][feature]
+    a.qh = d->head_dim; a.qs = a.qh * d->heads; a.qb = a.qs * d->queries;
+    a.kh = d->head_dim; a.ks = a.kh * d->kv_heads; a.kb = a.ks * d->keys;
+    if (m) {
+        a.doc_start = m->doc_start;
+        a.kv_len = m->kv_len;
+        if (m->q_stride[0] || m->q_stride[1] || m->q_stride[2]) { a.qb = m->q_stride[0]; a.qs = m->q_stride[1]; a.qh = m->q_stride[2]; }
+        if (m->kv_stride[0] || m->kv_stride[1] || m->kv_stride[2]) { a.kb = m->kv_stride[0]; a.ks = m->kv_stride[1]; a.kh = m->kv_stride[2]; }
+    }
+    return a;
 }
 
 }  // namespace
@@ -209,29 +238,65 @@ bool attention_simt_takes(const tb200_attn_desc *d) {
 }
 
 int attention_simt_fwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, void *o, float *lse,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const tb200_attn_mask *mask) {
     dim3 grid(static_cast<unsigned>(ceil_div(d->queries, kWarps)), d->heads, d->batch);
     attention_simt_fwd_kernel<<<grid, kWarps * 32, 0, stream>>>(
         static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k), static_cast<const __nv_bfloat16 *>(v),
-        static_cast<__nv_bfloat16 *>(o), lse, simt_args(d));
+        static_cast<__nv_bfloat16 *>(o), lse, simt_args(d, mask));
     TB200_CUDA(cudaGetLastError());
     return TB200_OK;
 }
 
 int attention_simt_bwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, const void *o,
-                       const float *lse, const void *dout, void *dq, void *dk, void *dv, cudaStream_t stream) {
+                       const float *lse, const void *dout, void *dq, void *dk, void *dv, cudaStream_t stream,
+                       const tb200_attn_mask *mask) {
     const __nv_bfloat16 *qb = static_cast<const __nv_bfloat16 *>(q), *kb = static_cast<const __nv_bfloat16 *>(k),
                         *vb = static_cast<const __nv_bfloat16 *>(v), *ob = static_cast<const __nv_bfloat16 *>(o),
                         *gb = static_cast<const __nv_bfloat16 *>(dout);
     dim3 gq(static_cast<unsigned>(ceil_div(d->queries, kWarps)), d->heads, d->batch);
     attention_simt_dq_kernel<<<gq, kWarps * 32, 0, stream>>>(qb, kb, vb, ob, lse, gb, static_cast<__nv_bfloat16 *>(dq),
-                                                            simt_args(d));
+                                                            simt_args(d, mask));
     TB200_CUDA(cudaGetLastError());
     dim3 gk(static_cast<unsigned>(ceil_div(d->keys, kWarps)), d->kv_heads, d->batch);
     attention_simt_dkdv_kernel<<<gk, kWarps * 32, 0, stream>>>(qb, kb, vb, ob, lse, gb, static_cast<__nv_bfloat16 *>(dk),
-                                                              static_cast<__nv_bfloat16 *>(dv), simt_args(d));
+                                                              static_cast<__nv_bfloat16 *>(dv), simt_args(d, mask));
     TB200_CUDA(cudaGetLastError());
     return TB200_OK;
 }
 
 }  // namespace tb200
+
+using namespace tb200;
+
+namespace {
+int check_masked(const tb200_attn_desc *d) {
+    if (!d) return TB200_ERR_NULL;
+    if (d->batch < 0 || d->heads <= 0 || d->kv_heads <= 0 || d->queries < 0 || d->keys < 0 || d->head_dim <= 0) return TB200_ERR_SHAPE;
+    if (d->heads % d->kv_heads != 0 || !(d->scale > 0.0f)) return TB200_ERR_SHAPE;
+    if (d->causal && d->queries != d->keys) return TB200_ERR_SHAPE;
+    if (d->dtype != TB200_BF16) return TB200_ERR_DTYPE;
+    if (!attention_simt_takes(d)) return TB200_ERR_UNSUPPORTED;
+    return TB200_OK;
+}
+}  // namespace
+
+extern "C" int tb200_attention_fwd_masked(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q, const void *k,
+                                          const void *v, void *o, float *lse, void *stream) {
+    int st = check_masked(d);
+    if (st) return st;
+    if (d->batch == 0 || d->queries == 0) return TB200_OK;
+    if (d->keys == 0) return TB200_ERR_UNSUPPORTED;
+    if (!q || !k || !v || !o) return TB200_ERR_NULL;
+    return attention_simt_fwd(d, q, k, v, o, lse, static_cast<cudaStream_t>(stream), mask);
+}
+
+extern "C" int tb200_attention_bwd_masked(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q, const void *k,
+                                          const void *v, const void *o, const float *lse, const void *dout, void *dq, void *dk,
+                                          void *dv, void *stream) {
+    int st = check_masked(d);
+    if (st) return st;
+    if (d->batch == 0 || (d->queries == 0 && d->keys == 0)) return TB200_OK;
+    if (d->queries == 0 || d->keys == 0) return TB200_ERR_UNSUPPORTED;
+    if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv) return TB200_ERR_NULL;
+    return attention_simt_bwd(d, q, k, v, o, lse, dout, dq, dk, dv, static_cast<cudaStream_t>(stream), mask);
+}

@@ -7,7 +7,8 @@
 namespace tb200 {
 bool attention_simt_takes(const tb200_attn_desc *d);
 int attention_simt_fwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, void *o, float *lse,
-                       cudaStream_t stream);
+                       cudaStream_t stream, const tb200_attn_mask *mask = nullptr);
 int attention_simt_bwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, const void *o,
-                       const float *lse, const void *dout, void *dq, void *dk, void *dv, cudaStream_t stream);
+                       const float *lse, const void *dout, void *dq, void *dk, void *dv, cudaStream_t stream,
+                       const tb200_attn_mask *mask = nullptr);
 }  // namespace tb200

@@ -39,6 +39,12 @@ class AttnDesc(ctypes.Structure):
                 ("causal", ctypes.c_int), ("scale", ctypes.c_float), ("dtype", ctypes.c_int)]
 
 
+class AttnMask(ctypes.Structure):
+    """tb200_attn_mask of include/tempest_b200.h."""
+    _fields_ = [("doc_start", ctypes.c_void_p), ("kv_len", ctypes.c_void_p),
+                ("q_stride", ctypes.c_int64 * 3), ("kv_stride", ctypes.c_int64 * 3)]
+
+
 class DeltanetDesc(ctypes.Structure):
     """tb200_deltanet_desc of include/tempest_b200.h."""
     _fields_ = [("heads", ctypes.c_int), ("positions", ctypes.c_int), ("dk", ctypes.c_int), ("dv", ctypes.c_int),
@@ -96,6 +102,8 @@ SIGNATURES = {
     "tb200_attention_bwd_device_error": (_i, []),
     "tb200_deltanet_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_fwd": (_i, [ctypes.POINTER(DeltanetDesc), _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "tb200_attention_fwd_masked": (_i, [ctypes.POINTER(AttnDesc), ctypes.POINTER(AttnMask), _p, _p, _p, _p, _p, _p]),
+    "tb200_attention_bwd_masked": (_i, [ctypes.POINTER(AttnDesc), ctypes.POINTER(AttnMask)] + [_p] * 10),
     "tb200_rowreduce_generic_check": (_i, [ctypes.POINTER(GroupDesc)]),
     "tb200_rowreduce_generic": (_i, [ctypes.POINTER(GroupDesc), ctypes.POINTER(_p), ctypes.POINTER(_p), _p]),
     "tb200_rowreduce_compile": (_i, [ctypes.POINTER(GroupDesc), ctypes.c_uint, ctypes.c_uint]),
@@ -357,3 +365,21 @@ def rowreduce_compiled(desc, inputs, outputs, stream=0):
     ins = (_p * max(len(inputs), 1))(*inputs)
     outs = (_p * max(len(outputs), 1))(*outputs)
     check("tb200_rowreduce_compiled", load().tb200_rowreduce_compiled(ctypes.byref(desc), ins, outs, stream or None))
+
+
+def attn_mask(doc_start=0, kv_len=0, q_stride=(0, 0, 0), kv_stride=(0, 0, 0)):
+    m = AttnMask()
+    m.doc_start, m.kv_len = doc_start or None, kv_len or None
+    m.q_stride[:] = q_stride
+    m.kv_stride[:] = kv_stride
+    return m
+
+
+def attention_fwd_masked(desc, mask, q, k, v, o, lse=0, stream=0):
+    check("tb200_attention_fwd_masked", load().tb200_attention_fwd_masked(
+        ctypes.byref(desc), ctypes.byref(mask), q, k, v, o, lse or None, stream or None))
+
+
+def attention_bwd_masked(desc, mask, q, k, v, o, lse, dout, dq, dk, dv, stream=0):
+    check("tb200_attention_bwd_masked", load().tb200_attention_bwd_masked(
+        ctypes.byref(desc), ctypes.byref(mask), q, k, v, o, lse, dout, dq, dk, dv, stream or None))
