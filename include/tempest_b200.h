@@ -194,6 +194,16 @@ int tb200_gemm(const tb200_gemm_desc *desc, const void *a, const void *b, void *
 /* Synchronises the device, then returns and clears the code a tensor-core
  * kernel recorded if one of its bounded waits gave up (0 = none).  No
  * reference counterpart: Tempest's kernels have no device-side waits. */
+/* Measures the compiled-in tile variants of one product on its own operands
+ * and returns the faster tile_n (128 or 256) to put in the descriptor, or a
+ * negative status: the measured stage of the reference's search over a claim's
+ * variants (src/Compiler/Implement/Implement.jl:120,
+ * ext/cuTileExt/contract.jl:171-235) over what this library holds.  Overwrites C
+ * (and aux_out) with the product's own result, synchronises the stream; call it
+ * while building, not inside a capture. */
+int tb200_gemm_tune(const tb200_gemm_desc *desc, const void *a, const void *b, void *c, const void *bias,
+                    const void *aux, void *aux_out, void *stream);
+
 int tb200_device_error(void);
 
 /* ---- attention -----------------------------------------------------------------

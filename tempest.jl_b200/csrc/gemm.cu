@@ -758,3 +758,44 @@ extern "C" int tb200_device_error(void) {
     if (code) TB200_CUDA(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
     return code;
 }
+
+// Times the compiled-in tile variants of one product on its own operands and returns the faster one's
+// tile_n (128 or 256) -- the measured stage of the reference's search over a claim's `variants`
+// (src/Compiler/Implement/Implement.jl:120, ext/cuTileExt/contract.jl:171-235), restricted to what this
+// library holds.  Runs the product several times (C and aux_out are overwritten with the product's own
+// result), synchronises the stream: a build-time call, not one for a capture.  Where there is nothing to
+// choose (narrow outputs, the CUDA-core path, the accumulating epilogue whose repeats would add up) it returns
+// the width tb200_gemm would take without measuring.
+extern "C" int tb200_gemm_tune(const tb200_gemm_desc *d, const void *a, const void *b, void *c, const void *bias, const void *aux,
+                               void *aux_out, void *stream_) {
+    if (!d) return TB200_ERR_NULL;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int fallback = d->n > 128 ? 256 : 128;
+    const bool measurable = d->in_dtype == TB200_BF16 && d->n > 128 && d->m > 0 && d->k > 0 && !d->force_simt &&
+                            d->epilogue != TB200_EPI_AXPY;
+    tb200_gemm_desc trial = *d;
+    if (!measurable) {
+        trial.tile_n = 0;
+        const int st = tb200_gemm(&trial, a, b, c, bias, aux, aux_out, stream_);   // still validates the request
+        return st ? st : fallback;
+    }
+    cudaEvent_t t0, t1;
+    TB200_CUDA(cudaEventCreate(&t0));
+    TB200_CUDA(cudaEventCreate(&t1));
+    float best_ms = 0.0f;
+    int best = fallback, status = TB200_OK;
+    for (int width : {128, 256}) {
+        trial.tile_n = width;
+        if ((status = tb200_gemm(&trial, a, b, c, bias, aux, aux_out, stream_))) break;   // warm-up and validation
+        if (cudaEventRecord(t0, stream) != cudaSuccess) { status = TB200_ERR_CUDA; break; }
+        for (int rep = 0; rep < 3 && !status; rep++) status = tb200_gemm(&trial, a, b, c, bias, aux, aux_out, stream_);
+        if (status) break;
+        float ms = 0.0f;
+        if (cudaEventRecord(t1, stream) != cudaSuccess || cudaEventSynchronize(t1) != cudaSuccess ||
+            cudaEventElapsedTime(&ms, t0, t1) != cudaSuccess) { status = TB200_ERR_CUDA; break; }
+        if (width == 128 || ms < best_ms) { best_ms = ms; best = width; }
+    }
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+    return status ? status : best;
+}

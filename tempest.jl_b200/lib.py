@@ -102,6 +102,7 @@ SIGNATURES = {
     "tb200_attention_bwd_device_error": (_i, []),
     "tb200_deltanet_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_fwd": (_i, [ctypes.POINTER(DeltanetDesc), _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "tb200_gemm_tune": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
     "tb200_attention_fwd_masked": (_i, [ctypes.POINTER(AttnDesc), ctypes.POINTER(AttnMask), _p, _p, _p, _p, _p, _p]),
     "tb200_attention_bwd_masked": (_i, [ctypes.POINTER(AttnDesc), ctypes.POINTER(AttnMask)] + [_p] * 10),
     "tb200_rowreduce_generic_check": (_i, [ctypes.POINTER(GroupDesc)]),
@@ -200,8 +201,9 @@ def layernorm_bwd(x, gamma, dy, mean, rstd, dx, dgamma, dbeta, eps, n, rows, ld,
 
 def gemm(a, b, c, m, n, k, *, lda=None, ldb=None, ldc=None, a_layout=K_MAJOR, b_layout=MN_MAJOR, in_dtype=BF16,
          out_dtype=None, epilogue=EPI_NONE, bias=0, aux=0, ld_aux=None, aux_out=0, ld_aux_out=None, alpha=1.0,
-         tile_n=0, force_simt=False, direct_epilogue=False, stream=0):
-    """C[m][n] = epilogue(alpha * A * B).  a_layout K_MAJOR: A is [m][k]; MN_MAJOR: [k][m].
+         tile_n=0, force_simt=False, direct_epilogue=False, stream=0, tune=False):
+    """C[m][n] = epilogue(alpha * A * B).  With `tune` the compiled-in tile variants are timed on these operands
+    and the faster tile_n is returned (the product's result is in C either way).  a_layout K_MAJOR: A is [m][k]; MN_MAJOR: [k][m].
     b_layout K_MAJOR: B is [n][k]; MN_MAJOR: [k][n] (a Julia (out,in) weight for y = w*x)."""
     d = GemmDesc()
     d.m, d.n, d.k = m, n, k
@@ -215,6 +217,11 @@ def gemm(a, b, c, m, n, k, *, lda=None, ldb=None, ldc=None, a_layout=K_MAJOR, b_
     d.out_dtype = in_dtype if out_dtype is None else out_dtype
     d.epilogue, d.alpha, d.tile_n, d.force_simt = epilogue, alpha, tile_n, int(force_simt)
     d.direct_epilogue = int(direct_epilogue)
+    if tune:
+        width = load().tb200_gemm_tune(ctypes.byref(d), a or None, b or None, c or None, bias or None,
+                                       aux or None, aux_out or None, stream or None)
+        check("tb200_gemm_tune", min(width, 0))
+        return width
     check("tb200_gemm", load().tb200_gemm(ctypes.byref(d), a or None, b or None, c or None, bias or None,
                                           aux or None, aux_out or None, stream or None))
 

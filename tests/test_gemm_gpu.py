@@ -316,3 +316,24 @@ def test_products_and_attention_through_the_plugin_mirror(pkg, cuda, oracle):
     for got, want in ((dq, dq64), (dk, dk64), (dv, dv64)):
         gotf = oracle.from_bf16(host(torch, got))
         assert np.abs(gotf - want).max() <= ATOL_BF16 * max(1.0, np.abs(want).max())
+
+
+def test_tune_returns_a_variant_and_leaves_the_product(pkg, cuda, oracle):
+    """tb200_gemm_tune times the 128- and 256-wide tiles on the operands, returns one of them, and C holds the
+    product; where there is nothing to choose it answers without measuring."""
+    torch, L = cuda, pkg.lib
+    M, N, K = 512, 1024, 256
+    A = torch.randn(M, K, device="cuda").bfloat16()
+    B = torch.randn(K, N, device="cuda").bfloat16()
+    C = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    width = L.gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, tune=True)
+    assert width in (128, 256)
+    want = A.float() @ B.float()
+    assert (C.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    C2 = torch.zeros_like(C)
+    L.gemm(A.data_ptr(), B.data_ptr(), C2.data_ptr(), M, N, K, tile_n=width)
+    assert torch.equal(C, C2)
+    narrow = torch.zeros(M, 64, device="cuda", dtype=torch.bfloat16)
+    assert L.gemm(A.data_ptr(), B.data_ptr(), narrow.data_ptr(), M, 64, K, ldb=N, tune=True) == 128
+    with pytest.raises(L.TB200Error):
+        L.gemm(0, B.data_ptr(), C.data_ptr(), M, N, K, tune=True)
