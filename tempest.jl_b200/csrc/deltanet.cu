@@ -174,6 +174,17 @@ __device__ __forceinline__ uint32_t tf32_of_bf16(const __nv_bfloat16 *p) {
 
 constexpr int kPadS = 40;   // Float32 row pitch of the 32-wide state and U tiles: B-fragment reads hit 32 banks
 
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+                 "l"(gmem_src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// The tiles of the next chunk are copied asynchronously into their buffers as soon as the current chunk's
+// last reader of each is past (W after the first product, Q and P after the second; K has two buffers), and
+// the next chunk's gates and Ut values are fetched meanwhile: a link of the chain waits for no load.
 __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
                                                             const float *a, const __nv_bfloat16 *w_in,
                                                             const __nv_bfloat16 *u_in, const __nv_bfloat16 *p_in,
@@ -181,14 +192,14 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
     extern __shared__ float sm[];
     float *S = sm;                                      // [128][40] the state slice
     float *U = S + kDK * kPadS;                         // [64][40]
-    float *eca = U + kC * kPadS;                        // [64] exp(ca)
-    float *ekd = eca + kC;                              // [64] exp(ca_C - ca)
-    __nv_bfloat16 *Wh = reinterpret_cast<__nv_bfloat16 *>(ekd + kC);   // [64][136]
+    float *eca2 = U + kC * kPadS;                       // [2][64] exp(ca), per chunk parity
+    float *ekd2 = eca2 + 2 * kC;                        // [2][64] exp(ca_C - ca)
+    __nv_bfloat16 *Wh = reinterpret_cast<__nv_bfloat16 *>(ekd2 + 2 * kC);   // [64][136]
     __nv_bfloat16 *Qh = Wh + kC * kPadH;
-    __nv_bfloat16 *Kh = Qh + kC * kPadH;
-    __nv_bfloat16 *Ph = Kh + kC * kPadH;                // [64][72]
+    __nv_bfloat16 *Kh2 = Qh + kC * kPadH;               // [2][64][136]
+    __nv_bfloat16 *Ph = Kh2 + 2 * kC * kPadH;           // [64][72]
     __nv_bfloat16 *Oh = Ph + kC * kPadP;                // [32][72] output staging, [feature][position]
-    __shared__ float gamma_sm;
+    __shared__ float gamma_sm[2];
 
     const int head = blockIdx.x, part = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -198,10 +209,30 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
 
     // U and o: warp -> 16 positions (mt) x 16 features (nh), two 8-feature tiles
     const int mt = warp & 3, nh = warp >> 2;
-    for (int chunk = 0; chunk < chunks; chunk++) {
-        const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
-        // Ut at this thread's accumulator positions, straight from global memory (latency hides behind the tile loads)
-        float acc[2][4];
+    const long long head_row = static_cast<long long>(head) * T;
+    auto copy_rows = [&](__nv_bfloat16 *dst, const __nv_bfloat16 *src, long long row0) {   // a [64][128] tile
+        for (int i = tid; i < kC * kDK / 8; i += 256) {
+            const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
+            cp_async16(dst + r * kPadH + c, src + (row0 + r) * kDK + c);
+        }
+    };
+    auto copy_p = [&](int chunk) {
+        for (int i = tid; i < kC * kC / 8; i += 256) {
+            const int r = i / (kC / 8), c = (i % (kC / 8)) * 8;
+            cp_async16(Ph + r * kPadP + c, p_in + (static_cast<long long>(head) * chunks + chunk) * kC * kC + r * kC + c);
+        }
+    };
+    auto gates = [&](int chunk) {   // warp 0
+        float lo, hi;
+        chunk_cumsum(a + head_row + static_cast<long long>(chunk) * kC, lane, lo, hi);
+        const float last = __shfl_sync(0xffffffffu, hi, 31);
+        float *eca = eca2 + (chunk & 1) * kC, *ekd = ekd2 + (chunk & 1) * kC;
+        eca[lane] = __expf(lo); eca[lane + 32] = __expf(hi);
+        ekd[lane] = __expf(last - lo); ekd[lane + 32] = __expf(last - hi);
+        if (lane == 0) gamma_sm[chunk & 1] = __expf(last);
+    };
+    auto fetch_ut = [&](int chunk, float (&acc)[2][4]) {   // Ut at this thread's accumulator positions
+        const long long row0 = head_row + static_cast<long long>(chunk) * kC;
 #pragma unroll
         for (int nt = 0; nt < 2; nt++)
 #pragma unroll
@@ -210,31 +241,29 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
                     u_in + (row0 + 16 * mt + g + 8 * hr) * kDV + part * kDVP + 16 * nh + 8 * nt + 2 * t4));
                 unpack_bf16x2(two, acc[nt][2 * hr], acc[nt][2 * hr + 1]);
             }
-        __syncthreads();   // the previous chunk's readers are done with the tiles
+    };
+
+    float acc[2][4];
+    if (chunks > 0) {
+        copy_rows(Wh, w_in, head_row);
+        copy_rows(Qh, q, head_row);
+        copy_rows(Kh2, k, head_row);
+        copy_p(0);
+        cp_async_commit();
+        if (warp == 0) gates(0);
+        fetch_ut(0, acc);
+    }
+    for (int chunk = 0; chunk < chunks; chunk++) {
+        const long long row0 = head_row + static_cast<long long>(chunk) * kC;
+        const float *eca = eca2 + (chunk & 1) * kC, *ekd = ekd2 + (chunk & 1) * kC;
+        const __nv_bfloat16 *Kh = Kh2 + (chunk & 1) * kC * kPadH;
+        const bool more = chunk + 1 < chunks;
+        cp_async_wait_all();
+        __syncthreads();   // this chunk's tiles and gates are in place; the previous chunk's state update is complete
         if (s_save) {      // the state this chunk starts from, for the backward
             float *dst = s_save + (static_cast<long long>(head) * chunks + chunk) * kDK * kDV + part * kDVP;
             for (int i = tid; i < kDK * kDVP; i += 256) dst[(i / kDVP) * kDV + (i % kDVP)] = S[(i / kDVP) * kPadS + (i % kDVP)];
         }
-        for (int i = tid; i < kC * kDK / 8; i += 256) {
-            const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
-            *reinterpret_cast<uint4 *>(Wh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(w_in + (row0 + r) * kDK + c));
-            *reinterpret_cast<uint4 *>(Qh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(q + (row0 + r) * kDK + c));
-            *reinterpret_cast<uint4 *>(Kh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(k + (row0 + r) * kDK + c));
-        }
-        for (int i = tid; i < kC * kC / 8; i += 256) {
-            const int r = i / (kC / 8), c = (i % (kC / 8)) * 8;
-            *reinterpret_cast<uint4 *>(Ph + r * kPadP + c) =
-                __ldg(reinterpret_cast<const uint4 *>(p_in + (static_cast<long long>(head) * chunks + chunk) * kC * kC + r * kC + c));
-        }
-        if (tid < 32) {
-            float lo, hi;
-            chunk_cumsum(a + row0, tid, lo, hi);
-            const float last = __shfl_sync(0xffffffffu, hi, 31);
-            eca[tid] = __expf(lo); eca[tid + 32] = __expf(hi);
-            ekd[tid] = __expf(last - lo); ekd[tid + 32] = __expf(last - hi);
-            if (tid == 0) gamma_sm = __expf(last);
-        }
-        __syncthreads();
 
         // U = Ut - W S
         {
@@ -258,7 +287,14 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
                     if (u_save) *reinterpret_cast<float2 *>(u_save + (row0 + row) * kDV + part * kDVP + col) = u2;
                 }
         }
-        __syncthreads();
+        __syncthreads();   // U is complete; W has been read
+        if (more) {
+            copy_rows(Wh, w_in, row0 + kC);
+            copy_rows(Kh2 + ((chunk + 1) & 1) * kC * kPadH, k, row0 + kC);
+            cp_async_commit();
+            if (warp == 0) gates(chunk + 1);
+            fetch_ut(chunk + 1, acc);
+        }
 
         // o = (e^ca Q) S + P U
         if (o) {
@@ -290,7 +326,12 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
                 for (int e = 0; e < 4; e++)
                     Oh[(16 * nh + 8 * nt + 2 * t4 + (e & 1)) * kPadP + 16 * mt + g + 8 * (e >> 1)] = __float2bfloat16_rn(oa[nt][e]);
         }
-        __syncthreads();   // every reader of S is done; the staged output is complete
+        __syncthreads();   // every reader of S, Q and P is done; the staged output is complete
+        if (more) {
+            copy_rows(Qh, q, row0 + kC);
+            copy_p(chunk + 1);
+            cp_async_commit();
+        }
 
         // the result is (positions, features): 128 contiguous bytes per feature
         if (o) {
@@ -301,7 +342,7 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
         }
         // S <- e^{ca_C} S + (e^{ca_C - ca} K)' U : warp -> 16 state rows, all 32 features
         {
-            const float gamma = gamma_sm;
+            const float gamma = gamma_sm[chunk & 1];
             float sa[4][4];
             float *s0 = S + (16 * warp + g) * kPadS + 2 * t4, *s1 = s0 + 8 * kPadS;
 #pragma unroll
@@ -345,17 +386,22 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
 // It is the chain rule through examples/deltanet.jl:58-85 taken by hand; Tempest derives the same
 // pullback from the forward program (examples/deltanet.jl:96-101).
 
-// One block per (head, 32 value features), chunks walked last to first.
+// One block per (head, 32 value features), chunks walked last to first.  The four products of a chunk are
+// TF32 warp-level MMAs as in the forward scan: dU and dZ take warp -> 16 positions x 16 features, the state
+// gradient takes warp -> 16 state rows x 32 features; transposed operands (P', Minv', (e Q)', (e beta K)') are
+// read transposed from the tiles as they lie.
+constexpr int kPadM = 72;   // Float32 row pitch of (I + A)^-1: transposed A-fragment reads hit 32 banks
+
 __global__ void __launch_bounds__(256) deltanet_bwd_scan_kernel(
     const __nv_bfloat16 *q, const __nv_bfloat16 *k, const float *a, const float *beta, const __nv_bfloat16 *p_in,
     const float *minv, const __nv_bfloat16 *dout, float *dsin_save, float *dz_save, __nv_bfloat16 *dv_out, int T) {
     extern __shared__ float sm[];
-    float *dS = sm;                         // [128][32]
-    float *dOs = dS + kDK * kDVP;           // [64][32]
-    float *dU = dOs + kC * kDVP;            // [64][32]
-    float *dZ = dU + kC * kDVP;             // [64][32]
-    float *Mi = dZ + kC * kDVP;             // [64][65]
-    float *eca = Mi + kC * 65;              // [64]
+    float *dS = sm;                         // [128][40]
+    float *dOs = dS + kDK * kPadS;          // [64][40]
+    float *dU = dOs + kC * kPadS;           // [64][40]
+    float *dZ = dU + kC * kPadS;            // [64][40]
+    float *Mi = dZ + kC * kPadS;            // [64][72]
+    float *eca = Mi + kC * kPadM;           // [64]
     float *ekd = eca + kC;                  // [64]
     float *be = ekd + kC;                   // [64]
     __nv_bfloat16 *Qh = reinterpret_cast<__nv_bfloat16 *>(be + kC);   // [64][136]
@@ -364,10 +410,11 @@ __global__ void __launch_bounds__(256) deltanet_bwd_scan_kernel(
     __shared__ float gamma_sm;
 
     const int head = blockIdx.x, part = blockIdx.y;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int mt = warp & 3, nh = warp >> 2;
     const int chunks = T / kC;
-    for (int i = tid; i < kDK * kDVP; i += 256) dS[i] = 0.0f;
-    const int ty = tid >> 3, tx = tid & 7;   // [64][32] outputs: rows 2ty, 2ty+1; columns 4tx..4tx+3
+    for (int i = tid; i < kDK * kPadS; i += 256) dS[i] = 0.0f;
 
     for (int chunk = chunks - 1; chunk >= 0; chunk--) {
         const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
@@ -375,7 +422,7 @@ __global__ void __launch_bounds__(256) deltanet_bwd_scan_kernel(
         __syncthreads();
         {   // the incoming state gradient, for the per-chunk kernel
             float *dst = dsin_save + cidx * kDK * kDV + part * kDVP;
-            for (int i = tid; i < kDK * kDVP; i += 256) dst[(i / kDVP) * kDV + (i % kDVP)] = dS[i];
+            for (int i = tid; i < kDK * kDVP; i += 256) dst[(i / kDVP) * kDV + (i % kDVP)] = dS[(i / kDVP) * kPadS + (i % kDVP)];
         }
         for (int i = tid; i < kC * kDK / 8; i += 256) {
             const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
@@ -386,14 +433,17 @@ __global__ void __launch_bounds__(256) deltanet_bwd_scan_kernel(
             const int r = i / (kC / 8), c = (i % (kC / 8)) * 8;
             *reinterpret_cast<uint4 *>(Ph + r * kPadP + c) = __ldg(reinterpret_cast<const uint4 *>(p_in + cidx * kC * kC + r * kC + c));
         }
-        for (int i = tid; i < kC * kC; i += 256) Mi[(i / kC) * 65 + (i % kC)] = __ldg(minv + row0 * kC + i);
+        for (int i = tid; i < kC * kC / 4; i += 256) {
+            const int r = i / (kC / 4), c = (i % (kC / 4)) * 4;
+            *reinterpret_cast<float4 *>(Mi + r * kPadM + c) = __ldg(reinterpret_cast<const float4 *>(minv + row0 * kC + r * kC + c));
+        }
         {   // dO arrives as (positions, features): 8 positions of one feature per thread
             const int f = tid >> 3, t8 = (tid & 7) * 8;
             float dv8[8];
             Access<__nv_bfloat16, true>::load_cached(
                 dout + (static_cast<long long>(head) * kDV + part * kDVP + f) * T + static_cast<long long>(chunk) * kC + t8, dv8);
 #pragma unroll
-            for (int e = 0; e < 8; e++) dOs[(t8 + e) * kDVP + f] = dv8[e];
+            for (int e = 0; e < 8; e++) dOs[(t8 + e) * kPadS + f] = dv8[e];
         }
         if (tid < kC) be[tid] = beta[row0 + tid];
         if (tid < 32) {
@@ -406,95 +456,101 @@ __global__ void __launch_bounds__(256) deltanet_bwd_scan_kernel(
         }
         __syncthreads();
 
-        // dU = P' dO + ed (K dS')
-        float acc[2][4] = {};
-        for (int i = 0; i < kDK; i += 8) {
-            float k0[8], k1[8];
-            unpack8(Kh + (2 * ty) * kPadH + i, k0);
-            unpack8(Kh + (2 * ty + 1) * kPadH + i, k1);
+        // dU = ed (K dS') + P' dO : rows t = 16 mt + g (+8), columns 16 nh + 8 nt + 2 t4 (+1)
+        {
+            float acc[2][4] = {};
+            const __nv_bfloat16 *k0p = Kh + (16 * mt + g) * kPadH + t4, *k1p = k0p + 8 * kPadH;
+            const float *sb = dS + t4 * kPadS + 16 * nh + g;
+#pragma unroll 4
+            for (int k0 = 0; k0 < kDK; k0 += 8) {
+                const uint32_t af[4] = {tf32_of_bf16(k0p + k0), tf32_of_bf16(k1p + k0), tf32_of_bf16(k0p + k0 + 4), tf32_of_bf16(k1p + k0 + 4)};
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const float4 s4 = *reinterpret_cast<const float4 *>(dS + (i + e) * kDVP + 4 * tx);
-                acc[0][0] = fmaf(k0[e], s4.x, acc[0][0]); acc[0][1] = fmaf(k0[e], s4.y, acc[0][1]);
-                acc[0][2] = fmaf(k0[e], s4.z, acc[0][2]); acc[0][3] = fmaf(k0[e], s4.w, acc[0][3]);
-                acc[1][0] = fmaf(k1[e], s4.x, acc[1][0]); acc[1][1] = fmaf(k1[e], s4.y, acc[1][1]);
-                acc[1][2] = fmaf(k1[e], s4.z, acc[1][2]); acc[1][3] = fmaf(k1[e], s4.w, acc[1][3]);
+                for (int nt = 0; nt < 2; nt++)
+                    mma_tf32(acc[nt], af, tf32_of(sb[k0 * kPadS + 8 * nt]), tf32_of(sb[(k0 + 4) * kPadS + 8 * nt]));
             }
-        }
+            const float e0 = ekd[16 * mt + g], e1 = ekd[16 * mt + g + 8];
 #pragma unroll
-        for (int r = 0; r < 2; r++) {
-            const float sc = ekd[2 * ty + r];
+            for (int nt = 0; nt < 2; nt++) { acc[nt][0] *= e0; acc[nt][1] *= e0; acc[nt][2] *= e1; acc[nt][3] *= e1; }
+            // A[t][s] = P[s][t]
+            const __nv_bfloat16 *pb = Ph + t4 * kPadP + 16 * mt + g;
+            const float *ob = dOs + t4 * kPadS + 16 * nh + g;
+#pragma unroll 4
+            for (int k0 = 0; k0 < kC; k0 += 8) {
+                const uint32_t af[4] = {tf32_of_bf16(pb + k0 * kPadP), tf32_of_bf16(pb + k0 * kPadP + 8), tf32_of_bf16(pb + (k0 + 4) * kPadP),
+                                        tf32_of_bf16(pb + (k0 + 4) * kPadP + 8)};
 #pragma unroll
-            for (int j = 0; j < 4; j++) acc[r][j] *= sc;
-        }
-        for (int s = 2 * ty; s < kC; s++) {   // P[s][t] is zero for s < t
-            float p0, p1;
-            unpack_bf16x2(*reinterpret_cast<const uint32_t *>(Ph + s * kPadP + 2 * ty), p0, p1);
-            const float4 d4 = *reinterpret_cast<const float4 *>(dOs + s * kDVP + 4 * tx);
-            acc[0][0] = fmaf(p0, d4.x, acc[0][0]); acc[0][1] = fmaf(p0, d4.y, acc[0][1]);
-            acc[0][2] = fmaf(p0, d4.z, acc[0][2]); acc[0][3] = fmaf(p0, d4.w, acc[0][3]);
-            acc[1][0] = fmaf(p1, d4.x, acc[1][0]); acc[1][1] = fmaf(p1, d4.y, acc[1][1]);
-            acc[1][2] = fmaf(p1, d4.z, acc[1][2]); acc[1][3] = fmaf(p1, d4.w, acc[1][3]);
-        }
+                for (int nt = 0; nt < 2; nt++)
+                    mma_tf32(acc[nt], af, tf32_of(ob[k0 * kPadS + 8 * nt]), tf32_of(ob[(k0 + 4) * kPadS + 8 * nt]));
+            }
 #pragma unroll
-        for (int r = 0; r < 2; r++)
-            *reinterpret_cast<float4 *>(dU + (2 * ty + r) * kDVP + 4 * tx) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
-        __syncthreads();
-
-        // dZ = Minv' dU  (Minv is lower triangular: rows s >= t contribute)
-        float z[2][4] = {};
-        for (int s = 2 * ty; s < kC; s++) {
-            const float m0 = Mi[s * 65 + 2 * ty], m1 = Mi[s * 65 + 2 * ty + 1];
-            const float4 u4 = *reinterpret_cast<const float4 *>(dU + s * kDVP + 4 * tx);
-            z[0][0] = fmaf(m0, u4.x, z[0][0]); z[0][1] = fmaf(m0, u4.y, z[0][1]);
-            z[0][2] = fmaf(m0, u4.z, z[0][2]); z[0][3] = fmaf(m0, u4.w, z[0][3]);
-            z[1][0] = fmaf(m1, u4.x, z[1][0]); z[1][1] = fmaf(m1, u4.y, z[1][1]);
-            z[1][2] = fmaf(m1, u4.z, z[1][2]); z[1][3] = fmaf(m1, u4.w, z[1][3]);
-        }
+            for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-        for (int r = 0; r < 2; r++) {
-            const int t = 2 * ty + r;
-            const float4 z4 = make_float4(z[r][0], z[r][1], z[r][2], z[r][3]);
-            *reinterpret_cast<float4 *>(dZ + t * kDVP + 4 * tx) = z4;
-            *reinterpret_cast<float4 *>(dz_save + (row0 + t) * kDV + part * kDVP + 4 * tx) = z4;
-            const float b = be[t];
-            uint2 packed;
-            packed.x = pack_bf16x2(b * z4.x, b * z4.y);
-            packed.y = pack_bf16x2(b * z4.z, b * z4.w);
-            *reinterpret_cast<uint2 *>(dv_out + (row0 + t) * kDV + part * kDVP + 4 * tx) = packed;
+                for (int hr = 0; hr < 2; hr++)
+                    *reinterpret_cast<float2 *>(dU + (16 * mt + g + 8 * hr) * kPadS + 16 * nh + 8 * nt + 2 * t4) =
+                        make_float2(acc[nt][2 * hr], acc[nt][2 * hr + 1]);
         }
         __syncthreads();
 
-        // dS = g dS' + (e Q)' dO - (e K)' (beta dZ): rows 4ty..4ty+3, columns 4tx..4tx+3
+        // dZ = Minv' dU : A[t][s] = Minv[s][t]
+        {
+            float z[2][4] = {};
+            const float *mb = Mi + t4 * kPadM + 16 * mt + g;
+            const float *ub = dU + t4 * kPadS + 16 * nh + g;
+#pragma unroll 4
+            for (int k0 = 0; k0 < kC; k0 += 8) {
+                const uint32_t af[4] = {tf32_of(mb[k0 * kPadM]), tf32_of(mb[k0 * kPadM + 8]), tf32_of(mb[(k0 + 4) * kPadM]),
+                                        tf32_of(mb[(k0 + 4) * kPadM + 8])};
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+                    mma_tf32(z[nt], af, tf32_of(ub[k0 * kPadS + 8 * nt]), tf32_of(ub[(k0 + 4) * kPadS + 8 * nt]));
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int hr = 0; hr < 2; hr++) {
+                    const int t = 16 * mt + g + 8 * hr, col = 16 * nh + 8 * nt + 2 * t4;
+                    const float2 z2 = make_float2(z[nt][2 * hr], z[nt][2 * hr + 1]);
+                    *reinterpret_cast<float2 *>(dZ + t * kPadS + col) = z2;
+                    *reinterpret_cast<float2 *>(dz_save + (row0 + t) * kDV + part * kDVP + col) = z2;
+                    const float b = be[t];
+                    *reinterpret_cast<uint32_t *>(dv_out + (row0 + t) * kDV + part * kDVP + col) = pack_bf16x2(b * z2.x, b * z2.y);
+                }
+        }
+        __syncthreads();
+
+        // dS = g dS' + (e Q)' dO - (e beta K)' dZ : warp -> state rows 16 warp + g (+8), all 32 features
         {
             const float gamma = gamma_sm;
             float sa[4][4];
+            float *s0 = dS + (16 * warp + g) * kPadS + 2 * t4, *s1 = s0 + 8 * kPadS;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float4 s4 = *reinterpret_cast<const float4 *>(dS + (4 * ty + i) * kDVP + 4 * tx);
-                sa[i][0] = gamma * s4.x; sa[i][1] = gamma * s4.y; sa[i][2] = gamma * s4.z; sa[i][3] = gamma * s4.w;
+            for (int nt = 0; nt < 4; nt++) {
+                const float2 lo = *reinterpret_cast<const float2 *>(s0 + 8 * nt), hi = *reinterpret_cast<const float2 *>(s1 + 8 * nt);
+                sa[nt][0] = gamma * lo.x; sa[nt][1] = gamma * lo.y; sa[nt][2] = gamma * hi.x; sa[nt][3] = gamma * hi.y;
             }
-            for (int t = 0; t < kC; t++) {
-                const float e = eca[t], eb = -e * be[t];
-                const uint2 qb = *reinterpret_cast<const uint2 *>(Qh + t * kPadH + 4 * ty);
-                const uint2 kb = *reinterpret_cast<const uint2 *>(Kh + t * kPadH + 4 * ty);
-                float qv[4], kv[4];
-                unpack_bf16x2(qb.x, qv[0], qv[1]); unpack_bf16x2(qb.y, qv[2], qv[3]);
-                unpack_bf16x2(kb.x, kv[0], kv[1]); unpack_bf16x2(kb.y, kv[2], kv[3]);
-                const float4 d4 = *reinterpret_cast<const float4 *>(dOs + t * kDVP + 4 * tx);
-                const float4 z4 = *reinterpret_cast<const float4 *>(dZ + t * kDVP + 4 * tx);
+            const __nv_bfloat16 *qb = Qh + t4 * kPadH + 16 * warp + g, *kb = Kh + t4 * kPadH + 16 * warp + g;
+            const float *ob = dOs + t4 * kPadS + g, *zb = dZ + t4 * kPadS + g;
+#pragma unroll 2
+            for (int k0 = 0; k0 < kC; k0 += 8) {
+                const float ea = eca[k0 + t4], eb = eca[k0 + t4 + 4];
+                const float ba = -ea * be[k0 + t4], bb = -eb * be[k0 + t4 + 4];
+                const uint32_t aq[4] = {tf32_of(__bfloat162float(qb[k0 * kPadH]) * ea), tf32_of(__bfloat162float(qb[k0 * kPadH + 8]) * ea),
+                                        tf32_of(__bfloat162float(qb[(k0 + 4) * kPadH]) * eb),
+                                        tf32_of(__bfloat162float(qb[(k0 + 4) * kPadH + 8]) * eb)};
+                const uint32_t ak[4] = {tf32_of(__bfloat162float(kb[k0 * kPadH]) * ba), tf32_of(__bfloat162float(kb[k0 * kPadH + 8]) * ba),
+                                        tf32_of(__bfloat162float(kb[(k0 + 4) * kPadH]) * bb),
+                                        tf32_of(__bfloat162float(kb[(k0 + 4) * kPadH + 8]) * bb)};
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float qe = qv[i] * e, ke = kv[i] * eb;
-                    sa[i][0] = fmaf(qe, d4.x, sa[i][0]); sa[i][1] = fmaf(qe, d4.y, sa[i][1]);
-                    sa[i][2] = fmaf(qe, d4.z, sa[i][2]); sa[i][3] = fmaf(qe, d4.w, sa[i][3]);
-                    sa[i][0] = fmaf(ke, z4.x, sa[i][0]); sa[i][1] = fmaf(ke, z4.y, sa[i][1]);
-                    sa[i][2] = fmaf(ke, z4.z, sa[i][2]); sa[i][3] = fmaf(ke, z4.w, sa[i][3]);
+                for (int nt = 0; nt < 4; nt++) {
+                    mma_tf32(sa[nt], aq, tf32_of(ob[k0 * kPadS + 8 * nt]), tf32_of(ob[(k0 + 4) * kPadS + 8 * nt]));
+                    mma_tf32(sa[nt], ak, tf32_of(zb[k0 * kPadS + 8 * nt]), tf32_of(zb[(k0 + 4) * kPadS + 8 * nt]));
                 }
             }
 #pragma unroll
-            for (int i = 0; i < 4; i++)
-                *reinterpret_cast<float4 *>(dS + (4 * ty + i) * kDVP + 4 * tx) = make_float4(sa[i][0], sa[i][1], sa[i][2], sa[i][3]);
+            for (int nt = 0; nt < 4; nt++) {
+                *reinterpret_cast<float2 *>(s0 + 8 * nt) = make_float2(sa[nt][0], sa[nt][1]);
+                *reinterpret_cast<float2 *>(s1 + 8 * nt) = make_float2(sa[nt][2], sa[nt][3]);
+            }
         }
     }
 }
@@ -871,9 +927,9 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
 }
 
 constexpr size_t kChunkSmem = (2 * kC * kPadF + kC * kC + 2 * kC) * sizeof(float);
-constexpr size_t kScanSmem = (kDK * kPadS + kC * kPadS + 2 * kC) * sizeof(float) +
-                             (3 * kC * kPadH + kC * kPadP + kDVP * kPadP) * sizeof(__nv_bfloat16);
-constexpr size_t kBwdScanSmem = (kDK * kDVP + 3 * kC * kDVP + kC * 65 + 3 * kC) * sizeof(float) +
+constexpr size_t kScanSmem = (kDK * kPadS + kC * kPadS + 4 * kC) * sizeof(float) +
+                             (4 * kC * kPadH + kC * kPadP + kDVP * kPadP) * sizeof(__nv_bfloat16);
+constexpr size_t kBwdScanSmem = (kDK * kPadS + 3 * kC * kPadS + kC * kPadM + 3 * kC) * sizeof(float) +
                                 (2 * kC * kPadH + kC * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdXgSmem = (3 * kC * kPadF + kC) * sizeof(float);
 constexpr size_t kBwdOutSmem = (kDK * kPadF + 2 * kC * kPadF + 2 * kC * 65 + 10 * kC + 8) * sizeof(float) +
