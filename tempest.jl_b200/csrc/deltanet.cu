@@ -85,34 +85,40 @@ __global__ void __launch_bounds__(320) deltanet_chunk_kernel(const __nv_bfloat16
     }
     __syncthreads();
 
-    // A = beta .* decay(t > s) .* (K K'), P = decay(t >= s) .* (Q K'): 4 x 4 outputs per thread
+    // A = beta .* decay(t > s) .* (K K'), P = decay(t >= s) .* (Q K'): thread (ty, tx) takes rows 4 ty .. 4 ty + 3 and
+    // columns tx, tx + 16, tx + 32, tx + 48 -- neighbouring threads read neighbouring rows of K, which the
+    // 132-float pitch spreads over all banks (rows 4 tx + j would fall on two bank groups).  Column blocks that
+    // lie wholly above the diagonal are skipped.
     if (tid < 256) {
         const int ty = tid >> 4, tx = tid & 15;
         float kk[4][4] = {}, qk[4][4] = {};
-        if (tx <= ty) {   // blocks above the diagonal are zero
-            for (int d = 0; d < kDK; d += 4) {
-                float4 kt[4], qt[4], ks[4];
+        const int nj = ty / 4 + 1;   // column blocks 16 j .. 16 j + 15 that reach the diagonal of rows 4 ty .. 4 ty + 3
+        for (int d = 0; d < kDK; d += 4) {
+            float4 kt[4], qt[4], ks[4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    kt[i] = *reinterpret_cast<const float4 *>(Kf + (ty * 4 + i) * kPadF + d);
-                    qt[i] = *reinterpret_cast<const float4 *>(Qf + (ty * 4 + i) * kPadF + d);
-                    ks[i] = *reinterpret_cast<const float4 *>(Kf + (tx * 4 + i) * kPadF + d);
-                }
+            for (int i = 0; i < 4; i++) {
+                kt[i] = *reinterpret_cast<const float4 *>(Kf + (ty * 4 + i) * kPadF + d);
+                qt[i] = *reinterpret_cast<const float4 *>(Qf + (ty * 4 + i) * kPadF + d);
+            }
 #pragma unroll
-                for (int i = 0; i < 4; i++)
+            for (int j = 0; j < 4; j++)
+                if (j < nj) ks[j] = *reinterpret_cast<const float4 *>(Kf + (tx + 16 * j) * kPadF + d);
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
+            for (int j = 0; j < 4; j++)
+                if (j < nj) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
                         kk[i][j] += kt[i].x * ks[j].x + kt[i].y * ks[j].y + kt[i].z * ks[j].z + kt[i].w * ks[j].w;
                         qk[i][j] += qt[i].x * ks[j].x + qt[i].y * ks[j].y + qt[i].z * ks[j].z + qt[i].w * ks[j].w;
                     }
-            }
+                }
         }
         __nv_bfloat16 *pc = p_out + (static_cast<long long>(head) * chunks + chunk) * kC * kC;
 #pragma unroll
         for (int i = 0; i < 4; i++)
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const int t = ty * 4 + i, s = tx * 4 + j;
+                const int t = ty * 4 + i, s = tx + 16 * j;
                 const float dec = t >= s ? __expf(ca[t] - ca[s]) : 0.0f;
                 A[t * kC + s] = t > s ? be[t] * dec * kk[i][j] : 0.0f;
                 pc[t * kC + s] = __float2bfloat16_rn(t >= s ? dec * qk[i][j] : 0.0f);
@@ -120,17 +126,26 @@ __global__ void __launch_bounds__(320) deltanet_chunk_kernel(const __nv_bfloat16
     }
     __syncthreads();
 
-    // (I + A) x = rhs by forward substitution, one right-hand column per thread, x in registers
+    // (I + A) x = rhs by forward substitution, one right-hand column per thread, x in registers.  The
+    // right-hand side is formed first, its three kinds outside the loops, so that the 2016-step
+    // substitution is straight-line code.
     {
-        const int c = tid;   // 0..127: W, 128..255: Ut
+        const int c = tid;   // 0..127: W, 128..255: Ut, 256..319: the identity (for (I + A)^-1)
         float x[kC];
+        if (c < kDK) {
 #pragma unroll
-        for (int t = 0; t < kC; t++) {
-            float rhs;
-            if (c < kDK) rhs = be[t] * __expf(ca[t]) * Kf[t * kPadF + c];
-            else if (c >= kDK + kDV) rhs = (t == c - kDK - kDV) ? 1.0f : 0.0f;
-            else rhs = be[t] * bf16_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(v) + (row0 + t) * kDV + (c - kDK)));
-            float acc = rhs;
+            for (int t = 0; t < kC; t++) x[t] = be[t] * __expf(ca[t]) * Kf[t * kPadF + c];
+        } else if (c < kDK + kDV) {
+#pragma unroll
+            for (int t = 0; t < kC; t++)
+                x[t] = be[t] * bf16_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(v) + (row0 + t) * kDV + (c - kDK)));
+        } else {
+#pragma unroll
+            for (int t = 0; t < kC; t++) x[t] = (t == c - kDK - kDV) ? 1.0f : 0.0f;
+        }
+#pragma unroll
+        for (int t = 1; t < kC; t++) {
+            float acc = x[t];
 #pragma unroll
             for (int s = 0; s < t; s++) acc = fmaf(-A[t * kC + s], x[s], acc);
             x[t] = acc;
