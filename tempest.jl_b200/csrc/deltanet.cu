@@ -602,40 +602,41 @@ __global__ void __launch_bounds__(256) deltanet_bwd_xg_kernel(const float *a, co
         ca[tid + 32] = hi;
     }
     __syncthreads();
+    // thread (ty, tx): rows 4 ty .. 4 ty + 3, columns tx + 16 j (neighbouring threads read neighbouring rows of U:
+    // no bank conflicts); column blocks wholly above the diagonal are skipped
     const int ty = tid >> 4, tx = tid & 15;
     float xo[4][4] = {}, zo[4][4] = {};
-    if (tx <= ty) {
-        for (int d = 0; d < kDV; d += 4) {
-            float4 dt[4], zt[4], us[4];
+    const int nj = ty / 4 + 1;
+    for (int d = 0; d < kDV; d += 4) {
+        float4 dt[4], zt[4], us[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                dt[i] = *reinterpret_cast<const float4 *>(dOs + (ty * 4 + i) * kPadF + d);
-                zt[i] = *reinterpret_cast<const float4 *>(dZs + (ty * 4 + i) * kPadF + d);
-                us[i] = *reinterpret_cast<const float4 *>(Us + (tx * 4 + i) * kPadF + d);
-            }
+        for (int i = 0; i < 4; i++) {
+            dt[i] = *reinterpret_cast<const float4 *>(dOs + (ty * 4 + i) * kPadF + d);
+            zt[i] = *reinterpret_cast<const float4 *>(dZs + (ty * 4 + i) * kPadF + d);
+        }
 #pragma unroll
-            for (int i = 0; i < 4; i++)
+        for (int j = 0; j < 4; j++)
+            if (j < nj) us[j] = *reinterpret_cast<const float4 *>(Us + (tx + 16 * j) * kPadF + d);
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
+        for (int j = 0; j < 4; j++)
+            if (j < nj) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
                     xo[i][j] += dt[i].x * us[j].x + dt[i].y * us[j].y + dt[i].z * us[j].z + dt[i].w * us[j].w;
                     zo[i][j] += zt[i].x * us[j].x + zt[i].y * us[j].y + zt[i].z * us[j].z + zt[i].w * us[j].w;
                 }
-        }
+            }
     }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int t = ty * 4 + i;
-        float4 xv, gv;
-        float *xp = &xv.x, *gp = &gv.x;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const int s = tx * 4 + j;
+            const int s = tx + 16 * j;
             const float dec = t >= s ? __expf(ca[t] - ca[s]) : 0.0f;
-            xp[j] = t >= s ? dec * xo[i][j] : 0.0f;
-            gp[j] = t > s ? -dec * zo[i][j] : 0.0f;
+            x_out[(row0 + t) * kC + s] = t >= s ? dec * xo[i][j] : 0.0f;
+            g_out[(row0 + t) * kC + s] = t > s ? -dec * zo[i][j] : 0.0f;
         }
-        *reinterpret_cast<float4 *>(x_out + (row0 + t) * kC + tx * 4) = xv;
-        *reinterpret_cast<float4 *>(g_out + (row0 + t) * kC + tx * 4) = gv;
     }
 }
 
