@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
     __shared__ __align__(8) uint64_t outer_full, outer_empty, acc_done, acc_free;
     __shared__ __align__(8) uint64_t inner_full[kStages], inner_empty[kStages];
     __shared__ __align__(8) uint64_t t_full[2], ds_full[2];
+    __shared__ __align__(8) uint64_t stats_ready[2];   // a group's four warps have written the step's statistics
     __shared__ uint32_t tmem_base_smem;
     __shared__ int failed_smem;
     // dK/dV: the step's 64 queries' lse*log2(e) [0, 64) and delta [64, 128), per group, double-buffered
@@ -149,6 +150,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
         for (int s = 0; s < 2; s++) {
             mbar_init(&t_full[s], 1);
             mbar_init(&ds_full[s], 4);
+            mbar_init(&stats_ready[s], 4);
         }
         fence_barrier_init();
         prefetch_tensormap(&p.outer_a); prefetch_tensormap(&p.outer_b);
@@ -278,7 +280,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
         const int group = (warp - 2) >> 2;
         const int row = q4 * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
-        uint32_t step_count = 0, item_count = 0;
+        uint32_t step_count = 0, item_count = 0, own_steps = 0;
         for (int item = blockIdx.x; item < p.items; item += gridDim.x) {
             const Steps<DKDV> steps(p, item);
             const int outer_pos = steps.tile * kOuter + row;   // this thread's key (dK/dV) or query (dQ)
@@ -309,7 +311,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 }
                 if (!bwd_wait(&t_full[tb], tph, failed, 8)) { ok = false; break; }
                 tcgen05_fence_after();
-                if (DKDV) asm volatile("bar.sync %0, 128;" ::"r"(2 + group) : "memory");
+                if (DKDV) {
+                    // the group's four warps meet (a bounded wait, unlike a named barrier: a warp that gave up on a
+                    // failed wait elsewhere must not leave the others hanging here)
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&stats_ready[group]);
+                    if (!bwd_wait(&stats_ready[group], own_steps & 1, failed, 12)) { ok = false; break; }
+                    own_steps++;
+                }
                 uint32_t s[kInner], dp[kInner];
                 const uint32_t t1 = tmem_base + lane_base + tb * 128;
                 tmem_ld_32x32(t1, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
