@@ -324,6 +324,23 @@ def run_also(torch, dist, pkg, world, rank):
                          "frac_of_measured_bf16_peak_per_gpu": round(flops / ms / 1e9 / world / tensor_peak, 4),
                          "gradient_allreduce_bytes": sum(b.numel() * 2 for b in step.bucket) if world > 1 else 0,
                          "device_error": L.device_error()}}
+    if world > 1:
+        # the same step with the per-replica batch held at 8192 (weak scaling): the gradient exchange is the
+        # same 84 MB while each replica has the whole single-GPU step to hide it behind
+        del step, x, y
+        wstep = pkg.mlp.MLPStep(torch, sizes, gb, 1e-3, world=world, global_batch=gb * world, seed=1)
+        wx = torch.randn(gb, sizes[0], device="cuda").bfloat16()
+        wy = torch.randn(gb, sizes[-1], device="cuda").bfloat16()
+        wstep.step(wx, wy)
+        wms = timed(lambda: wstep.step(wx, wy), 20, 5)
+        out["mlp_train_weak"] = {"steps_per_s": round(1000.0 / wms, 1), "ms_per_step": round(wms, 4), "n_gpus": world,
+                                 "global_batch": gb * world, "scaling": "weak",
+                                 "samples_per_s": round(gb * world * 1000.0 / wms, 1),
+                                 "TFLOP/s": round(flops * world / wms / 1e9, 1),
+                                 "frac_of_measured_bf16_peak_per_gpu": round(flops / wms / 1e9 / tensor_peak, 4),
+                                 "launch": "eager (one GPU replays a CUDA graph: compare samples_per_s with n_gpus x the 1-GPU eager rate)",
+                                 "device_error": L.device_error()}
+        del wstep, wx, wy
     if rank == 0 or world == 1:
         M, N, K = 8192, 4096, 4096
         A = torch.randn(M, K, device="cuda").bfloat16()
