@@ -640,39 +640,69 @@ __global__ void __launch_bounds__(256) deltanet_bwd_xg_kernel(const float *a, co
     }
 }
 
-__device__ __forceinline__ float sum16(float v) {   // over the 16 lanes that share a row group
-    v += __shfl_xor_sync(0xffffffffu, v, 8);
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    return v;
+// ---- fragment loaders for mma_tf32 (g = lane / 4, t = lane % 4) ----
+// A from a Float32 tile, rows r0 + g (+8), columns k0 + t (+4)
+__device__ __forceinline__ void frag_a_f32(uint32_t (&f)[4], const float *tile, int pitch, int r0, int k0, int g, int t) {
+    const float *p = tile + (r0 + g) * pitch + k0 + t;
+    f[0] = tf32_of(p[0]); f[1] = tf32_of(p[8 * pitch]); f[2] = tf32_of(p[4]); f[3] = tf32_of(p[8 * pitch + 4]);
+}
+// A transposed from a Float32 tile: A[m][k] = tile[k][m], optionally scaled per k by `scale[k]`
+__device__ __forceinline__ void frag_at_f32(uint32_t (&f)[4], const float *tile, int pitch, int r0, int k0, int g, int t,
+                                            const float *scale) {
+    const float *p = tile + (k0 + t) * pitch + r0 + g;
+    const float s0 = scale ? scale[k0 + t] : 1.0f, s1 = scale ? scale[k0 + t + 4] : 1.0f;
+    f[0] = tf32_of(p[0] * s0); f[1] = tf32_of(p[8] * s0); f[2] = tf32_of(p[4 * pitch] * s1); f[3] = tf32_of(p[4 * pitch + 8] * s1);
+}
+// A from a BFloat16 tile (exact in TF32)
+__device__ __forceinline__ void frag_a_bf16(uint32_t (&f)[4], const __nv_bfloat16 *tile, int pitch, int r0, int k0, int g, int t) {
+    const __nv_bfloat16 *p = tile + (r0 + g) * pitch + k0 + t;
+    f[0] = tf32_of_bf16(p); f[1] = tf32_of_bf16(p + 8 * pitch); f[2] = tf32_of_bf16(p + 4); f[3] = tf32_of_bf16(p + 8 * pitch + 4);
 }
 
-// acc[r][c] += sum_j  L[4ty + r][j] * R[tx + 16c][j]   for two left operands against one right operand
-__device__ __forceinline__ void rows_dot_rows(const float *L0, const float *L1, const float *R, int ty, int tx,
-                                              float (&o0)[4][8], float (&o1)[4][8]) {
-    for (int j = 0; j < 128; j += 4) {
-        float4 l0[4], l1[4];
+// acc[nt] += A(16 x 8) * B for the eight 8-column tiles n0 + 8 nt, B[k][n] = tile[n][k] (a Float32 tile read "by rows of n")
+__device__ __forceinline__ void mma_row_nk(float (&acc)[8][4], const uint32_t (&af)[4], const float *tile, int pitch, int n0, int k0, int g,
+                                           int t) {
 #pragma unroll
-        for (int r = 0; r < 4; r++) {
-            l0[r] = *reinterpret_cast<const float4 *>(L0 + (4 * ty + r) * kPadF + j);
-            if (L1) l1[r] = *reinterpret_cast<const float4 *>(L1 + (4 * ty + r) * kPadF + j);
-        }
+    for (int nt = 0; nt < 8; nt++) {
+        const float *p = tile + (n0 + 8 * nt + g) * pitch + k0 + t;
+        mma_tf32(acc[nt], af, tf32_of(p[0]), tf32_of(p[4]));
+    }
+}
+// two A operands against the same B[k][n] = tile[n][k]
+__device__ __forceinline__ void mma2_row_nk(float (&acc0)[8][4], float (&acc1)[8][4], const uint32_t (&a0)[4], const uint32_t (&a1)[4],
+                                            const float *tile, int pitch, int n0, int k0, int g, int t) {
 #pragma unroll
-        for (int c = 0; c < 8; c++) {
-            const float4 s4 = *reinterpret_cast<const float4 *>(R + (tx + 16 * c) * kPadF + j);
+    for (int nt = 0; nt < 8; nt++) {
+        const float *p = tile + (n0 + 8 * nt + g) * pitch + k0 + t;
+        const uint32_t b0 = tf32_of(p[0]), b1 = tf32_of(p[4]);
+        mma_tf32(acc0[nt], a0, b0, b1);
+        mma_tf32(acc1[nt], a1, b0, b1);
+    }
+}
+// B[k][n] = tile[k][n] from a Float32 tile
+__device__ __forceinline__ void mma_row_kn(float (&acc)[8][4], const uint32_t (&af)[4], const float *tile, int pitch, int n0, int k0, int g,
+                                           int t) {
 #pragma unroll
-            for (int r = 0; r < 4; r++) {
-                o0[r][c] += l0[r].x * s4.x + l0[r].y * s4.y + l0[r].z * s4.z + l0[r].w * s4.w;
-                if (L1) o1[r][c] += l1[r].x * s4.x + l1[r].y * s4.y + l1[r].z * s4.z + l1[r].w * s4.w;
-            }
-        }
+    for (int nt = 0; nt < 8; nt++) {
+        const float *p = tile + (k0 + t) * pitch + n0 + 8 * nt + g;
+        mma_tf32(acc[nt], af, tf32_of(p[0]), tf32_of(p[4 * pitch]));
     }
 }
 
-// dQ, dK, da, dbeta of one chunk; one block per (head, chunk).  Thread (ty, tx) owns rows 4ty..4ty+3 and
-// columns tx + 16c (c = 0..7) of every (position, feature) tile, which keeps the 128-bit reads of the state
-// rows free of bank conflicts.
+// sum over a row's columns held by the four lanes that share g
+__device__ __forceinline__ float sum_quad(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v;
+}
+
+// dQ, dK, da, dbeta of one chunk; one block per (head, chunk).  The eight products of the chunk are TF32
+// warp-level MMAs: warp w takes positions 16 (w % 4) .. + 15 and features 64 (w / 4) .. + 63 of every
+// (position, feature) result, i.e. eight 16 x 8 accumulator tiles per product; a thread holds rows
+// g, g + 8 and columns 2 t, 2 t + 1 of each tile.  Row sums of products of results with Q or K (the gate and
+// beta gradients) are taken on the accumulators and meet through shared memory.
+constexpr int kPadX = 68;   // Float32 row pitch of X and G: both their rows and their columns are read as A operands
+
 __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     const __nv_bfloat16 *q, const __nv_bfloat16 *k, const __nv_bfloat16 *v, const float *a, const float *beta,
     const __nv_bfloat16 *dout, const float *s_save, const float *dsin_save, const float *u_save, const float *dz_save,
@@ -681,22 +711,24 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     float *Sb = sm;                        // [128][132]: S, then dS'
     float *M0 = Sb + kDK * kPadF;          // [64][132]: dO, then U, then the dQ staging
     float *M1 = M0 + kC * kPadF;           // [64][132]: dZ, then the dK staging
-    float *Xs = M1 + kC * kPadF;           // [64][65]
-    float *Gs = Xs + kC * 65;              // [64][65]
-    float *vec = Gs + kC * 65;             // 10 x [64]
-    float *eca = vec, *ekd = vec + 64, *be = vec + 128, *v_de = vec + 192, *v_ded = vec + 256, *v_rq = vec + 320,
-          *v_rk = vec + 384, *v_cq = vec + 448, *v_ck = vec + 512, *v_rdz = vec + 576;
-    float *red = vec + 640;                // [8]
+    float *Xs = M1 + kC * kPadF;           // [64][68]
+    float *Gs = Xs + kC * kPadX;           // [64][68]
+    float *vec = Gs + kC * kPadX;
+    float *eca = vec, *ekd = vec + 64, *be = vec + 128;
+    float *part = vec + 192;               // [7 sums][2 feature halves][64 rows]
+    float *red = part + 7 * 128;           // [8]
     __nv_bfloat16 *Qh = reinterpret_cast<__nv_bfloat16 *>(red + 8);   // [64][136]
     __nv_bfloat16 *Kh = Qh + kC * kPadH;
     __shared__ float gamma_sm;
+    enum { DE = 0, DED, RQ, RK, CQ, CK, RDZ };
 
     const int chunks = T / kC;
     const int head = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
     const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
     const long long cidx = static_cast<long long>(head) * chunks + chunk;
-    const int tid = threadIdx.x;
-    const int ty = tid >> 4, tx = tid & 15;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int m0 = 16 * (warp & 3), nh = warp >> 2, n0 = 64 * nh;
 
     for (int i = tid; i < kDK * kDV / 4; i += 256) {
         const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
@@ -718,9 +750,10 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
         *reinterpret_cast<uint4 *>(Qh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(q + (row0 + r) * kDK + c));
         *reinterpret_cast<uint4 *>(Kh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(k + (row0 + r) * kDK + c));
     }
-    for (int i = tid; i < kC * kC; i += 256) {
-        Xs[(i / kC) * 65 + (i % kC)] = __ldg(x_in + row0 * kC + i);
-        Gs[(i / kC) * 65 + (i % kC)] = __ldg(g_in + row0 * kC + i);
+    for (int i = tid; i < kC * kC / 4; i += 256) {
+        const int r = i / (kC / 4), c = (i % (kC / 4)) * 4;
+        *reinterpret_cast<float4 *>(Xs + r * kPadX + c) = __ldg(reinterpret_cast<const float4 *>(x_in + row0 * kC + r * kC + c));
+        *reinterpret_cast<float4 *>(Gs + r * kPadX + c) = __ldg(reinterpret_cast<const float4 *>(g_in + row0 * kC + r * kC + c));
     }
     if (tid < kC) be[tid] = beta[row0 + tid];
     if (tid < 32) {
@@ -733,64 +766,73 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     }
     __syncthreads();
 
-    float qv[4][8], kv[4][8];   // this thread's Q and K entries
+    const int t0 = m0 + g, t1 = t0 + 8;   // this thread's two positions
+    // Q or K at the accumulator's positions: columns n0 + 8 nt + 2 t4 (+1) of rows t0, t1
+    auto pair_at = [&](const __nv_bfloat16 *tile, int row, int nt, float &x0, float &x1) {
+        unpack_bf16x2(*reinterpret_cast<const uint32_t *>(tile + row * kPadH + n0 + 8 * nt + 2 * t4), x0, x1);
+    };
+    // sum_i tile[row][i] * acc[.][row half] over this thread's columns
+    auto dot_rows = [&](const __nv_bfloat16 *tile, const float (&acc)[8][4], float &r0, float &r1) {
+        r0 = r1 = 0.0f;
 #pragma unroll
-    for (int r = 0; r < 4; r++)
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-            qv[r][c] = __bfloat162float(Qh[(4 * ty + r) * kPadH + tx + 16 * c]);
-            kv[r][c] = __bfloat162float(Kh[(4 * ty + r) * kPadH + tx + 16 * c]);
+        for (int nt = 0; nt < 8; nt++) {
+            float a0, a1, b0, b1;
+            pair_at(tile, t0, nt, a0, a1);
+            pair_at(tile, t1, nt, b0, b1);
+            r0 += a0 * acc[nt][0] + a1 * acc[nt][1];
+            r1 += b0 * acc[nt][2] + b1 * acc[nt][3];
         }
-    float dqa[4][8], dka[4][8];
+    };
+    auto put_rows = [&](int which, float r0, float r1) {   // this warp's share of a row sum
+        r0 = sum_quad(r0);
+        r1 = sum_quad(r1);
+        if (t4 == 0) { part[(which * 2 + nh) * 64 + t0] = r0; part[(which * 2 + nh) * 64 + t1] = r1; }
+    };
 
-    // phase 1: T1 = dO S', T2 = dZ S';  K S for dbeta
+    float dqa[8][4], dka[8][4];
+    // phase 1: T1 = dO S', T2 = dZ S' (one sweep over the state's rows for both)
     {
-        float t1[4][8] = {}, t2[4][8] = {};
-        rows_dot_rows(M0, M1, Sb, ty, tx, t1, t2);
-#pragma unroll
-        for (int r = 0; r < 4; r++) {
-            const int t = 4 * ty + r;
-            const float e = eca[t], b = be[t];
-            float de = 0.0f;
-#pragma unroll
-            for (int c = 0; c < 8; c++) {
-                dqa[r][c] = e * t1[r][c];
-                dka[r][c] = -e * b * t2[r][c];
-                de += qv[r][c] * t1[r][c] - b * kv[r][c] * t2[r][c];
-            }
-            de = sum16(de);
-            if (tx == 0) v_de[t] = de;
+        float t1a[8][4] = {}, t2a[8][4] = {};
+#pragma unroll 2
+        for (int k0 = 0; k0 < kDV; k0 += 8) {
+            uint32_t a0[4], a1[4];
+            frag_a_f32(a0, M0, kPadF, m0, k0, g, t4);
+            frag_a_f32(a1, M1, kPadF, m0, k0, g, t4);
+            mma2_row_nk(t1a, t2a, a0, a1, Sb, kPadF, n0, k0, g, t4);
         }
-        // (K S)[t][j] for j = tx + 16c, then rowsum(dZ .* (V - e K S))
-        float ks[4][8] = {};
-        for (int i = 0; i < kDK; i += 8) {
-            float kr[4][8];
+        float q0, q1, k0s, k1s;
+        dot_rows(Qh, t1a, q0, q1);
+        dot_rows(Kh, t2a, k0s, k1s);
+        put_rows(DE, q0 - be[t0] * k0s, q1 - be[t1] * k1s);
+        const float e0 = eca[t0], e1 = eca[t1], b0 = -e0 * be[t0], b1 = -e1 * be[t1];
 #pragma unroll
-            for (int r = 0; r < 4; r++) unpack8(Kh + (4 * ty + r) * kPadH + i, kr[r]);
-#pragma unroll
-            for (int e = 0; e < 8; e++) {
-                float sv[8];
-#pragma unroll
-                for (int c = 0; c < 8; c++) sv[c] = Sb[(i + e) * kPadF + tx + 16 * c];
-#pragma unroll
-                for (int r = 0; r < 4; r++)
-#pragma unroll
-                    for (int c = 0; c < 8; c++) ks[r][c] = fmaf(kr[r][e], sv[c], ks[r][c]);
-            }
+        for (int nt = 0; nt < 8; nt++) {
+            dqa[nt][0] = e0 * t1a[nt][0]; dqa[nt][1] = e0 * t1a[nt][1]; dqa[nt][2] = e1 * t1a[nt][2]; dqa[nt][3] = e1 * t1a[nt][3];
+            dka[nt][0] = b0 * t2a[nt][0]; dka[nt][1] = b0 * t2a[nt][1]; dka[nt][2] = b1 * t2a[nt][2]; dka[nt][3] = b1 * t2a[nt][3];
         }
-#pragma unroll
-        for (int r = 0; r < 4; r++) {
-            const int t = 4 * ty + r;
-            const float e = eca[t];
-            float rdz = 0.0f;
-#pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const float vv = bf16_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(v) + (row0 + t) * kDV + tx + 16 * c));
-                rdz += M1[t * kPadF + tx + 16 * c] * (vv - e * ks[r][c]);
-            }
-            rdz = sum16(rdz);
-            if (tx == 0) v_rdz[t] = rdz;
+    }
+    // K S at (position, value feature), then rowsum(dZ .* (V - e K S)) for dbeta
+    {
+        float ks[8][4] = {};
+#pragma unroll 2
+        for (int k0 = 0; k0 < kDK; k0 += 8) {
+            uint32_t af[4];
+            frag_a_bf16(af, Kh, kPadH, m0, k0, g, t4);
+            mma_row_kn(ks, af, Sb, kPadF, n0, k0, g, t4);
         }
+        const float e0 = eca[t0], e1 = eca[t1];
+        float r0 = 0.0f, r1 = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            const int col = n0 + 8 * nt + 2 * t4;
+            float v00, v01, v10, v11;
+            unpack_bf16x2(__ldg(reinterpret_cast<const uint32_t *>(v + (row0 + t0) * kDV + col)), v00, v01);
+            unpack_bf16x2(__ldg(reinterpret_cast<const uint32_t *>(v + (row0 + t1) * kDV + col)), v10, v11);
+            const float2 z0 = *reinterpret_cast<const float2 *>(M1 + t0 * kPadF + col), z1 = *reinterpret_cast<const float2 *>(M1 + t1 * kPadF + col);
+            r0 += z0.x * (v00 - e0 * ks[nt][0]) + z0.y * (v01 - e0 * ks[nt][1]);
+            r1 += z1.x * (v10 - e1 * ks[nt][2]) + z1.y * (v11 - e1 * ks[nt][3]);
+        }
+        put_rows(RDZ, r0, r1);
     }
     __syncthreads();
 
@@ -811,114 +853,123 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) dgp += __shfl_xor_sync(0xffffffffu, dgp, o);
-        if ((tid & 31) == 0) red[tid >> 5] = dgp;
+        if (lane == 0) red[warp] = dgp;
     }
     __syncthreads();
     {
-        float t3[4][8] = {};
-        float unused[4][8];
-        rows_dot_rows(M0, nullptr, Sb, ty, tx, t3, unused);
+        float t3[8][4] = {};
+#pragma unroll 2
+        for (int k0 = 0; k0 < kDV; k0 += 8) {
+            uint32_t af[4];
+            frag_a_f32(af, M0, kPadF, m0, k0, g, t4);
+            mma_row_nk(t3, af, Sb, kPadF, n0, k0, g, t4);
+        }
+        float r0, r1;
+        dot_rows(Kh, t3, r0, r1);
+        put_rows(DED, r0, r1);
+        const float e0 = ekd[t0], e1 = ekd[t1];
 #pragma unroll
-        for (int r = 0; r < 4; r++) {
-            const int t = 4 * ty + r;
-            const float ed = ekd[t];
-            float ded = 0.0f;
-#pragma unroll
-            for (int c = 0; c < 8; c++) {
-                dka[r][c] = fmaf(ed, t3[r][c], dka[r][c]);
-                ded += kv[r][c] * t3[r][c];
-            }
-            ded = sum16(ded);
-            if (tx == 0) v_ded[t] = ded;
+        for (int nt = 0; nt < 8; nt++) {
+            dka[nt][0] = fmaf(e0, t3[nt][0], dka[nt][0]); dka[nt][1] = fmaf(e0, t3[nt][1], dka[nt][1]);
+            dka[nt][2] = fmaf(e1, t3[nt][2], dka[nt][2]); dka[nt][3] = fmaf(e1, t3[nt][3], dka[nt][3]);
         }
     }
 
-    // phase 3a: X K and X' Q
-    {
-        float xk[4][8] = {}, xq[4][8] = {};
-        for (int s = 0; s < kC; s++) {
-            float ks[8], qs[8], xr[4], xc[4];
+    // phase 3: the four products over the chunk's own positions (B[k][n] = K[s][i] or Q[s][i], BFloat16 tiles)
+    auto mma_tile_bf16 = [&](float (&acc)[8][4], const uint32_t (&af)[4], const __nv_bfloat16 *tile, int k0) {
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                ks[c] = __bfloat162float(Kh[s * kPadH + tx + 16 * c]);
-                qs[c] = __bfloat162float(Qh[s * kPadH + tx + 16 * c]);
-            }
-#pragma unroll
-            for (int r = 0; r < 4; r++) { xr[r] = Xs[(4 * ty + r) * 65 + s]; xc[r] = Xs[s * 65 + 4 * ty + r]; }
-#pragma unroll
-            for (int r = 0; r < 4; r++)
-#pragma unroll
-                for (int c = 0; c < 8; c++) {
-                    xk[r][c] = fmaf(xr[r], ks[c], xk[r][c]);
-                    xq[r][c] = fmaf(xc[r], qs[c], xq[r][c]);
-                }
+        for (int nt = 0; nt < 8; nt++) {
+            const __nv_bfloat16 *p = tile + (k0 + t4) * kPadH + n0 + 8 * nt + g;
+            mma_tf32(acc[nt], af, tf32_of_bf16(p), tf32_of_bf16(p + 4 * kPadH));
         }
+    };
+    {   // X K -> dQ and its row sum with Q
+        float xk[8][4] = {};
+#pragma unroll 2
+        for (int k0 = 0; k0 < kC; k0 += 8) {
+            uint32_t af[4];
+            frag_a_f32(af, Xs, kPadX, m0, k0, g, t4);
+            mma_tile_bf16(xk, af, Kh, k0);
+        }
+        float r0, r1;
+        dot_rows(Qh, xk, r0, r1);
+        put_rows(RQ, r0, r1);
 #pragma unroll
-        for (int r = 0; r < 4; r++) {
-            float rq = 0.0f, cq = 0.0f;
+        for (int nt = 0; nt < 8; nt++)
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                dqa[r][c] += xk[r][c];
-                dka[r][c] += xq[r][c];
-                rq += qv[r][c] * xk[r][c];
-                cq += kv[r][c] * xq[r][c];
-            }
-            rq = sum16(rq);
-            cq = sum16(cq);
-            if (tx == 0) { v_rq[4 * ty + r] = rq; v_cq[4 * ty + r] = cq; }
+            for (int e = 0; e < 4; e++) dqa[nt][e] += xk[nt][e];
+    }
+    {   // X' Q -> dK and its row sum with K
+        float xq[8][4] = {};
+#pragma unroll 2
+        for (int k0 = 0; k0 < kC; k0 += 8) {
+            uint32_t af[4];
+            frag_at_f32(af, Xs, kPadX, m0, k0, g, t4, nullptr);
+            mma_tile_bf16(xq, af, Qh, k0);
+        }
+        float r0, r1;
+        dot_rows(Kh, xq, r0, r1);
+        put_rows(CQ, r0, r1);
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) dka[nt][e] += xq[nt][e];
+    }
+    {   // G K -> beta-scaled into dK, its row sum with K feeds dbeta and the gate gradient
+        float gk[8][4] = {};
+#pragma unroll 2
+        for (int k0 = 0; k0 < kC; k0 += 8) {
+            uint32_t af[4];
+            frag_a_f32(af, Gs, kPadX, m0, k0, g, t4);
+            mma_tile_bf16(gk, af, Kh, k0);
+        }
+        float r0, r1;
+        dot_rows(Kh, gk, r0, r1);
+        put_rows(RK, r0, r1);
+        const float b0 = be[t0], b1 = be[t1];
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            dka[nt][0] = fmaf(b0, gk[nt][0], dka[nt][0]); dka[nt][1] = fmaf(b0, gk[nt][1], dka[nt][1]);
+            dka[nt][2] = fmaf(b1, gk[nt][2], dka[nt][2]); dka[nt][3] = fmaf(b1, gk[nt][3], dka[nt][3]);
         }
     }
-    // phase 3b: G K and G' (beta K)
-    {
-        float gk[4][8] = {}, gb[4][8] = {};
-        for (int s = 0; s < kC; s++) {
-            float ks[8], gr[4], gc[4];
-            const float bs = be[s];
-#pragma unroll
-            for (int c = 0; c < 8; c++) ks[c] = __bfloat162float(Kh[s * kPadH + tx + 16 * c]);
-#pragma unroll
-            for (int r = 0; r < 4; r++) { gr[r] = Gs[(4 * ty + r) * 65 + s]; gc[r] = Gs[s * 65 + 4 * ty + r] * bs; }
-#pragma unroll
-            for (int r = 0; r < 4; r++)
-#pragma unroll
-                for (int c = 0; c < 8; c++) {
-                    gk[r][c] = fmaf(gr[r], ks[c], gk[r][c]);
-                    gb[r][c] = fmaf(gc[r], ks[c], gb[r][c]);
-                }
+    {   // G' (beta K)
+        float gb[8][4] = {};
+#pragma unroll 2
+        for (int k0 = 0; k0 < kC; k0 += 8) {
+            uint32_t af[4];
+            frag_at_f32(af, Gs, kPadX, m0, k0, g, t4, be);
+            mma_tile_bf16(gb, af, Kh, k0);
         }
+        float r0, r1;
+        dot_rows(Kh, gb, r0, r1);
+        put_rows(CK, r0, r1);
 #pragma unroll
-        for (int r = 0; r < 4; r++) {
-            const float b = be[4 * ty + r];
-            float rk = 0.0f, ck = 0.0f;
+        for (int nt = 0; nt < 8; nt++)
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                dka[r][c] += b * gk[r][c] + gb[r][c];
-                rk += kv[r][c] * gk[r][c];
-                ck += kv[r][c] * gb[r][c];
-            }
-            rk = sum16(rk);
-            ck = sum16(ck);
-            if (tx == 0) { v_rk[4 * ty + r] = rk; v_ck[4 * ty + r] = ck; }
-        }
+            for (int e = 0; e < 4; e++) dka[nt][e] += gb[nt][e];
     }
     __syncthreads();   // every reader of U (M0) and dZ (M1) is done; the row sums are visible
 
 #pragma unroll
-    for (int r = 0; r < 4; r++)
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-            M0[(4 * ty + r) * kPadF + tx + 16 * c] = dqa[r][c];
-            M1[(4 * ty + r) * kPadF + tx + 16 * c] = dka[r][c];
-        }
+    for (int nt = 0; nt < 8; nt++) {
+        const int col = n0 + 8 * nt + 2 * t4;
+        *reinterpret_cast<float2 *>(M0 + t0 * kPadF + col) = make_float2(dqa[nt][0], dqa[nt][1]);
+        *reinterpret_cast<float2 *>(M0 + t1 * kPadF + col) = make_float2(dqa[nt][2], dqa[nt][3]);
+        *reinterpret_cast<float2 *>(M1 + t0 * kPadF + col) = make_float2(dka[nt][0], dka[nt][1]);
+        *reinterpret_cast<float2 *>(M1 + t1 * kPadF + col) = make_float2(dka[nt][2], dka[nt][3]);
+    }
+    auto row_sum = [&](int which, int t) { return part[(which * 2) * 64 + t] + part[(which * 2 + 1) * 64 + t]; };
     if (tid == 0) {
         // the gradient of ca, then da = its reverse cumulative sum inside the chunk
         float dg = 0.0f;
         for (int w = 0; w < 8; w++) dg += red[w];
         float tail = dg * gamma_sm;
-        for (int t = 0; t < kC; t++) tail += v_ded[t] * ekd[t];
+        for (int t = 0; t < kC; t++) tail += row_sum(DED, t) * ekd[t];
         float run = 0.0f;
         for (int t = kC - 1; t >= 0; t--) {
-            float dca = v_rq[t] + be[t] * v_rk[t] - v_cq[t] - v_ck[t] + v_de[t] * eca[t] - v_ded[t] * ekd[t];
+            float dca = row_sum(RQ, t) + be[t] * row_sum(RK, t) - row_sum(CQ, t) - row_sum(CK, t) + row_sum(DE, t) * eca[t] -
+                        row_sum(DED, t) * ekd[t];
             if (t == kC - 1) dca += tail;
             run += dca;
             da[row0 + t] = run;
@@ -926,7 +977,7 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     }
     if (tid >= 32 && tid < 32 + kC) {
         const int t = tid - 32;
-        dbeta[row0 + t] = v_rdz[t] + v_rk[t];
+        dbeta[row0 + t] = row_sum(RDZ, t) + row_sum(RK, t);
     }
     __syncthreads();
     for (int i = tid; i < kC * kDK / 8; i += 256) {
@@ -948,7 +999,7 @@ constexpr size_t kScanSmem = (kDK * kPadS + kC * kPadS + 4 * kC) * sizeof(float)
 constexpr size_t kBwdScanSmem = (kDK * kPadS + 3 * kC * kPadS + kC * kPadM + 3 * kC) * sizeof(float) +
                                 (2 * kC * kPadH + kC * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdXgSmem = (3 * kC * kPadF + kC) * sizeof(float);
-constexpr size_t kBwdOutSmem = (kDK * kPadF + 2 * kC * kPadF + 2 * kC * 65 + 10 * kC + 8) * sizeof(float) +
+constexpr size_t kBwdOutSmem = (kDK * kPadF + 2 * kC * kPadF + 2 * kC * kPadX + 3 * kC + 7 * 2 * kC + 8) * sizeof(float) +
                                2 * kC * kPadH * sizeof(__nv_bfloat16);
 
 }  // namespace
