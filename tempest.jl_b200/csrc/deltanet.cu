@@ -1,4 +1,4 @@
-// Chunked gated DeltaNet forward (delta-rule linear attention) for sm_100a.
+// Chunked gated DeltaNet (delta-rule linear attention), forward and pullback, for sm_100a.
 //
 // The rule  S_t = exp(a_t) (S_{t-1} - beta_t k_t (k_t' S_{t-1})) + beta_t k_t v_t',  o_t = S_t' q_t  in the
 // chunked WY form of examples/deltanet.jl:58-85 (chunks of C = 64 positions):
@@ -14,9 +14,11 @@
 // columns at once, one column per thread with the solution held in registers -- the same numbers, no
 // inverse.  `deltanet_scan_kernel` carries the state, one block per (head, 32 value features): the state
 // slice (128 x 32 Float32) lives in shared memory for all 128 chunks and each chunk costs three small
-// products.  The path is bound by the chain of chunks and by HBM, not by the tensor cores (about 0.1 TFLOP
-// in all), which is why this first version keeps to Float32 CUDA-core arithmetic; W, Ut and P are rounded
-// to BFloat16 when they cross from one launch to the other.
+// products, issued as TF32 warp-level MMAs with operands in shared memory and results in registers (each
+// product feeds the next one of the chain at once; about 0.1 TFLOP in all).  The path is bound by the chain
+// of chunks, not by the tensor cores or HBM; W, Ut and P are rounded to BFloat16 when they cross from one
+// launch to the other.  The pullback (further down) recomputes the forward keeping the state at every chunk
+// start, walks the chunks backwards for the state gradient, and finishes per chunk.
 #include <mutex>
 
 #include "common.cuh"
