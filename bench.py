@@ -584,17 +584,35 @@ def run_e2e(torch, dist, wl, world, args):
     for eltype, outs in wl.outputs.items():
         d2h += sum(t.numel() * t.element_size() for t in outs)
 
+    # Three streams, as a host that feeds the kernels would run them: inputs arrive on a copy-in stream, each
+    # kernel waits only for the operands it reads, and each result leaves on a copy-out stream as soon as its
+    # kernel has finished -- PCIe carries both directions at once.  A step still contains every byte in and out.
+    compute = torch.cuda.current_stream()
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    # what each launch of wl.launches reads first, and which results it completes (names of wl.outputs' slots)
+    reads = {"softmax_fwd": 0, "softmax_bwd": 1, "layernorm_fwd": 0, "layernorm_bwd": 1}
+    writes = {"softmax_fwd": (0, 4), "softmax_bwd": (1,), "layernorm_fwd": (2,), "layernorm_bwd": (3, 5, 6)}
+
     def one_step():
-        for eltype in wl.inputs:
-            dev_in[eltype][0].copy_(host_in[eltype][0], non_blocking=True)
-            dev_in[eltype][1].copy_(host_in[eltype][1], non_blocking=True)
-        wl.step()
-        for eltype, (y, dx, yl, dxl, lse, dw, db) in wl.outputs.items():
-            for t in (y, dx, yl, dxl):
-                host_out[eltype].copy_(t, non_blocking=True)
-            host_small.copy_(lse, non_blocking=True)
-            host_vec[eltype].copy_(dw, non_blocking=True)
-            host_vec[eltype].copy_(db, non_blocking=True)
+        copy_in.wait_stream(compute)          # the previous step's kernels are done with the input buffers
+        arrived = {}
+        with torch.cuda.stream(copy_in):
+            for eltype in wl.inputs:
+                for slot in (0, 1):
+                    dev_in[eltype][slot].copy_(host_in[eltype][slot], non_blocking=True)
+                    arrived[(eltype, slot)] = copy_in.record_event()
+        for name, eltype, launch, _ in wl.launches:
+            compute.wait_event(arrived[(eltype, reads[name])])
+            launch()
+            done = compute.record_event()
+            outs = wl.outputs[eltype]
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(done)
+                for slot in writes[name]:
+                    t = outs[slot]
+                    target = host_out[eltype] if slot < 4 else host_small if slot == 4 else host_vec[eltype]
+                    target.copy_(t, non_blocking=True)
+        compute.wait_stream(copy_out)         # the step ends when its last result is on the host
 
     steps = max(1, min(args.steps, args.e2e_steps))
     one_step()

@@ -359,6 +359,107 @@ __global__ void __launch_bounds__(kResidentMaxThreads) layernorm_bwd_resident(Ro
     else layernorm_bwd_resident_body<T, VEC, VPT, false>(a);
 }
 
+// The BFloat16 LayerNorm backward again for the common case (128-bit accesses, rows that fill every slot,
+// mean and rstd saved by the forward), arranged for occupancy: the general kernel above holds x, dy and gamma
+// widened to Float32 beside its two sets of accumulators (127 registers, two blocks of 256 threads per SM),
+// and at that occupancy it waits on issue slots rather than on HBM.  Here x and dy stay packed as they were
+// loaded (eight registers per array instead of sixteen), gamma is re-read from L1, the dgamma / dbeta
+// accumulators live in shared memory (each thread's own slots, one 128-bit read-modify-write per four
+// elements per row), and the row is unpacked twice -- once for the two row sums and the accumulators, once
+// for dx -- which costs a few shifts and buys twice the resident warps.
+template <int VPT>
+__global__ void __launch_bounds__(256, 4) layernorm_bwd_compact(RowArgs a) {
+    using R = Row<__nv_bfloat16, true, VPT>;
+    __shared__ float red[2 * 32 * kRedWidth];
+    __shared__ float4 acc[2 * 2 * VPT * 256];   // [dgamma | dbeta][chunk][half of the chunk][thread]
+    RowCtx c = make_row_ctx(a.tpr, red);
+    const int tid = threadIdx.x;
+    const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(a.in0);
+    const __nv_bfloat16 *dy = static_cast<const __nv_bfloat16 *>(a.in1);
+    const __nv_bfloat16 *gamma = static_cast<const __nv_bfloat16 *>(a.gamma);
+    __nv_bfloat16 *dx = static_cast<__nv_bfloat16 *>(a.out0);
+    const float *mean_in = static_cast<const float *>(a.cstat0), *rstd_in = static_cast<const float *>(a.cstat1);
+#pragma unroll
+    for (int i = 0; i < 2 * 2 * VPT; i++) acc[i * 256 + tid] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const float inv_n = 1.0f / static_cast<float>(a.n);
+    const long long groups = a.rows / a.rpc;
+    for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
+        const long long r = g * a.rpc + c.slot;
+        uint4 rx[VPT], rd[VPT];
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            rx[k] = __ldcs(reinterpret_cast<const uint4 *>(x + r * a.ld + R::at(k, c.t, a.tpr)));
+            rd[k] = __ldcs(reinterpret_cast<const uint4 *>(dy + r * a.ld + R::at(k, c.t, a.tpr)));
+        }
+        const float mean = mean_in[r], rstd = rstd_in[r];
+        const float2 rs2 = make_float2(rstd, rstd), off2 = make_float2(-mean * rstd, -mean * rstd);
+        float2 sa = make_float2(0.0f, 0.0f), sb = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const uint4 gq = __ldg(reinterpret_cast<const uint4 *>(gamma + R::at(k, c.t, a.tpr)));
+            const uint32_t xw[4] = {rx[k].x, rx[k].y, rx[k].z, rx[k].w}, dw[4] = {rd[k].x, rd[k].y, rd[k].z, rd[k].w},
+                           gw[4] = {gq.x, gq.y, gq.z, gq.w};
+#pragma unroll
+            for (int h = 0; h < 2; h++) {   // four elements = one accumulator slot at a time
+                float4 *slot_g = &acc[((2 * k + h) * 256) + tid], *slot_b = &acc[((2 * VPT + 2 * k + h) * 256) + tid];
+                float4 ag = *slot_g, ab = *slot_b;
+                float *pg = &ag.x, *pb = &ab.x;
+#pragma unroll
+                for (int w = 0; w < 2; w++) {
+                    float2 xv, dy2, gm;
+                    unpack_bf16x2(xw[2 * h + w], xv.x, xv.y);
+                    unpack_bf16x2(dw[2 * h + w], dy2.x, dy2.y);
+                    unpack_bf16x2(gw[2 * h + w], gm.x, gm.y);
+                    const float2 xh = __ffma2_rn(xv, rs2, off2);
+                    const float2 gh = __fmul2_rn(dy2, gm);
+                    sa = __fadd2_rn(sa, gh);
+                    sb = __ffma2_rn(gh, xh, sb);
+                    const float2 g2 = __ffma2_rn(dy2, xh, make_float2(pg[2 * w], pg[2 * w + 1]));
+                    const float2 b2 = __fadd2_rn(make_float2(pb[2 * w], pb[2 * w + 1]), dy2);
+                    pg[2 * w] = g2.x; pg[2 * w + 1] = g2.y;
+                    pb[2 * w] = b2.x; pb[2 * w + 1] = b2.y;
+                }
+                *slot_g = ag;
+                *slot_b = ab;
+            }
+        }
+        float s2[2] = {sa.x + sa.y, sb.x + sb.y};
+        row_allreduce<2>(s2, c, SumOp());
+        const float c1 = s2[0] * inv_n, c2 = s2[1] * inv_n;
+        const float2 nc1 = make_float2(-c1, -c1), nc2 = make_float2(-c2, -c2);
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const uint4 gq = __ldg(reinterpret_cast<const uint4 *>(gamma + R::at(k, c.t, a.tpr)));
+            const uint32_t xw[4] = {rx[k].x, rx[k].y, rx[k].z, rx[k].w}, dw[4] = {rd[k].x, rd[k].y, rd[k].z, rd[k].w},
+                           gw[4] = {gq.x, gq.y, gq.z, gq.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                float2 xv, dy2, gm;
+                unpack_bf16x2(xw[w], xv.x, xv.y);
+                unpack_bf16x2(dw[w], dy2.x, dy2.y);
+                unpack_bf16x2(gw[w], gm.x, gm.y);
+                const float2 xh = __ffma2_rn(xv, rs2, off2);
+                const float2 gh = __fmul2_rn(dy2, gm);
+                const float2 u = __fmul2_rn(__ffma2_rn(xh, nc2, __fadd2_rn(gh, nc1)), rs2);
+                ow[w] = pack_bf16x2(u.x, u.y);
+            }
+            __stcs(reinterpret_cast<uint4 *>(dx + r * a.ld + R::at(k, c.t, a.tpr)), make_uint4(ow[0], ow[1], ow[2], ow[3]));
+        }
+    }
+    if (a.part0) {
+        const long long p = static_cast<long long>(blockIdx.x) * a.rpc + c.slot;
+#pragma unroll
+        for (int k = 0; k < VPT; k++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int col = R::at(k, c.t, a.tpr) + 4 * h;
+                *reinterpret_cast<float4 *>(a.part0 + p * a.n + col) = acc[((2 * k + h) * 256) + tid];
+                *reinterpret_cast<float4 *>(a.part1 + p * a.n + col) = acc[((2 * VPT + 2 * k + h) * 256) + tid];
+            }
+    }
+}
+
 // Column sums of the partial dgamma / dbeta rows: 32 columns x 8 lanes per
 // block; each lane strides over the parts in order, the 8 lanes merge in a
 // fixed tree.  Output in the element type, rounded once.
@@ -757,6 +858,16 @@ using namespace tb200;
 
 namespace {
 
+// The LayerNorm backward's kernel for a schedule: the compact BFloat16 form where it applies (128-bit accesses,
+// every slot filled, 256-thread blocks, statistics saved by the forward), else the general family.
+RowKernel ln_bwd_kernel(int dtype, const Schedule &s, bool saved_stats) {
+    if (dtype == TB200_BF16 && s.vec && s.exact && saved_stats && s.threads == 256) {
+        if (s.vpt == 1) return layernorm_bwd_compact<1>;
+        if (s.vpt == 2) return layernorm_bwd_compact<2>;
+    }
+    return pick<LayernormBwdResident>(dtype, s);
+}
+
 // Bytes of scratch one schedule of an operator needs.
 int schedule_workspace(RowOp op, const Schedule &s, const DeviceInfo &dev, int64_t n, int64_t rows, int dtype,
                        size_t *bytes) {
@@ -766,9 +877,12 @@ int schedule_workspace(RowOp op, const Schedule &s, const DeviceInfo &dev, int64
         return TB200_OK;
     }
     if (op == OP_LN_BWD) {
-        long long grid = 0;
-        int st = resident_grid(pick<LayernormBwdResident>(dtype, s), s, dev, &grid);
+        // either form may run (the call decides by its arguments): room for the larger grid
+        long long grid = 0, compact = 0;
+        int st = resident_grid(ln_bwd_kernel(dtype, s, false), s, dev, &grid);
         if (st) return st;
+        if ((st = resident_grid(ln_bwd_kernel(dtype, s, true), s, dev, &compact))) return st;
+        if (compact > grid) grid = compact;
         *bytes = static_cast<size_t>(grid) * s.rpc * static_cast<size_t>(n) * 2 * sizeof(float);
     }
     return TB200_OK;
@@ -890,7 +1004,7 @@ extern "C" int tb200_layernorm_bwd(const void *x, const void *gamma, const void 
     a.in0 = x; a.in1 = dy; a.gamma = gamma; a.out0 = dx; a.cstat0 = mean; a.cstat1 = rstd; a.eps = eps;
     a.n = static_cast<int>(n); a.rows = rows; a.ld = ld; a.tpr = s.tpr; a.rpc = s.rpc; a.splits = 1;
     a.exact = s.exact;
-    const RowKernel kernel = pick<LayernormBwdResident>(dtype, s);
+    const RowKernel kernel = ln_bwd_kernel(dtype, s, mean && rstd);
     long long grid = 0;
     if ((st = resident_grid(kernel, s, dev, &grid))) return st;
     const bool sums = dgamma || dbeta;
