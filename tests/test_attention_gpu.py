@@ -187,6 +187,26 @@ def test_decode_up_to_lengths(pkg, cuda, oracle):
     assert (o[0] == 0).all() and torch.isinf(lse[0]).all() and torch.isfinite(lse[1]).all()
 
 
+def test_masked_entries_refuse_bad_requests(pkg, cuda):
+    L, torch = pkg.lib, cuda
+    x = torch.zeros(4096, device="cuda", dtype=torch.bfloat16)
+    p = x.data_ptr()
+    mask = L.attn_mask()
+    with pytest.raises(L.TB200Error) as e:
+        L.attention_fwd_masked(L.attn_desc(1, 2, 8, 8, 512, False), mask, p, p, p, p)
+    assert e.value.status == -7
+    with pytest.raises(L.TB200Error) as e:
+        L.attention_fwd_masked(L.attn_desc(1, 2, 8, 8, 16, False), mask, p, 0, p, p)
+    assert e.value.status == -1
+    with pytest.raises(L.TB200Error) as e:   # causal needs as many queries as keys
+        L.attention_fwd_masked(L.attn_desc(1, 2, 8, 16, 16, True), mask, p, p, p, p)
+    assert e.value.status == -2
+    with pytest.raises(L.TB200Error) as e:
+        L.attention_bwd_masked(L.attn_desc(1, 2, 8, 8, 16, False), mask, p, p, p, p, 0, p, p, p, p)
+    assert e.value.status == -1
+    L.attention_fwd_masked(L.attn_desc(0, 2, 8, 8, 16, False), mask, 0, 0, 0, 0)   # an empty batch
+
+
 def torch_reference(torch, q, k, v, causal, dout=None):
     """Plain Float32 PyTorch restatement on the device, one head at a time."""
     B, S, H, D = q.shape

@@ -114,3 +114,23 @@ def test_refuses_other_geometries(pkg, cuda):
             L.deltanet_fwd(desc, x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(),
                            x.data_ptr(), 1 << 20)
         assert e.value.status == -7
+
+
+def test_pullback_refuses_what_it_cannot_run(pkg, cuda):
+    L = pkg.lib
+    x = cuda.zeros(1 << 16, device="cuda")
+    p = x.data_ptr()
+    args = [p] * 11
+    with pytest.raises(L.TB200Error) as e:   # other geometries
+        L.deltanet_bwd(L.deltanet_desc(1, 128, dk=64), *args, p, 1 << 30)
+    assert e.value.status == -7
+    d = L.deltanet_desc(1, 128)
+    need = L.deltanet_bwd_workspace_bytes(d)
+    assert need == L.deltanet_workspace_bytes(d) + 128 * 3840
+    with pytest.raises(L.TB200Error) as e:   # a workspace that is too small
+        L.deltanet_bwd(d, *args, p, need - 1)
+    assert e.value.status == -5
+    with pytest.raises(L.TB200Error) as e:   # a missing gradient array
+        L.deltanet_bwd(d, *([p] * 10), 0, p, need)
+    assert e.value.status == -1
+    L.deltanet_bwd(L.deltanet_desc(0, 128), *args, 0, 0)   # nothing to do
