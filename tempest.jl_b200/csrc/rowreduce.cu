@@ -748,8 +748,11 @@ Schedule plan_rows(RowOp op, int64_t n, int64_t rows, int64_t ld, int dtype, boo
     s.vec = aligned16 && n % epv_vec == 0 && ld % epv_vec == 0;
     const int epv = s.vec ? epv_vec : 1;
     const int max_e = resident_elems(op);
-    const int max_vpt = s.vec ? max_e / epv : 8;
+    int max_vpt = s.vec ? max_e / epv : 8;
     const int64_t nvec = n / epv;
+    // the forward kernels hold one row-sized array: four vectors a thread over twice the threads keep more warps
+    // resident than eight (measured on 4096-long Float32 rows); longer rows still take eight
+    if (s.vec && max_vpt > 4 && (op == OP_SOFTMAX_FWD || op == OP_LN_FWD) && nvec <= 4 * kResidentMaxThreads) max_vpt = 4;
     const int tpr = next_pow2(ceil_div(nvec, max_vpt));
     if (tpr <= kResidentMaxThreads) {
         s.split = false;
