@@ -115,7 +115,11 @@ int tb200_layernorm_fwd(const void *x, const void *gamma, const void *beta, void
  * reference's partial folds and merge kernel, ext/cuTileExt/emit.jl:744-753,
  * build.jl:654-696), so results repeat bit for bit.
  * mean/rstd NULL: recomputed from x.  dgamma and dbeta both NULL: no workspace
- * is needed.  Rows longer than 8192 elements: TB200_ERR_UNSUPPORTED. */
+ * is needed for rows the resident schedule holds (up to 8192 elements with
+ * 128-bit accesses, 4096 without).  Longer rows are streamed: one block walks
+ * a row three or four times through L2, a second kernel takes the column sums
+ * over row slabs; that form keeps recomputed statistics and the slabs'
+ * partial sums in the workspace (tb200_rowop_workspace_bytes covers it). */
 int tb200_layernorm_bwd(const void *x, const void *gamma, const void *dy, const float *mean,
                         const float *rstd, void *dx, void *dgamma, void *dbeta, float eps,
                         int64_t n, int64_t rows, int64_t ld, int dtype, void *workspace,

@@ -4,20 +4,25 @@
 //
 //   stats      delta[m] = sum_d dO[d,m] o[d,m] (o as stored in BFloat16) and lse * log2(e), both
 //              re-laid out [batch][head][query] so that consecutive queries are contiguous
-//   dK, dV     one item = 128 keys of one (batch, key/value head); steps of 64 queries (of every query
+//   dK, dV     one item = 128 keys of one (batch, key/value head); steps of 128 queries (of every query
 //              head of the group):  S' = K Q', dP' = V dO'  ->  P' = exp2(S' c - lse), dS' = P' (dP' - delta)
-//              ->  dV += P' dO,  dK += dS' Q
-//   dQ         one item = 128 queries of one (batch, head); steps of 64 keys:
+//              ->  dK += dS' Q,  dV += P' dO
+//   dQ         one item = 128 queries of one (batch, head); steps of 128 keys:
 //              S = Q K', dP = dO V'  ->  dS = P (dP - delta)  ->  dQ += dS K
 //
-// Both run the same warp-specialised pipeline as the forward kernel: one thread issues TMA loads (the
-// item's 128-row operands once, the steps' 64-row operands through a 3-stage ring), one thread issues
-// tcgen05.mma (the two score products of step t+1 before the gradient products of step t), four warps
-// own one tensor-memory lane = one of the item's 128 rows each, read both 64-column score tiles into
-// registers, and write P / dS as BFloat16 into 128-byte-swizzled shared tiles that feed the gradient
-// products as K-major A operands; the steps' operands serve as MN-major B operands straight from their
-// [position][feature] layout.  Accumulators stay in tensor memory for the whole item.
-// Tensor memory: 2 x (S, dP) of 64 columns + two 128-column accumulators = 512 columns.
+// Both run one warp-specialised pipeline.  One thread issues TMA loads: the item's 128-row operands once,
+// the steps' operands through two 2-stage rings (one per operand, so that each tile is released by the
+// last product that reads it).  One thread issues tcgen05.mma, every product 128 x 128 x 128, in the order
+//      S(t+1),  dK(t), dV(t),  dP(t+1),  S(t+2), ...
+// Eight warps own the item's 128 rows (one tensor-memory lane each), four per half of the step's 128
+// columns.  A row thread reads its 64 scores, releases the score buffer (so the next scores are computed
+// while it works), forms P while the gradient products of the step before run, then reads its 64 dP
+// values, forms dS and writes P and dS as packed BFloat16 over the dP columns it has just read; the
+// gradient products take them from tensor memory as their A operand and the step's tiles, straight from
+// their [position][feature] layout, as MN-major B operands.  Only the read-modify-write of dP sits
+// between two products, and the next scores fill that gap.  MMAs of one CTA run in issue order, so dP(t+1)
+// cannot overwrite P / dS of step t early.  Accumulators stay in tensor memory for the whole item.
+// Tensor memory: S | dP | two 128-column accumulators = 512 columns.
 // No load uses cluster multicast.  Every barrier wait is bounded.
 #include <cuda.h>
 
@@ -33,26 +38,26 @@ namespace {
 using namespace sm100;
 
 constexpr int kOuter = 128;                 // rows of an item
-constexpr int kInner = 64;                  // positions per step
+constexpr int kInner = 128;                 // positions per step
 constexpr int kD = 128;                     // features
-constexpr int kOuterSlab = kOuter * 128;    // [128 rows][64 features]: 16 KB
-constexpr int kOuterBytes = 2 * kOuterSlab;
-constexpr int kInnerSlab = kInner * 128;    // [64 rows][64 features]: 8 KB
-constexpr int kInnerBytes = 2 * kInnerSlab;
-constexpr int kDsBytes = kOuter * 128;      // [128 rows][64 positions] BFloat16: 16 KB
-constexpr int kStages = 3;
-constexpr int kBwdThreads = 320;   // loader, MMA issuer, two groups of four row warps taking alternate steps
+constexpr int kSlab = 128 * 128;            // [128 rows][64 features]: 16 KB
+constexpr int kTileBytes = 2 * kSlab;       // one operand tile: 32 KB
+// Ring depths.  dK/dV: two stages each.  dQ: the K tile is read by the scores and, three products later, by
+// dQ += dS K, so its ring is three deep, and the V tile, free as soon as dP has read it, has one stage.
+template <bool DKDV> struct Rings { static constexpr int A = DKDV ? 2 : 3, B = DKDV ? 2 : 1; };
+constexpr int kBwdThreads = 320;   // loader, MMA issuer, two groups of four row warps (one per column half)
+constexpr int kRowWarps = 8;
 
 __device__ int g_attn_bwd_error = 0;
 
 struct AttnBwdArgs {
     CUtensorMap outer_a, outer_b;   // dK/dV: K, V   | dQ: Q, dO     (boxes of 128 rows)
-    CUtensorMap inner_a, inner_b;   // dK/dV: Q, dO  | dQ: K, V      (boxes of 64 rows)
+    CUtensorMap inner_a, inner_b;   // dK/dV: Q, dO  | dQ: K, V      (boxes of 128 rows)
     CUtensorMap out1, out2;         // dK/dV: dV, dK | dQ: -, dQ     (boxes of 32 rows)
     const float *lse2;              // [batch][head][query]  lse * log2(e)
     const float *delta;             // [batch][head][query]
     int batch, heads, kv_heads, queries, keys;
-    int outer_tiles, items;
+    int outer_tiles, supers;
     int causal;
     float scale, scale_log2;
 };
@@ -77,29 +82,43 @@ __device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, volatil
     }
 }
 
-// The steps of an item: which head and which 64-position chunk step t reads.
+// The walk over the work.  A CTA takes whole "supers": the i-th heaviest and the i-th lightest 128-row tile of
+// one (batch, head), one after the other (walk step j: super blockIdx.x + (j / 2) gridDim.x, half j % 2).  Under
+// the causal mask every super costs the same, so the static round-robin over CTAs is balanced; and supers are
+// numbered (batch, head)-major, so the CTAs that run at the same time read the step operands of a few heads
+// only and find them in L2 instead of streaming them from HBM once per tile.
+//
+// Steps: the item of one walk step, and which head and which 128-position chunk its step t reads.
 template <bool DKDV>
 struct Steps {
     int b, head_outer, tile;   // the item
     int c0, nc, group, count;
-    __device__ __forceinline__ Steps(const AttnBwdArgs &p, int item) {
+    bool done, skip;           // past the CTA's last super | second half of a super whose halves are one tile
+    __device__ __forceinline__ Steps(const AttnBwdArgs &p, int j) {
+        const int half_tiles = (p.outer_tiles + 1) / 2;
+        const int sup = blockIdx.x + (j >> 1) * gridDim.x;
+        done = sup >= p.supers;
+        skip = false;
+        count = 0;
+        if (done) return;
+        const int bh = sup / half_tiles, i = sup % half_tiles;
+        const int light = i, heavy_or_light = (j & 1);
+        skip = heavy_or_light && (light == p.outer_tiles - 1 - light);
         group = p.heads / p.kv_heads;
         if (DKDV) {
-            // heaviest first under the causal mask: the first keys see every query
-            const int per = p.batch * p.kv_heads;
-            tile = item / per;
-            b = (item % per) / p.kv_heads;
-            head_outer = item % p.kv_heads;
+            // the first keys see every query: they are the heavy ones under the causal mask
+            tile = heavy_or_light ? p.outer_tiles - 1 - i : i;
+            b = bh / p.kv_heads;
+            head_outer = bh % p.kv_heads;
             const int all = (p.queries + kInner - 1) / kInner;
             c0 = p.causal ? (tile * kOuter) / kInner : 0;
             if (c0 > all) c0 = all;
             nc = all - c0;
             count = nc * group;
         } else {
-            const int per = p.batch * p.heads;
-            tile = p.outer_tiles - 1 - item / per;
-            b = (item % per) / p.heads;
-            head_outer = item % p.heads;
+            tile = heavy_or_light ? i : p.outer_tiles - 1 - i;
+            b = bh / p.heads;
+            head_outer = bh % p.heads;
             const int all = (p.keys + kInner - 1) / kInner;
             c0 = 0;
             nc = all;
@@ -127,31 +146,37 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *s_outer_a = smem;
-    uint8_t *s_outer_b = s_outer_a + kOuterBytes;
-    uint8_t *s_inner = s_outer_b + kOuterBytes;              // kStages x (A 16 KB | B 16 KB)
-    uint8_t *s_ds = s_inner + kStages * 2 * kInnerBytes;     // 2 x (P 16 KB | dS 16 KB); also stages the stores
+    uint8_t *s_outer_b = s_outer_a + kTileBytes;
+    constexpr int SA = Rings<DKDV>::A, SB = Rings<DKDV>::B;
+    uint8_t *s_ring_a = s_outer_b + kTileBytes;          // SA x 32 KB
+    uint8_t *s_ring_b = s_ring_a + SA * kTileBytes;      // SB x 32 KB
+    uint8_t *s_out = s_ring_b + SB * kTileBytes;         // 2 x 16 KB: one slab per group, stages the stores
 
     __shared__ __align__(8) uint64_t outer_full, outer_empty, acc_done, acc_free;
-    __shared__ __align__(8) uint64_t inner_full[kStages], inner_empty[kStages];
-    __shared__ __align__(8) uint64_t t_full[2], ds_full[2];
-    __shared__ __align__(8) uint64_t stats_ready[2];   // a group's four warps have written the step's statistics
+    __shared__ __align__(8) uint64_t a_full[SA], a_empty[SA], b_full[SB], b_empty[SB];
+    __shared__ __align__(8) uint64_t s_full;            // the step's scores are in tensor memory
+    __shared__ __align__(8) uint64_t dp_full[2];        // its dP is (by step parity: dQ computes dP a step ahead)
+    __shared__ __align__(8) uint64_t s_read;            // every row warp holds its scores in registers
+    // every row warp has written P and dS; by step parity, because the dQ kernel's row warps may finish step
+    // t + 1 (its scores and dP are issued ahead) before the issuing thread has looked at step t
+    __shared__ __align__(8) uint64_t pds_full[2];
+    __shared__ __align__(8) uint64_t stats_ready;       // every row warp has written the step's statistics
     __shared__ uint32_t tmem_base_smem;
     __shared__ int failed_smem;
-    // dK/dV: the step's 64 queries' lse*log2(e) [0, 64) and delta [64, 128), per group, double-buffered
-    __shared__ __align__(16) float col_stats[2][2][2 * kInner];
+    // dK/dV: the step's 128 queries' lse*log2(e) [0, 128) and delta [128, 256), double-buffered
+    __shared__ __align__(16) float col_stats[2][2 * kInner];
     volatile int *failed = &failed_smem;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         failed_smem = 0;
-        mbar_init(&outer_full, 1); mbar_init(&outer_empty, 1); mbar_init(&acc_done, 1); mbar_init(&acc_free, 8);
-        for (int s = 0; s < kStages; s++) { mbar_init(&inner_full[s], 1); mbar_init(&inner_empty[s], 1); }
-        for (int s = 0; s < 2; s++) {
-            mbar_init(&t_full[s], 1);
-            mbar_init(&ds_full[s], 4);
-            mbar_init(&stats_ready[s], 4);
-        }
+        mbar_init(&outer_full, 1); mbar_init(&outer_empty, 1); mbar_init(&acc_done, 1); mbar_init(&acc_free, kRowWarps);
+        for (int s = 0; s < SA; s++) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < SB; s++) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+        mbar_init(&s_full, 1); mbar_init(&dp_full[0], 1); mbar_init(&dp_full[1], 1);
+        mbar_init(&s_read, kRowWarps); mbar_init(&pds_full[0], kRowWarps); mbar_init(&pds_full[1], kRowWarps);
+        mbar_init(&stats_ready, kRowWarps);
         fence_barrier_init();
         prefetch_tensormap(&p.outer_a); prefetch_tensormap(&p.outer_b);
         prefetch_tensormap(&p.inner_a); prefetch_tensormap(&p.inner_b);
@@ -165,43 +190,89 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_smem;
+    const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 128;
     const uint32_t tmem_acc1 = tmem_base + 256, tmem_acc2 = tmem_base + 384;
 
     if (warp == 0) {
         if (elect_one()) {
-            uint32_t outer_phase = 0, step_count = 0;
-            for (int item = blockIdx.x; item < p.items && !*failed; item += gridDim.x) {
-                const Steps<DKDV> steps(p, item);
+            uint32_t outer_phase = 0, c = 0;
+            for (int j = 0; !*failed; j++) {
+                const Steps<DKDV> steps(p, j);
+                if (steps.done) break;
+                if (steps.skip) continue;
                 if (!bwd_wait(&outer_empty, outer_phase ^ 1, failed, 1)) break;
                 outer_phase ^= 1;
-                mbar_arrive_expect_tx(&outer_full, 2 * kOuterBytes);
+                mbar_arrive_expect_tx(&outer_full, 2 * kTileBytes);
                 const int r0 = steps.tile * kOuter;
                 tma_load_4d(s_outer_a, &p.outer_a, &outer_full, 0, steps.head_outer, r0, steps.b);
-                tma_load_4d(s_outer_a + kOuterSlab, &p.outer_a, &outer_full, 64, steps.head_outer, r0, steps.b);
+                tma_load_4d(s_outer_a + kSlab, &p.outer_a, &outer_full, 64, steps.head_outer, r0, steps.b);
                 tma_load_4d(s_outer_b, &p.outer_b, &outer_full, 0, steps.head_outer, r0, steps.b);
-                tma_load_4d(s_outer_b + kOuterSlab, &p.outer_b, &outer_full, 64, steps.head_outer, r0, steps.b);
-                for (int t = 0; t < steps.count; t++, step_count++) {
-                    const int st = step_count % kStages;
-                    const uint32_t ph = (step_count / kStages) & 1;
-                    if (!bwd_wait(&inner_empty[st], ph ^ 1, failed, 2)) break;
+                tma_load_4d(s_outer_b + kSlab, &p.outer_b, &outer_full, 64, steps.head_outer, r0, steps.b);
+                bool ok = true;
+                for (int t = 0; t < steps.count; t++, c++) {
+                    const int sta = c % SA, stb = c % SB;
                     int hi, pos0;
                     steps.at(t, hi, pos0);
-                    uint8_t *sa = s_inner + st * 2 * kInnerBytes, *sb = sa + kInnerBytes;
-                    mbar_arrive_expect_tx(&inner_full[st], 2 * kInnerBytes);
-                    tma_load_4d(sa, &p.inner_a, &inner_full[st], 0, hi, pos0, steps.b);
-                    tma_load_4d(sa + kInnerSlab, &p.inner_a, &inner_full[st], 64, hi, pos0, steps.b);
-                    tma_load_4d(sb, &p.inner_b, &inner_full[st], 0, hi, pos0, steps.b);
-                    tma_load_4d(sb + kInnerSlab, &p.inner_b, &inner_full[st], 64, hi, pos0, steps.b);
+                    if (!bwd_wait(&a_empty[sta], ((c / SA) & 1) ^ 1, failed, 2)) { ok = false; break; }
+                    uint8_t *sa = s_ring_a + sta * kTileBytes;
+                    mbar_arrive_expect_tx(&a_full[sta], kTileBytes);
+                    tma_load_4d(sa, &p.inner_a, &a_full[sta], 0, hi, pos0, steps.b);
+                    tma_load_4d(sa + kSlab, &p.inner_a, &a_full[sta], 64, hi, pos0, steps.b);
+                    if (!bwd_wait(&b_empty[stb], ((c / SB) & 1) ^ 1, failed, 13)) { ok = false; break; }
+                    uint8_t *sb = s_ring_b + stb * kTileBytes;
+                    mbar_arrive_expect_tx(&b_full[stb], kTileBytes);
+                    tma_load_4d(sb, &p.inner_b, &b_full[stb], 0, hi, pos0, steps.b);
+                    tma_load_4d(sb + kSlab, &p.inner_b, &b_full[stb], 64, hi, pos0, steps.b);
                 }
+                if (!ok) break;
             }
         }
     } else if (warp == 1) {
         if (elect_one()) {
-            const uint32_t idesc_t = umma_idesc_bf16(kOuter, kInner, false, false);   // 128 x 64, both K-major
-            const uint32_t idesc_g = umma_idesc_bf16(kOuter, kD, false, true);        // 128 x 128, B MN-major
-            uint32_t outer_phase = 0, step_count = 0, grad_count = 0, item_count = 0;
-            for (int item = blockIdx.x; item < p.items && !*failed; item += gridDim.x) {
-                const Steps<DKDV> steps(p, item);
+            const uint32_t idesc_t = umma_idesc_bf16(kOuter, kInner, false, false);   // scores: both K-major
+            const uint32_t idesc_g = umma_idesc_bf16(kOuter, kD, false, true);        // gradients: B MN-major
+            const uint32_t oa = smem_u32(s_outer_a), ob = smem_u32(s_outer_b);
+            uint32_t outer_phase = 0, c0 = 0, item_count = 0;
+            bool ok = true;
+            // scores of step c (a count over all of this CTA's steps) into the score columns
+            auto issue_scores = [&](uint32_t c) -> bool {
+                // the row warps must hold the scores of the step before in registers
+                if (c > 0 && !bwd_wait(&s_read, (c - 1) & 1, failed, 5)) return false;
+                const int st = c % SA;
+                if (!bwd_wait(&a_full[st], (c / SA) & 1, failed, 4)) return false;
+                tcgen05_fence_after();
+                const uint32_t ia = smem_u32(s_ring_a + st * kTileBytes);
+#pragma unroll
+                for (int k = 0; k < kD / 16; k++) {
+                    const uint32_t off = (k >> 2) * kSlab + (k & 3) * 32;
+                    tcgen05_mma_f16(tmem_s, umma_smem_desc(oa + off, 16, 1024), umma_smem_desc(ia + off, 16, 1024),
+                                    idesc_t, k != 0);
+                }
+                tcgen05_commit(&s_full);
+                return true;
+            };
+            // dP of step c.  dK/dV: one buffer; dP runs after the gradient products issued before it, which read
+            // P / dS of the step before from the same columns.  dQ has room for two buffers (it keeps one
+            // accumulator), so dP of step c is issued with the scores, before the gradient product of step c - 1.
+            auto issue_dp = [&](uint32_t c) -> bool {
+                const int st = c % SB;
+                if (!bwd_wait(&b_full[st], (c / SB) & 1, failed, 14)) return false;
+                tcgen05_fence_after();
+                const uint32_t ib = smem_u32(s_ring_b + st * kTileBytes);
+#pragma unroll
+                for (int k = 0; k < kD / 16; k++) {
+                    const uint32_t off = (k >> 2) * kSlab + (k & 3) * 32;
+                    tcgen05_mma_f16(tmem_dp + (DKDV ? 0 : (c & 1) * 128), umma_smem_desc(ob + off, 16, 1024),
+                                    umma_smem_desc(ib + off, 16, 1024), idesc_t, k != 0);
+                }
+                tcgen05_commit(&dp_full[c & 1]);
+                if (!DKDV) tcgen05_commit(&b_empty[st]);   // dQ: nothing else reads the step's V tile
+                return true;
+            };
+            for (int j = 0; !*failed && ok; j++) {
+                const Steps<DKDV> steps(p, j);
+                if (steps.done) break;
+                if (steps.skip) continue;
                 if (!bwd_wait(&outer_full, outer_phase, failed, 3)) break;
                 outer_phase ^= 1;
                 tcgen05_fence_after();
@@ -209,80 +280,77 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                     mbar_arrive(&outer_empty);
                     continue;
                 }
-                bool ok = true;
-                for (int t = 0; t <= steps.count && ok; t++) {
-                    if (t < steps.count) {
-                        const uint32_t c = step_count + t;
-                        const int st = c % kStages;
-                        const uint32_t ph = (c / kStages) & 1;
-                        const int tb = c & 1;
-                        const uint32_t tph = (c >> 1) & 1;
-                        // buffer tb was last read by the gradient products of two steps ago, issued before this
-                        // point: MMAs of one CTA run in issue order, so no barrier is needed to reuse it
-                        if (!bwd_wait(&inner_full[st], ph, failed, 4)) { ok = false; break; }
-                        tcgen05_fence_after();
-                        const uint32_t oa = smem_u32(s_outer_a), ob = smem_u32(s_outer_b);
-                        const uint32_t ia = smem_u32(s_inner + st * 2 * kInnerBytes), ib = ia + kInnerBytes;
-                        const uint32_t t1 = tmem_base + tb * 128, t2 = t1 + 64;
-#pragma unroll
-                        for (int k = 0; k < kD / 16; k++) {
-                            const uint32_t ooff = (k >> 2) * kOuterSlab + (k & 3) * 32;
-                            const uint32_t ioff = (k >> 2) * kInnerSlab + (k & 3) * 32;
-                            tcgen05_mma_f16(t1, umma_smem_desc(oa + ooff, 16, 1024), umma_smem_desc(ia + ioff, 16, 1024),
-                                            idesc_t, k != 0);
+                if (!issue_scores(c0) || !issue_dp(c0)) break;
+                if (steps.count == 1) tcgen05_commit(&outer_empty);
+                for (int t = 0; t < steps.count; t++) {
+                    const uint32_t c = c0 + t;
+                    const int sta = c % SA, stb = c % SB;
+                    if (t + 1 < steps.count) {
+                        if (!issue_scores(c + 1)) { ok = false; break; }
+                        if (!DKDV) {
+                            if (!issue_dp(c + 1)) { ok = false; break; }
+                            if (t + 2 == steps.count) tcgen05_commit(&outer_empty);
                         }
-#pragma unroll
-                        for (int k = 0; k < kD / 16; k++) {
-                            const uint32_t ooff = (k >> 2) * kOuterSlab + (k & 3) * 32;
-                            const uint32_t ioff = (k >> 2) * kInnerSlab + (k & 3) * 32;
-                            tcgen05_mma_f16(t2, umma_smem_desc(ob + ooff, 16, 1024), umma_smem_desc(ib + ioff, 16, 1024),
-                                            idesc_t, k != 0);
-                        }
-                        tcgen05_commit(&t_full[tb]);
-                        if (t == steps.count - 1) tcgen05_commit(&outer_empty);
                     }
-                    if (t > 0) {
-                        const uint32_t c = grad_count;
-                        const int st = c % kStages;
-                        const int db = c & 1;
-                        const uint32_t dph = (c >> 1) & 1;
-                        // the first gradient product of an item overwrites the accumulators
-                        if (t == 1 && !bwd_wait(&acc_free, (item_count & 1) ^ 1, failed, 6)) { ok = false; break; }
-                        if (!bwd_wait(&ds_full[db], dph, failed, 7)) { ok = false; break; }
-                        tcgen05_fence_after();
-                        const uint32_t ia = smem_u32(s_inner + st * 2 * kInnerBytes), ib = ia + kInnerBytes;
-                        // A: P / dS from tensor memory, 16 positions = 8 packed columns per MMA, written by the row
-                        // threads over the scores / dP they were computed from; B: 16 position lines of 128 bytes
-                        const uint32_t pa = tmem_base + db * 128, da = pa + 64;
+                    // the first gradient product of an item overwrites the accumulators
+                    if (t == 0 && !bwd_wait(&acc_free, (item_count & 1) ^ 1, failed, 6)) { ok = false; break; }
+                    if (!bwd_wait(&pds_full[c & 1], (c >> 1) & 1, failed, 7)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t ia = smem_u32(s_ring_a + sta * kTileBytes);
+                    const uint32_t ib = smem_u32(s_ring_b + stb * kTileBytes);
+                    // A: P / dS from tensor memory, 16 positions = 8 packed columns per MMA, where the row threads of
+                    // each column half left them (P in the first 32 of the half's 64 dP columns, dS in the last 32);
+                    // B: 16 position lines of 128 bytes per 64-feature slab
+#pragma unroll
+                    for (int k = 0; k < kInner / 16; k++) {
+                        const uint32_t ds_at = tmem_dp + (DKDV ? 0 : (c & 1) * 128) + (k >> 2) * 64 + 32 + (k & 3) * 8;
+                        tcgen05_mma_f16_ts(tmem_acc2, ds_at, umma_smem_desc(ia + k * 2048, kSlab, 1024), idesc_g, t | k);
+                    }
+                    tcgen05_commit(&a_empty[sta]);
+                    if (DKDV) {
 #pragma unroll
                         for (int k = 0; k < kInner / 16; k++) {
-                            if (DKDV)
-                                tcgen05_mma_f16_ts(tmem_acc1, pa + k * 8, umma_smem_desc(ib + k * 2048, kInnerSlab, 1024), idesc_g,
-                                                   (t - 1) | k);
-                            tcgen05_mma_f16_ts(tmem_acc2, da + k * 8, umma_smem_desc(ia + k * 2048, kInnerSlab, 1024), idesc_g,
-                                               (t - 1) | k);
+                            const uint32_t p_at = tmem_dp + (k >> 2) * 64 + (k & 3) * 8;
+                            tcgen05_mma_f16_ts(tmem_acc1, p_at, umma_smem_desc(ib + k * 2048, kSlab, 1024), idesc_g, t | k);
                         }
-                        tcgen05_commit(&inner_empty[st]);
-                        if (t == steps.count) tcgen05_commit(&acc_done);
-                        grad_count++;
+                        tcgen05_commit(&b_empty[stb]);
                     }
+                    if (DKDV && t + 1 < steps.count) {
+                        if (!issue_dp(c + 1)) { ok = false; break; }
+                        if (t + 2 == steps.count) tcgen05_commit(&outer_empty);
+                    }
+                    if (t + 1 == steps.count) tcgen05_commit(&acc_done);
                 }
-                step_count += steps.count;
+                c0 += steps.count;
                 item_count++;   // items that ran gradient products
-                if (!ok) break;
             }
         }
     } else {
-        // ---- one thread per row of the item; the two groups of four warps take alternate steps (the
-        // score and P / dS buffers of a step are those of its parity), so one group's chain of
-        // tensor-memory load -> exponentials -> shared-memory stores overlaps the other's
+        // ---- one thread per (row of the item, half of the step's columns)
         const int q4 = warp & 3;
         const int group = (warp - 2) >> 2;
         const int row = q4 * 32 + lane;
+        const int tid_r = (warp - 2) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
-        uint32_t step_count = 0, item_count = 0, own_steps = 0;
-        for (int item = blockIdx.x; item < p.items; item += gridDim.x) {
-            const Steps<DKDV> steps(p, item);
+        const uint32_t t_s = tmem_s + lane_base + group * 64;     // this thread's 64 scores
+        const uint32_t t_dp0 = tmem_dp + lane_base + group * 64;  // its 64 dP values; P and dS go over them
+        uint32_t c = 0, item_count = 0;
+        // dK/dV: this thread's share of a step's statistics (lse*log2(e) of query tid_r, or delta of query
+        // tid_r - 128), fetched one step ahead so that its latency never sits in the step that needs it
+        auto fetch_stat = [&](const Steps<DKDV> &of, int t) -> float {
+            int hi, pos0;
+            of.at(t, hi, pos0);
+            const int qpos = pos0 + (tid_r & (kInner - 1));
+            const long long base = (static_cast<long long>(of.b) * p.heads + hi) * p.queries;
+            const float *src = tid_r < kInner ? p.lse2 : p.delta;
+            return qpos < p.queries ? __ldg(src + base + qpos) : 0.0f;
+        };
+        float stat_next = 0.0f;
+        bool have_next = false;
+        for (int j = 0;; j++) {
+            const Steps<DKDV> steps(p, j);
+            if (steps.done) break;
+            if (steps.skip) continue;
             const int outer_pos = steps.tile * kOuter + row;   // this thread's key (dK/dV) or query (dQ)
             float row_lse2 = 0.0f, row_delta = 0.0f;
             if (!DKDV && outer_pos < p.queries) {
@@ -291,41 +359,43 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 row_delta = p.delta[i];
             }
             bool ok = true;
-            const uint32_t step_base = step_count;
-            step_count += steps.count;
-            for (int t = 0; t < steps.count; t++) {
-                const uint32_t sc = step_base + t;
-                const int tb = sc & 1;
-                if (tb != group) continue;
-                const uint32_t tph = (sc >> 1) & 1;
+            for (int t = 0; t < steps.count; t++, c++) {
+                const uint32_t ph = c & 1;
                 int hi, pos0;
                 steps.at(t, hi, pos0);
-                float *stats = col_stats[group][tph];
+                const int col0 = pos0 + group * 64;   // first position of this thread's columns
+                float *stats = col_stats[ph];
                 if (DKDV) {
-                    // fetched before the wait below so that the global-memory latency hides behind it
-                    const int i = row & (kInner - 1);
-                    const int qpos = pos0 + i;
-                    const long long base = (static_cast<long long>(steps.b) * p.heads + hi) * p.queries;
-                    const float *src = row < kInner ? p.lse2 : p.delta;
-                    stats[row] = qpos < p.queries ? __ldg(src + base + qpos) : 0.0f;
+                    stats[tid_r] = have_next ? stat_next : fetch_stat(steps, t);
+                    have_next = false;
+                    if (t + 1 < steps.count) {
+                        stat_next = fetch_stat(steps, t + 1);
+                        have_next = true;
+                    } else {
+                        const Steps<DKDV> after(p, j + 1);
+                        if (!after.done && !after.skip && after.count > 0) {
+                            stat_next = fetch_stat(after, 0);
+                            have_next = true;
+                        }
+                    }
                 }
-                if (!bwd_wait(&t_full[tb], tph, failed, 8)) { ok = false; break; }
+                if (!bwd_wait(&s_full, ph, failed, 8)) { ok = false; break; }
                 tcgen05_fence_after();
                 if (DKDV) {
-                    // the group's four warps meet (a bounded wait, unlike a named barrier: a warp that gave up on a
+                    // the row warps meet (a bounded wait, unlike a named barrier: a warp that gave up on a
                     // failed wait elsewhere must not leave the others hanging here)
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&stats_ready[group]);
-                    if (!bwd_wait(&stats_ready[group], own_steps & 1, failed, 12)) { ok = false; break; }
-                    own_steps++;
+                    if (lane == 0) mbar_arrive(&stats_ready);
+                    if (!bwd_wait(&stats_ready, ph, failed, 12)) { ok = false; break; }
                 }
-                uint32_t s[kInner], dp[kInner];
-                const uint32_t t1 = tmem_base + lane_base + tb * 128;
-                tmem_ld_32x32(t1, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-                tmem_ld_32x32(t1 + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-                tmem_ld_32x32(t1 + 64, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
-                tmem_ld_32x32(t1 + 96, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+                uint32_t s[64];
+                tmem_ld_32x32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+                tmem_ld_32x32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
                 tmem_ld_wait();
+                // the scores are in registers: the next step's may be computed
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_read);
                 const bool edge = DKDV ? (pos0 + kInner > p.queries || outer_pos >= p.keys ||
                                           (p.causal && pos0 < steps.tile * kOuter + kOuter))
                                        : (pos0 + kInner > p.keys || outer_pos >= p.queries ||
@@ -333,100 +403,104 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 if (edge) {
                     // masked positions get a score of -Inf: their weight and their dS are then exactly zero
 #pragma unroll
-                    for (int i = 0; i < kInner; i++) {
-                        const int inner_pos = pos0 + i;
+                    for (int i = 0; i < 64; i++) {
+                        const int inner_pos = col0 + i;
                         const int key = DKDV ? outer_pos : inner_pos;
                         const int query = DKDV ? inner_pos : outer_pos;
                         if (key >= p.keys || query >= p.queries || (p.causal && key > query)) s[i] = 0xff800000u;
                     }
                 }
+                // P, kept in Float32 for dS
 #pragma unroll
-                for (int g = 0; g < kInner / 8; g++) {
-                    float pv[8], dv[8];
-                    float l8[8], d8[8];
-                    if (DKDV) {
-                        const float4 a0 = *reinterpret_cast<const float4 *>(stats + 8 * g);
-                        const float4 a1 = *reinterpret_cast<const float4 *>(stats + 8 * g + 4);
-                        const float4 b0 = *reinterpret_cast<const float4 *>(stats + kInner + 8 * g);
-                        const float4 b1 = *reinterpret_cast<const float4 *>(stats + kInner + 8 * g + 4);
-                        l8[0] = a0.x; l8[1] = a0.y; l8[2] = a0.z; l8[3] = a0.w;
-                        l8[4] = a1.x; l8[5] = a1.y; l8[6] = a1.z; l8[7] = a1.w;
-                        d8[0] = b0.x; d8[1] = b0.y; d8[2] = b0.z; d8[3] = b0.w;
-                        d8[4] = b1.x; d8[5] = b1.y; d8[6] = b1.z; d8[7] = b1.w;
-                    }
-#pragma unroll
-                    for (int u = 0; u < 8; u++) {
-                        const int i = 8 * g + u;
-                        const float lse2 = DKDV ? l8[u] : row_lse2;
-                        const float dl = DKDV ? d8[u] : row_delta;
-                        const float pw = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
-                        pv[u] = pw;
-                        dv[u] = pw * (__uint_as_float(dp[i]) - dl);
-                    }
-                    // packed two per column over the values they came from: s becomes P, dp becomes dS
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        if (DKDV) s[4 * g + u] = pack_bf16x2(pv[2 * u], pv[2 * u + 1]);
-                        dp[4 * g + u] = pack_bf16x2(dv[2 * u], dv[2 * u + 1]);
-                    }
+                for (int g = 0; g < 16; g++) {
+                    float4 l4 = make_float4(row_lse2, row_lse2, row_lse2, row_lse2);
+                    if (DKDV) l4 = *reinterpret_cast<const float4 *>(stats + group * 64 + 4 * g);
+                    s[4 * g] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(s[4 * g]), p.scale_log2, -l4.x)));
+                    s[4 * g + 1] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(s[4 * g + 1]), p.scale_log2, -l4.y)));
+                    s[4 * g + 2] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(s[4 * g + 2]), p.scale_log2, -l4.z)));
+                    s[4 * g + 3] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(s[4 * g + 3]), p.scale_log2, -l4.w)));
                 }
-                if (DKDV) tmem_st_32x32(t1, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-                tmem_st_32x32(t1 + 64, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+                if (!bwd_wait(&dp_full[ph], (c >> 1) & 1, failed, 9)) { ok = false; break; }
+                const uint32_t t_dp = t_dp0 + (DKDV ? 0 : ph * 128);
+                tcgen05_fence_after();
+                uint32_t dp[64];
+                tmem_ld_32x32(t_dp, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+                tmem_ld_32x32(t_dp + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+                tmem_ld_wait();
+                // packed two per column: dp[0, 32) becomes P, dp[32, 64) becomes dS
+                uint32_t pk[32], dk[32];
+#pragma unroll
+                for (int g = 0; g < 16; g++) {
+                    float4 d4 = make_float4(row_delta, row_delta, row_delta, row_delta);
+                    if (DKDV) d4 = *reinterpret_cast<const float4 *>(stats + kInner + group * 64 + 4 * g);
+                    const float p0 = __uint_as_float(s[4 * g]), p1 = __uint_as_float(s[4 * g + 1]);
+                    const float p2 = __uint_as_float(s[4 * g + 2]), p3 = __uint_as_float(s[4 * g + 3]);
+                    const float e0 = p0 * (__uint_as_float(dp[4 * g]) - d4.x);
+                    const float e1 = p1 * (__uint_as_float(dp[4 * g + 1]) - d4.y);
+                    const float e2 = p2 * (__uint_as_float(dp[4 * g + 2]) - d4.z);
+                    const float e3 = p3 * (__uint_as_float(dp[4 * g + 3]) - d4.w);
+                    if (DKDV) {
+                        pk[2 * g] = pack_bf16x2(p0, p1);
+                        pk[2 * g + 1] = pack_bf16x2(p2, p3);
+                    }
+                    dk[2 * g] = pack_bf16x2(e0, e1);
+                    dk[2 * g + 1] = pack_bf16x2(e2, e3);
+                }
+                if (DKDV) tmem_st_32x32(t_dp, pk);
+                tmem_st_32x32(t_dp + 32, dk);
                 tmem_st_wait();
                 tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ds_full[tb]);
+                if (lane == 0) mbar_arrive(&pds_full[ph]);
             }
             if (!ok) break;
-            // ---- the item's gradients: accumulators -> BFloat16 -> shared staging -> TMA stores
+            // ---- the item's gradients: accumulators -> BFloat16 -> shared staging -> TMA stores.
+            // dK/dV: group 0 writes dV, group 1 dK, one 64-feature slab at a time; dQ: each group one slab.
             if (steps.count > 0) {
                 if (!bwd_wait(&acc_done, item_count & 1, failed, 10)) break;
             }
             tcgen05_fence_after();
-            // group 0 writes the first accumulator (dV), group 1 the second (dK, or dQ)
+            const int rounds = DKDV ? 2 : 1;
+            const uint32_t acc = (DKDV && group == 0) ? tmem_acc1 : tmem_acc2;
+            const float mul = (DKDV && group == 0) ? 1.0f : p.scale;
+            uint8_t *stage = s_out + group * kSlab;   // [128 rows][64 features], this warp's 32 rows of it
 #pragma unroll 1
-            for (int which = group; which <= group && (DKDV || which == 1); which++) {
-                const float mul = which == 0 ? 1.0f : p.scale;
-                uint8_t *stage = s_ds + which * 2 * kDsBytes;   // 32 KB: two 64-feature slabs of 128 rows
-                uint32_t r[kD];
+            for (int round = 0; round < rounds; round++) {
+                const int f0 = DKDV ? round * 64 : group * 64;
+                uint32_t r[64];
                 if (steps.count > 0) {
-#pragma unroll
-                    for (int c = 0; c < kD / 32; c++)
-                        tmem_ld_32x32((which == 0 ? tmem_acc1 : tmem_acc2) + lane_base + c * 32,
-                                      *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+                    tmem_ld_32x32(acc + lane_base + f0, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                    tmem_ld_32x32(acc + lane_base + f0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
                     tmem_ld_wait();
+                    if (round == rounds - 1) {   // this warp has read all it needs of the accumulators
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_free);
+                    }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < kD; i++) r[i] = 0u;   // no step touched this item: its gradient is zero
+                    for (int i = 0; i < 64; i++) r[i] = 0u;   // no step touched this item: its gradient is zero
                 }
 #pragma unroll
-                for (int g = 0; g < kD / 8; g++) {
+                for (int g = 0; g < 8; g++) {
                     uint4 v4;
                     v4.x = pack_bf16x2(__uint_as_float(r[8 * g]) * mul, __uint_as_float(r[8 * g + 1]) * mul);
                     v4.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * mul, __uint_as_float(r[8 * g + 3]) * mul);
                     v4.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * mul, __uint_as_float(r[8 * g + 5]) * mul);
                     v4.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * mul, __uint_as_float(r[8 * g + 7]) * mul);
-                    *reinterpret_cast<uint4 *>(stage + (g >> 3) * kOuterSlab + row * 128 + (((g & 7) ^ (row & 7)) << 4)) = v4;
+                    *reinterpret_cast<uint4 *>(stage + row * 128 + ((g ^ (row & 7)) << 4)) = v4;
                 }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    const int r0 = steps.tile * kOuter + q4 * 32;
+                    tma_store_4d((DKDV && group == 0) ? &p.out1 : &p.out2, stage + q4 * 32 * 128, f0, steps.head_outer, r0,
+                                 steps.b);
+                    bulk_commit_group();
+                    bulk_wait_group_read<0>();   // the staging rows may be rewritten
+                }
+                __syncwarp();
             }
-            tcgen05_fence_before();
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
-                const int r0 = steps.tile * kOuter + q4 * 32;
-                if (DKDV && group == 0) {
-                    tma_store_4d(&p.out1, s_ds + q4 * 32 * 128, 0, steps.head_outer, r0, steps.b);
-                    tma_store_4d(&p.out1, s_ds + kOuterSlab + q4 * 32 * 128, 64, steps.head_outer, r0, steps.b);
-                }
-                if (group == 1) {
-                    tma_store_4d(&p.out2, s_ds + 2 * kDsBytes + q4 * 32 * 128, 0, steps.head_outer, r0, steps.b);
-                    tma_store_4d(&p.out2, s_ds + 2 * kDsBytes + kOuterSlab + q4 * 32 * 128, 64, steps.head_outer, r0, steps.b);
-                }
-                bulk_commit_group();
-                bulk_wait_group_read<0>();
-                if (steps.count > 0) mbar_arrive(&acc_free);
-            }
-            __syncwarp();
             if (steps.count > 0) item_count++;
         }
         if (lane == 0) bulk_wait_group<0>();
@@ -509,7 +583,7 @@ template <bool DKDV>
 int launch_bwd(AttnBwdArgs &p, const DeviceInfo &dev, cudaStream_t stream) {
     // the tiles (224 KB, 1024-byte aligned) sit behind the kernel's static shared memory: take all the dynamic
     // shared memory the SM has left
-    const size_t tiles = 2 * kOuterBytes + kStages * 2 * kInnerBytes + 2 * 2 * kDsBytes;
+    const size_t tiles = 2 * kTileBytes + (Rings<DKDV>::A + Rings<DKDV>::B) * kTileBytes + 2 * kSlab;
     static std::mutex lock;
     static size_t dynamic_bytes[64] = {};
     {
@@ -526,7 +600,7 @@ int launch_bwd(AttnBwdArgs &p, const DeviceInfo &dev, cudaStream_t stream) {
         }
     }
     const size_t smem = dynamic_bytes[dev.device];
-    const unsigned grid = static_cast<unsigned>(p.items < dev.sms ? p.items : dev.sms);
+    const unsigned grid = static_cast<unsigned>(p.supers < dev.sms ? p.supers : dev.sms);
     attention_bwd_kernel<DKDV><<<grid, kBwdThreads, smem, stream>>>(p);
     TB200_CUDA(cudaGetLastError());
     return TB200_OK;
@@ -585,21 +659,21 @@ extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, cons
     // dK, dV: items over key tiles
     if ((st = bwd_tmap(&p.outer_a, k, kD, d->kv_heads, d->keys, d->batch, kOuter))) return st;
     if ((st = bwd_tmap(&p.outer_b, v, kD, d->kv_heads, d->keys, d->batch, kOuter))) return st;
-    if ((st = bwd_tmap(&p.inner_a, q, kD, d->heads, d->queries, d->batch, kInner))) return st;
-    if ((st = bwd_tmap(&p.inner_b, dout, kD, d->heads, d->queries, d->batch, kInner))) return st;
+    if ((st = bwd_tmap(&p.inner_a, q, kD, d->heads, d->queries, d->batch, kOuter))) return st;
+    if ((st = bwd_tmap(&p.inner_b, dout, kD, d->heads, d->queries, d->batch, kOuter))) return st;
     if ((st = bwd_tmap(&p.out1, dv, kD, d->kv_heads, d->keys, d->batch, 32))) return st;
     if ((st = bwd_tmap(&p.out2, dk, kD, d->kv_heads, d->keys, d->batch, 32))) return st;
     p.outer_tiles = static_cast<int>(ceil_div(d->keys, kOuter));
-    p.items = p.outer_tiles * d->batch * d->kv_heads;
+    p.supers = (p.outer_tiles + 1) / 2 * d->batch * d->kv_heads;
     if ((st = launch_bwd<true>(p, dev, stream))) return st;
     // dQ: items over query tiles
     if ((st = bwd_tmap(&p.outer_a, q, kD, d->heads, d->queries, d->batch, kOuter))) return st;
     if ((st = bwd_tmap(&p.outer_b, dout, kD, d->heads, d->queries, d->batch, kOuter))) return st;
-    if ((st = bwd_tmap(&p.inner_a, k, kD, d->kv_heads, d->keys, d->batch, kInner))) return st;
-    if ((st = bwd_tmap(&p.inner_b, v, kD, d->kv_heads, d->keys, d->batch, kInner))) return st;
+    if ((st = bwd_tmap(&p.inner_a, k, kD, d->kv_heads, d->keys, d->batch, kOuter))) return st;
+    if ((st = bwd_tmap(&p.inner_b, v, kD, d->kv_heads, d->keys, d->batch, kOuter))) return st;
     if ((st = bwd_tmap(&p.out2, dq, kD, d->heads, d->queries, d->batch, 32))) return st;
     p.outer_tiles = static_cast<int>(ceil_div(d->queries, kOuter));
-    p.items = p.outer_tiles * d->batch * d->heads;
+    p.supers = (p.outer_tiles + 1) / 2 * d->batch * d->heads;
     return launch_bwd<false>(p, dev, stream);
 }
 

@@ -423,15 +423,33 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_smem;
     const int group = p.heads / p.kv_heads;
+    // The walk over the work: a CTA takes whole "supers" = the i-th heaviest and the i-th lightest pair of query
+    // tiles of one (batch, head), one after the other.  Under the causal mask every super then costs the same, so
+    // the static round-robin over CTAs is balanced, and because supers are numbered (batch, head)-major the CTAs
+    // that run at the same time read the K and V of a few heads only: the tiles stay in L2 instead of
+    // being streamed from HBM once per query tile.
     const int pair_tiles = (p.q_tiles + 1) / 2;
-    const int per = p.batch * p.heads;
-    const int items = pair_tiles * per;
+    const int half_tiles = (pair_tiles + 1) / 2;
+    const int supers = half_tiles * p.batch * p.heads;
+    // walk step j of this CTA -> (batch*head, pair tile); false when the CTA is done, pt < 0 for the second half of
+    // a super whose two halves are the same tile
+    auto walk = [&](int j, int &bh, int &pt) -> bool {
+        const int sup = blockIdx.x + (j >> 1) * gridDim.x;
+        if (sup >= supers) return false;
+        bh = sup / half_tiles;
+        const int i = sup % half_tiles;
+        pt = (j & 1) ? i : pair_tiles - 1 - i;
+        if ((j & 1) && i == pair_tiles - 1 - i) pt = -1;
+        return true;
+    };
 
     if (warp == 0) {
         if (elect_one()) {
             uint32_t kv_count = 0, q_loads[2] = {0, 0};
-            for (int item = blockIdx.x; item < items && !*failed; item += gridDim.x) {
-                const int pt = pair_tiles - 1 - item / per, bh = item % per;
+            for (int j = 0; !*failed; j++) {
+                int bh, pt;
+                if (!walk(j, bh, pt)) break;
+                if (pt < 0) continue;
                 const int b = bh / p.heads, h = bh % p.heads, hk = h / group;
                 bool ok = true;
                 for (int g = 0; g < 2 && ok; g++) {
@@ -478,8 +496,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
                 }
                 tcgen05_commit(&s_full[g]);
             };
-            for (int item = blockIdx.x; item < items && !*failed; item += gridDim.x) {
-                const int pt = pair_tiles - 1 - item / per;
+            for (int j = 0; !*failed; j++) {
+                int bh, pt;
+                if (!walk(j, bh, pt)) break;
+                if (pt < 0) continue;
                 const int n[2] = {pair_kv_tiles(p, 2 * pt), pair_kv_tiles(p, 2 * pt + 1)};
                 const int nkv = n[0] > n[1] ? n[0] : n[1];
                 bool ok = true;
@@ -551,8 +571,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
         const uint32_t tmem_o = tmem_base + lane_base + (2 + g) * kTile;
         uint8_t *stage = sq + g * kTileBytes;
         uint32_t s_count = 0, pv_seen = 0;
-        for (int item = blockIdx.x; item < items; item += gridDim.x) {
-            const int pt = pair_tiles - 1 - item / per, bh = item % per;
+        for (int j = 0;; j++) {
+            int bh, pt;
+            if (!walk(j, bh, pt)) break;
+            if (pt < 0) continue;
             const int b = bh / p.heads, h = bh % p.heads;
             const int qt = 2 * pt + g;
             const int nkv = pair_kv_tiles(p, qt);
@@ -769,8 +791,8 @@ extern "C" int tb200_attention_fwd(const tb200_attn_desc *d, const void *q, cons
                 pair_configured[dev.device] = true;
             }
         }
-        const int pair_items = (p.q_tiles + 1) / 2 * d->batch * d->heads;
-        const unsigned pair_grid = static_cast<unsigned>(pair_items < dev.sms ? pair_items : dev.sms);
+        const int supers = ((p.q_tiles + 1) / 2 + 1) / 2 * d->batch * d->heads;
+        const unsigned pair_grid = static_cast<unsigned>(supers < dev.sms ? supers : dev.sms);
         attention_fwd_pair_kernel<<<pair_grid, kPairThreads, pair_smem, stream>>>(p);
         TB200_CUDA(cudaGetLastError());
         return TB200_OK;

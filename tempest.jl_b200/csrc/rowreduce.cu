@@ -460,6 +460,103 @@ __global__ void __launch_bounds__(256, 4) layernorm_bwd_compact(RowArgs a) {
     }
 }
 
+// ---------------------------------------- LayerNorm backward, rows beyond the resident schedule ----
+//
+// A row that does not fit one block's registers is streamed instead: one block of 512 threads walks the
+// row three times (four when the forward saved no statistics) -- the row sums  sum(dy gamma)  and
+// sum(dy gamma xh), then dx -- and the later walks find the row in L2.  dgamma / dbeta are column sums
+// over all rows, taken by a second kernel whose threads own one column each: row slabs x column blocks,
+// rows in order inside a slab, the slabs merged in order by merge_parts.
+constexpr int kLongSlabsMax = 64;
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kResidentMaxThreads) layernorm_bwd_long(RowArgs a) {
+    using A = Access<T, VEC>;
+    constexpr int E = A::EPV;
+    __shared__ float red[2 * 32 * kRedWidth];
+    RowCtx c = make_row_ctx(kResidentMaxThreads, red);
+    const float fn = static_cast<float>(a.n);
+    const int stride = kResidentMaxThreads * E;
+    const T *gamma = static_cast<const T *>(a.gamma);
+    for (long long r = blockIdx.x; r < a.rows; r += gridDim.x) {
+        const T *x = static_cast<const T *>(a.in0) + r * a.ld;
+        const T *dy = static_cast<const T *>(a.in1) + r * a.ld;
+        T *dx = static_cast<T *>(a.out0) + r * a.ld;
+        float mean, rstd;
+        if (a.cstat0) {
+            mean = static_cast<const float *>(a.cstat0)[r];
+            rstd = static_cast<const float *>(a.cstat1)[r];
+        } else {
+            float s = 0.0f;
+            for (int i = c.t * E; i < a.n; i += stride) {
+                float v[E];
+                A::load_cached(x + i, v);
+#pragma unroll
+                for (int e = 0; e < E; e++) s += v[e];
+            }
+            mean = row_allreduce1(s, c, SumOp()) / fn;
+            float q = 0.0f;
+            for (int i = c.t * E; i < a.n; i += stride) {
+                float v[E];
+                A::load_cached(x + i, v);
+#pragma unroll
+                for (int e = 0; e < E; e++) q = fmaf(v[e] - mean, v[e] - mean, q);
+            }
+            rstd = 1.0f / sqrtf(row_allreduce1(q, c, SumOp()) / fn + a.eps);
+            if (c.t == 0 && a.stat0) {   // the column sums read them
+                static_cast<float *>(a.stat0)[r] = mean;
+                static_cast<float *>(a.stat1)[r] = rstd;
+            }
+        }
+        float s2[2] = {0.0f, 0.0f};
+        for (int i = c.t * E; i < a.n; i += stride) {
+            float v[E], d[E], g[E];
+            A::load_cached(x + i, v);
+            A::load_cached(dy + i, d);
+            A::load_cached(gamma + i, g);
+#pragma unroll
+            for (int e = 0; e < E; e++) {
+                const float gh = d[e] * g[e];
+                s2[0] += gh;
+                s2[1] = fmaf(gh, (v[e] - mean) * rstd, s2[1]);
+            }
+        }
+        row_allreduce<2>(s2, c, SumOp());
+        const float c1 = s2[0] / fn, c2 = s2[1] / fn;
+        for (int i = c.t * E; i < a.n; i += stride) {
+            float v[E], d[E], g[E];
+            A::load(x + i, v);
+            A::load(dy + i, d);
+            A::load_cached(gamma + i, g);
+#pragma unroll
+            for (int e = 0; e < E; e++) d[e] = rstd * ((d[e] * g[e] - c1) - (v[e] - mean) * rstd * c2);
+            A::store(dx + i, d);
+        }
+    }
+}
+
+// part0[slab][col] = sum over the slab's rows of dy xh, part1[slab][col] = sum of dy
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_bwd_colsums(const T *x, const T *dy, const float *mean,
+                                                             const float *rstd, float *part0, float *part1, int n,
+                                                             long long rows, long long ld, int slabs) {
+    const int col = blockIdx.x * 256 + threadIdx.x;
+    const long long per = (rows + slabs - 1) / slabs;
+    const long long r0 = blockIdx.y * per;
+    const long long r1 = r0 + per < rows ? r0 + per : rows;
+    if (col >= n) return;
+    float dg = 0.0f, db = 0.0f;
+    for (long long r = r0; r < r1; r++) {
+        float v, d;
+        Access<T, false>::load_cached(x + r * ld + col, &v);
+        Access<T, false>::load_cached(dy + r * ld + col, &d);
+        dg = fmaf(d, (v - mean[r]) * rstd[r], dg);
+        db += d;
+    }
+    part0[static_cast<long long>(blockIdx.y) * n + col] = dg;
+    part1[static_cast<long long>(blockIdx.y) * n + col] = db;
+}
+
 // Column sums of the partial dgamma / dbeta rows: 32 columns x 8 lanes per
 // block; each lane strides over the parts in order, the 8 lanes merge in a
 // fixed tree.  Output in the element type, rounded once.
@@ -909,12 +1006,26 @@ RowKernel ln_bwd_kernel(int dtype, const Schedule &s, bool saved_stats) {
     return pick<LayernormBwdResident>(dtype, s);
 }
 
+// Scratch layout of the streamed LayerNorm backward: mean and rstd of every row (used when the forward saved
+// none), then the column sums' partial rows.
+int ln_long_slabs(int64_t n, int64_t rows, int sms) {
+    const int64_t col_blocks = ceil_div(n, 256);
+    int64_t slabs = ceil_div(static_cast<int64_t>(sms) * 8, col_blocks);
+    if (slabs > kLongSlabsMax) slabs = kLongSlabsMax;
+    if (slabs > rows) slabs = rows;
+    return static_cast<int>(slabs < 1 ? 1 : slabs);
+}
+size_t ln_long_stat_bytes(int64_t rows) { return (static_cast<size_t>(rows) * 2 * sizeof(float) + 15) / 16 * 16; }
+size_t ln_long_bytes(int64_t n, int64_t rows) {
+    return ln_long_stat_bytes(rows) + static_cast<size_t>(kLongSlabsMax) * n * 2 * sizeof(float);
+}
+
 // Bytes of scratch one schedule of an operator needs.
 int schedule_workspace(RowOp op, const Schedule &s, const DeviceInfo &dev, int64_t n, int64_t rows, int dtype,
                        size_t *bytes) {
     *bytes = 0;
     if (s.split) {
-        *bytes = split_state_bytes(s, rows);
+        *bytes = op == OP_LN_BWD ? ln_long_bytes(n, rows) : split_state_bytes(s, rows);
         return TB200_OK;
     }
     if (op == OP_LN_BWD) {
@@ -1040,11 +1151,51 @@ extern "C" int tb200_layernorm_bwd(const void *x, const void *gamma, const void 
     DeviceInfo dev;
     if ((st = current_device(&dev))) return st;
     const Schedule s = plan_rows(OP_LN_BWD, n, rows, ld, dtype, all_aligned(16, {x, gamma, dy, dx}));
-    if (s.split) return TB200_ERR_UNSUPPORTED;
     RowArgs a{};
     a.in0 = x; a.in1 = dy; a.gamma = gamma; a.out0 = dx; a.cstat0 = mean; a.cstat1 = rstd; a.eps = eps;
     a.n = static_cast<int>(n); a.rows = rows; a.ld = ld; a.tpr = s.tpr; a.rpc = s.rpc; a.splits = 1;
     a.exact = s.exact;
+    if (s.split) {   // rows beyond the resident schedule: streamed, column sums by a kernel of their own
+        const bool sums = dgamma || dbeta;
+        const bool saved = mean && rstd;
+        if ((sums || !saved) && !workspace_ok(workspace, workspace_bytes, ln_long_bytes(n, rows)))
+            return TB200_ERR_WORKSPACE;
+        float *own_stats = static_cast<float *>(workspace);
+        if (!saved) {
+            a.cstat0 = a.cstat1 = nullptr;
+            if (sums) { a.stat0 = own_stats; a.stat1 = own_stats + rows; }
+        }
+        const unsigned grid = static_cast<unsigned>(rows < 4LL * dev.sms ? rows : 4LL * dev.sms);
+        if (dtype == TB200_F32) {
+            if (s.vec) layernorm_bwd_long<float, true><<<grid, kResidentMaxThreads, 0, stream>>>(a);
+            else layernorm_bwd_long<float, false><<<grid, kResidentMaxThreads, 0, stream>>>(a);
+        } else {
+            if (s.vec) layernorm_bwd_long<__nv_bfloat16, true><<<grid, kResidentMaxThreads, 0, stream>>>(a);
+            else layernorm_bwd_long<__nv_bfloat16, false><<<grid, kResidentMaxThreads, 0, stream>>>(a);
+        }
+        TB200_CUDA(cudaGetLastError());
+        if (!sums) return TB200_OK;
+        const float *mean_at = saved ? mean : own_stats, *rstd_at = saved ? rstd : own_stats + rows;
+        float *part0 = reinterpret_cast<float *>(static_cast<char *>(workspace) + ln_long_stat_bytes(rows));
+        const int slabs = ln_long_slabs(n, rows, dev.sms);
+        float *part1 = part0 + static_cast<size_t>(slabs) * n;
+        const dim3 cgrid(static_cast<unsigned>(ceil_div(n, 256)), static_cast<unsigned>(slabs));
+        const unsigned mblocks = static_cast<unsigned>(ceil_div(n, 32));
+        if (dtype == TB200_F32) {
+            layernorm_bwd_colsums<float><<<cgrid, 256, 0, stream>>>(static_cast<const float *>(x), static_cast<const float *>(dy),
+                                                                   mean_at, rstd_at, part0, part1, a.n, rows, ld, slabs);
+            merge_parts<float><<<mblocks, 256, 0, stream>>>(part0, part1, static_cast<float *>(dgamma),
+                                                            static_cast<float *>(dbeta), a.n, slabs);
+        } else {
+            layernorm_bwd_colsums<__nv_bfloat16><<<cgrid, 256, 0, stream>>>(
+                static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(dy), mean_at, rstd_at, part0, part1,
+                a.n, rows, ld, slabs);
+            merge_parts<__nv_bfloat16><<<mblocks, 256, 0, stream>>>(part0, part1, static_cast<__nv_bfloat16 *>(dgamma),
+                                                                    static_cast<__nv_bfloat16 *>(dbeta), a.n, slabs);
+        }
+        TB200_CUDA(cudaGetLastError());
+        return TB200_OK;
+    }
     const RowKernel kernel = ln_bwd_kernel(dtype, s, mean && rstd);
     long long grid = 0;
     if ((st = resident_grid(kernel, s, dev, &grid))) return st;

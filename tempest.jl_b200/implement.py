@@ -374,8 +374,6 @@ class B200Kernels:
         lds = {s.strides[1] for name, s in b.arrays.items() if len(s.size) == 2 and s.size[0] == n and s.size[1] > 1}
         if len(lds) > 1:
             return False  # one leading dimension for all row-shaped operands
-        if _ROWOP[b.template] == lib.LAYERNORM_BWD and n > 8192:
-            return False
         return True
 
     def estimate(self, target: Target, b: Binding):
