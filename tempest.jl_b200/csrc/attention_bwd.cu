@@ -54,9 +54,10 @@ struct AttnBwdArgs {
     CUtensorMap outer_a, outer_b;   // dK/dV: K, V   | dQ: Q, dO     (boxes of 128 rows)
     CUtensorMap inner_a, inner_b;   // dK/dV: Q, dO  | dQ: K, V      (boxes of 128 rows)
     CUtensorMap out1, out2;         // dK/dV: dV, dK | dQ: -, dQ     (boxes of 32 rows)
-    const float *lse2;              // [batch][head][query]  lse * log2(e)
-    const float *delta;             // [batch][head][query]
+    const float *lse2;              // [batch][head][q_pad]  lse * log2(e)
+    const float *delta;             // [batch][head][q_pad]
     int batch, heads, kv_heads, queries, keys;
+    int q_pad;                      // queries rounded up to whole steps: rows of the two arrays above, zero-filled
     int outer_tiles, supers;
     int causal;
     float scale, scale_log2;
@@ -92,7 +93,7 @@ __device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, volatil
 template <bool DKDV>
 struct Steps {
     int b, head_outer, tile;   // the item
-    int c0, nc, group, count;
+    int c0, nc, group, count, head_first;
     bool done, skip;           // past the CTA's last super | second half of a super whose halves are one tile
     __device__ __forceinline__ Steps(const AttnBwdArgs &p, int j) {
         const int half_tiles = (p.outer_tiles + 1) / 2;
@@ -115,6 +116,7 @@ struct Steps {
             if (c0 > all) c0 = all;
             nc = all - c0;
             count = nc * group;
+            head_first = head_outer * group;
         } else {
             tile = heavy_or_light ? i : p.outer_tiles - 1 - i;
             b = bh / p.heads;
@@ -127,17 +129,24 @@ struct Steps {
                 if (upto < nc) nc = upto;
             }
             count = nc;
+            head_first = head_outer / group;
         }
     }
-    // head the inner operands of step t belong to, and their first position
-    __device__ __forceinline__ void at(int t, int &head_inner, int &pos0) const {
-        if (DKDV) {
-            head_inner = head_outer * group + t / nc;
-            pos0 = (c0 + t % nc) * kInner;
-        } else {
-            head_inner = head_outer / group;
-            pos0 = t * kInner;
+    // Where a step is: the walkers keep a cursor and advance it, because a division per step and thread sits
+    // squarely on the row warps' critical path.
+    struct Cursor {
+        int hrel = 0, chunk = 0;   // query head within the group (dK/dV), chunk within the head
+    };
+    __device__ __forceinline__ void advance(Cursor &k) const {
+        if (++k.chunk == nc) {
+            k.chunk = 0;
+            k.hrel++;
         }
+    }
+    // head the inner operands of the step belong to, and their first position
+    __device__ __forceinline__ void at(const Cursor &k, int &head_inner, int &pos0) const {
+        head_inner = head_first + k.hrel;   // dQ: one pass over the chunks, hrel stays 0
+        pos0 = (c0 + k.chunk) * kInner;
     }
 };
 
@@ -160,11 +169,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
     // every row warp has written P and dS; by step parity, because the dQ kernel's row warps may finish step
     // t + 1 (its scores and dP are issued ahead) before the issuing thread has looked at step t
     __shared__ __align__(8) uint64_t pds_full[2];
-    __shared__ __align__(8) uint64_t stats_ready;       // every row warp has written the step's statistics
     __shared__ uint32_t tmem_base_smem;
     __shared__ int failed_smem;
-    // dK/dV: the step's 128 queries' lse*log2(e) [0, 128) and delta [128, 256), double-buffered
-    __shared__ __align__(16) float col_stats[2][2 * kInner];
+    // dK/dV: the step's 128 queries' lse*log2(e) [0, 128) and delta [128, 256), one buffer per stage of the dO ring:
+    // the loading thread copies them with the dO tile and they complete on the same barrier
+    __shared__ __align__(16) float col_stats[Rings<true>::B][2 * kInner];
     volatile int *failed = &failed_smem;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -176,7 +185,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
         for (int s = 0; s < SB; s++) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
         mbar_init(&s_full, 1); mbar_init(&dp_full[0], 1); mbar_init(&dp_full[1], 1);
         mbar_init(&s_read, kRowWarps); mbar_init(&pds_full[0], kRowWarps); mbar_init(&pds_full[1], kRowWarps);
-        mbar_init(&stats_ready, kRowWarps);
         fence_barrier_init();
         prefetch_tensormap(&p.outer_a); prefetch_tensormap(&p.outer_b);
         prefetch_tensormap(&p.inner_a); prefetch_tensormap(&p.inner_b);
@@ -209,10 +217,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 tma_load_4d(s_outer_b, &p.outer_b, &outer_full, 0, steps.head_outer, r0, steps.b);
                 tma_load_4d(s_outer_b + kSlab, &p.outer_b, &outer_full, 64, steps.head_outer, r0, steps.b);
                 bool ok = true;
+                typename Steps<DKDV>::Cursor cur;
                 for (int t = 0; t < steps.count; t++, c++) {
                     const int sta = c % SA, stb = c % SB;
                     int hi, pos0;
-                    steps.at(t, hi, pos0);
+                    steps.at(cur, hi, pos0);
+                    steps.advance(cur);
                     if (!bwd_wait(&a_empty[sta], ((c / SA) & 1) ^ 1, failed, 2)) { ok = false; break; }
                     uint8_t *sa = s_ring_a + sta * kTileBytes;
                     mbar_arrive_expect_tx(&a_full[sta], kTileBytes);
@@ -220,7 +230,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                     tma_load_4d(sa + kSlab, &p.inner_a, &a_full[sta], 64, hi, pos0, steps.b);
                     if (!bwd_wait(&b_empty[stb], ((c / SB) & 1) ^ 1, failed, 13)) { ok = false; break; }
                     uint8_t *sb = s_ring_b + stb * kTileBytes;
-                    mbar_arrive_expect_tx(&b_full[stb], kTileBytes);
+                    mbar_arrive_expect_tx(&b_full[stb], kTileBytes + (DKDV ? 2 * kInner * 4 : 0));
+                    if (DKDV) {
+                        const long long at = (static_cast<long long>(steps.b) * p.heads + hi) * p.q_pad + pos0;
+                        bulk_load(&col_stats[stb][0], p.lse2 + at, kInner * 4, &b_full[stb]);
+                        bulk_load(&col_stats[stb][kInner], p.delta + at, kInner * 4, &b_full[stb]);
+                    }
                     tma_load_4d(sb, &p.inner_b, &b_full[stb], 0, hi, pos0, steps.b);
                     tma_load_4d(sb + kSlab, &p.inner_b, &b_full[stb], 64, hi, pos0, steps.b);
                 }
@@ -330,23 +345,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
         const int q4 = warp & 3;
         const int group = (warp - 2) >> 2;
         const int row = q4 * 32 + lane;
-        const int tid_r = (warp - 2) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
         const uint32_t t_s = tmem_s + lane_base + group * 64;     // this thread's 64 scores
         const uint32_t t_dp0 = tmem_dp + lane_base + group * 64;  // its 64 dP values; P and dS go over them
         uint32_t c = 0, item_count = 0;
-        // dK/dV: this thread's share of a step's statistics (lse*log2(e) of query tid_r, or delta of query
-        // tid_r - 128), fetched one step ahead so that its latency never sits in the step that needs it
-        auto fetch_stat = [&](const Steps<DKDV> &of, int t) -> float {
-            int hi, pos0;
-            of.at(t, hi, pos0);
-            const int qpos = pos0 + (tid_r & (kInner - 1));
-            const long long base = (static_cast<long long>(of.b) * p.heads + hi) * p.queries;
-            const float *src = tid_r < kInner ? p.lse2 : p.delta;
-            return qpos < p.queries ? __ldg(src + base + qpos) : 0.0f;
-        };
-        float stat_next = 0.0f;
-        bool have_next = false;
         for (int j = 0;; j++) {
             const Steps<DKDV> steps(p, j);
             if (steps.done) break;
@@ -354,40 +356,24 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
             const int outer_pos = steps.tile * kOuter + row;   // this thread's key (dK/dV) or query (dQ)
             float row_lse2 = 0.0f, row_delta = 0.0f;
             if (!DKDV && outer_pos < p.queries) {
-                const long long i = (static_cast<long long>(steps.b) * p.heads + steps.head_outer) * p.queries + outer_pos;
+                const long long i = (static_cast<long long>(steps.b) * p.heads + steps.head_outer) * p.q_pad + outer_pos;
                 row_lse2 = p.lse2[i];
                 row_delta = p.delta[i];
             }
             bool ok = true;
+            typename Steps<DKDV>::Cursor cur;
             for (int t = 0; t < steps.count; t++, c++) {
                 const uint32_t ph = c & 1;
                 int hi, pos0;
-                steps.at(t, hi, pos0);
+                steps.at(cur, hi, pos0);
+                steps.advance(cur);   // cur is now the next step's
                 const int col0 = pos0 + group * 64;   // first position of this thread's columns
-                float *stats = col_stats[ph];
-                if (DKDV) {
-                    stats[tid_r] = have_next ? stat_next : fetch_stat(steps, t);
-                    have_next = false;
-                    if (t + 1 < steps.count) {
-                        stat_next = fetch_stat(steps, t + 1);
-                        have_next = true;
-                    } else {
-                        const Steps<DKDV> after(p, j + 1);
-                        if (!after.done && !after.skip && after.count > 0) {
-                            stat_next = fetch_stat(after, 0);
-                            have_next = true;
-                        }
-                    }
-                }
+                // dK/dV: the statistics of the step's queries are per column; they arrived in shared memory with the
+                // step's dO tile (the wait is for a barrier that completed long ago: the issuing thread needed it first)
+                const float *stats = col_stats[c % SB] + group * 64;
+                if (DKDV && !bwd_wait(&b_full[c % SB], (c / SB) & 1, failed, 12)) { ok = false; break; }
                 if (!bwd_wait(&s_full, ph, failed, 8)) { ok = false; break; }
                 tcgen05_fence_after();
-                if (DKDV) {
-                    // the row warps meet (a bounded wait, unlike a named barrier: a warp that gave up on a
-                    // failed wait elsewhere must not leave the others hanging here)
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&stats_ready);
-                    if (!bwd_wait(&stats_ready, ph, failed, 12)) { ok = false; break; }
-                }
                 uint32_t s[64];
                 tmem_ld_32x32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
                 tmem_ld_32x32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
@@ -410,43 +396,63 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                         if (key >= p.keys || query >= p.queries || (p.causal && key > query)) s[i] = 0xff800000u;
                     }
                 }
-                // P, kept in Float32 for dS
+                // P.  dQ keeps it in Float32 for dS.  dK/dV rounds it to BFloat16 here -- P' feeds dV += P' dO in that
+                // precision anyway, the conversions issue in the shadow of the exponentials (this stretch waits on the
+                // special-function unit), and dS is then formed from the rounded weights: half the registers, which
+                // is what keeps this kernel's row threads from spilling.
+                uint32_t pk[32];
 #pragma unroll
                 for (int g = 0; g < 16; g++) {
                     float4 l4 = make_float4(row_lse2, row_lse2, row_lse2, row_lse2);
-                    if (DKDV) l4 = *reinterpret_cast<const float4 *>(stats + group * 64 + 4 * g);
-                    s[4 * g] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(s[4 * g]), p.scale_log2, -l4.x)));
-                    s[4 * g + 1] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(s[4 * g + 1]), p.scale_log2, -l4.y)));
-                    s[4 * g + 2] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(s[4 * g + 2]), p.scale_log2, -l4.z)));
-                    s[4 * g + 3] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(s[4 * g + 3]), p.scale_log2, -l4.w)));
+                    if (DKDV) l4 = *reinterpret_cast<const float4 *>(stats + 4 * g);
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(s[4 * g]), p.scale_log2, -l4.x));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(s[4 * g + 1]), p.scale_log2, -l4.y));
+                    const float p2 = fast_exp2(fmaf(__uint_as_float(s[4 * g + 2]), p.scale_log2, -l4.z));
+                    const float p3 = fast_exp2(fmaf(__uint_as_float(s[4 * g + 3]), p.scale_log2, -l4.w));
+                    if (DKDV) {
+                        pk[2 * g] = pack_bf16x2(p0, p1);
+                        pk[2 * g + 1] = pack_bf16x2(p2, p3);
+                    } else {
+                        s[4 * g] = __float_as_uint(p0); s[4 * g + 1] = __float_as_uint(p1);
+                        s[4 * g + 2] = __float_as_uint(p2); s[4 * g + 3] = __float_as_uint(p3);
+                    }
                 }
                 if (!bwd_wait(&dp_full[ph], (c >> 1) & 1, failed, 9)) { ok = false; break; }
                 const uint32_t t_dp = t_dp0 + (DKDV ? 0 : ph * 128);
                 tcgen05_fence_after();
-                uint32_t dp[64];
-                tmem_ld_32x32(t_dp, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
-                tmem_ld_32x32(t_dp + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+                // dS = P (dP - delta), packed two per column, in two halves of 32 columns: the first half's columns
+                // take P as soon as they are read, the second half's take dS
+                uint32_t dp[32], dk[32];
+                tmem_ld_32x32(t_dp, dp);
                 tmem_ld_wait();
-                // packed two per column: dp[0, 32) becomes P, dp[32, 64) becomes dS
-                uint32_t pk[32], dk[32];
-#pragma unroll
-                for (int g = 0; g < 16; g++) {
-                    float4 d4 = make_float4(row_delta, row_delta, row_delta, row_delta);
-                    if (DKDV) d4 = *reinterpret_cast<const float4 *>(stats + kInner + group * 64 + 4 * g);
-                    const float p0 = __uint_as_float(s[4 * g]), p1 = __uint_as_float(s[4 * g + 1]);
-                    const float p2 = __uint_as_float(s[4 * g + 2]), p3 = __uint_as_float(s[4 * g + 3]);
-                    const float e0 = p0 * (__uint_as_float(dp[4 * g]) - d4.x);
-                    const float e1 = p1 * (__uint_as_float(dp[4 * g + 1]) - d4.y);
-                    const float e2 = p2 * (__uint_as_float(dp[4 * g + 2]) - d4.z);
-                    const float e3 = p3 * (__uint_as_float(dp[4 * g + 3]) - d4.w);
-                    if (DKDV) {
-                        pk[2 * g] = pack_bf16x2(p0, p1);
-                        pk[2 * g + 1] = pack_bf16x2(p2, p3);
-                    }
-                    dk[2 * g] = pack_bf16x2(e0, e1);
-                    dk[2 * g + 1] = pack_bf16x2(e2, e3);
-                }
                 if (DKDV) tmem_st_32x32(t_dp, pk);
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    if (half == 1) {
+                        tmem_ld_32x32(t_dp + 32, dp);
+                        tmem_ld_wait();
+                    }
+#pragma unroll
+                    for (int g = 0; g < 8; g++) {
+                        const int i = 32 * half + 4 * g;
+                        float4 d4 = make_float4(row_delta, row_delta, row_delta, row_delta);
+                        if (DKDV) d4 = *reinterpret_cast<const float4 *>(stats + kInner + i);
+                        float p0, p1, p2, p3;
+                        if (DKDV) {
+                            unpack_bf16x2(pk[i / 2], p0, p1);
+                            unpack_bf16x2(pk[i / 2 + 1], p2, p3);
+                        } else {
+                            p0 = __uint_as_float(s[i]); p1 = __uint_as_float(s[i + 1]);
+                            p2 = __uint_as_float(s[i + 2]); p3 = __uint_as_float(s[i + 3]);
+                        }
+                        const float e0 = p0 * (__uint_as_float(dp[4 * g]) - d4.x);
+                        const float e1 = p1 * (__uint_as_float(dp[4 * g + 1]) - d4.y);
+                        const float e2 = p2 * (__uint_as_float(dp[4 * g + 2]) - d4.z);
+                        const float e3 = p3 * (__uint_as_float(dp[4 * g + 3]) - d4.w);
+                        dk[16 * half + 2 * g] = pack_bf16x2(e0, e1);
+                        dk[16 * half + 2 * g + 1] = pack_bf16x2(e2, e3);
+                    }
+                }
                 tmem_st_32x32(t_dp + 32, dk);
                 tmem_st_wait();
                 tcgen05_fence_before();
@@ -514,10 +520,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
     }
 }
 
-// delta[b][h][m] = sum_d dO o ; lse2[b][h][m] = lse[b][m][h] * log2(e).  16 threads per (b, m, h) row.
+// delta[b][h][m] = sum_d dO o ; lse2[b][h][m] = lse[b][m][h] * log2(e), rows of q_pad entries.  16 threads per (b, m, h) row.
 __global__ void __launch_bounds__(256) attention_stats_kernel(const __nv_bfloat16 *o, const __nv_bfloat16 *dout,
                                                               const float *lse, float *lse2, float *delta, int batch,
-                                                              int heads, int queries, int d) {
+                                                              int heads, int queries, int q_pad, int d) {
     const long long rows = static_cast<long long>(batch) * queries * heads;
     const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 4;
     const int t = threadIdx.x & 15;
@@ -538,7 +544,7 @@ __global__ void __launch_bounds__(256) attention_stats_kernel(const __nv_bfloat1
         const long long bm = r / heads;
         const int m = static_cast<int>(bm % queries);
         const long long b = bm / queries;
-        const long long out = (b * heads + h) * queries + m;
+        const long long out = (b * heads + h) * q_pad + m;
         delta[out] = s;
         lse2[out] = lse[r] * kLog2e;
     }
@@ -613,7 +619,8 @@ using namespace tb200;
 
 extern "C" size_t tb200_attention_bwd_workspace_bytes(const tb200_attn_desc *d) {
     if (!d || d->batch <= 0 || d->heads <= 0 || d->queries <= 0) return 0;
-    return static_cast<size_t>(2) * d->batch * d->heads * d->queries * sizeof(float);
+    const size_t q_pad = (static_cast<size_t>(d->queries) + kInner - 1) / kInner * kInner;
+    return static_cast<size_t>(2) * d->batch * d->heads * q_pad * sizeof(float);
 }
 
 extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v,
@@ -641,19 +648,21 @@ extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, cons
     int st = current_device(&dev);
     if (st) return st;
 
-    const long long stat_len = static_cast<long long>(d->batch) * d->heads * d->queries;
+    const int q_pad = (d->queries + kInner - 1) / kInner * kInner;
+    const long long stat_len = static_cast<long long>(d->batch) * d->heads * q_pad;
     float *lse2 = static_cast<float *>(workspace);
     float *delta = lse2 + stat_len;
     {
-        const long long threads = stat_len * 16;
+        if (q_pad != d->queries) TB200_CUDA(cudaMemsetAsync(workspace, 0, need, stream));   // the pads are read
+        const long long threads = static_cast<long long>(d->batch) * d->heads * d->queries * 16;
         const unsigned blocks = static_cast<unsigned>(ceil_div(threads, 256));
         attention_stats_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(o),
                                                            static_cast<const __nv_bfloat16 *>(dout), lse, lse2, delta,
-                                                           d->batch, d->heads, d->queries, d->head_dim);
+                                                           d->batch, d->heads, d->queries, q_pad, d->head_dim);
         TB200_CUDA(cudaGetLastError());
     }
     AttnBwdArgs p{};
-    p.lse2 = lse2; p.delta = delta;
+    p.lse2 = lse2; p.delta = delta; p.q_pad = q_pad;
     p.batch = d->batch; p.heads = d->heads; p.kv_heads = d->kv_heads; p.queries = d->queries; p.keys = d->keys;
     p.causal = d->causal; p.scale = d->scale; p.scale_log2 = d->scale * kLog2e;
     // dK, dV: items over key tiles

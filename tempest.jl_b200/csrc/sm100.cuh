@@ -82,6 +82,14 @@ __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *m, uin
         : "memory");
 }
 
+// `bytes` contiguous bytes, global -> this CTA's shared memory (no tensor map), completion counted on `bar`.
+// Both addresses 16-byte aligned, `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
 // One tile, this CTA's shared memory -> global, tracked by the thread's bulk-group counter.
 // Elements outside the tensor are not written.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *src, int x, int y) {
