@@ -315,8 +315,9 @@ def run_also(torch, dist, pkg, world, rank):
     y = torch.randn(per, sizes[-1], device="cuda").bfloat16()
     step.step(x, y)                      # every launch once, outside any capture
     # one GPU: the whole step replayed as one CUDA graph, as Tempest replays a compiled call; with
-    # replicas the step is launched eagerly (its all-reduces run on a side stream)
-    run = step.capture(x, y) if world == 1 else (lambda: step.step(x, y))
+    # replicas the stretches between two gradient exchanges are graphs and the all-reduces stay
+    # outside them, launched eagerly on a side stream
+    run = step.capture(x, y) if world == 1 else step.capture_segments(x, y)
     ms = timed(run, 20, 5)
     flops = 2 * gb * (1024 * 4096 + 2 * 4096 * 4096 + 4096 * 1024) * 3 - 2 * gb * 1024 * 4096
     out = {"mlp_train": {"steps_per_s": round(1000.0 / ms, 1), "ms_per_step": round(ms, 4), "n_gpus": world,
@@ -331,14 +332,13 @@ def run_also(torch, dist, pkg, world, rank):
         wstep = pkg.mlp.MLPStep(torch, sizes, gb, 1e-3, world=world, global_batch=gb * world, seed=1)
         wx = torch.randn(gb, sizes[0], device="cuda").bfloat16()
         wy = torch.randn(gb, sizes[-1], device="cuda").bfloat16()
-        wstep.step(wx, wy)
-        wms = timed(lambda: wstep.step(wx, wy), 20, 5)
+        wms = timed(wstep.capture_segments(wx, wy), 20, 5)
         out["mlp_train_weak"] = {"steps_per_s": round(1000.0 / wms, 1), "ms_per_step": round(wms, 4), "n_gpus": world,
                                  "global_batch": gb * world, "scaling": "weak",
                                  "samples_per_s": round(gb * world * 1000.0 / wms, 1),
                                  "TFLOP/s": round(flops * world / wms / 1e9, 1),
                                  "frac_of_measured_bf16_peak_per_gpu": round(flops / wms / 1e9 / tensor_peak, 4),
-                                 "launch": "eager (one GPU replays a CUDA graph: compare samples_per_s with n_gpus x the 1-GPU eager rate)",
+                                 "launch": "one CUDA graph per stretch between two gradient exchanges, NCCL all-reduces eager on a side stream (one GPU replays the whole step as one graph)",
                                  "device_error": L.device_error()}
         del wstep, wx, wy
     if rank == 0 or world == 1:

@@ -131,59 +131,121 @@ class MLPStep:
         torch = self.torch
         cur = torch.cuda.current_stream()
         stream = cur.cuda_stream
-        bf16 = lib.BF16
-        self.a[0] = x
-        out = self.forward(x, stream)
-        L = self.L
-        # loss = sum(abs2, out - y) / batch ; dz_last = 2 (out - y) / batch
-        inv = 1.0 / self.global_batch
-        lib.squared_error(out.data_ptr(), y.data_ptr(), self.dz[L - 1].data_ptr(), self.loss.data_ptr(),
-                          out.numel(), inv, inv, False, bf16, self.sq_ws.data_ptr(), self.sq_ws_bytes, stream)
-        self.launches += 1
+        self._head(x, y, stream)
         events = []
-        for i in range(L - 1, -1, -1):
-            fin, fout = self.sizes[i], self.sizes[i + 1]
-            dz = self.dz[i]
-            if i > 0:
-                # dz_below = (dz * w') .* act'(saved): A = dz [batch][fout], B = w as [n = fin][k = fout]
-                saved = self.z[i - 1] if self.saved == "z" else self.a[i]
-                lib.gemm(dz.data_ptr(), self.w[i].data_ptr(), self.dz[i - 1].data_ptr(), self.batch, fin, fout,
-                         a_layout=lib.K_MAJOR, b_layout=lib.K_MAJOR, in_dtype=bf16, epilogue=self.bwd_epi,
-                         aux=saved.data_ptr(), stream=stream)
-                self.launches += 1
-            lib.colsum(dz.data_ptr(), self.db[i].data_ptr(), self.batch, fout, fout, 1.0, bf16,
-                       self.cs_ws.data_ptr(), self.cs_ws_bytes, stream)
-            self.launches += 2
-            if self.fuse_update:
-                # w = w - rate * (a_in' * dz): the update rides in the product's epilogue
-                lib.gemm(self.a[i].data_ptr(), dz.data_ptr(), self.w[i].data_ptr(), fin, fout, self.batch,
-                         a_layout=lib.MN_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=bf16, epilogue=lib.EPI_AXPY,
-                         aux=self.w[i].data_ptr(), alpha=-self.rate, stream=stream)
-                lib.axpy(self.b[i].data_ptr(), self.db[i].data_ptr(), -self.rate, fout, bf16, bf16, stream)
-                self.launches += 2
-            else:
-                lib.gemm(self.a[i].data_ptr(), dz.data_ptr(), self.dw[i].data_ptr(), fin, fout, self.batch,
-                         a_layout=lib.MN_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=bf16, stream=stream)
-                self.launches += 1
-                done = None
-                if self.world > 1:
-                    ready = torch.cuda.Event()
-                    ready.record(cur)
-                    with torch.cuda.stream(self.comm_stream):
-                        self.comm_stream.wait_event(ready)
-                        torch.distributed.all_reduce(self.bucket[i], group=self.group)
-                        done = torch.cuda.Event()
-                        done.record(self.comm_stream)
-                events.append((i, done))
+        for i in range(self.L - 1, -1, -1):
+            self._layer_back(i, stream)
+            if not self.fuse_update:
+                events.append((i, self._exchange(i, cur)))
         for i, done in events:
             if done is not None:
                 cur.wait_event(done)
-            n = self.bucket[i].numel()
-            nw = self.sizes[i] * self.sizes[i + 1]
-            lib.axpy(self.w[i].data_ptr(), self.dw[i].data_ptr(), -self.rate, nw, bf16, bf16, stream)
-            lib.axpy(self.b[i].data_ptr(), self.db[i].data_ptr(), -self.rate, n - nw, bf16, bf16, stream)
-            self.launches += 2
+            self._update(i, stream)
         return self.loss
+
+    def _head(self, x, y, stream):
+        """Forward pass and loss: loss = sum(abs2, out - y) / batch ; dz_last = 2 (out - y) / batch."""
+        self.a[0] = x
+        out = self.forward(x, stream)
+        inv = 1.0 / self.global_batch
+        lib.squared_error(out.data_ptr(), y.data_ptr(), self.dz[self.L - 1].data_ptr(), self.loss.data_ptr(),
+                          out.numel(), inv, inv, False, lib.BF16, self.sq_ws.data_ptr(), self.sq_ws_bytes, stream)
+        self.launches += 1
+
+    def _layer_back(self, i, stream):
+        """Layer i of the backward pass: the gradient for the layer below, the bias gradient, the weight gradient
+        (applied in the product's epilogue when the update is fused, else left in dw[i])."""
+        bf16 = lib.BF16
+        fin, fout = self.sizes[i], self.sizes[i + 1]
+        dz = self.dz[i]
+        if i > 0:
+            # dz_below = (dz * w') .* act'(saved): A = dz [batch][fout], B = w as [n = fin][k = fout]
+            saved = self.z[i - 1] if self.saved == "z" else self.a[i]
+            lib.gemm(dz.data_ptr(), self.w[i].data_ptr(), self.dz[i - 1].data_ptr(), self.batch, fin, fout,
+                     a_layout=lib.K_MAJOR, b_layout=lib.K_MAJOR, in_dtype=bf16, epilogue=self.bwd_epi,
+                     aux=saved.data_ptr(), stream=stream)
+            self.launches += 1
+        lib.colsum(dz.data_ptr(), self.db[i].data_ptr(), self.batch, fout, fout, 1.0, bf16,
+                   self.cs_ws.data_ptr(), self.cs_ws_bytes, stream)
+        self.launches += 2
+        if self.fuse_update:
+            # w = w - rate * (a_in' * dz): the update rides in the product's epilogue
+            lib.gemm(self.a[i].data_ptr(), dz.data_ptr(), self.w[i].data_ptr(), fin, fout, self.batch,
+                     a_layout=lib.MN_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=bf16, epilogue=lib.EPI_AXPY,
+                     aux=self.w[i].data_ptr(), alpha=-self.rate, stream=stream)
+            lib.axpy(self.b[i].data_ptr(), self.db[i].data_ptr(), -self.rate, fout, bf16, bf16, stream)
+            self.launches += 2
+        else:
+            lib.gemm(self.a[i].data_ptr(), dz.data_ptr(), self.dw[i].data_ptr(), fin, fout, self.batch,
+                     a_layout=lib.MN_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=bf16, stream=stream)
+            self.launches += 1
+
+    def _exchange(self, i, cur):
+        """Layer i's gradient bucket summed over the replicas on the side stream, once `cur` has produced it.
+        Returns the event that marks the sum as landed (None on one GPU)."""
+        if self.world == 1:
+            return None
+        torch = self.torch
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ready)
+            torch.distributed.all_reduce(self.bucket[i], group=self.group)
+            done = torch.cuda.Event()
+            done.record(self.comm_stream)
+        return done
+
+    def _update(self, i, stream):
+        bf16 = lib.BF16
+        n = self.bucket[i].numel()
+        nw = self.sizes[i] * self.sizes[i + 1]
+        lib.axpy(self.w[i].data_ptr(), self.dw[i].data_ptr(), -self.rate, nw, bf16, bf16, stream)
+        lib.axpy(self.b[i].data_ptr(), self.db[i].data_ptr(), -self.rate, n - nw, bf16, bf16, stream)
+        self.launches += 2
+
+    def capture_segments(self, x, y):
+        """The data-parallel step with its own kernels recorded into CUDA graphs and the all-reduces left outside
+        them: one graph per stretch between two exchanges (forward + loss + the top layer's backward; each lower
+        layer's backward; all the updates), replayed on the current stream with NCCL's all-reduce launched eagerly
+        on the side stream in between.  A replica then makes about a dozen host calls per step instead of fifty,
+        which is what eight Python processes on one host need to keep their GPUs fed.  No collective is ever
+        inside a capture.  x and y are read in place at every replay.  Returns `replay()`."""
+        if self.fuse_update:
+            raise ValueError("capture_segments() is for data-parallel steps (unfused updates)")
+        torch = self.torch
+        side = torch.cuda.Stream()
+
+        def record(body):
+            graph = torch.cuda.CUDAGraph()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.graph(graph, stream=side):
+                body(torch.cuda.current_stream().cuda_stream)
+            torch.cuda.current_stream().wait_stream(side)
+            return graph
+
+        self.step(x, y)   # every launch and every NCCL connection once, outside any capture
+        torch.cuda.synchronize()
+        top = self.L - 1
+        stretches = [(top, record(lambda st: (self._head(x, y, st), self._layer_back(top, st))))]
+        for i in range(top - 1, -1, -1):
+            stretches.append((i, record(lambda st, i=i: self._layer_back(i, st))))
+        updates = record(lambda st: [self._update(i, st) for i in range(top, -1, -1)])
+        torch.cuda.synchronize()
+        self._graphs = (stretches, updates)
+
+        def replay():
+            cur = torch.cuda.current_stream()
+            events = []
+            for i, graph in stretches:
+                graph.replay()
+                events.append(self._exchange(i, cur))
+            for done in events:
+                if done is not None:
+                    cur.wait_event(done)
+            updates.replay()
+            return self.loss
+
+        return replay
 
     def capture(self, x, y):
         """Records one single-GPU step into a CUDA graph, as Tempest captures a compiled call

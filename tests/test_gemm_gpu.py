@@ -270,6 +270,31 @@ def test_mlp_step_against_oracle(pkg, cuda, oracle):
                 assert rel < 5e-3, rel
 
 
+def test_mlp_step_replayed_from_stretch_graphs(pkg, cuda, oracle):
+    """The data-parallel form of the step (unfused updates) replayed from one CUDA graph per stretch between two
+    gradient exchanges leaves the same bits as the same steps launched kernel by kernel."""
+    torch = cuda
+    sizes, batch, rate = (64, 128, 96, 32), 48, 1e-3
+    ws = [oracle.to_bf16(0.2 * oracle.normal((sizes[i], sizes[i + 1]), 50 + i)) for i in range(3)]
+    bs = [oracle.to_bf16(0.1 * oracle.normal((sizes[i + 1],), 60 + i)) for i in range(3)]
+    x, y = dev(torch, oracle.to_bf16(oracle.normal((batch, sizes[0]), 70))), dev(torch, oracle.to_bf16(oracle.normal((batch, sizes[-1]), 71)))
+    make = lambda: pkg.mlp.MLPStep(torch, sizes, batch, rate, weights=[dev(torch, w) for w in ws],
+                                   biases=[dev(torch, b) for b in bs], fuse_update=False)
+    eager, graphed = make(), make()
+    for _ in range(3):
+        eager.step(x, y)
+    replay = graphed.capture_segments(x, y)   # runs the step once itself
+    replay()
+    loss = replay()
+    torch.cuda.synchronize()
+    assert pkg.lib.device_error() == 0
+    assert loss.item() == eager.loss.item()
+    for i in range(3):
+        assert torch.equal(graphed.w[i], eager.w[i]) and torch.equal(graphed.b[i], eager.b[i])
+    with pytest.raises(ValueError):
+        pkg.mlp.MLPStep(torch, sizes, batch, rate, fuse_update=True).capture_segments(x, y)
+
+
 def test_products_and_attention_through_the_plugin_mirror(pkg, cuda, oracle):
     """Binding -> supports -> build -> launch for a product template and an attention template, with the
     arrays described as Tempest describes them (column-major `Strided` views)."""
