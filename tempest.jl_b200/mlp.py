@@ -206,7 +206,7 @@ class MLPStep:
     def capture_segments(self, x, y):
         """The data-parallel step with its own kernels recorded into CUDA graphs and the all-reduces left outside
         them: one graph per stretch between two exchanges (forward + loss + the top layer's backward; each lower
-        layer's backward; all the updates), replayed on the current stream with NCCL's all-reduce launched eagerly
+        layer's backward; each layer's update), replayed on the current stream with NCCL's all-reduce launched eagerly
         on the side stream in between.  A replica then makes about a dozen host calls per step instead of fifty,
         which is what eight Python processes on one host need to keep their GPUs fed.  No collective is ever
         inside a capture.  x and y are read in place at every replay.  Returns `replay()`."""
@@ -229,7 +229,7 @@ class MLPStep:
         stretches = [(top, record(lambda st: (self._head(x, y, st), self._layer_back(top, st))))]
         for i in range(top - 1, -1, -1):
             stretches.append((i, record(lambda st, i=i: self._layer_back(i, st))))
-        updates = record(lambda st: [self._update(i, st) for i in range(top, -1, -1)])
+        updates = [record(lambda st, i=i: self._update(i, st)) for i in range(top, -1, -1)]
         torch.cuda.synchronize()
         self._graphs = (stretches, updates)
 
@@ -239,10 +239,11 @@ class MLPStep:
             for i, graph in stretches:
                 graph.replay()
                 events.append(self._exchange(i, cur))
-            for done in events:
+            # a layer is updated as soon as its sum has landed, while the lower layers' sums are still in flight
+            for done, update in zip(events, updates):
                 if done is not None:
                     cur.wait_event(done)
-            updates.replay()
+                update.replay()
             return self.loss
 
         return replay
