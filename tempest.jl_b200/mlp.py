@@ -133,15 +133,42 @@ class MLPStep:
         stream = cur.cuda_stream
         self._head(x, y, stream)
         events = []
-        for i in range(self.L - 1, -1, -1):
-            self._layer_back(i, stream)
-            if not self.fuse_update:
-                events.append((i, self._exchange(i, cur)))
+        for kind, i in self._schedule():
+            if kind == "below":
+                self._dz_below(i, stream)
+            else:
+                self._grads(i, stream)
+                if not self.fuse_update:
+                    events.append((i, self._exchange(i, cur)))
         for i, done in events:
             if done is not None:
                 cur.wait_event(done)
             self._update(i, stream)
         return self.loss
+
+    def _schedule(self):
+        """The backward pass as a list of ("below", i) -- the gradient for the layer below layer i -- and
+        ("grads", i) -- layer i's bias and weight gradients, after which its bucket can be exchanged.
+        Fused updates need layer i's weights intact until the layer below has its gradient, so they go top down:
+        below(i), grads(i).  Replicas leave the weights alone until the end, which frees the order: the middle
+        layers' gradients (the large buckets) are formed as soon as their dz exists, so that their exchanges start
+        early, and the top and bottom layers' (small buckets here) come last, with a whole product still to run
+        behind the last large exchange."""
+        L = self.L
+        if self.fuse_update or L < 3:
+            out = []
+            for i in range(L - 1, -1, -1):
+                if i > 0:
+                    out.append(("below", i))
+                out.append(("grads", i))
+            return out
+        out = []
+        for i in range(L - 1, 0, -1):
+            out.append(("below", i))
+            if i - 1 >= 1:
+                out.append(("grads", i - 1))
+        out += [("grads", L - 1), ("grads", 0)]
+        return out
 
     def _head(self, x, y, stream):
         """Forward pass and loss: loss = sum(abs2, out - y) / batch ; dz_last = 2 (out - y) / batch."""
@@ -152,19 +179,21 @@ class MLPStep:
                           out.numel(), inv, inv, False, lib.BF16, self.sq_ws.data_ptr(), self.sq_ws_bytes, stream)
         self.launches += 1
 
-    def _layer_back(self, i, stream):
-        """Layer i of the backward pass: the gradient for the layer below, the bias gradient, the weight gradient
-        (applied in the product's epilogue when the update is fused, else left in dw[i])."""
+    def _dz_below(self, i, stream):
+        """dz[i - 1] = (dz[i] * w[i]') .* act'(saved): A = dz [batch][fout], B = w as [n = fin][k = fout]."""
+        fin, fout = self.sizes[i], self.sizes[i + 1]
+        saved = self.z[i - 1] if self.saved == "z" else self.a[i]
+        lib.gemm(self.dz[i].data_ptr(), self.w[i].data_ptr(), self.dz[i - 1].data_ptr(), self.batch, fin, fout,
+                 a_layout=lib.K_MAJOR, b_layout=lib.K_MAJOR, in_dtype=lib.BF16, epilogue=self.bwd_epi,
+                 aux=saved.data_ptr(), stream=stream)
+        self.launches += 1
+
+    def _grads(self, i, stream):
+        """Layer i's bias gradient and weight gradient (applied in the product's epilogue when the update is
+        fused, else left in dw[i])."""
         bf16 = lib.BF16
         fin, fout = self.sizes[i], self.sizes[i + 1]
         dz = self.dz[i]
-        if i > 0:
-            # dz_below = (dz * w') .* act'(saved): A = dz [batch][fout], B = w as [n = fin][k = fout]
-            saved = self.z[i - 1] if self.saved == "z" else self.a[i]
-            lib.gemm(dz.data_ptr(), self.w[i].data_ptr(), self.dz[i - 1].data_ptr(), self.batch, fin, fout,
-                     a_layout=lib.K_MAJOR, b_layout=lib.K_MAJOR, in_dtype=bf16, epilogue=self.bwd_epi,
-                     aux=saved.data_ptr(), stream=stream)
-            self.launches += 1
         lib.colsum(dz.data_ptr(), self.db[i].data_ptr(), self.batch, fout, fout, 1.0, bf16,
                    self.cs_ws.data_ptr(), self.cs_ws_bytes, stream)
         self.launches += 2
@@ -225,11 +254,25 @@ class MLPStep:
 
         self.step(x, y)   # every launch and every NCCL connection once, outside any capture
         torch.cuda.synchronize()
-        top = self.L - 1
-        stretches = [(top, record(lambda st: (self._head(x, y, st), self._layer_back(top, st))))]
-        for i in range(top - 1, -1, -1):
-            stretches.append((i, record(lambda st, i=i: self._layer_back(i, st))))
-        updates = [record(lambda st, i=i: self._update(i, st)) for i in range(top, -1, -1)]
+        # cut the schedule after every ("grads", i): that is where layer i's exchange is launched
+        pieces, run = [], [("head", -1)]
+        for kind, i in self._schedule():
+            run.append((kind, i))
+            if kind == "grads":
+                pieces.append((i, run))
+                run = []
+
+        def play(ops, st):
+            for kind, i in ops:
+                if kind == "head":
+                    self._head(x, y, st)
+                elif kind == "below":
+                    self._dz_below(i, st)
+                else:
+                    self._grads(i, st)
+
+        stretches = [(i, record(lambda st, ops=ops: play(ops, st))) for i, ops in pieces]
+        updates = [record(lambda st, i=i: self._update(i, st)) for i, _ in pieces]
         torch.cuda.synchronize()
         self._graphs = (stretches, updates)
 
