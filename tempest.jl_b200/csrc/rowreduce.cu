@@ -248,8 +248,12 @@ __device__ __forceinline__ void layernorm_fwd_resident_body(const RowArgs &a) {
     }
 }
 
+// Rows of at most 16 elements a thread are compiled for three resident blocks of 512 threads (40 registers): at
+// 64 registers the 4096-element Float32 rows of the benchmark ran four 256-thread blocks per SM, half the warps
+// the SM holds, and the kernel waited on memory latency rather than bandwidth.
 template <typename T, bool VEC, int VPT>
-__global__ void __launch_bounds__(kResidentMaxThreads, 2) layernorm_fwd_resident(RowArgs a) {
+__global__ void __launch_bounds__(kResidentMaxThreads, (VPT * Access<T, VEC>::EPV <= 16 ? 3 : 2))
+layernorm_fwd_resident(RowArgs a) {
     if (a.exact) layernorm_fwd_resident_body<T, VEC, VPT, true>(a);
     else layernorm_fwd_resident_body<T, VEC, VPT, false>(a);
 }
@@ -360,7 +364,8 @@ __global__ void __launch_bounds__(kResidentMaxThreads) layernorm_bwd_resident(Ro
 }
 
 // The BFloat16 LayerNorm backward again for the common case (128-bit accesses, rows that fill every slot,
-// mean and rstd saved by the forward), arranged for occupancy: the general kernel above holds x, dy and gamma
+// mean and rstd saved by the forward), arranged for occupancy (the same arrangement for Float32 rows was measured
+// slower than the general kernel, 5490 against 5750 GB/s, and is not kept): the general kernel above holds x, dy and gamma
 // widened to Float32 beside its two sets of accumulators (127 registers, two blocks of 256 threads per SM),
 // and at that occupancy it waits on issue slots rather than on HBM.  Here x and dy stay packed as they were
 // loaded (eight registers per array instead of sixteen), gamma is re-read from L1, the dgamma / dbeta
@@ -849,6 +854,8 @@ Schedule plan_rows(RowOp op, int64_t n, int64_t rows, int64_t ld, int dtype, boo
     const int64_t nvec = n / epv;
     // the forward kernels hold one row-sized array: four vectors a thread over twice the threads keep more warps
     // resident than eight (measured on 4096-long Float32 rows); longer rows still take eight
+    // (BFloat16 rows keep 32 elements a thread: at 16, over twice the threads, the LayerNorm forward fell from 5018
+    // to 3999 GB/s)
     if (s.vec && max_vpt > 4 && (op == OP_SOFTMAX_FWD || op == OP_LN_FWD) && nvec <= 4 * kResidentMaxThreads) max_vpt = 4;
     const int tpr = next_pow2(ceil_div(nvec, max_vpt));
     if (tpr <= kResidentMaxThreads) {
@@ -1003,6 +1010,7 @@ RowKernel ln_bwd_kernel(int dtype, const Schedule &s, bool saved_stats) {
         if (s.vpt == 1) return layernorm_bwd_compact<1>;
         if (s.vpt == 2) return layernorm_bwd_compact<2>;
     }
+
     return pick<LayernormBwdResident>(dtype, s);
 }
 
