@@ -408,6 +408,23 @@ size_t tb200_rowreduce_source(const tb200_group_desc *desc, unsigned vector_inpu
                               char *buffer, size_t buffer_bytes);
 const char *tb200_rowreduce_compile_log(void);
 
+/* The same descriptors with every fold running over the rows -- the other, strided axis --
+ * instead of along them: the bias gradient, LayerNorm's weight gradients, any sum over the
+ * batch the planner forms.  The reference realises these as partial folds per block and a
+ * merge kernel (ext/cuTileExt/emit.jl:729-753, ext/cuTileExt/build.jl:654-696); here one
+ * generated kernel lets each thread own a column and fold the rows of its slab in order,
+ * and a second merges the slabs in order, so results repeat bit for bit.  Terms are
+ * evaluated per element as above (full, along, per-row and scalar inputs, the element's
+ * index along the row) but may not read row statistics; folds: sum, max, min, prod; every
+ * output is the value of one fold (from = 1), `n` elements of its dtype, rounded once.
+ * workspace: tb200_colreduce_workspace_bytes bytes, 16-byte aligned.  Compiled by NVRTC on
+ * first use and cached, as above (TB200_ERR_UNSUPPORTED without NVRTC). */
+size_t tb200_colreduce_workspace_bytes(const tb200_group_desc *desc);
+int tb200_colreduce_compile(const tb200_group_desc *desc);
+int tb200_colreduce_compiled(const tb200_group_desc *desc, const void *const *inputs, void *const *outputs,
+                             void *workspace, size_t workspace_bytes, void *stream);
+size_t tb200_colreduce_source(const tb200_group_desc *desc, char *buffer, size_t buffer_bytes);
+
 /* ---- pointwise maps and folds over other axes -------------------------------
  * These replace the generated `:pointwise` kernels (ext/cuTileExt/build.jl:3-10)
  * and the full / partial folds with their merge launches

@@ -433,6 +433,71 @@ def group_eval(desc, inputs, outputs, threads=1, wide=False):
     return outputs
 
 
+def group_eval_cols(desc, inputs, wide=False):
+    """A generic group whose folds run over the rows (the other axis), on the host: the term DAG evaluated per
+    element, then each column folded over its rows in order (the sequential floor of
+    src/Compiler/codegen/scalar.jl:200-256 for a fold over the second axis).  Float32 arithmetic, or Float64
+    with `wide`.  `inputs`: numpy arrays in the descriptor's order (uint16 for BFloat16; full inputs
+    [rows][ld]).  Returns one array of `n` values per output, in its storage type."""
+    F = np.float64 if wide else np.float32
+    n, rows = int(desc.n), int(desc.rows)
+    vals = []
+    for i in range(desc.n_inputs):
+        inp = desc.inputs[i]
+        a = np.asarray(inputs[i])
+        a = from_bf16(a) if inp.dtype == 1 else a
+        a = a.astype(F)
+        if inp.shape == 0:
+            a = a.reshape(rows, -1)[:, :n]
+        elif inp.shape == 1:
+            a = a.reshape(1, n)
+        elif inp.shape == 2:
+            a = a.reshape(rows, 1)
+        else:
+            a = a.reshape(1, 1)
+        vals.append(a)
+    unary = {11: lambda x: -x, 12: np.exp, 13: np.log, 14: np.tanh, 15: np.sqrt, 16: lambda x: F(1) / np.sqrt(x),
+             17: np.abs, 18: lambda x: x * x, 19: lambda x: F(1) / x, 20: lambda x: F(1) / (F(1) + np.exp(-x)),
+             23: lambda x: from_bf16(to_bf16(x.astype(np.float32))).astype(F)}
+    binary = {5: np.add, 6: np.subtract, 7: np.multiply, 8: np.divide, 9: np.maximum, 10: np.minimum}
+    t = []
+    with np.errstate(all="ignore"):
+        for k in range(desc.n_terms):
+            T = desc.terms[k]
+            if T.op == 0:
+                v = vals[T.a]
+            elif T.op == 1:
+                v = np.full((1, 1), T.imm, F)
+            elif T.op == 2:
+                v = np.arange(n, dtype=F).reshape(1, n)
+            elif T.op in binary:
+                v = binary[T.op](t[T.a], t[T.b]).astype(F)
+            elif T.op in unary:
+                v = unary[T.op](t[T.a]).astype(F)
+            elif T.op == 21:
+                v = (t[T.a].astype(np.float64) * t[T.b] + t[T.c]).astype(F) if not wide else t[T.a] * t[T.b] + t[T.c]
+            elif T.op == 22:
+                v = np.where(t[T.a] > 0, t[T.b], t[T.c]).astype(F)
+            else:
+                raise ValueError("oracle cannot run this group")
+            t.append(v)
+        folded = []
+        for j in range(desc.n_folds):
+            kind, term = desc.folds[j].kind, desc.folds[j].term
+            v = np.broadcast_to(t[term], (rows, n))
+            ident = {0: 0.0, 1: -np.inf, 2: np.inf, 3: 1.0}[kind]
+            step = {0: np.add, 1: np.maximum, 2: np.minimum, 3: np.multiply}[kind]
+            acc = np.full(n, ident, F)
+            for r in range(rows):
+                acc = step(acc, v[r]).astype(F)
+            folded.append(acc)
+    outs = []
+    for o in range(desc.n_outputs):
+        v = folded[desc.outputs[o].index].astype(np.float32)
+        outs.append(to_bf16(v) if desc.outputs[o].dtype == 1 else v)
+    return outs
+
+
 def deltanet_sequential(q, k, v, a, beta, threads=1):
     """The gated delta rule token by token in Float64 (examples/deltanet.jl:89-101).
     q, k [heads][T][dk], v [heads][T][dv] BFloat16 bits; a, beta [heads][T] float32.

@@ -638,6 +638,177 @@ unsigned vector_mask_in(const tb200_group_desc *d, const void *const *inputs, in
     return mask;
 }
 
+// ------------------------------------------------ folds over the other axis ----
+//
+// The same descriptor with every fold running over the rows (the strided axis) instead of along them: the
+// bias gradient, the LayerNorm weight gradients, any "sum over the batch" the planner forms
+// (ext/cuTileExt/emit.jl:729-753, build.jl:654-696: partial folds + a merge kernel).  One thread owns a column,
+// walks the rows of its slab in order evaluating the term DAG, and writes one partial per fold; a second kernel
+// merges the slabs in order.  Coalesced (a warp reads 32 neighbouring columns of a row), deterministic, and the
+// outputs are rounded once.  Folds: sum, max, min, prod; terms may not read row statistics.
+
+constexpr int kColThreads = 256;
+constexpr int kColSlabsMax = 128;
+
+struct ColParams {
+    const void *in[TB200_GROUP_MAX_INPUTS];
+    void *out[TB200_GROUP_MAX_OUTPUTS];
+    long long ld_in[TB200_GROUP_MAX_INPUTS];
+    float *partial;
+    long long rows;
+    int slabs;
+};
+
+int check_cols(const tb200_group_desc *d) {
+    if (!d) return TB200_ERR_NULL;
+    if (d->n < 0 || d->rows < 0 || d->n > (int64_t(1) << 30)) return TB200_ERR_SHAPE;
+    if (d->n_inputs < 0 || d->n_inputs > TB200_GROUP_MAX_INPUTS || d->n_terms < 1 || d->n_terms > TB200_GROUP_MAX_TERMS ||
+        d->n_folds < 1 || d->n_folds > TB200_GROUP_MAX_FOLDS || d->n_outputs < 1 || d->n_outputs > TB200_GROUP_MAX_OUTPUTS)
+        return TB200_ERR_SHAPE;
+    for (int i = 0; i < d->n_inputs; i++) {
+        const tb200_group_input &in = d->inputs[i];
+        if (in.dtype != TB200_F32 && in.dtype != TB200_BF16) return TB200_ERR_DTYPE;
+        if (in.shape < TB200_SHAPE_FULL || in.shape > TB200_SHAPE_SCALAR) return TB200_ERR_SHAPE;
+        if (in.shape == TB200_SHAPE_FULL && in.ld < d->n) return TB200_ERR_SHAPE;
+    }
+    for (int k = 0; k < d->n_terms; k++) {
+        const tb200_term &T = d->terms[k];
+        if (T.op < TB200_T_LOAD || T.op > TB200_T_ROUND_BF16) return TB200_ERR_UNSUPPORTED;
+        if (T.op == TB200_T_STAT || T.op == TB200_T_STAT2) return TB200_ERR_UNSUPPORTED;
+        if (T.op == TB200_T_LOAD && (T.a < 0 || T.a >= d->n_inputs)) return TB200_ERR_SHAPE;
+        const int ar = term_arity(T.op);
+        if ((ar > 0 && (T.a < 0 || T.a >= k)) || (ar > 1 && (T.b < 0 || T.b >= k)) || (ar > 2 && (T.c < 0 || T.c >= k)))
+            return TB200_ERR_SHAPE;
+    }
+    for (int j = 0; j < d->n_folds; j++) {
+        const int kind = d->folds[j].kind;
+        if (kind != TB200_FOLD_SUM && kind != TB200_FOLD_MAX && kind != TB200_FOLD_MIN && kind != TB200_FOLD_PROD)
+            return TB200_ERR_UNSUPPORTED;
+        if (d->folds[j].term < 0 || d->folds[j].term >= d->n_terms) return TB200_ERR_SHAPE;
+    }
+    for (int o = 0; o < d->n_outputs; o++) {
+        if (d->outputs[o].from != 1 || d->outputs[o].index < 0 || d->outputs[o].index >= d->n_folds) return TB200_ERR_UNSUPPORTED;
+        if (d->outputs[o].dtype != TB200_F32 && d->outputs[o].dtype != TB200_BF16) return TB200_ERR_DTYPE;
+    }
+    return TB200_OK;
+}
+
+std::string col_load(const tb200_group_desc &d, int i, const std::string &index) {
+    const std::string at = "[" + index + "]";
+    return d.inputs[i].dtype == TB200_BF16 ? "bf2f(((const u16 *)p.in[" + num(i) + "])" + at + ")"
+                                           : "((const float *)p.in[" + num(i) + "])" + at;
+}
+
+std::string generate_cols(const tb200_group_desc &d) {
+    Emitter E;
+    E.line(0, "typedef unsigned short u16; typedef unsigned int u32; typedef long long i64;");
+    E.line(0, "struct Params { const void *in[8]; void *out[8]; i64 ld_in[8]; float *partial; i64 rows; int slabs; };");
+    E.line(0, "#define NEG_INF __uint_as_float(0xff800000u)");
+    E.line(0, "#define POS_INF __uint_as_float(0x7f800000u)");
+    E.line(0, "#define LOG2E 1.4426950408889634f");
+    E.line(0, "static __device__ __forceinline__ float ex2(float x) { float y; asm(\"ex2.approx.ftz.f32 %0, %1;\" : \"=f\"(y) : \"f\"(x)); return y; }");
+    E.line(0, "static __device__ __forceinline__ float exp_diff(float a, float b) { return ex2(fmaf(a, LOG2E, -(b * LOG2E))); }");
+    E.line(0, "static __device__ __forceinline__ float bf2f(u32 h) { return __uint_as_float(h << 16); }");
+    E.line(0, "static __device__ __forceinline__ u32 f2bf(float f) { u16 r; asm(\"cvt.rn.bf16.f32 %0, %1;\" : \"=h\"(r) : \"f\"(f)); return r; }");
+    E.line(0, "constexpr int N = " + num(d.n) + ", NF = " + num(d.n_folds) + ";");
+    bool used[TB200_GROUP_MAX_INPUTS] = {};
+    for (int k = 0; k < d.n_terms; k++)
+        if (d.terms[k].op == TB200_T_LOAD) used[d.terms[k].a] = true;
+    // ---- partial folds
+    E.line(0, "extern \"C\" __global__ void __launch_bounds__(" + num(kColThreads) + ") tb200_cols(const Params p) {");
+    E.line(1, "const int i0 = blockIdx.x * " + num(kColThreads) + " + threadIdx.x, e = 0;");
+    E.line(1, "if (i0 >= N) return;");
+    E.line(1, "const i64 per = (p.rows + p.slabs - 1) / p.slabs, r0 = blockIdx.y * per, r1 = r0 + per < p.rows ? r0 + per : p.rows;");
+    for (int i = 0; i < d.n_inputs; i++) {
+        if (!used[i]) continue;
+        if (d.inputs[i].shape == TB200_SHAPE_ALONG) E.line(1, "const float c" + num(i) + "[1] = {" + col_load(d, i, "i0") + "};");
+        if (d.inputs[i].shape == TB200_SHAPE_SCALAR) E.line(1, "const float sc" + num(i) + " = " + col_load(d, i, "0") + ";");
+    }
+    for (int j = 0; j < d.n_folds; j++) E.line(1, "float f" + num(j) + " = " + fold_identity(d.folds[j].kind) + ";");
+    E.line(1, "for (i64 r = r0; r < r1; r++) {");
+    for (int i = 0; i < d.n_inputs; i++) {
+        if (!used[i]) continue;
+        if (d.inputs[i].shape == TB200_SHAPE_PER_ROW) E.line(2, "const float pr" + num(i) + " = " + col_load(d, i, "r") + ";");
+        if (d.inputs[i].shape == TB200_SHAPE_FULL)
+            E.line(2, "const float c" + num(i) + "[1] = {" + col_load(d, i, "r * p.ld_in[" + num(i) + "] + i0") + "};");
+    }
+    for (int k = 0; k < d.n_terms; k++) E.line(2, "const float t" + num(k) + " = " + term_expr(d, k, "") + ";");
+    for (int j = 0; j < d.n_folds; j++) emit_merge(E, 2, d.folds[j].kind, "f" + num(j), "", "", "t" + num(d.folds[j].term), "", "");
+    E.line(1, "}");
+    for (int j = 0; j < d.n_folds; j++)
+        E.line(1, "p.partial[((i64)blockIdx.y * NF + " + num(j) + ") * N + i0] = f" + num(j) + ";");
+    E.line(0, "}");
+    // ---- merge of the slabs, in order
+    E.line(0, "extern \"C\" __global__ void __launch_bounds__(" + num(kColThreads) + ") tb200_cols_merge(const Params p) {");
+    E.line(1, "const int i0 = blockIdx.x * " + num(kColThreads) + " + threadIdx.x;");
+    E.line(1, "if (i0 >= N) return;");
+    for (int j = 0; j < d.n_folds; j++) {
+        E.line(1, "float f" + num(j) + " = " + fold_identity(d.folds[j].kind) + ";");
+        E.line(1, "for (int s = 0; s < p.slabs; s++) {");
+        E.line(2, "const float o = p.partial[((i64)s * NF + " + num(j) + ") * N + i0];");
+        emit_merge(E, 2, d.folds[j].kind, "f" + num(j), "", "", "o", "", "");
+        E.line(1, "}");
+    }
+    for (int o = 0; o < d.n_outputs; o++) {
+        const std::string v = "f" + num(d.outputs[o].index);
+        if (d.outputs[o].dtype == TB200_BF16) E.line(1, "((u16 *)p.out[" + num(o) + "])[i0] = (u16)f2bf(" + v + ");");
+        else E.line(1, "((float *)p.out[" + num(o) + "])[i0] = " + v + ";");
+    }
+    E.line(0, "}");
+    return E.s;
+}
+
+struct CompiledCols {
+    std::vector<char> cubin;
+    CUfunction fold[64] = {}, merge[64] = {};
+};
+std::map<std::string, CompiledCols *> g_col_cache;   // guarded by g_cache_lock
+
+int compile_cols(const tb200_group_desc *d, CompiledCols **out) {
+    int st = check_cols(d);
+    if (st) return st;
+    std::string key = "cols:" + cache_key(d, 0, 0);
+    for (int i = 0; i < d->n_inputs; i++) key.push_back(static_cast<char>('0' + d->inputs[i].shape));
+    std::lock_guard<std::mutex> hold(g_cache_lock);
+    auto it = g_col_cache.find(key);
+    if (it != g_col_cache.end()) {
+        *out = it->second;
+        return TB200_OK;
+    }
+    Nvrtc &n = nvrtc();
+    if (!n.ok) return TB200_ERR_UNSUPPORTED;
+    const std::string source = generate_cols(*d);
+    void *prog = nullptr;
+    if (n.create(&prog, source.c_str(), "tb200_cols.cu", 0, nullptr, nullptr) != 0) return TB200_ERR_UNSUPPORTED;
+    const char *options[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-default-device", "--disable-warnings"};
+    const int rc = n.compile(prog, 4, options);
+    size_t log_bytes = 0;
+    n.log_size(prog, &log_bytes);
+    g_log.assign(log_bytes, '\0');
+    if (log_bytes) n.log(prog, &g_log[0]);
+    if (rc != 0) {
+        n.destroy(&prog);
+        return TB200_ERR_UNSUPPORTED;
+    }
+    size_t bytes = 0;
+    n.cubin_size(prog, &bytes);
+    CompiledCols *c = new CompiledCols();
+    c->cubin.resize(bytes);
+    n.cubin(prog, c->cubin.data());
+    n.destroy(&prog);
+    g_col_cache[key] = c;
+    *out = c;
+    return TB200_OK;
+}
+
+int col_slabs(const tb200_group_desc *d, int sms) {
+    const int64_t col_blocks = ceil_div(d->n, kColThreads);
+    int64_t slabs = ceil_div(static_cast<int64_t>(sms) * 8, col_blocks);
+    if (slabs > kColSlabsMax) slabs = kColSlabsMax;
+    if (slabs > d->rows) slabs = d->rows;
+    return static_cast<int>(slabs < 1 ? 1 : slabs);
+}
+
 }  // namespace
 }  // namespace tb200
 
@@ -724,6 +895,82 @@ extern "C" int tb200_rowreduce_compiled(const tb200_group_desc *d, const void *c
     void *args[] = {&P};
     if (drv->launch(c->function[dev.device], static_cast<unsigned>(blocks < cap ? blocks : cap), 1, 1, kThreads, 1, 1, 0,
                     static_cast<CUstream>(stream_), args, nullptr) != CUDA_SUCCESS)
+        return TB200_ERR_CUDA;
+    return TB200_OK;
+}
+
+// ---- folds over the other axis
+
+extern "C" size_t tb200_colreduce_workspace_bytes(const tb200_group_desc *d) {
+    if (check_cols(d) != TB200_OK) return 0;
+    return static_cast<size_t>(kColSlabsMax) * d->n_folds * static_cast<size_t>(d->n) * sizeof(float);
+}
+
+extern "C" int tb200_colreduce_compile(const tb200_group_desc *d) {
+    if (!d) return TB200_ERR_NULL;
+    CompiledCols *c = nullptr;
+    return compile_cols(d, &c);
+}
+
+extern "C" size_t tb200_colreduce_source(const tb200_group_desc *d, char *buffer, size_t buffer_bytes) {
+    if (check_cols(d) != TB200_OK) return 0;
+    const std::string source = generate_cols(*d);
+    if (buffer && buffer_bytes) {
+        const size_t take = source.size() < buffer_bytes - 1 ? source.size() : buffer_bytes - 1;
+        memcpy(buffer, source.data(), take);
+        buffer[take] = '\0';
+    }
+    return source.size() + 1;
+}
+
+extern "C" int tb200_colreduce_compiled(const tb200_group_desc *d, const void *const *inputs, void *const *outputs,
+                                        void *workspace, size_t workspace_bytes, void *stream_) {
+    int st = check_cols(d);
+    if (st) return st;
+    if (d->n == 0) return TB200_OK;
+    if (!outputs || (d->n_inputs > 0 && !inputs)) return TB200_ERR_NULL;
+    ColParams P{};
+    for (int i = 0; i < d->n_inputs; i++) {
+        if (!inputs[i]) return TB200_ERR_NULL;
+        if (!aligned_to(inputs[i], dtype_size(d->inputs[i].dtype))) return TB200_ERR_ALIGN;
+        P.in[i] = inputs[i];
+        P.ld_in[i] = d->inputs[i].ld;
+    }
+    for (int o = 0; o < d->n_outputs; o++) {
+        if (!outputs[o]) return TB200_ERR_NULL;
+        if (!aligned_to(outputs[o], dtype_size(d->outputs[o].dtype))) return TB200_ERR_ALIGN;
+        P.out[o] = outputs[o];
+    }
+    if (!workspace || workspace_bytes < tb200_colreduce_workspace_bytes(d) || !aligned_to(workspace, 16)) return TB200_ERR_WORKSPACE;
+    CompiledCols *c = nullptr;
+    if ((st = compile_cols(d, &c))) return st;
+    DeviceInfo dev;
+    if ((st = current_device(&dev))) return st;
+    Driver *drv = nullptr;
+    if ((st = driver(&drv))) return st;
+    {
+        std::lock_guard<std::mutex> hold(g_cache_lock);
+        if (!c->fold[dev.device]) {
+            TB200_CUDA(cudaFree(nullptr));   // the runtime's context is current before the driver is used
+            CUmodule module = nullptr;
+            if (drv->module_load(&module, c->cubin.data()) != CUDA_SUCCESS) return TB200_ERR_CUDA;
+            CUfunction fold = nullptr, merge = nullptr;
+            if (drv->get_function(&fold, module, "tb200_cols") != CUDA_SUCCESS) return TB200_ERR_CUDA;
+            if (drv->get_function(&merge, module, "tb200_cols_merge") != CUDA_SUCCESS) return TB200_ERR_CUDA;
+            c->merge[dev.device] = merge;
+            c->fold[dev.device] = fold;
+        }
+    }
+    P.partial = static_cast<float *>(workspace);
+    P.rows = d->rows;
+    P.slabs = col_slabs(d, dev.sms);   // rows == 0: one slab of no rows, every fold's identity
+    const unsigned col_blocks = static_cast<unsigned>(ceil_div(d->n, kColThreads));
+    void *args[] = {&P};
+    if (drv->launch(c->fold[dev.device], col_blocks, static_cast<unsigned>(P.slabs), 1, kColThreads, 1, 1, 0,
+                    static_cast<CUstream>(stream_), args, nullptr) != CUDA_SUCCESS)
+        return TB200_ERR_CUDA;
+    if (drv->launch(c->merge[dev.device], col_blocks, 1, 1, kColThreads, 1, 1, 0, static_cast<CUstream>(stream_), args,
+                    nullptr) != CUDA_SUCCESS)
         return TB200_ERR_CUDA;
     return TB200_OK;
 }

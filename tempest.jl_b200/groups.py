@@ -180,3 +180,45 @@ def row_extrema(n, rows, eltype="Float32"):
     for kind in ("max", "min", "sum", "prod"):
         g.output_stat(g.fold(kind, x))
     return g
+
+
+# ---- groups whose folds run over the rows (the other axis): `lib.colreduce_compiled` ------------------------
+#
+# The same builder; `bytes()` of such a group counts `n` values per fold output (use `column_bytes`).
+
+def column_bytes(g):
+    size = {L.F32: 4, L.BF16: 2}
+    extent = {0: g.n * g.rows, 1: g.n, 2: g.rows, 3: 1}
+    return (sum(extent[shape] * size[dtype] for shape, dtype, _ in g.inputs) +
+            sum(g.n * size[dtype] for _, _, dtype, _ in g.outputs))
+
+
+def bias_gradient(n, rows, eltype="Float32"):
+    """db[i] = sum over rows of g[i, row]: `sum(g; dims = 2)`, the pullback of a broadcast bias
+    (test/fixtures/programs.jl:19-26 under withgradient)."""
+    g = Group(n, rows)
+    g.output_stat(g.fold("sum", g.load(g.input("full", eltype))), eltype)
+    return g
+
+
+def layernorm_weight_gradients(n, rows, eltype="Float32"):
+    """dgamma[i] = sum over rows of g * (x - mean) * rstd and dbeta[i] = sum over rows of g, with the forward's
+    saved mean and rstd: the two folds over the other axis of the LayerNorm pullback
+    (ext/cuTileExt/emit.jl:729-753)."""
+    g = Group(n, rows)
+    x, dy = g.load(g.input("full", eltype)), g.load(g.input("full", eltype))
+    mean, rstd = g.load(g.input("per_row", "Float32")), g.load(g.input("per_row", "Float32"))
+    xh = g.mul(g.sub(x, mean), rstd)
+    g.output_stat(g.fold("sum", g.mul(dy, xh)), eltype)
+    g.output_stat(g.fold("sum", dy), eltype)
+    return g
+
+
+def column_extrema(n, rows, eltype="Float32"):
+    """maximum, minimum and sum of |x| over the rows, per column."""
+    g = Group(n, rows)
+    x = g.load(g.input("full", eltype))
+    g.output_stat(g.fold("max", x))
+    g.output_stat(g.fold("min", x))
+    g.output_stat(g.fold("sum", g.abs(x)))
+    return g

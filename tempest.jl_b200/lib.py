@@ -111,6 +111,10 @@ SIGNATURES = {
     "tb200_rowreduce_compiled": (_i, [ctypes.POINTER(GroupDesc), ctypes.POINTER(_p), ctypes.POINTER(_p), _p]),
     "tb200_rowreduce_source": (_sz, [ctypes.POINTER(GroupDesc), ctypes.c_uint, ctypes.c_uint, ctypes.c_char_p, _sz]),
     "tb200_rowreduce_compile_log": (ctypes.c_char_p, []),
+    "tb200_colreduce_workspace_bytes": (_sz, [ctypes.POINTER(GroupDesc)]),
+    "tb200_colreduce_compile": (_i, [ctypes.POINTER(GroupDesc)]),
+    "tb200_colreduce_compiled": (_i, [ctypes.POINTER(GroupDesc), ctypes.POINTER(_p), ctypes.POINTER(_p), _p, _sz, _p]),
+    "tb200_colreduce_source": (_sz, [ctypes.POINTER(GroupDesc), ctypes.c_char_p, _sz]),
     "tb200_deltanet_bwd_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_bwd": (_i, [ctypes.POINTER(DeltanetDesc)] + [_p] * 12 + [_sz, _p]),
     "tb200_workspace_clear": (_i, [_p, _sz, _p]),
@@ -372,6 +376,32 @@ def rowreduce_compiled(desc, inputs, outputs, stream=0):
     ins = (_p * max(len(inputs), 1))(*inputs)
     outs = (_p * max(len(outputs), 1))(*outputs)
     check("tb200_rowreduce_compiled", load().tb200_rowreduce_compiled(ctypes.byref(desc), ins, outs, stream or None))
+
+
+def colreduce_workspace_bytes(desc):
+    return load().tb200_colreduce_workspace_bytes(ctypes.byref(desc))
+
+
+def colreduce_compile(desc):
+    """Compiles a group whose folds run over the rows (needs NVRTC, no device)."""
+    check("tb200_colreduce_compile", load().tb200_colreduce_compile(ctypes.byref(desc)))
+
+
+def colreduce_source(desc):
+    need = load().tb200_colreduce_source(ctypes.byref(desc), None, 0)
+    if not need:
+        return ""
+    buf = ctypes.create_string_buffer(need)
+    load().tb200_colreduce_source(ctypes.byref(desc), buf, need)
+    return buf.value.decode()
+
+
+def colreduce_compiled(desc, inputs, outputs, workspace=0, workspace_bytes=0, stream=0):
+    """A group whose folds run over the rows: outputs[j] receives `n` values of fold outputs[j].index."""
+    ins = (_p * max(len(inputs), 1))(*inputs)
+    outs = (_p * max(len(outputs), 1))(*outputs)
+    check("tb200_colreduce_compiled", load().tb200_colreduce_compiled(ctypes.byref(desc), ins, outs, workspace or None,
+                                                                      workspace_bytes, stream or None))
 
 
 def attn_mask(doc_start=0, kv_len=0, q_stride=(0, 0, 0), kv_stride=(0, 0, 0)):

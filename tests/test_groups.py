@@ -120,3 +120,31 @@ def test_generated_kernels_compile(pkg):
     bad = G.softmax(16, 2).desc()
     bad.terms[0].op = 99
     assert L.rowreduce_compile(bad) == -7 and L.rowreduce_source(bad) == ""
+
+
+def test_column_groups_compile_and_refusals(pkg, oracle):
+    """Groups whose folds run over the rows: the descriptor compiles (NVRTC, no device), the source names both
+    kernels, the oracle's evaluation of the bias gradient is the column sum, and what the form does not take
+    is refused with a status."""
+    G, L = pkg.groups, pkg.lib
+    for make in (G.bias_gradient, G.layernorm_weight_gradients, G.column_extrema):
+        for eltype in ("Float32", "BFloat16"):
+            d = make(300, 77, eltype).desc()
+            assert L.colreduce_workspace_bytes(d) >= 300 * 4
+            L.colreduce_compile(d)
+            src = L.colreduce_source(d)
+            assert "tb200_cols(" in src and "tb200_cols_merge(" in src
+    x = oracle.normal((77, 300), 5)
+    (db,) = oracle.group_eval_cols(G.bias_gradient(300, 77).desc(), [x])
+    assert np.allclose(db, x.astype(np.float64).sum(axis=0), rtol=0, atol=1e-4)
+    # a fold along the row's own statistic, or a full-shaped output, is not a column group
+    g = G.softmax(300, 77)
+    with pytest.raises(L.TB200Error) as e:
+        L.colreduce_compile(g.desc())
+    assert e.value.status == -7
+    g = G.Group(300, 77)
+    g.output_stat(g.fold("logsumexp", g.load(g.input("full"))))
+    with pytest.raises(L.TB200Error) as e:
+        L.colreduce_compile(g.desc())
+    assert e.value.status == -7
+    assert L.colreduce_workspace_bytes(g.desc()) == 0

@@ -174,3 +174,77 @@ def test_through_the_generator(pkg, cuda, oracle):
         torch.cuda.synchronize()
         assert np.abs(y.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
         assert torch.equal(y, y2)
+
+
+# ---- folds over the other axis ---------------------------------------------------------------------------
+
+def run_columns(pkg, torch, oracle, group, inputs):
+    L = pkg.lib
+    d = group.desc()
+    dev_in = [torch.from_numpy(np.ascontiguousarray(a).view(np.int16) if a.dtype == np.uint16 else np.ascontiguousarray(a)).cuda()
+              for a in inputs]
+    dev_out = [torch.zeros(group.n, device="cuda", dtype=torch.float32 if dtype == 0 else torch.int16)
+               for _, _, dtype, _ in group.outputs]
+    need = L.colreduce_workspace_bytes(d)
+    ws = torch.empty(max(need, 16), device="cuda", dtype=torch.uint8)
+    L.colreduce_compiled(d, [t.data_ptr() for t in dev_in], [t.data_ptr() for t in dev_out], ws.data_ptr(), need,
+                         torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    got = [t.cpu().numpy().view(np.uint16) if t.dtype == torch.int16 else t.cpu().numpy() for t in dev_out]
+    return got, oracle.group_eval_cols(d, inputs), oracle.group_eval_cols(d, inputs, wide=True)
+
+
+def agree_columns(oracle, got, floor, wide, scale):
+    """Float32 outputs: within 1e-5 of the Float64 evaluation relative to `scale` (the size of what was summed),
+    or no further from it than twice the sequential Float32 floor is; BFloat16 outputs: one rounding on top."""
+    for g, f, w in zip(got, floor, wide):
+        if g.dtype == np.uint16:
+            g, f, w = (oracle.from_bf16(a).astype(np.float64) for a in (g, f, w))
+            assert (np.abs(g - w) <= 2.0 ** -7 * np.maximum(np.abs(w), scale * 1e-2) + 1e-30).all()
+        else:
+            g, f, w = (a.astype(np.float64) for a in (g, f, w))
+            assert (np.abs(g - w) <= np.maximum(1e-5 * scale, 2.0 * np.abs(f - w)) + 1e-30).all()
+
+
+@pytest.mark.parametrize("rows,n", [(700, 256), (40, 9000), (3000, 100), (300, 512), (1, 5), (4099, 33)])
+@pytest.mark.parametrize("eltype", ["Float32", "BFloat16"])
+def test_column_groups(pkg, cuda, oracle, rows, n, eltype):
+    """The bias gradient, LayerNorm's weight gradients and per-column extrema against the oracle's sequential
+    fold over the rows, on the transposes of the reference's fold shapes (test/cuda/folds.jl:16-25)."""
+    G = pkg.groups
+    cast = (lambda a: oracle.to_bf16(a)) if eltype == "BFloat16" else (lambda a: a)
+    x, dy = oracle.normal((rows, n), 11 + n), oracle.normal((rows, n), 12 + n)
+    mean = x.mean(axis=1).astype(np.float32)
+    rstd = (1.0 / np.sqrt(x.var(axis=1) + 1e-5)).astype(np.float32)
+    root = float(np.sqrt(rows))
+    got, floor, wide = run_columns(pkg, cuda, oracle, G.bias_gradient(n, rows, eltype), [cast(dy)])
+    agree_columns(oracle, got, floor, wide, root)
+    got, floor, wide = run_columns(pkg, cuda, oracle, G.layernorm_weight_gradients(n, rows, eltype),
+                                   [cast(x), cast(dy), mean, rstd])
+    agree_columns(oracle, got, floor, wide, root)
+    got, floor, wide = run_columns(pkg, cuda, oracle, G.column_extrema(n, rows, eltype), [cast(x)])
+    assert np.array_equal(got[0], floor[0]) and np.array_equal(got[1], floor[1])   # extrema are exact
+    agree_columns(oracle, got[2:], floor[2:], wide[2:], float(rows))
+
+
+def test_column_groups_agree_with_the_named_kernels(pkg, cuda, oracle):
+    """dgamma and dbeta of the generated column group against the named LayerNorm backward on the same operands,
+    and a group over no rows gives every fold's identity."""
+    torch, L, G = cuda, pkg.lib, pkg.groups
+    rows, n = 512, 1024
+    x, dy, w = oracle.normal((rows, n), 1), oracle.normal((rows, n), 2), oracle.normal((n,), 3)
+    y, mean, rstd = oracle.layernorm_fwd(x, w, np.zeros(n, np.float32))
+    got, _, _ = run_columns(pkg, torch, oracle, G.layernorm_weight_gradients(n, rows), [x, dy, mean, rstd])
+    _, dw, db = oracle.layernorm_bwd_f64(x, w, dy)
+    assert np.abs(got[0] - dw).max() <= 1e-5 * np.sqrt(rows) * 4 and np.abs(got[1] - db).max() <= 1e-5 * np.sqrt(rows) * 4
+    g = G.column_extrema(8, 0)
+    d = g.desc()
+    outs = [torch.zeros(8, device="cuda") for _ in range(3)]
+    need = L.colreduce_workspace_bytes(d)
+    ws = torch.empty(max(need, 16), device="cuda", dtype=torch.uint8)
+    L.colreduce_compiled(d, [ws.data_ptr()], [o.data_ptr() for o in outs], ws.data_ptr(), need)
+    torch.cuda.synchronize()
+    assert torch.isinf(outs[0]).all() and (outs[0] < 0).all() and (outs[1] > 0).all() and (outs[2] == 0).all()
+    with pytest.raises(L.TB200Error) as e:   # no workspace
+        L.colreduce_compiled(G.bias_gradient(8, 4).desc(), [ws.data_ptr()], [outs[0].data_ptr()], 0, 0)
+    assert e.value.status == -5
