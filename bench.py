@@ -462,7 +462,16 @@ def run_also(torch, dist, pkg, world, rank):
         gms = clock(lambda: L.rowreduce_compiled(lnd, [xb.data_ptr(), wb.data_ptr(), bb.data_ptr()], [yb.data_ptr()], stream), 10)
         out["compiled_layernorm_bf16_4096x65536"] = {"ms": round(gms, 4), "algorithmic_GB/s": round(ln.bytes() / gms / 1e6, 1),
                                                      "frac_of_measured_hbm_peak": round(ln.bytes() / gms / 1e6 / hbm, 4)}
-        del xg, yg, xb, yb
+        # a group that folds the other axis: the bias gradient of a (4096, 65536) BFloat16 activation gradient
+        bg = G.bias_gradient(n, rows, "BFloat16")
+        bgd = bg.desc()
+        cneed = L.colreduce_workspace_bytes(bgd)
+        cws2 = torch.empty(max(cneed, 16), dtype=torch.uint8, device="cuda")
+        gms = clock(lambda: L.colreduce_compiled(bgd, [xb.data_ptr()], [wb.data_ptr()], cws2.data_ptr(), cneed, stream), 10)
+        cb = bg.bytes()
+        out["compiled_bias_gradient_bf16_4096x65536"] = {"ms": round(gms, 4), "algorithmic_GB/s": round(cb / gms / 1e6, 1),
+                                                         "frac_of_measured_hbm_peak": round(cb / gms / 1e6 / hbm, 4)}
+        del xg, yg, xb, yb, cws2
         # its pullback at the same size (forward recomputed inside)
         gq, gk, gv = (torch.empty(Hn, T, 128, device="cuda", dtype=torch.bfloat16) for _ in range(3))
         ga, gb = torch.empty(Hn, T, device="cuda"), torch.empty(Hn, T, device="cuda")

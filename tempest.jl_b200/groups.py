@@ -24,8 +24,10 @@ DTYPES = {"Float32": L.F32, "BFloat16": L.BF16}
 class Group:
     """A map -> fold group over (n, rows).  Methods return the index of the term / fold / input they add."""
 
-    def __init__(self, n, rows):
-        self.n, self.rows = int(n), int(rows)
+    def __init__(self, n, rows, across=False):
+        """`across`: the folds run over the rows (the other axis) and each yields `n` values -- the groups of
+        `lib.colreduce_compiled`; otherwise along each row, one value per row."""
+        self.n, self.rows, self.across = int(n), int(rows), bool(across)
         self.inputs, self.terms, self.folds, self.outputs = [], [], [], []
         self._level = []   # first phase in which a term can be evaluated
 
@@ -103,7 +105,8 @@ class Group:
         size = {L.F32: 4, L.BF16: 2}
         extent = {0: self.n * self.rows, 1: self.n, 2: self.rows, 3: 1}
         total = sum(extent[shape] * size[dtype] for shape, dtype, _ in self.inputs)
-        total += sum((self.n * self.rows if source == 0 else self.rows) * size[dtype]
+        per_fold = self.n if self.across else self.rows
+        total += sum((self.n * self.rows if source == 0 else per_fold) * size[dtype]
                      for source, _, dtype, _ in self.outputs)
         return total
 
@@ -184,19 +187,13 @@ def row_extrema(n, rows, eltype="Float32"):
 
 # ---- groups whose folds run over the rows (the other axis): `lib.colreduce_compiled` ------------------------
 #
-# The same builder; `bytes()` of such a group counts `n` values per fold output (use `column_bytes`).
-
-def column_bytes(g):
-    size = {L.F32: 4, L.BF16: 2}
-    extent = {0: g.n * g.rows, 1: g.n, 2: g.rows, 3: 1}
-    return (sum(extent[shape] * size[dtype] for shape, dtype, _ in g.inputs) +
-            sum(g.n * size[dtype] for _, _, dtype, _ in g.outputs))
+# The same builder with `across = True`.
 
 
 def bias_gradient(n, rows, eltype="Float32"):
     """db[i] = sum over rows of g[i, row]: `sum(g; dims = 2)`, the pullback of a broadcast bias
     (test/fixtures/programs.jl:19-26 under withgradient)."""
-    g = Group(n, rows)
+    g = Group(n, rows, across=True)
     g.output_stat(g.fold("sum", g.load(g.input("full", eltype))), eltype)
     return g
 
@@ -205,7 +202,7 @@ def layernorm_weight_gradients(n, rows, eltype="Float32"):
     """dgamma[i] = sum over rows of g * (x - mean) * rstd and dbeta[i] = sum over rows of g, with the forward's
     saved mean and rstd: the two folds over the other axis of the LayerNorm pullback
     (ext/cuTileExt/emit.jl:729-753)."""
-    g = Group(n, rows)
+    g = Group(n, rows, across=True)
     x, dy = g.load(g.input("full", eltype)), g.load(g.input("full", eltype))
     mean, rstd = g.load(g.input("per_row", "Float32")), g.load(g.input("per_row", "Float32"))
     xh = g.mul(g.sub(x, mean), rstd)
@@ -216,7 +213,7 @@ def layernorm_weight_gradients(n, rows, eltype="Float32"):
 
 def column_extrema(n, rows, eltype="Float32"):
     """maximum, minimum and sum of |x| over the rows, per column."""
-    g = Group(n, rows)
+    g = Group(n, rows, across=True)
     x = g.load(g.input("full", eltype))
     g.output_stat(g.fold("max", x))
     g.output_stat(g.fold("min", x))

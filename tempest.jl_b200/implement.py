@@ -463,6 +463,26 @@ class GroupLaunch:
         run(self.desc, [address(b) for _, b in self.inputs], [address(b) for _, b in self.outputs], _torch_stream())
 
 
+@dataclass(frozen=True)
+class ColumnClaim:
+    """What the generator offers for a group whose folds run over the rows: partial folds per row slab
+    (one thread per column) and an ordered merge, two launches, compiled by NVRTC."""
+    launches: int = 2
+
+
+class ColumnLaunch(GroupLaunch):
+    """The launch of a group that folds the other axis; holds the scratch for the slabs' partial folds."""
+
+    def __init__(self, group, inputs, outputs, workspace, workspace_bytes):
+        super().__init__(group, inputs, outputs, compiled=True)
+        self.workspace, self.workspace_bytes = workspace, workspace_bytes
+
+    def __call__(self):
+        address = lambda b: b.data_ptr() if hasattr(b, "data_ptr") else int(b)  # noqa: E731
+        lib.colreduce_compiled(self.desc, [address(b) for _, b in self.inputs], [address(b) for _, b in self.outputs],
+                               address(self.workspace), self.workspace_bytes, _torch_stream())
+
+
 class B200Generator:
     """`<: Implementation` for row groups: claims every group whose descriptor the library accepts."""
 
@@ -471,6 +491,12 @@ class B200Generator:
             desc = group.desc()
         except ValueError:
             return ()                                  # too large for one descriptor: decline
+        if getattr(group, "across", False):            # folds over the other axis: the compiled form or nothing
+            try:
+                lib.colreduce_compile(desc)
+            except lib.TB200Error:
+                return ()
+            return (ColumnClaim(),)
         if lib.rowreduce_generic_check(desc) != 0:
             return ()
         threads = 8
@@ -488,6 +514,8 @@ class B200Generator:
     def estimate(self, claim: RowClaim, target: Target, group):
         """One launch moving the group's bytes once; the interpreter also pays for every term of every element
         (`applied` in the reference's Work, src/Compiler/Implement/Implement.jl:61-82)."""
+        if isinstance(claim, ColumnClaim):
+            return [Work(bytes=group.bytes(), blocks=(group.n + 255) // 256, launches=claim.launches, applied=0)]
         applied = 0 if claim.compiled else len(group.terms) * claim.phases
         return [Work(bytes=group.bytes(), blocks=group.rows, launches=1, applied=applied)]
 
@@ -510,6 +538,12 @@ class B200Generator:
             outs = [(v, buffers[v]) for v in range(k, k + len(group.outputs))]
         if len(ins) != len(group.inputs) or len(outs) != len(group.outputs):
             raise ValueError("build_claim needs one buffer per input and per output")
+        if isinstance(claim, ColumnClaim):
+            need = lib.colreduce_workspace_bytes(group.desc())
+            resources = resources if resources is not None else Resources()
+            return (ColumnLaunch(group, ins, outs, resources.workspace(need), need),
+                    f"B200 compiled columns, {group.n} columns over {group.rows} rows, {len(group.terms)} terms, "
+                    f"{len(group.folds)} folds, slabs + ordered merge")
         if claim.compiled:
             status = lib.rowreduce_compile(group.desc())
             if status != 0:

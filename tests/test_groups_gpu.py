@@ -248,3 +248,26 @@ def test_column_groups_agree_with_the_named_kernels(pkg, cuda, oracle):
     with pytest.raises(L.TB200Error) as e:   # no workspace
         L.colreduce_compiled(G.bias_gradient(8, 4).desc(), [ws.data_ptr()], [outs[0].data_ptr()], 0, 0)
     assert e.value.status == -5
+
+
+def test_column_group_through_the_generator(pkg, cuda, oracle):
+    """A group marked `across` is claimed as a column group: two launches, scratch from the executable's
+    resources, repointable like any other launch."""
+    torch, I, G = cuda, pkg.implement, pkg.groups
+    n, rows = 300, 1000
+    g = G.bias_gradient(n, rows)
+    gen, target = I.B200Generator(), I.Target()
+    (claim,) = gen.claims(target, g)
+    assert isinstance(claim, I.ColumnClaim)
+    (work,) = gen.estimate(claim, target, g)
+    assert work.launches == 2 and work.bytes == n * rows * 4 + n * 4
+    x = torch.randn(rows, n, device="cuda")
+    db, db2 = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    launch, text = gen.build_claim(claim, target, g, {0: x, 1: db})
+    assert "columns" in text
+    launch()
+    launch.repoint(1, db2)()
+    torch.cuda.synchronize()
+    want = x.double().sum(dim=0)
+    assert (db.double() - want).abs().max().item() <= 1e-5 * rows ** 0.5 * 4
+    assert torch.equal(db, db2)

@@ -115,3 +115,9 @@ def test_generator_claims_groups(pkg):
     assert launch.repoints() and "3 sweeps" in text
     launch.repoint(3, 128)
     assert launch.outputs == [(3, 128)] and launch.inputs[0] == (0, 16)
+    # a group that folds the other axis: one claim, two launches, n values per fold
+    cols = G.layernorm_weight_gradients(4096, 65536, "BFloat16")
+    (cc,) = gen.claims(t, cols)
+    assert isinstance(cc, I.ColumnClaim)
+    (w,) = gen.estimate(cc, t, cols)
+    assert w.launches == 2 and w.bytes == 2 * 4096 * 65536 * 2 + 2 * 65536 * 4 + 2 * 4096 * 2
