@@ -648,7 +648,8 @@ unsigned vector_mask_in(const tb200_group_desc *d, const void *const *inputs, in
 // outputs are rounded once.  Folds: sum, max, min, prod; terms may not read row statistics.
 
 constexpr int kColThreads = 256;
-constexpr int kColSlabsMax = 128;
+constexpr int kColSlabsMax = 512;
+constexpr int kColBlocksWanted = 1536;   // about ten blocks of 256 threads per SM
 
 struct ColParams {
     const void *in[TB200_GROUP_MAX_INPUTS];
@@ -699,7 +700,31 @@ std::string col_load(const tb200_group_desc &d, int i, const std::string &index)
                                            : "((const float *)p.in[" + num(i) + "])" + at;
 }
 
-std::string generate_cols(const tb200_group_desc &d) {
+// declares `float c<i>[V]` holding V consecutive columns of input i starting at element `index`
+void col_load_chunk(Emitter &E, int ind, const tb200_group_desc &d, int i, const std::string &index, int V, bool streaming) {
+    const std::string c = "c" + num(i);
+    if (V == 1) {
+        E.line(ind, "const float " + c + "[1] = {" + col_load(d, i, index) + "};");
+        return;
+    }
+    const std::string ld = streaming ? "__ldcs" : "__ldg";
+    const std::string q = "q" + num(i);
+    if (d.inputs[i].dtype == TB200_BF16 && V == 8) {
+        E.line(ind, "const uint4 " + q + " = " + ld + "((const uint4 *)((const u16 *)p.in[" + num(i) + "] + " + index + "));");
+        E.line(ind, "const float " + c + "[8] = {bf_lo(" + q + ".x), bf_hi(" + q + ".x), bf_lo(" + q + ".y), bf_hi(" + q + ".y), bf_lo(" + q +
+                        ".z), bf_hi(" + q + ".z), bf_lo(" + q + ".w), bf_hi(" + q + ".w)};");
+    } else if (d.inputs[i].dtype == TB200_BF16) {
+        E.line(ind, "const uint2 q" + num(i) + " = " + ld + "((const uint2 *)((const u16 *)p.in[" + num(i) + "] + " + index + "));");
+        E.line(ind, "const float " + c + "[4] = {bf_lo(q" + num(i) + ".x), bf_hi(q" + num(i) + ".x), bf_lo(q" + num(i) + ".y), bf_hi(q" + num(i) + ".y)};");
+    } else {
+        E.line(ind, "const float4 q" + num(i) + " = " + ld + "((const float4 *)((const float *)p.in[" + num(i) + "] + " + index + "));");
+        E.line(ind, "const float " + c + "[4] = {q" + num(i) + ".x, q" + num(i) + ".y, q" + num(i) + ".z, q" + num(i) + ".w};");
+    }
+}
+
+// V = 4 (8 when every array input is BFloat16): a thread owns that many neighbouring columns (128-bit accesses
+// of the narrowest type; needs n, the row pitches and the addresses to allow it); V = 1: one column, any alignment
+std::string generate_cols(const tb200_group_desc &d, int V) {
     Emitter E;
     E.line(0, "typedef unsigned short u16; typedef unsigned int u32; typedef long long i64;");
     E.line(0, "struct Params { const void *in[8]; void *out[8]; i64 ld_in[8]; float *partial; i64 rows; int slabs; };");
@@ -709,34 +734,43 @@ std::string generate_cols(const tb200_group_desc &d) {
     E.line(0, "static __device__ __forceinline__ float ex2(float x) { float y; asm(\"ex2.approx.ftz.f32 %0, %1;\" : \"=f\"(y) : \"f\"(x)); return y; }");
     E.line(0, "static __device__ __forceinline__ float exp_diff(float a, float b) { return ex2(fmaf(a, LOG2E, -(b * LOG2E))); }");
     E.line(0, "static __device__ __forceinline__ float bf2f(u32 h) { return __uint_as_float(h << 16); }");
+    E.line(0, "static __device__ __forceinline__ float bf_lo(u32 w) { return __uint_as_float(w << 16); }");
+    E.line(0, "static __device__ __forceinline__ float bf_hi(u32 w) { return __uint_as_float(w & 0xffff0000u); }");
     E.line(0, "static __device__ __forceinline__ u32 f2bf(float f) { u16 r; asm(\"cvt.rn.bf16.f32 %0, %1;\" : \"=h\"(r) : \"f\"(f)); return r; }");
-    E.line(0, "constexpr int N = " + num(d.n) + ", NF = " + num(d.n_folds) + ";");
+    E.line(0, "constexpr int N = " + num(d.n) + ", NF = " + num(d.n_folds) + ", V = " + num(V) + ";");
     bool used[TB200_GROUP_MAX_INPUTS] = {};
     for (int k = 0; k < d.n_terms; k++)
         if (d.terms[k].op == TB200_T_LOAD) used[d.terms[k].a] = true;
     // ---- partial folds
     E.line(0, "extern \"C\" __global__ void __launch_bounds__(" + num(kColThreads) + ") tb200_cols(const Params p) {");
-    E.line(1, "const int i0 = blockIdx.x * " + num(kColThreads) + " + threadIdx.x, e = 0;");
+    E.line(1, "const int i0 = (blockIdx.x * " + num(kColThreads) + " + threadIdx.x) * V;");
     E.line(1, "if (i0 >= N) return;");
     E.line(1, "const i64 per = (p.rows + p.slabs - 1) / p.slabs, r0 = blockIdx.y * per, r1 = r0 + per < p.rows ? r0 + per : p.rows;");
     for (int i = 0; i < d.n_inputs; i++) {
         if (!used[i]) continue;
-        if (d.inputs[i].shape == TB200_SHAPE_ALONG) E.line(1, "const float c" + num(i) + "[1] = {" + col_load(d, i, "i0") + "};");
+        if (d.inputs[i].shape == TB200_SHAPE_ALONG) col_load_chunk(E, 1, d, i, "i0", V, false);
         if (d.inputs[i].shape == TB200_SHAPE_SCALAR) E.line(1, "const float sc" + num(i) + " = " + col_load(d, i, "0") + ";");
     }
-    for (int j = 0; j < d.n_folds; j++) E.line(1, "float f" + num(j) + " = " + fold_identity(d.folds[j].kind) + ";");
+    for (int j = 0; j < d.n_folds; j++) {
+        E.line(1, "float f" + num(j) + "[V];");
+        E.line(1, "for (int e = 0; e < V; e++) f" + num(j) + "[e] = " + fold_identity(d.folds[j].kind) + ";");
+    }
+    E.line(1, "#pragma unroll 4");
     E.line(1, "for (i64 r = r0; r < r1; r++) {");
     for (int i = 0; i < d.n_inputs; i++) {
         if (!used[i]) continue;
         if (d.inputs[i].shape == TB200_SHAPE_PER_ROW) E.line(2, "const float pr" + num(i) + " = " + col_load(d, i, "r") + ";");
-        if (d.inputs[i].shape == TB200_SHAPE_FULL)
-            E.line(2, "const float c" + num(i) + "[1] = {" + col_load(d, i, "r * p.ld_in[" + num(i) + "] + i0") + "};");
+        if (d.inputs[i].shape == TB200_SHAPE_FULL) col_load_chunk(E, 2, d, i, "r * p.ld_in[" + num(i) + "] + i0", V, true);
     }
-    for (int k = 0; k < d.n_terms; k++) E.line(2, "const float t" + num(k) + " = " + term_expr(d, k, "") + ";");
-    for (int j = 0; j < d.n_folds; j++) emit_merge(E, 2, d.folds[j].kind, "f" + num(j), "", "", "t" + num(d.folds[j].term), "", "");
+    E.line(2, "#pragma unroll");
+    E.line(2, "for (int e = 0; e < V; e++) {");
+    for (int k = 0; k < d.n_terms; k++) E.line(3, "const float t" + num(k) + " = " + term_expr(d, k, "") + ";");
+    for (int j = 0; j < d.n_folds; j++)
+        emit_merge(E, 3, d.folds[j].kind, "f" + num(j) + "[e]", "", "", "t" + num(d.folds[j].term), "", "");
+    E.line(2, "}");
     E.line(1, "}");
     for (int j = 0; j < d.n_folds; j++)
-        E.line(1, "p.partial[((i64)blockIdx.y * NF + " + num(j) + ") * N + i0] = f" + num(j) + ";");
+        E.line(1, "for (int e = 0; e < V; e++) p.partial[((i64)blockIdx.y * NF + " + num(j) + ") * N + i0 + e] = f" + num(j) + "[e];");
     E.line(0, "}");
     // ---- merge of the slabs, in order
     E.line(0, "extern \"C\" __global__ void __launch_bounds__(" + num(kColThreads) + ") tb200_cols_merge(const Params p) {");
@@ -764,10 +798,10 @@ struct CompiledCols {
 };
 std::map<std::string, CompiledCols *> g_col_cache;   // guarded by g_cache_lock
 
-int compile_cols(const tb200_group_desc *d, CompiledCols **out) {
+int compile_cols(const tb200_group_desc *d, int V, CompiledCols **out) {
     int st = check_cols(d);
     if (st) return st;
-    std::string key = "cols:" + cache_key(d, 0, 0);
+    std::string key = "cols" + num(V) + ":" + cache_key(d, 0, 0);
     for (int i = 0; i < d->n_inputs; i++) key.push_back(static_cast<char>('0' + d->inputs[i].shape));
     std::lock_guard<std::mutex> hold(g_cache_lock);
     auto it = g_col_cache.find(key);
@@ -777,7 +811,7 @@ int compile_cols(const tb200_group_desc *d, CompiledCols **out) {
     }
     Nvrtc &n = nvrtc();
     if (!n.ok) return TB200_ERR_UNSUPPORTED;
-    const std::string source = generate_cols(*d);
+    const std::string source = generate_cols(*d, V);
     void *prog = nullptr;
     if (n.create(&prog, source.c_str(), "tb200_cols.cu", 0, nullptr, nullptr) != 0) return TB200_ERR_UNSUPPORTED;
     const char *options[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-default-device", "--disable-warnings"};
@@ -801,9 +835,23 @@ int compile_cols(const tb200_group_desc *d, CompiledCols **out) {
     return TB200_OK;
 }
 
-int col_slabs(const tb200_group_desc *d, int sms) {
-    const int64_t col_blocks = ceil_div(d->n, kColThreads);
-    int64_t slabs = ceil_div(static_cast<int64_t>(sms) * 8, col_blocks);
+// columns a thread owns when the extents allow vectors (the addresses are checked at launch)
+int col_width(const tb200_group_desc *d) {
+    int V = 8;
+    for (int i = 0; i < d->n_inputs; i++)
+        if ((d->inputs[i].shape == TB200_SHAPE_FULL || d->inputs[i].shape == TB200_SHAPE_ALONG) && d->inputs[i].dtype == TB200_F32)
+            V = 4;
+    if (d->n % V != 0) return 1;
+    for (int i = 0; i < d->n_inputs; i++)
+        if (d->inputs[i].shape == TB200_SHAPE_FULL && d->inputs[i].ld % V != 0) return 1;
+    return V;
+}
+
+// row slabs: enough blocks to fill the GPU whatever the row length (a function of the extents only, so that
+// the workspace can be sized without a device)
+int col_slabs(const tb200_group_desc *d, int V) {
+    const int64_t col_blocks = ceil_div(d->n, static_cast<int64_t>(kColThreads) * V);
+    int64_t slabs = ceil_div(kColBlocksWanted, col_blocks);
     if (slabs > kColSlabsMax) slabs = kColSlabsMax;
     if (slabs > d->rows) slabs = d->rows;
     return static_cast<int>(slabs < 1 ? 1 : slabs);
@@ -903,18 +951,23 @@ extern "C" int tb200_rowreduce_compiled(const tb200_group_desc *d, const void *c
 
 extern "C" size_t tb200_colreduce_workspace_bytes(const tb200_group_desc *d) {
     if (check_cols(d) != TB200_OK) return 0;
-    return static_cast<size_t>(kColSlabsMax) * d->n_folds * static_cast<size_t>(d->n) * sizeof(float);
+    // the widest form has the fewest column blocks, hence the most slabs
+    tb200_group_desc any_rows = *d;
+    any_rows.rows = kColSlabsMax;
+    return static_cast<size_t>(col_slabs(&any_rows, 8)) * d->n_folds * static_cast<size_t>(d->n) * sizeof(float);
 }
 
 extern "C" int tb200_colreduce_compile(const tb200_group_desc *d) {
     if (!d) return TB200_ERR_NULL;
     CompiledCols *c = nullptr;
-    return compile_cols(d, &c);
+    int st = compile_cols(d, 1, &c);
+    if (st == TB200_OK && col_width(d) > 1) st = compile_cols(d, col_width(d), &c);
+    return st;
 }
 
 extern "C" size_t tb200_colreduce_source(const tb200_group_desc *d, char *buffer, size_t buffer_bytes) {
     if (check_cols(d) != TB200_OK) return 0;
-    const std::string source = generate_cols(*d);
+    const std::string source = generate_cols(*d, col_width(d));
     if (buffer && buffer_bytes) {
         const size_t take = source.size() < buffer_bytes - 1 ? source.size() : buffer_bytes - 1;
         memcpy(buffer, source.data(), take);
@@ -942,8 +995,14 @@ extern "C" int tb200_colreduce_compiled(const tb200_group_desc *d, const void *c
         P.out[o] = outputs[o];
     }
     if (!workspace || workspace_bytes < tb200_colreduce_workspace_bytes(d) || !aligned_to(workspace, 16)) return TB200_ERR_WORKSPACE;
+    int V = col_width(d);
+    for (int i = 0; i < d->n_inputs && V > 1; i++) {
+        const int shape = d->inputs[i].shape;
+        if ((shape == TB200_SHAPE_FULL || shape == TB200_SHAPE_ALONG) && !aligned_to(inputs[i], V * dtype_size(d->inputs[i].dtype)))
+            V = 1;
+    }
     CompiledCols *c = nullptr;
-    if ((st = compile_cols(d, &c))) return st;
+    if ((st = compile_cols(d, V, &c))) return st;
     DeviceInfo dev;
     if ((st = current_device(&dev))) return st;
     Driver *drv = nullptr;
@@ -963,13 +1022,14 @@ extern "C" int tb200_colreduce_compiled(const tb200_group_desc *d, const void *c
     }
     P.partial = static_cast<float *>(workspace);
     P.rows = d->rows;
-    P.slabs = col_slabs(d, dev.sms);   // rows == 0: one slab of no rows, every fold's identity
-    const unsigned col_blocks = static_cast<unsigned>(ceil_div(d->n, kColThreads));
+    P.slabs = col_slabs(d, V);   // rows == 0: one slab of no rows, every fold's identity
+    const unsigned col_blocks = static_cast<unsigned>(ceil_div(d->n, static_cast<int64_t>(kColThreads) * V));
+    const unsigned merge_blocks = static_cast<unsigned>(ceil_div(d->n, kColThreads));
     void *args[] = {&P};
     if (drv->launch(c->fold[dev.device], col_blocks, static_cast<unsigned>(P.slabs), 1, kColThreads, 1, 1, 0,
                     static_cast<CUstream>(stream_), args, nullptr) != CUDA_SUCCESS)
         return TB200_ERR_CUDA;
-    if (drv->launch(c->merge[dev.device], col_blocks, 1, 1, kColThreads, 1, 1, 0, static_cast<CUstream>(stream_), args,
+    if (drv->launch(c->merge[dev.device], merge_blocks, 1, 1, kColThreads, 1, 1, 0, static_cast<CUstream>(stream_), args,
                     nullptr) != CUDA_SUCCESS)
         return TB200_ERR_CUDA;
     return TB200_OK;
