@@ -568,6 +568,23 @@ def run_profile_case(args):
                 L.rowreduce_compiled(group.desc(), [t.data_ptr() for t in ins], [t.data_ptr() for t in outs], stream)
         group, ins, outs = cases[0]
         L.rowreduce_generic(group.desc(), [t.data_ptr() for t in ins], [t.data_ptr() for t in outs], stream)
+    elif case == "columns":
+        # groups that fold the other axis, 16384 rows of 4096: LayerNorm's weight gradients (Float32) and the
+        # bias gradient (BFloat16), each as partial folds per slab + ordered merge
+        G = pkg.groups
+        n, rows = 4096, 16384
+        x, dy = torch.randn(rows, n, device="cuda"), torch.randn(rows, n, device="cuda")
+        mean, rstd = torch.randn(rows, device="cuda"), torch.rand(rows, device="cuda") + 0.5
+        o1, o2 = torch.empty(n, device="cuda"), torch.empty(n, device="cuda")
+        xb, ob = x.bfloat16(), torch.empty(n, device="cuda", dtype=torch.bfloat16)
+        cases = [(G.layernorm_weight_gradients(n, rows), [x, dy, mean, rstd], [o1, o2]),
+                 (G.bias_gradient(n, rows, "BFloat16"), [xb], [ob])]
+        need = max(L.colreduce_workspace_bytes(g.desc()) for g, _, _ in cases)
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        for _ in range(2):
+            for group, ins, outs in cases:
+                L.colreduce_compiled(group.desc(), [t.data_ptr() for t in ins], [t.data_ptr() for t in outs], ws.data_ptr(),
+                                     need, stream)
     else:
         raise SystemExit(f"unknown profile case {case}")
     torch.cuda.synchronize()
@@ -733,7 +750,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the side measurements (MLP step, GEMM)")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "attention", "deltanet", "groups"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "attention", "deltanet", "groups", "columns"],
                     help="run one small case of a kernel family only (for ncu captures)")
     args = ap.parse_args()
     if args.profile_case:
