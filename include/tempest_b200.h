@@ -413,7 +413,7 @@ const char *tb200_rowreduce_compile_log(void);
  * batch the planner forms.  The reference realises these as partial folds per block and a
  * merge kernel (ext/cuTileExt/emit.jl:729-753, ext/cuTileExt/build.jl:654-696); here one
  * generated kernel lets each thread own a column and fold the rows of its slab in order,
- * and a second merges the slabs in order, so results repeat bit for bit.  Terms are
+ * and a second merges the slabs in a fixed order, so results repeat bit for bit.  Terms are
  * evaluated per element as above (full, along, per-row and scalar inputs, the element's
  * index along the row) but may not read row statistics; folds: sum, max, min, prod; every
  * output is the value of one fold (from = 1), `n` elements of its dtype, rounded once.

@@ -772,14 +772,28 @@ std::string generate_cols(const tb200_group_desc &d, int V) {
     for (int j = 0; j < d.n_folds; j++)
         E.line(1, "for (int e = 0; e < V; e++) p.partial[((i64)blockIdx.y * NF + " + num(j) + ") * N + i0 + e] = f" + num(j) + "[e];");
     E.line(0, "}");
-    // ---- merge of the slabs, in order
+    // ---- merge of the slabs in a fixed order: 32 columns x 8 lanes a block; lane l folds slabs l, l + 8, ... in
+    // order, then the eight lane results are folded in lane order
     E.line(0, "extern \"C\" __global__ void __launch_bounds__(" + num(kColThreads) + ") tb200_cols_merge(const Params p) {");
-    E.line(1, "const int i0 = blockIdx.x * " + num(kColThreads) + " + threadIdx.x;");
-    E.line(1, "if (i0 >= N) return;");
+    E.line(1, "__shared__ float sm[NF][8][33];");
+    E.line(1, "const int c = threadIdx.x & 31, l = threadIdx.x >> 5, i0 = blockIdx.x * 32 + c;");
     for (int j = 0; j < d.n_folds; j++) {
         E.line(1, "float f" + num(j) + " = " + fold_identity(d.folds[j].kind) + ";");
-        E.line(1, "for (int s = 0; s < p.slabs; s++) {");
-        E.line(2, "const float o = p.partial[((i64)s * NF + " + num(j) + ") * N + i0];");
+        E.line(1, "if (i0 < N) {");
+        E.line(2, "#pragma unroll 4");
+        E.line(2, "for (int s = l; s < p.slabs; s += 8) {");
+        E.line(3, "const float o = p.partial[((i64)s * NF + " + num(j) + ") * N + i0];");
+        emit_merge(E, 3, d.folds[j].kind, "f" + num(j), "", "", "o", "", "");
+        E.line(2, "}");
+        E.line(1, "}");
+        E.line(1, "sm[" + num(j) + "][l][c] = f" + num(j) + ";");
+    }
+    E.line(1, "__syncthreads();");
+    E.line(1, "if (l != 0 || i0 >= N) return;");
+    for (int j = 0; j < d.n_folds; j++) {
+        E.line(1, "f" + num(j) + " = sm[" + num(j) + "][0][c];");
+        E.line(1, "for (int k = 1; k < 8; k++) {");
+        E.line(2, "const float o = sm[" + num(j) + "][k][c];");
         emit_merge(E, 2, d.folds[j].kind, "f" + num(j), "", "", "o", "", "");
         E.line(1, "}");
     }
@@ -1024,7 +1038,7 @@ extern "C" int tb200_colreduce_compiled(const tb200_group_desc *d, const void *c
     P.rows = d->rows;
     P.slabs = col_slabs(d, V);   // rows == 0: one slab of no rows, every fold's identity
     const unsigned col_blocks = static_cast<unsigned>(ceil_div(d->n, static_cast<int64_t>(kColThreads) * V));
-    const unsigned merge_blocks = static_cast<unsigned>(ceil_div(d->n, kColThreads));
+    const unsigned merge_blocks = static_cast<unsigned>(ceil_div(d->n, 32));
     void *args[] = {&P};
     if (drv->launch(c->fold[dev.device], col_blocks, static_cast<unsigned>(P.slabs), 1, kColThreads, 1, 1, 0,
                     static_cast<CUstream>(stream_), args, nullptr) != CUDA_SUCCESS)
