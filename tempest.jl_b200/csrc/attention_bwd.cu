@@ -3,7 +3,8 @@
 // spelling, where dQ is a second fold of its own: ext/cuTileExt/build.jl:295-318, docs/src/cuda.md:64-75).
 //
 //   stats      delta[m] = sum_d dO[d,m] o[d,m] (o as stored in BFloat16) and lse * log2(e), both
-//              re-laid out [batch][head][query] so that consecutive queries are contiguous
+//              re-laid out [batch][head][query] (rows padded to whole steps) so that consecutive queries are
+//              contiguous
 //   dK, dV     one item = 128 keys of one (batch, key/value head); steps of 128 queries (of every query
 //              head of the group):  S' = K Q', dP' = V dO'  ->  P' = exp2(S' c - lse), dS' = P' (dP' - delta)
 //              ->  dK += dS' Q,  dV += P' dO
@@ -11,9 +12,11 @@
 //              S = Q K', dP = dO V'  ->  dS = P (dP - delta)  ->  dQ += dS K
 //
 // Both run one warp-specialised pipeline.  One thread issues TMA loads: the item's 128-row operands once,
-// the steps' operands through two 2-stage rings (one per operand, so that each tile is released by the
-// last product that reads it).  One thread issues tcgen05.mma, every product 128 x 128 x 128, in the order
+// the steps' operands through two rings (one per operand, so that each tile is released by the last product
+// that reads it; see Rings for their depths), and for dK/dV the step's per-query statistics by a bulk copy
+// on the dO tile's barrier.  One thread issues tcgen05.mma, every product 128 x 128 x 128, in the order
 //      S(t+1),  dK(t), dV(t),  dP(t+1),  S(t+2), ...
+// (dQ, which keeps one accumulator and so has room for two dP buffers, issues dP(t+1) with S(t+1)).
 // Eight warps own the item's 128 rows (one tensor-memory lane each), four per half of the step's 128
 // columns.  A row thread reads its 64 scores, releases the score buffer (so the next scores are computed
 // while it works), forms P while the gradient products of the step before run, then reads its 64 dP
@@ -22,6 +25,7 @@
 // their [position][feature] layout, as MN-major B operands.  Only the read-modify-write of dP sits
 // between two products, and the next scores fill that gap.  MMAs of one CTA run in issue order, so dP(t+1)
 // cannot overwrite P / dS of step t early.  Accumulators stay in tensor memory for the whole item.
+// Work is walked (batch, head)-major with a heavy and a light tile paired per CTA (see Steps).
 // Tensor memory: S | dP | two 128-column accumulators = 512 columns.
 // No load uses cluster multicast.  Every barrier wait is bounded.
 #include <cuda.h>
