@@ -7,8 +7,9 @@
 // weights are rounded to BFloat16 for the second product, the output is rounded once
 // (test/fixtures/operations.jl:21-76 and docs/src/cuda.md:40-46 of the reference).
 //
-// One persistent CTA per SM works through (batch, head, 128-query tile) items, heaviest (most key
-// tiles under the causal mask) first.  Warp roles:
+// One persistent CTA per SM works through (batch, head, query tile) items; with more than one query tile the
+// pair kernel further down takes two tiles at a time and walks them (batch, head)-major, a heavy and a light
+// pair back to back, so that concurrent CTAs share few heads' K and V in L2.  Warp roles of the one-tile kernel:
 //   warp 0      TMA loads: Q once per item, K and V tiles of 128 keys through 2-stage rings
 //   warp 1      tcgen05.mma: S = Q K^T into one of two tensor-memory score buffers, then
 //               O += P V (P from shared memory, V as an MN-major operand straight from its
