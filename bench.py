@@ -188,6 +188,12 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device (the backend has no CPU fallback)")
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL's own account of what it runs (is the reduction done in the switch, which algorithm and protocol
+        # its tuner picks) goes to a file per rank; rank 0's is summarised in the line's `dp.nccl`
+        os.environ.setdefault("NCCL_DEBUG", "INFO")
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT,TUNING")
+        os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(tempfile.gettempdir(), f"tb200_nccl_{os.getpid()}.log")
+                              if rank == 0 else os.devnull)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = entry.load_package()
     pkg.lib.load()
@@ -250,7 +256,7 @@ def run_gpu(args):
     also = None
     if not args.no_also:
         try:
-            also = run_also(torch, dist, pkg, world, rank)
+            also = run_also(torch, dist, pkg, world, rank, only=None if args.also == "all" else args.also)
         except Exception as err:  # the headline line must survive a failure of the side measurements
             also = {"error": repr(err)[:300]}
 
@@ -272,12 +278,148 @@ def run_gpu(args):
                    "element_types": ["f32", "bf16"], "sharding": f"rows x{world}, no collective",
                    "l2": "inputs larger than L2 (each operand 0.5-1 GiB vs 126 MB)"},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-        "gpu_launches": wl.kernels_per_step * args.steps, "kernels": kernels, "also": also,
+        "gpu_launches": wl.kernels_per_step * args.steps, "kernels": kernels,
+        "dp": (also or {}).get("dp") if isinstance(also, dict) else None, "also": also,
     }
     print(json.dumps(line))
 
 
-def run_also(torch, dist, pkg, world, rank):
+def nccl_notes(path):
+    """What NCCL said it would run (its INFO lines, written to `path` by rank 0): whether NVLS (reduction
+    in the switch) came up, and the algorithm / protocol lines of its tuner."""
+    notes = {"nvls": None, "lines": []}
+    try:
+        with open(path, errors="replace") as f:
+            text = f.read()
+    except OSError:
+        return notes
+    notes["nvls"] = ("NVLS" in text) and ("NVLS multicast support is available" in text or "Connected NVLS" in text
+                                         or "NVLS comm" in text)
+    seen = []
+    for line in text.splitlines():
+        if " Algo " in line or "Connected NVLS" in line or "NVLS multicast" in line:
+            tail = line.split("NCCL INFO", 1)[-1].strip()
+            if tail not in seen:
+                seen.append(tail)
+    notes["lines"] = seen[:16]
+    return notes
+
+
+def run_mlp(torch, dist, pkg, world, rank, timed, tensor_peak):
+    """BASELINE.json configs[2]: the MLP training step (1024-4096-4096-4096-1024, GELU(tanh), bias, BFloat16, MSE,
+    SGD 1e-3, batch 8192).  One GPU: the whole step replayed as one CUDA graph.  N GPUs: the global batch of
+    8192 split N ways (strong scaling) and 8192 samples per replica (weak scaling), gradients summed by NCCL
+    all-reduces of three flat buckets; before anything is timed one data-parallel step is checked against the
+    whole-batch step on one GPU (`dp_parity`)."""
+    sizes, gb = (1024, 4096, 4096, 4096, 1024), 8192
+    L = pkg.lib
+    flops = 2 * gb * (1024 * 4096 + 2 * 4096 * 4096 + 4096 * 1024) * 3 - 2 * gb * 1024 * 4096
+    gen = torch.Generator(device="cuda").manual_seed(SEED + 40)
+    gx = torch.randn(gb, sizes[0], device="cuda", generator=gen).bfloat16()     # the same global batch on every rank
+    gy = torch.randn(gb, sizes[-1], device="cuda", generator=gen).bfloat16()
+
+    # ---- one GPU, whole batch: the figure every efficiency below is taken against (every rank runs it)
+    one = pkg.mlp.MLPStep(torch, sizes, gb, 1e-3, seed=1)
+    start_w = one.params.clone()
+    one.step(gx, gy)
+    torch.cuda.synchronize()
+    one_loss, one_w = float(one.loss.item()), one.params.clone()
+    ms1 = timed(one.capture(gx, gy), 20, 5)
+    out = {"mlp_train": {"steps_per_s": round(1000.0 / ms1, 1), "ms_per_step": round(ms1, 4), "n_gpus": 1,
+                         "global_batch": gb, "TFLOP/s": round(flops / ms1 / 1e9, 1),
+                         "frac_of_measured_bf16_peak": round(flops / ms1 / 1e9 / tensor_peak, 4),
+                         "launch": "the whole step as one CUDA graph", "device_error": L.device_error()}}
+    del one
+    if world == 1:
+        return out
+
+    # ---- data parallel, strong: parity first
+    per = gb // world
+    lo, hi = pkg.mlp.shard_rows(gb, rank, world)
+    x, y = gx[lo:hi].contiguous(), gy[lo:hi].contiguous()
+    step = pkg.mlp.MLPStep(torch, sizes, per, 1e-3, world=world, global_batch=gb, seed=1)
+    assert torch.equal(step.params.view(torch.int16), _relayout(torch, pkg, start_w, sizes, step).view(torch.int16))
+    step.step(x, y)
+    torch.cuda.synchronize()
+    loss = step.loss.clone()
+    dist.all_reduce(loss)                                   # the replicas' shares of the global mean
+    ref = step.params.clone()
+    dist.broadcast(ref, src=0)
+    apart = (step.params.view(torch.int16).int() - ref.view(torch.int16).int()).abs().max().float()
+    dist.all_reduce(apart, op=dist.ReduceOp.MAX)
+    want = _relayout(torch, pkg, one_w, sizes, step)
+    # against the whole-batch step: sums in another order and gradients rounded to BFloat16 before the exchange,
+    # so weights may land one BFloat16 step apart where the update crosses a rounding boundary
+    steps = lambda t: torch.where(t.view(torch.int16) < 0, -(t.view(torch.int16).int() & 0x7fff), t.view(torch.int16).int())  # noqa: E731
+    ulps = (steps(step.params) - steps(want)).abs()
+    parity = {"replicas_bit_equal": bool(apart.item() == 0.0),
+              "loss_all_reduced": float(loss.item()), "loss_one_gpu_whole_batch": one_loss,
+              "loss_rel_diff": abs(float(loss.item()) - one_loss) / abs(one_loss),
+              "weights_max_bf16_steps_from_one_gpu": int(ulps.max().item()),
+              "weights_frac_differing_from_one_gpu": round(float((ulps != 0).float().mean().item()), 6),
+              "device_error": L.device_error()}
+    parity["ok"] = bool(parity["replicas_bit_equal"] and parity["loss_rel_diff"] <= 2e-3 and
+                        parity["weights_max_bf16_steps_from_one_gpu"] <= 1 and parity["device_error"] == 0)
+    del ref, want, ulps, one_w, start_w
+
+    # ---- the exchange alone: the floor under any overlap
+    def exchange_alone(buckets):
+        def run():
+            for b in buckets:
+                dist.all_reduce(b)
+        return run
+    alone = {"all_buckets_ms": round(timed(exchange_alone(step.bucket), 20, 5), 4),
+             "bucket_bytes": [b.numel() * 2 for b in step.bucket]}
+    alone["per_bucket_ms"] = [round(timed(exchange_alone([b]), 20, 5), 4) for b in step.bucket]
+    step.grads.zero_()
+
+    # both launch forms are timed and the faster one is reported (both figures stay in the line)
+    forms = {"ms_per_step_eager": round(timed(lambda: step.step(x, y), 20, 5), 4),
+             "ms_per_step_stretch_graphs": round(timed(step.capture_segments(x, y), 20, 5), 4)}
+    ms = min(forms.values())
+    out["mlp_train_strong"] = {"steps_per_s": round(1000.0 / ms, 1), "ms_per_step": round(ms, 4), "n_gpus": world,
+                               "global_batch": gb, "scaling": "strong", "TFLOP/s": round(flops / ms / 1e9, 1),
+                               "gradient_allreduce_bytes": sum(alone["bucket_bytes"]), **forms,
+                               "device_error": L.device_error()}
+    del step, x, y
+    # ---- weak: 8192 samples per replica, the same 84 MB exchange behind a whole single-GPU step
+    wstep = pkg.mlp.MLPStep(torch, sizes, gb, 1e-3, world=world, global_batch=gb * world, seed=1)
+    wstep.step(gx, gy)
+    wforms = {"ms_per_step_eager": round(timed(lambda: wstep.step(gx, gy), 20, 5), 4),
+              "ms_per_step_stretch_graphs": round(timed(wstep.capture_segments(gx, gy), 20, 5), 4)}
+    wms = min(wforms.values())
+    out["mlp_train_weak"] = {"steps_per_s": round(1000.0 / wms, 1), "ms_per_step": round(wms, 4), "n_gpus": world,
+                             "global_batch": gb * world, "scaling": "weak",
+                             "samples_per_s": round(gb * world * 1000.0 / wms, 1),
+                             "TFLOP/s": round(flops * world / wms / 1e9, 1), **wforms,
+                             "device_error": L.device_error()}
+    del wstep
+    out["dp"] = {
+        "n_gpus": world, "one_gpu_ms_per_step": round(ms1, 4),
+        "strong_ms_per_step": round(ms, 4), "strong_steps_per_s": round(1000.0 / ms, 1),
+        "strong_efficiency": round(ms1 / (world * ms), 4),
+        "weak_ms_per_step": round(wms, 4), "weak_efficiency": round(ms1 / wms, 4),
+        "efficiency_against": "the one-GPU whole-batch step (one CUDA graph) timed in this same run on every rank, max over ranks",
+        "launch": "the faster of: every kernel launched eagerly | one CUDA graph per stretch between two gradient "
+                  "exchanges; NCCL all-reduces always eager on a side stream",
+        "exchange_alone": alone, "dp_parity": parity,
+        "nccl": nccl_notes(os.environ.get("NCCL_DEBUG_FILE", "")) if rank == 0 else None,
+    }
+    return out
+
+
+def _relayout(torch, pkg, flat, sizes, step):
+    """The parameters of a single-GPU step's flat buffer (layers in order) copied into the layout of `step`."""
+    order, offsets, total, _ = pkg.mlp.flat_layout(list(sizes), True)
+    out = torch.zeros_like(step.params)
+    for i in range(len(sizes) - 1):
+        nw, nb = sizes[i] * sizes[i + 1], sizes[i + 1]
+        out[step.offsets[i][0]: step.offsets[i][0] + nw] = flat[offsets[i][0]: offsets[i][0] + nw]
+        out[step.offsets[i][1]: step.offsets[i][1] + nb] = flat[offsets[i][1]: offsets[i][1] + nb]
+    return out
+
+
+def run_also(torch, dist, pkg, world, rank, only=None):
     """Side measurements of the other kernel families on the same box (not the headline value):
     the MLP training step of BASELINE.json configs[2] (1024-4096-4096-4096-1024, GELU(tanh), bias,
     BFloat16, MSE, SGD 1e-3), global batch 8192 sharded over the ranks with an NCCL all-reduce of the
@@ -310,47 +452,9 @@ def run_also(torch, dist, pkg, world, rank):
             ms = float(t.item())
         return ms
 
-    step = pkg.mlp.MLPStep(torch, sizes, per, 1e-3, world=world, global_batch=gb, seed=1)
-    x = torch.randn(per, sizes[0], device="cuda").bfloat16()
-    y = torch.randn(per, sizes[-1], device="cuda").bfloat16()
-    step.step(x, y)                      # every launch once, outside any capture
-    # one GPU: the whole step replayed as one CUDA graph, as Tempest replays a compiled call; with
-    # replicas either every kernel is launched eagerly or the stretches between two gradient exchanges
-    # are graphs; the all-reduces stay outside any graph, launched eagerly on a side stream
-    if world == 1:
-        ms = timed(step.capture(x, y), 20, 5)
-        forms = {}
-    else:   # both launch forms are timed and the faster one is reported (both figures stay in the line)
-        forms = {"ms_per_step_eager": round(timed(lambda: step.step(x, y), 20, 5), 4),
-                 "ms_per_step_stretch_graphs": round(timed(step.capture_segments(x, y), 20, 5), 4)}
-        ms = min(forms.values())
-    flops = 2 * gb * (1024 * 4096 + 2 * 4096 * 4096 + 4096 * 1024) * 3 - 2 * gb * 1024 * 4096
-    out = {"mlp_train": {"steps_per_s": round(1000.0 / ms, 1), "ms_per_step": round(ms, 4), "n_gpus": world,
-                         "global_batch": gb, "scaling": "strong", "TFLOP/s": round(flops / ms / 1e9, 1),
-                         "frac_of_measured_bf16_peak_per_gpu": round(flops / ms / 1e9 / world / tensor_peak, 4),
-                         "gradient_allreduce_bytes": sum(b.numel() * 2 for b in step.bucket) if world > 1 else 0,
-                         **forms, "device_error": L.device_error()}}
-    if world > 1:
-        # the same step with the per-replica batch held at 8192 (weak scaling): the gradient exchange is the
-        # same 84 MB while each replica has the whole single-GPU step to hide it behind
-        del step, x, y
-        wstep = pkg.mlp.MLPStep(torch, sizes, gb, 1e-3, world=world, global_batch=gb * world, seed=1)
-        wx = torch.randn(gb, sizes[0], device="cuda").bfloat16()
-        wy = torch.randn(gb, sizes[-1], device="cuda").bfloat16()
-        # both launch forms are timed and the faster one is reported (both figures stay in the line)
-        wstep.step(wx, wy)
-        wms_eager = timed(lambda: wstep.step(wx, wy), 20, 5)
-        wms_graphs = timed(wstep.capture_segments(wx, wy), 20, 5)
-        wms = min(wms_eager, wms_graphs)
-        out["mlp_train_weak"] = {"steps_per_s": round(1000.0 / wms, 1), "ms_per_step": round(wms, 4), "n_gpus": world,
-                                 "global_batch": gb * world, "scaling": "weak",
-                                 "samples_per_s": round(gb * world * 1000.0 / wms, 1),
-                                 "TFLOP/s": round(flops * world / wms / 1e9, 1),
-                                 "frac_of_measured_bf16_peak_per_gpu": round(flops / wms / 1e9 / tensor_peak, 4),
-                                 "ms_per_step_eager": round(wms_eager, 4), "ms_per_step_stretch_graphs": round(wms_graphs, 4),
-                                 "launch": "the faster of: every kernel launched eagerly | one CUDA graph per stretch between two gradient exchanges; NCCL all-reduces always eager on a side stream (one GPU replays the whole step as one graph)",
-                                 "device_error": L.device_error()}
-        del wstep, wx, wy
+    out = run_mlp(torch, dist, pkg, world, rank, timed, tensor_peak)
+    if only == "mlp":
+        return out
     if rank == 0 or world == 1:
         M, N, K = 8192, 4096, 4096
         A = torch.randn(M, K, device="cuda").bfloat16()
@@ -374,8 +478,36 @@ def run_also(torch, dist, pkg, world, rank):
         torch.cuda.synchronize()
         gms = a.elapsed_time(b) / 20
         tf = 2.0 * M * N * K / gms / 1e9
+        # the incumbent on the same box, same shape, same minute: the plain product by cuBLAS (torch.matmul),
+        # with no bias, no activation and no second array to store
+        for _ in range(3):
+            torch.matmul(A, B, out=C)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(20):
+            torch.matmul(A, B, out=C)
+        b.record()
+        torch.cuda.synchronize()
+        cms = a.elapsed_time(b) / 20
+        ctf = 2.0 * M * N * K / cms / 1e9
+
+        def plain():
+            L.gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR,
+                   stream=stream)
+        for _ in range(3):
+            plain()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(20):
+            plain()
+        b.record()
+        torch.cuda.synchronize()
+        pms = a.elapsed_time(b) / 20
         out["gemm_bias_gelu_8192x4096x4096"] = {"TFLOP/s": round(tf, 1), "ms": round(gms, 4),
-                                                "frac_of_measured_bf16_peak": round(tf / tensor_peak, 4)}
+                                                "frac_of_measured_bf16_peak": round(tf / tensor_peak, 4),
+                                                "plain_product_TFLOP/s": round(2.0 * M * N * K / pms / 1e9, 1),
+                                                "cublas_plain_product_TFLOP/s": round(ctf, 1),
+                                                "cublas_plain_product_ms": round(cms, 4)}
 
         def clock(fn, iters):
             for _ in range(2):
@@ -397,18 +529,48 @@ def run_also(torch, dist, pkg, world, rank):
         desc = L.attn_desc(Bq, Hq, Sq, Sq, Dq, True)
         need = L.attention_bwd_workspace_bytes(desc)
         ws = torch.empty(need, dtype=torch.uint8, device="cuda")
-        fwd = clock(lambda: L.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                                            lse.data_ptr(), stream), 10)
-        bwd = clock(lambda: L.attention_bwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                                            lse.data_ptr(), g.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                            ws.data_ptr(), need, stream), 5)
+        def launches(fn, warm, iters):
+            """Per-launch device times (CUDA events around every launch), after `warm` untimed launches."""
+            for _ in range(warm):
+                fn()
+            torch.cuda.synchronize()
+            marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+            for a0, b0 in marks:
+                a0.record()
+                fn()
+                b0.record()
+            torch.cuda.synchronize()
+            return sorted(a0.elapsed_time(b0) for a0, b0 in marks)
+
+        watch = ClockSampler(physical_gpu_index(int(os.environ.get("LOCAL_RANK", "0"))))
+        fwd_ms = launches(lambda: L.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                                  lse.data_ptr(), stream), 6, 30)
+        bwd_forms = {}
+        for name, det in (("atomic", 0), ("deterministic", 1)):
+            desc.deterministic = det
+            bwd_forms[name] = launches(
+                lambda: L.attention_bwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                        g.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), need,
+                                        stream), 5, 30)
+        attn_clocks = watch.stop()
+        fwd = fwd_ms[len(fwd_ms) // 2]
+        bwd = bwd_forms["atomic"][15]
         fl = 4.0 * Bq * Hq * Sq * Sq * Dq * 0.5
+        mhz = attn_clocks.get("sm_mhz") or 0.0
         out["attention_causal_B8_H32_S4096_D128"] = {
             "fwd_ms": round(fwd, 4), "fwd_TFLOP/s": round(fl / fwd / 1e9, 1),
             "fwd_frac_of_measured_bf16_peak": round(fl / fwd / 1e9 / tensor_peak, 4),
+            "fwd_ms_min": round(fwd_ms[0], 4),
             "bwd_ms": round(bwd, 4), "bwd_TFLOP/s": round(2.5 * fl / bwd / 1e9, 1),
             "bwd_frac_of_measured_bf16_peak": round(2.5 * fl / bwd / 1e9 / tensor_peak, 4),
-            "bwd_note": "algorithmic 5 products (2.5 x forward); the deterministic two-kernel form executes 7",
+            "bwd_ms_min": round(bwd_forms["atomic"][0], 4),
+            "bwd_deterministic_ms": round(bwd_forms["deterministic"][15], 4),
+            "bwd_deterministic_TFLOP/s": round(2.5 * fl / bwd_forms["deterministic"][15] / 1e9, 1),
+            "timing": "median of 30 launches, each between its own CUDA events, after 5-6 untimed launches",
+            "sm_mhz_median": mhz, "fwd_ms_x_mhz": round(fwd * mhz, 1), "bwd_ms_x_mhz": round(bwd * mhz, 1),
+            "clock_reasons": attn_clocks.get("reasons"),
+            "bwd_note": "algorithmic 5 products (2.5 x forward) in both forms; the default form runs them in one kernel "
+                        "with dq added into a Float32 workspace, the deterministic two-kernel form executes 7",
             "device_error": L.attention_device_error() + L.attention_bwd_device_error()}
         del q, k, v, g, o, dq, dk, dv, ws
         # BASELINE.json configs[4]: chunked gated DeltaNet forward, B*H = 64 sequences of 8192, dk = dv = 128
@@ -706,7 +868,7 @@ def cpu_baseline(sample_rows, repeats):
             "seconds_per_sample": round(dt, 3),
             "sample": f"{sample_rows} of {ROWS} rows of the same workload (all 8 operators), rows over "
                       f"{threads} host threads; the reference's CPU path itself runs on one thread "
-                      "(Julia is not installed on the box: C restatement in oracle/)"}
+                      "(timed here as the C restatement in oracle/: no Julia runtime on this host)"}
 
 
 def run_reference(args):
@@ -750,6 +912,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the side measurements (MLP step, GEMM)")
+    ap.add_argument("--also", default="all", choices=["all", "mlp"],
+                    help="which side measurements to take: all of them, or the MLP training step alone")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "attention", "deltanet", "groups", "columns"],
                     help="run one small case of a kernel family only (for ncu captures)")
     args = ap.parse_args()

@@ -30,7 +30,8 @@ extern "C" {
 
 typedef enum tb200_dtype {
     TB200_F32 = 0,
-    TB200_BF16 = 1
+    TB200_BF16 = 1,
+    TB200_F16 = 2    /* products only (ext/cuBLASExt.jl:64-65, test/cuda/products.jl:25-30) */
 } tb200_dtype;
 
 typedef enum tb200_status {
@@ -133,7 +134,10 @@ int tb200_layernorm_bwd(const void *x, const void *gamma, const void *dy, const 
  * sums go to an 8 MiB array built into the library, which every GPU that loads
  * the library keeps resident until the process ends.  Rows longer than
  * tb200_layernorm_bwd_noalloc_max_row() elements (8192) are refused with
- * TB200_ERR_WORKSPACE.  The entry point itself allocates nothing.
+ * TB200_ERR_WORKSPACE, and so are rows of more than 4096 elements that cannot
+ * be read with 128-bit accesses (x, gamma, dy or dx not 16-byte aligned, or n
+ * or ld not a multiple of 4 Float32 / 8 BFloat16 elements): such rows do not fit
+ * one block's registers.  The entry point itself allocates nothing.
  * The first call on each device looks up the array's device address; make that
  * call outside any stream capture.  Every call on a device uses the same
  * array: calls whose kernels could overlap on the GPU (two streams) corrupt
@@ -185,19 +189,61 @@ typedef struct tb200_gemm_desc {
     int force_simt;              /* 1 = the generic kernel (Float32-exact, any alignment) */
     int direct_epilogue;         /* 1 = each thread stores its own output row instead of staging
                                     tiles through shared memory for TMA stores (a tuner variant) */
+    /* A batch of alike products in one launch, as cublasGemmStridedBatchedEx takes them
+     * (ext/cuBLASExt.jl:247-259): member i reads a + i * stride_a, b + i * stride_b and writes
+     * c + i * stride_c (elements).  batch 0 or 1 = one product.  A zero stride of an operand that is
+     * only read shares it among the members (one weight matrix for every member). */
+    int64_t batch;
+    int64_t stride_a, stride_b, stride_c;
+    int64_t stride_bias, stride_aux, stride_aux_out;
+    /* Split-K: the sum over k cut into `split_k` ranges whose Float32 partial results are merged in
+     * range order by a second launch (ext/cuTileExt/contract.jl:89-94, `product_split`; the merge is
+     * ext/cuTileExt/build.jl:654-696).  0 = the library decides (it splits when the output has too
+     * few tiles to fill a quarter of the SMs and k is long), 1 = never, s > 1 = s ranges at most.
+     * A split needs `workspace` (tb200_gemm_workspace_bytes, 16-byte aligned); without one the
+     * product runs unsplit. */
+    int split_k;
+    void *workspace;
+    size_t workspace_bytes;
+    /* Test hook, 0 in production.  Bit 0: the loading thread of the tensor-core kernel withholds its
+     * tiles and every bounded wait gives up after 20 ms instead of 2 s, so that the failure path (an
+     * error code in tb200_device_error, the launch returning, the context still usable) can be
+     * exercised without a fault. */
+    int debug;
 } tb200_gemm_desc;
 
-/* Enqueues the product.  BFloat16 operands with 16-byte aligned bases and
- * leading dimensions that are multiples of 8 run on the tensor cores
+/* Bytes of scratch a split of this product wants (0 when it would not split). */
+size_t tb200_gemm_workspace_bytes(const tb200_gemm_desc *desc);
+
+/* Enqueues the product.  BFloat16 or Float16 operands with 16-byte aligned bases and
+ * leading dimensions (and batch strides) that are multiples of 8 run on the tensor cores
  * (tcgen05, Float32 accumulation, one rounding at the store); everything else
  * runs the generic kernel.  The tensor-core path builds its TMA descriptors
- * from the raw pointers on every call and passes them as kernel parameters. */
+ * from the raw pointers on every call and passes them as kernel parameters;
+ * tb200_gemm_plan_create below builds them once.  Float16 takes the epilogues
+ * NONE, BIAS and AXPY on the tensor cores. */
 int tb200_gemm(const tb200_gemm_desc *desc, const void *a, const void *b, void *c, const void *bias,
                const void *aux, void *aux_out, void *stream);
 
-/* Synchronises the device, then returns and clears the code a tensor-core
- * kernel recorded if one of its bounded waits gave up (0 = none).  No
- * reference counterpart: Tempest's kernels have no device-side waits. */
+/* A prepared product: everything tb200_gemm works out per call (validation, schedule, the TMA
+ * descriptors) done once, so that a launch is one kernel launch -- the C side of the reference's
+ * `build` -> `launch()` / `repoint!` split (ext/cuBLASExt.jl:247-268, ext/cuTileExt/build.jl:949-976).
+ * tb200_gemm_plan_repoint replaces one operand's address (tb200_gemm_operand) and rebuilds what
+ * depends on it; the new address must be aligned as the old one was (src/Compiler/Implement/
+ * Implement.jl:162-175).  A plan belongs to the device that was current when it was created, may be
+ * launched any number of times on any stream of that device, and is not to be repointed while
+ * another thread launches it. */
+typedef struct tb200_gemm_plan tb200_gemm_plan;
+typedef enum tb200_gemm_operand {
+    TB200_GEMM_A = 0, TB200_GEMM_B = 1, TB200_GEMM_C = 2, TB200_GEMM_BIAS = 3, TB200_GEMM_AUX = 4,
+    TB200_GEMM_AUX_OUT = 5, TB200_GEMM_WORKSPACE = 6
+} tb200_gemm_operand;
+int tb200_gemm_plan_create(const tb200_gemm_desc *desc, const void *a, const void *b, void *c, const void *bias,
+                           const void *aux, void *aux_out, tb200_gemm_plan **plan);
+int tb200_gemm_plan_launch(const tb200_gemm_plan *plan, void *stream);
+int tb200_gemm_plan_repoint(tb200_gemm_plan *plan, int operand, const void *address);
+void tb200_gemm_plan_destroy(tb200_gemm_plan *plan);
+
 /* Measures the compiled-in tile variants of one product on its own operands
  * and returns the faster tile_n (128 or 256) to put in the descriptor, or a
  * negative status: the measured stage of the reference's search over a claim's
@@ -208,6 +254,17 @@ int tb200_gemm(const tb200_gemm_desc *desc, const void *a, const void *b, void *
 int tb200_gemm_tune(const tb200_gemm_desc *desc, const void *a, const void *b, void *c, const void *bias,
                     const void *aux, void *aux_out, void *stream);
 
+/* The wider search: times every compiled-in variant of the product -- tile widths 128 / 256, the
+ * sum unsplit or split (when a workspace is given), results stored through shared memory and TMA or
+ * by each thread -- and writes the fastest one's tile_n, split_k and direct_epilogue into *desc.
+ * Same rules as tb200_gemm_tune (overwrites C, synchronises, not for a capture).  Returns
+ * TB200_OK or a negative status. */
+int tb200_gemm_tune_desc(tb200_gemm_desc *desc, const void *a, const void *b, void *c, const void *bias,
+                         const void *aux, void *aux_out, void *stream);
+
+/* Synchronises the device, then returns and clears the code a tensor-core
+ * product kernel recorded if one of its bounded waits gave up (0 = none).  No
+ * reference counterpart: Tempest's kernels have no device-side waits. */
 int tb200_device_error(void);
 
 /* ---- attention -----------------------------------------------------------------
@@ -222,6 +279,11 @@ typedef struct tb200_attn_desc {
     int causal;                  /* keys after a query masked out (key index <= query index kept) */
     float scale;                 /* scores are scale * q.k ; 1/sqrt(head_dim) in the reference */
     int dtype;                   /* TB200_BF16 */
+    int deterministic;           /* the pullback only: 0 = one kernel whose dq contributions are added into a
+                                    Float32 workspace in whatever order the key tiles finish (the reference's
+                                    default, `CUDATarget(...; deterministic = false)`,
+                                    src/Compiler/runtime/target.jl:31); 1 = two kernels, no atomic adds, results
+                                    repeat bit for bit */
 } tb200_attn_desc;
 
 /* o = softmax(scale * k'q + mask) weighted sum of v, lse beside it (NULL: not
@@ -254,6 +316,16 @@ int tb200_attention_bwd(const tb200_attn_desc *desc, const void *q, const void *
                         void *dv, void *workspace, size_t workspace_bytes, void *stream);
 
 int tb200_attention_bwd_device_error(void);
+
+/* All three error words in one call: synchronises the device, returns
+ * product | attention forward << 8 | attention backward << 16 (0 = every bounded
+ * wait completed) and clears them, or a negative status.  The launch entry
+ * points return TB200_OK once their kernels are enqueued, so a wait that gives
+ * up later is visible only here: a caller polls this wherever it synchronises
+ * anyway (after a step, before it reads results back) and treats a non-zero
+ * value as a failed launch whose outputs must not be used.  No reference
+ * counterpart. */
+int tb200_device_errors(void);
 
 /* Masks the device holds, and operands at other strides.  Two of the reference's
  * mask programs (test/cuda/attention.jl:217-246, 248-275; the scheduling side is
@@ -456,7 +528,8 @@ int tb200_colsum(const void *x, void *out, int64_t rows, int64_t n, int64_t ld, 
                  int dtype, void *workspace, size_t workspace_bytes, void *stream);
 
 /* y[i] += alpha * x[i]: the update w .- rate .* dw (examples/mlp.jl:32-35).
- * y and x 16-byte aligned. */
+ * 128-bit accesses when y and x are both 16-byte aligned; a view that starts at
+ * an odd element runs one element a thread. */
 int tb200_axpy(void *y, const void *x, float alpha, int64_t count, int y_dtype, int x_dtype,
                void *stream);
 

@@ -323,6 +323,45 @@ def mlp_step(ws, bs, x, y, rate, global_batch=None):
     return loss, dz, dws, dbs, new_w, new_b, a, z
 
 
+def mlp_step_blas(ws, bs, x, y, rate, global_batch=None):
+    """`mlp_step` at sizes the scalar products cannot reach (the benchmark's 1024-4096-4096-4096-1024 at batch
+    8192 is 2 TFLOP): the same arithmetic with the same rounding points -- BFloat16 arrays widened to Float32,
+    every product accumulated in Float32 and rounded once where it is stored -- but the products taken by
+    numpy's Float32 matmul (BLAS) instead of sequential sums, which changes the order of summation only.
+    Returns loss, [dz bits], [dw Float32], [db Float32], [new w bits], [new b bits], [a bits], [z bits]."""
+    L = len(ws)
+    batch = x.shape[0]
+    gb = global_batch or batch
+    W = [from_bf16(w) for w in ws]
+    a, z = [x], []
+    h = from_bf16(x)
+    for i in range(L):
+        pre = h @ W[i] + from_bf16(bs[i])[None, :]
+        zb = to_bf16(pre)
+        z.append(zb)
+        if i == L - 1:
+            out = zb
+        else:
+            u = np.float32(0.7978846) * (pre + np.float32(0.044715) * pre * pre * pre)
+            out = to_bf16(np.float32(0.5) * pre * (np.float32(1.0) + np.tanh(u)))
+        a.append(out)
+        h = from_bf16(out)
+    d = from_bf16(a[-1]) - from_bf16(y)
+    loss = float(np.sum(d.astype(np.float64) ** 2) / gb)
+    dz = [None] * L
+    dz[L - 1] = to_bf16((np.float32(1.0 / gb) * (np.float32(2.0) * d)).astype(np.float32))
+    dws, dbs, new_w, new_b = [None] * L, [None] * L, [None] * L, [None] * L
+    for i in range(L - 1, -1, -1):
+        g = from_bf16(dz[i])
+        if i > 0:
+            dz[i - 1] = to_bf16((g @ W[i].T) * _gelu_grad_f32(from_bf16(z[i - 1])))
+        dbs[i] = g.astype(np.float64).sum(axis=0).astype(np.float32)
+        dws[i] = from_bf16(a[i]).T @ g
+        new_w[i] = to_bf16(W[i] - np.float32(rate) * dws[i])
+        new_b[i] = to_bf16(from_bf16(bs[i]) - np.float32(rate) * from_bf16(to_bf16(dbs[i])))
+    return loss, dz, dws, dbs, new_w, new_b, a, z
+
+
 # ------------------------------------------------------------- attention ----
 
 def _pool(jobs, threads):

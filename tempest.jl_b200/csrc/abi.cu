@@ -67,3 +67,15 @@ extern "C" int tb200_sm_count(void) {
     int st = tb200::current_device(&d);
     return st == TB200_OK ? d.sms : st;
 }
+
+// The three tensor-core kernel families each keep one error word; a caller that launches several kinds
+// polls them all at a synchronisation point through this one call.
+extern "C" int tb200_device_errors(void) {
+    const int product = tb200_device_error();
+    if (product < 0) return product;
+    const int forward = tb200_attention_device_error();
+    if (forward < 0) return forward;
+    const int backward = tb200_attention_bwd_device_error();
+    if (backward < 0) return backward;
+    return (product & 0xff) | ((forward & 0xff) << 8) | ((backward & 0xff) << 16);
+}

@@ -4,6 +4,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
@@ -37,7 +38,7 @@ struct DeviceInfo {
 int current_device(DeviceInfo *out);
 
 inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
-inline size_t dtype_size(int dtype) { return dtype == TB200_F32 ? 4 : dtype == TB200_BF16 ? 2 : 0; }
+inline size_t dtype_size(int dtype) { return dtype == TB200_F32 ? 4 : (dtype == TB200_BF16 || dtype == TB200_F16) ? 2 : 0; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int next_pow2(int64_t x) {
     int p = 1;

@@ -9,7 +9,12 @@
 // epilogue of tile i overlaps the main loop of tile i + 1.  Either operand may
 // be K-major or MN-major in memory (all of NN / NT / TN / TT), which is what
 // lets the backward products dX = dY * W' and dW = X' * dY read the forward's
-// arrays in place.  No load uses cluster multicast.
+// arrays in place.  No load uses cluster multicast.  A launch may hold a batch
+// of alike products (the batch is the third coordinate of every tensor map)
+// and may cut the sum over k into ranges (split-K): each (range, member, tile)
+// is one work item of the persistent loop, the ranges' Float32 partial tiles
+// go to a workspace and a second kernel merges them in range order and applies
+// the epilogue.  BFloat16 or Float16 operands.
 //
 // Generic path: a shared-memory tiled SIMT kernel for Float32 operands, odd
 // leading dimensions and anything else the TMA path cannot address.
@@ -49,13 +54,20 @@ struct GemmArgs {
     const void *aux;
     void *aux_out;
     long long ldc, ld_aux, ld_aux_out;
+    long long stride_c, stride_bias, stride_aux, stride_aux_out;   // between batch members, elements
     float alpha;
     int m, n, k;
     int epilogue;
-    int out_f32;
+    int in_f16;           // operands (and the bias) are Float16, not BFloat16
     int a_mn, b_mn;       // operand is MN-major in memory
+    int a_batched, b_batched;   // 0: every member reads the same array
     int tiles_m, tiles_n;
+    int batch;            // members
+    int splits;           // ranges of the sum over k (1 = unsplit)
+    int kb_per_split;     // 64-wide k blocks per range
     int stages;
+    int debug;            // bit 0: the loader withholds its tiles (test hook)
+    unsigned long long wait_ns;   // after which a bounded wait gives up
 };
 
 // ------------------------------------------------------------- epilogues ----
@@ -125,10 +137,42 @@ __device__ __forceinline__ bool aligned_dev(const void *p, uintptr_t a) {
     return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
 }
 
-// `count` (<= 32) consecutive values of one output row, as Float32 or rounded to BFloat16; 128-bit
-// stores when the whole chunk is there and the address allows.
-__device__ __forceinline__ void store_row32(void *base, int f32, long long offset, const float (&v)[32], int count) {
-    if (f32) {
+// Output element kinds of the tensor-core kernel.
+constexpr int OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2;
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ void unpack_f16x2(uint32_t w, float &lo, float &hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    lo = f.x; hi = f.y;
+}
+// two values rounded to the 16-bit output type OUT
+template <int OUT>
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    if constexpr (OUT == OUT_F16) return pack_f16x2(lo, hi);
+    else return pack_bf16x2(lo, hi);
+}
+// eight 16-bit values (Float16 when `f16`, else BFloat16) widened to Float32
+__device__ __forceinline__ void unpack_half8(uint4 q, float *v, bool f16) {
+    if (f16) {
+        unpack_f16x2(q.x, v[0], v[1]); unpack_f16x2(q.y, v[2], v[3]);
+        unpack_f16x2(q.z, v[4], v[5]); unpack_f16x2(q.w, v[6], v[7]);
+    } else {
+        Access<__nv_bfloat16, true>::unpack(q, v);
+    }
+}
+__device__ __forceinline__ float half_to_f32(const void *p, long long i, bool f16) {
+    return f16 ? __half2float(static_cast<const __half *>(p)[i])
+               : __bfloat162float(static_cast<const __nv_bfloat16 *>(p)[i]);
+}
+
+// `count` (<= 32) consecutive values of one output row, as Float32 or rounded to the 16-bit type;
+// 128-bit stores when the whole chunk is there and the address allows.
+template <int OUT>
+__device__ __forceinline__ void store_row32(void *base, long long offset, const float (&v)[32], int count) {
+    if constexpr (OUT == OUT_F32) {
         float *o = static_cast<float *>(base) + offset;
         if (count == 32 && aligned_dev(o, 16)) {
 #pragma unroll
@@ -140,21 +184,21 @@ __device__ __forceinline__ void store_row32(void *base, int f32, long long offse
                 if (j < count) o[j] = v[j];
         }
     } else {
-        __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(base) + offset;
+        uint16_t *o = static_cast<uint16_t *>(base) + offset;
         if (count == 32 && aligned_dev(o, 16)) {
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 uint4 q;
-                q.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
-                q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
-                q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
-                q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+                q.x = pack_half2<OUT>(v[8 * j], v[8 * j + 1]);
+                q.y = pack_half2<OUT>(v[8 * j + 2], v[8 * j + 3]);
+                q.z = pack_half2<OUT>(v[8 * j + 4], v[8 * j + 5]);
+                q.w = pack_half2<OUT>(v[8 * j + 6], v[8 * j + 7]);
                 reinterpret_cast<uint4 *>(o)[j] = q;
             }
         } else {
 #pragma unroll
             for (int j = 0; j < 32; j++)
-                if (j < count) o[j] = __float2bfloat16_rn(v[j]);
+                if (j < count) o[j] = static_cast<uint16_t>(pack_half2<OUT>(v[j], 0.0f) & 0xffffu);
         }
     }
 }
@@ -167,14 +211,15 @@ __device__ __forceinline__ uint64_t global_ns() {
     return t;
 }
 
-// Bounded wait: false once `*failed` is set by anyone or two seconds have passed.
-__device__ __forceinline__ bool wait_or_fail(uint64_t *bar, uint32_t parity, volatile int *failed, int code) {
+// Bounded wait: false once `*failed` is set by anyone or `limit_ns` have passed.
+__device__ __forceinline__ bool wait_or_fail(uint64_t *bar, uint32_t parity, volatile int *failed, int code,
+                                             unsigned long long limit_ns) {
     if (mbar_wait(bar, parity, 4096)) return true;
     const uint64_t t0 = global_ns();
     while (true) {
         if (mbar_wait(bar, parity, 1024)) return true;
         if (*failed) return false;
-        if (global_ns() - t0 > 2000000000ull) {
+        if (global_ns() - t0 > limit_ns) {
             *failed = code;
             atomicCAS(&g_gemm_error, 0, code);
             return false;
@@ -185,18 +230,40 @@ __device__ __forceinline__ bool wait_or_fail(uint64_t *bar, uint32_t parity, vol
 constexpr int kStageLine = 128;                   // bytes per staged row: one 128-byte swizzle line
 constexpr int kEpilogueStage = 32 * kStageLine;   // 32 rows of one warp
 
+// One work item of the persistent loop: which range of the sum, which batch member, which tile.
+struct WorkItem {
+    int zc;        // third coordinate of the output (member, or range * batch + member when the sum is split)
+    int member;
+    int tm, tn;
+    int kb0, kb1;  // 64-wide blocks of k
+};
+__device__ __forceinline__ WorkItem work_item(const GemmArgs &p, int item, int num_kb) {
+    const int tiles = p.tiles_m * p.tiles_n;
+    WorkItem w;
+    w.zc = item / tiles;
+    const int t = item - w.zc * tiles;
+    w.tm = t / p.tiles_n;
+    w.tn = t - w.tm * p.tiles_n;
+    const int range = w.zc / p.batch;
+    w.member = w.zc - range * p.batch;
+    w.kb0 = range * p.kb_per_split;
+    w.kb1 = w.kb0 + p.kb_per_split < num_kb ? w.kb0 + p.kb_per_split : num_kb;
+    return w;
+}
+
 // One warp's share of a finished accumulator tile, through shared memory: 32 rows x 128 bytes at a
 // time are written (128-byte swizzled, so a thread writing its own row does not collide with its
 // neighbours) into a staging buffer and handed to a TMA store, which writes whole lines; the operand an
 // epilogue reads (aux) arrives the same way by a TMA load.  Returns false if a bounded wait gave up.
-template <int BN, int EPI, bool OUT_F32>
-__device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tmem_acc, int row0, int n0, int lane,
-                                                  uint8_t *stage_c, uint8_t *stage_x, uint64_t *aux_bar,
-                                                  uint32_t &aux_phase, volatile int *failed) {
-    constexpr int EPL = OUT_F32 ? 32 : 64;   // elements per 128-byte line
+template <int BN, int EPI, int OUT>
+__device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tmem_acc, int row0, int n0, int zc,
+                                                  int member, int lane, uint8_t *stage_c, uint8_t *stage_x,
+                                                  uint64_t *aux_bar, uint32_t &aux_phase, volatile int *failed) {
+    constexpr int EPL = OUT == OUT_F32 ? 32 : 64;   // elements per 128-byte line
     constexpr bool reads_bias = epilogue_reads_bias(EPI), reads_aux = epilogue_reads_aux(EPI);
     const bool has_aux_out = EPI == TB200_EPI_BIAS_GELU && p.aux_out != nullptr;
     const int sw = lane & 7;
+    const bool in_f16 = p.in_f16 != 0;
 #pragma unroll 1
     for (int g = 0; g < BN / EPL; g++) {
         const int col0 = n0 + g * EPL;
@@ -207,9 +274,9 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tm
         if (reads_aux) {
             if (lane == 0) {
                 mbar_arrive_expect_tx(aux_bar, kEpilogueStage);
-                tma_load_2d(stage_x, &p.tmap_aux, aux_bar, col0, row0);
+                tma_load_3d(stage_x, &p.tmap_aux, aux_bar, col0, row0, member);
             }
-            if (!wait_or_fail(aux_bar, aux_phase, failed, 5)) return false;
+            if (!wait_or_fail(aux_bar, aux_phase, failed, 5, p.wait_ns)) return false;
             aux_phase ^= 1;
         }
 #pragma unroll 1
@@ -222,7 +289,7 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tm
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]) * p.alpha;
             if (reads_aux) {
-                if constexpr (OUT_F32) {
+                if constexpr (OUT == OUT_F32) {
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         const float4 q = *reinterpret_cast<const float4 *>(stage_x + lane * kStageLine + ((j ^ sw) << 4));
@@ -233,20 +300,20 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tm
                     for (int j = 0; j < 4; j++) {
                         const uint4 q =
                             *reinterpret_cast<const uint4 *>(stage_x + lane * kStageLine + (((4 * h + j) ^ sw) << 4));
-                        Access<__nv_bfloat16, true>::unpack(q, &auxv[8 * j]);
+                        unpack_half8(q, &auxv[8 * j], OUT == OUT_F16);
                     }
                 }
             }
             float bv[32];
             if (reads_bias) {
-                const __nv_bfloat16 *bp = static_cast<const __nv_bfloat16 *>(p.bias) + c0;
+                const uint16_t *bp = static_cast<const uint16_t *>(p.bias) + member * p.stride_bias + c0;
                 if (c0 + 32 <= p.n && aligned_dev(bp, 16)) {
 #pragma unroll
                     for (int j = 0; j < 4; j++)
-                        Access<__nv_bfloat16, true>::unpack(__ldg(reinterpret_cast<const uint4 *>(bp) + j), &bv[8 * j]);
+                        unpack_half8(__ldg(reinterpret_cast<const uint4 *>(bp) + j), &bv[8 * j], in_f16);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) bv[j] = (c0 + j < p.n) ? __bfloat162float(bp[j]) : 0.0f;
+                    for (int j = 0; j < 32; j++) bv[j] = (c0 + j < p.n) ? half_to_f32(bp, j, in_f16) : 0.0f;
                 }
             }
             float pre[32];
@@ -255,7 +322,7 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tm
                 pre[j] = v[j];
                 v[j] = epilogue_fixed<EPI>(v[j], reads_bias ? bv[j] : 0.0f, reads_aux ? auxv[j] : 0.0f, pre[j]);
             }
-            if constexpr (OUT_F32) {
+            if constexpr (OUT == OUT_F32) {
 #pragma unroll
                 for (int j = 0; j < 8; j++)
                     *reinterpret_cast<float4 *>(stage_c + lane * kStageLine + ((j ^ sw) << 4)) =
@@ -264,16 +331,16 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tm
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     uint4 q;
-                    q.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
-                    q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
-                    q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
-                    q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+                    q.x = pack_half2<OUT>(v[8 * j], v[8 * j + 1]);
+                    q.y = pack_half2<OUT>(v[8 * j + 2], v[8 * j + 3]);
+                    q.z = pack_half2<OUT>(v[8 * j + 4], v[8 * j + 5]);
+                    q.w = pack_half2<OUT>(v[8 * j + 6], v[8 * j + 7]);
                     *reinterpret_cast<uint4 *>(stage_c + lane * kStageLine + (((4 * h + j) ^ sw) << 4)) = q;
                     if (has_aux_out) {
-                        q.x = pack_bf16x2(pre[8 * j], pre[8 * j + 1]);
-                        q.y = pack_bf16x2(pre[8 * j + 2], pre[8 * j + 3]);
-                        q.z = pack_bf16x2(pre[8 * j + 4], pre[8 * j + 5]);
-                        q.w = pack_bf16x2(pre[8 * j + 6], pre[8 * j + 7]);
+                        q.x = pack_half2<OUT>(pre[8 * j], pre[8 * j + 1]);
+                        q.y = pack_half2<OUT>(pre[8 * j + 2], pre[8 * j + 3]);
+                        q.z = pack_half2<OUT>(pre[8 * j + 4], pre[8 * j + 5]);
+                        q.w = pack_half2<OUT>(pre[8 * j + 6], pre[8 * j + 7]);
                         *reinterpret_cast<uint4 *>(stage_x + lane * kStageLine + (((4 * h + j) ^ sw) << 4)) = q;
                     }
                 }
@@ -282,15 +349,15 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tm
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-            tma_store_2d(&p.tmap_c, stage_c, col0, row0);
-            if (has_aux_out) tma_store_2d(&p.tmap_aux_out, stage_x, col0, row0);
+            tma_store_3d(&p.tmap_c, stage_c, col0, row0, zc);
+            if (has_aux_out) tma_store_3d(&p.tmap_aux_out, stage_x, col0, row0, member);
             bulk_commit_group();
         }
     }
     return true;
 }
 
-template <int BN, int EPI, bool OUT_F32>
+template <int BN, int EPI, int OUT>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_constant__ GemmArgs p) {
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzle atoms are 1024 bytes: align the ring
@@ -313,7 +380,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     const int lane = threadIdx.x & 31;
     const int stages = p.stages;
     const int num_kb = (p.k + BK - 1) / BK;
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_items = p.tiles_m * p.tiles_n * p.batch * p.splits;
+    const unsigned long long wait_ns = p.wait_ns;
 
     if (threadIdx.x == 0) {
         failed_smem = 0;
@@ -341,30 +409,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     const uint32_t tmem_base = tmem_base_smem;
 
     if (warp == 0) {
-        // ---- TMA producer
-        if (elect_one()) {
+        // ---- TMA producer (with the test hook set it issues nothing: every consumer's wait then runs out)
+        if (elect_one() && !(p.debug & 1)) {
             int stage = 0;
             uint32_t phase = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && !*failed; tile += gridDim.x) {
-                const int m0 = (tile / p.tiles_n) * BM;
-                const int n0 = (tile % p.tiles_n) * BN;
-                for (int kb = 0; kb < num_kb; kb++) {
-                    if (!wait_or_fail(&empty_bar[stage], phase ^ 1, failed, 1)) break;
+            for (int item = blockIdx.x; item < num_items && !*failed; item += gridDim.x) {
+                const WorkItem w = work_item(p, item, num_kb);
+                const int m0 = w.tm * BM, n0 = w.tn * BN;
+                const int za = p.a_batched ? w.member : 0, zb = p.b_batched ? w.member : 0;
+                for (int kb = w.kb0; kb < w.kb1; kb++) {
+                    if (!wait_or_fail(&empty_bar[stage], phase ^ 1, failed, 1, wait_ns)) break;
                     uint8_t *sa = smem + stage * STAGE_BYTES;
                     uint8_t *sb = sa + A_BYTES;
                     mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
                     const int k0 = kb * BK;
                     if (p.a_mn) {   // [K][M]: slabs of 64 along M, each 64 K-lines of 128 bytes
                         for (int j = 0; j < BM / 64; j++)
-                            tma_load_2d(sa + j * (BK * 128), &p.tmap_a, &full_bar[stage], m0 + j * 64, k0);
+                            tma_load_3d(sa + j * (BK * 128), &p.tmap_a, &full_bar[stage], m0 + j * 64, k0, za);
                     } else {        // [M][K]: 128 rows of 128 bytes
-                        tma_load_2d(sa, &p.tmap_a, &full_bar[stage], k0, m0);
+                        tma_load_3d(sa, &p.tmap_a, &full_bar[stage], k0, m0, za);
                     }
                     if (p.b_mn) {
                         for (int j = 0; j < BN / 64; j++)
-                            tma_load_2d(sb + j * (BK * 128), &p.tmap_b, &full_bar[stage], n0 + j * 64, k0);
+                            tma_load_3d(sb + j * (BK * 128), &p.tmap_b, &full_bar[stage], n0 + j * 64, k0, zb);
                     } else {
-                        tma_load_2d(sb, &p.tmap_b, &full_bar[stage], k0, n0);
+                        tma_load_3d(sb, &p.tmap_b, &full_bar[stage], k0, n0, zb);
                     }
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
@@ -373,7 +442,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     } else if (warp == 1) {
         // ---- MMA issuer
         if (elect_one()) {
-            const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_mn != 0, p.b_mn != 0);
+            const uint32_t idesc = p.in_f16 ? umma_idesc_f16(BM, BN, p.a_mn != 0, p.b_mn != 0)
+                                            : umma_idesc_bf16(BM, BN, p.a_mn != 0, p.b_mn != 0);
             // K-major: 8-row groups 1024 bytes apart, 32 bytes per 16 K; MN-major: slabs BK*128 bytes
             // apart, 8-line groups 1024 bytes apart, 2048 bytes per 16 K
             const uint32_t a_lead = p.a_mn ? BK * 128 : 16, b_lead = p.b_mn ? BK * 128 : 16;
@@ -381,24 +451,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             const uint32_t b_step = (p.b_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
             int stage = 0, it = 0;
             uint32_t phase = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && !*failed; tile += gridDim.x, it++) {
+            for (int item = blockIdx.x; item < num_items && !*failed; item += gridDim.x, it++) {
+                const WorkItem w = work_item(p, item, num_kb);
                 const int acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
-                if (!wait_or_fail(&tmem_empty_bar[acc], acc_phase ^ 1, failed, 2)) break;
+                if (!wait_or_fail(&tmem_empty_bar[acc], acc_phase ^ 1, failed, 2, wait_ns)) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < num_kb; kb++) {
-                    if (!wait_or_fail(&full_bar[stage], phase, failed, 3)) break;
+                for (int kb = w.kb0; kb < w.kb1; kb++) {
+                    if (!wait_or_fail(&full_bar[stage], phase, failed, 3, wait_ns)) break;
                     tcgen05_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
                     const uint64_t a_desc = umma_smem_desc(sa, a_lead, 1024);
                     const uint64_t b_desc = umma_smem_desc(sa + A_BYTES, b_lead, 1024);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++)
-                        tcgen05_mma_f16(d_tmem, a_desc + k * a_step, b_desc + k * b_step, idesc, (kb | k) != 0);
+                        tcgen05_mma_f16(d_tmem, a_desc + k * a_step, b_desc + k * b_step, idesc,
+                                        ((kb - w.kb0) | k) != 0);
                     tcgen05_commit(&empty_bar[stage]);   // the stage is free once these MMAs have read it
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
+                if (*failed) break;
                 tcgen05_commit(&tmem_full_bar[acc]);     // the accumulator is complete
             }
         }
@@ -411,28 +484,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
         uint8_t *stage_c = smem + stages * STAGE_BYTES + (warp - 2) * 2 * kEpilogueStage;
         uint8_t *stage_x = stage_c + kEpilogueStage;
         uint32_t aux_phase = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, it++) {
+        const bool in_f16 = p.in_f16 != 0;
+        for (int item = blockIdx.x; item < num_items; item += gridDim.x, it++) {
+            const WorkItem w = work_item(p, item, num_kb);
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            if (!wait_or_fail(&tmem_full_bar[acc], acc_phase, failed, 4)) break;
+            if (!wait_or_fail(&tmem_full_bar[acc], acc_phase, failed, 4, wait_ns)) break;
             tcgen05_fence_after();
             if (p.tma_epilogue) {
-                const int row0 = (tile / p.tiles_n) * BM + q * 32;
+                const int row0 = w.tm * BM + q * 32;
                 const uint32_t tmem_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
                 bool ok = true;
                 if (row0 < p.m)
-                    ok = epilogue_tile_tma<BN, EPI, OUT_F32>(p, tmem_acc, row0, (tile % p.tiles_n) * BN, lane, stage_c,
-                                                             stage_x, &aux_bar[warp - 2], aux_phase, failed);
+                    ok = epilogue_tile_tma<BN, EPI, OUT>(p, tmem_acc, row0, w.tn * BN, w.zc, w.member, lane, stage_c,
+                                                         stage_x, &aux_bar[warp - 2], aux_phase, failed);
                 if (!ok) break;
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
                 continue;
             }
-            const int m = (tile / p.tiles_n) * BM + q * 32 + lane;
-            const int n0 = (tile % p.tiles_n) * BN;
+            const int m = w.tm * BM + q * 32 + lane;
+            const int n0 = w.tn * BN;
             const bool row_ok = m < p.m;
             constexpr bool reads_bias = epilogue_reads_bias(EPI), reads_aux = epilogue_reads_aux(EPI);
+            const long long c_base = static_cast<long long>(w.zc) * p.stride_c + static_cast<long long>(m) * p.ldc;
+            const long long x_base = static_cast<long long>(w.member) * p.stride_aux + static_cast<long long>(m) * p.ld_aux;
+            const long long o_base =
+                static_cast<long long>(w.member) * p.stride_aux_out + static_cast<long long>(m) * p.ld_aux_out;
+            const void *bias = static_cast<const uint16_t *>(p.bias) + w.member * p.stride_bias;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c++) {
                 uint32_t r[32];
@@ -447,36 +527,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
                 for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]) * p.alpha;
                 float auxv[32];
                 if (reads_aux) {
-                    if (OUT_F32 && EPI == TB200_EPI_AXPY) {
-                        const float *ap = static_cast<const float *>(p.aux) + static_cast<long long>(m) * p.ld_aux + col0;
+                    if (OUT == OUT_F32 && EPI == TB200_EPI_AXPY) {
+                        const float *ap = static_cast<const float *>(p.aux) + x_base + col0;
 #pragma unroll
                         for (int j = 0; j < 32; j++) auxv[j] = (whole || col0 + j < p.n) ? ap[j] : 0.0f;
                     } else {
-                        const __nv_bfloat16 *ap =
-                            static_cast<const __nv_bfloat16 *>(p.aux) + static_cast<long long>(m) * p.ld_aux + col0;
+                        // the activation pullbacks read the operands' type, the accumulating epilogue the result's
+                        const bool aux_f16 = EPI == TB200_EPI_AXPY ? OUT == OUT_F16 : in_f16;
+                        const uint16_t *ap = static_cast<const uint16_t *>(p.aux) + x_base + col0;
                         if (whole && aligned_dev(ap, 16)) {
 #pragma unroll
                             for (int j = 0; j < 4; j++)
-                                Access<__nv_bfloat16, true>::unpack(__ldg(reinterpret_cast<const uint4 *>(ap) + j), &auxv[j * 8]);
+                                unpack_half8(__ldg(reinterpret_cast<const uint4 *>(ap) + j), &auxv[j * 8], aux_f16);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                auxv[j] = (col0 + j < p.n) ? __bfloat162float(ap[j]) : 0.0f;
+                            for (int j = 0; j < 32; j++) auxv[j] = (col0 + j < p.n) ? half_to_f32(ap, j, aux_f16) : 0.0f;
                         }
                     }
                 }
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     float b = 0.0f;
-                    if (reads_bias && (whole || col0 + j < p.n))
-                        b = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.bias)[col0 + j]);
+                    if (reads_bias && (whole || col0 + j < p.n)) b = half_to_f32(bias, col0 + j, in_f16);
                     pre[j] = v[j];
                     v[j] = epilogue_fixed<EPI>(v[j], b, reads_aux ? auxv[j] : 0.0f, pre[j]);
                 }
-                store_row32(p.c, OUT_F32, static_cast<long long>(m) * p.ldc + col0, v, whole ? 32 : p.n - col0);
-                if (p.aux_out)
-                    store_row32(p.aux_out, 0, static_cast<long long>(m) * p.ld_aux_out + col0, pre,
-                                whole ? 32 : p.n - col0);
+                store_row32<OUT>(p.c, c_base + col0, v, whole ? 32 : p.n - col0);
+                if (p.aux_out) {
+                    if (in_f16) store_row32<OUT_F16>(p.aux_out, o_base + col0, pre, whole ? 32 : p.n - col0);
+                    else store_row32<OUT_BF16>(p.aux_out, o_base + col0, pre, whole ? 32 : p.n - col0);
+                }
             }
             tcgen05_fence_before();
             __syncwarp();
@@ -494,9 +574,56 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     }
 }
 
+// Split-K, second launch: C = epilogue(alpha * sum over ranges of the partial tiles), ranges added in order.
+struct MergeArgs {
+    const float *partial;   // [range][member][m][ld_partial]
+    void *c;
+    const void *bias, *aux;
+    void *aux_out;
+    long long ld_partial, ldc, ld_aux, ld_aux_out;
+    long long stride_c, stride_bias, stride_aux, stride_aux_out;
+    float alpha;
+    int m, n, batch, splits;
+    int epilogue;
+    int in_dtype, out_dtype;
+};
+
+__device__ __forceinline__ float load_elem(const void *p, long long i, int dtype) {
+    if (dtype == TB200_F32) return static_cast<const float *>(p)[i];
+    if (dtype == TB200_F16) return __half2float(static_cast<const __half *>(p)[i]);
+    return __bfloat162float(static_cast<const __nv_bfloat16 *>(p)[i]);
+}
+__device__ __forceinline__ void store_elem(void *p, long long i, float v, int dtype) {
+    if (dtype == TB200_F32) static_cast<float *>(p)[i] = v;
+    else if (dtype == TB200_F16) static_cast<__half *>(p)[i] = __float2half_rn(v);
+    else static_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
+}
+
+__global__ void __launch_bounds__(256) gemm_splitk_merge(const MergeArgs q) {
+    const long long per_member = static_cast<long long>(q.m) * q.n;
+    const long long total = per_member * q.batch;
+    const bool reads_bias = epilogue_reads_bias(q.epilogue), reads_aux = epilogue_reads_aux(q.epilogue);
+    const int aux_dtype = q.epilogue == TB200_EPI_AXPY ? q.out_dtype : q.in_dtype;
+    for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
+        const int member = static_cast<int>(i / per_member);
+        const long long r = i - member * per_member;
+        const int row = static_cast<int>(r / q.n), col = static_cast<int>(r - static_cast<long long>(row) * q.n);
+        float acc = 0.0f;
+        for (int s = 0; s < q.splits; s++)
+            acc += q.partial[((static_cast<long long>(s) * q.batch + member) * q.m + row) * q.ld_partial + col];
+        const float b = reads_bias ? load_elem(q.bias, member * q.stride_bias + col, q.in_dtype) : 0.0f;
+        const float x = reads_aux ? load_elem(q.aux, member * q.stride_aux + row * q.ld_aux + col, aux_dtype) : 0.0f;
+        float pre = acc * q.alpha;
+        const float v = epilogue_value<false>(q.epilogue, pre, b, x, pre);
+        store_elem(q.c, member * q.stride_c + row * q.ldc + col, v, q.out_dtype);
+        if (q.aux_out) store_elem(q.aux_out, member * q.stride_aux_out + row * q.ld_aux_out + col, pre, q.in_dtype);
+    }
+}
+
 // --------------------------------------------------------- SIMT kernel ----
 // C[M][N] = epilogue(alpha * A * B): 64 x 64 tile per block of 256 threads, 4 x 4 outputs per thread,
-// operands through shared memory in Float32.  Any layout, any leading dimension, either element type.
+// operands through shared memory in Float32.  Any layout, any leading dimension, any element type;
+// batch members along the grid's third axis.
 
 struct SimtArgs {
     const void *a, *b;
@@ -504,74 +631,73 @@ struct SimtArgs {
     const void *bias, *aux;
     void *aux_out;
     long long lda, ldb, ldc, ld_aux, ld_aux_out;
+    long long stride_a, stride_b, stride_c, stride_bias, stride_aux, stride_aux_out;
     float alpha;
-    int m, n, k;
+    int m, n, k, batch;
     int epilogue;
-    int in_f32, out_f32;
+    int in_dtype, out_dtype;
     int a_mn, b_mn;
 };
-
-__device__ __forceinline__ float load_elem(const void *p, long long i, int f32) {
-    return f32 ? static_cast<const float *>(p)[i] : __bfloat162float(static_cast<const __nv_bfloat16 *>(p)[i]);
-}
-__device__ __forceinline__ void store_elem(void *p, long long i, float v, int f32) {
-    if (f32) static_cast<float *>(p)[i] = v;
-    else static_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
-}
 
 __global__ void __launch_bounds__(256) gemm_simt(const SimtArgs p) {
     __shared__ float sa[16][65];
     __shared__ float sb[16][65];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
-    float acc[4][4] = {};
-    for (int k0 = 0; k0 < p.k; k0 += 16) {
-        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
-            // consecutive threads walk the operand's contiguous axis
-            int mm, kk;
-            if (p.a_mn) { mm = i & 63; kk = i >> 6; } else { kk = i & 15; mm = i >> 4; }
-            const int gm = m0 + mm, gk = k0 + kk;
-            float v = 0.0f;
-            if (gm < p.m && gk < p.k)
-                v = load_elem(p.a, p.a_mn ? static_cast<long long>(gk) * p.lda + gm : static_cast<long long>(gm) * p.lda + gk,
-                              p.in_f32);
-            sa[kk][mm] = v;
-            int nn;
-            if (p.b_mn) { nn = i & 63; kk = i >> 6; } else { kk = i & 15; nn = i >> 4; }
-            const int gn = n0 + nn;
-            const int gk2 = k0 + kk;
-            v = 0.0f;
-            if (gn < p.n && gk2 < p.k)
-                v = load_elem(p.b, p.b_mn ? static_cast<long long>(gk2) * p.ldb + gn : static_cast<long long>(gn) * p.ldb + gk2,
-                              p.in_f32);
-            sb[kk][nn] = v;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int kk = 0; kk < 16; kk++) {
-            float av[4], bv[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) { av[i] = sa[kk][ty * 4 + i]; bv[i] = sb[kk][tx * 4 + i]; }
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
-        }
-        __syncthreads();
-    }
     const bool reads_bias = epilogue_reads_bias(p.epilogue), reads_aux = epilogue_reads_aux(p.epilogue);
-    const int aux_f32 = p.in_f32 || (p.out_f32 && p.epilogue == TB200_EPI_AXPY);
-    for (int i = 0; i < 4; i++)
-        for (int j = 0; j < 4; j++) {
-            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-            if (m >= p.m || n >= p.n) continue;
-            const float b = reads_bias ? load_elem(p.bias, n, p.in_f32) : 0.0f;
-            const float x = reads_aux ? load_elem(p.aux, static_cast<long long>(m) * p.ld_aux + n, aux_f32) : 0.0f;
-            float pre = acc[i][j] * p.alpha;
-            const float v = epilogue_value<true>(p.epilogue, pre, b, x, pre);
-            store_elem(p.c, static_cast<long long>(m) * p.ldc + n, v, p.out_f32);
-            if (p.aux_out) store_elem(p.aux_out, static_cast<long long>(m) * p.ld_aux_out + n, pre, p.in_f32);
+    const int aux_dtype = p.epilogue == TB200_EPI_AXPY ? p.out_dtype : p.in_dtype;
+    for (int member = blockIdx.z; member < p.batch; member += gridDim.z) {
+        const long long a0 = member * p.stride_a, b0 = member * p.stride_b;
+        float acc[4][4] = {};
+        for (int k0 = 0; k0 < p.k; k0 += 16) {
+            for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+                // consecutive threads walk the operand's contiguous axis
+                int mm, kk;
+                if (p.a_mn) { mm = i & 63; kk = i >> 6; } else { kk = i & 15; mm = i >> 4; }
+                const int gm = m0 + mm, gk = k0 + kk;
+                float v = 0.0f;
+                if (gm < p.m && gk < p.k)
+                    v = load_elem(p.a, a0 + (p.a_mn ? static_cast<long long>(gk) * p.lda + gm
+                                                    : static_cast<long long>(gm) * p.lda + gk), p.in_dtype);
+                sa[kk][mm] = v;
+                int nn;
+                if (p.b_mn) { nn = i & 63; kk = i >> 6; } else { kk = i & 15; nn = i >> 4; }
+                const int gn = n0 + nn;
+                const int gk2 = k0 + kk;
+                v = 0.0f;
+                if (gn < p.n && gk2 < p.k)
+                    v = load_elem(p.b, b0 + (p.b_mn ? static_cast<long long>(gk2) * p.ldb + gn
+                                                    : static_cast<long long>(gn) * p.ldb + gk2), p.in_dtype);
+                sb[kk][nn] = v;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int kk = 0; kk < 16; kk++) {
+                float av[4], bv[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) { av[i] = sa[kk][ty * 4 + i]; bv[i] = sb[kk][tx * 4 + i]; }
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+            }
+            __syncthreads();
         }
+        for (int i = 0; i < 4; i++)
+            for (int j = 0; j < 4; j++) {
+                const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+                if (m >= p.m || n >= p.n) continue;
+                const float b = reads_bias ? load_elem(p.bias, member * p.stride_bias + n, p.in_dtype) : 0.0f;
+                const float x = reads_aux ? load_elem(p.aux, member * p.stride_aux + static_cast<long long>(m) * p.ld_aux + n, aux_dtype)
+                                          : 0.0f;
+                float pre = acc[i][j] * p.alpha;
+                const float v = epilogue_value<true>(p.epilogue, pre, b, x, pre);
+                store_elem(p.c, member * p.stride_c + static_cast<long long>(m) * p.ldc + n, v, p.out_dtype);
+                if (p.aux_out)
+                    store_elem(p.aux_out, member * p.stride_aux_out + static_cast<long long>(m) * p.ld_aux_out + n, pre,
+                               p.in_dtype);
+            }
+    }
 }
 
 // ------------------------------------------------------------ host side ----
@@ -595,71 +721,108 @@ int encode_fn(EncodeTiledFn *out) {
     return TB200_OK;
 }
 
-// A 2-D array `rows` x `cols` (cols contiguous, row pitch ld elements) as 128-byte-swizzled boxes of
-// box_rows rows x 128 bytes (64 BFloat16 or 32 Float32).
-int make_tmap(CUtensorMap *map, const void *base, int64_t cols, int64_t rows, int64_t ld, int box_rows,
-              bool f32 = false) {
+// `members` 2-D arrays of `rows` x `cols` (cols contiguous, row pitch ld elements, `member_stride` elements from
+// one array to the next) as 128-byte-swizzled boxes of box_rows rows x 128 bytes (64 16-bit or 32 Float32
+// elements) of one member.
+int make_tmap(CUtensorMap *map, const void *base, int64_t cols, int64_t rows, int64_t ld, int box_rows, int dtype,
+              int64_t members = 1, int64_t member_stride = 0) {
     EncodeTiledFn fn;
     int st = encode_fn(&fn);
     if (st) return st;
-    const cuuint64_t es = f32 ? 4 : 2;
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * es};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(box_rows)};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                    const_cast<void *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const cuuint64_t es = dtype == TB200_F32 ? 4 : 2;
+    if (members < 1) members = 1;
+    // an axis of one element still needs a legal pitch: any multiple of 16 bytes that covers the array
+    cuuint64_t pitch2 = static_cast<cuuint64_t>(member_stride) * es;
+    if (members == 1 || pitch2 == 0) pitch2 = ((static_cast<cuuint64_t>(rows) * ld * es + 15) / 16) * 16;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(members)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * es, pitch2};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    const CUtensorMapDataType type = dtype == TB200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                     : dtype == TB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    CUresult r = fn(map, type, 3, const_cast<void *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? TB200_OK : TB200_ERR_UNSUPPORTED;
 }
 
-template <int BN, int EPI, bool OUT_F32>
-int launch_tcgen05(GemmArgs &p, const DeviceInfo &dev, cudaStream_t stream) {
-    constexpr size_t stage_bytes = (BM + BN) * BK * 2;
-    constexpr size_t epilogue_bytes = 4 * 2 * kEpilogueStage;
-    int stages = static_cast<int>((dev.smem_optin - 2048 - epilogue_bytes) / stage_bytes);
-    if (stages > 8) stages = 8;
-    if (stages < 2) return TB200_ERR_UNSUPPORTED;
-    p.stages = stages;
-    p.tiles_m = static_cast<int>(ceil_div(p.m, BM));
-    p.tiles_n = static_cast<int>(ceil_div(p.n, BN));
-    const size_t smem = stages * stage_bytes + epilogue_bytes + 1024;
+// The kernel instantiation for (tile width, epilogue, result type), its shared-memory attribute set once per device.
+template <int BN, int EPI, int OUT>
+int kernel_for(const DeviceInfo &dev, const void **fn) {
     static std::mutex lock;
     static bool configured[64] = {};
-    {
-        std::lock_guard<std::mutex> hold(lock);
-        if (!configured[dev.device]) {
-            TB200_CUDA(cudaFuncSetAttribute(gemm_tcgen05<BN, EPI, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(dev.smem_optin - 1024)));
-            configured[dev.device] = true;
-        }
+    std::lock_guard<std::mutex> hold(lock);
+    if (!configured[dev.device]) {
+        TB200_CUDA(cudaFuncSetAttribute(gemm_tcgen05<BN, EPI, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(dev.smem_optin - 1024)));
+        configured[dev.device] = true;
     }
-    const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
-    const unsigned grid = static_cast<unsigned>(tiles < dev.sms ? tiles : dev.sms);
-    gemm_tcgen05<BN, EPI, OUT_F32><<<grid, kGemmThreads, smem, stream>>>(p);
-    TB200_CUDA(cudaGetLastError());
+    *fn = reinterpret_cast<const void *>(&gemm_tcgen05<BN, EPI, OUT>);
     return TB200_OK;
 }
 
-template <int BN, bool OUT_F32>
-int launch_by_epilogue(GemmArgs &p, const DeviceInfo &dev, cudaStream_t stream) {
-    switch (p.epilogue) {
-        case TB200_EPI_NONE: return launch_tcgen05<BN, TB200_EPI_NONE, OUT_F32>(p, dev, stream);
-        case TB200_EPI_BIAS: return launch_tcgen05<BN, TB200_EPI_BIAS, OUT_F32>(p, dev, stream);
-        case TB200_EPI_AXPY: return launch_tcgen05<BN, TB200_EPI_AXPY, OUT_F32>(p, dev, stream);
+template <int BN, int OUT>
+int kernel_by_epilogue(int epilogue, const DeviceInfo &dev, const void **fn) {
+    switch (epilogue) {
+        case TB200_EPI_NONE: return kernel_for<BN, TB200_EPI_NONE, OUT>(dev, fn);
+        case TB200_EPI_BIAS: return kernel_for<BN, TB200_EPI_BIAS, OUT>(dev, fn);
+        case TB200_EPI_AXPY: return kernel_for<BN, TB200_EPI_AXPY, OUT>(dev, fn);
         default: break;
     }
     // activations and their pullbacks are instantiated for BFloat16 results only
-    if constexpr (!OUT_F32) {
-        switch (p.epilogue) {
-            case TB200_EPI_BIAS_GELU: return launch_tcgen05<BN, TB200_EPI_BIAS_GELU, false>(p, dev, stream);
-            case TB200_EPI_BIAS_TANH: return launch_tcgen05<BN, TB200_EPI_BIAS_TANH, false>(p, dev, stream);
-            case TB200_EPI_MUL_GELU_GRAD: return launch_tcgen05<BN, TB200_EPI_MUL_GELU_GRAD, false>(p, dev, stream);
-            case TB200_EPI_MUL_TANH_GRAD: return launch_tcgen05<BN, TB200_EPI_MUL_TANH_GRAD, false>(p, dev, stream);
+    if constexpr (OUT == OUT_BF16) {
+        switch (epilogue) {
+            case TB200_EPI_BIAS_GELU: return kernel_for<BN, TB200_EPI_BIAS_GELU, OUT>(dev, fn);
+            case TB200_EPI_BIAS_TANH: return kernel_for<BN, TB200_EPI_BIAS_TANH, OUT>(dev, fn);
+            case TB200_EPI_MUL_GELU_GRAD: return kernel_for<BN, TB200_EPI_MUL_GELU_GRAD, OUT>(dev, fn);
+            case TB200_EPI_MUL_TANH_GRAD: return kernel_for<BN, TB200_EPI_MUL_TANH_GRAD, OUT>(dev, fn);
             default: break;
         }
     }
     return TB200_ERR_UNSUPPORTED;
+}
+
+int kernel_by_shape(int bn, int out_dtype, int epilogue, const DeviceInfo &dev, const void **fn) {
+    if (bn == 256) {
+        if (out_dtype == TB200_F32) return kernel_by_epilogue<256, OUT_F32>(epilogue, dev, fn);
+        if (out_dtype == TB200_F16) return kernel_by_epilogue<256, OUT_F16>(epilogue, dev, fn);
+        return kernel_by_epilogue<256, OUT_BF16>(epilogue, dev, fn);
+    }
+    if (out_dtype == TB200_F32) return kernel_by_epilogue<128, OUT_F32>(epilogue, dev, fn);
+    if (out_dtype == TB200_F16) return kernel_by_epilogue<128, OUT_F16>(epilogue, dev, fn);
+    return kernel_by_epilogue<128, OUT_BF16>(epilogue, dev, fn);
+}
+
+bool is_activation(int e) {
+    return e == TB200_EPI_BIAS_GELU || e == TB200_EPI_BIAS_TANH || e == TB200_EPI_MUL_GELU_GRAD ||
+           e == TB200_EPI_MUL_TANH_GRAD;
+}
+
+// How many ranges the sum over k is cut into, and how many 64-wide blocks each takes.
+void choose_split(const tb200_gemm_desc &d, int bn, int sms, int *splits, int *kb_per_split) {
+    const int64_t batch = d.batch > 1 ? d.batch : 1;
+    const int64_t tiles = ceil_div(d.m, BM) * ceil_div(d.n, bn) * batch;
+    const int64_t num_kb = ceil_div(d.k, BK);
+    int64_t s = 1;
+    if (d.split_k > 1) s = d.split_k;
+    else if (d.split_k == 0 && tiles * 4 <= sms && num_kb >= 8) s = sms / tiles;
+    if (s > num_kb / 2) s = num_kb / 2;   // a range of fewer than two blocks is not worth a work item
+    if (s < 1) s = 1;
+    const int64_t per = ceil_div(num_kb, s);
+    *kb_per_split = static_cast<int>(per < 1 ? 1 : per);
+    *splits = static_cast<int>(num_kb > 0 ? ceil_div(num_kb, *kb_per_split) : 1);
+}
+
+int tile_width(const tb200_gemm_desc &d) {
+    // 128 x 256 tiles halve the operand bytes per flop of 128 x 128 ones and measured faster on every
+    // shape wide enough to hold one, even when they leave a few SMs idle
+    return (d.tile_n == 256 || (d.tile_n == 0 && d.n > 128)) ? 256 : 128;
+}
+
+size_t split_workspace_bytes(const tb200_gemm_desc &d, int splits) {
+    const int64_t batch = d.batch > 1 ? d.batch : 1;
+    const int64_t ld = (d.n + 3) / 4 * 4;
+    return static_cast<size_t>(splits) * batch * d.m * ld * sizeof(float);
 }
 
 }  // namespace
@@ -667,90 +830,286 @@ int launch_by_epilogue(GemmArgs &p, const DeviceInfo &dev, cudaStream_t stream) 
 
 using namespace tb200;
 
-extern "C" int tb200_gemm(const tb200_gemm_desc *d, const void *a, const void *b, void *c, const void *bias,
-                          const void *aux, void *aux_out, void *stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+// Everything a product's launch needs, worked out once.
+struct tb200_gemm_plan {
+    tb200_gemm_desc desc;
+    const void *a, *b, *bias, *aux;
+    void *c, *aux_out;
+    int device;
+    bool nothing;        // an empty product
+    bool tensor;         // the tcgen05 kernel (else the generic one)
+    GemmArgs args;
+    const void *kernel;
+    unsigned grid;
+    size_t smem;
+    bool merge;          // split-K: a second launch
+    MergeArgs merge_args;
+    unsigned merge_grid;
+    SimtArgs simt;
+    dim3 simt_grid;
+};
+
+namespace {
+
+int validate(const tb200_gemm_desc *d, const void *a, const void *b, void *c, const void *bias, const void *aux,
+             void *aux_out) {
     if (!d) return TB200_ERR_NULL;
     if (d->m < 0 || d->n < 0 || d->k < 0 || d->m > INT32_MAX || d->n > INT32_MAX || d->k > INT32_MAX)
         return TB200_ERR_SHAPE;
-    if ((d->in_dtype != TB200_F32 && d->in_dtype != TB200_BF16) ||
-        (d->out_dtype != TB200_F32 && d->out_dtype != TB200_BF16))
-        return TB200_ERR_DTYPE;
+    const auto known = [](int t) { return t == TB200_F32 || t == TB200_BF16 || t == TB200_F16; };
+    if (!known(d->in_dtype) || !known(d->out_dtype)) return TB200_ERR_DTYPE;
+    // a 16-bit result has the operands' type, or the operands are Float32
+    if (d->out_dtype != TB200_F32 && d->in_dtype != TB200_F32 && d->out_dtype != d->in_dtype) return TB200_ERR_DTYPE;
     if (d->epilogue < TB200_EPI_NONE || d->epilogue > TB200_EPI_AXPY) return TB200_ERR_UNSUPPORTED;
+    if (d->batch < 0 || d->batch > (1 << 24) || d->split_k < 0) return TB200_ERR_SHAPE;
     if (d->m == 0 || d->n == 0) return TB200_OK;
     const int64_t a_inner = d->a_layout == TB200_MN_MAJOR ? d->m : d->k;
     const int64_t b_inner = d->b_layout == TB200_MN_MAJOR ? d->n : d->k;
     if (d->lda < a_inner || d->ldb < b_inner || d->ldc < d->n) return TB200_ERR_SHAPE;
+    if (d->batch > 1) {
+        if (d->stride_a < 0 || d->stride_b < 0 || d->stride_bias < 0 || d->stride_aux < 0) return TB200_ERR_SHAPE;
+        // members must not write over one another
+        if (d->stride_c < (d->m - 1) * d->ldc + d->n) return TB200_ERR_SHAPE;
+        if (aux_out && d->stride_aux_out < (d->m - 1) * d->ld_aux_out + d->n) return TB200_ERR_SHAPE;
+    }
     if (!c || (d->k > 0 && (!a || !b))) return TB200_ERR_NULL;
-    const bool needs_bias = d->epilogue == TB200_EPI_BIAS || d->epilogue == TB200_EPI_BIAS_GELU ||
-                            d->epilogue == TB200_EPI_BIAS_TANH;
-    const bool needs_aux = d->epilogue == TB200_EPI_MUL_GELU_GRAD || d->epilogue == TB200_EPI_MUL_TANH_GRAD ||
-                           d->epilogue == TB200_EPI_AXPY;
-    if ((needs_bias && !bias) || (needs_aux && !aux)) return TB200_ERR_NULL;
-    if (needs_aux && d->ld_aux < d->n) return TB200_ERR_SHAPE;
+    if ((epilogue_reads_bias(d->epilogue) && !bias) || (epilogue_reads_aux(d->epilogue) && !aux)) return TB200_ERR_NULL;
+    if (epilogue_reads_aux(d->epilogue) && d->ld_aux < d->n) return TB200_ERR_SHAPE;
     if (aux_out && d->ld_aux_out < d->n) return TB200_ERR_SHAPE;
     const size_t in_size = dtype_size(d->in_dtype), out_size = dtype_size(d->out_dtype);
     if (!aligned_to(a, in_size) || !aligned_to(b, in_size) || !aligned_to(c, out_size) ||
         !aligned_to(bias, in_size) || !aligned_to(aux, 2) || !aligned_to(aux_out, in_size))
         return TB200_ERR_ALIGN;
-    DeviceInfo dev;
-    int st = current_device(&dev);
-    if (st) return st;
-
-    const bool activation = d->epilogue == TB200_EPI_BIAS_GELU || d->epilogue == TB200_EPI_BIAS_TANH ||
-                            d->epilogue == TB200_EPI_MUL_GELU_GRAD || d->epilogue == TB200_EPI_MUL_TANH_GRAD;
-    const bool tma_ok = d->in_dtype == TB200_BF16 && d->k > 0 && aligned_to(a, 16) && aligned_to(b, 16) &&
-                        d->lda % 8 == 0 && d->ldb % 8 == 0 && !d->force_simt &&
-                        !(activation && d->out_dtype == TB200_F32);
-    if (tma_ok) {
-        GemmArgs p{};
-        p.c = c; p.bias = bias; p.aux = aux; p.aux_out = aux_out;
-        p.ldc = d->ldc; p.ld_aux = d->ld_aux; p.ld_aux_out = d->ld_aux_out;
-        p.alpha = d->alpha; p.m = static_cast<int>(d->m); p.n = static_cast<int>(d->n); p.k = static_cast<int>(d->k);
-        p.epilogue = d->epilogue; p.out_f32 = d->out_dtype == TB200_F32;
-        p.a_mn = d->a_layout == TB200_MN_MAJOR; p.b_mn = d->b_layout == TB200_MN_MAJOR;
-        // 128 x 256 tiles halve the operand bytes per flop of 128 x 128 ones and measured faster on every
-        // shape wide enough to hold one, even when they leave a few SMs idle
-        const bool wide = d->tile_n == 256 || (d->tile_n == 0 && d->n > 128);
-        const int bn = wide ? 256 : 128;
-        if (p.a_mn) st = make_tmap(&p.tmap_a, a, d->m, d->k, d->lda, 64);
-        else st = make_tmap(&p.tmap_a, a, d->k, d->m, d->lda, BM);
-        if (st) return st;
-        if (p.b_mn) st = make_tmap(&p.tmap_b, b, d->n, d->k, d->ldb, 64);
-        else st = make_tmap(&p.tmap_b, b, d->k, d->n, d->ldb, bn);
-        if (st) return st;
-        // the epilogue goes through shared memory and TMA when every array it touches can be
-        // described to the TMA unit; otherwise each thread stores its own row
-        const bool out_f32 = d->out_dtype == TB200_F32;
-        const size_t aux_size = (d->epilogue == TB200_EPI_AXPY) ? out_size : 2;
-        bool tma_epi = !d->direct_epilogue && aligned_to(c, 16) && (d->ldc * out_size) % 16 == 0;
-        if (needs_aux) tma_epi = tma_epi && aux_size == out_size && aligned_to(aux, 16) && (d->ld_aux * aux_size) % 16 == 0;
-        if (aux_out) tma_epi = tma_epi && !out_f32 && aligned_to(aux_out, 16) && (d->ld_aux_out * 2) % 16 == 0;
-        if (tma_epi) {
-            if ((st = make_tmap(&p.tmap_c, c, d->n, d->m, d->ldc, 32, out_f32))) return st;
-            if (needs_aux && (st = make_tmap(&p.tmap_aux, aux, d->n, d->m, d->ld_aux, 32, out_f32))) return st;
-            if (aux_out && (st = make_tmap(&p.tmap_aux_out, aux_out, d->n, d->m, d->ld_aux_out, 32, false))) return st;
-        }
-        p.tma_epilogue = tma_epi;
-        if (out_f32) return wide ? launch_by_epilogue<256, true>(p, dev, stream) : launch_by_epilogue<128, true>(p, dev, stream);
-        return wide ? launch_by_epilogue<256, false>(p, dev, stream) : launch_by_epilogue<128, false>(p, dev, stream);
-    }
-
-    SimtArgs p{};
-    p.a = a; p.b = b; p.c = c; p.bias = bias; p.aux = aux; p.aux_out = aux_out;
-    p.lda = d->lda; p.ldb = d->ldb; p.ldc = d->ldc; p.ld_aux = d->ld_aux; p.ld_aux_out = d->ld_aux_out;
-    p.alpha = d->alpha; p.m = static_cast<int>(d->m); p.n = static_cast<int>(d->n); p.k = static_cast<int>(d->k);
-    p.epilogue = d->epilogue; p.in_f32 = d->in_dtype == TB200_F32; p.out_f32 = d->out_dtype == TB200_F32;
-    p.a_mn = d->a_layout == TB200_MN_MAJOR; p.b_mn = d->b_layout == TB200_MN_MAJOR;
-    dim3 grid(static_cast<unsigned>(ceil_div(d->n, 64)), static_cast<unsigned>(ceil_div(d->m, 64)));
-    if (grid.y > 65535) return TB200_ERR_SHAPE;
-    gemm_simt<<<grid, 256, 0, stream>>>(p);
-    TB200_CUDA(cudaGetLastError());
     return TB200_OK;
 }
 
+// Fills `plan` for the current device from its desc and operand addresses.
+int prepare(tb200_gemm_plan *plan) {
+    const tb200_gemm_desc *d = &plan->desc;
+    const void *a = plan->a, *b = plan->b, *bias = plan->bias, *aux = plan->aux;
+    void *c = plan->c, *aux_out = plan->aux_out;
+    int st = validate(d, a, b, c, bias, aux, aux_out);
+    if (st) return st;
+    plan->nothing = d->m == 0 || d->n == 0 || d->batch < 0;
+    if (plan->nothing) return TB200_OK;
+    DeviceInfo dev;
+    if ((st = current_device(&dev))) return st;
+    plan->device = dev.device;
+    const int batch = static_cast<int>(d->batch > 1 ? d->batch : 1);
+    const bool batched = batch > 1;
+    const bool needs_aux = epilogue_reads_aux(d->epilogue);
+    const size_t in_size = dtype_size(d->in_dtype), out_size = dtype_size(d->out_dtype);
+    const bool half_in = d->in_dtype == TB200_BF16 || d->in_dtype == TB200_F16;
+    // Float16 results of the activation epilogues and Float32 results of any activation: generic kernel
+    const bool instantiated = !(is_activation(d->epilogue) && (d->out_dtype != TB200_BF16 || d->in_dtype != TB200_BF16));
+    const bool strides_ok = !batched || ((d->stride_a * in_size) % 16 == 0 && (d->stride_b * in_size) % 16 == 0);
+    const bool tma_ok = half_in && d->k > 0 && aligned_to(a, 16) && aligned_to(b, 16) && d->lda % 8 == 0 &&
+                        d->ldb % 8 == 0 && !d->force_simt && instantiated && strides_ok;
+    plan->tensor = tma_ok;
+    plan->merge = false;
+    if (tma_ok) {
+        GemmArgs &p = plan->args;
+        p = GemmArgs{};
+        const int bn = tile_width(*d);
+        int splits = 1, kb_per = static_cast<int>(ceil_div(d->k, BK));
+        choose_split(*d, bn, dev.sms, &splits, &kb_per);
+        if (splits > 1 && (!d->workspace || !aligned_to(d->workspace, 16) ||
+                           d->workspace_bytes < split_workspace_bytes(*d, splits))) {
+            splits = 1;
+            kb_per = static_cast<int>(ceil_div(d->k, BK));
+        }
+        p.m = static_cast<int>(d->m); p.n = static_cast<int>(d->n); p.k = static_cast<int>(d->k);
+        p.in_f16 = d->in_dtype == TB200_F16;
+        p.a_mn = d->a_layout == TB200_MN_MAJOR; p.b_mn = d->b_layout == TB200_MN_MAJOR;
+        p.a_batched = batched && d->stride_a != 0; p.b_batched = batched && d->stride_b != 0;
+        p.batch = batch; p.splits = splits; p.kb_per_split = kb_per;
+        p.debug = d->debug;
+        p.wait_ns = d->debug ? 20000000ull : 2000000000ull;
+        p.tiles_m = static_cast<int>(ceil_div(d->m, BM));
+        p.tiles_n = static_cast<int>(ceil_div(d->n, bn));
+        const int64_t am = p.a_batched ? batch : 1, bm = p.b_batched ? batch : 1;
+        if (p.a_mn) st = make_tmap(&p.tmap_a, a, d->m, d->k, d->lda, 64, d->in_dtype, am, d->stride_a);
+        else st = make_tmap(&p.tmap_a, a, d->k, d->m, d->lda, BM, d->in_dtype, am, d->stride_a);
+        if (st) return st;
+        if (p.b_mn) st = make_tmap(&p.tmap_b, b, d->n, d->k, d->ldb, 64, d->in_dtype, bm, d->stride_b);
+        else st = make_tmap(&p.tmap_b, b, d->k, d->n, d->ldb, bn, d->in_dtype, bm, d->stride_b);
+        if (st) return st;
+        int kernel_epilogue = d->epilogue, kernel_out = d->out_dtype;
+        if (splits > 1) {
+            // the ranges' partial tiles go to the workspace as they are; the merge applies alpha and the epilogue
+            const int64_t ldp = (d->n + 3) / 4 * 4;
+            p.c = d->workspace; p.ldc = ldp; p.stride_c = d->m * ldp;
+            p.alpha = 1.0f; p.epilogue = TB200_EPI_NONE;
+            kernel_epilogue = TB200_EPI_NONE; kernel_out = TB200_F32;
+            p.tma_epilogue = !d->direct_epilogue;
+            if (p.tma_epilogue &&
+                (st = make_tmap(&p.tmap_c, d->workspace, d->n, d->m, ldp, 32, TB200_F32, static_cast<int64_t>(batch) * splits,
+                                d->m * ldp)))
+                return st;
+            MergeArgs &q = plan->merge_args;
+            q = MergeArgs{};
+            q.partial = static_cast<const float *>(d->workspace); q.c = c; q.bias = bias; q.aux = aux; q.aux_out = aux_out;
+            q.ld_partial = ldp; q.ldc = d->ldc; q.ld_aux = d->ld_aux; q.ld_aux_out = d->ld_aux_out;
+            q.stride_c = d->stride_c; q.stride_bias = d->stride_bias; q.stride_aux = d->stride_aux;
+            q.stride_aux_out = d->stride_aux_out;
+            q.alpha = d->alpha; q.m = p.m; q.n = p.n; q.batch = batch; q.splits = splits; q.epilogue = d->epilogue;
+            q.in_dtype = d->in_dtype; q.out_dtype = d->out_dtype;
+            const long long blocks = ceil_div(static_cast<int64_t>(batch) * d->m * d->n, 256);
+            plan->merge_grid = static_cast<unsigned>(blocks < dev.sms * 8 ? blocks : dev.sms * 8);
+            plan->merge = true;
+        } else {
+            p.c = c; p.bias = bias; p.aux = aux; p.aux_out = aux_out;
+            p.ldc = d->ldc; p.ld_aux = d->ld_aux; p.ld_aux_out = d->ld_aux_out;
+            p.stride_c = batched ? d->stride_c : 0; p.stride_bias = batched ? d->stride_bias : 0;
+            p.stride_aux = batched ? d->stride_aux : 0; p.stride_aux_out = batched ? d->stride_aux_out : 0;
+            p.alpha = d->alpha; p.epilogue = d->epilogue;
+            // the epilogue goes through shared memory and TMA when every array it touches can be
+            // described to the TMA unit; otherwise each thread stores its own row
+            const size_t aux_size = (d->epilogue == TB200_EPI_AXPY) ? out_size : 2;
+            const int aux_dtype = d->epilogue == TB200_EPI_AXPY ? d->out_dtype : d->in_dtype;
+            const auto pitch_ok = [&](int64_t stride, size_t es) { return !batched || (stride * es) % 16 == 0; };
+            bool tma_epi = !d->direct_epilogue && aligned_to(c, 16) && (d->ldc * out_size) % 16 == 0 &&
+                           pitch_ok(d->stride_c, out_size);
+            if (needs_aux)
+                tma_epi = tma_epi && aux_size == out_size && aligned_to(aux, 16) && (d->ld_aux * aux_size) % 16 == 0 &&
+                          pitch_ok(d->stride_aux, aux_size);
+            if (aux_out)
+                tma_epi = tma_epi && d->out_dtype != TB200_F32 && aligned_to(aux_out, 16) && (d->ld_aux_out * 2) % 16 == 0 &&
+                          pitch_ok(d->stride_aux_out, 2);
+            if (tma_epi) {
+                if ((st = make_tmap(&p.tmap_c, c, d->n, d->m, d->ldc, 32, d->out_dtype, batch, d->stride_c))) return st;
+                if (needs_aux && (st = make_tmap(&p.tmap_aux, aux, d->n, d->m, d->ld_aux, 32, aux_dtype,
+                                                 d->stride_aux ? batch : 1, d->stride_aux)))
+                    return st;
+                if (needs_aux && batched && d->stride_aux == 0) tma_epi = false;   // a shared aux: plain loads
+                if (aux_out && (st = make_tmap(&p.tmap_aux_out, aux_out, d->n, d->m, d->ld_aux_out, 32, d->in_dtype, batch,
+                                               d->stride_aux_out)))
+                    return st;
+            }
+            p.tma_epilogue = tma_epi;
+        }
+        if ((st = kernel_by_shape(bn, kernel_out, kernel_epilogue, dev, &plan->kernel))) return st;
+        const size_t stage_bytes = static_cast<size_t>(BM + bn) * BK * 2;
+        const size_t epilogue_bytes = 4 * 2 * kEpilogueStage;
+        int stages = static_cast<int>((dev.smem_optin - 2048 - epilogue_bytes) / stage_bytes);
+        if (stages > 8) stages = 8;
+        if (stages < 2) return TB200_ERR_UNSUPPORTED;
+        p.stages = stages;
+        plan->smem = stages * stage_bytes + epilogue_bytes + 1024;
+        const long long items = static_cast<long long>(p.tiles_m) * p.tiles_n * batch * splits;
+        if (items > INT32_MAX) return TB200_ERR_SHAPE;
+        plan->grid = static_cast<unsigned>(items < dev.sms ? items : dev.sms);
+        return TB200_OK;
+    }
+
+    SimtArgs &p = plan->simt;
+    p = SimtArgs{};
+    p.a = a; p.b = b; p.c = c; p.bias = bias; p.aux = aux; p.aux_out = aux_out;
+    p.lda = d->lda; p.ldb = d->ldb; p.ldc = d->ldc; p.ld_aux = d->ld_aux; p.ld_aux_out = d->ld_aux_out;
+    if (batched) {
+        p.stride_a = d->stride_a; p.stride_b = d->stride_b; p.stride_c = d->stride_c; p.stride_bias = d->stride_bias;
+        p.stride_aux = d->stride_aux; p.stride_aux_out = d->stride_aux_out;
+    }
+    p.alpha = d->alpha; p.m = static_cast<int>(d->m); p.n = static_cast<int>(d->n); p.k = static_cast<int>(d->k);
+    p.batch = batch;
+    p.epilogue = d->epilogue; p.in_dtype = d->in_dtype; p.out_dtype = d->out_dtype;
+    p.a_mn = d->a_layout == TB200_MN_MAJOR; p.b_mn = d->b_layout == TB200_MN_MAJOR;
+    plan->simt_grid = dim3(static_cast<unsigned>(ceil_div(d->n, 64)), static_cast<unsigned>(ceil_div(d->m, 64)),
+                           static_cast<unsigned>(batch < 65535 ? batch : 65535));
+    if (plan->simt_grid.y > 65535) return TB200_ERR_SHAPE;
+    return TB200_OK;
+}
+
+int run(const tb200_gemm_plan *plan, cudaStream_t stream) {
+    if (plan->nothing) return TB200_OK;
+    if (!plan->tensor) {
+        gemm_simt<<<plan->simt_grid, 256, 0, stream>>>(plan->simt);
+        TB200_CUDA(cudaGetLastError());
+        return TB200_OK;
+    }
+    void *params[1] = {const_cast<GemmArgs *>(&plan->args)};
+    TB200_CUDA(cudaLaunchKernel(plan->kernel, dim3(plan->grid), dim3(kGemmThreads), params, plan->smem, stream));
+    if (plan->merge) {
+        gemm_splitk_merge<<<plan->merge_grid, 256, 0, stream>>>(plan->merge_args);
+        TB200_CUDA(cudaGetLastError());
+    }
+    return TB200_OK;
+}
+
+void fill(tb200_gemm_plan *plan, const tb200_gemm_desc *d, const void *a, const void *b, void *c, const void *bias,
+          const void *aux, void *aux_out) {
+    plan->desc = *d;
+    plan->a = a; plan->b = b; plan->c = c; plan->bias = bias; plan->aux = aux; plan->aux_out = aux_out;
+}
+
+}  // namespace
+
+extern "C" size_t tb200_gemm_workspace_bytes(const tb200_gemm_desc *d) {
+    if (!d || d->m <= 0 || d->n <= 0 || d->k <= 0 || d->split_k == 1) return 0;
+    DeviceInfo dev;
+    int sms = 148;
+    if (current_device(&dev) == TB200_OK) sms = dev.sms;
+    int splits = 1, per = 1;
+    choose_split(*d, tile_width(*d), sms, &splits, &per);
+    return splits > 1 ? split_workspace_bytes(*d, splits) : 0;
+}
+
+extern "C" int tb200_gemm(const tb200_gemm_desc *d, const void *a, const void *b, void *c, const void *bias,
+                          const void *aux, void *aux_out, void *stream_) {
+    if (!d) return TB200_ERR_NULL;
+    tb200_gemm_plan plan;
+    fill(&plan, d, a, b, c, bias, aux, aux_out);
+    const int st = prepare(&plan);
+    return st ? st : run(&plan, static_cast<cudaStream_t>(stream_));
+}
+
+extern "C" int tb200_gemm_plan_create(const tb200_gemm_desc *d, const void *a, const void *b, void *c, const void *bias,
+                                      const void *aux, void *aux_out, tb200_gemm_plan **out) {
+    if (!d || !out) return TB200_ERR_NULL;
+    *out = nullptr;
+    tb200_gemm_plan *plan = new (std::nothrow) tb200_gemm_plan;
+    if (!plan) return TB200_ERR_WORKSPACE;
+    fill(plan, d, a, b, c, bias, aux, aux_out);
+    const int st = prepare(plan);
+    if (st) { delete plan; return st; }
+    *out = plan;
+    return TB200_OK;
+}
+
+extern "C" int tb200_gemm_plan_launch(const tb200_gemm_plan *plan, void *stream_) {
+    if (!plan) return TB200_ERR_NULL;
+    return run(plan, static_cast<cudaStream_t>(stream_));
+}
+
+extern "C" int tb200_gemm_plan_repoint(tb200_gemm_plan *plan, int operand, const void *address) {
+    if (!plan) return TB200_ERR_NULL;
+    tb200_gemm_plan next = *plan;
+    switch (operand) {
+        case TB200_GEMM_A: next.a = address; break;
+        case TB200_GEMM_B: next.b = address; break;
+        case TB200_GEMM_C: next.c = const_cast<void *>(address); break;
+        case TB200_GEMM_BIAS: next.bias = address; break;
+        case TB200_GEMM_AUX: next.aux = address; break;
+        case TB200_GEMM_AUX_OUT: next.aux_out = const_cast<void *>(address); break;
+        case TB200_GEMM_WORKSPACE: next.desc.workspace = const_cast<void *>(address); break;
+        default: return TB200_ERR_SHAPE;
+    }
+    const int st = prepare(&next);
+    if (st) return st;          // the plan stays as it was
+    // a new address must leave the plan on the kernels it was built for (the reference requires the
+    // alignment compiled for, src/Compiler/Implement/Implement.jl:162-175)
+    if (next.tensor != plan->tensor || (next.tensor && (next.kernel != plan->kernel ||
+                                                         next.args.tma_epilogue != plan->args.tma_epilogue)))
+        return TB200_ERR_ALIGN;
+    *plan = next;
+    return TB200_OK;
+}
+
+extern "C" void tb200_gemm_plan_destroy(tb200_gemm_plan *plan) { delete plan; }
+
 // Synchronises the device and returns (then clears) the error code a tensor-core kernel recorded when one
-// of its bounded waits ran out: 0 none, 1 loader, 2 accumulator hand-back, 3 operands, 4 epilogue.
+// of its bounded waits ran out: 0 none, 1 loader, 2 accumulator hand-back, 3 operands, 4 epilogue, 5 the
+// epilogue's own operand.
 extern "C" int tb200_device_error(void) {
     int code = 0, zero = 0;
     TB200_CUDA(cudaDeviceSynchronize());
@@ -758,6 +1117,22 @@ extern "C" int tb200_device_error(void) {
     if (code) TB200_CUDA(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
     return code;
 }
+
+namespace {
+// Device time of `reps` launches of the product after one warm-up launch; negative status on failure.
+int time_variant(const tb200_gemm_desc &trial, const void *a, const void *b, void *c, const void *bias, const void *aux,
+                 void *aux_out, cudaStream_t stream, cudaEvent_t t0, cudaEvent_t t1, int reps, float *ms) {
+    int status = tb200_gemm(&trial, a, b, c, bias, aux, aux_out, stream);   // warm-up and validation
+    if (status) return status;
+    if (cudaEventRecord(t0, stream) != cudaSuccess) return TB200_ERR_CUDA;
+    for (int rep = 0; rep < reps && !status; rep++) status = tb200_gemm(&trial, a, b, c, bias, aux, aux_out, stream);
+    if (status) return status;
+    if (cudaEventRecord(t1, stream) != cudaSuccess || cudaEventSynchronize(t1) != cudaSuccess ||
+        cudaEventElapsedTime(ms, t0, t1) != cudaSuccess)
+        return TB200_ERR_CUDA;
+    return TB200_OK;
+}
+}  // namespace
 
 // Times the compiled-in tile variants of one product on its own operands and returns the faster one's
 // tile_n (128 or 256) -- the measured stage of the reference's search over a claim's `variants`
@@ -771,8 +1146,8 @@ extern "C" int tb200_gemm_tune(const tb200_gemm_desc *d, const void *a, const vo
     if (!d) return TB200_ERR_NULL;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const int fallback = d->n > 128 ? 256 : 128;
-    const bool measurable = d->in_dtype == TB200_BF16 && d->n > 128 && d->m > 0 && d->k > 0 && !d->force_simt &&
-                            d->epilogue != TB200_EPI_AXPY;
+    const bool measurable = (d->in_dtype == TB200_BF16 || d->in_dtype == TB200_F16) && d->n > 128 && d->m > 0 &&
+                            d->k > 0 && !d->force_simt && d->epilogue != TB200_EPI_AXPY;
     tb200_gemm_desc trial = *d;
     if (!measurable) {
         trial.tile_n = 0;
@@ -786,16 +1161,51 @@ extern "C" int tb200_gemm_tune(const tb200_gemm_desc *d, const void *a, const vo
     int best = fallback, status = TB200_OK;
     for (int width : {128, 256}) {
         trial.tile_n = width;
-        if ((status = tb200_gemm(&trial, a, b, c, bias, aux, aux_out, stream_))) break;   // warm-up and validation
-        if (cudaEventRecord(t0, stream) != cudaSuccess) { status = TB200_ERR_CUDA; break; }
-        for (int rep = 0; rep < 3 && !status; rep++) status = tb200_gemm(&trial, a, b, c, bias, aux, aux_out, stream_);
-        if (status) break;
         float ms = 0.0f;
-        if (cudaEventRecord(t1, stream) != cudaSuccess || cudaEventSynchronize(t1) != cudaSuccess ||
-            cudaEventElapsedTime(&ms, t0, t1) != cudaSuccess) { status = TB200_ERR_CUDA; break; }
+        if ((status = time_variant(trial, a, b, c, bias, aux, aux_out, stream, t0, t1, 3, &ms))) break;
         if (width == 128 || ms < best_ms) { best_ms = ms; best = width; }
     }
     cudaEventDestroy(t0);
     cudaEventDestroy(t1);
     return status ? status : best;
+}
+
+// The search over every compiled-in variant: tile width x split or not x how the result is stored.
+extern "C" int tb200_gemm_tune_desc(tb200_gemm_desc *d, const void *a, const void *b, void *c, const void *bias,
+                                    const void *aux, void *aux_out, void *stream_) {
+    if (!d) return TB200_ERR_NULL;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    tb200_gemm_desc trial = *d;
+    trial.tile_n = 0; trial.split_k = 0; trial.direct_epilogue = 0;
+    int status = tb200_gemm(&trial, a, b, c, bias, aux, aux_out, stream_);
+    if (status) return status;
+    const bool measurable = (d->in_dtype == TB200_BF16 || d->in_dtype == TB200_F16) && d->m > 0 && d->k > 0 &&
+                            !d->force_simt && d->epilogue != TB200_EPI_AXPY;
+    if (!measurable) { d->tile_n = 0; d->split_k = 0; d->direct_epilogue = 0; return TB200_OK; }
+    cudaEvent_t t0, t1;
+    TB200_CUDA(cudaEventCreate(&t0));
+    TB200_CUDA(cudaEventCreate(&t1));
+    float best_ms = -1.0f;
+    tb200_gemm_desc best = trial;
+    for (int width : {128, 256}) {
+        if (width == 256 && d->n <= 128) continue;
+        for (int split : {1, 0}) {
+            trial.tile_n = width; trial.split_k = split;
+            if (split == 0 && tb200_gemm_workspace_bytes(&trial) == 0) continue;           // would not split
+            if (split == 0 && (!d->workspace || d->workspace_bytes < tb200_gemm_workspace_bytes(&trial))) continue;
+            for (int direct : {0, 1}) {
+                trial.direct_epilogue = direct;
+                float ms = 0.0f;
+                if ((status = time_variant(trial, a, b, c, bias, aux, aux_out, stream, t0, t1, 3, &ms))) break;
+                if (best_ms < 0.0f || ms < best_ms) { best_ms = ms; best = trial; }
+            }
+            if (status) break;
+        }
+        if (status) break;
+    }
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+    if (status) return status;
+    d->tile_n = best.tile_n; d->split_k = best.split_k; d->direct_epilogue = best.direct_epilogue;
+    return TB200_OK;
 }

@@ -131,13 +131,26 @@ __global__ void __launch_bounds__(256) colsum_merge_kernel(const float *partial,
 }
 
 // y = y + alpha * x, elementwise; x may have another element type than y (BFloat16 gradients
-// into Float32 or BFloat16 weights).
-template <typename TY, typename TX>
+// into Float32 or BFloat16 weights).  VEC: both arrays 16-byte aligned, eight elements a thread in one
+// or two 128-bit accesses per array and the ragged end one element a thread; otherwise (a view that
+// starts at an odd element) every element goes alone.
+template <typename TY, typename TX, bool VEC>
 __global__ void __launch_bounds__(kThreads) axpy_kernel(TY *y, const TX *x, float alpha, long long count) {
-    constexpr int EPV = 8;   // 8 elements a thread: one or two 128-bit accesses per array
+    const long long first = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+    const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+    if constexpr (!VEC) {
+        for (long long i = first; i < count; i += stride) {
+            float yv[1], xv[1];
+            Access<TY, false>::load(y + i, yv);
+            Access<TX, false>::load(x + i, xv);
+            yv[0] = fmaf(alpha, xv[0], yv[0]);
+            Access<TY, false>::store(y + i, yv);
+        }
+        return;
+    }
+    constexpr int EPV = 8;
     const long long nvec = count / EPV;
-    for (long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; i < nvec;
-         i += static_cast<long long>(gridDim.x) * kThreads) {
+    for (long long i = first; i < nvec; i += stride) {
         float yv[EPV], xv[EPV];
 #pragma unroll
         for (int j = 0; j < EPV; j += Access<TY, true>::EPV) Access<TY, true>::load(y + i * EPV + j, yv + j);
@@ -148,9 +161,8 @@ __global__ void __launch_bounds__(kThreads) axpy_kernel(TY *y, const TX *x, floa
 #pragma unroll
         for (int j = 0; j < EPV; j += Access<TY, true>::EPV) Access<TY, true>::store(y + i * EPV + j, yv + j);
     }
-    // the ragged end, one element a thread
-    const long long tail = nvec * EPV + blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
-    if (tail < count && blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x < EPV) {
+    const long long tail = nvec * EPV + first;
+    if (tail < count && first < EPV) {
         float yv[1], xv[1];
         Access<TY, false>::load(y + tail, yv);
         Access<TX, false>::load(x + tail, xv);
@@ -287,14 +299,18 @@ extern "C" int tb200_axpy(void *y, const void *x, float alpha, int64_t count, in
     if (count < 0) return TB200_ERR_SHAPE;
     if (count == 0) return TB200_OK;
     if (!y || !x) return TB200_ERR_NULL;
-    // the vector path needs 16-byte alignment; unaligned views go one element a thread
+    if (!aligned_to(y, dtype_size(y_dtype)) || !aligned_to(x, dtype_size(x_dtype))) return TB200_ERR_ALIGN;
     DeviceInfo dev;
     int st = current_device(&dev);
     if (st) return st;
-    if (!aligned_to(y, 16) || !aligned_to(x, 16)) return TB200_ERR_ALIGN;
-    const int grid = stream_grid(dev, ceil_div(count, 8));
-#define TB200_AXPY(TY, TX) \
-    axpy_kernel<TY, TX><<<grid, kThreads, 0, stream>>>(static_cast<TY *>(y), static_cast<const TX *>(x), alpha, count)
+    // the vector path needs 16-byte alignment; unaligned views go one element a thread
+    const bool vec = aligned_to(y, 16) && aligned_to(x, 16);
+    const int grid = stream_grid(dev, vec ? ceil_div(count, 8) : count);
+#define TB200_AXPY(TY, TX)                                                                                              \
+    do {                                                                                                                \
+        if (vec) axpy_kernel<TY, TX, true><<<grid, kThreads, 0, stream>>>(static_cast<TY *>(y), static_cast<const TX *>(x), alpha, count);  \
+        else axpy_kernel<TY, TX, false><<<grid, kThreads, 0, stream>>>(static_cast<TY *>(y), static_cast<const TX *>(x), alpha, count); \
+    } while (0)
     if (y_dtype == TB200_F32 && x_dtype == TB200_F32) TB200_AXPY(float, float);
     else if (y_dtype == TB200_F32) TB200_AXPY(float, __nv_bfloat16);
     else if (x_dtype == TB200_F32) TB200_AXPY(__nv_bfloat16, float);

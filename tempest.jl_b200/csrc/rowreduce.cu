@@ -298,6 +298,9 @@ __device__ __forceinline__ void layernorm_bwd_resident_body(const RowArgs &a) {
                 }
             }
             rstd = 1.0f / sqrtf(row_allreduce1(q, c, SumOp()) / fn + a.eps);
+            // a slot past the last row holds zeros: with eps = 0 its rstd is infinite and 0 * inf would
+            // put NaN into the column sums, so it takes the same (0, 0) the saved-statistics branch gives it
+            if (!live) { mean = 0.0f; rstd = 0.0f; }
         }
         // xh in v; padded slots have gamma = 0 and dy = 0, so they add nothing.  The arithmetic runs on
         // pairs of Float32 (fma.rn.f32x2 and friends): the kernel is bound by instruction issue for

@@ -97,6 +97,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *s
                  ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(x), "r"(y)
                  : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *m, const void *src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap *m, const void *src, int x, int y, int z, int w) {
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                  ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z), "r"(w)
@@ -217,12 +222,17 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t 
 }
 
 // Instruction descriptor of tcgen05.mma kind::f16 with BF16 inputs and F32 accumulation.
-//   bits [4,6) D format (1 = F32); [7,10) A format (1 = BF16); [10,13) B format;
+//   bits [4,6) D format (1 = F32); [7,10) A format (0 = F16, 1 = BF16); [10,13) B format;
 //   bit 15 A is MN-major; bit 16 B is MN-major; [17,23) N >> 3; [24,29) M >> 4.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_major, bool b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
            (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
            (static_cast<uint32_t>(m >> 4) << 24);
+}
+// The same for Float16 inputs (both operands; Float32 accumulation).
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, bool a_mn_major, bool b_mn_major) {
+    return (1u << 4) | (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 }  // namespace sm100

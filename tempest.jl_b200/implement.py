@@ -199,6 +199,12 @@ class LinearLaunch:
                 s.buffer = buffer
         return self
 
+    @staticmethod
+    def check():
+        """Synchronises and raises if a tensor-core kernel gave up a bounded wait since the last poll
+        (the launch itself only enqueues and cannot know): call it where the results are about to be read."""
+        lib.check_device()
+
     def __call__(self):
         a, e = self.binding.arrays, self.binding.extents
         w, x, y = a["w"], a["x"], a["y"]
@@ -227,6 +233,12 @@ class AttentionLaunch:
             if s.value == value:
                 s.buffer = buffer
         return self
+
+    @staticmethod
+    def check():
+        """Synchronises and raises if a tensor-core kernel gave up a bounded wait since the last poll
+        (the launch itself only enqueues and cannot know): call it where the results are about to be read."""
+        lib.check_device()
 
     def __call__(self):
         a = self.binding.arrays
@@ -261,6 +273,15 @@ def _torch_allocate(nbytes):
     return torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
 
 
+def row_eltype(binding: "Binding") -> str:
+    """Element type of a row binding's rows: that of its arrays other than the statistics (`lse`,
+    `mean`, `rstd`), which may be Float32 beside BFloat16 rows and may come first in the dictionary."""
+    for name, s in binding.arrays.items():
+        if name not in ("lse", "mean", "rstd"):
+            return s.eltype
+    raise ValueError(f"{binding.template}: a binding with statistics only has no rows")
+
+
 class RowLaunch:
     """One fused row kernel on fixed operands.  Calling it enqueues the kernel;
     `repoint` replaces the buffer of one value (ext/cuDNNExt.jl:207-218)."""
@@ -270,8 +291,7 @@ class RowLaunch:
         self.eps = eps
         self.workspace = workspace
         self.workspace_bytes = workspace_bytes
-        first = next(iter(binding.arrays.values()))
-        self.dtype = ELTYPES[first.eltype][0]
+        self.dtype = ELTYPES[row_eltype(binding)][0]
         self.n, self.rows = binding.extents["n"], binding.extents["rows"]
 
     def repoints(self) -> bool:
@@ -390,8 +410,7 @@ class B200Kernels:
             if b.template.endswith("_pullback"):
                 return [Work(bytes=2 * moved, flops=2.5 * flops, launches=3)]
             return [Work(bytes=moved, flops=flops)]
-        first = next(iter(b.arrays.values()))
-        size = ELTYPES[first.eltype][1]
+        size = ELTYPES[row_eltype(b)][1]
         n, rows = b.extents["n"], b.extents["rows"]
         op = _ROWOP[b.template]
         launches = 2 if (op == lib.LAYERNORM_BWD or n > 16384) else 1
@@ -415,15 +434,15 @@ class B200Kernels:
             e = b.extents
             return launch, (f"B200 {b.template}, {e['h']} heads over {e['hk']} of {e['d']} features, "
                             f"{e['m']} queries by {e['n']} keys, batch {e['b']}")
-        first = next(iter(b.arrays.values()))
-        dtype = ELTYPES[first.eltype][0]
+        eltype = row_eltype(b)
+        dtype = ELTYPES[eltype][0]
         n, rows = b.extents["n"], b.extents["rows"]
         need = lib.rowop_workspace_bytes(_ROWOP[b.template], n, rows, dtype)
         resources = resources if resources is not None else Resources()
         ws = resources.workspace(need) if need else None
         launch = RowLaunch(b, self.eps, ws, need)
         schedule = "split" if n > 16384 else "resident"
-        return launch, f"B200 {b.template}, {rows} rows of {n} {first.eltype}, {schedule}"
+        return launch, f"B200 {b.template}, {rows} rows of {n} {eltype}, {schedule}"
 
 
 # ---------------------------------------------------------------- generic groups ----

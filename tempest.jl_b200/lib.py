@@ -7,7 +7,7 @@ library raises: there is no CPU fallback.
 import ctypes
 import os
 
-F32, BF16 = 0, 1
+F32, BF16, F16 = 0, 1, 2
 SOFTMAX_FWD, SOFTMAX_BWD, LAYERNORM_FWD, LAYERNORM_BWD = 0, 1, 2, 3
 
 K_MAJOR, MN_MAJOR = 0, 1
@@ -29,14 +29,19 @@ class GemmDesc(ctypes.Structure):
                 ("a_layout", ctypes.c_int), ("b_layout", ctypes.c_int),
                 ("in_dtype", ctypes.c_int), ("out_dtype", ctypes.c_int),
                 ("epilogue", ctypes.c_int), ("alpha", ctypes.c_float),
-                ("tile_n", ctypes.c_int), ("force_simt", ctypes.c_int), ("direct_epilogue", ctypes.c_int)]
+                ("tile_n", ctypes.c_int), ("force_simt", ctypes.c_int), ("direct_epilogue", ctypes.c_int),
+                ("batch", ctypes.c_int64), ("stride_a", ctypes.c_int64), ("stride_b", ctypes.c_int64),
+                ("stride_c", ctypes.c_int64), ("stride_bias", ctypes.c_int64), ("stride_aux", ctypes.c_int64),
+                ("stride_aux_out", ctypes.c_int64), ("split_k", ctypes.c_int), ("workspace", ctypes.c_void_p),
+                ("workspace_bytes", ctypes.c_size_t), ("debug", ctypes.c_int)]
 
 
 class AttnDesc(ctypes.Structure):
     """tb200_attn_desc of include/tempest_b200.h."""
     _fields_ = [("batch", ctypes.c_int), ("heads", ctypes.c_int), ("kv_heads", ctypes.c_int),
                 ("queries", ctypes.c_int), ("keys", ctypes.c_int), ("head_dim", ctypes.c_int),
-                ("causal", ctypes.c_int), ("scale", ctypes.c_float), ("dtype", ctypes.c_int)]
+                ("causal", ctypes.c_int), ("scale", ctypes.c_float), ("dtype", ctypes.c_int),
+                ("deterministic", ctypes.c_int)]
 
 
 class AttnMask(ctypes.Structure):
@@ -94,12 +99,19 @@ SIGNATURES = {
     "tb200_layernorm_bwd_noalloc_max_row": (_sz, []),
     "tb200_layernorm_bwd_noalloc": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i, _p]),
     "tb200_gemm": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
+    "tb200_gemm_workspace_bytes": (_sz, [ctypes.POINTER(GemmDesc)]),
+    "tb200_gemm_plan_create": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, ctypes.POINTER(_p)]),
+    "tb200_gemm_plan_launch": (_i, [_p, _p]),
+    "tb200_gemm_plan_repoint": (_i, [_p, _i, _p]),
+    "tb200_gemm_plan_destroy": (None, [_p]),
+    "tb200_gemm_tune_desc": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
     "tb200_device_error": (_i, []),
     "tb200_attention_fwd": (_i, [ctypes.POINTER(AttnDesc), _p, _p, _p, _p, _p, _p]),
     "tb200_attention_device_error": (_i, []),
     "tb200_attention_bwd_workspace_bytes": (_sz, [ctypes.POINTER(AttnDesc)]),
     "tb200_attention_bwd": (_i, [ctypes.POINTER(AttnDesc), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "tb200_attention_bwd_device_error": (_i, []),
+    "tb200_device_errors": (_i, []),
     "tb200_deltanet_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_fwd": (_i, [ctypes.POINTER(DeltanetDesc), _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "tb200_gemm_tune": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
@@ -203,12 +215,14 @@ def layernorm_bwd(x, gamma, dy, mean, rstd, dx, dgamma, dbeta, eps, n, rows, ld,
         workspace or None, workspace_bytes, stream or None))
 
 
-def gemm(a, b, c, m, n, k, *, lda=None, ldb=None, ldc=None, a_layout=K_MAJOR, b_layout=MN_MAJOR, in_dtype=BF16,
-         out_dtype=None, epilogue=EPI_NONE, bias=0, aux=0, ld_aux=None, aux_out=0, ld_aux_out=None, alpha=1.0,
-         tile_n=0, force_simt=False, direct_epilogue=False, stream=0, tune=False):
-    """C[m][n] = epilogue(alpha * A * B).  With `tune` the compiled-in tile variants are timed on these operands
-    and the faster tile_n is returned (the product's result is in C either way).  a_layout K_MAJOR: A is [m][k]; MN_MAJOR: [k][m].
-    b_layout K_MAJOR: B is [n][k]; MN_MAJOR: [k][n] (a Julia (out,in) weight for y = w*x)."""
+GEMM_A, GEMM_B, GEMM_C, GEMM_BIAS, GEMM_AUX, GEMM_AUX_OUT, GEMM_WORKSPACE = range(7)
+
+
+def gemm_desc(m, n, k, *, lda=None, ldb=None, ldc=None, a_layout=K_MAJOR, b_layout=MN_MAJOR, in_dtype=BF16,
+              out_dtype=None, epilogue=EPI_NONE, ld_aux=None, ld_aux_out=None, alpha=1.0, tile_n=0, force_simt=False,
+              direct_epilogue=False, batch=1, stride_a=None, stride_b=None, stride_c=None, stride_bias=0,
+              stride_aux=None, stride_aux_out=None, split_k=0, workspace=0, workspace_bytes=0, debug=0):
+    """tb200_gemm_desc with dense defaults: leading dimensions from the layouts, batch members one after another."""
     d = GemmDesc()
     d.m, d.n, d.k = m, n, k
     d.lda = lda if lda is not None else (m if a_layout == MN_MAJOR else k)
@@ -221,6 +235,27 @@ def gemm(a, b, c, m, n, k, *, lda=None, ldb=None, ldc=None, a_layout=K_MAJOR, b_
     d.out_dtype = in_dtype if out_dtype is None else out_dtype
     d.epilogue, d.alpha, d.tile_n, d.force_simt = epilogue, alpha, tile_n, int(force_simt)
     d.direct_epilogue = int(direct_epilogue)
+    d.batch = batch
+    a_rows = k if a_layout == MN_MAJOR else m
+    b_rows = k if b_layout == MN_MAJOR else n
+    d.stride_a = stride_a if stride_a is not None else a_rows * d.lda
+    d.stride_b = stride_b if stride_b is not None else b_rows * d.ldb
+    d.stride_c = stride_c if stride_c is not None else m * d.ldc
+    d.stride_bias = stride_bias
+    d.stride_aux = stride_aux if stride_aux is not None else m * d.ld_aux
+    d.stride_aux_out = stride_aux_out if stride_aux_out is not None else m * d.ld_aux_out
+    d.split_k = split_k
+    d.workspace, d.workspace_bytes = workspace or None, workspace_bytes
+    d.debug = debug
+    return d
+
+
+def gemm(a, b, c, m, n, k, *, bias=0, aux=0, aux_out=0, stream=0, tune=False, **options):
+    """C[m][n] = epilogue(alpha * A * B) (`options`: the fields of `gemm_desc`).  With `tune` the compiled-in tile
+    variants are timed on these operands and the faster tile_n is returned (the product's result is in C either
+    way).  a_layout K_MAJOR: A is [m][k]; MN_MAJOR: [k][m].  b_layout K_MAJOR: B is [n][k]; MN_MAJOR: [k][n] (a
+    Julia (out,in) weight for y = w*x).  batch > 1: that many alike products, operands `stride_*` elements apart."""
+    d = gemm_desc(m, n, k, **options)
     if tune:
         width = load().tb200_gemm_tune(ctypes.byref(d), a or None, b or None, c or None, bias or None,
                                        aux or None, aux_out or None, stream or None)
@@ -230,11 +265,77 @@ def gemm(a, b, c, m, n, k, *, lda=None, ldb=None, ldc=None, a_layout=K_MAJOR, b_
                                           aux or None, aux_out or None, stream or None))
 
 
+def gemm_workspace_bytes(desc):
+    """Scratch a split of the product's sum wants (0: it would not split)."""
+    return load().tb200_gemm_workspace_bytes(ctypes.byref(desc))
+
+
+def gemm_tune_desc(desc, a, b, c, bias=0, aux=0, aux_out=0, stream=0):
+    """Times every compiled-in variant (tile width, split or not, how results are stored) and leaves the fastest
+    one's choices in `desc`."""
+    check("tb200_gemm_tune_desc", load().tb200_gemm_tune_desc(ctypes.byref(desc), a or None, b or None, c or None,
+                                                              bias or None, aux or None, aux_out or None,
+                                                              stream or None))
+    return desc
+
+
+class GemmPlan:
+    """A prepared product (tb200_gemm_plan): validation, schedule and TMA descriptors built once; `launch(stream)`
+    is one C call and one kernel launch; `repoint(operand, address)` moves one operand."""
+
+    def __init__(self, desc, a, b, c, bias=0, aux=0, aux_out=0):
+        self._handle = _p()
+        self.desc = desc
+        check("tb200_gemm_plan_create", load().tb200_gemm_plan_create(
+            ctypes.byref(desc), a or None, b or None, c or None, bias or None, aux or None, aux_out or None,
+            ctypes.byref(self._handle)))
+        self._launch = load().tb200_gemm_plan_launch
+
+    def launch(self, stream=0):
+        st = self._launch(self._handle, stream or None)
+        if st:
+            check("tb200_gemm_plan_launch", st)
+
+    def repoint(self, operand, address):
+        check("tb200_gemm_plan_repoint", load().tb200_gemm_plan_repoint(self._handle, operand, address or None))
+        return self
+
+    def close(self):
+        if self._handle:
+            load().tb200_gemm_plan_destroy(self._handle)
+            self._handle = _p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown
+            pass
+
+
 def device_error():
     code = load().tb200_device_error()
     if code < 0:
         check("tb200_device_error", code)
     return code
+
+
+def device_errors():
+    """Synchronises the device; product | attention forward << 8 | attention backward << 16 of the codes the
+    tensor-core kernels record when a bounded wait gives up (0 = none), cleared by the call."""
+    code = load().tb200_device_errors()
+    if code < 0:
+        check("tb200_device_errors", code)
+    return code
+
+
+def check_device():
+    """Raises if any tensor-core kernel launched since the last poll gave up a bounded wait: its outputs
+    are not to be used.  Call where the host synchronises anyway."""
+    code = device_errors()
+    if code:
+        raise TB200Error("tb200_device_errors", code, "a tensor-core kernel gave up a bounded wait "
+                         f"(product {code & 0xff}, attention forward {(code >> 8) & 0xff}, "
+                         f"attention backward {(code >> 16) & 0xff}); results of that launch are invalid")
 
 
 def workspace_clear(workspace, nbytes, stream=0):
@@ -277,8 +378,10 @@ def layernorm_bwd_noalloc(x, gamma, dy, mean, rstd, dx, dgamma, dbeta, eps, n, r
         stream or None))
 
 
-def attn_desc(batch, heads, queries, keys, head_dim, causal, scale=None, kv_heads=None, dtype=BF16):
+def attn_desc(batch, heads, queries, keys, head_dim, causal, scale=None, kv_heads=None, dtype=BF16,
+              deterministic=False):
     d = AttnDesc()
+    d.deterministic = int(deterministic)
     d.batch, d.heads, d.kv_heads = batch, heads, kv_heads or heads
     d.queries, d.keys, d.head_dim = queries, keys, head_dim
     d.causal = int(causal)

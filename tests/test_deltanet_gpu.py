@@ -106,6 +106,72 @@ def test_pullback_is_linear_in_the_cotangent(pkg, cuda, oracle):
         assert (g == 0).all()
 
 
+def test_config_length_against_the_token_rule(pkg, cuda, oracle):
+    """The benchmark's sequence length, T = 8192 (128 chained chunks): forward of two sequences and the
+    pullback of one against the Float64 token rule."""
+    heads, T = 2, 8192
+    q, k, v, a, beta = oracle.deltanet_inputs(heads, T, 128, 128, 8192)
+    got = run(pkg, cuda, q, k, v, a, beta)
+    want = oracle.deltanet_sequential(q, k, v, a, beta, threads=2)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max()
+    assert np.linalg.norm(got - want) <= 1e-2 * np.linalg.norm(want)
+    one = slice(0, 1)
+    dout_bits = oracle.to_bf16(oracle.normal((1, 128, T), 8193))
+    dout = oracle.from_bf16(dout_bits).astype(np.float64)
+    grads = run_bwd(pkg, cuda, q[one], k[one], v[one], a[one], beta[one], dout_bits)
+    wants = oracle.deltanet_sequential_bwd(q[one], k[one], v[one], a[one], beta[one], dout)
+    for name, g, w in zip(("dq", "dk", "dv", "da", "dbeta"), grads, wants):
+        assert np.isfinite(g).all(), name
+        rel = np.abs(g - w).max() / np.abs(w).max()
+        assert rel <= 2e-2, (name, rel)
+        assert np.linalg.norm(g - w) <= 1e-2 * np.linalg.norm(w), name
+
+
+def test_config_launch_of_64_sequences(pkg, cuda, oracle):
+    """The whole benchmark launch (B * H = 64 sequences of 8192, forward and pullback): every result finite,
+    and two sampled sequences bit-equal to the same sequences run alone (sequences are independent, and
+    the kernels' order of summation does not depend on how many there are)."""
+    torch, L = cuda, pkg.lib
+    Hn, T = 64, 8192
+    g = torch.Generator(device="cuda").manual_seed(64)
+    unit = lambda x: torch.nn.functional.normalize(x, dim=-1)   # noqa: E731
+    q = unit(torch.randn(Hn, T, 128, device="cuda", generator=g)).bfloat16()
+    k = unit(torch.randn(Hn, T, 128, device="cuda", generator=g)).bfloat16()
+    v = torch.randn(Hn, T, 128, device="cuda", generator=g).bfloat16()
+    a = -torch.nn.functional.softplus(torch.randn(Hn, T, device="cuda", generator=g))
+    beta = torch.sigmoid(torch.randn(Hn, T, device="cuda", generator=g))
+    dout = torch.randn(Hn, 128, T, device="cuda", generator=g).bfloat16()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def both(sel):
+        qs, ks, vs, as_, bs, ds = (x[sel].contiguous() for x in (q, k, v, a, beta, dout))
+        n = qs.shape[0]
+        desc = L.deltanet_desc(n, T)
+        o = torch.full((n, 128, T), float("nan"), device="cuda", dtype=torch.bfloat16)
+        need = L.deltanet_workspace_bytes(desc)
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        L.deltanet_fwd(desc, qs.data_ptr(), ks.data_ptr(), vs.data_ptr(), as_.data_ptr(), bs.data_ptr(), o.data_ptr(),
+                       ws.data_ptr(), need, stream)
+        del ws
+        dq, dk, dv = (torch.full((n, T, 128), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        da, db = (torch.full((n, T), float("nan"), device="cuda") for _ in range(2))
+        need = L.deltanet_bwd_workspace_bytes(desc)
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        L.deltanet_bwd(desc, qs.data_ptr(), ks.data_ptr(), vs.data_ptr(), as_.data_ptr(), bs.data_ptr(), ds.data_ptr(),
+                       dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), da.data_ptr(), db.data_ptr(), ws.data_ptr(), need, stream)
+        torch.cuda.synchronize()
+        return o, dq, dk, dv, da, db
+
+    whole = both(slice(0, Hn))
+    for t in whole:
+        assert torch.isfinite(t.float()).all()
+    for h in (5, 63):
+        alone = both(slice(h, h + 1))
+        for w, s in zip(whole, alone):
+            assert torch.equal(w[h], s[0])
+
+
 def test_refuses_other_geometries(pkg, cuda):
     L = pkg.lib
     x = cuda.zeros(64, device="cuda")

@@ -64,6 +64,28 @@ def test_strided_pointer_and_repoint(I):
     assert b.arrays["x"].pointer() == 65536 + 16 and b.arrays["y"].pointer() == 8192
 
 
+def test_row_type_ignores_statistics_listed_first(I):
+    """A Float32 statistic ahead of BFloat16 rows in the binding must not decide the kernels' element type
+    (nor the workspace size or the byte count)."""
+    rows, n = 8, 4096
+    stat = lambda v: I.Strided("Float32", 0, (1, rows), (1, 1), 1 << 20, v)  # noqa: E731
+    arrays = {"mean": stat(7), "rstd": stat(8)}
+    for i, name in enumerate(("x", "g", "dx")):
+        arrays[name] = I.dense_columns(4096 * (i + 1), "BFloat16", n, rows, i + 1)
+    for i, name in enumerate(("w", "dw", "db")):
+        arrays[name] = I.dense_vector(1 << 16, "BFloat16", n, 4 + i)
+    b = I.Binding("layernorm_pullback", {"n": n, "rows": rows}, arrays)
+    lib, t = I.B200Kernels(), I.Target()
+    assert lib.supports(t, b)
+    assert I.row_eltype(b) == "BFloat16"
+    assert I.RowLaunch(b, 1e-5, None, 0).dtype == 1            # TB200_BF16
+    (w,) = lib.estimate(t, b)
+    assert w.bytes == 3 * n * rows * 2
+    lse_first = I.Binding("softmax_columns_lse", {"n": n, "rows": rows},
+                          {"lse": stat(3), "x": arrays["x"], "y": arrays["dx"]})
+    assert I.RowLaunch(lse_first, 1e-5, None, 0).dtype == 1
+
+
 def test_product_and_attention_templates(I):
     lib, t = I.B200Kernels(), I.Target()
     names = [x.name for x in lib.templates(t)]

@@ -156,3 +156,22 @@ def test_deltanet_pullback_against_autograd_and_differences(oracle):
     dn = oracle.deltanet_sequential(q, k, v, a - da, beta)
     step = ((a + da).astype(np.float64) - (a - da).astype(np.float64))
     assert abs(((up - dn) * dout).sum() - (got[3] * step).sum()) <= 1e-4 * abs((got[3] * step).sum()) + 1e-9
+
+
+def test_mlp_step_by_blas_equals_the_sequential_restatement(oracle):
+    """The BLAS form used at the benchmark's size takes the same step as the sequential restatement (only the
+    order of summation differs)."""
+    sizes, batch, rate = (24, 40, 32, 8), 16, 1e-2
+    ws = [oracle.to_bf16(0.3 * oracle.normal((sizes[i], sizes[i + 1]), 80 + i)) for i in range(3)]
+    bs = [oracle.to_bf16(0.1 * oracle.normal((sizes[i + 1],), 90 + i)) for i in range(3)]
+    x = oracle.to_bf16(oracle.normal((batch, sizes[0]), 95))
+    y = oracle.to_bf16(oracle.normal((batch, sizes[-1]), 96))
+    seq = oracle.mlp_step(ws, bs, x, y, rate)
+    fast = oracle.mlp_step_blas(ws, bs, x, y, rate)
+    assert abs(seq[0] - fast[0]) <= 1e-5 * abs(seq[0])
+    for i in range(3):
+        assert np.abs(oracle.from_bf16(seq[1][i]) - oracle.from_bf16(fast[1][i])).max() <= 2e-3   # dz, one ulp apart at most
+        assert np.linalg.norm(seq[2][i] - fast[2][i]) <= 1e-2 * np.linalg.norm(seq[2][i])       # dw (from dz a BFloat16 ulp apart)
+        assert np.abs(seq[3][i] - fast[3][i]).max() <= 1e-2 * max(1.0, np.abs(seq[3][i]).max())
+        for k, j in ((4, i), (5, i), (6, i + 1), (7, i)):   # updated w and b, the activations, what the activation saw
+            assert np.abs(oracle.from_bf16(seq[k][j]) - oracle.from_bf16(fast[k][j])).max() <= 2e-2
