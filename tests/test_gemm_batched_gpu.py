@@ -146,7 +146,8 @@ def test_split_sum_of_a_batch(pkg, cuda, oracle):
     assert need > 0
     ws = torch.empty(need, device="cuda", dtype=torch.uint8)
     C32 = torch.empty((batch, M, N), device="cuda")
-    L.gemm(dev(torch, A).data_ptr(), dev(torch, B).data_ptr(), C32.data_ptr(), M, N, K, batch=batch, out_dtype=L.F32,
+    Ad, Bd = dev(torch, A), dev(torch, B)
+    L.gemm(Ad.data_ptr(), Bd.data_ptr(), C32.data_ptr(), M, N, K, batch=batch, out_dtype=L.F32,
            workspace=ws.data_ptr(), workspace_bytes=need)
     assert L.device_error() == 0
     agree(C32.cpu().numpy(), want, 1e-5)
