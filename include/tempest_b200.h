@@ -232,7 +232,11 @@ int tb200_gemm(const tb200_gemm_desc *desc, const void *a, const void *b, void *
  * depends on it; the new address must be aligned as the old one was (src/Compiler/Implement/
  * Implement.jl:162-175).  A plan belongs to the device that was current when it was created, may be
  * launched any number of times on any stream of that device, and is not to be repointed while
- * another thread launches it. */
+ * another thread launches it.  Creating a plan allocates eight bytes of device memory (launching
+ * allocates nothing): two counters from which the persistent blocks draw their tiles, so that a block
+ * which reaches its SM late -- a communication kernel was running there -- takes fewer tiles instead of
+ * holding the launch up; because of them two launches of ONE plan must not overlap on the GPU (launch
+ * a plan on one stream at a time, or create two plans). */
 typedef struct tb200_gemm_plan tb200_gemm_plan;
 typedef enum tb200_gemm_operand {
     TB200_GEMM_A = 0, TB200_GEMM_B = 1, TB200_GEMM_C = 2, TB200_GEMM_BIAS = 3, TB200_GEMM_AUX = 4,
@@ -496,6 +500,47 @@ int tb200_colreduce_compile(const tb200_group_desc *desc);
 int tb200_colreduce_compiled(const tb200_group_desc *desc, const void *const *inputs, void *const *outputs,
                              void *workspace, size_t workspace_bytes, void *stream);
 size_t tb200_colreduce_source(const tb200_group_desc *desc, char *buffer, size_t buffer_bytes);
+
+/* ---- data-parallel update: gradient sum + SGD step in one kernel over NVLink -----
+ * The exchange of a data-parallel training step (the reference spells it `r .+ s` over the devices'
+ * gradients followed by the update on each, realised by peer copies and sums:
+ * src/Compiler/plan/devices.jl:7-11, test/fixtures/devices.jl `shards_sgd!`; replicas equal after
+ * every step is its stated property).  Every rank calls tb200_dp_update at the same point of its
+ * step with the same `count`, `alpha` and `blocks`.  Rank r sums the replicas' gradients over the
+ * r-th slice of the range, forms params + alpha * sum once (Float32 arithmetic, gradients' sum and
+ * the result rounded to BFloat16) and writes the result into every replica's `params`; the call
+ * returns (in stream order) when every replica's `params` range is complete.  The replicas are
+ * bit-equal by construction.  The gradient buffers are only read.
+ *
+ * grads[i], params[i], signals[i]: rank i's arrays as mapped into THIS process (peer-accessible
+ * memory, e.g. a symmetric allocation; entry `rank` is the local one), 16-byte aligned.  With
+ * grads_multicast / params_multicast (the same two ranges through an NVLink multicast mapping) the
+ * sum is taken by the NVSwitch (multimem.ld_reduce) and the result broadcast by it (multimem.st);
+ * NULL = plain loads from and stores to each peer.  signals[i]: tb200_dp_signal_bytes bytes,
+ * zero before the first call, never touched by the caller afterwards.  state: local device memory,
+ * tb200_dp_state_bytes bytes, zero before the first call.  Two calls that share signals or state
+ * must not overlap on the GPU.  Ranks wait for one another inside the kernel; each wait gives up
+ * after two seconds (a rank that never arrives) and tb200_dp_error then reports a non-zero code.
+ * No allocation, no host synchronisation: the call can be captured, provided every rank replays it
+ * the same number of times. */
+typedef struct tb200_dp_desc {
+    int rank, world;             /* world <= 16 */
+    int blocks;                  /* thread blocks (SMs) the kernel occupies; 0 = 16; the same on every rank */
+    int dtype;                   /* TB200_BF16 */
+    int64_t count;               /* elements in the range, a multiple of 8 */
+    float alpha;                 /* -rate */
+    const void *grads[16];
+    void *params[16];
+    void *signals[16];
+    const void *grads_multicast;
+    void *params_multicast;
+    void *state;
+} tb200_dp_desc;
+size_t tb200_dp_signal_bytes(void);
+size_t tb200_dp_state_bytes(void);
+int tb200_dp_update(const tb200_dp_desc *desc, void *stream);
+/* As tb200_device_error, for tb200_dp_update: 0, or 1 + 16 * rank + peer of the first wait that gave up. */
+int tb200_dp_error(void);
 
 /* ---- pointwise maps and folds over other axes -------------------------------
  * These replace the generated `:pointwise` kernels (ext/cuTileExt/build.jl:3-10)

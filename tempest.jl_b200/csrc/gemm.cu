@@ -68,6 +68,10 @@ struct GemmArgs {
     int stages;
     int debug;            // bit 0: the loader withholds its tiles (test hook)
     unsigned long long wait_ns;   // after which a bounded wait gives up
+    int *schedule;        // null: work items dealt round-robin by block index.  Else two counters (next item,
+                          // blocks finished), zero before the launch and left zero by it: every block takes
+                          // its next item from the first, so a block that reaches its SM late (another kernel
+                          // held it) takes fewer items instead of making the launch wait for its share
 };
 
 // ------------------------------------------------------------- epilogues ----
@@ -372,6 +376,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     __shared__ __align__(8) uint64_t tmem_full_bar[kAccumStages];
     __shared__ __align__(8) uint64_t tmem_empty_bar[kAccumStages];
     __shared__ __align__(8) uint64_t aux_bar[4];
+    // the work items of this block, handed from the loading thread to the MMA thread and the epilogue warps
+    constexpr int kItemSlots = 4;
+    __shared__ __align__(8) uint64_t item_full[kItemSlots];
+    __shared__ __align__(8) uint64_t item_empty[kItemSlots];
+    __shared__ int item_slot[kItemSlots];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int failed_smem;
     volatile int *failed = &failed_smem;
@@ -394,6 +403,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             mbar_init(&tmem_empty_bar[s], 4);
         }
         for (int s = 0; s < 4; s++) mbar_init(&aux_bar[s], 1);
+        for (int s = 0; s < kItemSlots; s++) {
+            mbar_init(&item_full[s], 1);
+            mbar_init(&item_empty[s], 5);   // the MMA thread and one lane of each epilogue warp
+        }
         fence_barrier_init();
         prefetch_tensormap(&p.tmap_a);
         prefetch_tensormap(&p.tmap_b);
@@ -409,12 +422,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     const uint32_t tmem_base = tmem_base_smem;
 
     if (warp == 0) {
-        // ---- TMA producer (with the test hook set it issues nothing: every consumer's wait then runs out)
-        if (elect_one() && !(p.debug & 1)) {
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int item = blockIdx.x; item < num_items && !*failed; item += gridDim.x) {
+        // ---- TMA producer; it also draws the block's work items and passes them on (with the test hook set it
+        // passes the items on but loads nothing: every consumer's wait for operands then runs out)
+        if (elect_one()) {
+            int stage = 0, slot = 0;
+            uint32_t phase = 0, slot_phase = 0;
+            const bool withhold = (p.debug & 1) != 0;
+            int item = p.schedule ? atomicAdd(p.schedule, 1) : static_cast<int>(blockIdx.x);
+            while (true) {
+                if (!wait_or_fail(&item_empty[slot], slot_phase ^ 1, failed, 6, wait_ns)) break;
+                const bool live = item < num_items && !*failed;
+                item_slot[slot] = live ? item : -1;
+                mbar_arrive(&item_full[slot]);
+                if (++slot == kItemSlots) { slot = 0; slot_phase ^= 1; }
+                if (!live) break;
+                // the next item is drawn now, so that the answer is there when this one's loads are out
+                const int next = p.schedule ? atomicAdd(p.schedule, 1) : item + static_cast<int>(gridDim.x);
                 const WorkItem w = work_item(p, item, num_kb);
+                item = next;
+                if (withhold) continue;
                 const int m0 = w.tm * BM, n0 = w.tn * BN;
                 const int za = p.a_batched ? w.member : 0, zb = p.b_batched ? w.member : 0;
                 for (int kb = w.kb0; kb < w.kb1; kb++) {
@@ -449,9 +475,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             const uint32_t a_lead = p.a_mn ? BK * 128 : 16, b_lead = p.b_mn ? BK * 128 : 16;
             const uint32_t a_step = (p.a_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
             const uint32_t b_step = (p.b_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
-            int stage = 0, it = 0;
-            uint32_t phase = 0;
-            for (int item = blockIdx.x; item < num_items && !*failed; item += gridDim.x, it++) {
+            int stage = 0, it = 0, slot = 0;
+            uint32_t phase = 0, slot_phase = 0;
+            for (;; it++) {
+                if (!wait_or_fail(&item_full[slot], slot_phase, failed, 7, wait_ns)) break;
+                const int item = item_slot[slot];
+                mbar_arrive(&item_empty[slot]);
+                if (++slot == kItemSlots) { slot = 0; slot_phase ^= 1; }
+                if (item < 0 || *failed) break;
                 const WorkItem w = work_item(p, item, num_kb);
                 const int acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
@@ -485,7 +516,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
         uint8_t *stage_x = stage_c + kEpilogueStage;
         uint32_t aux_phase = 0;
         const bool in_f16 = p.in_f16 != 0;
-        for (int item = blockIdx.x; item < num_items; item += gridDim.x, it++) {
+        int slot = 0;
+        uint32_t slot_phase = 0;
+        for (;; it++) {
+            if (!wait_or_fail(&item_full[slot], slot_phase, failed, 7, wait_ns)) break;
+            const int item = item_slot[slot];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&item_empty[slot]);
+            if (++slot == kItemSlots) { slot = 0; slot_phase ^= 1; }
+            if (item < 0) break;
             const WorkItem w = work_item(p, item, num_kb);
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
@@ -571,6 +610,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kAccumStages * BN);
+    }
+    // the last block out leaves the two counters as it found them, for the next launch
+    if (p.schedule && threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(p.schedule + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+            p.schedule[0] = 0;
+            p.schedule[1] = 0;
+            __threadfence();
+        }
     }
 }
 
@@ -847,6 +895,7 @@ struct tb200_gemm_plan {
     unsigned merge_grid;
     SimtArgs simt;
     dim3 simt_grid;
+    int *counters;       // device memory of a created plan (two ints, zero between launches), else null
 };
 
 namespace {
@@ -999,6 +1048,8 @@ int prepare(tb200_gemm_plan *plan) {
         const long long items = static_cast<long long>(p.tiles_m) * p.tiles_n * batch * splits;
         if (items > INT32_MAX) return TB200_ERR_SHAPE;
         plan->grid = static_cast<unsigned>(items < dev.sms ? items : dev.sms);
+        // more items than blocks: a created plan lets its blocks draw them from a counter
+        p.schedule = (plan->counters && items > plan->grid) ? plan->counters : nullptr;
         return TB200_OK;
     }
 
@@ -1039,6 +1090,7 @@ int run(const tb200_gemm_plan *plan, cudaStream_t stream) {
 void fill(tb200_gemm_plan *plan, const tb200_gemm_desc *d, const void *a, const void *b, void *c, const void *bias,
           const void *aux, void *aux_out) {
     plan->desc = *d;
+    plan->counters = nullptr;
     plan->a = a; plan->b = b; plan->c = c; plan->bias = bias; plan->aux = aux; plan->aux_out = aux_out;
 }
 
@@ -1070,8 +1122,18 @@ extern "C" int tb200_gemm_plan_create(const tb200_gemm_desc *d, const void *a, c
     tb200_gemm_plan *plan = new (std::nothrow) tb200_gemm_plan;
     if (!plan) return TB200_ERR_WORKSPACE;
     fill(plan, d, a, b, c, bias, aux, aux_out);
+    // building may allocate (launching may not): the two counters of the dynamic schedule
+    if (cudaMalloc(&plan->counters, 2 * sizeof(int)) != cudaSuccess || cudaMemset(plan->counters, 0, 2 * sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        if (plan->counters) cudaFree(plan->counters);
+        plan->counters = nullptr;     // without them the plan deals its items round-robin, as tb200_gemm does
+    }
     const int st = prepare(plan);
-    if (st) { delete plan; return st; }
+    if (st) {
+        if (plan->counters) cudaFree(plan->counters);
+        delete plan;
+        return st;
+    }
     *out = plan;
     return TB200_OK;
 }
@@ -1105,7 +1167,11 @@ extern "C" int tb200_gemm_plan_repoint(tb200_gemm_plan *plan, int operand, const
     return TB200_OK;
 }
 
-extern "C" void tb200_gemm_plan_destroy(tb200_gemm_plan *plan) { delete plan; }
+extern "C" void tb200_gemm_plan_destroy(tb200_gemm_plan *plan) {
+    if (!plan) return;
+    if (plan->counters) cudaFree(plan->counters);   // waits for launches still in flight
+    delete plan;
+}
 
 // Synchronises the device and returns (then clears) the error code a tensor-core kernel recorded when one
 // of its bounded waits ran out: 0 none, 1 loader, 2 accumulator hand-back, 3 operands, 4 epilogue, 5 the

@@ -56,6 +56,14 @@ class DeltanetDesc(ctypes.Structure):
                 ("chunk", ctypes.c_int), ("dtype", ctypes.c_int)]
 
 
+class DpDesc(ctypes.Structure):
+    """tb200_dp_desc of include/tempest_b200.h."""
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("blocks", ctypes.c_int), ("dtype", ctypes.c_int),
+                ("count", ctypes.c_int64), ("alpha", ctypes.c_float),
+                ("grads", ctypes.c_void_p * 16), ("params", ctypes.c_void_p * 16), ("signals", ctypes.c_void_p * 16),
+                ("grads_multicast", ctypes.c_void_p), ("params_multicast", ctypes.c_void_p), ("state", ctypes.c_void_p)]
+
+
 GROUP_MAX_INPUTS, GROUP_MAX_TERMS, GROUP_MAX_FOLDS, GROUP_MAX_OUTPUTS = 8, 48, 8, 8
 
 
@@ -129,6 +137,10 @@ SIGNATURES = {
     "tb200_colreduce_source": (_sz, [ctypes.POINTER(GroupDesc), ctypes.c_char_p, _sz]),
     "tb200_deltanet_bwd_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_bwd": (_i, [ctypes.POINTER(DeltanetDesc)] + [_p] * 12 + [_sz, _p]),
+    "tb200_dp_signal_bytes": (_sz, []),
+    "tb200_dp_state_bytes": (_sz, []),
+    "tb200_dp_update": (_i, [ctypes.POINTER(DpDesc), _p]),
+    "tb200_dp_error": (_i, []),
     "tb200_workspace_clear": (_i, [_p, _sz, _p]),
     "tb200_squared_error_workspace_bytes": (_sz, []),
     "tb200_squared_error": (_i, [_p, _p, _p, _p, _i64, _f, _f, _i, _i, _p, _sz, _p]),
@@ -523,3 +535,33 @@ def attention_fwd_masked(desc, mask, q, k, v, o, lse=0, stream=0):
 def attention_bwd_masked(desc, mask, q, k, v, o, lse, dout, dq, dk, dv, stream=0):
     check("tb200_attention_bwd_masked", load().tb200_attention_bwd_masked(
         ctypes.byref(desc), ctypes.byref(mask), q, k, v, o, lse, dout, dq, dk, dv, stream or None))
+
+
+def dp_signal_bytes():
+    return load().tb200_dp_signal_bytes()
+
+
+def dp_state_bytes():
+    return load().tb200_dp_state_bytes()
+
+
+def dp_desc(rank, world, count, alpha, grads, params, signals, state, grads_multicast=0, params_multicast=0, blocks=0):
+    """tb200_dp_desc: `grads`, `params`, `signals` are lists of addresses in rank order (this process's mappings)."""
+    d = DpDesc()
+    d.rank, d.world, d.blocks, d.dtype, d.count, d.alpha = rank, world, blocks, BF16, count, alpha
+    for i in range(world):
+        d.grads[i], d.params[i], d.signals[i] = grads[i] or None, params[i] or None, signals[i] or None
+    d.grads_multicast, d.params_multicast = grads_multicast or None, params_multicast or None
+    d.state = state or None
+    return d
+
+
+def dp_update(desc, stream=0):
+    check("tb200_dp_update", load().tb200_dp_update(ctypes.byref(desc), stream or None))
+
+
+def dp_error():
+    code = load().tb200_dp_error()
+    if code < 0:
+        check("tb200_dp_error", code)
+    return code

@@ -29,7 +29,10 @@ shard; a bucket of gradients is summed across replicas by an NCCL all-reduce
 issued on a side stream as soon as its layers' gradients exist, overlapping the
 remaining backward products; the update runs when the bucket has landed.  The
 MSE is a mean over the global batch, so each replica scales its pullback by
-1 / global batch.
+1 / global batch.  Given a `dp.ReplicaLink` (buffers every replica can address)
+the exchange and the update of a bucket are instead one kernel of the library's
+own, `tb200_dp_update`: each rank sums one slice of the bucket through the
+NVSwitch, applies the step and writes the new weights to every replica.
 """
 from . import lib
 
@@ -114,7 +117,7 @@ class MLPStep:
     """One compiled training step; `step(x, y)` runs it once."""
 
     def __init__(self, torch, sizes, batch, rate, activation="gelu_tanh", world=1, global_batch=None,
-                 process_group=None, seed=0, weights=None, biases=None, fuse_update=None, allocate=None):
+                 process_group=None, seed=0, weights=None, biases=None, fuse_update=None, link=None, exchange_blocks=0):
         self.torch = torch
         self.sizes, self.batch, self.rate = list(sizes), batch, rate
         self.world = world
@@ -122,17 +125,24 @@ class MLPStep:
         self.group = process_group
         # the update rides in dw's epilogue unless gradients must first be summed across replicas
         self.fuse_update = (world == 1) if fuse_update is None else (fuse_update and world == 1)
+        self.link = None
         self.fwd_epi, self.bwd_epi, self.saved = ACTIVATIONS[activation]
         bf = torch.bfloat16
         gen = torch.Generator(device="cuda").manual_seed(seed)
         L = len(sizes) - 1
         self.L = L
         self.order, self.offsets, total, self.buckets = flat_layout(self.sizes, self.fuse_update)
-        # `allocate(n)` returns a zeroed BFloat16 device vector of n elements (a caller may hand out memory
-        # registered with its communication library); the gaps that align each array are zero in both
-        # buffers and stay zero (0 + alpha * 0)
-        make = allocate or (lambda n: torch.zeros(n, device="cuda", dtype=bf))
-        self.params, self.grads = make(total), make(total)
+        # the gaps that align each array are zero in both buffers and stay zero (0 + alpha * 0).  With a `link`
+        # (dp.ReplicaLink: buffers every replica can address) the exchange and the update are one kernel of the
+        # library's own (tb200_dp_update) instead of an NCCL all-reduce followed by y += alpha x
+        self.link = link if world > 1 else None
+        if self.link is not None:
+            if self.link.elements < total:
+                raise ValueError("the replica link is smaller than the step's parameters")
+            self.params, self.grads = self.link.params[:total], self.link.grads[:total]
+        else:
+            self.params, self.grads = (torch.zeros(total, device="cuda", dtype=bf) for _ in range(2))
+        self.exchange_blocks = exchange_blocks
 
         def view(flat, at, *shape):
             return flat[at: at + _count(shape)].view(*shape)
@@ -162,6 +172,9 @@ class MLPStep:
         self.launches = 0
         self._plans = None
         self._x_ptr = None
+        self._dp = None
+        if self.link is not None:
+            self._dp = [self.link.desc(first, last, -rate, exchange_blocks) for first, last, _ in self.buckets]
 
     def parameters(self):
         return self.w, self.b
@@ -258,6 +271,14 @@ class MLPStep:
                 if i > 0:
                     order.append(("below", i))
                 order.append(("grads", i))
+        elif self.link is not None:
+            # the fused exchange writes the new weights of a bucket as soon as it runs, so a middle layer's
+            # gradients (and with them its exchange) wait until the layer below has its gradient
+            for i in range(L - 1, 0, -1):
+                order.append(("below", i))
+                if i <= L - 2:
+                    order.append(("grads", i))
+            order += [("grads", L - 1), ("grads", 0)]
         else:
             for i in range(L - 1, 0, -1):
                 order.append(("below", i))
@@ -311,13 +332,20 @@ class MLPStep:
         ready.record(cur)
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ready)
-            torch.distributed.all_reduce(self.bucket[j], group=self.group)
+            if self._dp is not None:
+                lib.dp_update(self._dp[j], self.comm_stream.cuda_stream)   # the sum and the update, every replica
+                self.launches += 1
+            else:
+                torch.distributed.all_reduce(self.bucket[j], group=self.group)
             done = torch.cuda.Event()
             done.record(self.comm_stream)
         return done
 
     def _update(self, j, stream):
-        """params[first:last] -= rate * grads[first:last]: every weight and bias of bucket j in one launch."""
+        """params[first:last] -= rate * grads[first:last]: every weight and bias of bucket j in one launch
+        (nothing to do where the exchange kernel has already written the new parameters)."""
+        if self._dp is not None:
+            return
         first, last, _ = self.buckets[j]
         bf16 = lib.BF16
         lib.axpy(self.params.data_ptr() + 2 * first, self.grads.data_ptr() + 2 * first, -self.rate, last - first,
@@ -364,7 +392,8 @@ class MLPStep:
                     self._grads(i, st)
 
         stretches = [(j, record(lambda st, ops=ops: play(ops, st))) for j, ops in pieces]
-        updates = [record(lambda st, j=j: self._update(j, st)) for j, _ in pieces]
+        # (with the fused exchange there is no separate update to record)
+        updates = [record(lambda st, j=j: self._update(j, st)) if self._dp is None else None for j, _ in pieces]
         torch.cuda.synchronize()
         self._graphs = (stretches, updates)
 
@@ -378,7 +407,8 @@ class MLPStep:
             for done, update in zip(events, updates):
                 if done is not None:
                     cur.wait_event(done)
-                update.replay()
+                if update is not None:
+                    update.replay()
             return self.loss
 
         return replay
@@ -387,10 +417,12 @@ class MLPStep:
         """Records one single-GPU step into a CUDA graph, as Tempest captures a compiled call
         (ext/CUDAExt.jl:565-572), and returns `replay()`: one graph launch per step instead of some
         thirty kernel launches.  x and y are read in place at every replay; the loss lands in
-        `self.loss`.  Data-parallel steps are not captured whole: their all-reduces stay outside any
-        graph (`capture_segments`)."""
-        if self.world != 1:
-            raise ValueError("capture() records single-GPU steps only")
+        `self.loss`.  A data-parallel step is captured whole only with the fused exchange (its kernel is
+        the library's own and is recorded like any other, on the side stream forked from and joined back
+        into the recording; every replica must then replay the graph the same number of times, since the
+        replicas meet inside it).  With NCCL the all-reduces stay outside any graph (`capture_segments`)."""
+        if self.world != 1 and self._dp is None:
+            raise ValueError("capture() records single-GPU steps, or data-parallel steps with the fused exchange")
         torch = self.torch
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())

@@ -89,7 +89,12 @@ def test_flat_layout(pkg):
     class Fake:
         pass
     step = Fake()
-    step.L, step.fuse_update, step.buckets = 4, False, mlp.flat_layout(sizes, False)[3]
+    step.L, step.fuse_update, step.buckets, step.link = 4, False, mlp.flat_layout(sizes, False)[3], None
     plan = mlp.MLPStep._schedule(step)
     assert plan == [("below", 3), ("grads", 2), ("exchange", 0), ("below", 2), ("grads", 1), ("exchange", 1),
                     ("below", 1), ("grads", 3), ("grads", 0), ("exchange", 2)]
+    # with the fused exchange (it writes the new weights at once) a layer's exchange waits for the layer below
+    step.link = object()
+    plan = mlp.MLPStep._schedule(step)
+    assert plan == [("below", 3), ("below", 2), ("grads", 2), ("exchange", 0), ("below", 1), ("grads", 1), ("exchange", 1),
+                    ("grads", 3), ("grads", 0), ("exchange", 2)]

@@ -250,6 +250,23 @@ def test_a_bounded_wait_runs_out_and_the_device_stays_usable(pkg, cuda):
     torch.cuda.synchronize()                                              # and the kernel ends by itself
     code = L.device_error()
     assert code in (3, 4), code                # the MMA thread's or the epilogue's wait for operands gave up
+    # a plan with more tiles than SMs draws them from a counter: same ending, and the counters are left ready
+    big = 2048
+    A2 = torch.randn(big, K, device="cuda").bfloat16()
+    B2 = torch.randn(K, big, device="cuda").bfloat16()
+    C2 = torch.zeros(big, big, device="cuda", dtype=torch.bfloat16)
+    plan = L.GemmPlan(L.gemm_desc(big, big, K, debug=1), A2.data_ptr(), B2.data_ptr(), C2.data_ptr())
+    plan.launch()
+    assert L.device_error() in (3, 4)
+    plan.close()
+    plan = L.GemmPlan(L.gemm_desc(big, big, K), A2.data_ptr(), B2.data_ptr(), C2.data_ptr())
+    for _ in range(3):
+        C2.zero_()
+        plan.launch()
+        want2 = A2.float() @ B2.float()
+        assert (C2.float() - want2).abs().max().item() <= ATOL_BF16 * want2.abs().max().item()
+    assert L.device_error() == 0
+    plan.close()
     assert L.device_error() == 0               # reading it cleared it
     L.gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, debug=1)
     with pytest.raises(L.TB200Error):
