@@ -309,15 +309,33 @@ size_t tb200_attention_bwd_workspace_bytes(const tb200_attn_desc *desc);
  * laid out as q, k, v).  Recomputes the scores, P = exp(s - lse), with
  * delta = sum_d dout*o from the output as stored (the reference's
  * `rounded_backward`, docs/src/cuda.md:54-63); P and dS enter their products
- * rounded to BFloat16 (docs/src/cuda.md:40-46).  Deterministic: dk and dv are
- * folded per key tile over the queries, dq by a second kernel per query tile
- * over the keys, with no atomic adds -- the reference's `deterministic = true`
- * form (ext/cuTileExt/build.jl:295-318) of its backward kernel
- * (ext/cuTileExt/transpose.jl:32-48, 165-213).  workspace:
- * tb200_attention_bwd_workspace_bytes bytes, 16-byte aligned. */
+ * rounded to BFloat16 (docs/src/cuda.md:40-46).  Two forms, chosen by
+ * desc->deterministic as the reference's `CUDATarget(...; deterministic)` chooses
+ * (src/Compiler/runtime/target.jl:31):
+ *   0  one kernel per key tile over the queries that keeps dk and dv in tensor
+ *      memory and adds each step's dq contribution into a Float32 accumulator in
+ *      the workspace, then a kernel that rounds it (ext/cuTileExt/transpose.jl:
+ *      165-187 `added_folds` / `add_step!`, :201-213 `late_kernel`): five products
+ *      per step; dq repeats to Float32 rounding, not bit for bit;
+ *   1  dk and dv folded per key tile over the queries, dq by a second kernel per
+ *      query tile over the keys, no atomic adds, results repeat bit for bit
+ *      (ext/cuTileExt/build.jl:295-318): seven products.
+ * workspace: tb200_attention_bwd_workspace_bytes bytes (it depends on the form),
+ * 16-byte aligned.  Head dimensions other than 128 run the CUDA-core kernels,
+ * which are deterministic either way. */
 int tb200_attention_bwd(const tb200_attn_desc *desc, const void *q, const void *k, const void *v,
                         const void *o, const float *lse, const void *dout, void *dq, void *dk,
                         void *dv, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Times both forms on these operands and returns the `deterministic` value (0 or 1)
+ * of the faster one, or a negative status: the measured stage of the reference's
+ * search over a claim's variants (src/Compiler/Implement/Implement.jl:120) over the
+ * library's two schedules.  For callers that accept either form.  Overwrites dq, dk,
+ * dv with the pullback's result, synchronises the stream (call it while building,
+ * not inside a capture); workspace sized for deterministic = 0. */
+int tb200_attention_bwd_tune(const tb200_attn_desc *desc, const void *q, const void *k, const void *v,
+                             const void *o, const float *lse, const void *dout, void *dq, void *dk,
+                             void *dv, void *workspace, size_t workspace_bytes, void *stream);
 
 int tb200_attention_bwd_device_error(void);
 
@@ -525,7 +543,7 @@ size_t tb200_colreduce_source(const tb200_group_desc *desc, char *buffer, size_t
  * the same number of times. */
 typedef struct tb200_dp_desc {
     int rank, world;             /* world <= 16 */
-    int blocks;                  /* thread blocks (SMs) the kernel occupies; 0 = 16; the same on every rank */
+    int blocks;                  /* thread blocks (SMs) the kernel occupies; 0 = 8; the same on every rank */
     int dtype;                   /* TB200_BF16 */
     int64_t count;               /* elements in the range, a multiple of 8 */
     float alpha;                 /* -rate */

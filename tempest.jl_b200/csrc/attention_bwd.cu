@@ -1,6 +1,14 @@
-// Flash-attention backward for sm_100a, the deterministic two-kernel form: no atomics, every
-// gradient element is written once, results repeat bit for bit (the reference's `deterministic = true`
-// spelling, where dQ is a second fold of its own: ext/cuTileExt/build.jl:295-318, docs/src/cuda.md:64-75).
+// Flash-attention backward for sm_100a, in the reference's two spellings.
+//
+// Default (`deterministic = false`, src/Compiler/runtime/target.jl:31): ONE kernel over key tiles that keeps dK and
+// dV in tensor memory, forms each step's dQ contribution as a product of its own and adds it into a Float32
+// workspace with red.global.add (ext/cuTileExt/transpose.jl:165-187, `added_folds` / `add_step!`), and a small
+// kernel that rounds the workspace to BFloat16 (`late_kernel`, :201-213).  Five products per step, the algorithmic
+// count; the order in which key tiles add into a dQ row is whatever the hardware makes it, so dQ repeats to
+// Float32 rounding, not bit for bit.
+//
+// `deterministic = true`: two kernels, no atomics, every gradient element written once, results repeat bit for
+// bit (dQ is a second fold of its own: ext/cuTileExt/build.jl:295-318, docs/src/cuda.md:64-75); seven products.
 //
 //   stats      delta[m] = sum_d dO[d,m] o[d,m] (o as stored in BFloat16) and lse * log2(e), both
 //              re-laid out [batch][head][query] (rows padded to whole steps) so that consecutive queries are
@@ -27,6 +35,14 @@
 // cannot overwrite P / dS of step t early.  Accumulators stay in tensor memory for the whole item.
 // Work is walked (batch, head)-major with a heavy and a light tile paired per CTA (see Steps).
 // Tensor memory: S | dP | two 128-column accumulators = 512 columns.
+//
+// The one-kernel form is the dK/dV pipeline with one more product per step: dS' (keys x queries), which the row
+// threads already hold, is also written to shared memory as [key][query] lines, and dQ' (features x queries) =
+// K' (features x keys, the item's K tile read as an MN-major A operand) * dS' lands in the dP columns once the
+// step's dK and dV products have read P and dS from them (MMAs of a CTA run in issue order).  The row threads
+// read it back at the start of the next step -- lanes are now features, so one warp instruction adds 32
+// consecutive features of one query: a 128-byte line -- and only then is the next dP issued into those columns;
+// their adds run under that product.  Per step the tensor pipe runs  S(t+1) | dK(t) dV(t) dQ(t) | dP(t+1).
 // No load uses cluster multicast.  Every barrier wait is bounded.
 #include <cuda.h>
 
@@ -60,6 +76,7 @@ struct AttnBwdArgs {
     CUtensorMap out1, out2;         // dK/dV: dV, dK | dQ: -, dQ     (boxes of 32 rows)
     const float *lse2;              // [batch][head][q_pad]  lse * log2(e)
     const float *delta;             // [batch][head][q_pad]
+    float *dq_acc;                  // one-kernel form: [batch][query][head][feature] Float32, zero before the launch
     int batch, heads, kv_heads, queries, keys;
     int q_pad;                      // queries rounded up to whole steps: rows of the two arrays above, zero-filled
     int outer_tiles, supers;
@@ -154,8 +171,10 @@ struct Steps {
     }
 };
 
-template <bool DKDV>
+// MODE 0: dQ of the deterministic form; 1: its dK / dV; 2: the one-kernel form (dK, dV, and dQ by atomic adds).
+template <int MODE>
 __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __grid_constant__ AttnBwdArgs p) {
+    constexpr bool DKDV = MODE != 0, ATOMIC = MODE == 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *s_outer_a = smem;
@@ -164,6 +183,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
     uint8_t *s_ring_a = s_outer_b + kTileBytes;          // SA x 32 KB
     uint8_t *s_ring_b = s_ring_a + SA * kTileBytes;      // SB x 32 KB
     uint8_t *s_out = s_ring_b + SB * kTileBytes;         // 2 x 16 KB: one slab per group, stages the stores
+    // one-kernel form: the step's dS' as [key][query] lines, one 64-query slab per group; each row warp writes and
+    // later stages in its own 32 rows of its group's slab only, and the item's last dQ product has read the lines
+    // before the item's results are staged, so the two uses share the buffer
+    uint8_t *s_ds = s_out;
 
     __shared__ __align__(8) uint64_t outer_full, outer_empty, acc_done, acc_free;
     __shared__ __align__(8) uint64_t a_full[SA], a_empty[SA], b_full[SB], b_empty[SB];
@@ -173,6 +196,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
     // every row warp has written P and dS; by step parity, because the dQ kernel's row warps may finish step
     // t + 1 (its scores and dP are issued ahead) before the issuing thread has looked at step t
     __shared__ __align__(8) uint64_t pds_full[2];
+    __shared__ __align__(8) uint64_t dq_full;           // one-kernel form: the step's dQ' is in the dP columns
+    __shared__ __align__(8) uint64_t x1_free;           // every row warp has read it: the next dP may be issued
     __shared__ uint32_t tmem_base_smem;
     __shared__ int failed_smem;
     // dK/dV: the step's 128 queries' lse*log2(e) [0, 128) and delta [128, 256), one buffer per stage of the dO ring:
@@ -189,6 +214,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
         for (int s = 0; s < SB; s++) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
         mbar_init(&s_full, 1); mbar_init(&dp_full[0], 1); mbar_init(&dp_full[1], 1);
         mbar_init(&s_read, kRowWarps); mbar_init(&pds_full[0], kRowWarps); mbar_init(&pds_full[1], kRowWarps);
+        mbar_init(&dq_full, 1); mbar_init(&x1_free, kRowWarps);
         fence_barrier_init();
         prefetch_tensormap(&p.outer_a); prefetch_tensormap(&p.outer_b);
         prefetch_tensormap(&p.inner_a); prefetch_tensormap(&p.inner_b);
@@ -250,6 +276,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
         if (elect_one()) {
             const uint32_t idesc_t = umma_idesc_bf16(kOuter, kInner, false, false);   // scores: both K-major
             const uint32_t idesc_g = umma_idesc_bf16(kOuter, kD, false, true);        // gradients: B MN-major
+            const uint32_t idesc_q = umma_idesc_bf16(kD, kInner, true, true);         // dQ' = K' dS': both MN-major
+            const uint32_t ds_smem = smem_u32(s_ds);
             const uint32_t oa = smem_u32(s_outer_a), ob = smem_u32(s_outer_b);
             uint32_t outer_phase = 0, c0 = 0, item_count = 0;
             bool ok = true;
@@ -275,6 +303,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
             // accumulator), so dP of step c is issued with the scores, before the gradient product of step c - 1.
             auto issue_dp = [&](uint32_t c) -> bool {
                 const int st = c % SB;
+                // one-kernel form: the dQ' of the step before sits in these columns until the row warps have read it
+                if (ATOMIC && c > 0 && !bwd_wait(&x1_free, (c - 1) & 1, failed, 15)) return false;
                 if (!bwd_wait(&b_full[st], (c / SB) & 1, failed, 14)) return false;
                 tcgen05_fence_after();
                 const uint32_t ib = smem_u32(s_ring_b + st * kTileBytes);
@@ -300,7 +330,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                     continue;
                 }
                 if (!issue_scores(c0) || !issue_dp(c0)) break;
-                if (steps.count == 1) tcgen05_commit(&outer_empty);
+                if (!ATOMIC && steps.count == 1) tcgen05_commit(&outer_empty);
                 for (int t = 0; t < steps.count; t++) {
                     const uint32_t c = c0 + t;
                     const int sta = c % SA, stb = c % SB;
@@ -334,9 +364,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                         }
                         tcgen05_commit(&b_empty[stb]);
                     }
+                    if (ATOMIC) {
+                        // dQ' (features x queries) = K' dS': A = the item's K tile, a line of 64 features per key
+                        // and slab; B = the dS' lines the row threads wrote, a line of 64 queries per key and slab
+#pragma unroll
+                        for (int k = 0; k < kOuter / 16; k++)
+                            tcgen05_mma_f16(tmem_dp, umma_smem_desc(oa + k * 2048, kSlab, 1024),
+                                            umma_smem_desc(ds_smem + k * 2048, kSlab, 1024), idesc_q, k != 0);
+                        tcgen05_commit(&dq_full);
+                        if (t + 1 == steps.count) tcgen05_commit(&outer_empty);   // the last reader of the item's K
+                    }
                     if (DKDV && t + 1 < steps.count) {
                         if (!issue_dp(c + 1)) { ok = false; break; }
-                        if (t + 2 == steps.count) tcgen05_commit(&outer_empty);
+                        if (!ATOMIC && t + 2 == steps.count) tcgen05_commit(&outer_empty);
                     }
                     if (t + 1 == steps.count) tcgen05_commit(&acc_done);
                 }
@@ -366,6 +406,30 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
             }
             bool ok = true;
             typename Steps<DKDV>::Cursor cur;
+            // One-kernel form: the dQ' of the step before, read out of the dP columns (lanes are features here, so
+            // `row` is this thread's feature) and added into the Float32 workspace: 32 consecutive features of one
+            // query per warp instruction.  The columns are handed back before the adds are issued.
+            int prev_hi = 0, prev_pos0 = 0;
+            auto add_dq = [&](uint32_t step) -> bool {
+                if (!bwd_wait(&dq_full, step & 1, failed, 16)) return false;
+                tcgen05_fence_after();
+                uint32_t dq[64];
+                tmem_ld_32x32(t_dp0, *reinterpret_cast<uint32_t(*)[32]>(&dq[0]));
+                tmem_ld_32x32(t_dp0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&dq[32]));
+                tmem_ld_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&x1_free);
+                const int q0 = prev_pos0 + group * 64;
+                const long long line = static_cast<long long>(p.heads) * kD;
+                float *dst = p.dq_acc + ((static_cast<long long>(steps.b) * p.queries + q0) * p.heads + prev_hi) * kD + row;
+                const int live = p.queries - q0;   // queries of this half that exist
+#pragma unroll
+                for (int i = 0; i < 64; i++)
+                    if (i < live)
+                        asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + i * line), "f"(__uint_as_float(dq[i])) : "memory");
+                return true;
+            };
             for (int t = 0; t < steps.count; t++, c++) {
                 const uint32_t ph = c & 1;
                 int hi, pos0;
@@ -421,6 +485,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                         s[4 * g + 2] = __float_as_uint(p2); s[4 * g + 3] = __float_as_uint(p3);
                     }
                 }
+                if (ATOMIC) {
+                    if (t > 0 && !add_dq(c - 1)) { ok = false; break; }
+                    prev_hi = hi;
+                    prev_pos0 = pos0;
+                }
                 if (!bwd_wait(&dp_full[ph], (c >> 1) & 1, failed, 9)) { ok = false; break; }
                 const uint32_t t_dp = t_dp0 + (DKDV ? 0 : ph * 128);
                 tcgen05_fence_after();
@@ -458,12 +527,23 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                     }
                 }
                 tmem_st_32x32(t_dp + 32, dk);
+                if (ATOMIC) {
+                    // the same dS' as this key's line of its group's slab (64 queries = 128 bytes, 16-byte chunks
+                    // swizzled by the row as the tensor core expects), for the dQ' product
+                    uint8_t *line = s_ds + group * kSlab + row * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        *reinterpret_cast<uint4 *>(line + ((j ^ (row & 7)) << 4)) =
+                            make_uint4(dk[4 * j], dk[4 * j + 1], dk[4 * j + 2], dk[4 * j + 3]);
+                    fence_proxy_async();
+                }
                 tmem_st_wait();
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&pds_full[ph]);
             }
             if (!ok) break;
+            if (ATOMIC && steps.count > 0 && !add_dq(c - 1)) break;   // the item's last step
             // ---- the item's gradients: accumulators -> BFloat16 -> shared staging -> TMA stores.
             // dK/dV: group 0 writes dV, group 1 dK, one 64-feature slab at a time; dQ: each group one slab.
             if (steps.count > 0) {
@@ -554,6 +634,16 @@ __global__ void __launch_bounds__(256) attention_stats_kernel(const __nv_bfloat1
     }
 }
 
+// The one-kernel form's second launch: dq = BFloat16(scale * accumulated Float32) (the reference's `late_kernel`,
+// ext/cuTileExt/transpose.jl:201-213).  Eight elements a thread.
+__global__ void __launch_bounds__(256) attention_dq_round_kernel(const float4 *acc, uint4 *dq, long long vectors, float scale) {
+    for (long long i = blockIdx.x * 256ll + threadIdx.x; i < vectors; i += gridDim.x * 256ll) {
+        const float4 a = __ldcs(acc + 2 * i), b = __ldcs(acc + 2 * i + 1);
+        __stcs(dq + i, make_uint4(pack_bf16x2(a.x * scale, a.y * scale), pack_bf16x2(a.z * scale, a.w * scale),
+                                  pack_bf16x2(b.x * scale, b.y * scale), pack_bf16x2(b.z * scale, b.w * scale)));
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -589,8 +679,9 @@ int bwd_tmap(CUtensorMap *map, const void *base, int d, int heads, int positions
     return r == CUDA_SUCCESS ? TB200_OK : TB200_ERR_UNSUPPORTED;
 }
 
-template <bool DKDV>
+template <int MODE>
 int launch_bwd(AttnBwdArgs &p, const DeviceInfo &dev, cudaStream_t stream) {
+    constexpr bool DKDV = MODE != 0;
     // the tiles (224 KB, 1024-byte aligned) sit behind the kernel's static shared memory: take all the dynamic
     // shared memory the SM has left
     const size_t tiles = 2 * kTileBytes + (Rings<DKDV>::A + Rings<DKDV>::B) * kTileBytes + 2 * kSlab;
@@ -600,18 +691,18 @@ int launch_bwd(AttnBwdArgs &p, const DeviceInfo &dev, cudaStream_t stream) {
         std::lock_guard<std::mutex> hold(lock);
         if (!dynamic_bytes[dev.device]) {
             cudaFuncAttributes attr;
-            TB200_CUDA(cudaFuncGetAttributes(&attr, attention_bwd_kernel<DKDV>));
+            TB200_CUDA(cudaFuncGetAttributes(&attr, attention_bwd_kernel<MODE>));
             const size_t first = (attr.sharedSizeBytes + 1023) / 1024 * 1024;
             if (first + tiles > dev.smem_optin) return TB200_ERR_UNSUPPORTED;
             const size_t room = dev.smem_optin - attr.sharedSizeBytes;
-            TB200_CUDA(cudaFuncSetAttribute(attention_bwd_kernel<DKDV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            TB200_CUDA(cudaFuncSetAttribute(attention_bwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             static_cast<int>(room)));
             dynamic_bytes[dev.device] = room;
         }
     }
     const size_t smem = dynamic_bytes[dev.device];
     const unsigned grid = static_cast<unsigned>(p.supers < dev.sms ? p.supers : dev.sms);
-    attention_bwd_kernel<DKDV><<<grid, kBwdThreads, smem, stream>>>(p);
+    attention_bwd_kernel<MODE><<<grid, kBwdThreads, smem, stream>>>(p);
     TB200_CUDA(cudaGetLastError());
     return TB200_OK;
 }
@@ -621,10 +712,20 @@ int launch_bwd(AttnBwdArgs &p, const DeviceInfo &dev, cudaStream_t stream) {
 
 using namespace tb200;
 
+namespace {
+size_t bwd_stat_bytes(const tb200_attn_desc *d) {
+    const size_t q_pad = (static_cast<size_t>(d->queries) + kInner - 1) / kInner * kInner;
+    return (static_cast<size_t>(2) * d->batch * d->heads * q_pad * sizeof(float) + 255) / 256 * 256;
+}
+}  // namespace
+
+// The per-query statistics, and for the one-kernel form on the tensor-core path the Float32 dQ accumulator.
 extern "C" size_t tb200_attention_bwd_workspace_bytes(const tb200_attn_desc *d) {
     if (!d || d->batch <= 0 || d->heads <= 0 || d->queries <= 0) return 0;
-    const size_t q_pad = (static_cast<size_t>(d->queries) + kInner - 1) / kInner * kInner;
-    return static_cast<size_t>(2) * d->batch * d->heads * q_pad * sizeof(float);
+    size_t bytes = bwd_stat_bytes(d);
+    if (!d->deterministic && d->head_dim == kD)
+        bytes += static_cast<size_t>(d->batch) * d->queries * d->heads * kD * sizeof(float);
+    return bytes;
 }
 
 extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v,
@@ -657,7 +758,7 @@ extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, cons
     float *lse2 = static_cast<float *>(workspace);
     float *delta = lse2 + stat_len;
     {
-        if (q_pad != d->queries) TB200_CUDA(cudaMemsetAsync(workspace, 0, need, stream));   // the pads are read
+        if (q_pad != d->queries) TB200_CUDA(cudaMemsetAsync(workspace, 0, bwd_stat_bytes(d), stream));   // the pads are read
         const long long threads = static_cast<long long>(d->batch) * d->heads * d->queries * 16;
         const unsigned blocks = static_cast<unsigned>(ceil_div(threads, 256));
         attention_stats_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(o),
@@ -678,7 +779,21 @@ extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, cons
     if ((st = bwd_tmap(&p.out2, dk, kD, d->kv_heads, d->keys, d->batch, 32))) return st;
     p.outer_tiles = static_cast<int>(ceil_div(d->keys, kOuter));
     p.supers = (p.outer_tiles + 1) / 2 * d->batch * d->kv_heads;
-    if ((st = launch_bwd<true>(p, dev, stream))) return st;
+    if (!d->deterministic) {
+        // one kernel: dK and dV as above, each step's dQ contribution added into the Float32 accumulator, which a
+        // second small kernel rounds
+        const size_t elements = static_cast<size_t>(d->batch) * d->queries * d->heads * kD;
+        p.dq_acc = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + bwd_stat_bytes(d));
+        TB200_CUDA(cudaMemsetAsync(p.dq_acc, 0, elements * sizeof(float), stream));
+        if ((st = launch_bwd<2>(p, dev, stream))) return st;
+        const long long vectors = static_cast<long long>(elements / 8);
+        const long long blocks = ceil_div(vectors, 256);
+        attention_dq_round_kernel<<<static_cast<unsigned>(blocks < dev.sms * 16ll ? blocks : dev.sms * 16ll), 256, 0, stream>>>(
+            reinterpret_cast<const float4 *>(p.dq_acc), static_cast<uint4 *>(dq), vectors, d->scale);
+        TB200_CUDA(cudaGetLastError());
+        return TB200_OK;
+    }
+    if ((st = launch_bwd<1>(p, dev, stream))) return st;
     // dQ: items over query tiles
     if ((st = bwd_tmap(&p.outer_a, q, kD, d->heads, d->queries, d->batch, kOuter))) return st;
     if ((st = bwd_tmap(&p.outer_b, dout, kD, d->heads, d->queries, d->batch, kOuter))) return st;
@@ -687,7 +802,46 @@ extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, cons
     if ((st = bwd_tmap(&p.out2, dq, kD, d->heads, d->queries, d->batch, 32))) return st;
     p.outer_tiles = static_cast<int>(ceil_div(d->queries, kOuter));
     p.supers = (p.outer_tiles + 1) / 2 * d->batch * d->heads;
-    return launch_bwd<false>(p, dev, stream);
+    return launch_bwd<0>(p, dev, stream);
+}
+
+// Times the two forms of the pullback on the caller's own operands and returns the `deterministic` value of the
+// faster one (0 = one kernel with atomic adds, 1 = two kernels): the measured stage of the reference's search over
+// a claim's variants (src/Compiler/Implement/Implement.jl:120), here over the two hand-written schedules.  A caller
+// that needs bit-repeatable gradients does not ask.  Overwrites dq, dk, dv with the pullback's own result,
+// synchronises the stream; `workspace` must hold tb200_attention_bwd_workspace_bytes of the desc with
+// deterministic = 0 (the larger of the two).  Other head dimensions than 128 have one schedule: returns 1.
+extern "C" int tb200_attention_bwd_tune(const tb200_attn_desc *d, const void *q, const void *k, const void *v, const void *o,
+                                        const float *lse, const void *dout, void *dq, void *dk, void *dv, void *workspace,
+                                        size_t workspace_bytes, void *stream_) {
+    if (!d) return TB200_ERR_NULL;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    tb200_attn_desc trial = *d;
+    if (d->head_dim != kD) {
+        trial.deterministic = 1;
+        const int st = tb200_attention_bwd(&trial, q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream_);
+        return st ? st : 1;
+    }
+    cudaEvent_t t0, t1;
+    TB200_CUDA(cudaEventCreate(&t0));
+    TB200_CUDA(cudaEventCreate(&t1));
+    float best_ms = 0.0f;
+    int best = 1, status = TB200_OK;
+    for (int form : {1, 0}) {
+        trial.deterministic = form;
+        if ((status = tb200_attention_bwd(&trial, q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream_))) break;
+        if (cudaEventRecord(t0, stream) != cudaSuccess) { status = TB200_ERR_CUDA; break; }
+        for (int rep = 0; rep < 3 && !status; rep++)
+            status = tb200_attention_bwd(&trial, q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream_);
+        if (status) break;
+        float ms = 0.0f;
+        if (cudaEventRecord(t1, stream) != cudaSuccess || cudaEventSynchronize(t1) != cudaSuccess ||
+            cudaEventElapsedTime(&ms, t0, t1) != cudaSuccess) { status = TB200_ERR_CUDA; break; }
+        if (form == 1 || ms < best_ms) { best_ms = ms; best = form; }
+    }
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+    return status ? status : best;
 }
 
 extern "C" int tb200_attention_bwd_device_error(void) {

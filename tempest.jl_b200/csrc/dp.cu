@@ -205,9 +205,9 @@ extern "C" int tb200_dp_update(const tb200_dp_desc *d, void *stream_) {
     if (st) return st;
     // every rank must launch the same number of blocks (block b meets block b): a function of the
     // descriptor alone, not of the device
-    // (16 measured best on 2 and on 8 B200s: more blocks take SMs from the products that run beside the exchange
-    // without moving the bytes any faster)
-    int blocks = d->blocks > 0 ? d->blocks : 16;
+    // (measured on 8 B200s, 84 MB of gradients: 48 blocks 0.289 ms, 16 blocks 0.261 ms, 8 blocks 0.236 ms -- more
+    // blocks take SMs from the products that run beside the exchange without moving the bytes any faster)
+    int blocks = d->blocks > 0 ? d->blocks : 8;
     if (blocks > kDpMaxBlocks) blocks = kDpMaxBlocks;
     if (multimem) dp_update_kernel<true><<<blocks, kDpThreads, 0, stream>>>(a);
     else dp_update_kernel<false><<<blocks, kDpThreads, 0, stream>>>(a);

@@ -84,7 +84,7 @@ class Target:
     """What of `CUDATarget` the kernels look at (src/Compiler/runtime/target.jl:71-75)."""
     device: int = 0
     online: bool = True
-    deterministic: bool = True
+    deterministic: bool = False   # the reference's default (src/Compiler/runtime/target.jl:31)
 
 
 def dense_columns(buffer, eltype, n, rows, value=0, offset=0, ld=None):
@@ -427,13 +427,26 @@ class B200Kernels:
             return LinearLaunch(b), f"B200 {b.template}, {e['m']} x {e['n']} over {e['k']}, {b.arrays['w'].eltype}"
         if b.template.startswith("attention"):
             launch = AttentionLaunch(b)
+            form = ""
             if b.template.endswith("_pullback"):
+                # a target that wants repeatable bits gets the two-kernel form; any other gets whichever of the two
+                # forms measures faster on these operands (the measured stage of the cover's search over variants)
+                launch.desc.deterministic = 0
                 need = lib.attention_bwd_workspace_bytes(launch.desc)
                 resources = resources if resources is not None else Resources()
                 launch.workspace, launch.workspace_bytes = resources.workspace(need), need
+                if target.deterministic:
+                    launch.desc.deterministic = 1
+                else:
+                    a = b.arrays
+                    launch.desc.deterministic = lib.attention_bwd_tune(
+                        launch.desc, a["q"].pointer(), a["k"].pointer(), a["v"].pointer(), a["o"].pointer(),
+                        a["lse"].pointer(), a["g"].pointer(), a["dq"].pointer(), a["dk"].pointer(), a["dv"].pointer(),
+                        launch.workspace.data_ptr(), need, current_stream())
+                form = ", two kernels (deterministic)" if launch.desc.deterministic else ", one kernel (dq by atomic adds)"
             e = b.extents
             return launch, (f"B200 {b.template}, {e['h']} heads over {e['hk']} of {e['d']} features, "
-                            f"{e['m']} queries by {e['n']} keys, batch {e['b']}")
+                            f"{e['m']} queries by {e['n']} keys, batch {e['b']}{form}")
         eltype = row_eltype(b)
         dtype = ELTYPES[eltype][0]
         n, rows = b.extents["n"], b.extents["rows"]

@@ -118,6 +118,7 @@ SIGNATURES = {
     "tb200_attention_device_error": (_i, []),
     "tb200_attention_bwd_workspace_bytes": (_sz, [ctypes.POINTER(AttnDesc)]),
     "tb200_attention_bwd": (_i, [ctypes.POINTER(AttnDesc), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "tb200_attention_bwd_tune": (_i, [ctypes.POINTER(AttnDesc), _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "tb200_attention_bwd_device_error": (_i, []),
     "tb200_device_errors": (_i, []),
     "tb200_deltanet_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
@@ -422,6 +423,14 @@ def attention_bwd_workspace_bytes(desc):
 def attention_bwd(desc, q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream=0):
     check("tb200_attention_bwd", load().tb200_attention_bwd(
         ctypes.byref(desc), q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream or None))
+
+
+def attention_bwd_tune(desc, q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream=0):
+    """Times the pullback's two forms on these operands; returns the `deterministic` value (0 or 1) of the faster."""
+    form = load().tb200_attention_bwd_tune(ctypes.byref(desc), q, k, v, o, lse, dout, dq, dk, dv, workspace,
+                                           workspace_bytes, stream or None)
+    check("tb200_attention_bwd_tune", min(form, 0))
+    return form
 
 
 def attention_bwd_device_error():
