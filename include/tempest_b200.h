@@ -519,6 +519,42 @@ int tb200_colreduce_compiled(const tb200_group_desc *desc, const void *const *in
                              void *workspace, size_t workspace_bytes, void *stream);
 size_t tb200_colreduce_source(const tb200_group_desc *desc, char *buffer, size_t buffer_bytes);
 
+/* ---- scans: running folds along or across the rows --------------------------------
+ * y = the running fold of x: every element of the result is the fold of the elements up to and
+ * including its own position (Julia's `cumsum`, `cumprod`, `accumulate(max, ...)`, and `accumulate` by a
+ * `GenericFold`), forward or from the far end (`reverse`: the derivative of a cumulative sum scans
+ * backwards).  Replaces the kernels the reference generates for `:scan` groups
+ * (ext/cuTileExt/build.jl:715-760), on the folds its scan tests exercise (test/cuda/scans.jl:12-22):
+ *   SUM, PROD, MAX, MIN   the builtin folds (src/Compiler/IR/folds.jl:66-89)
+ *   AFFINE                h = a h_prev + b from pairs (a, b) = (x, x2), starting from h = 0: the
+ *                         `GenericFold` recurrence of src/Compiler/IR/folds.jl:279-288 and
+ *                         test/fixtures/programs.jl:51-54 (combine ((a1,b1),(a2,b2)) = (a2 a1, a2 b1 + b2),
+ *                         observe = last)
+ *   VARIANCE              the running population variance by Welford's state merged Chan's way
+ *                         (test/fixtures/programs.jl:44)
+ * x, y are Julia (n, rows) matrices, memory [rows][n] with row pitches ld_* (elements); `across` = 0 scans
+ * along each row (Julia dims = 1, the contiguous axis), 1 scans across the rows (dims = 2), one scan per
+ * column; `batch` such matrices lie stride_* elements apart (a scan along the middle axis of a 3-axis
+ * array is `across` over a batch).  Float32 or BFloat16 elements, Float32 states, results rounded once.
+ * The order in which partial states are combined differs from a sequential sweep's (it is a tree over
+ * threads), which rounds differently: the reference compares at rtol 1e-4 (test/cuda/scans.jl:27).
+ * No workspace, nothing kept between calls. */
+typedef enum tb200_scan_op {
+    TB200_SCAN_SUM = 0, TB200_SCAN_PROD = 1, TB200_SCAN_MAX = 2, TB200_SCAN_MIN = 3,
+    TB200_SCAN_AFFINE = 4, TB200_SCAN_VARIANCE = 5
+} tb200_scan_op;
+typedef struct tb200_scan_desc {
+    int64_t n, rows;
+    int64_t ld_x, ld_x2, ld_y;
+    int64_t batch;                       /* 0 or 1 = one matrix */
+    int64_t stride_x, stride_x2, stride_y;
+    int op;                              /* tb200_scan_op */
+    int across;
+    int reverse;
+    int dtype;
+} tb200_scan_desc;
+int tb200_scan(const tb200_scan_desc *desc, const void *x, const void *x2, void *y, void *stream);
+
 /* ---- data-parallel update: gradient sum + SGD step in one kernel over NVLink -----
  * The exchange of a data-parallel training step (the reference spells it `r .+ s` over the devices'
  * gradients followed by the update on each, realised by peer copies and sums:

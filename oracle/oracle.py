@@ -136,6 +136,26 @@ def mean_var_f32(x):
     return m.value, v.value
 
 
+def scan(x, op, x2=None, across=False, reverse=False):
+    """The running fold of a [rows][n] Float32 array (or BFloat16 bits: widened, scanned in Float32, rounded once),
+    element after element in sequence: along each row, or across the rows (one scan per column).  op: "sum", "prod",
+    "max", "min", "affine" (h = x h + x2 from h = 0), "variance" (running population variance)."""
+    code = {"sum": 0, "prod": 1, "max": 2, "min": 3, "affine": 4, "variance": 5}[op]
+    if x.dtype == np.uint16:
+        out = scan(from_bf16(x), op, None if x2 is None else from_bf16(x2), across, reverse)
+        return to_bf16(out)
+    x = np.ascontiguousarray(x, np.float32)
+    x2c = None if x2 is None else np.ascontiguousarray(x2, np.float32)
+    y = np.empty_like(x)
+    rows, n = x.shape
+    fn = load().oracle_scan_f32
+    for k in range(n if across else rows):
+        off = k if across else k * n
+        fn(_ptr(x.reshape(-1)[off:]), None if x2c is None else _ptr(x2c.reshape(-1)[off:]), _ptr(y.reshape(-1)[off:]),
+           _i64(rows if across else n), _i64(n if across else 1), _int(code), _int(int(reverse)))
+    return y
+
+
 # ------------------------------------------------------------ row kernels ----
 
 def _rows(x):

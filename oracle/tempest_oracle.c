@@ -465,3 +465,34 @@ float oracle_readme_loss_grad(const float *w, const float *b, const float *x, fl
     free(gz);
     return loss;
 }
+
+/* ---- scans ------------------------------------------------------------------------------------------
+ * The running fold of a vector taken in sequence, one state carried from element to element, as the
+ * reference's CPU path sweeps a scan (src/Compiler/codegen/scalar.jl:200-256 with the scanned axis kept;
+ * folds: src/Compiler/IR/folds.jl:66-89, the GenericFold recurrence :279-288, Welford's variance named
+ * with GenericFold test/fixtures/programs.jl:40-44).  op: 0 sum, 1 prod, 2 max, 3 min, 4 affine
+ * (h = a h + b from (x[i], x2[i]), h starting at 0), 5 running population variance.  `stride` is the
+ * distance between consecutive scanned elements; `reverse` starts at the far end. */
+void oracle_scan_f32(const float *x, const float *x2, float *y, int64_t count, int64_t stride, int op, int reverse) {
+    float acc = op == 1 ? 1.0f : op == 2 ? -INFINITY : op == 3 ? INFINITY : 0.0f;
+    float n = 0.0f, mean = 0.0f, m2 = 0.0f;
+    for (int64_t p = 0; p < count; p++) {
+        const int64_t i = (reverse ? count - 1 - p : p) * stride;
+        const float v = x[i];
+        switch (op) {
+            case 0: acc = acc + v; break;
+            case 1: acc = acc * v; break;
+            case 2: acc = v > acc ? v : acc; break;
+            case 3: acc = v < acc ? v : acc; break;
+            case 4: acc = v * acc + x2[i]; break;
+            default: {   /* Welford: one element joins the state */
+                n += 1.0f;
+                const float d = v - mean;
+                mean += d / n;
+                m2 += d * (v - mean);
+                acc = m2 / n;
+            }
+        }
+        y[i] = acc;
+    }
+}

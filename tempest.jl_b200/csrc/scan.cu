@@ -1,0 +1,243 @@
+// Scans (running folds) for sm_100a: cumulative sum / product / maximum / minimum, the affine recurrence
+// h = a h_prev + b named with a GenericFold, and a running variance -- the folds of the reference's scan tests
+// (test/cuda/scans.jl:12-22; the user folds are test/fixtures/programs.jl:44, 51-54; the documented recurrence is
+// src/Compiler/IR/folds.jl:279-288), forward or reversed (a cumulative sum's derivative scans backwards), along
+// the contiguous axis of a (n, rows) matrix or across its rows, over a batch of such matrices.  They stand for
+// the kernels the reference generates for `:scan` groups (ext/cuTileExt/build.jl:715-760: a block per tile of
+// the kept axes sweeps the scanned axis a tile at a step, carrying each lane's state).
+//
+// Along a row (the scanned axis is contiguous): one block per row sweeps it in tiles of 256 threads x 8
+// elements.  A thread scans its own eight elements in registers, the threads' totals are scanned by warp shuffles
+// and one exchange through shared memory, and the carry of the tiles before is combined in front: every element
+// is read once and written once.  States combine strictly left to right (the affine recurrence does not commute).
+// Across the rows (the scanned axis is the strided one): one thread per column walks the rows in order with its
+// state in a register; neighbouring threads read neighbouring columns, so every access is coalesced.
+// Float32 or BFloat16 elements; states and arithmetic in Float32, each result rounded once.
+#include "common.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kScanThreads = 256;
+constexpr int kScanPer = 8;   // elements a thread scans in registers
+
+// One state per fold: `lift` an element, `combine` (earlier, later), `observe` the running result.
+struct SumState { float v; };
+struct AffineState { float a, b; };        // x -> a x + b
+struct MomentState { float n, mean, m2; }; // count, mean, centred sum of squares (Chan's merge)
+
+template <int OP> struct Fold;
+template <> struct Fold<TB200_SCAN_SUM> {
+    using S = SumState;
+    static __device__ __forceinline__ S identity() { return {0.0f}; }
+    static __device__ __forceinline__ S lift(float x, float) { return {x}; }
+    static __device__ __forceinline__ S combine(S l, S r) { return {l.v + r.v}; }
+    static __device__ __forceinline__ float observe(S s) { return s.v; }
+};
+template <> struct Fold<TB200_SCAN_PROD> {
+    using S = SumState;
+    static __device__ __forceinline__ S identity() { return {1.0f}; }
+    static __device__ __forceinline__ S lift(float x, float) { return {x}; }
+    static __device__ __forceinline__ S combine(S l, S r) { return {l.v * r.v}; }
+    static __device__ __forceinline__ float observe(S s) { return s.v; }
+};
+template <> struct Fold<TB200_SCAN_MAX> {
+    using S = SumState;
+    static __device__ __forceinline__ S identity() { return {-INFINITY}; }
+    static __device__ __forceinline__ S lift(float x, float) { return {x}; }
+    static __device__ __forceinline__ S combine(S l, S r) { return {fmaxf(l.v, r.v)}; }
+    static __device__ __forceinline__ float observe(S s) { return s.v; }
+};
+template <> struct Fold<TB200_SCAN_MIN> {
+    using S = SumState;
+    static __device__ __forceinline__ S identity() { return {INFINITY}; }
+    static __device__ __forceinline__ S lift(float x, float) { return {x}; }
+    static __device__ __forceinline__ S combine(S l, S r) { return {fminf(l.v, r.v)}; }
+    static __device__ __forceinline__ float observe(S s) { return s.v; }
+};
+// combine((a1, b1), (a2, b2)) = (a2 a1, a2 b1 + b2), observe = last, from init (1, 0): h_t = a_t h_{t-1} + b_t
+template <> struct Fold<TB200_SCAN_AFFINE> {
+    using S = AffineState;
+    static __device__ __forceinline__ S identity() { return {1.0f, 0.0f}; }
+    static __device__ __forceinline__ S lift(float a, float b) { return {a, b}; }
+    static __device__ __forceinline__ S combine(S l, S r) { return {r.a * l.a, fmaf(r.a, l.b, r.b)}; }
+    static __device__ __forceinline__ float observe(S s) { return s.b; }
+};
+// Welford's state merged Chan's way; observe = m2 / n, the population variance of the prefix
+template <> struct Fold<TB200_SCAN_VARIANCE> {
+    using S = MomentState;
+    static __device__ __forceinline__ S identity() { return {0.0f, 0.0f, 0.0f}; }
+    static __device__ __forceinline__ S lift(float x, float) { return {1.0f, x, 0.0f}; }
+    static __device__ __forceinline__ S combine(S l, S r) {
+        const float n = l.n + r.n;
+        if (n == 0.0f) return {0.0f, 0.0f, 0.0f};
+        const float d = r.mean - l.mean, w = r.n / n;
+        return {n, fmaf(d, w, l.mean), l.m2 + r.m2 + d * d * l.n * w};
+    }
+    static __device__ __forceinline__ float observe(S s) { return s.n > 0.0f ? s.m2 / s.n : 0.0f; }
+};
+
+template <typename S> struct Words { static constexpr int N = sizeof(S) / 4; };
+
+template <typename S>
+__device__ __forceinline__ S shuffle_up(S s, int delta) {
+    union { S s; float f[Words<S>::N]; } u;
+    u.s = s;
+#pragma unroll
+    for (int i = 0; i < Words<S>::N; i++) u.f[i] = __shfl_up_sync(0xffffffffu, u.f[i], delta);
+    return u.s;
+}
+
+template <typename T> __device__ __forceinline__ float load1(const T *p);
+template <> __device__ __forceinline__ float load1<float>(const float *p) { return *p; }
+template <> __device__ __forceinline__ float load1<__nv_bfloat16>(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void store1(T *p, float v);
+template <> __device__ __forceinline__ void store1<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store1<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+struct ScanArgs {
+    const void *x, *x2;
+    void *y;
+    long long n, rows, batch;
+    long long ld_x, ld_x2, ld_y;            // row pitches, elements
+    long long stride_x, stride_x2, stride_y;   // between the matrices of the batch
+    int reverse;
+};
+
+// ---- along each row
+template <int OP, typename T>
+__global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanArgs a) {
+    using F = Fold<OP>;
+    using S = typename F::S;
+    __shared__ S warp_total[kScanThreads / 32];
+    __shared__ S tile_total;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (long long item = blockIdx.x; item < a.rows * a.batch; item += gridDim.x) {
+        const long long m = item / a.rows, row = item - m * a.rows;
+        const T *x = static_cast<const T *>(a.x) + m * a.stride_x + row * a.ld_x;
+        const T *x2 = a.x2 ? static_cast<const T *>(a.x2) + m * a.stride_x2 + row * a.ld_x2 : nullptr;
+        T *y = static_cast<T *>(a.y) + m * a.stride_y + row * a.ld_y;
+        S carry = F::identity();
+        for (long long base = 0; base < a.n; base += kScanThreads * kScanPer) {
+            // this thread's eight consecutive scan positions; position p is element p, or n - 1 - p when reversed
+            const long long p0 = base + threadIdx.x * kScanPer;
+            S local[kScanPer];
+            S run = F::identity();
+#pragma unroll
+            for (int e = 0; e < kScanPer; e++) {
+                const long long p = p0 + e;
+                S s = F::identity();
+                if (p < a.n) {
+                    const long long i = a.reverse ? a.n - 1 - p : p;
+                    s = F::lift(load1(x + i), x2 ? load1(x2 + i) : 0.0f);
+                }
+                run = F::combine(run, s);
+                local[e] = run;
+            }
+            // inclusive scan of the threads' totals inside the warp, then of the warps' totals
+            S incl = run;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const S left = shuffle_up(incl, d);
+                if (lane >= d) incl = F::combine(left, incl);
+            }
+            if (lane == 31) warp_total[warp] = incl;
+            __syncthreads();
+            S before = carry;                       // everything ahead of this thread: earlier tiles, warps, lanes
+            for (int w = 0; w < warp; w++) before = F::combine(before, warp_total[w]);
+            S lane_excl = shuffle_up(incl, 1);
+            if (lane > 0) before = F::combine(before, lane_excl);
+            if (threadIdx.x == kScanThreads - 1) tile_total = F::combine(before, run);
+#pragma unroll
+            for (int e = 0; e < kScanPer; e++) {
+                const long long p = p0 + e;
+                if (p < a.n) {
+                    const long long i = a.reverse ? a.n - 1 - p : p;
+                    store1(y + i, F::observe(F::combine(before, local[e])));
+                }
+            }
+            __syncthreads();
+            carry = tile_total;
+            __syncthreads();   // tile_total and warp_total are rewritten by the next tile
+        }
+    }
+}
+
+// ---- across the rows: one thread per column
+template <int OP, typename T>
+__global__ void __launch_bounds__(kScanThreads) scan_columns_kernel(const ScanArgs a) {
+    using F = Fold<OP>;
+    using S = typename F::S;
+    const long long col = blockIdx.x * static_cast<long long>(kScanThreads) + threadIdx.x;
+    if (col >= a.n) return;
+    for (long long m = blockIdx.y; m < a.batch; m += gridDim.y) {
+        const T *x = static_cast<const T *>(a.x) + m * a.stride_x + col;
+        const T *x2 = a.x2 ? static_cast<const T *>(a.x2) + m * a.stride_x2 + col : nullptr;
+        T *y = static_cast<T *>(a.y) + m * a.stride_y + col;
+        S run = F::identity();
+        for (long long p = 0; p < a.rows; p++) {
+            const long long r = a.reverse ? a.rows - 1 - p : p;
+            run = F::combine(run, F::lift(load1(x + r * a.ld_x), x2 ? load1(x2 + r * a.ld_x2) : 0.0f));
+            store1(y + r * a.ld_y, F::observe(run));
+        }
+    }
+}
+
+template <int OP, typename T>
+int launch_scan(const ScanArgs &a, bool across, const DeviceInfo &dev, cudaStream_t stream) {
+    if (across) {
+        dim3 grid(static_cast<unsigned>(ceil_div(a.n, kScanThreads)), static_cast<unsigned>(a.batch < 65535 ? a.batch : 65535));
+        scan_columns_kernel<OP, T><<<grid, kScanThreads, 0, stream>>>(a);
+    } else {
+        const long long items = a.rows * a.batch;
+        const long long most = static_cast<long long>(dev.sms) * 8;
+        scan_rows_kernel<OP, T><<<static_cast<unsigned>(items < most ? items : most), kScanThreads, 0, stream>>>(a);
+    }
+    TB200_CUDA(cudaGetLastError());
+    return TB200_OK;
+}
+
+template <typename T>
+int launch_by_op(int op, const ScanArgs &a, bool across, const DeviceInfo &dev, cudaStream_t stream) {
+    switch (op) {
+        case TB200_SCAN_SUM: return launch_scan<TB200_SCAN_SUM, T>(a, across, dev, stream);
+        case TB200_SCAN_PROD: return launch_scan<TB200_SCAN_PROD, T>(a, across, dev, stream);
+        case TB200_SCAN_MAX: return launch_scan<TB200_SCAN_MAX, T>(a, across, dev, stream);
+        case TB200_SCAN_MIN: return launch_scan<TB200_SCAN_MIN, T>(a, across, dev, stream);
+        case TB200_SCAN_AFFINE: return launch_scan<TB200_SCAN_AFFINE, T>(a, across, dev, stream);
+        case TB200_SCAN_VARIANCE: return launch_scan<TB200_SCAN_VARIANCE, T>(a, across, dev, stream);
+        default: return TB200_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace
+}  // namespace tb200
+
+using namespace tb200;
+
+extern "C" int tb200_scan(const tb200_scan_desc *d, const void *x, const void *x2, void *y, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!d) return TB200_ERR_NULL;
+    if (d->dtype != TB200_F32 && d->dtype != TB200_BF16) return TB200_ERR_DTYPE;
+    if (d->op < TB200_SCAN_SUM || d->op > TB200_SCAN_VARIANCE) return TB200_ERR_UNSUPPORTED;
+    const long long batch = d->batch > 1 ? d->batch : 1;
+    if (d->n < 0 || d->rows < 0 || d->batch < 0 || d->ld_x < d->n || d->ld_y < d->n) return TB200_ERR_SHAPE;
+    const bool pairs = d->op == TB200_SCAN_AFFINE;
+    if (pairs && d->ld_x2 < d->n) return TB200_ERR_SHAPE;
+    if (d->n == 0 || d->rows == 0) return TB200_OK;
+    if (!x || !y || (pairs && !x2)) return TB200_ERR_NULL;
+    const size_t es = dtype_size(d->dtype);
+    if (!aligned_to(x, es) || !aligned_to(y, es) || !aligned_to(x2, es)) return TB200_ERR_ALIGN;
+    if (batch > 1 && (d->stride_x < 0 || d->stride_y < (d->rows - 1) * d->ld_y + d->n)) return TB200_ERR_SHAPE;
+    DeviceInfo dev;
+    int st = current_device(&dev);
+    if (st) return st;
+    ScanArgs a{};
+    a.x = x; a.x2 = pairs ? x2 : nullptr; a.y = y;
+    a.n = d->n; a.rows = d->rows; a.batch = batch;
+    a.ld_x = d->ld_x; a.ld_x2 = d->ld_x2; a.ld_y = d->ld_y;
+    a.stride_x = d->stride_x; a.stride_x2 = d->stride_x2; a.stride_y = d->stride_y;
+    a.reverse = d->reverse != 0;
+    if (d->dtype == TB200_F32) return launch_by_op<float>(d->op, a, d->across != 0, dev, stream);
+    return launch_by_op<__nv_bfloat16>(d->op, a, d->across != 0, dev, stream);
+}

@@ -175,3 +175,32 @@ def test_mlp_step_by_blas_equals_the_sequential_restatement(oracle):
         assert np.abs(seq[3][i] - fast[3][i]).max() <= 1e-2 * max(1.0, np.abs(seq[3][i]).max())
         for k, j in ((4, i), (5, i), (6, i + 1), (7, i)):   # updated w and b, the activations, what the activation saw
             assert np.abs(oracle.from_bf16(seq[k][j]) - oracle.from_bf16(fast[k][j])).max() <= 2e-2
+
+
+def test_generic_fold_recurrence_known_answer(oracle):
+    # accumulate(recurrence, [(0.5, 1.0), (0.5, 1.0), (0.5, 1.0)]) == [1.0, 1.5, 1.75] with
+    # combine((a1, b1), (a2, b2)) = (a2 a1, a2 b1 + b2), observe = last   (src/Compiler/IR/folds.jl:279-288)
+    a = np.full((1, 3), 0.5, np.float32)
+    b = np.ones((1, 3), np.float32)
+    assert oracle.scan(a, "affine", b).ravel().tolist() == [1.0, 1.5, 1.75]
+    assert oracle.scan(a.T.copy(), "affine", b.T.copy(), across=True).ravel().tolist() == [1.0, 1.5, 1.75]
+
+
+def test_scans_against_numpy(oracle):
+    x = oracle.data(40, 7, scale=0.37).astype(np.float32)          # [7][40]
+    assert np.allclose(oracle.scan(x, "sum"), np.cumsum(x.astype(np.float64), axis=1), rtol=1e-5, atol=1e-5)
+    assert np.allclose(oracle.scan(x, "sum", across=True), np.cumsum(x.astype(np.float64), axis=0), rtol=1e-5, atol=1e-5)
+    assert np.allclose(oracle.scan(x, "max", reverse=True), np.maximum.accumulate(x[:, ::-1], axis=1)[:, ::-1])
+    assert np.allclose(oracle.scan(1 + 0.01 * x, "prod"), np.cumprod(1 + 0.01 * x.astype(np.float64), axis=1), rtol=1e-5)
+    var = np.array([[x[r, : i + 1].astype(np.float64).var() for i in range(40)] for r in range(7)])
+    assert np.allclose(oracle.scan(x, "variance"), var, rtol=1e-4, atol=1e-5)
+
+
+def test_updated_state_and_its_sum_known_answer(oracle):
+    # f!(s, x) = (s .= 0.5 .* s .+ x; sum(s)) with s = [1, 2], x = [1, 1] gives (3.5, [1.5, 2.0])
+    # (docs/src/compiling.md:23-29): the update is the affine step h = a h + b per element, the value a plain sum
+    # written as two-element scans, one per entry of s: the first step loads s (a = 0, b = s), the second is the update
+    a = np.array([[0.0, 0.5], [0.0, 0.5]], np.float32)
+    b = np.array([[1.0, 1.0], [2.0, 1.0]], np.float32)
+    new = oracle.scan(a, "affine", b)[:, 1]
+    assert new.tolist() == [1.5, 2.0] and oracle.sum_f32(new) == 3.5
