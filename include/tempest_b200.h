@@ -436,7 +436,14 @@ typedef enum tb200_term_op {
     TB200_T_RSQRT = 16, TB200_T_ABS = 17, TB200_T_ABS2 = 18, TB200_T_RECIP = 19, TB200_T_SIGMOID = 20,
     TB200_T_FMA = 21,    /* a * b + c, fused */
     TB200_T_SELECT = 22, /* a > 0 ? b : c */
-    TB200_T_ROUND_BF16 = 23 /* Cast to BFloat16 and back: the rounding an Apply of that eltype makes */
+    TB200_T_ROUND_BF16 = 23, /* Cast to BFloat16 and back: the rounding an Apply of that eltype makes */
+    /* The two below describe groups that tb200_group_route recognises and hands to a kernel of their own; the term
+     * interpreter and the generator decline them. */
+    TB200_T_RECOMPUTED = 24, /* sum over e < c of X[row][e] * Y[i][e]: a fold formed where it is read (Recomputed,
+                                src/Compiler/IR/terms.jl:69-87) over one extra axis of extent c; a = input X of
+                                shape TB200_SHAPE_ROW_VECTORS, b = input Y of shape TB200_SHAPE_ALONG_VECTORS */
+    TB200_T_ROW_INDEX = 25   /* the row's own position, 0-based, as Float32: with TB200_T_INDEX under a
+                                TB200_T_SELECT it spells a mask on two positions (ext/cuTileExt/mask.jl:54-75) */
 } tb200_term_op;
 
 typedef struct tb200_term { int op, a, b, c; float imm; } tb200_term;
@@ -444,16 +451,20 @@ typedef struct tb200_term { int op, a, b, c; float imm; } tb200_term;
 typedef enum tb200_fold_kind {
     TB200_FOLD_SUM = 0, TB200_FOLD_MAX = 1, TB200_FOLD_MIN = 2, TB200_FOLD_PROD = 3,
     TB200_FOLD_LOGSUMEXP = 4, /* observes log(sum(exp(y))) from the online (max, rebased sum) state */
-    TB200_FOLD_MEANVAR = 5    /* observes the mean; TB200_T_STAT2 reads sum((y - mean)^2) / n */
+    TB200_FOLD_MEANVAR = 5,   /* observes the mean; TB200_T_STAT2 reads sum((y - mean)^2) / n */
+    TB200_FOLD_WEIGHTED = 6   /* sum over i of term(i) * V[i][:], one vector per row: `payload` = input V of shape
+                                 TB200_SHAPE_ALONG_VECTORS (the pair element of the attention fold; routed only) */
 } tb200_fold_kind;
 
-typedef struct tb200_fold { int kind, term, phase; } tb200_fold;
+typedef struct tb200_fold { int kind, term, phase, payload; } tb200_fold;
 
 typedef enum tb200_group_shape {
     TB200_SHAPE_FULL = 0,    /* (n, rows): element (i, row) at row * ld + i */
     TB200_SHAPE_ALONG = 1,   /* (n,): one value per position, shared by all rows (a LayerNorm weight) */
     TB200_SHAPE_PER_ROW = 2, /* (rows,): one value per row (a saved statistic) */
-    TB200_SHAPE_SCALAR = 3
+    TB200_SHAPE_SCALAR = 3,
+    TB200_SHAPE_ROW_VECTORS = 4,   /* (ld, rows): a vector of ld elements per row (routed groups only) */
+    TB200_SHAPE_ALONG_VECTORS = 5  /* (ld, n): a vector of ld elements per position along the row */
 } tb200_group_shape;
 
 typedef struct tb200_group_input { int shape, dtype; int64_t ld; } tb200_group_input;
@@ -477,6 +488,19 @@ int tb200_rowreduce_generic_check(const tb200_group_desc *desc);
 /* inputs[i], outputs[j]: device addresses in the descriptor's order.  No workspace. */
 int tb200_rowreduce_generic(const tb200_group_desc *desc, const void *const *inputs, void *const *outputs,
                             void *stream);
+
+/* Groups with a kernel of their own.  tb200_group_route looks at the structure of a descriptor's terms, as the
+ * reference's generator decides which of its sketches claims a group (ext/cuTileExt/cuTileExt.jl:899-929), and
+ * answers which dedicated kernel computes it: the attention group of the reference's plans -- scores recomputed
+ * over the features, optionally masked to the positions up to the row's own, their log-sum-exp, and the weights'
+ * sum of the value rows (test/fixtures/operations.jl:21-76 as the planner groups it) -- is the one it knows.
+ * tb200_group_attention runs such a descriptor: it states the computation at one (head, batch) of the domain's
+ * outer axes (n = keys, rows = queries), `heads`, `kv_heads`, `batch` give those axes, and the inputs are the
+ * reference's whole (features, heads, positions, batch) arrays; outputs as tb200_attention_fwd writes them. */
+typedef enum tb200_route { TB200_ROUTE_NONE = 0, TB200_ROUTE_ATTENTION = 1, TB200_ROUTE_ATTENTION_CAUSAL = 2 } tb200_route;
+int tb200_group_route(const tb200_group_desc *desc);
+int tb200_group_attention(const tb200_group_desc *desc, int heads, int kv_heads, int batch, const void *const *inputs,
+                          void *const *outputs, void *stream);
 
 /* The same groups compiled: the descriptor is turned into CUDA source with its
  * extents, element types, alignment and schedule as constants, compiled for

@@ -26,6 +26,7 @@ _i64, _int, _flt, _void = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c
 
 def build(force=False):
     srcs = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith((".c", ".inc"))]
+    srcs.append(os.path.join(os.path.dirname(HERE), "include", "tempest_b200.h"))   # group.c reads its data layouts
     if force or not os.path.exists(LIB) or any(os.path.getmtime(s) > os.path.getmtime(LIB) for s in srcs):
         subprocess.run(["make", "-C", HERE, "-B", "liboracle.so"], check=True, capture_output=True)
     return LIB

@@ -11,13 +11,13 @@ from . import lib as L
 
 OPS = {"load": 0, "lit": 1, "index": 2, "stat": 3, "stat2": 4, "add": 5, "sub": 6, "mul": 7, "div": 8, "max": 9,
        "min": 10, "neg": 11, "exp": 12, "log": 13, "tanh": 14, "sqrt": 15, "rsqrt": 16, "abs": 17, "abs2": 18,
-       "recip": 19, "sigmoid": 20, "fma": 21, "select": 22, "round_bf16": 23}
-ARITY = {**{k: 0 for k in ("load", "lit", "index", "stat", "stat2")},
+       "recip": 19, "sigmoid": 20, "fma": 21, "select": 22, "round_bf16": 23, "recomputed": 24, "row_index": 25}
+ARITY = {**{k: 0 for k in ("load", "lit", "index", "stat", "stat2", "recomputed", "row_index")},
          **{k: 2 for k in ("add", "sub", "mul", "div", "max", "min")},
          **{k: 1 for k in ("neg", "exp", "log", "tanh", "sqrt", "rsqrt", "abs", "abs2", "recip", "sigmoid", "round_bf16")},
          "fma": 3, "select": 3}
-FOLDS = {"sum": 0, "max": 1, "min": 2, "prod": 3, "logsumexp": 4, "meanvar": 5}
-SHAPES = {"full": 0, "along": 1, "per_row": 2, "scalar": 3}
+FOLDS = {"sum": 0, "max": 1, "min": 2, "prod": 3, "logsumexp": 4, "meanvar": 5, "weighted": 6}
+SHAPES = {"full": 0, "along": 1, "per_row": 2, "scalar": 3, "row_vectors": 4, "along_vectors": 5}
 DTYPES = {"Float32": L.F32, "BFloat16": L.BF16}
 
 
@@ -50,6 +50,15 @@ class Group:
     def index(self):
         return self._term("index")
 
+    def row_index(self):
+        """The row's own position (with `index` under a `select`: a mask on two positions)."""
+        return self._term("row_index")
+
+    def recomputed(self, per_row, along, extent):
+        """sum over e < extent of X[row][e] * Y[i][e]: a fold formed where it is read (`Recomputed`,
+        src/Compiler/IR/terms.jl:69-87); X an input of shape "row_vectors", Y one of shape "along_vectors"."""
+        return self._term("recomputed", per_row, along, extent)
+
     def stat(self, fold, second=False):
         return self._term("stat2" if second else "stat", fold, level=self.folds[fold][2] + 1)
 
@@ -65,10 +74,10 @@ class Group:
         raise AttributeError(op)
 
     # ---- folds and outputs
-    def fold(self, kind, term):
+    def fold(self, kind, term, payload=0):
         """The fold runs in the first phase in which its term is known (a term that reads a statistic waits
-        for that statistic's phase to finish)."""
-        self.folds.append((FOLDS[kind], int(term), self._level[term]))
+        for that statistic's phase to finish).  `payload`: the input of value rows a "weighted" fold sums."""
+        self.folds.append((FOLDS[kind], int(term), self._level[term], int(payload)))
         return len(self.folds) - 1
 
     def output(self, term, eltype="Float32", ld=None):
@@ -93,8 +102,8 @@ class Group:
         for i, (op, a, b, c, imm) in enumerate(self.terms):
             t = d.terms[i]
             t.op, t.a, t.b, t.c, t.imm = op, a, b, c, imm
-        for i, (kind, term, phase) in enumerate(self.folds):
-            d.folds[i].kind, d.folds[i].term, d.folds[i].phase = kind, term, phase
+        for i, (kind, term, phase, payload) in enumerate(self.folds):
+            d.folds[i].kind, d.folds[i].term, d.folds[i].phase, d.folds[i].payload = kind, term, phase, payload
         for i, (source, index, dtype, ld) in enumerate(self.outputs):
             o = d.outputs[i]
             o.source, o.index, o.dtype, o.ld = source, index, dtype, ld
@@ -173,6 +182,27 @@ def rmsnorm(n, rows, eltype="Float32", eps=1.0e-6):
     q = g.fold("sum", g.abs2(x))
     scale = g.rsqrt(g.fma(g.stat(q), g.lit(1.0 / n), g.lit(eps)))
     g.output(g.mul(g.mul(x, scale), w), eltype)
+    return g
+
+
+def attention(keys, queries, features, causal, scale=None, lse=True):
+    """The attention group of the reference's plans at one (head, batch) (test/fixtures/operations.jl:21-76 as the
+    planner groups it, src/Compiler/Implement/groups.jl:106-125): over the keys of each query row fold the pair
+    (score, value row) -- scores recomputed over the features and, when causal, masked to the keys up to the
+    query's own position; their log-sum-exp shares the sweep; the output is the weights' sum of the value rows.
+    Not a row fold of scalars: `lib.group_route` recognises it and `lib.group_attention` runs it."""
+    g = Group(keys, queries)
+    q = g.input("row_vectors", "BFloat16", ld=features)
+    k = g.input("along_vectors", "BFloat16", ld=features)
+    v = g.input("along_vectors", "BFloat16", ld=features)
+    s = g.mul(g.lit(features ** -0.5 if scale is None else scale), g.recomputed(q, k, features))
+    if causal:
+        s = g.select(g.add(g.sub(g.row_index(), g.index()), g.lit(0.5)), s, g.lit(float("-inf")))
+    stat = g.fold("logsumexp", s)
+    o = g.fold("weighted", g.exp(g.sub(s, g.stat(stat))), payload=v)
+    g.output_stat(o, "BFloat16")
+    if lse:
+        g.output_stat(stat, "Float32")
     return g
 
 

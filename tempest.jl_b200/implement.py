@@ -164,6 +164,54 @@ ATTENTION_PULLBACKS = tuple(
     for causal in (False, True))
 
 
+# Scans as Julia spells them (test/cuda/scans.jl:12-22): along the first axis (dims = 1, the contiguous one) or the
+# second (dims = 2) of a (n, rows) matrix; the recurrence takes its pairs from two arrays.
+SCAN_SPELLINGS = {
+    "cumsum": ("x -> cumsum(x; dims)", lib.SCAN_SUM), "cumprod": ("x -> cumprod(x; dims)", lib.SCAN_PROD),
+    "cummax": ("x -> accumulate(max, x; dims)", lib.SCAN_MAX), "cummin": ("x -> accumulate(min, x; dims)", lib.SCAN_MIN),
+    "recurrence": ("(a, b) -> accumulate(RECURRENCE, tuple.(a, b); dims)", lib.SCAN_AFFINE),
+    "running_variance": ("x -> accumulate(VARIANCE, x; dims)", lib.SCAN_VARIANCE),
+}
+SCAN_TEMPLATES = tuple(
+    Template(f"{name}_dims{dims}{'_reverse' if rev else ''}", spelling.replace("dims", f"dims = {dims}") +
+             (" from the last element back" if rev else ""),
+             {"x": ("n", "rows"), **({"x2": ("n", "rows")} if name == "recurrence" else {})}, ("y",))
+    for name, (spelling, _) in SCAN_SPELLINGS.items() for dims in (1, 2) for rev in (False, True))
+
+
+def _scan_parts(template):
+    """(op, across, reverse) of a scan template's name, or None."""
+    base, _, rest = template.partition("_dims")
+    if base not in SCAN_SPELLINGS or not rest or rest[0] not in "12":
+        return None
+    return SCAN_SPELLINGS[base][1], rest[0] == "2", rest.endswith("_reverse")
+
+
+class ScanLaunch:
+    """One scan on fixed operands (tb200_scan)."""
+
+    def __init__(self, binding: "Binding"):
+        self.binding = binding
+        self.op, self.across, self.reverse = _scan_parts(binding.template)
+
+    def repoints(self) -> bool:
+        return True
+
+    def repoint(self, value: int, buffer) -> "ScanLaunch":
+        for s in self.binding.arrays.values():
+            if s.value == value:
+                s.buffer = buffer
+        return self
+
+    def __call__(self):
+        a, e = self.binding.arrays, self.binding.extents
+        ld = lambda s: s.strides[1] if len(s.strides) > 1 and s.size[1] > 1 else s.size[0]   # noqa: E731
+        lib.scan(a["x"].pointer(), a["y"].pointer(), e["n"], e["rows"], self.op,
+                 x2=a["x2"].pointer() if "x2" in a else 0, across=self.across, reverse=self.reverse,
+                 dtype=ELTYPES[a["x"].eltype][0], ld_x=ld(a["x"]), ld_x2=ld(a["x2"]) if "x2" in a else None,
+                 ld_y=ld(a["y"]), stream=current_stream())
+
+
 def dense_matrix(buffer, eltype, rows, cols, value=0, offset=0):
     """A Julia (rows, cols) matrix, dense column-major."""
     return Strided(eltype, offset, (rows, cols), (1, rows), buffer, value)
@@ -349,7 +397,7 @@ class B200Kernels:
         # the row kernels and attention fold each statistic in one pass, which a target that
         # forbids the online rewrites does not permit (ext/cuDNNExt.jl:60-62); products always apply
         online = ROW_TEMPLATES + ATTENTION_TEMPLATES + ATTENTION_PULLBACKS if target.online else ()
-        return LINEAR_TEMPLATES + online
+        return LINEAR_TEMPLATES + SCAN_TEMPLATES + online
 
     def resources(self, target: Target) -> Resources:
         return Resources()
@@ -361,6 +409,11 @@ class B200Kernels:
                 return False
             # the contracted axis of x and the output axis of w and y must be contiguous
             return all(s.strides[0] == 1 or s.size[0] == 1 for s in b.arrays.values())
+        if _scan_parts(b.template) is not None:
+            types = {s.eltype for s in b.arrays.values()}
+            if len(types) != 1 or types.pop() not in ELTYPES or ("x2" in b.arrays) != b.template.startswith("recurrence"):
+                return False
+            return all(s.strides[0] == 1 or s.size[0] == 1 for s in b.arrays.values())   # rows contiguous
         if b.template.startswith("attention"):
             e = b.extents
             if not 0 < e.get("d", 0) <= 256 or e.get("h", 0) % max(e.get("hk", 1), 1) != 0:
@@ -397,6 +450,11 @@ class B200Kernels:
         return True
 
     def estimate(self, target: Target, b: Binding):
+        if _scan_parts(b.template) is not None:
+            e = b.extents
+            size = ELTYPES[b.arrays["x"].eltype][1]
+            across = _scan_parts(b.template)[1]
+            return [Work(bytes=len(b.arrays) * e["n"] * e["rows"] * size, blocks=(e["n"] + 255) // 256 if across else e["rows"])]
         if b.template in LINEAR_SPELLINGS:
             e = b.extents
             size = ELTYPES[b.arrays["w"].eltype][1]
@@ -425,6 +483,9 @@ class B200Kernels:
         if b.template in LINEAR_SPELLINGS:
             e = b.extents
             return LinearLaunch(b), f"B200 {b.template}, {e['m']} x {e['n']} over {e['k']}, {b.arrays['w'].eltype}"
+        if _scan_parts(b.template) is not None:
+            e = b.extents
+            return ScanLaunch(b), f"B200 {b.template}, {e['rows']} rows of {e['n']} {b.arrays['x'].eltype}"
         if b.template.startswith("attention"):
             launch = AttentionLaunch(b)
             form = ""
@@ -496,6 +557,27 @@ class GroupLaunch:
 
 
 @dataclass(frozen=True)
+class AttentionClaim:
+    """What the generator offers for the attention group (recomputed scores, mask, log-sum-exp, weighted value
+    rows): the attention kernels, reached through the descriptor's own structure."""
+    causal: bool
+
+
+class RoutedAttentionLaunch(GroupLaunch):
+    """The launch of a group `lib.group_route` recognised as attention; `outer` = (heads, kv_heads, batch), the
+    domain's outer axes, the buffers the reference's whole (features, heads, positions, batch) arrays."""
+
+    def __init__(self, group, inputs, outputs, outer):
+        super().__init__(group, inputs, outputs, compiled=True)
+        self.outer = outer
+
+    def __call__(self):
+        address = lambda b: b.data_ptr() if hasattr(b, "data_ptr") else int(b)  # noqa: E731
+        lib.group_attention(self.desc, *self.outer, [address(b) for _, b in self.inputs],
+                            [address(b) for _, b in self.outputs], _torch_stream())
+
+
+@dataclass(frozen=True)
 class ColumnClaim:
     """What the generator offers for a group whose folds run over the rows: partial folds per row slab
     (one thread per column) and an ordered merge, two launches, compiled by NVRTC."""
@@ -529,12 +611,15 @@ class B200Generator:
             except lib.TB200Error:
                 return ()
             return (ColumnClaim(),)
+        route = lib.group_route(desc)
+        if route in (lib.ROUTE_ATTENTION, lib.ROUTE_ATTENTION_CAUSAL):
+            return (AttentionClaim(route == lib.ROUTE_ATTENTION_CAUSAL),)
         if lib.rowreduce_generic_check(desc) != 0:
             return ()
         threads = 8
         while threads < 256 and threads * 4 < group.n:
             threads *= 2
-        phases = 1 + max((phase for _, _, phase in group.folds), default=-1) + 1
+        phases = 1 + max((fold[2] for fold in group.folds), default=-1) + 1
         claims = [RowClaim(threads, phases)]
         if lib.rowreduce_compile(desc) == 0:           # NVRTC at hand and the generated source compiles
             claims.insert(0, RowClaim(threads, phases, compiled=True))
@@ -546,6 +631,10 @@ class B200Generator:
     def estimate(self, claim: RowClaim, target: Target, group):
         """One launch moving the group's bytes once; the interpreter also pays for every term of every element
         (`applied` in the reference's Work, src/Compiler/Implement/Implement.jl:61-82)."""
+        if isinstance(claim, AttentionClaim):
+            d = group.inputs[0][2]
+            flops = 4.0 * d * group.n * group.rows * (0.5 if claim.causal else 1.0)
+            return [Work(bytes=2 * d * (2 * group.rows + 2 * group.n), flops=flops)]
         if isinstance(claim, ColumnClaim):
             return [Work(bytes=group.bytes(), blocks=(group.n + 255) // 256, launches=claim.launches, applied=0)]
         applied = 0 if claim.compiled else len(group.terms) * claim.phases
@@ -570,6 +659,12 @@ class B200Generator:
             outs = [(v, buffers[v]) for v in range(k, k + len(group.outputs))]
         if len(ins) != len(group.inputs) or len(outs) != len(group.outputs):
             raise ValueError("build_claim needs one buffer per input and per output")
+        if isinstance(claim, AttentionClaim):
+            heads, kv_heads, batch = buffers.get("outer", (1, 1, 1))
+            d = group.inputs[0][2]
+            return (RoutedAttentionLaunch(group, ins, outs, (heads, kv_heads, batch)),
+                    f"B200 attention{' (causal)' if claim.causal else ''} reached from the group's terms, {heads} heads "
+                    f"over {kv_heads} of {d} features, {group.rows} queries by {group.n} keys, batch {batch}")
         if isinstance(claim, ColumnClaim):
             need = lib.colreduce_workspace_bytes(group.desc())
             resources = resources if resources is not None else Resources()

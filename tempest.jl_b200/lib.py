@@ -88,7 +88,7 @@ class GroupTerm(ctypes.Structure):
 
 
 class GroupFold(ctypes.Structure):
-    _fields_ = [("kind", ctypes.c_int), ("term", ctypes.c_int), ("phase", ctypes.c_int)]
+    _fields_ = [("kind", ctypes.c_int), ("term", ctypes.c_int), ("phase", ctypes.c_int), ("payload", ctypes.c_int)]
 
 
 class GroupOutput(ctypes.Structure):
@@ -137,6 +137,8 @@ SIGNATURES = {
     "tb200_gemm_tune": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
     "tb200_attention_fwd_masked": (_i, [ctypes.POINTER(AttnDesc), ctypes.POINTER(AttnMask), _p, _p, _p, _p, _p, _p]),
     "tb200_attention_bwd_masked": (_i, [ctypes.POINTER(AttnDesc), ctypes.POINTER(AttnMask)] + [_p] * 10),
+    "tb200_group_route": (_i, [ctypes.POINTER(GroupDesc)]),
+    "tb200_group_attention": (_i, [ctypes.POINTER(GroupDesc), _i, _i, _i, ctypes.POINTER(_p), ctypes.POINTER(_p), _p]),
     "tb200_rowreduce_generic_check": (_i, [ctypes.POINTER(GroupDesc)]),
     "tb200_rowreduce_generic": (_i, [ctypes.POINTER(GroupDesc), ctypes.POINTER(_p), ctypes.POINTER(_p), _p]),
     "tb200_rowreduce_compile": (_i, [ctypes.POINTER(GroupDesc), ctypes.c_uint, ctypes.c_uint]),
@@ -600,3 +602,22 @@ def scan(x, y, n, rows, op, *, x2=0, across=False, reverse=False, dtype=F32, ld_
     d.stride_x2 = rows * d.ld_x2 if stride_x2 is None else stride_x2
     d.stride_y = rows * d.ld_y if stride_y is None else stride_y
     check("tb200_scan", load().tb200_scan(ctypes.byref(d), x or None, x2 or None, y or None, stream or None))
+
+
+ROUTE_NONE, ROUTE_ATTENTION, ROUTE_ATTENTION_CAUSAL = 0, 1, 2
+
+
+def group_route(desc):
+    """Which dedicated kernel computes this group (ROUTE_*), judged by the structure of its terms."""
+    r = load().tb200_group_route(ctypes.byref(desc))
+    if r < 0:
+        check("tb200_group_route", r)
+    return r
+
+
+def group_attention(desc, heads, kv_heads, batch, inputs, outputs, stream=0):
+    """Runs a descriptor that `group_route` recognised as attention on the attention kernels."""
+    ins = (_p * max(len(inputs), 1))(*inputs)
+    outs = (_p * max(len(outputs), 1))(*outputs)
+    check("tb200_group_attention", load().tb200_group_attention(ctypes.byref(desc), heads, kv_heads, batch, ins, outs,
+                                                                stream or None))

@@ -271,3 +271,31 @@ def test_column_group_through_the_generator(pkg, cuda, oracle):
     want = x.double().sum(dim=0)
     assert (db.double() - want).abs().max().item() <= 1e-5 * rows ** 0.5 * 4
     assert torch.equal(db, db2)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("heads,kv_heads,batch,S,D", [(2, 2, 1, 200, 128), (4, 2, 2, 133, 128), (3, 1, 3, 70, 32)])
+def test_attention_group_through_the_generic_door(pkg, cuda, oracle, causal, heads, kv_heads, batch, S, D):
+    """The attention group, spelled as terms (recomputed scores, the mask as a select on two positions, log-sum-exp,
+    the weights' sum of the value rows), offered to the generator, claimed as attention and run: against the
+    Float64 restatement of test/fixtures/operations.jl:21-76 (shapes of test/cuda/attention.jl:10-16)."""
+    torch, I, G = cuda, pkg.implement, pkg.groups
+    q = oracle.to_bf16(oracle.normal((batch, S, heads, D), 51))
+    k = oracle.to_bf16(oracle.normal((batch, S, kv_heads, D), 52))
+    v = oracle.to_bf16(oracle.normal((batch, S, kv_heads, D), 53))
+    to = lambda a: torch.from_numpy(a).view(torch.bfloat16).cuda()   # noqa: E731
+    qd, kd, vd = to(q), to(k), to(v)
+    o = torch.full_like(qd, float("nan"))
+    lse = torch.full((batch, S, heads), float("nan"), device="cuda")
+    group = G.attention(S, S, D, causal)
+    gen, target = I.B200Generator(), I.Target()
+    (claim,) = gen.claims(target, group)
+    assert isinstance(claim, I.AttentionClaim)
+    launch, _ = gen.build_claim(claim, target, group, {"inputs": [qd, kd, vd], "outputs": [o, lse], "outer": (heads, kv_heads, batch)})
+    launch()
+    torch.cuda.synchronize()
+    assert pkg.lib.attention_device_error() == 0
+    o64, lse64 = oracle.attention_f64(q, k, v, causal)
+    got = o.float().cpu().numpy()
+    assert np.abs(got - o64).max() <= 2e-2
+    assert np.abs(lse.cpu().numpy() - lse64).max() <= 1e-3

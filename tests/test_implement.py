@@ -17,9 +17,9 @@ def test_templates_follow_the_target(I):
     lib = I.B200Kernels()
     names = [t.name for t in lib.templates(I.Target(online=True))]
     assert "softmax_columns" in names and "layernorm_pullback" in names
-    # a target that keeps the two passes is offered no one-pass fold (ext/cuDNNExt.jl:60-62), only products
+    # a target that keeps the two passes is offered no one-pass fold (ext/cuDNNExt.jl:60-62), only products and scans
     kept = [t.name for t in lib.templates(I.Target(online=False))]
-    assert kept and all(n.startswith("linear") for n in kept)
+    assert kept and all(n.startswith("linear") or "_dims" in n for n in kept)
 
 
 def test_supports(I):
@@ -143,3 +143,20 @@ def test_generator_claims_groups(pkg):
     assert isinstance(cc, I.ColumnClaim)
     (w,) = gen.estimate(cc, t, cols)
     assert w.launches == 2 and w.bytes == 2 * 4096 * 65536 * 2 + 2 * 65536 * 4 + 2 * 4096 * 2
+
+
+def test_scan_templates(I):
+    lib, t = I.B200Kernels(), I.Target()
+    names = [x.name for x in lib.templates(t)]
+    assert "cumsum_dims1" in names and "recurrence_dims2_reverse" in names and "running_variance_dims1" in names
+    assert "cumsum_dims1" in [x.name for x in lib.templates(I.Target(online=False))]     # a scan needs no rewrite
+    n, rows = 1000, 64
+    arrays = {"x": I.dense_columns(None, "Float32", n, rows, 1), "y": I.dense_columns(None, "Float32", n, rows, 2)}
+    b = I.Binding("cumsum_dims2", {"n": n, "rows": rows}, arrays)
+    assert lib.supports(t, b)
+    (w,) = lib.estimate(t, b)
+    assert w.bytes == 2 * n * rows * 4 and w.blocks == 4
+    assert not lib.supports(t, I.Binding("recurrence_dims1", {"n": n, "rows": rows}, arrays))   # the pairs' second array is missing
+    assert not lib.supports(t, I.Binding("cumsum_dims3", {"n": n, "rows": rows}, arrays))
+    launch = I.ScanLaunch(I.Binding("cummax_dims1_reverse", {"n": n, "rows": rows}, arrays))
+    assert (launch.op, launch.across, launch.reverse) == (2, False, True)
