@@ -545,15 +545,36 @@ def group_eval_cols(desc, inputs, wide=False):
         for j in range(desc.n_folds):
             kind, term = desc.folds[j].kind, desc.folds[j].term
             v = np.broadcast_to(t[term], (rows, n))
+            if kind == 4:
+                # the online log-sum-exp, row after row: (maximum, sum of exp(y - maximum)) rebased when the maximum
+                # moves (src/Compiler/IR/folds.jl:123-198)
+                m, ssum = np.full(n, -np.inf, F), np.zeros(n, F)
+                for r in range(rows):
+                    m2 = np.maximum(m, v[r])
+                    shift = np.where(np.isfinite(m2), m2, F(0))
+                    ssum = (ssum * np.exp(m - shift) + np.exp(v[r] - shift)).astype(F)
+                    m = m2.astype(F)
+                folded.append((np.where(ssum > 0, m + np.log(ssum), m).astype(F), None))
+                continue
+            if kind == 5:
+                # Welford's update of (count, mean, centred sum of squares), row after row (folds.jl:143, 166-182)
+                mean, m2s = np.zeros(n, F), np.zeros(n, F)
+                for r in range(rows):
+                    d = (v[r] - mean).astype(F)
+                    mean = (mean + d / F(r + 1)).astype(F)
+                    m2s = (m2s + d * (v[r] - mean)).astype(F)
+                folded.append((mean, (m2s / F(max(rows, 1))).astype(F)))
+                continue
             ident = {0: 0.0, 1: -np.inf, 2: np.inf, 3: 1.0}[kind]
             step = {0: np.add, 1: np.maximum, 2: np.minimum, 3: np.multiply}[kind]
             acc = np.full(n, ident, F)
             for r in range(rows):
                 acc = step(acc, v[r]).astype(F)
-            folded.append(acc)
+            folded.append((acc, None))
     outs = []
     for o in range(desc.n_outputs):
-        v = folded[desc.outputs[o].index].astype(np.float32)
+        first, second = folded[desc.outputs[o].index]
+        v = (second if desc.outputs[o].source == 2 else first).astype(np.float32)
         outs.append(to_bf16(v) if desc.outputs[o].dtype == 1 else v)
     return outs
 

@@ -683,15 +683,25 @@ int check_cols(const tb200_group_desc *d) {
     }
     for (int j = 0; j < d->n_folds; j++) {
         const int kind = d->folds[j].kind;
-        if (kind != TB200_FOLD_SUM && kind != TB200_FOLD_MAX && kind != TB200_FOLD_MIN && kind != TB200_FOLD_PROD)
-            return TB200_ERR_UNSUPPORTED;
+        if (kind < TB200_FOLD_SUM || kind > TB200_FOLD_MEANVAR) return TB200_ERR_UNSUPPORTED;
         if (d->folds[j].term < 0 || d->folds[j].term >= d->n_terms) return TB200_ERR_SHAPE;
     }
     for (int o = 0; o < d->n_outputs; o++) {
-        if (d->outputs[o].from != 1 || d->outputs[o].index < 0 || d->outputs[o].index >= d->n_folds) return TB200_ERR_UNSUPPORTED;
-        if (d->outputs[o].dtype != TB200_F32 && d->outputs[o].dtype != TB200_BF16) return TB200_ERR_DTYPE;
+        const tb200_group_output &out = d->outputs[o];
+        if ((out.from != 1 && out.from != 2) || out.index < 0 || out.index >= d->n_folds) return TB200_ERR_UNSUPPORTED;
+        if (out.from == 2 && d->folds[out.index].kind != TB200_FOLD_MEANVAR) return TB200_ERR_SHAPE;
+        if (out.dtype != TB200_F32 && out.dtype != TB200_BF16) return TB200_ERR_DTYPE;
     }
     return TB200_OK;
+}
+
+// Float32 words of a fold's state: one, two for the log-sum-exp's (maximum, rebased sum), three for the
+// (count, mean, centred sum of squares) of mean and variance
+int state_words(int kind) { return kind == TB200_FOLD_LOGSUMEXP ? 2 : kind == TB200_FOLD_MEANVAR ? 3 : 1; }
+int total_state_words(const tb200_group_desc &d) {
+    int words = 0;
+    for (int j = 0; j < d.n_folds; j++) words += state_words(d.folds[j].kind);
+    return words;
 }
 
 std::string col_load(const tb200_group_desc &d, int i, const std::string &index) {
@@ -737,7 +747,20 @@ std::string generate_cols(const tb200_group_desc &d, int V) {
     E.line(0, "static __device__ __forceinline__ float bf_lo(u32 w) { return __uint_as_float(w << 16); }");
     E.line(0, "static __device__ __forceinline__ float bf_hi(u32 w) { return __uint_as_float(w & 0xffff0000u); }");
     E.line(0, "static __device__ __forceinline__ u32 f2bf(float f) { u16 r; asm(\"cvt.rn.bf16.f32 %0, %1;\" : \"=h\"(r) : \"f\"(f)); return r; }");
-    E.line(0, "constexpr int N = " + num(d.n) + ", NF = " + num(d.n_folds) + ", V = " + num(V) + ";");
+    // NF: Float32 words of all the folds' states (a fold's words lie one after another in the partial rows)
+    E.line(0, "constexpr int N = " + num(d.n) + ", NF = " + num(total_state_words(d)) + ", V = " + num(V) + ";");
+    int word0[TB200_GROUP_MAX_FOLDS];
+    for (int j = 0, w = 0; j < d.n_folds; j++) { word0[j] = w; w += state_words(d.folds[j].kind); }
+    // names of fold j's state words, and of the state an element lifts to
+    auto word = [](int j, int w, const std::string &at) { return std::string(w == 0 ? "f" : w == 1 ? "g" : "h") + num(j) + at; };
+    auto lift = [&](int j, int w) -> std::string {
+        const int kind = d.folds[j].kind;
+        const std::string t = "t" + num(d.folds[j].term);
+        if (kind == TB200_FOLD_LOGSUMEXP) return w == 0 ? t : "1.0f";
+        if (kind == TB200_FOLD_MEANVAR) return w == 0 ? "1.0f" : w == 1 ? t : "0.0f";
+        return t;
+    };
+    auto identity = [&](int j, int w) -> std::string { return w == 0 ? fold_identity(d.folds[j].kind) : "0.0f"; };
     bool used[TB200_GROUP_MAX_INPUTS] = {};
     for (int k = 0; k < d.n_terms; k++)
         if (d.terms[k].op == TB200_T_LOAD) used[d.terms[k].a] = true;
@@ -751,10 +774,11 @@ std::string generate_cols(const tb200_group_desc &d, int V) {
         if (d.inputs[i].shape == TB200_SHAPE_ALONG) col_load_chunk(E, 1, d, i, "i0", V, false);
         if (d.inputs[i].shape == TB200_SHAPE_SCALAR) E.line(1, "const float sc" + num(i) + " = " + col_load(d, i, "0") + ";");
     }
-    for (int j = 0; j < d.n_folds; j++) {
-        E.line(1, "float f" + num(j) + "[V];");
-        E.line(1, "for (int e = 0; e < V; e++) f" + num(j) + "[e] = " + fold_identity(d.folds[j].kind) + ";");
-    }
+    for (int j = 0; j < d.n_folds; j++)
+        for (int w = 0; w < state_words(d.folds[j].kind); w++) {
+            E.line(1, "float " + word(j, w, "[V]") + ";");
+            E.line(1, "for (int e = 0; e < V; e++) " + word(j, w, "[e]") + " = " + identity(j, w) + ";");
+        }
     E.line(1, "#pragma unroll 4");
     E.line(1, "for (i64 r = r0; r < r1; r++) {");
     for (int i = 0; i < d.n_inputs; i++) {
@@ -766,11 +790,13 @@ std::string generate_cols(const tb200_group_desc &d, int V) {
     E.line(2, "for (int e = 0; e < V; e++) {");
     for (int k = 0; k < d.n_terms; k++) E.line(3, "const float t" + num(k) + " = " + term_expr(d, k, "") + ";");
     for (int j = 0; j < d.n_folds; j++)
-        emit_merge(E, 3, d.folds[j].kind, "f" + num(j) + "[e]", "", "", "t" + num(d.folds[j].term), "", "");
+        emit_merge(E, 3, d.folds[j].kind, word(j, 0, "[e]"), word(j, 1, "[e]"), word(j, 2, "[e]"), lift(j, 0), lift(j, 1), lift(j, 2));
     E.line(2, "}");
     E.line(1, "}");
     for (int j = 0; j < d.n_folds; j++)
-        E.line(1, "for (int e = 0; e < V; e++) p.partial[((i64)blockIdx.y * NF + " + num(j) + ") * N + i0 + e] = f" + num(j) + "[e];");
+        for (int w = 0; w < state_words(d.folds[j].kind); w++)
+            E.line(1, "for (int e = 0; e < V; e++) p.partial[((i64)blockIdx.y * NF + " + num(word0[j] + w) + ") * N + i0 + e] = " +
+                          word(j, w, "[e]") + ";");
     E.line(0, "}");
     // ---- merge of the slabs in a fixed order: 32 columns x 8 lanes a block; lane l folds slabs l, l + 8, ... in
     // order, then the eight lane results are folded in lane order
@@ -778,27 +804,36 @@ std::string generate_cols(const tb200_group_desc &d, int V) {
     E.line(1, "__shared__ float sm[NF][8][33];");
     E.line(1, "const int c = threadIdx.x & 31, l = threadIdx.x >> 5, i0 = blockIdx.x * 32 + c;");
     for (int j = 0; j < d.n_folds; j++) {
-        E.line(1, "float f" + num(j) + " = " + fold_identity(d.folds[j].kind) + ";");
+        const int kind = d.folds[j].kind, words = state_words(kind);
+        for (int w = 0; w < words; w++) E.line(1, "float " + word(j, w, "") + " = " + identity(j, w) + ";");
         E.line(1, "if (i0 < N) {");
         E.line(2, "#pragma unroll 4");
         E.line(2, "for (int s = l; s < p.slabs; s += 8) {");
-        E.line(3, "const float o = p.partial[((i64)s * NF + " + num(j) + ") * N + i0];");
-        emit_merge(E, 3, d.folds[j].kind, "f" + num(j), "", "", "o", "", "");
+        for (int w = 0; w < words; w++)
+            E.line(3, "const float o" + num(w) + " = p.partial[((i64)s * NF + " + num(word0[j] + w) + ") * N + i0];");
+        emit_merge(E, 3, kind, word(j, 0, ""), word(j, 1, ""), word(j, 2, ""), "o0", "o1", "o2");
         E.line(2, "}");
         E.line(1, "}");
-        E.line(1, "sm[" + num(j) + "][l][c] = f" + num(j) + ";");
+        for (int w = 0; w < words; w++) E.line(1, "sm[" + num(word0[j] + w) + "][l][c] = " + word(j, w, "") + ";");
     }
     E.line(1, "__syncthreads();");
     E.line(1, "if (l != 0 || i0 >= N) return;");
     for (int j = 0; j < d.n_folds; j++) {
-        E.line(1, "f" + num(j) + " = sm[" + num(j) + "][0][c];");
+        const int kind = d.folds[j].kind, words = state_words(kind);
+        for (int w = 0; w < words; w++) E.line(1, word(j, w, "") + " = sm[" + num(word0[j] + w) + "][0][c];");
         E.line(1, "for (int k = 1; k < 8; k++) {");
-        E.line(2, "const float o = sm[" + num(j) + "][k][c];");
-        emit_merge(E, 2, d.folds[j].kind, "f" + num(j), "", "", "o", "", "");
+        for (int w = 0; w < words; w++) E.line(2, "const float o" + num(w) + " = sm[" + num(word0[j] + w) + "][k][c];");
+        emit_merge(E, 2, kind, word(j, 0, ""), word(j, 1, ""), word(j, 2, ""), "o0", "o1", "o2");
         E.line(1, "}");
     }
     for (int o = 0; o < d.n_outputs; o++) {
-        const std::string v = "f" + num(d.outputs[o].index);
+        // what a fold observes: the log-sum-exp from (maximum, rebased sum); the mean, or as the second value the
+        // variance, from (count, mean, centred sum of squares); any other fold its one word
+        const int j = d.outputs[o].index, kind = d.folds[j].kind;
+        std::string v = word(j, 0, "");
+        if (kind == TB200_FOLD_LOGSUMEXP) v = "(" + word(j, 1, "") + " > 0.0f ? " + word(j, 0, "") + " + logf(" + word(j, 1, "") + ") : " + word(j, 0, "") + ")";
+        if (kind == TB200_FOLD_MEANVAR)
+            v = d.outputs[o].from == 2 ? "(" + word(j, 0, "") + " > 0.0f ? " + word(j, 2, "") + " / " + word(j, 0, "") + " : 0.0f)" : word(j, 1, "");
         if (d.outputs[o].dtype == TB200_BF16) E.line(1, "((u16 *)p.out[" + num(o) + "])[i0] = (u16)f2bf(" + v + ");");
         else E.line(1, "((float *)p.out[" + num(o) + "])[i0] = " + v + ";");
     }
@@ -968,7 +1003,7 @@ extern "C" size_t tb200_colreduce_workspace_bytes(const tb200_group_desc *d) {
     // the widest form has the fewest column blocks, hence the most slabs
     tb200_group_desc any_rows = *d;
     any_rows.rows = kColSlabsMax;
-    return static_cast<size_t>(col_slabs(&any_rows, 8)) * d->n_folds * static_cast<size_t>(d->n) * sizeof(float);
+    return static_cast<size_t>(col_slabs(&any_rows, 8)) * total_state_words(*d) * static_cast<size_t>(d->n) * sizeof(float);
 }
 
 extern "C" int tb200_colreduce_compile(const tb200_group_desc *d) {

@@ -249,3 +249,15 @@ def column_extrema(n, rows, eltype="Float32"):
     g.output_stat(g.fold("min", x))
     g.output_stat(g.fold("sum", g.abs(x)))
     return g
+
+
+def column_statistics(n, rows, eltype="Float32"):
+    """Per column over the rows: the log-sum-exp, the mean and the variance -- the relative folds (online
+    log-sum-exp, Welford / Chan) running over the other axis, `logsumexp(x; dims = 2)` and the moments of a batch."""
+    g = Group(n, rows, across=True)
+    x = g.load(g.input("full", eltype))
+    g.output_stat(g.fold("logsumexp", x))
+    mv = g.fold("meanvar", x)
+    g.output_stat(mv)
+    g.output_stat(mv, second=True)
+    return g

@@ -227,6 +227,29 @@ def test_column_groups(pkg, cuda, oracle, rows, n, eltype):
     agree_columns(oracle, got[2:], floor[2:], wide[2:], float(rows))
 
 
+@pytest.mark.parametrize("rows,n", [(700, 256), (40, 9000), (3000, 100), (1, 5), (4099, 33)])
+@pytest.mark.parametrize("eltype", ["Float32", "BFloat16"])
+def test_relative_folds_over_the_rows(pkg, cuda, oracle, rows, n, eltype):
+    """The log-sum-exp and the mean / variance states carried over the other axis (partial states per row slab,
+    merged in a fixed order: ext/cuTileExt/emit.jl:729-753, build.jl:654-696) against the oracle's sequential fold
+    over the rows and the Float64 closed forms, on the transposes of the reference's fold shapes."""
+    G = pkg.groups
+    x = (3.0 * oracle.normal((rows, n), 31 + n)).astype(np.float32)
+    xin = oracle.to_bf16(x) if eltype == "BFloat16" else x
+    xf = (oracle.from_bf16(xin) if eltype == "BFloat16" else x).astype(np.float64)
+    got, floor, wide = run_columns(pkg, cuda, oracle, G.column_statistics(n, rows, eltype), [xin])
+    m = xf.max(axis=0)
+    lse = m + np.log(np.exp(xf - m).sum(axis=0))
+    for g, want in zip(got, (lse, xf.mean(axis=0), xf.var(axis=0))):
+        assert np.isfinite(g).all()
+        assert np.abs(g - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+    for g, w in zip(got, wide):
+        assert np.abs(g.astype(np.float64) - w).max() <= 2e-5 * max(1.0, np.abs(w).max())
+    # twice the same bits: slabs merge in a fixed order
+    again, _, _ = run_columns(pkg, cuda, oracle, G.column_statistics(n, rows, eltype), [xin])
+    assert all(np.array_equal(a, b) for a, b in zip(got, again))
+
+
 def test_column_groups_agree_with_the_named_kernels(pkg, cuda, oracle):
     """dgamma and dbeta of the generated column group against the named LayerNorm backward on the same operands,
     and a group over no rows gives every fold's identity."""
