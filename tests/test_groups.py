@@ -142,8 +142,16 @@ def test_column_groups_compile_and_refusals(pkg, oracle):
     with pytest.raises(L.TB200Error) as e:
         L.colreduce_compile(g.desc())
     assert e.value.status == -7
-    g = G.Group(300, 77)
-    g.output_stat(g.fold("logsumexp", g.load(g.input("full"))))
+    # the relative folds run over the rows too (two- and three-word states), and the oracle folds them in sequence
+    stats = G.column_statistics(300, 77)
+    L.colreduce_compile(stats.desc())
+    assert L.colreduce_workspace_bytes(stats.desc()) >= 5 * 300 * 4
+    lse, mean, var = oracle.group_eval_cols(stats.desc(), [x])
+    xf = x.astype(np.float64)
+    assert np.allclose(lse, np.log(np.exp(xf).sum(axis=0)), atol=1e-4) and np.allclose(mean, xf.mean(axis=0), atol=1e-5)
+    assert np.allclose(var, xf.var(axis=0), atol=1e-4)
+    g = G.Group(300, 77, across=True)
+    g.output_stat(g.fold("weighted", g.load(g.input("full"))))
     with pytest.raises(L.TB200Error) as e:
         L.colreduce_compile(g.desc())
     assert e.value.status == -7
