@@ -736,14 +736,39 @@ def run_profile_case(args):
         C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         bias = torch.zeros(N, device="cuda", dtype=torch.bfloat16)
         Z = torch.empty_like(C)
+        # the forward product as a prepared launch (tiles drawn from a counter), three times
+        plan = L.GemmPlan(L.gemm_desc(M, N, K, a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR, epilogue=L.EPI_BIAS_GELU),
+                          A.data_ptr(), B.data_ptr(), C.data_ptr(), bias=bias.data_ptr(), aux_out=Z.data_ptr())
         for _ in range(3):
-            L.gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR,
-                   epilogue=L.EPI_BIAS_GELU, bias=bias.data_ptr(), aux_out=Z.data_ptr(), stream=stream)
+            plan.launch(stream)
         # the backward's shapes: dX (both K-major) and dW (both MN-major)
         L.gemm(C.data_ptr(), B.data_ptr(), A.data_ptr(), M, K, N, a_layout=L.K_MAJOR, b_layout=L.K_MAJOR,
                epilogue=L.EPI_MUL_GELU_GRAD, aux=Z.data_ptr(), stream=stream)
         L.gemm(A.data_ptr(), C.data_ptr(), B.data_ptr(), K, N, M, a_layout=L.MN_MAJOR, b_layout=L.MN_MAJOR,
                stream=stream)
+        # a long sum over a small output, split among blocks and merged (the reference's split-K shape, scaled up),
+        # and a batch of the delta rule's per-chunk products
+        sd = L.gemm_desc(64, 48, 30000, a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR, out_dtype=L.F32)
+        need = L.gemm_workspace_bytes(sd)
+        sws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+        As, Bs = torch.randn(64, 30000, device="cuda").bfloat16(), torch.randn(30000, 48, device="cuda").bfloat16()
+        Cs = torch.empty(64, 48, device="cuda")
+        L.gemm(As.data_ptr(), Bs.data_ptr(), Cs.data_ptr(), 64, 48, 30000, out_dtype=L.F32, workspace=sws.data_ptr(),
+               workspace_bytes=need, stream=stream)
+        Ab, Bb = torch.randn(2048, 64, 128, device="cuda").bfloat16(), torch.randn(2048, 64, 128, device="cuda").bfloat16()
+        Cb = torch.empty(2048, 64, 64, device="cuda", dtype=torch.bfloat16)
+        L.gemm(Ab.data_ptr(), Bb.data_ptr(), Cb.data_ptr(), 64, 64, 128, a_layout=L.K_MAJOR, b_layout=L.K_MAJOR, batch=2048,
+               stream=stream)
+        plan.close()
+    elif case == "scan":
+        n, rows = 4096, 16384
+        x = torch.randn(rows, n, device="cuda")
+        y = torch.empty_like(x)
+        a = 0.9 + 0.1 * torch.rand(rows, n, device="cuda")
+        for _ in range(2):
+            L.scan(x.data_ptr(), y.data_ptr(), n, rows, L.SCAN_SUM, stream=stream)
+            L.scan(x.data_ptr(), y.data_ptr(), n, rows, L.SCAN_SUM, across=True, stream=stream)
+            L.scan(a.data_ptr(), y.data_ptr(), n, rows, L.SCAN_AFFINE, x2=x.data_ptr(), stream=stream)
     elif case == "attention":
         Bq, Hq, Sq, Dq = 1, 32, 4096, 128
         q, k, v, g = (torch.randn(Bq, Sq, Hq, Dq, device="cuda").bfloat16() for _ in range(4))
@@ -754,8 +779,11 @@ def run_profile_case(args):
         ws = torch.empty(need, dtype=torch.uint8, device="cuda")
         for _ in range(2):
             L.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), stream)
-            L.attention_bwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), g.data_ptr(),
-                            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), need, stream)
+            for form in (0, 1):   # the one-kernel form (dq by atomic adds), then the deterministic two-kernel form
+                desc.deterministic = form
+                L.attention_bwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), g.data_ptr(),
+                                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), need, stream)
+            desc.deterministic = 0
     elif case == "deltanet":
         Hn, T = 16, 8192
         qd = torch.nn.functional.normalize(torch.randn(Hn, T, 128, device="cuda"), dim=-1).bfloat16()
@@ -982,7 +1010,7 @@ def main():
     ap.add_argument("--no-also", action="store_true", help="skip the side measurements (MLP step, GEMM)")
     ap.add_argument("--also", default="all", choices=["all", "mlp"],
                     help="which side measurements to take: all of them, or the MLP training step alone")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "attention", "deltanet", "groups", "columns"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "attention", "deltanet", "groups", "columns", "scan"],
                     help="run one small case of a kernel family only (for ncu captures)")
     args = ap.parse_args()
     if args.profile_case:

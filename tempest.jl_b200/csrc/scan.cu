@@ -11,7 +11,9 @@
 // and one exchange through shared memory, and the carry of the tiles before is combined in front: every element
 // is read once and written once.  States combine strictly left to right (the affine recurrence does not commute).
 // Across the rows (the scanned axis is the strided one): one thread per column walks the rows in order with its
-// state in a register; neighbouring threads read neighbouring columns, so every access is coalesced.
+// state in a register, eight rows' loads in flight at a time; neighbouring threads read neighbouring columns, so
+// every access is coalesced.  Parallelism is the number of columns: a scan across many rows of few columns keeps
+// few SMs busy (measured: 16384 rows of 4096 Float32 columns, 16 blocks).
 // Float32 or BFloat16 elements; states and arithmetic in Float32, each result rounded once.
 #include "common.cuh"
 
@@ -175,10 +177,26 @@ __global__ void __launch_bounds__(kScanThreads) scan_columns_kernel(const ScanAr
         const T *x2 = a.x2 ? static_cast<const T *>(a.x2) + m * a.stride_x2 + col : nullptr;
         T *y = static_cast<T *>(a.y) + m * a.stride_y + col;
         S run = F::identity();
-        for (long long p = 0; p < a.rows; p++) {
-            const long long r = a.reverse ? a.rows - 1 - p : p;
-            run = F::combine(run, F::lift(load1(x + r * a.ld_x), x2 ? load1(x2 + r * a.ld_x2) : 0.0f));
-            store1(y + r * a.ld_y, F::observe(run));
+        // eight rows' loads are issued before the first is used: the chain through `run` is arithmetic only, so
+        // the walk waits for memory once per eight rows instead of once per row
+        constexpr int B = 8;
+        for (long long p0 = 0; p0 < a.rows; p0 += B) {
+            float v[B], w[B];
+#pragma unroll
+            for (int j = 0; j < B; j++) {
+                const long long p = p0 + j < a.rows ? p0 + j : a.rows - 1;
+                const long long r = a.reverse ? a.rows - 1 - p : p;
+                v[j] = load1(x + r * a.ld_x);
+                w[j] = x2 ? load1(x2 + r * a.ld_x2) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < B; j++) {
+                if (p0 + j < a.rows) {
+                    const long long r = a.reverse ? a.rows - 1 - (p0 + j) : p0 + j;
+                    run = F::combine(run, F::lift(v[j], w[j]));
+                    store1(y + r * a.ld_y, F::observe(run));
+                }
+            }
         }
     }
 }
