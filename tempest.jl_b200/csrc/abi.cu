@@ -68,7 +68,7 @@ extern "C" int tb200_sm_count(void) {
     return st == TB200_OK ? d.sms : st;
 }
 
-// The three tensor-core kernel families each keep one error word; a caller that launches several kinds
+// The tensor-core kernel families and the row kernels fed through shared memory each keep one error word; a caller that launches several kinds
 // polls them all at a synchronisation point through this one call.
 extern "C" int tb200_device_errors(void) {
     const int product = tb200_device_error();
@@ -77,5 +77,7 @@ extern "C" int tb200_device_errors(void) {
     if (forward < 0) return forward;
     const int backward = tb200_attention_bwd_device_error();
     if (backward < 0) return backward;
-    return (product & 0xff) | ((forward & 0xff) << 8) | ((backward & 0xff) << 16);
+    const int rows = tb200_rows_device_error();
+    if (rows < 0) return rows;
+    return (product & 0xff) | ((forward & 0xff) << 8) | ((backward & 0xff) << 16) | ((rows & 0x7f) << 24);
 }

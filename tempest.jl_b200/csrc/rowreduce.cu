@@ -18,12 +18,15 @@
 // Numerics: Float32 arithmetic for either element type, sums as fixed-order
 // trees (deterministic), exp as ex2.approx of a scaled argument, outputs
 // rounded once.
+#include <cstdio>
+#include <cstdlib>
 #include <initializer_list>
 #include <map>
 #include <mutex>
 #include <tuple>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace tb200 {
 namespace {
@@ -468,6 +471,215 @@ __global__ void __launch_bounds__(256, 4) layernorm_bwd_compact(RowArgs a) {
     }
 }
 
+// The LayerNorm backward for rows of 1024, 2048 or 4096 elements with saved statistics, fed through shared memory:
+// one thread issues bulk copies (cp.async.bulk, completion counted on an mbarrier) of whole rows of x and dy into a
+// ring of stages, several rows ahead of the arithmetic, so the bytes in flight per SM are set by the ring's depth and
+// not by how many registers the resident threads can spare for loads.  512 threads, eight elements each; a thread owns
+// the same eight columns of every row, so gamma is widened once per launch and the dgamma / dbeta sums are sixteen
+// registers that stay in the thread until the end; x-hat and dy*gamma stay widened across the row's two sums.  A stage
+// is free once every thread has passed the barrier inside the row sums' exchange, and is refilled there.
+// Every wait on a stage is bounded (about two seconds): a thread that gives up records it in g_rows_error and runs on
+// without waiting again, so the launch ends and the host can read the status.
+__device__ int g_rows_error = 0;
+
+template <typename T> struct Eight;
+template <> struct Eight<__nv_bfloat16> {
+    static constexpr int NV = 1;
+    static __device__ __forceinline__ int col(int k, int t, int tpr) { return t * 8; }
+    static __device__ __forceinline__ void load(const __nv_bfloat16 *row, int t, int tpr, float2 (&v)[4]) {
+        const uint4 q = *reinterpret_cast<const uint4 *>(row + t * 8);
+        unpack_bf16x2(q.x, v[0].x, v[0].y); unpack_bf16x2(q.y, v[1].x, v[1].y);
+        unpack_bf16x2(q.z, v[2].x, v[2].y); unpack_bf16x2(q.w, v[3].x, v[3].y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16 *row, int t, int tpr, const float2 (&v)[4]) {
+        __stcs(reinterpret_cast<uint4 *>(row + t * 8),
+               make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y), pack_bf16x2(v[2].x, v[2].y),
+                          pack_bf16x2(v[3].x, v[3].y)));
+    }
+};
+template <> struct Eight<float> {
+    static constexpr int NV = 2;
+    static __device__ __forceinline__ int col(int k, int t, int tpr) { return (k * tpr + t) * 4; }
+    static __device__ __forceinline__ void load(const float *row, int t, int tpr, float2 (&v)[4]) {
+        const float4 p = *reinterpret_cast<const float4 *>(row + t * 4);
+        const float4 q = *reinterpret_cast<const float4 *>(row + (tpr + t) * 4);
+        v[0] = make_float2(p.x, p.y); v[1] = make_float2(p.z, p.w);
+        v[2] = make_float2(q.x, q.y); v[3] = make_float2(q.z, q.w);
+    }
+    static __device__ __forceinline__ void store(float *row, int t, int tpr, const float2 (&v)[4]) {
+        __stcs(reinterpret_cast<float4 *>(row + t * 4), make_float4(v[0].x, v[0].y, v[1].x, v[1].y));
+        __stcs(reinterpret_cast<float4 *>(row + (tpr + t) * 4), make_float4(v[2].x, v[2].y, v[3].x, v[3].y));
+    }
+};
+// the eight Float32 partial sums of a thread, at the columns the thread owns
+template <typename T>
+__device__ __forceinline__ void store_sums(float *row, int t, int tpr, const float2 (&v)[4]) {
+    constexpr int half = Eight<T>::NV == 1 ? 4 : 0;   // BFloat16: eight neighbouring columns; Float32: two groups of four
+    *reinterpret_cast<float4 *>(row + Eight<T>::col(0, t, tpr)) = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
+    *reinterpret_cast<float4 *>(row + Eight<T>::col(Eight<T>::NV - 1, t, tpr) + half) = make_float4(v[2].x, v[2].y, v[3].x, v[3].y);
+}
+
+__device__ __forceinline__ bool stage_wait(uint64_t *bar, uint32_t parity) {
+    if (sm100::mbar_wait(bar, parity, 2048)) return true;
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    while (true) {
+        if (sm100::mbar_wait(bar, parity, 1024)) return true;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 2000000000ull) return false;
+    }
+}
+
+constexpr int kStagedThreads = 512;
+constexpr int kStagedRowsBf16 = 2;   // BFloat16 rows a block takes per turn
+
+// R rows a turn: the chain  row sums -> shuffles -> exchange -> shuffles  is as long for R rows' sums as for one, and
+// with two blocks of 512 threads per SM that chain, not HBM, set the pace of BFloat16 rows (measured: 0.339 ms with it,
+// 0.256 ms with the sums left out, 4096 x 65536).  With R > 1 nothing of a row but its sums is kept across the
+// exchange: the second pass reads the row from its stage again, so a stage is handed back one turn later.
+template <typename T, int R>
+__global__ void __launch_bounds__(kStagedThreads, 2) layernorm_bwd_staged(RowArgs a) {
+    using E = Eight<T>;
+    constexpr bool REREAD = R > 1;
+    extern __shared__ __align__(128) unsigned char staged_smem[];
+    __shared__ float red[2][kStagedThreads / 32][2 * R];
+    uint64_t *full = reinterpret_cast<uint64_t *>(staged_smem);      // one barrier per stage, in the first 128 bytes
+    T *ring = reinterpret_cast<T *>(staged_smem + 128);              // [stage][row of the turn][x | dy][row slot][n]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tpr = a.tpr, slot = tid / tpr, t = tid - slot * tpr, wpr = tpr >> 5;
+    const int stages = a.splits;
+    const T *x = static_cast<const T *>(a.in0);
+    const T *dy = static_cast<const T *>(a.in1);
+    T *dx = static_cast<T *>(a.out0);
+    const float *mean_in = static_cast<const float *>(a.cstat0), *rstd_in = static_cast<const float *>(a.cstat1);
+    const long long turn_rows = static_cast<long long>(R) * a.rpc;
+    const long long turns = a.rows / turn_rows, step = gridDim.x;
+    const size_t row_elems = static_cast<size_t>(2) * a.rpc * a.n;   // one row slot group: x rows, then dy rows
+    const size_t stage_elems = R * row_elems;
+    const uint32_t row_bytes = static_cast<uint32_t>(a.n * sizeof(T));
+
+    auto fill = [&](int stage, long long turn) {   // one thread: the turn's rows of x and dy
+        sm100::mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(2 * turn_rows) * row_bytes);
+        for (int j = 0; j < R; j++) {
+            T *dst = ring + stage * stage_elems + j * row_elems;
+            for (int i = 0; i < a.rpc; i++) {
+                const long long r = turn * turn_rows + static_cast<long long>(j) * a.rpc + i;
+                sm100::bulk_load(dst + static_cast<size_t>(i) * a.n, x + r * a.ld, row_bytes, &full[stage]);
+                sm100::bulk_load(dst + static_cast<size_t>(a.rpc + i) * a.n, dy + r * a.ld, row_bytes, &full[stage]);
+            }
+        }
+    };
+    if (tid == 0) {
+        for (int i = 0; i < stages; i++) sm100::mbar_init(&full[i], 1);
+        sm100::fence_barrier_init();
+    }
+    __syncthreads();
+    if (tid == 0)
+        for (int i = 0; i < stages; i++)
+            if (blockIdx.x + i * step < turns) fill(i, blockIdx.x + i * step);
+
+    float2 gm[4], dg[4], db[4];
+    E::load(static_cast<const T *>(a.gamma), t, tpr, gm);
+#pragma unroll
+    for (int w = 0; w < 4; w++) dg[w] = db[w] = make_float2(0.0f, 0.0f);
+    const float inv_n = 1.0f / static_cast<float>(a.n);
+    // the rows' saved statistics, fetched a turn ahead
+    float mean_next[R], rstd_next[R];
+    auto fetch_stats = [&](long long turn) {
+#pragma unroll
+        for (int j = 0; j < R; j++) {
+            const long long r = turn * turn_rows + static_cast<long long>(j) * a.rpc + slot;
+            mean_next[j] = turn < turns ? __ldg(mean_in + r) : 0.0f;
+            rstd_next[j] = turn < turns ? __ldg(rstd_in + r) : 0.0f;
+        }
+    };
+    fetch_stats(blockIdx.x);
+    bool failed = false;
+    int stage = 0, phase = 0, last_stage = -1;
+    uint32_t parity = 0;
+    for (long long g = blockIdx.x; g < turns; g += step) {
+        float mean[R], rstd[R];
+#pragma unroll
+        for (int j = 0; j < R; j++) { mean[j] = mean_next[j]; rstd[j] = rstd_next[j]; }
+        fetch_stats(g + step);
+        if (!failed && !stage_wait(&full[stage], parity)) {
+            failed = true;
+            atomicCAS(&g_rows_error, 0, 1);
+        }
+        const T *sx = ring + stage * stage_elems + static_cast<size_t>(slot) * a.n;
+        float2 xh[R][4], gh[R][4];
+        float sums[2 * R];
+#pragma unroll
+        for (int j = 0; j < R; j++) {
+            E::load(sx + j * row_elems, t, tpr, xh[j]);
+            E::load(sx + j * row_elems + static_cast<size_t>(a.rpc) * a.n, t, tpr, gh[j]);
+            const float2 rs2 = make_float2(rstd[j], rstd[j]), off2 = make_float2(-mean[j] * rstd[j], -mean[j] * rstd[j]);
+            float2 sa = make_float2(0.0f, 0.0f), sb = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float2 d2 = gh[j][w];
+                xh[j][w] = __ffma2_rn(xh[j][w], rs2, off2);
+                gh[j][w] = __fmul2_rn(d2, gm[w]);
+                sa = __fadd2_rn(sa, gh[j][w]);
+                sb = __ffma2_rn(gh[j][w], xh[j][w], sb);
+                dg[w] = __ffma2_rn(d2, xh[j][w], dg[w]);
+                db[w] = __fadd2_rn(db[w], d2);
+            }
+            sums[2 * j] = sa.x + sa.y;
+            sums[2 * j + 1] = sb.x + sb.y;
+        }
+        // the rows' sums over their threads: shuffles, one exchange through shared memory, shuffles again
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < 2 * R; i++) sums[i] += __shfl_xor_sync(0xffffffffu, sums[i], o);
+        if (lane == 0)
+#pragma unroll
+            for (int i = 0; i < 2 * R; i++) red[phase][warp][i] = sums[i];
+        __syncthreads();
+        // every thread is past its reads of a stage (this turn's when the rows stay in registers, the turn
+        // before's when the second pass reads them again): hand it back
+        if (tid == 0) {
+            const int back = REREAD ? last_stage : stage;
+            const long long ahead = g + (REREAD ? stages - 1 : stages) * step;
+            if (back >= 0 && ahead < turns) fill(back, ahead);
+        }
+        last_stage = stage;
+#pragma unroll
+        for (int i = 0; i < 2 * R; i++) sums[i] = red[phase][slot * wpr + (lane & (wpr - 1))][i];
+        for (int o = wpr >> 1; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < 2 * R; i++) sums[i] += __shfl_xor_sync(0xffffffffu, sums[i], o);
+        phase ^= 1;
+#pragma unroll
+        for (int j = 0; j < R; j++) {
+            const long long r = g * turn_rows + static_cast<long long>(j) * a.rpc + slot;
+            const float c1 = sums[2 * j] * inv_n, c2 = sums[2 * j + 1] * inv_n;
+            const float2 nc1 = make_float2(-c1, -c1), nc2 = make_float2(-c2, -c2), rs2 = make_float2(rstd[j], rstd[j]);
+            if constexpr (REREAD) {
+                const float2 off2 = make_float2(-mean[j] * rstd[j], -mean[j] * rstd[j]);
+                E::load(sx + j * row_elems, t, tpr, xh[j]);
+                E::load(sx + j * row_elems + static_cast<size_t>(a.rpc) * a.n, t, tpr, gh[j]);
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    xh[j][w] = __ffma2_rn(xh[j][w], rs2, off2);
+                    gh[j][w] = __fmul2_rn(gh[j][w], gm[w]);
+                }
+            }
+#pragma unroll
+            for (int w = 0; w < 4; w++)
+                xh[j][w] = __fmul2_rn(__ffma2_rn(xh[j][w], nc2, __fadd2_rn(gh[j][w], nc1)), rs2);
+            E::store(dx + r * a.ld, t, tpr, xh[j]);
+        }
+        if (++stage == stages) { stage = 0; parity ^= 1; }
+    }
+    if (a.part0) {
+        const long long p = static_cast<long long>(blockIdx.x) * a.rpc + slot;
+        store_sums<T>(a.part0 + p * a.n, t, tpr, dg);
+        store_sums<T>(a.part1 + p * a.n, t, tpr, db);
+    }
+}
+
 // ---------------------------------------- LayerNorm backward, rows beyond the resident schedule ----
 //
 // A row that does not fit one block's registers is streamed instead: one block of 512 threads walks the
@@ -842,6 +1054,7 @@ struct Schedule {
     int splits;
     long long blocks; // grid (resident: an upper bound before occupancy)
     bool exact;       // the rows fill every vector slot of every row slot of every block
+    bool staged;      // LayerNorm backward fed through a ring in shared memory (`splits` = its stages)
 };
 
 inline int round_vpt(int64_t v) { return v <= 1 ? 1 : v <= 2 ? 2 : v <= 4 ? 4 : 8; }
@@ -1009,12 +1222,62 @@ namespace {
 // The LayerNorm backward's kernel for a schedule: the compact BFloat16 form where it applies (128-bit accesses,
 // every slot filled, 256-thread blocks, statistics saved by the forward), else the general family.
 RowKernel ln_bwd_kernel(int dtype, const Schedule &s, bool saved_stats) {
+    if (s.staged) return dtype == TB200_F32 ? layernorm_bwd_staged<float, 1> : layernorm_bwd_staged<__nv_bfloat16, kStagedRowsBf16>;
     if (dtype == TB200_BF16 && s.vec && s.exact && saved_stats && s.threads == 256) {
         if (s.vpt == 1) return layernorm_bwd_compact<1>;
         if (s.vpt == 2) return layernorm_bwd_compact<2>;
     }
 
     return pick<LayernormBwdResident>(dtype, s);
+}
+
+// The schedule the LayerNorm backward runs: rows of 1024, 2048 or 4096 elements that allow 128-bit accesses, with
+// the statistics saved and whole groups of rows, take the form fed through shared memory (eight elements a thread,
+// 512 threads, `splits` = stages of the ring); everything else keeps the plan.
+constexpr size_t kStagedRingBytes = 96 * 1024;
+Schedule ln_bwd_schedule(const Schedule &s, int64_t n, int64_t rows, int dtype, bool saved_stats) {
+    if (!s.vec || s.split || !saved_stats || (n != 1024 && n != 2048 && n != 4096)) return s;
+    Schedule w = s;
+    w.staged = true;
+    w.threads = kStagedThreads;
+    w.tpr = static_cast<int>(n / 8);
+    w.rpc = kStagedThreads / w.tpr;
+    const int turn = (dtype == TB200_F32 ? 1 : kStagedRowsBf16) * w.rpc;   // rows a block takes per turn
+    if (rows % turn != 0) return s;
+    w.vpt = dtype == TB200_F32 ? 2 : 1;
+    w.exact = true;
+    w.blocks = rows / turn;
+    const size_t stage = static_cast<size_t>(2) * turn * n * dtype_size(dtype);
+    w.splits = static_cast<int>(kStagedRingBytes / stage);
+    if (w.splits > 8) w.splits = 8;
+    return w;
+}
+size_t staged_smem_bytes(const Schedule &s, int64_t n, int dtype) {
+    const int turn = (dtype == TB200_F32 ? 1 : kStagedRowsBf16) * s.rpc;
+    return 128 + static_cast<size_t>(s.splits) * 2 * turn * n * dtype_size(dtype);
+}
+// Grid of the staged form: two blocks per SM (its shared memory allows no more), never more than row groups.
+int staged_grid(RowKernel kernel, const Schedule &s, const DeviceInfo &dev, int64_t n, int dtype, long long *grid) {
+    static std::mutex lock;
+    static bool set[64][2] = {};
+    {
+        std::lock_guard<std::mutex> hold(lock);
+        bool &done = set[dev.device][dtype == TB200_F32 ? 0 : 1];
+        if (!done) {
+            TB200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(128 + kStagedRingBytes)));
+            done = true;
+        }
+    }
+    int per_sm = 0;
+    TB200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kStagedThreads, staged_smem_bytes(s, n, dtype)));
+    if (per_sm < 1) return TB200_ERR_UNSUPPORTED;
+    const long long g = static_cast<long long>(per_sm) * dev.sms;
+    *grid = g < s.blocks ? g : s.blocks;
+    return TB200_OK;
+}
+int ln_bwd_grid(RowKernel kernel, const Schedule &s, const DeviceInfo &dev, int64_t n, int dtype, long long *grid) {
+    return s.staged ? staged_grid(kernel, s, dev, n, dtype, grid) : resident_grid(kernel, s, dev, grid);
 }
 
 // Scratch layout of the streamed LayerNorm backward: mean and rstd of every row (used when the forward saved
@@ -1044,9 +1307,11 @@ int schedule_workspace(RowOp op, const Schedule &s, const DeviceInfo &dev, int64
         long long grid = 0, compact = 0;
         int st = resident_grid(ln_bwd_kernel(dtype, s, false), s, dev, &grid);
         if (st) return st;
-        if ((st = resident_grid(ln_bwd_kernel(dtype, s, true), s, dev, &compact))) return st;
-        if (compact > grid) grid = compact;
-        *bytes = static_cast<size_t>(grid) * s.rpc * static_cast<size_t>(n) * 2 * sizeof(float);
+        const Schedule saved = ln_bwd_schedule(s, n, rows, dtype, true);
+        if ((st = ln_bwd_grid(ln_bwd_kernel(dtype, saved, true), saved, dev, n, dtype, &compact))) return st;
+        long long parts = grid * s.rpc;
+        if (compact * saved.rpc > parts) parts = compact * saved.rpc;
+        *bytes = static_cast<size_t>(parts) * static_cast<size_t>(n) * 2 * sizeof(float);
     }
     return TB200_OK;
 }
@@ -1161,7 +1426,8 @@ extern "C" int tb200_layernorm_bwd(const void *x, const void *gamma, const void 
         return TB200_ERR_ALIGN;
     DeviceInfo dev;
     if ((st = current_device(&dev))) return st;
-    const Schedule s = plan_rows(OP_LN_BWD, n, rows, ld, dtype, all_aligned(16, {x, gamma, dy, dx}));
+    const Schedule s = ln_bwd_schedule(plan_rows(OP_LN_BWD, n, rows, ld, dtype, all_aligned(16, {x, gamma, dy, dx})), n,
+                                       rows, dtype, mean && rstd);
     RowArgs a{};
     a.in0 = x; a.in1 = dy; a.gamma = gamma; a.out0 = dx; a.cstat0 = mean; a.cstat1 = rstd; a.eps = eps;
     a.n = static_cast<int>(n); a.rows = rows; a.ld = ld; a.tpr = s.tpr; a.rpc = s.rpc; a.splits = 1;
@@ -1209,7 +1475,8 @@ extern "C" int tb200_layernorm_bwd(const void *x, const void *gamma, const void 
     }
     const RowKernel kernel = ln_bwd_kernel(dtype, s, mean && rstd);
     long long grid = 0;
-    if ((st = resident_grid(kernel, s, dev, &grid))) return st;
+    if ((st = ln_bwd_grid(kernel, s, dev, n, dtype, &grid))) return st;
+    if (s.staged) a.splits = s.splits;
     const bool sums = dgamma || dbeta;
     const size_t part_len = static_cast<size_t>(grid) * s.rpc * static_cast<size_t>(n);
     if (sums) {
@@ -1217,7 +1484,7 @@ extern "C" int tb200_layernorm_bwd(const void *x, const void *gamma, const void 
         a.part0 = static_cast<float *>(workspace);
         a.part1 = a.part0 + part_len;
     }
-    kernel<<<static_cast<unsigned>(grid), s.threads, 0, stream>>>(a);
+    kernel<<<static_cast<unsigned>(grid), s.threads, s.staged ? staged_smem_bytes(s, n, dtype) : 0, stream>>>(a);
     TB200_CUDA(cudaGetLastError());
     if (sums) {
         const int parts = static_cast<int>(grid * s.rpc);
@@ -1345,4 +1612,13 @@ extern "C" int tb200_layernorm_bwd_noalloc(const void *x, const void *gamma, con
         TB200_CUDA(cudaGetLastError());
     }
     return TB200_OK;
+}
+
+// As tb200_device_error, for the row kernels that wait on copies into shared memory: 0, or 1 when a wait gave up.
+extern "C" int tb200_rows_device_error(void) {
+    int code = 0, zero = 0;
+    TB200_CUDA(cudaDeviceSynchronize());
+    TB200_CUDA(cudaMemcpyFromSymbol(&code, tb200::g_rows_error, sizeof(int)));
+    if (code) TB200_CUDA(cudaMemcpyToSymbol(tb200::g_rows_error, &zero, sizeof(int)));
+    return code;
 }

@@ -114,6 +114,37 @@ def test_layernorm_bf16(run, oracle, rows, n):
     agree_bf16(db, db64, oracle)
 
 
+@pytest.mark.parametrize("eltype", ["Float32", "BFloat16"])
+@pytest.mark.parametrize("rows,n", [(64, 1024), (6, 2048), (1000, 4096), (7, 4096), (2, 4096), (1500, 2048)])
+def test_layernorm_pullback_with_saved_statistics(run, oracle, rows, n, eltype):
+    """Rows of 1024, 2048 and 4096 elements with the forward's mean and rstd handed in take the kernel that is fed
+    through a ring in shared memory (several rows a block, rows in whole turns; an odd row count falls back to the
+    resident kernels): the same results as the Float64 pullback, and nothing recorded by its bounded waits."""
+    x, g, w, _ = inputs(oracle, rows, n, 900 + n + rows)
+    if eltype == "BFloat16":
+        xb, gb, wb = (oracle.to_bf16(a) for a in (x, g, w))
+        xf, gf, wf = (oracle.from_bf16(a) for a in (xb, gb, wb))
+    else:
+        xb, gb, wb = xf, gf, wf = x, g, w
+    x64 = xf.astype(np.float64)
+    mean = x64.mean(axis=1).astype(np.float32)
+    rstd = (1.0 / np.sqrt(x64.var(axis=1) + 1e-5)).astype(np.float32)
+    dx, dw, db = run.layernorm_pullback(xb, wb, gb, mean, rstd)
+    dx64, dw64, db64 = oracle.layernorm_bwd_f64(xf, wf, gf)
+    if eltype == "BFloat16":
+        agree_bf16(dx, dx64, oracle)
+        agree_bf16(dw, dw64, oracle)
+        agree_bf16(db, db64, oracle)
+    else:
+        agree(dx, dx64, 4 * RTOL_F32)
+        agree(dw, dw64, 4 * RTOL_F32)
+        agree(db, db64, RTOL_F32)
+    again = run.layernorm_pullback(xb, wb, gb, mean, rstd)
+    for a, b in zip((dx, dw, db), again):
+        assert np.array_equal(a, b)
+    assert run.pkg.lib.rows_device_error() == 0
+
+
 def test_leading_dimension_and_unaligned_views(run, oracle, cuda):
     """Rows with a leading dimension larger than n, and views that start off a
     16-byte boundary (a value at an offset inside a shared slot)."""
