@@ -7,9 +7,10 @@
 // the kept axes sweeps the scanned axis a tile at a step, carrying each lane's state).
 //
 // Along a row (the scanned axis is contiguous): one block per row sweeps it in tiles of 256 threads x 8
-// elements.  A thread scans its own eight elements in registers, the threads' totals are scanned by warp shuffles
-// and one exchange through shared memory, and the carry of the tiles before is combined in front: every element
-// is read once and written once.  States combine strictly left to right (the affine recurrence does not commute).
+// elements.  A thread reads its own eight elements with 128-bit accesses (one at a time when addresses or lengths
+// do not allow it) and scans them in registers, the threads' totals are scanned by warp shuffles and one exchange
+// through shared memory with a single barrier per tile, and the carry of the tiles before is combined in front:
+// every element is read once and written once.  States combine strictly left to right (the affine recurrence does not commute).
 // Across the rows (the scanned axis is the strided one): one thread per column walks the rows in order with its
 // state in a register, eight rows' loads in flight at a time; neighbouring threads read neighbouring columns, so
 // every access is coalesced.  Parallelism is the number of columns: a scan across many rows of few columns keeps
@@ -104,32 +105,64 @@ struct ScanArgs {
     long long ld_x, ld_x2, ld_y;            // row pitches, elements
     long long stride_x, stride_x2, stride_y;   // between the matrices of the batch
     int reverse;
+    int vec;   // along rows: every row is a whole number of 16-byte aligned groups of eight elements
 };
 
 // ---- along each row
+// eight neighbouring elements of a row as one or two 128-bit accesses (`p` 16-byte aligned)
+__device__ __forceinline__ void load8(const float *p, float (&v)[8]) {
+    const float4 lo = __ldcs(reinterpret_cast<const float4 *>(p)), hi = __ldcs(reinterpret_cast<const float4 *>(p) + 1);
+    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8]) {
+    const uint4 q = __ldcs(reinterpret_cast<const uint4 *>(p));
+    unpack_bf16x2(q.x, v[0], v[1]); unpack_bf16x2(q.y, v[2], v[3]);
+    unpack_bf16x2(q.z, v[4], v[5]); unpack_bf16x2(q.w, v[6], v[7]);
+}
+__device__ __forceinline__ void store8(float *p, const float (&v)[8]) {
+    __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
+    __stcs(reinterpret_cast<float4 *>(p) + 1, make_float4(v[4], v[5], v[6], v[7]));
+}
+__device__ __forceinline__ void store8(__nv_bfloat16 *p, const float (&v)[8]) {
+    __stcs(reinterpret_cast<uint4 *>(p), make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                    pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
+}
+
 template <int OP, typename T>
 __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanArgs a) {
     using F = Fold<OP>;
     using S = typename F::S;
-    __shared__ S warp_total[kScanThreads / 32];
-    __shared__ S tile_total;
+    __shared__ S warp_total[2][kScanThreads / 32];   // two buffers, tiles alternate: one barrier per tile
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int turn = 0;
     for (long long item = blockIdx.x; item < a.rows * a.batch; item += gridDim.x) {
         const long long m = item / a.rows, row = item - m * a.rows;
         const T *x = static_cast<const T *>(a.x) + m * a.stride_x + row * a.ld_x;
         const T *x2 = a.x2 ? static_cast<const T *>(a.x2) + m * a.stride_x2 + row * a.ld_x2 : nullptr;
         T *y = static_cast<T *>(a.y) + m * a.stride_y + row * a.ld_y;
         S carry = F::identity();
-        for (long long base = 0; base < a.n; base += kScanThreads * kScanPer) {
+        for (long long base = 0; base < a.n; base += kScanThreads * kScanPer, turn ^= 1) {
             // this thread's eight consecutive scan positions; position p is element p, or n - 1 - p when reversed
             const long long p0 = base + threadIdx.x * kScanPer;
+            // with 128-bit accesses (every row a whole number of aligned groups of eight) a thread's eight
+            // positions are all inside the row or all outside; reversed, they are the mirrored group read backwards
+            const bool whole = a.vec && p0 < a.n;
+            const long long i0 = a.reverse ? a.n - kScanPer - p0 : p0;
+            float v[kScanPer], v2[kScanPer];
+            if (whole) {
+                load8(x + i0, v);
+                if (x2) load8(x2 + i0, v2);
+            }
             S local[kScanPer];
             S run = F::identity();
 #pragma unroll
             for (int e = 0; e < kScanPer; e++) {
                 const long long p = p0 + e;
                 S s = F::identity();
-                if (p < a.n) {
+                if (whole) {
+                    const int at = a.reverse ? kScanPer - 1 - e : e;
+                    s = F::lift(v[at], x2 ? v2[at] : 0.0f);
+                } else if (!a.vec && p < a.n) {
                     const long long i = a.reverse ? a.n - 1 - p : p;
                     s = F::lift(load1(x + i), x2 ? load1(x2 + i) : 0.0f);
                 }
@@ -143,24 +176,33 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanArgs 
                 const S left = shuffle_up(incl, d);
                 if (lane >= d) incl = F::combine(left, incl);
             }
-            if (lane == 31) warp_total[warp] = incl;
+            if (lane == 31) warp_total[turn][warp] = incl;
             __syncthreads();
-            S before = carry;                       // everything ahead of this thread: earlier tiles, warps, lanes
-            for (int w = 0; w < warp; w++) before = F::combine(before, warp_total[w]);
-            S lane_excl = shuffle_up(incl, 1);
-            if (lane > 0) before = F::combine(before, lane_excl);
-            if (threadIdx.x == kScanThreads - 1) tile_total = F::combine(before, run);
+            // everything ahead of this thread: earlier tiles, warps, lanes; and the carry for the next tile
+            S before = carry, running = carry;
 #pragma unroll
-            for (int e = 0; e < kScanPer; e++) {
-                const long long p = p0 + e;
-                if (p < a.n) {
-                    const long long i = a.reverse ? a.n - 1 - p : p;
-                    store1(y + i, F::observe(F::combine(before, local[e])));
+            for (int w = 0; w < kScanThreads / 32; w++) {
+                if (w == warp) before = running;
+                running = F::combine(running, warp_total[turn][w]);
+            }
+            carry = running;
+            const S lane_excl = shuffle_up(incl, 1);
+            if (lane > 0) before = F::combine(before, lane_excl);
+            if (whole) {
+#pragma unroll
+                for (int e = 0; e < kScanPer; e++)
+                    v[a.reverse ? kScanPer - 1 - e : e] = F::observe(F::combine(before, local[e]));
+                store8(y + i0, v);
+            } else if (!a.vec) {
+#pragma unroll
+                for (int e = 0; e < kScanPer; e++) {
+                    const long long p = p0 + e;
+                    if (p < a.n) {
+                        const long long i = a.reverse ? a.n - 1 - p : p;
+                        store1(y + i, F::observe(F::combine(before, local[e])));
+                    }
                 }
             }
-            __syncthreads();
-            carry = tile_total;
-            __syncthreads();   // tile_total and warp_total are rewritten by the next tile
         }
     }
 }
@@ -208,7 +250,9 @@ int launch_scan(const ScanArgs &a, bool across, const DeviceInfo &dev, cudaStrea
         scan_columns_kernel<OP, T><<<grid, kScanThreads, 0, stream>>>(a);
     } else {
         const long long items = a.rows * a.batch;
-        const long long most = static_cast<long long>(dev.sms) * 8;
+        int per_sm = 0;   // persistent blocks: as many as are resident at once, so that no block starts late
+        TB200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, scan_rows_kernel<OP, T>, kScanThreads, 0));
+        const long long most = static_cast<long long>(dev.sms) * (per_sm > 0 ? per_sm : 1);
         scan_rows_kernel<OP, T><<<static_cast<unsigned>(items < most ? items : most), kScanThreads, 0, stream>>>(a);
     }
     TB200_CUDA(cudaGetLastError());
@@ -256,6 +300,12 @@ extern "C" int tb200_scan(const tb200_scan_desc *d, const void *x, const void *x
     a.ld_x = d->ld_x; a.ld_x2 = d->ld_x2; a.ld_y = d->ld_y;
     a.stride_x = d->stride_x; a.stride_x2 = d->stride_x2; a.stride_y = d->stride_y;
     a.reverse = d->reverse != 0;
+    {
+        const long long per = 16 / static_cast<long long>(es);   // elements per 128-bit access
+        const bool pitches = a.ld_x % per == 0 && a.ld_y % per == 0 && (!pairs || a.ld_x2 % per == 0) &&
+                             (batch == 1 || (a.stride_x % per == 0 && a.stride_y % per == 0 && (!pairs || a.stride_x2 % per == 0)));
+        a.vec = !d->across && a.n % 8 == 0 && pitches && aligned_to(x, 16) && aligned_to(y, 16) && (!pairs || aligned_to(x2, 16));
+    }
     if (d->dtype == TB200_F32) return launch_by_op<float>(d->op, a, d->across != 0, dev, stream);
     return launch_by_op<__nv_bfloat16>(d->op, a, d->across != 0, dev, stream);
 }
