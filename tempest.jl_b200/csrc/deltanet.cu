@@ -9,10 +9,13 @@
 // the result (T, dv, heads) = memory [head][dv][t] (examples/deltanet.jl:56-57, 85).
 //
 // Two launches.  `deltanet_chunk_kernel` does everything inside a chunk, one block per (head, chunk):
-// the two 64 x 64 x 128 products on CUDA cores in Float32 and, instead of forming (I + A)^-1 by blocks as
-// the reference's `blocks` does (examples/deltanet.jl:39-54), a forward substitution on the 256 right-hand
-// columns at once, one column per thread with the solution held in registers -- the same numbers, no
-// inverse.  `deltanet_scan_kernel` carries the state, one block per (head, 32 value features): the state
+// the two 64 x 64 x 128 products as warp-level BFloat16 MMAs (exact products of the BFloat16 operands, Float32
+// sums), (I + A)^-1 by 16 x 16 blocks as the reference's `blocks` does (examples/deltanet.jl:39-54: the diagonal
+// blocks by substitution in Float32, the blocks below them by small products in 3xTF32), and
+// [W | Ut] = (I + A)^-1 [beta e^ca K | beta V] as TF32 MMAs.  (The first version solved the 256 right-hand columns
+// by forward substitution, one column per thread: 2016 dependent multiply-adds a thread; measured 1.61 -> 1.39 ms
+// for the whole forward with the products on MMAs and the sums split four ways, and less again with the inverse.)
+// `deltanet_scan_kernel` carries the state, one block per (head, 32 value features): the state
 // slice (128 x 32 Float32) lives in shared memory for all 128 chunks and each chunk costs three small
 // products, issued as TF32 warp-level MMAs with operands in shared memory and results in registers (each
 // product feeds the next one of the chain at once; about 0.1 TFLOP in all).  The path is bound by the chain
@@ -52,113 +55,223 @@ __device__ __forceinline__ void chunk_cumsum(const float *a, int lane, float &lo
 
 // ---------------------------------------------------------------- within a chunk ----
 
-// With minv_save (the backward's first launch) the block has 320 threads: the extra 64 solve
-// (I + A) X = I, one identity column each, which is (I + A)^-1 for the reverse scan.
-__global__ void __launch_bounds__(320) deltanet_chunk_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+// Warp-level BFloat16 tensor-core product step: D(16 x 8) += A(16 x 16) B(16 x 8), Float32 accumulate.  With
+// g = lane / 4 and t = lane % 4 a thread holds A[g][2t, 2t+1], A[g+8][2t, 2t+1], A[g][2t+8, 2t+9], A[g+8][2t+8, 2t+9];
+// B[2t, 2t+1][g], B[2t+8, 2t+9][g]; D[g][2t], D[g][2t+1], D[g+8][2t], D[g+8][2t+1].
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kPadA = 68;   // Float32 row pitch of the 64 x 64 tiles A, (I + A)^-1 and the scratch beside them
+
+// 3xTF32: a Float32 operand as the sum of two TF32 values; hi*hi + lo*hi + hi*lo keeps about 21 bits of the product.
+__device__ __forceinline__ void split_tf32(float x, uint32_t &hi, uint32_t &lo) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    const float rest = x - __uint_as_float(hi);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+}
+__device__ __forceinline__ void mma_tf32_raw(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// acc(16 x 16) += L(16 x 16) R(16 x 16), both Float32 blocks of pitch-kPadA tiles, by one warp in 3xTF32.
+__device__ __forceinline__ void block_product(float (&acc)[2][4], const float *L, const float *R, int lane) {
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int kk = 0; kk < 16; kk += 8) {
+        uint32_t ah[4], al[4];
+        split_tf32(L[g * kPadA + kk + t4], ah[0], al[0]);
+        split_tf32(L[(g + 8) * kPadA + kk + t4], ah[1], al[1]);
+        split_tf32(L[g * kPadA + kk + t4 + 4], ah[2], al[2]);
+        split_tf32(L[(g + 8) * kPadA + kk + t4 + 4], ah[3], al[3]);
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            uint32_t bh0, bl0, bh1, bl1;
+            split_tf32(R[(kk + t4) * kPadA + 8 * nt + g], bh0, bl0);
+            split_tf32(R[(kk + t4 + 4) * kPadA + 8 * nt + g], bh1, bl1);
+            mma_tf32_raw(acc[nt], al, bh0, bh1);
+            mma_tf32_raw(acc[nt], ah, bl0, bl1);
+            mma_tf32_raw(acc[nt], ah, bh0, bh1);
+        }
+    }
+}
+__device__ __forceinline__ void block_store(float *dst, const float (&acc)[2][4], int lane, float sign) {
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+        *reinterpret_cast<float2 *>(dst + g * kPadA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
+        *reinterpret_cast<float2 *>(dst + (g + 8) * kPadA + 8 * nt + 2 * t4) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
+    }
+}
+
+// One block of 256 threads per (head, chunk).  minv_save (the backward's first launch) receives (I + A)^-1.
+__device__ __forceinline__ uint32_t tf32_bits(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+
+__global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
                                                              const __nv_bfloat16 *v, const float *a, const float *beta,
                                                              __nv_bfloat16 *w_out, __nv_bfloat16 *u_out,
                                                              __nv_bfloat16 *p_out, float *minv_save,
                                                              int T) {
     extern __shared__ float sm[];
-    float *Kf = sm;                       // [64][132]
-    float *Qf = Kf + kC * kPadF;          // [64][132]
-    float *A = Qf + kC * kPadF;           // [64][64]
-    float *ca = A + kC * kC;              // [64]
+    float *A = sm;                        // [64][68]
+    float *Mi = A + kC * kPadA;           // [64][68]  (I + A)^-1
+    float *ca = Mi + kC * kPadA;          // [64]
     float *be = ca + kC;                  // [64]
+    float *sk = be + kC;                  // [64]  beta e^ca: the scale of K's rows on the right-hand side
+    __nv_bfloat16 *Kh = reinterpret_cast<__nv_bfloat16 *>(sk + kC);   // [64][136]
+    __nv_bfloat16 *Vh = Kh + kC * kPadH;                              // [64][136]
+    __nv_bfloat16 *Qh = Vh + kC * kPadH;                              // [64][136]; later the scratch Tm [64][68] Float32
+    float *Tm = reinterpret_cast<float *>(Qh);
+    static_assert(kC * kPadA * sizeof(float) <= kC * kPadH * sizeof(__nv_bfloat16), "the scratch fits Q's tile");
     const int chunks = T / kC;
     const int head = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
     const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
 
     for (int i = tid; i < kC * kDK / 8; i += blockDim.x) {
         const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
-        float kv[8], qv[8];
-        Access<__nv_bfloat16, true>::load_cached(k + (row0 + r) * kDK + c, kv);
-        Access<__nv_bfloat16, true>::load_cached(q + (row0 + r) * kDK + c, qv);
-#pragma unroll
-        for (int e = 0; e < 8; e++) { Kf[r * kPadF + c + e] = kv[e]; Qf[r * kPadF + c + e] = qv[e]; }
+        *reinterpret_cast<uint4 *>(Kh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(k + (row0 + r) * kDK + c));
+        *reinterpret_cast<uint4 *>(Qh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(q + (row0 + r) * kDK + c));
+        *reinterpret_cast<uint4 *>(Vh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(v + (row0 + r) * kDV + c));
     }
-    if (tid < kC) be[tid] = beta[row0 + tid];
     if (tid < 32) {
         float lo, hi;
         chunk_cumsum(a + row0, tid, lo, hi);
-        ca[tid] = lo;
-        ca[tid + 32] = hi;
+        const float b0 = beta[row0 + tid], b1 = beta[row0 + tid + 32];
+        ca[tid] = lo; ca[tid + 32] = hi;
+        be[tid] = b0; be[tid + 32] = b1;
+        sk[tid] = b0 * __expf(lo); sk[tid + 32] = b1 * __expf(hi);
     }
     __syncthreads();
 
-    // A = beta .* decay(t > s) .* (K K'), P = decay(t >= s) .* (Q K'): thread (ty, tx) takes rows 4 ty .. 4 ty + 3 and
-    // columns tx, tx + 16, tx + 32, tx + 48 -- neighbouring threads read neighbouring rows of K, which the
-    // 132-float pitch spreads over all banks (rows 4 tx + j would fall on two bank groups).  Column blocks that
-    // lie wholly above the diagonal are skipped.
-    if (tid < 256) {
-        const int ty = tid >> 4, tx = tid & 15;
+    // A = beta .* decay(t > s) .* (K K'), P = decay(t >= s) .* (Q K') on the tensor cores: the operands are BFloat16 as
+    // they arrive, so the products are exact and only the order of the Float32 additions differs from a sequential
+    // sum.  Warp w takes rows 16 (w % 4) .. + 15 and columns 32 (w / 4) .. + 31 (four 8-column tiles) of both; both
+    // operands are read along the feature axis from the row-major tiles (pitch 136: the 32 lanes of a fragment read hit
+    // 32 banks).  Tiles wholly above the diagonal are skipped.
+    {
+        const int m0 = 16 * (warp & 3), n0 = 32 * (warp >> 2);
         float kk[4][4] = {}, qk[4][4] = {};
-        const int nj = ty / 4 + 1;   // column blocks 16 j .. 16 j + 15 that reach the diagonal of rows 4 ty .. 4 ty + 3
-        for (int d = 0; d < kDK; d += 4) {
-            float4 kt[4], qt[4], ks[4];
+        const int live = n0 > m0 + 15 ? 0 : (m0 + 15 - n0) / 8 + 1;   // 8-column tiles that reach the diagonal
+        if (live > 0) {
+            for (int d = 0; d < kDK; d += 16) {
+                uint32_t ak[4], aq[4];
+                const __nv_bfloat16 *kr = Kh + (m0 + g) * kPadH + d + 2 * t4, *qr = Qh + (m0 + g) * kPadH + d + 2 * t4;
+                ak[0] = *reinterpret_cast<const uint32_t *>(kr);
+                ak[1] = *reinterpret_cast<const uint32_t *>(kr + 8 * kPadH);
+                ak[2] = *reinterpret_cast<const uint32_t *>(kr + 8);
+                ak[3] = *reinterpret_cast<const uint32_t *>(kr + 8 * kPadH + 8);
+                aq[0] = *reinterpret_cast<const uint32_t *>(qr);
+                aq[1] = *reinterpret_cast<const uint32_t *>(qr + 8 * kPadH);
+                aq[2] = *reinterpret_cast<const uint32_t *>(qr + 8);
+                aq[3] = *reinterpret_cast<const uint32_t *>(qr + 8 * kPadH + 8);
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                kt[i] = *reinterpret_cast<const float4 *>(Kf + (ty * 4 + i) * kPadF + d);
-                qt[i] = *reinterpret_cast<const float4 *>(Qf + (ty * 4 + i) * kPadF + d);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++)
-                if (j < nj) ks[j] = *reinterpret_cast<const float4 *>(Kf + (tx + 16 * j) * kPadF + d);
-#pragma unroll
-            for (int j = 0; j < 4; j++)
-                if (j < nj) {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        kk[i][j] += kt[i].x * ks[j].x + kt[i].y * ks[j].y + kt[i].z * ks[j].z + kt[i].w * ks[j].w;
-                        qk[i][j] += qt[i].x * ks[j].x + qt[i].y * ks[j].y + qt[i].z * ks[j].z + qt[i].w * ks[j].w;
+                for (int j = 0; j < 4; j++)
+                    if (j < live) {
+                        const __nv_bfloat16 *br = Kh + (n0 + 8 * j + g) * kPadH + d + 2 * t4;
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(br), b1 = *reinterpret_cast<const uint32_t *>(br + 8);
+                        mma_bf16(kk[j], ak, b0, b1);
+                        mma_bf16(qk[j], aq, b0, b1);
                     }
-                }
+            }
         }
         __nv_bfloat16 *pc = p_out + (static_cast<long long>(head) * chunks + chunk) * kC * kC;
 #pragma unroll
-        for (int i = 0; i < 4; i++)
+        for (int j = 0; j < 4; j++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int t = ty * 4 + i, s = tx + 16 * j;
-                const float dec = t >= s ? __expf(ca[t] - ca[s]) : 0.0f;
-                A[t * kC + s] = t > s ? be[t] * dec * kk[i][j] : 0.0f;
-                pc[t * kC + s] = __float2bfloat16_rn(t >= s ? dec * qk[i][j] : 0.0f);
+            for (int e = 0; e < 4; e += 2) {
+                const int t = m0 + g + 8 * (e >> 1), s = n0 + 8 * j + 2 * t4;
+                const float d0 = t >= s ? __expf(ca[t] - ca[s]) : 0.0f, d1 = t >= s + 1 ? __expf(ca[t] - ca[s + 1]) : 0.0f;
+                A[t * kPadA + s] = t > s ? be[t] * d0 * kk[j][e] : 0.0f;
+                A[t * kPadA + s + 1] = t > s + 1 ? be[t] * d1 * kk[j][e + 1] : 0.0f;
+                *reinterpret_cast<uint32_t *>(pc + t * kC + s) = pack_bf16x2(d0 * qk[j][e], d1 * qk[j][e + 1]);
             }
     }
-    __syncthreads();
+    __syncthreads();   // A is complete; Q's tile is free from here on (Tm)
 
-    // (I + A) x = rhs by forward substitution, one right-hand column per thread, x in registers.  The
-    // right-hand side is formed first, its three kinds outside the loops, so that the 2016-step
-    // substitution is straight-line code.
+    // (I + A)^-1 by 16 x 16 blocks, as the reference's `blocks` does (examples/deltanet.jl:39-54).  Diagonal blocks:
+    // 64 threads solve (I + A_ii) x = e_j by substitution, one column each, in Float32.
+    if (tid < kC) {
+        const int blk = tid >> 4, j = tid & 15;
+        const float *D = A + (16 * blk) * kPadA + 16 * blk;
+        float x[16];
+#pragma unroll
+        for (int r = 0; r < 16; r++) {
+            float acc = r == j ? 1.0f : 0.0f;
+#pragma unroll
+            for (int c = 0; c < r; c++) acc = fmaf(-D[r * kPadA + c], x[c], acc);
+            x[r] = acc;
+        }
+#pragma unroll
+        for (int r = 0; r < 16; r++) Mi[(16 * blk + r) * kPadA + 16 * blk + j] = x[r];
+    } else {
+        // the blocks above the diagonal are zero
+        for (int i = tid - kC; i < 6 * 256; i += blockDim.x - kC) {
+            const int pair = i >> 8, e = i & 255;
+            const int bi = pair < 3 ? 0 : pair < 5 ? 1 : 2, bj = pair < 3 ? pair + 1 : pair < 5 ? pair - 1 : 3;
+            Mi[(16 * bi + (e >> 4)) * kPadA + 16 * bj + (e & 15)] = 0.0f;
+        }
+    }
+    __syncthreads();
+    // Blocks below the diagonal, one distance from it at a time:  M_ij = -M_ii (sum_{j <= k < i} A_ik M_kj), each block
+    // by one warp, products in 3xTF32 (close to Float32: the inverse is an operand of everything after it).
+    for (int dist = 1; dist < 4; dist++) {
+        if (warp < 4 - dist) {
+            const int bi = warp + dist, bj = warp;
+            float acc[2][4] = {};
+            for (int bk = bj; bk < bi; bk++)
+                block_product(acc, A + (16 * bi) * kPadA + 16 * bk, Mi + (16 * bk) * kPadA + 16 * bj, lane);
+            float *scratch = Tm + (16 * bi) * kPadA + 16 * bj;
+            block_store(scratch, acc, lane, 1.0f);
+            __syncwarp();
+            float out[2][4] = {};
+            block_product(out, Mi + (16 * bi) * kPadA + 16 * bi, scratch, lane);
+            block_store(Mi + (16 * bi) * kPadA + 16 * bj, out, lane, -1.0f);
+        }
+        __syncthreads();
+    }
+    if (minv_save)
+        for (int i = tid; i < kC * kC / 4; i += blockDim.x) {
+            const int r = i / (kC / 4), c = (i % (kC / 4)) * 4;
+            *reinterpret_cast<float4 *>(minv_save + (row0 + r) * kC + c) = *reinterpret_cast<const float4 *>(Mi + r * kPadA + c);
+        }
+
+    // [W | Ut] = (I + A)^-1 [beta e^ca K | beta V]: warp w takes rows 16 (w % 4) .. + 15 of the 128 columns of W
+    // (w < 4) or of Ut, as TF32 MMAs (W and Ut leave as BFloat16, whose rounding is four times coarser than TF32's);
+    // the right-hand side is formed from the BFloat16 tiles as the fragments are read, and the inverse's zero blocks
+    // above the diagonal are skipped.
     {
-        const int c = tid;   // 0..127: W, 128..255: Ut, 256..319: the identity (for (I + A)^-1)
-        float x[kC];
-        if (c < kDK) {
+        const int m0 = 16 * (warp & 3), side = warp >> 2;
+        const __nv_bfloat16 *rhs = side ? Vh : Kh;
+        const float *scale = side ? be : sk;
+        float acc[16][4] = {};
+        for (int kk = 0; kk < m0 + 16; kk += 8) {
+            uint32_t af[4];
+            af[0] = tf32_bits(Mi[(m0 + g) * kPadA + kk + t4]);
+            af[1] = tf32_bits(Mi[(m0 + g + 8) * kPadA + kk + t4]);
+            af[2] = tf32_bits(Mi[(m0 + g) * kPadA + kk + t4 + 4]);
+            af[3] = tf32_bits(Mi[(m0 + g + 8) * kPadA + kk + t4 + 4]);
+            const float s0 = scale[kk + t4], s1 = scale[kk + t4 + 4];
+            const __nv_bfloat16 *r0 = rhs + (kk + t4) * kPadH + g, *r1 = r0 + 4 * kPadH;
 #pragma unroll
-            for (int t = 0; t < kC; t++) x[t] = be[t] * __expf(ca[t]) * Kf[t * kPadF + c];
-        } else if (c < kDK + kDV) {
-#pragma unroll
-            for (int t = 0; t < kC; t++)
-                x[t] = be[t] * bf16_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(v) + (row0 + t) * kDV + (c - kDK)));
-        } else {
-#pragma unroll
-            for (int t = 0; t < kC; t++) x[t] = (t == c - kDK - kDV) ? 1.0f : 0.0f;
+            for (int nt = 0; nt < 16; nt++) {
+                const uint32_t b0 = tf32_bits(s0 * __bfloat162float(r0[8 * nt]));
+                const uint32_t b1 = tf32_bits(s1 * __bfloat162float(r1[8 * nt]));
+                mma_tf32_raw(acc[nt], af, b0, b1);
+            }
         }
+        __nv_bfloat16 *dst = (side ? u_out : w_out) + row0 * 128;
 #pragma unroll
-        for (int t = 1; t < kC; t++) {
-            float acc = x[t];
-#pragma unroll
-            for (int s = 0; s < t; s++) acc = fmaf(-A[t * kC + s], x[s], acc);
-            x[t] = acc;
-        }
-        if (c >= kDK + kDV) {
-#pragma unroll
-            for (int t = 0; t < kC; t++) minv_save[(row0 + t) * kC + (c - kDK - kDV)] = x[t];
-        } else {
-            __nv_bfloat16 *dst = (c < kDK ? w_out : u_out) + row0 * 128 + (c & 127);
-#pragma unroll
-            for (int t = 0; t < kC; t++) dst[t * 128] = __float2bfloat16_rn(x[t]);
+        for (int nt = 0; nt < 16; nt++) {
+            *reinterpret_cast<uint32_t *>(dst + (m0 + g) * 128 + 8 * nt + 2 * t4) = pack_bf16x2(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<uint32_t *>(dst + (m0 + g + 8) * 128 + 8 * nt + 2 * t4) = pack_bf16x2(acc[nt][2], acc[nt][3]);
         }
     }
 }
@@ -995,7 +1108,7 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     }
 }
 
-constexpr size_t kChunkSmem = (2 * kC * kPadF + kC * kC + 2 * kC) * sizeof(float);
+constexpr size_t kChunkSmem = (2 * kC * kPadA + 3 * kC) * sizeof(float) + 3 * kC * kPadH * sizeof(__nv_bfloat16);
 constexpr size_t kScanSmem = (kDK * kPadS + kC * kPadS + 4 * kC) * sizeof(float) +
                              (4 * kC * kPadH + kC * kPadP + kDVP * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdScanSmem = (kDK * kPadS + 3 * kC * kPadS + kC * kPadM + 3 * kC) * sizeof(float) +
@@ -1119,7 +1232,7 @@ extern "C" int tb200_deltanet_bwd(const tb200_deltanet_desc *d, const void *q, c
     dim3 grid(static_cast<unsigned>(d->heads), kDV / kDVP);
 
     // the forward again, keeping what the pullback needs: (I + A)^-1, the state at every chunk start, U
-    deltanet_chunk_kernel<<<chunks, 320, kChunkSmem, stream>>>(qb, kb, vb, a, beta, w, u, pw, minv, T);
+    deltanet_chunk_kernel<<<chunks, 256, kChunkSmem, stream>>>(qb, kb, vb, a, beta, w, u, pw, minv, T);
     TB200_CUDA(cudaGetLastError());
     // no result pointer: the scan only carries the state
     deltanet_scan_kernel<<<grid, 256, kScanSmem, stream>>>(qb, kb, a, w, u, pw, nullptr, s_save, u_save, T);
