@@ -37,20 +37,22 @@ constexpr int kPadF = 132;    // Float32 row pitch of a 128-wide tile in shared 
 constexpr int kPadH = 136;    // BFloat16 row pitch of a 128-wide tile
 constexpr int kPadP = 72;     // BFloat16 row pitch of a 64-wide tile
 
-__device__ __forceinline__ float bf16_bits_to_float(unsigned short h) { return __uint_as_float(static_cast<uint32_t>(h) << 16); }
 
 // Inclusive running sum of a chunk's 64 log-decay gates by one warp: lane l gets ca[l] and ca[l + 32].  (One
 // thread adding them in turn would wait for 64 loads one after another at the head of every link of the
 // chain of chunks.)
-__device__ __forceinline__ void chunk_cumsum(const float *a, int lane, float &lo, float &hi) {
-    lo = __ldg(a + lane);
-    hi = __ldg(a + lane + 32);
+__device__ __forceinline__ void chunk_cumsum_of(int lane, float &lo, float &hi) {   // lo, hi: the gates themselves on entry
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
         const float l2 = __shfl_up_sync(0xffffffffu, lo, off), h2 = __shfl_up_sync(0xffffffffu, hi, off);
         if (lane >= off) { lo += l2; hi += h2; }
     }
     hi += __shfl_sync(0xffffffffu, lo, 31);
+}
+__device__ __forceinline__ void chunk_cumsum(const float *a, int lane, float &lo, float &hi) {
+    lo = __ldg(a + lane);
+    hi = __ldg(a + lane + 32);
+    chunk_cumsum_of(lane, lo, hi);
 }
 
 // ---------------------------------------------------------------- within a chunk ----
@@ -278,9 +280,6 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
 
 // ----------------------------------------------------------------- across chunks ----
 
-__device__ __forceinline__ void unpack8(const __nv_bfloat16 *p, float *v) {
-    Access<__nv_bfloat16, true>::unpack(*reinterpret_cast<const uint4 *>(p), v);
-}
 
 // Warp-level TF32 tensor-core product step: D(16 x 8) += A(16 x 8) B(8 x 8), Float32 accumulate.  With
 // g = lane / 4 and t = lane % 4 a thread holds A[g][t], A[g+8][t], A[g][t+4], A[g+8][t+4]; B[t][g], B[t+4][g];
@@ -311,20 +310,46 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src)
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
-// The tiles of the next chunk are copied asynchronously into their buffers as soon as the current chunk's
-// last reader of each is past (W after the first product, Q and P after the second; K has two buffers), and
-// the next chunk's gates and Ut values are fetched meanwhile: a link of the chain waits for no load.
+// Four 8 x 8 BFloat16 matrices from shared memory into a warp's registers, as the m16n8k16 fragments want them: each
+// lane gives the address of one 16-byte row (lanes 0-7 the first matrix, 8-15 the second, ...); with `trans` the
+// matrices arrive transposed (an operand stored with the other axis contiguous).
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void *row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(row))));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void *row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(row))));
+}
+
+constexpr int kPadB = 40;   // BFloat16 row pitch of the 32-wide operand copies of the state and of U: ldmatrix rows hit 32 banks
+
+// One block per (head, 32 value features) walks the chunks in order.  The state slice (128 x 32) lives in the
+// accumulator registers of the product that updates it (warp w: state rows 16 w .. + 15) for the whole sequence; what
+// the other products read is a BFloat16 copy in shared memory, rewritten after every update -- the reference rounds
+// the Float32 factor of a mixed product to the half type in the same way (ext/cuTileExt/emit.jl:914-921).  All four
+// products of a chunk are BFloat16 m16n8k16 MMAs whose fragments come through ldmatrix (transposed where the operand
+// lies the other way: the state and U as B operands, K' as an A operand), about 40 instructions a product a warp where
+// the TF32 form with scalar fragment loads and conversions needed 300; the chain of chunks was bound by exactly
+// those instructions (measured: 4.8 us a chunk, 8 warps, issue slots 42 % active).  The tiles of the next chunk
+// are copied asynchronously as soon as the current chunk's last reader of each is past (W after the first product,
+// K in two buffers, Q and P after the output product), and the next chunk's gates and Ut values are fetched
+// meanwhile.
 __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
                                                             const float *a, const __nv_bfloat16 *w_in,
                                                             const __nv_bfloat16 *u_in, const __nv_bfloat16 *p_in,
                                                             __nv_bfloat16 *o, float *s_save, float *u_save, int T) {
     extern __shared__ float sm[];
-    float *S = sm;                                      // [128][40] the state slice
-    float *U = S + kDK * kPadS;                         // [64][40]
-    float *eca2 = U + kC * kPadS;                       // [2][64] exp(ca), per chunk parity
+    float *eca2 = sm;                                   // [2][64] exp(ca), per chunk parity
     float *ekd2 = eca2 + 2 * kC;                        // [2][64] exp(ca_C - ca)
-    __nv_bfloat16 *Wh = reinterpret_cast<__nv_bfloat16 *>(ekd2 + 2 * kC);   // [64][136]
+    __nv_bfloat16 *Sb2 = reinterpret_cast<__nv_bfloat16 *>(ekd2 + 2 * kC);   // [2][128][40] the state as an operand
+    __nv_bfloat16 *Ub = Sb2 + 2 * kDK * kPadB;          // [64][40] U
+    __nv_bfloat16 *Ud = Ub + kC * kPadB;                // [64][40] e^{ca_C - ca} U
+    __nv_bfloat16 *Wh = Ud + kC * kPadB;                // [64][136]
     __nv_bfloat16 *Qh = Wh + kC * kPadH;
     __nv_bfloat16 *Kh2 = Qh + kC * kPadH;               // [2][64][136]
     __nv_bfloat16 *Ph = Kh2 + 2 * kC * kPadH;           // [64][72]
@@ -335,7 +360,10 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t4 = lane & 3;
     const int chunks = T / kC;
-    for (int i = tid; i < kDK * kPadS; i += 256) S[i] = 0.0f;
+    // ldmatrix lane -> (row, column) offsets inside a 16 x 16 operand block: `plain` for A operands stored
+    // [row][k] and (transposed) for B operands stored [k][n]; `flip` for A operands stored [k][row]
+    const int plain_r = (lane & 7) + 8 * ((lane >> 3) & 1), plain_c = 8 * (lane >> 4);
+    const int flip_r = (lane & 7) + 8 * (lane >> 4), flip_c = 8 * ((lane >> 3) & 1);
 
     // U and o: warp -> 16 positions (mt) x 16 features (nh), two 8-feature tiles
     const int mt = warp & 3, nh = warp >> 2;
@@ -352,9 +380,18 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
             cp_async16(Ph + r * kPadP + c, p_in + (static_cast<long long>(head) * chunks + chunk) * kC * kC + r * kC + c);
         }
     };
-    auto gates = [&](int chunk) {   // warp 0
-        float lo, hi;
-        chunk_cumsum(a + head_row + static_cast<long long>(chunk) * kC, lane, lo, hi);
+    // warp 0 keeps the gates of the chunk after next in two registers, so that a chunk's running sums start from
+    // values that are already here (a load at this point would sit on the chain of chunks)
+    float gate_lo = 0.0f, gate_hi = 0.0f;
+    auto fetch_gates = [&](int chunk) {
+        if (chunk < chunks) {
+            gate_lo = __ldg(a + head_row + static_cast<long long>(chunk) * kC + lane);
+            gate_hi = __ldg(a + head_row + static_cast<long long>(chunk) * kC + lane + 32);
+        }
+    };
+    auto gates = [&](int chunk) {   // warp 0, from the fetched values
+        float lo = gate_lo, hi = gate_hi;
+        chunk_cumsum_of(lane, lo, hi);
         const float last = __shfl_sync(0xffffffffu, hi, 31);
         float *eca = eca2 + (chunk & 1) * kC, *ekd = ekd2 + (chunk & 1) * kC;
         eca[lane] = __expf(lo); eca[lane + 32] = __expf(hi);
@@ -372,40 +409,71 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
                 unpack_bf16x2(two, acc[nt][2 * hr], acc[nt][2 * hr + 1]);
             }
     };
+    // the state rows of this warp as an operand copy: rows 16 warp + g (+8), columns 8 nt + 2 t4 (+1)
+    auto put_state = [&](__nv_bfloat16 *Sb, const float (&st)[4][4]) {
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            *reinterpret_cast<uint32_t *>(Sb + (16 * warp + g) * kPadB + 8 * nt + 2 * t4) = pack_bf16x2(st[nt][0], st[nt][1]);
+            *reinterpret_cast<uint32_t *>(Sb + (16 * warp + g + 8) * kPadB + 8 * nt + 2 * t4) = pack_bf16x2(st[nt][2], st[nt][3]);
+        }
+    };
+    auto write_out = [&](int chunk) {   // the result is (positions, features): 128 contiguous bytes per feature
+        const int f = tid >> 3, c = (tid & 7) * 8;
+        *reinterpret_cast<uint4 *>(o + (static_cast<long long>(head) * kDV + part * kDVP + f) * T +
+                                   static_cast<long long>(chunk) * kC + c) = *reinterpret_cast<const uint4 *>(Oh + f * kPadP + c);
+    };
 
+    float state[4][4] = {};
     float acc[2][4];
+    put_state(Sb2, state);
+    // Two groups of asynchronous copies are in flight at a time and complete in the order they were committed:
+    // {W, K} of the next chunk (committed after this chunk's first product) and {Q, P} (committed after its output
+    // product); each wait lets the younger group run on.
     if (chunks > 0) {
         copy_rows(Wh, w_in, head_row);
-        copy_rows(Qh, q, head_row);
         copy_rows(Kh2, k, head_row);
-        copy_p(0);
         cp_async_commit();
-        if (warp == 0) gates(0);
+        if (o) {
+            copy_rows(Qh, q, head_row);
+            copy_p(0);
+            cp_async_commit();
+        }
+        if (warp == 0) {
+            fetch_gates(0);
+            gates(0);
+            fetch_gates(1);
+        }
         fetch_ut(0, acc);
     }
     for (int chunk = 0; chunk < chunks; chunk++) {
         const long long row0 = head_row + static_cast<long long>(chunk) * kC;
         const float *eca = eca2 + (chunk & 1) * kC, *ekd = ekd2 + (chunk & 1) * kC;
         const __nv_bfloat16 *Kh = Kh2 + (chunk & 1) * kC * kPadH;
+        const __nv_bfloat16 *Sb = Sb2 + (chunk & 1) * kDK * kPadB;
         const bool more = chunk + 1 < chunks;
-        cp_async_wait_all();
-        __syncthreads();   // this chunk's tiles and gates are in place; the previous chunk's state update is complete
+        if (o) cp_async_wait_but_one();   // W and K; Q and P may still be on their way
+        else cp_async_wait_all();
+        __syncthreads();   // this chunk's W, K, gates and state copy are in place; the staged output of the chunk before is complete
+        if (o && chunk > 0) write_out(chunk - 1);
         if (s_save) {      // the state this chunk starts from, for the backward
             float *dst = s_save + (static_cast<long long>(head) * chunks + chunk) * kDK * kDV + part * kDVP;
-            for (int i = tid; i < kDK * kDVP; i += 256) dst[(i / kDVP) * kDV + (i % kDVP)] = S[(i / kDVP) * kPadS + (i % kDVP)];
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                *reinterpret_cast<float2 *>(dst + (16 * warp + g) * kDV + 8 * nt + 2 * t4) = make_float2(state[nt][0], state[nt][1]);
+                *reinterpret_cast<float2 *>(dst + (16 * warp + g + 8) * kDV + 8 * nt + 2 * t4) = make_float2(state[nt][2], state[nt][3]);
+            }
         }
 
         // U = Ut - W S
         {
             float ws[2][4] = {};
-            const __nv_bfloat16 *w0 = Wh + (16 * mt + g) * kPadH + t4, *w1 = w0 + 8 * kPadH;
-            const float *sb = S + t4 * kPadS + 16 * nh + g;
-#pragma unroll 4
-            for (int k0 = 0; k0 < kDK; k0 += 8) {
-                const uint32_t af[4] = {tf32_of_bf16(w0 + k0), tf32_of_bf16(w1 + k0), tf32_of_bf16(w0 + k0 + 4), tf32_of_bf16(w1 + k0 + 4)};
 #pragma unroll
-                for (int nt = 0; nt < 2; nt++)
-                    mma_tf32(ws[nt], af, tf32_of(sb[k0 * kPadS + 8 * nt]), tf32_of(sb[(k0 + 4) * kPadS + 8 * nt]));
+            for (int k0 = 0; k0 < kDK; k0 += 16) {
+                uint32_t af[4], bf[4];
+                ldsm_x4(af, Wh + (16 * mt + plain_r) * kPadH + k0 + plain_c);
+                ldsm_x4_trans(bf, Sb + (k0 + plain_r) * kPadB + 16 * nh + plain_c);
+                mma_bf16(ws[0], af, bf[0], bf[1]);
+                mma_bf16(ws[1], af, bf[2], bf[3]);
             }
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
@@ -413,7 +481,9 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
                 for (int hr = 0; hr < 2; hr++) {
                     const float2 u2 = make_float2(acc[nt][2 * hr] - ws[nt][2 * hr], acc[nt][2 * hr + 1] - ws[nt][2 * hr + 1]);
                     const int row = 16 * mt + g + 8 * hr, col = 16 * nh + 8 * nt + 2 * t4;
-                    *reinterpret_cast<float2 *>(U + row * kPadS + col) = u2;
+                    const float ed = ekd[row];
+                    *reinterpret_cast<uint32_t *>(Ub + row * kPadB + col) = pack_bf16x2(u2.x, u2.y);
+                    *reinterpret_cast<uint32_t *>(Ud + row * kPadB + col) = pack_bf16x2(ed * u2.x, ed * u2.y);
                     if (u_save) *reinterpret_cast<float2 *>(u_save + (row0 + row) * kDV + part * kDVP + col) = u2;
                 }
         }
@@ -422,83 +492,76 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
             copy_rows(Wh, w_in, row0 + kC);
             copy_rows(Kh2 + ((chunk + 1) & 1) * kC * kPadH, k, row0 + kC);
             cp_async_commit();
-            if (warp == 0) gates(chunk + 1);
+            if (warp == 0) {
+                gates(chunk + 1);
+                fetch_gates(chunk + 2);
+            }
             fetch_ut(chunk + 1, acc);
         }
 
-        // o = (e^ca Q) S + P U
-        if (o) {
-            float oa[2][4] = {};
-            const __nv_bfloat16 *q0 = Qh + (16 * mt + g) * kPadH + t4, *q1 = q0 + 8 * kPadH;
-            const float *sb = S + t4 * kPadS + 16 * nh + g;
-#pragma unroll 4
-            for (int k0 = 0; k0 < kDK; k0 += 8) {
-                const uint32_t af[4] = {tf32_of_bf16(q0 + k0), tf32_of_bf16(q1 + k0), tf32_of_bf16(q0 + k0 + 4), tf32_of_bf16(q1 + k0 + 4)};
+        // S <- e^{ca_C} S + K' (e^{ca_C - ca} U): warp -> 16 state rows, all 32 features; then the operand copy for
+        // the next chunk (the other buffer: this chunk's output product still reads the current one)
+        {
+            const float gamma = gamma_sm[chunk & 1];
 #pragma unroll
-                for (int nt = 0; nt < 2; nt++)
-                    mma_tf32(oa[nt], af, tf32_of(sb[k0 * kPadS + 8 * nt]), tf32_of(sb[(k0 + 4) * kPadS + 8 * nt]));
+            for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) state[nt][e] *= gamma;
+#pragma unroll
+            for (int k0 = 0; k0 < kC; k0 += 16) {
+                uint32_t af[4], b0[4], b1[4];
+                ldsm_x4_trans(af, Kh + (k0 + flip_r) * kPadH + 16 * warp + flip_c);
+                ldsm_x4_trans(b0, Ud + (k0 + plain_r) * kPadB + plain_c);
+                ldsm_x4_trans(b1, Ud + (k0 + plain_r) * kPadB + 16 + plain_c);
+                mma_bf16(state[0], af, b0[0], b0[1]);
+                mma_bf16(state[1], af, b0[2], b0[3]);
+                mma_bf16(state[2], af, b1[0], b1[1]);
+                mma_bf16(state[3], af, b1[2], b1[3]);
+            }
+            put_state(Sb2 + ((chunk + 1) & 1) * kDK * kPadB, state);
+        }
+
+        // o = e^ca (Q S) + P U, off the chain
+        if (o) {
+            if (more) cp_async_wait_but_one();   // Q and P (the next chunk's W and K run on)
+            else cp_async_wait_all();
+            __syncthreads();
+            float oa[2][4] = {};
+#pragma unroll
+            for (int k0 = 0; k0 < kDK; k0 += 16) {
+                uint32_t af[4], bf[4];
+                ldsm_x4(af, Qh + (16 * mt + plain_r) * kPadH + k0 + plain_c);
+                ldsm_x4_trans(bf, Sb + (k0 + plain_r) * kPadB + 16 * nh + plain_c);
+                mma_bf16(oa[0], af, bf[0], bf[1]);
+                mma_bf16(oa[1], af, bf[2], bf[3]);
             }
             const float e0 = eca[16 * mt + g], e1 = eca[16 * mt + g + 8];
 #pragma unroll
             for (int nt = 0; nt < 2; nt++) { oa[nt][0] *= e0; oa[nt][1] *= e0; oa[nt][2] *= e1; oa[nt][3] *= e1; }
-            const __nv_bfloat16 *p0 = Ph + (16 * mt + g) * kPadP + t4, *p1 = p0 + 8 * kPadP;
-            const float *ub = U + t4 * kPadS + 16 * nh + g;
-#pragma unroll 4
-            for (int k0 = 0; k0 < kC; k0 += 8) {
-                const uint32_t af[4] = {tf32_of_bf16(p0 + k0), tf32_of_bf16(p1 + k0), tf32_of_bf16(p0 + k0 + 4), tf32_of_bf16(p1 + k0 + 4)};
 #pragma unroll
-                for (int nt = 0; nt < 2; nt++)
-                    mma_tf32(oa[nt], af, tf32_of(ub[k0 * kPadS + 8 * nt]), tf32_of(ub[(k0 + 4) * kPadS + 8 * nt]));
+            for (int k0 = 0; k0 < kC; k0 += 16) {
+                uint32_t af[4], bf[4];
+                ldsm_x4(af, Ph + (16 * mt + plain_r) * kPadP + k0 + plain_c);
+                ldsm_x4_trans(bf, Ub + (k0 + plain_r) * kPadB + 16 * nh + plain_c);
+                mma_bf16(oa[0], af, bf[0], bf[1]);
+                mma_bf16(oa[1], af, bf[2], bf[3]);
             }
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
 #pragma unroll
                 for (int e = 0; e < 4; e++)
                     Oh[(16 * nh + 8 * nt + 2 * t4 + (e & 1)) * kPadP + 16 * mt + g + 8 * (e >> 1)] = __float2bfloat16_rn(oa[nt][e]);
-        }
-        __syncthreads();   // every reader of S, Q and P is done; the staged output is complete
-        if (more) {
-            copy_rows(Qh, q, row0 + kC);
-            copy_p(chunk + 1);
-            cp_async_commit();
-        }
-
-        // the result is (positions, features): 128 contiguous bytes per feature
-        if (o) {
-            const int f = tid >> 3, c = (tid & 7) * 8;
-            *reinterpret_cast<uint4 *>(o + (static_cast<long long>(head) * kDV + part * kDVP + f) * T +
-                                       static_cast<long long>(chunk) * kC + c) =
-                *reinterpret_cast<const uint4 *>(Oh + f * kPadP + c);
-        }
-        // S <- e^{ca_C} S + (e^{ca_C - ca} K)' U : warp -> 16 state rows, all 32 features
-        {
-            const float gamma = gamma_sm[chunk & 1];
-            float sa[4][4];
-            float *s0 = S + (16 * warp + g) * kPadS + 2 * t4, *s1 = s0 + 8 * kPadS;
-#pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                const float2 lo = *reinterpret_cast<const float2 *>(s0 + 8 * nt), hi = *reinterpret_cast<const float2 *>(s1 + 8 * nt);
-                sa[nt][0] = gamma * lo.x; sa[nt][1] = gamma * lo.y; sa[nt][2] = gamma * hi.x; sa[nt][3] = gamma * hi.y;
-            }
-            // A[i][t] = ekd[t] K[t][i]: rows i = 16 warp + g (+8), columns t = k0 + t4 (+4)
-            const __nv_bfloat16 *kb = Kh + t4 * kPadH + 16 * warp + g;
-            const float *ub = U + t4 * kPadS + g;
-#pragma unroll 2
-            for (int k0 = 0; k0 < kC; k0 += 8) {
-                const float ea = ekd[k0 + t4], eb = ekd[k0 + t4 + 4];
-                const uint32_t af[4] = {tf32_of(__bfloat162float(kb[k0 * kPadH]) * ea), tf32_of(__bfloat162float(kb[k0 * kPadH + 8]) * ea),
-                                        tf32_of(__bfloat162float(kb[(k0 + 4) * kPadH]) * eb),
-                                        tf32_of(__bfloat162float(kb[(k0 + 4) * kPadH + 8]) * eb)};
-#pragma unroll
-                for (int nt = 0; nt < 4; nt++)
-                    mma_tf32(sa[nt], af, tf32_of(ub[k0 * kPadS + 8 * nt]), tf32_of(ub[(k0 + 4) * kPadS + 8 * nt]));
-            }
-#pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                *reinterpret_cast<float2 *>(s0 + 8 * nt) = make_float2(sa[nt][0], sa[nt][1]);
-                *reinterpret_cast<float2 *>(s1 + 8 * nt) = make_float2(sa[nt][2], sa[nt][3]);
+            __syncthreads();   // every reader of Q and P is done
+            if (more) {
+                copy_rows(Qh, q, row0 + kC);
+                copy_p(chunk + 1);
+                cp_async_commit();
             }
         }
+    }
+    if (o && chunks > 0) {
+        __syncthreads();
+        write_out(chunks - 1);
     }
 }
 
@@ -1109,8 +1172,8 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
 }
 
 constexpr size_t kChunkSmem = (2 * kC * kPadA + 3 * kC) * sizeof(float) + 3 * kC * kPadH * sizeof(__nv_bfloat16);
-constexpr size_t kScanSmem = (kDK * kPadS + kC * kPadS + 4 * kC) * sizeof(float) +
-                             (4 * kC * kPadH + kC * kPadP + kDVP * kPadP) * sizeof(__nv_bfloat16);
+constexpr size_t kScanSmem = 4 * kC * sizeof(float) +
+                             (2 * kDK * kPadB + 2 * kC * kPadB + 4 * kC * kPadH + kC * kPadP + kDVP * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdScanSmem = (kDK * kPadS + 3 * kC * kPadS + kC * kPadM + 3 * kC) * sizeof(float) +
                                 (2 * kC * kPadH + kC * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdXgSmem = (3 * kC * kPadF + kC) * sizeof(float);
