@@ -25,6 +25,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace tb200 {
 namespace {
@@ -303,14 +304,6 @@ __device__ __forceinline__ uint32_t tf32_of_bf16(const __nv_bfloat16 *p) {
 
 constexpr int kPadS = 40;   // Float32 row pitch of the 32-wide state and U tiles: B-fragment reads hit 32 banks
 
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
-                 "l"(gmem_src)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 // Four 8 x 8 BFloat16 matrices from shared memory into a warp's registers, as the m16n8k16 fragments want them: each
 // lane gives the address of one 16-byte row (lanes 0-7 the first matrix, 8-15 the second, ...); with `trans` the
@@ -326,40 +319,56 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void *row)
                  : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(row))));
 }
 
+__device__ int g_deltanet_error = 0;   // 1 once a wait for a chunk's tiles has given up
+
 constexpr int kPadB = 40;   // BFloat16 row pitch of the 32-wide operand copies of the state and of U: ldmatrix rows hit 32 banks
 
-// One block per (head, 32 value features) walks the chunks in order.  The state slice (128 x 32) lives in the
-// accumulator registers of the product that updates it (warp w: state rows 16 w .. + 15) for the whole sequence; what
-// the other products read is a BFloat16 copy in shared memory, rewritten after every update -- the reference rounds
-// the Float32 factor of a mixed product to the half type in the same way (ext/cuTileExt/emit.jl:914-921).  All four
-// products of a chunk are BFloat16 m16n8k16 MMAs whose fragments come through ldmatrix (transposed where the operand
-// lies the other way: the state and U as B operands, K' as an A operand), about 40 instructions a product a warp where
-// the TF32 form with scalar fragment loads and conversions needed 300; the chain of chunks was bound by exactly
-// those instructions (measured: 4.8 us a chunk, 8 warps, issue slots 42 % active).  The tiles of the next chunk
-// are copied asynchronously as soon as the current chunk's last reader of each is past (W after the first product,
-// K in two buffers, Q and P after the output product), and the next chunk's gates and Ut values are fetched
-// meanwhile.
-__global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
-                                                            const float *a, const __nv_bfloat16 *w_in,
-                                                            const __nv_bfloat16 *u_in, const __nv_bfloat16 *p_in,
-                                                            __nv_bfloat16 *o, float *s_save, float *u_save, int T) {
-    extern __shared__ float sm[];
-    float *eca2 = sm;                                   // [2][64] exp(ca), per chunk parity
-    float *ekd2 = eca2 + 2 * kC;                        // [2][64] exp(ca_C - ca)
-    __nv_bfloat16 *Sb2 = reinterpret_cast<__nv_bfloat16 *>(ekd2 + 2 * kC);   // [2][128][40] the state as an operand
-    __nv_bfloat16 *Ub = Sb2 + 2 * kDK * kPadB;          // [64][40] U
-    __nv_bfloat16 *Ud = Ub + kC * kPadB;                // [64][40] e^{ca_C - ca} U
-    __nv_bfloat16 *Wh = Ud + kC * kPadB;                // [64][136]
-    __nv_bfloat16 *Qh = Wh + kC * kPadH;
-    __nv_bfloat16 *Kh2 = Qh + kC * kPadH;               // [2][64][136]
-    __nv_bfloat16 *Ph = Kh2 + 2 * kC * kPadH;           // [64][72]
-    __nv_bfloat16 *Oh = Ph + kC * kPadP;                // [32][72] output staging, [feature][position]
-    __shared__ float gamma_sm[2];
+// One block of 512 threads per (head, 64 value features) walks the chunks in order: two groups of eight warps, each
+// with its own 32 features, share the chunk's W, Q, K and P tiles.  A group's state slice (128 x 32) lives in the
+// accumulator registers of the product that updates it (warp w of the group: state rows 16 w .. + 15) for the whole
+// sequence; what the other products read is a BFloat16 copy in shared memory, rewritten after every update -- the
+// reference rounds the Float32 factor of a mixed product to the half type in the same way
+// (ext/cuTileExt/emit.jl:914-921).  All four products of a chunk are BFloat16 m16n8k16 MMAs whose fragments come
+// through ldmatrix (transposed where the operand lies the other way: the state and U as B operands, K' as an A
+// operand), about 40 instructions a product a warp where the TF32 form with scalar fragment loads and conversions
+// needed 300; the chain of chunks was bound by exactly those instructions (measured: 4.8 us a chunk, issue slots
+// 42 % active).  Every tile has two buffers: the next chunk's tiles are copied asynchronously while this chunk's
+// products run (a whole link of the chain ahead), and the next chunk's gates and Ut values are fetched meanwhile.
+constexpr int kScanThreads = 512;
+constexpr int kDVB = 64;          // value features per scan block (two groups of kDVP)
+constexpr int kBoxBytes = kC * 128;        // a TMA box: 64 rows of 64 BFloat16 (one 128-byte swizzled line each)
+constexpr int kTileSetBytes = 7 * kBoxBytes;   // one chunk's W, Q, K (two boxes each) and P (one)
+struct ScanMaps { CUtensorMap w, q, k, p; };   // [rows][128] for W, Q, K; [heads * chunks * 64][64] for P
 
-    const int head = blockIdx.x, part = blockIdx.y;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+// Address of the 16-byte piece that holds (row, col .. col + 7) of a [64][128] tile kept as two 128-byte-swizzled
+// boxes (or of a [64][64] tile: one box): what ldmatrix is given.
+__device__ __forceinline__ const unsigned char *swz(const unsigned char *tile, int row, int col) {
+    return tile + (col >> 6) * kBoxBytes + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __grid_constant__ ScanMaps maps, const float *a,
+                                                                     const __nv_bfloat16 *u_in, __nv_bfloat16 *o,
+                                                                     float *s_save, float *u_save, int T) {
+    extern __shared__ unsigned char sm_raw[];
+    // the tiles want 1024-byte alignment (the swizzle's period); the launch asks for 1 KB more than the layout
+    unsigned char *tiles = sm_raw + ((1024u - (sm100::smem_u32(sm_raw) & 1023u)) & 1023u);   // [2][7 boxes]
+    float *eca2 = reinterpret_cast<float *>(tiles + 2 * kTileSetBytes);   // [2][64] exp(ca), per chunk parity
+    float *ekd2 = eca2 + 2 * kC;                                          // [2][64] exp(ca_C - ca)
+    __nv_bfloat16 *group_base = reinterpret_cast<__nv_bfloat16 *>(ekd2 + 2 * kC);
+    __shared__ float gamma_sm[2];
+    __shared__ __align__(8) uint64_t tile_full[2];
+
+    const int head = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int group = tid >> 8, gtid = tid & 255, warp = (tid >> 5) & 7;   // warp: index inside the group
+    const int part = blockIdx.y * (kDVB / kDVP) + group;                  // which 32 features
     const int g = lane >> 2, t4 = lane & 3;
     const int chunks = T / kC;
+    // this group's operand copies and output staging
+    __nv_bfloat16 *Sb2 = group_base + group * (2 * kDK * kPadB + 2 * kC * kPadB + kDVP * kPadP);   // [2][128][40] the state
+    __nv_bfloat16 *Ub = Sb2 + 2 * kDK * kPadB;          // [64][40] U
+    __nv_bfloat16 *Ud = Ub + kC * kPadB;                // [64][40] e^{ca_C - ca} U
+    __nv_bfloat16 *Oh = Ud + kC * kPadB;                // [32][72] output staging, [feature][position]
     // ldmatrix lane -> (row, column) offsets inside a 16 x 16 operand block: `plain` for A operands stored
     // [row][k] and (transposed) for B operands stored [k][n]; `flip` for A operands stored [k][row]
     const int plain_r = (lane & 7) + 8 * ((lane >> 3) & 1), plain_c = 8 * (lane >> 4);
@@ -368,20 +377,46 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
     // U and o: warp -> 16 positions (mt) x 16 features (nh), two 8-feature tiles
     const int mt = warp & 3, nh = warp >> 2;
     const long long head_row = static_cast<long long>(head) * T;
-    auto copy_rows = [&](__nv_bfloat16 *dst, const __nv_bfloat16 *src, long long row0) {   // a [64][128] tile
-        for (int i = tid; i < kC * kDK / 8; i += 256) {
-            const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
-            cp_async16(dst + r * kPadH + c, src + (row0 + r) * kDK + c);
+    // A chunk's tiles arrive by TMA, seven boxes (four without a result to form) issued by one thread and counted in
+    // bytes on the buffer's mbarrier.
+    const uint32_t tile_bytes = (o ? 7u : 4u) * kBoxBytes;
+    auto copy_tiles = [&](int chunk) {
+        if (tid != 0) return;
+        unsigned char *set = tiles + (chunk & 1) * kTileSetBytes;
+        uint64_t *bar = &tile_full[chunk & 1];
+        const int row = static_cast<int>(head_row) + chunk * kC;
+        sm100::mbar_arrive_expect_tx(bar, tile_bytes);
+        sm100::tma_load_2d(set, &maps.w, bar, 0, row);
+        sm100::tma_load_2d(set + kBoxBytes, &maps.w, bar, 64, row);
+        sm100::tma_load_2d(set + 4 * kBoxBytes, &maps.k, bar, 0, row);
+        sm100::tma_load_2d(set + 5 * kBoxBytes, &maps.k, bar, 64, row);
+        if (o) {
+            sm100::tma_load_2d(set + 2 * kBoxBytes, &maps.q, bar, 0, row);
+            sm100::tma_load_2d(set + 3 * kBoxBytes, &maps.q, bar, 64, row);
+            sm100::tma_load_2d(set + 6 * kBoxBytes, &maps.p, bar, 0, (head * chunks + chunk) * kC);
         }
     };
-    auto copy_p = [&](int chunk) {
-        for (int i = tid; i < kC * kC / 8; i += 256) {
-            const int r = i / (kC / 8), c = (i % (kC / 8)) * 8;
-            cp_async16(Ph + r * kPadP + c, p_in + (static_cast<long long>(head) * chunks + chunk) * kC * kC + r * kC + c);
+    // Waits for a buffer's tiles, but not for ever: after about two seconds the thread records the failure and
+    // goes on without waiting again, so that the launch ends and the host can read the status.
+    bool gave_up = false;
+    auto wait_tiles = [&](int chunk) {
+        if (gave_up) return;
+        uint64_t *bar = &tile_full[chunk & 1];
+        const uint32_t parity = (chunk >> 1) & 1;
+        if (sm100::mbar_wait(bar, parity, 4096)) return;
+        unsigned long long t0, t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        while (!sm100::mbar_wait(bar, parity, 1024)) {
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > 2000000000ull) {
+                gave_up = true;
+                atomicCAS(&g_deltanet_error, 0, 1);
+                return;
+            }
         }
     };
-    // warp 0 keeps the gates of the chunk after next in two registers, so that a chunk's running sums start from
-    // values that are already here (a load at this point would sit on the chain of chunks)
+    // warp 0 of the block keeps the gates of the chunk after next in two registers, so that a chunk's running sums
+    // start from values that are already here (a load at this point would sit on the chain of chunks)
     float gate_lo = 0.0f, gate_hi = 0.0f;
     auto fetch_gates = [&](int chunk) {
         if (chunk < chunks) {
@@ -389,7 +424,7 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
             gate_hi = __ldg(a + head_row + static_cast<long long>(chunk) * kC + lane + 32);
         }
     };
-    auto gates = [&](int chunk) {   // warp 0, from the fetched values
+    auto gates = [&](int chunk) {   // warp 0 of the block, from the fetched values
         float lo = gate_lo, hi = gate_hi;
         chunk_cumsum_of(lane, lo, hi);
         const float last = __shfl_sync(0xffffffffu, hi, 31);
@@ -418,7 +453,7 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
         }
     };
     auto write_out = [&](int chunk) {   // the result is (positions, features): 128 contiguous bytes per feature
-        const int f = tid >> 3, c = (tid & 7) * 8;
+        const int f = gtid >> 3, c = (gtid & 7) * 8;
         *reinterpret_cast<uint4 *>(o + (static_cast<long long>(head) * kDV + part * kDVP + f) * T +
                                    static_cast<long long>(chunk) * kC + c) = *reinterpret_cast<const uint4 *>(Oh + f * kPadP + c);
     };
@@ -426,19 +461,15 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
     float state[4][4] = {};
     float acc[2][4];
     put_state(Sb2, state);
-    // Two groups of asynchronous copies are in flight at a time and complete in the order they were committed:
-    // {W, K} of the next chunk (committed after this chunk's first product) and {Q, P} (committed after its output
-    // product); each wait lets the younger group run on.
+    if (tid == 0) {
+        sm100::mbar_init(&tile_full[0], 1);
+        sm100::mbar_init(&tile_full[1], 1);
+        sm100::fence_barrier_init();
+    }
+    __syncthreads();
     if (chunks > 0) {
-        copy_rows(Wh, w_in, head_row);
-        copy_rows(Kh2, k, head_row);
-        cp_async_commit();
-        if (o) {
-            copy_rows(Qh, q, head_row);
-            copy_p(0);
-            cp_async_commit();
-        }
-        if (warp == 0) {
+        copy_tiles(0);
+        if (tid < 32) {
             fetch_gates(0);
             gates(0);
             fetch_gates(1);
@@ -448,12 +479,13 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
     for (int chunk = 0; chunk < chunks; chunk++) {
         const long long row0 = head_row + static_cast<long long>(chunk) * kC;
         const float *eca = eca2 + (chunk & 1) * kC, *ekd = ekd2 + (chunk & 1) * kC;
-        const __nv_bfloat16 *Kh = Kh2 + (chunk & 1) * kC * kPadH;
+        const unsigned char *Wt = tiles + (chunk & 1) * kTileSetBytes, *Qt = Wt + 2 * kBoxBytes, *Kt = Wt + 4 * kBoxBytes,
+                            *Pt = Wt + 6 * kBoxBytes;
         const __nv_bfloat16 *Sb = Sb2 + (chunk & 1) * kDK * kPadB;
         const bool more = chunk + 1 < chunks;
-        if (o) cp_async_wait_but_one();   // W and K; Q and P may still be on their way
-        else cp_async_wait_all();
-        __syncthreads();   // this chunk's W, K, gates and state copy are in place; the staged output of the chunk before is complete
+        __syncthreads();   // this chunk's gates and state copy are in place; everything of the chunk before is done
+        if (more) copy_tiles(chunk + 1);   // into the buffers the chunk before has left
+        wait_tiles(chunk);
         if (o && chunk > 0) write_out(chunk - 1);
         if (s_save) {      // the state this chunk starts from, for the backward
             float *dst = s_save + (static_cast<long long>(head) * chunks + chunk) * kDK * kDV + part * kDVP;
@@ -464,17 +496,25 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
             }
         }
 
-        // U = Ut - W S
+        // U = Ut - W S (the sum over the state rows in two halves, so that four accumulators are in flight)
         {
-            float ws[2][4] = {};
+            float ws[2][4] = {}, ws2[2][4] = {};
 #pragma unroll
-            for (int k0 = 0; k0 < kDK; k0 += 16) {
-                uint32_t af[4], bf[4];
-                ldsm_x4(af, Wh + (16 * mt + plain_r) * kPadH + k0 + plain_c);
+            for (int k0 = 0; k0 < kDK / 2; k0 += 16) {
+                uint32_t af[4], bf[4], af2[4], bf2[4];
+                ldsm_x4(af, swz(Wt, 16 * mt + plain_r, k0 + plain_c));
                 ldsm_x4_trans(bf, Sb + (k0 + plain_r) * kPadB + 16 * nh + plain_c);
+                ldsm_x4(af2, swz(Wt, 16 * mt + plain_r, kDK / 2 + k0 + plain_c));
+                ldsm_x4_trans(bf2, Sb + (kDK / 2 + k0 + plain_r) * kPadB + 16 * nh + plain_c);
                 mma_bf16(ws[0], af, bf[0], bf[1]);
                 mma_bf16(ws[1], af, bf[2], bf[3]);
+                mma_bf16(ws2[0], af2, bf2[0], bf2[1]);
+                mma_bf16(ws2[1], af2, bf2[2], bf2[3]);
             }
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) ws[nt][e] += ws2[nt][e];
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
 #pragma unroll
@@ -487,12 +527,9 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
                     if (u_save) *reinterpret_cast<float2 *>(u_save + (row0 + row) * kDV + part * kDVP + col) = u2;
                 }
         }
-        __syncthreads();   // U is complete; W has been read
+        __syncthreads();   // U is complete
         if (more) {
-            copy_rows(Wh, w_in, row0 + kC);
-            copy_rows(Kh2 + ((chunk + 1) & 1) * kC * kPadH, k, row0 + kC);
-            cp_async_commit();
-            if (warp == 0) {
+            if (tid < 32) {
                 gates(chunk + 1);
                 fetch_gates(chunk + 2);
             }
@@ -500,62 +537,60 @@ __global__ void __launch_bounds__(256) deltanet_scan_kernel(const __nv_bfloat16 
         }
 
         // S <- e^{ca_C} S + K' (e^{ca_C - ca} U): warp -> 16 state rows, all 32 features; then the operand copy for
-        // the next chunk (the other buffer: this chunk's output product still reads the current one)
+        // the next chunk (the other buffer: this chunk's output product still reads the current one).
+        // o = e^ca (Q S) + P U is off the chain: its MMAs are issued between the update's, whose four accumulators
+        // each wait for their own previous step, so that the tensor pipe has independent work in the gaps.
         {
             const float gamma = gamma_sm[chunk & 1];
 #pragma unroll
             for (int nt = 0; nt < 4; nt++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) state[nt][e] *= gamma;
+            float oa[2][4] = {}, ob[2][4] = {};   // Q S and P U apart: the first is scaled by e^ca afterwards
+            auto qs_step = [&](int k0) {
+                uint32_t af[4], bf[4];
+                ldsm_x4(af, swz(Qt, 16 * mt + plain_r, k0 + plain_c));
+                ldsm_x4_trans(bf, Sb + (k0 + plain_r) * kPadB + 16 * nh + plain_c);
+                mma_bf16(oa[0], af, bf[0], bf[1]);
+                mma_bf16(oa[1], af, bf[2], bf[3]);
+            };
+            auto pu_step = [&](int k0) {
+                uint32_t af[4], bf[4];
+                ldsm_x4(af, swz(Pt, 16 * mt + plain_r, k0 + plain_c));
+                ldsm_x4_trans(bf, Ub + (k0 + plain_r) * kPadB + 16 * nh + plain_c);
+                mma_bf16(ob[0], af, bf[0], bf[1]);
+                mma_bf16(ob[1], af, bf[2], bf[3]);
+            };
 #pragma unroll
-            for (int k0 = 0; k0 < kC; k0 += 16) {
+            for (int j = 0; j < 4; j++) {
+                const int k0 = 16 * j;
                 uint32_t af[4], b0[4], b1[4];
-                ldsm_x4_trans(af, Kh + (k0 + flip_r) * kPadH + 16 * warp + flip_c);
+                ldsm_x4_trans(af, swz(Kt, k0 + flip_r, 16 * warp + flip_c));
                 ldsm_x4_trans(b0, Ud + (k0 + plain_r) * kPadB + plain_c);
                 ldsm_x4_trans(b1, Ud + (k0 + plain_r) * kPadB + 16 + plain_c);
                 mma_bf16(state[0], af, b0[0], b0[1]);
                 mma_bf16(state[1], af, b0[2], b0[3]);
                 mma_bf16(state[2], af, b1[0], b1[1]);
                 mma_bf16(state[3], af, b1[2], b1[3]);
+                if (o) {
+                    qs_step(32 * j);
+                    pu_step(16 * j);
+                    qs_step(32 * j + 16);
+                }
             }
             put_state(Sb2 + ((chunk + 1) & 1) * kDK * kPadB, state);
-        }
-
-        // o = e^ca (Q S) + P U, off the chain
-        if (o) {
-            if (more) cp_async_wait_but_one();   // Q and P (the next chunk's W and K run on)
-            else cp_async_wait_all();
-            __syncthreads();
-            float oa[2][4] = {};
+            if (o) {
+                const float e0 = eca[16 * mt + g], e1 = eca[16 * mt + g + 8];
 #pragma unroll
-            for (int k0 = 0; k0 < kDK; k0 += 16) {
-                uint32_t af[4], bf[4];
-                ldsm_x4(af, Qh + (16 * mt + plain_r) * kPadH + k0 + plain_c);
-                ldsm_x4_trans(bf, Sb + (k0 + plain_r) * kPadB + 16 * nh + plain_c);
-                mma_bf16(oa[0], af, bf[0], bf[1]);
-                mma_bf16(oa[1], af, bf[2], bf[3]);
-            }
-            const float e0 = eca[16 * mt + g], e1 = eca[16 * mt + g + 8];
+                for (int nt = 0; nt < 2; nt++) {
+                    oa[nt][0] = fmaf(oa[nt][0], e0, ob[nt][0]); oa[nt][1] = fmaf(oa[nt][1], e0, ob[nt][1]);
+                    oa[nt][2] = fmaf(oa[nt][2], e1, ob[nt][2]); oa[nt][3] = fmaf(oa[nt][3], e1, ob[nt][3]);
+                }
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++) { oa[nt][0] *= e0; oa[nt][1] *= e0; oa[nt][2] *= e1; oa[nt][3] *= e1; }
+                for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-            for (int k0 = 0; k0 < kC; k0 += 16) {
-                uint32_t af[4], bf[4];
-                ldsm_x4(af, Ph + (16 * mt + plain_r) * kPadP + k0 + plain_c);
-                ldsm_x4_trans(bf, Ub + (k0 + plain_r) * kPadB + 16 * nh + plain_c);
-                mma_bf16(oa[0], af, bf[0], bf[1]);
-                mma_bf16(oa[1], af, bf[2], bf[3]);
-            }
-#pragma unroll
-            for (int nt = 0; nt < 2; nt++)
-#pragma unroll
-                for (int e = 0; e < 4; e++)
-                    Oh[(16 * nh + 8 * nt + 2 * t4 + (e & 1)) * kPadP + 16 * mt + g + 8 * (e >> 1)] = __float2bfloat16_rn(oa[nt][e]);
-            __syncthreads();   // every reader of Q and P is done
-            if (more) {
-                copy_rows(Qh, q, row0 + kC);
-                copy_p(chunk + 1);
-                cp_async_commit();
+                    for (int e = 0; e < 4; e++)
+                        Oh[(16 * nh + 8 * nt + 2 * t4 + (e & 1)) * kPadP + 16 * mt + g + 8 * (e >> 1)] = __float2bfloat16_rn(oa[nt][e]);
             }
         }
     }
@@ -1171,9 +1206,42 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     }
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// A [rows][cols] BFloat16 array as a tensor map of 64 x 64 boxes, 128-byte swizzle.
+int scan_tmap(CUtensorMap *map, const void *base, long long rows, int cols) {
+    static std::mutex lock;
+    static EncodeTiledFn fn = nullptr;
+    {
+        std::lock_guard<std::mutex> hold(lock);
+        if (!fn) {
+            void *sym = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            TB200_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+            if (!sym || qres != cudaDriverEntryPointSuccess) return TB200_ERR_UNSUPPORTED;
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        }
+    }
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+    cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kC)};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? TB200_OK : TB200_ERR_UNSUPPORTED;
+}
+
+// The forward scan's launch: tensor maps over W (scratch), Q, K and P (scratch), one block per (head, 64 features).
+int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, const float *a, const __nv_bfloat16 *w,
+                const __nv_bfloat16 *u, const __nv_bfloat16 *pw, __nv_bfloat16 *o, float *s_save, float *u_save,
+                cudaStream_t stream);
+
 constexpr size_t kChunkSmem = (2 * kC * kPadA + 3 * kC) * sizeof(float) + 3 * kC * kPadH * sizeof(__nv_bfloat16);
-constexpr size_t kScanSmem = 4 * kC * sizeof(float) +
-                             (2 * kDK * kPadB + 2 * kC * kPadB + 4 * kC * kPadH + kC * kPadP + kDVP * kPadP) * sizeof(__nv_bfloat16);
+constexpr size_t kScanSmem = 1024 + 2 * kTileSetBytes + 4 * kC * sizeof(float) +
+                             (kDVB / kDVP) * (2 * kDK * kPadB + 2 * kC * kPadB + kDVP * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdScanSmem = (kDK * kPadS + 3 * kC * kPadS + kC * kPadM + 3 * kC) * sizeof(float) +
                                 (2 * kC * kPadH + kC * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdXgSmem = (3 * kC * kPadF + kC) * sizeof(float);
@@ -1219,6 +1287,26 @@ extern "C" size_t tb200_deltanet_workspace_bytes(const tb200_deltanet_desc *d) {
     return rows * (kDK + kDV + kC) * sizeof(__nv_bfloat16);
 }
 
+namespace tb200 {
+namespace {
+int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, const float *a, const __nv_bfloat16 *w,
+                const __nv_bfloat16 *u, const __nv_bfloat16 *pw, __nv_bfloat16 *o, float *s_save, float *u_save,
+                cudaStream_t stream) {
+    const long long rows = static_cast<long long>(d->heads) * d->positions;
+    ScanMaps maps;
+    int st = scan_tmap(&maps.w, w, rows, kDK);
+    if (!st) st = scan_tmap(&maps.q, q, rows, kDK);
+    if (!st) st = scan_tmap(&maps.k, k, rows, kDK);
+    if (!st) st = scan_tmap(&maps.p, pw, rows, kC);
+    if (st) return st;
+    dim3 grid(static_cast<unsigned>(d->heads), kDV / kDVB);
+    deltanet_scan_kernel<<<grid, kScanThreads, kScanSmem, stream>>>(maps, a, u, o, s_save, u_save, d->positions);
+    TB200_CUDA(cudaGetLastError());
+    return TB200_OK;
+}
+}  // namespace
+}  // namespace tb200
+
 extern "C" int tb200_deltanet_fwd(const tb200_deltanet_desc *d, const void *q, const void *k, const void *v,
                                   const float *a, const float *beta, void *o, void *workspace, size_t workspace_bytes,
                                   void *stream_) {
@@ -1245,12 +1333,7 @@ extern "C" int tb200_deltanet_fwd(const tb200_deltanet_desc *d, const void *q, c
         static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k),
         static_cast<const __nv_bfloat16 *>(v), a, beta, w, u, pw, nullptr, T);
     TB200_CUDA(cudaGetLastError());
-    dim3 grid(static_cast<unsigned>(d->heads), kDV / kDVP);
-    deltanet_scan_kernel<<<grid, 256, kScanSmem, stream>>>(static_cast<const __nv_bfloat16 *>(q),
-                                                          static_cast<const __nv_bfloat16 *>(k), a, w, u, pw,
-                                                          static_cast<__nv_bfloat16 *>(o), nullptr, nullptr, T);
-    TB200_CUDA(cudaGetLastError());
-    return TB200_OK;
+    return launch_scan(d, q, k, a, w, u, pw, static_cast<__nv_bfloat16 *>(o), nullptr, nullptr, stream);
 }
 
 extern "C" size_t tb200_deltanet_bwd_workspace_bytes(const tb200_deltanet_desc *d) {
@@ -1298,8 +1381,7 @@ extern "C" int tb200_deltanet_bwd(const tb200_deltanet_desc *d, const void *q, c
     deltanet_chunk_kernel<<<chunks, 256, kChunkSmem, stream>>>(qb, kb, vb, a, beta, w, u, pw, minv, T);
     TB200_CUDA(cudaGetLastError());
     // no result pointer: the scan only carries the state
-    deltanet_scan_kernel<<<grid, 256, kScanSmem, stream>>>(qb, kb, a, w, u, pw, nullptr, s_save, u_save, T);
-    TB200_CUDA(cudaGetLastError());
+    if ((st = launch_scan(d, q, k, a, w, u, pw, nullptr, s_save, u_save, stream))) return st;
     deltanet_bwd_scan_kernel<<<grid, 256, kBwdScanSmem, stream>>>(qb, kb, a, beta, pw, minv, dob, dsin, dz,
                                                                   static_cast<__nv_bfloat16 *>(dv), T);
     TB200_CUDA(cudaGetLastError());
@@ -1310,4 +1392,14 @@ extern "C" int tb200_deltanet_bwd(const tb200_deltanet_desc *d, const void *q, c
                                                                  static_cast<__nv_bfloat16 *>(dk), da, dbeta, T);
     TB200_CUDA(cudaGetLastError());
     return TB200_OK;
+}
+
+// As tb200_device_error, for the DeltaNet scans (their tiles arrive by bulk copies on an mbarrier): 0, or 1 when a
+// wait gave up.
+extern "C" int tb200_deltanet_device_error(void) {
+    int code = 0, zero = 0;
+    TB200_CUDA(cudaDeviceSynchronize());
+    TB200_CUDA(cudaMemcpyFromSymbol(&code, tb200::g_deltanet_error, sizeof(int)));
+    if (code) TB200_CUDA(cudaMemcpyToSymbol(tb200::g_deltanet_error, &zero, sizeof(int)));
+    return code;
 }
