@@ -67,6 +67,7 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+constexpr int kGateFloats = 132;   // e^ca (64), e^(ca_C - ca) (64), e^ca_C, padded to a multiple of 16 bytes
 constexpr int kPadA = 68;   // Float32 row pitch of the 64 x 64 tiles A, (I + A)^-1 and the scratch beside them
 
 // 3xTF32: a Float32 operand as the sum of two TF32 values; hi*hi + lo*hi + hi*lo keeps about 21 bits of the product.
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
                                                              const __nv_bfloat16 *v, const float *a, const float *beta,
                                                              __nv_bfloat16 *w_out, __nv_bfloat16 *u_out,
                                                              __nv_bfloat16 *p_out, float *minv_save,
-                                                             int T) {
+                                                             float *gates_out, int T) {
     extern __shared__ float sm[];
     float *A = sm;                        // [64][68]
     float *Mi = A + kC * kPadA;           // [64][68]  (I + A)^-1
@@ -153,6 +154,14 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
         sk[tid] = b0 * __expf(lo); sk[tid + 32] = b1 * __expf(hi);
     }
     __syncthreads();
+    // what the scan across the chunks needs of the gates: e^ca, e^(ca_C - ca) and e^ca_C, kGateFloats a chunk
+    if (tid < kC) {
+        float *dst = gates_out + (static_cast<long long>(head) * chunks + chunk) * kGateFloats;
+        const float last = ca[kC - 1];
+        dst[tid] = __expf(ca[tid]);
+        dst[kC + tid] = __expf(last - ca[tid]);
+        if (tid == 0) dst[2 * kC] = __expf(last);
+    }
 
     // A = beta .* decay(t > s) .* (K K'), P = decay(t >= s) .* (Q K') on the tensor cores: the operands are BFloat16 as
     // they arrive, so the products are exact and only the order of the Float32 additions differs from a sequential
@@ -346,16 +355,15 @@ __device__ __forceinline__ const unsigned char *swz(const unsigned char *tile, i
     return tile + (col >> 6) * kBoxBytes + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4);
 }
 
-__global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __grid_constant__ ScanMaps maps, const float *a,
+__global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __grid_constant__ ScanMaps maps,
+                                                                     const float *gates_in,
                                                                      const __nv_bfloat16 *u_in, __nv_bfloat16 *o,
                                                                      float *s_save, float *u_save, int T) {
     extern __shared__ unsigned char sm_raw[];
     // the tiles want 1024-byte alignment (the swizzle's period); the launch asks for 1 KB more than the layout
     unsigned char *tiles = sm_raw + ((1024u - (sm100::smem_u32(sm_raw) & 1023u)) & 1023u);   // [2][7 boxes]
-    float *eca2 = reinterpret_cast<float *>(tiles + 2 * kTileSetBytes);   // [2][64] exp(ca), per chunk parity
-    float *ekd2 = eca2 + 2 * kC;                                          // [2][64] exp(ca_C - ca)
-    __nv_bfloat16 *group_base = reinterpret_cast<__nv_bfloat16 *>(ekd2 + 2 * kC);
-    __shared__ float gamma_sm[2];
+    float *gate2 = reinterpret_cast<float *>(tiles + 2 * kTileSetBytes);   // [2][kGateFloats] the chunk's gates, per parity
+    __nv_bfloat16 *group_base = reinterpret_cast<__nv_bfloat16 *>(gate2 + 2 * kGateFloats);
     __shared__ __align__(8) uint64_t tile_full[2];
 
     const int head = blockIdx.x;
@@ -379,13 +387,15 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __gri
     const long long head_row = static_cast<long long>(head) * T;
     // A chunk's tiles arrive by TMA, seven boxes (four without a result to form) issued by one thread and counted in
     // bytes on the buffer's mbarrier.
-    const uint32_t tile_bytes = (o ? 7u : 4u) * kBoxBytes;
+    const uint32_t tile_bytes = (o ? 7u : 4u) * kBoxBytes + kGateFloats * 4u;
     auto copy_tiles = [&](int chunk) {
         if (tid != 0) return;
         unsigned char *set = tiles + (chunk & 1) * kTileSetBytes;
         uint64_t *bar = &tile_full[chunk & 1];
         const int row = static_cast<int>(head_row) + chunk * kC;
         sm100::mbar_arrive_expect_tx(bar, tile_bytes);
+        sm100::bulk_load(gate2 + (chunk & 1) * kGateFloats, gates_in + (static_cast<long long>(head) * chunks + chunk) * kGateFloats,
+                         kGateFloats * 4, bar);
         sm100::tma_load_2d(set, &maps.w, bar, 0, row);
         sm100::tma_load_2d(set + kBoxBytes, &maps.w, bar, 64, row);
         sm100::tma_load_2d(set + 4 * kBoxBytes, &maps.k, bar, 0, row);
@@ -415,34 +425,16 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __gri
             }
         }
     };
-    // warp 0 of the block keeps the gates of the chunk after next in two registers, so that a chunk's running sums
-    // start from values that are already here (a load at this point would sit on the chain of chunks)
-    float gate_lo = 0.0f, gate_hi = 0.0f;
-    auto fetch_gates = [&](int chunk) {
-        if (chunk < chunks) {
-            gate_lo = __ldg(a + head_row + static_cast<long long>(chunk) * kC + lane);
-            gate_hi = __ldg(a + head_row + static_cast<long long>(chunk) * kC + lane + 32);
-        }
-    };
-    auto gates = [&](int chunk) {   // warp 0 of the block, from the fetched values
-        float lo = gate_lo, hi = gate_hi;
-        chunk_cumsum_of(lane, lo, hi);
-        const float last = __shfl_sync(0xffffffffu, hi, 31);
-        float *eca = eca2 + (chunk & 1) * kC, *ekd = ekd2 + (chunk & 1) * kC;
-        eca[lane] = __expf(lo); eca[lane + 32] = __expf(hi);
-        ekd[lane] = __expf(last - lo); ekd[lane + 32] = __expf(last - hi);
-        if (lane == 0) gamma_sm[chunk & 1] = __expf(last);
-    };
-    auto fetch_ut = [&](int chunk, float (&acc)[2][4]) {   // Ut at this thread's accumulator positions
+    // Ut at this thread's accumulator positions, as the packed pairs they are stored in: unpacked where they are
+    // used, a chunk later, so that nothing waits for these loads where they are issued
+    auto fetch_ut = [&](int chunk, uint32_t (&raw)[2][2]) {
         const long long row0 = head_row + static_cast<long long>(chunk) * kC;
 #pragma unroll
         for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-            for (int hr = 0; hr < 2; hr++) {
-                const uint32_t two = __ldg(reinterpret_cast<const uint32_t *>(
+            for (int hr = 0; hr < 2; hr++)
+                raw[nt][hr] = __ldg(reinterpret_cast<const uint32_t *>(
                     u_in + (row0 + 16 * mt + g + 8 * hr) * kDV + part * kDVP + 16 * nh + 8 * nt + 2 * t4));
-                unpack_bf16x2(two, acc[nt][2 * hr], acc[nt][2 * hr + 1]);
-            }
     };
     // the state rows of this warp as an operand copy: rows 16 warp + g (+8), columns 8 nt + 2 t4 (+1)
     auto put_state = [&](__nv_bfloat16 *Sb, const float (&st)[4][4]) {
@@ -459,7 +451,7 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __gri
     };
 
     float state[4][4] = {};
-    float acc[2][4];
+    uint32_t ut_raw[2][2];
     put_state(Sb2, state);
     if (tid == 0) {
         sm100::mbar_init(&tile_full[0], 1);
@@ -469,16 +461,11 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __gri
     __syncthreads();
     if (chunks > 0) {
         copy_tiles(0);
-        if (tid < 32) {
-            fetch_gates(0);
-            gates(0);
-            fetch_gates(1);
-        }
-        fetch_ut(0, acc);
+        fetch_ut(0, ut_raw);
     }
     for (int chunk = 0; chunk < chunks; chunk++) {
         const long long row0 = head_row + static_cast<long long>(chunk) * kC;
-        const float *eca = eca2 + (chunk & 1) * kC, *ekd = ekd2 + (chunk & 1) * kC;
+        const float *eca = gate2 + (chunk & 1) * kGateFloats, *ekd = eca + kC;
         const unsigned char *Wt = tiles + (chunk & 1) * kTileSetBytes, *Qt = Wt + 2 * kBoxBytes, *Kt = Wt + 4 * kBoxBytes,
                             *Pt = Wt + 6 * kBoxBytes;
         const __nv_bfloat16 *Sb = Sb2 + (chunk & 1) * kDK * kPadB;
@@ -519,7 +506,9 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __gri
             for (int nt = 0; nt < 2; nt++)
 #pragma unroll
                 for (int hr = 0; hr < 2; hr++) {
-                    const float2 u2 = make_float2(acc[nt][2 * hr] - ws[nt][2 * hr], acc[nt][2 * hr + 1] - ws[nt][2 * hr + 1]);
+                    float ut0, ut1;
+                    unpack_bf16x2(ut_raw[nt][hr], ut0, ut1);
+                    const float2 u2 = make_float2(ut0 - ws[nt][2 * hr], ut1 - ws[nt][2 * hr + 1]);
                     const int row = 16 * mt + g + 8 * hr, col = 16 * nh + 8 * nt + 2 * t4;
                     const float ed = ekd[row];
                     *reinterpret_cast<uint32_t *>(Ub + row * kPadB + col) = pack_bf16x2(u2.x, u2.y);
@@ -528,20 +517,14 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __gri
                 }
         }
         __syncthreads();   // U is complete
-        if (more) {
-            if (tid < 32) {
-                gates(chunk + 1);
-                fetch_gates(chunk + 2);
-            }
-            fetch_ut(chunk + 1, acc);
-        }
+        if (more) fetch_ut(chunk + 1, ut_raw);
 
         // S <- e^{ca_C} S + K' (e^{ca_C - ca} U): warp -> 16 state rows, all 32 features; then the operand copy for
         // the next chunk (the other buffer: this chunk's output product still reads the current one).
         // o = e^ca (Q S) + P U is off the chain: its MMAs are issued between the update's, whose four accumulators
         // each wait for their own previous step, so that the tensor pipe has independent work in the gaps.
         {
-            const float gamma = gamma_sm[chunk & 1];
+            const float gamma = eca[2 * kC];
 #pragma unroll
             for (int nt = 0; nt < 4; nt++)
 #pragma unroll
@@ -1235,12 +1218,12 @@ int scan_tmap(CUtensorMap *map, const void *base, long long rows, int cols) {
 }
 
 // The forward scan's launch: tensor maps over W (scratch), Q, K and P (scratch), one block per (head, 64 features).
-int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, const float *a, const __nv_bfloat16 *w,
+int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, const float *gates, const __nv_bfloat16 *w,
                 const __nv_bfloat16 *u, const __nv_bfloat16 *pw, __nv_bfloat16 *o, float *s_save, float *u_save,
                 cudaStream_t stream);
 
 constexpr size_t kChunkSmem = (2 * kC * kPadA + 3 * kC) * sizeof(float) + 3 * kC * kPadH * sizeof(__nv_bfloat16);
-constexpr size_t kScanSmem = 1024 + 2 * kTileSetBytes + 4 * kC * sizeof(float) +
+constexpr size_t kScanSmem = 1024 + 2 * kTileSetBytes + 2 * kGateFloats * sizeof(float) +
                              (kDVB / kDVP) * (2 * kDK * kPadB + 2 * kC * kPadB + kDVP * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdScanSmem = (kDK * kPadS + 3 * kC * kPadS + kC * kPadM + 3 * kC) * sizeof(float) +
                                 (2 * kC * kPadH + kC * kPadP) * sizeof(__nv_bfloat16);
@@ -1284,12 +1267,12 @@ constexpr size_t kBwdRowBytes = (kC /*Minv*/ + kDK * kDV / kC /*S*/ + kDV /*U*/ 
 extern "C" size_t tb200_deltanet_workspace_bytes(const tb200_deltanet_desc *d) {
     if (check_deltanet(d) != TB200_OK) return 0;
     const size_t rows = static_cast<size_t>(d->heads) * d->positions;
-    return rows * (kDK + kDV + kC) * sizeof(__nv_bfloat16);
+    return rows * (kDK + kDV + kC) * sizeof(__nv_bfloat16) + rows / kC * kGateFloats * sizeof(float);
 }
 
 namespace tb200 {
 namespace {
-int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, const float *a, const __nv_bfloat16 *w,
+int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, const float *gates, const __nv_bfloat16 *w,
                 const __nv_bfloat16 *u, const __nv_bfloat16 *pw, __nv_bfloat16 *o, float *s_save, float *u_save,
                 cudaStream_t stream) {
     const long long rows = static_cast<long long>(d->heads) * d->positions;
@@ -1300,7 +1283,7 @@ int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, cons
     if (!st) st = scan_tmap(&maps.p, pw, rows, kC);
     if (st) return st;
     dim3 grid(static_cast<unsigned>(d->heads), kDV / kDVB);
-    deltanet_scan_kernel<<<grid, kScanThreads, kScanSmem, stream>>>(maps, a, u, o, s_save, u_save, d->positions);
+    deltanet_scan_kernel<<<grid, kScanThreads, kScanSmem, stream>>>(maps, gates, u, o, s_save, u_save, d->positions);
     TB200_CUDA(cudaGetLastError());
     return TB200_OK;
 }
@@ -1327,13 +1310,14 @@ extern "C" int tb200_deltanet_fwd(const tb200_deltanet_desc *d, const void *q, c
     __nv_bfloat16 *w = static_cast<__nv_bfloat16 *>(workspace);
     __nv_bfloat16 *u = w + rows * kDK;
     __nv_bfloat16 *pw = u + rows * kDV;
+    float *gates = reinterpret_cast<float *>(pw + rows * kC);
     const int T = d->positions;
     const unsigned chunks = static_cast<unsigned>(d->heads) * (T / kC);
     deltanet_chunk_kernel<<<chunks, 256, kChunkSmem, stream>>>(
         static_cast<const __nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k),
-        static_cast<const __nv_bfloat16 *>(v), a, beta, w, u, pw, nullptr, T);
+        static_cast<const __nv_bfloat16 *>(v), a, beta, w, u, pw, nullptr, gates, T);
     TB200_CUDA(cudaGetLastError());
-    return launch_scan(d, q, k, a, w, u, pw, static_cast<__nv_bfloat16 *>(o), nullptr, nullptr, stream);
+    return launch_scan(d, q, k, gates, w, u, pw, static_cast<__nv_bfloat16 *>(o), nullptr, nullptr, stream);
 }
 
 extern "C" size_t tb200_deltanet_bwd_workspace_bytes(const tb200_deltanet_desc *d) {
@@ -1364,7 +1348,8 @@ extern "C" int tb200_deltanet_bwd(const tb200_deltanet_desc *d, const void *q, c
     __nv_bfloat16 *w = static_cast<__nv_bfloat16 *>(workspace);
     __nv_bfloat16 *u = w + rows * kDK;
     __nv_bfloat16 *pw = u + rows * kDV;
-    float *minv = reinterpret_cast<float *>(pw + rows * kC);
+    float *gates = reinterpret_cast<float *>(pw + rows * kC);
+    float *minv = gates + rows / kC * kGateFloats;
     float *s_save = minv + rows * kC;
     float *u_save = s_save + rows * (kDK * kDV / kC);
     float *dsin = u_save + rows * kDV;
@@ -1378,10 +1363,10 @@ extern "C" int tb200_deltanet_bwd(const tb200_deltanet_desc *d, const void *q, c
     dim3 grid(static_cast<unsigned>(d->heads), kDV / kDVP);
 
     // the forward again, keeping what the pullback needs: (I + A)^-1, the state at every chunk start, U
-    deltanet_chunk_kernel<<<chunks, 256, kChunkSmem, stream>>>(qb, kb, vb, a, beta, w, u, pw, minv, T);
+    deltanet_chunk_kernel<<<chunks, 256, kChunkSmem, stream>>>(qb, kb, vb, a, beta, w, u, pw, minv, gates, T);
     TB200_CUDA(cudaGetLastError());
     // no result pointer: the scan only carries the state
-    if ((st = launch_scan(d, q, k, a, w, u, pw, nullptr, s_save, u_save, stream))) return st;
+    if ((st = launch_scan(d, q, k, gates, w, u, pw, nullptr, s_save, u_save, stream))) return st;
     deltanet_bwd_scan_kernel<<<grid, 256, kBwdScanSmem, stream>>>(qb, kb, a, beta, pw, minv, dob, dsin, dz,
                                                                   static_cast<__nv_bfloat16 *>(dv), T);
     TB200_CUDA(cudaGetLastError());
