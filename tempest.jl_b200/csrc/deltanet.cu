@@ -836,55 +836,6 @@ __global__ void __launch_bounds__(256) deltanet_bwd_xg_kernel(const float *a, co
     }
 }
 
-// ---- fragment loaders for mma_tf32 (g = lane / 4, t = lane % 4) ----
-// A from a Float32 tile, rows r0 + g (+8), columns k0 + t (+4)
-__device__ __forceinline__ void frag_a_f32(uint32_t (&f)[4], const float *tile, int pitch, int r0, int k0, int g, int t) {
-    const float *p = tile + (r0 + g) * pitch + k0 + t;
-    f[0] = tf32_of(p[0]); f[1] = tf32_of(p[8 * pitch]); f[2] = tf32_of(p[4]); f[3] = tf32_of(p[8 * pitch + 4]);
-}
-// A transposed from a Float32 tile: A[m][k] = tile[k][m], optionally scaled per k by `scale[k]`
-__device__ __forceinline__ void frag_at_f32(uint32_t (&f)[4], const float *tile, int pitch, int r0, int k0, int g, int t,
-                                            const float *scale) {
-    const float *p = tile + (k0 + t) * pitch + r0 + g;
-    const float s0 = scale ? scale[k0 + t] : 1.0f, s1 = scale ? scale[k0 + t + 4] : 1.0f;
-    f[0] = tf32_of(p[0] * s0); f[1] = tf32_of(p[8] * s0); f[2] = tf32_of(p[4 * pitch] * s1); f[3] = tf32_of(p[4 * pitch + 8] * s1);
-}
-// A from a BFloat16 tile (exact in TF32)
-__device__ __forceinline__ void frag_a_bf16(uint32_t (&f)[4], const __nv_bfloat16 *tile, int pitch, int r0, int k0, int g, int t) {
-    const __nv_bfloat16 *p = tile + (r0 + g) * pitch + k0 + t;
-    f[0] = tf32_of_bf16(p); f[1] = tf32_of_bf16(p + 8 * pitch); f[2] = tf32_of_bf16(p + 4); f[3] = tf32_of_bf16(p + 8 * pitch + 4);
-}
-
-// acc[nt] += A(16 x 8) * B for the eight 8-column tiles n0 + 8 nt, B[k][n] = tile[n][k] (a Float32 tile read "by rows of n")
-__device__ __forceinline__ void mma_row_nk(float (&acc)[8][4], const uint32_t (&af)[4], const float *tile, int pitch, int n0, int k0, int g,
-                                           int t) {
-#pragma unroll
-    for (int nt = 0; nt < 8; nt++) {
-        const float *p = tile + (n0 + 8 * nt + g) * pitch + k0 + t;
-        mma_tf32(acc[nt], af, tf32_of(p[0]), tf32_of(p[4]));
-    }
-}
-// two A operands against the same B[k][n] = tile[n][k]
-__device__ __forceinline__ void mma2_row_nk(float (&acc0)[8][4], float (&acc1)[8][4], const uint32_t (&a0)[4], const uint32_t (&a1)[4],
-                                            const float *tile, int pitch, int n0, int k0, int g, int t) {
-#pragma unroll
-    for (int nt = 0; nt < 8; nt++) {
-        const float *p = tile + (n0 + 8 * nt + g) * pitch + k0 + t;
-        const uint32_t b0 = tf32_of(p[0]), b1 = tf32_of(p[4]);
-        mma_tf32(acc0[nt], a0, b0, b1);
-        mma_tf32(acc1[nt], a1, b0, b1);
-    }
-}
-// B[k][n] = tile[k][n] from a Float32 tile
-__device__ __forceinline__ void mma_row_kn(float (&acc)[8][4], const uint32_t (&af)[4], const float *tile, int pitch, int n0, int k0, int g,
-                                           int t) {
-#pragma unroll
-    for (int nt = 0; nt < 8; nt++) {
-        const float *p = tile + (k0 + t) * pitch + n0 + 8 * nt + g;
-        mma_tf32(acc[nt], af, tf32_of(p[0]), tf32_of(p[4 * pitch]));
-    }
-}
-
 // sum over a row's columns held by the four lanes that share g
 __device__ __forceinline__ float sum_quad(float v) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);
@@ -892,29 +843,32 @@ __device__ __forceinline__ float sum_quad(float v) {
     return v;
 }
 
-// dQ, dK, da, dbeta of one chunk; one block per (head, chunk).  The eight products of the chunk are TF32
-// warp-level MMAs: warp w takes positions 16 (w % 4) .. + 15 and features 64 (w / 4) .. + 63 of every
-// (position, feature) result, i.e. eight 16 x 8 accumulator tiles per product; a thread holds rows
-// g, g + 8 and columns 2 t, 2 t + 1 of each tile.  Row sums of products of results with Q or K (the gate and
-// beta gradients) are taken on the accumulators and meet through shared memory.
-constexpr int kPadX = 68;   // Float32 row pitch of X and G: both their rows and their columns are read as A operands
-
-__global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
+// dQ, dK, da, dbeta of one chunk; one block per (head, chunk), two blocks per SM.  The eight products of the chunk
+// are BFloat16 m16n8k16 MMAs whose fragments come through ldmatrix: the Float32 arrays the scans left (the state, its
+// gradient, U, dZ, X, G) are rounded to BFloat16 as they are staged in shared memory -- the rounding the reference
+// gives the Float32 factor of a mixed product (ext/cuTileExt/emit.jl:914-921) -- and Q, K, dO are BFloat16 already.
+// (As TF32 MMAs with one scalar load and one conversion per fragment element this kernel took half the pullback's
+// time: the warp-level MMA issues once in about 16 cycles per SM quarter on this part, whatever its operand type,
+// so halving the number of MMAs and dropping the conversions is what pays.)  Warp w takes positions
+// 16 (w % 4) .. + 15 and features 64 (w / 4) .. + 63 of every (position, feature) result, i.e. eight 16 x 8
+// accumulator tiles per product; a thread holds rows g, g + 8 and columns 2 t, 2 t + 1 of each tile.  Row sums of
+// products of results with Q or K (the gate and beta gradients) are taken on the accumulators and meet through
+// shared memory.  X, G and beta .* G take the state's place once the products with the state are done.
+__global__ void __launch_bounds__(256, 2) deltanet_bwd_out_kernel(
     const __nv_bfloat16 *q, const __nv_bfloat16 *k, const __nv_bfloat16 *v, const float *a, const float *beta,
     const __nv_bfloat16 *dout, const float *s_save, const float *dsin_save, const float *u_save, const float *dz_save,
     const float *x_in, const float *g_in, __nv_bfloat16 *dq, __nv_bfloat16 *dk, float *da, float *dbeta, int T) {
     extern __shared__ float sm[];
-    float *Sb = sm;                        // [128][132]: S, then dS'
-    float *M0 = Sb + kDK * kPadF;          // [64][132]: dO, then U, then the dQ staging
-    float *M1 = M0 + kC * kPadF;           // [64][132]: dZ, then the dK staging
-    float *Xs = M1 + kC * kPadF;           // [64][68]
-    float *Gs = Xs + kC * kPadX;           // [64][68]
-    float *vec = Gs + kC * kPadX;
+    float *vec = sm;
     float *eca = vec, *ekd = vec + 64, *be = vec + 128;
     float *part = vec + 192;               // [7 sums][2 feature halves][64 rows]
     float *red = part + 7 * 128;           // [8]
-    __nv_bfloat16 *Qh = reinterpret_cast<__nv_bfloat16 *>(red + 8);   // [64][136]
+    __nv_bfloat16 *Sh = reinterpret_cast<__nv_bfloat16 *>(red + 8);   // [128][136]: S, then dS'; then X, G, beta G [64][72] each
+    __nv_bfloat16 *M0 = Sh + kDK * kPadH;   // [64][136]: dO, then U, then the dQ staging
+    __nv_bfloat16 *M1 = M0 + kC * kPadH;    // [64][136]: dZ, then the dK staging
+    __nv_bfloat16 *Qh = M1 + kC * kPadH;    // [64][136]
     __nv_bfloat16 *Kh = Qh + kC * kPadH;
+    __nv_bfloat16 *Xh = Sh, *Gh = Xh + kC * kPadP, *Gb = Gh + kC * kPadP;
     __shared__ float gamma_sm;
     enum { DE = 0, DED, RQ, RK, CQ, CK, RDZ };
 
@@ -925,31 +879,37 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t4 = lane & 3;
     const int m0 = 16 * (warp & 3), nh = warp >> 2, n0 = 64 * nh;
+    const int plain_r = (lane & 7) + 8 * ((lane >> 3) & 1), plain_c = 8 * (lane >> 4);
+    const int flip_r = (lane & 7) + 8 * (lane >> 4), flip_c = 8 * ((lane >> 3) & 1);
 
-    for (int i = tid; i < kDK * kDV / 4; i += 256) {
-        const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
-        *reinterpret_cast<float4 *>(Sb + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(s_save + cidx * kDK * kDV + r * kDV + c));
+    // eight Float32 values from global memory, rounded, as one 16-byte piece of a BFloat16 tile
+    auto round8 = [](const float *src) {
+        const float4 lo = __ldg(reinterpret_cast<const float4 *>(src)), hi = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        return make_uint4(pack_bf16x2(lo.x, lo.y), pack_bf16x2(lo.z, lo.w), pack_bf16x2(hi.x, hi.y), pack_bf16x2(hi.z, hi.w));
+    };
+    for (int i = tid; i < kDK * kDV / 8; i += 256) {
+        const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
+        *reinterpret_cast<uint4 *>(Sh + r * kPadH + c) = round8(s_save + cidx * kDK * kDV + r * kDV + c);
     }
-    for (int i = tid; i < kDV * kC / 8; i += 256) {
+    for (int i = tid; i < kDV * kC / 8; i += 256) {   // dO arrives [feature][position]: turned as it is staged
         const int f = i >> 3, t8 = (i & 7) * 8;
-        float dv8[8];
-        Access<__nv_bfloat16, true>::load_cached(dout + (static_cast<long long>(head) * kDV + f) * T + static_cast<long long>(chunk) * kC + t8, dv8);
+        const uint4 d8 = __ldg(reinterpret_cast<const uint4 *>(dout + (static_cast<long long>(head) * kDV + f) * T +
+                                                               static_cast<long long>(chunk) * kC + t8));
+        const uint32_t w4[4] = {d8.x, d8.y, d8.z, d8.w};
 #pragma unroll
-        for (int e = 0; e < 8; e++) M0[(t8 + e) * kPadF + f] = dv8[e];
+        for (int e = 0; e < 4; e++) {
+            reinterpret_cast<unsigned short *>(M0)[(t8 + 2 * e) * kPadH + f] = static_cast<unsigned short>(w4[e] & 0xffffu);
+            reinterpret_cast<unsigned short *>(M0)[(t8 + 2 * e + 1) * kPadH + f] = static_cast<unsigned short>(w4[e] >> 16);
+        }
     }
-    for (int i = tid; i < kC * kDV / 4; i += 256) {
-        const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
-        *reinterpret_cast<float4 *>(M1 + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(dz_save + (row0 + r) * kDV + c));
+    for (int i = tid; i < kC * kDV / 8; i += 256) {
+        const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
+        *reinterpret_cast<uint4 *>(M1 + r * kPadH + c) = round8(dz_save + (row0 + r) * kDV + c);
     }
     for (int i = tid; i < kC * kDK / 8; i += 256) {
         const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
         *reinterpret_cast<uint4 *>(Qh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(q + (row0 + r) * kDK + c));
         *reinterpret_cast<uint4 *>(Kh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(k + (row0 + r) * kDK + c));
-    }
-    for (int i = tid; i < kC * kC / 4; i += 256) {
-        const int r = i / (kC / 4), c = (i % (kC / 4)) * 4;
-        *reinterpret_cast<float4 *>(Xs + r * kPadX + c) = __ldg(reinterpret_cast<const float4 *>(x_in + row0 * kC + r * kC + c));
-        *reinterpret_cast<float4 *>(Gs + r * kPadX + c) = __ldg(reinterpret_cast<const float4 *>(g_in + row0 * kC + r * kC + c));
     }
     if (tid < kC) be[tid] = beta[row0 + tid];
     if (tid < 32) {
@@ -984,17 +944,49 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
         r1 = sum_quad(r1);
         if (t4 == 0) { part[(which * 2 + nh) * 64 + t0] = r0; part[(which * 2 + nh) * 64 + t1] = r1; }
     };
+    // acc += A B over k0 .. k0 + 15 for this warp's eight feature tiles.  B stored [n][k] (rows of features, the summed
+    // axis contiguous) is read as it lies; B stored [k][n] is read transposed.
+    auto step_nk = [&](float (&acc)[8][4], const uint32_t (&af)[4], const __nv_bfloat16 *tile, int pitch, int k0) {
+#pragma unroll
+        for (int np = 0; np < 4; np++) {
+            uint32_t bf[4];
+            ldsm_x4(bf, tile + (n0 + 16 * np + flip_r) * pitch + k0 + flip_c);
+            mma_bf16(acc[2 * np], af, bf[0], bf[1]);
+            mma_bf16(acc[2 * np + 1], af, bf[2], bf[3]);
+        }
+    };
+    auto step2_nk = [&](float (&acc0)[8][4], float (&acc1)[8][4], const uint32_t (&a0)[4], const uint32_t (&a1)[4],
+                        const __nv_bfloat16 *tile, int pitch, int k0) {
+#pragma unroll
+        for (int np = 0; np < 4; np++) {
+            uint32_t bf[4];
+            ldsm_x4(bf, tile + (n0 + 16 * np + flip_r) * pitch + k0 + flip_c);
+            mma_bf16(acc0[2 * np], a0, bf[0], bf[1]);
+            mma_bf16(acc0[2 * np + 1], a0, bf[2], bf[3]);
+            mma_bf16(acc1[2 * np], a1, bf[0], bf[1]);
+            mma_bf16(acc1[2 * np + 1], a1, bf[2], bf[3]);
+        }
+    };
+    auto step_kn = [&](float (&acc)[8][4], const uint32_t (&af)[4], const __nv_bfloat16 *tile, int pitch, int k0) {
+#pragma unroll
+        for (int np = 0; np < 4; np++) {
+            uint32_t bf[4];
+            ldsm_x4_trans(bf, tile + (k0 + plain_r) * pitch + n0 + 16 * np + plain_c);
+            mma_bf16(acc[2 * np], af, bf[0], bf[1]);
+            mma_bf16(acc[2 * np + 1], af, bf[2], bf[3]);
+        }
+    };
 
     float dqa[8][4], dka[8][4];
     // phase 1: T1 = dO S', T2 = dZ S' (one sweep over the state's rows for both)
     {
         float t1a[8][4] = {}, t2a[8][4] = {};
 #pragma unroll 2
-        for (int k0 = 0; k0 < kDV; k0 += 8) {
+        for (int k0 = 0; k0 < kDV; k0 += 16) {
             uint32_t a0[4], a1[4];
-            frag_a_f32(a0, M0, kPadF, m0, k0, g, t4);
-            frag_a_f32(a1, M1, kPadF, m0, k0, g, t4);
-            mma2_row_nk(t1a, t2a, a0, a1, Sb, kPadF, n0, k0, g, t4);
+            ldsm_x4(a0, M0 + (m0 + plain_r) * kPadH + k0 + plain_c);
+            ldsm_x4(a1, M1 + (m0 + plain_r) * kPadH + k0 + plain_c);
+            step2_nk(t1a, t2a, a0, a1, Sh, kPadH, k0);
         }
         float q0, q1, k0s, k1s;
         dot_rows(Qh, t1a, q0, q1);
@@ -1011,22 +1003,23 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     {
         float ks[8][4] = {};
 #pragma unroll 2
-        for (int k0 = 0; k0 < kDK; k0 += 8) {
+        for (int k0 = 0; k0 < kDK; k0 += 16) {
             uint32_t af[4];
-            frag_a_bf16(af, Kh, kPadH, m0, k0, g, t4);
-            mma_row_kn(ks, af, Sb, kPadF, n0, k0, g, t4);
+            ldsm_x4(af, Kh + (m0 + plain_r) * kPadH + k0 + plain_c);
+            step_kn(ks, af, Sh, kPadH, k0);
         }
         const float e0 = eca[t0], e1 = eca[t1];
         float r0 = 0.0f, r1 = 0.0f;
 #pragma unroll
         for (int nt = 0; nt < 8; nt++) {
             const int col = n0 + 8 * nt + 2 * t4;
-            float v00, v01, v10, v11;
+            float v00, v01, v10, v11, z00, z01, z10, z11;
             unpack_bf16x2(__ldg(reinterpret_cast<const uint32_t *>(v + (row0 + t0) * kDV + col)), v00, v01);
             unpack_bf16x2(__ldg(reinterpret_cast<const uint32_t *>(v + (row0 + t1) * kDV + col)), v10, v11);
-            const float2 z0 = *reinterpret_cast<const float2 *>(M1 + t0 * kPadF + col), z1 = *reinterpret_cast<const float2 *>(M1 + t1 * kPadF + col);
-            r0 += z0.x * (v00 - e0 * ks[nt][0]) + z0.y * (v01 - e0 * ks[nt][1]);
-            r1 += z1.x * (v10 - e1 * ks[nt][2]) + z1.y * (v11 - e1 * ks[nt][3]);
+            unpack_bf16x2(*reinterpret_cast<const uint32_t *>(M1 + t0 * kPadH + col), z00, z01);
+            unpack_bf16x2(*reinterpret_cast<const uint32_t *>(M1 + t1 * kPadH + col), z10, z11);
+            r0 += z00 * (v00 - e0 * ks[nt][0]) + z01 * (v01 - e0 * ks[nt][1]);
+            r1 += z10 * (v10 - e1 * ks[nt][2]) + z11 * (v11 - e1 * ks[nt][3]);
         }
         put_rows(RDZ, r0, r1);
     }
@@ -1035,17 +1028,21 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     // phase 2: dS' replaces S (their inner product is the gradient of g), U replaces dO; T3 = U dS''
     {
         float dgp = 0.0f;
-        for (int i = tid; i < kDK * kDV / 4; i += 256) {
-            const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
-            const float4 nw = __ldg(reinterpret_cast<const float4 *>(dsin_save + cidx * kDK * kDV + r * kDV + c));
-            float4 *slot = reinterpret_cast<float4 *>(Sb + r * kPadF + c);
-            const float4 old = *slot;
-            dgp += old.x * nw.x + old.y * nw.y + old.z * nw.z + old.w * nw.w;
-            *slot = nw;
+        for (int i = tid; i < kDK * kDV / 8; i += 256) {
+            const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
+            const float *src = dsin_save + cidx * kDK * kDV + r * kDV + c;
+            const float4 lo = __ldg(reinterpret_cast<const float4 *>(src)), hi = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+            uint4 *slot = reinterpret_cast<uint4 *>(Sh + r * kPadH + c);
+            const uint4 old = *slot;
+            float o8[8];
+            unpack_bf16x2(old.x, o8[0], o8[1]); unpack_bf16x2(old.y, o8[2], o8[3]);
+            unpack_bf16x2(old.z, o8[4], o8[5]); unpack_bf16x2(old.w, o8[6], o8[7]);
+            dgp += o8[0] * lo.x + o8[1] * lo.y + o8[2] * lo.z + o8[3] * lo.w + o8[4] * hi.x + o8[5] * hi.y + o8[6] * hi.z + o8[7] * hi.w;
+            *slot = make_uint4(pack_bf16x2(lo.x, lo.y), pack_bf16x2(lo.z, lo.w), pack_bf16x2(hi.x, hi.y), pack_bf16x2(hi.z, hi.w));
         }
-        for (int i = tid; i < kC * kDV / 4; i += 256) {
-            const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
-            *reinterpret_cast<float4 *>(M0 + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(u_save + (row0 + r) * kDV + c));
+        for (int i = tid; i < kC * kDV / 8; i += 256) {
+            const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
+            *reinterpret_cast<uint4 *>(M0 + r * kPadH + c) = round8(u_save + (row0 + r) * kDV + c);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) dgp += __shfl_xor_sync(0xffffffffu, dgp, o);
@@ -1055,10 +1052,10 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     {
         float t3[8][4] = {};
 #pragma unroll 2
-        for (int k0 = 0; k0 < kDV; k0 += 8) {
+        for (int k0 = 0; k0 < kDV; k0 += 16) {
             uint32_t af[4];
-            frag_a_f32(af, M0, kPadF, m0, k0, g, t4);
-            mma_row_nk(t3, af, Sb, kPadF, n0, k0, g, t4);
+            ldsm_x4(af, M0 + (m0 + plain_r) * kPadH + k0 + plain_c);
+            step_nk(t3, af, Sh, kPadH, k0);
         }
         float r0, r1;
         dot_rows(Kh, t3, r0, r1);
@@ -1070,22 +1067,29 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
             dka[nt][2] = fmaf(e1, t3[nt][2], dka[nt][2]); dka[nt][3] = fmaf(e1, t3[nt][3], dka[nt][3]);
         }
     }
+    __syncthreads();   // the state's place is free: X, G and beta .* G move in
+    for (int i = tid; i < kC * kC / 8; i += 256) {
+        const int r = i / (kC / 8), c = (i % (kC / 8)) * 8;
+        *reinterpret_cast<uint4 *>(Xh + r * kPadP + c) = round8(x_in + row0 * kC + r * kC + c);
+        const float *src = g_in + row0 * kC + r * kC + c;
+        const float4 lo = __ldg(reinterpret_cast<const float4 *>(src)), hi = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        const float b = be[r];
+        *reinterpret_cast<uint4 *>(Gh + r * kPadP + c) =
+            make_uint4(pack_bf16x2(lo.x, lo.y), pack_bf16x2(lo.z, lo.w), pack_bf16x2(hi.x, hi.y), pack_bf16x2(hi.z, hi.w));
+        *reinterpret_cast<uint4 *>(Gb + r * kPadP + c) =
+            make_uint4(pack_bf16x2(b * lo.x, b * lo.y), pack_bf16x2(b * lo.z, b * lo.w), pack_bf16x2(b * hi.x, b * hi.y),
+                       pack_bf16x2(b * hi.z, b * hi.w));
+    }
+    __syncthreads();
 
-    // phase 3: the four products over the chunk's own positions (B[k][n] = K[s][i] or Q[s][i], BFloat16 tiles)
-    auto mma_tile_bf16 = [&](float (&acc)[8][4], const uint32_t (&af)[4], const __nv_bfloat16 *tile, int k0) {
-#pragma unroll
-        for (int nt = 0; nt < 8; nt++) {
-            const __nv_bfloat16 *p = tile + (k0 + t4) * kPadH + n0 + 8 * nt + g;
-            mma_tf32(acc[nt], af, tf32_of_bf16(p), tf32_of_bf16(p + 4 * kPadH));
-        }
-    };
+    // phase 3: the four products over the chunk's own positions (B[k][n] = K[s][i] or Q[s][i])
     {   // X K -> dQ and its row sum with Q
         float xk[8][4] = {};
-#pragma unroll 2
-        for (int k0 = 0; k0 < kC; k0 += 8) {
+#pragma unroll
+        for (int k0 = 0; k0 < kC; k0 += 16) {
             uint32_t af[4];
-            frag_a_f32(af, Xs, kPadX, m0, k0, g, t4);
-            mma_tile_bf16(xk, af, Kh, k0);
+            ldsm_x4(af, Xh + (m0 + plain_r) * kPadP + k0 + plain_c);
+            step_kn(xk, af, Kh, kPadH, k0);
         }
         float r0, r1;
         dot_rows(Qh, xk, r0, r1);
@@ -1097,11 +1101,11 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     }
     {   // X' Q -> dK and its row sum with K
         float xq[8][4] = {};
-#pragma unroll 2
-        for (int k0 = 0; k0 < kC; k0 += 8) {
+#pragma unroll
+        for (int k0 = 0; k0 < kC; k0 += 16) {
             uint32_t af[4];
-            frag_at_f32(af, Xs, kPadX, m0, k0, g, t4, nullptr);
-            mma_tile_bf16(xq, af, Qh, k0);
+            ldsm_x4_trans(af, Xh + (k0 + flip_r) * kPadP + m0 + flip_c);
+            step_kn(xq, af, Qh, kPadH, k0);
         }
         float r0, r1;
         dot_rows(Kh, xq, r0, r1);
@@ -1113,11 +1117,11 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     }
     {   // G K -> beta-scaled into dK, its row sum with K feeds dbeta and the gate gradient
         float gk[8][4] = {};
-#pragma unroll 2
-        for (int k0 = 0; k0 < kC; k0 += 8) {
+#pragma unroll
+        for (int k0 = 0; k0 < kC; k0 += 16) {
             uint32_t af[4];
-            frag_a_f32(af, Gs, kPadX, m0, k0, g, t4);
-            mma_tile_bf16(gk, af, Kh, k0);
+            ldsm_x4(af, Gh + (m0 + plain_r) * kPadP + k0 + plain_c);
+            step_kn(gk, af, Kh, kPadH, k0);
         }
         float r0, r1;
         dot_rows(Kh, gk, r0, r1);
@@ -1129,13 +1133,13 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
             dka[nt][2] = fmaf(b1, gk[nt][2], dka[nt][2]); dka[nt][3] = fmaf(b1, gk[nt][3], dka[nt][3]);
         }
     }
-    {   // G' (beta K)
+    {   // G' (beta K) = (beta .* G)' K
         float gb[8][4] = {};
-#pragma unroll 2
-        for (int k0 = 0; k0 < kC; k0 += 8) {
+#pragma unroll
+        for (int k0 = 0; k0 < kC; k0 += 16) {
             uint32_t af[4];
-            frag_at_f32(af, Gs, kPadX, m0, k0, g, t4, be);
-            mma_tile_bf16(gb, af, Kh, k0);
+            ldsm_x4_trans(af, Gb + (k0 + flip_r) * kPadP + m0 + flip_c);
+            step_kn(gb, af, Kh, kPadH, k0);
         }
         float r0, r1;
         dot_rows(Kh, gb, r0, r1);
@@ -1150,10 +1154,10 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
 #pragma unroll
     for (int nt = 0; nt < 8; nt++) {
         const int col = n0 + 8 * nt + 2 * t4;
-        *reinterpret_cast<float2 *>(M0 + t0 * kPadF + col) = make_float2(dqa[nt][0], dqa[nt][1]);
-        *reinterpret_cast<float2 *>(M0 + t1 * kPadF + col) = make_float2(dqa[nt][2], dqa[nt][3]);
-        *reinterpret_cast<float2 *>(M1 + t0 * kPadF + col) = make_float2(dka[nt][0], dka[nt][1]);
-        *reinterpret_cast<float2 *>(M1 + t1 * kPadF + col) = make_float2(dka[nt][2], dka[nt][3]);
+        *reinterpret_cast<uint32_t *>(M0 + t0 * kPadH + col) = pack_bf16x2(dqa[nt][0], dqa[nt][1]);
+        *reinterpret_cast<uint32_t *>(M0 + t1 * kPadH + col) = pack_bf16x2(dqa[nt][2], dqa[nt][3]);
+        *reinterpret_cast<uint32_t *>(M1 + t0 * kPadH + col) = pack_bf16x2(dka[nt][0], dka[nt][1]);
+        *reinterpret_cast<uint32_t *>(M1 + t1 * kPadH + col) = pack_bf16x2(dka[nt][2], dka[nt][3]);
     }
     auto row_sum = [&](int which, int t) { return part[(which * 2) * 64 + t] + part[(which * 2 + 1) * 64 + t]; };
     if (tid == 0) {
@@ -1178,14 +1182,8 @@ __global__ void __launch_bounds__(256) deltanet_bwd_out_kernel(
     __syncthreads();
     for (int i = tid; i < kC * kDK / 8; i += 256) {
         const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
-        const float *s0 = M0 + r * kPadF + c, *s1 = M1 + r * kPadF + c;
-        uint4 oq, ok;
-        oq.x = pack_bf16x2(s0[0], s0[1]); oq.y = pack_bf16x2(s0[2], s0[3]);
-        oq.z = pack_bf16x2(s0[4], s0[5]); oq.w = pack_bf16x2(s0[6], s0[7]);
-        ok.x = pack_bf16x2(s1[0], s1[1]); ok.y = pack_bf16x2(s1[2], s1[3]);
-        ok.z = pack_bf16x2(s1[4], s1[5]); ok.w = pack_bf16x2(s1[6], s1[7]);
-        *reinterpret_cast<uint4 *>(dq + (row0 + r) * kDK + c) = oq;
-        *reinterpret_cast<uint4 *>(dk + (row0 + r) * kDK + c) = ok;
+        *reinterpret_cast<uint4 *>(dq + (row0 + r) * kDK + c) = *reinterpret_cast<const uint4 *>(M0 + r * kPadH + c);
+        *reinterpret_cast<uint4 *>(dk + (row0 + r) * kDK + c) = *reinterpret_cast<const uint4 *>(M1 + r * kPadH + c);
     }
 }
 
@@ -1228,8 +1226,7 @@ constexpr size_t kScanSmem = 1024 + 2 * kTileSetBytes + 2 * kGateFloats * sizeof
 constexpr size_t kBwdScanSmem = (kDK * kPadS + 3 * kC * kPadS + kC * kPadM + 3 * kC) * sizeof(float) +
                                 (2 * kC * kPadH + kC * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdXgSmem = (3 * kC * kPadF + kC) * sizeof(float);
-constexpr size_t kBwdOutSmem = (kDK * kPadF + 2 * kC * kPadF + 2 * kC * kPadX + 3 * kC + 7 * 2 * kC + 8) * sizeof(float) +
-                               2 * kC * kPadH * sizeof(__nv_bfloat16);
+constexpr size_t kBwdOutSmem = (3 * kC + 7 * 2 * kC + 8) * sizeof(float) + (kDK * kPadH + 4 * kC * kPadH) * sizeof(__nv_bfloat16);
 
 }  // namespace
 }  // namespace tb200
