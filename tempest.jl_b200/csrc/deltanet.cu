@@ -67,7 +67,7 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-constexpr int kGateFloats = 132;   // e^ca (64), e^(ca_C - ca) (64), e^ca_C, padded to a multiple of 16 bytes
+constexpr int kGateFloats = 196;   // e^ca (64), e^(ca_C - ca) (64), beta (64), e^ca_C, padded to a multiple of 16 bytes
 constexpr int kPadA = 68;   // Float32 row pitch of the 64 x 64 tiles A, (I + A)^-1 and the scratch beside them
 
 // 3xTF32: a Float32 operand as the sum of two TF32 values; hi*hi + lo*hi + hi*lo keeps about 21 bits of the product.
@@ -111,7 +111,7 @@ __device__ __forceinline__ void block_store(float *dst, const float (&acc)[2][4]
     }
 }
 
-// One block of 256 threads per (head, chunk).  minv_save (the backward's first launch) receives (I + A)^-1.
+// One block of 256 threads per (head, chunk).  minv_save (the backward's first launch) receives (I + A)^-1, rounded.
 __device__ __forceinline__ uint32_t tf32_bits(float x) {
     uint32_t r;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
@@ -121,7 +121,7 @@ __device__ __forceinline__ uint32_t tf32_bits(float x) {
 __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
                                                              const __nv_bfloat16 *v, const float *a, const float *beta,
                                                              __nv_bfloat16 *w_out, __nv_bfloat16 *u_out,
-                                                             __nv_bfloat16 *p_out, float *minv_save,
+                                                             __nv_bfloat16 *p_out, __nv_bfloat16 *minv_save,
                                                              float *gates_out, int T) {
     extern __shared__ float sm[];
     float *A = sm;                        // [64][68]
@@ -160,7 +160,8 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
         const float last = ca[kC - 1];
         dst[tid] = __expf(ca[tid]);
         dst[kC + tid] = __expf(last - ca[tid]);
-        if (tid == 0) dst[2 * kC] = __expf(last);
+        dst[2 * kC + tid] = be[tid];
+        if (tid == 0) dst[3 * kC] = __expf(last);
     }
 
     // A = beta .* decay(t > s) .* (K K'), P = decay(t >= s) .* (Q K') on the tensor cores: the operands are BFloat16 as
@@ -249,10 +250,11 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
         }
         __syncthreads();
     }
-    if (minv_save)
+    if (minv_save)   // rounded: the reverse scan takes it as a BFloat16 operand
         for (int i = tid; i < kC * kC / 4; i += blockDim.x) {
             const int r = i / (kC / 4), c = (i % (kC / 4)) * 4;
-            *reinterpret_cast<float4 *>(minv_save + (row0 + r) * kC + c) = *reinterpret_cast<const float4 *>(Mi + r * kPadA + c);
+            const float4 m4 = *reinterpret_cast<const float4 *>(Mi + r * kPadA + c);
+            *reinterpret_cast<uint2 *>(minv_save + (row0 + r) * kC + c) = make_uint2(pack_bf16x2(m4.x, m4.y), pack_bf16x2(m4.z, m4.w));
         }
 
     // [W | Ut] = (I + A)^-1 [beta e^ca K | beta V]: warp w takes rows 16 (w % 4) .. + 15 of the 128 columns of W
@@ -289,29 +291,6 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
 }
 
 // ----------------------------------------------------------------- across chunks ----
-
-
-// Warp-level TF32 tensor-core product step: D(16 x 8) += A(16 x 8) B(8 x 8), Float32 accumulate.  With
-// g = lane / 4 and t = lane % 4 a thread holds A[g][t], A[g+8][t], A[g][t+4], A[g+8][t+4]; B[t][g], B[t+4][g];
-// D[g][2t], D[g][2t+1], D[g+8][2t], D[g+8][2t+1].  The products of a chunk are small (64 x 32 x 128) and sit on
-// the chain of chunks: the warp-level form keeps operands in shared memory and results in registers, with no
-// tensor-memory round trip per link of the chain.  TF32 operands: BFloat16 values are exact in TF32; the
-// Float32 state and U are rounded to TF32 (10 mantissa bits) as operands only, never in storage.
-__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t tf32_of(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return r;
-}
-__device__ __forceinline__ uint32_t tf32_of_bf16(const __nv_bfloat16 *p) {
-    return static_cast<uint32_t>(*reinterpret_cast<const unsigned short *>(p)) << 16;
-}
-
-constexpr int kPadS = 40;   // Float32 row pitch of the 32-wide state and U tiles: B-fragment reads hit 32 banks
 
 
 // Four 8 x 8 BFloat16 matrices from shared memory into a warp's registers, as the m16n8k16 fragments want them: each
@@ -524,7 +503,7 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __gri
         // o = e^ca (Q S) + P U is off the chain: its MMAs are issued between the update's, whose four accumulators
         // each wait for their own previous step, so that the tensor pipe has independent work in the gaps.
         {
-            const float gamma = eca[2 * kC];
+            const float gamma = eca[3 * kC];
 #pragma unroll
             for (int nt = 0; nt < 4; nt++)
 #pragma unroll
@@ -597,123 +576,172 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __gri
 // It is the chain rule through examples/deltanet.jl:58-85 taken by hand; Tempest derives the same
 // pullback from the forward program (examples/deltanet.jl:96-101).
 
-// One block per (head, 32 value features), chunks walked last to first.  The four products of a chunk are
-// TF32 warp-level MMAs as in the forward scan: dU and dZ take warp -> 16 positions x 16 features, the state
-// gradient takes warp -> 16 state rows x 32 features; transposed operands (P', Minv', (e Q)', (e beta K)') are
-// read transposed from the tiles as they lie.
-constexpr int kPadM = 72;   // Float32 row pitch of (I + A)^-1: transposed A-fragment reads hit 32 banks
+// One block of 512 threads per (head, 64 value features), chunks walked last to first, built like the forward scan:
+// two groups of eight warps with 32 features each share a chunk's K, Q, P and (I + A)^-1 tiles, which arrive by TMA
+// into swizzled boxes in two buffers, a chunk ahead, together with each group's box of dO (read as it lies,
+// [feature][position]) and the chunk's gates.  A group's slice of the state gradient lives in the accumulators of the
+// product that updates it; the other products read a BFloat16 copy.  The four products are BFloat16 m16n8k16 MMAs
+// through ldmatrix; the scalings along a summed axis go into the small operand as it is written (e into a copy of
+// dO, -e beta into the copy of dZ).
+struct BwdScanMaps { CUtensorMap k, q, p, minv, dout; };
+constexpr int kBwdSetBytes = 6 * kBoxBytes + 2 * (kDVP * 128);   // K, Q (two boxes each), P, Minv; dO for two groups
 
-__global__ void __launch_bounds__(256) deltanet_bwd_scan_kernel(
-    const __nv_bfloat16 *q, const __nv_bfloat16 *k, const float *a, const float *beta, const __nv_bfloat16 *p_in,
-    const float *minv, const __nv_bfloat16 *dout, float *dsin_save, float *dz_save, __nv_bfloat16 *dv_out, int T) {
-    extern __shared__ float sm[];
-    float *dS = sm;                         // [128][40]
-    float *dOs = dS + kDK * kPadS;          // [64][40]
-    float *dU = dOs + kC * kPadS;           // [64][40]
-    float *dZ = dU + kC * kPadS;            // [64][40]
-    float *Mi = dZ + kC * kPadS;            // [64][72]
-    float *eca = Mi + kC * kPadM;           // [64]
-    float *ekd = eca + kC;                  // [64]
-    float *be = ekd + kC;                   // [64]
-    __nv_bfloat16 *Qh = reinterpret_cast<__nv_bfloat16 *>(be + kC);   // [64][136]
-    __nv_bfloat16 *Kh = Qh + kC * kPadH;
-    __nv_bfloat16 *Ph = Kh + kC * kPadH;    // [64][72]
-    __shared__ float gamma_sm;
+__device__ __forceinline__ const unsigned char *swz_row128(const unsigned char *tile, int row, int col) {   // one box
+    return tile + row * 128 + (((col >> 3) ^ (row & 7)) << 4);
+}
 
-    const int head = blockIdx.x, part = blockIdx.y;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+__global__ void __launch_bounds__(kScanThreads) deltanet_bwd_scan_kernel(const __grid_constant__ BwdScanMaps maps,
+                                                                         const float *gates_in, float *dsin_save,
+                                                                         float *dz_save, __nv_bfloat16 *dv_out, int T) {
+    extern __shared__ unsigned char sm_raw[];
+    unsigned char *tiles = sm_raw + ((1024u - (sm100::smem_u32(sm_raw) & 1023u)) & 1023u);   // [2] sets
+    float *gate2 = reinterpret_cast<float *>(tiles + 2 * kBwdSetBytes);   // [2][kGateFloats]
+    __nv_bfloat16 *group_base = reinterpret_cast<__nv_bfloat16 *>(gate2 + 2 * kGateFloats);
+    __shared__ __align__(8) uint64_t tile_full[2];
+
+    const int head = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int group = tid >> 8, gtid = tid & 255, warp = (tid >> 5) & 7;
+    const int part = blockIdx.y * (kDVB / kDVP) + group;
     const int g = lane >> 2, t4 = lane & 3;
-    const int mt = warp & 3, nh = warp >> 2;
     const int chunks = T / kC;
-    for (int i = tid; i < kDK * kPadS; i += 256) dS[i] = 0.0f;
+    constexpr int kGroupElems = 2 * kDK * kPadB + 2 * kC * kPadB + kDVP * kPadP;
+    __nv_bfloat16 *Sb2 = group_base + group * kGroupElems;   // [2][128][40] the state gradient as an operand
+    __nv_bfloat16 *Ub = Sb2 + 2 * kDK * kPadB;               // [64][40] dU
+    __nv_bfloat16 *Zs = Ub + kC * kPadB;                     // [64][40] -e beta dZ
+    __nv_bfloat16 *Oe = Zs + kC * kPadB;                     // [32][72] e dO, [feature][position]
+    const int plain_r = (lane & 7) + 8 * ((lane >> 3) & 1), plain_c = 8 * (lane >> 4);
+    const int flip_r = (lane & 7) + 8 * (lane >> 4), flip_c = 8 * ((lane >> 3) & 1);
+    const int mt = warp & 3, nh = warp >> 2;
+    const long long head_row = static_cast<long long>(head) * T;
 
-    for (int chunk = chunks - 1; chunk >= 0; chunk--) {
-        const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
+    const uint32_t tile_bytes = kBwdSetBytes + kGateFloats * 4u;
+    auto copy_tiles = [&](int chunk) {   // one thread
+        if (tid != 0) return;
+        unsigned char *set = tiles + (chunk & 1) * kBwdSetBytes;
+        uint64_t *bar = &tile_full[chunk & 1];
+        const int row = static_cast<int>(head_row) + chunk * kC;
+        sm100::mbar_arrive_expect_tx(bar, tile_bytes);
+        sm100::bulk_load(gate2 + (chunk & 1) * kGateFloats, gates_in + (static_cast<long long>(head) * chunks + chunk) * kGateFloats,
+                         kGateFloats * 4, bar);
+        sm100::tma_load_2d(set, &maps.k, bar, 0, row);
+        sm100::tma_load_2d(set + kBoxBytes, &maps.k, bar, 64, row);
+        sm100::tma_load_2d(set + 2 * kBoxBytes, &maps.q, bar, 0, row);
+        sm100::tma_load_2d(set + 3 * kBoxBytes, &maps.q, bar, 64, row);
+        sm100::tma_load_2d(set + 4 * kBoxBytes, &maps.p, bar, 0, row);
+        sm100::tma_load_2d(set + 5 * kBoxBytes, &maps.minv, bar, 0, row);
+        const int feature0 = head * kDV + blockIdx.y * kDVB;
+        sm100::tma_load_2d(set + 6 * kBoxBytes, &maps.dout, bar, chunk * kC, feature0);
+        sm100::tma_load_2d(set + 6 * kBoxBytes + kDVP * 128, &maps.dout, bar, chunk * kC, feature0 + kDVP);
+    };
+    bool gave_up = false;
+    auto wait_tiles = [&](int chunk, uint32_t parity) {
+        if (gave_up) return;
+        uint64_t *bar = &tile_full[chunk & 1];
+        if (sm100::mbar_wait(bar, parity, 4096)) return;
+        unsigned long long t0, t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        while (!sm100::mbar_wait(bar, parity, 1024)) {
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > 2000000000ull) {
+                gave_up = true;
+                atomicCAS(&g_deltanet_error, 0, 2);
+                return;
+            }
+        }
+    };
+    auto put_state = [&](__nv_bfloat16 *Sb, const float (&st)[4][4]) {
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            *reinterpret_cast<uint32_t *>(Sb + (16 * warp + g) * kPadB + 8 * nt + 2 * t4) = pack_bf16x2(st[nt][0], st[nt][1]);
+            *reinterpret_cast<uint32_t *>(Sb + (16 * warp + g + 8) * kPadB + 8 * nt + 2 * t4) = pack_bf16x2(st[nt][2], st[nt][3]);
+        }
+    };
+
+    float state[4][4] = {};
+    put_state(Sb2, state);
+    if (tid == 0) {
+        sm100::mbar_init(&tile_full[0], 1);
+        sm100::mbar_init(&tile_full[1], 1);
+        sm100::fence_barrier_init();
+    }
+    __syncthreads();
+    if (chunks > 0) copy_tiles(chunks - 1);
+    int step = 0;   // chunks done so far: the copy buffers and barrier phases go by it
+    for (int chunk = chunks - 1; chunk >= 0; chunk--, step++) {
+        const long long row0 = head_row + static_cast<long long>(chunk) * kC;
         const long long cidx = static_cast<long long>(head) * chunks + chunk;
-        __syncthreads();
+        const float *eca = gate2 + (chunk & 1) * kGateFloats, *ekd = eca + kC, *be = eca + 2 * kC;
+        const unsigned char *Kt = tiles + (chunk & 1) * kBwdSetBytes, *Qt = Kt + 2 * kBoxBytes, *Pt = Kt + 4 * kBoxBytes,
+                            *Mt = Kt + 5 * kBoxBytes, *Ot = Kt + 6 * kBoxBytes + group * (kDVP * 128);
+        const __nv_bfloat16 *Sb = Sb2 + (step & 1) * kDK * kPadB;
+        __syncthreads();   // the state copy is in place; everything of the chunk before (after, in time order) is done
+        if (chunk > 0) copy_tiles(chunk - 1);
+        // a buffer is used by every other chunk: chunks - 1, chunks - 3, ... share one, so its phase goes by step / 2
+        wait_tiles(chunk, static_cast<uint32_t>((step >> 1) & 1));
         {   // the incoming state gradient, for the per-chunk kernel
             float *dst = dsin_save + cidx * kDK * kDV + part * kDVP;
-            for (int i = tid; i < kDK * kDVP; i += 256) dst[(i / kDVP) * kDV + (i % kDVP)] = dS[(i / kDVP) * kPadS + (i % kDVP)];
-        }
-        for (int i = tid; i < kC * kDK / 8; i += 256) {
-            const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
-            *reinterpret_cast<uint4 *>(Qh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(q + (row0 + r) * kDK + c));
-            *reinterpret_cast<uint4 *>(Kh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(k + (row0 + r) * kDK + c));
-        }
-        for (int i = tid; i < kC * kC / 8; i += 256) {
-            const int r = i / (kC / 8), c = (i % (kC / 8)) * 8;
-            *reinterpret_cast<uint4 *>(Ph + r * kPadP + c) = __ldg(reinterpret_cast<const uint4 *>(p_in + cidx * kC * kC + r * kC + c));
-        }
-        for (int i = tid; i < kC * kC / 4; i += 256) {
-            const int r = i / (kC / 4), c = (i % (kC / 4)) * 4;
-            *reinterpret_cast<float4 *>(Mi + r * kPadM + c) = __ldg(reinterpret_cast<const float4 *>(minv + row0 * kC + r * kC + c));
-        }
-        {   // dO arrives as (positions, features): 8 positions of one feature per thread
-            const int f = tid >> 3, t8 = (tid & 7) * 8;
-            float dv8[8];
-            Access<__nv_bfloat16, true>::load_cached(
-                dout + (static_cast<long long>(head) * kDV + part * kDVP + f) * T + static_cast<long long>(chunk) * kC + t8, dv8);
 #pragma unroll
-            for (int e = 0; e < 8; e++) dOs[(t8 + e) * kPadS + f] = dv8[e];
+            for (int nt = 0; nt < 4; nt++) {
+                *reinterpret_cast<float2 *>(dst + (16 * warp + g) * kDV + 8 * nt + 2 * t4) = make_float2(state[nt][0], state[nt][1]);
+                *reinterpret_cast<float2 *>(dst + (16 * warp + g + 8) * kDV + 8 * nt + 2 * t4) = make_float2(state[nt][2], state[nt][3]);
+            }
         }
-        if (tid < kC) be[tid] = beta[row0 + tid];
-        if (tid < 32) {
-            float lo, hi;
-            chunk_cumsum(a + row0, tid, lo, hi);
-            const float last = __shfl_sync(0xffffffffu, hi, 31);
-            eca[tid] = __expf(lo); eca[tid + 32] = __expf(hi);
-            ekd[tid] = __expf(last - lo); ekd[tid + 32] = __expf(last - hi);
-            if (tid == 0) gamma_sm = __expf(last);
+        {   // e dO beside dO: eight positions of one feature a thread
+            const int f = gtid >> 3, t8 = (gtid & 7) * 8;
+            const uint4 d8 = *reinterpret_cast<const uint4 *>(swz_row128(Ot, f, t8));
+            const uint32_t w4[4] = {d8.x, d8.y, d8.z, d8.w};
+            uint32_t o4[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                float lo, hi;
+                unpack_bf16x2(w4[e], lo, hi);
+                o4[e] = pack_bf16x2(lo * eca[t8 + 2 * e], hi * eca[t8 + 2 * e + 1]);
+            }
+            *reinterpret_cast<uint4 *>(Oe + f * kPadP + t8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
         }
-        __syncthreads();
 
         // dU = ed (K dS') + P' dO : rows t = 16 mt + g (+8), columns 16 nh + 8 nt + 2 t4 (+1)
         {
-            float acc[2][4] = {};
-            const __nv_bfloat16 *k0p = Kh + (16 * mt + g) * kPadH + t4, *k1p = k0p + 8 * kPadH;
-            const float *sb = dS + t4 * kPadS + 16 * nh + g;
-#pragma unroll 4
-            for (int k0 = 0; k0 < kDK; k0 += 8) {
-                const uint32_t af[4] = {tf32_of_bf16(k0p + k0), tf32_of_bf16(k1p + k0), tf32_of_bf16(k0p + k0 + 4), tf32_of_bf16(k1p + k0 + 4)};
+            float acc[2][4] = {}, pd[2][4] = {};
 #pragma unroll
-                for (int nt = 0; nt < 2; nt++)
-                    mma_tf32(acc[nt], af, tf32_of(sb[k0 * kPadS + 8 * nt]), tf32_of(sb[(k0 + 4) * kPadS + 8 * nt]));
+            for (int k0 = 0; k0 < kDK; k0 += 16) {
+                uint32_t af[4], bf[4];
+                ldsm_x4(af, swz(Kt, 16 * mt + plain_r, k0 + plain_c));
+                ldsm_x4_trans(bf, Sb + (k0 + plain_r) * kPadB + 16 * nh + plain_c);
+                mma_bf16(acc[0], af, bf[0], bf[1]);
+                mma_bf16(acc[1], af, bf[2], bf[3]);
+                if ((k0 & 16) == 0) {   // P' dO between them: four steps over the chunk's positions
+                    const int s0 = k0 >> 1;
+                    uint32_t ap[4], bo[4];
+                    ldsm_x4_trans(ap, swz_row128(Pt, s0 + flip_r, 16 * mt + flip_c));
+                    ldsm_x4(bo, swz_row128(Ot, 16 * nh + flip_r, s0 + flip_c));
+                    mma_bf16(pd[0], ap, bo[0], bo[1]);
+                    mma_bf16(pd[1], ap, bo[2], bo[3]);
+                }
             }
             const float e0 = ekd[16 * mt + g], e1 = ekd[16 * mt + g + 8];
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++) { acc[nt][0] *= e0; acc[nt][1] *= e0; acc[nt][2] *= e1; acc[nt][3] *= e1; }
-            // A[t][s] = P[s][t]
-            const __nv_bfloat16 *pb = Ph + t4 * kPadP + 16 * mt + g;
-            const float *ob = dOs + t4 * kPadS + 16 * nh + g;
-#pragma unroll 4
-            for (int k0 = 0; k0 < kC; k0 += 8) {
-                const uint32_t af[4] = {tf32_of_bf16(pb + k0 * kPadP), tf32_of_bf16(pb + k0 * kPadP + 8), tf32_of_bf16(pb + (k0 + 4) * kPadP),
-                                        tf32_of_bf16(pb + (k0 + 4) * kPadP + 8)};
-#pragma unroll
-                for (int nt = 0; nt < 2; nt++)
-                    mma_tf32(acc[nt], af, tf32_of(ob[k0 * kPadS + 8 * nt]), tf32_of(ob[(k0 + 4) * kPadS + 8 * nt]));
+            for (int nt = 0; nt < 2; nt++) {
+                const int col = 16 * nh + 8 * nt + 2 * t4;
+                *reinterpret_cast<uint32_t *>(Ub + (16 * mt + g) * kPadB + col) =
+                    pack_bf16x2(fmaf(acc[nt][0], e0, pd[nt][0]), fmaf(acc[nt][1], e0, pd[nt][1]));
+                *reinterpret_cast<uint32_t *>(Ub + (16 * mt + g + 8) * kPadB + col) =
+                    pack_bf16x2(fmaf(acc[nt][2], e1, pd[nt][2]), fmaf(acc[nt][3], e1, pd[nt][3]));
             }
-#pragma unroll
-            for (int nt = 0; nt < 2; nt++)
-#pragma unroll
-                for (int hr = 0; hr < 2; hr++)
-                    *reinterpret_cast<float2 *>(dU + (16 * mt + g + 8 * hr) * kPadS + 16 * nh + 8 * nt + 2 * t4) =
-                        make_float2(acc[nt][2 * hr], acc[nt][2 * hr + 1]);
         }
         __syncthreads();
 
         // dZ = Minv' dU : A[t][s] = Minv[s][t]
         {
             float z[2][4] = {};
-            const float *mb = Mi + t4 * kPadM + 16 * mt + g;
-            const float *ub = dU + t4 * kPadS + 16 * nh + g;
-#pragma unroll 4
-            for (int k0 = 0; k0 < kC; k0 += 8) {
-                const uint32_t af[4] = {tf32_of(mb[k0 * kPadM]), tf32_of(mb[k0 * kPadM + 8]), tf32_of(mb[(k0 + 4) * kPadM]),
-                                        tf32_of(mb[(k0 + 4) * kPadM + 8])};
 #pragma unroll
-                for (int nt = 0; nt < 2; nt++)
-                    mma_tf32(z[nt], af, tf32_of(ub[k0 * kPadS + 8 * nt]), tf32_of(ub[(k0 + 4) * kPadS + 8 * nt]));
+            for (int k0 = 0; k0 < kC; k0 += 16) {
+                uint32_t af[4], bf[4];
+                ldsm_x4_trans(af, swz_row128(Mt, k0 + flip_r, 16 * mt + flip_c));
+                ldsm_x4_trans(bf, Ub + (k0 + plain_r) * kPadB + 16 * nh + plain_c);
+                mma_bf16(z[0], af, bf[0], bf[1]);
+                mma_bf16(z[1], af, bf[2], bf[3]);
             }
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
@@ -721,47 +749,40 @@ __global__ void __launch_bounds__(256) deltanet_bwd_scan_kernel(
                 for (int hr = 0; hr < 2; hr++) {
                     const int t = 16 * mt + g + 8 * hr, col = 16 * nh + 8 * nt + 2 * t4;
                     const float2 z2 = make_float2(z[nt][2 * hr], z[nt][2 * hr + 1]);
-                    *reinterpret_cast<float2 *>(dZ + t * kPadS + col) = z2;
                     *reinterpret_cast<float2 *>(dz_save + (row0 + t) * kDV + part * kDVP + col) = z2;
-                    const float b = be[t];
+                    const float b = be[t], eb = -eca[t] * b;
+                    *reinterpret_cast<uint32_t *>(Zs + t * kPadB + col) = pack_bf16x2(eb * z2.x, eb * z2.y);
                     *reinterpret_cast<uint32_t *>(dv_out + (row0 + t) * kDV + part * kDVP + col) = pack_bf16x2(b * z2.x, b * z2.y);
                 }
         }
         __syncthreads();
 
-        // dS = g dS' + (e Q)' dO - (e beta K)' dZ : warp -> state rows 16 warp + g (+8), all 32 features
+        // dS = g dS' + Q' (e dO) + K' (-e beta dZ) : warp -> state rows 16 warp + g (+8), all 32 features
         {
-            const float gamma = gamma_sm;
-            float sa[4][4];
-            float *s0 = dS + (16 * warp + g) * kPadS + 2 * t4, *s1 = s0 + 8 * kPadS;
+            const float gamma = eca[3 * kC];
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                const float2 lo = *reinterpret_cast<const float2 *>(s0 + 8 * nt), hi = *reinterpret_cast<const float2 *>(s1 + 8 * nt);
-                sa[nt][0] = gamma * lo.x; sa[nt][1] = gamma * lo.y; sa[nt][2] = gamma * hi.x; sa[nt][3] = gamma * hi.y;
-            }
-            const __nv_bfloat16 *qb = Qh + t4 * kPadH + 16 * warp + g, *kb = Kh + t4 * kPadH + 16 * warp + g;
-            const float *ob = dOs + t4 * kPadS + g, *zb = dZ + t4 * kPadS + g;
-#pragma unroll 2
-            for (int k0 = 0; k0 < kC; k0 += 8) {
-                const float ea = eca[k0 + t4], eb = eca[k0 + t4 + 4];
-                const float ba = -ea * be[k0 + t4], bb = -eb * be[k0 + t4 + 4];
-                const uint32_t aq[4] = {tf32_of(__bfloat162float(qb[k0 * kPadH]) * ea), tf32_of(__bfloat162float(qb[k0 * kPadH + 8]) * ea),
-                                        tf32_of(__bfloat162float(qb[(k0 + 4) * kPadH]) * eb),
-                                        tf32_of(__bfloat162float(qb[(k0 + 4) * kPadH + 8]) * eb)};
-                const uint32_t ak[4] = {tf32_of(__bfloat162float(kb[k0 * kPadH]) * ba), tf32_of(__bfloat162float(kb[k0 * kPadH + 8]) * ba),
-                                        tf32_of(__bfloat162float(kb[(k0 + 4) * kPadH]) * bb),
-                                        tf32_of(__bfloat162float(kb[(k0 + 4) * kPadH + 8]) * bb)};
+            for (int nt = 0; nt < 4; nt++)
 #pragma unroll
-                for (int nt = 0; nt < 4; nt++) {
-                    mma_tf32(sa[nt], aq, tf32_of(ob[k0 * kPadS + 8 * nt]), tf32_of(ob[(k0 + 4) * kPadS + 8 * nt]));
-                    mma_tf32(sa[nt], ak, tf32_of(zb[k0 * kPadS + 8 * nt]), tf32_of(zb[(k0 + 4) * kPadS + 8 * nt]));
-                }
-            }
+                for (int e = 0; e < 4; e++) state[nt][e] *= gamma;
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                *reinterpret_cast<float2 *>(s0 + 8 * nt) = make_float2(sa[nt][0], sa[nt][1]);
-                *reinterpret_cast<float2 *>(s1 + 8 * nt) = make_float2(sa[nt][2], sa[nt][3]);
+            for (int k0 = 0; k0 < kC; k0 += 16) {
+                uint32_t aq[4], ak[4], bo0[4], bo1[4], bz0[4], bz1[4];
+                ldsm_x4_trans(aq, swz(Qt, k0 + flip_r, 16 * warp + flip_c));
+                ldsm_x4(bo0, Oe + flip_r * kPadP + k0 + flip_c);
+                ldsm_x4(bo1, Oe + (16 + flip_r) * kPadP + k0 + flip_c);
+                mma_bf16(state[0], aq, bo0[0], bo0[1]);
+                mma_bf16(state[1], aq, bo0[2], bo0[3]);
+                mma_bf16(state[2], aq, bo1[0], bo1[1]);
+                mma_bf16(state[3], aq, bo1[2], bo1[3]);
+                ldsm_x4_trans(ak, swz(Kt, k0 + flip_r, 16 * warp + flip_c));
+                ldsm_x4_trans(bz0, Zs + (k0 + plain_r) * kPadB + plain_c);
+                ldsm_x4_trans(bz1, Zs + (k0 + plain_r) * kPadB + 16 + plain_c);
+                mma_bf16(state[0], ak, bz0[0], bz0[1]);
+                mma_bf16(state[1], ak, bz0[2], bz0[3]);
+                mma_bf16(state[2], ak, bz1[0], bz1[1]);
+                mma_bf16(state[3], ak, bz1[2], bz1[3]);
             }
+            put_state(Sb2 + ((step + 1) & 1) * kDK * kPadB, state);
         }
     }
 }
@@ -1191,8 +1212,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// A [rows][cols] BFloat16 array as a tensor map of 64 x 64 boxes, 128-byte swizzle.
-int scan_tmap(CUtensorMap *map, const void *base, long long rows, int cols) {
+// A [rows][cols] BFloat16 array as a tensor map of boxes of 64 columns x box_rows rows, 128-byte swizzle.
+int scan_tmap(CUtensorMap *map, const void *base, long long rows, long long cols, int box_rows = kC) {
     static std::mutex lock;
     static EncodeTiledFn fn = nullptr;
     {
@@ -1207,7 +1228,7 @@ int scan_tmap(CUtensorMap *map, const void *base, long long rows, int cols) {
     }
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-    cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kC)};
+    cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
     cuuint32_t elem[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1223,8 +1244,8 @@ int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, cons
 constexpr size_t kChunkSmem = (2 * kC * kPadA + 3 * kC) * sizeof(float) + 3 * kC * kPadH * sizeof(__nv_bfloat16);
 constexpr size_t kScanSmem = 1024 + 2 * kTileSetBytes + 2 * kGateFloats * sizeof(float) +
                              (kDVB / kDVP) * (2 * kDK * kPadB + 2 * kC * kPadB + kDVP * kPadP) * sizeof(__nv_bfloat16);
-constexpr size_t kBwdScanSmem = (kDK * kPadS + 3 * kC * kPadS + kC * kPadM + 3 * kC) * sizeof(float) +
-                                (2 * kC * kPadH + kC * kPadP) * sizeof(__nv_bfloat16);
+constexpr size_t kBwdScanSmem = 1024 + 2 * kBwdSetBytes + 2 * kGateFloats * sizeof(float) +
+                                (kDVB / kDVP) * (2 * kDK * kPadB + 2 * kC * kPadB + kDVP * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdXgSmem = (3 * kC * kPadF + kC) * sizeof(float);
 constexpr size_t kBwdOutSmem = (3 * kC + 7 * 2 * kC + 8) * sizeof(float) + (kDK * kPadH + 4 * kC * kPadH) * sizeof(__nv_bfloat16);
 
@@ -1346,8 +1367,9 @@ extern "C" int tb200_deltanet_bwd(const tb200_deltanet_desc *d, const void *q, c
     __nv_bfloat16 *u = w + rows * kDK;
     __nv_bfloat16 *pw = u + rows * kDV;
     float *gates = reinterpret_cast<float *>(pw + rows * kC);
-    float *minv = gates + rows / kC * kGateFloats;
-    float *s_save = minv + rows * kC;
+    float *minv_room = gates + rows / kC * kGateFloats;                    // rows * kC floats, half of them used
+    __nv_bfloat16 *minv = reinterpret_cast<__nv_bfloat16 *>(minv_room);   // (I + A)^-1 as the reverse scan's operand
+    float *s_save = minv_room + rows * kC;
     float *u_save = s_save + rows * (kDK * kDV / kC);
     float *dsin = u_save + rows * kDV;
     float *dz = dsin + rows * (kDK * kDV / kC);
@@ -1364,9 +1386,17 @@ extern "C" int tb200_deltanet_bwd(const tb200_deltanet_desc *d, const void *q, c
     TB200_CUDA(cudaGetLastError());
     // no result pointer: the scan only carries the state
     if ((st = launch_scan(d, q, k, gates, w, u, pw, nullptr, s_save, u_save, stream))) return st;
-    deltanet_bwd_scan_kernel<<<grid, 256, kBwdScanSmem, stream>>>(qb, kb, a, beta, pw, minv, dob, dsin, dz,
-                                                                  static_cast<__nv_bfloat16 *>(dv), T);
-    TB200_CUDA(cudaGetLastError());
+    {
+        BwdScanMaps maps;
+        if ((st = scan_tmap(&maps.k, k, static_cast<long long>(rows), kDK))) return st;
+        if ((st = scan_tmap(&maps.q, q, static_cast<long long>(rows), kDK))) return st;
+        if ((st = scan_tmap(&maps.p, pw, static_cast<long long>(rows), kC))) return st;
+        if ((st = scan_tmap(&maps.minv, minv, static_cast<long long>(rows), kC))) return st;
+        if ((st = scan_tmap(&maps.dout, dout, static_cast<long long>(d->heads) * kDV, T, kDVP))) return st;
+        deltanet_bwd_scan_kernel<<<dim3(static_cast<unsigned>(d->heads), kDV / kDVB), kScanThreads, kBwdScanSmem, stream>>>(
+            maps, gates, dsin, dz, static_cast<__nv_bfloat16 *>(dv), T);
+        TB200_CUDA(cudaGetLastError());
+    }
     deltanet_bwd_xg_kernel<<<chunks, 256, kBwdXgSmem, stream>>>(a, dob, u_save, dz, xw, gw, T);
     TB200_CUDA(cudaGetLastError());
     deltanet_bwd_out_kernel<<<chunks, 256, kBwdOutSmem, stream>>>(qb, kb, vb, a, beta, dob, s_save, dsin, u_save, dz, xw,
