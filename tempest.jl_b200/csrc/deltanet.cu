@@ -34,7 +34,6 @@ constexpr int kC = 64;        // chunk length
 constexpr int kDK = 128;
 constexpr int kDV = 128;
 constexpr int kDVP = 32;      // value features per scan block
-constexpr int kPadF = 132;    // Float32 row pitch of a 128-wide tile in shared memory
 constexpr int kPadH = 136;    // BFloat16 row pitch of a 128-wide tile
 constexpr int kPadP = 72;     // BFloat16 row pitch of a 64-wide tile
 
@@ -787,30 +786,38 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_bwd_scan_kernel(const _
     }
 }
 
-// X = tril(dO U') .* D and G = -stril(dZ U') .* D, one block per (head, chunk).
+// X = tril(dO U') .* D and G = -stril(dZ U') .* D, one block per (head, chunk): two 64 x 64 x 128 products as
+// BFloat16 MMAs (U and dZ rounded as they are staged; dO is read as it lies, [feature][position], as a transposed A
+// operand).  Warp w takes rows 16 (w % 4) .. + 15 and columns 32 (w / 4) .. + 31; tiles wholly above the diagonal
+// are skipped.
 __global__ void __launch_bounds__(256) deltanet_bwd_xg_kernel(const float *a, const __nv_bfloat16 *dout,
                                                               const float *u_save, const float *dz_save, float *x_out,
                                                               float *g_out, int T) {
     extern __shared__ float sm[];
-    float *dOs = sm;                     // [64][132]
-    float *Us = dOs + kC * kPadF;
-    float *dZs = Us + kC * kPadF;
-    float *ca = dZs + kC * kPadF;        // [64]
+    float *ca = sm;                                                        // [64]
+    __nv_bfloat16 *Ot = reinterpret_cast<__nv_bfloat16 *>(ca + kC);        // [128 features][72]
+    __nv_bfloat16 *Uh = Ot + kDV * kPadP;                                  // [64][136]
+    __nv_bfloat16 *Zh = Uh + kC * kPadH;                                   // [64][136]
     const int chunks = T / kC;
     const int head = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
     const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int plain_r = (lane & 7) + 8 * ((lane >> 3) & 1), plain_c = 8 * (lane >> 4);
+    const int flip_r = (lane & 7) + 8 * (lane >> 4), flip_c = 8 * ((lane >> 3) & 1);
     for (int i = tid; i < kDV * kC / 8; i += 256) {
         const int f = i >> 3, t8 = (i & 7) * 8;
-        float dv8[8];
-        Access<__nv_bfloat16, true>::load_cached(dout + (static_cast<long long>(head) * kDV + f) * T + static_cast<long long>(chunk) * kC + t8, dv8);
-#pragma unroll
-        for (int e = 0; e < 8; e++) dOs[(t8 + e) * kPadF + f] = dv8[e];
+        *reinterpret_cast<uint4 *>(Ot + f * kPadP + t8) = __ldg(reinterpret_cast<const uint4 *>(
+            dout + (static_cast<long long>(head) * kDV + f) * T + static_cast<long long>(chunk) * kC + t8));
     }
-    for (int i = tid; i < kC * kDV / 4; i += 256) {
-        const int r = i / (kDV / 4), c = (i % (kDV / 4)) * 4;
-        *reinterpret_cast<float4 *>(Us + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(u_save + (row0 + r) * kDV + c));
-        *reinterpret_cast<float4 *>(dZs + r * kPadF + c) = __ldg(reinterpret_cast<const float4 *>(dz_save + (row0 + r) * kDV + c));
+    for (int i = tid; i < kC * kDV / 8; i += 256) {
+        const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
+        const float *us = u_save + (row0 + r) * kDV + c, *zs = dz_save + (row0 + r) * kDV + c;
+        const float4 u0 = __ldg(reinterpret_cast<const float4 *>(us)), u1 = __ldg(reinterpret_cast<const float4 *>(us) + 1);
+        const float4 z0 = __ldg(reinterpret_cast<const float4 *>(zs)), z1 = __ldg(reinterpret_cast<const float4 *>(zs) + 1);
+        *reinterpret_cast<uint4 *>(Uh + r * kPadH + c) =
+            make_uint4(pack_bf16x2(u0.x, u0.y), pack_bf16x2(u0.z, u0.w), pack_bf16x2(u1.x, u1.y), pack_bf16x2(u1.z, u1.w));
+        *reinterpret_cast<uint4 *>(Zh + r * kPadH + c) =
+            make_uint4(pack_bf16x2(z0.x, z0.y), pack_bf16x2(z0.z, z0.w), pack_bf16x2(z1.x, z1.y), pack_bf16x2(z1.z, z1.w));
     }
     if (tid < 32) {
         float lo, hi;
@@ -819,42 +826,33 @@ __global__ void __launch_bounds__(256) deltanet_bwd_xg_kernel(const float *a, co
         ca[tid + 32] = hi;
     }
     __syncthreads();
-    // thread (ty, tx): rows 4 ty .. 4 ty + 3, columns tx + 16 j (neighbouring threads read neighbouring rows of U:
-    // no bank conflicts); column blocks wholly above the diagonal are skipped
-    const int ty = tid >> 4, tx = tid & 15;
+    const int m0 = 16 * (warp & 3), n0 = 32 * (warp >> 2);
     float xo[4][4] = {}, zo[4][4] = {};
-    const int nj = ty / 4 + 1;
-    for (int d = 0; d < kDV; d += 4) {
-        float4 dt[4], zt[4], us[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            dt[i] = *reinterpret_cast<const float4 *>(dOs + (ty * 4 + i) * kPadF + d);
-            zt[i] = *reinterpret_cast<const float4 *>(dZs + (ty * 4 + i) * kPadF + d);
-        }
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-            if (j < nj) us[j] = *reinterpret_cast<const float4 *>(Us + (tx + 16 * j) * kPadF + d);
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-            if (j < nj) {
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    xo[i][j] += dt[i].x * us[j].x + dt[i].y * us[j].y + dt[i].z * us[j].z + dt[i].w * us[j].w;
-                    zo[i][j] += zt[i].x * us[j].x + zt[i].y * us[j].y + zt[i].z * us[j].z + zt[i].w * us[j].w;
-                }
-            }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const int t = ty * 4 + i;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int s = tx + 16 * j;
-            const float dec = t >= s ? __expf(ca[t] - ca[s]) : 0.0f;
-            x_out[(row0 + t) * kC + s] = t >= s ? dec * xo[i][j] : 0.0f;
-            g_out[(row0 + t) * kC + s] = t > s ? -dec * zo[i][j] : 0.0f;
+    const int live = n0 > m0 + 15 ? 0 : (m0 + 15 - n0) / 8 + 1;   // 8-column tiles that reach the diagonal
+    if (live > 0) {
+#pragma unroll 2
+        for (int d = 0; d < kDV; d += 16) {
+            uint32_t ao[4], az[4], b0[4], b1[4];
+            ldsm_x4_trans(ao, Ot + (d + flip_r) * kPadP + m0 + flip_c);         // A[t][f] = dO stored [f][t]
+            ldsm_x4(az, Zh + (m0 + plain_r) * kPadH + d + plain_c);
+            ldsm_x4(b0, Uh + (n0 + flip_r) * kPadH + d + flip_c);               // B[f][s] = U stored [s][f]
+            ldsm_x4(b1, Uh + (n0 + 16 + flip_r) * kPadH + d + flip_c);
+            mma_bf16(xo[0], ao, b0[0], b0[1]); mma_bf16(zo[0], az, b0[0], b0[1]);
+            if (live > 1) { mma_bf16(xo[1], ao, b0[2], b0[3]); mma_bf16(zo[1], az, b0[2], b0[3]); }
+            if (live > 2) { mma_bf16(xo[2], ao, b1[0], b1[1]); mma_bf16(zo[2], az, b1[0], b1[1]); }
+            if (live > 3) { mma_bf16(xo[3], ao, b1[2], b1[3]); mma_bf16(zo[3], az, b1[2], b1[3]); }
         }
     }
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e += 2) {
+            const int t = m0 + g + 8 * (e >> 1), s = n0 + 8 * j + 2 * t4;
+            const float d0 = t >= s ? __expf(ca[t] - ca[s]) : 0.0f, d1 = t >= s + 1 ? __expf(ca[t] - ca[s + 1]) : 0.0f;
+            *reinterpret_cast<float2 *>(x_out + (row0 + t) * kC + s) = make_float2(d0 * xo[j][e], d1 * xo[j][e + 1]);
+            *reinterpret_cast<float2 *>(g_out + (row0 + t) * kC + s) =
+                make_float2(t > s ? -d0 * zo[j][e] : 0.0f, t > s + 1 ? -d1 * zo[j][e + 1] : 0.0f);
+        }
 }
 
 // sum over a row's columns held by the four lanes that share g
@@ -1246,7 +1244,7 @@ constexpr size_t kScanSmem = 1024 + 2 * kTileSetBytes + 2 * kGateFloats * sizeof
                              (kDVB / kDVP) * (2 * kDK * kPadB + 2 * kC * kPadB + kDVP * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdScanSmem = 1024 + 2 * kBwdSetBytes + 2 * kGateFloats * sizeof(float) +
                                 (kDVB / kDVP) * (2 * kDK * kPadB + 2 * kC * kPadB + kDVP * kPadP) * sizeof(__nv_bfloat16);
-constexpr size_t kBwdXgSmem = (3 * kC * kPadF + kC) * sizeof(float);
+constexpr size_t kBwdXgSmem = kC * sizeof(float) + (kDV * kPadP + 2 * kC * kPadH) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdOutSmem = (3 * kC + 7 * 2 * kC + 8) * sizeof(float) + (kDK * kPadH + 4 * kC * kPadH) * sizeof(__nv_bfloat16);
 
 }  // namespace
