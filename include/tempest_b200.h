@@ -339,12 +339,16 @@ int tb200_attention_bwd_tune(const tb200_attn_desc *desc, const void *q, const v
 
 int tb200_attention_bwd_device_error(void);
 
+/* As tb200_device_error, for the DeltaNet scans, whose tiles arrive by TMA on an mbarrier: 0, or 1 (forward scan) /
+ * 2 (reverse scan) when a wait gave up. */
+int tb200_deltanet_device_error(void);
+
 /* As tb200_device_error, for the row kernels that wait on bulk copies into shared memory (the LayerNorm
  * backward of 1024-, 2048- and 4096-long rows with saved statistics): 0, or 1 when a wait gave up. */
 int tb200_rows_device_error(void);
 
 /* All the error words in one call: synchronises the device, returns
- * product | attention forward << 8 | attention backward << 16 | row kernels << 24 (0 = every bounded
+ * product | attention forward << 8 | attention backward << 16 | row kernels << 24 | DeltaNet scans << 28 (0 = every bounded
  * wait completed) and clears them, or a negative status.  The launch entry
  * points return TB200_OK once their kernels are enqueued, so a wait that gives
  * up later is visible only here: a caller polls this wherever it synchronises

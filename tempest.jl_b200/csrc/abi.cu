@@ -79,5 +79,7 @@ extern "C" int tb200_device_errors(void) {
     if (backward < 0) return backward;
     const int rows = tb200_rows_device_error();
     if (rows < 0) return rows;
-    return (product & 0xff) | ((forward & 0xff) << 8) | ((backward & 0xff) << 16) | ((rows & 0x7f) << 24);
+    const int scans = tb200_deltanet_device_error();
+    if (scans < 0) return scans;
+    return (product & 0xff) | ((forward & 0xff) << 8) | ((backward & 0xff) << 16) | ((rows & 0xf) << 24) | ((scans & 0x7) << 28);
 }

@@ -133,6 +133,7 @@ SIGNATURES = {
     "tb200_attention_bwd_device_error": (_i, []),
     "tb200_device_errors": (_i, []),
     "tb200_rows_device_error": (_i, []),
+    "tb200_deltanet_device_error": (_i, []),
     "tb200_deltanet_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_fwd": (_i, [ctypes.POINTER(DeltanetDesc), _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "tb200_gemm_tune": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
@@ -355,9 +356,17 @@ def rows_device_error():
     return code
 
 
+def deltanet_device_error():
+    """0, or 1 (forward scan) / 2 (reverse scan) when a DeltaNet scan gave up a bounded wait since the last call."""
+    code = load().tb200_deltanet_device_error()
+    if code < 0:
+        check("tb200_deltanet_device_error", code)
+    return code
+
+
 def device_errors():
-    """Synchronises the device; product | attention forward << 8 | attention backward << 16 | row kernels << 24 of
-    the codes the kernels record when a bounded wait gives up (0 = none), cleared by the call."""
+    """Synchronises the device; product | attention forward << 8 | attention backward << 16 | row kernels << 24 |
+    DeltaNet scans << 28 of the codes the kernels record when a bounded wait gives up (0 = none), cleared by the call."""
     code = load().tb200_device_errors()
     if code < 0:
         check("tb200_device_errors", code)

@@ -172,6 +172,11 @@ def test_config_launch_of_64_sequences(pkg, cuda, oracle):
             assert torch.equal(w[h], s[0])
 
 
+def test_bounded_waits_report_nothing(pkg, cuda):
+    """The scans wait for their tiles on mbarriers, with a limit; after every launch of this file none has given up."""
+    assert pkg.lib.deltanet_device_error() == 0
+
+
 def test_refuses_other_geometries(pkg, cuda):
     L = pkg.lib
     x = cuda.zeros(64, device="cuda")
