@@ -336,7 +336,7 @@ __device__ __forceinline__ const unsigned char *swz(const unsigned char *tile, i
 __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __grid_constant__ ScanMaps maps,
                                                                      const float *gates_in,
                                                                      const __nv_bfloat16 *u_in, __nv_bfloat16 *o,
-                                                                     float *s_save, float *u_save, int T) {
+                                                                     __nv_bfloat16 *s_save, __nv_bfloat16 *u_save, int T) {
     extern __shared__ unsigned char sm_raw[];
     // the tiles want 1024-byte alignment (the swizzle's period); the launch asks for 1 KB more than the layout
     unsigned char *tiles = sm_raw + ((1024u - (sm100::smem_u32(sm_raw) & 1023u)) & 1023u);   // [2][7 boxes]
@@ -453,11 +453,11 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __gri
         wait_tiles(chunk);
         if (o && chunk > 0) write_out(chunk - 1);
         if (s_save) {      // the state this chunk starts from, for the backward
-            float *dst = s_save + (static_cast<long long>(head) * chunks + chunk) * kDK * kDV + part * kDVP;
+            __nv_bfloat16 *dst = s_save + (static_cast<long long>(head) * chunks + chunk) * kDK * kDV + part * kDVP;
 #pragma unroll
             for (int nt = 0; nt < 4; nt++) {
-                *reinterpret_cast<float2 *>(dst + (16 * warp + g) * kDV + 8 * nt + 2 * t4) = make_float2(state[nt][0], state[nt][1]);
-                *reinterpret_cast<float2 *>(dst + (16 * warp + g + 8) * kDV + 8 * nt + 2 * t4) = make_float2(state[nt][2], state[nt][3]);
+                *reinterpret_cast<uint32_t *>(dst + (16 * warp + g) * kDV + 8 * nt + 2 * t4) = pack_bf16x2(state[nt][0], state[nt][1]);
+                *reinterpret_cast<uint32_t *>(dst + (16 * warp + g + 8) * kDV + 8 * nt + 2 * t4) = pack_bf16x2(state[nt][2], state[nt][3]);
             }
         }
 
@@ -491,7 +491,7 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const __gri
                     const float ed = ekd[row];
                     *reinterpret_cast<uint32_t *>(Ub + row * kPadB + col) = pack_bf16x2(u2.x, u2.y);
                     *reinterpret_cast<uint32_t *>(Ud + row * kPadB + col) = pack_bf16x2(ed * u2.x, ed * u2.y);
-                    if (u_save) *reinterpret_cast<float2 *>(u_save + (row0 + row) * kDV + part * kDVP + col) = u2;
+                    if (u_save) *reinterpret_cast<uint32_t *>(u_save + (row0 + row) * kDV + part * kDVP + col) = pack_bf16x2(u2.x, u2.y);
                 }
         }
         __syncthreads();   // U is complete
@@ -590,8 +590,8 @@ __device__ __forceinline__ const unsigned char *swz_row128(const unsigned char *
 }
 
 __global__ void __launch_bounds__(kScanThreads) deltanet_bwd_scan_kernel(const __grid_constant__ BwdScanMaps maps,
-                                                                         const float *gates_in, float *dsin_save,
-                                                                         float *dz_save, __nv_bfloat16 *dv_out, int T) {
+                                                                         const float *gates_in, __nv_bfloat16 *dsin_save,
+                                                                         __nv_bfloat16 *dz_save, __nv_bfloat16 *dv_out, int T) {
     extern __shared__ unsigned char sm_raw[];
     unsigned char *tiles = sm_raw + ((1024u - (sm100::smem_u32(sm_raw) & 1023u)) & 1023u);   // [2] sets
     float *gate2 = reinterpret_cast<float *>(tiles + 2 * kBwdSetBytes);   // [2][kGateFloats]
@@ -679,11 +679,11 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_bwd_scan_kernel(const _
         // a buffer is used by every other chunk: chunks - 1, chunks - 3, ... share one, so its phase goes by step / 2
         wait_tiles(chunk, static_cast<uint32_t>((step >> 1) & 1));
         {   // the incoming state gradient, for the per-chunk kernel
-            float *dst = dsin_save + cidx * kDK * kDV + part * kDVP;
+            __nv_bfloat16 *dst = dsin_save + cidx * kDK * kDV + part * kDVP;
 #pragma unroll
             for (int nt = 0; nt < 4; nt++) {
-                *reinterpret_cast<float2 *>(dst + (16 * warp + g) * kDV + 8 * nt + 2 * t4) = make_float2(state[nt][0], state[nt][1]);
-                *reinterpret_cast<float2 *>(dst + (16 * warp + g + 8) * kDV + 8 * nt + 2 * t4) = make_float2(state[nt][2], state[nt][3]);
+                *reinterpret_cast<uint32_t *>(dst + (16 * warp + g) * kDV + 8 * nt + 2 * t4) = pack_bf16x2(state[nt][0], state[nt][1]);
+                *reinterpret_cast<uint32_t *>(dst + (16 * warp + g + 8) * kDV + 8 * nt + 2 * t4) = pack_bf16x2(state[nt][2], state[nt][3]);
             }
         }
         {   // e dO beside dO: eight positions of one feature a thread
@@ -748,7 +748,7 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_bwd_scan_kernel(const _
                 for (int hr = 0; hr < 2; hr++) {
                     const int t = 16 * mt + g + 8 * hr, col = 16 * nh + 8 * nt + 2 * t4;
                     const float2 z2 = make_float2(z[nt][2 * hr], z[nt][2 * hr + 1]);
-                    *reinterpret_cast<float2 *>(dz_save + (row0 + t) * kDV + part * kDVP + col) = z2;
+                    *reinterpret_cast<uint32_t *>(dz_save + (row0 + t) * kDV + part * kDVP + col) = pack_bf16x2(z2.x, z2.y);
                     const float b = be[t], eb = -eca[t] * b;
                     *reinterpret_cast<uint32_t *>(Zs + t * kPadB + col) = pack_bf16x2(eb * z2.x, eb * z2.y);
                     *reinterpret_cast<uint32_t *>(dv_out + (row0 + t) * kDV + part * kDVP + col) = pack_bf16x2(b * z2.x, b * z2.y);
@@ -787,12 +787,12 @@ __global__ void __launch_bounds__(kScanThreads) deltanet_bwd_scan_kernel(const _
 }
 
 // X = tril(dO U') .* D and G = -stril(dZ U') .* D, one block per (head, chunk): two 64 x 64 x 128 products as
-// BFloat16 MMAs (U and dZ rounded as they are staged; dO is read as it lies, [feature][position], as a transposed A
+// BFloat16 MMAs (U and dZ arrive rounded from the scans; dO is read as it lies, [feature][position], as a transposed A
 // operand).  Warp w takes rows 16 (w % 4) .. + 15 and columns 32 (w / 4) .. + 31; tiles wholly above the diagonal
 // are skipped.
 __global__ void __launch_bounds__(256) deltanet_bwd_xg_kernel(const float *a, const __nv_bfloat16 *dout,
-                                                              const float *u_save, const float *dz_save, float *x_out,
-                                                              float *g_out, int T) {
+                                                              const __nv_bfloat16 *u_save, const __nv_bfloat16 *dz_save,
+                                                              __nv_bfloat16 *x_out, __nv_bfloat16 *g_out, int T) {
     extern __shared__ float sm[];
     float *ca = sm;                                                        // [64]
     __nv_bfloat16 *Ot = reinterpret_cast<__nv_bfloat16 *>(ca + kC);        // [128 features][72]
@@ -811,13 +811,8 @@ __global__ void __launch_bounds__(256) deltanet_bwd_xg_kernel(const float *a, co
     }
     for (int i = tid; i < kC * kDV / 8; i += 256) {
         const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
-        const float *us = u_save + (row0 + r) * kDV + c, *zs = dz_save + (row0 + r) * kDV + c;
-        const float4 u0 = __ldg(reinterpret_cast<const float4 *>(us)), u1 = __ldg(reinterpret_cast<const float4 *>(us) + 1);
-        const float4 z0 = __ldg(reinterpret_cast<const float4 *>(zs)), z1 = __ldg(reinterpret_cast<const float4 *>(zs) + 1);
-        *reinterpret_cast<uint4 *>(Uh + r * kPadH + c) =
-            make_uint4(pack_bf16x2(u0.x, u0.y), pack_bf16x2(u0.z, u0.w), pack_bf16x2(u1.x, u1.y), pack_bf16x2(u1.z, u1.w));
-        *reinterpret_cast<uint4 *>(Zh + r * kPadH + c) =
-            make_uint4(pack_bf16x2(z0.x, z0.y), pack_bf16x2(z0.z, z0.w), pack_bf16x2(z1.x, z1.y), pack_bf16x2(z1.z, z1.w));
+        *reinterpret_cast<uint4 *>(Uh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(u_save + (row0 + r) * kDV + c));
+        *reinterpret_cast<uint4 *>(Zh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(dz_save + (row0 + r) * kDV + c));
     }
     if (tid < 32) {
         float lo, hi;
@@ -849,9 +844,9 @@ __global__ void __launch_bounds__(256) deltanet_bwd_xg_kernel(const float *a, co
         for (int e = 0; e < 4; e += 2) {
             const int t = m0 + g + 8 * (e >> 1), s = n0 + 8 * j + 2 * t4;
             const float d0 = t >= s ? __expf(ca[t] - ca[s]) : 0.0f, d1 = t >= s + 1 ? __expf(ca[t] - ca[s + 1]) : 0.0f;
-            *reinterpret_cast<float2 *>(x_out + (row0 + t) * kC + s) = make_float2(d0 * xo[j][e], d1 * xo[j][e + 1]);
-            *reinterpret_cast<float2 *>(g_out + (row0 + t) * kC + s) =
-                make_float2(t > s ? -d0 * zo[j][e] : 0.0f, t > s + 1 ? -d1 * zo[j][e + 1] : 0.0f);
+            *reinterpret_cast<uint32_t *>(x_out + (row0 + t) * kC + s) = pack_bf16x2(d0 * xo[j][e], d1 * xo[j][e + 1]);
+            *reinterpret_cast<uint32_t *>(g_out + (row0 + t) * kC + s) =
+                pack_bf16x2(t > s ? -d0 * zo[j][e] : 0.0f, t > s + 1 ? -d1 * zo[j][e + 1] : 0.0f);
         }
 }
 
@@ -863,9 +858,9 @@ __device__ __forceinline__ float sum_quad(float v) {
 }
 
 // dQ, dK, da, dbeta of one chunk; one block per (head, chunk), two blocks per SM.  The eight products of the chunk
-// are BFloat16 m16n8k16 MMAs whose fragments come through ldmatrix: the Float32 arrays the scans left (the state, its
-// gradient, U, dZ, X, G) are rounded to BFloat16 as they are staged in shared memory -- the rounding the reference
-// gives the Float32 factor of a mixed product (ext/cuTileExt/emit.jl:914-921) -- and Q, K, dO are BFloat16 already.
+// are BFloat16 m16n8k16 MMAs whose fragments come through ldmatrix: what the scans and the X/G kernel left (the state,
+// its gradient, U, dZ, X, G) was rounded to BFloat16 where it was written -- the rounding the reference gives the
+// Float32 factor of a mixed product (ext/cuTileExt/emit.jl:914-921) -- and Q, K, dO are BFloat16 already.
 // (As TF32 MMAs with one scalar load and one conversion per fragment element this kernel took half the pullback's
 // time: the warp-level MMA issues once in about 16 cycles per SM quarter on this part, whatever its operand type,
 // so halving the number of MMAs and dropping the conversions is what pays.)  Warp w takes positions
@@ -875,8 +870,8 @@ __device__ __forceinline__ float sum_quad(float v) {
 // shared memory.  X, G and beta .* G take the state's place once the products with the state are done.
 __global__ void __launch_bounds__(256, 2) deltanet_bwd_out_kernel(
     const __nv_bfloat16 *q, const __nv_bfloat16 *k, const __nv_bfloat16 *v, const float *a, const float *beta,
-    const __nv_bfloat16 *dout, const float *s_save, const float *dsin_save, const float *u_save, const float *dz_save,
-    const float *x_in, const float *g_in, __nv_bfloat16 *dq, __nv_bfloat16 *dk, float *da, float *dbeta, int T) {
+    const __nv_bfloat16 *dout, const __nv_bfloat16 *s_save, const __nv_bfloat16 *dsin_save, const __nv_bfloat16 *u_save,
+    const __nv_bfloat16 *dz_save, const __nv_bfloat16 *x_in, const __nv_bfloat16 *g_in, __nv_bfloat16 *dq, __nv_bfloat16 *dk, float *da, float *dbeta, int T) {
     extern __shared__ float sm[];
     float *vec = sm;
     float *eca = vec, *ekd = vec + 64, *be = vec + 128;
@@ -901,14 +896,10 @@ __global__ void __launch_bounds__(256, 2) deltanet_bwd_out_kernel(
     const int plain_r = (lane & 7) + 8 * ((lane >> 3) & 1), plain_c = 8 * (lane >> 4);
     const int flip_r = (lane & 7) + 8 * (lane >> 4), flip_c = 8 * ((lane >> 3) & 1);
 
-    // eight Float32 values from global memory, rounded, as one 16-byte piece of a BFloat16 tile
-    auto round8 = [](const float *src) {
-        const float4 lo = __ldg(reinterpret_cast<const float4 *>(src)), hi = __ldg(reinterpret_cast<const float4 *>(src) + 1);
-        return make_uint4(pack_bf16x2(lo.x, lo.y), pack_bf16x2(lo.z, lo.w), pack_bf16x2(hi.x, hi.y), pack_bf16x2(hi.z, hi.w));
-    };
+    auto piece = [](const __nv_bfloat16 *src) { return __ldg(reinterpret_cast<const uint4 *>(src)); };   // eight values
     for (int i = tid; i < kDK * kDV / 8; i += 256) {
         const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
-        *reinterpret_cast<uint4 *>(Sh + r * kPadH + c) = round8(s_save + cidx * kDK * kDV + r * kDV + c);
+        *reinterpret_cast<uint4 *>(Sh + r * kPadH + c) = piece(s_save + cidx * kDK * kDV + r * kDV + c);
     }
     for (int i = tid; i < kDV * kC / 8; i += 256) {   // dO arrives [feature][position]: turned as it is staged
         const int f = i >> 3, t8 = (i & 7) * 8;
@@ -923,7 +914,7 @@ __global__ void __launch_bounds__(256, 2) deltanet_bwd_out_kernel(
     }
     for (int i = tid; i < kC * kDV / 8; i += 256) {
         const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
-        *reinterpret_cast<uint4 *>(M1 + r * kPadH + c) = round8(dz_save + (row0 + r) * kDV + c);
+        *reinterpret_cast<uint4 *>(M1 + r * kPadH + c) = piece(dz_save + (row0 + r) * kDV + c);
     }
     for (int i = tid; i < kC * kDK / 8; i += 256) {
         const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
@@ -1049,19 +1040,21 @@ __global__ void __launch_bounds__(256, 2) deltanet_bwd_out_kernel(
         float dgp = 0.0f;
         for (int i = tid; i < kDK * kDV / 8; i += 256) {
             const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
-            const float *src = dsin_save + cidx * kDK * kDV + r * kDV + c;
-            const float4 lo = __ldg(reinterpret_cast<const float4 *>(src)), hi = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+            const uint4 nw = piece(dsin_save + cidx * kDK * kDV + r * kDV + c);
             uint4 *slot = reinterpret_cast<uint4 *>(Sh + r * kPadH + c);
             const uint4 old = *slot;
-            float o8[8];
+            float o8[8], n8[8];
             unpack_bf16x2(old.x, o8[0], o8[1]); unpack_bf16x2(old.y, o8[2], o8[3]);
             unpack_bf16x2(old.z, o8[4], o8[5]); unpack_bf16x2(old.w, o8[6], o8[7]);
-            dgp += o8[0] * lo.x + o8[1] * lo.y + o8[2] * lo.z + o8[3] * lo.w + o8[4] * hi.x + o8[5] * hi.y + o8[6] * hi.z + o8[7] * hi.w;
-            *slot = make_uint4(pack_bf16x2(lo.x, lo.y), pack_bf16x2(lo.z, lo.w), pack_bf16x2(hi.x, hi.y), pack_bf16x2(hi.z, hi.w));
+            unpack_bf16x2(nw.x, n8[0], n8[1]); unpack_bf16x2(nw.y, n8[2], n8[3]);
+            unpack_bf16x2(nw.z, n8[4], n8[5]); unpack_bf16x2(nw.w, n8[6], n8[7]);
+#pragma unroll
+            for (int e = 0; e < 8; e++) dgp = fmaf(o8[e], n8[e], dgp);
+            *slot = nw;
         }
         for (int i = tid; i < kC * kDV / 8; i += 256) {
             const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
-            *reinterpret_cast<uint4 *>(M0 + r * kPadH + c) = round8(u_save + (row0 + r) * kDV + c);
+            *reinterpret_cast<uint4 *>(M0 + r * kPadH + c) = piece(u_save + (row0 + r) * kDV + c);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) dgp += __shfl_xor_sync(0xffffffffu, dgp, o);
@@ -1089,15 +1082,19 @@ __global__ void __launch_bounds__(256, 2) deltanet_bwd_out_kernel(
     __syncthreads();   // the state's place is free: X, G and beta .* G move in
     for (int i = tid; i < kC * kC / 8; i += 256) {
         const int r = i / (kC / 8), c = (i % (kC / 8)) * 8;
-        *reinterpret_cast<uint4 *>(Xh + r * kPadP + c) = round8(x_in + row0 * kC + r * kC + c);
-        const float *src = g_in + row0 * kC + r * kC + c;
-        const float4 lo = __ldg(reinterpret_cast<const float4 *>(src)), hi = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        *reinterpret_cast<uint4 *>(Xh + r * kPadP + c) = piece(x_in + row0 * kC + r * kC + c);
+        const uint4 g8 = piece(g_in + row0 * kC + r * kC + c);
+        *reinterpret_cast<uint4 *>(Gh + r * kPadP + c) = g8;
         const float b = be[r];
-        *reinterpret_cast<uint4 *>(Gh + r * kPadP + c) =
-            make_uint4(pack_bf16x2(lo.x, lo.y), pack_bf16x2(lo.z, lo.w), pack_bf16x2(hi.x, hi.y), pack_bf16x2(hi.z, hi.w));
-        *reinterpret_cast<uint4 *>(Gb + r * kPadP + c) =
-            make_uint4(pack_bf16x2(b * lo.x, b * lo.y), pack_bf16x2(b * lo.z, b * lo.w), pack_bf16x2(b * hi.x, b * hi.y),
-                       pack_bf16x2(b * hi.z, b * hi.w));
+        const uint32_t w4[4] = {g8.x, g8.y, g8.z, g8.w};
+        uint32_t s4[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            float lo, hi;
+            unpack_bf16x2(w4[e], lo, hi);
+            s4[e] = pack_bf16x2(b * lo, b * hi);
+        }
+        *reinterpret_cast<uint4 *>(Gb + r * kPadP + c) = make_uint4(s4[0], s4[1], s4[2], s4[3]);
     }
     __syncthreads();
 
@@ -1236,8 +1233,8 @@ int scan_tmap(CUtensorMap *map, const void *base, long long rows, long long cols
 
 // The forward scan's launch: tensor maps over W (scratch), Q, K and P (scratch), one block per (head, 64 features).
 int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, const float *gates, const __nv_bfloat16 *w,
-                const __nv_bfloat16 *u, const __nv_bfloat16 *pw, __nv_bfloat16 *o, float *s_save, float *u_save,
-                cudaStream_t stream);
+                const __nv_bfloat16 *u, const __nv_bfloat16 *pw, __nv_bfloat16 *o, __nv_bfloat16 *s_save,
+                __nv_bfloat16 *u_save, cudaStream_t stream);
 
 constexpr size_t kChunkSmem = (2 * kC * kPadA + 3 * kC) * sizeof(float) + 3 * kC * kPadH * sizeof(__nv_bfloat16);
 constexpr size_t kScanSmem = 1024 + 2 * kTileSetBytes + 2 * kGateFloats * sizeof(float) +
@@ -1277,7 +1274,7 @@ int configure_deltanet(int device) {
 
 // bytes per position of the backward's workspace, after the forward's part
 constexpr size_t kBwdRowBytes = (kC /*Minv*/ + kDK * kDV / kC /*S*/ + kDV /*U*/ + kDK * kDV / kC /*dS'*/ + kDV /*dZ*/ +
-                                 2 * kC /*X, G*/) * sizeof(float);
+                                 2 * kC /*X, G*/) * sizeof(__nv_bfloat16);
 }  // namespace
 
 extern "C" size_t tb200_deltanet_workspace_bytes(const tb200_deltanet_desc *d) {
@@ -1289,8 +1286,8 @@ extern "C" size_t tb200_deltanet_workspace_bytes(const tb200_deltanet_desc *d) {
 namespace tb200 {
 namespace {
 int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, const float *gates, const __nv_bfloat16 *w,
-                const __nv_bfloat16 *u, const __nv_bfloat16 *pw, __nv_bfloat16 *o, float *s_save, float *u_save,
-                cudaStream_t stream) {
+                const __nv_bfloat16 *u, const __nv_bfloat16 *pw, __nv_bfloat16 *o, __nv_bfloat16 *s_save,
+                __nv_bfloat16 *u_save, cudaStream_t stream) {
     const long long rows = static_cast<long long>(d->heads) * d->positions;
     ScanMaps maps;
     int st = scan_tmap(&maps.w, w, rows, kDK);
@@ -1365,14 +1362,14 @@ extern "C" int tb200_deltanet_bwd(const tb200_deltanet_desc *d, const void *q, c
     __nv_bfloat16 *u = w + rows * kDK;
     __nv_bfloat16 *pw = u + rows * kDV;
     float *gates = reinterpret_cast<float *>(pw + rows * kC);
-    float *minv_room = gates + rows / kC * kGateFloats;                    // rows * kC floats, half of them used
-    __nv_bfloat16 *minv = reinterpret_cast<__nv_bfloat16 *>(minv_room);   // (I + A)^-1 as the reverse scan's operand
-    float *s_save = minv_room + rows * kC;
-    float *u_save = s_save + rows * (kDK * kDV / kC);
-    float *dsin = u_save + rows * kDV;
-    float *dz = dsin + rows * (kDK * kDV / kC);
-    float *xw = dz + rows * kDV;
-    float *gw = xw + rows * kC;
+    // what the pullback keeps between its launches, all BFloat16 (every consumer takes it as an MMA operand)
+    __nv_bfloat16 *minv = reinterpret_cast<__nv_bfloat16 *>(gates + rows / kC * kGateFloats);   // (I + A)^-1
+    __nv_bfloat16 *s_save = minv + rows * kC;                       // the state at every chunk start
+    __nv_bfloat16 *u_save = s_save + rows * (kDK * kDV / kC);
+    __nv_bfloat16 *dsin = u_save + rows * kDV;                      // the state gradient arriving at every chunk
+    __nv_bfloat16 *dz = dsin + rows * (kDK * kDV / kC);
+    __nv_bfloat16 *xw = dz + rows * kDV;
+    __nv_bfloat16 *gw = xw + rows * kC;
     const int T = d->positions;
     const unsigned chunks = static_cast<unsigned>(d->heads) * (T / kC);
     const __nv_bfloat16 *qb = static_cast<const __nv_bfloat16 *>(q), *kb = static_cast<const __nv_bfloat16 *>(k),

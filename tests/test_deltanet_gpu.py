@@ -197,7 +197,7 @@ def test_pullback_refuses_what_it_cannot_run(pkg, cuda):
     assert e.value.status == -7
     d = L.deltanet_desc(1, 128)
     need = L.deltanet_bwd_workspace_bytes(d)
-    assert need == L.deltanet_workspace_bytes(d) + 128 * 3840
+    assert need == L.deltanet_workspace_bytes(d) + 128 * 1920   # what the launches hand each other, BFloat16
     with pytest.raises(L.TB200Error) as e:   # a workspace that is too small
         L.deltanet_bwd(d, *args, p, need - 1)
     assert e.value.status == -5
