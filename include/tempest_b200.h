@@ -570,7 +570,11 @@ size_t tb200_colreduce_source(const tb200_group_desc *desc, char *buffer, size_t
  * array is `across` over a batch).  Float32 or BFloat16 elements, Float32 states, results rounded once.
  * The order in which partial states are combined differs from a sequential sweep's (it is a tree over
  * threads), which rounds differently: the reference compares at rtol 1e-4 (test/cuda/scans.jl:27).
- * No workspace, nothing kept between calls. */
+ * Nothing is kept between calls.  A scan across the rows of a matrix with few columns has only its columns
+ * to spread over threads; given `workspace` (tb200_scan_workspace_bytes, 16-byte aligned) it is split into
+ * slabs of rows instead: one launch folds every slab to its total, a second sweeps every slab again starting
+ * from the totals before it (two reads and one write per element, in fixed order).  Without a workspace
+ * (null) one thread walks each column. */
 typedef enum tb200_scan_op {
     TB200_SCAN_SUM = 0, TB200_SCAN_PROD = 1, TB200_SCAN_MAX = 2, TB200_SCAN_MIN = 3,
     TB200_SCAN_AFFINE = 4, TB200_SCAN_VARIANCE = 5
@@ -584,7 +588,10 @@ typedef struct tb200_scan_desc {
     int across;
     int reverse;
     int dtype;
+    void *workspace;                     /* optional, for `across` */
+    size_t workspace_bytes;
 } tb200_scan_desc;
+size_t tb200_scan_workspace_bytes(const tb200_scan_desc *desc);
 int tb200_scan(const tb200_scan_desc *desc, const void *x, const void *x2, void *y, void *stream);
 
 /* ---- data-parallel update: gradient sum + SGD step in one kernel over NVLink -----

@@ -14,7 +14,9 @@
 // Across the rows (the scanned axis is the strided one): one thread per column walks the rows in order with its
 // state in a register, eight rows' loads in flight at a time; neighbouring threads read neighbouring columns, so
 // every access is coalesced.  Parallelism is the number of columns: a scan across many rows of few columns keeps
-// few SMs busy (measured: 16384 rows of 4096 Float32 columns, 16 blocks).
+// few SMs busy (measured: 16384 rows of 4096 Float32 columns, 16 blocks, 0.32 TB/s); with scratch for their totals
+// the rows are cut into slabs that are folded side by side and swept a second time from the totals before them
+// (2.6 TB/s at that shape).
 // Float32 or BFloat16 elements; states and arithmetic in Float32, each result rounded once.
 #include "common.cuh"
 
@@ -106,6 +108,8 @@ struct ScanArgs {
     long long stride_x, stride_x2, stride_y;   // between the matrices of the batch
     int reverse;
     int vec;   // along rows: every row is a whole number of 16-byte aligned groups of eight elements
+    int slabs;       // across rows: runs the rows are cut into (1: one thread walks a column)
+    float *totals;   // the slabs' totals (caller's workspace)
 };
 
 // ---- along each row
@@ -243,8 +247,88 @@ __global__ void __launch_bounds__(kScanThreads) scan_columns_kernel(const ScanAr
     }
 }
 
+// ---- across the rows, in slabs: the rows are cut into `slabs` runs; first every (slab, column) folds its run to a
+// total (kept in the workspace as the state's Float32 words, [slab][word][column]), then every (slab, column) folds
+// the totals of the slabs before it, in order, and sweeps its run again from there.  Two reads and one write per
+// element; which states are combined in which order is fixed by the shape alone.
+template <int OP, typename T, bool WRITE>
+__global__ void __launch_bounds__(kScanThreads) scan_slabs_kernel(const ScanArgs a, float *totals, int slabs, long long per) {
+    using F = Fold<OP>;
+    using S = typename F::S;
+    constexpr int W = Words<S>::N;
+    const long long col = blockIdx.x * static_cast<long long>(kScanThreads) + threadIdx.x;
+    if (col >= a.n) return;
+    const int slab = blockIdx.y;
+    for (long long m = blockIdx.z; m < a.batch; m += gridDim.z) {
+        const T *x = static_cast<const T *>(a.x) + m * a.stride_x + col;
+        const T *x2 = a.x2 ? static_cast<const T *>(a.x2) + m * a.stride_x2 + col : nullptr;
+        T *y = static_cast<T *>(a.y) + m * a.stride_y + col;
+        float *mine = totals + (m * slabs * W) * a.n + col;   // [slab][word] at this column
+        union { S s; float f[W]; } u;
+        S run = F::identity();
+        if (WRITE) {
+            for (int b = 0; b < slab; b++) {
+#pragma unroll
+                for (int w = 0; w < W; w++) u.f[w] = mine[(static_cast<long long>(b) * W + w) * a.n];
+                run = F::combine(run, u.s);
+            }
+        }
+        const long long p_begin = slab * per, p_end = p_begin + per < a.rows ? p_begin + per : a.rows;
+        constexpr int B = 8;
+        for (long long p0 = p_begin; p0 < p_end; p0 += B) {
+            float v[B], w2[B];
+#pragma unroll
+            for (int j = 0; j < B; j++) {
+                const long long p = p0 + j < p_end ? p0 + j : p_end - 1;
+                const long long r = a.reverse ? a.rows - 1 - p : p;
+                v[j] = load1(x + r * a.ld_x);
+                w2[j] = x2 ? load1(x2 + r * a.ld_x2) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < B; j++) {
+                if (p0 + j < p_end) {
+                    run = F::combine(run, F::lift(v[j], w2[j]));
+                    if (WRITE) {
+                        const long long r = a.reverse ? a.rows - 1 - (p0 + j) : p0 + j;
+                        store1(y + r * a.ld_y, F::observe(run));
+                    }
+                }
+            }
+        }
+        if (!WRITE) {
+            u.s = run;
+#pragma unroll
+            for (int w = 0; w < W; w++) mine[(static_cast<long long>(slab) * W + w) * a.n] = u.f[w];
+        }
+    }
+}
+
+// Slabs for a scan across `rows` rows of `n` columns: enough blocks to fill the device eight times over, at least
+// 64 rows a slab; 1 = not worth splitting.
+inline int scan_slabs(long long n, long long rows, long long batch, int sms) {
+    const long long col_blocks = ceil_div(n, kScanThreads) * (batch < 1 ? 1 : batch);
+    long long slabs = ceil_div(static_cast<long long>(sms) * 8, col_blocks);
+    if (slabs > rows / 64) slabs = rows / 64;
+    if (slabs > 1024) slabs = 1024;
+    return static_cast<int>(slabs < 1 ? 1 : slabs);
+}
+inline size_t scan_slab_bytes(int op, long long n, long long batch, int slabs) {
+    const int words = op == TB200_SCAN_AFFINE ? 2 : op == TB200_SCAN_VARIANCE ? 3 : 1;
+    return slabs <= 1 ? 0 : static_cast<size_t>(slabs) * words * n * (batch < 1 ? 1 : batch) * sizeof(float);
+}
+
 template <int OP, typename T>
 int launch_scan(const ScanArgs &a, bool across, const DeviceInfo &dev, cudaStream_t stream) {
+    if (across && a.slabs > 1) {
+        const long long per = ceil_div(a.rows, static_cast<long long>(a.slabs));
+        dim3 grid(static_cast<unsigned>(ceil_div(a.n, kScanThreads)), static_cast<unsigned>(a.slabs),
+                  static_cast<unsigned>(a.batch < 64 ? a.batch : 64));
+        scan_slabs_kernel<OP, T, false><<<grid, kScanThreads, 0, stream>>>(a, a.totals, a.slabs, per);
+        TB200_CUDA(cudaGetLastError());
+        scan_slabs_kernel<OP, T, true><<<grid, kScanThreads, 0, stream>>>(a, a.totals, a.slabs, per);
+        TB200_CUDA(cudaGetLastError());
+        return TB200_OK;
+    }
     if (across) {
         dim3 grid(static_cast<unsigned>(ceil_div(a.n, kScanThreads)), static_cast<unsigned>(a.batch < 65535 ? a.batch : 65535));
         scan_columns_kernel<OP, T><<<grid, kScanThreads, 0, stream>>>(a);
@@ -277,6 +361,14 @@ int launch_by_op(int op, const ScanArgs &a, bool across, const DeviceInfo &dev, 
 
 using namespace tb200;
 
+extern "C" size_t tb200_scan_workspace_bytes(const tb200_scan_desc *d) {
+    if (!d || !d->across || d->n <= 0 || d->rows <= 0 || d->op < TB200_SCAN_SUM || d->op > TB200_SCAN_VARIANCE) return 0;
+    DeviceInfo dev;
+    if (current_device(&dev) != TB200_OK) return 0;
+    const long long batch = d->batch > 1 ? d->batch : 1;
+    return scan_slab_bytes(d->op, d->n, batch, scan_slabs(d->n, d->rows, batch, dev.sms));
+}
+
 extern "C" int tb200_scan(const tb200_scan_desc *d, const void *x, const void *x2, void *y, void *stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!d) return TB200_ERR_NULL;
@@ -305,6 +397,16 @@ extern "C" int tb200_scan(const tb200_scan_desc *d, const void *x, const void *x
         const bool pitches = a.ld_x % per == 0 && a.ld_y % per == 0 && (!pairs || a.ld_x2 % per == 0) &&
                              (batch == 1 || (a.stride_x % per == 0 && a.stride_y % per == 0 && (!pairs || a.stride_x2 % per == 0)));
         a.vec = !d->across && a.n % 8 == 0 && pitches && aligned_to(x, 16) && aligned_to(y, 16) && (!pairs || aligned_to(x2, 16));
+    }
+    a.slabs = 1;
+    if (d->across && d->workspace) {
+        const int slabs = scan_slabs(d->n, d->rows, batch, dev.sms);
+        const size_t need = scan_slab_bytes(d->op, d->n, batch, slabs);
+        if (need) {
+            if (d->workspace_bytes < need || !aligned_to(d->workspace, 16)) return TB200_ERR_WORKSPACE;
+            a.slabs = slabs;
+            a.totals = static_cast<float *>(d->workspace);
+        }
     }
     if (d->dtype == TB200_F32) return launch_by_op<float>(d->op, a, d->across != 0, dev, stream);
     return launch_by_op<__nv_bfloat16>(d->op, a, d->across != 0, dev, stream);

@@ -190,9 +190,18 @@ def _scan_parts(template):
 class ScanLaunch:
     """One scan on fixed operands (tb200_scan)."""
 
-    def __init__(self, binding: "Binding"):
+    def __init__(self, binding: "Binding", resources=None):
         self.binding = binding
         self.op, self.across, self.reverse = _scan_parts(binding.template)
+        # a scan across many rows of few columns is cut into runs of rows when it is given scratch for their totals
+        self.workspace, self.workspace_bytes = None, 0
+        if self.across:
+            e, a = binding.extents, binding.arrays
+            need = lib.scan_workspace_bytes(lib.scan_desc(e["n"], e["rows"], self.op, across=True, reverse=self.reverse,
+                                                          dtype=ELTYPES[a["x"].eltype][0]))
+            if need:
+                resources = resources if resources is not None else Resources()
+                self.workspace, self.workspace_bytes = resources.workspace(need), need
 
     def repoints(self) -> bool:
         return True
@@ -209,7 +218,8 @@ class ScanLaunch:
         lib.scan(a["x"].pointer(), a["y"].pointer(), e["n"], e["rows"], self.op,
                  x2=a["x2"].pointer() if "x2" in a else 0, across=self.across, reverse=self.reverse,
                  dtype=ELTYPES[a["x"].eltype][0], ld_x=ld(a["x"]), ld_x2=ld(a["x2"]) if "x2" in a else None,
-                 ld_y=ld(a["y"]), stream=current_stream())
+                 ld_y=ld(a["y"]), workspace=self.workspace.data_ptr() if self.workspace is not None else 0,
+                 workspace_bytes=self.workspace_bytes, stream=current_stream())
 
 
 def dense_matrix(buffer, eltype, rows, cols, value=0, offset=0):
@@ -485,7 +495,7 @@ class B200Kernels:
             return LinearLaunch(b), f"B200 {b.template}, {e['m']} x {e['n']} over {e['k']}, {b.arrays['w'].eltype}"
         if _scan_parts(b.template) is not None:
             e = b.extents
-            return ScanLaunch(b), f"B200 {b.template}, {e['rows']} rows of {e['n']} {b.arrays['x'].eltype}"
+            return ScanLaunch(b, resources), f"B200 {b.template}, {e['rows']} rows of {e['n']} {b.arrays['x'].eltype}"
         if b.template.startswith("attention"):
             launch = AttentionLaunch(b)
             form = ""

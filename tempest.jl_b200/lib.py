@@ -61,7 +61,8 @@ class ScanDesc(ctypes.Structure):
     _fields_ = [("n", ctypes.c_int64), ("rows", ctypes.c_int64), ("ld_x", ctypes.c_int64), ("ld_x2", ctypes.c_int64),
                 ("ld_y", ctypes.c_int64), ("batch", ctypes.c_int64), ("stride_x", ctypes.c_int64),
                 ("stride_x2", ctypes.c_int64), ("stride_y", ctypes.c_int64), ("op", ctypes.c_int),
-                ("across", ctypes.c_int), ("reverse", ctypes.c_int), ("dtype", ctypes.c_int)]
+                ("across", ctypes.c_int), ("reverse", ctypes.c_int), ("dtype", ctypes.c_int),
+                ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t)]
 
 
 SCAN_SUM, SCAN_PROD, SCAN_MAX, SCAN_MIN, SCAN_AFFINE, SCAN_VARIANCE = range(6)
@@ -153,6 +154,7 @@ SIGNATURES = {
     "tb200_colreduce_source": (_sz, [ctypes.POINTER(GroupDesc), ctypes.c_char_p, _sz]),
     "tb200_deltanet_bwd_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_bwd": (_i, [ctypes.POINTER(DeltanetDesc)] + [_p] * 12 + [_sz, _p]),
+    "tb200_scan_workspace_bytes": (_sz, [ctypes.POINTER(ScanDesc)]),
     "tb200_scan": (_i, [ctypes.POINTER(ScanDesc), _p, _p, _p, _p]),
     "tb200_dp_signal_bytes": (_sz, []),
     "tb200_dp_state_bytes": (_sz, []),
@@ -608,10 +610,30 @@ def dp_error():
     return code
 
 
+def scan_desc(n, rows, op, *, across=False, reverse=False, dtype=F32, ld_x=None, ld_x2=None, ld_y=None, batch=1,
+              stride_x=None, stride_x2=None, stride_y=None, workspace=0, workspace_bytes=0):
+    d = ScanDesc()
+    d.n, d.rows, d.op, d.across, d.reverse, d.dtype, d.batch = n, rows, op, int(across), int(reverse), dtype, batch
+    d.ld_x = n if ld_x is None else ld_x
+    d.ld_x2 = n if ld_x2 is None else ld_x2
+    d.ld_y = n if ld_y is None else ld_y
+    d.stride_x = rows * d.ld_x if stride_x is None else stride_x
+    d.stride_x2 = rows * d.ld_x2 if stride_x2 is None else stride_x2
+    d.stride_y = rows * d.ld_y if stride_y is None else stride_y
+    d.workspace, d.workspace_bytes = workspace or None, workspace_bytes
+    return d
+
+
+def scan_workspace_bytes(desc):
+    """Scratch with which a scan across the rows is split into slabs of rows (0: the form has no use for it)."""
+    return load().tb200_scan_workspace_bytes(ctypes.byref(desc))
+
+
 def scan(x, y, n, rows, op, *, x2=0, across=False, reverse=False, dtype=F32, ld_x=None, ld_x2=None, ld_y=None, batch=1,
-         stride_x=None, stride_x2=None, stride_y=None, stream=0):
+         stride_x=None, stride_x2=None, stride_y=None, workspace=0, workspace_bytes=0, stream=0):
     """y = running fold of x (tb200_scan): along each row of the (n, rows) matrix, or across its rows."""
     d = ScanDesc()
+    d.workspace, d.workspace_bytes = workspace or None, workspace_bytes
     d.n, d.rows, d.op, d.across, d.reverse, d.dtype, d.batch = n, rows, op, int(across), int(reverse), dtype, batch
     d.ld_x = n if ld_x is None else ld_x
     d.ld_x2 = n if ld_x2 is None else ld_x2

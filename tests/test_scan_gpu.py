@@ -13,8 +13,9 @@ pytestmark = pytest.mark.gpu
 OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3, "affine": 4, "variance": 5}
 
 
-def run(pkg, torch, x, op, x2=None, across=False, reverse=False):
-    """x: [batch][rows][n] or [rows][n] numpy (Float32, or uint16 BFloat16 bits)."""
+def run(pkg, torch, x, op, x2=None, across=False, reverse=False, slabs=False):
+    """x: [batch][rows][n] or [rows][n] numpy (Float32, or uint16 BFloat16 bits).  `slabs`: hand over the scratch
+    with which a scan across the rows is split into runs of rows."""
     L = pkg.lib
     bf = x.dtype == np.uint16
     to = lambda a: (torch.from_numpy(np.ascontiguousarray(a)).view(torch.bfloat16) if bf else torch.from_numpy(np.ascontiguousarray(a))).cuda()  # noqa: E731
@@ -23,8 +24,14 @@ def run(pkg, torch, x, op, x2=None, across=False, reverse=False):
     y = torch.full_like(xd, float("nan"))
     batch = x.shape[0] if x.ndim == 3 else 1
     rows, n = x.shape[-2], x.shape[-1]
+    ws, need = None, 0
+    if slabs:
+        need = L.scan_workspace_bytes(L.scan_desc(n, rows, OPS[op], across=across, reverse=reverse,
+                                                   dtype=L.BF16 if bf else L.F32, batch=batch))
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
     L.scan(xd.data_ptr(), y.data_ptr(), n, rows, OPS[op], x2=x2d.data_ptr() if x2d is not None else 0, across=across,
-           reverse=reverse, dtype=L.BF16 if bf else L.F32, batch=batch)
+           reverse=reverse, dtype=L.BF16 if bf else L.F32, batch=batch, workspace=ws.data_ptr() if ws is not None else 0,
+           workspace_bytes=need)
     torch.cuda.synchronize()
     return y.view(torch.int16).cpu().numpy().view(np.uint16) if bf else y.cpu().numpy()
 
@@ -105,3 +112,37 @@ def test_degenerate_shapes_and_refusals(pkg, cuda, oracle):
     with pytest.raises(L.TB200Error) as e:
         L.scan(x.data_ptr(), x.data_ptr(), 8, 1, 0, ld_x=4)
     assert e.value.status == -2
+
+
+@pytest.mark.parametrize("reverse", [False, True])
+def test_across_rows_in_slabs(pkg, cuda, oracle, reverse):
+    """With scratch a scan across many rows of few columns is cut into runs of rows (totals, then a second sweep
+    from the totals before each run): the same results as the sequential sweep, for every fold, a batch, a row
+    count that does not divide, and BFloat16; and without need for scratch the entry says so (0 bytes)."""
+    L = pkg.lib
+    x = single(oracle.data(200, 3001))                       # 3001 rows of 200 columns
+    assert L.scan_workspace_bytes(L.scan_desc(200, 3001, 0, across=True)) > 0
+    assert L.scan_workspace_bytes(L.scan_desc(200, 3001, 0)) == 0          # along the rows: no use for it
+    assert L.scan_workspace_bytes(L.scan_desc(200, 40, 0, across=True)) == 0   # too few rows to split
+    for op in ("sum", "max", "min", "variance"):
+        got, ref = run(pkg, cuda, x, op, across=True, reverse=reverse, slabs=True), want(oracle, x, op, across=True, reverse=reverse)
+        if op in ("max", "min"):
+            assert np.array_equal(got, ref)
+        else:
+            agree(got, ref, 1e-4)
+    a = single(0.9 + 0.1 * oracle.data(96, 2000, scale=0.3))
+    b = single(oracle.data(96, 2000, scale=0.7))
+    agree(run(pkg, cuda, a, "affine", b, across=True, reverse=reverse, slabs=True),
+          want(oracle, a, "affine", b, across=True, reverse=reverse), 1e-4)
+    m = single(oracle.data(16, 900, 5))                      # a batch of five
+    agree(run(pkg, cuda, m, "sum", across=True, reverse=reverse, slabs=True), want(oracle, m, "sum", across=True, reverse=reverse), 1e-4)
+    h = oracle.to_bf16(single(0.05 * oracle.data(64, 1500)))
+    got, ref = run(pkg, cuda, h, "sum", across=True, reverse=reverse, slabs=True), want(oracle, h, "sum", across=True, reverse=reverse)
+    gf, rf = oracle.from_bf16(got).astype(np.float64), oracle.from_bf16(ref).astype(np.float64)
+    assert (np.abs(gf - rf) <= 2.0 ** -7 * np.abs(rf) + 1e-3).all()
+    # scratch that is too small is refused
+    d = L.scan_desc(200, 3001, 0, across=True)
+    xd = cuda.zeros(3001, 200, device="cuda")
+    with pytest.raises(L.TB200Error) as e:
+        L.scan(xd.data_ptr(), xd.data_ptr(), 200, 3001, 0, across=True, workspace=xd.data_ptr(), workspace_bytes=16)
+    assert e.value.status == -5
