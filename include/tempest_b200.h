@@ -212,6 +212,15 @@ typedef struct tb200_gemm_desc {
     int debug;
 } tb200_gemm_desc;
 
+/* Products alike by arrays of their operands' addresses: `count` products of the descriptor's shape, layouts and
+ * element types, member i reading a[i], b[i] and writing c[i]; a, b, c are DEVICE arrays of `count` device addresses
+ * (the reference's `Products`, ext/cuBLASExt.jl:273-306: cublasGemmBatchedEx on arrays it rewrites in `repoint!`).
+ * Plain products only (epilogue NONE, C = alpha * A * B with alpha 0 read as 1); the descriptor's batch, split and
+ * workspace fields are ignored.  BFloat16 or Float16 operands run as warp-level MMAs, any alignment and any
+ * extents; Float32 operands (or force_simt) on the CUDA cores in Float32.  No workspace. */
+int tb200_gemm_pointers(const tb200_gemm_desc *desc, const void *const *a, const void *const *b, void *const *c,
+                        int64_t count, void *stream);
+
 /* Bytes of scratch a split of this product wants (0 when it would not split). */
 size_t tb200_gemm_workspace_bytes(const tb200_gemm_desc *desc);
 

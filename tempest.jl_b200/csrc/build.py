@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 PACKAGE = os.path.dirname(HERE)
 LIB = os.path.join(PACKAGE, "libtempest_b200.so")
-SOURCES = ["abi.cu", "rowreduce.cu", "gemm.cu", "pointwise.cu", "attention_fwd.cu", "attention_bwd.cu", "attention_simt.cu", "deltanet.cu", "generic.cu", "rowgen.cu", "dp.cu", "scan.cu", "route.cu"]
+SOURCES = ["abi.cu", "rowreduce.cu", "gemm.cu", "pointwise.cu", "attention_fwd.cu", "attention_bwd.cu", "attention_simt.cu", "deltanet.cu", "generic.cu", "rowgen.cu", "dp.cu", "scan.cu", "route.cu", "products.cu"]
 HEADERS = ["common.cuh", "sm100.cuh", "attention_simt.cuh", "generic.cuh", os.path.join("..", "..", "include", "tempest_b200.h")]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -636,17 +636,6 @@ struct MergeArgs {
     int in_dtype, out_dtype;
 };
 
-__device__ __forceinline__ float load_elem(const void *p, long long i, int dtype) {
-    if (dtype == TB200_F32) return static_cast<const float *>(p)[i];
-    if (dtype == TB200_F16) return __half2float(static_cast<const __half *>(p)[i]);
-    return __bfloat162float(static_cast<const __nv_bfloat16 *>(p)[i]);
-}
-__device__ __forceinline__ void store_elem(void *p, long long i, float v, int dtype) {
-    if (dtype == TB200_F32) static_cast<float *>(p)[i] = v;
-    else if (dtype == TB200_F16) static_cast<__half *>(p)[i] = __float2half_rn(v);
-    else static_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
-}
-
 __global__ void __launch_bounds__(256) gemm_splitk_merge(const MergeArgs q) {
     const long long per_member = static_cast<long long>(q.m) * q.n;
     const long long total = per_member * q.batch;

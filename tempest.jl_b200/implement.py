@@ -273,6 +273,57 @@ class LinearLaunch:
                  epilogue=self.epilogue, bias=a["b"].pointer() if "b" in a else 0, stream=current_stream())
 
 
+class ProductsLaunch:
+    """Plain products alike as one launch, by arrays of their operands' addresses on the device (tb200_gemm_pointers):
+    the mirror of the reference's `Products` (ext/cuBLASExt.jl:273-330), which is built from several bindings of one
+    shape and rewrites its address arrays in `repoint!`.  The arrays are written on the current stream, after the
+    launches before that read them."""
+
+    def __init__(self, bindings):
+        import torch
+        self.bindings = list(bindings)
+        first = self.bindings[0]
+        e, a = first.extents, first.arrays
+        for b in self.bindings:
+            if b.template != "linear" or dict(b.extents) != dict(e):
+                raise ValueError("products alike: every binding is a plain `linear` of the same extents")
+            for name in ("w", "x", "y"):
+                if b.arrays[name].eltype != a[name].eltype or b.arrays[name].strides != a[name].strides:
+                    raise ValueError("products alike: the operands' element types and strides agree")
+        w, x, y = a["w"], a["x"], a["y"]
+        self.desc = lib.gemm_desc(e["n"], e["m"], e["k"], lda=x.strides[1], ldb=w.strides[1], ldc=y.strides[1],
+                                  a_layout=lib.K_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=ELTYPES[w.eltype][0],
+                                  out_dtype=ELTYPES[y.eltype][0])
+        self.count = len(self.bindings)
+        self._torch = torch
+        self.addresses = {name: torch.empty(self.count, dtype=torch.int64, device="cuda") for name in ("x", "w", "y")}
+        for name in self.addresses:
+            self._write(name)
+
+    def _write(self, name):
+        host = self._torch.tensor([b.arrays[name].pointer() for b in self.bindings], dtype=self._torch.int64).pin_memory()
+        self.addresses[name].copy_(host, non_blocking=True)
+        self._keep = host   # until the copy has run
+
+    def repoints(self) -> bool:
+        return True
+
+    def repoint(self, value: int, buffer) -> "ProductsLaunch":
+        for name in self.addresses:
+            moved = False
+            for b in self.bindings:
+                if b.arrays[name].value == value:
+                    b.arrays[name].buffer = buffer
+                    moved = True
+            if moved:
+                self._write(name)
+        return self
+
+    def __call__(self):
+        lib.gemm_pointers(self.desc, self.addresses["x"].data_ptr(), self.addresses["w"].data_ptr(),
+                          self.addresses["y"].data_ptr(), self.count, stream=current_stream())
+
+
 class AttentionLaunch:
     """Attention forward or its pullback on fixed operands."""
 
@@ -483,6 +534,20 @@ class B200Kernels:
         op = _ROWOP[b.template]
         launches = 2 if (op == lib.LAYERNORM_BWD or n > 16384) else 1
         return [Work(bytes=_STREAMS[op] * n * rows * size, blocks=rows, launches=launches)]
+
+    def build_alike(self, target: Target, bindings, resources: Optional[Resources] = None):
+        """Several plain products of one shape as one launch (the reference's `build(::cuBLASProducts, target,
+        bs::Vector{Binding}, scratch)`, ext/cuBLASExt.jl:273-284)."""
+        bindings = list(bindings)
+        for b in bindings:
+            if b.template != "linear" or not self.supports(target, b):
+                raise ValueError("B200Kernels.build_alike takes plain `linear` bindings it supports")
+            for s in b.arrays.values():
+                if s.buffer is None:
+                    raise ValueError("build needs every array's buffer")
+        e = bindings[0].extents
+        return (ProductsLaunch(bindings),
+                f"B200 {len(bindings)} products alike, {e['m']} x {e['n']} over {e['k']}, {bindings[0].arrays['w'].eltype}")
 
     def build(self, target: Target, b: Binding, resources: Optional[Resources] = None):
         if not self.supports(target, b):

@@ -154,6 +154,7 @@ SIGNATURES = {
     "tb200_colreduce_source": (_sz, [ctypes.POINTER(GroupDesc), ctypes.c_char_p, _sz]),
     "tb200_deltanet_bwd_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_bwd": (_i, [ctypes.POINTER(DeltanetDesc)] + [_p] * 12 + [_sz, _p]),
+    "tb200_gemm_pointers": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _i64, _p]),
     "tb200_scan_workspace_bytes": (_sz, [ctypes.POINTER(ScanDesc)]),
     "tb200_scan": (_i, [ctypes.POINTER(ScanDesc), _p, _p, _p, _p]),
     "tb200_dp_signal_bytes": (_sz, []),
@@ -294,6 +295,11 @@ def gemm(a, b, c, m, n, k, *, bias=0, aux=0, aux_out=0, stream=0, tune=False, **
         return width
     check("tb200_gemm", load().tb200_gemm(ctypes.byref(d), a or None, b or None, c or None, bias or None,
                                           aux or None, aux_out or None, stream or None))
+
+
+def gemm_pointers(desc, a, b, c, count, stream=0):
+    """`count` products alike (tb200_gemm_pointers): a, b, c are device arrays of `count` device addresses."""
+    check("tb200_gemm_pointers", load().tb200_gemm_pointers(ctypes.byref(desc), a, b, c, count, stream or None))
 
 
 def gemm_workspace_bytes(desc):

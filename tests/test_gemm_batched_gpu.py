@@ -359,3 +359,79 @@ def test_layernorm_backward_without_eps_and_with_empty_row_slots(pkg, cuda, orac
         agree(dx.cpu().numpy(), dx_ref, 1e-5)
         agree(dw.cpu().numpy(), dw_ref, 1e-5)
         agree(db.cpu().numpy(), db_ref, 1e-5)
+
+
+@pytest.mark.parametrize("count,M,N,K,a_mn,b_mn", [
+    (37, 64, 64, 128, True, False),    # the delta rule's per-chunk products, scattered in memory
+    (37, 64, 64, 128, False, True),
+    (5, 50, 70, 100, False, False),    # extents that are not multiples of the tile, every layout
+    (5, 50, 70, 100, True, True),
+    (3, 130, 200, 72, True, False),
+    (3, 130, 200, 72, False, True),
+])
+def test_products_by_arrays_of_addresses(pkg, cuda, oracle, count, M, N, K, a_mn, b_mn):
+    """tb200_gemm_pointers (the reference's `Products`, ext/cuBLASExt.jl:273-306): members anywhere in memory, in any
+    order, some off a 16-byte boundary; BFloat16 on the warp-level MMAs and on the generic kernel, Float32 results
+    against the oracle's Float32 product."""
+    torch, L = cuda, pkg.lib
+    A, B = batch_operands(oracle, count, M, N, K, a_mn, b_mn, 9100 + M + K)
+    want = np.stack([oracle.gemm(A[i], B[i], M=M, N=N, K=K, a_km=a_mn, b_kn=b_mn, want_pre=True)[1] for i in range(count)])
+    # members laid out in reverse order with gaps; every third one starts two elements off alignment
+    gap = 24
+    a_len, b_len = A[0].size, B[0].size
+    pool_a = torch.zeros(count * (a_len + gap) + 8, device="cuda", dtype=torch.bfloat16)
+    pool_b = torch.zeros(count * (b_len + gap) + 8, device="cuda", dtype=torch.bfloat16)
+    pool_c = torch.full((count * (M * N + gap) + 8,), float("nan"), device="cuda")
+    pa, pb, pc, views = [], [], [], []
+    for i in range(count):
+        j = count - 1 - i
+        off = 2 if i % 3 == 1 else 0
+        va = pool_a[j * (a_len + gap) + off: j * (a_len + gap) + off + a_len]
+        vb = pool_b[j * (b_len + gap) + off: j * (b_len + gap) + off + b_len]
+        vc = pool_c[j * (M * N + gap): j * (M * N + gap) + M * N]
+        va.copy_(dev(torch, A[i]).reshape(-1))
+        vb.copy_(dev(torch, B[i]).reshape(-1))
+        pa.append(va.data_ptr()); pb.append(vb.data_ptr()); pc.append(vc.data_ptr()); views.append(vc)
+    ptrs = [torch.tensor(p, dtype=torch.int64, device="cuda") for p in (pa, pb, pc)]
+    for force_simt in (False, True):
+        pool_c.fill_(float("nan"))
+        d = L.gemm_desc(M, N, K, a_layout=int(a_mn), b_layout=int(b_mn), out_dtype=L.F32, force_simt=force_simt)
+        L.gemm_pointers(d, ptrs[0].data_ptr(), ptrs[1].data_ptr(), ptrs[2].data_ptr(), count)
+        torch.cuda.synchronize()
+        got = np.stack([v.view(M, N).cpu().numpy() for v in views])
+        agree(got, want, 1e-5)
+    # BFloat16 results, rounded once
+    outs = torch.full((count, M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    pc16 = torch.tensor([outs[i].data_ptr() for i in range(count)], dtype=torch.int64, device="cuda")
+    L.gemm_pointers(L.gemm_desc(M, N, K, a_layout=int(a_mn), b_layout=int(b_mn)), ptrs[0].data_ptr(), ptrs[1].data_ptr(),
+                    pc16.data_ptr(), count)
+    torch.cuda.synchronize()
+    close_bf16(oracle, host(torch, outs), want, K)
+
+
+def test_products_by_addresses_other_types_and_refusals(pkg, cuda, oracle):
+    torch, L = cuda, pkg.lib
+    count, M, N, K = 4, 40, 56, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    A32 = torch.randn(count, M, K, device="cuda", generator=g)
+    B32 = torch.randn(count, N, K, device="cuda", generator=g)          # K-major B: [n][k]
+    want = torch.einsum("bmk,bnk->bmn", A32.double(), B32.double())
+    for dt, code, tol in ((torch.float32, L.F32, 1e-5), (torch.float16, L.F16, 2e-3)):
+        Ad, Bd = A32.to(dt), B32.to(dt)
+        ref = torch.einsum("bmk,bnk->bmn", Ad.double(), Bd.double())
+        C = torch.full((count, M, N), float("nan"), device="cuda")
+        mk = lambda t: torch.tensor([t[i].data_ptr() for i in range(count)], dtype=torch.int64, device="cuda")  # noqa: E731
+        pa, pb, pc = mk(Ad), mk(Bd), mk(C)
+        L.gemm_pointers(L.gemm_desc(M, N, K, a_layout=L.K_MAJOR, b_layout=L.K_MAJOR, in_dtype=code, out_dtype=L.F32),
+                        pa.data_ptr(), pb.data_ptr(), pc.data_ptr(), count)
+        torch.cuda.synchronize()
+        assert ((C.double() - ref).norm() / ref.norm()).item() <= tol
+    assert want.shape == (count, M, N)
+    d = L.gemm_desc(M, N, K, epilogue=L.EPI_BIAS)
+    with pytest.raises(L.TB200Error) as e:      # plain products only
+        L.gemm_pointers(d, pa.data_ptr(), pb.data_ptr(), pc.data_ptr(), count)
+    assert e.value.status == -7
+    with pytest.raises(L.TB200Error) as e:      # a missing array
+        L.gemm_pointers(L.gemm_desc(M, N, K), 0, pb.data_ptr(), pc.data_ptr(), count)
+    assert e.value.status == -1
+    L.gemm_pointers(L.gemm_desc(M, N, K), 0, 0, 0, 0)   # nothing to do

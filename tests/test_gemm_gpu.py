@@ -364,3 +364,35 @@ def test_tune_returns_a_variant_and_leaves_the_product(pkg, cuda, oracle):
     assert L.gemm(A.data_ptr(), B.data_ptr(), narrow.data_ptr(), M, 64, K, ldb=N, tune=True) == 128
     with pytest.raises(L.TB200Error):
         L.gemm(0, B.data_ptr(), C.data_ptr(), M, N, K, tune=True)
+
+
+def test_products_alike_through_the_plugin_mirror(pkg, cuda, oracle):
+    """Several plain products of one shape built as one launch (the reference's `Products`), and moved to other
+    buffers through `repoint` (which rewrites the arrays of addresses on the stream)."""
+    torch, I = cuda, pkg.implement
+    lib, target = I.B200Kernels(), I.Target()
+    m, k, n, count = 64, 128, 64, 9
+    ws = [oracle.to_bf16(0.2 * oracle.normal((k, m), 30 + i)) for i in range(count)]
+    xs = [oracle.to_bf16(oracle.normal((n, k), 50 + i)) for i in range(count)]
+    wd, xd = [dev(torch, w) for w in ws], [dev(torch, x) for x in xs]
+    ys = [torch.full((n, m), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(count)]
+    binds = [I.Binding("linear", {"m": m, "k": k, "n": n},
+                       {"w": I.dense_matrix(wd[i], "BFloat16", m, k, 10 * i + 1), "x": I.dense_matrix(xd[i], "BFloat16", k, n, 10 * i + 2),
+                        "y": I.dense_matrix(ys[i], "BFloat16", m, n, 10 * i + 3)}) for i in range(count)]
+    launch, description = lib.build_alike(target, binds)
+    assert "9 products alike" in description and launch.repoints()
+    launch()
+    torch.cuda.synchronize()
+    for i in range(count):
+        want = oracle.gemm(xs[i], ws[i], M=n, N=m, K=k, a_km=False, b_kn=True, want_pre=True)[1]
+        close_bf16(oracle, host(torch, ys[i]), want, k)
+    # the fourth product's input moves to another buffer
+    moved = dev(torch, xs[0])
+    launch.repoint(10 * 3 + 2, moved)
+    ys[3].fill_(float("nan"))
+    launch()
+    torch.cuda.synchronize()
+    want = oracle.gemm(xs[0], ws[3], M=n, N=m, K=k, a_km=False, b_kn=True, want_pre=True)[1]
+    close_bf16(oracle, host(torch, ys[3]), want, k)
+    with pytest.raises(ValueError):
+        lib.build_alike(target, binds[:2] + [I.Binding("linear", {"m": m, "k": k, "n": 32}, binds[0].arrays)])
