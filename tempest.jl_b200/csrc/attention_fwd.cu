@@ -398,7 +398,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
     uint8_t *sk = sq + 2 * kTileBytes;        // K ring, 2 stages
     uint8_t *sv = sk + 2 * kTileBytes;        // V ring, 2 stages
 
-    __shared__ __align__(8) uint64_t q_full[2], q_empty[2], s_full[2], p_full[2], pv_done[2], o_free[2];
+    __shared__ __align__(8) uint64_t q_full[2], q_empty[2], s_full[2], p_half[2][2], pv_done[2], o_free[2];
     __shared__ __align__(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int failed_smem;
@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
     if (threadIdx.x == 0) {
         failed_smem = 0;
         for (int s = 0; s < 2; s++) {
-            mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 4); mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4);
+            mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 4); mbar_init(&s_full[s], 1); mbar_init(&p_half[s][0], 4); mbar_init(&p_half[s][1], 4);
             mbar_init(&pv_done[s], 1); mbar_init(&o_free[s], 4);
             mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
         }
@@ -533,14 +533,22 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
                         // O_g += P_g V_j
                         if (j == 0 && !wait_bounded(&o_free[g], (items_of[g] & 1) ^ 1, failed, 5)) { ok = false; break; }
                         if (!wait_bounded(&v_full[st], ph, failed, 8)) { ok = false; break; }
-                        if (!wait_bounded(&p_full[g], p_count[g] & 1, failed, 9)) { ok = false; break; }
-                        p_count[g]++;
-                        tcgen05_fence_after();
+                        // the weights arrive in two halves of 64 keys: the first four steps run while the second
+                        // half's exponentials are still being taken
                         const uint32_t va = smem_u32(sv + st * kTileBytes);
+                        if (!wait_bounded(&p_half[g][0], p_count[g] & 1, failed, 9)) { ok = false; break; }
+                        tcgen05_fence_after();
 #pragma unroll
-                        for (int k = 0; k < kTile / 16; k++)
+                        for (int k = 0; k < kTile / 32; k++)
                             tcgen05_mma_f16_ts(tmem_base + (2 + g) * kTile, tmem_base + g * kTile + k * 8,
                                                umma_smem_desc(va + k * 16 * 128, kSlab, 1024), idesc_pv, j | k);
+                        if (!wait_bounded(&p_half[g][1], p_count[g] & 1, failed, 9)) { ok = false; break; }
+                        p_count[g]++;
+                        tcgen05_fence_after();
+#pragma unroll
+                        for (int k = kTile / 32; k < kTile / 16; k++)
+                            tcgen05_mma_f16_ts(tmem_base + (2 + g) * kTile, tmem_base + g * kTile + k * 8,
+                                               umma_smem_desc(va + k * 16 * 128, kSlab, 1024), idesc_pv, 1);
                         tcgen05_commit(&pv_done[g]);
                         // scores of the next key tile for this query tile
                         if (j + 1 < n[g]) {
@@ -616,18 +624,19 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
                 }
                 const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
                 float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                // weights packed two per column over the row's own scores
+                // weights packed two per column over the row's own scores, in two halves of 64 keys: the first half is
+                // handed to the product P V while the second half's exponentials are still being taken, so the
+                // product's first four steps run under them instead of after them
 #pragma unroll
-                for (int i = 0; i < kTile; i += 2) {
+                for (int i = 0; i < kTile / 2; i += 2) {
                     const float w0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
                     const float w1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
                     ls[(i >> 1) & 3] += w0 + w1;
                     r[i >> 1] = pack_bf16x2(w0, w1);
                 }
-                l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
                 tmem_st_32x32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-                tmem_st_32x32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-                // O_g holds the products up to tile j-1 once pv_done has completed
+                // O_g holds the products up to tile j-1 once pv_done has completed; a rescale has to be in place
+                // before any step of this tile's product adds to it
                 if (j > 0) {
                     if (!wait_bounded(&pv_done[g], pv_seen & 1, failed, 12)) { ok = false; break; }
                     pv_seen++;
@@ -647,7 +656,20 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
                 tmem_st_wait();
                 tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&p_full[g]);
+                if (lane == 0) mbar_arrive(&p_half[g][0]);
+#pragma unroll
+                for (int i = kTile / 2; i < kTile; i += 2) {
+                    const float w0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+                    const float w1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
+                    ls[(i >> 1) & 3] += w0 + w1;
+                    r[i >> 1] = pack_bf16x2(w0, w1);
+                }
+                l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                tmem_st_32x32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+                tmem_st_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_half[g][1]);
             }
             if (!ok) break;
             // ---- epilogue: O / l, the log-sum-exp, store through the tile's own Q buffer
