@@ -44,6 +44,12 @@ constexpr float kRescaleThreshold = 8.0f;   // in log2 units
 
 __device__ int g_attn_error = 0;
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 struct AttnFwdArgs {
     CUtensorMap q, k, v, o;   // 4-D (feature, head, position, batch), boxes of 64 features x 128 positions
     float *lse;               // [batch][query][head] or null
@@ -607,11 +613,12 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
                         if ((p.causal && key > qi) || key >= p.keys) r[i] = 0xff800000u;
                     }
                 }
+                // the row's maximum with three-input maxima, four chains: 64 instructions for the 128 scores
                 float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int i = 0; i < kTile; i += 4) {
+                for (int i = 0; i < kTile; i += 8) {
 #pragma unroll
-                    for (int u = 0; u < 4; u++) mx[u] = fmaxf(mx[u], __uint_as_float(r[i + u]));
+                    for (int u = 0; u < 4; u++) mx[u] = max3(mx[u], __uint_as_float(r[i + 2 * u]), __uint_as_float(r[i + 2 * u + 1]));
                 }
                 float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
                 float alpha = 1.0f;
@@ -623,17 +630,22 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
                     l *= alpha;
                 }
                 const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
-                float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 // weights packed two per column over the row's own scores, in two halves of 64 keys: the first half is
                 // handed to the product P V while the second half's exponentials are still being taken, so the
                 // product's first four steps run under them instead of after them
+                const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg_m2 = make_float2(neg_m, neg_m);
+                float2 ls2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+                // two scores at a time with packed Float32 arithmetic (the scaling and the row sum are one instruction
+                // per pair): this loop is bound by issue slots, not by the special-function unit -- taking part of the
+                // exponentials as a polynomial on the FMA pipe instead made it slower in every proportion tried
+                auto weights = [&](int i) {   // scores i, i + 1 -> their packed weights in r[i / 2]
+                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, neg_m2);
+                    const float2 w = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                    ls2[(i >> 1) & 1] = __fadd2_rn(ls2[(i >> 1) & 1], w);
+                    r[i >> 1] = pack_bf16x2(w.x, w.y);
+                };
 #pragma unroll
-                for (int i = 0; i < kTile / 2; i += 2) {
-                    const float w0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
-                    const float w1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
-                    ls[(i >> 1) & 3] += w0 + w1;
-                    r[i >> 1] = pack_bf16x2(w0, w1);
-                }
+                for (int i = 0; i < kTile / 2; i += 2) weights(i);
                 tmem_st_32x32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
                 // O_g holds the products up to tile j-1 once pv_done has completed; a rescale has to be in place
                 // before any step of this tile's product adds to it
@@ -658,13 +670,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) attention_fwd_pair_kernel(con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_half[g][0]);
 #pragma unroll
-                for (int i = kTile / 2; i < kTile; i += 2) {
-                    const float w0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
-                    const float w1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
-                    ls[(i >> 1) & 3] += w0 + w1;
-                    r[i >> 1] = pack_bf16x2(w0, w1);
-                }
-                l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                for (int i = kTile / 2; i < kTile; i += 2) weights(i);
+                l += (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y);
                 tmem_st_32x32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
                 tmem_st_wait();
                 tcgen05_fence_before();
