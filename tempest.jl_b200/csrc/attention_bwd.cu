@@ -10,7 +10,7 @@
 // `deterministic = true`: two kernels, no atomics, every gradient element written once, results repeat bit for
 // bit (dQ is a second fold of its own: ext/cuTileExt/build.jl:295-318, docs/src/cuda.md:64-75); seven products.
 //
-//   stats      delta[m] = sum_d dO[d,m] o[d,m] (o as stored in BFloat16) and lse * log2(e), both
+//   stats      delta[m] = sum_d dO[d,m] o[d,m] (o as stored in BFloat16) and lse * log2(e), both negated and both
 //              re-laid out [batch][head][query] (rows padded to whole steps) so that consecutive queries are
 //              contiguous
 //   dK, dV     one item = 128 keys of one (batch, key/value head); steps of 128 queries (of every query
@@ -74,8 +74,8 @@ struct AttnBwdArgs {
     CUtensorMap outer_a, outer_b;   // dK/dV: K, V   | dQ: Q, dO     (boxes of 128 rows)
     CUtensorMap inner_a, inner_b;   // dK/dV: Q, dO  | dQ: K, V      (boxes of 128 rows)
     CUtensorMap out1, out2;         // dK/dV: dV, dK | dQ: -, dQ     (boxes of 32 rows)
-    const float *lse2;              // [batch][head][q_pad]  lse * log2(e)
-    const float *delta;             // [batch][head][q_pad]
+    const float *lse2;              // [batch][head][q_pad]  -lse * log2(e)
+    const float *delta;             // [batch][head][q_pad]  -delta
     float *dq_acc;                  // one-kernel form: [batch][query][head][feature] Float32, zero before the launch
     int batch, heads, kv_heads, queries, keys;
     int q_pad;                      // queries rounded up to whole steps: rows of the two arrays above, zero-filled
@@ -468,15 +468,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 // precision anyway, the conversions issue in the shadow of the exponentials (this stretch waits on the
                 // special-function unit), and dS is then formed from the rounded weights: half the registers, which
                 // is what keeps this kernel's row threads from spilling.
+                // (two scores at a time: the scaling and the shift by the negated log-sum-exp are one packed multiply-add)
                 uint32_t pk[32];
+                const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
                 for (int g = 0; g < 16; g++) {
                     float4 l4 = make_float4(row_lse2, row_lse2, row_lse2, row_lse2);
                     if (DKDV) l4 = *reinterpret_cast<const float4 *>(stats + 4 * g);
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(s[4 * g]), p.scale_log2, -l4.x));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(s[4 * g + 1]), p.scale_log2, -l4.y));
-                    const float p2 = fast_exp2(fmaf(__uint_as_float(s[4 * g + 2]), p.scale_log2, -l4.z));
-                    const float p3 = fast_exp2(fmaf(__uint_as_float(s[4 * g + 3]), p.scale_log2, -l4.w));
+                    const float2 x01 = __ffma2_rn(make_float2(__uint_as_float(s[4 * g]), __uint_as_float(s[4 * g + 1])), scale2,
+                                                  make_float2(l4.x, l4.y));
+                    const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(s[4 * g + 2]), __uint_as_float(s[4 * g + 3])), scale2,
+                                                  make_float2(l4.z, l4.w));
+                    const float p0 = fast_exp2(x01.x), p1 = fast_exp2(x01.y), p2 = fast_exp2(x23.x), p3 = fast_exp2(x23.y);
                     if (DKDV) {
                         pk[2 * g] = pack_bf16x2(p0, p1);
                         pk[2 * g + 1] = pack_bf16x2(p2, p3);
@@ -518,12 +521,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                             p0 = __uint_as_float(s[i]); p1 = __uint_as_float(s[i + 1]);
                             p2 = __uint_as_float(s[i + 2]); p3 = __uint_as_float(s[i + 3]);
                         }
-                        const float e0 = p0 * (__uint_as_float(dp[4 * g]) - d4.x);
-                        const float e1 = p1 * (__uint_as_float(dp[4 * g + 1]) - d4.y);
-                        const float e2 = p2 * (__uint_as_float(dp[4 * g + 2]) - d4.z);
-                        const float e3 = p3 * (__uint_as_float(dp[4 * g + 3]) - d4.w);
-                        dk[16 * half + 2 * g] = pack_bf16x2(e0, e1);
-                        dk[16 * half + 2 * g + 1] = pack_bf16x2(e2, e3);
+                        const float2 e01 = __fmul2_rn(make_float2(p0, p1),
+                                                      __fadd2_rn(make_float2(__uint_as_float(dp[4 * g]), __uint_as_float(dp[4 * g + 1])),
+                                                                 make_float2(d4.x, d4.y)));
+                        const float2 e23 = __fmul2_rn(make_float2(p2, p3),
+                                                      __fadd2_rn(make_float2(__uint_as_float(dp[4 * g + 2]), __uint_as_float(dp[4 * g + 3])),
+                                                                 make_float2(d4.z, d4.w)));
+                        dk[16 * half + 2 * g] = pack_bf16x2(e01.x, e01.y);
+                        dk[16 * half + 2 * g + 1] = pack_bf16x2(e23.x, e23.y);
                     }
                 }
                 tmem_st_32x32(t_dp + 32, dk);
@@ -629,8 +634,9 @@ __global__ void __launch_bounds__(256) attention_stats_kernel(const __nv_bfloat1
         const int m = static_cast<int>(bm % queries);
         const long long b = bm / queries;
         const long long out = (b * heads + h) * q_pad + m;
-        delta[out] = s;
-        lse2[out] = lse[r] * kLog2e;
+        // both negated: the row threads add them with packed (two at a time) instructions, which have no negate
+        delta[out] = -s;
+        lse2[out] = -lse[r] * kLog2e;
     }
 }
 
