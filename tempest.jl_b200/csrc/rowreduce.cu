@@ -1390,7 +1390,7 @@ RowKernel ln_bwd_kernel(int dtype, const Schedule &s, bool saved_stats) {
 // the statistics saved and whole groups of rows, take the form fed through shared memory (eight elements a thread,
 // 512 threads, `splits` = stages of the ring); everything else keeps the plan.
 constexpr size_t kStagedRingBytes = 96 * 1024;
-constexpr int kStagedRowsFwd = 2;    // rows a block of the forward takes per turn
+constexpr int kStagedRowsFwd = 4;    // rows a block of the forward takes per turn
 // `arrays`: row-sized arrays a stage holds per row (x; x and dy); `turn`: rows per turn per row slot.
 Schedule staged_schedule(const Schedule &s, int64_t n, int64_t rows, int dtype, int arrays, int turn) {
     if (!s.vec || s.split || (n != 1024 && n != 2048 && n != 4096)) return s;
