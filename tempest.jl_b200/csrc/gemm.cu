@@ -850,10 +850,16 @@ void choose_split(const tb200_gemm_desc &d, int bn, int sms, int *splits, int *k
     *splits = static_cast<int>(num_kb > 0 ? ceil_div(num_kb, *kb_per_split) : 1);
 }
 
-int tile_width(const tb200_gemm_desc &d) {
+int tile_width(const tb200_gemm_desc &d, int sms) {
     // 128 x 256 tiles halve the operand bytes per flop of 128 x 128 ones and measured faster on every
-    // shape wide enough to hold one, even when they leave a few SMs idle
-    return (d.tile_n == 256 || (d.tile_n == 0 && d.n > 128)) ? 256 : 128;
+    // shape wide enough to hold one, even when they leave a few SMs idle -- except where the wide tiles fill
+    // less than half the device (a replica's slice of a batch against a narrow layer): the narrow ones then
+    // put twice the SMs to work in the same single wave
+    if (d.tile_n == 256 || d.tile_n == 128) return d.tile_n;
+    if (d.n <= 128) return 128;
+    const int64_t batch = d.batch > 1 ? d.batch : 1;
+    const int64_t wide = ceil_div(d.m, BM) * ceil_div(d.n, 256) * batch;
+    return 2 * wide <= sms ? 128 : 256;
 }
 
 size_t split_workspace_bytes(const tb200_gemm_desc &d, int splits) {
@@ -948,7 +954,7 @@ int prepare(tb200_gemm_plan *plan) {
     if (tma_ok) {
         GemmArgs &p = plan->args;
         p = GemmArgs{};
-        const int bn = tile_width(*d);
+        const int bn = tile_width(*d, dev.sms);
         int splits = 1, kb_per = static_cast<int>(ceil_div(d->k, BK));
         choose_split(*d, bn, dev.sms, &splits, &kb_per);
         if (splits > 1 && (!d->workspace || !aligned_to(d->workspace, 16) ||
@@ -1091,7 +1097,7 @@ extern "C" size_t tb200_gemm_workspace_bytes(const tb200_gemm_desc *d) {
     int sms = 148;
     if (current_device(&dev) == TB200_OK) sms = dev.sms;
     int splits = 1, per = 1;
-    choose_split(*d, tile_width(*d), sms, &splits, &per);
+    choose_split(*d, tile_width(*d, sms), sms, &splits, &per);
     return splits > 1 ? split_workspace_bytes(*d, splits) : 0;
 }
 

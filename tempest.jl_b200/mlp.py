@@ -196,11 +196,23 @@ class MLPStep:
             return
         bf16, L = lib.BF16, self.L
         fwd, below, grads = [], [None] * L, []
+        self._scratch = []
+
+        def plan(desc, *operands, **more):
+            # a product with too few tiles to fill the device (a replica's slice of the batch against a narrow
+            # layer) splits its sum over k when it is given scratch for the partial tiles
+            need = lib.gemm_workspace_bytes(desc)
+            if need:
+                ws = self.torch.empty(need, dtype=self.torch.uint8, device="cuda")
+                self._scratch.append(ws)
+                desc.workspace, desc.workspace_bytes = ws.data_ptr(), need
+            return lib.GemmPlan(desc, *operands, **more)
+
         for i in range(L):
             fin, fout = self.sizes[i], self.sizes[i + 1]
             last = i == L - 1
             h = ptr if i == 0 else self.a[i].data_ptr()
-            fwd.append(lib.GemmPlan(
+            fwd.append(plan(
                 lib.gemm_desc(self.batch, fout, fin, a_layout=lib.K_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=bf16,
                               epilogue=lib.EPI_BIAS if last else self.fwd_epi),
                 h, self.w[i].data_ptr(), self.a[i + 1].data_ptr(), bias=self.b[i].data_ptr(),
@@ -208,18 +220,18 @@ class MLPStep:
             if i > 0:
                 # dz[i - 1] = (dz[i] * w[i]') .* act'(saved): A = dz [batch][fout], B = w as [n = fin][k = fout]
                 saved = self.z[i - 1] if self.saved == "z" else self.a[i]
-                below[i] = lib.GemmPlan(
+                below[i] = plan(
                     lib.gemm_desc(self.batch, fin, fout, a_layout=lib.K_MAJOR, b_layout=lib.K_MAJOR, in_dtype=bf16,
                                   epilogue=self.bwd_epi),
                     self.dz[i].data_ptr(), self.w[i].data_ptr(), self.dz[i - 1].data_ptr(), aux=saved.data_ptr())
             if self.fuse_update:
                 # w = w - rate * (a_in' * dz): the update rides in the product's epilogue
-                grads.append(lib.GemmPlan(
+                grads.append(plan(
                     lib.gemm_desc(fin, fout, self.batch, a_layout=lib.MN_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=bf16,
                                   epilogue=lib.EPI_AXPY, alpha=-self.rate),
                     h, self.dz[i].data_ptr(), self.w[i].data_ptr(), aux=self.w[i].data_ptr()))
             else:
-                grads.append(lib.GemmPlan(
+                grads.append(plan(
                     lib.gemm_desc(fin, fout, self.batch, a_layout=lib.MN_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=bf16),
                     h, self.dz[i].data_ptr(), self.dw[i].data_ptr()))
         self._plans = {"fwd": fwd, "below": below, "grads": grads}
