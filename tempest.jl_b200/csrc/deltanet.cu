@@ -117,7 +117,7 @@ __device__ __forceinline__ uint32_t tf32_bits(float x) {
     return r;
 }
 
-__global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+__global__ void __launch_bounds__(256, 3) deltanet_chunk_kernel(const __nv_bfloat16 *q, const __nv_bfloat16 *k,
                                                              const __nv_bfloat16 *v, const float *a, const float *beta,
                                                              __nv_bfloat16 *w_out, __nv_bfloat16 *u_out,
                                                              __nv_bfloat16 *p_out, __nv_bfloat16 *minv_save,
@@ -129,10 +129,8 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
     float *be = ca + kC;                  // [64]
     float *sk = be + kC;                  // [64]  beta e^ca: the scale of K's rows on the right-hand side
     __nv_bfloat16 *Kh = reinterpret_cast<__nv_bfloat16 *>(sk + kC);   // [64][136]
-    __nv_bfloat16 *Vh = Kh + kC * kPadH;                              // [64][136]
-    __nv_bfloat16 *Qh = Vh + kC * kPadH;                              // [64][136]; later the scratch Tm [64][68] Float32
-    float *Tm = reinterpret_cast<float *>(Qh);
-    static_assert(kC * kPadA * sizeof(float) <= kC * kPadH * sizeof(__nv_bfloat16), "the scratch fits Q's tile");
+    __nv_bfloat16 *Qh = Kh + kC * kPadH;                              // [64][136]: Q, then (once A and P are formed) V
+    __nv_bfloat16 *Vh = Qh;
     const int chunks = T / kC;
     const int head = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
     const long long row0 = static_cast<long long>(head) * T + static_cast<long long>(chunk) * kC;
@@ -142,7 +140,6 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
         const int r = i / (kDK / 8), c = (i % (kDK / 8)) * 8;
         *reinterpret_cast<uint4 *>(Kh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(k + (row0 + r) * kDK + c));
         *reinterpret_cast<uint4 *>(Qh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(q + (row0 + r) * kDK + c));
-        *reinterpret_cast<uint4 *>(Vh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(v + (row0 + r) * kDV + c));
     }
     if (tid < 32) {
         float lo, hi;
@@ -206,7 +203,11 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
                 *reinterpret_cast<uint32_t *>(pc + t * kC + s) = pack_bf16x2(d0 * qk[j][e], d1 * qk[j][e + 1]);
             }
     }
-    __syncthreads();   // A is complete; Q's tile is free from here on (Tm)
+    __syncthreads();   // A is complete; Q's tile is free from here on: V takes its place (read again two phases on)
+    for (int i = tid; i < kC * kDV / 8; i += blockDim.x) {
+        const int r = i / (kDV / 8), c = (i % (kDV / 8)) * 8;
+        *reinterpret_cast<uint4 *>(Vh + r * kPadH + c) = __ldg(reinterpret_cast<const uint4 *>(v + (row0 + r) * kDV + c));
+    }
 
     // (I + A)^-1 by 16 x 16 blocks, as the reference's `blocks` does (examples/deltanet.jl:39-54).  Diagonal blocks:
     // 64 threads solve (I + A_ii) x = e_j by substitution, one column each, in Float32.
@@ -223,13 +224,6 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
         }
 #pragma unroll
         for (int r = 0; r < 16; r++) Mi[(16 * blk + r) * kPadA + 16 * blk + j] = x[r];
-    } else {
-        // the blocks above the diagonal are zero
-        for (int i = tid - kC; i < 6 * 256; i += blockDim.x - kC) {
-            const int pair = i >> 8, e = i & 255;
-            const int bi = pair < 3 ? 0 : pair < 5 ? 1 : 2, bj = pair < 3 ? pair + 1 : pair < 5 ? pair - 1 : 3;
-            Mi[(16 * bi + (e >> 4)) * kPadA + 16 * bj + (e & 15)] = 0.0f;
-        }
     }
     __syncthreads();
     // Blocks below the diagonal, one distance from it at a time:  M_ij = -M_ii (sum_{j <= k < i} A_ik M_kj), each block
@@ -240,7 +234,9 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
             float acc[2][4] = {};
             for (int bk = bj; bk < bi; bk++)
                 block_product(acc, A + (16 * bi) * kPadA + 16 * bk, Mi + (16 * bk) * kPadA + 16 * bj, lane);
-            float *scratch = Tm + (16 * bi) * kPadA + 16 * bj;
+            // the sum is parked in the mirrored block above the diagonal (zero in the result, and nobody reads it:
+            // it is cleared again below)
+            float *scratch = Mi + (16 * bj) * kPadA + 16 * bi;
             block_store(scratch, acc, lane, 1.0f);
             __syncwarp();
             float out[2][4] = {};
@@ -252,7 +248,8 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
     if (minv_save)   // rounded: the reverse scan takes it as a BFloat16 operand
         for (int i = tid; i < kC * kC / 4; i += blockDim.x) {
             const int r = i / (kC / 4), c = (i % (kC / 4)) * 4;
-            const float4 m4 = *reinterpret_cast<const float4 *>(Mi + r * kPadA + c);
+            float4 m4 = *reinterpret_cast<const float4 *>(Mi + r * kPadA + c);
+            if ((c >> 4) > (r >> 4)) m4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);   // blocks above the diagonal (scratch)
             *reinterpret_cast<uint2 *>(minv_save + (row0 + r) * kC + c) = make_uint2(pack_bf16x2(m4.x, m4.y), pack_bf16x2(m4.z, m4.w));
         }
 
@@ -264,27 +261,31 @@ __global__ void __launch_bounds__(256) deltanet_chunk_kernel(const __nv_bfloat16
         const int m0 = 16 * (warp & 3), side = warp >> 2;
         const __nv_bfloat16 *rhs = side ? Vh : Kh;
         const float *scale = side ? be : sk;
-        float acc[16][4] = {};
-        for (int kk = 0; kk < m0 + 16; kk += 8) {
-            uint32_t af[4];
-            af[0] = tf32_bits(Mi[(m0 + g) * kPadA + kk + t4]);
-            af[1] = tf32_bits(Mi[(m0 + g + 8) * kPadA + kk + t4]);
-            af[2] = tf32_bits(Mi[(m0 + g) * kPadA + kk + t4 + 4]);
-            af[3] = tf32_bits(Mi[(m0 + g + 8) * kPadA + kk + t4 + 4]);
-            const float s0 = scale[kk + t4], s1 = scale[kk + t4 + 4];
-            const __nv_bfloat16 *r0 = rhs + (kk + t4) * kPadH + g, *r1 = r0 + 4 * kPadH;
-#pragma unroll
-            for (int nt = 0; nt < 16; nt++) {
-                const uint32_t b0 = tf32_bits(s0 * __bfloat162float(r0[8 * nt]));
-                const uint32_t b1 = tf32_bits(s1 * __bfloat162float(r1[8 * nt]));
-                mma_tf32_raw(acc[nt], af, b0, b1);
-            }
-        }
         __nv_bfloat16 *dst = (side ? u_out : w_out) + row0 * 128;
+#pragma unroll 1
+        for (int half = 0; half < 2; half++) {   // 64 columns at a time: half the accumulators in registers
+            float acc[8][4] = {};
+            for (int kk = 0; kk < m0 + 16; kk += 8) {
+                uint32_t af[4];
+                af[0] = tf32_bits(Mi[(m0 + g) * kPadA + kk + t4]);
+                af[1] = tf32_bits(Mi[(m0 + g + 8) * kPadA + kk + t4]);
+                af[2] = tf32_bits(Mi[(m0 + g) * kPadA + kk + t4 + 4]);
+                af[3] = tf32_bits(Mi[(m0 + g + 8) * kPadA + kk + t4 + 4]);
+                const float s0 = scale[kk + t4], s1 = scale[kk + t4 + 4];
+                const __nv_bfloat16 *r0 = rhs + (kk + t4) * kPadH + 64 * half + g, *r1 = r0 + 4 * kPadH;
 #pragma unroll
-        for (int nt = 0; nt < 16; nt++) {
-            *reinterpret_cast<uint32_t *>(dst + (m0 + g) * 128 + 8 * nt + 2 * t4) = pack_bf16x2(acc[nt][0], acc[nt][1]);
-            *reinterpret_cast<uint32_t *>(dst + (m0 + g + 8) * 128 + 8 * nt + 2 * t4) = pack_bf16x2(acc[nt][2], acc[nt][3]);
+                for (int nt = 0; nt < 8; nt++) {
+                    const uint32_t b0 = tf32_bits(s0 * __bfloat162float(r0[8 * nt]));
+                    const uint32_t b1 = tf32_bits(s1 * __bfloat162float(r1[8 * nt]));
+                    mma_tf32_raw(acc[nt], af, b0, b1);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                const int col = 64 * half + 8 * nt + 2 * t4;
+                *reinterpret_cast<uint32_t *>(dst + (m0 + g) * 128 + col) = pack_bf16x2(acc[nt][0], acc[nt][1]);
+                *reinterpret_cast<uint32_t *>(dst + (m0 + g + 8) * 128 + col) = pack_bf16x2(acc[nt][2], acc[nt][3]);
+            }
         }
     }
 }
@@ -1236,7 +1237,7 @@ int launch_scan(const tb200_deltanet_desc *d, const void *q, const void *k, cons
                 const __nv_bfloat16 *u, const __nv_bfloat16 *pw, __nv_bfloat16 *o, __nv_bfloat16 *s_save,
                 __nv_bfloat16 *u_save, cudaStream_t stream);
 
-constexpr size_t kChunkSmem = (2 * kC * kPadA + 3 * kC) * sizeof(float) + 3 * kC * kPadH * sizeof(__nv_bfloat16);
+constexpr size_t kChunkSmem = (2 * kC * kPadA + 3 * kC) * sizeof(float) + 2 * kC * kPadH * sizeof(__nv_bfloat16);
 constexpr size_t kScanSmem = 1024 + 2 * kTileSetBytes + 2 * kGateFloats * sizeof(float) +
                              (kDVB / kDVP) * (2 * kDK * kPadB + 2 * kC * kPadB + kDVP * kPadP) * sizeof(__nv_bfloat16);
 constexpr size_t kBwdScanSmem = 1024 + 2 * kBwdSetBytes + 2 * kGateFloats * sizeof(float) +
