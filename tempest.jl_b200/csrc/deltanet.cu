@@ -1256,6 +1256,10 @@ int check_deltanet(const tb200_deltanet_desc *d) {
     if (d->heads < 0 || d->positions < 0) return TB200_ERR_SHAPE;
     if (d->dtype != TB200_BF16) return TB200_ERR_DTYPE;
     if (d->dk != kDK || d->dv != kDV || d->chunk != kC || d->positions % kC != 0) return TB200_ERR_UNSUPPORTED;
+    // the scans address rows of [heads * positions] arrays (and heads * 128 feature rows) by 32-bit tile coordinates,
+    // and the chunk kernels take one block per chunk
+    if (static_cast<long long>(d->heads) * d->positions >= (1ll << 31) || static_cast<long long>(d->heads) * kDV >= (1ll << 31))
+        return TB200_ERR_SHAPE;
     return TB200_OK;
 }
 

@@ -175,6 +175,7 @@ extern "C" int tb200_gemm_pointers(const tb200_gemm_desc *d, const void *const *
     if (!d) return TB200_ERR_NULL;
     if (d->m < 0 || d->n < 0 || d->k < 0 || count < 0) return TB200_ERR_SHAPE;
     if (d->m > (1 << 30) || d->n > (1 << 30) || d->k > (1 << 30)) return TB200_ERR_SHAPE;
+    if (ceil_div(d->m, 64) > 65535) return TB200_ERR_SHAPE;   // rows of 64 x 64 tiles are the grid's second axis
     const bool a_mn = d->a_layout == TB200_MN_MAJOR, b_mn = d->b_layout == TB200_MN_MAJOR;
     if ((d->a_layout != TB200_K_MAJOR && !a_mn) || (d->b_layout != TB200_K_MAJOR && !b_mn)) return TB200_ERR_UNSUPPORTED;
     if (d->lda < (a_mn ? d->m : d->k) || d->ldb < (b_mn ? d->n : d->k) || d->ldc < d->n) return TB200_ERR_SHAPE;
