@@ -459,8 +459,9 @@ typedef enum tb200_term_op {
     TB200_T_RECOMPUTED = 24, /* sum over e < c of X[row][e] * Y[i][e]: a fold formed where it is read (Recomputed,
                                 src/Compiler/IR/terms.jl:69-87) over one extra axis of extent c; a = input X of
                                 shape TB200_SHAPE_ROW_VECTORS, b = input Y of shape TB200_SHAPE_ALONG_VECTORS */
-    TB200_T_ROW_INDEX = 25   /* the row's own position, 0-based, as Float32: with TB200_T_INDEX under a
+    TB200_T_ROW_INDEX = 25,  /* the row's own position, 0-based, as Float32: with TB200_T_INDEX under a
                                 TB200_T_SELECT it spells a mask on two positions (ext/cuTileExt/mask.jl:54-75) */
+    TB200_T_STATE = 26       /* a = state index: the state's value before this step (recurrences only) */
 } tb200_term_op;
 
 typedef struct tb200_term { int op, a, b, c; float imm; } tb200_term;
@@ -602,6 +603,37 @@ typedef struct tb200_scan_desc {
 } tb200_scan_desc;
 size_t tb200_scan_workspace_bytes(const tb200_scan_desc *desc);
 int tb200_scan(const tb200_scan_desc *desc, const void *x, const void *x2, void *y, void *stream);
+
+/* ---- recurrences whose step is a map ------------------------------------------------
+ * The `:recurrence` groups of the reference (src/Compiler/Implement/groups.jl:29-47; its kernel:
+ * ext/cuTileExt/build.jl:772-835, a block per tile of the parallel axes stepping along the states' axis, the
+ * states held in tiles) whose step computes every member element by element: states carried from step to step
+ * (several, each assigned at once from the values before the step, so states may cross or lag:
+ * test/runtime/recurrences.jl:190-196), members stored at every step, the states as the steps leave them --
+ * h = tanh.(a .* h .+ x), exponential averages, gates that are maps of the step's inputs.  A step that contracts
+ * over the state (a matrix times the hidden state) is not a map and is not taken here: DeltaNet's kernels and the
+ * scans are the other recurrence kernels of this library.
+ *
+ * `body` is a group descriptor over (n, steps): n positions that do not interact (the parallel axes, collapsed),
+ * `rows` = steps.  Terms are evaluated at every step in order; TB200_T_STATE reads a state before the step,
+ * TB200_T_LOAD of a full input reads the step's row, of an `along` input a per-position constant, of a per-row
+ * input the step's scalar; TB200_T_ROW_INDEX is the step.  No folds.  Outputs: from = 0, the term at every
+ * step ((n, steps), row pitch ld); from = 3, state `index` after the last step (n values).  state k starts from
+ * input `start` (shape along, or scalar) and is `next` (a term) after each step; `reverse` walks the steps from the
+ * last.  One thread owns a position; eight steps' loads are issued ahead of the arithmetic.  Compiled by NVRTC on
+ * first use and cached (TB200_ERR_UNSUPPORTED without NVRTC).  No workspace. */
+#define TB200_RECURRENCE_MAX_STATES 4
+typedef struct tb200_state { int start, next; } tb200_state;
+typedef struct tb200_recurrence_desc {
+    tb200_group_desc body;
+    int n_states;
+    tb200_state states[TB200_RECURRENCE_MAX_STATES];
+    int reverse;
+} tb200_recurrence_desc;
+int tb200_recurrence_compile(const tb200_recurrence_desc *desc);
+size_t tb200_recurrence_source(const tb200_recurrence_desc *desc, char *buffer, size_t buffer_bytes);
+int tb200_recurrence_compiled(const tb200_recurrence_desc *desc, const void *const *inputs, void *const *outputs,
+                              void *stream);
 
 /* ---- data-parallel update: gradient sum + SGD step in one kernel over NVLink -----
  * The exchange of a data-parallel training step (the reference spells it `r .+ s` over the devices'

@@ -643,3 +643,69 @@ def deltanet_inputs(heads, T, dk, dv, seed):
     beta = (1.0 / (1.0 + np.exp(-normal((heads, T), seed + 3)))).astype(np.float32)
     a = (-np.log1p(np.exp(normal((heads, T), seed + 4)))).astype(np.float32)
     return to_bf16(q), to_bf16(k), to_bf16(v), a, beta
+
+
+def recurrence_eval(desc, inputs):
+    """A recurrence whose step is a map (include/tempest_b200.h, tb200_recurrence_desc), step by step in Float32 as the
+    reference's CPU path runs a recurrence (one step at a time, every member as its node's eltype: Float32 here, results
+    rounded once where they are stored): inputs in the descriptor's order (numpy; BFloat16 as uint16 bits).  Returns
+    the outputs in the descriptor's order (Float32 arrays, or uint16 bits for BFloat16 outputs)."""
+    import numpy as np
+    d = desc.body
+    n, steps = int(d.n), int(d.rows)
+    f32 = np.float32
+    arrays = []
+    for i in range(d.n_inputs):
+        a = np.asarray(inputs[i])
+        arrays.append(from_bf16(a).astype(f32) if d.inputs[i].dtype == 1 else a.astype(f32))
+    def start(k):
+        i = desc.states[k].start
+        v = arrays[i].reshape(-1)
+        return np.full(n, v[0], f32) if d.inputs[i].shape == 3 else v[:n].astype(f32).copy()
+    state = [start(k) for k in range(desc.n_states)]
+    outs = []
+    for o in range(d.n_outputs):
+        outs.append(np.zeros((steps, n), f32) if d.outputs[o].source == 0 else np.zeros(n, f32))
+    cols = np.arange(n, dtype=f32)
+    unary = {11: lambda a: -a, 12: np.exp, 13: np.log, 14: np.tanh, 15: np.sqrt, 16: lambda a: f32(1) / np.sqrt(a), 17: np.abs,
+             18: lambda a: a * a, 19: lambda a: f32(1) / a, 20: lambda a: f32(1) / (f32(1) + np.exp(-a)),
+             23: lambda a: from_bf16(to_bf16(a)).astype(f32)}
+    binary = {5: np.add, 6: np.subtract, 7: np.multiply, 8: np.divide, 9: np.maximum, 10: np.minimum}
+    with np.errstate(all="ignore"):
+        for s in range(steps):
+            row = steps - 1 - s if desc.reverse else s
+            t = []
+            for k in range(d.n_terms):
+                T = d.terms[k]
+                if T.op == 0:
+                    shape = d.inputs[T.a].shape
+                    a = arrays[T.a]
+                    v = (a.reshape(steps, -1)[row, :n] if shape == 0 else a.reshape(-1)[:n] if shape == 1
+                         else np.full(n, a.reshape(-1)[row], f32) if shape == 2 else np.full(n, a.reshape(-1)[0], f32))
+                elif T.op == 1:
+                    v = np.full(n, T.imm, f32)
+                elif T.op == 2:
+                    v = cols
+                elif T.op == 25:
+                    v = np.full(n, row, f32)
+                elif T.op == 26:
+                    v = state[T.a]
+                elif T.op in binary:
+                    v = binary[T.op](t[T.a], t[T.b])
+                elif T.op == 21:
+                    v = (t[T.a].astype(np.float64) * t[T.b].astype(np.float64) + t[T.c].astype(np.float64))   # fused: one rounding
+                elif T.op == 22:
+                    v = np.where(t[T.a] > 0, t[T.b], t[T.c])
+                else:
+                    v = unary[T.op](t[T.a])
+                t.append(np.asarray(v).astype(f32))
+            for o in range(d.n_outputs):
+                if d.outputs[o].source == 0:
+                    outs[o][row] = t[d.outputs[o].index]
+            state = [t[desc.states[k].next].copy() for k in range(desc.n_states)]
+    for o in range(d.n_outputs):
+        if d.outputs[o].source == 3:
+            outs[o] = state[d.outputs[o].index]
+        if d.outputs[o].dtype == 1:
+            outs[o] = to_bf16(outs[o])
+    return outs

@@ -72,7 +72,7 @@ std::string fbits(float f) {
 }
 
 int term_arity(int op) {
-    if (op <= TB200_T_STAT2) return 0;
+    if (op <= TB200_T_STAT2 || op == TB200_T_ROW_INDEX || op == TB200_T_STATE) return 0;
     if (op <= TB200_T_MIN) return 2;
     if (op == TB200_T_FMA || op == TB200_T_SELECT) return 3;
     return 1;
@@ -143,6 +143,8 @@ std::string term_expr(const tb200_group_desc &d, int k, const std::string &chunk
         case TB200_T_FMA: return "fmaf(" + t(T.a) + ", " + t(T.b) + ", " + t(T.c) + ")";
         case TB200_T_SELECT: return "(" + t(T.a) + " > 0.0f ? " + t(T.b) + " : " + t(T.c) + ")";
         case TB200_T_ROUND_BF16: return "bf2f(f2bf(" + t(T.a) + "))";
+        case TB200_T_STATE: return "st" + num(T.a);
+        case TB200_T_ROW_INDEX: return "(float)row";
         default: return "0.0f";
     }
 }
@@ -906,6 +908,206 @@ int col_slabs(const tb200_group_desc *d, int V) {
     return static_cast<int>(slabs < 1 ? 1 : slabs);
 }
 
+// ------------------------------------------------ recurrences whose step is a map ----
+//
+// One thread owns a position and walks the steps in order with the states in registers; the step's terms are
+// straight-line Float32 code generated from the descriptor.  The rows of the step inputs are fetched eight steps
+// ahead of the arithmetic (the chain through the states is arithmetic only), neighbouring threads read
+// neighbouring positions, every member is rounded once where it is stored.
+
+struct RecParams {
+    const void *in[TB200_GROUP_MAX_INPUTS];
+    void *out[TB200_GROUP_MAX_OUTPUTS];
+    long long ld_in[TB200_GROUP_MAX_INPUTS];
+    long long ld_out[TB200_GROUP_MAX_OUTPUTS];
+    long long n, steps;
+};
+
+int check_recurrence(const tb200_recurrence_desc *r) {
+    if (!r) return TB200_ERR_NULL;
+    const tb200_group_desc *d = &r->body;
+    if (d->n < 0 || d->rows < 0 || d->n > (int64_t(1) << 40)) return TB200_ERR_SHAPE;
+    if (d->n_inputs < 0 || d->n_inputs > TB200_GROUP_MAX_INPUTS || d->n_terms < 1 || d->n_terms > TB200_GROUP_MAX_TERMS ||
+        d->n_folds != 0 || d->n_outputs < 1 || d->n_outputs > TB200_GROUP_MAX_OUTPUTS)
+        return TB200_ERR_SHAPE;
+    if (r->n_states < 1 || r->n_states > TB200_RECURRENCE_MAX_STATES) return TB200_ERR_SHAPE;
+    for (int i = 0; i < d->n_inputs; i++) {
+        const tb200_group_input &in = d->inputs[i];
+        if (in.dtype != TB200_F32 && in.dtype != TB200_BF16) return TB200_ERR_DTYPE;
+        if (in.shape < TB200_SHAPE_FULL || in.shape > TB200_SHAPE_SCALAR) return TB200_ERR_UNSUPPORTED;
+        if (in.shape == TB200_SHAPE_FULL && in.ld < d->n) return TB200_ERR_SHAPE;
+    }
+    for (int k = 0; k < d->n_terms; k++) {
+        const tb200_term &T = d->terms[k];
+        const bool leaf_ok = T.op == TB200_T_STATE || T.op == TB200_T_ROW_INDEX;
+        if (!leaf_ok && (T.op < TB200_T_LOAD || T.op > TB200_T_ROUND_BF16)) return TB200_ERR_UNSUPPORTED;
+        if (T.op == TB200_T_STAT || T.op == TB200_T_STAT2) return TB200_ERR_UNSUPPORTED;
+        if (T.op == TB200_T_LOAD && (T.a < 0 || T.a >= d->n_inputs)) return TB200_ERR_SHAPE;
+        if (T.op == TB200_T_STATE && (T.a < 0 || T.a >= r->n_states)) return TB200_ERR_SHAPE;
+        const int ar = term_arity(T.op);
+        if ((ar > 0 && (T.a < 0 || T.a >= k)) || (ar > 1 && (T.b < 0 || T.b >= k)) || (ar > 2 && (T.c < 0 || T.c >= k)))
+            return TB200_ERR_SHAPE;
+    }
+    for (int k = 0; k < r->n_states; k++) {
+        const tb200_state &S = r->states[k];
+        if (S.start < 0 || S.start >= d->n_inputs || S.next < 0 || S.next >= d->n_terms) return TB200_ERR_SHAPE;
+        const int shape = d->inputs[S.start].shape;
+        if (shape != TB200_SHAPE_ALONG && shape != TB200_SHAPE_SCALAR) return TB200_ERR_SHAPE;
+    }
+    for (int o = 0; o < d->n_outputs; o++) {
+        const tb200_group_output &out = d->outputs[o];
+        if (out.dtype != TB200_F32 && out.dtype != TB200_BF16) return TB200_ERR_DTYPE;
+        if (out.from == 0) {
+            if (out.index < 0 || out.index >= d->n_terms || out.ld < d->n) return TB200_ERR_SHAPE;
+        } else if (out.from == 3) {
+            if (out.index < 0 || out.index >= r->n_states) return TB200_ERR_SHAPE;
+        } else {
+            return TB200_ERR_UNSUPPORTED;
+        }
+    }
+    return TB200_OK;
+}
+
+std::string generate_recurrence(const tb200_recurrence_desc &r) {
+    const tb200_group_desc &d = r.body;
+    int streamed = 0;
+    for (int i = 0; i < d.n_inputs; i++) streamed += d.inputs[i].shape == TB200_SHAPE_FULL || d.inputs[i].shape == TB200_SHAPE_PER_ROW;
+    const int B = streamed > 4 ? 4 : 8;   // steps whose loads are in flight together (two such sets of registers)
+    Emitter E;
+    E.line(0, "typedef unsigned short u16; typedef unsigned int u32; typedef long long i64;");
+    E.line(0, "struct Params { const void *in[8]; void *out[8]; i64 ld_in[8]; i64 ld_out[8]; i64 n, steps; };");
+    E.line(0, "#define LOG2E 1.4426950408889634f");
+    E.line(0, "static __device__ __forceinline__ float ex2(float x) { float y; asm(\"ex2.approx.ftz.f32 %0, %1;\" : \"=f\"(y) : \"f\"(x)); return y; }");
+    E.line(0, "static __device__ __forceinline__ float exp_diff(float a, float b) { return ex2(fmaf(a, LOG2E, -(b * LOG2E))); }");
+    E.line(0, "static __device__ __forceinline__ float bf2f(u32 h) { return __uint_as_float(h << 16); }");
+    E.line(0, "static __device__ __forceinline__ u32 f2bf(float f) { u16 r; asm(\"cvt.rn.bf16.f32 %0, %1;\" : \"=h\"(r) : \"f\"(f)); return r; }");
+    auto load = [&](int i, const std::string &index) {
+        const std::string at = "[" + index + "]";
+        return d.inputs[i].dtype == TB200_BF16 ? "bf2f(__ldg((const u16 *)p.in[" + num(i) + "] + " + index + "))"
+                                               : "__ldg((const float *)p.in[" + num(i) + "] + " + index + ")";
+    };
+    auto store = [&](int o, const std::string &index, const std::string &value) {
+        return d.outputs[o].dtype == TB200_BF16 ? "((u16 *)p.out[" + num(o) + "])[" + index + "] = (u16)f2bf(" + value + ");"
+                                                : "((float *)p.out[" + num(o) + "])[" + index + "] = " + value + ";";
+    };
+    E.line(0, "extern \"C\" __global__ void __launch_bounds__(256) tb200_recurrence(const Params p) {");
+    E.line(1, "const i64 col = (i64)blockIdx.x * blockDim.x + threadIdx.x;");
+    E.line(1, "if (col >= p.n) return;");
+    E.line(1, "const int i0 = (int)col, e = 0; (void)i0; (void)e;");
+    // constants of the position, and the states' starts
+    for (int i = 0; i < d.n_inputs; i++) {
+        if (d.inputs[i].shape == TB200_SHAPE_ALONG) E.line(1, "const float al" + num(i) + " = " + load(i, "col") + ";");
+        if (d.inputs[i].shape == TB200_SHAPE_SCALAR) E.line(1, "const float sc" + num(i) + " = " + load(i, "0") + ";");
+    }
+    for (int k = 0; k < r.n_states; k++) {
+        const int i = r.states[k].start;
+        E.line(1, "float st" + num(k) + " = " + (d.inputs[i].shape == TB200_SHAPE_ALONG ? "al" : "sc") + num(i) + ";");
+    }
+    // the loads of a block of steps are in flight while the block before it is computed: two sets of registers
+    for (int i = 0; i < d.n_inputs; i++) {
+        const std::string size = "[" + num(B) + "]";
+        if (d.inputs[i].shape == TB200_SHAPE_FULL) E.line(1, "float x" + num(i) + size + ", nx" + num(i) + size + ";");
+        if (d.inputs[i].shape == TB200_SHAPE_PER_ROW) E.line(1, "float pw" + num(i) + size + ", npw" + num(i) + size + ";");
+    }
+    auto fetch = [&](int level, const std::string &first) {
+        E.line(level, "#pragma unroll");
+        E.line(level, "for (int j = 0; j < " + num(B) + "; j++) {");
+        E.line(level + 1, "const i64 s = " + first + " + j < p.steps ? " + first + " + j : p.steps - 1;");
+        E.line(level + 1, std::string("const i64 row = ") + (r.reverse ? "p.steps - 1 - s" : "s") + ";");
+        for (int i = 0; i < d.n_inputs; i++) {
+            if (d.inputs[i].shape == TB200_SHAPE_FULL)
+                E.line(level + 1, "nx" + num(i) + "[j] = " + load(i, "row * p.ld_in[" + num(i) + "] + col") + ";");
+            if (d.inputs[i].shape == TB200_SHAPE_PER_ROW) E.line(level + 1, "npw" + num(i) + "[j] = " + load(i, "row") + ";");
+        }
+        E.line(level, "}");
+    };
+    E.line(1, "if (p.steps > 0) {");   // no steps: the states leave as they start, nothing is read
+    fetch(2, "0");
+    E.line(1, "}");
+    E.line(1, "for (i64 s0 = 0; s0 < p.steps; s0 += " + num(B) + ") {");
+    E.line(2, "#pragma unroll");
+    E.line(2, "for (int j = 0; j < " + num(B) + "; j++) {");
+    for (int i = 0; i < d.n_inputs; i++) {
+        if (d.inputs[i].shape == TB200_SHAPE_FULL) E.line(3, "x" + num(i) + "[j] = nx" + num(i) + "[j];");
+        if (d.inputs[i].shape == TB200_SHAPE_PER_ROW) E.line(3, "pw" + num(i) + "[j] = npw" + num(i) + "[j];");
+    }
+    E.line(2, "}");
+    fetch(2, "(s0 + " + num(B) + ")");
+    E.line(2, "#pragma unroll");
+    E.line(2, "for (int j = 0; j < " + num(B) + "; j++) {");
+    E.line(3, "if (s0 + j < p.steps) {");
+    E.line(4, std::string("const i64 row = ") + (r.reverse ? "p.steps - 1 - (s0 + j)" : "s0 + j") + ";");
+    for (int k = 0; k < d.n_terms; k++) {
+        const tb200_term &T = d.terms[k];
+        std::string expr;
+        if (T.op == TB200_T_LOAD) {
+            const int shape = d.inputs[T.a].shape;
+            expr = shape == TB200_SHAPE_FULL ? "x" + num(T.a) + "[j]" : shape == TB200_SHAPE_PER_ROW ? "pw" + num(T.a) + "[j]"
+                   : shape == TB200_SHAPE_ALONG ? "al" + num(T.a) : "sc" + num(T.a);
+        } else {
+            expr = term_expr(d, k, "");
+        }
+        E.line(4, "const float t" + num(k) + " = " + expr + ";");
+    }
+    for (int o = 0; o < d.n_outputs; o++)
+        if (d.outputs[o].from == 0) E.line(4, store(o, "row * p.ld_out[" + num(o) + "] + col", "t" + num(d.outputs[o].index)));
+    for (int k = 0; k < r.n_states; k++) E.line(4, "st" + num(k) + " = t" + num(r.states[k].next) + ";");
+    E.line(3, "}");
+    E.line(2, "}");
+    E.line(1, "}");
+    for (int o = 0; o < d.n_outputs; o++)
+        if (d.outputs[o].from == 3) E.line(1, store(o, "col", "st" + num(d.outputs[o].index)));
+    E.line(0, "}");
+    return E.s;
+}
+
+struct CompiledRec {
+    std::vector<char> cubin;
+    CUfunction function[64] = {};
+};
+std::map<std::string, CompiledRec *> g_rec_cache;   // guarded by g_cache_lock
+
+int compile_recurrence(const tb200_recurrence_desc *r, CompiledRec **out) {
+    int st = check_recurrence(r);
+    if (st) return st;
+    std::string key = "rec:" + cache_key(&r->body, 0, 0);
+    for (int i = 0; i < r->body.n_inputs; i++) key.push_back(static_cast<char>('0' + r->body.inputs[i].shape));
+    for (int k = 0; k < r->body.n_terms; k++)
+        if (r->body.terms[k].op == TB200_T_STATE) key += "s" + num(k) + "=" + num(r->body.terms[k].a) + ";";
+    for (int k = 0; k < r->n_states; k++) key += "|" + num(r->states[k].start) + "," + num(r->states[k].next);
+    key += r->reverse ? "R" : "F";
+    std::lock_guard<std::mutex> hold(g_cache_lock);
+    auto it = g_rec_cache.find(key);
+    if (it != g_rec_cache.end()) {
+        *out = it->second;
+        return TB200_OK;
+    }
+    Nvrtc &n = nvrtc();
+    if (!n.ok) return TB200_ERR_UNSUPPORTED;
+    const std::string source = generate_recurrence(*r);
+    void *prog = nullptr;
+    if (n.create(&prog, source.c_str(), "tb200_recurrence.cu", 0, nullptr, nullptr) != 0) return TB200_ERR_UNSUPPORTED;
+    const char *options[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-default-device", "--disable-warnings"};
+    const int rc = n.compile(prog, 4, options);
+    size_t log_bytes = 0;
+    n.log_size(prog, &log_bytes);
+    g_log.assign(log_bytes, '\0');
+    if (log_bytes) n.log(prog, &g_log[0]);
+    if (rc != 0) {
+        n.destroy(&prog);
+        return TB200_ERR_UNSUPPORTED;
+    }
+    size_t bytes = 0;
+    n.cubin_size(prog, &bytes);
+    CompiledRec *c = new CompiledRec();
+    c->cubin.resize(bytes);
+    n.cubin(prog, c->cubin.data());
+    n.destroy(&prog);
+    g_rec_cache[key] = c;
+    *out = c;
+    return TB200_OK;
+}
+
 }  // namespace
 }  // namespace tb200
 
@@ -946,14 +1148,16 @@ extern "C" int tb200_rowreduce_compiled(const tb200_group_desc *d, const void *c
     LaunchParams P{};
     bool any_f32 = false;
     for (int i = 0; i < d->n_inputs; i++) {
-        if (!inputs[i]) return TB200_ERR_NULL;
+        // with no steps the arrays that have one row per step are empty, and an empty array may have no address
+        const bool per_step = d->inputs[i].shape == TB200_SHAPE_FULL || d->inputs[i].shape == TB200_SHAPE_PER_ROW;
+        if (!inputs[i] && !(per_step && d->rows == 0)) return TB200_ERR_NULL;
         if (!aligned_to(inputs[i], dtype_size(d->inputs[i].dtype))) return TB200_ERR_ALIGN;
         P.in[i] = inputs[i];
         P.ld_in[i] = d->inputs[i].ld;
         if (d->inputs[i].shape == TB200_SHAPE_FULL || d->inputs[i].shape == TB200_SHAPE_ALONG) any_f32 |= d->inputs[i].dtype == TB200_F32;
     }
     for (int o = 0; o < d->n_outputs; o++) {
-        if (!outputs[o]) return TB200_ERR_NULL;
+        if (!outputs[o] && !(d->outputs[o].from == 0 && d->rows == 0)) return TB200_ERR_NULL;
         if (!aligned_to(outputs[o], dtype_size(d->outputs[o].dtype))) return TB200_ERR_ALIGN;
         P.out[o] = outputs[o];
         P.ld_out[o] = d->outputs[o].ld;
@@ -1033,7 +1237,9 @@ extern "C" int tb200_colreduce_compiled(const tb200_group_desc *d, const void *c
     if (!outputs || (d->n_inputs > 0 && !inputs)) return TB200_ERR_NULL;
     ColParams P{};
     for (int i = 0; i < d->n_inputs; i++) {
-        if (!inputs[i]) return TB200_ERR_NULL;
+        // with no steps the arrays that have one row per step are empty, and an empty array may have no address
+        const bool per_step = d->inputs[i].shape == TB200_SHAPE_FULL || d->inputs[i].shape == TB200_SHAPE_PER_ROW;
+        if (!inputs[i] && !(per_step && d->rows == 0)) return TB200_ERR_NULL;
         if (!aligned_to(inputs[i], dtype_size(d->inputs[i].dtype))) return TB200_ERR_ALIGN;
         P.in[i] = inputs[i];
         P.ld_in[i] = d->inputs[i].ld;
@@ -1079,6 +1285,76 @@ extern "C" int tb200_colreduce_compiled(const tb200_group_desc *d, const void *c
                     static_cast<CUstream>(stream_), args, nullptr) != CUDA_SUCCESS)
         return TB200_ERR_CUDA;
     if (drv->launch(c->merge[dev.device], merge_blocks, 1, 1, kColThreads, 1, 1, 0, static_cast<CUstream>(stream_), args,
+                    nullptr) != CUDA_SUCCESS)
+        return TB200_ERR_CUDA;
+    return TB200_OK;
+}
+
+extern "C" int tb200_recurrence_compile(const tb200_recurrence_desc *r) {
+    CompiledRec *c = nullptr;
+    return compile_recurrence(r, &c);
+}
+
+extern "C" size_t tb200_recurrence_source(const tb200_recurrence_desc *r, char *buffer, size_t buffer_bytes) {
+    if (check_recurrence(r) != TB200_OK) return 0;
+    const std::string source = generate_recurrence(*r);
+    if (buffer && buffer_bytes > 0) {
+        const size_t len = source.size() < buffer_bytes - 1 ? source.size() : buffer_bytes - 1;
+        memcpy(buffer, source.data(), len);
+        buffer[len] = '\0';
+    }
+    return source.size() + 1;
+}
+
+extern "C" int tb200_recurrence_compiled(const tb200_recurrence_desc *r, const void *const *inputs, void *const *outputs,
+                                         void *stream_) {
+    int st = check_recurrence(r);
+    if (st) return st;
+    const tb200_group_desc *d = &r->body;
+    if (d->n == 0) return TB200_OK;
+    if (!outputs || !inputs) return TB200_ERR_NULL;
+    RecParams P{};
+    for (int i = 0; i < d->n_inputs; i++) {
+        // with no steps the arrays that have one row per step are empty, and an empty array may have no address
+        const bool per_step = d->inputs[i].shape == TB200_SHAPE_FULL || d->inputs[i].shape == TB200_SHAPE_PER_ROW;
+        if (!inputs[i] && !(per_step && d->rows == 0)) return TB200_ERR_NULL;
+        if (!aligned_to(inputs[i], dtype_size(d->inputs[i].dtype))) return TB200_ERR_ALIGN;
+        P.in[i] = inputs[i];
+        P.ld_in[i] = d->inputs[i].ld;
+    }
+    for (int o = 0; o < d->n_outputs; o++) {
+        if (!outputs[o] && !(d->outputs[o].from == 0 && d->rows == 0)) return TB200_ERR_NULL;
+        if (!aligned_to(outputs[o], dtype_size(d->outputs[o].dtype))) return TB200_ERR_ALIGN;
+        P.out[o] = outputs[o];
+        P.ld_out[o] = d->outputs[o].ld;
+    }
+    P.n = d->n;
+    P.steps = d->rows;
+    CompiledRec *c = nullptr;
+    if ((st = compile_recurrence(r, &c))) return st;
+    DeviceInfo dev;
+    if ((st = current_device(&dev))) return st;
+    Driver *drv = nullptr;
+    if ((st = driver(&drv))) return st;
+    {
+        std::lock_guard<std::mutex> hold(g_cache_lock);
+        if (!c->function[dev.device]) {
+            TB200_CUDA(cudaFree(nullptr));   // the runtime's context is current before the driver is used
+            CUmodule module = nullptr;
+            if (drv->module_load(&module, c->cubin.data()) != CUDA_SUCCESS) return TB200_ERR_CUDA;
+            CUfunction fn = nullptr;
+            if (drv->get_function(&fn, module, "tb200_recurrence") != CUDA_SUCCESS) return TB200_ERR_CUDA;
+            c->function[dev.device] = fn;
+        }
+    }
+    // the steps are a dependent chain per position, so the positions are the only parallelism: blocks as small as it
+    // takes to put some on every SM (a warp at the least), 256 threads once there are enough positions for that
+    unsigned threads = 256;
+    while (threads > 32 && ceil_div(d->n, threads) < 2ll * dev.sms) threads /= 2;
+    const long long blocks = ceil_div(d->n, threads);
+    if (blocks > 0x7fffffffll) return TB200_ERR_SHAPE;
+    void *args[] = {&P};
+    if (drv->launch(c->function[dev.device], static_cast<unsigned>(blocks), 1, 1, threads, 1, 1, 0, static_cast<CUstream>(stream_), args,
                     nullptr) != CUDA_SUCCESS)
         return TB200_ERR_CUDA;
     return TB200_OK;

@@ -11,8 +11,8 @@ from . import lib as L
 
 OPS = {"load": 0, "lit": 1, "index": 2, "stat": 3, "stat2": 4, "add": 5, "sub": 6, "mul": 7, "div": 8, "max": 9,
        "min": 10, "neg": 11, "exp": 12, "log": 13, "tanh": 14, "sqrt": 15, "rsqrt": 16, "abs": 17, "abs2": 18,
-       "recip": 19, "sigmoid": 20, "fma": 21, "select": 22, "round_bf16": 23, "recomputed": 24, "row_index": 25}
-ARITY = {**{k: 0 for k in ("load", "lit", "index", "stat", "stat2", "recomputed", "row_index")},
+       "recip": 19, "sigmoid": 20, "fma": 21, "select": 22, "round_bf16": 23, "recomputed": 24, "row_index": 25, "state": 26}
+ARITY = {**{k: 0 for k in ("load", "lit", "index", "stat", "stat2", "recomputed", "row_index", "state")},
          **{k: 2 for k in ("add", "sub", "mul", "div", "max", "min")},
          **{k: 1 for k in ("neg", "exp", "log", "tanh", "sqrt", "rsqrt", "abs", "abs2", "recip", "sigmoid", "round_bf16")},
          "fma": 3, "select": 3}
@@ -118,6 +118,97 @@ class Group:
         total += sum((self.n * self.rows if source == 0 else per_fold) * size[dtype]
                      for source, _, dtype, _ in self.outputs)
         return total
+
+
+class Recurrence(Group):
+    """A recurrence whose step is a map, over (n, steps): `n` positions that do not interact, stepping along the
+    other axis with states carried from step to step (the `:recurrence` groups of
+    src/Compiler/Implement/groups.jl:29-47 whose members are computed element by element).  States are declared
+    first (`state(start)`, started from an input of shape "along" or "scalar"), read with `carried(k)`, and given
+    their value after the step with `carry(k, term)`; every state is assigned at once from the values before the step."""
+
+    kind = "recurrence"
+
+    def __init__(self, n, steps, reverse=False):
+        super().__init__(n, steps)
+        self.reverse = bool(reverse)
+        self.states = []   # [start input, next term]
+
+    def state(self, start):
+        self.states.append([int(start), -1])
+        return len(self.states) - 1
+
+    def carried(self, k):
+        """The state's value before this step."""
+        return self._term("state", k)
+
+    def step_index(self):
+        return self._term("row_index")
+
+    def carry(self, k, term):
+        self.states[k][1] = int(term)
+
+    def output_state(self, k, eltype="Float32"):
+        """State k as the steps leave it: n values."""
+        self.outputs.append((3, int(k), DTYPES[eltype], 0))
+        return len(self.outputs) - 1
+
+    def bytes(self):
+        size = {L.F32: 4, L.BF16: 2}
+        extent = {0: self.n * self.rows, 1: self.n, 2: self.rows, 3: 1}
+        total = sum(extent[shape] * size[dtype] for shape, dtype, _ in self.inputs)
+        return total + sum((self.n * self.rows if source == 0 else self.n) * size[dtype]
+                           for source, _, dtype, _ in self.outputs)
+
+    def desc(self):
+        if not self.states or any(nxt < 0 for _, nxt in self.states) or len(self.states) > 4:
+            raise ValueError("a recurrence has one to four states, each carried from a term")
+        r = L.RecurrenceDesc()
+        r.body = super().desc()
+        r.n_states = len(self.states)
+        for k, (start, nxt) in enumerate(self.states):
+            r.states[k].start, r.states[k].next = start, nxt
+        r.reverse = int(self.reverse)
+        return r
+
+
+def gated_tanh_cell(n, steps, eltype="Float32", reverse=False):
+    """h = tanh.(a .* h .+ x) at every step, h stored: the map part of the reference's `cell`
+    (test/runtime/recurrences.jl:14) with a per-position gate in place of the matrix."""
+    g = Recurrence(n, steps, reverse)
+    x, a, h0 = g.input("full", eltype), g.input("along", eltype), g.input("along", eltype)
+    h = g.state(h0)
+    new = g.tanh(g.fma(g.load(a), g.carried(h), g.load(x)))
+    g.carry(h, new)
+    g.output(new, eltype)
+    g.output_state(h, eltype)
+    return g
+
+
+def second_order(n, steps, eltype="Float32"):
+    """(y, last) -> (tanh.(1.5 .* y .- 0.5 .* last .+ x), y): two states assigned at once, the second lagging the first
+    (test/runtime/recurrences.jl:195)."""
+    g = Recurrence(n, steps)
+    x, a, b = g.input("full", eltype), g.input("along", eltype), g.input("along", eltype)
+    y, last = g.state(a), g.state(b)
+    new = g.tanh(g.add(g.sub(g.mul(g.lit(1.5), g.carried(y)), g.mul(g.lit(0.5), g.carried(last))), g.load(x)))
+    g.carry(y, new)
+    g.carry(last, g.carried(y))
+    g.output(new, eltype)
+    g.output_state(y, eltype)
+    g.output_state(last, eltype)
+    return g
+
+
+def decayed_sum(n, steps, eltype="Float32"):
+    """s = s .* 0.5 .+ abs2.(x) with a scalar start: the map form of the reference's `run`
+    (test/runtime/recurrences.jl:15), only the last state kept."""
+    g = Recurrence(n, steps)
+    x, s0 = g.input("full", eltype), g.input("scalar", eltype)
+    s = g.state(s0)
+    g.carry(s, g.fma(g.carried(s), g.lit(0.5), g.abs2(g.load(x))))
+    g.output_state(s, eltype)
+    return g
 
 
 # ---- the reference's programs as groups -------------------------------------------------------------------

@@ -672,6 +672,26 @@ class ColumnLaunch(GroupLaunch):
                                address(self.workspace), self.workspace_bytes, _torch_stream())
 
 
+@dataclass(frozen=True)
+class RecurrenceClaim:
+    """What the generator offers for a `:recurrence` group whose step is a map over the parallel axis (the state is
+    carried per position, no reduction inside the step): one launch, one thread per position walking the steps
+    with the state in registers, compiled by NVRTC."""
+    states: int
+
+
+class RecurrenceLaunch(GroupLaunch):
+    """The launch of a recurrence whose step is a map (tb200_recurrence_compiled)."""
+
+    def __init__(self, group, inputs, outputs):
+        super().__init__(group, inputs, outputs, compiled=True)
+
+    def __call__(self):
+        address = lambda b: b.data_ptr() if hasattr(b, "data_ptr") else int(b)  # noqa: E731
+        lib.recurrence_compiled(self.desc, [address(b) for _, b in self.inputs], [address(b) for _, b in self.outputs],
+                                _torch_stream())
+
+
 class B200Generator:
     """`<: Implementation` for row groups: claims every group whose descriptor the library accepts."""
 
@@ -680,6 +700,12 @@ class B200Generator:
             desc = group.desc()
         except ValueError:
             return ()                                  # too large for one descriptor: decline
+        if getattr(group, "kind", "") == "recurrence":  # a step that is a map: the compiled form or nothing
+            try:
+                lib.recurrence_compile(desc)
+            except lib.TB200Error:
+                return ()
+            return (RecurrenceClaim(desc.n_states),)
         if getattr(group, "across", False):            # folds over the other axis: the compiled form or nothing
             try:
                 lib.colreduce_compile(desc)
@@ -712,6 +738,8 @@ class B200Generator:
             return [Work(bytes=2 * d * (2 * group.rows + 2 * group.n), flops=flops)]
         if isinstance(claim, ColumnClaim):
             return [Work(bytes=group.bytes(), blocks=(group.n + 255) // 256, launches=claim.launches, applied=0)]
+        if isinstance(claim, RecurrenceClaim):
+            return [Work(bytes=group.bytes(), blocks=(group.n + 255) // 256, launches=1, applied=0)]
         applied = 0 if claim.compiled else len(group.terms) * claim.phases
         return [Work(bytes=group.bytes(), blocks=group.rows, launches=1, applied=applied)]
 
@@ -740,6 +768,10 @@ class B200Generator:
             return (RoutedAttentionLaunch(group, ins, outs, (heads, kv_heads, batch)),
                     f"B200 attention{' (causal)' if claim.causal else ''} reached from the group's terms, {heads} heads "
                     f"over {kv_heads} of {d} features, {group.rows} queries by {group.n} keys, batch {batch}")
+        if isinstance(claim, RecurrenceClaim):
+            return (RecurrenceLaunch(group, ins, outs),
+                    f"B200 compiled recurrence, {group.n} positions over {group.rows} steps"
+                    f"{' in reverse' if group.reverse else ''}, {claim.states} states in registers, {len(group.terms)} terms")
         if isinstance(claim, ColumnClaim):
             need = lib.colreduce_workspace_bytes(group.desc())
             resources = resources if resources is not None else Resources()

@@ -105,6 +105,15 @@ class GroupDesc(ctypes.Structure):
                 ("folds", GroupFold * GROUP_MAX_FOLDS), ("outputs", GroupOutput * GROUP_MAX_OUTPUTS)]
 
 
+class StateDesc(ctypes.Structure):
+    _fields_ = [("start", ctypes.c_int), ("next", ctypes.c_int)]
+
+
+class RecurrenceDesc(ctypes.Structure):
+    """tb200_recurrence_desc of include/tempest_b200.h."""
+    _fields_ = [("body", GroupDesc), ("n_states", ctypes.c_int), ("states", StateDesc * 4), ("reverse", ctypes.c_int)]
+
+
 # name -> (restype, argtypes): the declarations of include/tempest_b200.h
 SIGNATURES = {
     "tb200_version": (_i, []),
@@ -154,6 +163,9 @@ SIGNATURES = {
     "tb200_colreduce_source": (_sz, [ctypes.POINTER(GroupDesc), ctypes.c_char_p, _sz]),
     "tb200_deltanet_bwd_workspace_bytes": (_sz, [ctypes.POINTER(DeltanetDesc)]),
     "tb200_deltanet_bwd": (_i, [ctypes.POINTER(DeltanetDesc)] + [_p] * 12 + [_sz, _p]),
+    "tb200_recurrence_compile": (_i, [ctypes.POINTER(RecurrenceDesc)]),
+    "tb200_recurrence_source": (_sz, [ctypes.POINTER(RecurrenceDesc), ctypes.c_char_p, _sz]),
+    "tb200_recurrence_compiled": (_i, [ctypes.POINTER(RecurrenceDesc), _p, _p, _p]),
     "tb200_gemm_pointers": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _i64, _p]),
     "tb200_scan_workspace_bytes": (_sz, [ctypes.POINTER(ScanDesc)]),
     "tb200_scan": (_i, [ctypes.POINTER(ScanDesc), _p, _p, _p, _p]),
@@ -614,6 +626,26 @@ def dp_error():
     if code < 0:
         check("tb200_dp_error", code)
     return code
+
+
+def recurrence_compile(desc):
+    check("tb200_recurrence_compile", load().tb200_recurrence_compile(ctypes.byref(desc)))
+
+
+def recurrence_source(desc):
+    need = load().tb200_recurrence_source(ctypes.byref(desc), None, 0)
+    if need == 0:
+        return ""
+    buf = ctypes.create_string_buffer(need)
+    load().tb200_recurrence_source(ctypes.byref(desc), buf, need)
+    return buf.value.decode()
+
+
+def recurrence_compiled(desc, inputs, outputs, stream=0):
+    """A recurrence whose step is a map (tb200_recurrence_compiled): inputs / outputs in the descriptor's order."""
+    ins = (ctypes.c_void_p * max(len(inputs), 1))(*inputs)
+    outs = (ctypes.c_void_p * max(len(outputs), 1))(*outputs)
+    check("tb200_recurrence_compiled", load().tb200_recurrence_compiled(ctypes.byref(desc), ins, outs, stream or None))
 
 
 def scan_desc(n, rows, op, *, across=False, reverse=False, dtype=F32, ld_x=None, ld_x2=None, ld_y=None, batch=1,
