@@ -3,10 +3,12 @@
 // Fast path (BFloat16 in, Float32 accumulate): a persistent, warp-specialised
 // kernel, one CTA per SM.  One thread issues TMA tile loads into a ring of
 // 128-byte-swizzled shared-memory stages; one thread issues tcgen05.mma
-// (128 x BN x 16 per instruction) accumulating in tensor memory; four warps
+// (128 x BN x 16 per instruction) accumulating in tensor memory; eight warps
 // drain finished accumulators with tcgen05.ld, apply the epilogue in
-// registers and store.  Tensor memory holds two accumulator tiles, so the
-// epilogue of tile i overlaps the main loop of tile i + 1.  Either operand may
+// registers and store whole lines through a staging buffer.  Tensor memory
+// holds two accumulator tiles, so the epilogue of tile i overlaps the main
+// loop of tile i + 1; what is not hidden is the last tile's drain, which is
+// why it is spread over eight warps.  Either operand may
 // be K-major or MN-major in memory (all of NN / NT / TN / TT), which is what
 // lets the backward products dX = dY * W' and dW = X' * dY read the forward's
 // arrays in place.  No load uses cluster multicast.  A launch may hold a batch
@@ -37,7 +39,8 @@ using namespace sm100;
 constexpr int BM = 128;
 constexpr int BK = 64;          // 64 BFloat16 = one 128-byte swizzle line
 constexpr int UMMA_K = 16;
-constexpr int kGemmThreads = 192;   // warp 0 loads, warp 1 issues MMAs, warps 2-5 run the epilogue
+constexpr int kGemmThreads = 320;   // warp 0 loads, warp 1 issues MMAs, warps 2-9 run the epilogue
+constexpr int kEpilogueWarps = 8;    // two per quarter of the accumulator's lanes, half of the tile's columns each
 constexpr int kAccumStages = 2;
 
 __device__ int g_gemm_error = 0;
@@ -45,10 +48,8 @@ __device__ int g_gemm_error = 0;
 struct GemmArgs {
     CUtensorMap tmap_a;
     CUtensorMap tmap_b;
-    CUtensorMap tmap_c;        // output tiles of 32 rows x 128 bytes (TMA epilogue only)
     CUtensorMap tmap_aux;
-    CUtensorMap tmap_aux_out;
-    int tma_epilogue;
+    int tma_epilogue;     // results leave through the staging buffers in whole lines (aux arrives by TMA)
     void *c;
     const void *bias;
     const void *aux;
@@ -255,81 +256,142 @@ __device__ __forceinline__ WorkItem work_item(const GemmArgs &p, int item, int n
     return w;
 }
 
-// One warp's share of a finished accumulator tile, through shared memory: 32 rows x 128 bytes at a
-// time are written (128-byte swizzled, so a thread writing its own row does not collide with its
-// neighbours) into a staging buffer and handed to a TMA store, which writes whole lines; the operand an
-// epilogue reads (aux) arrives the same way by a TMA load.  Returns false if a bounded wait gave up.
-template <int BN, int EPI, int OUT>
-__device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tmem_acc, int row0, int n0, int zc,
-                                                  int member, int lane, uint8_t *stage_c, uint8_t *stage_x,
-                                                  uint64_t *aux_bar, uint32_t &aux_phase, volatile int *failed) {
+// 32 staged rows of 128 bytes (swizzled as the threads wrote them) to global memory: eight lanes a row, a
+// 16-byte piece each, so a warp instruction writes four whole 128-byte lines.  `ES` bytes per element.
+template <int ES>
+__device__ __forceinline__ void flush_stage(const uint8_t *stage, uint8_t *base, long long pitch_bytes, int row0, int m,
+                                            int col0, int n, int lane) {
+    constexpr int PER = 16 / ES;
+    const int piece = lane & 7, sub = lane >> 3;
+    uint4 q[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int r = 4 * i + sub;
+        q[i] = *reinterpret_cast<const uint4 *>(stage + r * kStageLine + ((piece ^ (r & 7)) << 4));
+    }
+    const int col = col0 + piece * PER;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = row0 + 4 * i + sub;
+        if (row >= m || col >= n) continue;
+        uint8_t *dst = base + row * pitch_bytes + static_cast<long long>(col) * ES;
+        if (col + PER <= n) {
+            *reinterpret_cast<uint4 *>(dst) = q[i];
+        } else {
+            // the row's last piece, cut by the edge of the array
+            const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+#pragma unroll
+            for (int e = 0; e < PER; e++)
+                if (col + e < n) {
+                    if constexpr (ES == 4) reinterpret_cast<uint32_t *>(dst)[e] = w[e];
+                    else reinterpret_cast<uint16_t *>(dst)[e] = static_cast<uint16_t>(w[e >> 1] >> ((e & 1) * 16));
+                }
+        }
+    }
+}
+
+// 32 values of one row through the epilogue: acc -> v (what is stored), pre (what the activation saw).  Bias + GELU,
+// the forward's epilogue, runs as packed pairs: gelu(x) = x/2 + x/2 tanh(x (c + 0.044715 c x^2)), c = 0.7978846.
+template <int EPI>
+__device__ __forceinline__ void epilogue_values(const uint32_t (&r)[32], float alpha, const float (&bv)[32],
+                                                const float (&auxv)[32], float (&v)[32], float (&pre)[32]) {
+    if constexpr (EPI == TB200_EPI_BIAS_GELU) {
+        const float2 al = make_float2(alpha, alpha), c1 = make_float2(0.7978846f, 0.7978846f),
+                     c2 = make_float2(0.7978846f * 0.044715f, 0.7978846f * 0.044715f), half = make_float2(0.5f, 0.5f);
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), al,
+                                        make_float2(bv[j], bv[j + 1]));
+            const float2 u = __fmul2_rn(x, __ffma2_rn(__fmul2_rn(x, x), c2, c1));
+            const float2 hx = __fmul2_rn(x, half);
+            const float2 y = __ffma2_rn(hx, make_float2(tanh_fast(u.x), tanh_fast(u.y)), hx);
+            pre[j] = x.x; pre[j + 1] = x.y;
+            v[j] = y.x; v[j + 1] = y.y;
+        }
+    } else {
+        constexpr bool reads_bias = epilogue_reads_bias(EPI), reads_aux = epilogue_reads_aux(EPI);
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float a = __uint_as_float(r[j]) * alpha;
+            pre[j] = a;
+            v[j] = epilogue_fixed<EPI>(a, reads_bias ? bv[j] : 0.0f, reads_aux ? auxv[j] : 0.0f, pre[j]);
+        }
+    }
+}
+
+// One epilogue warp's share of a finished accumulator tile -- 32 rows by `COLS` columns from column `c_off` of the
+// tile -- through shared memory: the threads (one accumulator row each) write 32 rows x 128 bytes at a time into the
+// warp's staging buffer (128-byte swizzled, so that a thread writing its own row does not collide with its
+// neighbours), and the warp reads the buffer back a line at a time and stores whole 128-byte lines.  The operand an
+// epilogue reads (aux) arrives in the same buffer by a TMA load and is taken into registers before the results go
+// over it; a second result (the pre-activation values) goes through the buffer after the first.  `bias_q`: the tile's
+// bias, eight columns a lane.  Returns false if a bounded wait gave up.
+template <int COLS, int EPI, int OUT>
+__device__ __forceinline__ bool epilogue_tile_staged(const GemmArgs &p, uint32_t tmem_acc, int row0, int n0, int c_off,
+                                                     int zc, int member, int lane, uint8_t *stage, uint64_t *aux_bar,
+                                                     uint32_t &aux_phase, volatile int *failed, uint4 bias_q) {
     constexpr int EPL = OUT == OUT_F32 ? 32 : 64;   // elements per 128-byte line
+    constexpr int HALVES = EPL / 32;
+    constexpr int ES = OUT == OUT_F32 ? 4 : 2;
     constexpr bool reads_bias = epilogue_reads_bias(EPI), reads_aux = epilogue_reads_aux(EPI);
     const bool has_aux_out = EPI == TB200_EPI_BIAS_GELU && p.aux_out != nullptr;
     const int sw = lane & 7;
     const bool in_f16 = p.in_f16 != 0;
+    uint8_t *mine = stage + lane * kStageLine;
 #pragma unroll 1
-    for (int g = 0; g < BN / EPL; g++) {
-        const int col0 = n0 + g * EPL;
+    for (int g = 0; g < COLS / EPL; g++) {
+        const int col0 = n0 + c_off + g * EPL;
         if (col0 >= p.n) break;
-        // one staging buffer per warp: the previous group's stores must have read it
-        if (lane == 0) bulk_wait_group_read<0>();
-        __syncwarp();
+        uint4 ax[8];
         if (reads_aux) {
+            __syncwarp();   // every lane has read the previous group out of the buffer
             if (lane == 0) {
                 mbar_arrive_expect_tx(aux_bar, kEpilogueStage);
-                tma_load_3d(stage_x, &p.tmap_aux, aux_bar, col0, row0, member);
+                tma_load_3d(stage, &p.tmap_aux, aux_bar, col0, row0, member);
             }
             if (!wait_or_fail(aux_bar, aux_phase, failed, 5, p.wait_ns)) return false;
             aux_phase ^= 1;
-        }
-#pragma unroll 1
-        for (int h = 0; h < EPL / 32; h++) {
-            uint32_t r[32];
-            tmem_ld_32x32(tmem_acc + g * EPL + h * 32, r);
-            tmem_ld_wait();
-            const int c0 = col0 + h * 32;
-            float v[32], auxv[32];
 #pragma unroll
-            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]) * p.alpha;
+            for (int j = 0; j < 8; j++) ax[j] = *reinterpret_cast<const uint4 *>(mine + ((j ^ sw) << 4));
+        }
+        __syncwarp();   // the buffer is free: the results may go over it
+        uint4 zq[8];
+#pragma unroll
+        for (int h = 0; h < HALVES; h++) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_acc + c_off + g * EPL + h * 32, r);
+            tmem_ld_wait();
+            float auxv[32], bv[32];
             if (reads_aux) {
                 if constexpr (OUT == OUT_F32) {
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
-                        const float4 q = *reinterpret_cast<const float4 *>(stage_x + lane * kStageLine + ((j ^ sw) << 4));
-                        auxv[4 * j] = q.x; auxv[4 * j + 1] = q.y; auxv[4 * j + 2] = q.z; auxv[4 * j + 3] = q.w;
+                        auxv[4 * j] = __uint_as_float(ax[j].x); auxv[4 * j + 1] = __uint_as_float(ax[j].y);
+                        auxv[4 * j + 2] = __uint_as_float(ax[j].z); auxv[4 * j + 3] = __uint_as_float(ax[j].w);
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const uint4 q =
-                            *reinterpret_cast<const uint4 *>(stage_x + lane * kStageLine + (((4 * h + j) ^ sw) << 4));
-                        unpack_half8(q, &auxv[8 * j], OUT == OUT_F16);
-                    }
+                    for (int j = 0; j < 4; j++) unpack_half8(ax[4 * h + j], &auxv[8 * j], OUT == OUT_F16);
                 }
             }
-            float bv[32];
             if (reads_bias) {
-                const uint16_t *bp = static_cast<const uint16_t *>(p.bias) + member * p.stride_bias + c0;
-                if (c0 + 32 <= p.n && aligned_dev(bp, 16)) {
+                const int src = (c_off + g * EPL + h * 32) >> 3;
 #pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        unpack_half8(__ldg(reinterpret_cast<const uint4 *>(bp) + j), &bv[8 * j], in_f16);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) bv[j] = (c0 + j < p.n) ? half_to_f32(bp, j, in_f16) : 0.0f;
+                for (int j = 0; j < 4; j++) {
+                    uint4 q;
+                    q.x = __shfl_sync(0xffffffffu, bias_q.x, src + j);
+                    q.y = __shfl_sync(0xffffffffu, bias_q.y, src + j);
+                    q.z = __shfl_sync(0xffffffffu, bias_q.z, src + j);
+                    q.w = __shfl_sync(0xffffffffu, bias_q.w, src + j);
+                    unpack_half8(q, &bv[8 * j], in_f16);
                 }
             }
-            float pre[32];
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-                pre[j] = v[j];
-                v[j] = epilogue_fixed<EPI>(v[j], reads_bias ? bv[j] : 0.0f, reads_aux ? auxv[j] : 0.0f, pre[j]);
-            }
+            float v[32], pre[32];
+            epilogue_values<EPI>(r, p.alpha, bv, auxv, v, pre);
             if constexpr (OUT == OUT_F32) {
 #pragma unroll
                 for (int j = 0; j < 8; j++)
-                    *reinterpret_cast<float4 *>(stage_c + lane * kStageLine + ((j ^ sw) << 4)) =
+                    *reinterpret_cast<float4 *>(mine + ((j ^ sw) << 4)) =
                         make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             } else {
 #pragma unroll
@@ -339,23 +401,28 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs &p, uint32_t tm
                     q.y = pack_half2<OUT>(v[8 * j + 2], v[8 * j + 3]);
                     q.z = pack_half2<OUT>(v[8 * j + 4], v[8 * j + 5]);
                     q.w = pack_half2<OUT>(v[8 * j + 6], v[8 * j + 7]);
-                    *reinterpret_cast<uint4 *>(stage_c + lane * kStageLine + (((4 * h + j) ^ sw) << 4)) = q;
+                    *reinterpret_cast<uint4 *>(mine + (((4 * h + j) ^ sw) << 4)) = q;
                     if (has_aux_out) {
-                        q.x = pack_half2<OUT>(pre[8 * j], pre[8 * j + 1]);
-                        q.y = pack_half2<OUT>(pre[8 * j + 2], pre[8 * j + 3]);
-                        q.z = pack_half2<OUT>(pre[8 * j + 4], pre[8 * j + 5]);
-                        q.w = pack_half2<OUT>(pre[8 * j + 6], pre[8 * j + 7]);
-                        *reinterpret_cast<uint4 *>(stage_x + lane * kStageLine + (((4 * h + j) ^ sw) << 4)) = q;
+                        zq[4 * h + j].x = pack_half2<OUT>(pre[8 * j], pre[8 * j + 1]);
+                        zq[4 * h + j].y = pack_half2<OUT>(pre[8 * j + 2], pre[8 * j + 3]);
+                        zq[4 * h + j].z = pack_half2<OUT>(pre[8 * j + 4], pre[8 * j + 5]);
+                        zq[4 * h + j].w = pack_half2<OUT>(pre[8 * j + 6], pre[8 * j + 7]);
                     }
                 }
             }
         }
-        fence_proxy_async();
         __syncwarp();
-        if (lane == 0) {
-            tma_store_3d(&p.tmap_c, stage_c, col0, row0, zc);
-            if (has_aux_out) tma_store_3d(&p.tmap_aux_out, stage_x, col0, row0, member);
-            bulk_commit_group();
+        flush_stage<ES>(stage, static_cast<uint8_t *>(p.c) + static_cast<long long>(zc) * p.stride_c * ES, p.ldc * ES, row0,
+                        p.m, col0, p.n, lane);
+        if constexpr (OUT != OUT_F32) {
+            if (has_aux_out) {
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 8; j++) *reinterpret_cast<uint4 *>(mine + ((j ^ sw) << 4)) = zq[j];
+                __syncwarp();
+                flush_stage<2>(stage, static_cast<uint8_t *>(p.aux_out) + static_cast<long long>(member) * p.stride_aux_out * 2,
+                               p.ld_aux_out * 2, row0, p.m, col0, p.n, lane);
+            }
         }
     }
     return true;
@@ -375,7 +442,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
     __shared__ __align__(8) uint64_t tmem_full_bar[kAccumStages];
     __shared__ __align__(8) uint64_t tmem_empty_bar[kAccumStages];
-    __shared__ __align__(8) uint64_t aux_bar[4];
+    __shared__ __align__(8) uint64_t aux_bar[kEpilogueWarps];
     // the work items of this block, handed from the loading thread to the MMA thread and the epilogue warps
     constexpr int kItemSlots = 4;
     __shared__ __align__(8) uint64_t item_full[kItemSlots];
@@ -400,17 +467,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
         }
         for (int s = 0; s < kAccumStages; s++) {
             mbar_init(&tmem_full_bar[s], 1);
-            mbar_init(&tmem_empty_bar[s], 4);
+            mbar_init(&tmem_empty_bar[s], kEpilogueWarps);
         }
-        for (int s = 0; s < 4; s++) mbar_init(&aux_bar[s], 1);
+        for (int s = 0; s < kEpilogueWarps; s++) mbar_init(&aux_bar[s], 1);
         for (int s = 0; s < kItemSlots; s++) {
             mbar_init(&item_full[s], 1);
-            mbar_init(&item_empty[s], 5);   // the MMA thread and one lane of each epilogue warp
+            mbar_init(&item_empty[s], 1 + kEpilogueWarps);   // the MMA thread and one lane of each epilogue warp
         }
         fence_barrier_init();
         prefetch_tensormap(&p.tmap_a);
         prefetch_tensormap(&p.tmap_b);
-        if (p.tma_epilogue) prefetch_tensormap(&p.tmap_c);
+        if (p.tma_epilogue && epilogue_reads_aux(EPI)) prefetch_tensormap(&p.tmap_aux);
     }
     if (warp == 1) {
         tmem_alloc(&tmem_base_smem, kAccumStages * BN);
@@ -507,13 +574,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             }
         }
     } else {
-        // ---- epilogue: warp q owns tensor-memory lanes [32 q, 32 q + 32)
+        // ---- epilogue: warps q and q + 4 own tensor-memory lanes [32 q, 32 q + 32), half of the tile's columns each
         const int q = warp & 3;
+        const int c_off = ((warp - 2) >> 2) * (BN / 2);
         int it = 0;
-        // staging for the TMA epilogue sits behind the operand ring: per warp one buffer for the
-        // output and one for the operand the epilogue reads or the second array it writes
-        uint8_t *stage_c = smem + stages * STAGE_BYTES + (warp - 2) * 2 * kEpilogueStage;
-        uint8_t *stage_x = stage_c + kEpilogueStage;
+        // staging for the epilogue sits behind the operand ring: one buffer of 32 lines per warp
+        uint8_t *stage = smem + stages * STAGE_BYTES + (warp - 2) * kEpilogueStage;
         uint32_t aux_phase = 0;
         const bool in_f16 = p.in_f16 != 0;
         int slot = 0;
@@ -528,6 +594,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             const WorkItem w = work_item(p, item, num_kb);
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
+            // the tile's bias, eight columns a lane, fetched while the accumulator is still being summed
+            uint4 bias_q = make_uint4(0u, 0u, 0u, 0u);
+            if (epilogue_reads_bias(EPI) && p.tma_epilogue && lane < BN / 8) {
+                const int col = w.tn * BN + lane * 8;
+                const uint16_t *bp = static_cast<const uint16_t *>(p.bias) + w.member * p.stride_bias + col;
+                if (col + 8 <= p.n && aligned_dev(bp, 16)) {
+                    bias_q = __ldg(reinterpret_cast<const uint4 *>(bp));
+                } else {
+                    uint32_t h[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) h[e] = col + e < p.n ? bp[e] : 0u;
+                    bias_q = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+                }
+            }
             if (!wait_or_fail(&tmem_full_bar[acc], acc_phase, failed, 4, wait_ns)) break;
             tcgen05_fence_after();
             if (p.tma_epilogue) {
@@ -535,8 +615,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
                 const uint32_t tmem_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
                 bool ok = true;
                 if (row0 < p.m)
-                    ok = epilogue_tile_tma<BN, EPI, OUT>(p, tmem_acc, row0, w.tn * BN, w.zc, w.member, lane, stage_c,
-                                                         stage_x, &aux_bar[warp - 2], aux_phase, failed);
+                    ok = epilogue_tile_staged<BN / 2, EPI, OUT>(p, tmem_acc, row0, w.tn * BN, c_off, w.zc, w.member, lane,
+                                                                stage, &aux_bar[warp - 2], aux_phase, failed, bias_q);
                 if (!ok) break;
                 tcgen05_fence_before();
                 __syncwarp();
@@ -553,7 +633,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
                 static_cast<long long>(w.member) * p.stride_aux_out + static_cast<long long>(m) * p.ld_aux_out;
             const void *bias = static_cast<const uint16_t *>(p.bias) + w.member * p.stride_bias;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
+            for (int c = c_off / 32; c < (c_off + BN / 2) / 32; c++) {
                 uint32_t r[32];
                 __syncwarp();   // rows past the edge skip the stores below: rejoin before the warp-wide load
                 tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
@@ -601,8 +681,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
         }
-        // the staging buffers must outlive the stores that read them
-        if (p.tma_epilogue && lane == 0) bulk_wait_group<0>();
     }
 
     tcgen05_fence_before();
@@ -985,11 +1063,7 @@ int prepare(tb200_gemm_plan *plan) {
             p.c = d->workspace; p.ldc = ldp; p.stride_c = d->m * ldp;
             p.alpha = 1.0f; p.epilogue = TB200_EPI_NONE;
             kernel_epilogue = TB200_EPI_NONE; kernel_out = TB200_F32;
-            p.tma_epilogue = !d->direct_epilogue;
-            if (p.tma_epilogue &&
-                (st = make_tmap(&p.tmap_c, d->workspace, d->n, d->m, ldp, 32, TB200_F32, static_cast<int64_t>(batch) * splits,
-                                d->m * ldp)))
-                return st;
+            p.tma_epilogue = !d->direct_epilogue && aligned_to(d->workspace, 16);
             MergeArgs &q = plan->merge_args;
             q = MergeArgs{};
             q.partial = static_cast<const float *>(d->workspace); q.c = c; q.bias = bias; q.aux = aux; q.aux_out = aux_out;
@@ -1021,20 +1095,16 @@ int prepare(tb200_gemm_plan *plan) {
                 tma_epi = tma_epi && d->out_dtype != TB200_F32 && aligned_to(aux_out, 16) && (d->ld_aux_out * 2) % 16 == 0 &&
                           pitch_ok(d->stride_aux_out, 2);
             if (tma_epi) {
-                if ((st = make_tmap(&p.tmap_c, c, d->n, d->m, d->ldc, 32, d->out_dtype, batch, d->stride_c))) return st;
                 if (needs_aux && (st = make_tmap(&p.tmap_aux, aux, d->n, d->m, d->ld_aux, 32, aux_dtype,
                                                  d->stride_aux ? batch : 1, d->stride_aux)))
                     return st;
                 if (needs_aux && batched && d->stride_aux == 0) tma_epi = false;   // a shared aux: plain loads
-                if (aux_out && (st = make_tmap(&p.tmap_aux_out, aux_out, d->n, d->m, d->ld_aux_out, 32, d->in_dtype, batch,
-                                               d->stride_aux_out)))
-                    return st;
             }
             p.tma_epilogue = tma_epi;
         }
         if ((st = kernel_by_shape(bn, kernel_out, kernel_epilogue, dev, &plan->kernel))) return st;
         const size_t stage_bytes = static_cast<size_t>(BM + bn) * BK * 2;
-        const size_t epilogue_bytes = 4 * 2 * kEpilogueStage;
+        const size_t epilogue_bytes = kEpilogueWarps * kEpilogueStage;
         int stages = static_cast<int>((dev.smem_optin - 2048 - epilogue_bytes) / stage_bytes);
         if (stages > 8) stages = 8;
         if (stages < 2) return TB200_ERR_UNSUPPORTED;
