@@ -185,7 +185,12 @@ typedef struct tb200_gemm_desc {
     int epilogue;                /* tb200_epilogue */
     float alpha;
     int tile_n;                  /* 0 = choose; 128 or 256 = the variant the tuner picked
-                                    (the counterpart of TEMPEST_PRODUCT_TILE, ext/cuTileExt/contract.jl:36-49) */
+                                    (the counterpart of TEMPEST_PRODUCT_TILE, ext/cuTileExt/contract.jl:36-49);
+                                    512 = tiles of 256 x 256 computed by pairs of CTAs on neighbouring SMs
+                                    (each loads half of either operand's tile; the pairs take their tiles in a
+                                    fixed order, not from a plan's counter); -1 = choose among the single-CTA
+                                    tiles only (for products that run beside another kernel and should draw
+                                    their tiles from the plan's counter) */
     int force_simt;              /* 1 = the generic kernel (Float32-exact, any alignment) */
     int direct_epilogue;         /* 1 = each thread stores its own output row instead of staging
                                     tiles through shared memory for TMA stores (a tuner variant) */
@@ -258,7 +263,7 @@ int tb200_gemm_plan_repoint(tb200_gemm_plan *plan, int operand, const void *addr
 void tb200_gemm_plan_destroy(tb200_gemm_plan *plan);
 
 /* Measures the compiled-in tile variants of one product on its own operands
- * and returns the faster tile_n (128 or 256) to put in the descriptor, or a
+ * and returns the faster tile_n (128, 256 or 512) to put in the descriptor, or a
  * negative status: the measured stage of the reference's search over a claim's
  * variants (src/Compiler/Implement/Implement.jl:120,
  * ext/cuTileExt/contract.jl:171-235) over what this library holds.  Overwrites C

@@ -428,13 +428,20 @@ __device__ __forceinline__ bool epilogue_tile_staged(const GemmArgs &p, uint32_t
     return true;
 }
 
-template <int BN, int EPI, int OUT>
+// PAIR: launched as clusters of two CTAs that share tiles of 256 x BN -- each CTA loads its 128 rows of A and its
+// half of B's columns, the first CTA's MMA thread issues 256-row instructions that read both, each CTA drains its own
+// 128 rows.  Per CTA and 64 of k that is 32 KB from L2 instead of 48 KB for the same 128 x 256 x 64 of work, and the
+// ring is six stages deep.  Both CTAs' loads count on the first CTA's barrier, where the MMA thread waits (plain
+// loads with one destination each: no multicast); the MMAs' completion arrives on both CTAs' barriers.
+template <int BN, int EPI, int OUT, bool PAIR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_constant__ GemmArgs p) {
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzle atoms are 1024 bytes: align the ring
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int ROWS = PAIR ? 2 * BM : BM;     // rows of a tile
+    constexpr int BNL = PAIR ? BN / 2 : BN;      // columns of B this CTA loads
     constexpr uint32_t A_BYTES = BM * BK * 2;
-    constexpr uint32_t B_BYTES = BN * BK * 2;
+    constexpr uint32_t B_BYTES = BNL * BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int MAX_STAGES = 8;
 
@@ -458,6 +465,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     const int num_kb = (p.k + BK - 1) / BK;
     const int num_items = p.tiles_m * p.tiles_n * p.batch * p.splits;
     const unsigned long long wait_ns = p.wait_ns;
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;
 
     if (threadIdx.x == 0) {
         failed_smem = 0;
@@ -467,7 +475,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
         }
         for (int s = 0; s < kAccumStages; s++) {
             mbar_init(&tmem_full_bar[s], 1);
-            mbar_init(&tmem_empty_bar[s], kEpilogueWarps);
+            mbar_init(&tmem_empty_bar[s], PAIR ? 2 * kEpilogueWarps : kEpilogueWarps);   // pair: both CTAs' warps
         }
         for (int s = 0; s < kEpilogueWarps; s++) mbar_init(&aux_bar[s], 1);
         for (int s = 0; s < kItemSlots; s++) {
@@ -480,11 +488,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
         if (p.tma_epilogue && epilogue_reads_aux(EPI)) prefetch_tensormap(&p.tmap_aux);
     }
     if (warp == 1) {
+        // each CTA of a pair allocates its own tensor memory: all of it, so both get the same (first) column
         tmem_alloc(&tmem_base_smem, kAccumStages * BN);
         tmem_relinquish();
     }
     tcgen05_fence_before();
-    __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();   // the other CTA's barriers are initialised before anything arrives on them
+    else __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_smem;
 
@@ -495,7 +505,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             int stage = 0, slot = 0;
             uint32_t phase = 0, slot_phase = 0;
             const bool withhold = (p.debug & 1) != 0;
-            int item = p.schedule ? atomicAdd(p.schedule, 1) : static_cast<int>(blockIdx.x);
+            // a pair takes its tiles by the cluster's index: both CTAs walk the same list
+            const int first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+            const int step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+            int item = (!PAIR && p.schedule) ? atomicAdd(p.schedule, 1) : first;
             while (true) {
                 if (!wait_or_fail(&item_empty[slot], slot_phase ^ 1, failed, 6, wait_ns)) break;
                 const bool live = item < num_items && !*failed;
@@ -504,39 +517,71 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
                 if (++slot == kItemSlots) { slot = 0; slot_phase ^= 1; }
                 if (!live) break;
                 // the next item is drawn now, so that the answer is there when this one's loads are out
-                const int next = p.schedule ? atomicAdd(p.schedule, 1) : item + static_cast<int>(gridDim.x);
+                const int next = (!PAIR && p.schedule) ? atomicAdd(p.schedule, 1) : item + step;
                 const WorkItem w = work_item(p, item, num_kb);
                 item = next;
                 if (withhold) continue;
-                const int m0 = w.tm * BM, n0 = w.tn * BN;
+                const int m0 = w.tm * ROWS + static_cast<int>(rank) * BM, n0 = w.tn * BN + static_cast<int>(rank) * (BN - BNL);
                 const int za = p.a_batched ? w.member : 0, zb = p.b_batched ? w.member : 0;
                 for (int kb = w.kb0; kb < w.kb1; kb++) {
                     if (!wait_or_fail(&empty_bar[stage], phase ^ 1, failed, 1, wait_ns)) break;
+
                     uint8_t *sa = smem + stage * STAGE_BYTES;
                     uint8_t *sb = sa + A_BYTES;
-                    mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
                     const int k0 = kb * BK;
-                    if (p.a_mn) {   // [K][M]: slabs of 64 along M, each 64 K-lines of 128 bytes
-                        for (int j = 0; j < BM / 64; j++)
-                            tma_load_3d(sa + j * (BK * 128), &p.tmap_a, &full_bar[stage], m0 + j * 64, k0, za);
-                    } else {        // [M][K]: 128 rows of 128 bytes
-                        tma_load_3d(sa, &p.tmap_a, &full_bar[stage], k0, m0, za);
-                    }
-                    if (p.b_mn) {
-                        for (int j = 0; j < BN / 64; j++)
-                            tma_load_3d(sb + j * (BK * 128), &p.tmap_b, &full_bar[stage], n0 + j * 64, k0, zb);
+                    if constexpr (PAIR) {
+                        // both CTAs' operands are counted on the first CTA's barrier, where the MMA thread waits
+                        if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+                        const uint32_t bar = cluster_map(&full_bar[stage], 0);
+                        if (p.a_mn) {
+                            for (int j = 0; j < BM / 64; j++)
+                                tma_load_3d_pair(sa + j * (BK * 128), &p.tmap_a, bar, m0 + j * 64, k0, za);
+                        } else {
+                            tma_load_3d_pair(sa, &p.tmap_a, bar, k0, m0, za);
+                        }
+                        if (p.b_mn) {
+                            for (int j = 0; j < BNL / 64; j++)
+                                tma_load_3d_pair(sb + j * (BK * 128), &p.tmap_b, bar, n0 + j * 64, k0, zb);
+                        } else {
+                            tma_load_3d_pair(sb, &p.tmap_b, bar, k0, n0, zb);
+                        }
                     } else {
-                        tma_load_3d(sb, &p.tmap_b, &full_bar[stage], k0, n0, zb);
+                        mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+                        if (p.a_mn) {   // [K][M]: slabs of 64 along M, each 64 K-lines of 128 bytes
+                            for (int j = 0; j < BM / 64; j++)
+                                tma_load_3d(sa + j * (BK * 128), &p.tmap_a, &full_bar[stage], m0 + j * 64, k0, za);
+                        } else {        // [M][K]: 128 rows of 128 bytes
+                            tma_load_3d(sa, &p.tmap_a, &full_bar[stage], k0, m0, za);
+                        }
+                        if (p.b_mn) {
+                            for (int j = 0; j < BNL / 64; j++)
+                                tma_load_3d(sb + j * (BK * 128), &p.tmap_b, &full_bar[stage], n0 + j * 64, k0, zb);
+                        } else {
+                            tma_load_3d(sb, &p.tmap_b, &full_bar[stage], k0, n0, zb);
+                        }
                     }
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
             }
         }
+    } else if (warp == 1 && PAIR && rank != 0) {
+        // ---- second CTA of a pair: no MMAs are issued here; the items are taken and let go
+        if (elect_one()) {
+            int slot = 0;
+            uint32_t slot_phase = 0;
+            for (;;) {
+                if (!wait_or_fail(&item_full[slot], slot_phase, failed, 7, wait_ns)) break;
+                const int item = item_slot[slot];
+                mbar_arrive(&item_empty[slot]);
+                if (++slot == kItemSlots) { slot = 0; slot_phase ^= 1; }
+                if (item < 0 || *failed) break;
+            }
+        }
     } else if (warp == 1) {
         // ---- MMA issuer
         if (elect_one()) {
-            const uint32_t idesc = p.in_f16 ? umma_idesc_f16(BM, BN, p.a_mn != 0, p.b_mn != 0)
-                                            : umma_idesc_bf16(BM, BN, p.a_mn != 0, p.b_mn != 0);
+            const uint32_t idesc = p.in_f16 ? umma_idesc_f16(ROWS, BN, p.a_mn != 0, p.b_mn != 0)
+                                            : umma_idesc_bf16(ROWS, BN, p.a_mn != 0, p.b_mn != 0);
             // K-major: 8-row groups 1024 bytes apart, 32 bytes per 16 K; MN-major: slabs BK*128 bytes
             // apart, 8-line groups 1024 bytes apart, 2048 bytes per 16 K
             const uint32_t a_lead = p.a_mn ? BK * 128 : 16, b_lead = p.b_mn ? BK * 128 : 16;
@@ -563,14 +608,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
                     const uint64_t a_desc = umma_smem_desc(sa, a_lead, 1024);
                     const uint64_t b_desc = umma_smem_desc(sa + A_BYTES, b_lead, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++)
-                        tcgen05_mma_f16(d_tmem, a_desc + k * a_step, b_desc + k * b_step, idesc,
-                                        ((kb - w.kb0) | k) != 0);
-                    tcgen05_commit(&empty_bar[stage]);   // the stage is free once these MMAs have read it
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        if constexpr (PAIR)
+                            tcgen05_mma_f16_pair(d_tmem, a_desc + k * a_step, b_desc + k * b_step, idesc,
+                                                 ((kb - w.kb0) | k) != 0);
+                        else
+                            tcgen05_mma_f16(d_tmem, a_desc + k * a_step, b_desc + k * b_step, idesc,
+                                            ((kb - w.kb0) | k) != 0);
+                    }
+                    // the stage is free (in both CTAs of a pair) once these MMAs have read it
+                    if constexpr (PAIR) tcgen05_commit_pair(&empty_bar[stage]);
+                    else tcgen05_commit(&empty_bar[stage]);
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
                 if (*failed) break;
-                tcgen05_commit(&tmem_full_bar[acc]);     // the accumulator is complete
+                // the accumulator is complete (in both CTAs of a pair)
+                if constexpr (PAIR) tcgen05_commit_pair(&tmem_full_bar[acc]);
+                else tcgen05_commit(&tmem_full_bar[acc]);
             }
         }
     } else {
@@ -611,7 +665,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             if (!wait_or_fail(&tmem_full_bar[acc], acc_phase, failed, 4, wait_ns)) break;
             tcgen05_fence_after();
             if (p.tma_epilogue) {
-                const int row0 = w.tm * BM + q * 32;
+                const int row0 = w.tm * ROWS + static_cast<int>(rank) * BM + q * 32;
                 const uint32_t tmem_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
                 bool ok = true;
                 if (row0 < p.m)
@@ -620,10 +674,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
                 if (!ok) break;
                 tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+                if (lane == 0) {
+                    if constexpr (PAIR) mbar_arrive_cluster(cluster_map(&tmem_empty_bar[acc], 0));
+                    else mbar_arrive(&tmem_empty_bar[acc]);
+                }
                 continue;
             }
-            const int m = w.tm * BM + q * 32 + lane;
+            const int m = w.tm * ROWS + static_cast<int>(rank) * BM + q * 32 + lane;
             const int n0 = w.tn * BN;
             const bool row_ok = m < p.m;
             constexpr bool reads_bias = epilogue_reads_bias(EPI), reads_aux = epilogue_reads_aux(EPI);
@@ -679,18 +736,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(cluster_map(&tmem_empty_bar[acc], 0));
+                else mbar_arrive(&tmem_empty_bar[acc]);
+            }
         }
     }
 
     tcgen05_fence_before();
-    __syncthreads();
+    // neither CTA of a pair leaves (or frees tensor memory) while the other may still arrive on its barriers
+    if constexpr (PAIR) cluster_sync_all();
+    else __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kAccumStages * BN);
     }
     // the last block out leaves the two counters as it found them, for the next launch
-    if (p.schedule && threadIdx.x == 0) {
+    if (!PAIR && p.schedule && threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(p.schedule + 1, 1) == static_cast<int>(gridDim.x) - 1) {
             p.schedule[0] = 0;
@@ -862,42 +924,47 @@ int make_tmap(CUtensorMap *map, const void *base, int64_t cols, int64_t rows, in
 }
 
 // The kernel instantiation for (tile width, epilogue, result type), its shared-memory attribute set once per device.
-template <int BN, int EPI, int OUT>
+template <int BN, int EPI, int OUT, bool PAIR>
 int kernel_for(const DeviceInfo &dev, const void **fn) {
     static std::mutex lock;
     static bool configured[64] = {};
     std::lock_guard<std::mutex> hold(lock);
     if (!configured[dev.device]) {
-        TB200_CUDA(cudaFuncSetAttribute(gemm_tcgen05<BN, EPI, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TB200_CUDA(cudaFuncSetAttribute(gemm_tcgen05<BN, EPI, OUT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(dev.smem_optin - 1024)));
         configured[dev.device] = true;
     }
-    *fn = reinterpret_cast<const void *>(&gemm_tcgen05<BN, EPI, OUT>);
+    *fn = reinterpret_cast<const void *>(&gemm_tcgen05<BN, EPI, OUT, PAIR>);
     return TB200_OK;
 }
 
-template <int BN, int OUT>
+template <int BN, int OUT, bool PAIR = false>
 int kernel_by_epilogue(int epilogue, const DeviceInfo &dev, const void **fn) {
     switch (epilogue) {
-        case TB200_EPI_NONE: return kernel_for<BN, TB200_EPI_NONE, OUT>(dev, fn);
-        case TB200_EPI_BIAS: return kernel_for<BN, TB200_EPI_BIAS, OUT>(dev, fn);
-        case TB200_EPI_AXPY: return kernel_for<BN, TB200_EPI_AXPY, OUT>(dev, fn);
+        case TB200_EPI_NONE: return kernel_for<BN, TB200_EPI_NONE, OUT, PAIR>(dev, fn);
+        case TB200_EPI_BIAS: return kernel_for<BN, TB200_EPI_BIAS, OUT, PAIR>(dev, fn);
+        case TB200_EPI_AXPY: return kernel_for<BN, TB200_EPI_AXPY, OUT, PAIR>(dev, fn);
         default: break;
     }
     // activations and their pullbacks are instantiated for BFloat16 results only
     if constexpr (OUT == OUT_BF16) {
         switch (epilogue) {
-            case TB200_EPI_BIAS_GELU: return kernel_for<BN, TB200_EPI_BIAS_GELU, OUT>(dev, fn);
-            case TB200_EPI_BIAS_TANH: return kernel_for<BN, TB200_EPI_BIAS_TANH, OUT>(dev, fn);
-            case TB200_EPI_MUL_GELU_GRAD: return kernel_for<BN, TB200_EPI_MUL_GELU_GRAD, OUT>(dev, fn);
-            case TB200_EPI_MUL_TANH_GRAD: return kernel_for<BN, TB200_EPI_MUL_TANH_GRAD, OUT>(dev, fn);
+            case TB200_EPI_BIAS_GELU: return kernel_for<BN, TB200_EPI_BIAS_GELU, OUT, PAIR>(dev, fn);
+            case TB200_EPI_BIAS_TANH: return kernel_for<BN, TB200_EPI_BIAS_TANH, OUT, PAIR>(dev, fn);
+            case TB200_EPI_MUL_GELU_GRAD: return kernel_for<BN, TB200_EPI_MUL_GELU_GRAD, OUT, PAIR>(dev, fn);
+            case TB200_EPI_MUL_TANH_GRAD: return kernel_for<BN, TB200_EPI_MUL_TANH_GRAD, OUT, PAIR>(dev, fn);
             default: break;
         }
     }
     return TB200_ERR_UNSUPPORTED;
 }
 
-int kernel_by_shape(int bn, int out_dtype, int epilogue, const DeviceInfo &dev, const void **fn) {
+int kernel_by_shape(int bn, bool pair, int out_dtype, int epilogue, const DeviceInfo &dev, const void **fn) {
+    if (pair) {
+        if (out_dtype == TB200_F32) return kernel_by_epilogue<256, OUT_F32, true>(epilogue, dev, fn);
+        if (out_dtype == TB200_F16) return kernel_by_epilogue<256, OUT_F16, true>(epilogue, dev, fn);
+        return kernel_by_epilogue<256, OUT_BF16, true>(epilogue, dev, fn);
+    }
     if (bn == 256) {
         if (out_dtype == TB200_F32) return kernel_by_epilogue<256, OUT_F32>(epilogue, dev, fn);
         if (out_dtype == TB200_F16) return kernel_by_epilogue<256, OUT_F16>(epilogue, dev, fn);
@@ -934,6 +1001,7 @@ int tile_width(const tb200_gemm_desc &d, int sms) {
     // less than half the device (a replica's slice of a batch against a narrow layer): the narrow ones then
     // put twice the SMs to work in the same single wave
     if (d.tile_n == 256 || d.tile_n == 128) return d.tile_n;
+    if (d.tile_n == 512) return 256;   // 256 x 256 tiles, one per pair of CTAs
     if (d.n <= 128) return 128;
     const int64_t batch = d.batch > 1 ? d.batch : 1;
     const int64_t wide = ceil_div(d.m, BM) * ceil_div(d.n, 256) * batch;
@@ -968,6 +1036,7 @@ struct tb200_gemm_plan {
     unsigned merge_grid;
     SimtArgs simt;
     dim3 simt_grid;
+    bool pair;           // launched as clusters of two CTAs sharing 256 x 256 tiles
     int *counters;       // device memory of a created plan (two ints, zero between launches), else null
 };
 
@@ -1033,8 +1102,14 @@ int prepare(tb200_gemm_plan *plan) {
         GemmArgs &p = plan->args;
         p = GemmArgs{};
         const int bn = tile_width(*d, dev.sms);
+        // pairs of CTAs on 256 x 256 tiles where there is at least one such tile per pair of SMs: a third less
+        // operand traffic per SM, which is what this kernel is short of
+        const int64_t pair_items = ceil_div(d->m, 2 * BM) * ceil_div(d->n, 256) * batch;
+        const bool pair = d->n > 128 && d->m > BM &&
+                          (d->tile_n == 512 || (d->tile_n == 0 && bn == 256 && d->split_k <= 1 && 2 * pair_items >= dev.sms));
+        plan->pair = pair;
         int splits = 1, kb_per = static_cast<int>(ceil_div(d->k, BK));
-        choose_split(*d, bn, dev.sms, &splits, &kb_per);
+        if (!pair) choose_split(*d, bn, dev.sms, &splits, &kb_per);
         if (splits > 1 && (!d->workspace || !aligned_to(d->workspace, 16) ||
                            d->workspace_bytes < split_workspace_bytes(*d, splits))) {
             splits = 1;
@@ -1047,14 +1122,14 @@ int prepare(tb200_gemm_plan *plan) {
         p.batch = batch; p.splits = splits; p.kb_per_split = kb_per;
         p.debug = d->debug;
         p.wait_ns = d->debug ? 20000000ull : 2000000000ull;
-        p.tiles_m = static_cast<int>(ceil_div(d->m, BM));
+        p.tiles_m = static_cast<int>(ceil_div(d->m, pair ? 2 * BM : BM));
         p.tiles_n = static_cast<int>(ceil_div(d->n, bn));
         const int64_t am = p.a_batched ? batch : 1, bm = p.b_batched ? batch : 1;
         if (p.a_mn) st = make_tmap(&p.tmap_a, a, d->m, d->k, d->lda, 64, d->in_dtype, am, d->stride_a);
         else st = make_tmap(&p.tmap_a, a, d->k, d->m, d->lda, BM, d->in_dtype, am, d->stride_a);
         if (st) return st;
         if (p.b_mn) st = make_tmap(&p.tmap_b, b, d->n, d->k, d->ldb, 64, d->in_dtype, bm, d->stride_b);
-        else st = make_tmap(&p.tmap_b, b, d->k, d->n, d->ldb, bn, d->in_dtype, bm, d->stride_b);
+        else st = make_tmap(&p.tmap_b, b, d->k, d->n, d->ldb, pair ? bn / 2 : bn, d->in_dtype, bm, d->stride_b);
         if (st) return st;
         int kernel_epilogue = d->epilogue, kernel_out = d->out_dtype;
         if (splits > 1) {
@@ -1102,8 +1177,8 @@ int prepare(tb200_gemm_plan *plan) {
             }
             p.tma_epilogue = tma_epi;
         }
-        if ((st = kernel_by_shape(bn, kernel_out, kernel_epilogue, dev, &plan->kernel))) return st;
-        const size_t stage_bytes = static_cast<size_t>(BM + bn) * BK * 2;
+        if ((st = kernel_by_shape(bn, pair, kernel_out, kernel_epilogue, dev, &plan->kernel))) return st;
+        const size_t stage_bytes = static_cast<size_t>(BM + (pair ? bn / 2 : bn)) * BK * 2;
         const size_t epilogue_bytes = kEpilogueWarps * kEpilogueStage;
         int stages = static_cast<int>((dev.smem_optin - 2048 - epilogue_bytes) / stage_bytes);
         if (stages > 8) stages = 8;
@@ -1115,6 +1190,11 @@ int prepare(tb200_gemm_plan *plan) {
         plan->grid = static_cast<unsigned>(items < dev.sms ? items : dev.sms);
         // more items than blocks: a created plan lets its blocks draw them from a counter
         p.schedule = (plan->counters && items > plan->grid) ? plan->counters : nullptr;
+        if (pair) {   // two CTAs per item; the pairs walk their items in a fixed order
+            const long long pairs = items < dev.sms / 2 ? items : dev.sms / 2;
+            plan->grid = static_cast<unsigned>(2 * pairs);
+            p.schedule = nullptr;
+        }
         return TB200_OK;
     }
 
@@ -1144,7 +1224,21 @@ int run(const tb200_gemm_plan *plan, cudaStream_t stream) {
         return TB200_OK;
     }
     void *params[1] = {const_cast<GemmArgs *>(&plan->args)};
-    TB200_CUDA(cudaLaunchKernel(plan->kernel, dim3(plan->grid), dim3(kGemmThreads), params, plan->smem, stream));
+    if (plan->pair) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(plan->grid);
+        config.blockDim = dim3(kGemmThreads);
+        config.dynamicSmemBytes = plan->smem;
+        config.stream = stream;
+        cudaLaunchAttribute cluster = {};
+        cluster.id = cudaLaunchAttributeClusterDimension;
+        cluster.val.clusterDim.x = 2; cluster.val.clusterDim.y = 1; cluster.val.clusterDim.z = 1;
+        config.attrs = &cluster;
+        config.numAttrs = 1;
+        TB200_CUDA(cudaLaunchKernelExC(&config, plan->kernel, params));
+    } else {
+        TB200_CUDA(cudaLaunchKernel(plan->kernel, dim3(plan->grid), dim3(kGemmThreads), params, plan->smem, stream));
+    }
     if (plan->merge) {
         gemm_splitk_merge<<<plan->merge_grid, 256, 0, stream>>>(plan->merge_args);
         TB200_CUDA(cudaGetLastError());
@@ -1156,6 +1250,7 @@ void fill(tb200_gemm_plan *plan, const tb200_gemm_desc *d, const void *a, const 
           const void *aux, void *aux_out) {
     plan->desc = *d;
     plan->counters = nullptr;
+    plan->pair = false;
     plan->a = a; plan->b = b; plan->c = c; plan->bias = bias; plan->aux = aux; plan->aux_out = aux_out;
 }
 
@@ -1266,7 +1361,7 @@ int time_variant(const tb200_gemm_desc &trial, const void *a, const void *b, voi
 }  // namespace
 
 // Times the compiled-in tile variants of one product on its own operands and returns the faster one's
-// tile_n (128 or 256) -- the measured stage of the reference's search over a claim's `variants`
+// tile_n (128, 256, or 512 for 256 x 256 tiles by pairs of CTAs) -- the measured stage of the reference's search over a claim's `variants`
 // (src/Compiler/Implement/Implement.jl:120, ext/cuTileExt/contract.jl:171-235), restricted to what this
 // library holds.  Runs the product several times (C and aux_out are overwritten with the product's own
 // result), synchronises the stream: a build-time call, not one for a capture.  Where there is nothing to
@@ -1290,7 +1385,8 @@ extern "C" int tb200_gemm_tune(const tb200_gemm_desc *d, const void *a, const vo
     TB200_CUDA(cudaEventCreate(&t1));
     float best_ms = 0.0f;
     int best = fallback, status = TB200_OK;
-    for (int width : {128, 256}) {
+    for (int width : {128, 256, 512}) {
+        if (width == 512 && d->m <= BM) continue;
         trial.tile_n = width;
         float ms = 0.0f;
         if ((status = time_variant(trial, a, b, c, bias, aux, aux_out, stream, t0, t1, 3, &ms))) break;
@@ -1318,9 +1414,11 @@ extern "C" int tb200_gemm_tune_desc(tb200_gemm_desc *d, const void *a, const voi
     TB200_CUDA(cudaEventCreate(&t1));
     float best_ms = -1.0f;
     tb200_gemm_desc best = trial;
-    for (int width : {128, 256}) {
-        if (width == 256 && d->n <= 128) continue;
+    for (int width : {128, 256, 512}) {
+        if (width >= 256 && d->n <= 128) continue;
+        if (width == 512 && d->m <= BM) continue;
         for (int split : {1, 0}) {
+            if (width == 512 && split == 0) continue;   // pairs do not split the sum
             trial.tile_n = width; trial.split_k = split;
             if (split == 0 && tb200_gemm_workspace_bytes(&trial) == 0) continue;           // would not split
             if (split == 0 && (!d->workspace || d->workspace_bytes < tb200_gemm_workspace_bytes(&trial))) continue;

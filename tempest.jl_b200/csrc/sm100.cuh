@@ -200,6 +200,56 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ------------------------------------------------------- pairs of CTAs ----
+// A cluster of two CTAs on neighbouring SMs can run one tcgen05.mma of 256 rows: each CTA holds its 128 rows of A and
+// half of B's columns in its own shared memory and its 128 rows of the accumulator in its own tensor memory; the
+// instruction is issued by one thread of the first CTA and reads both halves.  Loads are plain per-CTA TMA loads.
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// every thread of every CTA of the cluster
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// One tile, global -> this CTA's shared memory, completion counted on a barrier that may belong to the other CTA of
+// the pair (`cluster_bar`: its address in the cluster's shared window).  Not a multicast: one destination.
+__device__ __forceinline__ void tma_load_3d_pair(void *dst, const CUtensorMap *m, uint32_t cluster_bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+// the address, in the cluster's shared window, of this CTA's `p` as CTA `rank` of the cluster holds it
+__device__ __forceinline__ uint32_t cluster_map(const void *p, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(p)), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// D[tensor memory of both CTAs] (+)= A * B over the pair: 256 rows, issued by one thread of the first CTA.
+__device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                     uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the barrier at `bar`'s place in both CTAs when every pair MMA this thread issued has completed.
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t *bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(both)
+                 : "memory");
+}
+
 // ---------------------------------------------------------- descriptors ----
 
 // Shared-memory matrix descriptor of a 128-byte-swizzled operand tile.

@@ -36,15 +36,15 @@ def test_batched_products(pkg, cuda, oracle, batch, M, N, K, a_mn, b_mn):
     want = np.stack([oracle.gemm(A[i], B[i], M=M, N=N, K=K, a_km=a_mn, b_kn=b_mn, want_pre=True)[1]
                      for i in range(batch)])
     Ad, Bd = dev(torch, A), dev(torch, B)
-    for force_simt, direct in ((False, False), (False, True), (True, False)):
+    for force_simt, direct, tile_n in ((False, False, 0), (False, True, 0), (True, False, 0), (False, False, 512)):
         C = torch.full((batch, M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
         L.gemm(Ad.data_ptr(), Bd.data_ptr(), C.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn),
-               batch=batch, force_simt=force_simt, direct_epilogue=direct)
+               batch=batch, force_simt=force_simt, direct_epilogue=direct, tile_n=tile_n)
         assert L.device_error() == 0
         close_bf16(oracle, host(torch, C), want, K)
         C32 = torch.full((batch, M, N), float("nan"), device="cuda")
         L.gemm(Ad.data_ptr(), Bd.data_ptr(), C32.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn),
-               batch=batch, out_dtype=L.F32, force_simt=force_simt, direct_epilogue=direct)
+               batch=batch, out_dtype=L.F32, force_simt=force_simt, direct_epilogue=direct, tile_n=tile_n)
         assert L.device_error() == 0
         agree(C32.cpu().numpy(), want, 1e-5)
 
@@ -250,6 +250,10 @@ def test_a_bounded_wait_runs_out_and_the_device_stays_usable(pkg, cuda):
     torch.cuda.synchronize()                                              # and the kernel ends by itself
     code = L.device_error()
     assert code in (3, 4), code                # the MMA thread's or the epilogue's wait for operands gave up
+    # the same with pairs of CTAs on a tile: both CTAs' waits run out, both reach the pair's closing barrier
+    L.gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, debug=1, tile_n=512)
+    torch.cuda.synchronize()
+    assert L.device_error() in (3, 4)
     # a plan with more tiles than SMs draws them from a counter: same ending, and the counters are left ready
     big = 2048
     A2 = torch.randn(big, K, device="cuda").bfloat16()

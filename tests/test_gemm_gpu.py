@@ -49,7 +49,7 @@ def test_bf16_tensor_core_product(pkg, cuda, oracle, M, N, K, a_mn, b_mn):
     A, B = operands(oracle, M, N, K, a_mn, b_mn, 1000 + M + K, True)
     want = oracle.gemm(A, B, M=M, N=N, K=K, a_km=a_mn, b_kn=b_mn, want_pre=True)[1]
     Ad, Bd = dev(cuda, A), dev(cuda, B)
-    for tile_n, direct in ((128, False), (256, False), (256, True)):
+    for tile_n, direct in ((128, False), (256, False), (256, True), (512, False), (512, True)):
         C = cuda.full((M, N), float("nan"), device="cuda", dtype=cuda.bfloat16)
         L.gemm(Ad.data_ptr(), Bd.data_ptr(), C.data_ptr(), M, N, K, a_layout=int(a_mn), b_layout=int(b_mn),
                tile_n=tile_n, direct_epilogue=direct, stream=cuda.cuda.current_stream().cuda_stream)
@@ -82,17 +82,20 @@ def test_generic_kernel_float32(pkg, cuda, oracle, a_mn, b_mn):
     close_bf16(oracle, host(cuda, C), oracle.gemm(A, B, M=M, N=N, K=K, a_km=a_mn, b_kn=b_mn, want_pre=True)[1], K)
 
 
-@pytest.mark.parametrize("force_simt,direct", [(False, False), (False, True), (True, False)])
-def test_epilogues(pkg, cuda, oracle, force_simt, direct):
+@pytest.mark.parametrize("force_simt,direct,tile_n", [(False, False, 0), (False, True, 0), (True, False, 0),
+                                                      (False, False, 512), (False, True, 512)])
+def test_epilogues(pkg, cuda, oracle, force_simt, direct, tile_n):
+    """tile_n 512: the same epilogues behind tiles of 256 x 256 computed by pairs of CTAs (300 rows: one whole pair
+    tile and a ragged one)."""
     L = pkg.lib
-    M, N, K = 200, 136, 96
+    M, N, K = (300, 264, 96) if tile_n else (200, 136, 96)
     A, B = operands(oracle, M, N, K, False, True, 21, True)
     A = oracle.to_bf16(oracle.from_bf16(A) * 0.1)
     bias = oracle.to_bf16(oracle.normal((N,), 23))
     Ad, Bd, bd = dev(cuda, A), dev(cuda, B), dev(cuda, bias)
     acc = oracle.gemm(A, B, M=M, N=N, K=K, want_pre=True)[1]
     pre = acc + oracle.from_bf16(bias)
-    run = dict(a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR, force_simt=force_simt, direct_epilogue=direct)
+    run = dict(a_layout=L.K_MAJOR, b_layout=L.MN_MAJOR, force_simt=force_simt, direct_epilogue=direct, tile_n=tile_n)
 
     def call(**kw):
         C = cuda.empty((M, N), device="cuda", dtype=cuda.bfloat16)
@@ -346,15 +349,15 @@ def test_products_and_attention_through_the_plugin_mirror(pkg, cuda, oracle):
 
 
 def test_tune_returns_a_variant_and_leaves_the_product(pkg, cuda, oracle):
-    """tb200_gemm_tune times the 128- and 256-wide tiles on the operands, returns one of them, and C holds the
-    product; where there is nothing to choose it answers without measuring."""
+    """tb200_gemm_tune times the 128- and 256-wide tiles and the 256 x 256 tiles of CTA pairs (512) on the operands,
+    returns one of them, and C holds the product; where there is nothing to choose it answers without measuring."""
     torch, L = cuda, pkg.lib
     M, N, K = 512, 1024, 256
     A = torch.randn(M, K, device="cuda").bfloat16()
     B = torch.randn(K, N, device="cuda").bfloat16()
     C = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
     width = L.gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, tune=True)
-    assert width in (128, 256)
+    assert width in (128, 256, 512)
     want = A.float() @ B.float()
     assert (C.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
     C2 = torch.zeros_like(C)
