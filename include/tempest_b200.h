@@ -187,10 +187,8 @@ typedef struct tb200_gemm_desc {
     int tile_n;                  /* 0 = choose; 128 or 256 = the variant the tuner picked
                                     (the counterpart of TEMPEST_PRODUCT_TILE, ext/cuTileExt/contract.jl:36-49);
                                     512 = tiles of 256 x 256 computed by pairs of CTAs on neighbouring SMs
-                                    (each loads half of either operand's tile; the pairs take their tiles in a
-                                    fixed order, not from a plan's counter); -1 = choose among the single-CTA
-                                    tiles only (for products that run beside another kernel and should draw
-                                    their tiles from the plan's counter) */
+                                    (each loads half of either operand's tile); -1 = choose among the single-CTA
+                                    tiles only */
     int force_simt;              /* 1 = the generic kernel (Float32-exact, any alignment) */
     int direct_epilogue;         /* 1 = each thread stores its own output row instead of staging
                                     tiles through shared memory for TMA stores (a tuner variant) */

@@ -216,13 +216,15 @@ __device__ __forceinline__ uint64_t global_ns() {
     return t;
 }
 
-// Bounded wait: false once `*failed` is set by anyone or `limit_ns` have passed.
+// Bounded wait: false once `*failed` is set by anyone or `limit_ns` have passed.  PEER: a thread of the pair's
+// other CTA arrives, after writing what this thread reads next.
+template <bool PEER = false>
 __device__ __forceinline__ bool wait_or_fail(uint64_t *bar, uint32_t parity, volatile int *failed, int code,
                                              unsigned long long limit_ns) {
-    if (mbar_wait(bar, parity, 4096)) return true;
+    if (PEER ? mbar_wait_cluster(bar, parity, 4096) : mbar_wait(bar, parity, 4096)) return true;
     const uint64_t t0 = global_ns();
     while (true) {
-        if (mbar_wait(bar, parity, 1024)) return true;
+        if (PEER ? mbar_wait_cluster(bar, parity, 1024) : mbar_wait(bar, parity, 1024)) return true;
         if (*failed) return false;
         if (global_ns() - t0 > limit_ns) {
             *failed = code;
@@ -455,6 +457,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     __shared__ __align__(8) uint64_t item_full[kItemSlots];
     __shared__ __align__(8) uint64_t item_empty[kItemSlots];
     __shared__ int item_slot[kItemSlots];
+    // pair with a tile counter: the first CTA's loading thread draws the items and writes them into the second's ring
+    __shared__ __align__(8) uint64_t mail_full[kItemSlots];    // used in the second CTA: an item has arrived
+    __shared__ __align__(8) uint64_t mail_empty[kItemSlots];   // used in the first CTA: the second has read it
+    __shared__ int mail_item[kItemSlots];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int failed_smem;
     volatile int *failed = &failed_smem;
@@ -479,6 +485,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
         }
         for (int s = 0; s < kEpilogueWarps; s++) mbar_init(&aux_bar[s], 1);
         for (int s = 0; s < kItemSlots; s++) {
+            mbar_init(&mail_full[s], 1);
+            mbar_init(&mail_empty[s], 1);
             mbar_init(&item_full[s], 1);
             mbar_init(&item_empty[s], 1 + kEpilogueWarps);   // the MMA thread and one lane of each epilogue warp
         }
@@ -508,16 +516,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             // a pair takes its tiles by the cluster's index: both CTAs walk the same list
             const int first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
             const int step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-            int item = (!PAIR && p.schedule) ? atomicAdd(p.schedule, 1) : first;
+            const bool drawn = p.schedule != nullptr;          // items come from the plan's counter
+            const bool draws = drawn && rank == 0;             // ... which this thread reads
+            const bool told = PAIR && drawn && rank != 0;      // ... or the first CTA's loading thread tells it
+            int item = draws ? atomicAdd(p.schedule, 1) : first;
+            int mslot = 0;
+            uint32_t mphase = 0;
             while (true) {
                 if (!wait_or_fail(&item_empty[slot], slot_phase ^ 1, failed, 6, wait_ns)) break;
-                const bool live = item < num_items && !*failed;
+                if (told) {
+                    if (!wait_or_fail<true>(&mail_full[mslot], mphase, failed, 10, wait_ns)) break;
+                    item = mail_item[mslot];
+                    mbar_arrive_cluster(cluster_map(&mail_empty[mslot], 0));
+                    if (++mslot == kItemSlots) { mslot = 0; mphase ^= 1; }
+                }
+                const bool live = item >= 0 && item < num_items && !*failed;
+                if (PAIR && draws) {
+                    if (!wait_or_fail(&mail_empty[mslot], mphase ^ 1, failed, 11, wait_ns)) break;
+                    st_cluster_u32(cluster_map(&mail_item[mslot], 1), static_cast<uint32_t>(live ? item : -1));
+                    mbar_arrive_cluster(cluster_map(&mail_full[mslot], 1));
+                    if (++mslot == kItemSlots) { mslot = 0; mphase ^= 1; }
+                }
                 item_slot[slot] = live ? item : -1;
                 mbar_arrive(&item_full[slot]);
                 if (++slot == kItemSlots) { slot = 0; slot_phase ^= 1; }
                 if (!live) break;
                 // the next item is drawn now, so that the answer is there when this one's loads are out
-                const int next = (!PAIR && p.schedule) ? atomicAdd(p.schedule, 1) : item + step;
+                const int next = draws ? atomicAdd(p.schedule, 1) : item + step;
                 const WorkItem w = work_item(p, item, num_kb);
                 item = next;
                 if (withhold) continue;
@@ -752,7 +777,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
         tmem_dealloc(tmem_base, kAccumStages * BN);
     }
     // the last block out leaves the two counters as it found them, for the next launch
-    if (!PAIR && p.schedule && threadIdx.x == 0) {
+    if (p.schedule && threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(p.schedule + 1, 1) == static_cast<int>(gridDim.x) - 1) {
             p.schedule[0] = 0;
@@ -1190,10 +1215,10 @@ int prepare(tb200_gemm_plan *plan) {
         plan->grid = static_cast<unsigned>(items < dev.sms ? items : dev.sms);
         // more items than blocks: a created plan lets its blocks draw them from a counter
         p.schedule = (plan->counters && items > plan->grid) ? plan->counters : nullptr;
-        if (pair) {   // two CTAs per item; the pairs walk their items in a fixed order
+        if (pair) {   // two CTAs per item
             const long long pairs = items < dev.sms / 2 ? items : dev.sms / 2;
             plan->grid = static_cast<unsigned>(2 * pairs);
-            p.schedule = nullptr;
+            p.schedule = (plan->counters && items > pairs) ? plan->counters : nullptr;
         }
         return TB200_OK;
     }

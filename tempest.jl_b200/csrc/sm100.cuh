@@ -232,6 +232,23 @@ __device__ __forceinline__ uint32_t cluster_map(const void *p, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// mbar_wait for a barrier on which a thread of the other CTA arrives after writing this CTA's shared memory
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// one word into the other CTA's shared memory
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t value) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(value) : "memory");
+}
 // D[tensor memory of both CTAs] (+)= A * B over the pair: 256 rows, issued by one thread of the first CTA.
 __device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                      uint32_t accumulate) {

@@ -199,12 +199,6 @@ class MLPStep:
         self._scratch = []
 
         def plan(desc, *operands, **more):
-            # beside an exchange kernel the blocks draw their tiles from the plan's counter, so that the SMs the
-            # exchange holds cost a few tiles and not a wait; pairs of CTAs take tiles in a fixed order, so the
-            # replicas' products stay on single-CTA tiles and one GPU alone lets the library choose (pairs, where
-            # a product has enough tiles for them)
-            if self.world > 1:
-                desc.tile_n = -1
             # a product with too few tiles to fill the device (a replica's slice of the batch against a narrow
             # layer) splits its sum over k when it is given scratch for the partial tiles
             need = lib.gemm_workspace_bytes(desc)

@@ -234,6 +234,39 @@ def test_prepared_launch_and_repoint(pkg, cuda, oracle):
         L.GemmPlan(L.gemm_desc(8, 8, 8), 0, B.data_ptr(), C.data_ptr())
 
 
+def test_a_plan_on_pairs_of_ctas_draws_its_tiles_from_the_counter(pkg, cuda):
+    """More 256 x 256 tiles than pairs of SMs: the first CTA of a pair draws the tile and passes it to the second;
+    launched several times (the counter is left ready), with an epilogue, and after a launch whose loads were
+    withheld (every wait runs out, both CTAs of every pair leave together)."""
+    torch, L = cuda, pkg.lib
+    M, N, K = 4096, 4352, 192
+    A = (0.1 * torch.randn(M, K, device="cuda")).bfloat16()
+    B = torch.randn(K, N, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    C = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    want = A.float() @ B.float() + bias.float()
+    plan = L.GemmPlan(L.gemm_desc(M, N, K, epilogue=L.EPI_BIAS, tile_n=512), A.data_ptr(), B.data_ptr(), C.data_ptr(),
+                      bias=bias.data_ptr())
+    for _ in range(3):
+        C.zero_()
+        plan.launch()
+        assert (C.float() - want).abs().max().item() <= ATOL_BF16 * want.abs().max().item()
+    assert L.device_error() == 0
+    plan.close()
+    plan = L.GemmPlan(L.gemm_desc(M, N, K, epilogue=L.EPI_BIAS, tile_n=512, debug=1), A.data_ptr(), B.data_ptr(),
+                      C.data_ptr(), bias=bias.data_ptr())
+    plan.launch()
+    assert L.device_error() in (3, 4)
+    plan.close()
+    plan = L.GemmPlan(L.gemm_desc(M, N, K, epilogue=L.EPI_BIAS), A.data_ptr(), B.data_ptr(), C.data_ptr(),
+                      bias=bias.data_ptr())       # the library's own choice: pairs here
+    C.zero_()
+    plan.launch()
+    assert (C.float() - want).abs().max().item() <= ATOL_BF16 * want.abs().max().item()
+    assert L.device_error() == 0
+    plan.close()
+
+
 def test_a_bounded_wait_runs_out_and_the_device_stays_usable(pkg, cuda):
     """The failure path of the tensor-core product: with the test hook set the loading thread withholds its
     tiles, so the consumers' waits find nothing; each wait gives up after its (shortened) limit, the kernel
