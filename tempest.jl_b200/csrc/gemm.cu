@@ -505,6 +505,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
     else __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_smem;
+    // barriers, tensor memory and descriptors are ready; global memory is touched from here on
+    grid_dependency_wait();
 
     if (warp == 0) {
         // ---- TMA producer; it also draws the block's work items and passes them on (with the test hook set it
@@ -1249,21 +1251,20 @@ int run(const tb200_gemm_plan *plan, cudaStream_t stream) {
         return TB200_OK;
     }
     void *params[1] = {const_cast<GemmArgs *>(&plan->args)};
-    if (plan->pair) {
-        cudaLaunchConfig_t config = {};
-        config.gridDim = dim3(plan->grid);
-        config.blockDim = dim3(kGemmThreads);
-        config.dynamicSmemBytes = plan->smem;
-        config.stream = stream;
-        cudaLaunchAttribute cluster = {};
-        cluster.id = cudaLaunchAttributeClusterDimension;
-        cluster.val.clusterDim.x = 2; cluster.val.clusterDim.y = 1; cluster.val.clusterDim.z = 1;
-        config.attrs = &cluster;
-        config.numAttrs = 1;
-        TB200_CUDA(cudaLaunchKernelExC(&config, plan->kernel, params));
-    } else {
-        TB200_CUDA(cudaLaunchKernel(plan->kernel, dim3(plan->grid), dim3(kGemmThreads), params, plan->smem, stream));
-    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(plan->grid);
+    config.blockDim = dim3(kGemmThreads);
+    config.dynamicSmemBytes = plan->smem;
+    config.stream = stream;
+    cudaLaunchAttribute attrs[2] = {};
+    // the kernel's prologue may run under the tail of the kernel before it (it waits before touching global memory)
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    attrs[1].id = cudaLaunchAttributeClusterDimension;
+    attrs[1].val.clusterDim.x = 2; attrs[1].val.clusterDim.y = 1; attrs[1].val.clusterDim.z = 1;
+    config.attrs = attrs;
+    config.numAttrs = plan->pair ? 2 : 1;
+    TB200_CUDA(cudaLaunchKernelExC(&config, plan->kernel, params));
     if (plan->merge) {
         gemm_splitk_merge<<<plan->merge_grid, 256, 0, stream>>>(plan->merge_args);
         TB200_CUDA(cudaGetLastError());

@@ -24,6 +24,11 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// A kernel launched with programmatic stream serialization may start while the kernel before it in the stream is
+// still finishing: everything up to this call overlaps that kernel's tail, nothing after it does (the call returns
+// when the earlier kernel has completed and its writes are visible).  A no-op in an ordinary launch.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ------------------------------------------------------------- mbarrier ----
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
