@@ -12,6 +12,7 @@ The directory name contains a dot, so it is loaded by path (see
 from . import lib  # noqa: F401
 from .lib import TB200Error, load, F32, BF16  # noqa: F401
 from . import groups  # noqa: F401
+from . import tuning  # noqa: F401
 from . import implement  # noqa: F401
 from . import mlp  # noqa: F401,E402
 from . import dp  # noqa: F401,E402

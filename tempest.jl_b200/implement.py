@@ -242,11 +242,30 @@ def _dense(s: "Strided") -> bool:
 
 
 class LinearLaunch:
-    """One product with its fused epilogue on fixed operands (tb200_gemm)."""
+    """One product with its fused epilogue on fixed operands (tb200_gemm).  `pick`: the variant a tuning run chose
+    (tile_n, split_k, direct_epilogue of the descriptor); none: the library's own choice."""
 
-    def __init__(self, binding: Binding):
+    def __init__(self, binding: Binding, pick=None):
         self.binding = binding
         self.epilogue = LINEAR_SPELLINGS[binding.template][1]
+        self.pick = dict(pick or {})
+
+    def _options(self):
+        a, e = self.binding.arrays, self.binding.extents
+        w, x, y = a["w"], a["x"], a["y"]
+        return dict(lda=x.strides[1], ldb=w.strides[1], ldc=y.strides[1], a_layout=lib.K_MAJOR, b_layout=lib.MN_MAJOR,
+                    in_dtype=ELTYPES[w.eltype][0], epilogue=self.epilogue)
+
+    def tune(self):
+        """Times the compiled-in variants on the launch's own operands (y is overwritten with the product's result)
+        and keeps the fastest; returns the pick."""
+        a, e = self.binding.arrays, self.binding.extents
+        d = lib.gemm_desc(e["n"], e["m"], e["k"], **self._options())
+        lib.gemm_tune_desc(d, a["x"].pointer(), a["w"].pointer(), a["y"].pointer(),
+                           bias=a["b"].pointer() if "b" in a else 0, stream=current_stream())
+        # a split needs scratch the launch does not bring: the pick keeps the unsplit form
+        self.pick = {"tile_n": d.tile_n, "direct_epilogue": d.direct_epilogue}
+        return dict(self.pick)
 
     def repoints(self) -> bool:
         return True
@@ -266,11 +285,9 @@ class LinearLaunch:
     def __call__(self):
         a, e = self.binding.arrays, self.binding.extents
         w, x, y = a["w"], a["x"], a["y"]
-        dtype = ELTYPES[w.eltype][0]
         # memory: x [n][k] is the K-major A, w [k][m] the MN-major B, y [n][m] the result
-        lib.gemm(x.pointer(), w.pointer(), y.pointer(), e["n"], e["m"], e["k"], lda=x.strides[1], ldb=w.strides[1],
-                 ldc=y.strides[1], a_layout=lib.K_MAJOR, b_layout=lib.MN_MAJOR, in_dtype=dtype,
-                 epilogue=self.epilogue, bias=a["b"].pointer() if "b" in a else 0, stream=current_stream())
+        lib.gemm(x.pointer(), w.pointer(), y.pointer(), e["n"], e["m"], e["k"], **self._options(), **self.pick,
+                 bias=a["b"].pointer() if "b" in a else 0, stream=current_stream())
 
 
 class ProductsLaunch:
@@ -451,8 +468,12 @@ class B200Kernels:
     """The library (`<: Library`): which templates it computes, whether it takes
     a binding, what a launch costs, and the launch itself."""
 
-    def __init__(self, eps: float = 1.0e-5):
+    def __init__(self, eps: float = 1.0e-5, record=None):
+        """`record`: a `tuning.TuningRecord`; with one, `build` measures a product's variants (and an attention
+        pullback's two forms) the first time it meets a shape, keeps the pick in the record's file, and reads it back
+        in later sessions instead of measuring again."""
         self.eps = eps
+        self.record = record
 
     def templates(self, target: Target):
         # the row kernels and attention fold each statistic in one pass, which a target that
@@ -557,7 +578,18 @@ class B200Kernels:
                 raise ValueError("build needs every array's buffer")
         if b.template in LINEAR_SPELLINGS:
             e = b.extents
-            return LinearLaunch(b), f"B200 {b.template}, {e['m']} x {e['n']} over {e['k']}, {b.arrays['w'].eltype}"
+            launch, how = LinearLaunch(b), ""
+            if self.record is not None:
+                key = self.record.key(b.template, e["m"], e["n"], e["k"], b.arrays["w"].eltype)
+                pick = self.record.lookup("product", key)
+                if pick is None:
+                    pick = self.record.keep("product", key, launch.tune())
+                    how = ", variants measured"
+                else:
+                    how = ", variant from the tuning record"
+                launch.pick = pick
+                how += f" (tile_n {pick.get('tile_n', 0)})"
+            return launch, f"B200 {b.template}, {e['m']} x {e['n']} over {e['k']}, {b.arrays['w'].eltype}{how}"
         if _scan_parts(b.template) is not None:
             e = b.extents
             return ScanLaunch(b, resources), f"B200 {b.template}, {e['rows']} rows of {e['n']} {b.arrays['x'].eltype}"
@@ -571,14 +603,22 @@ class B200Kernels:
                 need = lib.attention_bwd_workspace_bytes(launch.desc)
                 resources = resources if resources is not None else Resources()
                 launch.workspace, launch.workspace_bytes = resources.workspace(need), need
+                e = b.extents
+                key = None if self.record is None else self.record.key(
+                    b.template, e["d"], e["h"], e["hk"], e["m"], e["n"], e["b"], int(bool(launch.desc.causal)))
+                kept = self.record.lookup("attention_pullback", key) if key else None
                 if target.deterministic:
                     launch.desc.deterministic = 1
+                elif kept is not None:
+                    launch.desc.deterministic = kept["deterministic"]
                 else:
                     a = b.arrays
                     launch.desc.deterministic = lib.attention_bwd_tune(
                         launch.desc, a["q"].pointer(), a["k"].pointer(), a["v"].pointer(), a["o"].pointer(),
                         a["lse"].pointer(), a["g"].pointer(), a["dq"].pointer(), a["dk"].pointer(), a["dv"].pointer(),
                         launch.workspace.data_ptr(), need, current_stream())
+                    if key:
+                        self.record.keep("attention_pullback", key, {"deterministic": launch.desc.deterministic})
                 form = ", two kernels (deterministic)" if launch.desc.deterministic else ", one kernel (dq by atomic adds)"
             e = b.extents
             return launch, (f"B200 {b.template}, {e['h']} heads over {e['hk']} of {e['d']} features, "

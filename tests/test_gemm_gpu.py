@@ -348,6 +348,35 @@ def test_products_and_attention_through_the_plugin_mirror(pkg, cuda, oracle):
         assert np.abs(gotf - want).max() <= ATOL_BF16 * max(1.0, np.abs(want).max())
 
 
+def test_builds_keep_their_measured_picks_in_the_tuning_record(pkg, cuda, oracle, tmp_path, monkeypatch):
+    """With a tuning record the mirror's `build` measures a product's variants once, keeps the pick in the record's
+    file, and a later session (a new record on the same file) builds the same launch without measuring."""
+    torch, I, T = cuda, pkg.implement, pkg.tuning
+    m, k, n = 512, 256, 1024
+    w = (0.1 * torch.randn(k, m, device="cuda")).bfloat16()
+    x = torch.randn(n, k, device="cuda").bfloat16()
+    y = torch.empty(n, m, device="cuda", dtype=torch.bfloat16)
+    bind = I.Binding("linear", {"m": m, "k": k, "n": n},
+                     {"w": I.dense_matrix(w, "BFloat16", m, k, 1), "x": I.dense_matrix(x, "BFloat16", k, n, 2),
+                      "y": I.dense_matrix(y, "BFloat16", m, n, 4)})
+    record = T.TuningRecord(torch.cuda.get_device_name(0), str(tmp_path))
+    launch, note = I.B200Kernels(record=record).build(I.Target(), bind)
+    assert "variants measured" in note and launch.pick["tile_n"] in (128, 256, 512) and record.written == 1
+    y.zero_()
+    launch()
+    torch.cuda.synchronize()
+    want = x.float() @ w.float()
+    assert (y.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    later = T.TuningRecord(torch.cuda.get_device_name(0), str(tmp_path))
+    monkeypatch.setattr(pkg.lib, "gemm_tune_desc", lambda *a, **k: (_ for _ in ()).throw(AssertionError("measured again")))
+    launch2, note2 = I.B200Kernels(record=later).build(I.Target(), bind)
+    assert "from the tuning record" in note2 and launch2.pick == launch.pick and later.written == 0
+    y.zero_()
+    launch2()
+    torch.cuda.synchronize()
+    assert (y.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+
+
 def test_tune_returns_a_variant_and_leaves_the_product(pkg, cuda, oracle):
     """tb200_gemm_tune times the 128- and 256-wide tiles and the 256 x 256 tiles of CTA pairs (512) on the operands,
     returns one of them, and C holds the product; where there is nothing to choose it answers without measuring."""

@@ -160,3 +160,34 @@ def test_scan_templates(I):
     assert not lib.supports(t, I.Binding("cumsum_dims3", {"n": n, "rows": rows}, arrays))
     launch = I.ScanLaunch(I.Binding("cummax_dims1_reverse", {"n": n, "rows": rows}, arrays))
     assert (launch.op, launch.across, launch.reverse) == (2, False, True)
+
+
+def test_tuning_record_keeps_and_reads_back(pkg, tmp_path, monkeypatch):
+    """The picks made while building launches, kept between sessions as the reference keeps its tuning record
+    (src/Compiler/cover/record.jl:22-32, 60-80): a tab-separated file per device under TEMPEST_CACHE/tuning,
+    appended to, the later line winning, a line cut short ignored."""
+    T = pkg.tuning
+    assert T.file_name("NVIDIA B200 (sm_100a)") == "NVIDIA_B200__sm_100a_"
+    monkeypatch.delenv("TEMPEST_CACHE", raising=False)
+    assert T.tuning_directory() is None
+    nowhere = T.TuningRecord("NVIDIA B200")
+    assert nowhere.path is None
+    nowhere.keep("product", "k", {"tile_n": 512})
+    assert nowhere.lookup("product", "k") == {"tile_n": 512}      # kept in memory, written nowhere
+    monkeypatch.setenv("TEMPEST_CACHE", str(tmp_path))
+    assert T.tuning_directory() == str(tmp_path / "tuning")
+    r = T.TuningRecord("NVIDIA B200")
+    assert r.path == str(tmp_path / "tuning" / "NVIDIA_B200.b200.tsv") and r.lookup("product", "a") is None
+    key = r.key("linear_bias_gelu", 4096, 8192, 4096, "BFloat16")
+    assert key == "linear_bias_gelu 4096 8192 4096 BFloat16"
+    r.keep("product", key, {"tile_n": 256, "direct_epilogue": 0}, 0.21)
+    r.keep("product", key, {"tile_n": 512, "direct_epilogue": 0}, 0.19)
+    r.keep("attention_pullback", "x", {"deterministic": 1})
+    with open(r.path, "a") as f:
+        f.write("product\tcut short")
+    again = T.TuningRecord("NVIDIA B200")
+    assert again.lookup("product", key) == {"tile_n": 512, "direct_epilogue": 0}
+    assert again.lookup("attention_pullback", "x") == {"deterministic": 1}
+    assert again.lookup("product", "cut short") is None and again.written == 0
+    other = T.TuningRecord("NVIDIA H100")                           # another device: another file
+    assert other.lookup("product", key) is None
