@@ -379,9 +379,12 @@ int tb200_device_errors(void);
  * Strides are in elements over (batch, position, head) with the features
  * contiguous; all zero = the dense [batch][position][head][feature] default.  A
  * key cache laid out (features, positions, key heads, sequences) is
- * kv_stride = {kv_heads * keys * d, d, keys * d}.  These entries run the
- * CUDA-core kernels for every head dimension up to 256 (the tensor-core kernels
- * take the unmasked and the plain causal programs). */
+ * kv_stride = {kv_heads * keys * d, d, keys * d}.  The forward with 128 features
+ * runs on the tensor cores (strides that are multiples of 8 elements, 16-byte
+ * aligned arrays): every query tile finds the key tiles it has to visit from its
+ * queries' starts and the sequence's length, and masks the tiles those fall in
+ * row by row.  Other head dimensions (up to 256), other strides and the pullback
+ * run the CUDA-core kernels. */
 typedef struct tb200_attn_mask {
     const int32_t *doc_start;   /* [batch][queries] or NULL */
     const int32_t *kv_len;      /* [batch] or NULL */

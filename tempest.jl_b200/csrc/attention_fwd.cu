@@ -21,6 +21,11 @@
 //               in tensor memory only when a row's maximum grew by more than 2^8 (the sum absorbs
 //               smaller drifts exactly), and at the end normalises O, stages it in shared memory and
 //               stores it by TMA.
+// The one-tile kernel also takes masks the device holds (the starts of packed documents per query, a length per
+// sequence) and operands at other strides: every role finds the item's key tiles [lo, hi) the same way -- all lanes of
+// its warp read the tile's 128 starts, four a lane, and take their minimum and maximum -- key tiles before the
+// earliest start or beyond the length are never loaded, the tiles a start or the length falls in are masked row by
+// row, and an item that sees no key at all is answered by the softmax warps alone (zero rows, -Inf).
 // No load uses cluster multicast.  Every barrier wait is bounded.
 #include <cuda.h>
 
@@ -57,7 +62,48 @@ struct AttnFwdArgs {
     int q_tiles, items;
     int causal;
     float scale_log2;         // scale * log2(e)
+    // masks the device holds (the one-tile kernel takes them; null: none)
+    const int *doc_start;     // [batch][queries]: with `causal`, query j sees keys doc_start[b][j] <= i <= j
+    const int *kv_len;        // [batch]: keys at and beyond kv_len[b] are masked
+    __nv_bfloat16 *o_rows;    // O again as a plain pointer with its element strides: items that see no key at all
+    long long o_batch, o_pos, o_head;   // write their zeros without the tensor core's help
 };
+
+// The key tiles one query tile visits, [lo, hi), under the causal mask, a length and the starts of packed documents.
+// `dmax`: the largest start among the tile's queries (key tiles that begin before it need the per-row test).
+struct KeyRange { int lo, hi, keys, dmax; };
+
+// Every lane of a warp calls it (the starts of the tile's 128 queries are read four a lane).
+__device__ __forceinline__ KeyRange key_range(const AttnFwdArgs &p, int b, int qt, int lane) {
+    KeyRange r;
+    r.keys = p.keys;
+    if (p.kv_len) {
+        const int n = p.kv_len[b];
+        r.keys = n < 0 ? 0 : (n < p.keys ? n : p.keys);
+    }
+    r.hi = (r.keys + kTile - 1) / kTile;
+    if (p.causal && qt + 1 < r.hi) r.hi = qt + 1;
+    int dmin = 0;
+    r.dmax = 0;
+    if (p.doc_start) {
+        int lo = 0x7fffffff, hi = 0;
+        for (int i = lane; i < kTile; i += 32) {
+            const int qi = qt * kTile + i;
+            if (qi < p.queries) {
+                int s = p.doc_start[static_cast<long long>(b) * p.queries + qi];
+                s = s < 0 ? 0 : s;
+                lo = s < lo ? s : lo;
+                hi = s > hi ? s : hi;
+            }
+        }
+        dmin = __reduce_min_sync(0xffffffffu, lo);
+        r.dmax = __reduce_max_sync(0xffffffffu, hi);
+        if (dmin == 0x7fffffff) dmin = 0;
+    }
+    r.lo = dmin / kTile;
+    if (r.lo > r.hi) r.lo = r.hi;
+    return r;
+}
 
 __device__ __forceinline__ uint64_t now_ns() {
     uint64_t t;
@@ -135,47 +181,55 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
     const int group = p.heads / p.kv_heads;
 
     if (warp == 0) {
-        if (elect_one()) {
-            uint32_t q_phase = 0, kv_count = 0;
-            for (int item = blockIdx.x; item < p.items && !*failed; item += gridDim.x) {
-                int bh, qt;
-                decode_item(p, item, bh, qt);
-                const int b = bh / p.heads, h = bh % p.heads, hk = h / group;
-                if (!wait_bounded(&q_empty, q_phase ^ 1, failed, 1)) break;
-                mbar_arrive_expect_tx(&q_full, kTileBytes);
-                tma_load_4d(sq, &p.q, &q_full, 0, h, qt * kTile, b);
-                tma_load_4d(sq + kSlab, &p.q, &q_full, 64, h, qt * kTile, b);
-                q_phase ^= 1;
-                const int nkv = kv_tiles_of(p, qt);
-                for (int j = 0; j < nkv; j++, kv_count++) {
-                    const int st = kv_count & 1;
-                    const uint32_t ph = (kv_count >> 1) & 1;
-                    if (!wait_bounded(&k_empty[st], ph ^ 1, failed, 2)) break;
-                    mbar_arrive_expect_tx(&k_full[st], kTileBytes);
-                    tma_load_4d(sk + st * kTileBytes, &p.k, &k_full[st], 0, hk, j * kTile, b);
-                    tma_load_4d(sk + st * kTileBytes + kSlab, &p.k, &k_full[st], 64, hk, j * kTile, b);
-                    if (!wait_bounded(&v_empty[st], ph ^ 1, failed, 3)) break;
-                    mbar_arrive_expect_tx(&v_full[st], kTileBytes);
-                    tma_load_4d(sv + st * kTileBytes, &p.v, &v_full[st], 0, hk, j * kTile, b);
-                    tma_load_4d(sv + st * kTileBytes + kSlab, &p.v, &v_full[st], 64, hk, j * kTile, b);
-                }
+        // the whole warp walks the items (the key range of an item is found by all its lanes); lane 0 loads
+        uint32_t q_phase = 0, kv_count = 0;
+        for (int item = blockIdx.x; item < p.items && !*failed; item += gridDim.x) {
+            int bh, qt;
+            decode_item(p, item, bh, qt);
+            const int b = bh / p.heads, h = bh % p.heads, hk = h / group;
+            const KeyRange kr = key_range(p, b, qt, lane);
+            if (kr.lo >= kr.hi) continue;   // no key to see: the softmax warps write the zeros
+            int ok = 1;
+            if (lane == 0) {
+                do {
+                    if (!wait_bounded(&q_empty, q_phase ^ 1, failed, 1)) { ok = 0; break; }
+                    mbar_arrive_expect_tx(&q_full, kTileBytes);
+                    tma_load_4d(sq, &p.q, &q_full, 0, h, qt * kTile, b);
+                    tma_load_4d(sq + kSlab, &p.q, &q_full, 64, h, qt * kTile, b);
+                    for (int j = kr.lo; j < kr.hi; j++, kv_count++) {
+                        const int st = kv_count & 1;
+                        const uint32_t ph = (kv_count >> 1) & 1;
+                        if (!wait_bounded(&k_empty[st], ph ^ 1, failed, 2)) { ok = 0; break; }
+                        mbar_arrive_expect_tx(&k_full[st], kTileBytes);
+                        tma_load_4d(sk + st * kTileBytes, &p.k, &k_full[st], 0, hk, j * kTile, b);
+                        tma_load_4d(sk + st * kTileBytes + kSlab, &p.k, &k_full[st], 64, hk, j * kTile, b);
+                        if (!wait_bounded(&v_empty[st], ph ^ 1, failed, 3)) { ok = 0; break; }
+                        mbar_arrive_expect_tx(&v_full[st], kTileBytes);
+                        tma_load_4d(sv + st * kTileBytes, &p.v, &v_full[st], 0, hk, j * kTile, b);
+                        tma_load_4d(sv + st * kTileBytes + kSlab, &p.v, &v_full[st], 64, hk, j * kTile, b);
+                    }
+                } while (false);
             }
+            q_phase ^= 1;
+            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
         }
     } else if (warp == 1) {
-        if (elect_one()) {
+        {
             // S = Q K^T: both operands K-major (feature axis contiguous), two 64-feature slabs
             const uint32_t idesc_qk = umma_idesc_bf16(kTile, kTile, false, false);
             // O += P V: P K-major (key axis contiguous), V MN-major (feature axis contiguous)
             const uint32_t idesc_pv = umma_idesc_bf16(kTile, kHeadDim, false, true);
             uint32_t q_phase = 0, kv_count = 0, pv_count = 0, item_count = 0;
-            for (int item = blockIdx.x; item < p.items && !*failed; item += gridDim.x, item_count++) {
+            for (int item = blockIdx.x; item < p.items && !*failed; item += gridDim.x) {
                 int bh, qt;
                 decode_item(p, item, bh, qt);
-                const int nkv = kv_tiles_of(p, qt);
-                if (!wait_bounded(&q_full, q_phase, failed, 4)) break;
-                q_phase ^= 1;
-                tcgen05_fence_after();
+                const KeyRange kr = key_range(p, bh / p.heads, qt, lane);
+                const int nkv = kr.hi - kr.lo;
+                if (nkv <= 0) continue;
                 bool ok = true;
+                if (lane == 0) {
+                if (!wait_bounded(&q_full, q_phase, failed, 4)) ok = false;
+                tcgen05_fence_after();
                 for (int j = 0; j <= nkv && ok; j++) {
                     if (j < nkv) {
                         const uint32_t c = kv_count + j;
@@ -219,8 +273,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
                         pv_count++;
                     }
                 }
+                }
+                q_phase ^= 1;
                 kv_count += nkv;
-                if (!ok) break;
+                item_count++;
+                if (!__shfl_sync(0xffffffffu, static_cast<int>(ok), 0)) break;
             }
         }
     } else {
@@ -229,22 +286,34 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
         const int row = q * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
         uint32_t kv_count = 0, item_count = 0, pv_seen = 0;
-        for (int item = blockIdx.x; item < p.items; item += gridDim.x, item_count++) {
+        for (int item = blockIdx.x; item < p.items; item += gridDim.x) {
             int bh, qt;
             decode_item(p, item, bh, qt);
             const int b = bh / p.heads, h = bh % p.heads;
-            const int nkv = kv_tiles_of(p, qt);
+            const KeyRange kr = key_range(p, b, qt, lane);
             const int qi = qt * kTile + row;    // this thread's query
+            if (kr.lo >= kr.hi) {
+                // no key to see for any query of the tile: zero rows, a log-sum-exp of -Inf, no product
+                if (qi < p.queries) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(p.o_rows + b * p.o_batch + qi * p.o_pos + h * p.o_head);
+#pragma unroll
+                    for (int c = 0; c < kHeadDim / 8; c++) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+                    if (p.lse) p.lse[(static_cast<long long>(b) * p.queries + qi) * p.heads + h] = -INFINITY;
+                }
+                continue;
+            }
+            // the first key this query sees (packed documents), 0 without
+            const int first_key = (p.doc_start && qi < p.queries) ? p.doc_start[static_cast<long long>(b) * p.queries + qi] : 0;
             float m_used = -INFINITY, l = 0.0f;
             bool ok = true;
-            for (int j = 0; j < nkv; j++, kv_count++) {
+            for (int j = kr.lo; j < kr.hi; j++, kv_count++) {
                 const int st = kv_count & 1;
                 const uint32_t ph = (kv_count >> 1) & 1;
                 if (!wait_bounded(&s_full[st], ph, failed, 10)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t ts = tmem_base + lane_base + st * kTile;
                 const int key0 = j * kTile;
-                const bool edge = (p.causal && key0 + kTile - 1 > qt * kTile) || key0 + kTile > p.keys;
+                const bool edge = (p.causal && key0 + kTile - 1 > qt * kTile) || key0 + kTile > kr.keys || key0 < kr.dmax;
                 // the whole row of 128 scores into registers: the four loads are in flight together
                 // (one load-then-wait at a time costs about 800 cycles each)
                 uint32_t r[kTile];
@@ -260,7 +329,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
 #pragma unroll
                     for (int i = 0; i < kTile; i++) {
                         const int key = key0 + i;
-                        if ((p.causal && key > qi) || key >= p.keys) r[i] = 0xff800000u;   // -Inf
+                        if ((p.causal && key > qi) || key >= kr.keys || key < first_key) r[i] = 0xff800000u;   // -Inf
                     }
                 }
                 float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -275,7 +344,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
                 bool grew = false;
                 if (m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY)) {
                     alpha = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_tile);
-                    grew = j > 0 && m_used != -INFINITY;
+                    grew = j > kr.lo && m_used != -INFINITY;
                     m_used = m_tile;
                     l *= alpha;
                 }
@@ -302,8 +371,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
                     *reinterpret_cast<uint4 *>(prow + (g >> 3) * kSlab + (((g & 7) ^ (row & 7)) << 4)) = v4;
                 }
                 l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-                // O holds the products up to tile j-1 once pv_done has completed j times for this item
-                if (j > 0) {
+                // O holds the products up to tile j-1 once pv_done has completed that many times for this item
+                if (j > kr.lo) {
                     if (!wait_bounded(&pv_done, pv_seen & 1, failed, 12)) { ok = false; break; }
                     pv_seen++;
                     tcgen05_fence_after();
@@ -331,7 +400,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
             if (!wait_bounded(&pv_done, pv_seen & 1, failed, 14)) break;   // the last product's arrival
             pv_seen++;
             tcgen05_fence_after();
-            const float inv = 1.0f / l;
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;   // a query that sees no key: a zero row
             // every product of the item is complete, so P buffer 0 is idle: each warp stages its own 32
             // rows of O there (the rows it alone writes when the buffer next holds P)
             {
@@ -366,6 +435,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const __
                 mbar_arrive(&o_free);
             }
             __syncwarp();
+            item_count++;
         }
         if (lane == 0) bulk_wait_group<0>();
     }
@@ -746,7 +816,9 @@ int attn_encode_fn(EncodeTiledFn *out) {
 }
 
 // (feature, head, position, batch) BFloat16 array, dense, as boxes of 64 features x `rows` positions.
-int attn_tmap(CUtensorMap *map, const void *base, int d, int heads, int positions, int batch, int rows) {
+// `stride`: elements from one batch member, position, head to the next (null: dense).
+int attn_tmap(CUtensorMap *map, const void *base, int d, int heads, int positions, int batch, int rows,
+              const long long *stride = nullptr) {
     EncodeTiledFn fn;
     int st = attn_encode_fn(&fn);
     if (st) return st;
@@ -754,6 +826,11 @@ int attn_tmap(CUtensorMap *map, const void *base, int d, int heads, int position
                           static_cast<cuuint64_t>(positions), static_cast<cuuint64_t>(batch)};
     cuuint64_t strides[3] = {static_cast<cuuint64_t>(d) * 2, static_cast<cuuint64_t>(d) * heads * 2,
                              static_cast<cuuint64_t>(d) * heads * positions * 2};
+    if (stride) {
+        strides[0] = static_cast<cuuint64_t>(stride[2]) * 2;
+        strides[1] = static_cast<cuuint64_t>(stride[1]) * 2;
+        strides[2] = static_cast<cuuint64_t>(stride[0]) * 2;
+    }
     cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(rows), 1};
     cuuint32_t elem[4] = {1, 1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, elem,
@@ -767,37 +844,46 @@ int attn_tmap(CUtensorMap *map, const void *base, int d, int heads, int position
 
 using namespace tb200;
 
-extern "C" int tb200_attention_fwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, void *o,
-                                   float *lse, void *stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (!d) return TB200_ERR_NULL;
-    if (d->batch < 0 || d->heads <= 0 || d->kv_heads <= 0 || d->queries < 0 || d->keys < 0 || d->head_dim <= 0)
-        return TB200_ERR_SHAPE;
-    if (d->heads % d->kv_heads != 0 || !(d->scale > 0.0f)) return TB200_ERR_SHAPE;
-    if (d->causal && d->queries != d->keys) return TB200_ERR_SHAPE;
-    if (d->dtype != TB200_BF16) return TB200_ERR_DTYPE;
-    if (d->head_dim != kHeadDim && !attention_simt_takes(d)) return TB200_ERR_UNSUPPORTED;
-    if (d->batch == 0 || d->queries == 0) return TB200_OK;
-    if (d->keys == 0) return TB200_ERR_UNSUPPORTED;
-    if (!q || !k || !v || !o) return TB200_ERR_NULL;
-    if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(o, 16) || !aligned_to(lse, 4))
-        return TB200_ERR_ALIGN;
-    if (d->queries > (1 << 24) || d->keys > (1 << 24)) return TB200_ERR_SHAPE;
-    if (d->head_dim != kHeadDim) return attention_simt_fwd(d, q, k, v, o, lse, stream);
+namespace tb200 {
+
+// The tensor-core forward on checked arguments.  `mask` (may be null): masks the device holds and operands at other
+// strides -- those run on the one-tile kernel, which finds each item's key range and masks row by row; the plain
+// programs with more than one query tile take the pair kernel.  TB200_ERR_UNSUPPORTED: strides the TMA unit cannot
+// describe (the caller then falls to the CUDA-core kernels).
+int attention_tensor_fwd(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q, const void *k, const void *v,
+                         void *o, float *lse, cudaStream_t stream) {
     DeviceInfo dev;
     int st = current_device(&dev);
     if (st) return st;
+    long long qs[3] = {static_cast<long long>(d->queries) * d->heads * d->head_dim, static_cast<long long>(d->heads) * d->head_dim,
+                       d->head_dim};
+    long long ks[3] = {static_cast<long long>(d->keys) * d->kv_heads * d->head_dim,
+                       static_cast<long long>(d->kv_heads) * d->head_dim, d->head_dim};
+    bool masked = false;
+    if (mask) {
+        if (mask->q_stride[0] || mask->q_stride[1] || mask->q_stride[2])
+            for (int i = 0; i < 3; i++) qs[i] = mask->q_stride[i];
+        if (mask->kv_stride[0] || mask->kv_stride[1] || mask->kv_stride[2])
+            for (int i = 0; i < 3; i++) ks[i] = mask->kv_stride[i];
+        masked = mask->doc_start || mask->kv_len;
+        for (int i = 0; i < 3; i++)
+            if (qs[i] <= 0 || ks[i] <= 0 || qs[i] % 8 || ks[i] % 8) return TB200_ERR_UNSUPPORTED;
+    }
     AttnFwdArgs p{};
-    if ((st = attn_tmap(&p.q, q, d->head_dim, d->heads, d->queries, d->batch, kTile))) return st;
-    if ((st = attn_tmap(&p.k, k, d->head_dim, d->kv_heads, d->keys, d->batch, kTile))) return st;
-    if ((st = attn_tmap(&p.v, v, d->head_dim, d->kv_heads, d->keys, d->batch, kTile))) return st;
-    if ((st = attn_tmap(&p.o, o, d->head_dim, d->heads, d->queries, d->batch, 32))) return st;
+    if ((st = attn_tmap(&p.q, q, d->head_dim, d->heads, d->queries, d->batch, kTile, qs))) return st;
+    if ((st = attn_tmap(&p.k, k, d->head_dim, d->kv_heads, d->keys, d->batch, kTile, ks))) return st;
+    if ((st = attn_tmap(&p.v, v, d->head_dim, d->kv_heads, d->keys, d->batch, kTile, ks))) return st;
+    if ((st = attn_tmap(&p.o, o, d->head_dim, d->heads, d->queries, d->batch, 32, qs))) return st;
     p.lse = lse;
     p.batch = d->batch; p.heads = d->heads; p.kv_heads = d->kv_heads; p.queries = d->queries; p.keys = d->keys;
     p.q_tiles = static_cast<int>(ceil_div(d->queries, kTile));
     p.items = p.q_tiles * d->batch * d->heads;
     p.causal = d->causal;
     p.scale_log2 = d->scale * kLog2e;
+    p.doc_start = mask ? mask->doc_start : nullptr;
+    p.kv_len = mask ? mask->kv_len : nullptr;
+    p.o_rows = static_cast<__nv_bfloat16 *>(o);
+    p.o_batch = qs[0]; p.o_pos = qs[1]; p.o_head = qs[2];
     const size_t smem = 7 * kTileBytes + 1024;
     static std::mutex lock;
     static bool configured[64] = {};
@@ -809,8 +895,8 @@ extern "C" int tb200_attention_fwd(const tb200_attn_desc *d, const void *q, cons
             configured[dev.device] = true;
         }
     }
-    // more than one query tile: two tiles per CTA, each with its own softmax warps
-    if (p.q_tiles > 1) {
+    // more than one query tile and nothing but the causal mask: two tiles per CTA, each with its own softmax warps
+    if (p.q_tiles > 1 && !masked) {
         const size_t pair_smem = 6 * kTileBytes + 1024;
         {
             std::lock_guard<std::mutex> hold(lock);
@@ -831,6 +917,28 @@ extern "C" int tb200_attention_fwd(const tb200_attn_desc *d, const void *q, cons
     attention_fwd_kernel<<<grid, kAttnThreads, smem, stream>>>(p);
     TB200_CUDA(cudaGetLastError());
     return TB200_OK;
+}
+
+}  // namespace tb200
+
+extern "C" int tb200_attention_fwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, void *o,
+                                   float *lse, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!d) return TB200_ERR_NULL;
+    if (d->batch < 0 || d->heads <= 0 || d->kv_heads <= 0 || d->queries < 0 || d->keys < 0 || d->head_dim <= 0)
+        return TB200_ERR_SHAPE;
+    if (d->heads % d->kv_heads != 0 || !(d->scale > 0.0f)) return TB200_ERR_SHAPE;
+    if (d->causal && d->queries != d->keys) return TB200_ERR_SHAPE;
+    if (d->dtype != TB200_BF16) return TB200_ERR_DTYPE;
+    if (d->head_dim != kHeadDim && !attention_simt_takes(d)) return TB200_ERR_UNSUPPORTED;
+    if (d->batch == 0 || d->queries == 0) return TB200_OK;
+    if (d->keys == 0) return TB200_ERR_UNSUPPORTED;
+    if (!q || !k || !v || !o) return TB200_ERR_NULL;
+    if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(o, 16) || !aligned_to(lse, 4))
+        return TB200_ERR_ALIGN;
+    if (d->queries > (1 << 24) || d->keys > (1 << 24)) return TB200_ERR_SHAPE;
+    if (d->head_dim != kHeadDim) return attention_simt_fwd(d, q, k, v, o, lse, stream);
+    return attention_tensor_fwd(d, nullptr, q, k, v, o, lse, stream);
 }
 
 extern "C" int tb200_attention_device_error(void) {

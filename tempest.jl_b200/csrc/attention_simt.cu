@@ -287,6 +287,12 @@ extern "C" int tb200_attention_fwd_masked(const tb200_attn_desc *d, const tb200_
     if (d->batch == 0 || d->queries == 0) return TB200_OK;
     if (d->keys == 0) return TB200_ERR_UNSUPPORTED;
     if (!q || !k || !v || !o) return TB200_ERR_NULL;
+    // 128 features, 16-byte aligned arrays, strides the TMA unit can describe: the tensor-core kernel
+    if (d->head_dim == 128 && d->dtype == TB200_BF16 && aligned_to(q, 16) && aligned_to(k, 16) && aligned_to(v, 16) &&
+        aligned_to(o, 16) && d->queries <= (1 << 24) && d->keys <= (1 << 24)) {
+        st = attention_tensor_fwd(d, mask, q, k, v, o, lse, static_cast<cudaStream_t>(stream));
+        if (st != TB200_ERR_UNSUPPORTED) return st;
+    }
     return attention_simt_fwd(d, q, k, v, o, lse, static_cast<cudaStream_t>(stream), mask);
 }
 

@@ -11,4 +11,8 @@ int attention_simt_fwd(const tb200_attn_desc *d, const void *q, const void *k, c
 int attention_simt_bwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, const void *o,
                        const float *lse, const void *dout, void *dq, void *dk, void *dv, cudaStream_t stream,
                        const tb200_attn_mask *mask = nullptr);
+// The tensor-core forward (attention_fwd.cu; 128 features) with masks the device holds and operands at other strides.
+// TB200_ERR_UNSUPPORTED where the TMA unit cannot describe the strides.
+int attention_tensor_fwd(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q, const void *k, const void *v,
+                         void *o, float *lse, cudaStream_t stream);
 }  // namespace tb200

@@ -158,12 +158,13 @@ def test_packed_documents(pkg, cuda, oracle, D):
         close_grad(oracle, host(torch, dv), dv64, "dv")
 
 
-def test_decode_up_to_lengths(pkg, cuda, oracle):
+@pytest.mark.parametrize("D", [16, 128])
+def test_decode_up_to_lengths(pkg, cuda, oracle, D):
     """The reference's decode program (test/cuda/attention.jl:248-275): one query per head, 8 query heads over
     2 key heads, a cache (features, positions, key heads, sequences) of 200 positions read up to a length the
-    device holds; another set of lengths is the same launch."""
+    device holds; another set of lengths is the same launch.  128 features: the tensor-core kernel."""
     torch, L = cuda, pkg.lib
-    B, H, Hkv, N, D = 3, 8, 2, 200, 16
+    B, H, Hkv, N = 3, 8, 2, 200
     q = oracle.to_bf16(oracle.normal((B, 1, H, D), 71))
     kc = oracle.to_bf16(oracle.normal((B, Hkv, N, D), 72))     # the cache's memory order
     vc = oracle.to_bf16(oracle.normal((B, Hkv, N, D), 73))
@@ -185,6 +186,49 @@ def test_decode_up_to_lengths(pkg, cuda, oracle):
     o, lse = torch.full_like(qd, float("nan")), torch.full((B, 1, H), float("nan"), device="cuda")
     L.attention_fwd_masked(desc, mask, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr())
     assert (o[0] == 0).all() and torch.isinf(lse[0]).all() and torch.isfinite(lse[1]).all()
+
+
+def test_masks_on_the_tensor_core_forward(pkg, cuda, oracle):
+    """128 features: the masked forward runs on the tensor cores.  Documents longer and shorter than a tile of 128
+    (whole key tiles before a document's start are skipped, the tile the start falls in is masked row by row);
+    starts that are not sorted (every tile's range is found from all its queries' starts); lengths over several key
+    tiles with grouped heads and more keys than queries; the pair of outputs agrees with the CUDA-core kernels'."""
+    torch, L = cuda, pkg.lib
+    D = 128
+    B, S, H = 2, 1000, 2
+    q, k, v = (oracle.to_bf16(oracle.normal((B, S, H, D), 81 + i)) for i in range(3))
+    qd, kd, vd = (dev(torch, a) for a in (q, k, v))
+    desc = L.attn_desc(B, H, S, S, D, True, scale=0.1)
+    rng = np.random.default_rng(5)
+    unsorted = np.minimum(rng.integers(0, S, (B, S)), np.arange(S)[None, :]).astype(np.int32)
+    for start in (np.stack([doc_starts([300, 500, 200]), doc_starts([129, 1, 126, 744])]), unsorted):
+        sd = torch.from_numpy(start).cuda()
+        mask = L.attn_mask(doc_start=sd.data_ptr())
+        o, lse = torch.full_like(qd, float("nan")), torch.full((B, S, H), float("nan"), device="cuda")
+        L.attention_fwd_masked(desc, mask, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr())
+        torch.cuda.synchronize()
+        assert L.attention_device_error() == 0
+        o64, lse64 = oracle.attention_f64(q, k, v, True, scale=0.1, doc_start=start)
+        assert np.abs(oracle.from_bf16(host(torch, o)) - o64).max() <= ATOL_BF16
+        assert np.abs(lse.cpu().numpy() - lse64).max() <= 2e-5 * max(1.0, np.abs(lse64).max())
+    # lengths: 200 queries against up to 700 keys, 4 query heads over 2 key heads, one sequence with no key at all
+    Bq, M, N, Hq, Hkv = 3, 200, 700, 4, 2
+    q = oracle.to_bf16(oracle.normal((Bq, M, Hq, D), 91))
+    k, v = (oracle.to_bf16(oracle.normal((Bq, N, Hkv, D), 92 + i)) for i in range(2))
+    qd, kd, vd = (dev(torch, a) for a in (q, k, v))
+    lengths = [513, 0, 90]
+    ld = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    desc = L.attn_desc(Bq, Hq, M, N, D, False, scale=0.1, kv_heads=Hkv)
+    o, lse = torch.full_like(qd, float("nan")), torch.full((Bq, M, Hq), float("nan"), device="cuda")
+    L.attention_fwd_masked(desc, L.attn_mask(kv_len=ld.data_ptr()), qd.data_ptr(), kd.data_ptr(), vd.data_ptr(),
+                           o.data_ptr(), lse.data_ptr())
+    torch.cuda.synchronize()
+    assert L.attention_device_error() == 0
+    o64, lse64 = oracle.attention_f64(q, k, v, False, scale=0.1, kv_len=np.array(lengths))
+    assert np.abs(oracle.from_bf16(host(torch, o)) - o64).max() <= ATOL_BF16
+    assert (o[1] == 0).all() and torch.isinf(lse[1]).all()
+    fin = np.isfinite(lse64)
+    assert np.abs(lse.cpu().numpy()[fin] - lse64[fin]).max() <= 2e-5 * max(1.0, np.abs(lse64[fin]).max())
 
 
 def test_masked_entries_refuse_bad_requests(pkg, cuda):
