@@ -765,10 +765,20 @@ def run_profile_case(args):
         x = torch.randn(rows, n, device="cuda")
         y = torch.empty_like(x)
         a = 0.9 + 0.1 * torch.rand(rows, n, device="cuda")
+        need = L.scan_workspace_bytes(L.scan_desc(n, rows, L.SCAN_SUM, across=True))
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+        # a recurrence whose step is a map, h = tanh(a h + x) with h stored: 2^20 positions, 64 steps
+        cell = pkg.groups.gated_tanh_cell(1 << 20, 64)
+        cx = torch.randn(64, 1 << 20, device="cuda")
+        ca, ch = torch.full((1 << 20,), 0.7, device="cuda"), torch.zeros(1 << 20, device="cuda")
+        cy, cl = torch.empty_like(cx), torch.empty_like(ch)
         for _ in range(2):
             L.scan(x.data_ptr(), y.data_ptr(), n, rows, L.SCAN_SUM, stream=stream)
-            L.scan(x.data_ptr(), y.data_ptr(), n, rows, L.SCAN_SUM, across=True, stream=stream)
+            L.scan(x.data_ptr(), y.data_ptr(), n, rows, L.SCAN_SUM, across=True, workspace=ws.data_ptr(),
+                   workspace_bytes=need, stream=stream)
             L.scan(a.data_ptr(), y.data_ptr(), n, rows, L.SCAN_AFFINE, x2=x.data_ptr(), stream=stream)
+            L.recurrence_compiled(cell.desc(), [cx.data_ptr(), ca.data_ptr(), ch.data_ptr()], [cy.data_ptr(), cl.data_ptr()],
+                                  stream)
     elif case == "attention":
         Bq, Hq, Sq, Dq = 1, 32, 4096, 128
         q, k, v, g = (torch.randn(Bq, Sq, Hq, Dq, device="cuda").bfloat16() for _ in range(4))
