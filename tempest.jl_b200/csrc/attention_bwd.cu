@@ -77,6 +77,7 @@ struct AttnBwdArgs {
     const float *lse2;              // [batch][head][q_pad]  -lse * log2(e)
     const float *delta;             // [batch][head][q_pad]  -delta
     float *dq_acc;                  // one-kernel form: [batch][query][head][feature] Float32, zero before the launch
+    CUtensorMap dq_map;             // the same as (feature, head, query, batch), boxes of 32 features x 16 queries
     int batch, heads, kv_heads, queries, keys;
     int q_pad;                      // queries rounded up to whole steps: rows of the two arrays above, zero-filled
     int outer_tiles, supers;
@@ -410,6 +411,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
             // `row` is this thread's feature) and added into the Float32 workspace: 32 consecutive features of one
             // query per warp instruction.  The columns are handed back before the adds are issued.
             int prev_hi = 0, prev_pos0 = 0;
+            bool dq_pending = false;   // a reduction may still be reading this warp's part of the slab
+            // before that part is written for anything else
+            auto slab_free = [&]() {
+                if (!dq_pending) return;
+                if (lane == 0) bulk_wait_group_read<0>();
+                __syncwarp();
+                dq_pending = false;
+            };
             auto add_dq = [&](uint32_t step) -> bool {
                 if (!bwd_wait(&dq_full, step & 1, failed, 16)) return false;
                 tcgen05_fence_after();
@@ -420,14 +429,30 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&x1_free);
+                // Added into the Float32 workspace by the TMA unit, not by this thread: the warp lays its 32 features of
+                // 16 queries side by side, [query][feature], in its own 4 KB of the dS' slab (the bytes only this warp
+                // writes, free now that the dQ' product which read them is complete, written again later in this
+                // step) and one lane hands them over as a reduction; two halves of 2 KB take turns, so a round waits
+                // only for the reduction two rounds back.  The additions happen in L2 while the step goes on.
+                uint8_t *mine = s_ds + group * kSlab + q4 * 4096;
                 const int q0 = prev_pos0 + group * 64;
-                const long long line = static_cast<long long>(p.heads) * kD;
-                float *dst = p.dq_acc + ((static_cast<long long>(steps.b) * p.queries + q0) * p.heads + prev_hi) * kD + row;
-                const int live = p.queries - q0;   // queries of this half that exist
 #pragma unroll
-                for (int i = 0; i < 64; i++)
-                    if (i < live)
-                        asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + i * line), "f"(__uint_as_float(dq[i])) : "memory");
+                for (int round = 0; round < 4; round++) {
+                    if (lane == 0) bulk_wait_group_read<1>();
+                    __syncwarp();
+                    float *stage = reinterpret_cast<float *>(mine + (round & 1) * 2048);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) stage[i * 32 + lane] = __uint_as_float(dq[16 * round + i]);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        // queries past the end: nothing to add, but the (empty) group keeps the count of rounds
+                        if (q0 + 16 * round < p.queries)
+                            tma_reduce_add_4d(&p.dq_map, stage, q4 * 32, prev_hi, q0 + 16 * round, steps.b);
+                        bulk_commit_group();
+                    }
+                }
+                dq_pending = true;
                 return true;
             };
             for (int t = 0; t < steps.count; t++, c++) {
@@ -535,6 +560,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 if (ATOMIC) {
                     // the same dS' as this key's line of its group's slab (64 queries = 128 bytes, 16-byte chunks
                     // swizzled by the row as the tensor core expects), for the dQ' product
+                    slab_free();
                     uint8_t *line = s_ds + group * kSlab + row * 128;
 #pragma unroll
                     for (int j = 0; j < 8; j++)
@@ -549,6 +575,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
             }
             if (!ok) break;
             if (ATOMIC && steps.count > 0 && !add_dq(c - 1)) break;   // the item's last step
+            if (ATOMIC) slab_free();   // the staging below uses the same memory
             // ---- the item's gradients: accumulators -> BFloat16 -> shared staging -> TMA stores.
             // dK/dV: group 0 writes dV, group 1 dK, one 64-feature slab at a time; dQ: each group one slab.
             if (steps.count > 0) {
@@ -791,6 +818,19 @@ extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, cons
         const size_t elements = static_cast<size_t>(d->batch) * d->queries * d->heads * kD;
         p.dq_acc = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + bwd_stat_bytes(d));
         TB200_CUDA(cudaMemsetAsync(p.dq_acc, 0, elements * sizeof(float), stream));
+        {
+            EncodeTiledFn fn;
+            if ((st = bwd_encode_fn(&fn))) return st;
+            cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(d->heads),
+                                  static_cast<cuuint64_t>(d->queries), static_cast<cuuint64_t>(d->batch)};
+            cuuint64_t strides[3] = {static_cast<cuuint64_t>(kD) * 4, static_cast<cuuint64_t>(kD) * d->heads * 4,
+                                     static_cast<cuuint64_t>(kD) * d->heads * d->queries * 4};
+            cuuint32_t box[4] = {32, 1, 16, 1};
+            cuuint32_t elem[4] = {1, 1, 1, 1};
+            if (fn(&p.dq_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.dq_acc, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return TB200_ERR_UNSUPPORTED;
+        }
         if ((st = launch_bwd<2>(p, dev, stream))) return st;
         const long long vectors = static_cast<long long>(elements / 8);
         const long long blocks = ceil_div(vectors, 256);

@@ -112,6 +112,13 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap *m, const void *s
                  ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z), "r"(w)
                  : "memory");
 }
+// One tile of Float32, this CTA's shared memory added into global memory (the additions happen in L2), tracked by the
+// thread's bulk-group counter like a store.  Elements outside the tensor are left out.
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap *m, const void *src, int x, int y, int z, int w) {
+    asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z), "r"(w)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // until at most N of this thread's bulk groups are still reading their shared-memory source
 template <int N>
