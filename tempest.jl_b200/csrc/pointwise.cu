@@ -119,15 +119,24 @@ __global__ void __launch_bounds__(256) colsum_slab_kernel(const T *x, float *par
     }
 }
 
+// Eight lanes a column, each over every eighth slab in order, then the lanes in a fixed tree: the same sum whatever
+// the grid, and 32 columns a block so that a narrow array still spreads over many SMs.
 template <typename T>
 __global__ void __launch_bounds__(256) colsum_merge_kernel(const float *partial, T *out, int n, int slabs,
                                                            float scale) {
-    const int col = blockIdx.x * 256 + threadIdx.x;
-    if (col >= n) return;
+    __shared__ float sm[8][33];
+    const int tx = threadIdx.x & 31, lane = threadIdx.x >> 5;
+    const int col = blockIdx.x * 32 + tx;
     float t = 0.0f;
-    for (int s = 0; s < slabs; s++) t += partial[static_cast<long long>(s) * n + col];
-    float o[1] = {t * scale};
-    Access<T, false>::store(out + col, o);
+    if (col < n)
+        for (int s = lane; s < slabs; s += 8) t += partial[static_cast<long long>(s) * n + col];
+    sm[lane][tx] = t;
+    __syncthreads();
+    if (lane == 0 && col < n) {
+        const float sum = ((sm[0][tx] + sm[1][tx]) + (sm[2][tx] + sm[3][tx])) + ((sm[4][tx] + sm[5][tx]) + (sm[6][tx] + sm[7][tx]));
+        float o[1] = {sum * scale};
+        Access<T, false>::store(out + col, o);
+    }
 }
 
 // y = y + alpha * x, elementwise; x may have another element type than y (BFloat16 gradients
@@ -272,7 +281,7 @@ extern "C" int tb200_colsum(const void *x, void *out, int64_t rows, int64_t n, i
     if (!workspace || workspace_bytes < need || !aligned_to(workspace, 16)) return TB200_ERR_WORKSPACE;
     float *partial = static_cast<float *>(workspace);
     dim3 grid(static_cast<unsigned>(ceil_div(n, 32 * epv)), static_cast<unsigned>(slabs));
-    const unsigned merge_blocks = static_cast<unsigned>(ceil_div(n, 256));
+    const unsigned merge_blocks = static_cast<unsigned>(ceil_div(n, 32));
     const int ni = static_cast<int>(n);
     if (dtype == TB200_F32) {
         const float *xp = static_cast<const float *>(x);
