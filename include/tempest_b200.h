@@ -398,6 +398,19 @@ int tb200_attention_bwd_masked(const tb200_attn_desc *desc, const tb200_attn_mas
                                const void *k, const void *v, const void *o, const float *lse, const void *dout,
                                void *dq, void *dk, void *dv, void *stream);
 
+/* The masked pullback on the tensor cores: 128 features, dense arrays (a mask
+ * with strides, another head dimension: TB200_ERR_UNSUPPORTED, for which the
+ * entry above remains), in either of the pullback's forms (desc->deterministic).
+ * Keys beyond a sequence's length and key tiles that lie wholly beyond it are
+ * skipped; with packed documents every visited tile is masked element by
+ * element (tiles that lie wholly before a document's start are still visited).
+ * The workspace is tb200_attention_bwd's plus a row of starts per (batch, head). */
+size_t tb200_attention_bwd_masked_workspace_bytes(const tb200_attn_desc *desc);
+int tb200_attention_bwd_masked_ws(const tb200_attn_desc *desc, const tb200_attn_mask *mask, const void *q,
+                                  const void *k, const void *v, const void *o, const float *lse, const void *dout,
+                                  void *dq, void *dk, void *dv, void *workspace, size_t workspace_bytes,
+                                  void *stream);
+
 /* ---- chunked gated DeltaNet ------------------------------------------------------
  * The program of examples/deltanet.jl:56-85: q, k (dk, T, heads) = memory
  * [head][t][dk], v (dv, T, heads), a (log decay) and beta (T, heads) in

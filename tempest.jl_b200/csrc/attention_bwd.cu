@@ -78,8 +78,13 @@ struct AttnBwdArgs {
     const float *delta;             // [batch][head][q_pad]  -delta
     float *dq_acc;                  // one-kernel form: [batch][query][head][feature] Float32, zero before the launch
     CUtensorMap dq_map;             // the same as (feature, head, query, batch), boxes of 32 features x 16 queries
+    // masks the device holds (null: none).  A key beyond its sequence's length, or before the start of its query's
+    // document, gets a score of -Inf like a key the causal mask hides.
+    const int *kv_len;              // [batch]
+    const int *doc_start;           // [batch][queries]: the dQ kernel's row threads read their own query's
+    const int *starts;              // the same as [batch][head][q_pad] rows, which the dK/dV kernels' row threads read
     int batch, heads, kv_heads, queries, keys;
-    int q_pad;                      // queries rounded up to whole steps: rows of the two arrays above, zero-filled
+    int q_pad;                      // queries rounded up to whole steps: rows of the arrays above, zero-filled
     int outer_tiles, supers;
     int causal;
     float scale, scale_log2;
@@ -112,10 +117,17 @@ __device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, volatil
 // only and find them in L2 instead of streaming them from HBM once per tile.
 //
 // Steps: the item of one walk step, and which head and which 128-position chunk its step t reads.
+__device__ __forceinline__ int sequence_keys(const AttnBwdArgs &p, int b) {
+    if (!p.kv_len) return p.keys;
+    const int n = p.kv_len[b];
+    return n < 0 ? 0 : (n < p.keys ? n : p.keys);
+}
+
 template <bool DKDV>
 struct Steps {
     int b, head_outer, tile;   // the item
     int c0, nc, group, count, head_first;
+    int keys;                  // the sequence's keys (its length when the device holds lengths)
     bool done, skip;           // past the CTA's last super | second half of a super whose halves are one tile
     __device__ __forceinline__ Steps(const AttnBwdArgs &p, int j) {
         const int half_tiles = (p.outer_tiles + 1) / 2;
@@ -133,17 +145,20 @@ struct Steps {
             tile = heavy_or_light ? p.outer_tiles - 1 - i : i;
             b = bh / p.kv_heads;
             head_outer = bh % p.kv_heads;
+            keys = sequence_keys(p, b);
             const int all = (p.queries + kInner - 1) / kInner;
             c0 = p.causal ? (tile * kOuter) / kInner : 0;
             if (c0 > all) c0 = all;
             nc = all - c0;
+            if (tile * kOuter >= keys) nc = 0;   // every key of the tile lies beyond the length: zero gradients
             count = nc * group;
             head_first = head_outer * group;
         } else {
             tile = heavy_or_light ? i : p.outer_tiles - 1 - i;
             b = bh / p.heads;
             head_outer = bh % p.heads;
-            const int all = (p.keys + kInner - 1) / kInner;
+            keys = sequence_keys(p, b);
+            const int all = (keys + kInner - 1) / kInner;
             c0 = 0;
             nc = all;
             if (p.causal) {
@@ -400,10 +415,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
             if (steps.skip) continue;
             const int outer_pos = steps.tile * kOuter + row;   // this thread's key (dK/dV) or query (dQ)
             float row_lse2 = 0.0f, row_delta = 0.0f;
+            int row_start = 0;   // dQ: the first key this thread's query sees (packed documents)
             if (!DKDV && outer_pos < p.queries) {
                 const long long i = (static_cast<long long>(steps.b) * p.heads + steps.head_outer) * p.q_pad + outer_pos;
                 row_lse2 = p.lse2[i];
                 row_delta = p.delta[i];
+                if (p.doc_start) row_start = p.doc_start[static_cast<long long>(steps.b) * p.queries + outer_pos];
             }
             bool ok = true;
             typename Steps<DKDV>::Cursor cur;
@@ -475,18 +492,33 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s_read);
-                const bool edge = DKDV ? (pos0 + kInner > p.queries || outer_pos >= p.keys ||
-                                          (p.causal && pos0 < steps.tile * kOuter + kOuter))
-                                       : (pos0 + kInner > p.keys || outer_pos >= p.queries ||
-                                          (p.causal && pos0 + kInner - 1 > steps.tile * kOuter));
+                // (with packed documents every step takes the per-element test: where the starts fall is not known here)
+                const bool edge = p.doc_start != nullptr ||
+                                  (DKDV ? (pos0 + kInner > p.queries || outer_pos >= steps.keys ||
+                                           (p.causal && pos0 < steps.tile * kOuter + kOuter))
+                                        : (pos0 + kInner > steps.keys || outer_pos >= p.queries ||
+                                           (p.causal && pos0 + kInner - 1 > steps.tile * kOuter)));
                 if (edge) {
                     // masked positions get a score of -Inf: their weight and their dS are then exactly zero
+                    // dK/dV: the starts of the step's queries, the same 64 for every thread of the group (L1 hands them out)
+                    const int4 *starts = reinterpret_cast<const int4 *>(
+                        p.starts + (static_cast<long long>(steps.b) * p.heads + hi) * p.q_pad + col0);
 #pragma unroll
                     for (int i = 0; i < 64; i++) {
                         const int inner_pos = col0 + i;
                         const int key = DKDV ? outer_pos : inner_pos;
                         const int query = DKDV ? inner_pos : outer_pos;
-                        if (key >= p.keys || query >= p.queries || (p.causal && key > query)) s[i] = 0xff800000u;
+                        int first = 0;
+                        if (p.doc_start) {
+                            if (DKDV) {
+                                const int4 q4s = __ldg(starts + (i >> 2));
+                                first = (i & 3) == 0 ? q4s.x : (i & 3) == 1 ? q4s.y : (i & 3) == 2 ? q4s.z : q4s.w;
+                            } else {
+                                first = row_start;
+                            }
+                        }
+                        if (key >= steps.keys || query >= p.queries || (p.causal && key > query) || key < first)
+                            s[i] = 0xff800000u;
                     }
                 }
                 // P.  dQ keeps it in Float32 for dS.  dK/dV rounds it to BFloat16 here -- P' feeds dV += P' dO in that
@@ -639,7 +671,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
 // delta[b][h][m] = sum_d dO o ; lse2[b][h][m] = lse[b][m][h] * log2(e), rows of q_pad entries.  16 threads per (b, m, h) row.
 __global__ void __launch_bounds__(256) attention_stats_kernel(const __nv_bfloat16 *o, const __nv_bfloat16 *dout,
                                                               const float *lse, float *lse2, float *delta, int batch,
-                                                              int heads, int queries, int q_pad, int d) {
+                                                              int heads, int queries, int q_pad, int d,
+                                                              const int *doc_start, int *starts) {
     const long long rows = static_cast<long long>(batch) * queries * heads;
     const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 4;
     const int t = threadIdx.x & 15;
@@ -663,7 +696,11 @@ __global__ void __launch_bounds__(256) attention_stats_kernel(const __nv_bfloat1
         const long long out = (b * heads + h) * q_pad + m;
         // both negated: the row threads add them with packed (two at a time) instructions, which have no negate
         delta[out] = -s;
-        lse2[out] = -lse[r] * kLog2e;
+        // a query that saw no key has a log-sum-exp of -Inf: its weights are zero whatever the scores (a finite huge
+        // shift instead of the infinite one, which would meet the masked scores' -Inf as NaN)
+        const float l = lse[r];
+        lse2[out] = l == -INFINITY ? -1.0e30f : -l * kLog2e;
+        if (starts) starts[out] = doc_start[b * queries + m];
     }
 }
 
@@ -761,9 +798,46 @@ extern "C" size_t tb200_attention_bwd_workspace_bytes(const tb200_attn_desc *d) 
     return bytes;
 }
 
+namespace {
+size_t bwd_start_bytes(const tb200_attn_desc *d) {
+    const size_t q_pad = (static_cast<size_t>(d->queries) + kInner - 1) / kInner * kInner;
+    return (static_cast<size_t>(d->batch) * d->heads * q_pad * sizeof(int) + 255) / 256 * 256;
+}
+int bwd_run(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q, const void *k, const void *v, const void *o,
+            const float *lse, const void *dout, void *dq, void *dk, void *dv, void *workspace, size_t workspace_bytes,
+            void *stream_);
+}  // namespace
+
 extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v,
                                    const void *o, const float *lse, const void *dout, void *dq, void *dk, void *dv,
                                    void *workspace, size_t workspace_bytes, void *stream_) {
+    return bwd_run(d, nullptr, q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream_);
+}
+
+// The pullback with masks the device holds, on the tensor cores: 128 features, dense arrays (a mask with strides, or
+// another head dimension: TB200_ERR_UNSUPPORTED -- tb200_attention_bwd_masked takes those).  The workspace is
+// tb200_attention_bwd's plus one row of starts per (batch, head) when documents are packed.
+extern "C" size_t tb200_attention_bwd_masked_workspace_bytes(const tb200_attn_desc *d) {
+    const size_t base = tb200_attention_bwd_workspace_bytes(d);
+    return base ? base + bwd_start_bytes(d) : 0;
+}
+
+extern "C" int tb200_attention_bwd_masked_ws(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q, const void *k,
+                                             const void *v, const void *o, const float *lse, const void *dout, void *dq,
+                                             void *dk, void *dv, void *workspace, size_t workspace_bytes, void *stream_) {
+    if (!d) return TB200_ERR_NULL;
+    if (d->head_dim != kD) return TB200_ERR_UNSUPPORTED;
+    if (mask)
+        for (int i = 0; i < 3; i++)
+            if (mask->q_stride[i] || mask->kv_stride[i]) return TB200_ERR_UNSUPPORTED;
+    if (workspace_bytes < tb200_attention_bwd_masked_workspace_bytes(d)) return TB200_ERR_WORKSPACE;
+    return bwd_run(d, mask, q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream_);
+}
+
+namespace {
+int bwd_run(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q, const void *k, const void *v, const void *o,
+            const float *lse, const void *dout, void *dq, void *dk, void *dv, void *workspace, size_t workspace_bytes,
+            void *stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!d) return TB200_ERR_NULL;
     if (d->batch < 0 || d->heads <= 0 || d->kv_heads <= 0 || d->queries < 0 || d->keys < 0 || d->head_dim <= 0)
@@ -790,17 +864,26 @@ extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, cons
     const long long stat_len = static_cast<long long>(d->batch) * d->heads * q_pad;
     float *lse2 = static_cast<float *>(workspace);
     float *delta = lse2 + stat_len;
+    // packed documents: the starts again as rows per (batch, head), behind everything else in the workspace
+    const int *doc_start = mask ? mask->doc_start : nullptr;
+    int *starts = doc_start ? reinterpret_cast<int *>(static_cast<uint8_t *>(workspace) + tb200_attention_bwd_workspace_bytes(d))
+                            : nullptr;
     {
         if (q_pad != d->queries) TB200_CUDA(cudaMemsetAsync(workspace, 0, bwd_stat_bytes(d), stream));   // the pads are read
         const long long threads = static_cast<long long>(d->batch) * d->heads * d->queries * 16;
         const unsigned blocks = static_cast<unsigned>(ceil_div(threads, 256));
+        if (doc_start && q_pad != d->queries) TB200_CUDA(cudaMemsetAsync(starts, 0, bwd_start_bytes(d), stream));
         attention_stats_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(o),
                                                            static_cast<const __nv_bfloat16 *>(dout), lse, lse2, delta,
-                                                           d->batch, d->heads, d->queries, q_pad, d->head_dim);
+                                                           d->batch, d->heads, d->queries, q_pad, d->head_dim, doc_start,
+                                                           starts);
         TB200_CUDA(cudaGetLastError());
     }
     AttnBwdArgs p{};
     p.lse2 = lse2; p.delta = delta; p.q_pad = q_pad;
+    p.kv_len = mask ? mask->kv_len : nullptr;
+    p.doc_start = doc_start;
+    p.starts = starts;
     p.batch = d->batch; p.heads = d->heads; p.kv_heads = d->kv_heads; p.queries = d->queries; p.keys = d->keys;
     p.causal = d->causal; p.scale = d->scale; p.scale_log2 = d->scale * kLog2e;
     // dK, dV: items over key tiles
@@ -850,6 +933,7 @@ extern "C" int tb200_attention_bwd(const tb200_attn_desc *d, const void *q, cons
     p.supers = (p.outer_tiles + 1) / 2 * d->batch * d->heads;
     return launch_bwd<0>(p, dev, stream);
 }
+}  // namespace
 
 // Times the two forms of the pullback on the caller's own operands and returns the `deterministic` value of the
 // faster one (0 = one kernel with atomic adds, 1 = two kernels): the measured stage of the reference's search over

@@ -149,6 +149,8 @@ SIGNATURES = {
     "tb200_gemm_tune": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
     "tb200_attention_fwd_masked": (_i, [ctypes.POINTER(AttnDesc), ctypes.POINTER(AttnMask), _p, _p, _p, _p, _p, _p]),
     "tb200_attention_bwd_masked": (_i, [ctypes.POINTER(AttnDesc), ctypes.POINTER(AttnMask)] + [_p] * 10),
+    "tb200_attention_bwd_masked_workspace_bytes": (_sz, [ctypes.POINTER(AttnDesc)]),
+    "tb200_attention_bwd_masked_ws": (_i, [ctypes.POINTER(AttnDesc), ctypes.POINTER(AttnMask)] + [_p] * 10 + [_sz, _p]),
     "tb200_group_route": (_i, [ctypes.POINTER(GroupDesc)]),
     "tb200_group_attention": (_i, [ctypes.POINTER(GroupDesc), _i, _i, _i, ctypes.POINTER(_p), ctypes.POINTER(_p), _p]),
     "tb200_rowreduce_generic_check": (_i, [ctypes.POINTER(GroupDesc)]),
@@ -596,6 +598,17 @@ def attention_fwd_masked(desc, mask, q, k, v, o, lse=0, stream=0):
 def attention_bwd_masked(desc, mask, q, k, v, o, lse, dout, dq, dk, dv, stream=0):
     check("tb200_attention_bwd_masked", load().tb200_attention_bwd_masked(
         ctypes.byref(desc), ctypes.byref(mask), q, k, v, o, lse, dout, dq, dk, dv, stream or None))
+
+
+def attention_bwd_masked_workspace_bytes(desc):
+    return load().tb200_attention_bwd_masked_workspace_bytes(ctypes.byref(desc))
+
+
+def attention_bwd_masked_ws(desc, mask, q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream=0):
+    """The masked pullback on the tensor cores (128 features, dense arrays), either form (`desc.deterministic`)."""
+    check("tb200_attention_bwd_masked_ws", load().tb200_attention_bwd_masked_ws(
+        ctypes.byref(desc), ctypes.byref(mask), q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes,
+        stream or None))
 
 
 def dp_signal_bytes():

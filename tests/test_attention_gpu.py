@@ -231,6 +231,65 @@ def test_masks_on_the_tensor_core_forward(pkg, cuda, oracle):
     assert np.abs(lse.cpu().numpy()[fin] - lse64[fin]).max() <= 2e-5 * max(1.0, np.abs(lse64[fin]).max())
 
 
+@pytest.mark.parametrize("deterministic", [0, 1])
+def test_masked_pullback_on_the_tensor_cores(pkg, cuda, oracle, deterministic):
+    """128 features: packed documents (sorted starts, and starts that are not), then lengths with grouped heads and
+    more keys than queries (one sequence with no key: zero gradients), forward and pullback on the tensor cores, both
+    forms of the pullback, against the Float64 yardstick."""
+    torch, L = cuda, pkg.lib
+    D = 128
+    B, S, H = 2, 300, 2
+    q, k, v, g = (oracle.to_bf16(oracle.normal((B, S, H, D), 101 + i)) for i in range(4))
+    qd, kd, vd, gd = (dev(torch, a) for a in (q, k, v, g))
+    desc = L.attn_desc(B, H, S, S, D, True, scale=0.1, deterministic=deterministic)
+    need = L.attention_bwd_masked_workspace_bytes(desc)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    rng = np.random.default_rng(6)
+    unsorted = np.minimum(rng.integers(0, S, (B, S)), np.arange(S)[None, :]).astype(np.int32)
+    for start in (np.stack([doc_starts([90, 1, 130, 40, 39]), doc_starts([7, 200, 93])]), unsorted):
+        sd = torch.from_numpy(start).cuda()
+        mask = L.attn_mask(doc_start=sd.data_ptr())
+        o, lse = torch.full_like(qd, float("nan")), torch.full((B, S, H), float("nan"), device="cuda")
+        dq, dk, dv = (torch.full_like(t, float("nan")) for t in (qd, kd, vd))
+        L.attention_fwd_masked(desc, mask, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr())
+        L.attention_bwd_masked_ws(desc, mask, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                  gd.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), need)
+        torch.cuda.synchronize()
+        assert L.attention_bwd_device_error() == 0
+        o64, lse64, dq64, dk64, dv64 = oracle.attention_f64(q, k, v, True, scale=0.1, dout=g, doc_start=start)
+        close_grad(oracle, host(torch, dq), dq64, "dq")
+        close_grad(oracle, host(torch, dk), dk64, "dk")
+        close_grad(oracle, host(torch, dv), dv64, "dv")
+    Bq, M, N, Hq, Hkv = 3, 200, 700, 4, 2
+    q, g = (oracle.to_bf16(oracle.normal((Bq, M, Hq, D), 111 + i)) for i in range(2))
+    k, v = (oracle.to_bf16(oracle.normal((Bq, N, Hkv, D), 113 + i)) for i in range(2))
+    qd, kd, vd, gd = (dev(torch, a) for a in (q, k, v, g))
+    lengths = [513, 0, 90]
+    ld = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    mask = L.attn_mask(kv_len=ld.data_ptr())
+    desc = L.attn_desc(Bq, Hq, M, N, D, False, scale=0.1, kv_heads=Hkv, deterministic=deterministic)
+    need = L.attention_bwd_masked_workspace_bytes(desc)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    o, lse = torch.full_like(qd, float("nan")), torch.full((Bq, M, Hq), float("nan"), device="cuda")
+    dq, dk, dv = (torch.full_like(t, float("nan")) for t in (qd, kd, vd))
+    L.attention_fwd_masked(desc, mask, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr())
+    L.attention_bwd_masked_ws(desc, mask, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                              gd.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), need)
+    torch.cuda.synchronize()
+    assert L.attention_bwd_device_error() == 0
+    o64, lse64, dq64, dk64, dv64 = oracle.attention_f64(q, k, v, False, scale=0.1, dout=g, kv_len=np.array(lengths))
+    close_grad(oracle, host(torch, dq), dq64, "dq")
+    close_grad(oracle, host(torch, dk), dk64, "dk")
+    close_grad(oracle, host(torch, dv), dv64, "dv")
+    assert (dq[1] == 0).all() and (dk[1] == 0).all() and (dv[1] == 0).all()
+    # strides the tensor-core path does not take: refused, the CUDA-core entry remains
+    with pytest.raises(L.TB200Error) as e:
+        L.attention_bwd_masked_ws(desc, L.attn_mask(kv_len=ld.data_ptr(), kv_stride=(Hkv * N * D, D, N * D)), qd.data_ptr(),
+                                  kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr(), gd.data_ptr(), dq.data_ptr(),
+                                  dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), need)
+    assert e.value.status == -7
+
+
 def test_masked_entries_refuse_bad_requests(pkg, cuda):
     L, torch = pkg.lib, cuda
     x = torch.zeros(4096, device="cuda", dtype=torch.bfloat16)
