@@ -300,6 +300,10 @@ typedef struct tb200_attn_desc {
                                     default, `CUDATarget(...; deterministic = false)`,
                                     src/Compiler/runtime/target.jl:31); 1 = two kernels, no atomic adds, results
                                     repeat bit for bit */
+    int value_dim;               /* features of v, o, dout and dv when they differ from head_dim (the queries' and
+                                    keys'), as multi-head latent attention's do (test/cuda/attention.jl:150-177;
+                                    `own_domain`, src/Compiler/Implement/groups.jl:211-219); 0 = head_dim.  Such
+                                    programs run the CUDA-core kernels (dense arrays, both up to 256 features) */
 } tb200_attn_desc;
 
 /* o = softmax(scale * k'q + mask) weighted sum of v, lse beside it (NULL: not

@@ -470,7 +470,7 @@ def attention_f64(q, k, v, causal, scale=None, dout=None, doc_start=None, kv_len
     dq = np.einsum("bhmn,bnhd->bmhd", ds, kx) * scale
     dkx = np.einsum("bhmn,bmhd->bnhd", ds, qf) * scale
     dk = dkx.reshape(B, Skv, Hkv, g, D).sum(axis=3)
-    dv = dvx.reshape(B, Skv, Hkv, g, D).sum(axis=3)
+    dv = dvx.reshape(B, Skv, Hkv, g, vf.shape[-1]).sum(axis=3)   # the values may have features of their own
     return o, lse, dq, dk, dv
 
 

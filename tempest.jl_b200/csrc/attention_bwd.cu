@@ -793,7 +793,7 @@ size_t bwd_stat_bytes(const tb200_attn_desc *d) {
 extern "C" size_t tb200_attention_bwd_workspace_bytes(const tb200_attn_desc *d) {
     if (!d || d->batch <= 0 || d->heads <= 0 || d->queries <= 0) return 0;
     size_t bytes = bwd_stat_bytes(d);
-    if (!d->deterministic && d->head_dim == kD)
+    if (!d->deterministic && attention_tensor_geometry(d))
         bytes += static_cast<size_t>(d->batch) * d->queries * d->heads * kD * sizeof(float);
     return bytes;
 }
@@ -826,7 +826,7 @@ extern "C" int tb200_attention_bwd_masked_ws(const tb200_attn_desc *d, const tb2
                                              const void *v, const void *o, const float *lse, const void *dout, void *dq,
                                              void *dk, void *dv, void *workspace, size_t workspace_bytes, void *stream_) {
     if (!d) return TB200_ERR_NULL;
-    if (d->head_dim != kD) return TB200_ERR_UNSUPPORTED;
+    if (!attention_tensor_geometry(d)) return TB200_ERR_UNSUPPORTED;
     if (mask)
         for (int i = 0; i < 3; i++)
             if (mask->q_stride[i] || mask->kv_stride[i]) return TB200_ERR_UNSUPPORTED;
@@ -845,7 +845,7 @@ int bwd_run(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q
     if (d->heads % d->kv_heads != 0 || !(d->scale > 0.0f)) return TB200_ERR_SHAPE;
     if (d->causal && d->queries != d->keys) return TB200_ERR_SHAPE;
     if (d->dtype != TB200_BF16) return TB200_ERR_DTYPE;
-    if (d->head_dim != kD && !attention_simt_takes(d)) return TB200_ERR_UNSUPPORTED;
+    if (!attention_tensor_geometry(d) && !attention_simt_takes(d)) return TB200_ERR_UNSUPPORTED;
     if (d->batch == 0 || (d->queries == 0 && d->keys == 0)) return TB200_OK;
     if (d->queries == 0 || d->keys == 0) return TB200_ERR_UNSUPPORTED;
     if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv) return TB200_ERR_NULL;
@@ -855,7 +855,7 @@ int bwd_run(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q
     if (!aligned_to(lse, 4)) return TB200_ERR_ALIGN;
     const size_t need = tb200_attention_bwd_workspace_bytes(d);
     if (!workspace || workspace_bytes < need || !aligned_to(workspace, 16)) return TB200_ERR_WORKSPACE;
-    if (d->head_dim != kD) return attention_simt_bwd(d, q, k, v, o, lse, dout, dq, dk, dv, stream);
+    if (!attention_tensor_geometry(d)) return attention_simt_bwd(d, q, k, v, o, lse, dout, dq, dk, dv, stream);
     DeviceInfo dev;
     int st = current_device(&dev);
     if (st) return st;
@@ -947,7 +947,7 @@ extern "C" int tb200_attention_bwd_tune(const tb200_attn_desc *d, const void *q,
     if (!d) return TB200_ERR_NULL;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     tb200_attn_desc trial = *d;
-    if (d->head_dim != kD) {
+    if (!attention_tensor_geometry(d)) {
         trial.deterministic = 1;
         const int st = tb200_attention_bwd(&trial, q, k, v, o, lse, dout, dq, dk, dv, workspace, workspace_bytes, stream_);
         return st ? st : 1;

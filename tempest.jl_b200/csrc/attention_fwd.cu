@@ -930,14 +930,14 @@ extern "C" int tb200_attention_fwd(const tb200_attn_desc *d, const void *q, cons
     if (d->heads % d->kv_heads != 0 || !(d->scale > 0.0f)) return TB200_ERR_SHAPE;
     if (d->causal && d->queries != d->keys) return TB200_ERR_SHAPE;
     if (d->dtype != TB200_BF16) return TB200_ERR_DTYPE;
-    if (d->head_dim != kHeadDim && !attention_simt_takes(d)) return TB200_ERR_UNSUPPORTED;
+    if (!attention_tensor_geometry(d) && !attention_simt_takes(d)) return TB200_ERR_UNSUPPORTED;
     if (d->batch == 0 || d->queries == 0) return TB200_OK;
     if (d->keys == 0) return TB200_ERR_UNSUPPORTED;
     if (!q || !k || !v || !o) return TB200_ERR_NULL;
     if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(o, 16) || !aligned_to(lse, 4))
         return TB200_ERR_ALIGN;
     if (d->queries > (1 << 24) || d->keys > (1 << 24)) return TB200_ERR_SHAPE;
-    if (d->head_dim != kHeadDim) return attention_simt_fwd(d, q, k, v, o, lse, stream);
+    if (!attention_tensor_geometry(d)) return attention_simt_fwd(d, q, k, v, o, lse, stream);
     return attention_tensor_fwd(d, nullptr, q, k, v, o, lse, stream);
 }
 

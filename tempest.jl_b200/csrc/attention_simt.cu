@@ -22,9 +22,12 @@ constexpr int kWarps = 4;
 
 struct SimtArgs {
     int batch, heads, kv_heads, queries, keys, d, causal;
+    int dv;                        // features of the values (v, o, dout, dv); d unless the descriptor says otherwise
     float scale;
-    long long qb, qs, qh;          // element strides of q, o, dq, dout over (batch, position, head)
-    long long kb, ks, kh;          // and of k, v, dk, dv
+    long long qb, qs, qh;          // element strides of q, dq over (batch, position, head)
+    long long kb, ks, kh;          // of k, dk
+    long long ob, os, oh;          // of o, dout
+    long long vb, vs, vh;          // of v, dv
     const int *doc_start;          // [batch][queries]: first key a query sees, or null
     const int *kv_len;             // [batch]: keys from this index on are masked, or null
 };
@@ -60,6 +63,7 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_fwd_kernel(const _
     if (i >= a.queries) return;
     const int g = h / (a.heads / a.kv_heads);
     const long long qrow = b * a.qb + i * a.qs + h * a.qh;
+    const long long orow = b * a.ob + i * a.os + h * a.oh;
     for (int d = lane; d < a.d; d += 32) qs[warp][d] = ldbf(q + qrow + d) * a.scale;
     __syncwarp();
     int first, last;
@@ -83,11 +87,11 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_fwd_kernel(const _
         const int count = min(32, last - key0 + 1);
         for (int jj = 0; jj < count; jj++) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const __nv_bfloat16 *vr = v + b * a.kb + (key0 + jj) * a.ks + g * a.kh;
+            const __nv_bfloat16 *vr = v + b * a.vb + (key0 + jj) * a.vs + g * a.vh;
 #pragma unroll
             for (int c = 0; c < kMaxD / 32; c++) {
                 const int d = lane + 32 * c;
-                if (d < a.d) acc[c] = fmaf(pj, ldbf(vr + d), acc[c]);
+                if (d < a.dv) acc[c] = fmaf(pj, ldbf(vr + d), acc[c]);
             }
         }
         m = m_new;
@@ -96,7 +100,7 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_fwd_kernel(const _
 #pragma unroll
     for (int c = 0; c < kMaxD / 32; c++) {
         const int d = lane + 32 * c;
-        if (d < a.d) o[qrow + d] = __float2bfloat16_rn(acc[c] * inv);
+        if (d < a.dv) o[orow + d] = __float2bfloat16_rn(acc[c] * inv);
     }
     if (lse && lane == 0) lse[(static_cast<long long>(b) * a.queries + i) * a.heads + h] = l > 0.0f ? m + __logf(l) : -INFINITY;
 }
@@ -111,12 +115,13 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dq_kernel(const __
     if (i >= a.queries) return;
     const int g = h / (a.heads / a.kv_heads);
     const long long qrow = b * a.qb + i * a.qs + h * a.qh;
+    const long long orow = b * a.ob + i * a.os + h * a.oh;
     float delta = 0.0f;
-    for (int d = lane; d < a.d; d += 32) {
-        qs[warp][d] = ldbf(q + qrow + d) * a.scale;
-        const float gd = ldbf(dout + qrow + d);
+    for (int d = lane; d < a.d; d += 32) qs[warp][d] = ldbf(q + qrow + d) * a.scale;
+    for (int d = lane; d < a.dv; d += 32) {
+        const float gd = ldbf(dout + orow + d);
         gs[warp][d] = gd;
-        delta = fmaf(gd, ldbf(o + qrow + d), delta);
+        delta = fmaf(gd, ldbf(o + orow + d), delta);
     }
     delta = warp_sum(delta);
     __syncwarp();
@@ -129,11 +134,10 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dq_kernel(const __
         float ds = 0.0f;
         if (j <= last) {
             const long long kv = b * a.kb + j * a.ks + g * a.kh;
+            const long long vv = b * a.vb + j * a.vs + g * a.vh;
             float s = 0.0f, dp = 0.0f;
-            for (int d = 0; d < a.d; d++) {
-                s = fmaf(qs[warp][d], ldbf(k + kv + d), s);
-                dp = fmaf(gs[warp][d], ldbf(v + kv + d), dp);
-            }
+            for (int d = 0; d < a.d; d++) s = fmaf(qs[warp][d], ldbf(k + kv + d), s);
+            for (int d = 0; d < a.dv; d++) dp = fmaf(gs[warp][d], ldbf(v + vv + d), dp);
             ds = __expf(s - L) * (dp - delta);
         }
         const int count = min(32, last - key0 + 1);
@@ -163,11 +167,10 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dkdv_kernel(const 
     const int j = blockIdx.x * kWarps + warp, g = blockIdx.y, b = blockIdx.z;
     if (j >= a.keys) return;
     const long long krow = b * a.kb + j * a.ks + g * a.kh;
+    const long long vrow = b * a.vb + j * a.vs + g * a.vh;
     const bool key_live = !a.kv_len || j < a.kv_len[b];
-    for (int d = lane; d < a.d; d += 32) {
-        ks[warp][d] = ldbf(k + krow + d) * a.scale;
-        vs[warp][d] = ldbf(v + krow + d);
-    }
+    for (int d = lane; d < a.d; d += 32) ks[warp][d] = ldbf(k + krow + d) * a.scale;
+    for (int d = lane; d < a.dv; d += 32) vs[warp][d] = ldbf(v + vrow + d);
     __syncwarp();
     const int rep = a.heads / a.kv_heads;
     float acck[kMaxD / 32] = {}, accv[kMaxD / 32] = {};
@@ -179,12 +182,13 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dkdv_kernel(const 
             if (key_live && i < a.queries && (!a.causal || i >= j) &&
                 (!a.doc_start || a.doc_start[static_cast<long long>(b) * a.queries + i] <= j)) {
                 const long long qr = b * a.qb + i * a.qs + h * a.qh;
+                const long long orr = b * a.ob + i * a.os + h * a.oh;
                 float s = 0.0f, dp = 0.0f, delta = 0.0f;
-                for (int d = 0; d < a.d; d++) {
-                    const float gd = ldbf(dout + qr + d);
-                    s = fmaf(ks[warp][d], ldbf(q + qr + d), s);
+                for (int d = 0; d < a.d; d++) s = fmaf(ks[warp][d], ldbf(q + qr + d), s);
+                for (int d = 0; d < a.dv; d++) {
+                    const float gd = ldbf(dout + orr + d);
                     dp = fmaf(gd, vs[warp][d], dp);
-                    delta = fmaf(gd, ldbf(o + qr + d), delta);
+                    delta = fmaf(gd, ldbf(o + orr + d), delta);
                 }
                 p = __expf(s - lse[(static_cast<long long>(b) * a.queries + i) * a.heads + h]);
                 ds = p * (dp - delta);
@@ -194,13 +198,12 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dkdv_kernel(const 
                 const float pi = __shfl_sync(0xffffffffu, p, ii), dsi = __shfl_sync(0xffffffffu, ds, ii);
                 if (pi == 0.0f && dsi == 0.0f) continue;   // masked (uniform across the warp)
                 const long long qr = b * a.qb + (i0 + ii) * a.qs + h * a.qh;
+                const long long orr = b * a.ob + (i0 + ii) * a.os + h * a.oh;
 #pragma unroll
                 for (int c = 0; c < kMaxD / 32; c++) {
                     const int d = lane + 32 * c;
-                    if (d < a.d) {
-                        accv[c] = fmaf(pi, ldbf(dout + qr + d), accv[c]);
-                        acck[c] = fmaf(dsi, ldbf(q + qr + d), acck[c]);
-                    }
+                    if (d < a.dv) accv[c] = fmaf(pi, ldbf(dout + orr + d), accv[c]);
+                    if (d < a.d) acck[c] = fmaf(dsi, ldbf(q + qr + d), acck[c]);
                 }
             }
         }
@@ -208,10 +211,8 @@ __global__ void __launch_bounds__(kWarps * 32) attention_simt_dkdv_kernel(const 
 #pragma unroll
     for (int c = 0; c < kMaxD / 32; c++) {
         const int d = lane + 32 * c;
-        if (d < a.d) {
-            dk[krow + d] = __float2bfloat16_rn(acck[c] * a.scale);
-            dv[krow + d] = __float2bfloat16_rn(accv[c]);
-        }
+        if (d < a.d) dk[krow + d] = __float2bfloat16_rn(acck[c] * a.scale);
+        if (d < a.dv) dv[vrow + d] = __float2bfloat16_rn(accv[c]);
     }
 }
 
@@ -219,14 +220,23 @@ SimtArgs simt_args(const tb200_attn_desc *d, const tb200_attn_mask *m) {
     SimtArgs a{};
     a.batch = d->batch; a.heads = d->heads; a.kv_heads = d->kv_heads; a.queries = d->queries; a.keys = d->keys;
     a.d = d->head_dim; a.causal = d->causal; a.scale = d->scale;
+    a.dv = attention_value_dim(d);
     // the dense default: [batch][position][head][feature]
     a.qh = d->head_dim; a.qs = a.qh * d->heads; a.qb = a.qs * d->queries;
     a.kh = d->head_dim; a.ks = a.kh * d->kv_heads; a.kb = a.ks * d->keys;
+    a.oh = a.dv; a.os = a.oh * d->heads; a.ob = a.os * d->queries;
+    a.vh = a.dv; a.vs = a.vh * d->kv_heads; a.vb = a.vs * d->keys;
     if (m) {
         a.doc_start = m->doc_start;
         a.kv_len = m->kv_len;
-        if (m->q_stride[0] || m->q_stride[1] || m->q_stride[2]) { a.qb = m->q_stride[0]; a.qs = m->q_stride[1]; a.qh = m->q_stride[2]; }
-        if (m->kv_stride[0] || m->kv_stride[1] || m->kv_stride[2]) { a.kb = m->kv_stride[0]; a.ks = m->kv_stride[1]; a.kh = m->kv_stride[2]; }
+        // other strides: the same for the arrays of either kind (refused before this where the values have features
+        // of their own)
+        if (m->q_stride[0] || m->q_stride[1] || m->q_stride[2]) {
+            a.qb = a.ob = m->q_stride[0]; a.qs = a.os = m->q_stride[1]; a.qh = a.oh = m->q_stride[2];
+        }
+        if (m->kv_stride[0] || m->kv_stride[1] || m->kv_stride[2]) {
+            a.kb = a.vb = m->kv_stride[0]; a.ks = a.vs = m->kv_stride[1]; a.kh = a.vh = m->kv_stride[2];
+        }
     }
     return a;
 }
@@ -234,7 +244,8 @@ SimtArgs simt_args(const tb200_attn_desc *d, const tb200_attn_mask *m) {
 }  // namespace
 
 bool attention_simt_takes(const tb200_attn_desc *d) {
-    return d->head_dim <= kMaxD && d->heads <= 65535 && d->batch <= 65535;
+    return d->head_dim <= kMaxD && attention_value_dim(d) <= kMaxD && d->value_dim >= 0 && d->heads <= 65535 &&
+           d->batch <= 65535;
 }
 
 int attention_simt_fwd(const tb200_attn_desc *d, const void *q, const void *k, const void *v, void *o, float *lse,
@@ -278,17 +289,25 @@ int check_masked(const tb200_attn_desc *d) {
     if (!attention_simt_takes(d)) return TB200_ERR_UNSUPPORTED;
     return TB200_OK;
 }
+// values with features of their own come as dense arrays
+bool strided_values(const tb200_attn_desc *d, const tb200_attn_mask *m) {
+    if (!m || attention_value_dim(d) == d->head_dim) return false;
+    for (int i = 0; i < 3; i++)
+        if (m->q_stride[i] || m->kv_stride[i]) return true;
+    return false;
+}
 }  // namespace
 
 extern "C" int tb200_attention_fwd_masked(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q, const void *k,
                                           const void *v, void *o, float *lse, void *stream) {
     int st = check_masked(d);
     if (st) return st;
+    if (strided_values(d, mask)) return TB200_ERR_UNSUPPORTED;
     if (d->batch == 0 || d->queries == 0) return TB200_OK;
     if (d->keys == 0) return TB200_ERR_UNSUPPORTED;
     if (!q || !k || !v || !o) return TB200_ERR_NULL;
     // 128 features, 16-byte aligned arrays, strides the TMA unit can describe: the tensor-core kernel
-    if (d->head_dim == 128 && d->dtype == TB200_BF16 && aligned_to(q, 16) && aligned_to(k, 16) && aligned_to(v, 16) &&
+    if (attention_tensor_geometry(d) && d->dtype == TB200_BF16 && aligned_to(q, 16) && aligned_to(k, 16) && aligned_to(v, 16) &&
         aligned_to(o, 16) && d->queries <= (1 << 24) && d->keys <= (1 << 24)) {
         st = attention_tensor_fwd(d, mask, q, k, v, o, lse, static_cast<cudaStream_t>(stream));
         if (st != TB200_ERR_UNSUPPORTED) return st;
@@ -301,6 +320,7 @@ extern "C" int tb200_attention_bwd_masked(const tb200_attn_desc *d, const tb200_
                                           void *dv, void *stream) {
     int st = check_masked(d);
     if (st) return st;
+    if (strided_values(d, mask)) return TB200_ERR_UNSUPPORTED;
     if (d->batch == 0 || (d->queries == 0 && d->keys == 0)) return TB200_OK;
     if (d->queries == 0 || d->keys == 0) return TB200_ERR_UNSUPPORTED;
     if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv) return TB200_ERR_NULL;

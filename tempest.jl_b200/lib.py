@@ -41,7 +41,7 @@ class AttnDesc(ctypes.Structure):
     _fields_ = [("batch", ctypes.c_int), ("heads", ctypes.c_int), ("kv_heads", ctypes.c_int),
                 ("queries", ctypes.c_int), ("keys", ctypes.c_int), ("head_dim", ctypes.c_int),
                 ("causal", ctypes.c_int), ("scale", ctypes.c_float), ("dtype", ctypes.c_int),
-                ("deterministic", ctypes.c_int)]
+                ("deterministic", ctypes.c_int), ("value_dim", ctypes.c_int)]
 
 
 class AttnMask(ctypes.Structure):
@@ -446,9 +446,10 @@ def layernorm_bwd_noalloc(x, gamma, dy, mean, rstd, dx, dgamma, dbeta, eps, n, r
 
 
 def attn_desc(batch, heads, queries, keys, head_dim, causal, scale=None, kv_heads=None, dtype=BF16,
-              deterministic=False):
+              deterministic=False, value_dim=0):
     d = AttnDesc()
     d.deterministic = int(deterministic)
+    d.value_dim = int(value_dim)
     d.batch, d.heads, d.kv_heads = batch, heads, kv_heads or heads
     d.queries, d.keys, d.head_dim = queries, keys, head_dim
     d.causal = int(causal)

@@ -290,6 +290,43 @@ def test_masked_pullback_on_the_tensor_cores(pkg, cuda, oracle, deterministic):
     assert e.value.status == -7
 
 
+@pytest.mark.parametrize("dqk,dv", [(24, 16), (16, 24), (128, 64), (192, 128)])
+def test_values_with_features_of_their_own(pkg, cuda, oracle, dqk, dv):
+    """Values with other features than the queries and keys, as multi-head latent attention's (the reference's
+    test/cuda/attention.jl:150-177: (24, 16) and (16, 24), 2 heads, 70 positions, 2 sequences, causal; here also
+    128-feature keys with 64-feature values, and 192 with 128): forward and pullback, each gradient over its own
+    features, against the Float64 yardstick; grouped heads in the last case."""
+    torch, L = cuda, pkg.lib
+    B, S, H = 2, 70, 2
+    Hkv = 1 if dqk == 192 else H
+    q = oracle.to_bf16(0.5 * oracle.normal((B, S, H, dqk), 121))
+    k = oracle.to_bf16(0.5 * oracle.normal((B, S, Hkv, dqk), 122))
+    v = oracle.to_bf16(oracle.normal((B, S, Hkv, dv), 123))
+    g = oracle.to_bf16(oracle.normal((B, S, H, dv), 124))
+    qd, kd, vd, gd = (dev(torch, a) for a in (q, k, v, g))
+    desc = L.attn_desc(B, H, S, S, dqk, True, scale=0.25, kv_heads=Hkv, value_dim=dv)
+    o, lse = torch.full((B, S, H, dv), float("nan"), device="cuda", dtype=torch.bfloat16), torch.full((B, S, H), float("nan"), device="cuda")
+    L.attention_fwd(desc, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr())
+    need = L.attention_bwd_workspace_bytes(desc)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    dq, dk, dvv = torch.full_like(qd, float("nan")), torch.full_like(kd, float("nan")), torch.full_like(vd, float("nan"))
+    L.attention_bwd(desc, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr(), gd.data_ptr(),
+                    dq.data_ptr(), dk.data_ptr(), dvv.data_ptr(), ws.data_ptr(), need)
+    torch.cuda.synchronize()
+    o64, lse64, dq64, dk64, dv64 = oracle.attention_f64(q, k, v, True, scale=0.25, dout=g)
+    assert o64.shape == (B, S, H, dv) and dv64.shape == (B, S, Hkv, dv)
+    assert np.abs(oracle.from_bf16(host(torch, o)) - o64).max() <= ATOL_BF16
+    assert np.abs(lse.cpu().numpy() - lse64).max() <= 2e-5 * max(1.0, np.abs(lse64).max())
+    close_grad(oracle, host(torch, dq), dq64, "dq")
+    close_grad(oracle, host(torch, dk), dk64, "dk")
+    close_grad(oracle, host(torch, dvv), dv64, "dv")
+    # the masked entries take them as dense arrays only
+    with pytest.raises(L.TB200Error) as e:
+        L.attention_fwd_masked(desc, L.attn_mask(kv_stride=(Hkv * S * dqk, dqk, S * dqk)), qd.data_ptr(), kd.data_ptr(),
+                               vd.data_ptr(), o.data_ptr(), lse.data_ptr())
+    assert e.value.status == -7
+
+
 def test_masked_entries_refuse_bad_requests(pkg, cuda):
     L, torch = pkg.lib, cuda
     x = torch.zeros(4096, device="cuda", dtype=torch.bfloat16)
