@@ -25,6 +25,7 @@ from typing import Any, Callable, Dict, Optional, Tuple
 from . import lib
 
 ELTYPES = {"Float32": (lib.F32, 4), "BFloat16": (lib.BF16, 2)}
+_BYTES = {"Float32": 4, "BFloat16": 2, "Int32": 4}   # of every element type an array of a binding may have (masks: Int32)
 
 
 def _torch_stream():
@@ -58,7 +59,7 @@ class Strided:
 
     def pointer(self) -> int:
         base = self.buffer if isinstance(self.buffer, int) else self.buffer.data_ptr()
-        return base + self.offset * ELTYPES[self.eltype][1]
+        return base + self.offset * _BYTES[self.eltype]
 
 
 @dataclass
@@ -155,6 +156,22 @@ ATTENTION_TEMPLATES = tuple(
              {"q": ("d", "h", "m", "b"), "k": ("d", "hk", "n", "b"), "v": ("d", "hk", "n", "b")},
              ("o", "lse") if stats else ("o",))
     for stats in (False, True) for causal in (False, True))
+# With masks the device holds (test/cuda/attention.jl:217-275): `start` (m, b) Int32, the first key each query sees
+# (0-based) under the causal mask -- packed documents; `lengths` (b,) Int32, keys at and beyond a sequence's length
+# hidden -- decode over a cache.
+_MASK_INPUTS = {"documents": {"start": ("m", "b")}, "lengths": {"lengths": ("b",)}}
+ATTENTION_MASKED = tuple(
+    Template(f"attention_{kind}{'_lse' if stats else ''}",
+             f"(q, k, v, {list(extra)[0]}) -> attention with the mask read from the device" + (".o" if not stats else ""),
+             {"q": ("d", "h", "m", "b"), "k": ("d", "hk", "n", "b"), "v": ("d", "hk", "n", "b"), **extra},
+             ("o", "lse") if stats else ("o",))
+    for kind, extra in (("causal_documents", _MASK_INPUTS["documents"]), ("lengths", _MASK_INPUTS["lengths"]))
+    for stats in (False, True)) + tuple(
+    Template(f"attention_{kind}_pullback", "(q, k, v, mask, o, lse, g) -> the tape's derivative by q, k and v",
+             {"q": ("d", "h", "m", "b"), "k": ("d", "hk", "n", "b"), "v": ("d", "hk", "n", "b"), **extra,
+              "o": ("d", "h", "m", "b"), "lse": ("one", "h", "m", "b"), "g": ("d", "h", "m", "b")},
+             ("dq", "dk", "dv"))
+    for kind, extra in (("causal_documents", _MASK_INPUTS["documents"]), ("lengths", _MASK_INPUTS["lengths"])))
 ATTENTION_PULLBACKS = tuple(
     Template(f"attention{'_causal' if causal else ''}_pullback",
              "(q, k, v, o, lse, g) -> the tape's derivative of attention by q, k and v",
@@ -369,6 +386,21 @@ class AttentionLaunch:
     def __call__(self):
         a = self.binding.arrays
         stream = current_stream()
+        if "start" in a or "lengths" in a:
+            mask = lib.attn_mask(doc_start=a["start"].pointer() if "start" in a else 0,
+                                 kv_len=a["lengths"].pointer() if "lengths" in a else 0)
+            if not self.binding.template.endswith("_pullback"):
+                lib.attention_fwd_masked(self.desc, mask, a["q"].pointer(), a["k"].pointer(), a["v"].pointer(),
+                                         a["o"].pointer(), a["lse"].pointer() if "lse" in a else 0, stream)
+                return
+            operands = (a["q"].pointer(), a["k"].pointer(), a["v"].pointer(), a["o"].pointer(), a["lse"].pointer(),
+                        a["g"].pointer(), a["dq"].pointer(), a["dk"].pointer(), a["dv"].pointer())
+            if self.workspace is not None:   # 128 features: the tensor-core kernels, which want scratch
+                lib.attention_bwd_masked_ws(self.desc, mask, *operands, self.workspace.data_ptr(), self.workspace_bytes,
+                                            stream)
+            else:
+                lib.attention_bwd_masked(self.desc, mask, *operands, stream)
+            return
         if self.binding.template.endswith("_pullback"):
             lib.attention_bwd(self.desc, a["q"].pointer(), a["k"].pointer(), a["v"].pointer(), a["o"].pointer(),
                               a["lse"].pointer(), a["g"].pointer(), a["dq"].pointer(), a["dk"].pointer(),
@@ -478,7 +510,7 @@ class B200Kernels:
     def templates(self, target: Target):
         # the row kernels and attention fold each statistic in one pass, which a target that
         # forbids the online rewrites does not permit (ext/cuDNNExt.jl:60-62); products always apply
-        online = ROW_TEMPLATES + ATTENTION_TEMPLATES + ATTENTION_PULLBACKS if target.online else ()
+        online = ROW_TEMPLATES + ATTENTION_TEMPLATES + ATTENTION_PULLBACKS + ATTENTION_MASKED if target.online else ()
         return LINEAR_TEMPLATES + SCAN_TEMPLATES + online
 
     def resources(self, target: Target) -> Resources:
@@ -502,8 +534,13 @@ class B200Kernels:
                 return False   # as cuDNNAttention declines what its engines do not take (ext/cuDNNExt.jl:90-109)
             if "causal" in b.template and e.get("m") != e.get("n"):
                 return False
+            masked = "documents" in b.template or "lengths" in b.template
+            if masked and ("start" in b.arrays) != ("documents" in b.template):
+                return False
+            if masked and ("lengths" in b.arrays) != ("_lengths" in b.template):
+                return False
             for name, s in b.arrays.items():
-                want = "Float32" if name == "lse" else "BFloat16"
+                want = "Float32" if name == "lse" else "Int32" if name in ("start", "lengths") else "BFloat16"
                 if s.eltype != want or not _dense(s):
                     return False
             return True
@@ -596,6 +633,17 @@ class B200Kernels:
         if b.template.startswith("attention"):
             launch = AttentionLaunch(b)
             form = ""
+            if "documents" in b.template or "lengths" in b.template:
+                e = b.extents
+                if b.template.endswith("_pullback") and e["d"] == 128:
+                    # the tensor-core pullback: repeatable bits when the target asks, else the one-kernel form
+                    launch.desc.deterministic = int(bool(target.deterministic))
+                    need = lib.attention_bwd_masked_workspace_bytes(launch.desc)
+                    resources = resources if resources is not None else Resources()
+                    launch.workspace, launch.workspace_bytes = resources.workspace(need), need
+                what = "the starts of packed documents" if "documents" in b.template else "lengths"
+                return launch, (f"B200 {b.template}, {what} read on the device, {e['h']} heads over {e['hk']} of "
+                                f"{e['d']} features, {e['m']} queries by {e['n']} keys, batch {e['b']}")
             if b.template.endswith("_pullback"):
                 # a target that wants repeatable bits gets the two-kernel form; any other gets whichever of the two
                 # forms measures faster on these operands (the measured stage of the cover's search over variants)

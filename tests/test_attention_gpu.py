@@ -327,6 +327,54 @@ def test_values_with_features_of_their_own(pkg, cuda, oracle, dqk, dv):
     assert e.value.status == -7
 
 
+def test_masked_attention_through_the_plugin_mirror(pkg, cuda, oracle):
+    """Binding -> supports -> build -> launch for packed documents, forward with its log-sum-exp and the pullback
+    (tensor cores at 128 features, scratch from the executable's resources), and a decode-like forward with lengths."""
+    torch, I = cuda, pkg.implement
+    lib, target = I.B200Kernels(), I.Target()
+    D, H, S, B = 128, 2, 300, 2
+    q, k, v, g = (oracle.to_bf16(oracle.normal((B, S, H, D), 131 + i)) for i in range(4))
+    qd, kd, vd, gd = (dev(torch, a) for a in (q, k, v, g))
+    start = np.stack([doc_starts([90, 1, 130, 40, 39]), doc_starts([7, 200, 93])])
+    sd = torch.from_numpy(start).cuda()
+    o, lse = torch.empty_like(qd), torch.empty(B, S, H, device="cuda")
+    dq, dk, dv = (torch.empty_like(qd) for _ in range(3))
+    e = {"d": D, "h": H, "hk": H, "m": S, "n": S, "b": B, "one": 1}
+    heads = lambda t, val: I.dense_heads(t, "BFloat16", D, H, S, B, val)  # noqa: E731
+    arrays = {"q": heads(qd, 1), "k": heads(kd, 2), "v": heads(vd, 3), "o": heads(o, 4),
+              "lse": I.Strided("Float32", 0, (1, H, S, B), (1, 1, H, H * S), lse, 5),
+              "start": I.Strided("Int32", 0, (S, B), (1, S), sd, 6)}
+    fwd = I.Binding("attention_causal_documents_lse", e, arrays)
+    assert lib.supports(target, fwd)
+    launch, note = lib.build(target, fwd)
+    assert "packed documents" in note
+    launch()
+    res = I.Resources()
+    bwd = I.Binding("attention_causal_documents_pullback", e, dict(arrays, g=heads(gd, 7), dq=heads(dq, 8), dk=heads(dk, 9),
+                                                                  dv=heads(dv, 10)))
+    assert lib.supports(target, bwd)
+    launch, _ = lib.build(target, bwd, res)
+    assert launch.workspace is not None and res.bytes >= pkg.lib.attention_bwd_masked_workspace_bytes(launch.desc)
+    launch()
+    torch.cuda.synchronize()
+    assert pkg.lib.attention_device_error() == 0 and pkg.lib.attention_bwd_device_error() == 0
+    o64, lse64, dq64, dk64, dv64 = oracle.attention_f64(q, k, v, True, dout=g, doc_start=start)
+    assert np.abs(oracle.from_bf16(host(torch, o)) - o64).max() <= ATOL_BF16
+    assert np.abs(lse.cpu().numpy() - lse64).max() <= 2e-5 * max(1.0, np.abs(lse64).max())
+    close_grad(oracle, host(torch, dq), dq64, "dq")
+    close_grad(oracle, host(torch, dk), dk64, "dk")
+    close_grad(oracle, host(torch, dv), dv64, "dv")
+    lengths = torch.tensor([17, 300], dtype=torch.int32, device="cuda")
+    dec = I.Binding("attention_lengths", e, {"q": heads(qd, 1), "k": heads(kd, 2), "v": heads(vd, 3), "o": heads(o, 4),
+                                             "lengths": I.dense_vector(lengths, "Int32", B, 11)})
+    assert lib.supports(target, dec)
+    launch, _ = lib.build(target, dec)
+    launch()
+    torch.cuda.synchronize()
+    o64, _ = oracle.attention_f64(q, k, v, False, kv_len=np.array([17, 300]))
+    assert np.abs(oracle.from_bf16(host(torch, o)) - o64).max() <= ATOL_BF16
+
+
 def test_masked_entries_refuse_bad_requests(pkg, cuda):
     L, torch = pkg.lib, cuda
     x = torch.zeros(4096, device="cuda", dtype=torch.bfloat16)

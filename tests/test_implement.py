@@ -191,3 +191,24 @@ def test_tuning_record_keeps_and_reads_back(pkg, tmp_path, monkeypatch):
     assert again.lookup("product", "cut short") is None and again.written == 0
     other = T.TuningRecord("NVIDIA H100")                           # another device: another file
     assert other.lookup("product", key) is None
+
+
+def test_masked_attention_templates(I):
+    """Attention whose mask the device holds, as the reference's packed-documents and decode programs
+    (test/cuda/attention.jl:217-275): offered on a target that allows one-pass folds, the mask array Int32 and dense."""
+    lib, t = I.B200Kernels(), I.Target()
+    names = [x.name for x in lib.templates(t)]
+    for want in ("attention_causal_documents", "attention_causal_documents_lse", "attention_lengths_lse",
+                 "attention_causal_documents_pullback", "attention_lengths_pullback"):
+        assert want in names
+    D, H, S, B = 128, 2, 300, 2
+    heads = lambda v: I.dense_heads(None, "BFloat16", D, H, S, B, v)  # noqa: E731
+    e = {"d": D, "h": H, "hk": H, "m": S, "n": S, "b": B, "one": 1}
+    arrays = {"q": heads(1), "k": heads(2), "v": heads(3), "o": heads(4),
+              "start": I.Strided("Int32", 0, (S, B), (1, S), None, 5)}
+    assert lib.supports(t, I.Binding("attention_causal_documents", e, arrays))
+    assert not lib.supports(t, I.Binding("attention_causal_documents", e, {k: v for k, v in arrays.items() if k != "start"}))
+    assert not lib.supports(t, I.Binding("attention_causal_documents", e, dict(arrays, start=I.Strided("Float32", 0, (S, B), (1, S), None, 5))))
+    assert not lib.supports(t, I.Binding("attention_lengths", e, arrays))       # the other mask's array
+    lengths = dict({k: v for k, v in arrays.items() if k != "start"}, lengths=I.dense_vector(None, "Int32", B, 6))
+    assert lib.supports(t, I.Binding("attention_lengths", e, lengths))
