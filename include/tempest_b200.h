@@ -191,7 +191,7 @@ typedef struct tb200_gemm_desc {
                                     tiles only */
     int force_simt;              /* 1 = the generic kernel (Float32-exact, any alignment) */
     int direct_epilogue;         /* 1 = each thread stores its own output row instead of staging
-                                    tiles through shared memory for TMA stores (a tuner variant) */
+                                    tiles in shared memory and writing whole lines (a tuner variant) */
     /* A batch of alike products in one launch, as cublasGemmStridedBatchedEx takes them
      * (ext/cuBLASExt.jl:247-259): member i reads a + i * stride_a, b + i * stride_b and writes
      * c + i * stride_c (elements).  batch 0 or 1 = one product.  A zero stride of an operand that is

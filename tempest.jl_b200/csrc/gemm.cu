@@ -49,7 +49,7 @@ struct GemmArgs {
     CUtensorMap tmap_a;
     CUtensorMap tmap_b;
     CUtensorMap tmap_aux;
-    int tma_epilogue;     // results leave through the staging buffers in whole lines (aux arrives by TMA)
+    int staged_epilogue;     // results leave through the staging buffers in whole lines (aux arrives by TMA)
     void *c;
     const void *bias;
     const void *aux;
@@ -493,7 +493,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
         fence_barrier_init();
         prefetch_tensormap(&p.tmap_a);
         prefetch_tensormap(&p.tmap_b);
-        if (p.tma_epilogue && epilogue_reads_aux(EPI)) prefetch_tensormap(&p.tmap_aux);
+        if (p.staged_epilogue && epilogue_reads_aux(EPI)) prefetch_tensormap(&p.tmap_aux);
     }
     if (warp == 1) {
         // each CTA of a pair allocates its own tensor memory: all of it, so both get the same (first) column
@@ -677,7 +677,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             const uint32_t acc_phase = (it >> 1) & 1;
             // the tile's bias, eight columns a lane, fetched while the accumulator is still being summed
             uint4 bias_q = make_uint4(0u, 0u, 0u, 0u);
-            if (epilogue_reads_bias(EPI) && p.tma_epilogue && lane < BN / 8) {
+            if (epilogue_reads_bias(EPI) && p.staged_epilogue && lane < BN / 8) {
                 const int col = w.tn * BN + lane * 8;
                 const uint16_t *bp = static_cast<const uint16_t *>(p.bias) + w.member * p.stride_bias + col;
                 if (col + 8 <= p.n && aligned_dev(bp, 16)) {
@@ -691,7 +691,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05(const __grid_con
             }
             if (!wait_or_fail(&tmem_full_bar[acc], acc_phase, failed, 4, wait_ns)) break;
             tcgen05_fence_after();
-            if (p.tma_epilogue) {
+            if (p.staged_epilogue) {
                 const int row0 = w.tm * ROWS + static_cast<int>(rank) * BM + q * 32;
                 const uint32_t tmem_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
                 bool ok = true;
@@ -1165,7 +1165,7 @@ int prepare(tb200_gemm_plan *plan) {
             p.c = d->workspace; p.ldc = ldp; p.stride_c = d->m * ldp;
             p.alpha = 1.0f; p.epilogue = TB200_EPI_NONE;
             kernel_epilogue = TB200_EPI_NONE; kernel_out = TB200_F32;
-            p.tma_epilogue = !d->direct_epilogue && aligned_to(d->workspace, 16);
+            p.staged_epilogue = !d->direct_epilogue && aligned_to(d->workspace, 16);
             MergeArgs &q = plan->merge_args;
             q = MergeArgs{};
             q.partial = static_cast<const float *>(d->workspace); q.c = c; q.bias = bias; q.aux = aux; q.aux_out = aux_out;
@@ -1183,26 +1183,26 @@ int prepare(tb200_gemm_plan *plan) {
             p.stride_c = batched ? d->stride_c : 0; p.stride_bias = batched ? d->stride_bias : 0;
             p.stride_aux = batched ? d->stride_aux : 0; p.stride_aux_out = batched ? d->stride_aux_out : 0;
             p.alpha = d->alpha; p.epilogue = d->epilogue;
-            // the epilogue goes through shared memory and TMA when every array it touches can be
-            // described to the TMA unit; otherwise each thread stores its own row
+            // the epilogue goes through the staging buffers (whole 128-byte lines out, the operand it reads in by TMA)
+            // when every array it touches allows 16-byte accesses; otherwise each thread stores its own row
             const size_t aux_size = (d->epilogue == TB200_EPI_AXPY) ? out_size : 2;
             const int aux_dtype = d->epilogue == TB200_EPI_AXPY ? d->out_dtype : d->in_dtype;
             const auto pitch_ok = [&](int64_t stride, size_t es) { return !batched || (stride * es) % 16 == 0; };
-            bool tma_epi = !d->direct_epilogue && aligned_to(c, 16) && (d->ldc * out_size) % 16 == 0 &&
+            bool staged = !d->direct_epilogue && aligned_to(c, 16) && (d->ldc * out_size) % 16 == 0 &&
                            pitch_ok(d->stride_c, out_size);
             if (needs_aux)
-                tma_epi = tma_epi && aux_size == out_size && aligned_to(aux, 16) && (d->ld_aux * aux_size) % 16 == 0 &&
+                staged = staged && aux_size == out_size && aligned_to(aux, 16) && (d->ld_aux * aux_size) % 16 == 0 &&
                           pitch_ok(d->stride_aux, aux_size);
             if (aux_out)
-                tma_epi = tma_epi && d->out_dtype != TB200_F32 && aligned_to(aux_out, 16) && (d->ld_aux_out * 2) % 16 == 0 &&
+                staged = staged && d->out_dtype != TB200_F32 && aligned_to(aux_out, 16) && (d->ld_aux_out * 2) % 16 == 0 &&
                           pitch_ok(d->stride_aux_out, 2);
-            if (tma_epi) {
+            if (staged) {
                 if (needs_aux && (st = make_tmap(&p.tmap_aux, aux, d->n, d->m, d->ld_aux, 32, aux_dtype,
                                                  d->stride_aux ? batch : 1, d->stride_aux)))
                     return st;
-                if (needs_aux && batched && d->stride_aux == 0) tma_epi = false;   // a shared aux: plain loads
+                if (needs_aux && batched && d->stride_aux == 0) staged = false;   // a shared aux: plain loads
             }
-            p.tma_epilogue = tma_epi;
+            p.staged_epilogue = staged;
         }
         if ((st = kernel_by_shape(bn, pair, kernel_out, kernel_epilogue, dev, &plan->kernel))) return st;
         const size_t stage_bytes = static_cast<size_t>(BM + (pair ? bn / 2 : bn)) * BK * 2;
@@ -1347,7 +1347,7 @@ extern "C" int tb200_gemm_plan_repoint(tb200_gemm_plan *plan, int operand, const
     // a new address must leave the plan on the kernels it was built for (the reference requires the
     // alignment compiled for, src/Compiler/Implement/Implement.jl:162-175)
     if (next.tensor != plan->tensor || (next.tensor && (next.kernel != plan->kernel ||
-                                                         next.args.tma_epilogue != plan->args.tma_epilogue)))
+                                                         next.args.staged_epilogue != plan->args.staged_epilogue)))
         return TB200_ERR_ALIGN;
     *plan = next;
     return TB200_OK;
