@@ -2,7 +2,7 @@
 //
 // Default (`deterministic = false`, src/Compiler/runtime/target.jl:31): ONE kernel over key tiles that keeps dK and
 // dV in tensor memory, forms each step's dQ contribution as a product of its own and adds it into a Float32
-// workspace with red.global.add (ext/cuTileExt/transpose.jl:165-187, `added_folds` / `add_step!`), and a small
+// workspace by TMA reductions, additions done in L2 (ext/cuTileExt/transpose.jl:165-187, `added_folds` / `add_step!`), and a small
 // kernel that rounds the workspace to BFloat16 (`late_kernel`, :201-213).  Five products per step, the algorithmic
 // count; the order in which key tiles add into a dQ row is whatever the hardware makes it, so dQ repeats to
 // Float32 rounding, not bit for bit.
@@ -40,9 +40,12 @@
 // threads already hold, is also written to shared memory as [key][query] lines, and dQ' (features x queries) =
 // K' (features x keys, the item's K tile read as an MN-major A operand) * dS' lands in the dP columns once the
 // step's dK and dV products have read P and dS from them (MMAs of a CTA run in issue order).  The row threads
-// read it back at the start of the next step -- lanes are now features, so one warp instruction adds 32
-// consecutive features of one query: a 128-byte line -- and only then is the next dP issued into those columns;
-// their adds run under that product.  Per step the tensor pipe runs  S(t+1) | dK(t) dV(t) dQ(t) | dP(t+1).
+// read it back at the start of the next step -- lanes are now features -- and only then is the next dP issued into
+// those columns.  A warp lays its 32 features of 16 queries side by side in its own 4 KB of the dS' buffer and one
+// lane hands them to the TMA unit as a reduction into the Float32 workspace (cp.reduce.async.bulk.tensor ... add);
+// the additions run in L2 under the step's products.  Per step the tensor pipe runs  S(t+1) | dK(t) dV(t) dQ(t) | dP(t+1).
+// With masks the device holds (a length per sequence, the starts of packed documents per query) a hidden key gets a
+// score of -Inf like one the causal mask hides; key tiles beyond the length have no steps.
 // No load uses cluster multicast.  Every barrier wait is bounded.
 #include <cuda.h>
 

@@ -667,7 +667,7 @@ class B200Kernels:
                         launch.workspace.data_ptr(), need, current_stream())
                     if key:
                         self.record.keep("attention_pullback", key, {"deterministic": launch.desc.deterministic})
-                form = ", two kernels (deterministic)" if launch.desc.deterministic else ", one kernel (dq by atomic adds)"
+                form = ", two kernels (deterministic)" if launch.desc.deterministic else ", one kernel (dq added in L2)"
             e = b.extents
             return launch, (f"B200 {b.template}, {e['h']} heads over {e['hk']} of {e['d']} features, "
                             f"{e['m']} queries by {e['n']} keys, batch {e['b']}{form}")
