@@ -640,7 +640,29 @@ def run_also(torch, dist, pkg, world, rank, only=None):
                         "adds dq into a Float32 workspace (memset + rounding kernel included in its time), the "
                         "deterministic two-kernel form executes 7",
             "device_error": L.attention_device_error() + L.attention_bwd_device_error()}
-        del q, k, v, g, o, dq, dk, dv, ws
+        # the same arrays as four packed documents of 1024 positions a sequence, the starts held on the device
+        # (the reference's packed-documents program, test/cuda/attention.jl:217-246): forward and pullback on the
+        # tensor cores; work counted over the visible (query, key) pairs
+        docs = torch.arange(Sq, device="cuda", dtype=torch.int32) // 1024 * 1024
+        starts = docs.repeat(Bq, 1).contiguous()
+        mask = L.attn_mask(doc_start=starts.data_ptr())
+        desc.deterministic = 0
+        mneed = L.attention_bwd_masked_workspace_bytes(desc)
+        mws = torch.empty(mneed, dtype=torch.uint8, device="cuda")
+        mf = clock(lambda: L.attention_fwd_masked(desc, mask, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                                  lse.data_ptr(), stream), 5)
+        mb = clock(lambda: L.attention_bwd_masked_ws(desc, mask, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                                     lse.data_ptr(), g.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                                     dv.data_ptr(), mws.data_ptr(), mneed, stream), 5)
+        visible = 4.0 * Bq * Hq * Dq * 4 * (1024 * 1025 / 2)
+        out["attention_packed_documents_B8_H32_S4096_D128"] = {
+            "documents": "4 x 1024 positions a sequence, starts on the device",
+            "fwd_ms": round(mf, 4), "fwd_TFLOP/s_of_visible_pairs": round(visible / mf / 1e9, 1),
+            "bwd_ms": round(mb, 4), "bwd_TFLOP/s_of_visible_pairs": round(2.5 * visible / mb / 1e9, 1),
+            "note": "forward: the one-tile tensor-core kernel, key tiles before a document's start skipped; pullback: the "
+                    "one-kernel form, each tile's steps cut to the chunks that can see it",
+            "device_error": L.attention_device_error() + L.attention_bwd_device_error()}
+        del q, k, v, g, o, dq, dk, dv, ws, mws, starts
         # BASELINE.json configs[4]: chunked gated DeltaNet forward, B*H = 64 sequences of 8192, dk = dv = 128
         Hn, T = 64, 8192
         qd = torch.nn.functional.normalize(torch.randn(Hn, T, 128, device="cuda"), dim=-1).bfloat16()
@@ -702,6 +724,28 @@ def run_also(torch, dist, pkg, world, rank, only=None):
         out["compiled_bias_gradient_bf16_4096x65536"] = {"ms": round(gms, 4), "algorithmic_GB/s": round(cb / gms / 1e6, 1),
                                                          "frac_of_measured_hbm_peak": round(cb / gms / 1e6 / hbm, 4)}
         del xg, yg, xb, yb, cws2
+        # scans and a recurrence whose step is a map, 16384 rows of 4096 Float32 (268 MB an array)
+        sn, srows = 4096, 16384
+        sx = torch.randn(srows, sn, device="cuda")
+        sy = torch.empty_like(sx)
+        sneed = L.scan_workspace_bytes(L.scan_desc(sn, srows, L.SCAN_SUM, across=True))
+        sws = torch.empty(max(sneed, 16), dtype=torch.uint8, device="cuda")
+        along = clock(lambda: L.scan(sx.data_ptr(), sy.data_ptr(), sn, srows, L.SCAN_SUM, stream=stream), 5)
+        across = clock(lambda: L.scan(sx.data_ptr(), sy.data_ptr(), sn, srows, L.SCAN_SUM, across=True,
+                                      workspace=sws.data_ptr(), workspace_bytes=sneed, stream=stream), 5)
+        cell = pkg.groups.gated_tanh_cell(1 << 20, 64)
+        ca, ch = torch.full((1 << 20,), 0.7, device="cuda"), torch.zeros(1 << 20, device="cuda")
+        cl = torch.empty_like(ch)
+        cdesc = cell.desc()
+        rec = clock(lambda: L.recurrence_compiled(cdesc, [sx.data_ptr(), ca.data_ptr(), ch.data_ptr()],
+                                                  [sy.data_ptr(), cl.data_ptr()], stream), 5)
+        sb = 2.0 * sx.numel() * 4
+        out["scans_f32_16384x4096"] = {
+            "cumsum_along_rows_GB/s": round(sb / along / 1e6, 1), "cumsum_across_rows_in_slabs_GB/s": round(sb / across / 1e6, 1),
+            "map_recurrence_tanh_cell_2^20x64_GB/s": round(cell.bytes() / rec / 1e6, 1),
+            "frac_of_measured_hbm_peak": [round(sb / along / 1e6 / hbm, 4), round(sb / across / 1e6 / hbm, 4),
+                                          round(cell.bytes() / rec / 1e6 / hbm, 4)]}
+        del sx, sy, sws, ca, ch, cl
         # its pullback at the same size (forward recomputed inside)
         gq, gk, gv = (torch.empty(Hn, T, 128, device="cuda", dtype=torch.bfloat16) for _ in range(3))
         ga, gb = torch.empty(Hn, T, device="cuda"), torch.empty(Hn, T, device="cuda")

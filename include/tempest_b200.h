@@ -406,9 +406,12 @@ int tb200_attention_bwd_masked(const tb200_attn_desc *desc, const tb200_attn_mas
  * with strides, another head dimension: TB200_ERR_UNSUPPORTED, for which the
  * entry above remains), in either of the pullback's forms (desc->deterministic).
  * Keys beyond a sequence's length and key tiles that lie wholly beyond it are
- * skipped; with packed documents every visited tile is masked element by
- * element (tiles that lie wholly before a document's start are still visited).
- * The workspace is tb200_attention_bwd's plus a row of starts per (batch, head). */
+ * skipped; with packed documents a key tile stops at the last chunk of queries
+ * that can see it and a query tile starts at the first keys any of its queries
+ * sees (found from the smallest start of every 64 queries, so starts need not be
+ * sorted), and steps in between take the element-by-element test only where a
+ * start can hide a key.  The workspace is tb200_attention_bwd's plus a row of
+ * starts per (batch, head) and their block minima and maxima. */
 size_t tb200_attention_bwd_masked_workspace_bytes(const tb200_attn_desc *desc);
 int tb200_attention_bwd_masked_ws(const tb200_attn_desc *desc, const tb200_attn_mask *mask, const void *q,
                                   const void *k, const void *v, const void *o, const float *lse, const void *dout,

@@ -86,6 +86,8 @@ struct AttnBwdArgs {
     const int *kv_len;              // [batch]
     const int *doc_start;           // [batch][queries]: the dQ kernel's row threads read their own query's
     const int *starts;              // the same as [batch][head][q_pad] rows, which the dK/dV kernels' row threads read
+    const int *start_max;           // the largest start of every 64 queries of such a row: [batch][head][q_pad / 64]
+    const int *start_min;           // and the smallest (0x7f7f7f7f where a block has no query)
     int batch, heads, kv_heads, queries, keys;
     int q_pad;                      // queries rounded up to whole steps: rows of the arrays above, zero-filled
     int outer_tiles, supers;
@@ -154,6 +156,19 @@ struct Steps {
             if (c0 > all) c0 = all;
             nc = all - c0;
             if (tile * kOuter >= keys) nc = 0;   // every key of the tile lies beyond the length: zero gradients
+            if (p.start_min && nc > 0) {
+                // packed documents: the chunks of queries past the last one that can see a key of this tile are left
+                // out (a chunk sees none when even its smallest start lies beyond the tile's last key)
+                const int *mins = p.start_min + static_cast<long long>(b) * p.heads * (p.q_pad / 64);
+                const int last_key = tile * kOuter + kOuter - 1;
+                int last = c0 + nc - 1;
+                while (last >= c0) {
+                    const int lo = min(__ldg(mins + 2 * last), __ldg(mins + 2 * last + 1));
+                    if (lo <= last_key) break;
+                    last--;
+                }
+                nc = last - c0 + 1;
+            }
             count = nc * group;
             head_first = head_outer * group;
         } else {
@@ -167,6 +182,14 @@ struct Steps {
             if (p.causal) {
                 const int upto = (tile * kOuter + kOuter - 1) / kInner + 1;
                 if (upto < nc) nc = upto;
+            }
+            if (p.start_min) {
+                // packed documents: keys before the smallest start among the tile's queries are hidden from all of them
+                const int *mins = p.start_min + static_cast<long long>(b) * p.heads * (p.q_pad / 64);
+                const int lo = min(__ldg(mins + 2 * tile), __ldg(mins + 2 * tile + 1));
+                const int skip = lo == 0x7f7f7f7f ? 0 : lo / kInner;
+                c0 = skip < nc ? skip : nc;
+                nc -= c0;
             }
             count = nc;
             head_first = head_outer / group;
@@ -495,8 +518,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s_read);
-                // (with packed documents every step takes the per-element test: where the starts fall is not known here)
-                const bool edge = p.doc_start != nullptr ||
+                // packed documents: the per-element test only where a start can hide a key -- dK/dV: the largest start
+                // among the step's 64 queries lies beyond the tile's first key; dQ: this query's start lies beyond the
+                // step's first key
+                bool doc_edge = false;
+                if (p.doc_start) {
+                    if (DKDV)
+                        doc_edge = __ldg(p.start_max + ((static_cast<long long>(steps.b) * p.heads + hi) * p.q_pad + col0) / 64) >
+                                   steps.tile * kOuter;
+                    else
+                        doc_edge = row_start > col0;
+                }
+                const bool edge = doc_edge ||
                                   (DKDV ? (pos0 + kInner > p.queries || outer_pos >= steps.keys ||
                                            (p.causal && pos0 < steps.tile * kOuter + kOuter))
                                         : (pos0 + kInner > steps.keys || outer_pos >= p.queries ||
@@ -675,7 +708,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) attention_bwd_kernel(const __g
 __global__ void __launch_bounds__(256) attention_stats_kernel(const __nv_bfloat16 *o, const __nv_bfloat16 *dout,
                                                               const float *lse, float *lse2, float *delta, int batch,
                                                               int heads, int queries, int q_pad, int d,
-                                                              const int *doc_start, int *starts) {
+                                                              const int *doc_start, int *starts, int *start_max,
+                                                              int *start_min) {
     const long long rows = static_cast<long long>(batch) * queries * heads;
     const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 4;
     const int t = threadIdx.x & 15;
@@ -703,7 +737,12 @@ __global__ void __launch_bounds__(256) attention_stats_kernel(const __nv_bfloat1
         // shift instead of the infinite one, which would meet the masked scores' -Inf as NaN)
         const float l = lse[r];
         lse2[out] = l == -INFINITY ? -1.0e30f : -l * kLog2e;
-        if (starts) starts[out] = doc_start[b * queries + m];
+        if (starts) {
+            const int first = doc_start[b * queries + m];
+            starts[out] = first;
+            atomicMax(start_max + out / 64, first);   // zero before the launch; starts are not negative
+            atomicMin(start_min + out / 64, first);   // 0x7f7f7f7f before the launch
+        }
     }
 }
 
@@ -802,9 +841,18 @@ extern "C" size_t tb200_attention_bwd_workspace_bytes(const tb200_attn_desc *d) 
 }
 
 namespace {
-size_t bwd_start_bytes(const tb200_attn_desc *d) {
+// a row of starts per (batch, head), and behind them the largest and the smallest start of every 64 queries
+size_t bwd_start_row_bytes(const tb200_attn_desc *d) {
     const size_t q_pad = (static_cast<size_t>(d->queries) + kInner - 1) / kInner * kInner;
     return (static_cast<size_t>(d->batch) * d->heads * q_pad * sizeof(int) + 255) / 256 * 256;
+}
+size_t bwd_start_block_bytes(const tb200_attn_desc *d) {
+    const size_t q_pad = (static_cast<size_t>(d->queries) + kInner - 1) / kInner * kInner;
+    return (static_cast<size_t>(d->batch) * d->heads * (q_pad / 64) * sizeof(int) + 255) / 256 * 256;
+}
+size_t bwd_start_bytes(const tb200_attn_desc *d) {
+    const size_t q_pad = (static_cast<size_t>(d->queries) + kInner - 1) / kInner * kInner;
+    return bwd_start_row_bytes(d) + 2 * bwd_start_block_bytes(d);
 }
 int bwd_run(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q, const void *k, const void *v, const void *o,
             const float *lse, const void *dout, void *dq, void *dk, void *dv, void *workspace, size_t workspace_bytes,
@@ -871,15 +919,20 @@ int bwd_run(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q
     const int *doc_start = mask ? mask->doc_start : nullptr;
     int *starts = doc_start ? reinterpret_cast<int *>(static_cast<uint8_t *>(workspace) + tb200_attention_bwd_workspace_bytes(d))
                             : nullptr;
+    int *start_max = doc_start ? reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(starts) + bwd_start_row_bytes(d)) : nullptr;
+    int *start_min = doc_start ? reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(start_max) + bwd_start_block_bytes(d)) : nullptr;
     {
         if (q_pad != d->queries) TB200_CUDA(cudaMemsetAsync(workspace, 0, bwd_stat_bytes(d), stream));   // the pads are read
         const long long threads = static_cast<long long>(d->batch) * d->heads * d->queries * 16;
         const unsigned blocks = static_cast<unsigned>(ceil_div(threads, 256));
-        if (doc_start && q_pad != d->queries) TB200_CUDA(cudaMemsetAsync(starts, 0, bwd_start_bytes(d), stream));
+        if (doc_start) {   // pads and maxima start at zero, minima at 0x7f7f7f7f
+            TB200_CUDA(cudaMemsetAsync(starts, 0, bwd_start_row_bytes(d) + bwd_start_block_bytes(d), stream));
+            TB200_CUDA(cudaMemsetAsync(start_min, 0x7f, bwd_start_block_bytes(d), stream));
+        }
         attention_stats_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(o),
                                                            static_cast<const __nv_bfloat16 *>(dout), lse, lse2, delta,
                                                            d->batch, d->heads, d->queries, q_pad, d->head_dim, doc_start,
-                                                           starts);
+                                                           starts, start_max, start_min);
         TB200_CUDA(cudaGetLastError());
     }
     AttnBwdArgs p{};
@@ -887,6 +940,8 @@ int bwd_run(const tb200_attn_desc *d, const tb200_attn_mask *mask, const void *q
     p.kv_len = mask ? mask->kv_len : nullptr;
     p.doc_start = doc_start;
     p.starts = starts;
+    p.start_max = start_max;
+    p.start_min = start_min;
     p.batch = d->batch; p.heads = d->heads; p.kv_heads = d->kv_heads; p.queries = d->queries; p.keys = d->keys;
     p.causal = d->causal; p.scale = d->scale; p.scale_log2 = d->scale * kLog2e;
     // dK, dV: items over key tiles
