@@ -310,6 +310,28 @@ __device__ __forceinline__ void epilogue_values(const uint32_t (&r)[32], float a
             pre[j] = x.x; pre[j + 1] = x.y;
             v[j] = y.x; v[j + 1] = y.y;
         }
+    } else if constexpr (EPI == TB200_EPI_MUL_GELU_GRAD) {
+        // acc * gelu'(x), x the saved pre-activation: gelu'(x) = (1 + t) / 2 + x / 2 (1 - t^2) c (1 + 3 * 0.044715 x^2),
+        // t = tanh(x c (1 + 0.044715 x^2)), c = 0.7978846; as packed pairs
+        const float2 al = make_float2(alpha, alpha), c1 = make_float2(0.7978846f, 0.7978846f),
+                     c2 = make_float2(0.7978846f * 0.044715f, 0.7978846f * 0.044715f),
+                     c3 = make_float2(0.7978846f * 0.134145f, 0.7978846f * 0.134145f), half = make_float2(0.5f, 0.5f),
+                     one = make_float2(1.0f, 1.0f), minus = make_float2(-1.0f, -1.0f);
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+            const float2 x = make_float2(auxv[j], auxv[j + 1]);
+            const float2 x2 = __fmul2_rn(x, x);
+            const float2 u = __fmul2_rn(x, __ffma2_rn(x2, c2, c1));
+            const float2 t = make_float2(tanh_fast(u.x), tanh_fast(u.y));
+            const float2 du = __ffma2_rn(x2, c3, c1);
+            const float2 h = __ffma2_rn(t, half, half);
+            const float2 omt2 = __ffma2_rn(__fmul2_rn(t, t), minus, one);
+            const float2 grad = __ffma2_rn(__fmul2_rn(__fmul2_rn(x, half), omt2), du, h);
+            const float2 a = __fmul2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), al);
+            const float2 y = __fmul2_rn(a, grad);
+            pre[j] = a.x; pre[j + 1] = a.y;
+            v[j] = y.x; v[j + 1] = y.y;
+        }
     } else {
         constexpr bool reads_bias = epilogue_reads_bias(EPI), reads_aux = epilogue_reads_aux(EPI);
 #pragma unroll
