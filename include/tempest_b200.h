@@ -227,6 +227,12 @@ int tb200_gemm_pointers(const tb200_gemm_desc *desc, const void *const *a, const
 /* Bytes of scratch a split of this product wants (0 when it would not split). */
 size_t tb200_gemm_workspace_bytes(const tb200_gemm_desc *desc);
 
+/* The tile form the tensor-core path takes for a descriptor: 128 or 256 (columns of
+ * a single CTA's 128-row tile) or 512 (256 x 256 tiles by pairs of CTAs), 0 for an
+ * empty product.  Host arithmetic only; what sends a product to the CUDA-core
+ * kernel instead (types, alignments) is not looked at. */
+int tb200_gemm_tile_form(const tb200_gemm_desc *desc);
+
 /* Enqueues the product.  BFloat16 or Float16 operands with 16-byte aligned bases and
  * leading dimensions (and batch strides) that are multiples of 8 run on the tensor cores
  * (tcgen05, Float32 accumulation, one rounding at the store); everything else

@@ -1057,6 +1057,14 @@ int tile_width(const tb200_gemm_desc &d, int sms) {
     return 2 * wide <= sms ? 128 : 256;
 }
 
+// Pairs of CTAs on 256 x 256 tiles: asked for (tile_n 512), or the library's choice where there is at least one such
+// tile per pair of SMs -- a third less operand traffic per SM, which is what the single-CTA kernel is short of.
+bool tile_pairs(const tb200_gemm_desc &d, int bn, int sms) {
+    const int64_t batch = d.batch > 1 ? d.batch : 1;
+    const int64_t pair_items = ceil_div(d.m, 2 * BM) * ceil_div(d.n, 256) * batch;
+    return d.n > 128 && d.m > BM && (d.tile_n == 512 || (d.tile_n == 0 && bn == 256 && d.split_k <= 1 && 2 * pair_items >= sms));
+}
+
 size_t split_workspace_bytes(const tb200_gemm_desc &d, int splits) {
     const int64_t batch = d.batch > 1 ? d.batch : 1;
     const int64_t ld = (d.n + 3) / 4 * 4;
@@ -1151,11 +1159,7 @@ int prepare(tb200_gemm_plan *plan) {
         GemmArgs &p = plan->args;
         p = GemmArgs{};
         const int bn = tile_width(*d, dev.sms);
-        // pairs of CTAs on 256 x 256 tiles where there is at least one such tile per pair of SMs: a third less
-        // operand traffic per SM, which is what this kernel is short of
-        const int64_t pair_items = ceil_div(d->m, 2 * BM) * ceil_div(d->n, 256) * batch;
-        const bool pair = d->n > 128 && d->m > BM &&
-                          (d->tile_n == 512 || (d->tile_n == 0 && bn == 256 && d->split_k <= 1 && 2 * pair_items >= dev.sms));
+        const bool pair = tile_pairs(*d, bn, dev.sms);
         plan->pair = pair;
         int splits = 1, kb_per = static_cast<int>(ceil_div(d->k, BK));
         if (!pair) choose_split(*d, bn, dev.sms, &splits, &kb_per);
@@ -1312,6 +1316,19 @@ extern "C" size_t tb200_gemm_workspace_bytes(const tb200_gemm_desc *d) {
     int splits = 1, per = 1;
     choose_split(*d, tile_width(*d, sms), sms, &splits, &per);
     return splits > 1 ? split_workspace_bytes(*d, splits) : 0;
+}
+
+// The tile form the tensor-core path takes for a descriptor: 128 or 256 (columns of a single CTA's 128-row tile) or
+// 512 (256 x 256 tiles by pairs of CTAs); 0 for an empty product.  Host arithmetic only (148 SMs assumed where no
+// device answers), for cost statements and tests: the layouts, alignments and types that send a product to the
+// CUDA-core kernel instead are not looked at.
+extern "C" int tb200_gemm_tile_form(const tb200_gemm_desc *d) {
+    if (!d || d->m <= 0 || d->n <= 0 || d->k <= 0) return 0;
+    DeviceInfo dev;
+    int sms = 148;
+    if (current_device(&dev) == TB200_OK) sms = dev.sms;
+    const int bn = tile_width(*d, sms);
+    return tile_pairs(*d, bn, sms) ? 512 : bn;
 }
 
 extern "C" int tb200_gemm(const tb200_gemm_desc *d, const void *a, const void *b, void *c, const void *bias,

@@ -129,6 +129,7 @@ SIGNATURES = {
     "tb200_layernorm_bwd_noalloc": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i, _p]),
     "tb200_gemm": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
     "tb200_gemm_workspace_bytes": (_sz, [ctypes.POINTER(GemmDesc)]),
+    "tb200_gemm_tile_form": (_i, [ctypes.POINTER(GemmDesc)]),
     "tb200_gemm_plan_create": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, ctypes.POINTER(_p)]),
     "tb200_gemm_plan_launch": (_i, [_p, _p]),
     "tb200_gemm_plan_repoint": (_i, [_p, _i, _p]),
@@ -314,6 +315,11 @@ def gemm(a, b, c, m, n, k, *, bias=0, aux=0, aux_out=0, stream=0, tune=False, **
 def gemm_pointers(desc, a, b, c, count, stream=0):
     """`count` products alike (tb200_gemm_pointers): a, b, c are device arrays of `count` device addresses."""
     check("tb200_gemm_pointers", load().tb200_gemm_pointers(ctypes.byref(desc), a, b, c, count, stream or None))
+
+
+def gemm_tile_form(desc):
+    """128 / 256: single-CTA tiles of that many columns; 512: 256 x 256 tiles by pairs of CTAs (tb200_gemm_tile_form)."""
+    return load().tb200_gemm_tile_form(ctypes.byref(desc))
 
 
 def gemm_workspace_bytes(desc):

@@ -212,3 +212,21 @@ def test_masked_attention_templates(I):
     assert not lib.supports(t, I.Binding("attention_lengths", e, arrays))       # the other mask's array
     lengths = dict({k: v for k, v in arrays.items() if k != "start"}, lengths=I.dense_vector(None, "Int32", B, 6))
     assert lib.supports(t, I.Binding("attention_lengths", e, lengths))
+
+
+def test_tile_form_of_a_product(pkg):
+    """Which tiles a product takes, decided on the host: pairs of CTAs on 256 x 256 tiles wherever there is at least
+    one such tile per pair of SMs (148 SMs where no device answers), single-CTA tiles of 256 columns below that, of 128
+    where the wide ones would fill less than half the device or the result is narrow; the descriptor can ask."""
+    L = pkg.lib
+    assert L.gemm_tile_form(L.gemm_desc(8192, 4096, 4096)) == 512          # 32 x 16 tiles for 74 pairs
+    assert L.gemm_tile_form(L.gemm_desc(8192, 1024, 4096)) == 512          # 128 tiles
+    assert L.gemm_tile_form(L.gemm_desc(2048, 2048, 256)) == 256           # 64 pair tiles: not one per pair of SMs
+    assert L.gemm_tile_form(L.gemm_desc(1024, 1024, 4096)) == 128          # 32 wide tiles: under half the device
+    assert L.gemm_tile_form(L.gemm_desc(4096, 128, 512)) == 128            # a narrow result
+    assert L.gemm_tile_form(L.gemm_desc(8192, 4096, 4096, tile_n=-1)) == 256   # single-CTA tiles asked for
+    assert L.gemm_tile_form(L.gemm_desc(8192, 4096, 4096, tile_n=128)) == 128
+    assert L.gemm_tile_form(L.gemm_desc(512, 512, 64, tile_n=512)) == 512
+    assert L.gemm_tile_form(L.gemm_desc(128, 512, 64, tile_n=512)) == 256  # one row of tiles: nothing to pair
+    assert L.gemm_tile_form(L.gemm_desc(64, 2048, 2048, batch=64)) == 256  # a batch of short products: one row of tiles each, nothing to pair
+    assert L.gemm_tile_form(L.gemm_desc(0, 512, 64)) == 0
