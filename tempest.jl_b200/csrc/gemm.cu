@@ -27,6 +27,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -1008,6 +1009,36 @@ int kernel_by_epilogue(int epilogue, const DeviceInfo &dev, const void **fn) {
     return TB200_ERR_UNSUPPORTED;
 }
 
+// How many CTA pairs of `kernel` the device holds at once.  A part with an odd number of multiprocessors left in
+// some cluster of its die holds fewer pairs than half its multiprocessor count, and a grid with more pairs than
+// that would run the surplus after the rest has finished: with a fixed share of the tiles each, at twice the
+// time.  Asked of the driver once per device and kernel; half the multiprocessors if it does not answer.
+int resident_pairs(const void *kernel, size_t smem, const DeviceInfo &dev) {
+    struct Known { int device; const void *kernel; int pairs; };
+    static std::mutex lock;
+    static std::vector<Known> known;
+    std::lock_guard<std::mutex> hold(lock);
+    for (const Known &k : known)
+        if (k.device == dev.device && k.kernel == kernel) return k.pairs;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(dev.sms / 2 * 2));
+    config.blockDim = dim3(kGemmThreads);
+    config.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    config.attrs = &attr;
+    config.numAttrs = 1;
+    int pairs = 0;
+    if (cudaOccupancyMaxActiveClusters(&pairs, kernel, &config) != cudaSuccess || pairs <= 0) {
+        cudaGetLastError();
+        pairs = dev.sms / 2;
+    }
+    if (pairs > dev.sms / 2) pairs = dev.sms / 2;
+    known.push_back(Known{dev.device, kernel, pairs});
+    return pairs;
+}
+
 int kernel_by_shape(int bn, bool pair, int out_dtype, int epilogue, const DeviceInfo &dev, const void **fn) {
     if (pair) {
         if (out_dtype == TB200_F32) return kernel_by_epilogue<256, OUT_F32, true>(epilogue, dev, fn);
@@ -1244,7 +1275,8 @@ int prepare(tb200_gemm_plan *plan) {
         // more items than blocks: a created plan lets its blocks draw them from a counter
         p.schedule = (plan->counters && items > plan->grid) ? plan->counters : nullptr;
         if (pair) {   // two CTAs per item
-            const long long pairs = items < dev.sms / 2 ? items : dev.sms / 2;
+            const long long held = resident_pairs(plan->kernel, plan->smem, dev);
+            const long long pairs = items < held ? items : held;
             plan->grid = static_cast<unsigned>(2 * pairs);
             p.schedule = (plan->counters && items > pairs) ? plan->counters : nullptr;
         }
