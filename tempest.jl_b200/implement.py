@@ -22,7 +22,7 @@ default), as a Tempest launch takes the task's.
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, Optional, Tuple
 
-from . import lib
+from . import groups, lib
 
 ELTYPES = {"Float32": (lib.F32, 4), "BFloat16": (lib.BF16, 2)}
 _BYTES = {"Float32": 4, "BFloat16": 2, "Int32": 4}   # of every element type an array of a binding may have (masks: Int32)
@@ -516,6 +516,15 @@ class B200Kernels:
     def resources(self, target: Target) -> Resources:
         return Resources()
 
+    def package_of(self) -> str:
+        """The package whose kernels the launches run (src/Compiler/Implement/Implement.jl:91)."""
+        return PACKAGE
+
+    @staticmethod
+    def loaded() -> bool:
+        """Whether the library can be made (src/Compiler/Implement/Implement.jl:99)."""
+        return library_loaded()
+
     def supports(self, target: Target, b: Binding) -> bool:
         if b.template in LINEAR_SPELLINGS:
             types = {s.eltype for s in b.arrays.values()}
@@ -780,6 +789,20 @@ class RecurrenceLaunch(GroupLaunch):
                                 _torch_stream())
 
 
+PACKAGE = "tempest_b200"
+_LOWERED = frozenset(name for name, arity in groups.ARITY.items() if arity > 0)
+_LOWERED_CODES = frozenset(groups.OPS.values())
+
+
+def library_loaded() -> bool:
+    """Whether the shared library can be loaded in this process."""
+    try:
+        lib.load()
+    except (RuntimeError, OSError):
+        return False
+    return True
+
+
 class B200Generator:
     """`<: Implementation` for row groups: claims every group whose descriptor the library accepts."""
 
@@ -816,6 +839,42 @@ class B200Generator:
 
     def variants(self, target: Target, group, claim):
         return ()                                      # one schedule per claim: nothing further to search
+
+    # ---- the rest of the protocol (src/Compiler/Implement/Implement.jl:85-214): what the cover asks before it
+    # offers a group, each with the reference default's meaning
+    def package_of(self) -> str:
+        """The package whose kernels the launches run: the line of the rates file they are priced on (:91)."""
+        return PACKAGE
+
+    @staticmethod
+    def loaded() -> bool:
+        """Whether the implementation can be made (:99): whether the shared library is there to load."""
+        return library_loaded()
+
+    def resources(self, target: Target) -> Resources:
+        """One executable's scratch, shared by its launches (:141): the column groups' partial sums."""
+        return Resources()
+
+    def candidates(self, target: Target, plan):
+        """No regrouping of the plan's values is proposed (:186): the generator takes the groups as cut."""
+        return []
+
+    def record_name(self, claim) -> str:
+        """A claim's name in the tuning record (:189); claims hold schedules, never value numbers."""
+        return f"{type(self).__name__} {claim}"
+
+    def recomputes_folds(self, target: Target) -> bool:
+        """A fold formed where it is read (`recomputed` terms: attention's scores) is computed in the reading
+        kernel, by the term interpreter and by the attention kernels a group's terms lead to (:192)."""
+        return True
+
+    def lowers(self, target: Target, term, group=None) -> bool:
+        """Whether a group applying `term` can be realized (:214): `term` is a scalar function's name, or the
+        number of a term of `group`.  What has no code in `groups.OPS` is declared here, before any claim."""
+        if isinstance(term, int):
+            code = group.terms[term][0]
+            return code in _LOWERED_CODES
+        return term in _LOWERED
 
     def estimate(self, claim: RowClaim, target: Target, group):
         """One launch moving the group's bytes once; the interpreter also pays for every term of every element

@@ -230,3 +230,22 @@ def test_tile_form_of_a_product(pkg):
     assert L.gemm_tile_form(L.gemm_desc(128, 512, 64, tile_n=512)) == 256  # one row of tiles: nothing to pair
     assert L.gemm_tile_form(L.gemm_desc(64, 2048, 2048, batch=64)) == 256  # a batch of short products: one row of tiles each, nothing to pair
     assert L.gemm_tile_form(L.gemm_desc(0, 512, 64)) == 0
+
+
+def test_the_rest_of_the_protocol(pkg):
+    """What the cover asks of an implementation before it offers it a group
+    (src/Compiler/Implement/Implement.jl:85-214), each answer checked against the default's meaning."""
+    I, G = pkg.implement, pkg.groups
+    gen, lib, t = I.B200Generator(), I.B200Kernels(), I.Target()
+    assert gen.package_of() == lib.package_of() == "tempest_b200"       # one line of the rates file for both doors
+    assert gen.loaded() and lib.loaded()
+    assert isinstance(gen.resources(t), I.Resources) and gen.resources(t) is not gen.resources(t)
+    assert gen.candidates(t, plan=None) == []
+    assert gen.recomputes_folds(t)
+    g = G.softmax(4096, 8)
+    claim = gen.claims(t, g)[-1]
+    name = gen.record_name(claim)
+    assert name.startswith("B200Generator RowClaim(") and name == gen.record_name(gen.claims(t, G.softmax(4096, 8))[-1])
+    # scalar functions: by name, or as a term of a group
+    assert gen.lowers(t, "tanh") and gen.lowers(t, "fma") and not gen.lowers(t, "erf") and not gen.lowers(t, "load")
+    assert all(gen.lowers(t, i, g) for i in range(len(g.terms)))
