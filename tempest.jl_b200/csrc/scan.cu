@@ -109,6 +109,7 @@ struct ScanArgs {
     int reverse;
     int vec;   // along rows: every row is a whole number of 16-byte aligned groups of eight elements
     int slabs;       // across rows: runs the rows are cut into (1: one thread walks a column)
+    int quad;        // across rows in slabs: every row is a whole number of aligned groups of four columns
     float *totals;   // the slabs' totals (caller's workspace)
 };
 
@@ -303,6 +304,132 @@ __global__ void __launch_bounds__(kScanThreads) scan_slabs_kernel(const ScanArgs
     }
 }
 
+// four neighbouring columns of one row as one access (128 bits of Float32, 64 of BFloat16; `p` aligned to that),
+// kept as loaded until they are used.  `keep`: the line is wanted again soon (the totals' sweep leaves the head of
+// every slab in L2 for the second sweep)
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+    using Raw = float4;
+    static __device__ __forceinline__ Raw load(const float *p, bool keep) {
+        return keep ? __ldg(reinterpret_cast<const float4 *>(p)) : __ldcs(reinterpret_cast<const float4 *>(p));
+    }
+    static __device__ __forceinline__ void unpack(const Raw &q, float (&v)[4]) { v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+    static __device__ __forceinline__ void store(float *p, const float (&v)[4]) {
+        __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
+    }
+};
+template <> struct Quad<__nv_bfloat16> {
+    using Raw = uint2;
+    static __device__ __forceinline__ Raw load(const __nv_bfloat16 *p, bool keep) {
+        return keep ? __ldg(reinterpret_cast<const uint2 *>(p)) : __ldcs(reinterpret_cast<const uint2 *>(p));
+    }
+    static __device__ __forceinline__ void unpack(const Raw &q, float (&v)[4]) {
+        unpack_bf16x2(q.x, v[0], v[1]); unpack_bf16x2(q.y, v[2], v[3]);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float (&v)[4]) {
+        __stcs(reinterpret_cast<uint2 *>(p), make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3])));
+    }
+};
+
+// The same two sweeps with four columns a thread (rows that are whole aligned groups of four): a quarter of the
+// instructions per byte, and the next eight rows' loads are in flight while these eight are folded.  The totals'
+// sweep walks its slab from the last row to the first, putting each element *before* what it has (the folds are
+// associative, so the total is the same product of the same elements in the same order, grouped from the right);
+// it ends on the rows the second sweep begins with, which are then still in L2.
+template <int OP, typename T, bool WRITE>
+__global__ void __launch_bounds__(kScanThreads, 2) scan_slabs_quad_kernel(const ScanArgs a, float *totals, int slabs,
+                                                                           long long per) {
+    using F = Fold<OP>;
+    using S = typename F::S;
+    constexpr int W = Words<S>::N;
+    constexpr bool PAIRS = OP == TB200_SCAN_AFFINE;
+    using Q = Quad<T>;
+    using Raw = typename Q::Raw;
+    constexpr int B = sizeof(T) == 2 ? (PAIRS ? 6 : 12) : (PAIRS ? 4 : 8);   // rows in flight: 96-128 bytes a thread per array
+    const long long col = (blockIdx.x * static_cast<long long>(kScanThreads) + threadIdx.x) * 4;
+    if (col >= a.n) return;
+    const int slab = blockIdx.y;
+    const long long p_begin = slab * per, p_end = p_begin + per < a.rows ? p_begin + per : a.rows;
+    const long long count = p_end - p_begin;
+    for (long long m = blockIdx.z; m < a.batch; m += gridDim.z) {
+        const T *x = static_cast<const T *>(a.x) + m * a.stride_x + col;
+        const T *x2 = PAIRS ? static_cast<const T *>(a.x2) + m * a.stride_x2 + col : nullptr;
+        T *y = static_cast<T *>(a.y) + m * a.stride_y + col;
+        float *mine = totals + (m * slabs * W) * a.n + col;   // [slab][word] at these columns
+        union State { S s; float f[W]; };
+        S run[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) run[c] = F::identity();
+        if (WRITE) {
+            for (int b = 0; b < slab; b++) {
+                float4 t[W];
+#pragma unroll
+                for (int w = 0; w < W; w++)
+                    t[w] = *reinterpret_cast<const float4 *>(mine + (static_cast<long long>(b) * W + w) * a.n);
+                State u[4];
+#pragma unroll
+                for (int w = 0; w < W; w++) { u[0].f[w] = t[w].x; u[1].f[w] = t[w].y; u[2].f[w] = t[w].z; u[3].f[w] = t[w].w; }
+#pragma unroll
+                for (int c = 0; c < 4; c++) run[c] = F::combine(run[c], u[c].s);
+            }
+        }
+        // the i-th row this sweep visits: forward from the slab's first when writing, backward from its last when not
+        const auto row_of = [&](long long i) {
+            if (i >= count) i = count - 1;
+            const long long p = WRITE ? p_begin + i : p_end - 1 - i;
+            return a.reverse ? a.rows - 1 - p : p;
+        };
+        Raw cv[B], cw[B], nv[B], nw[B];
+        if (count > 0) {   // (a slab past the last row has none: its total is the identity)
+#pragma unroll
+            for (int j = 0; j < B; j++) {
+                const long long r = row_of(j);
+                cv[j] = Q::load(x + r * a.ld_x, !WRITE);
+                if (PAIRS) cw[j] = Q::load(x2 + r * a.ld_x2, !WRITE);
+            }
+        }
+        for (long long i0 = 0; i0 < count; i0 += B) {
+            if (i0 + B < count) {
+#pragma unroll
+                for (int j = 0; j < B; j++) {
+                    const long long r = row_of(i0 + B + j);
+                    nv[j] = Q::load(x + r * a.ld_x, !WRITE);
+                    if (PAIRS) nw[j] = Q::load(x2 + r * a.ld_x2, !WRITE);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < B; j++) {
+                if (i0 + j < count) {
+                    float v[4], w[4] = {0.0f, 0.0f, 0.0f, 0.0f}, out[4];
+                    Q::unpack(cv[j], v);
+                    if (PAIRS) Q::unpack(cw[j], w);
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const S e = F::lift(v[c], w[c]);
+                        run[c] = WRITE ? F::combine(run[c], e) : F::combine(e, run[c]);
+                        out[c] = F::observe(run[c]);
+                    }
+                    if (WRITE) Q::store(y + row_of(i0 + j) * a.ld_y, out);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < B; j++) {
+                cv[j] = nv[j];
+                if (PAIRS) cw[j] = nw[j];
+            }
+        }
+        if (!WRITE) {
+            State u[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) u[c].s = run[c];
+#pragma unroll
+            for (int w = 0; w < W; w++)
+                *reinterpret_cast<float4 *>(mine + (static_cast<long long>(slab) * W + w) * a.n) =
+                    make_float4(u[0].f[w], u[1].f[w], u[2].f[w], u[3].f[w]);
+        }
+    }
+}
+
 // Slabs for a scan across `rows` rows of `n` columns: enough blocks to fill the device eight times over, at least
 // 64 rows a slab; 1 = not worth splitting.
 inline int scan_slabs(long long n, long long rows, long long batch, int sms) {
@@ -321,6 +448,15 @@ template <int OP, typename T>
 int launch_scan(const ScanArgs &a, bool across, const DeviceInfo &dev, cudaStream_t stream) {
     if (across && a.slabs > 1) {
         const long long per = ceil_div(a.rows, static_cast<long long>(a.slabs));
+        if (a.quad) {
+            dim3 grid(static_cast<unsigned>(ceil_div(a.n, 4ll * kScanThreads)), static_cast<unsigned>(a.slabs),
+                      static_cast<unsigned>(a.batch < 64 ? a.batch : 64));
+            scan_slabs_quad_kernel<OP, T, false><<<grid, kScanThreads, 0, stream>>>(a, a.totals, a.slabs, per);
+            TB200_CUDA(cudaGetLastError());
+            scan_slabs_quad_kernel<OP, T, true><<<grid, kScanThreads, 0, stream>>>(a, a.totals, a.slabs, per);
+            TB200_CUDA(cudaGetLastError());
+            return TB200_OK;
+        }
         dim3 grid(static_cast<unsigned>(ceil_div(a.n, kScanThreads)), static_cast<unsigned>(a.slabs),
                   static_cast<unsigned>(a.batch < 64 ? a.batch : 64));
         scan_slabs_kernel<OP, T, false><<<grid, kScanThreads, 0, stream>>>(a, a.totals, a.slabs, per);
@@ -406,6 +542,9 @@ extern "C" int tb200_scan(const tb200_scan_desc *d, const void *x, const void *x
             if (d->workspace_bytes < need || !aligned_to(d->workspace, 16)) return TB200_ERR_WORKSPACE;
             a.slabs = slabs;
             a.totals = static_cast<float *>(d->workspace);
+            const bool pitches4 = a.n % 4 == 0 && a.ld_x % 4 == 0 && a.ld_y % 4 == 0 && (!pairs || a.ld_x2 % 4 == 0) &&
+                                  (batch == 1 || (a.stride_x % 4 == 0 && a.stride_y % 4 == 0 && (!pairs || a.stride_x2 % 4 == 0)));
+            a.quad = pitches4 && aligned_to(x, 4 * es) && aligned_to(y, 4 * es) && (!pairs || aligned_to(x2, 4 * es));
         }
     }
     if (d->dtype == TB200_F32) return launch_by_op<float>(d->op, a, d->across != 0, dev, stream);

@@ -140,6 +140,13 @@ def test_across_rows_in_slabs(pkg, cuda, oracle, reverse):
     got, ref = run(pkg, cuda, h, "sum", across=True, reverse=reverse, slabs=True), want(oracle, h, "sum", across=True, reverse=reverse)
     gf, rf = oracle.from_bf16(got).astype(np.float64), oracle.from_bf16(ref).astype(np.float64)
     assert (np.abs(gf - rf) <= 2.0 ** -7 * np.abs(rf) + 1e-3).all()
+    # rows that are not whole groups of four columns take one column a thread; and a row count that leaves the
+    # last slabs without rows (1024 slabs of 65 rows cover more than 65537)
+    odd = single(oracle.data(203, 1500))
+    agree(run(pkg, cuda, odd, "sum", across=True, reverse=reverse, slabs=True), want(oracle, odd, "sum", across=True, reverse=reverse), 1e-4)
+    long = single(0.01 * oracle.data(8, 65537))
+    assert np.array_equal(run(pkg, cuda, long, "max", across=True, reverse=reverse, slabs=True),
+                          want(oracle, long, "max", across=True, reverse=reverse))
     # scratch that is too small is refused
     d = L.scan_desc(200, 3001, 0, across=True)
     xd = cuda.zeros(3001, 200, device="cuda")
