@@ -1255,32 +1255,38 @@ using RowKernel = void (*)(RowArgs);
 
 // One struct per kernel family, so a family can be named as a type and
 // instantiated for the schedule's (element type, access width, vectors per thread).
-#define TB200_FAMILY(NAME, KERNEL)                                         \
+// ELEMS: the most elements a thread holds in any schedule of the family (`resident_elems`; split chunks hold 32);
+// wider instantiations are never launched and are not compiled.
+#define TB200_FAMILY(NAME, KERNEL, ELEMS)                                  \
     struct NAME {                                                          \
+        static constexpr int kMaxElems = ELEMS;                            \
         template <typename T, bool VEC, int VPT>                           \
         static RowKernel get() { return KERNEL<T, VEC, VPT>; }             \
     }
-TB200_FAMILY(SoftmaxFwdResident, softmax_fwd_resident);
-TB200_FAMILY(SoftmaxBwdResident, softmax_bwd_resident);
-TB200_FAMILY(LayernormFwdResident, layernorm_fwd_resident);
-TB200_FAMILY(LayernormBwdResident, layernorm_bwd_resident);
-TB200_FAMILY(SoftmaxFwdSplitFold, softmax_fwd_split_fold);
-TB200_FAMILY(SoftmaxFwdSplitWrite, softmax_fwd_split_write);
-TB200_FAMILY(SoftmaxBwdSplitFold, softmax_bwd_split_fold);
-TB200_FAMILY(SoftmaxBwdSplitWrite, softmax_bwd_split_write);
-TB200_FAMILY(LayernormSplitFold, layernorm_split_fold);
-TB200_FAMILY(LayernormFwdSplitWrite, layernorm_fwd_split_write);
+TB200_FAMILY(SoftmaxFwdResident, softmax_fwd_resident, 32);
+TB200_FAMILY(SoftmaxBwdResident, softmax_bwd_resident, 32);
+TB200_FAMILY(LayernormFwdResident, layernorm_fwd_resident, 32);
+TB200_FAMILY(LayernormBwdResident, layernorm_bwd_resident, 16);
+TB200_FAMILY(SoftmaxFwdSplitFold, softmax_fwd_split_fold, 32);
+TB200_FAMILY(SoftmaxFwdSplitWrite, softmax_fwd_split_write, 32);
+TB200_FAMILY(SoftmaxBwdSplitFold, softmax_bwd_split_fold, 32);
+TB200_FAMILY(SoftmaxBwdSplitWrite, softmax_bwd_split_write, 32);
+TB200_FAMILY(LayernormSplitFold, layernorm_split_fold, 32);
+TB200_FAMILY(LayernormFwdSplitWrite, layernorm_fwd_split_write, 32);
 #undef TB200_FAMILY
 
 template <typename Fam, typename T, bool VEC>
 RowKernel pick_vpt(int vpt) {
+    constexpr int EPV = Access<T, VEC>::EPV;
     switch (vpt) {
         case 1: return Fam::template get<T, VEC, 1>();
         case 2: return Fam::template get<T, VEC, 2>();
-        case 4: return Fam::template get<T, VEC, 4>();
+        case 4:
+            if constexpr (4 * EPV <= Fam::kMaxElems) return Fam::template get<T, VEC, 4>();
+            else return nullptr;
         case 8:
-            // 8 vectors of 8 BFloat16 would be 64 elements a thread: never scheduled
-            if constexpr (!VEC || sizeof(T) == 4) return Fam::template get<T, VEC, 8>();
+            // (8 vectors of 8 BFloat16 would be 64 elements a thread: never scheduled by any family)
+            if constexpr (8 * EPV <= Fam::kMaxElems) return Fam::template get<T, VEC, 8>();
             else return nullptr;
         default: return nullptr;
     }
