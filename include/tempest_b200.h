@@ -349,6 +349,20 @@ int tb200_attention_bwd(const tb200_attn_desc *desc, const void *q, const void *
                         const void *o, const float *lse, const void *dout, void *dq, void *dk,
                         void *dv, void *workspace, size_t workspace_bytes, void *stream);
 
+/* Which kernels a descriptor is computed by -- host arithmetic only, nothing is
+ * launched and no device is needed: what `claims` can say about a group before it is
+ * built.  `masked`: the call carries masks the device holds (tb200_attn_mask with
+ * starts or lengths); `pullback`: the gradient entry rather than the forward.
+ * Returns a TB200_ATTN_FORM_* value, or the negative status the entry itself would
+ * return for the descriptor (pointer alignment, which the entries also look at, is
+ * the caller's: Tempest's buffers are 128-byte aligned). */
+#define TB200_ATTN_FORM_CUDA_CORES 0   /* a warp per query (or key), Float32, any geometry up to 256 features */
+#define TB200_ATTN_FORM_TILE 1         /* tensor cores, one 128-query tile per block (forward) */
+#define TB200_ATTN_FORM_TWO_TILES 2    /* tensor cores, two query tiles per block (forward, more than one tile, no device-held mask) */
+#define TB200_ATTN_FORM_ONE_KERNEL 3   /* pullback on the tensor cores, dQ added by TMA reductions (deterministic = 0) */
+#define TB200_ATTN_FORM_TWO_KERNELS 4  /* pullback on the tensor cores, dK/dV and dQ kernels (deterministic = 1) */
+int tb200_attention_form(const tb200_attn_desc *desc, int masked, int pullback);
+
 /* Times both forms on these operands and returns the `deterministic` value (0 or 1)
  * of the faster one, or a negative status: the measured stage of the reference's
  * search over a claim's variants (src/Compiler/Implement/Implement.jl:120) over the

@@ -326,3 +326,17 @@ extern "C" int tb200_attention_bwd_masked(const tb200_attn_desc *d, const tb200_
     if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv) return TB200_ERR_NULL;
     return attention_simt_bwd(d, q, k, v, o, lse, dout, dq, dk, dv, static_cast<cudaStream_t>(stream), mask);
 }
+
+// Which kernels compute a descriptor: the tests the entries make, in their order, without a device.
+extern "C" int tb200_attention_form(const tb200_attn_desc *d, int masked, int pullback) {
+    if (!d) return TB200_ERR_NULL;
+    if (d->batch < 0 || d->heads <= 0 || d->kv_heads <= 0 || d->queries < 0 || d->keys < 0 || d->head_dim <= 0)
+        return TB200_ERR_SHAPE;
+    if (d->heads % d->kv_heads != 0 || !(d->scale > 0.0f)) return TB200_ERR_SHAPE;
+    if (d->causal && d->queries != d->keys) return TB200_ERR_SHAPE;
+    if (d->dtype != TB200_BF16) return TB200_ERR_DTYPE;
+    if (d->queries > (1 << 24) || d->keys > (1 << 24)) return TB200_ERR_SHAPE;
+    if (!attention_tensor_geometry(d)) return attention_simt_takes(d) ? TB200_ATTN_FORM_CUDA_CORES : TB200_ERR_UNSUPPORTED;
+    if (pullback) return d->deterministic ? TB200_ATTN_FORM_TWO_KERNELS : TB200_ATTN_FORM_ONE_KERNEL;
+    return (d->queries > 128 && !masked) ? TB200_ATTN_FORM_TWO_TILES : TB200_ATTN_FORM_TILE;
+}

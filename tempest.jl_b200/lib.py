@@ -130,6 +130,7 @@ SIGNATURES = {
     "tb200_gemm": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, _p]),
     "tb200_gemm_workspace_bytes": (_sz, [ctypes.POINTER(GemmDesc)]),
     "tb200_gemm_tile_form": (_i, [ctypes.POINTER(GemmDesc)]),
+    "tb200_attention_form": (_i, [ctypes.POINTER(AttnDesc), _i, _i]),
     "tb200_gemm_plan_create": (_i, [ctypes.POINTER(GemmDesc), _p, _p, _p, _p, _p, _p, ctypes.POINTER(_p)]),
     "tb200_gemm_plan_launch": (_i, [_p, _p]),
     "tb200_gemm_plan_repoint": (_i, [_p, _i, _p]),
@@ -320,6 +321,17 @@ def gemm_pointers(desc, a, b, c, count, stream=0):
 def gemm_tile_form(desc):
     """128 / 256: single-CTA tiles of that many columns; 512: 256 x 256 tiles by pairs of CTAs (tb200_gemm_tile_form)."""
     return load().tb200_gemm_tile_form(ctypes.byref(desc))
+
+
+ATTN_FORM_CUDA_CORES, ATTN_FORM_TILE, ATTN_FORM_TWO_TILES, ATTN_FORM_ONE_KERNEL, ATTN_FORM_TWO_KERNELS = range(5)
+
+
+def attention_form(desc, masked=False, pullback=False):
+    """Which kernels compute the descriptor (tb200_attention_form): an ATTN_FORM_* value; no device needed."""
+    form = load().tb200_attention_form(ctypes.byref(desc), int(masked), int(pullback))
+    if form < 0:
+        check("tb200_attention_form", form)
+    return form
 
 
 def gemm_workspace_bytes(desc):

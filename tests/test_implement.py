@@ -249,3 +249,23 @@ def test_the_rest_of_the_protocol(pkg):
     # scalar functions: by name, or as a term of a group
     assert gen.lowers(t, "tanh") and gen.lowers(t, "fma") and not gen.lowers(t, "erf") and not gen.lowers(t, "load")
     assert all(gen.lowers(t, i, g) for i in range(len(g.terms)))
+
+
+def test_which_kernels_compute_an_attention(pkg):
+    """tb200_attention_form: the entries' own routing as host arithmetic -- the benchmark's geometry goes to the
+    tensor cores in every direction, the reference's small test geometries to the CUDA cores."""
+    L = pkg.lib
+    bench = L.attn_desc(8, 32, 4096, 4096, 128, True)
+    assert L.attention_form(bench) == L.ATTN_FORM_TWO_TILES
+    assert L.attention_form(bench, masked=True) == L.ATTN_FORM_TILE          # device-held masks: one tile a block
+    assert L.attention_form(bench, pullback=True) == L.ATTN_FORM_ONE_KERNEL  # the reference's default, not deterministic
+    det = L.attn_desc(8, 32, 4096, 4096, 128, True, deterministic=True)
+    assert L.attention_form(det, pullback=True) == L.ATTN_FORM_TWO_KERNELS
+    assert L.attention_form(L.attn_desc(1, 32, 128, 8192, 128, False, kv_heads=8)) == L.ATTN_FORM_TILE   # decode over a cache
+    for d, h, kv, s, b in ((16, 2, 2, 200, 2), (16, 4, 2, 200, 2), (32, 3, 1, 70, 3), (8, 1, 1, 133, 1)):
+        small = L.attn_desc(b, h, s, s, d, True, kv_heads=kv)                # test/cuda/attention.jl:10-16
+        assert L.attention_form(small) == L.attention_form(small, pullback=True) == L.ATTN_FORM_CUDA_CORES
+    assert L.attention_form(L.attn_desc(1, 4, 64, 64, 128, False, value_dim=64)) == L.ATTN_FORM_CUDA_CORES
+    import pytest
+    with pytest.raises(L.TB200Error):
+        L.attention_form(L.attn_desc(1, 3, 64, 64, 128, False, kv_heads=2))  # heads not a multiple of key heads
