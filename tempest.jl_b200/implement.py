@@ -496,6 +496,20 @@ class RowLaunch:
             raise ValueError(t)
 
 
+_ATTENTION_KERNELS = {
+    lib.ATTN_FORM_CUDA_CORES: "CUDA-core kernels",
+    lib.ATTN_FORM_TILE: "tensor cores, one query tile a block",
+    lib.ATTN_FORM_TWO_TILES: "tensor cores, two query tiles a block",
+    lib.ATTN_FORM_ONE_KERNEL: "tensor cores, one kernel (dq added in L2)",
+    lib.ATTN_FORM_TWO_KERNELS: "tensor cores, two kernels (deterministic)",
+}
+
+
+def _attention_kernels(desc, masked, pullback) -> str:
+    """The kernels a built attention launch runs, for its description (tb200_attention_form)."""
+    return _ATTENTION_KERNELS[lib.attention_form(desc, masked=masked, pullback=pullback)]
+
+
 class B200Kernels:
     """The library (`<: Library`): which templates it computes, whether it takes
     a binding, what a launch costs, and the launch itself."""
@@ -641,7 +655,6 @@ class B200Kernels:
             return ScanLaunch(b, resources), f"B200 {b.template}, {e['rows']} rows of {e['n']} {b.arrays['x'].eltype}"
         if b.template.startswith("attention"):
             launch = AttentionLaunch(b)
-            form = ""
             if "documents" in b.template or "lengths" in b.template:
                 e = b.extents
                 if b.template.endswith("_pullback") and e["d"] == 128:
@@ -651,8 +664,9 @@ class B200Kernels:
                     resources = resources if resources is not None else Resources()
                     launch.workspace, launch.workspace_bytes = resources.workspace(need), need
                 what = "the starts of packed documents" if "documents" in b.template else "lengths"
+                kernels = _attention_kernels(launch.desc, masked=True, pullback=b.template.endswith("_pullback"))
                 return launch, (f"B200 {b.template}, {what} read on the device, {e['h']} heads over {e['hk']} of "
-                                f"{e['d']} features, {e['m']} queries by {e['n']} keys, batch {e['b']}")
+                                f"{e['d']} features, {e['m']} queries by {e['n']} keys, batch {e['b']}, {kernels}")
             if b.template.endswith("_pullback"):
                 # a target that wants repeatable bits gets the two-kernel form; any other gets whichever of the two
                 # forms measures faster on these operands (the measured stage of the cover's search over variants)
@@ -676,7 +690,7 @@ class B200Kernels:
                         launch.workspace.data_ptr(), need, current_stream())
                     if key:
                         self.record.keep("attention_pullback", key, {"deterministic": launch.desc.deterministic})
-                form = ", two kernels (deterministic)" if launch.desc.deterministic else ", one kernel (dq added in L2)"
+            form = ", " + _attention_kernels(launch.desc, masked=False, pullback=b.template.endswith("_pullback"))
             e = b.extents
             return launch, (f"B200 {b.template}, {e['h']} heads over {e['hk']} of {e['d']} features, "
                             f"{e['m']} queries by {e['n']} keys, batch {e['b']}{form}")

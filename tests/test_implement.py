@@ -105,6 +105,10 @@ def test_product_and_attention_templates(I):
     assert lib.supports(t, a)
     (w,) = lib.estimate(t, a)
     assert abs(w.flops - 1.0995e12) / 1.0995e12 < 1e-3
+    # the forward builds without touching the device (addresses stand in for buffers); its description names the kernels
+    at = lambda d: {n: I.dense_heads(4096 * (i + 1), "BFloat16", d, 32, 4096, 8, i) for i, n in enumerate(("q", "k", "v", "o"))}  # noqa: E731
+    assert lib.build(t, I.Binding("attention_causal", e, at(128)))[1].endswith("tensor cores, two query tiles a block")
+    assert lib.build(t, I.Binding("attention_causal", dict(e, d=64), at(64)))[1].endswith("CUDA-core kernels")
     assert lib.supports(t, I.Binding("attention_causal", dict(e, d=64), arrays))      # CUDA-core path
     assert not lib.supports(t, I.Binding("attention_causal", dict(e, d=512), arrays))
     assert not lib.supports(t, I.Binding("attention_causal", dict(e, n=2048), arrays))
