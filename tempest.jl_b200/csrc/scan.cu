@@ -334,7 +334,7 @@ template <> struct Quad<__nv_bfloat16> {
 };
 
 // The same two sweeps with four columns a thread (rows that are whole aligned groups of four): a quarter of the
-// instructions per byte, and the next eight rows' loads are in flight while these eight are folded.  The totals'
+// instructions per byte, and the next rows' loads (B of them) are in flight while these are folded.  The totals'
 // sweep walks its slab from the last row to the first, putting each element *before* what it has (the folds are
 // associative, so the total is the same product of the same elements in the same order, grouped from the right);
 // it ends on the rows the second sweep begins with, which are then still in L2.
