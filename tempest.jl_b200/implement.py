@@ -72,12 +72,22 @@ class Binding:
 
 @dataclass
 class Work:
-    """The cost statement of one launch (src/Compiler/Implement/Implement.jl:61-82)."""
+    """The cost statement of a claim (src/Compiler/Implement/Implement.jl:30-82).  The reference states one `Work`
+    per launch; the mirror states a claim's launches together (`launches`) with the fields the reference prices:
+    what is moved, what is read again, what passes between the claim's launches, the products' flops and factor
+    type, the flops of folds recomputed inside them, the blocks and whether they split sums, the steps a block
+    takes one after another."""
     bytes: int
     flops: float = 0.0
     blocks: int = 0
     launches: int = 1
     applied: int = 0     # function applications per element the launch pays for beyond its bytes
+    reread: int = 0      # bytes read again, beyond the first time (operand tiles fetched by several blocks)
+    passed: int = 0      # bytes passed between the claim's launches through a workspace (partial sums, dq in Float32)
+    recomputed: float = 0.0   # flops of folds recomputed inside the products (attention's scores)
+    factor: str = "Float32"   # the products' factor type
+    split: bool = False  # the blocks split sums among them
+    steps: int = 0       # steps a block takes one after another, each waiting for what it loads
 
 
 @dataclass
@@ -596,25 +606,51 @@ class B200Kernels:
             e = b.extents
             size = ELTYPES[b.arrays["x"].eltype][1]
             across = _scan_parts(b.template)[1]
-            return [Work(bytes=len(b.arrays) * e["n"] * e["rows"] * size, blocks=(e["n"] + 255) // 256 if across else e["rows"])]
+            moved = len(b.arrays) * e["n"] * e["rows"] * size
+            if across and e["rows"] >= 128 and (e["n"] + 255) // 256 < 8 * 148:
+                # in slabs (scratch from the executable's resources): the inputs are read twice, the slabs' totals pass
+                # between the two launches
+                inputs = (len(b.arrays) - 1) * e["n"] * e["rows"] * size
+                return [Work(bytes=moved, blocks=(e["n"] + 255) // 256, launches=2, reread=inputs, split=True)]
+            return [Work(bytes=moved, blocks=(e["n"] + 255) // 256 if across else e["rows"])]
         if b.template in LINEAR_SPELLINGS:
             e = b.extents
             size = ELTYPES[b.arrays["w"].eltype][1]
             moved = size * (e["m"] * e["k"] + e["k"] * e["n"] + e["m"] * e["n"])
-            return [Work(bytes=moved, flops=2.0 * e["m"] * e["n"] * e["k"])]
+            # the kernel's M is Tempest's n (the batch), its N Tempest's m; every tile row fetches w again and every
+            # tile column x, from L2 once the first has brought them in
+            form = lib.gemm_tile_form(lib.gemm_desc(e["n"], e["m"], e["k"]))
+            tile_m, tile_n = (256, 256) if form == 512 else (128, max(form, 128))
+            tiles_m, tiles_n = -(-e["n"] // tile_m), -(-e["m"] // tile_n)
+            reread = size * (e["m"] * e["k"] * (tiles_m - 1) + e["k"] * e["n"] * (tiles_n - 1))
+            return [Work(bytes=moved, flops=2.0 * e["m"] * e["n"] * e["k"], factor=b.arrays["w"].eltype,
+                         blocks=tiles_m * tiles_n, reread=reread, steps=-(-e["k"] // 64))]
         if b.template.startswith("attention"):
             e = b.extents
             flops = 4.0 * e["d"] * e["h"] * e["m"] * e["b"] * e["n"]     # both products (ext/cuDNNExt.jl:141-145)
             flops = flops / 2 if "causal" in b.template else flops
             moved = 2 * e["d"] * e["b"] * (2 * e["h"] * e["m"] + 2 * e["hk"] * e["n"])
+            q_tiles, k_tiles = -(-e["m"] // 128), -(-e["n"] // 128)
+            items = q_tiles * e["h"] * e["b"]
+            keys = 2 * e["d"] * e["b"] * 2 * e["hk"] * e["n"]            # K and V: fetched again by every query tile
+            seen = 0.5 if "causal" in b.template else 1.0
             if b.template.endswith("_pullback"):
-                return [Work(bytes=2 * moved, flops=2.5 * flops, launches=3)]
-            return [Work(bytes=moved, flops=flops)]
+                # the scores are formed again (one of the five products), dq passes through Float32 scratch in the
+                # one-kernel form, statistics + the rounding kernel are launches of their own
+                return [Work(bytes=2 * moved, flops=2.5 * flops, launches=3, recomputed=0.5 * flops, factor="BFloat16",
+                             blocks=k_tiles * e["hk"] * e["b"], passed=2 * 4 * e["d"] * e["h"] * e["m"] * e["b"],
+                             reread=int(seen * (k_tiles - 1) * 2 * e["d"] * e["b"] * 2 * e["h"] * e["m"]),
+                             steps=max(1, int(seen * q_tiles)))]
+            return [Work(bytes=moved, flops=flops, recomputed=0.5 * flops, factor="BFloat16", blocks=items,
+                         reread=int(seen * (q_tiles * e["h"] // e["hk"] - 1) * keys), steps=max(1, int(seen * k_tiles)))]
         size = ELTYPES[row_eltype(b)][1]
         n, rows = b.extents["n"], b.extents["rows"]
         op = _ROWOP[b.template]
         launches = 2 if (op == lib.LAYERNORM_BWD or n > 16384) else 1
-        return [Work(bytes=_STREAMS[op] * n * rows * size, blocks=rows, launches=launches)]
+        # what passes between the launches: the row blocks' partial weight gradients, or a long row's chunk states
+        passed = lib.rowop_workspace_bytes(op, n, rows, ELTYPES[row_eltype(b)][0]) if launches > 1 else 0
+        return [Work(bytes=_STREAMS[op] * n * rows * size, blocks=rows, launches=launches, passed=passed,
+                     split=n > 16384)]
 
     def build_alike(self, target: Target, bindings, resources: Optional[Resources] = None):
         """Several plain products of one shape as one launch (the reference's `build(::cuBLASProducts, target,

@@ -99,12 +99,22 @@ def test_product_and_attention_templates(I):
     assert lib.supports(t, b)
     (w,) = lib.estimate(t, b)
     assert w.flops == 2.0 * 4096 * 8192 * 1024
+    # the rest of the cost statement (src/Compiler/Implement/Implement.jl:30-82): 8192 x 4096 results in 256 x 256
+    # tiles by pairs of CTAs, each tile row fetching w again and each tile column x, 16 steps of 64 along k
+    assert w.factor == "BFloat16" and w.blocks == 32 * 16 and w.steps == 16 and not w.split
+    assert w.reread == 2 * (4096 * 1024 * 31 + 1024 * 8192 * 15)
     e = {"d": 128, "h": 32, "hk": 32, "m": 4096, "n": 4096, "b": 8}
     arrays = {n: I.dense_heads(None, "BFloat16", 128, 32, 4096, 8, i) for i, n in enumerate(("q", "k", "v", "o"))}
     a = I.Binding("attention_causal", e, arrays)
     assert lib.supports(t, a)
     (w,) = lib.estimate(t, a)
     assert abs(w.flops - 1.0995e12) / 1.0995e12 < 1e-3
+    # the scores are a fold recomputed inside the products: half the flops; 32 query tiles x 32 heads x 8, each
+    # sweeping on average half of the 32 key tiles
+    assert w.recomputed == 0.5 * w.flops and w.blocks == 32 * 32 * 8 and w.steps == 16 and w.factor == "BFloat16"
+    pull = I.Binding("attention_causal_pullback", e, arrays)
+    (wp,) = lib.estimate(t, pull)
+    assert wp.flops == 2.5 * w.flops and wp.passed == 2 * 4 * 128 * 32 * 4096 * 8 and wp.launches == 3
     # the forward builds without touching the device (addresses stand in for buffers); its description names the kernels
     at = lambda d: {n: I.dense_heads(4096 * (i + 1), "BFloat16", d, 32, 4096, 8, i) for i, n in enumerate(("q", "k", "v", "o"))}  # noqa: E731
     assert lib.build(t, I.Binding("attention_causal", e, at(128)))[1].endswith("tensor cores, two query tiles a block")
@@ -160,6 +170,11 @@ def test_scan_templates(I):
     assert lib.supports(t, b)
     (w,) = lib.estimate(t, b)
     assert w.bytes == 2 * n * rows * 4 and w.blocks == 4
+    # many rows: cut into slabs, two launches, the input read twice
+    tall = I.Binding("cumsum_dims2", {"n": 4096, "rows": 16384}, {"x": I.dense_columns(None, "Float32", 4096, 16384, 1),
+                                                                  "y": I.dense_columns(None, "Float32", 4096, 16384, 2)})
+    (w,) = lib.estimate(t, tall)
+    assert w.launches == 2 and w.reread == 4096 * 16384 * 4 and w.split
     assert not lib.supports(t, I.Binding("recurrence_dims1", {"n": n, "rows": rows}, arrays))   # the pairs' second array is missing
     assert not lib.supports(t, I.Binding("cumsum_dims3", {"n": n, "rows": rows}, arrays))
     launch = I.ScanLaunch(I.Binding("cummax_dims1_reverse", {"n": n, "rows": rows}, arrays))
